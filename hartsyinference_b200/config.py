@@ -1,0 +1,101 @@
+"""Typed flag registry.
+
+Every runtime switch is declared here once, with a type, a default and a doc string, and is read
+from the environment with the single prefix ``B200_``. Nothing else in the package calls
+``os.getenv`` for a behaviour switch. The reference scatters 171 ``HARTSY_*`` variables over its
+sources and reads most of them ad hoc or through a tri-state helper
+(src/HartsyInference.Core/Runtime/EnvSwitch.cs); the same tri-state semantics are kept
+(unset -> default, ``0/false/off/no`` -> off, anything else -> on).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Any, Callable
+
+_FALSE = {"0", "false", "off", "no", ""}
+
+
+@dataclass(frozen=True)
+class Flag:
+    name: str
+    type: type
+    default: Any
+    doc: str
+
+    @property
+    def env(self) -> str:
+        return "B200_" + self.name.upper()
+
+    def parse(self, raw: str) -> Any:
+        if self.type is bool:
+            return raw.strip().lower() not in _FALSE
+        return self.type(raw)
+
+
+_REGISTRY: dict[str, Flag] = {}
+_OVERRIDES: dict[str, Any] = {}
+
+
+def declare(name: str, type_: type, default: Any, doc: str) -> Flag:
+    if name in _REGISTRY:
+        raise ValueError(f"flag {name} declared twice")
+    f = Flag(name, type_, default, doc)
+    _REGISTRY[name] = f
+    return f
+
+
+def get(name: str) -> Any:
+    f = _REGISTRY[name]
+    if name in _OVERRIDES:
+        return _OVERRIDES[name]
+    raw = os.environ.get(f.env)
+    if raw is None:
+        return f.default
+    try:
+        return f.parse(raw)
+    except ValueError:
+        return f.default
+
+
+def set_override(name: str, value: Any) -> None:
+    """Programmatic override (tests, CLI flags); ``None`` removes it."""
+    if name not in _REGISTRY:
+        raise KeyError(name)
+    if value is None:
+        _OVERRIDES.pop(name, None)
+    else:
+        _OVERRIDES[name] = value
+
+
+def all_flags() -> list[Flag]:
+    return sorted(_REGISTRY.values(), key=lambda f: f.name)
+
+
+def describe() -> str:
+    """Human-readable table used by ``--help`` and the docs."""
+    rows = [f"{f.env:<34} {f.type.__name__:<6} default={f.default!r:<12} {f.doc}" for f in all_flags()]
+    return "\n".join(rows)
+
+
+# --- declarations -------------------------------------------------------------------------------
+declare("log_level", str, "info", "minimum log level: trace, debug, info, warn, error")
+declare("profile", bool, False, "accumulate per-op device time (CUDA events) and print a table at exit")
+declare("profile_sync", bool, False, "synchronise after every profiled op so host ranges equal device time")
+declare("nvtx", bool, False, "emit NVTX ranges around ops and engine phases")
+declare("kv_page_size", int, 16, "tokens per KV page")
+declare("kv_pool_bytes", int, 0, "KV pool budget in bytes; 0 = size from free device memory")
+declare("kv_dtype", str, "bf16", "KV cache dtype: bf16")
+declare("cuda_graphs", bool, True, "capture the decode step in CUDA graphs")
+declare("max_batch", int, 256, "largest decode batch the scheduler forms")
+declare("prefill_chunk", int, 8192, "tokens per prefill chunk")
+declare("fused_comm", bool, True, "use the fused compute+collective kernels; off = NCCL baseline")
+declare("nvls", bool, True, "allow multimem (in-switch) reductions when the symmetric heap has a multicast mapping")
+declare("wait_budget_ms", int, 2000, "budget of every bounded device-side wait")
+declare("p2p_disable", bool, False, "never map peer memory; collectives fall back to NCCL")
+declare("fp8_linears", bool, True, "quantise eligible linears to 128x128 block-scaled e4m3 at load")
+declare("low_vram", bool, False, "stream transformer blocks from pinned host memory instead of keeping weights resident")
+declare("model_cache_dir", str, "~/.hartsyinference/models", "where resolved checkpoints are cached")
+declare("same_gpu_concurrent", bool, False, "allow two requests to share one device slot")
+declare("assert_ambient", bool, False, "debug: verify every op runs on the device its tensors live on")
+declare("step_cache_threshold", float, 0.0, "first-block-cache relative-L1 threshold; 0 disables")

@@ -1,0 +1,793 @@
+// Bandwidth-bound fused row kernels: (residual add +) RMSNorm, LayerNorm + AdaLN modulation,
+// SwiGLU / GEGLU, fp8 1x128 block quantisation (also fused as an optional second output of the
+// norm and activation kernels), QK-norm + RoPE + paged-KV write, embedding gather, argmax,
+// repetition penalty, CFG + Euler step, and the weight initialisers used by synthetic benchmarks.
+//
+// They replace the reference's scalar decode-step kernels (src/HartsyInference.Cuda/Kernels/lm/
+// lm_f32.cu: lm_add_rmsnorm_f32:470, lm_qkv_rope_scatter_f32:393, lm_qknorm_rope_scatter_f32:1304,
+// lm_glu_act_f32:357, lm_argmax_lastdim_f32:214, lm_embed_gather_decode_f32:1461,
+// lm_repetition_penalty_f32:1500), its DiT row kernels (Kernels/dit/dit_f32.cu:
+// dit_layernorm_modulate_f32:1323, dit_gated_residual_lastdim_f32:85, dit_cfg_euler_f32:182,
+// dit_fp8emit.cu) and its two-pass per-tensor fp8 quantiser (Kernels/dequant/fp8_quant.cu).
+// All rows are processed with 16-byte loads, one CTA per row (or several rows per CTA for short
+// rows), fp32 math, bf16 storage.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr float kFp8Max = 448.f;
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? red[l] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+struct NormParams {
+  const __nv_bfloat16* x;         // [rows][dim]
+  const __nv_bfloat16* residual;  // optional [rows][dim]: h = x + residual
+  __nv_bfloat16* residual_out;    // optional: receives h
+  const __nv_bfloat16* weight;    // optional [dim]
+  const __nv_bfloat16* bias;      // optional [dim] (LayerNorm affine)
+  const __nv_bfloat16* shift;     // optional AdaLN shift [batch][mod_stride]
+  const __nv_bfloat16* scale;     // optional AdaLN scale [batch][mod_stride]  -> y * (1 + scale) + shift
+  __nv_bfloat16* out;             // optional bf16 output
+  uint8_t* out_fp8;               // optional e4m3 output [rows][dim]
+  float* out_scale;               // [dim/128][rows] fp32, k-block-major
+  int rows, dim, rows_per_batch, mod_stride;
+  float eps;
+  int layernorm;                  // 0 = RMSNorm, 1 = LayerNorm (mean-centred)
+  int weight_plus_one;            // Gemma-style (1 + w)
+};
+
+// dim % 8 == 0; blockDim.x * 8 >= dim handled by a strided loop keeping the row in registers for
+// dim <= 8 * 1024 (blockDim 1024) .. generic fallback re-reads the row.
+template <int kMaxVec>
+__global__ void __launch_bounds__(1024) norm_kernel(const NormParams p) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int nvec = p.dim >> 3;
+  const __nv_bfloat16* xr = p.x + static_cast<long long>(row) * p.dim;
+  float v[kMaxVec][8];
+  float sum = 0.f, sumsq = 0.f;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int vi = threadIdx.x + it * blockDim.x;
+    if (vi < nvec) {
+      uint4 raw = *reinterpret_cast<const uint4*>(xr + vi * 8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(h[i]);
+        v[it][2 * i] = f.x;
+        v[it][2 * i + 1] = f.y;
+      }
+      if (p.residual) {
+        uint4 rr = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(row) * p.dim + vi * 8);
+        const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __bfloat1622float2(rh[i]);
+          v[it][2 * i] += f.x;
+          v[it][2 * i + 1] += f.y;
+        }
+      }
+      if (p.residual_out) {
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ow[i] = pack_bf16x2(v[it][2 * i], v[it][2 * i + 1]);
+        *reinterpret_cast<uint4*>(p.residual_out + static_cast<long long>(row) * p.dim + vi * 8) = o;
+        // the norm must see the value that was stored (bf16-rounded), as the unfused path does
+        const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __bfloat1622float2(oh[i]);
+          v[it][2 * i] = f.x;
+          v[it][2 * i + 1] = f.y;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sum += v[it][i];
+        sumsq += v[it][i] * v[it][i];
+      }
+    }
+  }
+  float mean = 0.f;
+  if (p.layernorm) {
+    mean = block_sum(sum, red) / p.dim;
+    // second pass over registers for a numerically stable variance
+    float var = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it) {
+      const int vi = threadIdx.x + it * blockDim.x;
+      if (vi < nvec) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = v[it][i] - mean;
+          var += d * d;
+        }
+      }
+    }
+    sumsq = var;
+  }
+  const float total = block_sum(sumsq, red);
+  const float rstd = rsqrtf(total / p.dim + p.eps);
+  const int batch = p.rows_per_batch > 0 ? row / p.rows_per_batch : 0;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int vi = threadIdx.x + it * blockDim.x;
+    const bool active = vi < nvec;
+    float y[8];
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = vi * 8 + i;
+        float t = (v[it][i] - mean) * rstd;
+        if (p.weight) {
+          const float w = __bfloat162float(p.weight[c]);
+          t *= p.weight_plus_one ? (1.f + w) : w;
+        }
+        if (p.bias) t += __bfloat162float(p.bias[c]);
+        if (p.scale) t *= 1.f + __bfloat162float(p.scale[static_cast<long long>(batch) * p.mod_stride + c]);
+        if (p.shift) t += __bfloat162float(p.shift[static_cast<long long>(batch) * p.mod_stride + c]);
+        y[i] = t;
+      }
+      if (p.out) {
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ow[i] = pack_bf16x2(y[2 * i], y[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p.out + static_cast<long long>(row) * p.dim + vi * 8) = o;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = 0.f;
+    }
+    if (p.out_fp8) {
+      // all 32 lanes take part in the half-warp shuffles; inactive lanes carry zeros and do not
+      // store. dim % 128 == 0 is required for the fp8 output, so a 16-lane group is all-active
+      // or all-inactive.
+      if (active) {
+        // fp8 consumers see the bf16-rounded activations, exactly like the unfused path
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = __bfloat162float(__float2bfloat16(y[i]));
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(y[i]));
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      if (active) {
+        const float sc = fmaxf(amax, 1e-12f) / kFp8Max;
+        const float inv = 1.f / sc;
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) lo |= static_cast<uint32_t>(to_e4m3(y[i] * inv)) << (8 * i);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) hi |= static_cast<uint32_t>(to_e4m3(y[4 + i] * inv)) << (8 * i);
+        *reinterpret_cast<uint2*>(p.out_fp8 + static_cast<long long>(row) * p.dim + vi * 8) =
+            make_uint2(lo, hi);
+        if ((vi & 15) == 0) p.out_scale[static_cast<long long>(vi >> 4) * p.rows + row] = sc;
+      }
+    }
+  }
+}
+
+// fp8 1x128 quantisation of a bf16 matrix [rows][dim] (dim % 128 == 0) with row pitch ld.
+__global__ void quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out,
+                                 float* __restrict__ scales, int rows, int dim, long long ld) {
+  const int groups = dim >> 7;
+  const long long total = static_cast<long long>(rows) * groups * 16;   // one thread per 8 values
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  // total is a multiple of 16, blockDim is a multiple of 32: a 16-lane group is uniform
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+       i < ((total + 31) / 32) * 32; i += stride) {
+    const bool active = i < total;
+    const long long ii = active ? i : total - 1;
+    const int sub = static_cast<int>(ii & 15);
+    const long long g = ii >> 4;
+    const int row = static_cast<int>(g / groups), grp = static_cast<int>(g % groups);
+    uint4 raw = *reinterpret_cast<const uint4*>(x + row * ld + grp * 128 + sub * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 f = __bfloat1622float2(h[k]);
+      v[2 * k] = f.x;
+      v[2 * k + 1] = f.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (active) {
+      const float sc = fmaxf(amax, 1e-12f) / kFp8Max;
+      const float inv = 1.f / sc;
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) lo |= static_cast<uint32_t>(to_e4m3(v[k] * inv)) << (8 * k);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) hi |= static_cast<uint32_t>(to_e4m3(v[4 + k] * inv)) << (8 * k);
+      *reinterpret_cast<uint2*>(out + static_cast<long long>(row) * dim + grp * 128 + sub * 8) =
+          make_uint2(lo, hi);
+      if (sub == 0) scales[static_cast<long long>(grp) * rows + row] = sc;
+    }
+  }
+}
+
+// Weight quantisation to e4m3 with one scale per 128 x 128 block. w [n][k] bf16 -> out [n][k] u8,
+// scales [k/128][ceil(n/128)] fp32. One CTA (256 threads) per block.
+__global__ void quant_fp8_weight_kernel(const __nv_bfloat16* __restrict__ w,
+                                        uint8_t* __restrict__ out, float* __restrict__ scales,
+                                        int n, int k) {
+  __shared__ float red[32];
+  const int nb = blockIdx.x, kb = blockIdx.y;
+  const int nblocks = gridDim.x;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < 128 * 16; i += blockDim.x) {
+    const int r = nb * 128 + (i >> 4), c = kb * 128 + (i & 15) * 8;
+    if (r < n) {
+      uint4 raw = *reinterpret_cast<const uint4*>(w + static_cast<long long>(r) * k + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float2 f = __bfloat1622float2(h[q]);
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int i = 0; i < (blockDim.x >> 5); ++i) amax = fmaxf(amax, red[i]);
+  const float sc = fmaxf(amax, 1e-12f) / kFp8Max;
+  const float inv = 1.f / sc;
+  if (threadIdx.x == 0) scales[static_cast<long long>(kb) * nblocks + nb] = sc;
+  for (int i = threadIdx.x; i < 128 * 16; i += blockDim.x) {
+    const int r = nb * 128 + (i >> 4), c = kb * 128 + (i & 15) * 8;
+    if (r < n) {
+      uint4 raw = *reinterpret_cast<const uint4*>(w + static_cast<long long>(r) * k + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        float2 f = __bfloat1622float2(h[q]);
+        lo |= static_cast<uint32_t>(to_e4m3(f.x * inv)) << (16 * q);
+        lo |= static_cast<uint32_t>(to_e4m3(f.y * inv)) << (16 * q + 8);
+      }
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        float2 f = __bfloat1622float2(h[2 + q]);
+        hi |= static_cast<uint32_t>(to_e4m3(f.x * inv)) << (16 * q);
+        hi |= static_cast<uint32_t>(to_e4m3(f.y * inv)) << (16 * q + 8);
+      }
+      *reinterpret_cast<uint2*>(out + static_cast<long long>(r) * k + c) = make_uint2(lo, hi);
+    }
+  }
+}
+
+// Gated activation: out[r][c] = act(in[r][c]) * in[r][F + c] for in [rows][2F] (gate first, then
+// up), act: 0 = SiLU, 1 = GELU-tanh. Optional fp8 1x128 output (F % 128 == 0).
+__global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                           uint8_t* __restrict__ out_fp8, float* __restrict__ out_scale, int rows,
+                           int f, int act) {
+  const int nvec = f >> 3;
+  const long long total = static_cast<long long>(rows) * nvec;
+  const long long padded = ((total + 31) / 32) * 32;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < padded;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const bool active = i < total;
+    const long long ii = active ? i : total - 1;
+    const int row = static_cast<int>(ii / nvec), vi = static_cast<int>(ii % nvec);
+    const __nv_bfloat16* g = in + static_cast<long long>(row) * 2 * f + vi * 8;
+    uint4 graw = *reinterpret_cast<const uint4*>(g);
+    uint4 uraw = *reinterpret_cast<const uint4*>(g + f);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    float y[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = __bfloat1622float2(gh[k]), b = __bfloat1622float2(uh[k]);
+      y[2 * k] = (act == 0 ? silu(a.x) : gelu_tanh(a.x)) * b.x;
+      y[2 * k + 1] = (act == 0 ? silu(a.y) : gelu_tanh(a.y)) * b.y;
+    }
+    if (out && active) {
+      uint4 o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) ow[k] = pack_bf16x2(y[2 * k], y[2 * k + 1]);
+      *reinterpret_cast<uint4*>(out + static_cast<long long>(row) * f + vi * 8) = o;
+    }
+    if (out_fp8) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) y[k] = __bfloat162float(__float2bfloat16(y[k]));
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(y[k]));
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      if (active) {
+        const float sc = fmaxf(amax, 1e-12f) / kFp8Max;
+        const float inv = 1.f / sc;
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) lo |= static_cast<uint32_t>(to_e4m3(y[k] * inv)) << (8 * k);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) hi |= static_cast<uint32_t>(to_e4m3(y[4 + k] * inv)) << (8 * k);
+        *reinterpret_cast<uint2*>(out_fp8 + static_cast<long long>(row) * f + vi * 8) =
+            make_uint2(lo, hi);
+        if ((vi & 15) == 0) out_scale[static_cast<long long>(vi >> 4) * rows + row] = sc;
+      }
+    }
+  }
+}
+
+// QK-norm (optional) + rotary embedding + paged KV write for a packed qkv activation.
+//   qkv  [T][(hq + 2*hkv) * d] bf16 (q heads, then k heads, then v heads)
+//   q_out [T][hq][d] bf16 (rotated), k/v written to cache pages
+//   cache layout [num_pages][hkv][page][d]; slot_mapping[t] = page_index * page + offset
+//   rope: style 0 = split-half (pairs (i, i + rot/2)), 1 = interleaved (pairs (2i, 2i+1));
+//   rotary dims = rot (<= d); angle = pos * theta^(-2i/rot) * freq_scale[i] (optional table)
+// One warp per (token, head).
+struct RopeParams {
+  const __nv_bfloat16* qkv;
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  __nv_bfloat16* k_out;   // optional contiguous [T][hkv][d] outputs (prefill attention reads these)
+  __nv_bfloat16* v_out;
+  const int* positions;
+  const long long* slot_mapping;  // may be null (no cache write)
+  const __nv_bfloat16* q_norm_w;  // optional [d]
+  const __nv_bfloat16* k_norm_w;
+  const float* inv_freq;          // optional [rot/2] precomputed (scaled) inverse frequencies
+  int tokens, hq, hkv, d, rot, style, page;
+  float theta, eps;
+};
+
+__global__ void rope_kv_kernel(const RopeParams p) {
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int heads = p.hq + 2 * p.hkv;
+  if (warp_global >= p.tokens * heads) return;
+  const int t = warp_global / heads, h = warp_global % heads;
+  const __nv_bfloat16* src = p.qkv + (static_cast<long long>(t) * heads + h) * p.d;
+  const int kind = h < p.hq ? 0 : (h < p.hq + p.hkv ? 1 : 2);
+  // each lane owns elements lane, lane+32, ... (d <= 256)
+  float v[8];
+  const int per = (p.d + 31) / 32;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = lane + 32 * i;
+    v[i] = (i < per && c < p.d) ? __bfloat162float(src[c]) : 0.f;
+  }
+  const __nv_bfloat16* nw = kind == 0 ? p.q_norm_w : (kind == 1 ? p.k_norm_w : nullptr);
+  if (nw) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / p.d + p.eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;
+      if (i < per && c < p.d) v[i] = v[i] * rstd * __bfloat162float(nw[c]);
+    }
+  }
+  __nv_bfloat16* dst;
+  __nv_bfloat16* dst2 = nullptr;
+  if (kind == 0) {
+    dst = p.q_out + (static_cast<long long>(t) * p.hq + h) * p.d;
+  } else {
+    const int hk = kind == 1 ? h - p.hq : h - p.hq - p.hkv;
+    __nv_bfloat16* cache = kind == 1 ? p.k_cache : p.v_cache;
+    __nv_bfloat16* lin = kind == 1 ? p.k_out : p.v_out;
+    dst = nullptr;
+    if (cache && p.slot_mapping) {
+      const long long slot = p.slot_mapping[t];
+      if (slot >= 0) {
+        const long long pg = slot / p.page, off = slot % p.page;
+        dst = cache + ((pg * p.hkv + hk) * p.page + off) * p.d;
+      }
+    }
+    if (lin) dst2 = lin + (static_cast<long long>(t) * p.hkv + hk) * p.d;
+  }
+  if (kind != 2 && p.rot > 0) {
+    // The partner element of a rotary pair is fetched from its owner lane with shuffles; every
+    // lane executes every shuffle. Partner of element c: split-half -> c +- rot/2,
+    // interleaved -> c ^ 1.
+    const float pos = static_cast<float>(p.positions[t]);
+    const int half = p.rot >> 1;
+    float outv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;
+      const bool in_rot = (i < per) && (c < p.rot);
+      int partner = c, pair_idx = 0;
+      bool first = true;
+      if (p.style == 0) {
+        first = c < half;
+        pair_idx = first ? c : c - half;
+        partner = first ? c + half : c - half;
+      } else {
+        first = (c & 1) == 0;
+        pair_idx = c >> 1;
+        partner = c ^ 1;
+      }
+      // partner slot may differ from i (split-half with half % 32 != 0 is not supported when
+      // half < 32; d = 64/128/256 with rot = d or rot = d/2 all satisfy half % 32 == 0 or the
+      // interleaved style keeps the partner in the same slot)
+      float pv = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float cand = __shfl_sync(0xffffffffu, v[j], partner & 31);
+        if (j == (partner >> 5)) pv = cand;
+      }
+      if (in_rot) {
+        const float inv = p.inv_freq ? p.inv_freq[pair_idx]
+                                     : __powf(p.theta, -2.f * pair_idx / static_cast<float>(p.rot));
+        float sn, cs;
+        sincosf(pos * inv, &sn, &cs);
+        outv[i] = first ? (v[i] * cs - pv * sn) : (v[i] * cs + pv * sn);
+      } else {
+        outv[i] = v[i];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = outv[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = lane + 32 * i;
+    if (i < per && c < p.d) {
+      const __nv_bfloat16 b = __float2bfloat16(v[i]);
+      if (dst) dst[c] = b;
+      if (dst2) dst2[c] = b;
+    }
+  }
+}
+
+__global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                 __nv_bfloat16* __restrict__ out, int tokens, int dim, int vocab,
+                                 float scale) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<long long>(id) * dim);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(t) * dim);
+  for (int i = threadIdx.x; i < (dim >> 3); i += blockDim.x) {
+    uint4 raw = src[i];
+    if (scale != 1.f) {
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 f = __bfloat1622float2(h[k]);
+        h[k] = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+      }
+    }
+    dst[i] = raw;
+  }
+}
+
+// argmax over the last dim of bf16 / fp32 logits [rows][vocab]; ties -> lowest index.
+template <typename T>
+__global__ void argmax_kernel(const T* __restrict__ logits, int* __restrict__ out, int vocab,
+                              long long ld) {
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  const T* row = logits + blockIdx.x * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = static_cast<float>(row[i]);
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sval[threadIdx.x >> 5] = best; sidx[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = blockDim.x >> 5;
+    best = threadIdx.x < nw ? sval[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < nw ? sidx[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = bi;
+  }
+}
+
+// logits[b][tok] /= penalty when > 0 else *= penalty, for every token in the row's history.
+__global__ void repetition_penalty_kernel(float* __restrict__ logits, const int* __restrict__ history,
+                                          const int* __restrict__ hist_len, int max_hist, int vocab,
+                                          const float* __restrict__ penalty) {
+  const int b = blockIdx.x;
+  const float pen = penalty[b];
+  if (pen == 1.f) return;
+  const int n = hist_len[b];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int tok = history[static_cast<long long>(b) * max_hist + i];
+    if (tok >= 0 && tok < vocab) {
+      // duplicates in the history would race; resolve by letting only the first occurrence act
+      bool first = true;
+      for (int j = 0; j < i; ++j)
+        if (history[static_cast<long long>(b) * max_hist + j] == tok) { first = false; break; }
+      if (first) {
+        float* l = logits + static_cast<long long>(b) * vocab + tok;
+        *l = *l > 0.f ? *l / pen : *l * pen;
+      }
+    }
+  }
+}
+
+// Classifier-free-guidance combine fused with the Euler / flow-match step:
+//   v = g * cond + (1 - g) * uncond ; z += v * dt     (uncond may be null: v = cond)
+__global__ void cfg_euler_kernel(float* __restrict__ z, const __nv_bfloat16* __restrict__ cond,
+                                 const __nv_bfloat16* __restrict__ uncond, long long n, float g,
+                                 float dt) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float c = __bfloat162float(cond[i]);
+    const float v = uncond ? g * c + (1.f - g) * __bfloat162float(uncond[i]) : c;
+    z[i] += v * dt;
+  }
+}
+
+// out = x + gate[batch][c] * y   (gated residual of DiT blocks), bf16
+__global__ void gated_residual_kernel(const __nv_bfloat16* __restrict__ x,
+                                      const __nv_bfloat16* __restrict__ y,
+                                      const __nv_bfloat16* __restrict__ gate,
+                                      __nv_bfloat16* __restrict__ out, int rows, int dim,
+                                      int rows_per_batch, int mod_stride) {
+  const int nvec = dim >> 3;
+  const long long total = static_cast<long long>(rows) * nvec;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / nvec), vi = static_cast<int>(i % nvec);
+    const int batch = rows_per_batch > 0 ? row / rows_per_batch : 0;
+    uint4 xr = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * dim + vi * 8);
+    uint4 yr = *reinterpret_cast<const uint4*>(y + static_cast<long long>(row) * dim + vi * 8);
+    uint4 gr = *reinterpret_cast<const uint4*>(gate + static_cast<long long>(batch) * mod_stride + vi * 8);
+    const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xr);
+    const __nv_bfloat162* yh = reinterpret_cast<const __nv_bfloat162*>(&yr);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gr);
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = __bfloat1622float2(xh[k]), b = __bfloat1622float2(yh[k]), g = __bfloat1622float2(gh[k]);
+      ow[k] = pack_bf16x2(a.x + g.x * b.x, a.y + g.y * b.y);
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<long long>(row) * dim + vi * 8) = o;
+  }
+}
+
+// Deterministic pseudo-random fill (hash of the element index) for synthetic weights: bf16
+// N(0, std) approximated by a sum of uniforms, or raw e4m3 bytes with |value| <= 448 * amp.
+__device__ __forceinline__ uint32_t hash32(uint64_t x) {
+  x ^= x >> 33; x *= 0xff51afd7ed558ccdull; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ull; x ^= x >> 33;
+  return static_cast<uint32_t>(x);
+}
+__global__ void fill_random_bf16_kernel(__nv_bfloat16* out, long long n, uint64_t seed, float std) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t a = hash32(seed * 0x9e3779b97f4a7c15ull + 2 * i);
+    const uint32_t b = hash32(seed * 0x9e3779b97f4a7c15ull + 2 * i + 1);
+    // sum of four 16-bit uniforms: variance 4/12, mean 2 -> scale to unit variance
+    const float u = ((a & 0xffff) + (a >> 16) + (b & 0xffff) + (b >> 16)) * (1.f / 65536.f) - 2.f;
+    out[i] = __float2bfloat16(u * 1.7320508f * std);
+  }
+}
+__global__ void fill_random_fp8_kernel(uint8_t* out, long long n, uint64_t seed) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t a = hash32(seed * 0x9e3779b97f4a7c15ull + 2 * i);
+    const uint32_t b = hash32(seed * 0x9e3779b97f4a7c15ull + 2 * i + 1);
+    const float u = ((a & 0xffff) + (a >> 16) + (b & 0xffff) + (b >> 16)) * (1.f / 65536.f) - 2.f;
+    // unit-variance value scaled so that ~4 sigma maps to the e4m3 maximum
+    out[i] = to_e4m3(u * 1.7320508f * 112.f);
+  }
+}
+
+inline int grid_for(long long n, int block, int cap_mult = 8) {
+  long long g = (n + block - 1) / block;
+  const long long cap = 148ll * cap_mult;
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+#define CHECK_LAUNCH()                                            \
+  do {                                                            \
+    cudaError_t e__ = cudaGetLastError();                         \
+    if (e__ != cudaSuccess) return -static_cast<int>(e__) - 300;  \
+  } while (0)
+
+// (residual +) RMSNorm / LayerNorm with optional affine, AdaLN modulation, bf16 and/or fp8 output.
+B200_API int b200_norm(const void* x, const void* residual, void* residual_out, const void* weight,
+                       const void* bias, const void* shift, const void* scale, void* out,
+                       void* out_fp8, float* out_scale, int rows, int dim, int rows_per_batch,
+                       int mod_stride, float eps, int layernorm, int weight_plus_one,
+                       cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dim % 8 != 0 || dim > 16384) return -2;
+  if (out_fp8 && dim % 128 != 0) return -3;
+  NormParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.residual_out = static_cast<__nv_bfloat16*>(residual_out);
+  p.weight = static_cast<const __nv_bfloat16*>(weight);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.shift = static_cast<const __nv_bfloat16*>(shift);
+  p.scale = static_cast<const __nv_bfloat16*>(scale);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_fp8 = static_cast<uint8_t*>(out_fp8);
+  p.out_scale = out_scale;
+  p.rows = rows; p.dim = dim; p.rows_per_batch = rows_per_batch; p.mod_stride = mod_stride;
+  p.eps = eps; p.layernorm = layernorm; p.weight_plus_one = weight_plus_one;
+  const int nvec = dim / 8;
+  // threads: multiple of 32 covering the row with at most 2 vectors per thread
+  int threads = ((nvec + 31) / 32) * 32;
+  if (threads <= 1024) {
+    norm_kernel<1><<<rows, threads < 32 ? 32 : threads, 0, stream>>>(p);
+  } else {
+    threads = (((nvec + 1) / 2 + 31) / 32) * 32;
+    norm_kernel<2><<<rows, threads, 0, stream>>>(p);
+  }
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_quant_fp8(const void* x, void* out, float* scales, int rows, int dim,
+                            long long ld, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dim % 128 != 0 || ld % 8 != 0) return -2;
+  const long long n = static_cast<long long>(rows) * (dim / 8);
+  quant_fp8_kernel<<<grid_for(n, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                         static_cast<uint8_t*>(out), scales, rows,
+                                                         dim, ld);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_quant_fp8_weight(const void* w, void* out, float* scales, int n, int k,
+                                   cudaStream_t stream) {
+  if (k % 128 != 0) return -2;
+  dim3 grid((n + 127) / 128, k / 128);
+  quant_fp8_weight_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w),
+                                                    static_cast<uint8_t*>(out), scales, n, k);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_glu(const void* in, void* out, void* out_fp8, float* out_scale, int rows, int f,
+                      int act, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (f % 8 != 0 || (out_fp8 && f % 128 != 0)) return -2;
+  const long long n = static_cast<long long>(rows) * (f / 8);
+  glu_kernel<<<grid_for(n, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in),
+                                                   static_cast<__nv_bfloat16*>(out),
+                                                   static_cast<uint8_t*>(out_fp8), out_scale, rows,
+                                                   f, act);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_cache, void* k_out,
+                          void* v_out, const int* positions, const long long* slot_mapping,
+                          const void* q_norm_w, const void* k_norm_w, const float* inv_freq,
+                          int tokens, int hq, int hkv, int d, int rot, int style, int page,
+                          float theta, float eps, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (d > 256 || rot > d || (rot & 1)) return -2;
+  if (style == 0 && rot > 0 && ((rot / 2) % 32) != 0) return -3;
+  RopeParams p{};
+  p.qkv = static_cast<const __nv_bfloat16*>(qkv);
+  p.q_out = static_cast<__nv_bfloat16*>(q_out);
+  p.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+  p.k_out = static_cast<__nv_bfloat16*>(k_out);
+  p.v_out = static_cast<__nv_bfloat16*>(v_out);
+  p.positions = positions;
+  p.slot_mapping = slot_mapping;
+  p.q_norm_w = static_cast<const __nv_bfloat16*>(q_norm_w);
+  p.k_norm_w = static_cast<const __nv_bfloat16*>(k_norm_w);
+  p.inv_freq = inv_freq;
+  p.tokens = tokens; p.hq = hq; p.hkv = hkv; p.d = d; p.rot = rot; p.style = style; p.page = page;
+  p.theta = theta; p.eps = eps;
+  const long long warps = static_cast<long long>(tokens) * (hq + 2 * hkv);
+  const int block = 256;
+  const long long blocks = (warps * 32 + block - 1) / block;
+  rope_kv_kernel<<<static_cast<int>(blocks), block, 0, stream>>>(p);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_embedding(const int* ids, const void* table, void* out, int tokens, int dim,
+                            int vocab, float scale, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dim % 8 != 0) return -2;
+  embedding_kernel<<<tokens, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table),
+                                               static_cast<__nv_bfloat16*>(out), tokens, dim, vocab,
+                                               scale);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_argmax(const void* logits, int* out, int rows, int vocab, long long ld,
+                         int is_fp32, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (is_fp32)
+    argmax_kernel<float><<<rows, 1024, 0, stream>>>(static_cast<const float*>(logits), out, vocab, ld);
+  else
+    argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), out, vocab, ld);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_repetition_penalty(float* logits, const int* history, const int* hist_len,
+                                     int max_hist, int rows, int vocab, const float* penalty,
+                                     cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  repetition_penalty_kernel<<<rows, 256, 0, stream>>>(logits, history, hist_len, max_hist, vocab,
+                                                      penalty);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_cfg_euler(float* z, const void* cond, const void* uncond, long long n, float g,
+                            float dt, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  cfg_euler_kernel<<<grid_for(n, 256), 256, 0, stream>>>(z, static_cast<const __nv_bfloat16*>(cond),
+                                                         static_cast<const __nv_bfloat16*>(uncond),
+                                                         n, g, dt);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_gated_residual(const void* x, const void* y, const void* gate, void* out,
+                                 int rows, int dim, int rows_per_batch, int mod_stride,
+                                 cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dim % 8 != 0 || mod_stride % 8 != 0) return -2;
+  const long long n = static_cast<long long>(rows) * (dim / 8);
+  gated_residual_kernel<<<grid_for(n, 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(y),
+      static_cast<const __nv_bfloat16*>(gate), static_cast<__nv_bfloat16*>(out), rows, dim,
+      rows_per_batch, mod_stride);
+  CHECK_LAUNCH();
+  return 0;
+}
+
+B200_API int b200_fill_random(void* out, long long n, unsigned long long seed, float std,
+                              int is_fp8, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (is_fp8)
+    fill_random_fp8_kernel<<<grid_for(n, 256, 16), 256, 0, stream>>>(static_cast<uint8_t*>(out), n, seed);
+  else
+    fill_random_bf16_kernel<<<grid_for(n, 256, 16), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(out), n, seed, std);
+  CHECK_LAUNCH();
+  return 0;
+}

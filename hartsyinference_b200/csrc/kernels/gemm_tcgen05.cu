@@ -1,0 +1,603 @@
+// Dense GEMM on the 5th-generation tensor cores: C = A * B^T with both operands K-major
+// ("nn.Linear" orientation), bf16 or fp8-e4m3 inputs with 128-wide block scales, fp32
+// accumulation in TMEM.
+//
+// Replaces the reference's cuBLASLt / cublasGemmEx ladder (src/HartsyInference.Cuda/
+// CudaBackend.cs:1769-2425, LtGemmExecutor.cs, Fp8GemmExecutor.cs:110-111 which is per-tensor
+// scaled) and its mma.sync kernels (Kernels/dequant/int8_mma_gemm.cu, Ptx/hgemm_mma_sm80.ptx).
+//
+// Structure of one CTA (192 threads, persistent over a static list of work items):
+//   warp 0      TMA producer: one thread issues cp.async.bulk.tensor loads of a 128 x 128-byte A
+//               tile and a BN x 128-byte B tile per stage into 128B-swizzled shared memory
+//   warp 1      allocates TMEM; one thread issues tcgen05.mma (M = 128, N = BN, K = 32 bytes) and
+//               commits to the stage's "empty" barrier and to the accumulator's "full" barrier
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator quarter that belongs to the warp, scale /
+//               bias / activation / gate / residual, store
+// A "work item" is (tile of 128 A rows, tile of BN B rows, K split). The caller decides which
+// operand is the activation: for small token counts the weight matrix is passed as A so that its
+// rows fill the 128-row MMA dimension and the tokens become the narrow N dimension
+// (`swap_out = 1` then stores C transposed).
+//
+// fp8 block scaling (128 x 128 weight blocks, 1 x 128 activation groups): every 128-deep K block
+// is accumulated into its own TMEM buffer (two buffers alternate); the epilogue warps pull the
+// block out, multiply by scale_a(row, kb) * scale_b(col, kb) and add into fp32 registers while
+// the tensor core already works on the next block.
+#include "common.cuh"
+
+namespace b200 {
+
+struct GemmParams {
+  int rows_a;          // rows of the A operand (tiled by 128)
+  int rows_b;          // rows of the B operand (tiled by BN)
+  int k;               // reduction length in elements
+  int splits;          // K splits (>= 1); > 1 writes fp32 partials to `out`
+  int kblocks_per_split;
+  int stages;
+  int swap_out;        // 0: C[a_row][b_row]; 1: C[b_row][a_row]
+  int out_fp32;        // 1: write fp32 (split-K partials or fp32 result), no epilogue
+  long long ldc;       // leading dimension of C in elements
+  long long split_stride;  // elements between split partials
+  void* out;
+  const __nv_bfloat16* bias;      // per output feature (column of C), may be null
+  const __nv_bfloat16* gate;      // per output feature multiplicative gate, may be null
+  const __nv_bfloat16* residual;  // same layout as C, may be null
+  int act;                        // 0 none, 1 gelu-tanh, 2 silu
+  // fp8 block scales, k-block-major: scale(row, kb) = s[kb * ld + row / gran]
+  const float* scale_a;
+  const float* scale_b;
+  int sa_gran, sa_ld, sb_gran, sb_ld;
+  DeviceStatus* status;
+};
+
+constexpr int kTileA = 128;
+constexpr int kStageBytesA = kTileA * 128;
+constexpr int kGemmThreads = 192;
+
+struct alignas(8) GemmBarriers {
+  uint64_t full[12];
+  uint64_t empty[12];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+__device__ __forceinline__ float apply_epilogue(const GemmParams& p, float v, long long row,
+                                                long long col) {
+  // row = token index, col = output feature, both already bounds-checked
+  if (p.bias) v += __bfloat162float(p.bias[col]);
+  if (p.act == 1) v = gelu_tanh(v);
+  else if (p.act == 2) v = silu(v);
+  if (p.gate) v *= __bfloat162float(p.gate[col]);
+  if (p.residual) v += __bfloat162float(p.residual[row * p.ldc + col]);
+  return v;
+}
+
+// Stores 32 consecutive accumulator columns (B rows b0..b0+31) of A row `a_row`.
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[32], int a_row,
+                                            int b0, int split) {
+  if (a_row >= p.rows_a) return;
+  if (p.out_fp32) {
+    float* out = reinterpret_cast<float*>(p.out) + static_cast<long long>(split) * p.split_stride;
+    if (!p.swap_out) {
+      float* dst = out + static_cast<long long>(a_row) * p.ldc + b0;
+      if (b0 + 32 <= p.rows_b && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (b0 + j < p.rows_b) dst[j] = v[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (b0 + j < p.rows_b) out[static_cast<long long>(b0 + j) * p.ldc + a_row] = v[j];
+    }
+    return;
+  }
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
+  if (!p.swap_out) {
+    __nv_bfloat16* dst = out + static_cast<long long>(a_row) * p.ldc + b0;
+    if (b0 + 32 <= p.rows_b && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 32; j += 2)
+        w[j >> 1] = pack_bf16x2(apply_epilogue(p, v[j], a_row, b0 + j),
+                                apply_epilogue(p, v[j + 1], a_row, b0 + j + 1));
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (b0 + j < p.rows_b)
+          dst[j] = __float2bfloat16(apply_epilogue(p, v[j], a_row, b0 + j));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (b0 + j < p.rows_b)
+        out[static_cast<long long>(b0 + j) * p.ldc + a_row] =
+            __float2bfloat16(apply_epilogue(p, v[j], b0 + j, a_row));
+  }
+}
+
+template <bool kFp8, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a,
+                    const __grid_constant__ CUtensorMap tm_b) {
+  constexpr int kStageBytesB = BN * 128;
+  constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+  constexpr int kElemsPerStage = kFp8 ? 128 : 64;   // K elements in 128 bytes
+  // two accumulator buffers; BN = 16 still reads 32-column chunks, so it gets 64 columns
+  constexpr uint32_t kTmemCols = BN == 16 ? 64 : 2 * BN;
+  constexpr uint32_t kIdesc = kFp8 ? make_idesc(128, BN, kFmtE4m3, kFmtE4m3)
+                                   : make_idesc(128, BN, kFmtBf16, kFmtBf16);
+  static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256,
+                "tcgen05.mma M=128 needs N % 16 == 0; TMEM allocations are powers of two");
+  static_assert(!kFp8 || BN <= 128, "fp8 path keeps BN fp32 accumulators per thread");
+
+  extern __shared__ uint8_t smem_raw[];
+  // 128B-swizzled tiles need 1024-byte aligned bases.
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int stages = p.stages;
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + stages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_a = (p.rows_a + kTileA - 1) / kTileA;
+  const int tiles_b = (p.rows_b + BN - 1) / BN;
+  const int total_kblocks = (p.k + kElemsPerStage - 1) / kElemsPerStage;
+  const long long work_items = static_cast<long long>(tiles_a) * tiles_b * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->tmem_full[b], 1);
+      mbar_init(&bars->tmem_empty[b], 4);   // one arrival per epilogue warp
+    }
+    mbar_init(&bars->drain, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
+        const int ta = static_cast<int>(w % tiles_a);
+        const long long rest = w / tiles_a;
+        const int tb = static_cast<int>(rest % tiles_b);
+        const int split = static_cast<int>(rest / tiles_b);
+        const int kb0 = split * p.kblocks_per_split;
+        const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag)) {
+            report_status(p.status, kWaitTimeout, kKernelGemm, 1, blockIdx.x);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * kStageBytes;
+          uint8_t* sb = sa + kStageBytesA;
+          mbar_arrive_expect_tx(&bars->full[s], kStageBytes);
+          tma_load_2d(sa, &tm_a, &bars->full[s], kb * kElemsPerStage, ta * kTileA);
+          tma_load_2d(sb, &tm_b, &bars->full[s], kb * kElemsPerStage, tb * BN);
+          ++issued;
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Let copies that are still in flight land before the CTA exits.
+        for (int i = 0; i < stages && i < issued; ++i) {
+          int ss = s - 1 - i;
+          uint32_t pp = ph;
+          if (ss < 0) { ss += stages; pp ^= 1; }
+          uint32_t dummy = 0;
+          mbar_wait(&bars->full[ss], pp, &dummy, 2000000ull);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int abuf = 0;
+      uint32_t aph = 0;
+      bool ok = true;
+      bool issued_any = false;
+      for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
+        const long long rest = w / tiles_a;
+        const int split = static_cast<int>(rest / tiles_b);
+        const int kb0 = split * p.kblocks_per_split;
+        const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
+        if (!kFp8) {
+          if (!mbar_wait(&bars->tmem_empty[abuf], aph ^ 1, abort_flag)) {
+            report_status(p.status, kWaitTimeout, kKernelGemm, 2, blockIdx.x);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+        }
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
+            report_status(p.status, kWaitTimeout, kKernelGemm, 3, blockIdx.x);
+            ok = false;
+            break;
+          }
+          if (kFp8) {
+            if (!mbar_wait(&bars->tmem_empty[abuf], aph ^ 1, abort_flag)) {
+              report_status(p.status, kWaitTimeout, kKernelGemm, 4, blockIdx.x);
+              ok = false;
+              break;
+            }
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const uint32_t sb = sa + kStageBytesA;
+          const uint64_t adesc = make_desc_sw128(sa);
+          const uint64_t bdesc = make_desc_sw128(sb);
+          const uint32_t d_tmem = tmem_base + abuf * BN;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // advancing 32 bytes along K inside the 128-byte swizzle atom = +2 in the
+            // (address >> 4) field of the descriptor
+            const uint32_t acc = kFp8 ? (k > 0) : (kb > kb0 || k > 0);
+            if (kFp8) mma_fp8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            else      mma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+          }
+          issued_any = true;
+          tc_commit(&bars->empty[s]);
+          if (kFp8) {
+            tc_commit(&bars->tmem_full[abuf]);
+            if (++abuf == 2) { abuf = 0; aph ^= 1; }
+          }
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+        if (!kFp8 && ok) {
+          tc_commit(&bars->tmem_full[abuf]);
+          if (++abuf == 2) { abuf = 0; aph ^= 1; }
+        }
+      }
+      if (!ok && issued_any) {
+        // make sure no MMA still reads shared memory / writes TMEM when the CTA tears down
+        tc_commit(&bars->drain);
+        uint32_t dummy = 0;
+        mbar_wait(&bars->drain, 0, &dummy, 2000000ull);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps 2..5
+    const int q = warp & 3;   // TMEM lane quarter this warp may read
+    int abuf = 0;
+    uint32_t aph = 0;
+    bool ok = true;
+    for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
+      const int ta = static_cast<int>(w % tiles_a);
+      const long long rest = w / tiles_a;
+      const int tb = static_cast<int>(rest % tiles_b);
+      const int split = static_cast<int>(rest / tiles_b);
+      const int a_row = ta * kTileA + q * 32 + lane;
+      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      if constexpr (!kFp8) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[abuf], aph, abort_flag))) {
+          if (lane == 0) report_status(p.status, kWaitTimeout, kKernelGemm, 5, blockIdx.x);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < BN / 32 + (BN % 32 ? 1 : 0); ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(lane_base + abuf * BN + c * 32, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          store_chunk(p, v, a_row, tb * BN + c * 32, split);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
+        if (++abuf == 2) { abuf = 0; aph ^= 1; }
+      } else {
+        constexpr int kChunks = (BN + 31) / 32;
+        float acc[kChunks * 32];
+#pragma unroll
+        for (int j = 0; j < kChunks * 32; ++j) acc[j] = 0.f;
+        const int kb0 = split * p.kblocks_per_split;
+        const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
+        const int a_row_c = min(a_row, p.rows_a - 1);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          // fetch scales before blocking on the accumulator
+          const float sa = p.scale_a[static_cast<long long>(kb) * p.sa_ld + a_row_c / p.sa_gran];
+          const float* sbp = p.scale_b + static_cast<long long>(kb) * p.sb_ld;
+          float sb_scalar = 0.f;
+          if (p.sb_gran != 1) sb_scalar = sbp[(tb * BN) / p.sb_gran] * sa;
+          if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[abuf], aph, abort_flag))) {
+            if (lane == 0) report_status(p.status, kWaitTimeout, kKernelGemm, 6, blockIdx.x);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(lane_base + abuf * BN + c * 32, r);
+            tmem_ld_wait();
+            if (p.sb_gran != 1) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                acc[c * 32 + j] = fmaf(__uint_as_float(r[j]), sb_scalar, acc[c * 32 + j]);
+            } else {
+              const int b0 = tb * BN + c * 32;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int b = min(b0 + j, p.rows_b - 1);
+                acc[c * 32 + j] =
+                    fmaf(__uint_as_float(r[j]), __ldg(sbp + b) * sa, acc[c * 32 + j]);
+              }
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
+          if (++abuf == 2) { abuf = 0; aph ^= 1; }
+        }
+        if (ok) {
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = acc[c * 32 + j];
+            if (c * 32 < BN) store_chunk(p, v, a_row, tb * BN + c * 32, split);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Sums split-K partials and applies the epilogue. ws is [splits][rows][ldc] fp32 in C's layout.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, GemmParams p, int rows,
+                                     int cols) {
+  // p.ldc is C's leading dimension here; the partials are dense [splits][rows][cols]
+  const long long total = static_cast<long long>(rows) * cols;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols, c = i % cols;
+    float v = 0.f;
+    for (int s = 0; s < p.splits; ++s) v += ws[s * p.split_stride + i];
+    reinterpret_cast<__nv_bfloat16*>(p.out)[r * p.ldc + c] =
+        __float2bfloat16(apply_epilogue(p, v, r, c));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D K-major matrix [rows][k] with row pitch ld elements; box = 128 bytes x box_rows, 128B swizzle.
+int make_kmajor_map(CUtensorMap* out, const void* base, int elem_bytes, long long rows,
+                    long long k, long long ld, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld * elem_bytes)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes),
+                       static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt =
+      elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 100;
+}
+
+template <bool kFp8, int BN>
+int launch_gemm(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, int grid,
+                cudaStream_t stream) {
+  const int stage_bytes = kStageBytesA + BN * 128;
+  const int smem = p.stages * stage_bytes + static_cast<int>(sizeof(GemmBarriers)) + 1024;
+  static int configured = 0;
+  if (configured < smem) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<kFp8, BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    if (e != cudaSuccess) return -static_cast<int>(e) - 200;
+    configured = 232448;
+  }
+  gemm_tcgen05_kernel<kFp8, BN><<<grid, kGemmThreads, smem, stream>>>(p, ta, tb);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e) - 300;
+}
+
+static int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Workspace needed by b200_gemm for the chosen split count (bytes of fp32 partials), 0 if no split.
+B200_API long long b200_gemm_workspace_bytes(int m, int n, int splits) {
+  return splits > 1 ? static_cast<long long>(splits) * m * n * 4 : 0;
+}
+
+// Picks the K split for a memory-bound (small-M) GEMM so that the grid covers the SMs.
+B200_API int b200_gemm_pick_splits(int m, int n, int k, int is_fp8) {
+  const int kelems = is_fp8 ? 128 : 64;
+  const int kblocks = (k + kelems - 1) / kelems;
+  if (m > 128) return 1;
+  const int tiles = (n + 127) / 128;   // weights ride the 128-row dimension for small m
+  const int sms = num_sms();
+  if (tiles >= sms) return 1;
+  int splits = sms / tiles;
+  if (splits > kblocks / 4) splits = kblocks / 4;   // keep >= 4 k-blocks per split
+  if (splits > 16) splits = 16;
+  return splits < 1 ? 1 : splits;
+}
+
+// out[m][n] (bf16, leading dim ldc) = epilogue(x[m][k] * w[n][k]^T)
+//   dtype: 0 = bf16 operands, 1 = fp8 e4m3 operands with block scales
+//   x_scale: [k/128][m] fp32 (per token, per 128-wide K group); w_scale: [k/128][ceil(n/128)] fp32
+//   workspace: fp32 scratch of b200_gemm_workspace_bytes() when splits > 1
+// Returns 0 on success, negative on a launch-time error.
+B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
+                       long long ldw, long long ldc, int dtype, const float* x_scale,
+                       const float* w_scale, const void* bias, const void* gate,
+                       const void* residual, int act, int splits, void* workspace,
+                       void* status, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  const bool fp8 = dtype == 1;
+  const int esz = fp8 ? 1 : 2;
+  const int kelems = fp8 ? 128 : 64;
+  if ((ldx * esz) % 16 != 0 || (ldw * esz) % 16 != 0) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -3;
+  if (fp8 && (k % 128 != 0 || !x_scale || !w_scale)) return -4;
+  if (splits > 1 && workspace == nullptr) return -5;
+
+  // Small token counts: weights take the 128-row MMA dimension, tokens the N dimension.
+  const bool swap = m <= 128;
+  GemmParams p{};
+  p.k = k;
+  p.out = out;
+  p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.act = act;
+  p.status = static_cast<DeviceStatus*>(status);
+  p.swap_out = swap ? 1 : 0;
+  const int total_kblocks = (k + kelems - 1) / kelems;
+  if (splits < 1) splits = 1;
+  if (splits > total_kblocks) splits = total_kblocks;
+  p.kblocks_per_split = (total_kblocks + splits - 1) / splits;
+  splits = (total_kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  p.splits = splits;
+  if (splits > 1) {
+    // partials are [splits][m][n] fp32, densely packed
+    p.out_fp32 = 1;
+    p.out = workspace;
+    p.ldc = n;
+    p.split_stride = static_cast<long long>(m) * n;
+  }
+
+  int bn;
+  const void *a_ptr, *b_ptr;
+  long long lda, ldb;
+  if (swap) {
+    p.rows_a = n; p.rows_b = m;
+    a_ptr = w; lda = ldw; b_ptr = x; ldb = ldx;
+    bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
+    p.scale_a = w_scale; p.sa_gran = 128; p.sa_ld = (n + 127) / 128;
+    p.scale_b = x_scale; p.sb_gran = 1;   p.sb_ld = m;
+  } else {
+    p.rows_a = m; p.rows_b = n;
+    a_ptr = x; lda = ldx; b_ptr = w; ldb = ldw;
+    bn = fp8 ? 128 : 256;
+    if (!fp8 && n <= 128) bn = 128;
+    p.scale_a = x_scale; p.sa_gran = 1;   p.sa_ld = m;
+    p.scale_b = w_scale; p.sb_gran = 128; p.sb_ld = (n + 127) / 128;
+  }
+  const int stage_bytes = kStageBytesA + bn * 128;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 12) stages = 12;
+  p.stages = stages;
+
+  CUtensorMap ta, tb;
+  int rc = make_kmajor_map(&ta, a_ptr, esz, p.rows_a, k, lda, kTileA);
+  if (rc) return rc;
+  rc = make_kmajor_map(&tb, b_ptr, esz, p.rows_b, k, ldb, bn);
+  if (rc) return rc;
+
+  const long long tiles = static_cast<long long>((p.rows_a + 127) / 128) *
+                          ((p.rows_b + bn - 1) / bn) * splits;
+  const int grid = static_cast<int>(tiles < num_sms() ? tiles : num_sms());
+
+  if (fp8) {
+    switch (bn) {
+      case 16: rc = launch_gemm<true, 16>(p, ta, tb, grid, stream); break;
+      case 32: rc = launch_gemm<true, 32>(p, ta, tb, grid, stream); break;
+      case 64: rc = launch_gemm<true, 64>(p, ta, tb, grid, stream); break;
+      default: rc = launch_gemm<true, 128>(p, ta, tb, grid, stream); break;
+    }
+  } else {
+    switch (bn) {
+      case 16: rc = launch_gemm<false, 16>(p, ta, tb, grid, stream); break;
+      case 32: rc = launch_gemm<false, 32>(p, ta, tb, grid, stream); break;
+      case 64: rc = launch_gemm<false, 64>(p, ta, tb, grid, stream); break;
+      case 128: rc = launch_gemm<false, 128>(p, ta, tb, grid, stream); break;
+      default: rc = launch_gemm<false, 256>(p, ta, tb, grid, stream); break;
+    }
+  }
+  if (rc) return rc;
+  if (splits > 1) {
+    GemmParams rp = p;
+    rp.out = out;
+    rp.ldc = ldc;
+    const long long total = static_cast<long long>(m) * n;
+    int blocks = static_cast<int>((total + 255) / 256);
+    if (blocks > 4 * num_sms()) blocks = 4 * num_sms();
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(workspace), rp, m,
+                                                     n);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return -static_cast<int>(e) - 400;
+  }
+  return 0;
+}

@@ -1,0 +1,28 @@
+"""Op namespace of the engine.
+
+One function per op; CUDA tensors go to the hand-written sm_100a kernels in
+``libb200_kernels.so`` (and fail loudly if that library is missing), CPU tensors go to the fp32
+PyTorch statements in :mod:`.reference`. There is no backend interface and no fallback ladder:
+the reference's ``IBackend`` (src/HartsyInference.Core/Backends/IBackend.cs, ~150 ops with CPU
+default bodies) collapses into this module plus ``torch.Tensor``.
+"""
+from .core import (  # noqa: F401
+    Fp8Act,
+    LinearWeight,
+    argmax,
+    attention,
+    attn_decode,
+    attn_prefill_paged,
+    cfg_euler_step,
+    embedding,
+    fill_random_,
+    gated_residual,
+    glu,
+    linear,
+    norm,
+    quant_fp8_act,
+    quant_fp8_weight,
+    repetition_penalty_,
+    rope_kv,
+)
+from . import reference  # noqa: F401

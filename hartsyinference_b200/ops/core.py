@@ -1,0 +1,415 @@
+"""Python entry points of the fused ops (see the package docstring for the dispatch rule)."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _native as N
+from . import reference as R
+
+_ACT = {None: 0, "none": 0, "gelu_tanh": 1, "silu": 2}
+
+
+@dataclass
+class Fp8Act:
+    """e4m3 activations [M, K] (uint8 storage) with 1x128 scales stored k-block-major [K/128, M]."""
+    data: torch.Tensor
+    scale: torch.Tensor
+
+    @property
+    def shape(self):
+        return self.data.shape
+
+
+@dataclass
+class LinearWeight:
+    """Weight of a linear layer, [N, K] K-major. bf16, or e4m3 bytes with 128x128 block scales
+    stored k-block-major [K/128, ceil(N/128)]."""
+    weight: torch.Tensor
+    scale: Optional[torch.Tensor] = None
+    bias: Optional[torch.Tensor] = None
+
+    @property
+    def is_fp8(self) -> bool:
+        return self.scale is not None
+
+    @property
+    def out_features(self) -> int:
+        return self.weight.shape[0]
+
+    @property
+    def in_features(self) -> int:
+        return self.weight.shape[1]
+
+    def nbytes(self) -> int:
+        n = self.weight.numel() * self.weight.element_size()
+        if self.scale is not None:
+            n += self.scale.numel() * 4
+        if self.bias is not None:
+            n += self.bias.numel() * self.bias.element_size()
+        return n
+
+    @staticmethod
+    def from_dense(w: torch.Tensor, bias: Optional[torch.Tensor] = None, fp8: bool = False) -> "LinearWeight":
+        w = w.to(torch.bfloat16).contiguous()
+        if fp8 and w.shape[1] % 128 == 0:
+            q, s = quant_fp8_weight(w)
+            return LinearWeight(q, s, None if bias is None else bias.to(torch.bfloat16))
+        return LinearWeight(w, None, None if bias is None else bias.to(torch.bfloat16))
+
+
+# ---------------------------------------------------------------------------------------------
+def quant_fp8_act(x: torch.Tensor) -> Fp8Act:
+    """bf16 [M, K] -> e4m3 with one scale per 128 consecutive K values."""
+    if not x.is_cuda:
+        q, s = R.quant_fp8_act(x)
+        return Fp8Act(q, s)
+    m, k = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    q = torch.empty(m, k, dtype=torch.uint8, device=x.device)
+    s = torch.empty(k // 128, m, dtype=torch.float32, device=x.device)
+    N.check(N.lib().b200_quant_fp8(x.data_ptr(), q.data_ptr(), s.data_ptr(), m, k, x.stride(0), N.stream()),
+            "b200_quant_fp8")
+    return Fp8Act(q, s)
+
+
+def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [N, K] -> (e4m3 bytes, scales [K/128, ceil(N/128)]) with one scale per 128x128 block."""
+    if not w.is_cuda:
+        return R.quant_fp8_weight(w)
+    n, k = w.shape
+    w = w.to(torch.bfloat16).contiguous()
+    q = torch.empty(n, k, dtype=torch.uint8, device=w.device)
+    s = torch.empty(k // 128, (n + 127) // 128, dtype=torch.float32, device=w.device)
+    N.check(N.lib().b200_quant_fp8_weight(w.data_ptr(), q.data_ptr(), s.data_ptr(), n, k, N.stream()),
+            "b200_quant_fp8_weight")
+    return q, s
+
+
+def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+           splits: Optional[int] = None) -> torch.Tensor:
+    """y = residual + gate * act(x @ W^T + bias), bf16 output [M, N].
+
+    ``x`` is a bf16 tensor [M, K] or an :class:`Fp8Act`. With an fp8 weight a bf16 ``x`` is
+    quantised on the fly (1x128 groups). ``gate`` is a per-output-feature vector [N].
+    """
+    xd = x.data if isinstance(x, Fp8Act) else x
+    if not xd.is_cuda:
+        if isinstance(x, Fp8Act):
+            y = R.linear(x.data, w.weight, w.scale, x.scale, w.bias, act, gate, residual)
+        elif w.is_fp8:
+            q, s = R.quant_fp8_act(x)
+            y = R.linear(q, w.weight, w.scale, s, w.bias, act, gate, residual)
+        else:
+            y = R.linear(x, w.weight, None, None, w.bias, act, gate, residual)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if w.is_fp8 and not isinstance(x, Fp8Act):
+        x = quant_fp8_act(x)
+        xd = x.data
+    if not w.is_fp8 and isinstance(x, Fp8Act):
+        raise ValueError("fp8 activations need an fp8 weight")
+    m, k = xd.shape
+    n = w.weight.shape[0]
+    assert w.weight.shape[1] == k, (w.weight.shape, xd.shape)
+    assert xd.stride(1) == 1 and w.weight.stride(1) == 1
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=xd.device)
+    fp8 = w.is_fp8
+    L = N.lib()
+    if splits is None:
+        splits = L.b200_gemm_pick_splits(m, n, k, 1 if fp8 else 0)
+    st = N.state(xd.device)
+    ws = None
+    if splits > 1:
+        ws = st.scratch(L.b200_gemm_workspace_bytes(m, n, splits)).data_ptr()
+    rc = L.b200_gemm(xd.data_ptr(), w.weight.data_ptr(), out.data_ptr(), m, n, k,
+                     xd.stride(0), w.weight.stride(0), out.stride(0), 1 if fp8 else 0,
+                     x.scale.data_ptr() if fp8 else None, w.scale.data_ptr() if fp8 else None,
+                     N.ptr(w.bias), N.ptr(gate), N.ptr(residual), _ACT[act], splits, ws,
+                     st.status.data_ptr(), N.stream())
+    N.check(rc, "b200_gemm")
+    return out
+
+
+def norm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, *, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
+         scale: Optional[torch.Tensor] = None, rows_per_batch: int = 0, eps: float = 1e-6,
+         layernorm: bool = False, weight_plus_one: bool = False, emit_fp8: bool = False,
+         emit_bf16: bool = True):
+    """(residual add +) RMSNorm / LayerNorm (+ affine) (+ AdaLN ``y * (1 + scale) + shift``).
+
+    x [rows, dim] bf16. ``shift``/``scale`` are [batch, >= dim] with ``rows_per_batch`` rows
+    sharing a batch entry. Returns ``(y, h, y_fp8)``: y bf16 (or None), h = x + residual (or
+    None), y_fp8 an :class:`Fp8Act` (or None).
+    """
+    rows, dim = x.shape
+    if not x.is_cuda:
+        yf, h = R.norm(x, weight, bias, residual, shift, scale, rows_per_batch, eps, layernorm, weight_plus_one)
+        y = yf.to(x.dtype)
+        fq = None
+        if emit_fp8:
+            q, s = R.quant_fp8_act(y)
+            fq = Fp8Act(q, s)
+        return (y if emit_bf16 else None), h, fq
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    y = torch.empty_like(x) if emit_bf16 else None
+    h = torch.empty_like(x) if residual is not None else None
+    q = s = None
+    if emit_fp8:
+        q = torch.empty(rows, dim, dtype=torch.uint8, device=x.device)
+        s = torch.empty(dim // 128, rows, dtype=torch.float32, device=x.device)
+    mod_stride = 0
+    if shift is not None or scale is not None:
+        ref = shift if shift is not None else scale
+        mod_stride = ref.stride(0) if ref.dim() > 1 else 0
+    rc = N.lib().b200_norm(x.data_ptr(), N.ptr(residual), N.ptr(h), N.ptr(weight), N.ptr(bias),
+                           N.ptr(shift), N.ptr(scale), N.ptr(y), N.ptr(q), N.ptr(s), rows, dim,
+                           rows_per_batch, mod_stride, eps, int(layernorm), int(weight_plus_one),
+                           N.stream())
+    N.check(rc, "b200_norm")
+    return y, h, (Fp8Act(q, s) if emit_fp8 else None)
+
+
+def glu(x: torch.Tensor, act: str = "silu", emit_fp8: bool = False, emit_bf16: bool = True):
+    """act(x[:, :F]) * x[:, F:] for x [rows, 2F]. Returns (y bf16 or None, y_fp8 or None)."""
+    rows, f2 = x.shape
+    f = f2 // 2
+    if not x.is_cuda:
+        y = R.glu(x, act).to(x.dtype)
+        fq = None
+        if emit_fp8:
+            q, s = R.quant_fp8_act(y)
+            fq = Fp8Act(q, s)
+        return (y if emit_bf16 else None), fq
+    assert x.is_contiguous() and x.dtype == torch.bfloat16
+    y = torch.empty(rows, f, dtype=torch.bfloat16, device=x.device) if emit_bf16 else None
+    q = s = None
+    if emit_fp8:
+        q = torch.empty(rows, f, dtype=torch.uint8, device=x.device)
+        s = torch.empty(f // 128, rows, dtype=torch.float32, device=x.device)
+    rc = N.lib().b200_glu(x.data_ptr(), N.ptr(y), N.ptr(q), N.ptr(s), rows, f, 0 if act == "silu" else 1, N.stream())
+    N.check(rc, "b200_glu")
+    return y, (Fp8Act(q, s) if emit_fp8 else None)
+
+
+def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, hq: int, hkv: int, d: int, *,
+            k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None,
+            slot_mapping: Optional[torch.Tensor] = None, rot: Optional[int] = None,
+            theta: float = 10000.0, inv_freq: Optional[torch.Tensor] = None, style: int = 0,
+            q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None,
+            eps: float = 1e-6, want_kv: bool = False):
+    """Optional QK RMSNorm + rotary embedding on a packed qkv activation [T, (hq + 2 hkv) d], and
+    the K/V write into the page pool ([pages, hkv, page, d], slot = page_index * page + offset).
+    Returns (q [T, hq, d], k [T, hkv, d] or None, v or None)."""
+    t = qkv.shape[0]
+    rot = d if rot is None else rot
+    if not qkv.is_cuda:
+        x = qkv.float().reshape(t, hq + 2 * hkv, d)
+        q, k, v = x[:, :hq], x[:, hq:hq + hkv], x[:, hq + hkv:]
+        if q_norm_w is not None:
+            q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm_w.float()
+        if k_norm_w is not None:
+            k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + eps) * k_norm_w.float()
+        if rot > 0:
+            fr = inv_freq if inv_freq is not None else R.rope_inv_freq(rot, theta, qkv.device)
+            q = R.apply_rope(q, positions, fr, style)
+            k = R.apply_rope(k, positions, fr, style)
+        q, k, v = q.to(qkv.dtype), k.to(qkv.dtype), v.to(qkv.dtype)
+        if k_cache is not None and slot_mapping is not None:
+            page = k_cache.shape[2]
+            ok = slot_mapping >= 0
+            pg, off = (slot_mapping[ok] // page).long(), (slot_mapping[ok] % page).long()
+            k_cache[pg, :, off] = k[ok]
+            v_cache[pg, :, off] = v[ok]
+        return q.contiguous(), (k.contiguous() if want_kv else None), (v.contiguous() if want_kv else None)
+    assert qkv.is_contiguous() and qkv.dtype == torch.bfloat16
+    q = torch.empty(t, hq, d, dtype=torch.bfloat16, device=qkv.device)
+    k = torch.empty(t, hkv, d, dtype=torch.bfloat16, device=qkv.device) if want_kv else None
+    v = torch.empty(t, hkv, d, dtype=torch.bfloat16, device=qkv.device) if want_kv else None
+    page = k_cache.shape[2] if k_cache is not None else 16
+    if slot_mapping is not None:
+        assert slot_mapping.dtype == torch.int64
+    assert positions.dtype == torch.int32
+    rc = N.lib().b200_rope_kv(qkv.data_ptr(), q.data_ptr(), N.ptr(k_cache), N.ptr(v_cache), N.ptr(k), N.ptr(v),
+                              positions.data_ptr(), N.ptr(slot_mapping), N.ptr(q_norm_w), N.ptr(k_norm_w),
+                              N.ptr(inv_freq), t, hq, hkv, d, rot, style, page, theta, eps, N.stream())
+    N.check(rc, "b200_rope_kv")
+    return q, k, v
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                kv_lens: torch.Tensor, scale: Optional[float] = None, softcap: float = 0.0,
+                window: int = 0, splits: Optional[int] = None, max_kv_len: Optional[int] = None) -> torch.Tensor:
+    """One query token per sequence against a paged KV pool. q [B, hq, d] -> [B, hq, d]."""
+    b, hq, d = q.shape
+    hkv, page = k_cache.shape[1], k_cache.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if not q.is_cuda:
+        outs = []
+        for i in range(b):
+            ln = int(kv_lens[i])
+            kk = R.gather_paged(k_cache, block_table[i], ln)
+            vv = R.gather_paged(v_cache, block_table[i], ln)
+            outs.append(R.attention(q[i:i + 1], kk, vv, causal=False, scale=scale, softcap=softcap,
+                                    window=window))
+        return torch.cat(outs, 0).to(q.dtype)
+    assert block_table.dtype == torch.int32 and kv_lens.dtype == torch.int32
+    out = torch.empty_like(q)
+    L = N.lib()
+    if splits is None:
+        mk = max_kv_len if max_kv_len is not None else block_table.shape[1] * page
+        splits = L.b200_attn_decode_pick_splits(b, hkv, mk)
+    ws = None
+    if splits > 1:
+        ws = N.state(q.device).scratch(L.b200_attn_decode_workspace_bytes(b, hq, d, splits)).data_ptr()
+    rc = L.b200_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                            block_table.data_ptr(), kv_lens.data_ptr(), b, hq, hkv, d, page,
+                            block_table.shape[1], splits, ws, scale, softcap, window, N.stream())
+    N.check(rc, "b200_attn_decode")
+    return out
+
+
+def attn_prefill_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                       block_table: torch.Tensor, kv_lens: torch.Tensor, cu_q: torch.Tensor,
+                       max_q_len: int, causal: bool = True, scale: Optional[float] = None,
+                       softcap: float = 0.0, window: int = 0) -> torch.Tensor:
+    """Variable-length (chunked) prefill: q [total_q, hq, d] packed by cu_q; keys come from the page
+    pool and include any cached prefix (kv_lens[i] >= q_len[i])."""
+    tq, hq, d = q.shape
+    hkv, page = k_cache.shape[1], k_cache.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    nseq = cu_q.numel() - 1
+    if not q.is_cuda:
+        out = torch.empty_like(q)
+        for i in range(nseq):
+            a, b = int(cu_q[i]), int(cu_q[i + 1])
+            ln = int(kv_lens[i])
+            kk = R.gather_paged(k_cache, block_table[i], ln)
+            vv = R.gather_paged(v_cache, block_table[i], ln)
+            out[a:b] = R.attention(q[a:b], kk, vv, causal=causal, scale=scale, softcap=softcap,
+                                   window=window).to(q.dtype)
+        return out
+    out = torch.empty_like(q)
+    rc = N.lib().b200_attn_prefill(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                   block_table.data_ptr(), kv_lens.data_ptr(), cu_q.data_ptr(), None,
+                                   nseq, max_q_len, 0, 0, hq, hkv, d, page, block_table.shape[1], 1,
+                                   int(causal), window, scale, softcap, N.stream())
+    N.check(rc, "b200_attn_prefill")
+    return out
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
+              scale: Optional[float] = None, softcap: float = 0.0, window: int = 0) -> torch.Tensor:
+    """Dense attention for one sequence: q [Tq, hq, d], k/v [Tk, hkv, d] -> [Tq, hq, d]."""
+    tq, hq, d = q.shape
+    tk, hkv, _ = k.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if not q.is_cuda:
+        return R.attention(q, k, v, causal, scale, softcap, window).to(q.dtype)
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+    out = torch.empty_like(q)
+    rc = N.lib().b200_attn_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), None, None,
+                                   None, None, 1, tq, tq, tk, hq, hkv, d, 16, 0, 0, int(causal), window,
+                                   scale, softcap, N.stream())
+    N.check(rc, "b200_attn_prefill")
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    if not table.is_cuda:
+        y = table[ids.long()]
+        return y if scale == 1.0 else (y.float() * scale).to(table.dtype)
+    assert ids.dtype == torch.int32 and table.dtype == torch.bfloat16
+    t = ids.numel()
+    out = torch.empty(t, table.shape[1], dtype=torch.bfloat16, device=table.device)
+    N.check(N.lib().b200_embedding(ids.data_ptr(), table.data_ptr(), out.data_ptr(), t, table.shape[1],
+                                   table.shape[0], scale, N.stream()), "b200_embedding")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-wise argmax of [rows, vocab] (bf16 or fp32) -> int32 [rows]; ties resolve to the lowest id."""
+    if not logits.is_cuda:
+        r = logits.float().argmax(dim=-1).to(torch.int32)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    N.check(N.lib().b200_argmax(logits.data_ptr(), out.data_ptr(), rows, vocab, logits.stride(0),
+                                1 if logits.dtype == torch.float32 else 0, N.stream()), "b200_argmax")
+    return out
+
+
+def repetition_penalty_(logits: torch.Tensor, history: torch.Tensor, hist_len: torch.Tensor,
+                        penalty: torch.Tensor) -> torch.Tensor:
+    """In place: logits[b, t] /= p if > 0 else *= p for every token id t in history[b, :hist_len[b]]."""
+    rows, vocab = logits.shape
+    if not logits.is_cuda:
+        for b in range(rows):
+            p = float(penalty[b])
+            if p == 1.0:
+                continue
+            ids = torch.unique(history[b, : int(hist_len[b])].long())
+            ids = ids[(ids >= 0) & (ids < vocab)]
+            vals = logits[b, ids]
+            logits[b, ids] = torch.where(vals > 0, vals / p, vals * p)
+        return logits
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    N.check(N.lib().b200_repetition_penalty(logits.data_ptr(), history.data_ptr(), hist_len.data_ptr(),
+                                            history.shape[1], rows, vocab, penalty.data_ptr(), N.stream()),
+            "b200_repetition_penalty")
+    return logits
+
+
+def cfg_euler_step(z: torch.Tensor, cond: torch.Tensor, uncond: Optional[torch.Tensor], guidance: float,
+                   dt: float) -> torch.Tensor:
+    """In place on fp32 latents: z += (g * cond + (1 - g) * uncond) * dt (uncond None -> v = cond)."""
+    if not z.is_cuda:
+        z.copy_(R.cfg_euler(z, cond, uncond, guidance, dt))
+        return z
+    assert z.dtype == torch.float32 and cond.dtype == torch.bfloat16
+    N.check(N.lib().b200_cfg_euler(z.data_ptr(), cond.data_ptr(), N.ptr(uncond), z.numel(), guidance, dt,
+                                   N.stream()), "b200_cfg_euler")
+    return z
+
+
+def gated_residual(x: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, rows_per_batch: int = 0) -> torch.Tensor:
+    """x + gate[batch] * y for [rows, dim] bf16 with gate [batch, >= dim]."""
+    rows, dim = x.shape
+    if not x.is_cuda:
+        rpb = rows_per_batch if rows_per_batch > 0 else rows
+        idx = torch.arange(rows) // rpb
+        g = gate.float().reshape(-1, gate.shape[-1])[idx][:, :dim]
+        return (x.float() + g * y.float()).to(x.dtype)
+    out = torch.empty_like(x)
+    ms = gate.stride(0) if gate.dim() > 1 else 0
+    N.check(N.lib().b200_gated_residual(x.data_ptr(), y.data_ptr(), gate.data_ptr(), out.data_ptr(), rows,
+                                        dim, rows_per_batch, ms, N.stream()), "b200_gated_residual")
+    return out
+
+
+def fill_random_(t: torch.Tensor, seed: int, std: float = 0.02) -> torch.Tensor:
+    """Deterministic synthetic fill: bf16 ~ N(0, std); uint8 tensors get e4m3 bytes of unit-variance
+    values scaled by 112 (so a block scale of std / 112 reproduces N(0, std))."""
+    if not t.is_cuda:
+        g = torch.Generator().manual_seed(seed)
+        if t.dtype == torch.uint8:
+            v = (torch.randn(t.shape, generator=g) * 112.0).clamp(-448, 448).to(torch.float8_e4m3fn)
+            t.copy_(v.view(torch.uint8))
+        else:
+            t.copy_((torch.randn(t.shape, generator=g) * std).to(t.dtype))
+        return t
+    assert t.is_contiguous()
+    N.check(N.lib().b200_fill_random(t.data_ptr(), t.numel(), seed, std, 1 if t.dtype == torch.uint8 else 0,
+                                     N.stream()), "b200_fill_random")
+    return t

@@ -1,0 +1,196 @@
+"""Plain PyTorch fp32 statements of every op: the numerical oracle of the CUDA kernels and the
+implementation used for CPU tensors.
+
+The reference engine keeps the same idea: every ``IBackend`` op has a CPU default body that the
+accelerated backends are tested against (src/HartsyInference.Core/Backends/IBackend.cs,
+src/HartsyInference.Core/Backends/AttentionReference.cs). Nothing here is tuned for speed.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+FP8_MAX = 448.0
+
+
+# --------------------------------------------------------------------------------------------
+# quantisation
+# --------------------------------------------------------------------------------------------
+def quant_fp8_act(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """1x128 block quantisation of activations [M, K] -> (e4m3 bytes [M, K], scales [K/128, M])."""
+    m, k = x.shape
+    assert k % 128 == 0
+    xf = x.float().reshape(m, k // 128, 128)
+    amax = xf.abs().amax(dim=-1).clamp_min(1e-12)
+    scale = amax / FP8_MAX
+    q = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q.reshape(m, k).view(torch.uint8), scale.t().contiguous()
+
+
+def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """128x128 block quantisation of a weight [N, K] -> (bytes [N, K], scales [K/128, ceil(N/128)])."""
+    n, k = w.shape
+    assert k % 128 == 0
+    nb = (n + 127) // 128
+    wf = torch.zeros(nb * 128, k, dtype=torch.float32, device=w.device)
+    wf[:n] = w.float()
+    blocks = wf.reshape(nb, 128, k // 128, 128)
+    amax = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12)       # [nb, kb]
+    scale = amax / FP8_MAX
+    q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    q = q.reshape(nb * 128, k)[:n]
+    return q.contiguous().view(torch.uint8), scale.t().contiguous()
+
+
+def dequant_fp8_act(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    m, k = q.shape
+    f = q.view(torch.float8_e4m3fn).float().reshape(m, k // 128, 128)
+    return (f * scale.t().unsqueeze(-1)).reshape(m, k)
+
+
+def dequant_fp8_weight(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    n, k = q.shape
+    s = scale.t()                                                # [nb, kb]
+    s = s.repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)
+    return q.view(torch.float8_e4m3fn).float() * s
+
+
+# --------------------------------------------------------------------------------------------
+# linear
+# --------------------------------------------------------------------------------------------
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    return torch.nn.functional.gelu(x, approximate="tanh")
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, w_scale: Optional[torch.Tensor] = None,
+           x_scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+           act: Optional[str] = None, gate: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """y = residual + gate * act(x @ w^T + bias); fp8 operands are dequantised first."""
+    xf = dequant_fp8_act(x, x_scale) if x_scale is not None else x.float()
+    wf = dequant_fp8_weight(w, w_scale) if w_scale is not None else w.float()
+    y = xf @ wf.t()
+    if bias is not None:
+        y = y + bias.float()
+    if act == "gelu_tanh":
+        y = gelu_tanh(y)
+    elif act == "silu":
+        y = torch.nn.functional.silu(y)
+    if gate is not None:
+        y = y * gate.float()
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(out_dtype)
+
+
+# --------------------------------------------------------------------------------------------
+# norms / activations
+# --------------------------------------------------------------------------------------------
+def norm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
+         scale: Optional[torch.Tensor] = None, rows_per_batch: int = 0, eps: float = 1e-6,
+         layernorm: bool = False, weight_plus_one: bool = False):
+    """Returns (y fp32, h) where h = x + residual rounded to the storage dtype (or None)."""
+    h = x.float()
+    h_out = None
+    if residual is not None:
+        h = (h + residual.float()).to(x.dtype)
+        h_out = h
+        h = h.float()
+    if layernorm:
+        mean = h.mean(dim=-1, keepdim=True)
+        var = ((h - mean) ** 2).mean(dim=-1, keepdim=True)
+        y = (h - mean) * torch.rsqrt(var + eps)
+    else:
+        y = h * torch.rsqrt((h * h).mean(dim=-1, keepdim=True) + eps)
+    if weight is not None:
+        w = weight.float()
+        y = y * ((1.0 + w) if weight_plus_one else w)
+    if bias is not None:
+        y = y + bias.float()
+    if scale is not None or shift is not None:
+        rows = y.shape[0]
+        rpb = rows_per_batch if rows_per_batch > 0 else rows
+        idx = torch.arange(rows, device=y.device) // rpb
+        if scale is not None:
+            y = y * (1.0 + scale.float()[idx][:, : y.shape[1]])
+        if shift is not None:
+            y = y + shift.float()[idx][:, : y.shape[1]]
+    return y, h_out
+
+
+def glu(x: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    f = x.shape[-1] // 2
+    g, u = x[..., :f].float(), x[..., f:].float()
+    a = torch.nn.functional.silu(g) if act == "silu" else gelu_tanh(g)
+    return a * u
+
+
+# --------------------------------------------------------------------------------------------
+# rotary embedding
+# --------------------------------------------------------------------------------------------
+def rope_inv_freq(rot: int, theta: float, device=None) -> torch.Tensor:
+    return theta ** (-torch.arange(0, rot, 2, dtype=torch.float32, device=device) / rot)
+
+
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, style: int = 0) -> torch.Tensor:
+    """x [T, H, D]; rotates the first 2 * len(inv_freq) dims. style 0 = split-half, 1 = interleaved."""
+    rot = inv_freq.numel() * 2
+    xf = x.float()
+    ang = positions.float()[:, None] * inv_freq[None, :]          # [T, rot/2]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    xr, rest = xf[..., :rot], xf[..., rot:]
+    if style == 0:
+        a, b = xr[..., : rot // 2], xr[..., rot // 2:]
+        out = torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+    else:
+        a, b = xr[..., 0::2], xr[..., 1::2]
+        out = torch.stack([a * cos - b * sin, b * cos + a * sin], dim=-1).flatten(-2)
+    return torch.cat([out, rest], dim=-1)
+
+
+# --------------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------------
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
+              scale: Optional[float] = None, softcap: float = 0.0, window: int = 0) -> torch.Tensor:
+    """q [Tq, Hq, D], k/v [Tk, Hkv, D] (one sequence). The last query row sits at key position
+    Tk - 1 (so a query chunk with a cached prefix is expressed by Tk > Tq). Returns fp32 [Tq, Hq, D]."""
+    tq, hq, d = q.shape
+    tk, hkv, _ = k.shape
+    g = hq // hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    kf = k.float().repeat_interleave(g, dim=1)
+    vf = v.float().repeat_interleave(g, dim=1)
+    s = torch.einsum("qhd,khd->hqk", q.float(), kf) * scale
+    if softcap > 0:
+        s = softcap * torch.tanh(s / softcap)
+    qpos = torch.arange(tq, device=q.device)[:, None] + (tk - tq)
+    kpos = torch.arange(tk, device=q.device)[None, :]
+    mask = torch.ones(tq, tk, dtype=torch.bool, device=q.device)
+    if causal:
+        mask &= kpos <= qpos
+    if window > 0:
+        mask &= kpos > qpos - window
+    s = s.masked_fill(~mask[None], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    p = torch.nan_to_num(p)
+    return torch.einsum("hqk,khd->qhd", p, vf)
+
+
+def gather_paged(cache: torch.Tensor, table: torch.Tensor, length: int) -> torch.Tensor:
+    """cache [pages, Hkv, page, D], table [max_pages] -> [length, Hkv, D]."""
+    page = cache.shape[2]
+    n = (length + page - 1) // page
+    pages = cache[table[:n].long()]                               # [n, Hkv, page, D]
+    return pages.permute(0, 2, 1, 3).reshape(n * page, cache.shape[1], cache.shape[3])[:length]
+
+
+# --------------------------------------------------------------------------------------------
+# diffusion scheduler step
+# --------------------------------------------------------------------------------------------
+def cfg_euler(z: torch.Tensor, cond: torch.Tensor, uncond: Optional[torch.Tensor], g: float, dt: float) -> torch.Tensor:
+    v = cond.float() if uncond is None else g * cond.float() + (1.0 - g) * uncond.float()
+    return z + v * dt
