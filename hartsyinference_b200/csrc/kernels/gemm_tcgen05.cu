@@ -380,6 +380,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
     }
   }
 
+  // the single-lane roles rejoin their warps before the CTA-wide barrier
+  __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
