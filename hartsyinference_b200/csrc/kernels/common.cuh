@@ -64,10 +64,12 @@ __device__ __forceinline__ void report_status(DeviceStatus* st, uint32_t code, u
   }
 }
 
-// Default budget for any single wait: 2 s of wall time on the GPU's global timer. Waits between
-// CTAs of one kernel normally complete in microseconds; a value this long only triggers when a
-// peer never arrives. Tests of the timeout path pass a much smaller budget.
-constexpr uint64_t kWaitBudgetNs = 2000000000ull;
+// Default budget for any single wait, in SM clock cycles (about two seconds at 2 GHz). Waits
+// between CTAs of one kernel normally complete in microseconds; a value this long only triggers
+// when a peer never arrives. Tests of the timeout path pass a much smaller budget. The budget is
+// counted with clock64(), which costs a few cycles; %globaltimer is far too slow to read inside a
+// pipeline handshake (it showed up as microseconds per k-block in the block-scaled GEMM).
+constexpr long long kWaitBudgetCycles = 4000000000ll;
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
@@ -129,15 +131,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // waiting quickly instead of each burning a full budget.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile uint32_t* abort_flag,
-                                          uint64_t budget_ns = kWaitBudgetNs) {
+                                          long long budget_cycles = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3f) == 0) {
+    if ((++spins & 0xff) == 0) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > budget_ns) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_cycles) {
         *abort_flag = 1;
         return false;
       }

@@ -6,13 +6,14 @@
 // CudaBackend.cs:1769-2425, LtGemmExecutor.cs, Fp8GemmExecutor.cs:110-111 which is per-tensor
 // scaled) and its mma.sync kernels (Kernels/dequant/int8_mma_gemm.cu, Ptx/hgemm_mma_sm80.ptx).
 //
-// Structure of one CTA (192 threads, persistent over a static list of work items):
+// Structure of one CTA (320 threads, persistent over a static list of work items):
 //   warp 0      TMA producer: one thread issues cp.async.bulk.tensor loads of a 128 x 128-byte A
 //               tile and a BN x 128-byte B tile per stage into 128B-swizzled shared memory
 //   warp 1      allocates TMEM; one thread issues tcgen05.mma (M = 128, N = BN, K = 32 bytes) and
 //               commits to the stage's "empty" barrier and to the accumulator's "full" barrier
-//   warps 2..5  epilogue: tcgen05.ld of the accumulator quarter that belongs to the warp, scale /
-//               bias / activation / gate / residual, store
+//   warps 2..9  epilogue: tcgen05.ld of the accumulator quarter that belongs to the warp (two
+//               warps per quarter split the columns), scale / bias / activation / gate /
+//               residual, store
 // A "work item" is (tile of 128 A rows, tile of BN B rows, K split). The caller decides which
 // operand is the activation: for small token counts the weight matrix is passed as A so that its
 // rows fill the 128-row MMA dimension and the tokens become the narrow N dimension
@@ -51,13 +52,13 @@ struct GemmParams {
 
 constexpr int kTileA = 128;
 constexpr int kStageBytesA = kTileA * 128;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps
 
 struct alignas(8) GemmBarriers {
   uint64_t full[12];
   uint64_t empty[12];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+  uint64_t tmem_full[8];
+  uint64_t tmem_empty[8];
   uint64_t drain;
   uint32_t tmem_base;
   uint32_t abort_flag;
@@ -132,8 +133,12 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
   constexpr int kStageBytesB = BN * 128;
   constexpr int kStageBytes = kStageBytesA + kStageBytesB;
   constexpr int kElemsPerStage = kFp8 ? 128 : 64;   // K elements in 128 bytes
-  // two accumulator buffers; BN = 16 still reads 32-column chunks, so it gets 64 columns
-  constexpr uint32_t kTmemCols = BN == 16 ? 64 : 2 * BN;
+  // Accumulator ring in TMEM: as many buffers as fit in the 512 columns (at most 8). The
+  // block-scaled path hands one buffer per 128-deep K block to the epilogue warps, so a deep ring
+  // lets the tensor core run ahead of the promotion; the bf16 path uses one buffer per tile.
+  constexpr int kBufStride = BN < 32 ? 32 : BN;   // loads are 32 columns wide
+  constexpr int kAccBufs = (512 / kBufStride) < 8 ? (512 / kBufStride) : 8;
+  constexpr uint32_t kTmemCols = kAccBufs * kBufStride;
   constexpr uint32_t kIdesc = kFp8 ? make_idesc(128, BN, kFmtE4m3, kFmtE4m3)
                                    : make_idesc(128, BN, kFmtBf16, kFmtBf16);
   static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256,
@@ -160,9 +165,9 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < 8; ++b) {
       mbar_init(&bars->tmem_full[b], 1);
-      mbar_init(&bars->tmem_empty[b], 4);   // one arrival per epilogue warp
+      mbar_init(&bars->tmem_empty[b], 8);   // one arrival per epilogue warp
     }
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
@@ -216,7 +221,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           uint32_t pp = ph;
           if (ss < 0) { ss += stages; pp ^= 1; }
           uint32_t dummy = 0;
-          mbar_wait(&bars->full[ss], pp, &dummy, 2000000ull);
+          mbar_wait(&bars->full[ss], pp, &dummy, 4000000ll);
         }
       }
     }
@@ -260,7 +265,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           const uint32_t sb = sa + kStageBytesA;
           const uint64_t adesc = make_desc_sw128(sa);
           const uint64_t bdesc = make_desc_sw128(sb);
-          const uint32_t d_tmem = tmem_base + abuf * BN;
+          const uint32_t d_tmem = tmem_base + abuf * kBufStride;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // advancing 32 bytes along K inside the 128-byte swizzle atom = +2 in the
@@ -273,25 +278,30 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           tc_commit(&bars->empty[s]);
           if (kFp8) {
             tc_commit(&bars->tmem_full[abuf]);
-            if (++abuf == 2) { abuf = 0; aph ^= 1; }
+            if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
           }
           if (++s == stages) { s = 0; ph ^= 1; }
         }
         if (!kFp8 && ok) {
           tc_commit(&bars->tmem_full[abuf]);
-          if (++abuf == 2) { abuf = 0; aph ^= 1; }
+          if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
         }
       }
       if (!ok && issued_any) {
         // make sure no MMA still reads shared memory / writes TMEM when the CTA tears down
         tc_commit(&bars->drain);
         uint32_t dummy = 0;
-        mbar_wait(&bars->drain, 0, &dummy, 2000000ull);
+        mbar_wait(&bars->drain, 0, &dummy, 4000000ll);
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue warps 2..5
-    const int q = warp & 3;   // TMEM lane quarter this warp may read
+    // ------------------------------------------------------------------ epilogue warps 2..9
+    // Two warps share each TMEM lane quarter; they split the accumulator columns in 32-column
+    // chunks (even chunks -> first warp, odd chunks -> second warp).
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int hsel = (warp - 2) >> 2;  // which half of the chunks
+    constexpr int kChunks = (BN + 31) / 32;
+    constexpr int kMine = (kChunks + 1) / 2;
     int abuf = 0;
     uint32_t aph = 0;
     bool ok = true;
@@ -310,9 +320,9 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
         }
         tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < BN / 32 + (BN % 32 ? 1 : 0); ++c) {
+        for (int c = hsel; c < kChunks; c += 2) {
           uint32_t r[32];
-          tmem_ld_32x32(lane_base + abuf * BN + c * 32, r);
+          tmem_ld_32x32(lane_base + abuf * kBufStride + c * 32, r);
           tmem_ld_wait();
           float v[32];
 #pragma unroll
@@ -322,21 +332,42 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
-        if (++abuf == 2) { abuf = 0; aph ^= 1; }
+        if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
       } else {
-        constexpr int kChunks = (BN + 31) / 32;
-        float acc[kChunks * 32];
+        float acc[kMine * 32];
 #pragma unroll
-        for (int j = 0; j < kChunks * 32; ++j) acc[j] = 0.f;
+        for (int j = 0; j < kMine * 32; ++j) acc[j] = 0.f;
         const int kb0 = split * p.kblocks_per_split;
         const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
         const int a_row_c = min(a_row, p.rows_a - 1);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          // fetch scales before blocking on the accumulator
-          const float sa = p.scale_a[static_cast<long long>(kb) * p.sa_ld + a_row_c / p.sa_gran];
+        const bool col_vector = p.sb_gran == 1;
+        // Scales are fetched one k-block ahead so that their latency never sits between the
+        // accumulator becoming ready and the FMAs. Row scale: one value per thread. Column scale:
+        // either one value per tile (128-wide weight blocks) or one value per column, in which case
+        // lane l holds the scale of column (chunk * 32 + l) and it is broadcast with shuffles.
+        auto load_row_scale = [&](int kb) {
+          return p.scale_a[static_cast<long long>(kb) * p.sa_ld + a_row_c / p.sa_gran];
+        };
+        auto load_col_scale = [&](int kb, int i) {
           const float* sbp = p.scale_b + static_cast<long long>(kb) * p.sb_ld;
-          float sb_scalar = 0.f;
-          if (p.sb_gran != 1) sb_scalar = sbp[(tb * BN) / p.sb_gran] * sa;
+          if (!col_vector) return sbp[(tb * BN) / p.sb_gran];
+          const int col = min(tb * BN + (hsel + 2 * i) * 32 + lane, p.rows_b - 1);
+          return sbp[col];
+        };
+        float sa_next = load_row_scale(kb0);
+        float cs_next[kMine];
+#pragma unroll
+        for (int i = 0; i < kMine; ++i) cs_next[i] = load_col_scale(kb0, i);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          const float sa = sa_next;
+          float cs[kMine];
+#pragma unroll
+          for (int i = 0; i < kMine; ++i) cs[i] = cs_next[i];
+          if (kb + 1 < kb1) {
+            sa_next = load_row_scale(kb + 1);
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) cs_next[i] = load_col_scale(kb + 1, i);
+          }
           if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[abuf], aph, abort_flag))) {
             if (lane == 0) report_status(p.status, kWaitTimeout, kKernelGemm, 6, blockIdx.x);
             ok = false;
@@ -344,36 +375,41 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           }
           tc_fence_after_sync();
 #pragma unroll
-          for (int c = 0; c < kChunks; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(lane_base + abuf * BN + c * 32, r);
-            tmem_ld_wait();
-            if (p.sb_gran != 1) {
+          for (int i = 0; i < kMine; ++i) {
+            const int c = hsel + 2 * i;
+            if (c < kChunks) {
+              uint32_t r[32];
+              tmem_ld_32x32(lane_base + abuf * kBufStride + c * 32, r);
+              tmem_ld_wait();
+              if (!col_vector) {
+                const float sc = sa * cs[i];
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                acc[c * 32 + j] = fmaf(__uint_as_float(r[j]), sb_scalar, acc[c * 32 + j]);
-            } else {
-              const int b0 = tb * BN + c * 32;
+                for (int j = 0; j < 32; ++j)
+                  acc[i * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[i * 32 + j]);
+              } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int b = min(b0 + j, p.rows_b - 1);
-                acc[c * 32 + j] =
-                    fmaf(__uint_as_float(r[j]), __ldg(sbp + b) * sa, acc[c * 32 + j]);
+                for (int j = 0; j < 32; ++j) {
+                  const float sc = sa * __shfl_sync(0xffffffffu, cs[i], j);
+                  acc[i * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[i * 32 + j]);
+                }
               }
             }
           }
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
-          if (++abuf == 2) { abuf = 0; aph ^= 1; }
+          if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
         }
         if (ok) {
 #pragma unroll
-          for (int c = 0; c < kChunks; ++c) {
-            float v[32];
+          for (int i = 0; i < kMine; ++i) {
+            const int c = hsel + 2 * i;
+            if (c < kChunks) {
+              float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = acc[c * 32 + j];
-            if (c * 32 < BN) store_chunk(p, v, a_row, tb * BN + c * 32, split);
+              for (int j = 0; j < 32; ++j) v[j] = acc[i * 32 + j];
+              store_chunk(p, v, a_row, tb * BN + c * 32, split);
+            }
           }
         }
       }

@@ -1,0 +1,400 @@
+"""Continuous-batching LLM engine: paged KV cache, chunked prefill, CUDA-graph decode.
+
+One engine step = ask the C++ scheduler core what to run, fill pinned host buffers with the batch
+metadata (token ids, positions, KV slots, block tables, lengths), copy them to the device, run the
+prefill chunk batch and/or the decode batch, sample, read the sampled ids back, update requests.
+
+Counterpart in the reference: ``DynamicBatchScheduler`` (SubmitAsync:153, RunLoopAsync:162-268,
+AdmitAndPrefill:311-383 prefills each request alone, RunDecodeRound:460-483 gathers pages per
+sequence before attention, CaptureGraphSession:397-458 only for a single greedy request;
+src/HartsyInference.LLM/Generation/DynamicBatchScheduler.cs), ``TextGenerationPipeline``
+(Generate:132-246, GenerateGraphDecode:303-375; src/HartsyInference.LLM/Generation/
+TextGenerationPipeline.cs) and ``ModelManager`` (pool sizing ComputeKvPoolPageCount:167;
+src/HartsyInference.Engine/ModelManager.cs). Fault containment follows the same rule: an
+exception inside a step fails the requests of that step only, the loop stays alive.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Optional, Sequence
+
+import torch
+
+from .. import config, log, ops
+from ..exceptions import HartsyInferenceError, KvPoolExhaustedError
+from ..models.llm.transformer import DecoderModel, ForwardBatch
+from ..ops import _native as N
+from ..runtime import KvAllocator, SchedulerCore
+from .sampling import SamplingParams, sample_row
+
+
+@dataclass
+class Request:
+    id: int
+    prompt: list[int]
+    params: SamplingParams
+    output: list[int] = field(default_factory=list)
+    finished: bool = False
+    finish_reason: Optional[str] = None     # stop | length | cancelled | error
+    on_token: Optional[Callable[[int, int, bool], None]] = None   # (request id, token, finished)
+    t_submit: float = 0.0
+    t_first_token: float = 0.0
+    t_done: float = 0.0
+    error: Optional[str] = None
+    generator: Optional[torch.Generator] = None
+
+
+def _bucket(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+class LLMEngine:
+    def __init__(self, model: DecoderModel, *, num_pages: Optional[int] = None, page_size: Optional[int] = None,
+                 max_batch: Optional[int] = None, prefill_chunk: Optional[int] = None,
+                 max_model_len: int = 8192, use_cuda_graphs: Optional[bool] = None,
+                 kv_pool_bytes: Optional[int] = None):
+        self.model = model
+        self.device = model.device
+        self.cuda = self.device.type == "cuda"
+        self.page = page_size or config.get("kv_page_size")
+        self.max_batch = max_batch or config.get("max_batch")
+        self.prefill_chunk = prefill_chunk or config.get("prefill_chunk")
+        self.max_model_len = max_model_len
+        self.max_pages_per_seq = (max_model_len + self.page - 1) // self.page
+        self.use_graphs = (config.get("cuda_graphs") if use_cuda_graphs is None else use_cuda_graphs) and self.cuda
+        if num_pages is None:
+            budget = kv_pool_bytes if kv_pool_bytes is not None else config.get("kv_pool_bytes")
+            per_page = model.kv_bytes_per_page(self.page)
+            if budget <= 0:
+                if self.cuda:
+                    free, _ = torch.cuda.mem_get_info(self.device)
+                    budget = int(free * 0.85)
+                else:
+                    budget = 512 << 20      # the reference's default pool budget
+            num_pages = max(8, budget // per_page)
+            # no point in holding more pages than max_batch full-length sequences can use
+            num_pages = min(num_pages, self.max_batch * self.max_pages_per_seq)
+        self.num_pages = int(num_pages)
+        model.alloc_kv(self.num_pages, self.page)
+        self.kv = KvAllocator(self.num_pages, self.page)
+        self.sched = SchedulerCore(self.kv, self.max_batch, self.prefill_chunk, 0, cap=max(1024, 2 * self.max_batch))
+        self.requests: dict[int, Request] = {}
+        self._next_id = 1
+        self._graphs: dict[int, tuple] = {}
+        self._graphs_disabled = False
+        self.fault_injector: Optional[Callable[[str], None]] = None   # host-side test hook
+        self.steps = 0
+        self.alive = True
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+        self.kernel_launches_last = 0
+        pin = self.cuda
+        mp = self.max_pages_per_seq
+        cap_tokens = max(self.prefill_chunk, self.max_batch)
+        cap_seqs = max(self.max_batch, 1)
+        # pinned host staging, reused every step
+        self.h_tokens = torch.zeros(cap_tokens, dtype=torch.int32, pin_memory=pin)
+        self.h_positions = torch.zeros(cap_tokens, dtype=torch.int32, pin_memory=pin)
+        self.h_slots = torch.zeros(cap_tokens, dtype=torch.int64, pin_memory=pin)
+        self.h_table = torch.zeros(cap_seqs, mp, dtype=torch.int32, pin_memory=pin)
+        self.h_kv_lens = torch.zeros(cap_seqs, dtype=torch.int32, pin_memory=pin)
+        self.h_cu_q = torch.zeros(cap_seqs + 1, dtype=torch.int32, pin_memory=pin)
+        self.h_rows = torch.zeros(cap_seqs, dtype=torch.int64, pin_memory=pin)
+        self.h_out = torch.zeros(cap_seqs, dtype=torch.int32, pin_memory=pin)
+        if self.cuda:
+            N.reserve_workspace(self.device, 256 << 20)
+        log.info(f"[Engine] kv pages={self.num_pages} x {self.page} tokens "
+                 f"({self.num_pages * model.kv_bytes_per_page(self.page) / 2**30:.2f} GiB), "
+                 f"max_batch={self.max_batch}, graphs={'on' if self.use_graphs else 'off'}")
+
+    # ------------------------------------------------------------------------------- requests
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    on_token: Optional[Callable[[int, int, bool], None]] = None) -> int:
+        params = params or SamplingParams()
+        prompt = list(prompt)
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        max_new = min(params.max_tokens, self.max_model_len - len(prompt))
+        if max_new <= 0:
+            raise ValueError(f"prompt of {len(prompt)} tokens leaves no room (max_model_len={self.max_model_len})")
+        rid = self._next_id
+        self._next_id += 1
+        self.sched.submit(rid, len(prompt), max_new)
+        req = Request(rid, prompt, params, on_token=on_token, t_submit=time.perf_counter())
+        if params.seed is not None and not params.is_greedy:
+            req.generator = torch.Generator(device=self.device).manual_seed(params.seed)
+        self.requests[rid] = req
+        return rid
+
+    def cancel(self, rid: int) -> None:
+        req = self.requests.get(rid)
+        if req is None or req.finished:
+            return
+        self.sched.abort(rid)
+        self._finish(req, "cancelled")
+
+    def has_work(self) -> bool:
+        return any(not r.finished for r in self.requests.values())
+
+    def _finish(self, req: Request, reason: str) -> None:
+        req.finished = True
+        req.finish_reason = reason
+        req.t_done = time.perf_counter()
+
+    # ------------------------------------------------------------------------------- batches
+    def _seq_tokens(self, req: Request) -> list[int]:
+        return req.prompt + req.output
+
+    def _fill_table(self, row: int, rid: int) -> None:
+        self.kv.block_table_into(rid, self.h_table[row].data_ptr(), self.max_pages_per_seq)
+
+    def _to_device(self, t: torch.Tensor, n: int) -> torch.Tensor:
+        v = t[:n]
+        self.h2d_bytes_last += v.numel() * v.element_size()
+        return v.to(self.device, non_blocking=True) if self.cuda else v.clone()
+
+    def _run_prefill(self, chunks: list[tuple[int, int, int]]) -> list[tuple[Request, int]]:
+        """Runs one batch of prompt chunks. Returns [(request, sampled token)] for requests whose
+        prompt completed in this step."""
+        page = self.page
+        t = 0
+        sample_rows: list[tuple[int, Request]] = []
+        max_q = max_kv = 0
+        for i, (rid, start, count) in enumerate(chunks):
+            req = self.requests[rid]
+            toks = self._seq_tokens(req)
+            target = len(req.prompt) + len(req.output) - (1 if req.output else 0)
+            self.h_tokens[t:t + count] = torch.tensor(toks[start:start + count], dtype=torch.int32)
+            self.h_positions[t:t + count] = torch.arange(start, start + count, dtype=torch.int32)
+            self._fill_table(i, rid)
+            pos = torch.arange(start, start + count, dtype=torch.int64)
+            self.h_slots[t:t + count] = self.h_table[i][(pos // page)].to(torch.int64) * page + pos % page
+            self.h_cu_q[i] = t
+            self.h_kv_lens[i] = start + count
+            max_q = max(max_q, count)
+            max_kv = max(max_kv, start + count)
+            if start + count >= target:
+                sample_rows.append((t + count - 1, req))
+            t += count
+        n = len(chunks)
+        self.h_cu_q[n] = t
+        batch = ForwardBatch(tokens=self._to_device(self.h_tokens, t), positions=self._to_device(self.h_positions, t),
+                             slot_mapping=self._to_device(self.h_slots, t), block_table=self._to_device(self.h_table, n),
+                             kv_lens=self._to_device(self.h_kv_lens, n), is_decode=False,
+                             cu_q=self._to_device(self.h_cu_q, n + 1), max_q_len=max_q, max_kv_len=max_kv)
+        hidden = self.model.forward_hidden(batch)
+        done: list[tuple[Request, int]] = []
+        fresh = [(row, req) for row, req in sample_rows if not req.output]
+        if fresh:
+            rows = torch.tensor([r for r, _ in fresh], dtype=torch.int64)
+            rows_d = rows.to(self.device, non_blocking=True) if self.cuda else rows
+            self.h2d_bytes_last += rows.numel() * 8
+            toks = self._sample(hidden[rows_d].contiguous(), [req for _, req in fresh])
+            done = [(req, tok) for (_, req), tok in zip(fresh, toks)]
+        # requests that re-computed their context after a pre-emption continue decoding without sampling
+        for row, req in sample_rows:
+            if req.output:
+                done.append((req, -1))
+        return done
+
+    def _sample(self, hidden: torch.Tensor, reqs: list[Request]) -> list[int]:
+        """hidden [n, H] for n requests -> one sampled token each."""
+        n = len(reqs)
+        if all(not r.params.needs_logits for r in reqs):
+            tok = self.model.greedy_tokens(hidden)
+            if self.cuda:
+                self.h_out[:n].copy_(tok, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                self.d2h_bytes_last += n * 4
+                return self.h_out[:n].tolist()
+            return tok.tolist()
+        logits = self.model.full_logits(hidden).float()
+        out = []
+        for i, r in enumerate(reqs):
+            out.append(sample_row(logits[i], r.params, r.prompt + r.output, r.generator))
+        self.d2h_bytes_last += n * 4
+        return out
+
+    def _decode_batch_tensors(self, rids: list[int], bucket: int):
+        page = self.page
+        n = len(rids)
+        max_kv = 0
+        for i, rid in enumerate(rids):
+            req = self.requests[rid]
+            pos = len(req.prompt) + len(req.output) - 1       # position of the token being fed
+            self.h_tokens[i] = req.output[-1]
+            self.h_positions[i] = pos
+            self._fill_table(i, rid)
+            self.h_slots[i] = int(self.h_table[i, pos // page]) * page + pos % page
+            self.h_kv_lens[i] = pos + 1
+            max_kv = max(max_kv, pos + 1)
+        for i in range(n, bucket):                             # padding rows: no KV write, empty context
+            self.h_tokens[i] = 0
+            self.h_positions[i] = 0
+            self.h_slots[i] = -1
+            self.h_kv_lens[i] = 0
+            self.h_table[i].zero_()
+        return max_kv
+
+    def _run_decode(self, rids: list[int]) -> list[int]:
+        n = len(rids)
+        reqs = [self.requests[r] for r in rids]
+        greedy = all(not r.params.needs_logits for r in reqs)
+        if self.use_graphs and greedy and not self._graphs_disabled:
+            try:
+                return self._run_decode_graph(rids)
+            except HartsyInferenceError:
+                raise
+            except Exception as e:  # capture failure -> circuit breaker, fall back to eager
+                self._graphs_disabled = True
+                log.warn(f"[Engine] CUDA graph decode disabled after failure: {e}")
+        max_kv = self._decode_batch_tensors(rids, n)
+        batch = ForwardBatch(tokens=self._to_device(self.h_tokens, n), positions=self._to_device(self.h_positions, n),
+                             slot_mapping=self._to_device(self.h_slots, n), block_table=self._to_device(self.h_table, n),
+                             kv_lens=self._to_device(self.h_kv_lens, n), is_decode=True, max_kv_len=self.max_model_len)
+        hidden = self.model.forward_hidden(batch)
+        return self._sample(hidden, reqs)
+
+    def _run_decode_graph(self, rids: list[int]) -> list[int]:
+        n = len(rids)
+        bucket = min(_bucket(n), _bucket(self.max_batch))
+        self._decode_batch_tensors(rids, bucket)
+        entry = self._graphs.get(bucket)
+        if entry is None:
+            entry = self._capture(bucket)
+            self._graphs[bucket] = entry
+        graph, st = entry
+        mp = self.max_pages_per_seq
+        st["tokens"].copy_(self.h_tokens[:bucket], non_blocking=True)
+        st["positions"].copy_(self.h_positions[:bucket], non_blocking=True)
+        st["slots"].copy_(self.h_slots[:bucket], non_blocking=True)
+        st["table"].copy_(self.h_table[:bucket], non_blocking=True)
+        st["kv_lens"].copy_(self.h_kv_lens[:bucket], non_blocking=True)
+        self.h2d_bytes_last += bucket * (4 + 4 + 8 + 4 + 4 * mp)
+        graph.replay()
+        self.h_out[:bucket].copy_(st["out"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes_last += bucket * 4
+        return self.h_out[:n].tolist()
+
+    def _capture(self, bucket: int):
+        dev, mp = self.device, self.max_pages_per_seq
+        st = {
+            "tokens": torch.zeros(bucket, dtype=torch.int32, device=dev),
+            "positions": torch.zeros(bucket, dtype=torch.int32, device=dev),
+            "slots": torch.full((bucket,), -1, dtype=torch.int64, device=dev),
+            "table": torch.zeros(bucket, mp, dtype=torch.int32, device=dev),
+            "kv_lens": torch.zeros(bucket, dtype=torch.int32, device=dev),
+            "out": torch.zeros(bucket, dtype=torch.int32, device=dev),
+        }
+        if self.fault_injector is not None:
+            self.fault_injector("graph_capture")
+
+        def run():
+            batch = ForwardBatch(tokens=st["tokens"], positions=st["positions"], slot_mapping=st["slots"],
+                                 block_table=st["table"], kv_lens=st["kv_lens"], is_decode=True,
+                                 max_kv_len=self.max_model_len)
+            hidden = self.model.forward_hidden(batch)
+            self.model.greedy_tokens(hidden, st["out"])
+
+        # warm up on a side stream (loads kernels, sizes scratch) before capturing
+        s = torch.cuda.Stream(device=dev)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            run()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            run()
+        log.debug(f"[Engine] captured decode graph for batch {bucket}")
+        return g, st
+
+    # ------------------------------------------------------------------------------- step loop
+    def step(self) -> list[tuple[int, int, bool]]:
+        """One engine iteration. Returns [(request id, new token, finished)]."""
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+        prefill, decode, preempted = self.sched.step()
+        for rid in preempted:
+            log.debug(f"[Engine] request {rid} pre-empted (KV pool full), will recompute")
+        events: list[tuple[int, int, bool]] = []
+        involved = [rid for rid, _, _ in prefill] + list(decode)
+        try:
+            if self.fault_injector is not None:
+                self.fault_injector("step")
+            new_tokens: dict[int, int] = {}
+            if decode:
+                toks = self._run_decode(decode)
+                for rid, tok in zip(decode, toks):
+                    new_tokens[rid] = tok
+            completed_prefill: list[tuple[Request, int]] = []
+            if prefill:
+                completed_prefill = self._run_prefill(prefill)
+            done_ids = {req.id for req, _ in completed_prefill}
+            for rid, _, _ in prefill:
+                if rid not in done_ids:
+                    self.sched.update(rid, 0, False)        # partial chunk: nothing sampled yet
+            for req, tok in completed_prefill:
+                if tok < 0:
+                    self.sched.update(req.id, 0, False)     # context rebuilt after pre-emption
+                else:
+                    new_tokens[req.id] = tok
+            now = time.perf_counter()
+            for rid, tok in new_tokens.items():
+                req = self.requests[rid]
+                if req.finished:
+                    continue
+                req.output.append(tok)
+                if len(req.output) == 1:
+                    req.t_first_token = now
+                p = req.params
+                stop = (not p.ignore_eos and tok in self.model.cfg.eos_token_ids) or tok in p.stop_token_ids
+                limit = len(req.output) >= min(p.max_tokens, self.max_model_len - len(req.prompt))
+                fin = stop or limit
+                self.sched.update(rid, 1, fin)
+                if fin:
+                    self._finish(req, "stop" if stop else "length")
+                events.append((rid, tok, fin))
+                if req.on_token is not None:
+                    req.on_token(rid, tok, fin)
+        except Exception as e:
+            # fault containment: fail the requests of this step, keep the loop alive
+            log.warn(f"[Engine] step failed ({type(e).__name__}: {e}); failing {len(involved)} request(s)")
+            for rid in involved:
+                req = self.requests.get(rid)
+                if req is not None and not req.finished:
+                    self.sched.abort(rid)
+                    req.error = f"{type(e).__name__}: {e}"
+                    self._finish(req, "error")
+                    events.append((rid, -1, True))
+                    if req.on_token is not None:
+                        req.on_token(rid, -1, True)
+        self.steps += 1
+        return events
+
+    def run_until_done(self, max_steps: int = 1 << 30) -> None:
+        n = 0
+        while self.has_work() and n < max_steps:
+            self.step()
+            n += 1
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[SamplingParams] = None) -> list[list[int]]:
+        """Blocking convenience call: submit all prompts, run to completion, return the generated ids."""
+        ids = [self.add_request(p, params) for p in prompts]
+        self.run_until_done()
+        outs = [self.requests[i].output for i in ids]
+        return outs
+
+    def release(self, rid: int) -> Optional[Request]:
+        return self.requests.pop(rid, None)
+
+    def stats(self) -> dict:
+        s = self.sched.stats()
+        s.update(steps=self.steps, pages=self.num_pages, pages_used=self.num_pages - s["free_blocks"],
+                 graphs=len(self._graphs), alive=self.alive)
+        return s

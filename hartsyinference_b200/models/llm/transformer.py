@@ -1,0 +1,384 @@
+"""Config-driven decoder transformer over the fused ops.
+
+One class runs every dense decoder architecture of :mod:`.config` (llama, mistral, qwen2/3, gemma
+1-3, granite, glm4, olmo2, ...), single-GPU or tensor-parallel. Activations are bf16, weights bf16
+or 128x128 block-scaled e4m3; the KV cache is a page pool written by the RoPE kernel and read in
+place by the attention kernels.
+
+Role in the reference: ``GenericTransformer`` (config-driven decoder, fp32 activations;
+src/HartsyInference.LLM/Transformer/GenericTransformer.cs: LoadWeights:171, ForwardEmbeds:409-535,
+Layer.Forward:1575-1751, ForwardBatchDecode:856-902, ProjectLogits:931-978) and
+``TensorParallelTransformer`` (Megatron split with two all-reduces per layer, ranks executed one
+after another by one thread; TensorParallelTransformer.cs:251-341, slicing :529/:552). Here every
+rank is its own process and the all-reduce is either NCCL or the fused GEMM+all-reduce kernel.
+
+Layer dataflow (one launch per arrow, residual adds folded into the norm kernel):
+
+    norm(+res) -> qkv GEMM -> [qk-norm] rope + KV page write -> attention -> o GEMM (-> all-reduce)
+    norm(+res) -> gate|up GEMM -> GLU (emits fp8 for the next GEMM) -> down GEMM (-> all-reduce)
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from ... import ops
+from ...ops import LinearWeight
+from ...parallel.comm import Comm, SingleComm
+from .config import RopeScaling, TransformerConfig
+
+
+@dataclass
+class ForwardBatch:
+    """Device-side description of one forward pass (a prefill chunk batch or a decode batch)."""
+    tokens: torch.Tensor                 # [T] int32
+    positions: torch.Tensor              # [T] int32
+    slot_mapping: torch.Tensor           # [T] int64, page_index * page + offset, -1 = do not store
+    block_table: torch.Tensor            # [S, max_pages] int32
+    kv_lens: torch.Tensor                # [S] int32, keys visible to the last query of each sequence
+    is_decode: bool
+    cu_q: Optional[torch.Tensor] = None  # prefill: [S + 1] int32
+    max_q_len: int = 1
+    max_kv_len: int = 0
+    logit_rows: Optional[torch.Tensor] = None   # prefill: rows (into T) whose logits are needed
+    embeds: Optional[torch.Tensor] = None       # optional precomputed input embeddings [T, H]
+
+
+def build_inv_freq(rot: int, theta: float, scaling: RopeScaling, device) -> tuple[torch.Tensor, float]:
+    """Inverse rotary frequencies with linear / llama3 / YaRN scaling, and the attention factor.
+    (Reference: src/HartsyInference.Core/Rope/RopeFrequencyBuilder.cs, RopeScaling.cs.)"""
+    inv = theta ** (-torch.arange(0, rot, 2, dtype=torch.float64) / rot)
+    attn_factor = 1.0
+    if scaling.kind == "linear":
+        inv = inv / scaling.factor
+    elif scaling.kind == "llama3":
+        low = scaling.original_max_position / scaling.low_freq_factor
+        high = scaling.original_max_position / scaling.high_freq_factor
+        wavelen = 2 * math.pi / inv
+        smooth = ((scaling.original_max_position / wavelen) - scaling.low_freq_factor) / (
+            scaling.high_freq_factor - scaling.low_freq_factor)
+        scaled = torch.where(wavelen > low, inv / scaling.factor, inv)
+        mid = (wavelen <= low) & (wavelen >= high)
+        scaled = torch.where(mid, (1 - smooth) * inv / scaling.factor + smooth * inv, scaled)
+        inv = scaled
+    elif scaling.kind == "yarn":
+        def corr_dim(n_rot):
+            return (rot * math.log(scaling.original_max_position / (n_rot * 2 * math.pi))) / (2 * math.log(theta))
+        lo = max(math.floor(corr_dim(scaling.beta_fast)), 0)
+        hi = min(math.ceil(corr_dim(scaling.beta_slow)), rot // 2 - 1)
+        ramp = ((torch.arange(rot // 2, dtype=torch.float64) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
+        mask = 1 - ramp
+        inv = inv / scaling.factor * (1 - mask) + inv * mask
+        attn_factor = scaling.attn_factor * (0.1 * math.log(scaling.factor) + 1.0) if scaling.factor > 1 else 1.0
+    return inv.to(torch.float32).to(device), attn_factor
+
+
+@dataclass
+class LayerWeights:
+    in_norm: torch.Tensor
+    qkv: LinearWeight
+    o: LinearWeight
+    post_norm: torch.Tensor
+    gate_up: Optional[LinearWeight] = None
+    down: Optional[LinearWeight] = None
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    post_attn_norm: Optional[torch.Tensor] = None     # sandwich norms (Gemma 2/3)
+    post_ffn_norm: Optional[torch.Tensor] = None
+    ffn_module: Optional[object] = None               # MoE feed-forward (callable) instead of gate_up/down
+    attn_module: Optional[object] = None              # MLA attention (callable) instead of qkv/o
+
+
+class DecoderModel:
+    def __init__(self, cfg: TransformerConfig, device: torch.device | str = "cpu", comm: Optional[Comm] = None,
+                 fp8: bool = False):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.comm = comm or SingleComm()
+        self.tp = self.comm.world
+        self.tp_rank = self.comm.rank
+        cfg.validate_tp(self.tp)
+        self.fp8 = fp8
+        self.hq = cfg.num_heads // self.tp
+        self.hkv = max(1, cfg.num_kv_heads // self.tp)
+        self.ffn = cfg.ffn_size // self.tp
+        self.vocab_local = (cfg.vocab_size + self.tp - 1) // self.tp
+        self.embed: Optional[torch.Tensor] = None
+        self.lm_head: Optional[LinearWeight] = None
+        self.final_norm: Optional[torch.Tensor] = None
+        self.layers: list[LayerWeights] = []
+        self.inv_freq, self.rope_attn_factor = build_inv_freq(cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling,
+                                                              self.device)
+        self.kv_cache: Optional[torch.Tensor] = None
+        self.all_reduce: Callable[[torch.Tensor], torch.Tensor] = self.comm.all_reduce
+        # hook for the fused GEMM + all-reduce path: (x, weight, residual) -> reduced output
+        self.row_parallel_linear: Optional[Callable] = None
+
+    # ------------------------------------------------------------------------------ weights
+    def _lw(self, w: torch.Tensor, bias: Optional[torch.Tensor] = None, allow_fp8: bool = True) -> LinearWeight:
+        w = w.to(self.device)
+        b = None if bias is None else bias.to(self.device)
+        return LinearWeight.from_dense(w, b, fp8=self.fp8 and allow_fp8)
+
+    def kv_head_slice(self) -> slice:
+        """KV heads owned by this rank (replicated across ranks when tp > num_kv_heads)."""
+        hkv_total = self.cfg.num_kv_heads
+        if self.tp <= hkv_total:
+            return slice(self.tp_rank * self.hkv, (self.tp_rank + 1) * self.hkv)
+        rep = self.tp // hkv_total
+        idx = self.tp_rank // rep
+        return slice(idx, idx + 1)
+
+    def load_state_dict(self, get: Callable[[str], Optional[torch.Tensor]]) -> None:
+        """Load Hugging Face-named tensors (``model.layers.N.self_attn.q_proj.weight`` ...), slicing
+        each tensor to this rank's shard. ``get(name)`` returns a CPU tensor or None."""
+        cfg, d = self.cfg, self.cfg.head_dim
+        r, tp = self.tp_rank, self.tp
+        dt = torch.bfloat16
+
+        def need(name):
+            t = get(name)
+            if t is None:
+                raise KeyError(f"missing tensor {name}")
+            return t
+
+        emb = need("model.embed_tokens.weight")
+        self.embed = emb.to(dt).to(self.device)
+        head = get("lm_head.weight")
+        if head is None or cfg.tie_embeddings:
+            head = emb
+        v0, v1 = r * self.vocab_local, min(cfg.vocab_size, (r + 1) * self.vocab_local)
+        hw = head[v0:v1]
+        if hw.shape[0] < self.vocab_local:   # pad the last shard so every rank has the same shape
+            hw = torch.cat([hw, torch.zeros(self.vocab_local - hw.shape[0], hw.shape[1], dtype=hw.dtype)])
+        self.lm_head = self._lw(hw.to(dt), allow_fp8=False)
+        self.final_norm = need("model.norm.weight").to(dt).to(self.device)
+        kvs = self.kv_head_slice()
+        self.layers = []
+        for i in range(cfg.num_layers):
+            p = f"model.layers.{i}."
+            q = need(p + "self_attn.q_proj.weight")[r * self.hq * d:(r + 1) * self.hq * d]
+            k = need(p + "self_attn.k_proj.weight")[kvs.start * d:kvs.stop * d]
+            v = need(p + "self_attn.v_proj.weight")[kvs.start * d:kvs.stop * d]
+            qkv_b = None
+            if cfg.qkv_bias and get(p + "self_attn.q_proj.bias") is not None:
+                qkv_b = torch.cat([need(p + "self_attn.q_proj.bias")[r * self.hq * d:(r + 1) * self.hq * d],
+                                   need(p + "self_attn.k_proj.bias")[kvs.start * d:kvs.stop * d],
+                                   need(p + "self_attn.v_proj.bias")[kvs.start * d:kvs.stop * d]])
+            o = need(p + "self_attn.o_proj.weight")[:, r * self.hq * d:(r + 1) * self.hq * d]
+            gate = need(p + "mlp.gate_proj.weight")[r * self.ffn:(r + 1) * self.ffn]
+            up = need(p + "mlp.up_proj.weight")[r * self.ffn:(r + 1) * self.ffn]
+            down = need(p + "mlp.down_proj.weight")[:, r * self.ffn:(r + 1) * self.ffn]
+            lw = LayerWeights(
+                in_norm=need(p + "input_layernorm.weight").to(dt).to(self.device),
+                qkv=self._lw(torch.cat([q, k, v]).to(dt), None if qkv_b is None else qkv_b.to(dt)),
+                o=self._lw(o.contiguous().to(dt)),
+                post_norm=need(p + "post_attention_layernorm.weight").to(dt).to(self.device),
+                gate_up=self._lw(torch.cat([gate, up]).to(dt)),
+                down=self._lw(down.contiguous().to(dt)))
+            if cfg.qk_norm:
+                lw.q_norm = need(p + "self_attn.q_norm.weight").to(dt).to(self.device)
+                lw.k_norm = need(p + "self_attn.k_norm.weight").to(dt).to(self.device)
+            if cfg.post_norms:
+                lw.post_attn_norm = lw.post_norm
+                lw.post_norm = need(p + "pre_feedforward_layernorm.weight").to(dt).to(self.device)
+                lw.post_ffn_norm = need(p + "post_feedforward_layernorm.weight").to(dt).to(self.device)
+            self.layers.append(lw)
+
+    def random_init(self, seed: int = 0, std: float = 0.02) -> None:
+        """Synthetic weights generated on the device (no host copy): bf16 N(0, std), or e4m3 bytes
+        with constant block scales that reproduce the same distribution."""
+        cfg, d, dev = self.cfg, self.cfg.head_dim, self.device
+        counter = [seed * 1000003 + self.tp_rank * 7919]
+
+        def dense(n, k, s=std):
+            counter[0] += 1
+            t = torch.empty(n, k, dtype=torch.bfloat16, device=dev)
+            ops.fill_random_(t, counter[0], s)
+            return t
+
+        def lin(n, k, bias=False, allow_fp8=True):
+            counter[0] += 1
+            if self.fp8 and allow_fp8 and k % 128 == 0:
+                w = torch.empty(n, k, dtype=torch.uint8, device=dev)
+                ops.fill_random_(w, counter[0])
+                sc = torch.full((k // 128, (n + 127) // 128), std / 112.0, dtype=torch.float32, device=dev)
+                b = dense(1, n).reshape(n) if bias else None
+                return LinearWeight(w, sc, b)
+            b = dense(1, n).reshape(n) if bias else None
+            return LinearWeight(dense(n, k), None, b)
+
+        ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device=dev)
+        # the embedding table is shared by all ranks: seed it independently of the rank
+        emb_seed = seed * 1000003 + 17
+        self.embed = torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=torch.bfloat16, device=dev)
+        ops.fill_random_(self.embed, emb_seed, std)
+        if cfg.tie_embeddings:
+            v0 = self.tp_rank * self.vocab_local
+            hw = self.embed[v0:v0 + self.vocab_local]
+            if hw.shape[0] < self.vocab_local:
+                hw = torch.cat([hw, torch.zeros(self.vocab_local - hw.shape[0], cfg.hidden_size, dtype=hw.dtype, device=dev)])
+            self.lm_head = LinearWeight(hw.contiguous() if self.tp > 1 else hw)
+        else:
+            self.lm_head = lin(self.vocab_local, cfg.hidden_size, allow_fp8=False)
+        self.final_norm = ones(cfg.hidden_size)
+        self.layers = []
+        for _ in range(cfg.num_layers):
+            lw = LayerWeights(
+                in_norm=ones(cfg.hidden_size),
+                qkv=lin((self.hq + 2 * self.hkv) * d, cfg.hidden_size, bias=cfg.qkv_bias),
+                o=lin(cfg.hidden_size, self.hq * d),
+                post_norm=ones(cfg.hidden_size),
+                gate_up=lin(2 * self.ffn, cfg.hidden_size),
+                down=lin(cfg.hidden_size, self.ffn))
+            if cfg.qk_norm:
+                lw.q_norm, lw.k_norm = ones(d), ones(d)
+            if cfg.post_norms:
+                lw.post_attn_norm, lw.post_ffn_norm = ones(cfg.hidden_size), ones(cfg.hidden_size)
+            self.layers.append(lw)
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() * 2 + self.final_norm.numel() * 2
+        if self.lm_head.weight.data_ptr() != self.embed.data_ptr():
+            n += self.lm_head.nbytes()
+        for lw in self.layers:
+            for w in (lw.qkv, lw.o, lw.gate_up, lw.down):
+                if w is not None:
+                    n += w.nbytes()
+            if lw.ffn_module is not None and hasattr(lw.ffn_module, "nbytes"):
+                n += lw.ffn_module.nbytes()
+            if lw.attn_module is not None and hasattr(lw.attn_module, "nbytes"):
+                n += lw.attn_module.nbytes()
+        return n
+
+    # ------------------------------------------------------------------------------ KV cache
+    def kv_bytes_per_page(self, page: int) -> int:
+        return self.cfg.num_layers * 2 * self.hkv * page * self.cfg.head_dim * 2
+
+    def alloc_kv(self, num_pages: int, page: int = 16) -> torch.Tensor:
+        """[layers, 2, pages, hkv_local, page, head_dim] bf16."""
+        self.kv_cache = torch.zeros(self.cfg.num_layers, 2, num_pages, self.hkv, page, self.cfg.head_dim,
+                                    dtype=torch.bfloat16, device=self.device)
+        return self.kv_cache
+
+    # ------------------------------------------------------------------------------ forward
+    def _attn_scale(self) -> float:
+        s = self.cfg.attn_scale if self.cfg.attn_scale > 0 else 1.0 / math.sqrt(self.cfg.head_dim)
+        return s * self.rope_attn_factor * self.rope_attn_factor if self.rope_attn_factor != 1.0 else s
+
+    def _reduce_linear(self, x, w: LinearWeight) -> torch.Tensor:
+        """Row-parallel linear: local partial product, then sum over the TP group."""
+        if self.tp > 1 and self.row_parallel_linear is not None:
+            return self.row_parallel_linear(x, w)
+        y = ops.linear(x, w)
+        return self.all_reduce(y) if self.tp > 1 else y
+
+    def forward_hidden(self, batch: ForwardBatch) -> torch.Tensor:
+        """Runs all layers; returns the final-normed hidden states [T, H]."""
+        cfg = self.cfg
+        d = cfg.head_dim
+        if batch.embeds is not None:
+            x = batch.embeds
+        else:
+            x = ops.embedding(batch.tokens, self.embed, cfg.embed_scale * cfg.embedding_multiplier)
+        t = x.shape[0]
+        res: Optional[torch.Tensor] = None
+        scale = self._attn_scale()
+        fp8 = self.fp8 and x.is_cuda
+        for li, lw in enumerate(self.layers):
+            # ---- attention block
+            if res is None:
+                h, _, hq8 = ops.norm(x, lw.in_norm, eps=cfg.rms_eps, weight_plus_one=cfg.norm_plus_one,
+                                     emit_fp8=fp8 and lw.qkv is not None and lw.qkv.is_fp8, emit_bf16=True)
+                res = x
+            else:
+                h, res, hq8 = ops.norm(x, lw.in_norm, residual=res, eps=cfg.rms_eps,
+                                       weight_plus_one=cfg.norm_plus_one,
+                                       emit_fp8=fp8 and lw.qkv is not None and lw.qkv.is_fp8, emit_bf16=True)
+            if lw.attn_module is not None:
+                a = lw.attn_module(h, batch, li, self)
+            else:
+                qkv = ops.linear(hq8 if hq8 is not None else h, lw.qkv)
+                kc, vc = (self.kv_cache[li, 0], self.kv_cache[li, 1]) if self.kv_cache is not None else (None, None)
+                q, _, _ = ops.rope_kv(qkv, batch.positions, self.hq, self.hkv, d, k_cache=kc, v_cache=vc,
+                                      slot_mapping=batch.slot_mapping, rot=cfg.rotary_dim, theta=cfg.rope_theta,
+                                      inv_freq=self.inv_freq, style=cfg.rope_style, q_norm_w=lw.q_norm,
+                                      k_norm_w=lw.k_norm, eps=cfg.rms_eps)
+                window = cfg.layer_window(li)
+                if batch.is_decode:
+                    att = ops.attn_decode(q, kc, vc, batch.block_table, batch.kv_lens, scale=scale,
+                                          softcap=cfg.attn_softcap, window=window,
+                                          max_kv_len=batch.max_kv_len or None)
+                else:
+                    att = ops.attn_prefill_paged(q, kc, vc, batch.block_table, batch.kv_lens, batch.cu_q,
+                                                 batch.max_q_len, causal=True, scale=scale,
+                                                 softcap=cfg.attn_softcap, window=window)
+                a = self._reduce_linear(att.reshape(t, self.hq * d), lw.o)
+            if lw.post_attn_norm is not None:
+                a, _, _ = ops.norm(a, lw.post_attn_norm, eps=cfg.rms_eps, weight_plus_one=cfg.norm_plus_one)
+            if cfg.residual_multiplier != 1.0:
+                a = (a.float() * cfg.residual_multiplier).to(a.dtype)
+            # ---- feed-forward block
+            dense_fp8 = fp8 and lw.gate_up is not None and lw.gate_up.is_fp8
+            h2, res, h2q8 = ops.norm(a, lw.post_norm, residual=res, eps=cfg.rms_eps,
+                                     weight_plus_one=cfg.norm_plus_one, emit_fp8=dense_fp8, emit_bf16=True)
+            if lw.ffn_module is not None:
+                f = lw.ffn_module(h2, self)
+            else:
+                gu = ops.linear(h2q8 if h2q8 is not None else h2, lw.gate_up)
+                if cfg.gated_ffn:
+                    act, act8 = ops.glu(gu, cfg.activation, emit_fp8=fp8 and lw.down.is_fp8,
+                                        emit_bf16=not (fp8 and lw.down.is_fp8))
+                    f = self._reduce_linear(act8 if act8 is not None else act, lw.down)
+                else:
+                    f = self._reduce_linear(gu, lw.down)
+            if lw.post_ffn_norm is not None:
+                f, _, _ = ops.norm(f, lw.post_ffn_norm, eps=cfg.rms_eps, weight_plus_one=cfg.norm_plus_one)
+            if cfg.residual_multiplier != 1.0:
+                f = (f.float() * cfg.residual_multiplier).to(f.dtype)
+            x = f
+        out, _, _ = ops.norm(x, self.final_norm, residual=res, eps=cfg.rms_eps, weight_plus_one=cfg.norm_plus_one)
+        return out
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """[rows, H] -> local vocabulary shard logits [rows, vocab_local] (bf16)."""
+        y = ops.linear(hidden, self.lm_head)
+        cfg = self.cfg
+        if cfg.logits_scale != 1.0:
+            y = (y.float() * cfg.logits_scale).to(y.dtype)
+        if cfg.logit_softcap > 0:
+            y = (torch.tanh(y.float() / cfg.logit_softcap) * cfg.logit_softcap).to(y.dtype)
+        return y
+
+    def full_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Logits over the whole vocabulary (gathers the shards when tensor parallel)."""
+        y = self.logits(hidden)
+        if self.tp > 1:
+            y = self.comm.all_gather(y, dim=1)
+        return y[:, : self.cfg.vocab_size]
+
+    def greedy_tokens(self, hidden: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """argmax over the vocabulary; with TP each rank reduces its shard and the (value, index)
+        pairs are combined, so only 8 bytes per row and rank cross the wire."""
+        y = self.logits(hidden)
+        if self.tp == 1:
+            if y.shape[1] > self.cfg.vocab_size:
+                y = y[:, : self.cfg.vocab_size]
+            return ops.argmax(y, out)
+        v0 = self.tp_rank * self.vocab_local
+        valid = min(self.vocab_local, self.cfg.vocab_size - v0)
+        yl = y[:, :valid]
+        idx = ops.argmax(yl)
+        val = yl.float().gather(1, idx.long()[:, None])[:, 0]
+        packed = torch.stack([val, (idx + v0).float()], dim=1)          # [rows, 2]
+        allp = self.comm.all_gather(packed.unsqueeze(0), dim=0)         # [tp, rows, 2]
+        vals, ids = allp[..., 0], allp[..., 1]
+        best = vals.argmax(dim=0)                                       # first max -> lowest rank -> lowest id
+        tok = ids.gather(0, best[None])[0].to(torch.int32)
+        if out is not None:
+            out.copy_(tok)
+            return out
+        return tok

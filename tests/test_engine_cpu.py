@@ -1,0 +1,154 @@
+"""End-to-end engine tests on CPU with toy models: paged KV + scheduler + model forward."""
+import torch
+import pytest
+
+from hartsyinference_b200.engine import LLMEngine, SamplingParams
+from hartsyinference_b200.models.llm import config as C
+from hartsyinference_b200.models.llm.transformer import DecoderModel, ForwardBatch
+from hartsyinference_b200.ops import reference as R
+
+
+def _dense_reference(model: DecoderModel, tokens: list[int]) -> torch.Tensor:
+    """Independent fp32 forward (no paging, no fused ops) -> logits of the last position."""
+    cfg = model.cfg
+    x = model.embed[torch.tensor(tokens)].float() * cfg.embed_scale
+    t = len(tokens)
+    pos = torch.arange(t)
+    for lw in model.layers:
+        h = R.norm(x.to(torch.bfloat16), lw.in_norm, eps=cfg.rms_eps)[0]
+        qkv = h.to(torch.bfloat16).float() @ lw.qkv.weight.float().t()
+        if lw.qkv.bias is not None:
+            qkv = qkv + lw.qkv.bias.float()
+        qkv = qkv.to(torch.bfloat16).float().reshape(t, -1, cfg.head_dim)
+        q, k, v = qkv[:, :cfg.num_heads], qkv[:, cfg.num_heads:cfg.num_heads + cfg.num_kv_heads], qkv[:, cfg.num_heads + cfg.num_kv_heads:]
+        q = R.apply_rope(q, pos, model.inv_freq, cfg.rope_style).to(torch.bfloat16)
+        k = R.apply_rope(k, pos, model.inv_freq, cfg.rope_style).to(torch.bfloat16)
+        a = R.attention(q, k, v.to(torch.bfloat16), causal=True).to(torch.bfloat16).reshape(t, -1)
+        o = (a.float() @ lw.o.weight.float().t()).to(torch.bfloat16)
+        x = (o.float() + x.to(torch.bfloat16).float()).to(torch.bfloat16).float()
+        h2 = R.norm(x.to(torch.bfloat16), lw.post_norm, eps=cfg.rms_eps)[0].to(torch.bfloat16)
+        gu = (h2.float() @ lw.gate_up.weight.float().t()).to(torch.bfloat16)
+        act = R.glu(gu, cfg.activation).to(torch.bfloat16)
+        dn = (act.float() @ lw.down.weight.float().t()).to(torch.bfloat16)
+        x = (dn.float() + x).to(torch.bfloat16).float()
+    h = R.norm(x.to(torch.bfloat16), model.final_norm, eps=cfg.rms_eps)[0].to(torch.bfloat16)
+    return h[-1].float() @ model.lm_head.weight.float().t()
+
+
+def _toy(seed=0, **kw):
+    cfg = C.tiny(**kw)
+    m = DecoderModel(cfg, "cpu")
+    m.random_init(seed, std=0.05)
+    return m
+
+
+def test_prefill_logits_match_dense_reference():
+    m = _toy()
+    eng = LLMEngine(m, num_pages=64, page_size=16, max_batch=8, prefill_chunk=256, max_model_len=256)
+    torch.manual_seed(0)
+    toks = torch.randint(0, 512, (37,)).tolist()
+    # run the prefill through the engine path manually
+    eng.add_request(toks, SamplingParams(greedy=True, max_tokens=1))
+    ev = eng.step()
+    ref = _dense_reference(m, toks)
+    # bf16 rounding differs slightly between the fused and the unfused statement: accept a near tie
+    assert ref[ev[0][1]] >= ref.max() - 0.05
+
+
+def test_greedy_generation_matches_recompute_each_step():
+    m = _toy(seed=1)
+    eng = LLMEngine(m, num_pages=64, page_size=16, max_batch=8, prefill_chunk=64, max_model_len=256)
+    torch.manual_seed(1)
+    prompt = torch.randint(0, 512, (20,)).tolist()
+    out = eng.generate([prompt], SamplingParams(greedy=True, max_tokens=6, ignore_eos=True))[0]
+    seq = list(prompt)
+    for tok in out:
+        ref = _dense_reference(m, seq)
+        top2 = torch.topk(ref, 2).values
+        if (top2[0] - top2[1]) > 0.05:        # only compare well-separated decisions
+            assert tok == int(ref.argmax())
+        seq.append(tok)
+    assert len(out) == 6
+
+
+def test_chunked_prefill_equals_single_chunk():
+    m = _toy(seed=2)
+    torch.manual_seed(2)
+    prompt = torch.randint(0, 512, (90,)).tolist()
+    outs = []
+    for chunk in (256, 32):
+        eng = LLMEngine(m, num_pages=64, page_size=16, max_batch=4, prefill_chunk=chunk, max_model_len=256)
+        outs.append(eng.generate([prompt], SamplingParams(greedy=True, max_tokens=4, ignore_eos=True))[0])
+    assert outs[0] == outs[1]
+
+
+def test_continuous_batching_matches_sequential():
+    m = _toy(seed=3)
+    torch.manual_seed(3)
+    prompts = [torch.randint(0, 512, (n,)).tolist() for n in (5, 33, 17, 64, 9)]
+    p = SamplingParams(greedy=True, max_tokens=5, ignore_eos=True)
+    seq_out = []
+    for pr in prompts:
+        eng = LLMEngine(m, num_pages=64, page_size=16, max_batch=8, prefill_chunk=128, max_model_len=256)
+        seq_out.append(eng.generate([pr], p)[0])
+    eng = LLMEngine(m, num_pages=64, page_size=16, max_batch=8, prefill_chunk=128, max_model_len=256)
+    assert eng.generate(prompts, p) == seq_out
+
+
+def test_preemption_recompute_produces_same_tokens():
+    m = _toy(seed=4)
+    torch.manual_seed(4)
+    prompts = [torch.randint(0, 512, (30,)).tolist() for _ in range(4)]
+    p = SamplingParams(greedy=True, max_tokens=24, ignore_eos=True)
+    big = LLMEngine(m, num_pages=64, page_size=16, max_batch=8, prefill_chunk=128, max_model_len=128)
+    ref = big.generate(prompts, p)
+    small = LLMEngine(m, num_pages=11, page_size=16, max_batch=8, prefill_chunk=128, max_model_len=128)
+    got = small.generate(prompts, p)
+    assert small.stats()["preemptions"] > 0
+    assert got == ref
+    assert small.stats()["free_blocks"] == 11
+
+
+def test_fault_isolation_keeps_loop_alive():
+    m = _toy(seed=5)
+    eng = LLMEngine(m, num_pages=64, page_size=16, max_batch=8, prefill_chunk=128, max_model_len=128)
+    a = eng.add_request([1, 2, 3], SamplingParams(greedy=True, max_tokens=3, ignore_eos=True))
+    calls = {"n": 0}
+
+    def boom(where):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise RuntimeError("injected")
+
+    eng.fault_injector = boom
+    ev = eng.step()
+    assert ev == [(a, -1, True)] and eng.requests[a].finish_reason == "error"
+    b = eng.add_request([4, 5, 6], SamplingParams(greedy=True, max_tokens=3, ignore_eos=True))
+    eng.run_until_done()
+    assert eng.requests[b].finish_reason == "length" and len(eng.requests[b].output) == 3
+    assert eng.stats()["free_blocks"] == 64
+
+
+def test_sampling_params_seeded_and_stop():
+    m = _toy(seed=6)
+    eng = LLMEngine(m, num_pages=64, page_size=16, max_batch=8, prefill_chunk=128, max_model_len=128)
+    p = SamplingParams(temperature=0.8, top_k=20, top_p=0.9, min_p=0.01, repetition_penalty=1.1, seed=123,
+                       max_tokens=8, ignore_eos=True)
+    a = eng.generate([[5, 6, 7]], p)[0]
+    eng2 = LLMEngine(m, num_pages=64, page_size=16, max_batch=8, prefill_chunk=128, max_model_len=128)
+    b = eng2.generate([[5, 6, 7]], p)[0]
+    assert a == b and len(a) == 8
+    stop_tok = a[2]
+    eng3 = LLMEngine(m, num_pages=64, page_size=16, max_batch=8, prefill_chunk=128, max_model_len=128)
+    p2 = SamplingParams(temperature=0.8, top_k=20, top_p=0.9, min_p=0.01, repetition_penalty=1.1, seed=123,
+                        max_tokens=8, stop_token_ids=(stop_tok,))
+    c = eng3.generate([[5, 6, 7]], p2)[0]
+    assert c[-1] == stop_tok and len(c) <= 3
+
+
+def test_request_too_large_for_pool_is_rejected():
+    m = _toy(seed=7)
+    eng = LLMEngine(m, num_pages=4, page_size=16, max_batch=8, prefill_chunk=128, max_model_len=1024)
+    from hartsyinference_b200.exceptions import KvPoolExhaustedError
+    with pytest.raises(KvPoolExhaustedError):
+        eng.add_request(list(range(100)), SamplingParams(max_tokens=10))
