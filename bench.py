@@ -1,0 +1,259 @@
+#!/usr/bin/env python
+"""Headline benchmark: decode throughput of a Llama-3-70B-architecture model served with fp8
+(128x128 block-scaled) weights, tensor-parallel over N GPUs, continuous batching of 64 requests
+with 2048-token prompts and paged KV (16-token pages).
+
+    python bench.py --gpus N --steps K --warmup W          (N > 1: launched through torchrun)
+
+A "step" is one engine decode iteration for the whole batch (64 new tokens). The weights are
+random-init tensors of the named architecture and the prompts are uniform-random token ids
+(there is no network for checkpoints or datasets). The prompts are really prefilled, so the KV
+pool holds 2048+ tokens of context per request while the decode steps are timed.
+
+Two numbers come out of the same K timed steps, both through the public engine API
+(``LLMEngine.step``), which every step copies the batch metadata (token ids, positions, KV slots,
+block tables, lengths) from pinned host memory to the device and reads the sampled ids back:
+  * ``value``      tokens/s from CUDA-event device time of the steps (max over ranks),
+  * ``e2e.value``  tokens/s from host wall time around the K steps (max over ranks), i.e. including
+                   the scheduler, the host-side batch assembly and the synchronising read-back.
+``--impl reference`` reports that the reference cannot run here (it is a .NET solution; no .NET
+SDK exists on the build or the GPU machine and it has no Python packaging).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--preset", default="llama-3-70b", help="architecture preset (the headline is llama-3-70b)")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--decode-len", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
+    ap.add_argument("--bf16", action="store_true", help="debug only: bf16 weights instead of fp8")
+    ap.add_argument("--no-fused-comm", action="store_true", help="NCCL all-reduce instead of the fused kernels")
+    ap.add_argument("--no-graphs", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.samples.append([c.strip() for c in line.split(",")])
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        mhz, mx, reasons = [], None, set()
+        for s in self.samples:
+            try:
+                mhz.append(float(s[1]))
+                mx = float(s[2])
+                for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                                  ("sw_power_cap", 8)):
+                    if s[col].lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def run_reference(args) -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference is a C#/.NET solution without Python packaging (pip: no setup.py/pyproject.toml) "
+                       "and no .NET SDK exists on this machine, so its CUDA backend cannot be built or run",
+    }))
+    return 0
+
+
+def main() -> int:
+    args = parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    from hartsyinference_b200 import log
+    from hartsyinference_b200.engine import LLMEngine, SamplingParams
+    from hartsyinference_b200.models.llm import config as C
+    from hartsyinference_b200.models.llm.transformer import DecoderModel
+    from hartsyinference_b200.parallel import init_comm
+    from hartsyinference_b200.ops import _native as N
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world != args.gpus:
+        if args.gpus > 1 and world == 1:
+            # re-launch under torchrun when called directly with --gpus N
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29517"),
+                   os.path.abspath(__file__)] + sys.argv[1:]
+            return subprocess.call(cmd)
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    comm = init_comm()
+    if rank != 0:
+        import logging
+        log.logger.setLevel(logging.WARNING)
+
+    cfg = C.PRESETS[args.preset]
+    invalid = []
+    if args.layers:
+        from dataclasses import replace
+        cfg = replace(cfg, num_layers=args.layers)
+        invalid.append(f"layers={args.layers}")
+    if args.bf16:
+        invalid.append("bf16 weights")
+    t0 = time.perf_counter()
+    model = DecoderModel(cfg, device, comm=comm, fp8=not args.bf16)
+    model.random_init(seed=0)
+    fused = False
+    if world > 1 and not args.no_fused_comm:
+        try:
+            from hartsyinference_b200.parallel.fused import enable_fused_tp
+            fused = enable_fused_tp(model, comm, max_tokens=max(args.batch, 128))
+        except Exception as e:  # keep the run alive on NCCL, but say so
+            log.warn(f"[Collective] fused TP kernels unavailable ({type(e).__name__}: {e}); using NCCL")
+    torch.cuda.synchronize()
+    t_load = time.perf_counter() - t0
+
+    total_len = args.prompt_len + args.decode_len
+    page = 16
+    pages_per_seq = (total_len + page - 1) // page + 1
+    eng = LLMEngine(model, num_pages=args.batch * pages_per_seq + 8, page_size=page, max_batch=args.batch,
+                    prefill_chunk=8192, max_model_len=pages_per_seq * page, use_cuda_graphs=not args.no_graphs)
+    g = torch.Generator().manual_seed(1234)      # same prompts on every rank
+    prompts = torch.randint(0, cfg.vocab_size, (args.batch, args.prompt_len), generator=g).tolist()
+    params = SamplingParams(greedy=True, ignore_eos=True, max_tokens=args.decode_len)
+    for p in prompts:
+        eng.add_request(p, params)
+
+    # ---- prefill (untimed for the headline; reported as TTFT of the whole batch)
+    comm.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    first_token_times = []
+    while any(len(r.output) == 0 for r in eng.requests.values()):
+        eng.step()
+    torch.cuda.synchronize()
+    t_prefill = time.perf_counter() - t0
+    ttft = sorted(r.t_first_token - r.t_submit for r in eng.requests.values())
+    N.check_status(device)
+
+    steps_possible = args.decode_len - 1 - args.warmup
+    steps = min(args.steps, steps_possible)
+    for _ in range(args.warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    comm.barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    eng.time_steps = True
+    dev_ms = 0.0
+    launches = 0
+    h2d = d2h = 0
+    comm.barrier()
+    torch.cuda.synchronize()
+    w0 = time.perf_counter()
+    for _ in range(steps):
+        ev = eng.step()
+        dev_ms += eng.device_ms_last
+        launches += eng.kernel_launches_last
+        h2d += eng.h2d_bytes_last
+        d2h += eng.d2h_bytes_last
+        assert len(ev) == args.batch
+    torch.cuda.synchronize()
+    comm.barrier()
+    wall_ms = (time.perf_counter() - w0) * 1e3
+    clocks = sampler.stop() if rank == 0 else None
+    N.check_status(device)
+
+    t = torch.tensor([dev_ms, wall_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, wall_ms = t.tolist()
+    tokens = steps * args.batch
+    if rank == 0:
+        out = {
+            "metric": "decode tok/s (Llama-3-70B-architecture, fp8 128x128 block-scaled weights, TP=N, 64 x (2048 prompt + 256 decode), paged KV)",
+            "value": tokens / (dev_ms / 1e3),
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": steps,
+            "warmup": args.warmup,
+            "ms_per_step": dev_ms / steps,
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "fp8-e4m3 weights+activations (128x128 / 1x128 block scales), bf16 KV and accumulators out",
+            "data": "synthetic: random-init weights, uniform-random prompt token ids",
+            "config": {"model": args.preset, "global_batch": args.batch, "seq_len": args.prompt_len,
+                       "decode_len": args.decode_len, "parallelism": f"tp{world}", "kv_page": page,
+                       "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
+                       "cuda_graphs": not args.no_graphs, "fused_comm": fused,
+                       "invalid_debug_overrides": invalid},
+            "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "ms_per_step": wall_ms / steps,
+                    "h2d_bytes_per_step": h2d // steps, "d2h_bytes_per_step": d2h // steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "ttft_s": {"batch_prefill_wall": t_prefill, "median": ttft[len(ttft) // 2], "max": ttft[-1]},
+            "load_s": t_load,
+            "weight_bytes_per_gpu": model.weight_bytes(),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -36,7 +36,7 @@ struct AttnParams {
   const int* cu_kv;             // contiguous prefill: [seqs + 1] offsets into k/v
   float* ws_o;                  // split partials [seqs][hq][splits][d]
   float* ws_ml;                 // [seqs][hq][splits][2]
-  int seqs, hq, hkv, max_pages, page, splits;
+  int seqs, hq, hkv, max_pages, page, page_shift, splits;
   int q_len_single, kv_len_single;   // used when cu_q / kv_lens are null
   int causal, window;           // window <= 0: unlimited
   float scale_log2;             // softmax scale * log2(e)
@@ -83,22 +83,37 @@ __device__ __forceinline__ uint32_t tile_off(int token, int chunk) {
   return static_cast<uint32_t>(token * (D * 2) + ((chunk ^ (token & 7)) << 4));
 }
 
-// Loads one 64-token K or V tile. `row_ptr(t)` semantics are implemented by the two callers below.
+// Loads one 64-token K or V tile through the block table. The tile's page ids were staged in
+// shared memory (`pg`, 64 / page entries) an iteration earlier, so no cp.async waits on a
+// dependent global load of the table; page sizes are powers of two (8..64), so token -> (page,
+// offset) is a shift and a mask.
 template <int D>
 __device__ __forceinline__ void load_tile_paged(uint32_t smem_base, const __nv_bfloat16* pool,
-                                                const int* table, int kv_head, int hkv, int page,
+                                                const int* pg, int kv_head, int hkv, int page_shift,
                                                 int tok0, int kv_len) {
   constexpr int kChunks = D / 8;
+  const int page_mask = (1 << page_shift) - 1;
   for (int i = threadIdx.x; i < kTileTokens * kChunks; i += kAttnThreads) {
     const int t = i / kChunks, c = i % kChunks;
-    const int tok = tok0 + t;
-    const bool valid = tok < kv_len;
+    const bool valid = tok0 + t < kv_len;
     const __nv_bfloat16* src = pool;
     if (valid) {
-      const int pg = table[tok / page];
-      src = pool + ((static_cast<long long>(pg) * hkv + kv_head) * page + (tok % page)) * D + c * 8;
+      const long long pgi = pg[t >> page_shift];
+      src = pool + (((pgi * hkv + kv_head) << page_shift) + (t & page_mask)) * D + c * 8;
     }
     cp_async_16(smem_base + tile_off<D>(t, c), src, valid);
+  }
+}
+// Stages the page ids of tile `tile` into ring slot (tile & 3). Tiles start on page boundaries
+// because 64 is a multiple of every supported page size.
+__device__ __forceinline__ void stage_pages(int (*ring)[8], const int* table, int tile, int n_tiles,
+                                            int page_shift, int kv_len) {
+  const int per_tile = kTileTokens >> page_shift;
+  if (tile < n_tiles && threadIdx.x < per_tile) {
+    const int first = (tile * kTileTokens) >> page_shift;
+    const int idx = first + threadIdx.x;
+    const int last_page = (kv_len - 1) >> page_shift;
+    ring[tile & 3][threadIdx.x] = idx <= last_page ? table[idx] : 0;
   }
 }
 template <int D>
@@ -272,18 +287,26 @@ attn_decode_kernel(const AttnParams p) {
   const int start_key = p.window > 0 ? max(0, kv_len - p.window) : 0;
   const int start[2] = {start_key, start_key};
 
+  __shared__ int pg_ring[4][8];
   auto issue = [&](int tile, int stage) {
     if (tile < tile_end) {
       const uint32_t kb = smem_base + stage * 2 * kTileBytes;
-      load_tile_paged<D>(kb, p.k, table, kvh, p.hkv, p.page, tile * kTileTokens, kv_len);
-      load_tile_paged<D>(kb + kTileBytes, p.v, table, kvh, p.hkv, p.page, tile * kTileTokens, kv_len);
+      load_tile_paged<D>(kb, p.k, pg_ring[tile & 3], kvh, p.hkv, p.page_shift, tile * kTileTokens, kv_len);
+      load_tile_paged<D>(kb + kTileBytes, p.v, pg_ring[tile & 3], kvh, p.hkv, p.page_shift,
+                         tile * kTileTokens, kv_len);
     }
     cp_async_commit();
   };
+  stage_pages(pg_ring, table, tile_begin, tile_end, p.page_shift, kv_len);
+  stage_pages(pg_ring, table, tile_begin + 1, tile_end, p.page_shift, kv_len);
+  stage_pages(pg_ring, table, tile_begin + 2, tile_end, p.page_shift, kv_len);
+  __syncthreads();
   issue(tile_begin, 0);
   issue(tile_begin + 1, 1);
   int stage = 0;
   for (int tile = tile_begin; tile < tile_end; ++tile) {
+    // page ids of tile + 3 are read by issue() in the next iteration, after two barriers
+    stage_pages(pg_ring, table, tile + 3, tile_end, p.page_shift, kv_len);
     issue(tile + 2, (stage + 2) % kStages);
     cp_async_wait<2>();
     __syncthreads();
@@ -417,12 +440,14 @@ attn_prefill_kernel(const AttnParams p) {
   const __nv_bfloat16* kbase = kPaged ? p.k : p.k + (static_cast<long long>(kv_off) * p.hkv + kvh) * D;
   const __nv_bfloat16* vbase = kPaged ? p.v : p.v + (static_cast<long long>(kv_off) * p.hkv + kvh) * D;
 
+  __shared__ int pg_ring[4][8];
   auto issue = [&](int tile, int stage) {
     if (tile < n_tiles) {
       const uint32_t kb = smem_base + stage * 2 * kTileBytes;
       if (kPaged) {
-        load_tile_paged<D>(kb, p.k, table, kvh, p.hkv, p.page, tile * kTileTokens, kv_needed);
-        load_tile_paged<D>(kb + kTileBytes, p.v, table, kvh, p.hkv, p.page, tile * kTileTokens, kv_needed);
+        load_tile_paged<D>(kb, p.k, pg_ring[tile & 3], kvh, p.hkv, p.page_shift, tile * kTileTokens, kv_needed);
+        load_tile_paged<D>(kb + kTileBytes, p.v, pg_ring[tile & 3], kvh, p.hkv, p.page_shift,
+                           tile * kTileTokens, kv_needed);
       } else {
         load_tile_linear<D>(kb, kbase, kv_rs, tile * kTileTokens, kv_needed);
         load_tile_linear<D>(kb + kTileBytes, vbase, kv_rs, tile * kTileTokens, kv_needed);
@@ -430,9 +455,15 @@ attn_prefill_kernel(const AttnParams p) {
     }
     cp_async_commit();
   };
+  if (kPaged) {
+    stage_pages(pg_ring, table, tile0, n_tiles, p.page_shift, kv_needed);
+    stage_pages(pg_ring, table, tile0 + 1, n_tiles, p.page_shift, kv_needed);
+    __syncthreads();
+  }
   issue(tile0, 0);
   int stage = 0;
   for (int tile = tile0; tile < n_tiles; ++tile) {
+    if (kPaged) stage_pages(pg_ring, table, tile + 2, n_tiles, p.page_shift, kv_needed);
     issue(tile + 1, stage ^ 1);
     cp_async_wait<1>();
     __syncthreads();
@@ -476,7 +507,8 @@ B200_API int b200_attn_decode_pick_splits(int seqs, int hkv, int max_kv_len) {
   const int ctas = seqs * hkv;
   const int tiles = (max_kv_len + kTileTokens - 1) / kTileTokens;
   int splits = 1;
-  while (ctas * splits < 2 * 148 && splits * 2 <= tiles && splits < 16) splits *= 2;
+  // two CTAs fit per SM; aim for at least ~3 full waves so that the tail wave is cheap
+  while (ctas * splits < 6 * 148 && splits * 2 <= tiles && splits < 16) splits *= 2;
   return splits;
 }
 
@@ -496,6 +528,8 @@ B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_
   p.block_table = block_table;
   p.kv_lens = kv_lens;
   p.seqs = seqs; p.hq = hq; p.hkv = hkv; p.max_pages = max_pages; p.page = page;
+  p.page_shift = page == 8 ? 3 : page == 16 ? 4 : page == 32 ? 5 : page == 64 ? 6 : -1;
+  if (p.page_shift < 0) return -4;
   p.splits = splits < 1 ? 1 : splits;
   p.window = window;
   p.scale = scale;
@@ -549,6 +583,8 @@ B200_API int b200_attn_prefill(const void* q, const void* k, const void* v, void
   p.cu_q = cu_q;
   p.cu_kv = cu_kv;
   p.seqs = seqs; p.hq = hq; p.hkv = hkv; p.max_pages = max_pages; p.page = page; p.splits = 1;
+  p.page_shift = page == 8 ? 3 : page == 16 ? 4 : page == 32 ? 5 : page == 64 ? 6 : -1;
+  if (paged && p.page_shift < 0) return -4;
   p.q_len_single = q_len_single; p.kv_len_single = kv_len_single;
   p.causal = causal; p.window = window;
   p.scale = scale;

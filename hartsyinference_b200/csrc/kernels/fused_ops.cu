@@ -42,7 +42,7 @@ struct NormParams {
   const __nv_bfloat16* scale;     // optional AdaLN scale [batch][mod_stride]  -> y * (1 + scale) + shift
   __nv_bfloat16* out;             // optional bf16 output
   uint8_t* out_fp8;               // optional e4m3 output [rows][dim]
-  float* out_scale;               // [dim/128][rows] fp32, k-block-major
+  float* out_scale;               // [rows][dim/128] fp32
   int rows, dim, rows_per_batch, mod_stride;
   float eps;
   int layernorm;                  // 0 = RMSNorm, 1 = LayerNorm (mean-centred)
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(1024) norm_kernel(const NormParams p) {
         for (int i = 0; i < 4; ++i) hi |= static_cast<uint32_t>(to_e4m3(y[4 + i] * inv)) << (8 * i);
         *reinterpret_cast<uint2*>(p.out_fp8 + static_cast<long long>(row) * p.dim + vi * 8) =
             make_uint2(lo, hi);
-        if ((vi & 15) == 0) p.out_scale[static_cast<long long>(vi >> 4) * p.rows + row] = sc;
+        if ((vi & 15) == 0) p.out_scale[static_cast<long long>(row) * (p.dim >> 7) + (vi >> 4)] = sc;
       }
     }
   }
@@ -222,19 +222,18 @@ __global__ void quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* _
       for (int k = 0; k < 4; ++k) hi |= static_cast<uint32_t>(to_e4m3(v[4 + k] * inv)) << (8 * k);
       *reinterpret_cast<uint2*>(out + static_cast<long long>(row) * dim + grp * 128 + sub * 8) =
           make_uint2(lo, hi);
-      if (sub == 0) scales[static_cast<long long>(grp) * rows + row] = sc;
+      if (sub == 0) scales[static_cast<long long>(row) * groups + grp] = sc;
     }
   }
 }
 
 // Weight quantisation to e4m3 with one scale per 128 x 128 block. w [n][k] bf16 -> out [n][k] u8,
-// scales [k/128][ceil(n/128)] fp32. One CTA (256 threads) per block.
+// scales [ceil(n/128)][k/128] fp32. One CTA (256 threads) per block.
 __global__ void quant_fp8_weight_kernel(const __nv_bfloat16* __restrict__ w,
                                         uint8_t* __restrict__ out, float* __restrict__ scales,
                                         int n, int k) {
   __shared__ float red[32];
   const int nb = blockIdx.x, kb = blockIdx.y;
-  const int nblocks = gridDim.x;
   float amax = 0.f;
   for (int i = threadIdx.x; i < 128 * 16; i += blockDim.x) {
     const int r = nb * 128 + (i >> 4), c = kb * 128 + (i & 15) * 8;
@@ -255,7 +254,7 @@ __global__ void quant_fp8_weight_kernel(const __nv_bfloat16* __restrict__ w,
   for (int i = 0; i < (blockDim.x >> 5); ++i) amax = fmaxf(amax, red[i]);
   const float sc = fmaxf(amax, 1e-12f) / kFp8Max;
   const float inv = 1.f / sc;
-  if (threadIdx.x == 0) scales[static_cast<long long>(kb) * nblocks + nb] = sc;
+  if (threadIdx.x == 0) scales[static_cast<long long>(nb) * gridDim.y + kb] = sc;
   for (int i = threadIdx.x; i < 128 * 16; i += blockDim.x) {
     const int r = nb * 128 + (i >> 4), c = kb * 128 + (i & 15) * 8;
     if (r < n) {
@@ -329,7 +328,7 @@ __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* 
         for (int k = 0; k < 4; ++k) hi |= static_cast<uint32_t>(to_e4m3(y[4 + k] * inv)) << (8 * k);
         *reinterpret_cast<uint2*>(out_fp8 + static_cast<long long>(row) * f + vi * 8) =
             make_uint2(lo, hi);
-        if ((vi & 15) == 0) out_scale[static_cast<long long>(vi >> 4) * rows + row] = sc;
+        if ((vi & 15) == 0) out_scale[static_cast<long long>(row) * (f >> 7) + (vi >> 4)] = sc;
       }
     }
   }

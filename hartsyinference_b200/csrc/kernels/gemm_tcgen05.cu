@@ -20,12 +20,31 @@
 // (`swap_out = 1` then stores C transposed).
 //
 // fp8 block scaling (128 x 128 weight blocks, 1 x 128 activation groups): every 128-deep K block
-// is accumulated into its own TMEM buffer (two buffers alternate); the epilogue warps pull the
+// is accumulated into its own TMEM buffer (a ring of up to eight); the epilogue warps pull the
 // block out, multiply by scale_a(row, kb) * scale_b(col, kb) and add into fp32 registers while
 // the tensor core already works on the next block.
 #include "common.cuh"
 
 namespace b200 {
+
+// Fused GEMM -> all-reduce over NVLink peer memory (row-parallel linears of a tensor-parallel
+// group, token counts up to 128). All pointers are into the symmetric heap; index = rank.
+//   stage[r]      bf16 [world][tiles_per_rank][128 tokens][128 features]: partial tiles pushed by
+//                 every source rank into the rank that owns the tile's output columns
+//   out[r]        bf16 [tokens][ldc]: reduced result, written by the owner into every rank
+//   tile_flag[r]  u32 [tiles_per_rank]: arrivals of partials, monotonic (world per call)
+//   done[r]       u32: reduced tiles that have landed in rank r's out, monotonic
+//   epoch / fin   local u32 counters: calls completed; CTAs finished in the current call
+struct AllReduceParams {
+  __nv_bfloat16* stage[8];
+  __nv_bfloat16* out[8];
+  uint32_t* tile_flag[8];
+  uint32_t* done[8];
+  uint32_t* epoch;
+  uint32_t* fin;
+  int rank, world, tiles_per_rank;
+  long long wait_budget;   // cycles
+};
 
 struct GemmParams {
   int rows_a;          // rows of the A operand (tiled by 128)
@@ -43,11 +62,14 @@ struct GemmParams {
   const __nv_bfloat16* gate;      // per output feature multiplicative gate, may be null
   const __nv_bfloat16* residual;  // same layout as C, may be null
   int act;                        // 0 none, 1 gelu-tanh, 2 silu
-  // fp8 block scales, k-block-major: scale(row, kb) = s[kb * ld + row / gran]
+  // fp8 block scales, K-contiguous: scale(row, kb) = s[(row / gran) * ld + kb], ld = K / 128.
+  // A thread walks one row's scales along K, so consecutive k-blocks hit the same cache line.
   const float* scale_a;
   const float* scale_b;
   int sa_gran, sa_ld, sb_gran, sb_ld;
   DeviceStatus* status;
+  int debug;   // experiment switches, 0 in production
+  AllReduceParams ar;   // ar.world == 0: plain GEMM
 };
 
 constexpr int kTileA = 128;
@@ -62,6 +84,8 @@ struct alignas(8) GemmBarriers {
   uint64_t drain;
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t ar_flag;
+  uint32_t pad;
 };
 
 __device__ __forceinline__ float apply_epilogue(const GemmParams& p, float v, long long row,
@@ -75,10 +99,121 @@ __device__ __forceinline__ float apply_epilogue(const GemmParams& p, float v, lo
   return v;
 }
 
+
+// ---- peer signalling -------------------------------------------------------------------------
+__device__ __forceinline__ void red_release_sys_add(uint32_t* addr, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+// Spins until *addr >= target (wrap-safe) or the budget runs out. One thread calls this.
+__device__ __forceinline__ bool wait_flag_geq(const uint32_t* addr, uint32_t target, long long budget) {
+  long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (static_cast<int32_t>(ld_acquire_sys(addr) - target) >= 0) return true;
+    if ((++spins & 0x3f) == 0) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget) return false;
+    }
+  }
+}
+__device__ __forceinline__ void epilogue_barrier() {   // the 8 epilogue warps only
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
+// Partial tile -> staging buffer of the rank that owns these output columns.
+__device__ __forceinline__ void store_chunk_ar(const GemmParams& p, const float (&v)[32], int a_row,
+                                               int b0) {
+  const int ta = a_row >> 7;
+  const int owner = ta / p.ar.tiles_per_rank, tl = ta % p.ar.tiles_per_rank;
+  __nv_bfloat16* dst = p.ar.stage[owner] +
+      (static_cast<long long>(p.ar.rank * p.ar.tiles_per_rank + tl) * 128 + b0) * 128 + (a_row & 127);
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (b0 + j < p.rows_b) dst[j * 128] = __float2bfloat16(v[j]);
+}
+
+// All epilogue warps call this once their part of tile `ta` is stored.
+// The barrier is executed even after a failed wait (`ok` false) so that the eight warps never
+// disagree on the number of barrier calls; only the signal is suppressed then.
+__device__ __forceinline__ void ar_signal_tile(const GemmParams& p, int ta, bool ok) {
+  __threadfence_system();
+  epilogue_barrier();
+  if (ok && threadIdx.x == 64) {
+    const int owner = ta / p.ar.tiles_per_rank, tl = ta % p.ar.tiles_per_rank;
+    red_release_sys_add(p.ar.tile_flag[owner] + tl, 1u);
+  }
+}
+
+// Owner side: sum the `world` partials of tile `ta`, apply the epilogue, write the result into
+// every rank's output and count the tile as delivered there. Called by all epilogue warps.
+__device__ __forceinline__ bool ar_reduce_tile(const GemmParams& p, int ta, uint32_t epoch,
+                                               uint32_t* smem_flag) {
+  const int et = threadIdx.x - 64;   // 0..255
+  const int tl = ta % p.ar.tiles_per_rank;
+  if (et == 0) {
+    const bool ok = wait_flag_geq(p.ar.tile_flag[p.ar.rank] + tl, epoch * p.ar.world, p.ar.wait_budget);
+    if (!ok) report_status(p.status, kWaitTimeout, kKernelGemmAllReduce, 1, ta);
+    *smem_flag = ok ? 1u : 0u;
+  }
+  epilogue_barrier();
+  const bool ok = *smem_flag != 0;
+  epilogue_barrier();
+  if (ok) {
+    const int m = p.rows_b;
+    const int n0 = ta * 128;
+    const int ncols = min(128, p.rows_a - n0);
+    const __nv_bfloat16* st = p.ar.stage[p.ar.rank] + static_cast<long long>(tl) * 128 * 128;
+    const long long src_stride = static_cast<long long>(p.ar.tiles_per_rank) * 128 * 128;
+    for (int v = et; v < m * 16; v += 256) {
+      const int tok = v >> 4, f0 = (v & 15) * 8;
+      if (f0 >= ncols) continue;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int s = 0; s < p.ar.world; ++s) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(st + s * src_stride + tok * 128 + f0);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          acc[2 * i] += f.x;
+          acc[2 * i + 1] += f.y;
+        }
+      }
+      uint4 o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        ow[i] = pack_bf16x2(apply_epilogue(p, acc[2 * i], tok, n0 + f0 + 2 * i),
+                            apply_epilogue(p, acc[2 * i + 1], tok, n0 + f0 + 2 * i + 1));
+      const long long off = static_cast<long long>(tok) * p.ldc + n0 + f0;
+      for (int r = 0; r < p.ar.world; ++r) {
+        // start with the local copy's neighbour so that the ranks do not all hit rank 0 first
+        const int dst = (p.ar.rank + r) % p.ar.world;
+        *reinterpret_cast<uint4*>(p.ar.out[dst] + off) = o;
+      }
+    }
+  }
+  __threadfence_system();
+  epilogue_barrier();
+  if (ok && et < p.ar.world) red_release_sys_add(p.ar.done[et], 1u);
+  return ok;
+}
+
 // Stores 32 consecutive accumulator columns (B rows b0..b0+31) of A row `a_row`.
 __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[32], int a_row,
                                             int b0, int split) {
   if (a_row >= p.rows_a) return;
+  if (p.ar.world > 0) {
+    store_chunk_ar(p, v, a_row, b0);
+    return;
+  }
   if (p.out_fp32) {
     float* out = reinterpret_cast<float*>(p.out) + static_cast<long long>(split) * p.split_stride;
     if (!p.swap_out) {
@@ -126,13 +261,16 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
   }
 }
 
-template <bool kFp8, int BN>
+template <bool kFp8, int BN, int kAtoms>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a,
                     const __grid_constant__ CUtensorMap tm_b) {
-  constexpr int kStageBytesB = BN * 128;
-  constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-  constexpr int kElemsPerStage = kFp8 ? 128 : 64;   // K elements in 128 bytes
+  // A stage holds kAtoms swizzle atoms (128 bytes of K each) per operand: [A atoms][B atoms].
+  // Two atoms make every row's fetch 256 contiguous bytes issued back to back, which DRAM serves
+  // more efficiently than isolated 128-byte segments when the GEMM is bandwidth-bound.
+  constexpr int kAtomBytesB = BN * 128;
+  constexpr int kStageBytes = kAtoms * (kStageBytesA + kAtomBytesB);
+  constexpr int kElemsPerStage = kFp8 ? 128 : 64;   // K elements in one 128-byte atom
   // Accumulator ring in TMEM: as many buffers as fit in the 512 columns (at most 8). The
   // block-scaled path hands one buffer per 128-deep K block to the epilogue warps, so a deep ring
   // lets the tensor core run ahead of the promotion; the bf16 path uses one buffer per tile.
@@ -199,17 +337,20 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
         const int split = static_cast<int>(rest / tiles_b);
         const int kb0 = split * p.kblocks_per_split;
         const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += kAtoms) {
+          const int na = min(kAtoms, kb1 - kb);
           if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag)) {
             report_status(p.status, kWaitTimeout, kKernelGemm, 1, blockIdx.x);
             ok = false;
             break;
           }
           uint8_t* sa = smem + s * kStageBytes;
-          uint8_t* sb = sa + kStageBytesA;
-          mbar_arrive_expect_tx(&bars->full[s], kStageBytes);
-          tma_load_2d(sa, &tm_a, &bars->full[s], kb * kElemsPerStage, ta * kTileA);
-          tma_load_2d(sb, &tm_b, &bars->full[s], kb * kElemsPerStage, tb * BN);
+          uint8_t* sb = sa + kAtoms * kStageBytesA;
+          mbar_arrive_expect_tx(&bars->full[s], na * (kStageBytesA + kAtomBytesB));
+          for (int a = 0; a < na; ++a) {
+            tma_load_2d(sa + a * kStageBytesA, &tm_a, &bars->full[s], (kb + a) * kElemsPerStage, ta * kTileA);
+            tma_load_2d(sb + a * kAtomBytesB, &tm_b, &bars->full[s], (kb + a) * kElemsPerStage, tb * BN);
+          }
           ++issued;
           if (++s == stages) { s = 0; ph ^= 1; }
         }
@@ -247,39 +388,42 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           }
           tc_fence_after_sync();
         }
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1 && ok; kb += kAtoms) {
+          const int na = min(kAtoms, kb1 - kb);
           if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
             report_status(p.status, kWaitTimeout, kKernelGemm, 3, blockIdx.x);
             ok = false;
             break;
           }
-          if (kFp8) {
-            if (!mbar_wait(&bars->tmem_empty[abuf], aph ^ 1, abort_flag)) {
-              report_status(p.status, kWaitTimeout, kKernelGemm, 4, blockIdx.x);
-              ok = false;
-              break;
+          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const uint32_t sb = sa + kAtoms * kStageBytesA;
+          for (int a = 0; a < na; ++a) {
+            if (kFp8) {
+              if (!mbar_wait(&bars->tmem_empty[abuf], aph ^ 1, abort_flag)) {
+                report_status(p.status, kWaitTimeout, kKernelGemm, 4, blockIdx.x);
+                ok = false;
+                break;
+              }
+            }
+            tc_fence_after_sync();
+            const uint64_t adesc = make_desc_sw128(sa + a * kStageBytesA);
+            const uint64_t bdesc = make_desc_sw128(sb + a * kAtomBytesB);
+            const uint32_t d_tmem = tmem_base + abuf * kBufStride;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              // advancing 32 bytes along K inside the 128-byte swizzle atom = +2 in the
+              // (address >> 4) field of the descriptor
+              const uint32_t acc = kFp8 ? (k > 0) : (kb + a > kb0 || k > 0);
+              if (kFp8) mma_fp8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+              else      mma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            }
+            issued_any = true;
+            if (kFp8) {
+              tc_commit(&bars->tmem_full[abuf]);
+              if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
             }
           }
-          tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + s * kStageBytes);
-          const uint32_t sb = sa + kStageBytesA;
-          const uint64_t adesc = make_desc_sw128(sa);
-          const uint64_t bdesc = make_desc_sw128(sb);
-          const uint32_t d_tmem = tmem_base + abuf * kBufStride;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // advancing 32 bytes along K inside the 128-byte swizzle atom = +2 in the
-            // (address >> 4) field of the descriptor
-            const uint32_t acc = kFp8 ? (k > 0) : (kb > kb0 || k > 0);
-            if (kFp8) mma_fp8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
-            else      mma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
-          }
-          issued_any = true;
           tc_commit(&bars->empty[s]);
-          if (kFp8) {
-            tc_commit(&bars->tmem_full[abuf]);
-            if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
-          }
           if (++s == stages) { s = 0; ph ^= 1; }
         }
         if (!kFp8 && ok) {
@@ -305,18 +449,23 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
     int abuf = 0;
     uint32_t aph = 0;
     bool ok = true;
-    for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
+    for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
       const int ta = static_cast<int>(w % tiles_a);
       const long long rest = w / tiles_a;
       const int tb = static_cast<int>(rest % tiles_b);
       const int split = static_cast<int>(rest / tiles_b);
       const int a_row = ta * kTileA + q * 32 + lane;
       const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      if (!ok) {   // a wait failed earlier: keep the loop shape (barriers) but do no work
+        if (p.ar.world > 0) ar_signal_tile(p, ta, false);
+        continue;
+      }
       if constexpr (!kFp8) {
         if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[abuf], aph, abort_flag))) {
           if (lane == 0) report_status(p.status, kWaitTimeout, kKernelGemm, 5, blockIdx.x);
           ok = false;
-          break;
+          if (p.ar.world > 0) ar_signal_tile(p, ta, false);
+          continue;
         }
         tc_fence_after_sync();
 #pragma unroll 1
@@ -333,6 +482,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
         if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
+        if (p.ar.world > 0) ar_signal_tile(p, ta, true);
       } else {
         float acc[kMine * 32];
 #pragma unroll
@@ -346,13 +496,13 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
         // either one value per tile (128-wide weight blocks) or one value per column, in which case
         // lane l holds the scale of column (chunk * 32 + l) and it is broadcast with shuffles.
         auto load_row_scale = [&](int kb) {
-          return p.scale_a[static_cast<long long>(kb) * p.sa_ld + a_row_c / p.sa_gran];
+          return __ldg(p.scale_a + static_cast<long long>(a_row_c / p.sa_gran) * p.sa_ld + kb);
         };
         auto load_col_scale = [&](int kb, int i) {
-          const float* sbp = p.scale_b + static_cast<long long>(kb) * p.sb_ld;
-          if (!col_vector) return sbp[(tb * BN) / p.sb_gran];
+          if (!col_vector)
+            return __ldg(p.scale_b + static_cast<long long>((tb * BN) / p.sb_gran) * p.sb_ld + kb);
           const int col = min(tb * BN + (hsel + 2 * i) * 32 + lane, p.rows_b - 1);
-          return sbp[col];
+          return __ldg(p.scale_b + static_cast<long long>(col) * p.sb_ld + kb);
         };
         float sa_next = load_row_scale(kb0);
         float cs_next[kMine];
@@ -379,9 +529,17 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
             const int c = hsel + 2 * i;
             if (c < kChunks) {
               uint32_t r[32];
-              tmem_ld_32x32(lane_base + abuf * kBufStride + c * 32, r);
-              tmem_ld_wait();
-              if (!col_vector) {
+              if (p.debug & 2) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0;
+              } else {
+                tmem_ld_32x32(lane_base + abuf * kBufStride + c * 32, r);
+                tmem_ld_wait();
+              }
+              if (p.debug & 1) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[i * 32 + j] += __uint_as_float(r[j]);
+              } else if (!col_vector) {
                 const float sc = sa * cs[i];
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
@@ -412,6 +570,20 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
             }
           }
         }
+        if (p.ar.world > 0) ar_signal_tile(p, ta, ok);
+      }
+    }
+    if (p.ar.world > 0) {
+      // ---- reduce phase: tiles whose output columns this rank owns, then wait until every
+      // reduced tile of this call has landed in the local output.
+      const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1u;
+      for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
+        const int ta = static_cast<int>(w % tiles_a);
+        if (ta / p.ar.tiles_per_rank == p.ar.rank) ok &= ar_reduce_tile(p, ta, epoch, &bars->ar_flag);
+      }
+      if (threadIdx.x == 64) {
+        if (!wait_flag_geq(p.ar.done[p.ar.rank], epoch * static_cast<uint32_t>(tiles_a), p.ar.wait_budget))
+          report_status(p.status, kWaitTimeout, kKernelGemmAllReduce, 2, blockIdx.x);
       }
     }
   }
@@ -423,6 +595,16 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (p.ar.world > 0 && threadIdx.x == 0) {
+    // the last CTA to finish closes the call: every CTA has read the old epoch by now
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch);
+    __threadfence();
+    if (atomicAdd(p.ar.fin, 1u) == gridDim.x - 1) {
+      *p.ar.fin = 0;
+      *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) = e + 1u;
+      __threadfence();
+    }
   }
 }
 
@@ -480,19 +662,19 @@ int make_kmajor_map(CUtensorMap* out, const void* base, int elem_bytes, long lon
   return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 100;
 }
 
-template <bool kFp8, int BN>
+template <bool kFp8, int BN, int kAtoms>
 int launch_gemm(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, int grid,
                 cudaStream_t stream) {
-  const int stage_bytes = kStageBytesA + BN * 128;
+  const int stage_bytes = kAtoms * (kStageBytesA + BN * 128);
   const int smem = p.stages * stage_bytes + static_cast<int>(sizeof(GemmBarriers)) + 1024;
   static int configured = 0;
   if (configured < smem) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<kFp8, BN>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<kFp8, BN, kAtoms>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
     if (e != cudaSuccess) return -static_cast<int>(e) - 200;
     configured = 232448;
   }
-  gemm_tcgen05_kernel<kFp8, BN><<<grid, kGemmThreads, smem, stream>>>(p, ta, tb);
+  gemm_tcgen05_kernel<kFp8, BN, kAtoms><<<grid, kGemmThreads, smem, stream>>>(p, ta, tb);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 300;
 }
@@ -511,6 +693,9 @@ int num_sms() {
 }  // namespace b200
 
 using namespace b200;
+
+static int g_gemm_debug = 0;
+B200_API void b200_gemm_set_debug(int v) { g_gemm_debug = v; }
 
 // Workspace needed by b200_gemm for the chosen split count (bytes of fp32 partials), 0 if no split.
 B200_API long long b200_gemm_workspace_bytes(int m, int n, int splits) {
@@ -533,14 +718,14 @@ B200_API int b200_gemm_pick_splits(int m, int n, int k, int is_fp8) {
 
 // out[m][n] (bf16, leading dim ldc) = epilogue(x[m][k] * w[n][k]^T)
 //   dtype: 0 = bf16 operands, 1 = fp8 e4m3 operands with block scales
-//   x_scale: [k/128][m] fp32 (per token, per 128-wide K group); w_scale: [k/128][ceil(n/128)] fp32
+//   x_scale: [m][k/128] fp32 (per token, per 128-wide K group); w_scale: [ceil(n/128)][k/128] fp32
 //   workspace: fp32 scratch of b200_gemm_workspace_bytes() when splits > 1
 // Returns 0 on success, negative on a launch-time error.
-B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
-                       long long ldw, long long ldc, int dtype, const float* x_scale,
-                       const float* w_scale, const void* bias, const void* gate,
-                       const void* residual, int act, int splits, void* workspace,
-                       void* status, cudaStream_t stream) {
+static int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
+                     long long ldw, long long ldc, int dtype, const float* x_scale,
+                     const float* w_scale, const void* bias, const void* gate, const void* residual,
+                     int act, int splits, void* workspace, void* status, cudaStream_t stream,
+                     const AllReduceParams* ar) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   const bool fp8 = dtype == 1;
   const int esz = fp8 ? 1 : 2;
@@ -561,6 +746,13 @@ B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, in
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.act = act;
   p.status = static_cast<DeviceStatus*>(status);
+  p.debug = g_gemm_debug;
+  if (ar != nullptr) {
+    if (m > 128 || n % (128 * ar->world) != 0) return -6;   // one token tile; whole tiles per owner
+    p.ar = *ar;
+    p.ar.tiles_per_rank = n / 128 / ar->world;
+    splits = 1;
+  }
   p.swap_out = swap ? 1 : 0;
   const int total_kblocks = (k + kelems - 1) / kelems;
   if (splits < 1) splits = 1;
@@ -583,17 +775,19 @@ B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, in
     p.rows_a = n; p.rows_b = m;
     a_ptr = w; lda = ldw; b_ptr = x; ldb = ldx;
     bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
-    p.scale_a = w_scale; p.sa_gran = 128; p.sa_ld = (n + 127) / 128;
-    p.scale_b = x_scale; p.sb_gran = 1;   p.sb_ld = m;
+    p.scale_a = w_scale; p.sa_gran = 128; p.sa_ld = k / 128;
+    p.scale_b = x_scale; p.sb_gran = 1;   p.sb_ld = k / 128;
   } else {
     p.rows_a = m; p.rows_b = n;
     a_ptr = x; lda = ldx; b_ptr = w; ldb = ldw;
     bn = fp8 ? 128 : 256;
     if (!fp8 && n <= 128) bn = 128;
-    p.scale_a = x_scale; p.sa_gran = 1;   p.sa_ld = m;
-    p.scale_b = w_scale; p.sb_gran = 128; p.sb_ld = (n + 127) / 128;
+    p.scale_a = x_scale; p.sa_gran = 1;   p.sa_ld = k / 128;
+    p.scale_b = w_scale; p.sb_gran = 128; p.sb_ld = k / 128;
   }
-  const int stage_bytes = kStageBytesA + bn * 128;
+  // two atoms per stage for the bandwidth-bound small-token orientation
+  const int atoms = swap ? 2 : 1;
+  const int stage_bytes = atoms * (kStageBytesA + bn * 128);
   int stages = (200 * 1024) / stage_bytes;
   if (stages > 12) stages = 12;
   p.stages = stages;
@@ -609,19 +803,28 @@ B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, in
   const int grid = static_cast<int>(tiles < num_sms() ? tiles : num_sms());
 
   if (fp8) {
-    switch (bn) {
-      case 16: rc = launch_gemm<true, 16>(p, ta, tb, grid, stream); break;
-      case 32: rc = launch_gemm<true, 32>(p, ta, tb, grid, stream); break;
-      case 64: rc = launch_gemm<true, 64>(p, ta, tb, grid, stream); break;
-      default: rc = launch_gemm<true, 128>(p, ta, tb, grid, stream); break;
+    if (swap) {
+      switch (bn) {
+        case 16: rc = launch_gemm<true, 16, 2>(p, ta, tb, grid, stream); break;
+        case 32: rc = launch_gemm<true, 32, 2>(p, ta, tb, grid, stream); break;
+        case 64: rc = launch_gemm<true, 64, 2>(p, ta, tb, grid, stream); break;
+        default: rc = launch_gemm<true, 128, 2>(p, ta, tb, grid, stream); break;
+      }
+    } else {
+      rc = launch_gemm<true, 128, 1>(p, ta, tb, grid, stream);
     }
   } else {
-    switch (bn) {
-      case 16: rc = launch_gemm<false, 16>(p, ta, tb, grid, stream); break;
-      case 32: rc = launch_gemm<false, 32>(p, ta, tb, grid, stream); break;
-      case 64: rc = launch_gemm<false, 64>(p, ta, tb, grid, stream); break;
-      case 128: rc = launch_gemm<false, 128>(p, ta, tb, grid, stream); break;
-      default: rc = launch_gemm<false, 256>(p, ta, tb, grid, stream); break;
+    if (swap) {
+      switch (bn) {
+        case 16: rc = launch_gemm<false, 16, 2>(p, ta, tb, grid, stream); break;
+        case 32: rc = launch_gemm<false, 32, 2>(p, ta, tb, grid, stream); break;
+        case 64: rc = launch_gemm<false, 64, 2>(p, ta, tb, grid, stream); break;
+        default: rc = launch_gemm<false, 128, 2>(p, ta, tb, grid, stream); break;
+      }
+    } else if (bn == 128) {
+      rc = launch_gemm<false, 128, 1>(p, ta, tb, grid, stream);
+    } else {
+      rc = launch_gemm<false, 256, 1>(p, ta, tb, grid, stream);
     }
   }
   if (rc) return rc;
@@ -638,4 +841,45 @@ B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, in
     if (e != cudaSuccess) return -static_cast<int>(e) - 400;
   }
   return 0;
+}
+
+B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
+                       long long ldw, long long ldc, int dtype, const float* x_scale,
+                       const float* w_scale, const void* bias, const void* gate,
+                       const void* residual, int act, int splits, void* workspace,
+                       void* status, cudaStream_t stream) {
+  return gemm_impl(x, w, out, m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, gate, residual,
+                   act, splits, workspace, status, stream, nullptr);
+}
+
+// Row-parallel linear of a tensor-parallel group fused with the all-reduce of its output:
+//   out_r[m][n] = epilogue(sum over ranks of x_r[m][k_r] * w_r[n][k_r]^T)   on every rank r
+// for m <= 128 tokens. `stage`, `out`, `tile_flag`, `done` are arrays of `world` peer pointers into
+// the symmetric heap (see AllReduceParams); `epoch` and `fin` are local u32 counters that start at
+// zero. Partials cross NVLink once as bf16 (push to the owner of each 128-column tile), the owner
+// reduces in fp32, applies bias / activation / gate / residual and pushes the bf16 result to every
+// rank. The kernel returns on a rank only after all tiles of its output have landed. Every wait on
+// a peer is bounded by `wait_budget_cycles` and reports through `status`.
+B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int k, long long ldx,
+                                 long long ldw, long long ldc, int dtype, const float* x_scale,
+                                 const float* w_scale, const void* bias, const void* gate,
+                                 const void* residual, int act, void* const* stage,
+                                 void* const* out, void* const* tile_flag, void* const* done,
+                                 void* epoch, void* fin, int rank, int world,
+                                 long long wait_budget_cycles, void* status, cudaStream_t stream) {
+  if (world < 1 || world > 8) return -7;
+  AllReduceParams ar{};
+  for (int r = 0; r < world; ++r) {
+    ar.stage[r] = static_cast<__nv_bfloat16*>(stage[r]);
+    ar.out[r] = static_cast<__nv_bfloat16*>(out[r]);
+    ar.tile_flag[r] = static_cast<uint32_t*>(tile_flag[r]);
+    ar.done[r] = static_cast<uint32_t*>(done[r]);
+  }
+  ar.epoch = static_cast<uint32_t*>(epoch);
+  ar.fin = static_cast<uint32_t*>(fin);
+  ar.rank = rank;
+  ar.world = world;
+  ar.wait_budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
+  return gemm_impl(x, w, out[rank], m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, gate,
+                   residual, act, 1, nullptr, status, stream, &ar);
 }

@@ -92,6 +92,9 @@ class LLMEngine:
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         self.kernel_launches_last = 0
+        self.time_steps = False          # record device time of every step with CUDA events
+        self.device_ms_last = 0.0
+        self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) if self.cuda else None
         pin = self.cuda
         mp = self.max_pages_per_seq
         cap_tokens = max(self.prefill_chunk, self.max_batch)
@@ -267,7 +270,8 @@ class LLMEngine:
         if entry is None:
             entry = self._capture(bucket)
             self._graphs[bucket] = entry
-        graph, st = entry
+        graph, st, launches = entry
+        self.kernel_launches_last += launches
         mp = self.max_pages_per_seq
         st["tokens"].copy_(self.h_tokens[:bucket], non_blocking=True)
         st["positions"].copy_(self.h_positions[:bucket], non_blocking=True)
@@ -309,16 +313,22 @@ class LLMEngine:
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
+        before = N.launch_count
         with torch.cuda.graph(g):
             run()
-        log.debug(f"[Engine] captured decode graph for batch {bucket}")
-        return g, st
+        launches = N.launch_count - before
+        log.debug(f"[Engine] captured decode graph for batch {bucket} ({launches} kernel launches)")
+        return g, st, launches
 
     # ------------------------------------------------------------------------------- step loop
     def step(self) -> list[tuple[int, int, bool]]:
         """One engine iteration. Returns [(request id, new token, finished)]."""
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
+        self.kernel_launches_last = 0
+        launches_before = N.launch_count
+        if self.time_steps and self.cuda:
+            self._ev[0].record()
         prefill, decode, preempted = self.sched.step()
         for rid in preempted:
             log.debug(f"[Engine] request {rid} pre-empted (KV pool full), will recompute")
@@ -375,6 +385,11 @@ class LLMEngine:
                     if req.on_token is not None:
                         req.on_token(rid, -1, True)
         self.steps += 1
+        self.kernel_launches_last += N.launch_count - launches_before
+        if self.time_steps and self.cuda:
+            self._ev[1].record()
+            self._ev[1].synchronize()
+            self.device_ms_last = self._ev[0].elapsed_time(self._ev[1])
         return events
 
     def run_until_done(self, max_steps: int = 1 << 30) -> None:

@@ -205,7 +205,7 @@ class DecoderModel:
             if self.fp8 and allow_fp8 and k % 128 == 0:
                 w = torch.empty(n, k, dtype=torch.uint8, device=dev)
                 ops.fill_random_(w, counter[0])
-                sc = torch.full((k // 128, (n + 127) // 128), std / 112.0, dtype=torch.float32, device=dev)
+                sc = torch.full(((n + 127) // 128, k // 128), std / 112.0, dtype=torch.float32, device=dev)
                 b = dense(1, n).reshape(n) if bias else None
                 return LinearWeight(w, sc, b)
             b = dense(1, n).reshape(n) if bias else None

@@ -91,9 +91,15 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def check(rc: int, what: str) -> None:
+# number of kernels of this library launched so far by this process (ops report their own count)
+launch_count = 0
+
+
+def check(rc: int, what: str, launches: int = 1) -> None:
+    global launch_count
     if rc != 0:
         raise NativeLibraryError(f"{what} failed with code {rc}")
+    launch_count += launches
 
 
 class _DeviceState:

@@ -15,7 +15,7 @@ _ACT = {None: 0, "none": 0, "gelu_tanh": 1, "silu": 2}
 
 @dataclass
 class Fp8Act:
-    """e4m3 activations [M, K] (uint8 storage) with 1x128 scales stored k-block-major [K/128, M]."""
+    """e4m3 activations [M, K] (uint8 storage) with 1x128 scales [M, K/128]."""
     data: torch.Tensor
     scale: torch.Tensor
 
@@ -27,7 +27,7 @@ class Fp8Act:
 @dataclass
 class LinearWeight:
     """Weight of a linear layer, [N, K] K-major. bf16, or e4m3 bytes with 128x128 block scales
-    stored k-block-major [K/128, ceil(N/128)]."""
+    [ceil(N/128), K/128]."""
     weight: torch.Tensor
     scale: Optional[torch.Tensor] = None
     bias: Optional[torch.Tensor] = None
@@ -70,20 +70,20 @@ def quant_fp8_act(x: torch.Tensor) -> Fp8Act:
     m, k = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1
     q = torch.empty(m, k, dtype=torch.uint8, device=x.device)
-    s = torch.empty(k // 128, m, dtype=torch.float32, device=x.device)
+    s = torch.empty(m, k // 128, dtype=torch.float32, device=x.device)
     N.check(N.lib().b200_quant_fp8(x.data_ptr(), q.data_ptr(), s.data_ptr(), m, k, x.stride(0), N.stream()),
             "b200_quant_fp8")
     return Fp8Act(q, s)
 
 
 def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """bf16 [N, K] -> (e4m3 bytes, scales [K/128, ceil(N/128)]) with one scale per 128x128 block."""
+    """bf16 [N, K] -> (e4m3 bytes, scales [ceil(N/128), K/128]) with one scale per 128x128 block."""
     if not w.is_cuda:
         return R.quant_fp8_weight(w)
     n, k = w.shape
     w = w.to(torch.bfloat16).contiguous()
     q = torch.empty(n, k, dtype=torch.uint8, device=w.device)
-    s = torch.empty(k // 128, (n + 127) // 128, dtype=torch.float32, device=w.device)
+    s = torch.empty((n + 127) // 128, k // 128, dtype=torch.float32, device=w.device)
     N.check(N.lib().b200_quant_fp8_weight(w.data_ptr(), q.data_ptr(), s.data_ptr(), n, k, N.stream()),
             "b200_quant_fp8_weight")
     return q, s
@@ -134,7 +134,7 @@ def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.T
                      x.scale.data_ptr() if fp8 else None, w.scale.data_ptr() if fp8 else None,
                      N.ptr(w.bias), N.ptr(gate), N.ptr(residual), _ACT[act], splits, ws,
                      st.status.data_ptr(), N.stream())
-    N.check(rc, "b200_gemm")
+    N.check(rc, "b200_gemm", 2 if splits > 1 else 1)
     return out
 
 
@@ -164,7 +164,7 @@ def norm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, *, bias: Option
     q = s = None
     if emit_fp8:
         q = torch.empty(rows, dim, dtype=torch.uint8, device=x.device)
-        s = torch.empty(dim // 128, rows, dtype=torch.float32, device=x.device)
+        s = torch.empty(rows, dim // 128, dtype=torch.float32, device=x.device)
     mod_stride = 0
     if shift is not None or scale is not None:
         ref = shift if shift is not None else scale
@@ -193,7 +193,7 @@ def glu(x: torch.Tensor, act: str = "silu", emit_fp8: bool = False, emit_bf16: b
     q = s = None
     if emit_fp8:
         q = torch.empty(rows, f, dtype=torch.uint8, device=x.device)
-        s = torch.empty(f // 128, rows, dtype=torch.float32, device=x.device)
+        s = torch.empty(rows, f // 128, dtype=torch.float32, device=x.device)
     rc = N.lib().b200_glu(x.data_ptr(), N.ptr(y), N.ptr(q), N.ptr(s), rows, f, 0 if act == "silu" else 1, N.stream())
     N.check(rc, "b200_glu")
     return y, (Fp8Act(q, s) if emit_fp8 else None)
@@ -272,7 +272,7 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
     rc = L.b200_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                             block_table.data_ptr(), kv_lens.data_ptr(), b, hq, hkv, d, page,
                             block_table.shape[1], splits, ws, scale, softcap, window, N.stream())
-    N.check(rc, "b200_attn_decode")
+    N.check(rc, "b200_attn_decode", 2 if splits > 1 else 1)
     return out
 
 

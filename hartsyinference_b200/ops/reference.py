@@ -19,18 +19,18 @@ FP8_MAX = 448.0
 # quantisation
 # --------------------------------------------------------------------------------------------
 def quant_fp8_act(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """1x128 block quantisation of activations [M, K] -> (e4m3 bytes [M, K], scales [K/128, M])."""
+    """1x128 block quantisation of activations [M, K] -> (e4m3 bytes [M, K], scales [M, K/128])."""
     m, k = x.shape
     assert k % 128 == 0
     xf = x.float().reshape(m, k // 128, 128)
     amax = xf.abs().amax(dim=-1).clamp_min(1e-12)
     scale = amax / FP8_MAX
     q = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
-    return q.reshape(m, k).view(torch.uint8), scale.t().contiguous()
+    return q.reshape(m, k).view(torch.uint8), scale.contiguous()
 
 
 def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """128x128 block quantisation of a weight [N, K] -> (bytes [N, K], scales [K/128, ceil(N/128)])."""
+    """128x128 block quantisation of a weight [N, K] -> (bytes [N, K], scales [ceil(N/128), K/128])."""
     n, k = w.shape
     assert k % 128 == 0
     nb = (n + 127) // 128
@@ -41,19 +41,18 @@ def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     scale = amax / FP8_MAX
     q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     q = q.reshape(nb * 128, k)[:n]
-    return q.contiguous().view(torch.uint8), scale.t().contiguous()
+    return q.contiguous().view(torch.uint8), scale.contiguous()
 
 
 def dequant_fp8_act(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     m, k = q.shape
     f = q.view(torch.float8_e4m3fn).float().reshape(m, k // 128, 128)
-    return (f * scale.t().unsqueeze(-1)).reshape(m, k)
+    return (f * scale.unsqueeze(-1)).reshape(m, k)
 
 
 def dequant_fp8_weight(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     n, k = q.shape
-    s = scale.t()                                                # [nb, kb]
-    s = s.repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)
+    s = scale.repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)
     return q.view(torch.float8_e4m3fn).float() * s
 
 

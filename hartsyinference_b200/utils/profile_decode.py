@@ -1,0 +1,69 @@
+"""Profile one decode step of the serving engine.
+
+    python -m hartsyinference_b200.utils.profile_decode --preset llama-3-8b --batch 64 --prompt-len 2048
+
+Builds a random-init model, prefills ``batch`` prompts, runs a few decode steps, then runs ONE
+eager (graph-free) decode step inside a cudaProfilerStart/Stop window so that
+``ncu --profile-from-start off --metrics gpu__time_duration.sum`` lists exactly the kernels of one
+step. Without a profiler attached it prints the per-op device-time table instead.
+"""
+from __future__ import annotations
+
+import argparse
+from dataclasses import replace
+
+import torch
+
+from .. import config
+from ..engine import LLMEngine, SamplingParams
+from ..models.llm import config as C
+from ..models.llm.transformer import DecoderModel
+from . import profiling
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--preset", default="llama-3-8b")
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--bf16", action="store_true")
+    ap.add_argument("--tp-shard", type=int, default=1, help="build the 1/N tensor-parallel shard shapes on one GPU")
+    args = ap.parse_args()
+    cfg = C.PRESETS[args.preset]
+    if args.layers:
+        cfg = replace(cfg, num_layers=args.layers)
+    if args.tp_shard > 1:   # same per-GPU GEMM / attention shapes as rank 0 of a TP group (no collectives)
+        n = args.tp_shard
+        cfg = replace(cfg, num_heads=cfg.num_heads // n, num_kv_heads=max(1, cfg.num_kv_heads // n),
+                      ffn_size=cfg.ffn_size // n)
+    dev = torch.device("cuda", 0)
+    model = DecoderModel(cfg, dev, fp8=not args.bf16)
+    if args.tp_shard > 1:
+        # keep the hidden size of the full model: q/o projections use num_heads * head_dim columns
+        pass
+    model.random_init(0)
+    total = args.prompt_len + 64
+    pages = (total + 15) // 16 + 1
+    eng = LLMEngine(model, num_pages=args.batch * pages + 8, page_size=16, max_batch=args.batch, prefill_chunk=8192,
+                    max_model_len=pages * 16, use_cuda_graphs=False)
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab_size, (args.batch, args.prompt_len), generator=g).tolist()
+    for p in prompts:
+        eng.add_request(p, SamplingParams(greedy=True, ignore_eos=True, max_tokens=32))
+    while any(len(r.output) == 0 for r in eng.requests.values()):
+        eng.step()
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    config.set_override("profile", True)
+    profiling.reset_profile()
+    eng.time_steps = True
+    with profiling.capture_window():
+        eng.step()
+    print(f"decode step device time: {eng.device_ms_last:.3f} ms, launches: {eng.kernel_launches_last}")
+    print(profiling.dump_profile())
+
+
+if __name__ == "__main__":
+    main()

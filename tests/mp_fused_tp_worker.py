@@ -1,0 +1,103 @@
+"""Worker of the multi-GPU fused tensor-parallel test (one process per GPU under torchrun).
+
+Checks (1) the fused GEMM+all-reduce kernel against a NCCL all-reduce of the plain GEMM and
+(2) that a tensor-parallel toy decoder produces the same logits as the single-GPU model built from
+the same full weights, through both the NCCL path and the fused path."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+from hartsyinference_b200 import ops
+from hartsyinference_b200.models.llm import config as C
+from hartsyinference_b200.models.llm.transformer import DecoderModel, ForwardBatch
+from hartsyinference_b200.ops import _native as N
+from hartsyinference_b200.parallel import init_comm
+from hartsyinference_b200.parallel.fused import FusedRowParallel, enable_fused_tp
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item()
+
+
+def main():
+    comm = init_comm()
+    rank, world = comm.rank, comm.world
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.manual_seed(100 + rank)
+    fused = FusedRowParallel(comm, 2048, dev)
+    for fp8 in (False, True):
+        for m in (64, 5, 128):
+            n, k = 2048, 512
+            x = (torch.randn(m, k, device=dev) * 0.5).to(torch.bfloat16)
+            w = ops.LinearWeight.from_dense((torch.randn(n, k, device=dev) * 0.2).to(torch.bfloat16), fp8=fp8)
+            res = torch.randn(m, n, device=dev).to(torch.bfloat16)
+            dist.broadcast(res, 0)
+            y = fused(x, w, residual=res).clone()
+            part = ops.linear(x, w, splits=1).float()
+            dist.all_reduce(part)
+            ref = part + res.float()
+            N.check_status(dev)
+            e = rel(y, ref)
+            assert e < 1.5e-2, (fp8, m, e)
+    # ---- TP model vs single-GPU model
+    cfg = C.tiny("llama-3-70b", vocab_size=1024, hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=2,
+                 head_dim=128, ffn_size=1024)
+    g = torch.Generator().manual_seed(7)
+    full = {}
+
+    def mk(name, *shape, std=0.05):
+        full[name] = (torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
+
+    mk("model.embed_tokens.weight", cfg.vocab_size, cfg.hidden_size)
+    mk("lm_head.weight", cfg.vocab_size, cfg.hidden_size)
+    full["model.norm.weight"] = torch.ones(cfg.hidden_size, dtype=torch.bfloat16)
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}."
+        mk(p + "self_attn.q_proj.weight", cfg.q_size, cfg.hidden_size)
+        mk(p + "self_attn.k_proj.weight", cfg.kv_size, cfg.hidden_size)
+        mk(p + "self_attn.v_proj.weight", cfg.kv_size, cfg.hidden_size)
+        mk(p + "self_attn.o_proj.weight", cfg.hidden_size, cfg.q_size)
+        mk(p + "mlp.gate_proj.weight", cfg.ffn_size, cfg.hidden_size)
+        mk(p + "mlp.up_proj.weight", cfg.ffn_size, cfg.hidden_size)
+        mk(p + "mlp.down_proj.weight", cfg.hidden_size, cfg.ffn_size)
+        full[p + "input_layernorm.weight"] = torch.ones(cfg.hidden_size, dtype=torch.bfloat16)
+        full[p + "post_attention_layernorm.weight"] = torch.ones(cfg.hidden_size, dtype=torch.bfloat16)
+    t = 48
+    toks = torch.randint(0, cfg.vocab_size, (t,), generator=g).to(torch.int32)
+
+    def run(model):
+        model.alloc_kv(8, 16)
+        b = ForwardBatch(tokens=toks.to(dev), positions=torch.arange(t, dtype=torch.int32, device=dev),
+                         slot_mapping=torch.arange(t, dtype=torch.int64, device=dev),
+                         block_table=torch.arange(8, dtype=torch.int32, device=dev)[None],
+                         kv_lens=torch.tensor([t], dtype=torch.int32, device=dev), is_decode=False,
+                         cu_q=torch.tensor([0, t], dtype=torch.int32, device=dev), max_q_len=t, max_kv_len=t)
+        return model.full_logits(model.forward_hidden(b)).float()
+
+    single = DecoderModel(cfg, dev)
+    single.load_state_dict(full.get)
+    ref = run(single)
+    tp = DecoderModel(cfg, dev, comm=comm)
+    tp.load_state_dict(full.get)
+    got = run(tp)
+    cos = torch.nn.functional.cosine_similarity(got, ref, dim=-1).min().item()
+    assert cos > 0.999, ("nccl", cos)
+    assert enable_fused_tp(tp, comm)
+    got2 = run(tp)
+    N.check_status(dev)
+    cos2 = torch.nn.functional.cosine_similarity(got2, ref, dim=-1).min().item()
+    assert cos2 > 0.999, ("fused", cos2)
+    tok_a = tp.greedy_tokens(tp.forward_hidden.__self__.final_norm[None].expand(1, -1).contiguous() * 0 + 1)
+    comm.barrier()
+    fused.close()
+    if rank == 0:
+        print("FUSED_TP_OK", cos, cos2)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
