@@ -1,28 +1,37 @@
 // Dense GEMM on the 5th-generation tensor cores: C = A * B^T with both operands K-major
 // ("nn.Linear" orientation), bf16 or fp8-e4m3 inputs with 128-wide block scales, fp32
-// accumulation in TMEM.
+// accumulation in TMEM. Optionally fused with the all-reduce of a tensor-parallel group.
 //
 // Replaces the reference's cuBLASLt / cublasGemmEx ladder (src/HartsyInference.Cuda/
 // CudaBackend.cs:1769-2425, LtGemmExecutor.cs, Fp8GemmExecutor.cs:110-111 which is per-tensor
-// scaled) and its mma.sync kernels (Kernels/dequant/int8_mma_gemm.cu, Ptx/hgemm_mma_sm80.ptx).
+// scaled), its mma.sync kernels (Kernels/dequant/int8_mma_gemm.cu, Ptx/hgemm_mma_sm80.ptx) and, in
+// the fused form, the GEMM + NCCL all-reduce pairs of its tensor-parallel transformer
+// (src/HartsyInference.LLM/Transformer/TensorParallelTransformer.cs:298,307).
 //
 // Structure of one CTA (320 threads, persistent over a static list of work items):
-//   warp 0      TMA producer: one thread issues cp.async.bulk.tensor loads of a 128 x 128-byte A
-//               tile and a BN x 128-byte B tile per stage into 128B-swizzled shared memory
+//   warp 0      TMA producer: one thread issues cp.async.bulk.tensor loads of 128 x 128-byte A
+//               atoms and BN x 128-byte B atoms (one or two atoms per stage) into 128B-swizzled
+//               shared memory
 //   warp 1      allocates TMEM; one thread issues tcgen05.mma (M = 128, N = BN, K = 32 bytes) and
 //               commits to the stage's "empty" barrier and to the accumulator's "full" barrier
 //   warps 2..9  epilogue: tcgen05.ld of the accumulator quarter that belongs to the warp (two
 //               warps per quarter split the columns), scale / bias / activation / gate /
 //               residual, store
-// A "work item" is (tile of 128 A rows, tile of BN B rows, K split). The caller decides which
-// operand is the activation: for small token counts the weight matrix is passed as A so that its
-// rows fill the 128-row MMA dimension and the tokens become the narrow N dimension
-// (`swap_out = 1` then stores C transposed).
+// The caller decides which operand is the activation: for small token counts the weight matrix is
+// passed as A so that its rows fill the 128-row MMA dimension and the tokens become the narrow N
+// dimension (`swap_out = 1` then stores C transposed).
 //
-// fp8 block scaling (128 x 128 weight blocks, 1 x 128 activation groups): every 128-deep K block
-// is accumulated into its own TMEM buffer (a ring of up to eight); the epilogue warps pull the
-// block out, multiply by scale_a(row, kb) * scale_b(col, kb) and add into fp32 registers while
-// the tensor core already works on the next block.
+// Work items. Output tiles are dealt round-robin to the CTAs. When the tile count is not a
+// multiple of the grid, the tiles of the last, partial wave are split along K so that this wave
+// also covers every SM (a bandwidth-bound GEMM otherwise loses up to half its throughput to wave
+// quantisation). The CTAs of a split tile write fp32 partials to a scratch buffer and bump a
+// counter; whoever arrives last sums the partials in split order (deterministic) and runs the
+// epilogue. No second kernel is launched.
+//
+// fp8 block scaling (128 x 128 weight blocks, 1 x 128 activation groups, fp32 scales): every
+// 128-deep K block is accumulated into its own TMEM buffer (a ring of up to eight); the epilogue
+// warps pull the block out, multiply by scale_a(row, kb) * scale_b(col, kb) and add into fp32
+// registers while the tensor core already works on the next blocks.
 #include "common.cuh"
 
 namespace b200 {
@@ -50,14 +59,18 @@ struct GemmParams {
   int rows_a;          // rows of the A operand (tiled by 128)
   int rows_b;          // rows of the B operand (tiled by BN)
   int k;               // reduction length in elements
-  int splits;          // K splits (>= 1); > 1 writes fp32 partials to `out`
-  int kblocks_per_split;
   int stages;
   int swap_out;        // 0: C[a_row][b_row]; 1: C[b_row][a_row]
-  int out_fp32;        // 1: write fp32 (split-K partials or fp32 result), no epilogue
-  long long ldc;       // leading dimension of C in elements
-  long long split_stride;  // elements between split partials
-  void* out;
+  // K-split of the trailing tiles: tiles [0, first_split_tile) are whole, every later tile is
+  // cut into `splits` ranges of `kblocks_per_split` k-blocks
+  int first_split_tile;
+  int num_tiles;
+  int splits;
+  int kblocks_per_split;
+  float* split_ws;          // [split tiles][splits][BN][128] fp32 partials
+  uint32_t* split_counter;  // [split tiles], zero between launches
+  long long ldc;            // leading dimension of C in elements
+  __nv_bfloat16* out;
   const __nv_bfloat16* bias;      // per output feature (column of C), may be null
   const __nv_bfloat16* gate;      // per output feature multiplicative gate, may be null
   const __nv_bfloat16* residual;  // same layout as C, may be null
@@ -68,7 +81,6 @@ struct GemmParams {
   const float* scale_b;
   int sa_gran, sa_ld, sb_gran, sb_ld;
   DeviceStatus* status;
-  int debug;   // experiment switches, 0 in production
   AllReduceParams ar;   // ar.world == 0: plain GEMM
 };
 
@@ -84,9 +96,44 @@ struct alignas(8) GemmBarriers {
   uint64_t drain;
   uint32_t tmem_base;
   uint32_t abort_flag;
-  uint32_t ar_flag;
+  uint32_t flag;      // broadcast slot of the epilogue warps
   uint32_t pad;
 };
+
+// One unit of work of a CTA: an output tile and a range of k-blocks.
+struct WorkItem {
+  int ta, tb;        // tile coordinates
+  int kb0, kb1;      // k-block range
+  int slot;          // index among the split tiles, -1 for a whole tile
+  int split;         // which range of the split tile
+};
+
+__device__ __forceinline__ long long num_work_items(const GemmParams& p) {
+  return p.first_split_tile + static_cast<long long>(p.num_tiles - p.first_split_tile) * p.splits;
+}
+
+__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, long long w, int tiles_a,
+                                                int total_kblocks) {
+  WorkItem it;
+  long long tile;
+  if (w < p.first_split_tile) {
+    tile = w;
+    it.slot = -1;
+    it.split = 0;
+    it.kb0 = 0;
+    it.kb1 = total_kblocks;
+  } else {
+    const long long r = w - p.first_split_tile;
+    it.slot = static_cast<int>(r / p.splits);
+    it.split = static_cast<int>(r % p.splits);
+    tile = p.first_split_tile + it.slot;
+    it.kb0 = it.split * p.kblocks_per_split;
+    it.kb1 = min(total_kblocks, it.kb0 + p.kblocks_per_split);
+  }
+  it.ta = static_cast<int>(tile % tiles_a);
+  it.tb = static_cast<int>(tile / tiles_a);
+  return it;
+}
 
 __device__ __forceinline__ float apply_epilogue(const GemmParams& p, float v, long long row,
                                                 long long col) {
@@ -99,8 +146,7 @@ __device__ __forceinline__ float apply_epilogue(const GemmParams& p, float v, lo
   return v;
 }
 
-
-// ---- peer signalling -------------------------------------------------------------------------
+// ---- signalling between CTAs and between GPUs --------------------------------------------------
 __device__ __forceinline__ void red_release_sys_add(uint32_t* addr, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
@@ -126,32 +172,140 @@ __device__ __forceinline__ void epilogue_barrier() {   // the 8 epilogue warps o
   asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
-// Partial tile -> staging buffer of the rank that owns these output columns.
-__device__ __forceinline__ void store_chunk_ar(const GemmParams& p, const float (&v)[32], int a_row,
-                                               int b0) {
-  const int ta = a_row >> 7;
-  const int owner = ta / p.ar.tiles_per_rank, tl = ta % p.ar.tiles_per_rank;
-  __nv_bfloat16* dst = p.ar.stage[owner] +
-      (static_cast<long long>(p.ar.rank * p.ar.tiles_per_rank + tl) * 128 + b0) * 128 + (a_row & 127);
-#pragma unroll
-  for (int j = 0; j < 32; ++j)
-    if (b0 + j < p.rows_b) dst[j * 128] = __float2bfloat16(v[j]);
-}
-
-// All epilogue warps call this once their part of tile `ta` is stored.
-// The barrier is executed even after a failed wait (`ok` false) so that the eight warps never
-// disagree on the number of barrier calls; only the signal is suppressed then.
-__device__ __forceinline__ void ar_signal_tile(const GemmParams& p, int ta, bool ok) {
-  __threadfence_system();
-  epilogue_barrier();
-  if (ok && threadIdx.x == 64) {
+// Stores 32 consecutive accumulator columns (B rows b0..b0+31) of A row `a_row` of a whole tile
+// to its destination: C, or (fused all-reduce) the staging buffer of the owning rank.
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[32], int a_row,
+                                            int b0) {
+  if (a_row >= p.rows_a) return;
+  if (p.ar.world > 0) {
+    const int ta = a_row >> 7;
     const int owner = ta / p.ar.tiles_per_rank, tl = ta % p.ar.tiles_per_rank;
-    red_release_sys_add(p.ar.tile_flag[owner] + tl, 1u);
+    __nv_bfloat16* dst = p.ar.stage[owner] +
+        (static_cast<long long>(p.ar.rank * p.ar.tiles_per_rank + tl) * 128 + b0) * 128 + (a_row & 127);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (b0 + j < p.rows_b) dst[j * 128] = __float2bfloat16(v[j]);
+    return;
+  }
+  if (!p.swap_out) {
+    __nv_bfloat16* dst = p.out + static_cast<long long>(a_row) * p.ldc + b0;
+    if (b0 + 32 <= p.rows_b && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 32; j += 2)
+        w[j >> 1] = pack_bf16x2(apply_epilogue(p, v[j], a_row, b0 + j),
+                                apply_epilogue(p, v[j + 1], a_row, b0 + j + 1));
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (b0 + j < p.rows_b)
+          dst[j] = __float2bfloat16(apply_epilogue(p, v[j], a_row, b0 + j));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (b0 + j < p.rows_b)
+        p.out[static_cast<long long>(b0 + j) * p.ldc + a_row] =
+            __float2bfloat16(apply_epilogue(p, v[j], b0 + j, a_row));
   }
 }
 
-// Owner side: sum the `world` partials of tile `ta`, apply the epilogue, write the result into
-// every rank's output and count the tile as delivered there. Called by all epilogue warps.
+// fp32 partial of a split tile: slot layout [BN columns][128 rows], so that the 32 lanes of a warp
+// (consecutive rows) write and later read consecutive addresses.
+template <int BN>
+__device__ __forceinline__ void store_partial(const GemmParams& p, const float (&v)[32], int row_local,
+                                              int col0_local, const WorkItem& it) {
+  float* ws = p.split_ws + (static_cast<long long>(it.slot) * p.splits + it.split) * (BN * 128);
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (col0_local + j < BN) ws[(col0_local + j) * 128 + row_local] = v[j];
+}
+
+// Routes one 32-column chunk of accumulator values of work item `it`.
+template <int BN>
+__device__ __forceinline__ void emit_chunk(const GemmParams& p, const float (&v)[32], const WorkItem& it,
+                                           int row_local, int chunk) {
+  if (it.slot >= 0) store_partial<BN>(p, v, row_local, chunk * 32, it);
+  else store_chunk(p, v, it.ta * kTileA + row_local, it.tb * BN + chunk * 32);
+}
+
+// Called by all 256 epilogue threads once the item's values are stored. Whole tile: nothing to do
+// (or, fused all-reduce: tell the owner rank). Split tile: count the arrival; the last CTA to
+// arrive sums the partials in split order, applies the epilogue and writes C.
+// The barriers are executed even after a failed wait (`ok` false) so that the eight warps never
+// disagree on the number of barrier calls; only signals and stores are suppressed then.
+template <int BN>
+__device__ __forceinline__ void finish_item(const GemmParams& p, const WorkItem& it, bool ok,
+                                            uint32_t* smem_flag) {
+  const int et = threadIdx.x - 64;
+  if (p.ar.world > 0) {
+    __threadfence_system();
+    epilogue_barrier();
+    if (ok && et == 0) {
+      const int owner = it.ta / p.ar.tiles_per_rank, tl = it.ta % p.ar.tiles_per_rank;
+      red_release_sys_add(p.ar.tile_flag[owner] + tl, 1u);
+    }
+    return;
+  }
+  if (it.slot < 0) return;
+  __threadfence();
+  epilogue_barrier();
+  if (et == 0) {
+    uint32_t last = 0;
+    if (ok) {
+      const uint32_t old = atomicAdd(p.split_counter + it.slot, 1u);
+      last = old == static_cast<uint32_t>(p.splits) - 1 ? 1u : 0u;
+      if (last) p.split_counter[it.slot] = 0;   // ready for the next launch
+    }
+    *smem_flag = last;
+  }
+  epilogue_barrier();
+  const bool last = *smem_flag != 0;
+  epilogue_barrier();
+  if (!last) return;
+  __threadfence();
+  const float* ws = p.split_ws + static_cast<long long>(it.slot) * p.splits * (BN * 128);
+  // four consecutive rows per thread (one 16-byte load per partial); the loads of four partials
+  // are issued together so that their L2 latencies overlap
+  for (int e4 = et; e4 < BN * 32; e4 += 256) {
+    const int e = e4 * 4;
+    const int a_local = e & 127, b_local = e >> 7;
+    const int a_row = it.ta * kTileA + a_local, b_row = it.tb * BN + b_local;
+    if (a_row >= p.rows_a || b_row >= p.rows_b) continue;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int sp = 0;
+    for (; sp + 4 <= p.splits; sp += 4) {
+      float4 t[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        t[u] = __ldcg(reinterpret_cast<const float4*>(ws + static_cast<long long>(sp + u) * (BN * 128) + e));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { acc.x += t[u].x; acc.y += t[u].y; acc.z += t[u].z; acc.w += t[u].w; }
+    }
+    for (; sp < p.splits; ++sp) {
+      const float4 t = __ldcg(reinterpret_cast<const float4*>(ws + static_cast<long long>(sp) * (BN * 128) + e));
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+    const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (a_row + u >= p.rows_a) break;
+      if (p.swap_out)
+        p.out[static_cast<long long>(b_row) * p.ldc + a_row + u] =
+            __float2bfloat16(apply_epilogue(p, v[u], b_row, a_row + u));
+      else
+        p.out[static_cast<long long>(a_row + u) * p.ldc + b_row] =
+            __float2bfloat16(apply_epilogue(p, v[u], a_row + u, b_row));
+    }
+  }
+}
+
+// Owner side of the fused all-reduce: sum the `world` partials of tile `ta`, apply the epilogue,
+// write the result into every rank's output and count the tile as delivered there. Called by all
+// epilogue warps.
 __device__ __forceinline__ bool ar_reduce_tile(const GemmParams& p, int ta, uint32_t epoch,
                                                uint32_t* smem_flag) {
   const int et = threadIdx.x - 64;   // 0..255
@@ -206,74 +360,17 @@ __device__ __forceinline__ bool ar_reduce_tile(const GemmParams& p, int ta, uint
   return ok;
 }
 
-// Stores 32 consecutive accumulator columns (B rows b0..b0+31) of A row `a_row`.
-__device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[32], int a_row,
-                                            int b0, int split) {
-  if (a_row >= p.rows_a) return;
-  if (p.ar.world > 0) {
-    store_chunk_ar(p, v, a_row, b0);
-    return;
-  }
-  if (p.out_fp32) {
-    float* out = reinterpret_cast<float*>(p.out) + static_cast<long long>(split) * p.split_stride;
-    if (!p.swap_out) {
-      float* dst = out + static_cast<long long>(a_row) * p.ldc + b0;
-      if (b0 + 32 <= p.rows_b && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (b0 + j < p.rows_b) dst[j] = v[j];
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (b0 + j < p.rows_b) out[static_cast<long long>(b0 + j) * p.ldc + a_row] = v[j];
-    }
-    return;
-  }
-  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
-  if (!p.swap_out) {
-    __nv_bfloat16* dst = out + static_cast<long long>(a_row) * p.ldc + b0;
-    if (b0 + 32 <= p.rows_b && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-      uint32_t w[16];
-#pragma unroll
-      for (int j = 0; j < 32; j += 2)
-        w[j >> 1] = pack_bf16x2(apply_epilogue(p, v[j], a_row, b0 + j),
-                                apply_epilogue(p, v[j + 1], a_row, b0 + j + 1));
-#pragma unroll
-      for (int j = 0; j < 16; j += 4)
-        *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (b0 + j < p.rows_b)
-          dst[j] = __float2bfloat16(apply_epilogue(p, v[j], a_row, b0 + j));
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (b0 + j < p.rows_b)
-        out[static_cast<long long>(b0 + j) * p.ldc + a_row] =
-            __float2bfloat16(apply_epilogue(p, v[j], b0 + j, a_row));
-  }
-}
-
 template <bool kFp8, int BN, int kAtoms>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a,
                     const __grid_constant__ CUtensorMap tm_b) {
   // A stage holds kAtoms swizzle atoms (128 bytes of K each) per operand: [A atoms][B atoms].
-  // Two atoms make every row's fetch 256 contiguous bytes issued back to back, which DRAM serves
-  // more efficiently than isolated 128-byte segments when the GEMM is bandwidth-bound.
   constexpr int kAtomBytesB = BN * 128;
   constexpr int kStageBytes = kAtoms * (kStageBytesA + kAtomBytesB);
-  constexpr int kElemsPerStage = kFp8 ? 128 : 64;   // K elements in one 128-byte atom
+  constexpr int kElemsPerAtom = kFp8 ? 128 : 64;   // K elements in one 128-byte atom
   // Accumulator ring in TMEM: as many buffers as fit in the 512 columns (at most 8). The
   // block-scaled path hands one buffer per 128-deep K block to the epilogue warps, so a deep ring
-  // lets the tensor core run ahead of the promotion; the bf16 path uses one buffer per tile.
+  // lets the tensor core run ahead of the promotion; the bf16 path uses one buffer per work item.
   constexpr int kBufStride = BN < 32 ? 32 : BN;   // loads are 32 columns wide
   constexpr int kAccBufs = (512 / kBufStride) < 8 ? (512 / kBufStride) : 8;
   constexpr uint32_t kTmemCols = kAccBufs * kBufStride;
@@ -281,7 +378,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
                                    : make_idesc(128, BN, kFmtBf16, kFmtBf16);
   static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256,
                 "tcgen05.mma M=128 needs N % 16 == 0; TMEM allocations are powers of two");
-  static_assert(!kFp8 || BN <= 128, "fp8 path keeps BN fp32 accumulators per thread");
+  static_assert(!kFp8 || BN <= 128, "fp8 path keeps BN / 2 fp32 accumulators per thread");
 
   extern __shared__ uint8_t smem_raw[];
   // 128B-swizzled tiles need 1024-byte aligned bases.
@@ -294,9 +391,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
   const int lane = threadIdx.x & 31;
 
   const int tiles_a = (p.rows_a + kTileA - 1) / kTileA;
-  const int tiles_b = (p.rows_b + BN - 1) / BN;
-  const int total_kblocks = (p.k + kElemsPerStage - 1) / kElemsPerStage;
-  const long long work_items = static_cast<long long>(tiles_a) * tiles_b * p.splits;
+  const int total_kblocks = (p.k + kElemsPerAtom - 1) / kElemsPerAtom;
+  const long long work_items = num_work_items(p);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -309,6 +405,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
     }
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
+    bars->flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tm_a);
     prefetch_tensormap(&tm_b);
@@ -331,14 +428,9 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       long long issued = 0;
       bool ok = true;
       for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
-        const int ta = static_cast<int>(w % tiles_a);
-        const long long rest = w / tiles_a;
-        const int tb = static_cast<int>(rest % tiles_b);
-        const int split = static_cast<int>(rest / tiles_b);
-        const int kb0 = split * p.kblocks_per_split;
-        const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
-        for (int kb = kb0; kb < kb1; kb += kAtoms) {
-          const int na = min(kAtoms, kb1 - kb);
+        const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
+        for (int kb = it.kb0; kb < it.kb1; kb += kAtoms) {
+          const int na = min(kAtoms, it.kb1 - kb);
           if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag)) {
             report_status(p.status, kWaitTimeout, kKernelGemm, 1, blockIdx.x);
             ok = false;
@@ -348,8 +440,10 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           uint8_t* sb = sa + kAtoms * kStageBytesA;
           mbar_arrive_expect_tx(&bars->full[s], na * (kStageBytesA + kAtomBytesB));
           for (int a = 0; a < na; ++a) {
-            tma_load_2d(sa + a * kStageBytesA, &tm_a, &bars->full[s], (kb + a) * kElemsPerStage, ta * kTileA);
-            tma_load_2d(sb + a * kAtomBytesB, &tm_b, &bars->full[s], (kb + a) * kElemsPerStage, tb * BN);
+            tma_load_2d(sa + a * kStageBytesA, &tm_a, &bars->full[s], (kb + a) * kElemsPerAtom,
+                        it.ta * kTileA);
+            tma_load_2d(sb + a * kAtomBytesB, &tm_b, &bars->full[s], (kb + a) * kElemsPerAtom,
+                        it.tb * BN);
           }
           ++issued;
           if (++s == stages) { s = 0; ph ^= 1; }
@@ -376,10 +470,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       bool ok = true;
       bool issued_any = false;
       for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
-        const long long rest = w / tiles_a;
-        const int split = static_cast<int>(rest / tiles_b);
-        const int kb0 = split * p.kblocks_per_split;
-        const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
+        const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
         if (!kFp8) {
           if (!mbar_wait(&bars->tmem_empty[abuf], aph ^ 1, abort_flag)) {
             report_status(p.status, kWaitTimeout, kKernelGemm, 2, blockIdx.x);
@@ -388,8 +479,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           }
           tc_fence_after_sync();
         }
-        for (int kb = kb0; kb < kb1 && ok; kb += kAtoms) {
-          const int na = min(kAtoms, kb1 - kb);
+        for (int kb = it.kb0; kb < it.kb1 && ok; kb += kAtoms) {
+          const int na = min(kAtoms, it.kb1 - kb);
           if (!mbar_wait(&bars->full[s], ph, abort_flag)) {
             report_status(p.status, kWaitTimeout, kKernelGemm, 3, blockIdx.x);
             ok = false;
@@ -413,7 +504,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
             for (int k = 0; k < 4; ++k) {
               // advancing 32 bytes along K inside the 128-byte swizzle atom = +2 in the
               // (address >> 4) field of the descriptor
-              const uint32_t acc = kFp8 ? (k > 0) : (kb + a > kb0 || k > 0);
+              const uint32_t acc = kFp8 ? (k > 0) : (kb + a > it.kb0 || k > 0);
               if (kFp8) mma_fp8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
               else      mma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
             }
@@ -446,132 +537,115 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
     const int hsel = (warp - 2) >> 2;  // which half of the chunks
     constexpr int kChunks = (BN + 31) / 32;
     constexpr int kMine = (kChunks + 1) / 2;
+    const int row_local = q * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     int abuf = 0;
     uint32_t aph = 0;
     bool ok = true;
     for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
-      const int ta = static_cast<int>(w % tiles_a);
-      const long long rest = w / tiles_a;
-      const int tb = static_cast<int>(rest % tiles_b);
-      const int split = static_cast<int>(rest / tiles_b);
-      const int a_row = ta * kTileA + q * 32 + lane;
-      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      if (!ok) {   // a wait failed earlier: keep the loop shape (barriers) but do no work
-        if (p.ar.world > 0) ar_signal_tile(p, ta, false);
-        continue;
-      }
-      if constexpr (!kFp8) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[abuf], aph, abort_flag))) {
-          if (lane == 0) report_status(p.status, kWaitTimeout, kKernelGemm, 5, blockIdx.x);
-          ok = false;
-          if (p.ar.world > 0) ar_signal_tile(p, ta, false);
-          continue;
-        }
-        tc_fence_after_sync();
-#pragma unroll 1
-        for (int c = hsel; c < kChunks; c += 2) {
-          uint32_t r[32];
-          tmem_ld_32x32(lane_base + abuf * kBufStride + c * 32, r);
-          tmem_ld_wait();
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          store_chunk(p, v, a_row, tb * BN + c * 32, split);
-        }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
-        if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
-        if (p.ar.world > 0) ar_signal_tile(p, ta, true);
-      } else {
-        float acc[kMine * 32];
-#pragma unroll
-        for (int j = 0; j < kMine * 32; ++j) acc[j] = 0.f;
-        const int kb0 = split * p.kblocks_per_split;
-        const int kb1 = min(total_kblocks, kb0 + p.kblocks_per_split);
-        const int a_row_c = min(a_row, p.rows_a - 1);
-        const bool col_vector = p.sb_gran == 1;
-        // Scales are fetched one k-block ahead so that their latency never sits between the
-        // accumulator becoming ready and the FMAs. Row scale: one value per thread. Column scale:
-        // either one value per tile (128-wide weight blocks) or one value per column, in which case
-        // lane l holds the scale of column (chunk * 32 + l) and it is broadcast with shuffles.
-        auto load_row_scale = [&](int kb) {
-          return __ldg(p.scale_a + static_cast<long long>(a_row_c / p.sa_gran) * p.sa_ld + kb);
-        };
-        auto load_col_scale = [&](int kb, int i) {
-          if (!col_vector)
-            return __ldg(p.scale_b + static_cast<long long>((tb * BN) / p.sb_gran) * p.sb_ld + kb);
-          const int col = min(tb * BN + (hsel + 2 * i) * 32 + lane, p.rows_b - 1);
-          return __ldg(p.scale_b + static_cast<long long>(col) * p.sb_ld + kb);
-        };
-        float sa_next = load_row_scale(kb0);
-        float cs_next[kMine];
-#pragma unroll
-        for (int i = 0; i < kMine; ++i) cs_next[i] = load_col_scale(kb0, i);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          const float sa = sa_next;
-          float cs[kMine];
-#pragma unroll
-          for (int i = 0; i < kMine; ++i) cs[i] = cs_next[i];
-          if (kb + 1 < kb1) {
-            sa_next = load_row_scale(kb + 1);
-#pragma unroll
-            for (int i = 0; i < kMine; ++i) cs_next[i] = load_col_scale(kb + 1, i);
-          }
+      const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
+      if (ok) {
+        if constexpr (!kFp8) {
           if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[abuf], aph, abort_flag))) {
-            if (lane == 0) report_status(p.status, kWaitTimeout, kKernelGemm, 6, blockIdx.x);
+            if (lane == 0) report_status(p.status, kWaitTimeout, kKernelGemm, 5, blockIdx.x);
             ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-#pragma unroll
-          for (int i = 0; i < kMine; ++i) {
-            const int c = hsel + 2 * i;
-            if (c < kChunks) {
+          } else {
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = hsel; c < kChunks; c += 2) {
               uint32_t r[32];
-              if (p.debug & 2) {
+              tmem_ld_32x32(lane_base + abuf * kBufStride + c * 32, r);
+              tmem_ld_wait();
+              float v[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = 0;
-              } else {
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              emit_chunk<BN>(p, v, it, row_local, c);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
+            if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
+          }
+        } else {
+          float acc[kMine * 32];
+#pragma unroll
+          for (int j = 0; j < kMine * 32; ++j) acc[j] = 0.f;
+          const int a_row_c = min(it.ta * kTileA + row_local, p.rows_a - 1);
+          const bool col_vector = p.sb_gran == 1;
+          // Scales are fetched one k-block ahead so that their latency never sits between the
+          // accumulator becoming ready and the FMAs. Row scale: one value per thread. Column
+          // scale: one value per tile (128-wide weight blocks) or one per column, in which case
+          // lane l holds the scale of column (chunk * 32 + l) and it is broadcast with shuffles.
+          auto load_row_scale = [&](int kb) {
+            return __ldg(p.scale_a + static_cast<long long>(a_row_c / p.sa_gran) * p.sa_ld + kb);
+          };
+          auto load_col_scale = [&](int kb, int i) {
+            if (!col_vector)
+              return __ldg(p.scale_b + static_cast<long long>((it.tb * BN) / p.sb_gran) * p.sb_ld + kb);
+            const int col = min(it.tb * BN + (hsel + 2 * i) * 32 + lane, p.rows_b - 1);
+            return __ldg(p.scale_b + static_cast<long long>(col) * p.sb_ld + kb);
+          };
+          float sa_next = load_row_scale(it.kb0);
+          float cs_next[kMine];
+#pragma unroll
+          for (int i = 0; i < kMine; ++i) cs_next[i] = load_col_scale(it.kb0, i);
+          for (int kb = it.kb0; kb < it.kb1; ++kb) {
+            const float sa = sa_next;
+            float cs[kMine];
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) cs[i] = cs_next[i];
+            if (kb + 1 < it.kb1) {
+              sa_next = load_row_scale(kb + 1);
+#pragma unroll
+              for (int i = 0; i < kMine; ++i) cs_next[i] = load_col_scale(kb + 1, i);
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[abuf], aph, abort_flag))) {
+              if (lane == 0) report_status(p.status, kWaitTimeout, kKernelGemm, 6, blockIdx.x);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) {
+              const int c = hsel + 2 * i;
+              if (c < kChunks) {
+                uint32_t r[32];
                 tmem_ld_32x32(lane_base + abuf * kBufStride + c * 32, r);
                 tmem_ld_wait();
-              }
-              if (p.debug & 1) {
+                if (!col_vector) {
+                  const float sc = sa * cs[i];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) acc[i * 32 + j] += __uint_as_float(r[j]);
-              } else if (!col_vector) {
-                const float sc = sa * cs[i];
+                  for (int j = 0; j < 32; ++j)
+                    acc[i * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[i * 32 + j]);
+                } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  acc[i * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[i * 32 + j]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  const float sc = sa * __shfl_sync(0xffffffffu, cs[i], j);
-                  acc[i * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[i * 32 + j]);
+                  for (int j = 0; j < 32; ++j) {
+                    const float sc = sa * __shfl_sync(0xffffffffu, cs[i], j);
+                    acc[i * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[i * 32 + j]);
+                  }
                 }
               }
             }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
+            if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
           }
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
-          if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
-        }
-        if (ok) {
+          if (ok) {
 #pragma unroll
-          for (int i = 0; i < kMine; ++i) {
-            const int c = hsel + 2 * i;
-            if (c < kChunks) {
-              float v[32];
+            for (int i = 0; i < kMine; ++i) {
+              const int c = hsel + 2 * i;
+              if (c < kChunks) {
+                float v[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = acc[i * 32 + j];
-              store_chunk(p, v, a_row, tb * BN + c * 32, split);
+                for (int j = 0; j < 32; ++j) v[j] = acc[i * 32 + j];
+                emit_chunk<BN>(p, v, it, row_local, c);
+              }
             }
           }
         }
-        if (p.ar.world > 0) ar_signal_tile(p, ta, ok);
       }
+      finish_item<BN>(p, it, ok, &bars->flag);
     }
     if (p.ar.world > 0) {
       // ---- reduce phase: tiles whose output columns this rank owns, then wait until every
@@ -579,7 +653,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1u;
       for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
         const int ta = static_cast<int>(w % tiles_a);
-        if (ta / p.ar.tiles_per_rank == p.ar.rank) ok &= ar_reduce_tile(p, ta, epoch, &bars->ar_flag);
+        if (ta / p.ar.tiles_per_rank == p.ar.rank) ok &= ar_reduce_tile(p, ta, epoch, &bars->flag);
       }
       if (threadIdx.x == 64) {
         if (!wait_flag_geq(p.ar.done[p.ar.rank], epoch * static_cast<uint32_t>(tiles_a), p.ar.wait_budget))
@@ -605,21 +679,6 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) = e + 1u;
       __threadfence();
     }
-  }
-}
-
-// Sums split-K partials and applies the epilogue. ws is [splits][rows][ldc] fp32 in C's layout.
-__global__ void splitk_reduce_kernel(const float* __restrict__ ws, GemmParams p, int rows,
-                                     int cols) {
-  // p.ldc is C's leading dimension here; the partials are dense [splits][rows][cols]
-  const long long total = static_cast<long long>(rows) * cols;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / cols, c = i % cols;
-    float v = 0.f;
-    for (int s = 0; s < p.splits; ++s) v += ws[s * p.split_stride + i];
-    reinterpret_cast<__nv_bfloat16*>(p.out)[r * p.ldc + c] =
-        __float2bfloat16(apply_epilogue(p, v, r, c));
   }
 }
 
@@ -667,12 +726,12 @@ int launch_gemm(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& t
                 cudaStream_t stream) {
   const int stage_bytes = kAtoms * (kStageBytesA + BN * 128);
   const int smem = p.stages * stage_bytes + static_cast<int>(sizeof(GemmBarriers)) + 1024;
-  static int configured = 0;
-  if (configured < smem) {
+  static bool configured = false;
+  if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<kFp8, BN, kAtoms>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
     if (e != cudaSuccess) return -static_cast<int>(e) - 200;
-    configured = 232448;
+    configured = true;
   }
   gemm_tcgen05_kernel<kFp8, BN, kAtoms><<<grid, kGemmThreads, smem, stream>>>(p, ta, tb);
   cudaError_t e = cudaGetLastError();
@@ -690,42 +749,13 @@ int num_sms() {
   return g_num_sms;
 }
 
-}  // namespace b200
+constexpr long long kSplitCounterBytes = 16384;   // head of the scratch buffer: 4096 tile counters
 
-using namespace b200;
-
-static int g_gemm_debug = 0;
-B200_API void b200_gemm_set_debug(int v) { g_gemm_debug = v; }
-
-// Workspace needed by b200_gemm for the chosen split count (bytes of fp32 partials), 0 if no split.
-B200_API long long b200_gemm_workspace_bytes(int m, int n, int splits) {
-  return splits > 1 ? static_cast<long long>(splits) * m * n * 4 : 0;
-}
-
-// Picks the K split for a memory-bound (small-M) GEMM so that the grid covers the SMs.
-B200_API int b200_gemm_pick_splits(int m, int n, int k, int is_fp8) {
-  const int kelems = is_fp8 ? 128 : 64;
-  const int kblocks = (k + kelems - 1) / kelems;
-  if (m > 128) return 1;
-  const int tiles = (n + 127) / 128;   // weights ride the 128-row dimension for small m
-  const int sms = num_sms();
-  if (tiles >= sms) return 1;
-  int splits = sms / tiles;
-  if (splits > kblocks / 4) splits = kblocks / 4;   // keep >= 4 k-blocks per split
-  if (splits > 16) splits = 16;
-  return splits < 1 ? 1 : splits;
-}
-
-// out[m][n] (bf16, leading dim ldc) = epilogue(x[m][k] * w[n][k]^T)
-//   dtype: 0 = bf16 operands, 1 = fp8 e4m3 operands with block scales
-//   x_scale: [m][k/128] fp32 (per token, per 128-wide K group); w_scale: [ceil(n/128)][k/128] fp32
-//   workspace: fp32 scratch of b200_gemm_workspace_bytes() when splits > 1
-// Returns 0 on success, negative on a launch-time error.
 static int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
                      long long ldw, long long ldc, int dtype, const float* x_scale,
                      const float* w_scale, const void* bias, const void* gate, const void* residual,
-                     int act, int splits, void* workspace, void* status, cudaStream_t stream,
-                     const AllReduceParams* ar) {
+                     int act, int splits, void* workspace, long long workspace_bytes, void* status,
+                     cudaStream_t stream, const AllReduceParams* ar) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   const bool fp8 = dtype == 1;
   const int esz = fp8 ? 1 : 2;
@@ -733,39 +763,24 @@ static int gemm_impl(const void* x, const void* w, void* out, int m, int n, int 
   if ((ldx * esz) % 16 != 0 || (ldw * esz) % 16 != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -3;
   if (fp8 && (k % 128 != 0 || !x_scale || !w_scale)) return -4;
-  if (splits > 1 && workspace == nullptr) return -5;
 
   // Small token counts: weights take the 128-row MMA dimension, tokens the N dimension.
   const bool swap = m <= 128;
   GemmParams p{};
   p.k = k;
-  p.out = out;
+  p.out = static_cast<__nv_bfloat16*>(out);
   p.ldc = ldc;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.gate = static_cast<const __nv_bfloat16*>(gate);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.act = act;
   p.status = static_cast<DeviceStatus*>(status);
-  p.debug = g_gemm_debug;
+  p.swap_out = swap ? 1 : 0;
   if (ar != nullptr) {
     if (m > 128 || n % (128 * ar->world) != 0) return -6;   // one token tile; whole tiles per owner
     p.ar = *ar;
     p.ar.tiles_per_rank = n / 128 / ar->world;
     splits = 1;
-  }
-  p.swap_out = swap ? 1 : 0;
-  const int total_kblocks = (k + kelems - 1) / kelems;
-  if (splits < 1) splits = 1;
-  if (splits > total_kblocks) splits = total_kblocks;
-  p.kblocks_per_split = (total_kblocks + splits - 1) / splits;
-  splits = (total_kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
-  p.splits = splits;
-  if (splits > 1) {
-    // partials are [splits][m][n] fp32, densely packed
-    p.out_fp32 = 1;
-    p.out = workspace;
-    p.ldc = n;
-    p.split_stride = static_cast<long long>(m) * n;
   }
 
   int bn;
@@ -785,6 +800,48 @@ static int gemm_impl(const void* x, const void* w, void* out, int m, int n, int 
     p.scale_a = x_scale; p.sa_gran = 1;   p.sa_ld = k / 128;
     p.scale_b = w_scale; p.sb_gran = 128; p.sb_ld = k / 128;
   }
+  const int total_kblocks = (k + kelems - 1) / kelems;
+  const int tiles = ((p.rows_a + 127) / 128) * ((p.rows_b + bn - 1) / bn);
+  const int sms = num_sms();
+  p.num_tiles = tiles;
+
+  // ---- K-split policy (see the header comment)
+  int first_split = tiles, s_eff = 1;
+  const long long slot_bytes = static_cast<long long>(bn) * 128 * 4;
+  if (splits > 1) {                                  // caller-forced uniform split
+    first_split = 0;
+    s_eff = splits;
+  } else if (splits <= 0) {                          // automatic
+    const int q = tiles / sms, r = tiles % sms;
+    // worthwhile when the partial wave is a visible share of the run: always for the
+    // bandwidth-bound orientation, for the other only when there are few waves
+    if (r != 0 && (swap || q < 4)) {
+      int s = sms / r;
+      if (s > total_kblocks / 2) s = total_kblocks / 2;   // at least two k-blocks per range
+      // after full waves a modest split already shrinks the tail to 1/s of a tile; without full
+      // waves the split is what fills the machine
+      const int cap = q >= 1 ? 8 : 16;
+      if (s > cap) s = cap;
+      if (s > 1) { first_split = q * sms; s_eff = s; }
+    }
+  }
+  if (s_eff > total_kblocks) s_eff = total_kblocks;
+  p.kblocks_per_split = (total_kblocks + s_eff - 1) / s_eff;
+  s_eff = (total_kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  if (s_eff <= 1) { first_split = tiles; s_eff = 1; p.kblocks_per_split = total_kblocks; }
+  const int split_tiles = tiles - first_split;
+  if (split_tiles > 0) {
+    const long long need = kSplitCounterBytes + static_cast<long long>(split_tiles) * s_eff * slot_bytes;
+    if (workspace == nullptr || need > workspace_bytes || split_tiles > 4096) {
+      if (splits > 1) return -5;                     // forced split without room: say so
+      first_split = tiles; s_eff = 1; p.kblocks_per_split = total_kblocks;
+    }
+  }
+  p.first_split_tile = first_split;
+  p.splits = s_eff;
+  p.split_counter = static_cast<uint32_t*>(workspace);
+  p.split_ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kSplitCounterBytes);
+
   // two atoms per stage for the bandwidth-bound small-token orientation
   const int atoms = swap ? 2 : 1;
   const int stage_bytes = atoms * (kStageBytesA + bn * 128);
@@ -798,9 +855,8 @@ static int gemm_impl(const void* x, const void* w, void* out, int m, int n, int 
   rc = make_kmajor_map(&tb, b_ptr, esz, p.rows_b, k, ldb, bn);
   if (rc) return rc;
 
-  const long long tiles = static_cast<long long>((p.rows_a + 127) / 128) *
-                          ((p.rows_b + bn - 1) / bn) * splits;
-  const int grid = static_cast<int>(tiles < num_sms() ? tiles : num_sms());
+  const long long items = first_split + static_cast<long long>(tiles - first_split) * s_eff;
+  const int grid = static_cast<int>(items < sms ? items : sms);
 
   if (fp8) {
     if (swap) {
@@ -827,29 +883,34 @@ static int gemm_impl(const void* x, const void* w, void* out, int m, int n, int 
       rc = launch_gemm<false, 256, 1>(p, ta, tb, grid, stream);
     }
   }
-  if (rc) return rc;
-  if (splits > 1) {
-    GemmParams rp = p;
-    rp.out = out;
-    rp.ldc = ldc;
-    const long long total = static_cast<long long>(m) * n;
-    int blocks = static_cast<int>((total + 255) / 256);
-    if (blocks > 4 * num_sms()) blocks = 4 * num_sms();
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(workspace), rp, m,
-                                                     n);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return -static_cast<int>(e) - 400;
-  }
-  return 0;
+  return rc;
 }
 
+}  // namespace b200
+
+using namespace b200;
+
+// Scratch that b200_gemm needs to be able to split tiles along K: a zero-initialised buffer of at
+// least this many bytes (tile counters followed by fp32 partials). The kernel leaves the counters
+// at zero again, so the buffer is zeroed once, at allocation.
+B200_API long long b200_gemm_workspace_bytes() {
+  return 64ll << 20;   // the automatic policy needs at most 16 KB + 148 slots of 64 KB
+}
+
+// out[m][n] (bf16, leading dim ldc) = epilogue(x[m][k] * w[n][k]^T)
+//   dtype: 0 = bf16 operands, 1 = fp8 e4m3 operands with block scales
+//   x_scale: [m][k/128] fp32 (per token, per 128-wide K group); w_scale: [ceil(n/128)][k/128] fp32
+//   splits: 0 = automatic (split only the tiles of a partial last wave), 1 = never, > 1 = split
+//           every tile that many ways
+//   workspace: zero-initialised scratch (see b200_gemm_workspace_bytes), may be null (no splitting)
+// Returns 0 on success, negative on a launch-time error.
 B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
                        long long ldw, long long ldc, int dtype, const float* x_scale,
                        const float* w_scale, const void* bias, const void* gate,
                        const void* residual, int act, int splits, void* workspace,
-                       void* status, cudaStream_t stream) {
+                       long long workspace_bytes, void* status, cudaStream_t stream) {
   return gemm_impl(x, w, out, m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, gate, residual,
-                   act, splits, workspace, status, stream, nullptr);
+                   act, splits, workspace, workspace_bytes, status, stream, nullptr);
 }
 
 // Row-parallel linear of a tensor-parallel group fused with the all-reduce of its output:
@@ -881,5 +942,5 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
   ar.world = world;
   ar.wait_budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
   return gemm_impl(x, w, out[rank], m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, gate,
-                   residual, act, 1, nullptr, status, stream, &ar);
+                   residual, act, 1, nullptr, 0, status, stream, &ar);
 }

@@ -110,6 +110,7 @@ class LLMEngine:
         self.h_out = torch.zeros(cap_seqs, dtype=torch.int32, pin_memory=pin)
         if self.cuda:
             N.reserve_workspace(self.device, 256 << 20)
+            N.state(self.device).gemm_workspace()
         log.info(f"[Engine] kv pages={self.num_pages} x {self.page} tokens "
                  f"({self.num_pages * model.kv_bytes_per_page(self.page) / 2**30:.2f} GiB), "
                  f"max_batch={self.max_batch}, graphs={'on' if self.use_graphs else 'off'}")

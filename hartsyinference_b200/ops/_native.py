@@ -23,9 +23,8 @@ _lib: Optional[C.CDLL] = None
 vp, i32, i64, f32, u64 = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulonglong
 
 _SIGNATURES = {
-    "b200_gemm": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, vp, vp, i32, i32, vp, vp, vp]),
-    "b200_gemm_pick_splits": (i32, [i32, i32, i32, i32]),
-    "b200_gemm_workspace_bytes": (i64, [i32, i32, i32]),
+    "b200_gemm": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, vp, vp, i32, i32, vp, i64, vp, vp]),
+    "b200_gemm_workspace_bytes": (i64, []),
     "b200_norm": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, i32, vp]),
     "b200_quant_fp8": (i32, [vp, vp, vp, i32, i32, i64, vp]),
     "b200_quant_fp8_weight": (i32, [vp, vp, vp, i32, i32, vp]),
@@ -109,6 +108,14 @@ class _DeviceState:
         self.device = device
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.workspace = torch.empty(0, dtype=torch.uint8, device=device)
+        self._gemm_ws = None
+
+    def gemm_workspace(self) -> torch.Tensor:
+        """Zero-initialised scratch of the GEMM's K-split path (tile counters + fp32 partials). The
+        kernel leaves the counters at zero, so it is cleared only here, once."""
+        if self._gemm_ws is None:
+            self._gemm_ws = torch.zeros(lib().b200_gemm_workspace_bytes(), dtype=torch.uint8, device=self.device)
+        return self._gemm_ws
 
     def scratch(self, nbytes: int) -> torch.Tensor:
         if self.workspace.numel() < nbytes:

@@ -123,18 +123,14 @@ def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.T
         out = torch.empty(m, n, dtype=torch.bfloat16, device=xd.device)
     fp8 = w.is_fp8
     L = N.lib()
-    if splits is None:
-        splits = L.b200_gemm_pick_splits(m, n, k, 1 if fp8 else 0)
     st = N.state(xd.device)
-    ws = None
-    if splits > 1:
-        ws = st.scratch(L.b200_gemm_workspace_bytes(m, n, splits)).data_ptr()
+    ws = st.gemm_workspace()
     rc = L.b200_gemm(xd.data_ptr(), w.weight.data_ptr(), out.data_ptr(), m, n, k,
                      xd.stride(0), w.weight.stride(0), out.stride(0), 1 if fp8 else 0,
                      x.scale.data_ptr() if fp8 else None, w.scale.data_ptr() if fp8 else None,
-                     N.ptr(w.bias), N.ptr(gate), N.ptr(residual), _ACT[act], splits, ws,
-                     st.status.data_ptr(), N.stream())
-    N.check(rc, "b200_gemm", 2 if splits > 1 else 1)
+                     N.ptr(w.bias), N.ptr(gate), N.ptr(residual), _ACT[act], 0 if splits is None else splits,
+                     ws.data_ptr(), ws.numel(), st.status.data_ptr(), N.stream())
+    N.check(rc, "b200_gemm")
     return out
 
 
