@@ -751,7 +751,7 @@ int num_sms() {
 
 constexpr long long kSplitCounterBytes = 16384;   // head of the scratch buffer: 4096 tile counters
 
-static int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
+int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
                      long long ldw, long long ldc, int dtype, const float* x_scale,
                      const float* w_scale, const void* bias, const void* gate, const void* residual,
                      int act, int splits, void* workspace, long long workspace_bytes, void* status,
@@ -943,4 +943,38 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
   ar.wait_budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
   return gemm_impl(x, w, out[rank], m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, gate,
                    residual, act, 1, nullptr, 0, status, stream, &ar);
+}
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in b200_noalloc.h).
+// ------------------------------------------------------------------------------------------
+#include "b200_noalloc.h"
+
+// Scratch of the split-K path, resident in the library image: tile counters, then fp32 partials.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[B200_NOALLOC_SCRATCH_BYTES];
+
+// In host code the symbol above is only a stand-in; the address a kernel can use has to be asked
+// for per device. Resolved on the first call on each device and remembered.
+static void* g_noalloc_ptr[64] = {nullptr};
+
+B200_API int b200_gemm_noalloc(const void* x, const void* w, void* out, int m, int n, int k,
+                               long long ldx, long long ldw, long long ldc, int dtype,
+                               const float* x_scale, const float* w_scale, const void* bias,
+                               const void* residual, cudaStream_t stream) {
+  if (m > B200_NOALLOC_MAX_TOKENS) return B200_NOALLOC_ERR_TOO_LARGE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_NOALLOC_ERR_SETUP;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr)
+      return B200_NOALLOC_ERR_SETUP;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  void* scratch = g_noalloc_ptr[dev];
+  // m <= 128 keeps every partial slot at 64 KB or less and the automatic policy never uses more
+  // than one slot per SM, so counters + partials always fit; gemm_impl re-checks against the size.
+  if (cudaMemsetAsync(scratch, 0, b200::kSplitCounterBytes, stream) != cudaSuccess)
+    return B200_NOALLOC_ERR_SETUP;
+  return b200::gemm_impl(x, w, out, m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, nullptr,
+                         residual, 0, 0, scratch, B200_NOALLOC_SCRATCH_BYTES, nullptr, stream, nullptr);
 }
