@@ -115,6 +115,9 @@ def main() -> int:
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if os.environ.get("B200_BENCH_TRACE_AFTER"):
+        import faulthandler
+        faulthandler.dump_traceback_later(float(os.environ["B200_BENCH_TRACE_AFTER"]), repeat=False, exit=True)
 
     import torch
     from hartsyinference_b200 import log
@@ -185,11 +188,26 @@ def main() -> int:
     ttft = sorted(r.t_first_token - r.t_submit for r in eng.requests.values())
     N.check_status(device)
 
-    steps_possible = args.decode_len - 1 - args.warmup
+    steps_possible = args.decode_len - 3 - args.warmup
     steps = min(args.steps, steps_possible)
     for _ in range(args.warmup):
         eng.step()
     torch.cuda.synchronize()
+    if fused:
+        # A bounded wait of the fused kernels that gave up on any rank means the peer protocol did
+        # not work on this machine: fall back to NCCL on every rank rather than time garbage.
+        bad = torch.tensor([int(N.state(device).status[0].item() != 0)], device=device)
+        import torch.distributed as dist
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()) != 0:
+            log.warn("[Collective] fused TP kernels reported a wait timeout; falling back to NCCL")
+            N.state(device).status.zero_()
+            model.row_parallel_linear = None
+            eng._graphs.clear()
+            fused = False
+            for _ in range(2):
+                eng.step()
+            torch.cuda.synchronize()
     comm.barrier()
 
     sampler = ClockSampler(local_rank)
@@ -250,8 +268,13 @@ def main() -> int:
         }
         print(json.dumps(out))
     if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+        # NCCL communicators that were captured into CUDA graphs can block in their teardown; the
+        # result is already printed, so leave without running it.
+        comm.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 
