@@ -1,0 +1,311 @@
+"""Tokenizers: byte-level BPE (``tokenizer.json`` of Llama-3 / Qwen / GPT-2 style models) and
+SentencePiece-style score BPE (vocabularies embedded in GGUF files), with special-token splitting
+and an incremental, UTF-8-safe detokenizer for streaming.
+
+The merge loops run in C++ (``csrc/runtime/tokenizer.cpp``); this module does pre-tokenisation
+(regex), special tokens, and decoding. Reference: src/HartsyInference.ModelAssets/Tokenizers/
+(BPE for Llama / Qwen2/3 / GPT-OSS, SentencePiece for Gemma / T5, ``Gguf/SpmGguf``,
+``HfTokenizerJson``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+from pathlib import Path
+from typing import Iterable, Optional, Sequence
+
+import numpy as np
+
+try:
+    import regex as _re
+except ImportError:  # pragma: no cover
+    import re as _re
+
+from .. import runtime
+
+GPT2_PATTERN = r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
+LLAMA3_PATTERN = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|"
+                  r"\s*[\r\n]+|\s+(?!\S)|\s+")
+QWEN2_PATTERN = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|"
+                 r"\s*[\r\n]+|\s+(?!\S)|\s+")
+
+
+def _bytes_to_unicode() -> dict[int, str]:
+    bs = list(range(ord("!"), ord("~") + 1)) + list(range(ord("¡"), ord("¬") + 1)) + list(range(ord("®"), ord("ÿ") + 1))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    return dict(zip(bs, (chr(c) for c in cs)))
+
+
+_B2U = _bytes_to_unicode()
+_U2B = {v: k for k, v in _B2U.items()}
+_bound = False
+
+
+def _lib():
+    global _bound
+    L = runtime.lib()
+    if not _bound:
+        vp, i32 = C.c_void_p, C.c_int32
+        for name, res, args in (
+            ("b200_tok_create", vp, [vp, vp, i32, vp, i32]), ("b200_tok_destroy", None, [vp]),
+            ("b200_tok_add_merge", None, [vp, i32, i32, i32]), ("b200_tok_set_byte_token", None, [vp, i32, i32]),
+            ("b200_tok_lookup", i32, [vp, C.c_char_p, i32]),
+            ("b200_tok_encode_rank", i32, [vp, C.c_char_p, i32, vp, i32]),
+            ("b200_tok_encode_score", i32, [vp, C.c_char_p, i32, vp, i32]),
+            ("b200_tok_bytes", i32, [vp, i32, vp, i32]), ("b200_tok_size", i32, [vp]),
+        ):
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _bound = True
+    return L
+
+
+class Tokenizer:
+    """``kind`` is ``"bpe"`` (byte-level rank BPE) or ``"spm"`` (score BPE)."""
+
+    def __init__(self, kind: str, token_bytes: Sequence[bytes], *, merges: Optional[Sequence[tuple[int, int]]] = None,
+                 scores: Optional[Sequence[float]] = None, special_tokens: Optional[dict[str, int]] = None,
+                 pattern: str = GPT2_PATTERN, bos_id: Optional[int] = None, eos_id: Optional[int] = None,
+                 add_bos: bool = False, add_space_prefix: bool = True, unk_id: int = -1,
+                 byte_fallback: Optional[dict[int, int]] = None):
+        self.kind = kind
+        self.vocab_bytes = list(token_bytes)
+        self.special_tokens = dict(special_tokens or {})
+        self.special_ids = set(self.special_tokens.values())
+        self.bos_id, self.eos_id, self.add_bos = bos_id, eos_id, add_bos
+        self.add_space_prefix = add_space_prefix
+        self._pattern = _re.compile(pattern)
+        L = _lib()
+        self._L = L
+        blob = b"".join(self.vocab_bytes)
+        lens = np.asarray([len(b) for b in self.vocab_bytes], dtype=np.int32)
+        sc = np.asarray(scores, dtype=np.float32) if scores is not None else None
+        self._h = L.b200_tok_create(blob, lens.ctypes.data, len(self.vocab_bytes),
+                                    sc.ctypes.data if sc is not None else None, unk_id)
+        if kind == "bpe":
+            for b in range(256):
+                tid = L.b200_tok_lookup(self._h, bytes([b]), 1)
+                if tid >= 0:
+                    L.b200_tok_set_byte_token(self._h, b, tid)
+            for rank, (a, b) in enumerate(merges or ()):
+                L.b200_tok_add_merge(self._h, a, b, rank)
+        else:
+            for b, tid in (byte_fallback or {}).items():
+                L.b200_tok_set_byte_token(self._h, b, tid)
+        if self.special_tokens:
+            alt = "|".join(_re.escape(s) for s in sorted(self.special_tokens, key=len, reverse=True))
+            self._special_re = _re.compile(f"({alt})")
+        else:
+            self._special_re = None
+        self._buf = (C.c_int32 * 4096)()
+
+    def __del__(self):  # pragma: no cover
+        try:
+            if self._h:
+                self._L.b200_tok_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    @property
+    def vocab_size(self) -> int:
+        return len(self.vocab_bytes)
+
+    # ------------------------------------------------------------------------------ encode
+    def _encode_piece(self, data: bytes, fn) -> list[int]:
+        cap = max(len(data), 1)
+        buf = self._buf if cap <= 4096 else (C.c_int32 * cap)()
+        n = fn(self._h, data, len(data), buf, cap)
+        if n < 0:
+            raise ValueError("tokenizer buffer overflow")
+        return list(buf[:n])
+
+    def _encode_ordinary(self, text: str) -> list[int]:
+        out: list[int] = []
+        if not text:
+            return out
+        if self.kind == "bpe":
+            for m in self._pattern.finditer(text):
+                out.extend(self._encode_piece(m.group().encode("utf-8"), self._L.b200_tok_encode_rank))
+        else:
+            t = text.replace(" ", "▁")
+            out.extend(self._encode_piece(t.encode("utf-8"), self._L.b200_tok_encode_score))
+        return out
+
+    def encode(self, text: str, add_special: bool = True, allow_special: bool = True) -> list[int]:
+        ids: list[int] = []
+        if add_special and self.add_bos and self.bos_id is not None:
+            ids.append(self.bos_id)
+        first = True
+        parts = self._special_re.split(text) if (self._special_re is not None and allow_special) else [text]
+        for part in parts:
+            if not part:
+                continue
+            if allow_special and part in self.special_tokens:
+                ids.append(self.special_tokens[part])
+            else:
+                if self.kind == "spm" and self.add_space_prefix and first:
+                    part = " " + part
+                ids.extend(self._encode_ordinary(part))
+            first = False
+        return ids
+
+    # ------------------------------------------------------------------------------ decode
+    def token_bytes(self, tid: int) -> bytes:
+        if 0 <= tid < len(self.vocab_bytes):
+            return self.vocab_bytes[tid]
+        return b""
+
+    def decode_bytes(self, ids: Iterable[int], skip_special: bool = True) -> bytes:
+        out = bytearray()
+        for t in ids:
+            if skip_special and t in self.special_ids:
+                continue
+            out += self.token_bytes(t)
+        return bytes(out)
+
+    def decode(self, ids: Iterable[int], skip_special: bool = True) -> str:
+        text = self.decode_bytes(ids, skip_special).decode("utf-8", errors="replace")
+        if self.kind == "spm":
+            text = text.replace("▁", " ")
+            if self.add_space_prefix and text.startswith(" "):
+                text = text[1:]
+        return text
+
+    def stream_decoder(self) -> "StreamDecoder":
+        return StreamDecoder(self)
+
+    # ------------------------------------------------------------------------------ loaders
+    @staticmethod
+    def from_hf_json(path: str | Path) -> "Tokenizer":
+        """Load a Hugging Face ``tokenizer.json`` with a BPE model (byte-level or byte-fallback)."""
+        d = json.loads(Path(path).read_text(encoding="utf-8"))
+        model = d["model"]
+        if model.get("type") != "BPE":
+            raise ValueError(f"unsupported tokenizer model {model.get('type')}")
+        vocab: dict[str, int] = model["vocab"]
+        added = {t["content"]: t["id"] for t in d.get("added_tokens", [])}
+        size = max(list(vocab.values()) + list(added.values())) + 1
+        pre = json.dumps(d.get("pre_tokenizer") or {})
+        byte_level = "ByteLevel" in pre or "ByteLevel" in json.dumps(d.get("decoder") or {})
+        toks: list[bytes] = [b""] * size
+        for s, i in vocab.items():
+            toks[i] = bytes(_U2B[c] for c in s) if byte_level and all(c in _U2B for c in s) else s.encode("utf-8")
+        for s, i in added.items():
+            toks[i] = s.encode("utf-8")
+        merges = []
+        for m in model.get("merges", []):
+            a, b = m.split(" ", 1) if isinstance(m, str) else m
+            if a in vocab and b in vocab:
+                merges.append((vocab[a], vocab[b]))
+        pattern = GPT2_PATTERN
+        mobj = _re.search(r'"Regex":\s*"((?:[^"\\]|\\.)*)"', pre)
+        if mobj:
+            try:
+                cand = json.loads('"' + mobj.group(1) + '"')
+                _re.compile(cand)
+                pattern = cand
+            except Exception:
+                pass
+        if byte_level:
+            return Tokenizer("bpe", toks, merges=merges, special_tokens=added, pattern=pattern)
+        # SentencePiece-BPE exported to tokenizer.json (Llama-2 / Mistral): score = -rank
+        scores = [0.0] * size
+        for rank, (a, b) in enumerate(merges):
+            mid = vocab.get(next(k for k, v in vocab.items() if v == a) + next(k for k, v in vocab.items() if v == b))
+            if mid is not None:
+                scores[mid] = -float(rank)
+        fb = {b: vocab[f"<0x{b:02X}>"] for b in range(256) if f"<0x{b:02X}>" in vocab}
+        return Tokenizer("spm", toks, scores=scores, special_tokens=added, byte_fallback=fb,
+                         unk_id=vocab.get("<unk>", -1))
+
+    @staticmethod
+    def from_gguf_metadata(md: dict) -> "Tokenizer":
+        """Build from ``tokenizer.ggml.*`` keys (model ``gpt2`` = byte-level BPE, ``llama`` = score BPE)."""
+        tokens: list[str] = md["tokenizer.ggml.tokens"]
+        kind = md.get("tokenizer.ggml.model", "llama")
+        types = md.get("tokenizer.ggml.token_type") or [1] * len(tokens)
+        bos, eos = md.get("tokenizer.ggml.bos_token_id"), md.get("tokenizer.ggml.eos_token_id")
+        add_bos = bool(md.get("tokenizer.ggml.add_bos_token", kind == "llama"))
+        special = {t: i for i, (t, ty) in enumerate(zip(tokens, types)) if ty in (3, 4) and t}
+        if kind == "gpt2":
+            toks = [bytes(_U2B[c] for c in t) if all(c in _U2B for c in t) else t.encode("utf-8") for t in tokens]
+            index = {t: i for i, t in enumerate(tokens)}
+            merges = []
+            for m in md.get("tokenizer.ggml.merges", []):
+                a, b = m.split(" ", 1)
+                if a in index and b in index:
+                    merges.append((index[a], index[b]))
+            pre = md.get("tokenizer.ggml.pre", "")
+            pattern = LLAMA3_PATTERN if "llama" in pre else QWEN2_PATTERN if "qwen" in pre else GPT2_PATTERN
+            return Tokenizer("bpe", toks, merges=merges, special_tokens=special, pattern=pattern, bos_id=bos,
+                             eos_id=eos, add_bos=add_bos)
+        toks, fb = [], {}
+        for i, (t, ty) in enumerate(zip(tokens, types)):
+            if ty == 6 and len(t) == 6 and t.startswith("<0x"):
+                b = int(t[3:5], 16)
+                fb[b] = i
+                toks.append(bytes([b]))
+            else:
+                toks.append(t.encode("utf-8"))
+        scores = md.get("tokenizer.ggml.scores") or [0.0] * len(tokens)
+        return Tokenizer("spm", toks, scores=scores, special_tokens=special, bos_id=bos, eos_id=eos, add_bos=add_bos,
+                         add_space_prefix=bool(md.get("tokenizer.ggml.add_space_prefix", True)),
+                         unk_id=md.get("tokenizer.ggml.unknown_token_id", -1) or -1, byte_fallback=fb)
+
+
+class StreamDecoder:
+    """Feed token ids one at a time; get back only complete UTF-8 text (no broken code points)."""
+
+    def __init__(self, tok: Tokenizer):
+        self.tok = tok
+        self._pending = b""
+        self._first = True
+
+    def push(self, tid: int) -> str:
+        if tid in self.tok.special_ids:
+            return ""
+        self._pending += self.tok.token_bytes(tid)
+        # emit the longest prefix that is valid UTF-8
+        end = len(self._pending)
+        for cut in range(0, min(4, end) + 1):
+            try:
+                text = self._pending[:end - cut].decode("utf-8")
+                self._pending = self._pending[end - cut:]
+                break
+            except UnicodeDecodeError:
+                continue
+        else:
+            text = self._pending.decode("utf-8", errors="replace")
+            self._pending = b""
+        if self.tok.kind == "spm":
+            text = text.replace("▁", " ")
+            if self._first and self.tok.add_space_prefix and text.startswith(" "):
+                text = text[1:]
+        if text:
+            self._first = False
+        return text
+
+    def flush(self) -> str:
+        text = self._pending.decode("utf-8", errors="replace")
+        self._pending = b""
+        return text
+
+
+class ByteTokenizer(Tokenizer):
+    """Trivial tokenizer (one token per byte + optional specials) for synthetic checkpoints and tests
+    (the role of the reference's ``StubTokenizer``)."""
+
+    def __init__(self, specials: Optional[dict[str, int]] = None, vocab_size: int = 256):
+        toks = [bytes([i]) for i in range(256)] + [b""] * max(0, vocab_size - 256)
+        for s, i in (specials or {}).items():
+            if i >= len(toks):
+                toks += [b""] * (i + 1 - len(toks))
+            toks[i] = s.encode()
+        super().__init__("bpe", toks, merges=[], special_tokens=specials or {}, pattern=r"(?s).")

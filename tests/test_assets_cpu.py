@@ -1,0 +1,127 @@
+"""Checkpoint containers and codecs on CPU."""
+import numpy as np
+import pytest
+import torch
+
+from hartsyinference_b200.assets import gguf as G
+from hartsyinference_b200.assets import safetensors as ST
+
+
+def test_safetensors_roundtrip_and_sharded(tmp_path):
+    a = {"w.a": torch.randn(5, 7), "w.b": torch.randn(3).to(torch.bfloat16), "w.c": torch.arange(6, dtype=torch.int32).reshape(2, 3),
+         "w.q": (torch.randn(4, 4) * 10).to(torch.float8_e4m3fn), "empty": torch.empty(0, 4)}
+    ST.save_file(a, tmp_path / "x.safetensors", {"format": "pt", "note": 'quote " and \\ slash'})
+    f = ST.SafeTensorsFile(tmp_path / "x.safetensors")
+    assert set(f.keys()) == set(a)
+    for k, v in a.items():
+        got = f.get(k)
+        assert got.dtype == v.dtype and tuple(got.shape) == tuple(v.shape)
+        assert torch.equal(got.view(torch.uint8), v.view(torch.uint8)) if v.numel() else True
+    assert f.metadata["note"] == 'quote " and \\ slash'
+    # cross-check with the reference implementation of the format when it is installed
+    try:
+        from safetensors.torch import load_file
+        ref = load_file(str(tmp_path / "x.safetensors"))
+        assert torch.equal(ref["w.a"], a["w.a"])
+    except ImportError:
+        pass
+    ST.save_file({"p": torch.ones(2)}, tmp_path / "m-00001.safetensors")
+    ST.save_file({"q": torch.zeros(2)}, tmp_path / "m-00002.safetensors")
+    (tmp_path / "x.safetensors").unlink()
+    ck = ST.ShardedCheckpoint(tmp_path)
+    assert torch.equal(ck.get("p"), torch.ones(2)) and ck.get("nope") is None
+
+
+def test_safetensors_rejects_garbage(tmp_path):
+    p = tmp_path / "bad.safetensors"
+    p.write_bytes(b"\xff" * 64)
+    with pytest.raises(Exception):
+        ST.SafeTensorsFile(p)
+
+
+@pytest.mark.parametrize("name,tol", [("Q8_0", 0.01), ("Q4_0", 0.12), ("Q4_K", 0.08)])
+def test_ggml_quant_dequant_roundtrip(name, tol):
+    torch.manual_seed(0)
+    x = torch.randn(8, 512)
+    t = G.GGML_TYPES[name]
+    raw = G.quantize(x, t)
+    blk, nb = G.type_geometry(t)
+    assert raw.numel() == x.numel() // blk * nb
+    y = G.dequantize(raw, t, x.numel()).reshape(x.shape)
+    rel = ((y - x).norm() / x.norm()).item()
+    assert rel < tol, rel
+
+
+def test_q8_0_matches_the_format_definition():
+    # x = scale * q with scale = absmax / 127 stored as fp16, q = round(x / scale) clamped to +-127
+    torch.manual_seed(1)
+    x = torch.randn(64)
+    raw = G.quantize(x, 8).numpy()
+    for b in range(2):
+        blk = raw[b * 34:(b + 1) * 34]
+        d = np.frombuffer(blk[:2].tobytes(), dtype=np.float16)[0].astype(np.float32)
+        q = np.frombuffer(blk[2:].tobytes(), dtype=np.int8).astype(np.float32)
+        xs = x[b * 32:(b + 1) * 32].numpy()
+        assert abs(d - np.abs(xs).max() / 127) < 1e-3 * max(1.0, d)
+        assert np.abs(q * d - xs).max() <= d * 0.51 + 1e-3
+
+
+def test_other_codecs_decode_hand_built_blocks():
+    # Q4_1: y = q * d + m ; Q5_0: 5-bit value minus 16 ; IQ4_NL: table lookup
+    d, m = np.float16(0.5), np.float16(-1.0)
+    qs = np.arange(16, dtype=np.uint8) | (np.arange(16, dtype=np.uint8)[::-1] << 4)
+    blk = d.tobytes() + m.tobytes() + qs.tobytes()
+    y = G.dequantize(blk, 3, 32).numpy()
+    assert np.allclose(y[:16], np.arange(16) * 0.5 - 1.0) and np.allclose(y[16:], np.arange(16)[::-1] * 0.5 - 1.0)
+    qh = np.uint32(0xFFFF0000)
+    blk5 = np.float16(1.0).tobytes() + qh.tobytes() + np.zeros(16, dtype=np.uint8).tobytes()
+    y5 = G.dequantize(blk5, 6, 32).numpy()
+    assert np.allclose(y5[:16], -16.0) and np.allclose(y5[16:], 0.0)
+    blkn = np.float16(1.0).tobytes() + np.full(16, 0x0F, dtype=np.uint8).tobytes()
+    yn = G.dequantize(blkn, 20, 32).numpy()
+    assert np.allclose(yn[:16], 113.0) and np.allclose(yn[16:], -127.0)
+
+
+def test_q6_k_and_q5_k_against_numpy_restatement():
+    rng = np.random.default_rng(0)
+    # Q6_K
+    ql = rng.integers(0, 256, 128, dtype=np.uint8); qh = rng.integers(0, 256, 64, dtype=np.uint8)
+    qli, qhi = ql.astype(np.int32), qh.astype(np.int32)
+    sc = rng.integers(-32, 32, 16, dtype=np.int8); d = np.float16(0.01)
+    blk = ql.tobytes() + qh.tobytes() + sc.tobytes() + d.tobytes()
+    y = G.dequantize(blk, 14, 256).numpy()
+    ref = np.zeros(256, dtype=np.float32)
+    for n0 in (0, 1):
+        for l in range(32):
+            i_s = l // 16
+            base = n0 * 128
+            q_l, q_h, s = qli[n0 * 64:], qhi[n0 * 32:], sc[n0 * 8:].astype(np.int32)
+            q1 = ((q_l[l] & 0xF) | (((q_h[l] >> 0) & 3) << 4)) - 32
+            q2 = ((q_l[l + 32] & 0xF) | (((q_h[l] >> 2) & 3) << 4)) - 32
+            q3 = ((q_l[l] >> 4) | (((q_h[l] >> 4) & 3) << 4)) - 32
+            q4 = ((q_l[l + 32] >> 4) | (((q_h[l] >> 6) & 3) << 4)) - 32
+            ref[base + l] = float(d) * s[i_s] * q1; ref[base + l + 32] = float(d) * s[i_s + 2] * q2
+            ref[base + l + 64] = float(d) * s[i_s + 4] * q3; ref[base + l + 96] = float(d) * s[i_s + 6] * q4
+    assert np.allclose(y, ref, atol=1e-5)
+
+
+def test_gguf_write_read(tmp_path):
+    torch.manual_seed(2)
+    tensors = {"token_embd.weight": torch.randn(64, 256), "blk.0.attn_q.weight": torch.randn(256, 256),
+               "output_norm.weight": torch.ones(256)}
+    md = {"general.architecture": "llama", "llama.block_count": 1, "llama.embedding_length": 256,
+          "llama.attention.head_count": 4, "llama.rope.freq_base": 10000.0, "general.name": "toy ✓",
+          "tokenizer.ggml.tokens": ["a", "b", "c"], "tokenizer.ggml.scores": [0.5, 1.0, 2.0],
+          "tokenizer.ggml.token_type": [1, 1, 1], "llama.use_thing": True}
+    G.write_gguf(tmp_path / "t.gguf", md, tensors, quant={"blk.0.attn_q.weight": 12, "token_embd.weight": 8})
+    f = G.GgufFile(tmp_path / "t.gguf")
+    assert f.version == 3 and f.metadata["general.name"] == "toy ✓" and f.metadata["llama.block_count"] == 1
+    assert f.metadata["tokenizer.ggml.tokens"] == ["a", "b", "c"] and f.metadata["llama.use_thing"] is True
+    assert f.info("blk.0.attn_q.weight") == (12, (256, 256)) and f.info("output_norm.weight")[0] == 0
+    q = f.get("blk.0.attn_q.weight")
+    assert ((q - tensors["blk.0.attn_q.weight"]).norm() / tensors["blk.0.attn_q.weight"].norm()).item() < 0.08
+    assert torch.equal(f.get("output_norm.weight"), tensors["output_norm.weight"])
+    assert f.raw("token_embd.weight").numel() == 64 * 256 // 32 * 34
+    from hartsyinference_b200.models.llm.config import from_gguf_metadata
+    cfg = from_gguf_metadata(f.metadata)
+    assert cfg.hidden_size == 256 and cfg.num_heads == 4 and cfg.vocab_size == 3
