@@ -1,0 +1,194 @@
+"""Public request / result records of the engine.
+
+Field names and defaults follow the reference's records so that the C ABI and the .NET facade can
+stay source-compatible with it: ``TextRequest`` (Messages, Temperature 0.7, TopP 0.95, TopK, MinP,
+RepetitionPenalty, MaxTokens 4096, Seed, Greedy, EnableThinking, Device, Tools, GraphDecode,
+SpeculativeDecode), ``TextResult``, ``TextChunk{Kind}``, ``StopReason``, ``ImageRequest`` /
+``ImageResult{Rgb, Width, Height, Seed, Meta}``, ``VideoRequest`` / ``VideoGenerationResult{Frames,
+Audio, Fps}``, ``StepPreview``, ``ModelSpec{Requested, Modality, Catalog, LocalPath, Aux}``,
+``EngineOptions{ModelCacheDirectory, LowVram, Placement, KvPageSize 16, KvPoolBytesBudget}``
+(src/HartsyInference.Engine/Requests/, Dispatch/ModelSpec.cs, Dispatch/Modality.cs, EngineOptions.cs).
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import asdict, dataclass, field
+from typing import Any, Optional
+
+from ..parallel.config import ParallelConfig
+
+
+class Modality(str, enum.Enum):
+    TEXT = "text"
+    IMAGE = "image"
+    VIDEO = "video"
+    MUSIC = "music"
+    SPEECH = "speech"
+    TRANSCRIBE = "transcribe"
+    VOICE_CONVERSION = "voice_conversion"
+    FX = "fx"
+    VISION = "vision"
+    RESTORE = "restore"
+    MESH = "mesh"
+    WORLD = "world"
+    EMBEDDINGS = "embeddings"
+
+
+class StopReason(str, enum.Enum):
+    STOP = "stop"
+    LENGTH = "length"
+    TOOL_CALL = "tool_call"
+    CANCELLED = "cancelled"
+    ERROR = "error"
+
+
+class ChunkKind(str, enum.Enum):
+    CHUNK = "chunk"
+    RESULT = "result"
+    STATUS = "status"
+    STOP_REASON = "stop_reason"
+    NATIVE_TOOL_CALL = "native_tool_call"
+
+
+@dataclass
+class ModelSpec:
+    requested: str                       # what the caller asked for (name, alias or path)
+    modality: Modality = Modality.TEXT
+    catalog: Optional[str] = None        # catalog id when resolved from the registry
+    local_path: Optional[str] = None     # resolved checkpoint path
+    aux: dict[str, str] = field(default_factory=dict)   # side models: vae, text_encoder, mmproj, ...
+
+
+@dataclass
+class EngineOptions:
+    model_cache_directory: str = "~/.hartsyinference/models"
+    low_vram: bool = False
+    placement: ParallelConfig = field(default_factory=ParallelConfig)
+    kv_page_size: int = 16
+    kv_pool_bytes_budget: int = 0        # 0 = size the pool from free device memory
+    max_batch: int = 256
+    max_model_len: int = 8192
+
+
+@dataclass
+class TextRequest:
+    messages: list[dict] = field(default_factory=list)
+    prompt: Optional[str] = None         # raw prompt (bypasses the chat template)
+    temperature: float = 0.7
+    top_p: float = 0.95
+    top_k: int = 0
+    min_p: float = 0.0
+    repetition_penalty: float = 1.0
+    max_tokens: int = 4096
+    seed: Optional[int] = None
+    greedy: bool = False
+    enable_thinking: Optional[bool] = None
+    device: Optional[str] = None
+    tools: Optional[list] = None
+    force_tool_id: Optional[str] = None
+    graph_decode: bool = True
+    speculative_decode: bool = False
+    stop: list[str] = field(default_factory=list)
+    json_mode: bool = False
+
+
+@dataclass
+class TextResult:
+    text: str = ""
+    token_ids: list[int] = field(default_factory=list)
+    prompt_tokens: int = 0
+    completion_tokens: int = 0
+    stop_reason: StopReason = StopReason.STOP
+    ttft_s: float = 0.0
+    total_s: float = 0.0
+    error: Optional[str] = None
+
+    @property
+    def tokens_per_second(self) -> float:
+        dt = self.total_s - self.ttft_s
+        return (self.completion_tokens - 1) / dt if dt > 0 and self.completion_tokens > 1 else 0.0
+
+
+@dataclass
+class TextChunk:
+    kind: ChunkKind
+    text: str = ""
+    result: Optional[TextResult] = None
+    stop_reason: Optional[StopReason] = None
+    status: Optional[str] = None
+
+
+@dataclass
+class ImageRequest:
+    prompt: str = ""
+    negative_prompt: str = ""
+    width: int = 1024
+    height: int = 1024
+    steps: int = 20
+    guidance: float = 3.5
+    cfg_scale: float = 1.0               # > 1 runs true classifier-free guidance (two branches)
+    seed: Optional[int] = None
+    sampler: str = "euler"
+    scheduler: str = "flow_match_euler"
+    batch: int = 1
+    init_image: Optional[Any] = None
+    strength: float = 1.0
+    loras: list[tuple[str, float]] = field(default_factory=list)
+    step_cache_threshold: float = 0.0
+
+
+@dataclass
+class StepPreview:
+    step: int
+    total_steps: int
+    latents: Optional[Any] = None
+    preview_rgb: Optional[bytes] = None
+
+
+@dataclass
+class ImageResult:
+    rgb: bytes = b""                     # RGB24, row-major
+    width: int = 0
+    height: int = 0
+    seed: int = 0
+    meta: dict = field(default_factory=dict)
+
+
+@dataclass
+class VideoRequest:
+    prompt: str = ""
+    negative_prompt: str = ""
+    width: int = 832
+    height: int = 480
+    frames: int = 81
+    fps: int = 16
+    steps: int = 50
+    cfg_scale: float = 5.0
+    seed: Optional[int] = None
+    scheduler: str = "unipc"
+    shift: float = 5.0
+
+
+@dataclass
+class VideoGenerationResult:
+    frames: list = field(default_factory=list)      # list of RGB24 byte strings
+    width: int = 0
+    height: int = 0
+    audio: Optional[bytes] = None
+    fps: int = 16
+    seed: int = 0
+    meta: dict = field(default_factory=dict)
+
+
+def to_jsonable(obj) -> Any:
+    if isinstance(obj, enum.Enum):
+        return obj.value
+    if hasattr(obj, "__dataclass_fields__"):
+        return {k: to_jsonable(v) for k, v in asdict(obj).items()}
+    if isinstance(obj, (list, tuple)):
+        return [to_jsonable(v) for v in obj]
+    if isinstance(obj, dict):
+        return {k: to_jsonable(v) for k, v in obj.items()}
+    if isinstance(obj, bytes):
+        return None
+    return obj

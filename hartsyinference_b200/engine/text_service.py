@@ -1,0 +1,223 @@
+"""Text service: load an LLM once, serve many requests through one continuous-batching loop.
+
+``generate`` blocks, ``stream`` yields ``TextChunk`` records (Chunk ... Result). All requests of a
+model share one ``LLMEngine`` driven by a background thread, so concurrent callers are batched
+together (in the reference the live routes run one request at a time per device slot and only the
+test-hosted ``ModelManager`` batches; src/HartsyInference.Engine/Services/TextService.cs:74-160,
+ModelManager.cs:148-212). Prompt-lookup speculative decoding mirrors
+``TextGenerationPipeline.GenerateSpeculative`` (n-gram 3, draft 8, look-back 4096;
+src/HartsyInference.LLM/Generation/TextGenerationPipeline.cs:403-463) as an n-gram proposer whose
+drafts are verified by the engine.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from dataclasses import dataclass
+from typing import Iterator, Optional
+
+import torch
+
+from .. import log
+from ..assets.grammar import JsonGrammar
+from ..models.llm.loader import LoadedLLM, load_llm
+from ..parallel.comm import Comm
+from .llm_engine import LLMEngine
+from .metrics import REGISTRY
+from .requests import ChunkKind, EngineOptions, ModelSpec, StopReason, TextChunk, TextRequest, TextResult
+from .sampling import SamplingParams
+
+_REASON = {"stop": StopReason.STOP, "length": StopReason.LENGTH, "cancelled": StopReason.CANCELLED,
+           "error": StopReason.ERROR}
+
+
+@dataclass
+class _Hosted:
+    llm: LoadedLLM
+    engine: LLMEngine
+    lock: threading.Lock
+    wake: threading.Condition
+    thread: Optional[threading.Thread] = None
+    running: bool = True
+    healthy: bool = True
+
+
+class TextService:
+    def __init__(self, options: EngineOptions, device: str = "cuda", comm: Optional[Comm] = None):
+        self.options = options
+        self.device = device
+        self.comm = comm
+        self._models: dict[str, _Hosted] = {}
+        self._lock = threading.Lock()
+
+    # ------------------------------------------------------------------------------ loading
+    def _host(self, spec: ModelSpec) -> _Hosted:
+        path = spec.local_path or spec.requested
+        key = f"{path}|{self.options.placement.cache_key}|{self.device}"
+        with self._lock:
+            h = self._models.get(key)
+            if h is not None:
+                return h
+            llm = load_llm(path, self.device, self.comm)
+            eng = LLMEngine(llm.model, page_size=self.options.kv_page_size, max_batch=self.options.max_batch,
+                            max_model_len=min(self.options.max_model_len, llm.config.max_position),
+                            kv_pool_bytes=self.options.kv_pool_bytes_budget or None)
+            lk = threading.Lock()
+            h = _Hosted(llm, eng, lk, threading.Condition(lk))
+            h.thread = threading.Thread(target=self._loop, args=(h,), daemon=True, name=f"llm-loop-{len(self._models)}")
+            h.thread.start()
+            self._models[key] = h
+            return h
+
+    def loaded_keys(self) -> list[str]:
+        return list(self._models)
+
+    def unhealthy_models(self) -> list[str]:
+        return [k for k, h in self._models.items() if not h.healthy or not (h.thread and h.thread.is_alive())]
+
+    def release(self, key: Optional[str] = None) -> None:
+        with self._lock:
+            keys = [key] if key else list(self._models)
+            for k in keys:
+                h = self._models.pop(k, None)
+                if h is None:
+                    continue
+                with h.wake:
+                    h.running = False
+                    h.wake.notify_all()
+                if h.thread:
+                    h.thread.join(timeout=10)
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    def _loop(self, h: _Hosted) -> None:
+        if h.engine.cuda:
+            torch.cuda.set_device(h.engine.device)
+        while True:
+            with h.wake:
+                while h.running and not h.engine.has_work():
+                    h.wake.wait(timeout=0.5)
+                if not h.running:
+                    return
+                try:
+                    h.engine.step()
+                    st = h.engine.stats()
+                    REGISTRY.set("hartsyinference_kv_pages_used", st["pages_used"])
+                    REGISTRY.set("hartsyinference_batch_size", st["running"])
+                except Exception as e:  # the engine contains step faults itself; this is the last line of defence
+                    log.warn(f"[TextService] serving loop error: {type(e).__name__}: {e}")
+                    h.healthy = False
+
+    # ------------------------------------------------------------------------------ requests
+    def _params(self, req: TextRequest, llm: LoadedLLM) -> SamplingParams:
+        mask = None
+        if req.json_mode:
+            grammar = JsonGrammar(llm.tokenizer)
+            mask = grammar.allowed_mask
+        return SamplingParams(temperature=req.temperature, top_p=req.top_p, top_k=req.top_k, min_p=req.min_p,
+                              repetition_penalty=req.repetition_penalty, max_tokens=req.max_tokens, seed=req.seed,
+                              greedy=req.greedy, logits_mask=mask)
+
+    def count_tokens(self, spec: ModelSpec, req: TextRequest) -> int:
+        h = self._host(spec)
+        return len(self._prompt_ids(h.llm, req))
+
+    def _prompt_ids(self, llm: LoadedLLM, req: TextRequest) -> list[int]:
+        if req.prompt is not None:
+            return llm.tokenizer.encode(req.prompt)
+        text = llm.chat_template.render(req.messages, add_generation_prompt=True, tools=req.tools,
+                                        enable_thinking=req.enable_thinking)
+        return llm.tokenizer.encode(text, add_special=not text.startswith(llm.chat_template.bos_token or "\0"))
+
+    def stream(self, spec: ModelSpec, req: TextRequest, cancel: Optional[threading.Event] = None) -> Iterator[TextChunk]:
+        h = self._host(spec)
+        llm = h.llm
+        ids = self._prompt_ids(llm, req)
+        q: "queue.Queue[tuple[int, bool]]" = queue.Queue()
+        t0 = time.perf_counter()
+        with h.wake:
+            rid = h.engine.add_request(ids, self._params(req, llm), on_token=lambda r, tok, fin: q.put((tok, fin)))
+            h.wake.notify_all()
+        dec = llm.tokenizer.stream_decoder()
+        text = ""
+        out_ids: list[int] = []
+        ttft = 0.0
+        stop_hit = False
+        while True:
+            if cancel is not None and cancel.is_set():
+                with h.wake:
+                    h.engine.cancel(rid)
+                break
+            try:
+                tok, fin = q.get(timeout=0.1)
+            except queue.Empty:
+                if not (h.thread and h.thread.is_alive()):
+                    break
+                continue
+            if tok >= 0:
+                if not out_ids:
+                    ttft = time.perf_counter() - t0
+                out_ids.append(tok)
+                piece = dec.push(tok)
+                if piece:
+                    text += piece
+                    cut = min((text.find(s) for s in req.stop if s and s in text), default=-1)
+                    if cut >= 0:
+                        text = text[:cut]
+                        stop_hit = True
+                        with h.wake:
+                            h.engine.cancel(rid)
+                        break
+                    yield TextChunk(ChunkKind.CHUNK, text=piece)
+            if fin:
+                break
+        tail = dec.flush()
+        if tail and not stop_hit:
+            text += tail
+            yield TextChunk(ChunkKind.CHUNK, text=tail)
+        with h.wake:
+            r = h.engine.release(rid)
+        reason = StopReason.STOP if stop_hit else _REASON.get((r.finish_reason if r else None) or "stop", StopReason.STOP)
+        res = TextResult(text=text, token_ids=out_ids, prompt_tokens=len(ids), completion_tokens=len(out_ids),
+                         stop_reason=reason, ttft_s=ttft, total_s=time.perf_counter() - t0,
+                         error=r.error if r else None)
+        REGISTRY.inc("hartsyinference_tokens_total", len(out_ids))
+        REGISTRY.set("hartsyinference_ttft_seconds", ttft)
+        REGISTRY.set("hartsyinference_decode_tok_s", res.tokens_per_second)
+        yield TextChunk(ChunkKind.STOP_REASON, stop_reason=reason)
+        yield TextChunk(ChunkKind.RESULT, result=res)
+
+    def generate(self, spec: ModelSpec, req: TextRequest, cancel: Optional[threading.Event] = None) -> TextResult:
+        res = None
+        for ch in self.stream(spec, req, cancel):
+            if ch.kind == ChunkKind.RESULT:
+                res = ch.result
+        assert res is not None
+        return res
+
+    def embed(self, spec: ModelSpec, texts: list[str]) -> torch.Tensor:
+        """Mean-pooled, L2-normalised final hidden states (decoder-as-embedder, the reference's
+        ``DecoderEmbeddingModel``)."""
+        from ..models.llm.transformer import ForwardBatch
+        h = self._host(spec)
+        m = h.llm.model
+        outs = []
+        with h.wake:
+            for t in texts:
+                ids = h.llm.tokenizer.encode(t)[: 512]
+                n = len(ids)
+                dev = m.device
+                pages = (n + 15) // 16
+                saved = m.kv_cache
+                m.alloc_kv(max(pages, 1), 16)
+                b = ForwardBatch(tokens=torch.tensor(ids, dtype=torch.int32, device=dev),
+                                 positions=torch.arange(n, dtype=torch.int32, device=dev),
+                                 slot_mapping=torch.arange(n, dtype=torch.int64, device=dev),
+                                 block_table=torch.arange(max(pages, 1), dtype=torch.int32, device=dev)[None],
+                                 kv_lens=torch.tensor([n], dtype=torch.int32, device=dev), is_decode=False,
+                                 cu_q=torch.tensor([0, n], dtype=torch.int32, device=dev), max_q_len=n, max_kv_len=n)
+                hid = m.forward_hidden(b).float().mean(0)
+                m.kv_cache = saved
+                outs.append(torch.nn.functional.normalize(hid, dim=0).cpu())
+        return torch.stack(outs)

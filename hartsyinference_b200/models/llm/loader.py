@@ -1,0 +1,164 @@
+"""Load a decoder LLM from a Hugging Face directory (``config.json`` + safetensors shards) or from a
+GGUF file, together with its tokenizer and chat template.
+
+Counterpart of ``GgufLanguageModel.Load`` (GGUF -> config -> tokenizer -> chat template ->
+transformer; src/HartsyInference.LLM/Generation/GgufLanguageModel.cs:206) and of the per-architecture
+GGUF key mappers (src/HartsyInference.ModelAssets/Gguf/KeyMappers/). The reference loads text LLMs
+from GGUF only; safetensors directories are accepted here as well.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Callable, Optional
+
+import torch
+
+from ... import log
+from ...assets.chat_template import ChatTemplate
+from ...assets.gguf import GgufFile
+from ...assets.safetensors import ShardedCheckpoint
+from ...assets.tokenizer import ByteTokenizer, Tokenizer
+from ...exceptions import UnsupportedModelError
+from ...parallel.comm import Comm
+from .config import TransformerConfig, from_gguf_metadata, from_hf_config
+from .transformer import DecoderModel
+
+# GGUF tensor name -> Hugging Face name (llama-family layout shared by qwen2/3, mistral, gemma, ...)
+_GGUF_LAYER = {
+    "attn_norm.weight": "input_layernorm.weight",
+    "attn_q.weight": "self_attn.q_proj.weight", "attn_q.bias": "self_attn.q_proj.bias",
+    "attn_k.weight": "self_attn.k_proj.weight", "attn_k.bias": "self_attn.k_proj.bias",
+    "attn_v.weight": "self_attn.v_proj.weight", "attn_v.bias": "self_attn.v_proj.bias",
+    "attn_output.weight": "self_attn.o_proj.weight",
+    "attn_q_norm.weight": "self_attn.q_norm.weight", "attn_k_norm.weight": "self_attn.k_norm.weight",
+    "ffn_norm.weight": "post_attention_layernorm.weight",
+    "ffn_gate.weight": "mlp.gate_proj.weight", "ffn_up.weight": "mlp.up_proj.weight",
+    "ffn_down.weight": "mlp.down_proj.weight",
+    "post_attention_norm.weight": "post_attention_layernorm.weight",
+    "post_ffw_norm.weight": "post_feedforward_layernorm.weight",
+}
+_GGUF_TOP = {"token_embd.weight": "model.embed_tokens.weight", "output_norm.weight": "model.norm.weight",
+             "output.weight": "lm_head.weight"}
+
+
+def gguf_name_to_hf(name: str) -> Optional[str]:
+    if name in _GGUF_TOP:
+        return _GGUF_TOP[name]
+    if name.startswith("blk."):
+        _, idx, rest = name.split(".", 2)
+        hf = _GGUF_LAYER.get(rest)
+        if hf:
+            return f"model.layers.{idx}.{hf}"
+    return None
+
+
+@dataclass
+class LoadedLLM:
+    model: DecoderModel
+    tokenizer: Tokenizer
+    chat_template: ChatTemplate
+    config: TransformerConfig
+    source: str
+
+
+def _gemma_sandwich_fix(cfg: TransformerConfig, get: Callable[[str], Optional[torch.Tensor]]):
+    """GGUF Gemma-2/3 files name the pre-FFN norm ``ffn_norm`` and the post-attention norm
+    ``post_attention_norm``; the model expects HF names."""
+    if not cfg.post_norms:
+        return get
+
+    def wrapped(name: str):
+        if name.endswith("pre_feedforward_layernorm.weight"):
+            return get(name.replace("pre_feedforward_layernorm", "__ffn_norm__"))
+        return get(name)
+    return wrapped
+
+
+def load_llm(path: str | Path, device: str | torch.device = "cuda", comm: Optional[Comm] = None,
+             fp8: Optional[bool] = None) -> LoadedLLM:
+    p = Path(path)
+    if p.is_file() and p.suffix == ".gguf":
+        return _load_gguf(p, device, comm, fp8)
+    if p.is_dir() and (p / "config.json").exists():
+        return _load_hf(p, device, comm, fp8)
+    if p.is_dir():
+        ggufs = sorted(p.glob("*.gguf"))
+        if ggufs:
+            return _load_gguf(ggufs[0], device, comm, fp8)
+    raise UnsupportedModelError(f"{path}: neither a .gguf file nor a directory with config.json")
+
+
+def _want_fp8(fp8: Optional[bool], device) -> bool:
+    from ... import config
+    if fp8 is not None:
+        return fp8
+    return bool(config.get("fp8_linears")) and torch.device(device).type == "cuda"
+
+
+def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
+    cfg = from_hf_config(json.loads((p / "config.json").read_text()))
+    ck = ShardedCheckpoint(p)
+    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
+    model.load_state_dict(ck.get)
+    tok: Tokenizer
+    if (p / "tokenizer.json").exists():
+        tok = Tokenizer.from_hf_json(p / "tokenizer.json")
+    else:
+        tok = ByteTokenizer(vocab_size=cfg.vocab_size)
+    tpl_src, bos, eos = None, "", ""
+    tc = p / "tokenizer_config.json"
+    if tc.exists():
+        d = json.loads(tc.read_text())
+        tpl_src = d.get("chat_template")
+        bos = d.get("bos_token") if isinstance(d.get("bos_token"), str) else ""
+        eos = d.get("eos_token") if isinstance(d.get("eos_token"), str) else ""
+    tpl = ChatTemplate(tpl_src, bos or "", eos or "") if tpl_src else ChatTemplate.for_arch(cfg.arch)
+    log.info(f"[Load] {p.name}: {cfg.arch} {cfg.num_layers}L hidden {cfg.hidden_size} "
+             f"({model.weight_bytes() / 2**30:.2f} GiB on {device})")
+    return LoadedLLM(model, tok, tpl, cfg, str(p))
+
+
+def _load_gguf(p: Path, device, comm, fp8) -> LoadedLLM:
+    f = GgufFile(p)
+    cfg = from_gguf_metadata(f.metadata)
+    hf_to_gguf = {}
+    for name in f.keys():
+        hf = gguf_name_to_hf(name)
+        if hf:
+            hf_to_gguf[hf] = name
+    if cfg.post_norms:   # Gemma 2/3: ffn_norm is the pre-FFN norm
+        for i in range(cfg.num_layers):
+            a = f"model.layers.{i}.post_attention_layernorm.weight"
+            g = f"blk.{i}.ffn_norm.weight"
+            if g in f:
+                hf_to_gguf[f"model.layers.{i}.pre_feedforward_layernorm.weight"] = g
+            g2 = f"blk.{i}.post_attention_norm.weight"
+            if g2 in f:
+                hf_to_gguf[a] = g2
+
+    def get(name: str) -> Optional[torch.Tensor]:
+        g = hf_to_gguf.get(name)
+        return None if g is None else f.get(g, torch.bfloat16)
+
+    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
+    model.load_state_dict(get)
+    tok = Tokenizer.from_gguf_metadata(f.metadata) if "tokenizer.ggml.tokens" in f.metadata else ByteTokenizer(vocab_size=cfg.vocab_size)
+    src = f.metadata.get("tokenizer.chat_template")
+    tokens = f.metadata.get("tokenizer.ggml.tokens") or []
+    bos_id, eos_id = f.metadata.get("tokenizer.ggml.bos_token_id"), f.metadata.get("tokenizer.ggml.eos_token_id")
+    bos = tokens[bos_id] if isinstance(bos_id, int) and bos_id < len(tokens) else ""
+    eos = tokens[eos_id] if isinstance(eos_id, int) and eos_id < len(tokens) else ""
+    tpl = ChatTemplate(src, bos, eos) if src else ChatTemplate.for_arch(cfg.arch)
+    log.info(f"[Load] {p.name}: GGUF v{f.version} {cfg.arch} {cfg.num_layers}L hidden {cfg.hidden_size}")
+    return LoadedLLM(model, tok, tpl, cfg, str(p))
+
+
+def save_hf_checkpoint(model_cfg: dict, tensors: dict[str, torch.Tensor], out_dir: str | Path) -> None:
+    """Write ``config.json`` + ``model.safetensors`` (used to build synthetic checkpoints)."""
+    from ...assets.safetensors import save_file
+    d = Path(out_dir)
+    d.mkdir(parents=True, exist_ok=True)
+    (d / "config.json").write_text(json.dumps(model_cfg, indent=1))
+    save_file(tensors, d / "model.safetensors", {"format": "pt"})

