@@ -790,3 +790,100 @@ B200_API int b200_fill_random(void* out, long long n, unsigned long long seed, f
   CHECK_LAUNCH();
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------
+// DiT: split a packed qkv activation into head-major-free [T][H][D] q, k, v with optional per-head
+// RMSNorm on q and k and rotary embedding from per-token (cos, sin) tables. Pairs are interleaved
+// (2i, 2i+1), as in the Flux and Wan rotary layouts (src/HartsyInference.Diffusion/Models/
+// Denoisers/DiTBlocks/FluxRope.cs, WanRope.cs:18-25; kernels dit_qkv_split_norm_f32:1358,
+// dit_rope_f32:514, wan/wan_rope.cu). One warp per (token, head); d <= 256.
+//   qkv [T][q_cols + 2 * kv_cols] with q first, then k, then v (row pitch ld)
+//   cos/sin [T][d/2] fp32 (null = no rotation)
+// ------------------------------------------------------------------------------------------
+namespace b200 {
+struct DitQkvParams {
+  const __nv_bfloat16* qkv;
+  __nv_bfloat16 *q, *k, *v;
+  const __nv_bfloat16 *q_norm_w, *k_norm_w;
+  const float *cos, *sin;
+  int tokens, hq, hkv, d;
+  long long ld;
+  float eps;
+};
+
+__global__ void dit_qkv_kernel(const DitQkvParams p) {
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int heads = p.hq + 2 * p.hkv;
+  if (warp_global >= p.tokens * heads) return;
+  const int t = warp_global / heads, h = warp_global % heads;
+  const int kind = h < p.hq ? 0 : (h < p.hq + p.hkv ? 1 : 2);
+  const __nv_bfloat16* src = p.qkv + static_cast<long long>(t) * p.ld + static_cast<long long>(h) * p.d;
+  // lane owns pairs (2 * (lane + 32 * i), +1): d / 2 pairs over 32 lanes
+  const int pairs = p.d >> 1;
+  float a[4], b[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int pi = lane + 32 * i;
+    if (pi < pairs) {
+      const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(src + 2 * pi);
+      const float2 f = __bfloat1622float2(v2);
+      a[i] = f.x; b[i] = f.y;
+      ss += f.x * f.x + f.y * f.y;
+    } else { a[i] = b[i] = 0.f; }
+  }
+  const __nv_bfloat16* nw = kind == 0 ? p.q_norm_w : (kind == 1 ? p.k_norm_w : nullptr);
+  if (nw) {
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / p.d + p.eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int pi = lane + 32 * i;
+      if (pi < pairs) {
+        a[i] *= rstd * __bfloat162float(nw[2 * pi]);
+        b[i] *= rstd * __bfloat162float(nw[2 * pi + 1]);
+      }
+    }
+  }
+  __nv_bfloat16* dst;
+  if (kind == 0) dst = p.q + (static_cast<long long>(t) * p.hq + h) * p.d;
+  else if (kind == 1) dst = p.k + (static_cast<long long>(t) * p.hkv + (h - p.hq)) * p.d;
+  else dst = p.v + (static_cast<long long>(t) * p.hkv + (h - p.hq - p.hkv)) * p.d;
+  const bool rot = kind != 2 && p.cos != nullptr;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int pi = lane + 32 * i;
+    if (pi < pairs) {
+      float x = a[i], y = b[i];
+      if (rot) {
+        const float c = p.cos[static_cast<long long>(t) * pairs + pi], s = p.sin[static_cast<long long>(t) * pairs + pi];
+        x = a[i] * c - b[i] * s;
+        y = b[i] * c + a[i] * s;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(dst + 2 * pi) = __floats2bfloat162_rn(x, y);
+    }
+  }
+}
+}  // namespace b200
+
+B200_API int b200_dit_qkv(const void* qkv, void* q, void* k, void* v, const void* q_norm_w,
+                          const void* k_norm_w, const float* cos, const float* sin, int tokens, int hq,
+                          int hkv, int d, long long ld, float eps, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (d > 256 || (d & 1)) return -2;
+  DitQkvParams p{};
+  p.qkv = static_cast<const __nv_bfloat16*>(qkv);
+  p.q = static_cast<__nv_bfloat16*>(q);
+  p.k = static_cast<__nv_bfloat16*>(k);
+  p.v = static_cast<__nv_bfloat16*>(v);
+  p.q_norm_w = static_cast<const __nv_bfloat16*>(q_norm_w);
+  p.k_norm_w = static_cast<const __nv_bfloat16*>(k_norm_w);
+  p.cos = cos; p.sin = sin;
+  p.tokens = tokens; p.hq = hq; p.hkv = hkv; p.d = d; p.ld = ld; p.eps = eps;
+  const long long warps = static_cast<long long>(tokens) * (hq + 2 * hkv);
+  const long long blocks = (warps * 32 + 255) / 256;
+  dit_qkv_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p);
+  CHECK_LAUNCH();
+  return 0;
+}

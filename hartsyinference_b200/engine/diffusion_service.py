@@ -1,0 +1,119 @@
+"""Image and video services: resolve a model spec to a pipeline (cached per placement), run it.
+
+Counterparts: ``ImagesService.GenerateAsync`` (src/HartsyInference.Engine/Services/ImagesService.cs:
+26-52), the video service, and the per-family recipes that wire DiT + text encoders + VAE
+(src/HartsyInference.Engine/Recipes/Image/Flux1Recipe*.cs, Recipes/Video/). A spec whose
+``requested`` is ``synthetic:<family>[-tiny]`` builds a random-init model of that architecture
+(benchmarks and tests; there are no real checkpoints on an offline machine)."""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Callable, Optional
+
+import torch
+
+from .. import config, log
+from ..assets.safetensors import ShardedCheckpoint
+from ..exceptions import UnsupportedModelError
+from .requests import EngineOptions, ImageRequest, ImageResult, ModelSpec, StepPreview, VideoGenerationResult, VideoRequest
+
+
+class _PipelineCache:
+    def __init__(self, options: EngineOptions, device: str):
+        self.options, self.device = options, device
+        self._pipes: dict[str, object] = {}
+
+    def key(self, spec: ModelSpec) -> str:
+        return f"{spec.local_path or spec.requested}|{self.options.placement.cache_key}|{self.device}"
+
+    def loaded_keys(self) -> list[str]:
+        return list(self._pipes)
+
+    def release(self, key: Optional[str] = None) -> None:
+        if key is None:
+            self._pipes.clear()
+        else:
+            self._pipes.pop(key, None)
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+
+class ImagesService(_PipelineCache):
+    def _build(self, spec: ModelSpec):
+        from ..models.dit import flux as F
+        from ..models.vae.vae2d import FLUX_VAE, Vae2dDecoder, tiny_vae2d
+        from ..pipelines.flux import FluxComponents, FluxPipeline
+        name = spec.requested
+        fp8 = bool(config.get("fp8_linears")) and self.device.startswith("cuda")
+        if name.startswith("synthetic:"):
+            tiny = name.endswith("-tiny")
+            cfg = F.tiny_flux() if tiny else F.FLUX_DEV
+            tr = F.FluxTransformer(cfg, self.device, fp8=fp8 and not tiny)
+            vae = Vae2dDecoder(tiny_vae2d() if tiny else FLUX_VAE, self.device,
+                               torch.bfloat16 if self.device.startswith("cuda") else torch.float32)
+            if tiny:   # the tiny DiT packs 4 latent channels
+                assert cfg.in_channels == 16
+            return FluxPipeline(FluxComponents(tr, vae))
+        path = Path(spec.local_path or name)
+        if not path.exists():
+            raise UnsupportedModelError(f"{name}: no such checkpoint")
+        ck = ShardedCheckpoint(path / "transformer" if (path / "transformer").exists() else path)
+        tr = F.FluxTransformer(F.FLUX_DEV, self.device, fp8=fp8, get=ck.get)
+        vae = None
+        if "vae" in spec.aux or (path / "vae").exists():
+            vck = ShardedCheckpoint(spec.aux.get("vae", path / "vae"))
+            vae = Vae2dDecoder(FLUX_VAE, self.device, get=vck.get)
+        return FluxPipeline(FluxComponents(tr, vae))
+
+    def pipeline(self, spec: ModelSpec):
+        k = self.key(spec)
+        if k not in self._pipes:
+            log.info(f"[Images] constructing pipeline for {spec.requested}")
+            self._pipes[k] = self._build(spec)
+        return self._pipes[k]
+
+    def generate(self, spec: ModelSpec, req: ImageRequest, progress: Optional[Callable[[StepPreview], None]] = None) -> ImageResult:
+        return self.pipeline(spec).generate(req, progress)
+
+
+class VideoService(_PipelineCache):
+    def _build(self, spec: ModelSpec):
+        from ..models.dit import wan as W
+        from ..models.vae.vae3d import WAN_VAE, Vae3dDecoder, tiny_vae3d
+        from ..pipelines.wan import WanComponents, WanPipeline
+        name = spec.requested
+        fp8 = bool(config.get("fp8_linears")) and self.device.startswith("cuda")
+        dt = torch.bfloat16 if self.device.startswith("cuda") else torch.float32
+        if name.startswith("synthetic:"):
+            tiny = name.endswith("-tiny")
+            cfg = W.tiny_wan() if tiny else (W.WAN_1_3B if "1.3b" in name else W.WAN_14B)
+            tr = W.WanTransformer(cfg, self.device, fp8=fp8 and not tiny)
+            vae = Vae3dDecoder(Vae3dDecoderCfg(tiny, cfg), self.device, dt)
+            return WanPipeline(WanComponents(tr, vae))
+        path = Path(spec.local_path or name)
+        if not path.exists():
+            raise UnsupportedModelError(f"{name}: no such checkpoint")
+        ck = ShardedCheckpoint(path)
+        tr = W.WanTransformer(W.WAN_14B, self.device, fp8=fp8, get=ck.get)
+        vae = None
+        if "vae" in spec.aux:
+            vae = Vae3dDecoder(WAN_VAE, self.device, dt, get=ShardedCheckpoint(spec.aux["vae"]).get)
+        return WanPipeline(WanComponents(tr, vae))
+
+    def pipeline(self, spec: ModelSpec):
+        k = self.key(spec)
+        if k not in self._pipes:
+            log.info(f"[Video] constructing pipeline for {spec.requested}")
+            self._pipes[k] = self._build(spec)
+        return self._pipes[k]
+
+    def generate(self, spec: ModelSpec, req: VideoRequest, progress: Optional[Callable[[StepPreview], None]] = None) -> VideoGenerationResult:
+        return self.pipeline(spec).generate(req, progress)
+
+
+def Vae3dDecoderCfg(tiny: bool, wan_cfg):
+    from ..models.vae.vae3d import WAN_VAE, Vae3dConfig
+    if not tiny:
+        return WAN_VAE
+    return Vae3dConfig(z_dim=wan_cfg.in_channels, dim=8, dim_mult=(1, 2, 2, 2), num_res_blocks=1,
+                       temporal_upsample=(True, True, False))

@@ -1,0 +1,202 @@
+"""Diffusion schedulers.
+
+* ``FlowMatchEulerScheduler``: ``t_i = 1 - i / N``, ``sigma = s t / (1 + (s - 1) t)``, optional
+  Flux dynamic shift ``s = exp(mu)`` with ``mu`` linear in the image sequence length between
+  (256, 0.5) and (4096, 1.15), model timestep ``1000 sigma``, step ``x += v (sigma_next - sigma)``,
+  img2img noise ``(1 - sigma) x0 + sigma eps``
+  (src/HartsyInference.Diffusion/Schedulers/FlowMatchEulerDiscreteScheduler.cs:43-171).
+* ``FlowUniPCScheduler``: UniPC multistep (order 2, ``B(h) = expm1(h)``) in data-prediction form
+  on the flow parameterisation ``alpha = 1 - sigma``: corrector then predictor every step
+  (src/HartsyInference.Diffusion/Schedulers/FlowUniPCMultistepScheduler.cs:17-238). The reference
+  runs it on the host; here every update is a handful of device tensor ops.
+* ``EulerDiscreteScheduler`` / ``DDIMScheduler`` for epsilon-prediction UNet families.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ... import ops
+
+
+def flux_mu(seq_len: int, base_len: int = 256, max_len: int = 4096, base_shift: float = 0.5, max_shift: float = 1.15) -> float:
+    m = (max_shift - base_shift) / (max_len - base_len)
+    return seq_len * m + (base_shift - m * base_len)
+
+
+class FlowMatchEulerScheduler:
+    def __init__(self, num_steps: int, shift: float = 1.0, mu: Optional[float] = None, terminal: Optional[float] = None):
+        t = torch.linspace(1.0, 0.0, num_steps + 1, dtype=torch.float64)[:-1]
+        s = math.exp(mu) if mu is not None else shift
+        sig = s * t / (1 + (s - 1) * t)
+        if terminal is not None:                    # stretch so that the last sigma equals `terminal`
+            one_minus = 1 - sig
+            sig = 1 - one_minus / (one_minus[-1] / (1 - terminal))
+        self.sigmas = torch.cat([sig, torch.zeros(1, dtype=torch.float64)]).float()
+        self.num_steps = num_steps
+
+    def timestep(self, i: int) -> float:
+        return float(self.sigmas[i]) * 1000.0
+
+    def sigma(self, i: int) -> float:
+        return float(self.sigmas[i])
+
+    def dt(self, i: int) -> float:
+        return float(self.sigmas[i + 1] - self.sigmas[i])
+
+    def step(self, latents: torch.Tensor, cond: torch.Tensor, i: int, uncond: Optional[torch.Tensor] = None,
+             guidance: float = 1.0) -> torch.Tensor:
+        """In-place CFG combine + Euler step on fp32 latents (one fused kernel)."""
+        return ops.cfg_euler_step(latents, cond, uncond, guidance, self.dt(i))
+
+    def add_noise(self, x0: torch.Tensor, noise: torch.Tensor, i: int) -> torch.Tensor:
+        s = self.sigma(i)
+        return (1 - s) * x0 + s * noise
+
+
+class FlowUniPCScheduler:
+    def __init__(self, num_steps: int, shift: float = 5.0, order: int = 2, num_train_timesteps: int = 1000):
+        sig = torch.linspace(1.0, 1.0 / num_train_timesteps, num_steps, dtype=torch.float64)
+        sig = shift * sig / (1 + (shift - 1) * sig)
+        self.sigmas = torch.cat([sig, torch.zeros(1, dtype=torch.float64)])
+        self.num_steps = num_steps
+        self.order = order
+        self.model_outputs: list[Optional[torch.Tensor]] = [None] * order
+        self.lower_order_nums = 0
+        self.last_sample: Optional[torch.Tensor] = None
+        self.this_order = 1
+        self.step_index = 0
+
+    def timestep(self, i: int) -> float:
+        return float(self.sigmas[i]) * 1000.0
+
+    @staticmethod
+    def _lambda(sigma: float) -> float:
+        if sigma <= 0:
+            return math.inf
+        return math.log(1 - sigma) - math.log(sigma) if sigma < 1 else -math.inf
+
+    def _coeffs(self, order: int, step_from: int, step_to: int, outputs_back: int):
+        """Shared set-up of the UniP / UniC updates: returns (h_phi_1, B_h, rks, R, b, alpha_t, ratio)."""
+        sigma_t, sigma_s0 = float(self.sigmas[step_to]), float(self.sigmas[step_from])
+        alpha_t = 1 - sigma_t
+        lam_t, lam_s0 = self._lambda(sigma_t), self._lambda(sigma_s0)
+        h = lam_t - lam_s0
+        rks = []
+        for i in range(1, order):
+            si = step_from - i
+            lam_si = self._lambda(float(self.sigmas[si]))
+            rks.append((lam_si - lam_s0) / h)
+        rks.append(1.0)
+        hh = -h
+        h_phi_1 = math.expm1(hh) if hh > -700 else -1.0
+        B_h = h_phi_1
+        h_phi_k = (h_phi_1 / hh - 1) if math.isfinite(hh) else -1.0
+        fact = 1
+        R, b = [], []
+        for i in range(1, order + 1):
+            R.append([rk ** (i - 1) for rk in rks])
+            b.append(h_phi_k * fact / B_h)
+            fact *= i + 1
+            h_phi_k = (h_phi_k / hh - 1 / fact) if math.isfinite(hh) else -1.0 / fact
+        ratio = sigma_t / sigma_s0
+        return h_phi_1, B_h, rks, R, b, alpha_t, ratio
+
+    def _predict(self, sample: torch.Tensor, order: int) -> torch.Tensor:
+        m0 = self.model_outputs[-1]
+        i = self.step_index
+        h_phi_1, B_h, rks, R, b, alpha_t, ratio = self._coeffs(order, i, i + 1, 0)
+        x = ratio * sample - alpha_t * h_phi_1 * m0
+        if order >= 2:
+            d1 = (self.model_outputs[-2] - m0) / rks[0]
+            x = x - alpha_t * B_h * 0.5 * d1
+        return x
+
+    def _correct(self, this_x0: torch.Tensor, last_sample: torch.Tensor, order: int) -> torch.Tensor:
+        m0 = self.model_outputs[-1]
+        i = self.step_index
+        h_phi_1, B_h, rks, R, b, alpha_t, ratio = self._coeffs(order, i - 1, i, 0)
+        x = ratio * last_sample - alpha_t * h_phi_1 * m0
+        d1_t = this_x0 - m0
+        if order == 1:
+            return x - alpha_t * B_h * 0.5 * d1_t
+        rhos = torch.linalg.solve(torch.tensor(R, dtype=torch.float64), torch.tensor(b, dtype=torch.float64)).tolist()
+        d1 = (self.model_outputs[-2] - m0) / rks[0]
+        return x - alpha_t * B_h * (rhos[0] * d1 + rhos[-1] * d1_t)
+
+    def step(self, velocity: torch.Tensor, sample: torch.Tensor) -> torch.Tensor:
+        """velocity: model output at the current step (fp32 or bf16), sample fp32 -> next sample."""
+        i = self.step_index
+        sigma = float(self.sigmas[i])
+        x0 = sample - sigma * velocity.float()
+        if i > 0 and self.last_sample is not None:
+            sample = self._correct(x0, self.last_sample, self.this_order)
+        self.model_outputs = self.model_outputs[1:] + [x0]
+        order = min(self.order, self.num_steps - i)           # lower order for the final steps
+        self.this_order = min(order, self.lower_order_nums + 1)
+        self.last_sample = sample
+        nxt = self._predict(sample, self.this_order)
+        if self.lower_order_nums < self.order:
+            self.lower_order_nums += 1
+        self.step_index += 1
+        return nxt
+
+
+class EulerDiscreteScheduler:
+    """Epsilon-prediction Euler sampler over a scaled-linear beta schedule (SD 1.5 / SDXL)."""
+
+    def __init__(self, num_steps: int, beta_start: float = 0.00085, beta_end: float = 0.012, train_steps: int = 1000):
+        betas = torch.linspace(beta_start ** 0.5, beta_end ** 0.5, train_steps, dtype=torch.float64) ** 2
+        ac = torch.cumprod(1 - betas, 0)
+        sig_all = ((1 - ac) / ac) ** 0.5
+        ts = torch.linspace(train_steps - 1, 0, num_steps, dtype=torch.float64)
+        lo, hi = ts.floor().long(), ts.ceil().long()
+        w = ts - lo
+        self.sigmas = torch.cat([(1 - w) * sig_all[lo] + w * sig_all[hi], torch.zeros(1, dtype=torch.float64)]).float()
+        self.timesteps = ts.float()
+        self.init_noise_sigma = float((self.sigmas.max() ** 2 + 1) ** 0.5)
+
+    def scale_input(self, x: torch.Tensor, i: int) -> torch.Tensor:
+        return x / ((float(self.sigmas[i]) ** 2 + 1) ** 0.5)
+
+    def step(self, eps: torch.Tensor, i: int, x: torch.Tensor) -> torch.Tensor:
+        return x + eps.float() * float(self.sigmas[i + 1] - self.sigmas[i])
+
+
+class DDIMScheduler:
+    def __init__(self, num_steps: int, beta_start: float = 0.00085, beta_end: float = 0.012, train_steps: int = 1000,
+                 v_prediction: bool = False):
+        betas = torch.linspace(beta_start ** 0.5, beta_end ** 0.5, train_steps, dtype=torch.float64) ** 2
+        self.ac = torch.cumprod(1 - betas, 0)
+        step = train_steps // num_steps
+        self.timesteps = (torch.arange(num_steps) * step).flip(0) + 1
+        self.v_prediction = v_prediction
+
+    def step(self, out: torch.Tensor, i: int, x: torch.Tensor) -> torch.Tensor:
+        t = int(self.timesteps[i])
+        prev = int(self.timesteps[i + 1]) if i + 1 < len(self.timesteps) else -1
+        a_t = float(self.ac[min(t, len(self.ac) - 1)])
+        a_p = float(self.ac[prev]) if prev >= 0 else 1.0
+        o = out.float()
+        if self.v_prediction:
+            x0 = a_t ** 0.5 * x - (1 - a_t) ** 0.5 * o
+            eps = a_t ** 0.5 * o + (1 - a_t) ** 0.5 * x
+        else:
+            eps = o
+            x0 = (x - (1 - a_t) ** 0.5 * eps) / a_t ** 0.5
+        return a_p ** 0.5 * x0 + (1 - a_p) ** 0.5 * eps
+
+
+def make_scheduler(name: str, steps: int, **kw):
+    name = name.lower()
+    if name in ("flow_match_euler", "euler_flow", "flowmatch"):
+        return FlowMatchEulerScheduler(steps, **kw)
+    if name in ("unipc", "flow_unipc"):
+        return FlowUniPCScheduler(steps, **kw)
+    if name in ("euler", "euler_discrete"):
+        return EulerDiscreteScheduler(steps, **kw)
+    if name == "ddim":
+        return DDIMScheduler(steps, **kw)
+    raise ValueError(f"unknown scheduler '{name}'")

@@ -1,0 +1,105 @@
+"""T5-v1.1 / umT5 encoder (RMS LayerNorm, relative-position attention bias, gated-GELU FFN).
+T5-XXL (24 layers, d_model 4096, 64 heads x 64, d_ff 10240) conditions Flux; umT5-XXL (per-layer
+position bias) conditions Wan. Reference: src/HartsyInference.Diffusion/Models/TextEncoders/ and
+src/HartsyInference.LLM/Seq2Seq/T5Model.cs. Linears run through the tcgen05 GEMM; attention uses
+PyTorch SDPA because of the additive bias (the encoder runs once per prompt)."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.nn.functional as F
+
+from ... import ops
+from ..dit.common import WeightFactory
+
+
+@dataclass(frozen=True)
+class T5Config:
+    vocab_size: int = 32128
+    d_model: int = 4096
+    num_layers: int = 24
+    num_heads: int = 64
+    d_kv: int = 64
+    d_ff: int = 10240
+    num_buckets: int = 32
+    max_distance: int = 128
+    per_layer_bias: bool = False      # umT5
+    eps: float = 1e-6
+
+
+T5_XXL = T5Config()
+UMT5_XXL = T5Config(vocab_size=256384, per_layer_bias=True)
+
+
+def tiny_t5(**over) -> T5Config:
+    kw = dict(vocab_size=128, d_model=64, num_layers=2, num_heads=4, d_kv=16, d_ff=128)
+    kw.update(over)
+    return T5Config(**kw)
+
+
+def _relative_buckets(n: int, num_buckets: int, max_distance: int, device) -> torch.Tensor:
+    ctx = torch.arange(n, device=device)[:, None]
+    mem = torch.arange(n, device=device)[None, :]
+    rel = mem - ctx
+    nb = num_buckets // 2
+    ret = (rel > 0).long() * nb
+    rel = rel.abs()
+    max_exact = nb // 2
+    large = max_exact + (torch.log(rel.float().clamp_min(1) / max_exact) / math.log(max_distance / max_exact) *
+                         (nb - max_exact)).long()
+    large = large.clamp_max(nb - 1)
+    return ret + torch.where(rel < max_exact, rel, large)
+
+
+class T5Encoder:
+    def __init__(self, cfg: T5Config = T5_XXL, device="cpu", fp8: bool = False,
+                 get: Optional[Callable[[str], Optional[torch.Tensor]]] = None, seed: int = 0):
+        self.cfg, self.device = cfg, torch.device(device)
+        f = WeightFactory(self.device, fp8, get=get, seed=seed)
+        inner = cfg.num_heads * cfg.d_kv
+        self.embed = f.tensor("shared.weight", cfg.vocab_size, cfg.d_model)
+        self.layers = []
+        for i in range(cfg.num_layers):
+            p = f"encoder.block.{i}.layer."
+            lw = dict(
+                ln1=f.tensor(p + "0.layer_norm.weight", cfg.d_model, ones=True),
+                qkv=ops.LinearWeight.from_dense(torch.cat([f.linear(p + f"0.SelfAttention.{n}", inner, cfg.d_model, bias=False, allow_fp8=False).weight
+                                                           for n in ("q", "k", "v")], 0), fp8=f.fp8 and self.device.type == "cuda"),
+                o=f.linear(p + "0.SelfAttention.o", cfg.d_model, inner, bias=False),
+                ln2=f.tensor(p + "1.layer_norm.weight", cfg.d_model, ones=True),
+                wi=ops.LinearWeight.from_dense(torch.cat([f.linear(p + "1.DenseReluDense.wi_0", cfg.d_ff, cfg.d_model, bias=False, allow_fp8=False).weight,
+                                                          f.linear(p + "1.DenseReluDense.wi_1", cfg.d_ff, cfg.d_model, bias=False, allow_fp8=False).weight], 0),
+                                               fp8=f.fp8 and self.device.type == "cuda"),
+                wo=f.linear(p + "1.DenseReluDense.wo", cfg.d_model, cfg.d_ff, bias=False))
+            if i == 0 or cfg.per_layer_bias:
+                lw["rel"] = f.tensor(p + "0.SelfAttention.relative_attention_bias.weight", cfg.num_buckets, cfg.num_heads)
+            self.layers.append(lw)
+        self.final_ln = f.tensor("encoder.final_layer_norm.weight", cfg.d_model, ones=True)
+
+    @torch.no_grad()
+    def encode(self, ids: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """ids [L] int -> [L, d_model] bf16. ``mask`` [L] bool marks real tokens (padding keys are ignored)."""
+        cfg = self.cfg
+        L = ids.shape[0]
+        x = self.embed[ids.long().to(self.device)]
+        buckets = _relative_buckets(L, cfg.num_buckets, cfg.max_distance, self.device)
+        bias = None
+        for lw in self.layers:
+            if "rel" in lw:
+                bias = lw["rel"].float()[buckets].permute(2, 0, 1)            # [heads, L, L]
+                if mask is not None:
+                    bias = bias.masked_fill(~mask.to(self.device)[None, None, :], float("-inf"))
+            h, _, _ = ops.norm(x, lw["ln1"], eps=cfg.eps)
+            qkv = ops.linear(h, lw["qkv"]).float().reshape(L, 3, cfg.num_heads, cfg.d_kv)
+            q, k, v = (qkv[:, i].transpose(0, 1) for i in range(3))           # [heads, L, d]
+            att = F.scaled_dot_product_attention(q[None], k[None], v[None], attn_mask=bias[None], scale=1.0)[0]
+            att = att.transpose(0, 1).reshape(L, -1).to(torch.bfloat16)
+            x = ops.linear(att, lw["o"], residual=x)
+            h, _, _ = ops.norm(x, lw["ln2"], eps=cfg.eps)
+            g, _ = ops.glu(ops.linear(h, lw["wi"]), "gelu_tanh")
+            x = ops.linear(g, lw["wo"], residual=x)
+        out, _, _ = ops.norm(x, self.final_ln, eps=cfg.eps)
+        return out

@@ -1,0 +1,144 @@
+"""2-D VAE decoder (AutoencoderKL layout used by Flux and the SD families): conv_in, mid block
+(ResNet, single-head attention, ResNet), four up blocks of ResNets with nearest-2x upsampling,
+GroupNorm + SiLU, conv_out. Reference: src/HartsyInference.Diffusion/Models/Vae/VaeDecoder.cs (663).
+Convolutions and GroupNorm run through PyTorch (cuDNN); they are off the named hot paths."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.nn.functional as F
+
+
+@dataclass(frozen=True)
+class Vae2dConfig:
+    latent_channels: int = 16
+    block_out_channels: tuple = (128, 256, 512, 512)
+    layers_per_block: int = 2
+    out_channels: int = 3
+    norm_groups: int = 32
+    scaling_factor: float = 0.3611
+    shift_factor: float = 0.1159
+
+
+FLUX_VAE = Vae2dConfig()
+
+
+def tiny_vae2d() -> Vae2dConfig:
+    return Vae2dConfig(latent_channels=4, block_out_channels=(8, 16, 16, 16), layers_per_block=1, norm_groups=4)
+
+
+class Vae2dDecoder:
+    def __init__(self, cfg: Vae2dConfig = FLUX_VAE, device="cpu", dtype=torch.bfloat16,
+                 get: Optional[Callable[[str], Optional[torch.Tensor]]] = None, seed: int = 0):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self._get = get
+        self._g = torch.Generator().manual_seed(seed)
+        self.w: dict[str, torch.Tensor] = {}
+        ch = list(cfg.block_out_channels)
+        top = ch[-1]
+        self._conv("decoder.conv_in", top, cfg.latent_channels, 3)
+        self._resnet("decoder.mid_block.resnets.0", top, top)
+        self._attn("decoder.mid_block.attentions.0", top)
+        self._resnet("decoder.mid_block.resnets.1", top, top)
+        prev = top
+        self.up: list[tuple[list[tuple[str, int, int]], Optional[str]]] = []
+        for i, c in enumerate(reversed(ch)):
+            blocks = []
+            for j in range(cfg.layers_per_block + 1):
+                name = f"decoder.up_blocks.{i}.resnets.{j}"
+                self._resnet(name, prev, c)
+                blocks.append((name, prev, c))
+                prev = c
+            up = None
+            if i < len(ch) - 1:
+                up = f"decoder.up_blocks.{i}.upsamplers.0.conv"
+                self._conv(up, c, c, 3)
+            self.up.append((blocks, up))
+        self._norm("decoder.conv_norm_out", prev)
+        self._conv("decoder.conv_out", cfg.out_channels, prev, 3)
+
+    # -- parameters ---------------------------------------------------------------------
+    def _p(self, name: str, shape, init: str) -> None:
+        t = self._get(name) if self._get is not None else None
+        if t is None:
+            if init == "ones":
+                t = torch.ones(shape)
+            elif init == "zeros":
+                t = torch.zeros(shape)
+            else:
+                fan = 1
+                for s in shape[1:]:
+                    fan *= s
+                t = torch.randn(shape, generator=self._g) * (1.0 / max(fan, 1)) ** 0.5
+        self.w[name] = t.to(self.dtype).to(self.device)
+
+    def _conv(self, name, co, ci, k):
+        self._p(name + ".weight", (co, ci, k, k), "rand")
+        self._p(name + ".bias", (co,), "zeros")
+
+    def _norm(self, name, c):
+        self._p(name + ".weight", (c,), "ones")
+        self._p(name + ".bias", (c,), "zeros")
+
+    def _resnet(self, name, ci, co):
+        self._norm(name + ".norm1", ci)
+        self._conv(name + ".conv1", co, ci, 3)
+        self._norm(name + ".norm2", co)
+        self._conv(name + ".conv2", co, co, 3)
+        if ci != co:
+            self._conv(name + ".conv_shortcut", co, ci, 1)
+
+    def _attn(self, name, c):
+        self._norm(name + ".group_norm", c)
+        for n in ("to_q", "to_k", "to_v", "to_out.0"):
+            self._p(f"{name}.{n}.weight", (c, c), "rand")
+            self._p(f"{name}.{n}.bias", (c,), "zeros")
+
+    # -- forward ------------------------------------------------------------------------
+    def _gn_silu(self, x, name):
+        return F.silu(F.group_norm(x, self.cfg.norm_groups, self.w[name + ".weight"], self.w[name + ".bias"], eps=1e-6))
+
+    def _c(self, x, name, pad=1):
+        return F.conv2d(x, self.w[name + ".weight"], self.w[name + ".bias"], padding=pad)
+
+    def _res(self, x, name, ci, co):
+        h = self._c(self._gn_silu(x, name + ".norm1"), name + ".conv1")
+        h = self._c(self._gn_silu(h, name + ".norm2"), name + ".conv2")
+        if ci != co:
+            x = self._c(x, name + ".conv_shortcut", pad=0)
+        return x + h
+
+    def _attention(self, x, name):
+        b, c, hh, ww = x.shape
+        h = F.group_norm(x, self.cfg.norm_groups, self.w[name + ".group_norm.weight"], self.w[name + ".group_norm.bias"], eps=1e-6)
+        t = h.reshape(b, c, hh * ww).transpose(1, 2)
+        lin = lambda n: F.linear(t, self.w[f"{name}.{n}.weight"].reshape(c, c), self.w[f"{name}.{n}.bias"])
+        q, k, v = lin("to_q"), lin("to_k"), lin("to_v")
+        o = F.scaled_dot_product_attention(q[:, None], k[:, None], v[:, None])[:, 0]
+        o = F.linear(o, self.w[f"{name}.to_out.0.weight"].reshape(c, c), self.w[f"{name}.to_out.0.bias"])
+        return x + o.transpose(1, 2).reshape(b, c, hh, ww)
+
+    @torch.no_grad()
+    def decode(self, latents: torch.Tensor) -> torch.Tensor:
+        """latents [B, C, h, w] (model space) -> images [B, 3, 8h, 8w] in [-1, 1] (float32)."""
+        z = latents.to(self.device).float() / self.cfg.scaling_factor + self.cfg.shift_factor
+        x = self._c(z.to(self.dtype), "decoder.conv_in")
+        top = self.cfg.block_out_channels[-1]
+        x = self._res(x, "decoder.mid_block.resnets.0", top, top)
+        x = self._attention(x, "decoder.mid_block.attentions.0")
+        x = self._res(x, "decoder.mid_block.resnets.1", top, top)
+        for blocks, up in self.up:
+            for name, ci, co in blocks:
+                x = self._res(x, name, ci, co)
+            if up is not None:
+                x = self._c(F.interpolate(x, scale_factor=2.0, mode="nearest"), up)
+        x = self._c(self._gn_silu(x, "decoder.conv_norm_out"), "decoder.conv_out")
+        return x.float().clamp(-1, 1)
+
+
+def to_rgb24(images: torch.Tensor) -> list[bytes]:
+    """[B, 3, H, W] in [-1, 1] -> RGB24 byte strings."""
+    u8 = ((images.float().clamp(-1, 1) + 1) * 127.5).round().to(torch.uint8).permute(0, 2, 3, 1).contiguous().cpu()
+    return [u8[i].numpy().tobytes() for i in range(u8.shape[0])]

@@ -14,6 +14,7 @@ from .core import (  # noqa: F401
     attn_decode,
     attn_prefill_paged,
     cfg_euler_step,
+    dit_qkv,
     embedding,
     fill_random_,
     gated_residual,

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "b200_repetition_penalty": (i32, [vp, vp, vp, i32, i32, i32, vp, vp]),
     "b200_cfg_euler": (i32, [vp, vp, vp, i64, f32, f32, vp]),
     "b200_gated_residual": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "b200_dit_qkv": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, f32, vp]),
     "b200_fill_random": (i32, [vp, i64, u64, f32, i32, vp]),
     "b200_attn_decode": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, f32, f32, i32, vp]),
     "b200_attn_decode_pick_splits": (i32, [i32, i32, i32]),

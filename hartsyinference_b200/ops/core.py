@@ -409,3 +409,35 @@ def fill_random_(t: torch.Tensor, seed: int, std: float = 0.02) -> torch.Tensor:
     N.check(N.lib().b200_fill_random(t.data_ptr(), t.numel(), seed, std, 1 if t.dtype == torch.uint8 else 0,
                                      N.stream()), "b200_fill_random")
     return t
+
+
+def dit_qkv(qkv: torch.Tensor, hq: int, hkv: int, d: int, *, q_norm_w: Optional[torch.Tensor] = None,
+            k_norm_w: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+            sin: Optional[torch.Tensor] = None, eps: float = 1e-6):
+    """Split packed qkv [T, (hq + 2 hkv) d] into q [T, hq, d], k, v [T, hkv, d] with optional per-head
+    RMSNorm on q / k and interleaved-pair rotary embedding from per-token tables cos / sin [T, d/2]."""
+    t = qkv.shape[0]
+    if not qkv.is_cuda:
+        x = qkv.float().reshape(t, hq + 2 * hkv, d)
+        q, k, v = x[:, :hq], x[:, hq:hq + hkv], x[:, hq + hkv:]
+        if q_norm_w is not None:
+            q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm_w.float()
+        if k_norm_w is not None:
+            k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + eps) * k_norm_w.float()
+        if cos is not None:
+            def rot(z):
+                a, b = z[..., 0::2], z[..., 1::2]
+                c, s = cos.float()[:, None, :], sin.float()[:, None, :]
+                return torch.stack([a * c - b * s, b * c + a * s], dim=-1).flatten(-2)
+            q, k = rot(q), rot(k)
+        return q.to(qkv.dtype).contiguous(), k.to(qkv.dtype).contiguous(), v.to(qkv.dtype).contiguous()
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
+    q = torch.empty(t, hq, d, dtype=torch.bfloat16, device=qkv.device)
+    k = torch.empty(t, hkv, d, dtype=torch.bfloat16, device=qkv.device)
+    v = torch.empty(t, hkv, d, dtype=torch.bfloat16, device=qkv.device)
+    if cos is not None:
+        assert cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+    N.check(N.lib().b200_dit_qkv(qkv.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), N.ptr(q_norm_w),
+                                 N.ptr(k_norm_w), N.ptr(cos), N.ptr(sin), t, hq, hkv, d, qkv.stride(0), eps,
+                                 N.stream()), "b200_dit_qkv")
+    return q, k, v

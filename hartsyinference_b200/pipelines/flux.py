@@ -1,0 +1,160 @@
+"""Flux text-to-image pipeline: text encode -> noise -> pack 2x2 -> N denoise steps (DiT forward +
+fused CFG / Euler step on the device) -> unpack -> VAE decode -> RGB24.
+
+Follows ``FluxPipeline`` (src/HartsyInference.Diffusion/Pipelines/FluxPipeline.cs: denoise loop
+:722-1002, CFG-parallel branch :750-807, fused CfgEulerStep :821) with the FlowMatch-Euler schedule
+and Flux's dynamic shift. True CFG (``cfg_scale > 1``) runs a second, unconditional forward, or,
+with ``cfg_comm`` (two ranks / two groups), one branch per group whose outputs are exchanged
+before the combine + step kernel. A first-block cache (relative-L1 on the timestep embedding's
+modulated input, as ``DeviceFeatureCache``: ShouldCompute:82) can skip the transformer on steps
+whose conditioning changed little.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+
+from .. import log
+from ..engine.metrics import REGISTRY
+from ..engine.requests import ImageRequest, ImageResult, StepPreview
+from ..models.diffusion.schedulers import FlowMatchEulerScheduler, flux_mu
+from ..models.dit.flux import FluxTransformer, flux_ids
+from ..models.vae.vae2d import Vae2dDecoder, to_rgb24
+from ..parallel.comm import Comm
+
+
+def pack_latents(z: torch.Tensor) -> torch.Tensor:
+    """[B, C, H, W] -> [B, (H/2)(W/2), 4C] (2x2 patches, channel-major inside a patch)."""
+    b, c, h, w = z.shape
+    return z.reshape(b, c, h // 2, 2, w // 2, 2).permute(0, 2, 4, 1, 3, 5).reshape(b, (h // 2) * (w // 2), c * 4)
+
+
+def unpack_latents(x: torch.Tensor, h: int, w: int) -> torch.Tensor:
+    b, _, c4 = x.shape
+    c = c4 // 4
+    return x.reshape(b, h // 2, w // 2, c, 2, 2).permute(0, 3, 1, 4, 2, 5).reshape(b, c, h, w)
+
+
+@dataclass
+class FluxComponents:
+    transformer: FluxTransformer
+    vae: Optional[Vae2dDecoder] = None
+    t5: Optional[object] = None
+    clip: Optional[object] = None
+    t5_tokenizer: Optional[object] = None
+    clip_tokenizer: Optional[object] = None
+
+
+class FluxPipeline:
+    def __init__(self, comp: FluxComponents, cfg_comm: Optional[Comm] = None):
+        self.c = comp
+        self.device = comp.transformer.device
+        self.cfg_comm = cfg_comm            # 2-rank communicator pairing the cond / uncond branches
+        self.last_step_ms: list[float] = []
+
+    # -- conditioning -------------------------------------------------------------------
+    def encode_prompt(self, prompt: str, max_len: int = 512) -> tuple[torch.Tensor, torch.Tensor]:
+        c = self.c
+        tdim, pdim = c.transformer.cfg.context_dim, c.transformer.cfg.pooled_dim
+        if c.t5 is None or c.t5_tokenizer is None:
+            # synthetic conditioning (no text encoder loaded): deterministic N(0, 1) from the prompt text
+            g = torch.Generator().manual_seed(abs(hash(prompt)) % (2 ** 31))
+            return torch.randn(max_len, tdim, generator=g), torch.randn(pdim, generator=g)
+        ids = torch.tensor(c.t5_tokenizer.encode(prompt)[:max_len], dtype=torch.int64)
+        ctx = c.t5.encode(ids)
+        if ctx.shape[0] < max_len:
+            ctx = torch.cat([ctx, torch.zeros(max_len - ctx.shape[0], ctx.shape[1], dtype=ctx.dtype, device=ctx.device)])
+        pooled = torch.zeros(pdim)
+        if c.clip is not None and c.clip_tokenizer is not None:
+            cid = torch.tensor(c.clip_tokenizer.encode(prompt)[:77], dtype=torch.int64)
+            pooled = c.clip.encode(cid)[1]
+        return ctx, pooled
+
+    # -- denoise ------------------------------------------------------------------------
+    @torch.no_grad()
+    def denoise(self, ctx: torch.Tensor, pooled: torch.Tensor, height: int, width: int, steps: int, guidance: float,
+                seed: int, neg: Optional[tuple[torch.Tensor, torch.Tensor]] = None, cfg_scale: float = 1.0,
+                on_step: Optional[Callable[[StepPreview], None]] = None, step_cache_threshold: float = 0.0,
+                latents: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Returns the final latents [1, C, H/8, W/8] fp32 on the device."""
+        tr = self.c.transformer
+        dev = self.device
+        C = tr.cfg.in_channels // 4
+        lh, lw = height // 8, width // 8
+        g = torch.Generator().manual_seed(seed)
+        z = latents if latents is not None else torch.randn(1, C, lh, lw, generator=g)
+        x = pack_latents(z.float()).to(dev).contiguous()                           # [1, S, 4C] fp32
+        S = x.shape[1]
+        img_ids, txt_ids = flux_ids(lh // 2, lw // 2, ctx.shape[0], dev)
+        sched = FlowMatchEulerScheduler(steps, mu=flux_mu(S))
+        ctx_d, pooled_d = ctx.to(dev)[None], pooled.to(dev)[None]
+        gvec = torch.tensor([guidance], device=dev) if tr.cfg.guidance_embed else None
+        true_cfg = cfg_scale > 1.0 and neg is not None
+        branch = None
+        if true_cfg and self.cfg_comm is not None and self.cfg_comm.world == 2:
+            branch = self.cfg_comm.rank                                           # 0 = cond, 1 = uncond
+        cache_prev_t: Optional[torch.Tensor] = None
+        cache_v: Optional[torch.Tensor] = None
+        self.last_step_ms = []
+        use_cuda = dev.type == "cuda"
+        for i in range(steps):
+            if use_cuda:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            t0 = time.perf_counter()
+            sigma = torch.tensor([sched.sigma(i)], device=dev)
+            skip = False
+            if step_cache_threshold > 0 and cache_v is not None:
+                temb = tr.time_embedding(sigma, gvec, pooled_d).float()
+                rel = ((temb - cache_prev_t).abs().mean() / cache_prev_t.abs().mean().clamp_min(1e-6)).item()
+                skip = rel < step_cache_threshold
+            if skip:
+                v_cond, v_unc = cache_v, None
+            else:
+                xin = x.to(torch.bfloat16)
+                if branch is None:
+                    v_cond = tr.forward(xin, ctx_d, sigma, pooled_d, img_ids, txt_ids, gvec)
+                    v_unc = tr.forward(xin, neg[0].to(dev)[None], sigma, neg[1].to(dev)[None], img_ids, txt_ids, gvec) if true_cfg else None
+                else:
+                    c_in, p_in = (ctx_d, pooled_d) if branch == 0 else (neg[0].to(dev)[None], neg[1].to(dev)[None])
+                    mine = tr.forward(xin, c_in, sigma, p_in, img_ids, txt_ids, gvec).contiguous()
+                    both = self.cfg_comm.all_gather(mine[None], dim=0)             # [2, 1, S, C]
+                    v_cond, v_unc = both[0].contiguous(), both[1].contiguous()
+                if step_cache_threshold > 0:
+                    cache_prev_t = tr.time_embedding(sigma, gvec, pooled_d).float()
+                    cache_v = v_cond if not true_cfg else (cfg_scale * v_cond.float() + (1 - cfg_scale) * v_unc.float()).to(torch.bfloat16)
+                    if true_cfg:
+                        v_cond, v_unc = cache_v, None
+            sched.step(x, v_cond.contiguous(), i, v_unc, cfg_scale)
+            if use_cuda:
+                e1.record()
+                e1.synchronize()
+                ms = e0.elapsed_time(e1)
+            else:
+                ms = (time.perf_counter() - t0) * 1e3
+            self.last_step_ms.append(ms)
+            REGISTRY.set("hartsyinference_step_seconds", ms / 1e3, model="flux")
+            if on_step is not None:
+                on_step(StepPreview(i + 1, steps))
+        return unpack_latents(x, lh, lw)
+
+    def generate(self, req: ImageRequest, on_step: Optional[Callable[[StepPreview], None]] = None) -> ImageResult:
+        seed = req.seed if req.seed is not None else int(time.time() * 1000) % (2 ** 31)
+        ctx, pooled = self.encode_prompt(req.prompt)
+        neg = self.encode_prompt(req.negative_prompt) if req.cfg_scale > 1.0 else None
+        t0 = time.perf_counter()
+        z = self.denoise(ctx, pooled, req.height, req.width, req.steps, req.guidance, seed, neg, req.cfg_scale, on_step,
+                         req.step_cache_threshold)
+        t_denoise = time.perf_counter() - t0
+        if self.c.vae is None:
+            img = torch.zeros(1, 3, req.height, req.width)
+        else:
+            img = self.c.vae.decode(z)
+        rgb = to_rgb24(img)[0]
+        meta = {"steps": req.steps, "denoise_s": t_denoise, "step_ms_median": sorted(self.last_step_ms)[len(self.last_step_ms) // 2] if self.last_step_ms else 0.0,
+                "sampler": "euler", "scheduler": "flow_match_euler", "guidance": req.guidance}
+        log.info(f"[Flux] {req.width}x{req.height} {req.steps} steps in {t_denoise:.2f}s")
+        return ImageResult(rgb=rgb, width=img.shape[-1], height=img.shape[-2], seed=seed, meta=meta)

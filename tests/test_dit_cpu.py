@@ -1,0 +1,93 @@
+"""DiT families on CPU with toy configs: shapes, determinism, parallel-split parity, pipelines."""
+import torch
+
+from hartsyinference_b200.engine.inference_engine import InferenceEngine
+from hartsyinference_b200.engine.requests import ImageRequest, ModelSpec, Modality, VideoRequest
+from hartsyinference_b200.models.dit import flux as F
+from hartsyinference_b200.models.dit import wan as W
+from hartsyinference_b200.models.encoders.clip import ClipTextEncoder, tiny_clip
+from hartsyinference_b200.models.encoders.t5 import T5Encoder, tiny_t5
+from hartsyinference_b200.pipelines.flux import pack_latents, unpack_latents
+
+
+def _flux_inputs(cfg, S_side=4, St=6, B=1):
+    g = torch.Generator().manual_seed(0)
+    img = torch.randn(B, S_side * S_side, cfg.in_channels, generator=g)
+    txt = torch.randn(B, St, cfg.context_dim, generator=g)
+    pooled = torch.randn(B, cfg.pooled_dim, generator=g)
+    ids_i, ids_t = F.flux_ids(S_side, S_side, St)
+    return img, txt, torch.full((B,), 0.7), pooled, ids_i, ids_t, torch.full((B,), 3.5)
+
+
+def test_flux_forward_shapes_and_batch_consistency():
+    cfg = F.tiny_flux()
+    m = F.FluxTransformer(cfg, "cpu", seed=1)
+    img, txt, t, pooled, ii, it, g = _flux_inputs(cfg)
+    out = m.forward(img, txt, t, pooled, ii, it, g)
+    assert out.shape == (1, 16, cfg.in_channels) and torch.isfinite(out.float()).all()
+    # a batch of two identical samples gives the single-sample result twice
+    out2 = m.forward(img.repeat(2, 1, 1), txt.repeat(2, 1, 1), t.repeat(2), pooled.repeat(2, 1), ii, it, g.repeat(2))
+    assert torch.allclose(out2[0].float(), out[0].float(), atol=2e-2) and torch.allclose(out2[1].float(), out[0].float(), atol=2e-2)
+
+
+def test_flux_block_pipeline_split_is_bit_identical():
+    """Running blocks [0, k) and [k, end) in two instances (the block-sharded layout) must equal
+    the unsplit forward exactly (the reference asserts bit parity of ForwardSharded vs Forward)."""
+    cfg = F.tiny_flux()
+    full = F.FluxTransformer(cfg, "cpu", seed=2)
+    a = F.FluxTransformer(cfg, "cpu", seed=2, block_range=(0, 3))
+    b = F.FluxTransformer(cfg, "cpu", seed=2, block_range=(3, 4))
+    # same seed => same random stream only if the same tensors are drawn; share the weights explicitly
+    a.__dict__.update({k: v for k, v in full.__dict__.items() if k in ("x_embedder", "context_embedder", "t_in", "t_out", "g_in", "g_out", "p_in", "p_out")})
+    b.__dict__.update({k: v for k, v in full.__dict__.items() if k in ("t_in", "t_out", "g_in", "g_out", "p_in", "p_out", "norm_out", "proj_out")})
+    a.double, a.single = full.double, full.single[:1]
+    b.double, b.single = [], full.single[1:]
+    inp = _flux_inputs(cfg)
+    ref = full.forward(*inp)
+    hid = a.forward(*inp)
+    out = b.forward(*inp, hidden_in=hid)
+    assert torch.equal(out, ref)
+
+
+def test_wan_forward_and_patchify_roundtrip():
+    cfg = W.tiny_wan()
+    lat = torch.randn(16, 3, 4, 4)
+    tok, grid = W.patchify(lat, cfg.patch)
+    assert tok.shape == (3 * 2 * 2, 64) and grid == (3, 2, 2)
+    m = W.WanTransformer(cfg, "cpu", seed=3)
+    ctx = m.encode_text(torch.randn(cfg.text_len, cfg.text_dim))
+    out = m.forward(lat, torch.tensor(500.0), ctx)
+    assert out.shape == lat.shape and torch.isfinite(out).all()
+    out2 = m.forward(lat, torch.tensor(500.0), ctx)
+    assert torch.equal(out, out2)
+    assert cfg.axes_dim == (12, 10, 10) and W.WAN_14B.axes_dim == (44, 42, 42)
+
+
+def test_pack_unpack_and_text_encoders():
+    z = torch.randn(1, 4, 6, 8)
+    assert torch.equal(unpack_latents(pack_latents(z), 6, 8), z)
+    t5 = T5Encoder(tiny_t5(), "cpu")
+    h = t5.encode(torch.arange(10))
+    assert h.shape == (10, 64) and torch.isfinite(h.float()).all()
+    um = T5Encoder(tiny_t5(per_layer_bias=True), "cpu")
+    assert all("rel" in l for l in um.layers) and sum("rel" in l for l in t5.layers) == 1
+    clip = ClipTextEncoder(tiny_clip(), "cpu")
+    hid, pooled = clip.encode(torch.tensor([1, 5, 9, 127, 0, 0]))
+    assert hid.shape == (6, 64) and torch.equal(pooled, hid[3])
+
+
+def test_image_and_video_services_end_to_end_tiny():
+    eng = InferenceEngine("cpu")
+    img = eng.images.generate(ModelSpec("synthetic:flux-tiny", Modality.IMAGE),
+                              ImageRequest(prompt="a cat", width=64, height=64, steps=3, seed=1, cfg_scale=2.0, negative_prompt="blurry"))
+    assert img.width == 64 and img.height == 64 and len(img.rgb) == 64 * 64 * 3 and img.seed == 1
+    again = eng.images.generate(ModelSpec("synthetic:flux-tiny", Modality.IMAGE),
+                                ImageRequest(prompt="a cat", width=64, height=64, steps=3, seed=1, cfg_scale=2.0, negative_prompt="blurry"))
+    assert again.rgb == img.rgb
+    steps = []
+    vid = eng.video.generate(ModelSpec("synthetic:wan-tiny", Modality.VIDEO),
+                             VideoRequest(prompt="waves", width=32, height=32, frames=5, steps=3, seed=2, cfg_scale=3.0),
+                             lambda p: steps.append(p.step))
+    assert len(vid.frames) == 5 and vid.width == 32 and len(vid.frames[0]) == 32 * 32 * 3 and steps == [1, 2, 3]
+    assert len(eng.loaded_pipeline_keys) == 2
+    eng.free_memory()
