@@ -1,0 +1,307 @@
+"""FastAPI application with the reference server's routes.
+
+OpenAI-compatible: ``GET /v1/models``, ``POST /v1/chat/completions`` (SSE streaming with
+``data: {json}\\n\\n`` frames and a final ``data: [DONE]``), ``POST /v1/embeddings``,
+``POST /v1/images/generations``. Native: ``POST /v1/native/text``, ``/v1/native/text/stream``,
+``/v1/native/text/count-tokens``, ``/v1/native/image``, ``/v1/native/video``. Operations:
+``/health``, ``/ready`` (reports dead serving loops / unhealthy models), ``/version``, ``/metrics``
+(Prometheus), ``/v1/native/admin/free-memory``, ``/v1/native/settings``.
+API-key auth (``x-api-key`` or ``Authorization: Bearer``), a per-key rate limiter, usage metering and
+a bounded queue that answers 429 when full.
+
+Reference: src/HartsyInference.API/HartsyInferenceServiceExtensions.cs:26-140, Endpoints/
+CompatEndpoints.cs:36-258, TextEndpoints.cs, HealthEndpoints.cs:14-20, Metrics.cs, ApiKeyStore,
+UsageTracker, HartsyInferenceServerOptions (MaxConcurrency 1, MaxQueueDepth 16).
+"""
+from __future__ import annotations
+
+import base64
+import json
+import threading
+import time
+import uuid
+from collections import defaultdict, deque
+from dataclasses import dataclass, field
+from typing import Optional
+
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from .. import __version__
+from ..engine.gates import InferenceQueue
+from ..engine.inference_engine import InferenceEngine
+from ..engine.metrics import REGISTRY
+from ..engine.requests import (ChunkKind, EngineOptions, ImageRequest, Modality, ModelSpec, TextRequest, VideoRequest,
+                               to_jsonable)
+from ..exceptions import HartsyInferenceError, QueueFullError, UnsupportedModelError
+
+
+@dataclass
+class ServerOptions:
+    backend: str = "auto"
+    max_concurrency: int = 1
+    max_queue_depth: int = 16
+    api_keys: list[str] = field(default_factory=list)       # empty = auth off
+    rate_limit_per_minute: int = 0                          # 0 = unlimited
+    models: dict[str, str] = field(default_factory=dict)    # public name -> path / synthetic spec
+    default_text_model: Optional[str] = None
+    default_image_model: Optional[str] = None
+    default_video_model: Optional[str] = None
+    text_max_concurrency: int = 64                          # the text path batches requests itself
+
+
+class _RateLimiter:
+    def __init__(self, per_minute: int):
+        self.per_minute = per_minute
+        self._hits: dict[str, deque] = defaultdict(deque)
+        self._lock = threading.Lock()
+
+    def allow(self, key: str) -> bool:
+        if self.per_minute <= 0:
+            return True
+        now = time.monotonic()
+        with self._lock:
+            q = self._hits[key]
+            while q and now - q[0] > 60.0:
+                q.popleft()
+            if len(q) >= self.per_minute:
+                return False
+            q.append(now)
+            return True
+
+
+class UsageTracker:
+    def __init__(self):
+        self.by_key: dict[str, dict[str, int]] = defaultdict(lambda: defaultdict(int))
+        self._lock = threading.Lock()
+
+    def add(self, key: str, **counts: int) -> None:
+        with self._lock:
+            for k, v in counts.items():
+                self.by_key[key][k] += v
+
+
+def create_app(options: Optional[ServerOptions] = None, engine: Optional[InferenceEngine] = None,
+               engine_options: Optional[EngineOptions] = None) -> FastAPI:
+    opts = options or ServerOptions()
+    eng = engine or InferenceEngine(opts.backend, engine_options)
+    app = FastAPI(title="hartsyinference-b200", version=__version__)
+    heavy_queue = InferenceQueue(opts.max_concurrency, opts.max_queue_depth)          # image / video
+    text_queue = InferenceQueue(opts.text_max_concurrency, opts.max_queue_depth)      # batched by the engine
+    limiter = _RateLimiter(opts.rate_limit_per_minute)
+    usage = UsageTracker()
+    app.state.engine, app.state.usage, app.state.options = eng, usage, opts
+
+    def resolve(name: Optional[str], modality: Modality) -> ModelSpec:
+        default = {Modality.TEXT: opts.default_text_model, Modality.IMAGE: opts.default_image_model,
+                   Modality.VIDEO: opts.default_video_model, Modality.EMBEDDINGS: opts.default_text_model}.get(modality)
+        name = name or default
+        if not name:
+            raise UnsupportedModelError("no model named in the request and no default configured")
+        path = opts.models.get(name, name)
+        return ModelSpec(requested=path, modality=modality, catalog=name if name in opts.models else None, local_path=path)
+
+    @app.middleware("http")
+    async def auth_and_metrics(request: Request, call_next):
+        route = request.url.path
+        key = request.headers.get("x-api-key") or ""
+        auth = request.headers.get("authorization", "")
+        if not key and auth.lower().startswith("bearer "):
+            key = auth[7:].strip()
+        open_routes = ("/health", "/ready", "/version", "/metrics", "/openapi.json", "/docs")
+        if opts.api_keys and route not in open_routes and key not in opts.api_keys:
+            REGISTRY.inc("hartsyinference_requests_total", route=route, outcome="unauthorized")
+            return JSONResponse({"error": {"message": "invalid or missing API key", "type": "unauthorized"}}, status_code=401)
+        if route not in open_routes and not limiter.allow(key or request.client.host if request.client else "anon"):
+            REGISTRY.inc("hartsyinference_requests_total", route=route, outcome="rate_limited")
+            return JSONResponse({"error": {"message": "rate limit exceeded", "type": "rate_limited"}}, status_code=429)
+        request.state.api_key = key or "anonymous"
+        try:
+            resp = await call_next(request)
+            outcome = "ok" if resp.status_code < 400 else f"http_{resp.status_code}"
+        except Exception:
+            outcome = "exception"
+            raise
+        finally:
+            REGISTRY.set("hartsyinference_queue_pending", heavy_queue.pending + text_queue.pending)
+        REGISTRY.inc("hartsyinference_requests_total", route=route, outcome=outcome)
+        return resp
+
+    @app.exception_handler(QueueFullError)
+    async def _queue_full(_, exc):
+        return JSONResponse({"error": {"message": str(exc), "type": "queue_full"}}, status_code=429)
+
+    @app.exception_handler(UnsupportedModelError)
+    async def _unsupported(_, exc):
+        return JSONResponse({"error": {"message": str(exc), "type": "unsupported_model"}}, status_code=400)
+
+    @app.exception_handler(HartsyInferenceError)
+    async def _engine_error(_, exc):
+        return JSONResponse({"error": {"message": str(exc), "type": type(exc).__name__}}, status_code=500)
+
+    # -------------------------------------------------------------------------- ops routes
+    @app.get("/health")
+    def health():
+        return {"status": "ok"}
+
+    @app.get("/ready")
+    def ready():
+        bad = eng.unhealthy()
+        if bad:
+            return JSONResponse({"status": "unhealthy", "models": bad}, status_code=503)
+        return {"status": "ready", "backend": eng.backend_description, "loaded": eng.loaded_pipeline_keys}
+
+    @app.get("/version")
+    def version():
+        return {"version": __version__, "backend": eng.backend_description}
+
+    @app.get("/metrics")
+    def metrics():
+        return PlainTextResponse(REGISTRY.render(), media_type="text/plain; version=0.0.4")
+
+    @app.post("/v1/native/admin/free-memory")
+    def free_memory():
+        eng.free_memory()
+        return {"status": "freed"}
+
+    @app.get("/v1/native/settings")
+    def settings():
+        from .. import config
+        return {"flags": {f.env: config.get(f.name) for f in config.all_flags()},
+                "server": {"max_concurrency": opts.max_concurrency, "max_queue_depth": opts.max_queue_depth}}
+
+    @app.get("/v1/models")
+    def models():
+        return {"object": "list", "data": [{"id": k, "object": "model", "owned_by": "local"} for k in opts.models]}
+
+    # -------------------------------------------------------------------------- text
+    def _text_request(body: dict) -> TextRequest:
+        stop = body.get("stop") or []
+        if isinstance(stop, str):
+            stop = [stop]
+        rf = body.get("response_format") or {}
+        return TextRequest(messages=body.get("messages") or [], prompt=body.get("prompt"),
+                           temperature=float(body.get("temperature", 0.7)), top_p=float(body.get("top_p", 0.95)),
+                           top_k=int(body.get("top_k", 0)), min_p=float(body.get("min_p", 0.0)),
+                           repetition_penalty=float(body.get("repetition_penalty", 1.0)),
+                           max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 4096),
+                           seed=body.get("seed"), greedy=bool(body.get("greedy", False)) or float(body.get("temperature", 0.7)) == 0.0,
+                           enable_thinking=body.get("enable_thinking"), tools=body.get("tools"), stop=list(stop),
+                           json_mode=rf.get("type") == "json_object")
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(request: Request):
+        body = await request.json()
+        spec = resolve(body.get("model"), Modality.TEXT)
+        treq = _text_request(body)
+        rid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        created = int(time.time())
+        key = request.state.api_key
+        if body.get("stream"):
+            def gen():
+                with text_queue.slot():
+                    first = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": body.get("model"),
+                             "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}
+                    yield f"data: {json.dumps(first)}\n\n"
+                    for ch in eng.text.stream(spec, treq):
+                        if ch.kind == ChunkKind.CHUNK:
+                            d = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": body.get("model"),
+                                 "choices": [{"index": 0, "delta": {"content": ch.text}, "finish_reason": None}]}
+                            yield f"data: {json.dumps(d)}\n\n"
+                        elif ch.kind == ChunkKind.RESULT:
+                            r = ch.result
+                            usage.add(key, prompt_tokens=r.prompt_tokens, completion_tokens=r.completion_tokens)
+                            d = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": body.get("model"),
+                                 "choices": [{"index": 0, "delta": {}, "finish_reason": "length" if r.stop_reason.value == "length" else "stop"}],
+                                 "usage": {"prompt_tokens": r.prompt_tokens, "completion_tokens": r.completion_tokens,
+                                           "total_tokens": r.prompt_tokens + r.completion_tokens}}
+                            yield f"data: {json.dumps(d)}\n\n"
+                    yield "data: [DONE]\n\n"
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        with text_queue.slot():
+            r = eng.text.generate(spec, treq)
+        usage.add(key, prompt_tokens=r.prompt_tokens, completion_tokens=r.completion_tokens)
+        return {"id": rid, "object": "chat.completion", "created": created, "model": body.get("model"),
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": r.text},
+                             "finish_reason": "length" if r.stop_reason.value == "length" else "stop"}],
+                "usage": {"prompt_tokens": r.prompt_tokens, "completion_tokens": r.completion_tokens,
+                          "total_tokens": r.prompt_tokens + r.completion_tokens}}
+
+    @app.post("/v1/native/text")
+    async def native_text(request: Request):
+        body = await request.json()
+        with text_queue.slot():
+            r = eng.text.generate(resolve(body.get("model"), Modality.TEXT), _text_request(body))
+        return to_jsonable(r)
+
+    @app.post("/v1/native/text/stream")
+    async def native_text_stream(request: Request):
+        body = await request.json()
+        spec, treq = resolve(body.get("model"), Modality.TEXT), _text_request(body)
+
+        def gen():
+            with text_queue.slot():
+                for ch in eng.text.stream(spec, treq):
+                    yield f"data: {json.dumps(to_jsonable(ch))}\n\n"
+                yield "data: [DONE]\n\n"
+        return StreamingResponse(gen(), media_type="text/event-stream")
+
+    @app.post("/v1/native/text/count-tokens")
+    async def count_tokens(request: Request):
+        body = await request.json()
+        return {"tokens": eng.text.count_tokens(resolve(body.get("model"), Modality.TEXT), _text_request(body))}
+
+    @app.post("/v1/embeddings")
+    async def embeddings(request: Request):
+        body = await request.json()
+        inp = body.get("input")
+        texts = [inp] if isinstance(inp, str) else list(inp or [])
+        with text_queue.slot():
+            emb = eng.embeddings.embed(resolve(body.get("model"), Modality.EMBEDDINGS), texts)
+        return {"object": "list", "model": body.get("model"),
+                "data": [{"object": "embedding", "index": i, "embedding": e.tolist()} for i, e in enumerate(emb)]}
+
+    # -------------------------------------------------------------------------- image / video
+    def _png(rgb: bytes, w: int, h: int) -> bytes:
+        from ..utils.png import encode_png
+        return encode_png(rgb, w, h)
+
+    @app.post("/v1/images/generations")
+    async def images_generations(request: Request):
+        body = await request.json()
+        size = body.get("size", "1024x1024")
+        w, h = (int(v) for v in size.lower().split("x"))
+        req = ImageRequest(prompt=body.get("prompt", ""), width=w, height=h, steps=int(body.get("steps", 20)),
+                           guidance=float(body.get("guidance", 3.5)), seed=body.get("seed"))
+        with heavy_queue.slot():
+            res = eng.with_vram_cleanup(lambda: eng.images.generate(resolve(body.get("model"), Modality.IMAGE), req))
+        return {"created": int(time.time()), "data": [{"b64_json": base64.b64encode(_png(res.rgb, res.width, res.height)).decode(),
+                                                       "seed": res.seed}]}
+
+    @app.post("/v1/native/image")
+    async def native_image(request: Request):
+        body = await request.json()
+        fields = {k: v for k, v in body.items() if k in ImageRequest.__dataclass_fields__}
+        with heavy_queue.slot():
+            res = eng.with_vram_cleanup(lambda: eng.images.generate(resolve(body.get("model"), Modality.IMAGE), ImageRequest(**fields)))
+        return {"width": res.width, "height": res.height, "seed": res.seed, "meta": res.meta,
+                "png_base64": base64.b64encode(_png(res.rgb, res.width, res.height)).decode()}
+
+    @app.post("/v1/native/video")
+    async def native_video(request: Request):
+        body = await request.json()
+        fields = {k: v for k, v in body.items() if k in VideoRequest.__dataclass_fields__}
+        with heavy_queue.slot():
+            res = eng.with_vram_cleanup(lambda: eng.video.generate(resolve(body.get("model"), Modality.VIDEO), VideoRequest(**fields)))
+        return {"width": res.width, "height": res.height, "fps": res.fps, "seed": res.seed, "meta": res.meta,
+                "frames": len(res.frames),
+                "first_frame_png_base64": base64.b64encode(_png(res.frames[0], res.width, res.height)).decode() if res.frames else None}
+
+    for route in ("/v1/audio/speech", "/v1/audio/transcriptions", "/v1/native/mesh", "/v1/native/vision",
+                  "/v1/native/restore", "/v1/native/world", "/v1/native/music"):
+        def _make(r):
+            async def _nyi():
+                raise UnsupportedModelError(f"{r}: this modality is not built in this engine yet")
+            return _nyi
+        app.post(route)(_make(route))
+    return app
