@@ -148,9 +148,11 @@ def build_cabi(force: bool = False, verbose: bool = False) -> Path:
     d = _digest(srcs + hdrs, "cabi")
     if force or not out.exists() or stamp.get("cabi") != d:
         inc = sysconfig.get_paths()["include"]
-        cxx = os.environ.get("CXX", "g++")
-        _run([cxx, "-O2", "-fPIC", "-shared", "-o", str(out), *[str(s) for s in srcs], "-I", inc,
-              "-I", str(CSRC / "cabi"), "-ldl", "-pthread"], verbose)
+        libdir = sysconfig.get_config_var("LIBDIR") or "/usr/lib"
+        ver = sysconfig.get_config_var("LDVERSION") or "3"
+        cc = os.environ.get("CC", "gcc")
+        _run([cc, "-O2", "-fPIC", "-shared", "-o", str(out), *[str(s) for s in srcs], "-I", inc,
+              "-I", str(CSRC / "cabi"), f"-L{libdir}", f"-lpython{ver}", "-ldl", "-pthread"], verbose)
         stamp["cabi"] = d
         _save_stamp(stamp)
     return out

@@ -1,0 +1,236 @@
+"""CLI with the reference's verbs for the built modalities: ``text``, ``image``, ``video``,
+``embed``, ``serve``, ``convert``, ``models`` / ``list``, ``flags``, ``plan`` (plus an interactive
+``chat`` REPL). Placement flags follow src/HartsyInference.Cli/Infra/PlacementCli.cs
+(``--gpu``, ``--device "cuda:0+cuda:1"``, ``--parallel auto``) and add the NVSwitch degrees
+``--tp / --sp / --ep / --cfg-parallel / --pp``. Multi-GPU runs are SPMD: launch the same command
+under ``torchrun --nproc-per-node N``.
+"""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import click
+
+from .. import config
+from ..engine.requests import EngineOptions, ImageRequest, Modality, ModelSpec, TextRequest, VideoRequest
+from ..parallel.config import ParallelConfig
+
+
+def _engine(device: str, tp: int, sp: int, ep: int, cfg_parallel: bool, pp: int, max_len: int = 8192):
+    from ..engine.inference_engine import InferenceEngine
+    placement = ParallelConfig(tp=tp, sp=sp, ep=ep, cfg=2 if cfg_parallel else 1, pp=pp)
+    return InferenceEngine(device, EngineOptions(placement=placement, max_model_len=max_len))
+
+
+def placement_options(f):
+    for opt in (click.option("--device", "--gpu", default="auto", help="auto | cpu | cuda | cuda:N | cuda:0+cuda:1"),
+                click.option("--tp", default=1, help="tensor-parallel degree"),
+                click.option("--sp", default=1, help="Ulysses sequence-parallel degree (DiT)"),
+                click.option("--ep", default=1, help="expert-parallel degree (MoE)"),
+                click.option("--cfg-parallel", is_flag=True, help="run the two guidance branches on two device groups"),
+                click.option("--pp", default=1, help="pipeline stages (layer / block split)")):
+        f = opt(f)
+    return f
+
+
+@click.group()
+def cli():
+    """hartsyinference-b200: Blackwell-native multimodal inference."""
+
+
+@cli.command()
+@click.argument("model")
+@click.argument("prompt")
+@click.option("--max-tokens", default=256)
+@click.option("--temperature", default=0.7)
+@click.option("--top-p", default=0.95)
+@click.option("--top-k", default=0)
+@click.option("--seed", default=None, type=int)
+@click.option("--greedy", is_flag=True)
+@click.option("--raw", is_flag=True, help="do not apply the chat template")
+@click.option("--json-mode", is_flag=True)
+@placement_options
+def text(model, prompt, max_tokens, temperature, top_p, top_k, seed, greedy, raw, json_mode, device, tp, sp, ep, cfg_parallel, pp):
+    """Generate text (streams to stdout)."""
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    req = TextRequest(messages=[] if raw else [{"role": "user", "content": prompt}], prompt=prompt if raw else None,
+                      max_tokens=max_tokens, temperature=temperature, top_p=top_p, top_k=top_k, seed=seed, greedy=greedy,
+                      json_mode=json_mode)
+    res = None
+    for ch in eng.text.stream(ModelSpec(model, Modality.TEXT, local_path=model), req):
+        if ch.text:
+            click.echo(ch.text, nl=False)
+        if ch.result is not None:
+            res = ch.result
+    click.echo()
+    if res is not None:
+        click.echo(f"[{res.completion_tokens} tokens, ttft {res.ttft_s * 1e3:.0f} ms, {res.tokens_per_second:.1f} tok/s, {res.stop_reason.value}]", err=True)
+
+
+@cli.command()
+@click.argument("model")
+@placement_options
+def chat(model, device, tp, sp, ep, cfg_parallel, pp):
+    """Interactive chat REPL (empty line or Ctrl-D quits)."""
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    spec = ModelSpec(model, Modality.TEXT, local_path=model)
+    history: list[dict] = []
+    while True:
+        try:
+            line = input("> ")
+        except EOFError:
+            break
+        if not line.strip():
+            break
+        history.append({"role": "user", "content": line})
+        out = ""
+        for ch in eng.text.stream(spec, TextRequest(messages=history, max_tokens=1024)):
+            if ch.text:
+                out += ch.text
+                click.echo(ch.text, nl=False)
+        click.echo()
+        history.append({"role": "assistant", "content": out})
+
+
+@cli.command()
+@click.argument("model")
+@click.argument("prompt")
+@click.option("--out", "-o", default="out.png")
+@click.option("--width", default=1024)
+@click.option("--height", default=1024)
+@click.option("--steps", default=20)
+@click.option("--guidance", default=3.5)
+@click.option("--cfg-scale", default=1.0)
+@click.option("--negative", default="")
+@click.option("--seed", default=None, type=int)
+@placement_options
+def image(model, prompt, out, width, height, steps, guidance, cfg_scale, negative, seed, device, tp, sp, ep, cfg_parallel, pp):
+    """Generate an image (PNG)."""
+    from ..utils.png import encode_png
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    res = eng.images.generate(ModelSpec(model, Modality.IMAGE, local_path=model if Path(model).exists() else None),
+                              ImageRequest(prompt=prompt, negative_prompt=negative, width=width, height=height, steps=steps,
+                                           guidance=guidance, cfg_scale=cfg_scale, seed=seed),
+                              lambda p: click.echo(f"step {p.step}/{p.total_steps}", err=True))
+    Path(out).write_bytes(encode_png(res.rgb, res.width, res.height))
+    click.echo(f"{out}: {res.width}x{res.height}, seed {res.seed}, {res.meta.get('step_ms_median', 0):.1f} ms/step")
+
+
+@cli.command()
+@click.argument("model")
+@click.argument("prompt")
+@click.option("--out-dir", "-o", default="frames")
+@click.option("--width", default=832)
+@click.option("--height", default=480)
+@click.option("--frames", default=81)
+@click.option("--steps", default=50)
+@click.option("--cfg-scale", default=5.0)
+@click.option("--seed", default=None, type=int)
+@placement_options
+def video(model, prompt, out_dir, width, height, frames, steps, cfg_scale, seed, device, tp, sp, ep, cfg_parallel, pp):
+    """Generate a video (PNG frame sequence; pipe to ffmpeg to mux)."""
+    from ..utils.png import encode_png
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    res = eng.video.generate(ModelSpec(model, Modality.VIDEO, local_path=model if Path(model).exists() else None),
+                             VideoRequest(prompt=prompt, width=width, height=height, frames=frames, steps=steps,
+                                          cfg_scale=cfg_scale, seed=seed),
+                             lambda p: click.echo(f"step {p.step}/{p.total_steps}", err=True))
+    d = Path(out_dir)
+    d.mkdir(parents=True, exist_ok=True)
+    for i, f in enumerate(res.frames):
+        (d / f"frame_{i:05d}.png").write_bytes(encode_png(f, res.width, res.height))
+    click.echo(f"{len(res.frames)} frames in {d} ({res.width}x{res.height} @ {res.fps} fps)")
+
+
+@cli.command()
+@click.argument("model")
+@click.argument("texts", nargs=-1)
+@placement_options
+def embed(model, texts, device, tp, sp, ep, cfg_parallel, pp):
+    """Embed texts; prints one JSON array per line."""
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    for e in eng.embeddings.embed(ModelSpec(model, Modality.EMBEDDINGS, local_path=model), list(texts)):
+        click.echo(json.dumps([round(float(x), 6) for x in e]))
+
+
+@cli.command()
+@click.option("--host", default="127.0.0.1")
+@click.option("--port", default=8080)
+@click.option("--model", "models", multiple=True, help="name=path (repeatable)")
+@click.option("--api-key", "api_keys", multiple=True)
+@click.option("--max-concurrency", default=1)
+@click.option("--max-queue-depth", default=16)
+@click.option("--device", default="auto")
+def serve(host, port, models, api_keys, max_concurrency, max_queue_depth, device):
+    """Run the HTTP server."""
+    import uvicorn
+    from ..server import ServerOptions, create_app
+    table = dict(m.split("=", 1) for m in models)
+    first = next(iter(table), None)
+    app = create_app(ServerOptions(backend=device, models=table, api_keys=list(api_keys), max_concurrency=max_concurrency,
+                                   max_queue_depth=max_queue_depth, default_text_model=first))
+    uvicorn.run(app, host=host, port=port)
+
+
+@cli.command()
+@click.argument("src")
+@click.argument("dst")
+@click.option("--quant", default=None, help="GGUF target type for 2-D tensors: Q8_0 | Q4_0 | Q4_K")
+def convert(src, dst, quant):
+    """Convert between checkpoint containers: .safetensors <-> .gguf (optionally quantising), or .pth -> .safetensors."""
+    import torch
+    from ..assets import gguf as G
+    from ..assets.safetensors import SafeTensorsFile, save_file
+    if src.endswith(".gguf") and dst.endswith(".safetensors"):
+        f = G.GgufFile(src)
+        save_file({k: f.get(k) for k in f.keys()}, dst, {"format": "pt", "source": Path(src).name})
+    elif dst.endswith(".gguf"):
+        f = SafeTensorsFile(src)
+        G.write_gguf(dst, {"general.name": Path(src).stem}, {k: f.get(k).float() for k in f.keys()},
+                     quant=G.GGML_TYPES[quant] if quant else None)
+    elif src.endswith((".pth", ".pt", ".bin")):
+        sd = torch.load(src, map_location="cpu", weights_only=True)
+        sd = sd.get("state_dict", sd) if isinstance(sd, dict) else sd
+        save_file({k: v for k, v in sd.items() if isinstance(v, torch.Tensor)}, dst, {"format": "pt"})
+    else:
+        raise click.UsageError("unsupported conversion")
+    click.echo(f"wrote {dst}")
+
+
+@cli.command("models")
+@click.option("--dir", "cache_dir", default=None)
+def list_models(cache_dir):
+    """List checkpoints in the model cache directory."""
+    d = Path(cache_dir or config.get("model_cache_dir")).expanduser()
+    if not d.exists():
+        click.echo(f"(no cache directory at {d})")
+        return
+    for p in sorted(d.iterdir()):
+        click.echo(p.name)
+
+
+cli.add_command(list_models, "list")
+
+
+@cli.command()
+def flags():
+    """Print every runtime flag (environment variable, type, default, description)."""
+    click.echo(config.describe())
+
+
+@cli.command()
+@click.option("--kind", default="llm", type=click.Choice(["llm", "moe_llm", "image_dit", "video_dit"]))
+@click.option("--weight-gb", default=70.0)
+@click.option("--heads", default=64)
+@click.option("--ffn", default=28672)
+@click.option("--experts", default=0)
+@click.option("--tokens", default=0)
+@click.option("--true-cfg", is_flag=True)
+@click.option("--gpus", default=8)
+def plan(kind, weight_gb, heads, ffn, experts, tokens, true_cfg, gpus):
+    """Suggest a parallel layout for a model shape on N GPUs."""
+    from ..engine import planner as P
+    p = P.suggest(P.ModelShape(kind, int(weight_gb * 1e9), heads, heads, ffn, 0, experts, tokens, true_cfg), gpus)
+    click.echo(p.describe())
