@@ -61,6 +61,18 @@ struct GemmParams {
   int k;               // reduction length in elements
   int stages;
   int swap_out;        // 0: C[a_row][b_row]; 1: C[b_row][a_row]
+  // Grouped mode (MoE experts): A stacks `rows_a / group_n` weight matrices of group_n rows, B
+  // stacks one BN-row token block per group; A tile t pairs with B block (t * 128) / group_n and
+  // the output column is a_row % group_n. 0 = ordinary GEMM.
+  int group_n;
+  // Grouped mode: number of used slots per group (device memory, may be null). Groups with a zero
+  // count are skipped by every role of every CTA, so idle experts cost no weight traffic.
+  const int* group_counts;
+  // Grouped "column-batched" variant (per-head projections): every group reads the SAME token rows
+  // of B at column offset g * group_b_koff (elements) and writes output columns starting at
+  // g * group_out_stride. 0 = stacked token blocks as described above.
+  int group_b_koff;
+  int group_out_stride;
   // K-split of the trailing tiles: tiles [0, first_split_tile) are whole, every later tile is
   // cut into `splits` ranges of `kblocks_per_split` k-blocks
   int first_split_tile;
@@ -106,6 +118,8 @@ struct WorkItem {
   int kb0, kb1;      // k-block range
   int slot;          // index among the split tiles, -1 for a whole tile
   int split;         // which range of the split tile
+  bool skip;         // grouped mode: the group has no tokens
+  int bk;            // element offset of the group's columns in B (column-batched mode)
 };
 
 __device__ __forceinline__ long long num_work_items(const GemmParams& p) {
@@ -131,8 +145,24 @@ __device__ __forceinline__ WorkItem decode_item(const GemmParams& p, long long w
     it.kb1 = min(total_kblocks, it.kb0 + p.kblocks_per_split);
   }
   it.ta = static_cast<int>(tile % tiles_a);
-  it.tb = static_cast<int>(tile / tiles_a);
+  it.bk = 0;
+  if (p.group_n > 0) {
+    const int g = (it.ta * kTileA) / p.group_n;
+    if (p.group_b_koff > 0) { it.tb = 0; it.bk = g * p.group_b_koff; }
+    else it.tb = g;
+    it.skip = p.group_counts != nullptr && p.group_counts[g] == 0;
+  } else {
+    it.tb = static_cast<int>(tile / tiles_a);
+    it.skip = false;
+  }
   return it;
+}
+
+// Output column of weight row `a_row` in the small-token orientation.
+__device__ __forceinline__ long long swap_col(const GemmParams& p, int a_row) {
+  if (p.group_n <= 0) return a_row;
+  const int g = a_row / p.group_n, c = a_row - g * p.group_n;
+  return p.group_b_koff > 0 ? static_cast<long long>(g) * p.group_out_stride + c : c;
 }
 
 __device__ __forceinline__ float apply_epilogue(const GemmParams& p, float v, long long row,
@@ -205,11 +235,12 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
           dst[j] = __float2bfloat16(apply_epilogue(p, v[j], a_row, b0 + j));
     }
   } else {
+    const long long col = swap_col(p, a_row);
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (b0 + j < p.rows_b)
-        p.out[static_cast<long long>(b0 + j) * p.ldc + a_row] =
-            __float2bfloat16(apply_epilogue(p, v[j], b0 + j, a_row));
+        p.out[static_cast<long long>(b0 + j) * p.ldc + col] =
+            __float2bfloat16(apply_epilogue(p, v[j], b0 + j, col));
   }
 }
 
@@ -293,9 +324,10 @@ __device__ __forceinline__ void finish_item(const GemmParams& p, const WorkItem&
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       if (a_row + u >= p.rows_a) break;
-      if (p.swap_out)
-        p.out[static_cast<long long>(b_row) * p.ldc + a_row + u] =
-            __float2bfloat16(apply_epilogue(p, v[u], b_row, a_row + u));
+      if (p.swap_out) {
+        const long long col = swap_col(p, a_row + u);
+        p.out[static_cast<long long>(b_row) * p.ldc + col] = __float2bfloat16(apply_epilogue(p, v[u], b_row, col));
+      }
       else
         p.out[static_cast<long long>(a_row + u) * p.ldc + b_row] =
             __float2bfloat16(apply_epilogue(p, v[u], a_row + u, b_row));
@@ -429,6 +461,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       bool ok = true;
       for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
         const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
+        if (it.skip) continue;
         for (int kb = it.kb0; kb < it.kb1; kb += kAtoms) {
           const int na = min(kAtoms, it.kb1 - kb);
           if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag)) {
@@ -442,7 +475,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           for (int a = 0; a < na; ++a) {
             tma_load_2d(sa + a * kStageBytesA, &tm_a, &bars->full[s], (kb + a) * kElemsPerAtom,
                         it.ta * kTileA);
-            tma_load_2d(sb + a * kAtomBytesB, &tm_b, &bars->full[s], (kb + a) * kElemsPerAtom,
+            tma_load_2d(sb + a * kAtomBytesB, &tm_b, &bars->full[s], (kb + a) * kElemsPerAtom + it.bk,
                         it.tb * BN);
           }
           ++issued;
@@ -471,6 +504,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       bool issued_any = false;
       for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
         const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
+        if (it.skip) continue;
         if (!kFp8) {
           if (!mbar_wait(&bars->tmem_empty[abuf], aph ^ 1, abort_flag)) {
             report_status(p.status, kWaitTimeout, kKernelGemm, 2, blockIdx.x);
@@ -544,6 +578,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
     bool ok = true;
     for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
       const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
+      if (it.skip) continue;
       if (ok) {
         if constexpr (!kFp8) {
           if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[abuf], aph, abort_flag))) {
@@ -751,18 +786,36 @@ int num_sms() {
 
 constexpr long long kSplitCounterBytes = 16384;   // head of the scratch buffer: 4096 tile counters
 
+// Host description of a grouped launch (see GemmParams::group_n and ::group_b_koff).
+struct GroupSpec {
+  int groups;
+  const int* counts;     // device, optional
+  int b_koff;            // > 0: column-batched variant
+  int out_stride;
+};
+
 int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
                      long long ldw, long long ldc, int dtype, const float* x_scale,
                      const float* w_scale, const void* bias, const void* gate, const void* residual,
                      int act, int splits, void* workspace, long long workspace_bytes, void* status,
-                     cudaStream_t stream, const AllReduceParams* ar) {
+                     cudaStream_t stream, const AllReduceParams* ar, const GroupSpec* gs = nullptr) {
+  const int groups = gs ? gs->groups : 0;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
+  // grouped: x is [groups * m][k], w is [groups * n][k], out is [groups * m][n]; m = tokens per group
   const bool fp8 = dtype == 1;
   const int esz = fp8 ? 1 : 2;
   const int kelems = fp8 ? 128 : 64;
   if ((ldx * esz) % 16 != 0 || (ldw * esz) % 16 != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -3;
   if (fp8 && (k % 128 != 0 || !x_scale || !w_scale)) return -4;
+  if (groups > 0) {
+    if (m < 1 || m > 128 || n % 128 != 0) return -9;
+    if (gs->b_koff > 0) {
+      if (fp8 || k % kelems != 0 || (gs->b_koff * esz) % 16 != 0) return -9;
+    } else if (m != 16 && m != 32 && m != 64 && m != 128) {
+      return -9;
+    }
+  }
 
   // Small token counts: weights take the 128-row MMA dimension, tokens the N dimension.
   const bool swap = m <= 128;
@@ -786,7 +839,18 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   int bn;
   const void *a_ptr, *b_ptr;
   long long lda, ldb;
-  if (swap) {
+  if (groups > 0) {
+    p.group_n = n;
+    p.group_counts = gs->counts;
+    p.group_b_koff = gs->b_koff;
+    p.group_out_stride = gs->out_stride;
+    p.rows_a = groups * n;
+    p.rows_b = gs->b_koff > 0 ? m : groups * m;
+    a_ptr = w; lda = ldw; b_ptr = x; ldb = ldx;
+    bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
+    p.scale_a = w_scale; p.sa_gran = 128; p.sa_ld = k / 128;
+    p.scale_b = x_scale; p.sb_gran = 1;   p.sb_ld = k / 128;
+  } else if (swap) {
     p.rows_a = n; p.rows_b = m;
     a_ptr = w; lda = ldw; b_ptr = x; ldb = ldx;
     bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
@@ -801,7 +865,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     p.scale_b = w_scale; p.sb_gran = 128; p.sb_ld = k / 128;
   }
   const int total_kblocks = (k + kelems - 1) / kelems;
-  const int tiles = ((p.rows_a + 127) / 128) * ((p.rows_b + bn - 1) / bn);
+  const int tiles = groups > 0 ? (p.rows_a + 127) / 128 : ((p.rows_a + 127) / 128) * ((p.rows_b + bn - 1) / bn);
   const int sms = num_sms();
   p.num_tiles = tiles;
 
@@ -852,7 +916,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   CUtensorMap ta, tb;
   int rc = make_kmajor_map(&ta, a_ptr, esz, p.rows_a, k, lda, kTileA);
   if (rc) return rc;
-  rc = make_kmajor_map(&tb, b_ptr, esz, p.rows_b, k, ldb, bn);
+  rc = make_kmajor_map(&tb, b_ptr, esz, p.rows_b, p.group_b_koff > 0 ? ldb : k, ldb, bn);
   if (rc) return rc;
 
   const long long items = first_split + static_cast<long long>(tiles - first_split) * s_eff;
@@ -977,4 +1041,34 @@ B200_API int b200_gemm_noalloc(const void* x, const void* w, void* out, int m, i
     return B200_NOALLOC_ERR_SETUP;
   return b200::gemm_impl(x, w, out, m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, nullptr,
                          residual, 0, 0, scratch, B200_NOALLOC_SCRATCH_BYTES, nullptr, stream, nullptr);
+}
+
+// Grouped GEMM for expert layers: for every group g, out[g][m][n] = x[g][m][k] * w[g][n][k]^T with
+// all groups in ONE launch (weights stacked as [groups * n][k], token blocks as [groups * m][k],
+// m in {16, 32, 64, 128} slots per group, unused slots zero; groups whose entry of the optional
+// device array group_counts is zero are skipped and their output rows left untouched). Same kernel as b200_gemm: expert
+// weights fill the 128-row MMA dimension, each expert's token block is the N operand.
+B200_API int b200_gemm_grouped(const void* x, const void* w, void* out, int groups, int m, int n, int k,
+                               int dtype, const float* x_scale, const float* w_scale, int act,
+                               const int* group_counts, void* workspace, long long workspace_bytes,
+                               void* status, cudaStream_t stream) {
+  if (groups <= 0) return 0;
+  const GroupSpec gs{groups, group_counts, 0, 0};
+  return gemm_impl(x, w, out, m, n, k, k, k, n, dtype, x_scale, w_scale, nullptr, nullptr, nullptr, act, 0,
+                   workspace, workspace_bytes, status, stream, nullptr, &gs);
+}
+
+// Column-batched grouped GEMM (bf16): out[t][g * out_stride + j] = sum_i x[t][g * x_koff + i] *
+// w[g * n + j][i] for t < m <= 128 tokens, j < n, i < k. Per-head projections of one token block
+// (multi-head latent attention: absorbing W_uk into the query and applying W_uv to the output)
+// without transposing activations to head-major order. x_koff * 2 bytes must be a multiple of 16
+// and k a multiple of 64.
+B200_API int b200_gemm_colbatched(const void* x, const void* w, void* out, int groups, int m, int n, int k,
+                                  long long ldx, int x_koff, long long ldc, int out_stride, void* workspace,
+                                  long long workspace_bytes, void* status, cudaStream_t stream) {
+  if (groups <= 0 || m <= 0) return 0;
+  if (x_koff <= 0) return -9;
+  const GroupSpec gs{groups, nullptr, x_koff, out_stride};
+  return gemm_impl(x, w, out, m, n, k, ldx, k, ldc, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0,
+                   workspace, workspace_bytes, status, stream, nullptr, &gs);
 }

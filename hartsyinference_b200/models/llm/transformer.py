@@ -110,8 +110,8 @@ class DecoderModel:
         self.lm_head: Optional[LinearWeight] = None
         self.final_norm: Optional[torch.Tensor] = None
         self.layers: list[LayerWeights] = []
-        self.inv_freq, self.rope_attn_factor = build_inv_freq(cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling,
-                                                              self.device)
+        rot = cfg.mla.qk_rope_head_dim if cfg.mla is not None else cfg.rotary_dim
+        self.inv_freq, self.rope_attn_factor = build_inv_freq(rot, cfg.rope_theta, cfg.rope_scaling, self.device)
         self.kv_cache: Optional[torch.Tensor] = None
         self.all_reduce: Callable[[torch.Tensor], torch.Tensor] = self.comm.all_reduce
         # hook for the fused GEMM + all-reduce path: (x, weight, residual) -> reduced output
@@ -160,25 +160,33 @@ class DecoderModel:
         self.layers = []
         for i in range(cfg.num_layers):
             p = f"model.layers.{i}."
-            q = need(p + "self_attn.q_proj.weight")[r * self.hq * d:(r + 1) * self.hq * d]
-            k = need(p + "self_attn.k_proj.weight")[kvs.start * d:kvs.stop * d]
-            v = need(p + "self_attn.v_proj.weight")[kvs.start * d:kvs.stop * d]
-            qkv_b = None
-            if cfg.qkv_bias and get(p + "self_attn.q_proj.bias") is not None:
-                qkv_b = torch.cat([need(p + "self_attn.q_proj.bias")[r * self.hq * d:(r + 1) * self.hq * d],
-                                   need(p + "self_attn.k_proj.bias")[kvs.start * d:kvs.stop * d],
-                                   need(p + "self_attn.v_proj.bias")[kvs.start * d:kvs.stop * d]])
-            o = need(p + "self_attn.o_proj.weight")[:, r * self.hq * d:(r + 1) * self.hq * d]
-            gate = need(p + "mlp.gate_proj.weight")[r * self.ffn:(r + 1) * self.ffn]
-            up = need(p + "mlp.up_proj.weight")[r * self.ffn:(r + 1) * self.ffn]
-            down = need(p + "mlp.down_proj.weight")[:, r * self.ffn:(r + 1) * self.ffn]
+            is_moe = cfg.moe is not None and cfg.moe.num_experts > 0 and i >= cfg.moe.first_dense_layers
             lw = LayerWeights(
                 in_norm=need(p + "input_layernorm.weight").to(dt).to(self.device),
-                qkv=self._lw(torch.cat([q, k, v]).to(dt), None if qkv_b is None else qkv_b.to(dt)),
-                o=self._lw(o.contiguous().to(dt)),
-                post_norm=need(p + "post_attention_layernorm.weight").to(dt).to(self.device),
-                gate_up=self._lw(torch.cat([gate, up]).to(dt)),
-                down=self._lw(down.contiguous().to(dt)))
+                qkv=None, o=None,
+                post_norm=need(p + "post_attention_layernorm.weight").to(dt).to(self.device))
+            if cfg.mla is not None:
+                lw.attn_module = self._load_mla(need, get, p + "self_attn.")
+            else:
+                q = need(p + "self_attn.q_proj.weight")[r * self.hq * d:(r + 1) * self.hq * d]
+                k = need(p + "self_attn.k_proj.weight")[kvs.start * d:kvs.stop * d]
+                v = need(p + "self_attn.v_proj.weight")[kvs.start * d:kvs.stop * d]
+                qkv_b = None
+                if cfg.qkv_bias and get(p + "self_attn.q_proj.bias") is not None:
+                    qkv_b = torch.cat([need(p + "self_attn.q_proj.bias")[r * self.hq * d:(r + 1) * self.hq * d],
+                                       need(p + "self_attn.k_proj.bias")[kvs.start * d:kvs.stop * d],
+                                       need(p + "self_attn.v_proj.bias")[kvs.start * d:kvs.stop * d]])
+                o = need(p + "self_attn.o_proj.weight")[:, r * self.hq * d:(r + 1) * self.hq * d]
+                lw.qkv = self._lw(torch.cat([q, k, v]).to(dt), None if qkv_b is None else qkv_b.to(dt))
+                lw.o = self._lw(o.contiguous().to(dt))
+            if is_moe:
+                lw.ffn_module = self._load_moe(need, get, p)
+            else:
+                gate = need(p + "mlp.gate_proj.weight")[r * self.ffn:(r + 1) * self.ffn]
+                up = need(p + "mlp.up_proj.weight")[r * self.ffn:(r + 1) * self.ffn]
+                down = need(p + "mlp.down_proj.weight")[:, r * self.ffn:(r + 1) * self.ffn]
+                lw.gate_up = self._lw(torch.cat([gate, up]).to(dt))
+                lw.down = self._lw(down.contiguous().to(dt))
             if cfg.qk_norm:
                 lw.q_norm = need(p + "self_attn.q_norm.weight").to(dt).to(self.device)
                 lw.k_norm = need(p + "self_attn.k_norm.weight").to(dt).to(self.device)
@@ -187,6 +195,66 @@ class DecoderModel:
                 lw.post_norm = need(p + "pre_feedforward_layernorm.weight").to(dt).to(self.device)
                 lw.post_ffn_norm = need(p + "post_feedforward_layernorm.weight").to(dt).to(self.device)
             self.layers.append(lw)
+
+    def _load_mla(self, need, get, p: str):
+        """Hugging Face DeepSeek attention tensors -> absorbed, head-sharded MLA weights."""
+        from .mla import MlaAttention, MlaWeights, split_kv_b
+        cfg, m, dt = self.cfg, self.cfg.mla, torch.bfloat16
+        r, hl = self.tp_rank, self.hq
+        dq = m.qk_nope_head_dim + m.qk_rope_head_dim
+        dev = lambda t_: t_.to(dt).to(self.device)
+        if m.q_lora_rank:
+            q_a = self._lw(need(p + "q_a_proj.weight").to(dt))
+            q_a_norm = dev(need(p + "q_a_layernorm.weight"))
+            q_b = self._lw(need(p + "q_b_proj.weight")[r * hl * dq:(r + 1) * hl * dq].to(dt))
+        else:
+            q_a, q_a_norm = None, None
+            q_b = self._lw(need(p + "q_proj.weight")[r * hl * dq:(r + 1) * hl * dq].to(dt))
+        per = m.qk_nope_head_dim + m.v_head_dim
+        kv_b = need(p + "kv_b_proj.weight")[r * hl * per:(r + 1) * hl * per].to(dt)
+        w_uk, w_uv = split_kv_b(kv_b, hl, m.qk_nope_head_dim, m.v_head_dim)
+        w = MlaWeights(
+            q_a=q_a, q_a_norm=q_a_norm, q_b=q_b,
+            kv_a=self._lw(need(p + "kv_a_proj_with_mqa.weight").to(dt), allow_fp8=False),
+            kv_a_norm=dev(need(p + "kv_a_layernorm.weight")),
+            w_uk=self._lw(w_uk, allow_fp8=False), w_uv=self._lw(w_uv, allow_fp8=False),
+            o=self._lw(need(p + "o_proj.weight")[:, r * hl * m.v_head_dim:(r + 1) * hl * m.v_head_dim]
+                       .contiguous().to(dt)))
+        return MlaAttention(cfg, w, hl)
+
+    def _load_moe(self, need, get, p: str):
+        """Expert tensors of one layer (DeepSeek / Qwen-MoE / OLMoE ``mlp.*`` names or Mixtral
+        ``block_sparse_moe.*`` names) -> this rank's stacked expert weights."""
+        from .moe import MoeFeedForward, MoeWeights
+        cfg, moe, dt = self.cfg, self.cfg.moe, torch.bfloat16
+        r, tp = self.tp_rank, self.tp
+        e_local = moe.num_experts // tp
+        mixtral = get(p + "block_sparse_moe.gate.weight") is not None
+        base = p + ("block_sparse_moe." if mixtral else "mlp.")
+        names = ("w1", "w3", "w2") if mixtral else ("gate_proj", "up_proj", "down_proj")
+        router = LinearWeight(need(base + "gate.weight").to(dt).to(self.device))
+        bias = get(base + "gate.e_score_correction_bias")
+        gus, dns = [], []
+        for e in range(r * e_local, (r + 1) * e_local):
+            ep = f"{base}experts.{e}."
+            gus.append(torch.cat([need(ep + names[0] + ".weight"), need(ep + names[1] + ".weight")]).to(dt))
+            dns.append(need(ep + names[2] + ".weight").to(dt))
+        w = MoeWeights(router=router,
+                       router_bias=None if bias is None else bias.float().contiguous().to(self.device),
+                       gate_up=self._lw(torch.cat(gus)), down=self._lw(torch.cat(dns)))
+        for sp in ("shared_experts.", "shared_expert."):
+            sg = get(base + sp + "gate_proj.weight")
+            if sg is None:
+                continue
+            fs = sg.shape[0] // tp
+            su = need(base + sp + "up_proj.weight")
+            sd = need(base + sp + "down_proj.weight")
+            w.shared_gate_up = self._lw(torch.cat([sg[r * fs:(r + 1) * fs], su[r * fs:(r + 1) * fs]]).to(dt))
+            w.shared_down = self._lw(sd[:, r * fs:(r + 1) * fs].contiguous().to(dt))
+            gate = get(base + "shared_expert_gate.weight")
+            if gate is not None:
+                w.shared_gate = LinearWeight(gate.to(dt).to(self.device))
+        return MoeFeedForward(cfg, w, r, tp, all_reduce=lambda y: self.all_reduce(y))
 
     def random_init(self, seed: int = 0, std: float = 0.02) -> None:
         """Synthetic weights generated on the device (no host copy): bf16 N(0, std), or e4m3 bytes
@@ -226,19 +294,62 @@ class DecoderModel:
             self.lm_head = lin(self.vocab_local, cfg.hidden_size, allow_fp8=False)
         self.final_norm = ones(cfg.hidden_size)
         self.layers = []
-        for _ in range(cfg.num_layers):
+        for li in range(cfg.num_layers):
+            is_moe = cfg.moe is not None and cfg.moe.num_experts > 0 and li >= cfg.moe.first_dense_layers
             lw = LayerWeights(
                 in_norm=ones(cfg.hidden_size),
-                qkv=lin((self.hq + 2 * self.hkv) * d, cfg.hidden_size, bias=cfg.qkv_bias),
-                o=lin(cfg.hidden_size, self.hq * d),
+                qkv=None if cfg.mla is not None else lin((self.hq + 2 * self.hkv) * d, cfg.hidden_size, bias=cfg.qkv_bias),
+                o=None if cfg.mla is not None else lin(cfg.hidden_size, self.hq * d),
                 post_norm=ones(cfg.hidden_size),
-                gate_up=lin(2 * self.ffn, cfg.hidden_size),
-                down=lin(cfg.hidden_size, self.ffn))
+                gate_up=None if is_moe else lin(2 * self.ffn, cfg.hidden_size),
+                down=None if is_moe else lin(cfg.hidden_size, self.ffn))
+            if is_moe:
+                lw.ffn_module = self._random_moe(lin, dense)
+            if cfg.mla is not None:
+                lw.attn_module = self._random_mla(lin, ones)
             if cfg.qk_norm:
                 lw.q_norm, lw.k_norm = ones(d), ones(d)
             if cfg.post_norms:
                 lw.post_attn_norm, lw.post_ffn_norm = ones(cfg.hidden_size), ones(cfg.hidden_size)
             self.layers.append(lw)
+
+    def _random_moe(self, lin, dense):
+        from .moe import MoeFeedForward, MoeWeights
+        cfg, moe, dev = self.cfg, self.cfg.moe, self.device
+        e_local = moe.num_experts // self.tp
+        router = LinearWeight(torch.empty(moe.num_experts, cfg.hidden_size, dtype=torch.bfloat16, device=dev))
+        # the router is replicated: seed it independently of the rank
+        self._shared_seed = getattr(self, "_shared_seed", 7_000_003) + 1
+        ops.fill_random_(router.weight, self._shared_seed, 0.05)
+        bias = None
+        if moe.use_correction_bias:
+            b = torch.empty(1, moe.num_experts, dtype=torch.bfloat16, device=dev)
+            ops.fill_random_(b, self._shared_seed + 500_000, 0.01)
+            bias = b.float().reshape(-1).contiguous()
+        w = MoeWeights(router=router, router_bias=bias,
+                       gate_up=lin(e_local * 2 * moe.expert_ffn, cfg.hidden_size),
+                       down=lin(e_local * cfg.hidden_size, moe.expert_ffn))
+        if moe.num_shared_experts > 0:
+            fs = moe.shared_ffn * moe.num_shared_experts // self.tp
+            w.shared_gate_up = lin(2 * fs, cfg.hidden_size)
+            w.shared_down = lin(cfg.hidden_size, fs)
+        return MoeFeedForward(cfg, w, self.tp_rank, self.tp, all_reduce=lambda y: self.all_reduce(y))
+
+    def _random_mla(self, lin, ones):
+        from .mla import MlaAttention, MlaWeights
+        cfg, m = self.cfg, self.cfg.mla
+        hl = self.hq
+        dq = m.qk_nope_head_dim + m.qk_rope_head_dim
+        w = MlaWeights(
+            q_a=lin(m.q_lora_rank, cfg.hidden_size) if m.q_lora_rank else None,
+            q_a_norm=ones(m.q_lora_rank) if m.q_lora_rank else None,
+            q_b=lin(hl * dq, m.q_lora_rank if m.q_lora_rank else cfg.hidden_size),
+            kv_a=lin(m.kv_lora_rank + m.qk_rope_head_dim, cfg.hidden_size, allow_fp8=False),
+            kv_a_norm=ones(m.kv_lora_rank),
+            w_uk=lin(hl * m.kv_lora_rank, m.qk_nope_head_dim, allow_fp8=False),
+            w_uv=lin(hl * m.v_head_dim, m.kv_lora_rank, allow_fp8=False),
+            o=lin(cfg.hidden_size, hl * m.v_head_dim))
+        return MlaAttention(cfg, w, hl)
 
     def weight_bytes(self) -> int:
         n = self.embed.numel() * 2 + self.final_norm.numel() * 2
@@ -256,10 +367,18 @@ class DecoderModel:
 
     # ------------------------------------------------------------------------------ KV cache
     def kv_bytes_per_page(self, page: int) -> int:
+        if self.cfg.mla is not None:
+            return self.cfg.num_layers * page * (self.cfg.mla.kv_lora_rank + self.cfg.mla.qk_rope_head_dim) * 2
         return self.cfg.num_layers * 2 * self.hkv * page * self.cfg.head_dim * 2
 
     def alloc_kv(self, num_pages: int, page: int = 16) -> torch.Tensor:
-        """[layers, 2, pages, hkv_local, page, head_dim] bf16."""
+        """[layers, 2, pages, hkv_local, page, head_dim] bf16, or with multi-head latent attention
+        [layers, pages, page, 576] (latent + rotated shared key, replicated on every rank)."""
+        if self.cfg.mla is not None:
+            row = self.cfg.mla.kv_lora_rank + self.cfg.mla.qk_rope_head_dim
+            self.kv_cache = torch.zeros(self.cfg.num_layers, num_pages, page, row, dtype=torch.bfloat16,
+                                        device=self.device)
+            return self.kv_cache
         self.kv_cache = torch.zeros(self.cfg.num_layers, 2, num_pages, self.hkv, page, self.cfg.head_dim,
                                     dtype=torch.bfloat16, device=self.device)
         return self.kv_cache

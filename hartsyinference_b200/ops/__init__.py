@@ -14,12 +14,20 @@ from .core import (  # noqa: F401
     attn_decode,
     attn_prefill_paged,
     cfg_euler_step,
+    colbatched_linear,
     dit_qkv,
     embedding,
     fill_random_,
     gated_residual,
     glu,
+    grouped_linear,
+    moe_capacity,
+    moe_combine,
+    moe_dispatch,
+    moe_route,
     linear,
+    mla_attn,
+    mla_prep,
     norm,
     quant_fp8_act,
     quant_fp8_weight,

@@ -441,3 +441,206 @@ def dit_qkv(qkv: torch.Tensor, hq: int, hkv: int, d: int, *, q_norm_w: Optional[
                                  N.ptr(k_norm_w), N.ptr(cos), N.ptr(sin), t, hq, hkv, d, qkv.stride(0), eps,
                                  N.stream()), "b200_dit_qkv")
     return q, k, v
+
+
+# ---------------------------------------------------------------------------------------------
+# mixture of experts
+# ---------------------------------------------------------------------------------------------
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, *, n_group: int = 1,
+              topk_group: int = 1, sigmoid: bool = False, norm_topk: bool = False,
+              scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Router: logits [T, E] (fp32 or bf16) -> (expert ids int32 [T, k], weights fp32 [T, k]),
+    entirely on the device (see :func:`reference.moe_route` for the exact rule)."""
+    if not logits.is_cuda:
+        return R.moe_route(logits, bias, top_k, n_group, topk_group, sigmoid, norm_topk, scale)
+    t, e = logits.shape
+    assert logits.is_contiguous() and logits.dtype in (torch.float32, torch.bfloat16)
+    ids = torch.empty(t, top_k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(t, top_k, dtype=torch.float32, device=logits.device)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.is_contiguous()
+    rc = N.lib().b200_moe_route(logits.data_ptr(), 1 if logits.dtype == torch.bfloat16 else 0, N.ptr(bias),
+                                ids.data_ptr(), w.data_ptr(), t, e, top_k, n_group, topk_group,
+                                1 if sigmoid else 0, 1 if norm_topk else 0, float(scale), N.stream())
+    N.check(rc, "b200_moe_route")
+    return ids, w
+
+
+def moe_capacity(tokens: int) -> int:
+    """Slots per expert for a chunk of ``tokens`` (a token picks an expert at most once)."""
+    for c in (16, 32, 64, 128):
+        if tokens <= c:
+            return c
+    raise ValueError("MoE chunks hold at most 128 tokens")
+
+
+def moe_dispatch(x: torch.Tensor, topk_ids: torch.Tensor, e0: int, e_local: int, capacity: int,
+                 xs: torch.Tensor, slot_of: Optional[torch.Tensor] = None,
+                 counts: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Copy each token row into a slot of every local expert that it selected.
+
+    ``xs`` [e_local * capacity, dim] is a caller-owned buffer (slots without a token keep stale,
+    finite values). Returns (slot_of int32 [T, k] with -1 for remote experts, counts int32 [e_local])."""
+    t, k = topk_ids.shape
+    dim = x.shape[1]
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and xs.shape == (e_local * capacity, dim)
+    if slot_of is None:
+        slot_of = torch.empty(t, k, dtype=torch.int32, device=x.device)
+    if counts is None:
+        counts = torch.empty(e_local, dtype=torch.int32, device=x.device)
+    rc = N.lib().b200_moe_dispatch(x.data_ptr(), xs.data_ptr(), topk_ids.data_ptr(), slot_of.data_ptr(),
+                                   counts.data_ptr(), t, k, dim, e0, e_local, capacity, N.stream())
+    N.check(rc, "b200_moe_dispatch")
+    return slot_of, counts
+
+
+def grouped_linear(x, w: LinearWeight, groups: int, act: Optional[str] = None,
+                   counts: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-group y[g] = x[g] @ w[g]^T in one launch. ``x`` [groups * m, K] (bf16 or Fp8Act, m in
+    {16, 32, 64, 128}), ``w`` stacked [groups * N, K]; groups with ``counts[g] == 0`` are skipped."""
+    xd = x.data if isinstance(x, Fp8Act) else x
+    m = xd.shape[0] // groups
+    k = xd.shape[1]
+    n = w.weight.shape[0] // groups
+    if not xd.is_cuda:
+        ys = []
+        for g in range(groups):
+            wg = w.weight[g * n:(g + 1) * n]
+            if w.is_fp8:
+                sg = w.scale[g * (n // 128):(g + 1) * (n // 128)]
+                if isinstance(x, Fp8Act):
+                    q, s = x.data[g * m:(g + 1) * m], x.scale[g * m:(g + 1) * m]
+                else:
+                    q, s = R.quant_fp8_act(xd[g * m:(g + 1) * m])
+                ys.append(R.linear(q, wg, sg, s, None, act, None, None))
+            else:
+                ys.append(R.linear(xd[g * m:(g + 1) * m], wg, None, None, None, act, None, None))
+        return torch.cat(ys)
+    if w.is_fp8 and not isinstance(x, Fp8Act):
+        x = quant_fp8_act(x)
+        xd = x.data
+    assert xd.is_contiguous() and w.weight.is_contiguous() and w.weight.shape[1] == k
+    if out is None:
+        out = torch.empty(groups * m, n, dtype=torch.bfloat16, device=xd.device)
+    fp8 = w.is_fp8
+    st = N.state(xd.device)
+    ws = st.gemm_workspace()
+    rc = N.lib().b200_gemm_grouped(xd.data_ptr(), w.weight.data_ptr(), out.data_ptr(), groups, m, n, k,
+                                   1 if fp8 else 0, x.scale.data_ptr() if fp8 else None,
+                                   w.scale.data_ptr() if fp8 else None, _ACT[act], N.ptr(counts),
+                                   ws.data_ptr(), ws.numel(), st.status.data_ptr(), N.stream())
+    N.check(rc, "b200_gemm_grouped")
+    return out
+
+
+def moe_combine(y: torch.Tensor, slot_of: torch.Tensor, topk_w: torch.Tensor, out: torch.Tensor,
+                accumulate: bool = False) -> torch.Tensor:
+    """out[t] (+)= sum_k topk_w[t, k] * y[slot_of[t, k]] over the locally computed slots."""
+    t, k = slot_of.shape
+    dim = y.shape[1]
+    assert y.is_cuda and y.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.is_contiguous()
+    rc = N.lib().b200_moe_combine(y.data_ptr(), slot_of.data_ptr(), topk_w.data_ptr(), out.data_ptr(), t, k, dim,
+                                  1 if accumulate else 0, N.stream())
+    N.check(rc, "b200_moe_combine")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# multi-head latent attention
+# ---------------------------------------------------------------------------------------------
+MLA_LATENT = 512
+MLA_ROPE = 64
+MLA_ROW = MLA_LATENT + MLA_ROPE
+
+
+def colbatched_linear(x: torch.Tensor, w: torch.Tensor, groups: int, x_koff: int, out: torch.Tensor,
+                      out_stride: int) -> torch.Tensor:
+    """Per-group projection of one token block without a head-major transpose:
+    ``out[t, g * out_stride + j] = sum_i x[t, g * x_koff + i] * w[g * n + j, i]`` with ``w`` stacked
+    [groups * n, k] bf16, at most 128 tokens per call (longer inputs are processed in blocks)."""
+    t = x.shape[0]
+    n, k = w.shape[0] // groups, w.shape[1]
+    if not x.is_cuda:
+        xf, wf = x.float(), w.float()
+        for g in range(groups):
+            out[:, g * out_stride:g * out_stride + n] = (xf[:, g * x_koff:g * x_koff + k] @ wf[g * n:(g + 1) * n].t()).to(out.dtype)
+        return out
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and out.stride(1) == 1
+    st = N.state(x.device)
+    ws = st.gemm_workspace()
+    for t0 in range(0, t, 128):
+        m = min(128, t - t0)
+        xb, ob = x[t0:t0 + m], out[t0:t0 + m]
+        rc = N.lib().b200_gemm_colbatched(xb.data_ptr(), w.data_ptr(), ob.data_ptr(), groups, m, n, k, x.stride(0),
+                                          x_koff, out.stride(0), out_stride, ws.data_ptr(), ws.numel(),
+                                          st.status.data_ptr(), N.stream())
+        N.check(rc, "b200_gemm_colbatched")
+    return out
+
+
+def mla_prep(kv: torch.Tensor, kv_norm_w: torch.Tensor, q: torch.Tensor, q_abs: torch.Tensor,
+             cache: Optional[torch.Tensor], positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+             inv_freq: torch.Tensor, heads: int, q_stride: int, q_rope_off: int, eps: float = 1e-6,
+             rope_mscale: float = 1.0) -> None:
+    """Latent RMSNorm + RoPE of the shared key part + cache write ([pages, page, 576] flattened to
+    slots), and RoPE of each head's q_pe into ``q_abs[:, :, 512:]``. Interleaved-pair rotation."""
+    t = kv.shape[0]
+    if not kv.is_cuda:
+        c = kv[:, :MLA_LATENT].float()
+        c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * kv_norm_w.float()
+        kpe = R.apply_rope(kv[:, MLA_LATENT:].float().unsqueeze(1), positions, inv_freq, 1)[:, 0] * 1.0
+        qpe = q.reshape(t, heads, q_stride)[:, :, q_rope_off:q_rope_off + MLA_ROPE].float()
+        qpe = R.apply_rope(qpe, positions, inv_freq, 1)
+        if rope_mscale != 1.0:
+            kpe, qpe = kpe * rope_mscale, qpe * rope_mscale
+        q_abs[:, :, MLA_LATENT:] = qpe.to(q_abs.dtype)
+        if cache is not None and slot_mapping is not None:
+            ok = slot_mapping >= 0
+            flat = cache.view(-1, MLA_ROW)
+            flat[slot_mapping[ok].long()] = torch.cat([c, kpe], dim=-1).to(cache.dtype)[ok]
+        return
+    assert kv.is_contiguous() and q.is_contiguous() and q_abs.is_contiguous() and positions.dtype == torch.int32
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == MLA_ROPE // 2
+    if slot_mapping is not None:
+        assert slot_mapping.dtype == torch.int64
+    rc = N.lib().b200_mla_prep(kv.data_ptr(), kv_norm_w.data_ptr(), q.data_ptr(), q_abs.data_ptr(), N.ptr(cache),
+                               positions.data_ptr(), N.ptr(slot_mapping), inv_freq.data_ptr(), t, heads, q_stride,
+                               q_rope_off, eps, rope_mscale, N.stream())
+    N.check(rc, "b200_mla_prep")
+
+
+def mla_attn(q_abs: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, kv_lens: torch.Tensor,
+             scale: float, row_seq: Optional[torch.Tensor] = None, max_kv_len: Optional[int] = None,
+             splits: Optional[int] = None) -> torch.Tensor:
+    """Multi-query attention of absorbed queries [rows, heads, 576] over the latent cache
+    [pages, page, 576]; row r attends to the first ``kv_lens[r]`` tokens of block-table row
+    ``row_seq[r]`` (identity when None). Returns the latent outputs [rows, heads, 512]."""
+    rows, heads, _ = q_abs.shape
+    page = cache.shape[1]
+    if not q_abs.is_cuda:
+        out = torch.zeros(rows, heads, MLA_LATENT, dtype=q_abs.dtype)
+        for r in range(rows):
+            n = int(kv_lens[r])
+            if n == 0:
+                continue
+            sq = int(row_seq[r]) if row_seq is not None else r
+            npg = (n + page - 1) // page
+            lat = cache[block_table[sq, :npg].long()].reshape(-1, MLA_ROW)[:n].float()
+            sc = (q_abs[r].float() @ lat.t()) * scale
+            out[r] = (torch.softmax(sc, dim=-1) @ lat[:, :MLA_LATENT]).to(out.dtype)
+        return out
+    assert q_abs.is_contiguous() and cache.is_contiguous() and block_table.dtype == torch.int32
+    assert kv_lens.dtype == torch.int32 and (row_seq is None or row_seq.dtype == torch.int32)
+    L = N.lib()
+    if splits is None:
+        mk = max_kv_len if max_kv_len else block_table.shape[1] * page
+        splits = L.b200_mla_pick_splits(rows, heads, int(mk))
+    out = torch.empty(rows, heads, MLA_LATENT, dtype=torch.bfloat16, device=q_abs.device)
+    ws = None
+    if splits > 1:
+        ws = torch.empty(L.b200_mla_workspace_bytes(rows, heads, splits), dtype=torch.uint8, device=q_abs.device)
+    rc = L.b200_mla_attn(q_abs.data_ptr(), cache.data_ptr(), out.data_ptr(), block_table.data_ptr(),
+                         kv_lens.data_ptr(), N.ptr(row_seq), rows, heads, page, block_table.stride(0), splits,
+                         N.ptr(ws), float(scale), N.stream())
+    N.check(rc, "b200_mla_attn")
+    return out

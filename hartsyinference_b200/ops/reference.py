@@ -193,3 +193,41 @@ def gather_paged(cache: torch.Tensor, table: torch.Tensor, length: int) -> torch
 def cfg_euler(z: torch.Tensor, cond: torch.Tensor, uncond: Optional[torch.Tensor], g: float, dt: float) -> torch.Tensor:
     v = cond.float() if uncond is None else g * cond.float() + (1.0 - g) * uncond.float()
     return z + v * dt
+
+
+# --------------------------------------------------------------------------------------------
+# mixture of experts
+# --------------------------------------------------------------------------------------------
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_group: int = 1,
+              topk_group: int = 1, sigmoid: bool = False, norm_topk: bool = False,
+              scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Top-k routing. Returns (expert ids int32 [T, k], mixing weights fp32 [T, k]).
+
+    Softmax or sigmoid scores; optional DeepSeek-V3 group-limited selection (selection score =
+    score + bias, group score = sum of the group's two best, keep ``topk_group`` groups); the
+    weight is the unbiased score, renormalised when ``norm_topk`` and multiplied by ``scale``.
+    Ties go to the lower expert index."""
+    lg = logits.float()
+    t, e = lg.shape
+    score = torch.sigmoid(lg) if sigmoid else torch.softmax(lg, dim=-1)
+    sel = score + bias.float() if bias is not None else score.clone()
+    if n_group > 1 and topk_group < n_group:
+        g = sel.view(t, n_group, e // n_group)
+        gscore = g.topk(min(2, e // n_group), dim=-1).values.sum(-1)
+        keep = torch.zeros(t, n_group, dtype=torch.bool, device=lg.device)
+        work = gscore.clone()
+        for _ in range(topk_group):
+            idx = work.argmax(dim=-1, keepdim=True)     # first maximum = lowest index
+            keep.scatter_(1, idx, True)
+            work.scatter_(1, idx, float("-inf"))
+        sel = sel.masked_fill(~keep.unsqueeze(-1).expand(t, n_group, e // n_group).reshape(t, e), float("-inf"))
+    ids = torch.empty(t, top_k, dtype=torch.int64, device=lg.device)
+    work = sel.clone()
+    for r in range(top_k):
+        idx = work.argmax(dim=-1)
+        ids[:, r] = idx
+        work.scatter_(1, idx.unsqueeze(1), float("-inf"))
+    w = score.gather(1, ids)
+    if norm_topk:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return ids.to(torch.int32), w * scale
