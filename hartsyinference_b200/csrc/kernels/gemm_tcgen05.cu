@@ -73,6 +73,9 @@ struct GemmParams {
   // g * group_out_stride. 0 = stacked token blocks as described above.
   int group_b_koff;
   int group_out_stride;
+  // 1: every tile is split and a second kernel (splitk_reduce_kernel) sums the partials with the
+  // whole machine; 0: the last CTA to arrive at a split tile sums them inside this kernel.
+  int external_reduce;
   // K-split of the trailing tiles: tiles [0, first_split_tile) are whole, every later tile is
   // cut into `splits` ranges of `kblocks_per_split` k-blocks
   int first_split_tile;
@@ -100,7 +103,7 @@ constexpr int kTileA = 128;
 constexpr int kStageBytesA = kTileA * 128;
 constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, 8 epilogue warps
 
-struct alignas(8) GemmBarriers {
+struct alignas(16) GemmBarriers {
   uint64_t full[12];
   uint64_t empty[12];
   uint64_t tmem_full[8];
@@ -110,6 +113,9 @@ struct alignas(8) GemmBarriers {
   uint32_t abort_flag;
   uint32_t flag;      // broadcast slot of the epilogue warps
   uint32_t pad;
+  // per epilogue warp: the 32 (x2 chunks) column scales of the current k-block, double-buffered
+  // by k-block parity, so that every lane can read all of them as broadcast vector loads
+  alignas(16) float cs_bcast[8][2][64];
 };
 
 // One unit of work of a CTA: an output tile and a range of k-blocks.
@@ -204,8 +210,10 @@ __device__ __forceinline__ void epilogue_barrier() {   // the 8 epilogue warps o
 
 // Stores 32 consecutive accumulator columns (B rows b0..b0+31) of A row `a_row` of a whole tile
 // to its destination: C, or (fused all-reduce) the staging buffer of the owning rank.
+// `b_end` is the end of the tile's B rows (a 16-row tile fills only half of a 32-column chunk; the
+// rest of the chunk is not this tile's data).
 __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[32], int a_row,
-                                            int b0) {
+                                            int b0, int b_end) {
   if (a_row >= p.rows_a) return;
   if (p.ar.world > 0) {
     const int ta = a_row >> 7;
@@ -214,12 +222,12 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
         (static_cast<long long>(p.ar.rank * p.ar.tiles_per_rank + tl) * 128 + b0) * 128 + (a_row & 127);
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      if (b0 + j < p.rows_b) dst[j * 128] = __float2bfloat16(v[j]);
+      if (b0 + j < b_end) dst[j * 128] = __float2bfloat16(v[j]);
     return;
   }
   if (!p.swap_out) {
     __nv_bfloat16* dst = p.out + static_cast<long long>(a_row) * p.ldc + b0;
-    if (b0 + 32 <= p.rows_b && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+    if (b0 + 32 <= b_end && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
       uint32_t w[16];
 #pragma unroll
       for (int j = 0; j < 32; j += 2)
@@ -231,14 +239,14 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (b0 + j < p.rows_b)
+        if (b0 + j < b_end)
           dst[j] = __float2bfloat16(apply_epilogue(p, v[j], a_row, b0 + j));
     }
   } else {
     const long long col = swap_col(p, a_row);
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      if (b0 + j < p.rows_b)
+      if (b0 + j < b_end)
         p.out[static_cast<long long>(b0 + j) * p.ldc + col] =
             __float2bfloat16(apply_epilogue(p, v[j], b0 + j, col));
   }
@@ -260,7 +268,45 @@ template <int BN>
 __device__ __forceinline__ void emit_chunk(const GemmParams& p, const float (&v)[32], const WorkItem& it,
                                            int row_local, int chunk) {
   if (it.slot >= 0) store_partial<BN>(p, v, row_local, chunk * 32, it);
-  else store_chunk(p, v, it.ta * kTileA + row_local, it.tb * BN + chunk * 32);
+  else store_chunk(p, v, it.ta * kTileA + row_local, it.tb * BN + chunk * 32, min(p.rows_b, (it.tb + 1) * BN));
+}
+
+// Sums the partials of four consecutive weight rows (one 16-byte load per partial) of split tile
+// `it`, applies the epilogue and writes C. kBatch loads are issued together so that their L2
+// latencies overlap.
+template <int kBatch>
+__device__ __forceinline__ void reduce_partials(const GemmParams& p, const WorkItem& it, int bn, int e4) {
+  const float* ws = p.split_ws + static_cast<long long>(it.slot) * p.splits * (bn * 128);
+  const int e = e4 * 4;
+  const int a_local = e & 127, b_local = e >> 7;
+  const int a_row = it.ta * kTileA + a_local, b_row = it.tb * bn + b_local;
+  if (a_row >= p.rows_a || b_row >= p.rows_b) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  int sp = 0;
+  for (; sp + kBatch <= p.splits; sp += kBatch) {
+    float4 t[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u)
+      t[u] = __ldcg(reinterpret_cast<const float4*>(ws + static_cast<long long>(sp + u) * (bn * 128) + e));
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) { acc.x += t[u].x; acc.y += t[u].y; acc.z += t[u].z; acc.w += t[u].w; }
+  }
+  for (; sp < p.splits; ++sp) {
+    const float4 t = __ldcg(reinterpret_cast<const float4*>(ws + static_cast<long long>(sp) * (bn * 128) + e));
+    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+  }
+  const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    if (a_row + u >= p.rows_a) break;
+    if (p.swap_out) {
+      const long long col = swap_col(p, a_row + u);
+      p.out[static_cast<long long>(b_row) * p.ldc + col] = __float2bfloat16(apply_epilogue(p, v[u], b_row, col));
+    } else {
+      p.out[static_cast<long long>(a_row + u) * p.ldc + b_row] =
+          __float2bfloat16(apply_epilogue(p, v[u], a_row + u, b_row));
+    }
+  }
 }
 
 // Called by all 256 epilogue threads once the item's values are stored. Whole tile: nothing to do
@@ -281,7 +327,7 @@ __device__ __forceinline__ void finish_item(const GemmParams& p, const WorkItem&
     }
     return;
   }
-  if (it.slot < 0) return;
+  if (it.slot < 0 || p.external_reduce) return;
   __threadfence();
   epilogue_barrier();
   if (et == 0) {
@@ -298,41 +344,7 @@ __device__ __forceinline__ void finish_item(const GemmParams& p, const WorkItem&
   epilogue_barrier();
   if (!last) return;
   __threadfence();
-  const float* ws = p.split_ws + static_cast<long long>(it.slot) * p.splits * (BN * 128);
-  // four consecutive rows per thread (one 16-byte load per partial); the loads of four partials
-  // are issued together so that their L2 latencies overlap
-  for (int e4 = et; e4 < BN * 32; e4 += 256) {
-    const int e = e4 * 4;
-    const int a_local = e & 127, b_local = e >> 7;
-    const int a_row = it.ta * kTileA + a_local, b_row = it.tb * BN + b_local;
-    if (a_row >= p.rows_a || b_row >= p.rows_b) continue;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    int sp = 0;
-    for (; sp + 4 <= p.splits; sp += 4) {
-      float4 t[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        t[u] = __ldcg(reinterpret_cast<const float4*>(ws + static_cast<long long>(sp + u) * (BN * 128) + e));
-#pragma unroll
-      for (int u = 0; u < 4; ++u) { acc.x += t[u].x; acc.y += t[u].y; acc.z += t[u].z; acc.w += t[u].w; }
-    }
-    for (; sp < p.splits; ++sp) {
-      const float4 t = __ldcg(reinterpret_cast<const float4*>(ws + static_cast<long long>(sp) * (BN * 128) + e));
-      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
-    }
-    const float v[4] = {acc.x, acc.y, acc.z, acc.w};
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      if (a_row + u >= p.rows_a) break;
-      if (p.swap_out) {
-        const long long col = swap_col(p, a_row + u);
-        p.out[static_cast<long long>(b_row) * p.ldc + col] = __float2bfloat16(apply_epilogue(p, v[u], b_row, col));
-      }
-      else
-        p.out[static_cast<long long>(a_row + u) * p.ldc + b_row] =
-            __float2bfloat16(apply_epilogue(p, v[u], a_row + u, b_row));
-    }
-  }
+  for (int e4 = et; e4 < BN * 32; e4 += 256) reduce_partials<4>(p, it, BN, e4);
 }
 
 // Owner side of the fused all-reduce: sum the `world` partials of tile `ta`, apply the epilogue,
@@ -390,6 +402,19 @@ __device__ __forceinline__ bool ar_reduce_tile(const GemmParams& p, int ta, uint
   epilogue_barrier();
   if (ok && et < p.ar.world) red_release_sys_add(p.ar.done[et], 1u);
   return ok;
+}
+
+// Second kernel of a fully split GEMM: one thread per four output values, grid.y = tile. Sums the
+// partials in split order (deterministic), so a small GEMM whose few tiles were split to fill
+// the machine is also reduced by the whole machine instead of by one CTA per tile.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p, int bn, int tiles_a,
+                                                            int total_kblocks) {
+  const int e4 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e4 >= bn * 32) return;
+  const WorkItem it = decode_item(p, p.first_split_tile + static_cast<long long>(blockIdx.y) * p.splits,
+                                  tiles_a, total_kblocks);
+  if (it.skip) return;
+  reduce_partials<8>(p, it, bn, e4);
 }
 
 template <bool kFp8, int BN, int kAtoms>
@@ -611,15 +636,21 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           // accumulator becoming ready and the FMAs. Row scale: one value per thread. Column
           // scale: one value per tile (128-wide weight blocks) or one per column, in which case
           // lane l holds the scale of column (chunk * 32 + l) and it is broadcast with shuffles.
-          auto load_row_scale = [&](int kb) {
-            return __ldg(p.scale_a + static_cast<long long>(a_row_c / p.sa_gran) * p.sa_ld + kb);
-          };
-          auto load_col_scale = [&](int kb, int i) {
-            if (!col_vector)
-              return __ldg(p.scale_b + static_cast<long long>((it.tb * BN) / p.sb_gran) * p.sb_ld + kb);
-            const int col = min(it.tb * BN + (hsel + 2 * i) * 32 + lane, p.rows_b - 1);
-            return __ldg(p.scale_b + static_cast<long long>(col) * p.sb_ld + kb);
-          };
+          // (index arithmetic hoisted out of the k loop: the granularities are run-time values
+          // and an integer division per k-block kept the conversion pipe busy)
+          const float* sa_ptr = p.scale_a + static_cast<long long>(a_row_c / p.sa_gran) * p.sa_ld;
+          const float* cs_ptr[kMine];
+#pragma unroll
+          for (int i = 0; i < kMine; ++i) {
+            if (!col_vector) {
+              cs_ptr[i] = p.scale_b + static_cast<long long>((it.tb * BN) / p.sb_gran) * p.sb_ld;
+            } else {
+              const int col = min(it.tb * BN + (hsel + 2 * i) * 32 + lane, p.rows_b - 1);
+              cs_ptr[i] = p.scale_b + static_cast<long long>(col) * p.sb_ld;
+            }
+          }
+          auto load_row_scale = [&](int kb) { return __ldg(sa_ptr + kb); };
+          auto load_col_scale = [&](int kb, int i) { return __ldg(cs_ptr[i] + kb); };
           float sa_next = load_row_scale(it.kb0);
           float cs_next[kMine];
 #pragma unroll
@@ -640,30 +671,50 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
               break;
             }
             tc_fence_after_sync();
+            float* bc = bars->cs_bcast[warp - 2][kb & 1];
+            if (col_vector) {
+#pragma unroll
+              for (int i = 0; i < kMine; ++i) bc[i * 32 + lane] = cs[i];
+              __syncwarp();
+            }
 #pragma unroll
             for (int i = 0; i < kMine; ++i) {
               const int c = hsel + 2 * i;
+              const bool last_chunk = (i == kMine - 1) || (hsel + 2 * (i + 1) >= kChunks);
               if (c < kChunks) {
                 uint32_t r[32];
                 tmem_ld_32x32(lane_base + abuf * kBufStride + c * 32, r);
                 tmem_ld_wait();
+                if (last_chunk) {
+                  // the values are in registers: hand the TMEM buffer back before the FMAs
+                  tc_fence_before_sync();
+                  __syncwarp();
+                  if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
+                }
                 if (!col_vector) {
                   const float sc = sa * cs[i];
 #pragma unroll
                   for (int j = 0; j < 32; ++j)
                     acc[i * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[i * 32 + j]);
                 } else {
+                  const float4* b4 = reinterpret_cast<const float4*>(bc + i * 32);
 #pragma unroll
-                  for (int j = 0; j < 32; ++j) {
-                    const float sc = sa * __shfl_sync(0xffffffffu, cs[i], j);
-                    acc[i * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[i * 32 + j]);
+                  for (int j4 = 0; j4 < 8; ++j4) {
+                    const float4 sv = b4[j4];
+                    acc[i * 32 + 4 * j4 + 0] = fmaf(__uint_as_float(r[4 * j4 + 0]), sa * sv.x, acc[i * 32 + 4 * j4 + 0]);
+                    acc[i * 32 + 4 * j4 + 1] = fmaf(__uint_as_float(r[4 * j4 + 1]), sa * sv.y, acc[i * 32 + 4 * j4 + 1]);
+                    acc[i * 32 + 4 * j4 + 2] = fmaf(__uint_as_float(r[4 * j4 + 2]), sa * sv.z, acc[i * 32 + 4 * j4 + 2]);
+                    acc[i * 32 + 4 * j4 + 3] = fmaf(__uint_as_float(r[4 * j4 + 3]), sa * sv.w, acc[i * 32 + 4 * j4 + 3]);
                   }
                 }
               }
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
+            if (hsel >= kChunks) {
+              // a warp without a chunk of its own still takes part in the buffer hand-back
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&bars->tmem_empty[abuf]);
+            }
             if (++abuf == kAccBufs) { abuf = 0; aph ^= 1; }
           }
           if (ok) {
@@ -903,6 +954,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   }
   p.first_split_tile = first_split;
   p.splits = s_eff;
+  p.external_reduce = (first_split == 0 && s_eff > 1 && ar == nullptr) ? 1 : 0;
   p.split_counter = static_cast<uint32_t*>(workspace);
   p.split_ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kSplitCounterBytes);
 
@@ -946,6 +998,11 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     } else {
       rc = launch_gemm<false, 256, 1>(p, ta, tb, grid, stream);
     }
+  }
+  if (rc == 0 && p.external_reduce) {
+    const dim3 rgrid((bn * 32 + 255) / 256, tiles);
+    splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(p, bn, (p.rows_a + kTileA - 1) / kTileA, total_kblocks);
+    if (cudaGetLastError() != cudaSuccess) rc = -300;
   }
   return rc;
 }

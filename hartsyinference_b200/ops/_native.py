@@ -54,7 +54,10 @@ _SIGNATURES = {
 
 
 def lib_path() -> Path:
-    return _LIB_DIR / "libb200_kernels.so"
+    """The kernels library; ``B200_KERNELS_LIB`` points at another build of it (kernel experiments)."""
+    import os
+    override = os.environ.get("B200_KERNELS_LIB")
+    return Path(override) if override else _LIB_DIR / "libb200_kernels.so"
 
 
 def available() -> bool:

@@ -1,0 +1,90 @@
+"""Runs ONE kernel on a small, fixed case a few times: the program that profiler captures wrap.
+
+    python -m hartsyinference_b200.utils.kernel_case gemm fp8 64 28672 4096
+    python -m hartsyinference_b200.utils.kernel_case grouped fp8 32 16 4096 7168
+    python -m hartsyinference_b200.utils.kernel_case attn_decode 64 8 1 128 2304
+    python -m hartsyinference_b200.utils.kernel_case mla 64 16 2304
+
+Inputs are larger than the L2 cache where the op is bandwidth bound but stay far below a few GB,
+so a full-metric capture (dozens of replays per launch) ends in about a minute. The status word is
+checked at the end and the process exits non-zero if a kernel reported a failed wait.
+"""
+from __future__ import annotations
+
+import math
+import sys
+
+import torch
+
+from .. import ops
+from ..ops import _native as N
+
+
+def _gemm(argv):
+    fp8 = argv[0] == "fp8"
+    m, n, k = (int(v) for v in argv[1:4])
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16)
+    lw = ops.LinearWeight.from_dense(w, fp8=fp8)
+    xin = ops.quant_fp8_act(x) if fp8 else x
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        ops.linear(xin, lw, out=out)
+
+
+def _grouped(argv):
+    fp8 = argv[0] == "fp8"
+    groups, m, n, k = (int(v) for v in argv[1:5])
+    x = (torch.randn(groups * m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(groups * n, k, device="cuda") * 0.1).to(torch.bfloat16)
+    lw = ops.LinearWeight.from_dense(w, fp8=fp8)
+    xin = ops.quant_fp8_act(x) if fp8 else x
+    for _ in range(3):
+        ops.grouped_linear(xin, lw, groups)
+
+
+def _attn_decode(argv):
+    seqs, hkv, group, d, ctx = (int(v) for v in argv[:5])
+    page = 16
+    per = (ctx + page - 1) // page
+    pool = seqs * per + 1
+    kc = torch.randn(pool, hkv, page, d, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(pool, hkv, page, d, device="cuda").to(torch.bfloat16)
+    table = (torch.randperm(pool - 1, device="cuda")[:seqs * per] + 1).to(torch.int32).reshape(seqs, per)
+    lens = torch.full((seqs,), ctx, dtype=torch.int32, device="cuda")
+    q = torch.randn(seqs, hkv * group, d, device="cuda").to(torch.bfloat16)
+    for _ in range(3):
+        ops.attn_decode(q, kc, vc, table, lens, max_kv_len=ctx)
+
+
+def _mla(argv):
+    rows, heads, ctx = (int(v) for v in argv[:3])
+    page = 16
+    per = (ctx + page - 1) // page
+    pool = rows * per + 1
+    cache = (torch.randn(pool, page, 576, device="cuda") * 0.5).to(torch.bfloat16)
+    table = (torch.randperm(pool - 1, device="cuda")[:rows * per] + 1).to(torch.int32).reshape(rows, per)
+    lens = torch.full((rows,), ctx, dtype=torch.int32, device="cuda")
+    q = (torch.randn(rows, heads, 576, device="cuda") * 0.3).to(torch.bfloat16)
+    for _ in range(3):
+        ops.mla_attn(q, cache, table, lens, 1.0 / math.sqrt(192), max_kv_len=ctx)
+
+
+CASES = {"gemm": _gemm, "grouped": _grouped, "attn_decode": _attn_decode, "mla": _mla}
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if not argv or argv[0] not in CASES:
+        print(__doc__)
+        return 2
+    torch.manual_seed(0)
+    CASES[argv[0]](argv[1:])
+    torch.cuda.synchronize()
+    N.check_status()
+    print("ok")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

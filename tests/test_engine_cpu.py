@@ -152,3 +152,19 @@ def test_request_too_large_for_pool_is_rejected():
     from hartsyinference_b200.exceptions import KvPoolExhaustedError
     with pytest.raises(KvPoolExhaustedError):
         eng.add_request(list(range(100)), SamplingParams(max_tokens=10))
+
+
+def test_prompt_lookup_speculative_matches_plain_greedy():
+    from hartsyinference_b200.engine.speculative import find_draft, generate_speculative
+    assert find_draft([1, 2, 3, 9, 9, 1, 2, 3], ngram=3, max_draft=2) == [9, 9]
+    assert find_draft([1, 2, 3], ngram=3) == []
+    m = _toy(seed=3)
+    eng = LLMEngine(m, num_pages=64, page_size=16, max_batch=4, prefill_chunk=64, max_model_len=256)
+    # a repetitive prompt so that drafts exist
+    prompt = [7, 8, 9, 10, 11] * 6
+    plain = eng.generate([prompt], SamplingParams(greedy=True, max_tokens=24, ignore_eos=True))[0]
+    free_before = eng.kv.num_free
+    spec, stats = generate_speculative(eng, prompt, SamplingParams(greedy=True, max_tokens=24, ignore_eos=True))
+    assert spec == plain
+    assert stats.drafted > 0 and stats.forward_passes <= 1 + 24
+    assert eng.kv.num_free == free_before            # the sequence was released
