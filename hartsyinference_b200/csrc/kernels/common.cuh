@@ -256,6 +256,50 @@ __device__ __forceinline__ void mma_fp8_ss(uint32_t d_tmem, uint64_t adesc, uint
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// ---- hardware block scaling (kind::mxf8f6f4.block_scale, one UE8M0 scale per 32 K elements) ----
+// Instruction descriptor of the block-scaled form: no D format field (always fp32);
+//   [4,6) B scale-factor id  [7,10) A format  [10,13) B format  [17,23) N >> 3
+//   [23] scale format (1 = UE8M0)  [24,29) M >> 4  [29,31) A scale-factor id.
+// The scale-factor id picks one of the four bytes of a 32-bit TMEM scale column, so a column holds
+// the scales of four consecutive K groups and is refreshed once per four.
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t m, uint32_t n) {
+  return (kFmtE4m3 << 7) | (kFmtE4m3 << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_mxf8_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate, uint32_t sfa_tmem,
+                                            uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// Shared-memory descriptor of one 512-byte scale-factor block: 32 rows of 16 bytes, no swizzle
+// (8-row core matrices of 128 bytes, so the stride between them is 128 bytes).
+__device__ __forceinline__ uint64_t make_desc_sf(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;     // SBO
+  d |= static_cast<uint64_t>(1) << 46;            // descriptor version for sm_100
+  return d;
+}
+// Copies a 32 x 128-bit block from shared memory into 4 TMEM columns of all four lane quarters.
+__device__ __forceinline__ void tmem_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
+}
+// Untiled bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16), completion
+// counted as transaction bytes on `bar`.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
 __device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
                                           uint32_t idesc, uint32_t accumulate) {
   asm volatile(

@@ -32,6 +32,25 @@ __device__ __forceinline__ uint8_t to_e4m3(float v) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
 }
 
+// UE8M0 (power-of-two) scale for hardware block scaling: the smallest 2^e >= amax / 448.
+// Returns 2^-e and the biased exponent byte e + 127.
+__device__ __forceinline__ float mx_scale_inv(float amax, uint32_t& e_biased) {
+  const uint32_t bits = __float_as_uint(amax / kFp8Max);
+  int e = static_cast<int>(bits >> 23) - 127 + ((bits & 0x7fffffu) != 0 ? 1 : 0);
+  e = max(-126, min(126, e));
+  e_biased = static_cast<uint32_t>(e + 127);
+  return __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+}
+// Blocked scale-factor layout read by the block-scaled GEMM: rows are grouped in tiles of
+// `tile_rows` (<= 128, each padded to a 128-row block), K in groups of four 128-wide blocks; a
+// block is 128 x uint32 with row r at word (r % 32) * 4 + r / 32 and K block kb at byte kb % 4.
+__device__ __forceinline__ void store_sf(uint8_t* sf, int row, int kb, int tile_rows, int kgroups,
+                                         uint32_t e_biased) {
+  const int tile = row / tile_rows, r = row - tile * tile_rows;
+  const long long blk = static_cast<long long>(tile) * kgroups + (kb >> 2);
+  sf[(blk * 128 + (r & 31) * 4 + (r >> 5)) * 4 + (kb & 3)] = static_cast<uint8_t>(e_biased);
+}
+
 struct NormParams {
   const __nv_bfloat16* x;         // [rows][dim]
   const __nv_bfloat16* residual;  // optional [rows][dim]: h = x + residual
@@ -47,6 +66,7 @@ struct NormParams {
   float eps;
   int layernorm;                  // 0 = RMSNorm, 1 = LayerNorm (mean-centred)
   int weight_plus_one;            // Gemma-style (1 + w)
+  int sf_tile_rows;               // > 0: out_scale is a blocked UE8M0 scale-factor array
 };
 
 // dim % 8 == 0; blockDim.x * 8 >= dim handled by a strided loop keeping the row in registers for
@@ -169,8 +189,10 @@ __global__ void __launch_bounds__(1024) norm_kernel(const NormParams p) {
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       if (active) {
-        const float sc = fmaxf(amax, 1e-12f) / kFp8Max;
-        const float inv = 1.f / sc;
+        float sc = fmaxf(amax, 1e-12f) / kFp8Max;
+        float inv = 1.f / sc;
+        uint32_t eb = 0;
+        if (p.sf_tile_rows > 0) inv = mx_scale_inv(amax, eb);
         uint32_t lo = 0, hi = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) lo |= static_cast<uint32_t>(to_e4m3(y[i] * inv)) << (8 * i);
@@ -178,7 +200,12 @@ __global__ void __launch_bounds__(1024) norm_kernel(const NormParams p) {
         for (int i = 0; i < 4; ++i) hi |= static_cast<uint32_t>(to_e4m3(y[4 + i] * inv)) << (8 * i);
         *reinterpret_cast<uint2*>(p.out_fp8 + static_cast<long long>(row) * p.dim + vi * 8) =
             make_uint2(lo, hi);
-        if ((vi & 15) == 0) p.out_scale[static_cast<long long>(row) * (p.dim >> 7) + (vi >> 4)] = sc;
+        if ((vi & 15) == 0) {
+          if (p.sf_tile_rows > 0)
+            store_sf(reinterpret_cast<uint8_t*>(p.out_scale), row, vi >> 4, p.sf_tile_rows, (p.dim + 511) >> 9, eb);
+          else
+            p.out_scale[static_cast<long long>(row) * (p.dim >> 7) + (vi >> 4)] = sc;
+        }
       }
     }
   }
@@ -186,7 +213,8 @@ __global__ void __launch_bounds__(1024) norm_kernel(const NormParams p) {
 
 // fp8 1x128 quantisation of a bf16 matrix [rows][dim] (dim % 128 == 0) with row pitch ld.
 __global__ void quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out,
-                                 float* __restrict__ scales, int rows, int dim, long long ld) {
+                                 float* __restrict__ scales, int rows, int dim, long long ld,
+                                 int sf_tile_rows) {
   const int groups = dim >> 7;
   const long long total = static_cast<long long>(rows) * groups * 16;   // one thread per 8 values
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -213,8 +241,10 @@ __global__ void quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* _
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if (active) {
-      const float sc = fmaxf(amax, 1e-12f) / kFp8Max;
-      const float inv = 1.f / sc;
+      float sc = fmaxf(amax, 1e-12f) / kFp8Max;
+      float inv = 1.f / sc;
+      uint32_t eb = 0;
+      if (sf_tile_rows > 0) inv = mx_scale_inv(amax, eb);
       uint32_t lo = 0, hi = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) lo |= static_cast<uint32_t>(to_e4m3(v[k] * inv)) << (8 * k);
@@ -222,7 +252,12 @@ __global__ void quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* _
       for (int k = 0; k < 4; ++k) hi |= static_cast<uint32_t>(to_e4m3(v[4 + k] * inv)) << (8 * k);
       *reinterpret_cast<uint2*>(out + static_cast<long long>(row) * dim + grp * 128 + sub * 8) =
           make_uint2(lo, hi);
-      if (sub == 0) scales[static_cast<long long>(row) * groups + grp] = sc;
+      if (sub == 0) {
+        if (sf_tile_rows > 0)
+          store_sf(reinterpret_cast<uint8_t*>(scales), row, grp, sf_tile_rows, (dim + 511) >> 9, eb);
+        else
+          scales[static_cast<long long>(row) * groups + grp] = sc;
+      }
     }
   }
 }
@@ -282,7 +317,7 @@ __global__ void quant_fp8_weight_kernel(const __nv_bfloat16* __restrict__ w,
 // up), act: 0 = SiLU, 1 = GELU-tanh. Optional fp8 1x128 output (F % 128 == 0).
 __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                            uint8_t* __restrict__ out_fp8, float* __restrict__ out_scale, int rows,
-                           int f, int act) {
+                           int f, int act, int sf_tile_rows) {
   const int nvec = f >> 3;
   const long long total = static_cast<long long>(rows) * nvec;
   const long long padded = ((total + 31) / 32) * 32;
@@ -319,8 +354,10 @@ __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* 
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       if (active) {
-        const float sc = fmaxf(amax, 1e-12f) / kFp8Max;
-        const float inv = 1.f / sc;
+        float sc = fmaxf(amax, 1e-12f) / kFp8Max;
+        float inv = 1.f / sc;
+        uint32_t eb = 0;
+        if (sf_tile_rows > 0) inv = mx_scale_inv(amax, eb);
         uint32_t lo = 0, hi = 0;
 #pragma unroll
         for (int k = 0; k < 4; ++k) lo |= static_cast<uint32_t>(to_e4m3(y[k] * inv)) << (8 * k);
@@ -328,7 +365,12 @@ __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* 
         for (int k = 0; k < 4; ++k) hi |= static_cast<uint32_t>(to_e4m3(y[4 + k] * inv)) << (8 * k);
         *reinterpret_cast<uint2*>(out_fp8 + static_cast<long long>(row) * f + vi * 8) =
             make_uint2(lo, hi);
-        if ((vi & 15) == 0) out_scale[static_cast<long long>(row) * (f >> 7) + (vi >> 4)] = sc;
+        if ((vi & 15) == 0) {
+          if (sf_tile_rows > 0)
+            store_sf(reinterpret_cast<uint8_t*>(out_scale), row, vi >> 4, sf_tile_rows, (f + 511) >> 9, eb);
+          else
+            out_scale[static_cast<long long>(row) * (f >> 7) + (vi >> 4)] = sc;
+        }
       }
     }
   }
@@ -629,7 +671,7 @@ B200_API int b200_norm(const void* x, const void* residual, void* residual_out, 
                        const void* bias, const void* shift, const void* scale, void* out,
                        void* out_fp8, float* out_scale, int rows, int dim, int rows_per_batch,
                        int mod_stride, float eps, int layernorm, int weight_plus_one,
-                       cudaStream_t stream) {
+                       int sf_tile_rows, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (dim % 8 != 0 || dim > 16384) return -2;
   if (out_fp8 && dim % 128 != 0) return -3;
@@ -646,6 +688,7 @@ B200_API int b200_norm(const void* x, const void* residual, void* residual_out, 
   p.out_scale = out_scale;
   p.rows = rows; p.dim = dim; p.rows_per_batch = rows_per_batch; p.mod_stride = mod_stride;
   p.eps = eps; p.layernorm = layernorm; p.weight_plus_one = weight_plus_one;
+  p.sf_tile_rows = sf_tile_rows;
   const int nvec = dim / 8;
   // threads: multiple of 32 covering the row with at most 2 vectors per thread
   int threads = ((nvec + 31) / 32) * 32;
@@ -659,14 +702,16 @@ B200_API int b200_norm(const void* x, const void* residual, void* residual_out, 
   return 0;
 }
 
+// sf_tile_rows > 0: `scales` is a blocked UE8M0 scale-factor array (see store_sf) instead of fp32
+// [rows][dim / 128]; the same convention applies to b200_norm and b200_glu.
 B200_API int b200_quant_fp8(const void* x, void* out, float* scales, int rows, int dim,
-                            long long ld, cudaStream_t stream) {
+                            long long ld, int sf_tile_rows, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (dim % 128 != 0 || ld % 8 != 0) return -2;
   const long long n = static_cast<long long>(rows) * (dim / 8);
   quant_fp8_kernel<<<grid_for(n, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
                                                          static_cast<uint8_t*>(out), scales, rows,
-                                                         dim, ld);
+                                                         dim, ld, sf_tile_rows);
   CHECK_LAUNCH();
   return 0;
 }
@@ -682,14 +727,14 @@ B200_API int b200_quant_fp8_weight(const void* w, void* out, float* scales, int 
 }
 
 B200_API int b200_glu(const void* in, void* out, void* out_fp8, float* out_scale, int rows, int f,
-                      int act, cudaStream_t stream) {
+                      int act, int sf_tile_rows, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (f % 8 != 0 || (out_fp8 && f % 128 != 0)) return -2;
   const long long n = static_cast<long long>(rows) * (f / 8);
   glu_kernel<<<grid_for(n, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in),
                                                    static_cast<__nv_bfloat16*>(out),
                                                    static_cast<uint8_t*>(out_fp8), out_scale, rows,
-                                                   f, act);
+                                                   f, act, sf_tile_rows);
   CHECK_LAUNCH();
   return 0;
 }

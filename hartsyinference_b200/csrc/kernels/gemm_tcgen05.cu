@@ -73,6 +73,12 @@ struct GemmParams {
   // g * group_out_stride. 0 = stacked token blocks as described above.
   int group_b_koff;
   int group_out_stride;
+  // MX mode (hardware block scaling): UE8M0 scale factors in the blocked layout
+  // [row tile][k group of 512][128 x uint32], see quant_mx.cuh; sf_tile_b = B rows per SF block.
+  const uint32_t* sf_a;
+  const uint32_t* sf_b;
+  int sf_kgroups;
+  int sf_tile_b;
   // 1: every tile is split and a second kernel (splitk_reduce_kernel) sums the partials with the
   // whole machine; 0: the last CTA to arrive at a split tile sums them inside this kernel.
   int external_reduce;
@@ -417,22 +423,35 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p, 
   reduce_partials<8>(p, it, bn, e4);
 }
 
-template <bool kFp8, int BN, int kAtoms>
+template <int kMode, int BN, int kAtoms>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a,
                     const __grid_constant__ CUtensorMap tm_b) {
   // A stage holds kAtoms swizzle atoms (128 bytes of K each) per operand: [A atoms][B atoms].
+  // kMode: 0 = bf16, 1 = e4m3 with fp32 block scales promoted by the epilogue warps per k-block,
+  // 2 = e4m3 with UE8M0 block scales applied by the tensor core (kind::mxf8f6f4.block_scale).
+  constexpr bool kFp8Data = kMode != 0;
+  constexpr bool kFp8 = kMode == 1;                // software promotion
+  constexpr bool kMx = kMode == 2;
   constexpr int kAtomBytesB = BN * 128;
-  constexpr int kStageBytes = kAtoms * (kStageBytesA + kAtomBytesB);
-  constexpr int kElemsPerAtom = kFp8 ? 128 : 64;   // K elements in one 128-byte atom
+  constexpr int kSfBytes = kMx ? 1536 : 0;         // per stage: SF block of A + up to two of B
+  constexpr int kStageBytes = kAtoms * (kStageBytesA + kAtomBytesB) + (kMx ? 2048 : 0);
+  constexpr int kSfOffset = kAtoms * (kStageBytesA + kAtomBytesB);
+  constexpr int kElemsPerAtom = kFp8Data ? 128 : 64;   // K elements in one 128-byte atom
   // Accumulator ring in TMEM: as many buffers as fit in the 512 columns (at most 8). The
   // block-scaled path hands one buffer per 128-deep K block to the epilogue warps, so a deep ring
   // lets the tensor core run ahead of the promotion; the bf16 path uses one buffer per work item.
   constexpr int kBufStride = BN < 32 ? 32 : BN;   // loads are 32 columns wide
-  constexpr int kAccBufs = (512 / kBufStride) < 8 ? (512 / kBufStride) : 8;
-  constexpr uint32_t kTmemCols = kAccBufs * kBufStride;
-  constexpr uint32_t kIdesc = kFp8 ? make_idesc(128, BN, kFmtE4m3, kFmtE4m3)
-                                   : make_idesc(128, BN, kFmtBf16, kFmtBf16);
+  constexpr int kAccCols = kMx ? 480 : 512;        // MX keeps 32 columns for the scale factors
+  constexpr int kAccBufsRaw = (kAccCols / kBufStride) < 8 ? (kAccCols / kBufStride) : 8;
+  constexpr int kAccBufs = kMx && kAccBufsRaw > 4 ? 4 : kAccBufsRaw;
+  constexpr uint32_t kSfCol = kAccBufs * kBufStride;                  // first SF column
+  constexpr uint32_t kTmemNeed = kAccBufs * kBufStride + (kMx ? 32 : 0);
+  constexpr uint32_t kTmemCols = kTmemNeed <= 32 ? 32 : kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128
+                               : kTmemNeed <= 256 ? 256 : 512;
+  constexpr uint32_t kIdesc = kMx ? make_idesc_mx(128, BN)
+                            : kFp8Data ? make_idesc(128, BN, kFmtE4m3, kFmtE4m3)
+                                       : make_idesc(128, BN, kFmtBf16, kFmtBf16);
   static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256,
                 "tcgen05.mma M=128 needs N % 16 == 0; TMEM allocations are powers of two");
   static_assert(!kFp8 || BN <= 128, "fp8 path keeps BN / 2 fp32 accumulators per thread");
@@ -496,7 +515,21 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           }
           uint8_t* sa = smem + s * kStageBytes;
           uint8_t* sb = sa + kAtoms * kStageBytesA;
-          mbar_arrive_expect_tx(&bars->full[s], na * (kStageBytesA + kAtomBytesB));
+          // MX: the stage that starts a group of four k-blocks also carries the group's scale factors
+          const bool with_sf = kMx && ((kb & 3) == 0 || kb == it.kb0);
+          constexpr int kSfBlocksB = BN > 128 ? 2 : 1;
+          mbar_arrive_expect_tx(&bars->full[s], na * (kStageBytesA + kAtomBytesB) +
+                                                    (with_sf ? 512 * (1 + kSfBlocksB) : 0));
+          if (with_sf) {
+            const long long ga = (static_cast<long long>(it.ta) * p.sf_kgroups + (kb >> 2)) * 128;
+            bulk_load(sa + kSfOffset, p.sf_a + ga, 512, &bars->full[s]);
+            const long long tile_b = (static_cast<long long>(it.tb) * BN) / p.sf_tile_b;
+#pragma unroll
+            for (int j = 0; j < kSfBlocksB; ++j) {
+              const long long gb = ((tile_b + j) * p.sf_kgroups + (kb >> 2)) * 128;
+              bulk_load(sa + kSfOffset + 512 * (1 + j), p.sf_b + gb, 512, &bars->full[s]);
+            }
+          }
           for (int a = 0; a < na; ++a) {
             tma_load_2d(sa + a * kStageBytesA, &tm_a, &bars->full[s], (kb + a) * kElemsPerAtom,
                         it.ta * kTileA);
@@ -547,6 +580,15 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
           }
           const uint32_t sa = smem_u32(smem + s * kStageBytes);
           const uint32_t sb = sa + kAtoms * kStageBytesA;
+          if (kMx && ((kb & 3) == 0 || kb == it.kb0)) {
+            // scale factors of this group of four k-blocks: shared memory -> TMEM (4 columns per
+            // 128 rows), two TMEM slots used alternately
+            tc_fence_after_sync();
+            const uint32_t slot = tmem_base + kSfCol + ((kb >> 2) & 1) * 16;
+            tmem_cp_sf(slot, make_desc_sf(sa + kSfOffset));
+            tmem_cp_sf(slot + 4, make_desc_sf(sa + kSfOffset + 512));
+            if (BN > 128) tmem_cp_sf(slot + 8, make_desc_sf(sa + kSfOffset + 1024));
+          }
           for (int a = 0; a < na; ++a) {
             if (kFp8) {
               if (!mbar_wait(&bars->tmem_empty[abuf], aph ^ 1, abort_flag)) {
@@ -564,8 +606,16 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
               // advancing 32 bytes along K inside the 128-byte swizzle atom = +2 in the
               // (address >> 4) field of the descriptor
               const uint32_t acc = kFp8 ? (k > 0) : (kb + a > it.kb0 || k > 0);
-              if (kFp8) mma_fp8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
-              else      mma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+              if (kMx) {
+                const uint32_t sf_id = static_cast<uint32_t>(kb + a) & 3u;
+                const uint32_t slot = tmem_base + kSfCol + (((kb + a) >> 2) & 1) * 16;
+                mma_mxf8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc | (sf_id << 29) | (sf_id << 4), acc,
+                            slot, slot + 4);
+              } else if (kFp8Data) {
+                mma_fp8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+              } else {
+                mma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+              }
             }
             issued_any = true;
             if (kFp8) {
@@ -807,19 +857,19 @@ int make_kmajor_map(CUtensorMap* out, const void* base, int elem_bytes, long lon
   return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 100;
 }
 
-template <bool kFp8, int BN, int kAtoms>
+template <int kMode, int BN, int kAtoms>
 int launch_gemm(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, int grid,
                 cudaStream_t stream) {
-  const int stage_bytes = kAtoms * (kStageBytesA + BN * 128);
+  const int stage_bytes = kAtoms * (kStageBytesA + BN * 128) + (kMode == 2 ? 2048 : 0);
   const int smem = p.stages * stage_bytes + static_cast<int>(sizeof(GemmBarriers)) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<kFp8, BN, kAtoms>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<kMode, BN, kAtoms>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
     if (e != cudaSuccess) return -static_cast<int>(e) - 200;
     configured = true;
   }
-  gemm_tcgen05_kernel<kFp8, BN, kAtoms><<<grid, kGemmThreads, smem, stream>>>(p, ta, tb);
+  gemm_tcgen05_kernel<kMode, BN, kAtoms><<<grid, kGemmThreads, smem, stream>>>(p, ta, tb);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 300;
 }
@@ -853,12 +903,13 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   const int groups = gs ? gs->groups : 0;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   // grouped: x is [groups * m][k], w is [groups * n][k], out is [groups * m][n]; m = tokens per group
-  const bool fp8 = dtype == 1;
+  const bool fp8 = dtype != 0;          // 1: fp32 block scales, 2: UE8M0 scale factors (blocked layout)
+  const bool mx = dtype == 2;
   const int esz = fp8 ? 1 : 2;
   const int kelems = fp8 ? 128 : 64;
   if ((ldx * esz) % 16 != 0 || (ldw * esz) % 16 != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -3;
-  if (fp8 && (k % 128 != 0 || !x_scale || !w_scale)) return -4;
+  if (fp8 && ((!mx && k % 128 != 0) || k % 16 != 0 || !x_scale || !w_scale)) return -4;
   if (groups > 0) {
     if (m < 1 || m > 128 || n % 128 != 0) return -9;
     if (gs->b_koff > 0) {
@@ -915,6 +966,16 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     p.scale_a = x_scale; p.sa_gran = 1;   p.sa_ld = k / 128;
     p.scale_b = w_scale; p.sb_gran = 128; p.sb_ld = k / 128;
   }
+  if (mx) {
+    const bool a_is_w = groups > 0 || swap;
+    p.sf_a = reinterpret_cast<const uint32_t*>(a_is_w ? w_scale : x_scale);
+    p.sf_b = reinterpret_cast<const uint32_t*>(a_is_w ? x_scale : w_scale);
+    p.sf_kgroups = (k + 511) / 512;
+    // SF blocks of the token operand cover one tile of `m` slots per group in the stacked grouped
+    // mode (each padded to 128 rows), otherwise 128 consecutive rows
+    p.sf_tile_b = (groups > 0 && gs->b_koff == 0) ? m : 128;
+    if (groups > 0 && gs->b_koff > 0) return -9;
+  }
   const int total_kblocks = (k + kelems - 1) / kelems;
   const int tiles = groups > 0 ? (p.rows_a + 127) / 128 : ((p.rows_a + 127) / 128) * ((p.rows_b + bn - 1) / bn);
   const int sms = num_sms();
@@ -942,6 +1003,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   }
   if (s_eff > total_kblocks) s_eff = total_kblocks;
   p.kblocks_per_split = (total_kblocks + s_eff - 1) / s_eff;
+  if (mx) p.kblocks_per_split = (p.kblocks_per_split + 3) / 4 * 4;   // ranges start on a scale-factor group
   s_eff = (total_kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
   if (s_eff <= 1) { first_split = tiles; s_eff = 1; p.kblocks_per_split = total_kblocks; }
   const int split_tiles = tiles - first_split;
@@ -960,7 +1022,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
 
   // two atoms per stage for the bandwidth-bound small-token orientation
   const int atoms = swap ? 2 : 1;
-  const int stage_bytes = atoms * (kStageBytesA + bn * 128);
+  const int stage_bytes = atoms * (kStageBytesA + bn * 128) + (mx ? 2048 : 0);
   int stages = (200 * 1024) / stage_bytes;
   if (stages > 12) stages = 12;
   p.stages = stages;
@@ -974,29 +1036,40 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   const long long items = first_split + static_cast<long long>(tiles - first_split) * s_eff;
   const int grid = static_cast<int>(items < sms ? items : sms);
 
-  if (fp8) {
+  if (mx) {
     if (swap) {
       switch (bn) {
-        case 16: rc = launch_gemm<true, 16, 2>(p, ta, tb, grid, stream); break;
-        case 32: rc = launch_gemm<true, 32, 2>(p, ta, tb, grid, stream); break;
-        case 64: rc = launch_gemm<true, 64, 2>(p, ta, tb, grid, stream); break;
-        default: rc = launch_gemm<true, 128, 2>(p, ta, tb, grid, stream); break;
+        case 16: rc = launch_gemm<2, 16, 2>(p, ta, tb, grid, stream); break;
+        case 32: rc = launch_gemm<2, 32, 2>(p, ta, tb, grid, stream); break;
+        case 64: rc = launch_gemm<2, 64, 2>(p, ta, tb, grid, stream); break;
+        default: rc = launch_gemm<2, 128, 2>(p, ta, tb, grid, stream); break;
       }
     } else {
-      rc = launch_gemm<true, 128, 1>(p, ta, tb, grid, stream);
+      rc = launch_gemm<2, 128, 1>(p, ta, tb, grid, stream);
+    }
+  } else if (fp8) {
+    if (swap) {
+      switch (bn) {
+        case 16: rc = launch_gemm<1, 16, 2>(p, ta, tb, grid, stream); break;
+        case 32: rc = launch_gemm<1, 32, 2>(p, ta, tb, grid, stream); break;
+        case 64: rc = launch_gemm<1, 64, 2>(p, ta, tb, grid, stream); break;
+        default: rc = launch_gemm<1, 128, 2>(p, ta, tb, grid, stream); break;
+      }
+    } else {
+      rc = launch_gemm<1, 128, 1>(p, ta, tb, grid, stream);
     }
   } else {
     if (swap) {
       switch (bn) {
-        case 16: rc = launch_gemm<false, 16, 2>(p, ta, tb, grid, stream); break;
-        case 32: rc = launch_gemm<false, 32, 2>(p, ta, tb, grid, stream); break;
-        case 64: rc = launch_gemm<false, 64, 2>(p, ta, tb, grid, stream); break;
-        default: rc = launch_gemm<false, 128, 2>(p, ta, tb, grid, stream); break;
+        case 16: rc = launch_gemm<0, 16, 2>(p, ta, tb, grid, stream); break;
+        case 32: rc = launch_gemm<0, 32, 2>(p, ta, tb, grid, stream); break;
+        case 64: rc = launch_gemm<0, 64, 2>(p, ta, tb, grid, stream); break;
+        default: rc = launch_gemm<0, 128, 2>(p, ta, tb, grid, stream); break;
       }
     } else if (bn == 128) {
-      rc = launch_gemm<false, 128, 1>(p, ta, tb, grid, stream);
+      rc = launch_gemm<0, 128, 1>(p, ta, tb, grid, stream);
     } else {
-      rc = launch_gemm<false, 256, 1>(p, ta, tb, grid, stream);
+      rc = launch_gemm<0, 256, 1>(p, ta, tb, grid, stream);
     }
   }
   if (rc == 0 && p.external_reduce) {

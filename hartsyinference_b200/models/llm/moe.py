@@ -122,7 +122,7 @@ class MoeFeedForward:
         slot_of, counts = ops.moe_dispatch(h, ids, self.e0, self.e_local, cap, xs)
         gu = ops.grouped_linear(xs, self.w.gate_up, self.e_local, counts=counts)
         fp8 = self.w.down.is_fp8
-        a, a8 = ops.glu(gu, self.cfg.activation, emit_fp8=fp8, emit_bf16=not fp8)
+        a, a8 = ops.glu(gu, self.cfg.activation, emit_fp8=fp8, emit_bf16=not fp8, fp8_tile_rows=cap)
         y = ops.grouped_linear(a8 if a8 is not None else a, self.w.down, self.e_local, counts=counts)
         ops.moe_combine(y, slot_of, wts, out, accumulate=accumulate)
 

@@ -275,7 +275,7 @@ class DecoderModel:
                 ops.fill_random_(w, counter[0])
                 sc = torch.full(((n + 127) // 128, k // 128), std / 112.0, dtype=torch.float32, device=dev)
                 b = dense(1, n).reshape(n) if bias else None
-                return LinearWeight(w, sc, b)
+                return LinearWeight.from_quantized(w, sc, b)
             b = dense(1, n).reshape(n) if bias else None
             return LinearWeight(dense(n, k), None, b)
 

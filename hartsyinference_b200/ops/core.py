@@ -13,15 +13,42 @@ from . import reference as R
 _ACT = {None: 0, "none": 0, "gelu_tanh": 1, "silu": 2}
 
 
+def fp8_mx() -> bool:
+    """True when fp8 linears use UE8M0 (power-of-two) block scales applied by the tensor core
+    (config flag ``fp8_scales``), False for fp32 scales promoted by the epilogue."""
+    from .. import config
+    return config.get("fp8_scales") == "ue8m0"
+
+
+def _alloc_sf(rows: int, k: int, tile_rows: int, device) -> torch.Tensor:
+    """Blocked scale-factor array for ``rows`` x ``k`` e4m3 values (see reference.pack_sf). Bytes of
+    K blocks past the end of K must be finite (they meet zero data), so a ragged last group is
+    zero-filled; rows past the end only feed output rows that are never stored."""
+    tiles, kg = (rows + tile_rows - 1) // tile_rows, (k + 511) // 512
+    if k % 512:
+        return torch.zeros(tiles, kg, 128, dtype=torch.int32, device=device)
+    return torch.empty(tiles, kg, 128, dtype=torch.int32, device=device)
+
+
 @dataclass
 class Fp8Act:
-    """e4m3 activations [M, K] (uint8 storage) with 1x128 scales [M, K/128]."""
+    """e4m3 activations [M, K] (uint8 storage) with 1x128 scales: fp32 ``scale`` [M, K/128], or
+    (device, UE8M0 mode) the blocked scale-factor array ``sf`` covering ``tile_rows`` rows per block."""
     data: torch.Tensor
-    scale: torch.Tensor
+    scale: Optional[torch.Tensor]
+    sf: Optional[torch.Tensor] = None
+    tile_rows: int = 128
 
     @property
     def shape(self):
         return self.data.shape
+
+    def scales_fp32(self) -> torch.Tensor:
+        """The scales as fp32 [M, K/128] whichever way they are stored."""
+        if self.scale is not None:
+            return self.scale
+        m, k = self.data.shape
+        return R.unpack_sf(self.sf, m, k // 128, self.tile_rows)
 
 
 @dataclass
@@ -31,10 +58,25 @@ class LinearWeight:
     weight: torch.Tensor
     scale: Optional[torch.Tensor] = None
     bias: Optional[torch.Tensor] = None
+    sf: Optional[torch.Tensor] = None       # UE8M0 mode: blocked scale factors built from ``scale``
 
     @property
     def is_fp8(self) -> bool:
         return self.scale is not None
+
+    @property
+    def is_mx(self) -> bool:
+        return self.sf is not None
+
+    @staticmethod
+    def from_quantized(q: torch.Tensor, scale: torch.Tensor, bias: Optional[torch.Tensor] = None) -> "LinearWeight":
+        """e4m3 bytes [N, K] + block scales [ceil(N/128), K/128]. In UE8M0 mode the scales must be
+        powers of two (they are rounded to the nearest one) and the blocked array is built here."""
+        if fp8_mx():
+            scale = torch.exp2(torch.log2(scale.float()).round())
+            sf = R.pack_sf(scale.repeat_interleave(128, dim=0)[:((q.shape[0] + 127) // 128) * 128], 128)
+            return LinearWeight(q, scale.contiguous(), bias, sf.contiguous())
+        return LinearWeight(q, scale, bias)
 
     @property
     def out_features(self) -> int:
@@ -48,6 +90,8 @@ class LinearWeight:
         n = self.weight.numel() * self.weight.element_size()
         if self.scale is not None:
             n += self.scale.numel() * 4
+        if self.sf is not None:
+            n += self.sf.numel() * 4
         if self.bias is not None:
             n += self.bias.numel() * self.bias.element_size()
         return n
@@ -57,29 +101,37 @@ class LinearWeight:
         w = w.to(torch.bfloat16).contiguous()
         if fp8 and w.shape[1] % 128 == 0:
             q, s = quant_fp8_weight(w)
-            return LinearWeight(q, s, None if bias is None else bias.to(torch.bfloat16))
+            return LinearWeight.from_quantized(q, s, None if bias is None else bias.to(torch.bfloat16))
         return LinearWeight(w, None, None if bias is None else bias.to(torch.bfloat16))
 
 
 # ---------------------------------------------------------------------------------------------
-def quant_fp8_act(x: torch.Tensor) -> Fp8Act:
-    """bf16 [M, K] -> e4m3 with one scale per 128 consecutive K values."""
+def quant_fp8_act(x: torch.Tensor, tile_rows: int = 128, mx: Optional[bool] = None) -> Fp8Act:
+    """bf16 [M, K] -> e4m3 with one scale per 128 consecutive K values (fp32, or UE8M0 in the
+    blocked layout with ``tile_rows`` rows per block when the UE8M0 mode is on)."""
+    mx = fp8_mx() if mx is None else mx
     if not x.is_cuda:
-        q, s = R.quant_fp8_act(x)
+        q, s = R.quant_fp8_act(x, pow2=mx)
         return Fp8Act(q, s)
     m, k = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1
     q = torch.empty(m, k, dtype=torch.uint8, device=x.device)
+    if mx:
+        sf = _alloc_sf(m, k, tile_rows, x.device)
+        N.check(N.lib().b200_quant_fp8(x.data_ptr(), q.data_ptr(), sf.data_ptr(), m, k, x.stride(0), tile_rows,
+                                       N.stream()), "b200_quant_fp8")
+        return Fp8Act(q, None, sf, tile_rows)
     s = torch.empty(m, k // 128, dtype=torch.float32, device=x.device)
-    N.check(N.lib().b200_quant_fp8(x.data_ptr(), q.data_ptr(), s.data_ptr(), m, k, x.stride(0), N.stream()),
+    N.check(N.lib().b200_quant_fp8(x.data_ptr(), q.data_ptr(), s.data_ptr(), m, k, x.stride(0), 0, N.stream()),
             "b200_quant_fp8")
     return Fp8Act(q, s)
 
 
 def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """bf16 [N, K] -> (e4m3 bytes, scales [ceil(N/128), K/128]) with one scale per 128x128 block."""
-    if not w.is_cuda:
-        return R.quant_fp8_weight(w)
+    if not w.is_cuda or fp8_mx():
+        # UE8M0 mode: power-of-two scales; a load-time step, so plain tensor ops are fine
+        return R.quant_fp8_weight(w, pow2=fp8_mx())
     n, k = w.shape
     w = w.to(torch.bfloat16).contiguous()
     q = torch.empty(n, k, dtype=torch.uint8, device=w.device)
@@ -87,6 +139,18 @@ def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     N.check(N.lib().b200_quant_fp8_weight(w.data_ptr(), q.data_ptr(), s.data_ptr(), n, k, N.stream()),
             "b200_quant_fp8_weight")
     return q, s
+
+
+def _gemm_dtype(w: LinearWeight) -> int:
+    return 2 if w.is_mx else 1 if w.is_fp8 else 0
+
+
+def _scale_ptrs(x, w: LinearWeight):
+    if not w.is_fp8:
+        return None, None
+    if w.is_mx:
+        return x.sf.data_ptr(), w.sf.data_ptr()
+    return x.scale.data_ptr(), w.scale.data_ptr()
 
 
 def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.Tensor] = None,
@@ -102,7 +166,7 @@ def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.T
         if isinstance(x, Fp8Act):
             y = R.linear(x.data, w.weight, w.scale, x.scale, w.bias, act, gate, residual)
         elif w.is_fp8:
-            q, s = R.quant_fp8_act(x)
+            q, s = R.quant_fp8_act(x, pow2=fp8_mx())
             y = R.linear(q, w.weight, w.scale, s, w.bias, act, gate, residual)
         else:
             y = R.linear(x, w.weight, None, None, w.bias, act, gate, residual)
@@ -111,10 +175,12 @@ def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.T
             return out
         return y
     if w.is_fp8 and not isinstance(x, Fp8Act):
-        x = quant_fp8_act(x)
+        x = quant_fp8_act(x, mx=w.is_mx)
         xd = x.data
     if not w.is_fp8 and isinstance(x, Fp8Act):
         raise ValueError("fp8 activations need an fp8 weight")
+    if w.is_fp8 and (x.sf is not None) != w.is_mx:
+        raise ValueError("activation and weight use different fp8 scale formats")
     m, k = xd.shape
     n = w.weight.shape[0]
     assert w.weight.shape[1] == k, (w.weight.shape, xd.shape)
@@ -125,9 +191,10 @@ def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.T
     L = N.lib()
     st = N.state(xd.device)
     ws = st.gemm_workspace()
+    xs_ptr, ws_ptr = _scale_ptrs(x, w)
     rc = L.b200_gemm(xd.data_ptr(), w.weight.data_ptr(), out.data_ptr(), m, n, k,
-                     xd.stride(0), w.weight.stride(0), out.stride(0), 1 if fp8 else 0,
-                     x.scale.data_ptr() if fp8 else None, w.scale.data_ptr() if fp8 else None,
+                     xd.stride(0), w.weight.stride(0), out.stride(0), _gemm_dtype(w),
+                     xs_ptr, ws_ptr,
                      N.ptr(w.bias), N.ptr(gate), N.ptr(residual), _ACT[act], 0 if splits is None else splits,
                      ws.data_ptr(), ws.numel(), st.status.data_ptr(), N.stream())
     N.check(rc, "b200_gemm")
@@ -138,7 +205,7 @@ def norm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, *, bias: Option
          residual: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
          scale: Optional[torch.Tensor] = None, rows_per_batch: int = 0, eps: float = 1e-6,
          layernorm: bool = False, weight_plus_one: bool = False, emit_fp8: bool = False,
-         emit_bf16: bool = True):
+         emit_bf16: bool = True, fp8_tile_rows: int = 128):
     """(residual add +) RMSNorm / LayerNorm (+ affine) (+ AdaLN ``y * (1 + scale) + shift``).
 
     x [rows, dim] bf16. ``shift``/``scale`` are [batch, >= dim] with ``rows_per_batch`` rows
@@ -151,16 +218,18 @@ def norm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, *, bias: Option
         y = yf.to(x.dtype)
         fq = None
         if emit_fp8:
-            q, s = R.quant_fp8_act(y)
+            q, s = R.quant_fp8_act(y, pow2=fp8_mx())
             fq = Fp8Act(q, s)
         return (y if emit_bf16 else None), h, fq
     assert x.dtype == torch.bfloat16 and x.is_contiguous()
     y = torch.empty_like(x) if emit_bf16 else None
     h = torch.empty_like(x) if residual is not None else None
     q = s = None
+    mx = emit_fp8 and fp8_mx()
     if emit_fp8:
         q = torch.empty(rows, dim, dtype=torch.uint8, device=x.device)
-        s = torch.empty(rows, dim // 128, dtype=torch.float32, device=x.device)
+        s = _alloc_sf(rows, dim, fp8_tile_rows, x.device) if mx else \
+            torch.empty(rows, dim // 128, dtype=torch.float32, device=x.device)
     mod_stride = 0
     if shift is not None or scale is not None:
         ref = shift if shift is not None else scale
@@ -168,12 +237,15 @@ def norm(x: torch.Tensor, weight: Optional[torch.Tensor] = None, *, bias: Option
     rc = N.lib().b200_norm(x.data_ptr(), N.ptr(residual), N.ptr(h), N.ptr(weight), N.ptr(bias),
                            N.ptr(shift), N.ptr(scale), N.ptr(y), N.ptr(q), N.ptr(s), rows, dim,
                            rows_per_batch, mod_stride, eps, int(layernorm), int(weight_plus_one),
-                           N.stream())
+                           fp8_tile_rows if mx else 0, N.stream())
     N.check(rc, "b200_norm")
-    return y, h, (Fp8Act(q, s) if emit_fp8 else None)
+    if not emit_fp8:
+        return y, h, None
+    return y, h, (Fp8Act(q, None, s, fp8_tile_rows) if mx else Fp8Act(q, s))
 
 
-def glu(x: torch.Tensor, act: str = "silu", emit_fp8: bool = False, emit_bf16: bool = True):
+def glu(x: torch.Tensor, act: str = "silu", emit_fp8: bool = False, emit_bf16: bool = True,
+        fp8_tile_rows: int = 128):
     """act(x[:, :F]) * x[:, F:] for x [rows, 2F]. Returns (y bf16 or None, y_fp8 or None)."""
     rows, f2 = x.shape
     f = f2 // 2
@@ -181,18 +253,23 @@ def glu(x: torch.Tensor, act: str = "silu", emit_fp8: bool = False, emit_bf16: b
         y = R.glu(x, act).to(x.dtype)
         fq = None
         if emit_fp8:
-            q, s = R.quant_fp8_act(y)
+            q, s = R.quant_fp8_act(y, pow2=fp8_mx())
             fq = Fp8Act(q, s)
         return (y if emit_bf16 else None), fq
     assert x.is_contiguous() and x.dtype == torch.bfloat16
     y = torch.empty(rows, f, dtype=torch.bfloat16, device=x.device) if emit_bf16 else None
     q = s = None
+    mx = emit_fp8 and fp8_mx()
     if emit_fp8:
         q = torch.empty(rows, f, dtype=torch.uint8, device=x.device)
-        s = torch.empty(rows, f // 128, dtype=torch.float32, device=x.device)
-    rc = N.lib().b200_glu(x.data_ptr(), N.ptr(y), N.ptr(q), N.ptr(s), rows, f, 0 if act == "silu" else 1, N.stream())
+        s = _alloc_sf(rows, f, fp8_tile_rows, x.device) if mx else \
+            torch.empty(rows, f // 128, dtype=torch.float32, device=x.device)
+    rc = N.lib().b200_glu(x.data_ptr(), N.ptr(y), N.ptr(q), N.ptr(s), rows, f, 0 if act == "silu" else 1,
+                          fp8_tile_rows if mx else 0, N.stream())
     N.check(rc, "b200_glu")
-    return y, (Fp8Act(q, s) if emit_fp8 else None)
+    if not emit_fp8:
+        return y, None
+    return y, (Fp8Act(q, None, s, fp8_tile_rows) if mx else Fp8Act(q, s))
 
 
 def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, hq: int, hkv: int, d: int, *,
@@ -511,23 +588,25 @@ def grouped_linear(x, w: LinearWeight, groups: int, act: Optional[str] = None,
                 if isinstance(x, Fp8Act):
                     q, s = x.data[g * m:(g + 1) * m], x.scale[g * m:(g + 1) * m]
                 else:
-                    q, s = R.quant_fp8_act(xd[g * m:(g + 1) * m])
+                    q, s = R.quant_fp8_act(xd[g * m:(g + 1) * m], pow2=fp8_mx())
                 ys.append(R.linear(q, wg, sg, s, None, act, None, None))
             else:
                 ys.append(R.linear(xd[g * m:(g + 1) * m], wg, None, None, None, act, None, None))
         return torch.cat(ys)
     if w.is_fp8 and not isinstance(x, Fp8Act):
-        x = quant_fp8_act(x)
+        x = quant_fp8_act(x, tile_rows=m, mx=w.is_mx)
         xd = x.data
+    if w.is_mx and x.tile_rows != m:
+        raise ValueError("UE8M0 activations of a grouped GEMM need one scale-factor block per group")
     assert xd.is_contiguous() and w.weight.is_contiguous() and w.weight.shape[1] == k
     if out is None:
         out = torch.empty(groups * m, n, dtype=torch.bfloat16, device=xd.device)
     fp8 = w.is_fp8
     st = N.state(xd.device)
     ws = st.gemm_workspace()
+    xs_ptr, ws_ptr = _scale_ptrs(x, w)
     rc = N.lib().b200_gemm_grouped(xd.data_ptr(), w.weight.data_ptr(), out.data_ptr(), groups, m, n, k,
-                                   1 if fp8 else 0, x.scale.data_ptr() if fp8 else None,
-                                   w.scale.data_ptr() if fp8 else None, _ACT[act], N.ptr(counts),
+                                   _gemm_dtype(w), xs_ptr, ws_ptr, _ACT[act], N.ptr(counts),
                                    ws.data_ptr(), ws.numel(), st.status.data_ptr(), N.stream())
     N.check(rc, "b200_gemm_grouped")
     return out

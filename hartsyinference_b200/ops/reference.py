@@ -18,18 +18,52 @@ FP8_MAX = 448.0
 # --------------------------------------------------------------------------------------------
 # quantisation
 # --------------------------------------------------------------------------------------------
-def quant_fp8_act(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+def pow2_scale(amax: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= amax / 448 (UE8M0 scale), exponent clamped to [-126, 126]."""
+    m, ex = torch.frexp(amax.float() / FP8_MAX)          # value = m * 2^ex, m in [0.5, 1)
+    e = torch.where(m == 0.5, ex - 1, ex).clamp(-126, 126)
+    return torch.ldexp(torch.ones_like(m), e)
+
+
+def pack_sf(scale: torch.Tensor, tile_rows: int = 128) -> torch.Tensor:
+    """Power-of-two scales [rows, K/128] -> the blocked UE8M0 layout of the block-scaled GEMM:
+    int32 [row tiles, ceil(K/512), 128]; a tile covers ``tile_rows`` (<= 128) rows, row r of a tile
+    sits at word (r % 32) * 4 + r // 32 and K block kb at byte kb % 4 of the word."""
+    rows, kb = scale.shape
+    e = (torch.log2(scale.float()).round().to(torch.int32) + 127).clamp(0, 254).to(torch.uint8)
+    kg = (kb + 3) // 4
+    tiles = (rows + tile_rows - 1) // tile_rows
+    ep = torch.full((rows, kg * 4), 127, dtype=torch.uint8, device=scale.device)
+    ep[:, :kb] = e
+    out = torch.full((tiles, kg, 128, 4), 127, dtype=torch.uint8, device=scale.device)
+    r = torch.arange(rows, device=scale.device)
+    tile, rr = r // tile_rows, r % tile_rows
+    out[tile, :, (rr % 32) * 4 + rr // 32, :] = ep.reshape(rows, kg, 4)
+    return out.view(torch.int32).reshape(tiles, kg, 128)
+
+
+def unpack_sf(sf: torch.Tensor, rows: int, kb: int, tile_rows: int = 128) -> torch.Tensor:
+    """Inverse of :func:`pack_sf`: fp32 scales [rows, kb]."""
+    tiles, kg, _ = sf.shape
+    b = sf.contiguous().view(torch.uint8).reshape(tiles, kg, 128, 4)
+    r = torch.arange(rows, device=sf.device)
+    tile, rr = r // tile_rows, r % tile_rows
+    e = b[tile, :, (rr % 32) * 4 + rr // 32, :].reshape(rows, kg * 4)[:, :kb]
+    return torch.ldexp(torch.ones(rows, kb, device=sf.device), e.to(torch.int32) - 127)
+
+
+def quant_fp8_act(x: torch.Tensor, pow2: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """1x128 block quantisation of activations [M, K] -> (e4m3 bytes [M, K], scales [M, K/128])."""
     m, k = x.shape
     assert k % 128 == 0
     xf = x.float().reshape(m, k // 128, 128)
     amax = xf.abs().amax(dim=-1).clamp_min(1e-12)
-    scale = amax / FP8_MAX
+    scale = pow2_scale(amax) if pow2 else amax / FP8_MAX
     q = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q.reshape(m, k).view(torch.uint8), scale.contiguous()
 
 
-def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+def quant_fp8_weight(w: torch.Tensor, pow2: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """128x128 block quantisation of a weight [N, K] -> (bytes [N, K], scales [ceil(N/128), K/128])."""
     n, k = w.shape
     assert k % 128 == 0
@@ -38,7 +72,7 @@ def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     wf[:n] = w.float()
     blocks = wf.reshape(nb, 128, k // 128, 128)
     amax = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12)       # [nb, kb]
-    scale = amax / FP8_MAX
+    scale = pow2_scale(amax) if pow2 else amax / FP8_MAX
     q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     q = q.reshape(nb * 128, k)[:n]
     return q.contiguous().view(torch.uint8), scale.contiguous()

@@ -65,7 +65,7 @@ class FusedRowParallel:
         """All ranks call this together. Returns the reduced [m, n] bf16 result, a view of one of
         the heap's output buffers (valid until the buffer comes round again)."""
         if w.is_fp8 and not isinstance(x, Fp8Act):
-            x = ops.quant_fp8_act(x)
+            x = ops.quant_fp8_act(x, mx=w.is_mx)
         xd = x.data if isinstance(x, Fp8Act) else x
         m, k = xd.shape
         n = w.weight.shape[0]
@@ -74,7 +74,9 @@ class FusedRowParallel:
         fp8 = w.is_fp8
         st = N.state(self.device)
         rc = self._fn(xd.data_ptr(), w.weight.data_ptr(), m, n, k, xd.stride(0), w.weight.stride(0), n,
-                      1 if fp8 else 0, x.scale.data_ptr() if fp8 else None, w.scale.data_ptr() if fp8 else None,
+                      2 if w.is_mx else 1 if fp8 else 0,
+                      None if not fp8 else x.sf.data_ptr() if w.is_mx else x.scale.data_ptr(),
+                      None if not fp8 else w.sf.data_ptr() if w.is_mx else w.scale.data_ptr(),
                       N.ptr(w.bias), N.ptr(gate), N.ptr(residual), {None: 0, "gelu_tanh": 1, "silu": 2}[act],
                       self._stage, self._outs[slot], self._tile_flag, self._done, self._epoch, self._fin,
                       self.rank, self.world, self.budget_cycles, st.status.data_ptr(), N.stream())

@@ -38,7 +38,7 @@ def _grouped(argv):
     x = (torch.randn(groups * m, k, device="cuda") * 0.5).to(torch.bfloat16)
     w = (torch.randn(groups * n, k, device="cuda") * 0.1).to(torch.bfloat16)
     lw = ops.LinearWeight.from_dense(w, fp8=fp8)
-    xin = ops.quant_fp8_act(x) if fp8 else x
+    xin = ops.quant_fp8_act(x, tile_rows=m) if fp8 else x
     for _ in range(3):
         ops.grouped_linear(xin, lw, groups)
 

@@ -28,3 +28,12 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip_gpu)
         if "multigpu" in item.keywords and ngpu < 2:
             item.add_marker(skip_multi)
+
+
+@pytest.fixture
+def fp8_fp32_scales():
+    """Runs a test with fp32 block scales (epilogue promotion) instead of the default UE8M0 mode."""
+    from hartsyinference_b200 import config
+    config.set_override("fp8_scales", "fp32")
+    yield
+    config.set_override("fp8_scales", None)

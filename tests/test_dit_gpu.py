@@ -28,7 +28,7 @@ def _mv(v, dev):
     if isinstance(v, torch.Tensor):
         return v.to(dev)
     if isinstance(v, LinearWeight):
-        return LinearWeight(_mv(v.weight, dev), _mv(v.scale, dev), _mv(v.bias, dev))
+        return LinearWeight(_mv(v.weight, dev), _mv(v.scale, dev), _mv(v.bias, dev), _mv(v.sf, dev))
     if isinstance(v, (list, tuple)):
         return type(v)(_mv(x, dev) for x in v)
     if isinstance(v, dict):

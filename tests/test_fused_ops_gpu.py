@@ -27,7 +27,7 @@ def test_rmsnorm_residual(rows, dim):
     close(y2, R.norm(x, w, eps=1e-6)[0])
 
 
-def test_layernorm_modulate_and_fp8_emit():
+def test_layernorm_modulate_and_fp8_emit(fp8_fp32_scales):
     torch.manual_seed(1)
     rows, dim, batch = 96, 3072, 2
     x = torch.randn(rows, dim, device="cuda").to(torch.bfloat16)
@@ -43,7 +43,7 @@ def test_layernorm_modulate_and_fp8_emit():
     assert torch.allclose(q.scale, sr, rtol=1e-5)
 
 
-def test_glu_and_fp8():
+def test_glu_and_fp8(fp8_fp32_scales):
     torch.manual_seed(2)
     x = torch.randn(37, 2 * 4864, device="cuda").to(torch.bfloat16)
     y, _ = ops.glu(x, "silu")

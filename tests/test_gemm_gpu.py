@@ -73,7 +73,7 @@ def test_gemm_epilogue():
     (128, 128, 128), (256, 384, 512), (1000, 640, 1024), (4608, 3072, 3072),
     (1, 256, 256), (16, 512, 1024), (64, 1280, 8192), (40, 200, 512), (128, 1024, 2048),
 ])
-def test_gemm_fp8_blockscaled(m, n, k):
+def test_gemm_fp8_blockscaled(m, n, k, fp8_fp32_scales):
     torch.manual_seed(m + n + k)
     x = (torch.randn(m, k, device="cuda") * torch.rand(m, 1, device="cuda") * 2).to(torch.bfloat16)
     w = (torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16)
@@ -94,7 +94,7 @@ def test_gemm_fp8_blockscaled(m, n, k):
     assert _rel_err(y, full) < 0.08
 
 
-def test_gemm_fp8_splitk():
+def test_gemm_fp8_splitk(fp8_fp32_scales):
     torch.manual_seed(5)
     m, n, k = 64, 1024, 8192
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)

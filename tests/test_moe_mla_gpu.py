@@ -72,8 +72,8 @@ def test_grouped_gemm_matches_per_group_matmul(fp8, groups, m, n, k):
     lw = LinearWeight.from_dense(w, fp8=fp8)
     y = ops.grouped_linear(x, lw, groups)
     if fp8:
-        xq = ops.quant_fp8_act(x)
-        xr = R.dequant_fp8_act(xq.data.cpu(), xq.scale.cpu())
+        xq = ops.quant_fp8_act(x, tile_rows=m)
+        xr = R.dequant_fp8_act(xq.data.cpu(), xq.scales_fp32().cpu())
         wr = R.dequant_fp8_weight(lw.weight.cpu(), lw.scale.cpu())
     else:
         xr, wr = x.float().cpu(), w.float().cpu()

@@ -50,8 +50,9 @@ def test_noalloc_gemm_matches_regular_entry_twice(fp8):
         for call in range(2):
             out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
             rc = fn(xd.data_ptr(), lw.weight.data_ptr(), out.data_ptr(), m, n, k, xd.stride(0),
-                    lw.weight.stride(0), out.stride(0), 1 if fp8 else 0,
-                    xin.scale.data_ptr() if fp8 else None, lw.scale.data_ptr() if fp8 else None,
+                    lw.weight.stride(0), out.stride(0), (2 if lw.is_mx else 1) if fp8 else 0,
+                    (xin.sf if lw.is_mx else xin.scale).data_ptr() if fp8 else None,
+                    (lw.sf if lw.is_mx else lw.scale).data_ptr() if fp8 else None,
                     bias.data_ptr(), res.data_ptr(), stream)
             assert rc == 0, rc
             torch.cuda.synchronize()
