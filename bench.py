@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--bf16", action="store_true", help="debug only: bf16 weights instead of fp8")
     ap.add_argument("--no-fused-comm", action="store_true", help="NCCL all-reduce instead of the fused kernels")
+    ap.add_argument("--force-fused", action="store_true", help="keep the fused kernels even where GEMM + NCCL measures faster")
     ap.add_argument("--no-graphs", action="store_true")
     return ap.parse_args()
 
@@ -159,7 +160,8 @@ def main() -> int:
     if world > 1 and not args.no_fused_comm:
         try:
             from hartsyinference_b200.parallel.fused import enable_fused_tp
-            fused = enable_fused_tp(model, comm, max_tokens=max(args.batch, 128))
+            fused = enable_fused_tp(model, comm, max_tokens=max(args.batch, 128),
+                                    autotune_tokens=0 if args.force_fused else args.batch)
         except Exception as e:  # keep the run alive on NCCL, but say so
             log.warn(f"[Collective] fused TP kernels unavailable ({type(e).__name__}: {e}); using NCCL")
     torch.cuda.synchronize()

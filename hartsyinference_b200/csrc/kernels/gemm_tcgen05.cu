@@ -44,6 +44,8 @@ namespace b200 {
 //   tile_flag[r]  u32 [tiles_per_rank]: arrivals of partials, monotonic (world per call)
 //   done[r]       u32: reduced tiles that have landed in rank r's out, monotonic
 //   epoch / fin   local u32 counters: calls completed; CTAs finished in the current call
+constexpr uint32_t kArFlagUnits = 12;   // divisible by every allowed number of K splits
+
 struct AllReduceParams {
   __nv_bfloat16* stage[8];
   __nv_bfloat16* out[8];
@@ -53,6 +55,7 @@ struct AllReduceParams {
   uint32_t* fin;
   int rank, world, tiles_per_rank;
   long long wait_budget;   // cycles
+  int stage_splits;        // K splits the staging buffers have room for
 };
 
 struct GemmParams {
@@ -219,13 +222,15 @@ __device__ __forceinline__ void epilogue_barrier() {   // the 8 epilogue warps o
 // `b_end` is the end of the tile's B rows (a 16-row tile fills only half of a 32-column chunk; the
 // rest of the chunk is not this tile's data).
 __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[32], int a_row,
-                                            int b0, int b_end) {
+                                            int b0, int b_end, int split = 0) {
   if (a_row >= p.rows_a) return;
   if (p.ar.world > 0) {
+    // staging slot of this (rank, K split) at the owner of the tile's output columns
     const int ta = a_row >> 7;
     const int owner = ta / p.ar.tiles_per_rank, tl = ta % p.ar.tiles_per_rank;
+    const int slot = p.ar.rank * p.splits + split;
     __nv_bfloat16* dst = p.ar.stage[owner] +
-        (static_cast<long long>(p.ar.rank * p.ar.tiles_per_rank + tl) * 128 + b0) * 128 + (a_row & 127);
+        (static_cast<long long>(slot * p.ar.tiles_per_rank + tl) * 128 + b0) * 128 + (a_row & 127);
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (b0 + j < b_end) dst[j * 128] = __float2bfloat16(v[j]);
@@ -273,8 +278,9 @@ __device__ __forceinline__ void store_partial(const GemmParams& p, const float (
 template <int BN>
 __device__ __forceinline__ void emit_chunk(const GemmParams& p, const float (&v)[32], const WorkItem& it,
                                            int row_local, int chunk) {
-  if (it.slot >= 0) store_partial<BN>(p, v, row_local, chunk * 32, it);
-  else store_chunk(p, v, it.ta * kTileA + row_local, it.tb * BN + chunk * 32, min(p.rows_b, (it.tb + 1) * BN));
+  if (it.slot >= 0 && p.ar.world == 0) store_partial<BN>(p, v, row_local, chunk * 32, it);
+  else store_chunk(p, v, it.ta * kTileA + row_local, it.tb * BN + chunk * 32, min(p.rows_b, (it.tb + 1) * BN),
+                   it.split);
 }
 
 // Sums the partials of four consecutive weight rows (one 16-byte load per partial) of split tile
@@ -329,7 +335,9 @@ __device__ __forceinline__ void finish_item(const GemmParams& p, const WorkItem&
     epilogue_barrier();
     if (ok && et == 0) {
       const int owner = it.ta / p.ar.tiles_per_rank, tl = it.ta % p.ar.tiles_per_rank;
-      red_release_sys_add(p.ar.tile_flag[owner] + tl, 1u);
+      // arrivals are counted in twelfths so that a call adds the same total per tile whatever its
+      // number of K splits (1 to 4): the flags are cumulative over calls
+      red_release_sys_add(p.ar.tile_flag[owner] + tl, kArFlagUnits / static_cast<uint32_t>(p.splits));
     }
     return;
   }
@@ -353,7 +361,7 @@ __device__ __forceinline__ void finish_item(const GemmParams& p, const WorkItem&
   for (int e4 = et; e4 < BN * 32; e4 += 256) reduce_partials<4>(p, it, BN, e4);
 }
 
-// Owner side of the fused all-reduce: sum the `world` partials of tile `ta`, apply the epilogue,
+// Owner side of the fused all-reduce: sum the `world` x `splits` partials of tile `ta`, apply the epilogue,
 // write the result into every rank's output and count the tile as delivered there. Called by all
 // epilogue warps.
 __device__ __forceinline__ bool ar_reduce_tile(const GemmParams& p, int ta, uint32_t epoch,
@@ -361,7 +369,7 @@ __device__ __forceinline__ bool ar_reduce_tile(const GemmParams& p, int ta, uint
   const int et = threadIdx.x - 64;   // 0..255
   const int tl = ta % p.ar.tiles_per_rank;
   if (et == 0) {
-    const bool ok = wait_flag_geq(p.ar.tile_flag[p.ar.rank] + tl, epoch * p.ar.world, p.ar.wait_budget);
+    const bool ok = wait_flag_geq(p.ar.tile_flag[p.ar.rank] + tl, epoch * p.ar.world * kArFlagUnits, p.ar.wait_budget);
     if (!ok) report_status(p.status, kWaitTimeout, kKernelGemmAllReduce, 1, ta);
     *smem_flag = ok ? 1u : 0u;
   }
@@ -380,7 +388,7 @@ __device__ __forceinline__ bool ar_reduce_tile(const GemmParams& p, int ta, uint
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int s = 0; s < p.ar.world; ++s) {
+      for (int s = 0; s < p.ar.world * p.splits; ++s) {
         const uint4 raw = *reinterpret_cast<const uint4*>(st + s * src_stride + tok * 128 + f0);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
@@ -788,8 +796,10 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       // reduced tile of this call has landed in the local output.
       const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1u;
       for (long long w = blockIdx.x; w < work_items; w += gridDim.x) {
-        const int ta = static_cast<int>(w % tiles_a);
-        if (ta / p.ar.tiles_per_rank == p.ar.rank) ok &= ar_reduce_tile(p, ta, epoch, &bars->flag);
+        const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
+        // one CTA per tile reduces: the one that computed its first K range
+        if (it.split == 0 && it.ta / p.ar.tiles_per_rank == p.ar.rank)
+          ok &= ar_reduce_tile(p, it.ta, epoch, &bars->flag);
       }
       if (threadIdx.x == 64) {
         if (!wait_flag_geq(p.ar.done[p.ar.rank], epoch * static_cast<uint32_t>(tiles_a), p.ar.wait_budget))
@@ -935,7 +945,14 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     if (m > 128 || n % (128 * ar->world) != 0) return -6;   // one token tile; whole tiles per owner
     p.ar = *ar;
     p.ar.tiles_per_rank = n / 128 / ar->world;
-    splits = 1;
+    // K splits fill the machine when there are fewer tiles than SMs; every (rank, split) pair has
+    // its own staging slot at the owner, so the limit is what the caller's staging buffer holds
+    int s_ar = num_sms() / (n / 128);
+    if (s_ar > ar->stage_splits) s_ar = ar->stage_splits;
+    if (s_ar > 4) s_ar = 4;
+    const int kb_all = (k + kelems - 1) / kelems;
+    if (s_ar > kb_all / 4) s_ar = kb_all / 4;
+    splits = s_ar < 1 ? 1 : s_ar;
   }
 
   int bn;
@@ -1007,7 +1024,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   s_eff = (total_kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;
   if (s_eff <= 1) { first_split = tiles; s_eff = 1; p.kblocks_per_split = total_kblocks; }
   const int split_tiles = tiles - first_split;
-  if (split_tiles > 0) {
+  if (split_tiles > 0 && ar == nullptr) {
     const long long need = kSplitCounterBytes + static_cast<long long>(split_tiles) * s_eff * slot_bytes;
     if (workspace == nullptr || need > workspace_bytes || split_tiles > 4096) {
       if (splits > 1) return -5;                     // forced split without room: say so
@@ -1120,7 +1137,7 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
                                  const float* w_scale, const void* bias, const void* gate,
                                  const void* residual, int act, void* const* stage,
                                  void* const* out, void* const* tile_flag, void* const* done,
-                                 void* epoch, void* fin, int rank, int world,
+                                 void* epoch, void* fin, int rank, int world, int stage_splits,
                                  long long wait_budget_cycles, void* status, cudaStream_t stream) {
   if (world < 1 || world > 8) return -7;
   AllReduceParams ar{};
@@ -1134,6 +1151,7 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
   ar.fin = static_cast<uint32_t*>(fin);
   ar.rank = rank;
   ar.world = world;
+  ar.stage_splits = stage_splits < 1 ? 1 : stage_splits;
   ar.wait_budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
   return gemm_impl(x, w, out[rank], m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, gate,
                    residual, act, 1, nullptr, 0, status, stream, &ar);

@@ -26,6 +26,7 @@ from .comm import Comm
 from .symm import SymmetricHeap
 
 MAX_TOKENS = 128
+STAGE_SPLITS = 4      # K splits per rank that the staging buffer has slots for
 
 
 class FusedRowParallel:
@@ -36,7 +37,7 @@ class FusedRowParallel:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.max_features = max_features
         tiles = (max_features + 127) // 128
-        stage_bytes = tiles * 128 * 128 * 2            # [world][tiles/world][128][128] bf16
+        stage_bytes = STAGE_SPLITS * tiles * 128 * 128 * 2   # [world * splits][tiles/world][128][128] bf16
         out_bytes = MAX_TOKENS * max_features * 2
         flags_bytes = 4096
         self.heap = SymmetricHeap(comm, stage_bytes + num_out_buffers * out_bytes + flags_bytes + 4096, self.device)
@@ -54,7 +55,7 @@ class FusedRowParallel:
         vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
         self._fn = N.bind("b200_gemm_allreduce", i32,
                           [vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, vp, vp, i32,
-                           vp, vp, vp, vp, vp, vp, i32, i32, i64, vp, vp])
+                           vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, vp, vp])
         self.budget_cycles = int(config.get("wait_budget_ms")) * 2_000_000
 
     def supports(self, m: int, n: int) -> bool:
@@ -79,7 +80,7 @@ class FusedRowParallel:
                       None if not fp8 else w.sf.data_ptr() if w.is_mx else w.scale.data_ptr(),
                       N.ptr(w.bias), N.ptr(gate), N.ptr(residual), {None: 0, "gelu_tanh": 1, "silu": 2}[act],
                       self._stage, self._outs[slot], self._tile_flag, self._done, self._epoch, self._fin,
-                      self.rank, self.world, self.budget_cycles, st.status.data_ptr(), N.stream())
+                      self.rank, self.world, STAGE_SPLITS, self.budget_cycles, st.status.data_ptr(), N.stream())
         N.check(rc, "b200_gemm_allreduce")
         return self.heap.tensor(self.off_out[slot], (m, n), torch.bfloat16)
 
@@ -87,8 +88,10 @@ class FusedRowParallel:
         self.heap.close()
 
 
-def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS) -> bool:
+def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_tokens: int = 0) -> bool:
     """Route the model's row-parallel linears through the fused kernel when the shapes allow it.
+    With ``autotune_tokens`` > 0 the fused kernel and GEMM + NCCL all-reduce are both timed on this
+    model's o / down projections at that token count and the faster one is kept.
     Returns True when the fused path is active."""
     if comm.world <= 1 or not config.get("fused_comm") or config.get("p2p_disable"):
         return False
@@ -107,5 +110,62 @@ def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS) -> bool:
 
     model.row_parallel_linear = row_parallel
     model._fused_tp = fused
+    if autotune_tokens > 0 and model.layers:
+        t_fused, t_nccl = _measure_row_parallel(model, comm, fused, autotune_tokens)
+        if t_fused > t_nccl:
+            model.row_parallel_linear = None
+            log.decision("TensorParallel", f"fused GEMM+all-reduce off: {t_fused * 1e3:.1f} us per layer against "
+                                           f"{t_nccl * 1e3:.1f} us for GEMM + NCCL at {autotune_tokens} tokens (tp={comm.world})")
+            return False
+        log.decision("TensorParallel", f"fused GEMM+all-reduce on for <= {MAX_TOKENS} tokens (tp={comm.world}): "
+                                       f"{t_fused * 1e3:.1f} us per layer against {t_nccl * 1e3:.1f} us for GEMM + NCCL")
+        return True
     log.decision("TensorParallel", f"fused GEMM+all-reduce on for <= {MAX_TOKENS} tokens (tp={comm.world})")
     return True
+
+
+def _measure_row_parallel(model, comm: Comm, fused: FusedRowParallel, tokens: int) -> tuple[float, float]:
+    """Device time (ms, summed over ranks so that every rank decides alike) of the two row-parallel
+    linears of one layer through the fused kernel and through GEMM + NCCL all-reduce."""
+    lw = next((l for l in model.layers if l.o is not None and l.down is not None), None)
+    if lw is None:
+        return 0.0, 1.0
+    dev = model.device
+    xs = [torch.randn(tokens, w.in_features, device=dev).to(torch.bfloat16) * 0.1 for w in (lw.o, lw.down)]
+    ws = (lw.o, lw.down)
+
+    def run_fused():
+        for x, w in zip(xs, ws):
+            fused(x, w)
+
+    def run_nccl():
+        for x, w in zip(xs, ws):
+            comm.all_reduce(ops.linear(x, w))
+
+    # Both candidates are timed as CUDA-graph replays, the way the decode step runs them, so that
+    # host launch overhead (which differs: one launch against three) does not decide.
+    times = []
+    inner, reps = 8, 5
+    for fn in (run_fused, run_nccl):
+        for _ in range(3):
+            fn()
+        comm.barrier()
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+        graph.replay()
+        comm.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        times.append(e0.elapsed_time(e1) / (inner * reps))
+        del graph
+    t = torch.tensor(times, device=dev, dtype=torch.float32)
+    t = comm.all_reduce(t)
+    return float(t[0].item()), float(t[1].item())
