@@ -199,4 +199,90 @@ def make_scheduler(name: str, steps: int, **kw):
         return EulerDiscreteScheduler(steps, **kw)
     if name == "ddim":
         return DDIMScheduler(steps, **kw)
+    if name in ("dpm++2m", "dpmpp_2m", "dpm_solver_multistep"):
+        return DPMSolverMultistepScheduler(steps, **kw)
+    if name == "lcm":
+        return LCMScheduler(steps, **kw)
     raise ValueError(f"unknown scheduler '{name}'")
+
+
+class DPMSolverMultistepScheduler:
+    """DPM-Solver++ (2M) for epsilon- or v-prediction models on the scaled-linear beta schedule:
+    data prediction ``x0``, half log-SNR ``lambda = log(alpha / sigma)``, second-order multistep
+    update with a first-order first and last step
+    (src/HartsyInference.Diffusion/Schedulers/DpmSolverMultistepScheduler.cs)."""
+
+    def __init__(self, num_steps: int, beta_start: float = 0.00085, beta_end: float = 0.012, train_steps: int = 1000,
+                 prediction: str = "epsilon"):
+        betas = torch.linspace(beta_start ** 0.5, beta_end ** 0.5, train_steps, dtype=torch.float64) ** 2
+        ac = torch.cumprod(1 - betas, 0)
+        ts = torch.linspace(train_steps - 1, 0, num_steps + 1, dtype=torch.float64).round().long()[:-1]
+        self.timesteps = ts
+        a = ac[ts] ** 0.5
+        s = (1 - ac[ts]) ** 0.5
+        self.alpha = torch.cat([a, torch.ones(1, dtype=torch.float64)])
+        self.sigma = torch.cat([s, torch.zeros(1, dtype=torch.float64)])
+        self.lam = torch.log(self.alpha.clamp_min(1e-20)) - torch.log(self.sigma.clamp_min(1e-20))
+        self.prediction = prediction
+        self.num_steps = num_steps
+        self._prev_x0: Optional[torch.Tensor] = None
+
+    def timestep(self, i: int) -> float:
+        return float(self.timesteps[i])
+
+    def _x0(self, out: torch.Tensor, x: torch.Tensor, i: int) -> torch.Tensor:
+        a, s = float(self.alpha[i]), float(self.sigma[i])
+        if self.prediction == "v_prediction":
+            return a * x - s * out
+        return (x - s * out) / a
+
+    def step(self, out: torch.Tensor, i: int, x: torch.Tensor) -> torch.Tensor:
+        x0 = self._x0(out.float(), x.float(), i)
+        a_n, s_n, s_c = float(self.alpha[i + 1]), float(self.sigma[i + 1]), float(self.sigma[i])
+        last = i == self.num_steps - 1
+        if last:
+            self._prev_x0 = None
+            return x0.to(x.dtype)                       # sigma_next = 0: the sample is the data prediction
+        h = float(self.lam[i + 1] - self.lam[i])
+        if self._prev_x0 is None or i == self.num_steps - 2:
+            d = x0                                      # first-order (also "lower order final")
+        else:
+            h0 = float(self.lam[i] - self.lam[i - 1])
+            r = h0 / h
+            d = x0 + (x0 - self._prev_x0) / (2 * r)
+        self._prev_x0 = x0
+        return ((s_n / s_c) * x.float() - a_n * math.expm1(-h) * d).to(x.dtype)
+
+
+class LCMScheduler:
+    """Latent-consistency sampling: predict x0, then re-noise to the next timestep (the last step
+    returns x0). Boundary-condition scalings ``c_skip`` / ``c_out`` with sigma_data 0.5 and
+    timestep scaling 10 (src/HartsyInference.Diffusion/Schedulers/LcmScheduler.cs)."""
+
+    def __init__(self, num_steps: int, beta_start: float = 0.00085, beta_end: float = 0.012, train_steps: int = 1000,
+                 original_steps: int = 50, seed: int = 0):
+        betas = torch.linspace(beta_start ** 0.5, beta_end ** 0.5, train_steps, dtype=torch.float64) ** 2
+        self.ac = torch.cumprod(1 - betas, 0)
+        k = train_steps // original_steps
+        lcm_ts = (torch.arange(1, original_steps + 1) * k - 1).flip(0)
+        idx = torch.linspace(0, original_steps, num_steps + 1).floor().long()[:-1]
+        self.timesteps = lcm_ts[idx]
+        self.num_steps = num_steps
+        self.gen = torch.Generator().manual_seed(seed)
+
+    def timestep(self, i: int) -> float:
+        return float(self.timesteps[i])
+
+    def step(self, eps: torch.Tensor, i: int, x: torch.Tensor) -> torch.Tensor:
+        t = int(self.timesteps[i])
+        a_t = float(self.ac[t])
+        x0 = (x.float() - (1 - a_t) ** 0.5 * eps.float()) / a_t ** 0.5
+        sd, ts = 0.5, t * 10.0
+        c_skip = sd * sd / (ts * ts + sd * sd)
+        c_out = ts / (ts * ts + sd * sd) ** 0.5
+        den = c_out * x0 + c_skip * x.float()
+        if i == self.num_steps - 1:
+            return den.to(x.dtype)
+        a_p = float(self.ac[int(self.timesteps[i + 1])])
+        noise = torch.randn(x.shape, generator=self.gen, dtype=torch.float32).to(x.device)
+        return (a_p ** 0.5 * den + (1 - a_p) ** 0.5 * noise).to(x.dtype)

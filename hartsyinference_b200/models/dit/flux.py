@@ -203,10 +203,12 @@ class FluxTransformer:
 
     def forward(self, img: torch.Tensor, txt: torch.Tensor, timestep: torch.Tensor, pooled: torch.Tensor,
                 img_ids: torch.Tensor, txt_ids: torch.Tensor, guidance: Optional[torch.Tensor] = None,
-                hidden_in: Optional[tuple] = None):
+                hidden_in: Optional[tuple] = None, step_cache=None):
         """img [B, S_i, C_in] packed latents, txt [B, S_t, context_dim], timestep (sigma) [B],
         pooled [B, pooled_dim], ids [S, 3]. Returns the velocity prediction [B, S_i, C_in] (bf16), or
-        the (img, txt | joint) hidden state when this instance holds only a block range."""
+        the (img, txt | joint) hidden state when this instance holds only a block range.
+        ``step_cache`` (a :class:`~.step_cache.FirstBlockCache`, whole-model instances only): after the
+        first block decide whether the rest of the stack can be replaced by last step's residual."""
         cfg = self.cfg
         B, S_i = img.shape[0], img.shape[1]
         S_t = txt.shape[1]
@@ -241,7 +243,13 @@ class FluxTransformer:
             y = self._reduce(ops.linear(h, w.mlp_out))
             return self._gated_add(x, y, mod[:, 5 * H:6 * H], S)
 
-        for wi, wt in self.double:
+        whole = self.block_range == (0, cfg.num_double_blocks + cfg.num_single_blocks)
+        use_cache = step_cache is not None and step_cache.enabled and whole and len(self.double) > 0
+        first_x_i = None
+        skip_rest = False
+        for bi, (wi, wt) in enumerate(self.double):
+            if skip_rest:
+                break
             mod_i, mod_t = modulation(temb_act, wi.mod), modulation(temb_act, wt.mod)
             qi, ki, vi = stream_pre(x_i, wi, mod_i, S_i, cos_i, sin_i)
             qt, kt, vt = stream_pre(x_t, wt, mod_t, S_t, cos_t, sin_t)
@@ -259,8 +267,13 @@ class FluxTransformer:
                 a_i = torch.cat([att[i * S + S_t:(i + 1) * S] for i in range(B)], 0)
             x_i = stream_post(x_i, a_i.contiguous(), wi, mod_i, S_i)
             x_t = stream_post(x_t, a_t.contiguous(), wt, mod_t, S_t)
+            if use_cache and bi == 0:
+                first_x_i = x_i
+                if not step_cache.should_compute(x_i):
+                    x_i = step_cache.apply_residual(x_i)
+                    skip_rest = True
 
-        if self.single or self.block_range[1] > cfg.num_double_blocks:
+        if not skip_rest and (self.single or self.block_range[1] > cfg.num_double_blocks):
             S = S_t + S_i
             if joint is None:
                 if B == 1:
@@ -287,6 +300,8 @@ class FluxTransformer:
                     x_i = torch.cat([joint[i * S + S_t:(i + 1) * S] for i in range(B)], 0)
         if self.block_range[1] != cfg.num_double_blocks + cfg.num_single_blocks:
             return x_i, x_t, joint
+        if use_cache and not skip_rest:
+            step_cache.store_residual(first_x_i, x_i)
         mo = ops.linear(temb_act, self.norm_out)                              # [B, 2H]: scale, shift
         xn, _, _ = ops.norm(x_i.contiguous(), None, shift=mo[:, H:2 * H], scale=mo[:, 0:H], rows_per_batch=S_i, layernorm=True)
         out = ops.linear(xn, self.proj_out)

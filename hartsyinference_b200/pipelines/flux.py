@@ -77,7 +77,7 @@ class FluxPipeline:
     @torch.no_grad()
     def denoise(self, ctx: torch.Tensor, pooled: torch.Tensor, height: int, width: int, steps: int, guidance: float,
                 seed: int, neg: Optional[tuple[torch.Tensor, torch.Tensor]] = None, cfg_scale: float = 1.0,
-                on_step: Optional[Callable[[StepPreview], None]] = None, step_cache_threshold: float = 0.0,
+                on_step: Optional[Callable[[StepPreview], None]] = None, step_cache_threshold: float = 0.0, first_block_cache: float = 0.0,
                 latents: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Returns the final latents [1, C, H/8, W/8] fp32 on the device."""
         tr = self.c.transformer
@@ -98,6 +98,9 @@ class FluxPipeline:
             branch = self.cfg_comm.rank                                           # 0 = cond, 1 = uncond
         cache_prev_t: Optional[torch.Tensor] = None
         cache_v: Optional[torch.Tensor] = None
+        # first-block cache: one per CFG branch, decided inside the transformer after block 0
+        from ..models.dit.step_cache import FirstBlockCache
+        fbc = [FirstBlockCache(first_block_cache), FirstBlockCache(first_block_cache)] if first_block_cache > 0 else [None, None]
         self.last_step_ms = []
         use_cuda = dev.type == "cuda"
         for i in range(steps):
@@ -116,11 +119,12 @@ class FluxPipeline:
             else:
                 xin = x.to(torch.bfloat16)
                 if branch is None:
-                    v_cond = tr.forward(xin, ctx_d, sigma, pooled_d, img_ids, txt_ids, gvec)
-                    v_unc = tr.forward(xin, neg[0].to(dev)[None], sigma, neg[1].to(dev)[None], img_ids, txt_ids, gvec) if true_cfg else None
+                    v_cond = tr.forward(xin, ctx_d, sigma, pooled_d, img_ids, txt_ids, gvec, step_cache=fbc[0])
+                    v_unc = tr.forward(xin, neg[0].to(dev)[None], sigma, neg[1].to(dev)[None], img_ids, txt_ids, gvec,
+                                       step_cache=fbc[1]) if true_cfg else None
                 else:
                     c_in, p_in = (ctx_d, pooled_d) if branch == 0 else (neg[0].to(dev)[None], neg[1].to(dev)[None])
-                    mine = tr.forward(xin, c_in, sigma, p_in, img_ids, txt_ids, gvec).contiguous()
+                    mine = tr.forward(xin, c_in, sigma, p_in, img_ids, txt_ids, gvec, step_cache=fbc[0]).contiguous()
                     both = self.cfg_comm.all_gather(mine[None], dim=0)             # [2, 1, S, C]
                     v_cond, v_unc = both[0].contiguous(), both[1].contiguous()
                 if step_cache_threshold > 0:
