@@ -94,8 +94,11 @@ class LayerWeights:
 
 class DecoderModel:
     def __init__(self, cfg: TransformerConfig, device: torch.device | str = "cpu", comm: Optional[Comm] = None,
-                 fp8: bool = False):
+                 fp8: bool = False, layer_range: Optional[tuple[int, int]] = None):
         self.cfg = cfg
+        # pipeline stage: this instance holds layers [layer0, layer1) only (all of them by default)
+        self.layer0, self.layer1 = layer_range if layer_range is not None else (0, cfg.num_layers)
+        self.first_stage, self.last_stage = self.layer0 == 0, self.layer1 == cfg.num_layers
         self.device = torch.device(device)
         self.comm = comm or SingleComm()
         self.tp = self.comm.world
@@ -158,7 +161,7 @@ class DecoderModel:
         self.final_norm = need("model.norm.weight").to(dt).to(self.device)
         kvs = self.kv_head_slice()
         self.layers = []
-        for i in range(cfg.num_layers):
+        for i in range(self.layer0, self.layer1):
             p = f"model.layers.{i}."
             is_moe = cfg.moe is not None and cfg.moe.num_experts > 0 and i >= cfg.moe.first_dense_layers
             lw = LayerWeights(
@@ -295,6 +298,10 @@ class DecoderModel:
         self.final_norm = ones(cfg.hidden_size)
         self.layers = []
         for li in range(cfg.num_layers):
+            if not (self.layer0 <= li < self.layer1):
+                counter[0] += 64          # keep the remaining layers' seeds independent of the stage split
+                continue
+            counter[0] = (seed * 1000003 + self.tp_rank * 7919) + 1000 + li * 64
             is_moe = cfg.moe is not None and cfg.moe.num_experts > 0 and li >= cfg.moe.first_dense_layers
             lw = LayerWeights(
                 in_norm=ones(cfg.hidden_size),
@@ -368,18 +375,18 @@ class DecoderModel:
     # ------------------------------------------------------------------------------ KV cache
     def kv_bytes_per_page(self, page: int) -> int:
         if self.cfg.mla is not None:
-            return self.cfg.num_layers * page * (self.cfg.mla.kv_lora_rank + self.cfg.mla.qk_rope_head_dim) * 2
-        return self.cfg.num_layers * 2 * self.hkv * page * self.cfg.head_dim * 2
+            return (self.layer1 - self.layer0) * page * (self.cfg.mla.kv_lora_rank + self.cfg.mla.qk_rope_head_dim) * 2
+        return (self.layer1 - self.layer0) * 2 * self.hkv * page * self.cfg.head_dim * 2
 
     def alloc_kv(self, num_pages: int, page: int = 16) -> torch.Tensor:
         """[layers, 2, pages, hkv_local, page, head_dim] bf16, or with multi-head latent attention
         [layers, pages, page, 576] (latent + rotated shared key, replicated on every rank)."""
         if self.cfg.mla is not None:
             row = self.cfg.mla.kv_lora_rank + self.cfg.mla.qk_rope_head_dim
-            self.kv_cache = torch.zeros(self.cfg.num_layers, num_pages, page, row, dtype=torch.bfloat16,
+            self.kv_cache = torch.zeros(self.layer1 - self.layer0, num_pages, page, row, dtype=torch.bfloat16,
                                         device=self.device)
             return self.kv_cache
-        self.kv_cache = torch.zeros(self.cfg.num_layers, 2, num_pages, self.hkv, page, self.cfg.head_dim,
+        self.kv_cache = torch.zeros(self.layer1 - self.layer0, 2, num_pages, self.hkv, page, self.cfg.head_dim,
                                     dtype=torch.bfloat16, device=self.device)
         return self.kv_cache
 
@@ -395,16 +402,20 @@ class DecoderModel:
         y = ops.linear(x, w)
         return self.all_reduce(y) if self.tp > 1 else y
 
-    def forward_hidden(self, batch: ForwardBatch) -> torch.Tensor:
-        """Runs all layers; returns the final-normed hidden states [T, H]."""
+    def forward_hidden(self, batch: ForwardBatch, hidden_in: Optional[tuple] = None):
+        """Runs this instance's layers. The last pipeline stage (the only one by default) returns the
+        final-normed hidden states [T, H]; an earlier stage returns ``(x, residual)`` for the next
+        stage, which receives it as ``hidden_in``."""
         cfg = self.cfg
         d = cfg.head_dim
-        if batch.embeds is not None:
+        res: Optional[torch.Tensor] = None
+        if hidden_in is not None:
+            x, res = hidden_in
+        elif batch.embeds is not None:
             x = batch.embeds
         else:
             x = ops.embedding(batch.tokens, self.embed, cfg.embed_scale * cfg.embedding_multiplier)
         t = x.shape[0]
-        res: Optional[torch.Tensor] = None
         scale = self._attn_scale()
         fp8 = self.fp8 and x.is_cuda
         for li, lw in enumerate(self.layers):
@@ -426,7 +437,7 @@ class DecoderModel:
                                       slot_mapping=batch.slot_mapping, rot=cfg.rotary_dim, theta=cfg.rope_theta,
                                       inv_freq=self.inv_freq, style=cfg.rope_style, q_norm_w=lw.q_norm,
                                       k_norm_w=lw.k_norm, eps=cfg.rms_eps)
-                window = cfg.layer_window(li)
+                window = cfg.layer_window(self.layer0 + li)
                 if batch.is_decode:
                     att = ops.attn_decode(q, kc, vc, batch.block_table, batch.kv_lens, scale=scale,
                                           softcap=cfg.attn_softcap, window=window,
@@ -459,6 +470,8 @@ class DecoderModel:
             if cfg.residual_multiplier != 1.0:
                 f = (f.float() * cfg.residual_multiplier).to(f.dtype)
             x = f
+        if not self.last_stage:
+            return x, res
         out, _, _ = ops.norm(x, self.final_norm, residual=res, eps=cfg.rms_eps, weight_plus_one=cfg.norm_plus_one)
         return out
 

@@ -53,6 +53,22 @@ def main():
     (ls, ts), (lt, tt) = run(single), run(tp)
     assert cos(ls, lt) > 0.999, cos(ls, lt)
     assert int(ts) == int(tt) or abs(float(ls[-1, int(ts)]) - float(ls[-1, int(tt)])) < 0.05
+    # ---- layer-split pipeline vs single: stage 0 holds layer 0, stage 1 layer 1 + head; generation
+    # through one engine per stage gives the single-process tokens
+    from hartsyinference_b200.engine import LLMEngine, SamplingParams
+    from hartsyinference_b200.parallel.pipeline import PipelinedModel, split_layers
+    assert split_layers(7, 3, [1, 1, 2]) == [(0, 2), (2, 4), (4, 7)]
+    pp = PipelinedModel(cfg, comm, "cpu")
+    pp.load_state_dict(full.get)
+    assert len(pp.model.layers) == 1
+    lp, tpk = run(pp)
+    assert cos(ls, lp) > 0.9999, cos(ls, lp)
+    assert int(tpk) == int(ts)
+    prompts = [toks.tolist(), toks[:7].tolist()]
+    sp = SamplingParams(greedy=True, max_tokens=6, ignore_eos=True)
+    ref_out = LLMEngine(single, num_pages=16, page_size=16, max_batch=4, prefill_chunk=64, max_model_len=64).generate(prompts, sp)
+    pp_out = LLMEngine(pp, num_pages=16, page_size=16, max_batch=4, prefill_chunk=64, max_model_len=64).generate(prompts, sp)
+    assert pp_out == ref_out, (pp_out, ref_out)
     # ---- TP Flux vs single (same seed => same full weights, sharded per rank)
     fcfg = F.tiny_flux(num_heads=4, head_dim=32)
     gi = torch.Generator().manual_seed(5)
