@@ -309,3 +309,105 @@ class ByteTokenizer(Tokenizer):
                 toks += [b""] * (i + 1 - len(toks))
             toks[i] = s.encode()
         super().__init__("bpe", toks, merges=[], special_tokens=specials or {}, pattern=r"(?s).")
+
+
+class WordPieceTokenizer:
+    """BERT WordPiece: lower-casing / accent stripping (optional), whitespace + punctuation
+    pre-tokenisation, greedy longest-match-first pieces with the ``##`` continuation prefix,
+    ``[CLS] ... [SEP]`` framing. Loads ``vocab.txt`` or a ``tokenizer.json`` whose model type is
+    WordPiece (reference: the BERT tokenizer under src/HartsyInference.ModelAssets/Tokenizers/)."""
+
+    def __init__(self, vocab: list[str], lower: bool = True, unk: str = "[UNK]", cls: str = "[CLS]", sep: str = "[SEP]",
+                 max_word_chars: int = 100):
+        self.vocab = vocab
+        self.index = {t: i for i, t in enumerate(vocab)}
+        self.lower = lower
+        self.unk_id = self.index.get(unk, 0)
+        self.cls_id = self.index.get(cls)
+        self.sep_id = self.index.get(sep)
+        self.max_word_chars = max_word_chars
+
+    @staticmethod
+    def from_dir(path) -> "WordPieceTokenizer":
+        import json
+        from pathlib import Path
+        p = Path(path)
+        lower = True
+        cfg = p / "tokenizer_config.json"
+        if cfg.exists():
+            lower = bool(json.loads(cfg.read_text()).get("do_lower_case", True))
+        if (p / "vocab.txt").exists():
+            vocab = (p / "vocab.txt").read_text(encoding="utf-8").split("\n")
+            if vocab and vocab[-1] == "":
+                vocab.pop()
+            return WordPieceTokenizer(vocab, lower)
+        tj = json.loads((p / "tokenizer.json").read_text(encoding="utf-8"))
+        if tj.get("model", {}).get("type") != "WordPiece":
+            raise ValueError("tokenizer.json does not hold a WordPiece model")
+        items = sorted(tj["model"]["vocab"].items(), key=lambda kv: kv[1])
+        norm = tj.get("normalizer") or {}
+        return WordPieceTokenizer([k for k, _ in items], bool(norm.get("lowercase", True)))
+
+    @staticmethod
+    def _is_punct(ch: str) -> bool:
+        import unicodedata
+        cp = ord(ch)
+        if 33 <= cp <= 47 or 58 <= cp <= 64 or 91 <= cp <= 96 or 123 <= cp <= 126:
+            return True
+        return unicodedata.category(ch).startswith("P")
+
+    def _basic(self, text: str) -> list[str]:
+        import unicodedata
+        if self.lower:
+            text = unicodedata.normalize("NFD", text.lower())
+            text = "".join(c for c in text if unicodedata.category(c) != "Mn")
+        words, cur = [], []
+        for ch in text:
+            if ch.isspace():
+                if cur:
+                    words.append("".join(cur)); cur = []
+            elif self._is_punct(ch) or 0x4E00 <= ord(ch) <= 0x9FFF:
+                if cur:
+                    words.append("".join(cur)); cur = []
+                words.append(ch)
+            else:
+                cur.append(ch)
+        if cur:
+            words.append("".join(cur))
+        return words
+
+    def _pieces(self, word: str) -> list[int]:
+        if len(word) > self.max_word_chars:
+            return [self.unk_id]
+        out, start = [], 0
+        while start < len(word):
+            end, cur = len(word), None
+            while start < end:
+                sub = word[start:end] if start == 0 else "##" + word[start:end]
+                if sub in self.index:
+                    cur = self.index[sub]
+                    break
+                end -= 1
+            if cur is None:
+                return [self.unk_id]
+            out.append(cur)
+            start = end
+        return out
+
+    def encode(self, text: str, add_special: bool = True) -> list[int]:
+        ids = [i for w in self._basic(text) for i in self._pieces(w)]
+        if add_special and self.cls_id is not None and self.sep_id is not None:
+            return [self.cls_id] + ids + [self.sep_id]
+        return ids
+
+    def decode(self, ids) -> str:
+        out = []
+        for i in ids:
+            t = self.vocab[i] if 0 <= i < len(self.vocab) else ""
+            if t in ("[CLS]", "[SEP]", "[PAD]"):
+                continue
+            if t.startswith("##") and out:
+                out[-1] += t[2:]
+            else:
+                out.append(t)
+        return " ".join(out)

@@ -101,7 +101,9 @@ class InferenceEngine:
 
     @property
     def embeddings(self):
-        return self.text
+        """Encoder checkpoints (BERT family) get their own service; decoder checkpoints are embedded
+        by the text service."""
+        return _EmbeddingsRouter(self)
 
     @property
     def images(self):
@@ -170,3 +172,17 @@ class InferenceEngine:
     def close(self) -> None:
         self.release_loaded()
         self._services.clear()
+
+
+class _EmbeddingsRouter:
+    def __init__(self, engine: "InferenceEngine"):
+        self._engine = engine
+
+    def embed(self, spec, texts):
+        from .embeddings_service import BertEmbeddingsService, is_bert_dir
+        eng = self._engine
+        path = spec.local_path or spec.requested
+        if is_bert_dir(path):
+            svc = eng._service("bert_embeddings", lambda: BertEmbeddingsService(eng.device))
+            return svc.embed(spec, texts)
+        return eng.text.embed(spec, texts)

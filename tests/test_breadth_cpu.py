@@ -112,3 +112,68 @@ def test_first_block_cache_skips_small_changes_and_bounds_the_run():
     assert c.skipped == 2 and c.computed == 2
     off = FirstBlockCache(0.0)
     assert off.should_compute(first) and off.should_compute(first)
+
+
+def test_bert_encoder_matches_transformers_bert():
+    import transformers
+    from hartsyinference_b200.models.encoders.bert import BertEncoder, tiny_bert
+    cfg = tiny_bert()
+    hf_cfg = transformers.BertConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden, num_hidden_layers=cfg.layers,
+                                     num_attention_heads=cfg.heads, intermediate_size=cfg.intermediate,
+                                     max_position_embeddings=cfg.max_len, type_vocab_size=cfg.type_vocab,
+                                     layer_norm_eps=cfg.eps, hidden_act="gelu")
+    torch.manual_seed(0)
+    hf = transformers.BertModel(hf_cfg, add_pooling_layer=False).eval()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    enc = BertEncoder(cfg, "cpu", get=lambda n: sd.get(n))
+    ids = torch.randint(0, cfg.vocab_size, (11,))
+    ours = enc.hidden_states(ids).float()
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).last_hidden_state[0]
+    cos = torch.nn.functional.cosine_similarity(ours, ref, dim=-1)
+    assert cos.min() > 0.995, cos.min()
+    e = enc.embed(ids)
+    assert abs(float(e.norm()) - 1.0) < 1e-3
+
+
+def test_wordpiece_and_bert_embeddings_service(tmp_path):
+    import json
+    from hartsyinference_b200.assets.safetensors import save_file
+    from hartsyinference_b200.assets.tokenizer import WordPieceTokenizer
+    from hartsyinference_b200.engine.embeddings_service import BertEmbeddingsService, is_bert_dir
+    from hartsyinference_b200.engine.requests import ModelSpec
+    from hartsyinference_b200.models.encoders.bert import BertEncoder, tiny_bert
+    vocab = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "hello", "world", "un", "##aff", "##able", ",", "!"] + [f"t{i}" for i in range(117)]
+    tok = WordPieceTokenizer(vocab)
+    assert tok.encode("Hello, unaffable world!") == [2, 4, 9, 6, 7, 8, 5, 10, 3]
+    assert tok.encode("zzz", add_special=False) == [1]
+    assert tok.decode(tok.encode("hello unaffable")) == "hello unaffable"
+    # a checkpoint directory round trip through the service
+    cfg = tiny_bert()
+    enc = BertEncoder(cfg, "cpu", seed=4)
+    sd = {"embeddings.word_embeddings.weight": enc.tok, "embeddings.position_embeddings.weight": enc.pos,
+          "embeddings.token_type_embeddings.weight": enc.typ, "embeddings.LayerNorm.weight": enc.ln_w,
+          "embeddings.LayerNorm.bias": enc.ln_b}
+    H = cfg.hidden
+    for i, b in enumerate(enc.blocks):
+        p = f"encoder.layer.{i}."
+        for j, n in enumerate(("query", "key", "value")):
+            sd[p + f"attention.self.{n}.weight"] = b["qkv"].weight[j * H:(j + 1) * H].contiguous()
+            sd[p + f"attention.self.{n}.bias"] = b["qkv"].bias[j * H:(j + 1) * H].contiguous()
+        for name, key in (("attention.output.dense", "o"), ("intermediate.dense", "fc1"), ("output.dense", "fc2")):
+            sd[p + name + ".weight"], sd[p + name + ".bias"] = b[key].weight, b[key].bias
+        sd[p + "attention.output.LayerNorm.weight"], sd[p + "attention.output.LayerNorm.bias"] = b["ln1w"], b["ln1b"]
+        sd[p + "output.LayerNorm.weight"], sd[p + "output.LayerNorm.bias"] = b["ln2w"], b["ln2b"]
+    d = tmp_path / "bert"
+    d.mkdir()
+    save_file({k: v.contiguous() for k, v in sd.items()}, d / "model.safetensors")
+    (d / "config.json").write_text(json.dumps(dict(model_type="bert", vocab_size=cfg.vocab_size, hidden_size=H,
+                                                   num_hidden_layers=cfg.layers, num_attention_heads=cfg.heads,
+                                                   intermediate_size=cfg.intermediate, max_position_embeddings=cfg.max_len)))
+    (d / "vocab.txt").write_text("\n".join(vocab) + "\n")
+    assert is_bert_dir(d)
+    svc = BertEmbeddingsService("cpu")
+    out = svc.embed(ModelSpec(requested=str(d), local_path=str(d)), ["hello world", "unaffable !"])
+    assert out.shape == (2, H)
+    ref = enc.embed(torch.tensor(tok.encode("hello world")))
+    assert torch.allclose(out[0], ref.float(), atol=2e-2)
