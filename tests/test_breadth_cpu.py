@@ -177,3 +177,55 @@ def test_wordpiece_and_bert_embeddings_service(tmp_path):
     assert out.shape == (2, H)
     ref = enc.embed(torch.tensor(tok.encode("hello world")))
     assert torch.allclose(out[0], ref.float(), atol=2e-2)
+
+
+def test_iso_surface_of_a_sphere_is_closed_oriented_and_accurate(tmp_path):
+    from hartsyinference_b200.threed import marching_cubes, write_glb, write_obj, write_ply
+    from hartsyinference_b200.threed.writers import vertex_normals
+    n = 20
+    g = torch.linspace(-1, 1, n)
+    x, y, z = torch.meshgrid(g, g, g, indexing="ij")
+    sdf = (x * x + y * y + z * z).sqrt() - 0.6
+    v, f = marching_cubes(sdf, 0.0, spacing=(2 / (n - 1),) * 3, origin=(-1, -1, -1))
+    assert f.shape[0] > 1000
+    assert (v.norm(dim=1) - 0.6).abs().max() < 0.02
+    e = torch.cat([f[:, [0, 1]], f[:, [1, 2]], f[:, [2, 0]]], 0)
+    fwd, rev = set(map(tuple, e.tolist())), set(map(tuple, e[:, [1, 0]].tolist()))
+    assert fwd == rev and len(fwd) == e.shape[0]                 # closed and consistently wound
+    a, b, c = v[f[:, 0]], v[f[:, 1]], v[f[:, 2]]
+    vol = (a * torch.cross(b, c, dim=1)).sum() / 6
+    assert abs(float(vol) - 4 / 3 * 3.14159265 * 0.6 ** 3) < 0.03   # positive: normals point outwards
+    assert marching_cubes(torch.ones(4, 4, 4))[1].shape[0] == 0
+    # writers
+    nrm = vertex_normals(v, f)
+    write_obj(tmp_path / "m.obj", v, f, nrm)
+    txt = (tmp_path / "m.obj").read_text().splitlines()
+    assert sum(l.startswith("v ") for l in txt) == v.shape[0] and sum(l.startswith("f ") for l in txt) == f.shape[0]
+    write_ply(tmp_path / "m.ply", v, f, colors=torch.full((v.shape[0], 3), 128, dtype=torch.uint8))
+    raw = (tmp_path / "m.ply").read_bytes()
+    head = raw[:raw.index(b"end_header\n") + 11].decode()
+    assert f"element vertex {v.shape[0]}" in head and f"element face {f.shape[0]}" in head
+    assert len(raw) == len(head) + v.shape[0] * 15 + f.shape[0] * 13
+    write_glb(tmp_path / "m.glb", v, f, nrm)
+    import json, struct
+    blob = (tmp_path / "m.glb").read_bytes()
+    magic, ver, total = struct.unpack("<4sII", blob[:12])
+    assert magic == b"glTF" and ver == 2 and total == len(blob)
+    jlen = struct.unpack("<I", blob[12:16])[0]
+    doc = json.loads(blob[20:20 + jlen])
+    assert doc["accessors"][0]["count"] == v.shape[0] and doc["accessors"][-1]["count"] == f.numel()
+
+
+def test_video_frames_and_sequence_fallback(tmp_path, monkeypatch):
+    from hartsyinference_b200 import video as V
+    fr = torch.rand(5, 3, 16, 24) * 2 - 1
+    u8 = V.frames_to_uint8(fr)
+    assert u8.shape == (5, 16, 24, 3) and u8.dtype == torch.uint8
+    assert torch.equal(V.frames_to_uint8(fr.permute(1, 0, 2, 3)), u8)
+    monkeypatch.setattr(V.io, "ffmpeg_path", lambda: None)
+    out = V.encode_video(fr, tmp_path / "clip.mp4", fps=8)
+    assert out.is_dir() and len(list(out.glob("frame_*.png"))) == 5
+    import json
+    man = json.loads((out / "manifest.json").read_text())
+    assert man == {"fps": 8, "frames": 5, "width": 24, "height": 16, "pattern": "frame_%06d.png"}
+    assert (out / "frame_000000.png").read_bytes()[:8] == b"\\x89PNG\\r\\n\\x1a\\n"
