@@ -228,4 +228,4 @@ def test_video_frames_and_sequence_fallback(tmp_path, monkeypatch):
     import json
     man = json.loads((out / "manifest.json").read_text())
     assert man == {"fps": 8, "frames": 5, "width": 24, "height": 16, "pattern": "frame_%06d.png"}
-    assert (out / "frame_000000.png").read_bytes()[:8] == b"\\x89PNG\\r\\n\\x1a\\n"
+    assert (out / "frame_000000.png").read_bytes()[:8] == b"\x89PNG\r\n\x1a\n"
