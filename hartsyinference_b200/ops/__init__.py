@@ -8,6 +8,7 @@ default bodies) collapses into this module plus ``torch.Tensor``.
 """
 from .core import (  # noqa: F401
     Fp8Act,
+    GgufWeight,
     LinearWeight,
     argmax,
     attention,
@@ -20,6 +21,7 @@ from .core import (  # noqa: F401
     fill_random_,
     gated_residual,
     glu,
+    gguf_linear,
     grouped_linear,
     moe_capacity,
     moe_combine,

@@ -31,6 +31,10 @@ _SIGNATURES = {
     "b200_mla_pick_splits": (i32, [i32, i32, i32]),
     "b200_mla_workspace_bytes": (i64, [i32, i32, i32]),
     "b200_mla_attn": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, f32, vp]),
+    "b200_gguf_row_bytes": (i64, [i32, i32]),
+    "b200_gguf_gemv_workspace_bytes": (i64, [i32, i32]),
+    "b200_gguf_gemv": (i32, [vp, i64, vp, i32, vp, i64, vp, i32, i32, i32, vp, vp]),
+    "b200_gguf_dequant": (i32, [vp, i32, vp, i64, i32, vp]),
     "b200_moe_route": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp]),
     "b200_moe_dispatch": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "b200_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),

@@ -723,3 +723,75 @@ def mla_attn(q_abs: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor
                          N.ptr(ws), float(scale), N.stream())
     N.check(rc, "b200_mla_attn")
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# GGUF block-quantised weights kept in their file layout on the device
+# ---------------------------------------------------------------------------------------------
+GGML_Q8_0, GGML_Q4_K = 8, 12
+_GGUF_ROW = {GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144)}      # type -> (values per block, bytes per block)
+GGUF_GEMV_MAX_TOKENS = 16
+
+
+@dataclass
+class GgufWeight:
+    """A [N, K] weight as raw ggml blocks: ``blocks`` uint8 [N, K / block * block_bytes]."""
+    blocks: torch.Tensor
+    ggml_type: int
+    k: int
+    bias: Optional[torch.Tensor] = None
+
+    @property
+    def out_features(self) -> int:
+        return self.blocks.shape[0]
+
+    @property
+    def in_features(self) -> int:
+        return self.k
+
+    def nbytes(self) -> int:
+        return self.blocks.numel() + (0 if self.bias is None else self.bias.numel() * 2)
+
+    @staticmethod
+    def supported(ggml_type: int, k: int) -> bool:
+        return ggml_type in _GGUF_ROW and k % _GGUF_ROW[ggml_type][0] == 0
+
+    @staticmethod
+    def from_raw(raw: torch.Tensor, ggml_type: int, n: int, k: int, bias: Optional[torch.Tensor] = None) -> "GgufWeight":
+        per, nbytes = _GGUF_ROW[ggml_type]
+        return GgufWeight(raw.reshape(n, k // per * nbytes), ggml_type, k, bias)
+
+    def dequantize(self) -> torch.Tensor:
+        """bf16 [N, K] (device kernel on CUDA, host codec on CPU)."""
+        n = self.blocks.shape[0]
+        if not self.blocks.is_cuda:
+            from ..assets.gguf import dequantize
+            return dequantize(self.blocks.contiguous(), self.ggml_type, n * self.k).reshape(n, self.k).to(torch.bfloat16)
+        out = torch.empty(n, self.k, dtype=torch.bfloat16, device=self.blocks.device)
+        rc = N.lib().b200_gguf_dequant(self.blocks.data_ptr(), self.ggml_type, out.data_ptr(), n, self.k, N.stream())
+        N.check(rc, "b200_gguf_dequant")
+        return out
+
+
+def gguf_linear(x: torch.Tensor, w: GgufWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ W^T + bias with W read as ggml blocks: up to 16 tokens go through the integer-dot
+    GEMV (each weight bit read once), more tokens dequantise to a bf16 scratch and use the GEMM."""
+    m, k = x.shape
+    assert k == w.k
+    if not x.is_cuda:
+        y = x.float() @ w.dequantize().float().t()
+        if w.bias is not None:
+            y = y + w.bias.float()
+        return y.to(x.dtype)
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.blocks.is_contiguous()
+    n = w.out_features
+    if m > GGUF_GEMV_MAX_TOKENS:
+        return linear(x, LinearWeight(w.dequantize(), None, w.bias), out=out)
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    L = N.lib()
+    ws = torch.empty(L.b200_gguf_gemv_workspace_bytes(m, k), dtype=torch.uint8, device=x.device)
+    rc = L.b200_gguf_gemv(x.data_ptr(), x.stride(0), w.blocks.data_ptr(), w.ggml_type, out.data_ptr(), out.stride(0),
+                          N.ptr(w.bias), m, n, k, ws.data_ptr(), N.stream())
+    N.check(rc, "b200_gguf_gemv")
+    return out
