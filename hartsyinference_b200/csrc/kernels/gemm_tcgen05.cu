@@ -82,6 +82,11 @@ struct GemmParams {
   const uint32_t* sf_b;
   int sf_kgroups;
   int sf_tile_b;
+  // Shifted-row accumulation (convolutions as one GEMM): K is a sequence of taps of tap_kblocks
+  // k-blocks each; tap t reads A rows shifted down by tap_shift[t] and A columns
+  // [0, tap_kblocks * 64). 0 = ordinary GEMM.
+  int tap_kblocks;
+  int tap_shift[28];
   // 1: every tile is split and a second kernel (splitk_reduce_kernel) sums the partials with the
   // whole machine; 0: the last CTA to arrive at a split tile sums them inside this kernel.
   int external_reduce;
@@ -539,8 +544,13 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
             }
           }
           for (int a = 0; a < na; ++a) {
-            tma_load_2d(sa + a * kStageBytesA, &tm_a, &bars->full[s], (kb + a) * kElemsPerAtom,
-                        it.ta * kTileA);
+            int ax = (kb + a) * kElemsPerAtom, ay = it.ta * kTileA;
+            if (p.tap_kblocks > 0) {
+              const int tap = (kb + a) / p.tap_kblocks;
+              ax = ((kb + a) - tap * p.tap_kblocks) * kElemsPerAtom;
+              ay += p.tap_shift[tap];
+            }
+            tma_load_2d(sa + a * kStageBytesA, &tm_a, &bars->full[s], ax, ay);
             tma_load_2d(sb + a * kAtomBytesB, &tm_b, &bars->full[s], (kb + a) * kElemsPerAtom + it.bk,
                         it.tb * BN);
           }
@@ -905,11 +915,21 @@ struct GroupSpec {
   int out_stride;
 };
 
+// Host description of a shifted-row (convolution) launch: x is [x_rows][cin] (cin a multiple of
+// 64), w is [n][taps * cin], output row r = sum over taps of x[r + shift[t]] . w[:, t * cin ...].
+struct ConvSpec {
+  int taps;
+  int cin;
+  long long x_rows;
+  int shift[28];
+};
+
 int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
                      long long ldw, long long ldc, int dtype, const float* x_scale,
                      const float* w_scale, const void* bias, const void* gate, const void* residual,
                      int act, int splits, void* workspace, long long workspace_bytes, void* status,
-                     cudaStream_t stream, const AllReduceParams* ar, const GroupSpec* gs = nullptr) {
+                     cudaStream_t stream, const AllReduceParams* ar, const GroupSpec* gs = nullptr,
+                     const ConvSpec* cs = nullptr) {
   const int groups = gs ? gs->groups : 0;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   // grouped: x is [groups * m][k], w is [groups * n][k], out is [groups * m][n]; m = tokens per group
@@ -930,7 +950,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   }
 
   // Small token counts: weights take the 128-row MMA dimension, tokens the N dimension.
-  const bool swap = m <= 128;
+  const bool swap = m <= 128 && cs == nullptr;
   GemmParams p{};
   p.k = k;
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -1045,7 +1065,13 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   p.stages = stages;
 
   CUtensorMap ta, tb;
-  int rc = make_kmajor_map(&ta, a_ptr, esz, p.rows_a, k, lda, kTileA);
+  if (cs != nullptr) {
+    if (fp8 || groups > 0 || ar != nullptr || cs->taps < 1 || cs->taps > 28 || cs->cin % 64 != 0) return -10;
+    p.tap_kblocks = cs->cin / 64;
+    for (int t = 0; t < cs->taps; ++t) p.tap_shift[t] = cs->shift[t];
+  }
+  int rc = cs != nullptr ? make_kmajor_map(&ta, a_ptr, esz, cs->x_rows, cs->cin, lda, kTileA)
+                         : make_kmajor_map(&ta, a_ptr, esz, p.rows_a, k, lda, kTileA);
   if (rc) return rc;
   rc = make_kmajor_map(&tb, b_ptr, esz, p.rows_b, p.group_b_koff > 0 ? ldb : k, ldb, bn);
   if (rc) return rc;
@@ -1155,6 +1181,28 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
   ar.wait_budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
   return gemm_impl(x, w, out[rank], m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, gate,
                    residual, act, 1, nullptr, 0, status, stream, &ar);
+}
+
+// Convolution as ONE tcgen05 GEMM without an im2col buffer. The input is a zero-padded,
+// channels-last volume flattened to rows [x_rows][cin] (cin a multiple of 64, bf16); kernel tap t
+// is the same matrix shifted down by shift[t] rows, so the K loop walks taps x cin while the A tile
+// coordinate moves by the tap's row offset and the accumulator stays in TMEM for all taps.
+// out[r][co] (bf16, row pitch ldc) = bias[co] + sum_t sum_ci x[r + shift[t]][ci] * w[co][t * cin + ci]
+// for r < rows. Rows whose window runs past x_rows read zeros.
+B200_API int b200_conv_gemm(const void* x, long long x_rows, int cin, const void* w, int cout, int taps,
+                            const int* shift, void* out, long long rows, long long ldc, const void* bias,
+                            int act, void* workspace, long long workspace_bytes, void* status,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (rows > 0x7fffffffll || taps < 1 || taps > 28) return -10;
+  ConvSpec cs{};
+  cs.taps = taps;
+  cs.cin = cin;
+  cs.x_rows = x_rows;
+  for (int t = 0; t < taps; ++t) cs.shift[t] = shift[t];
+  return gemm_impl(x, w, out, static_cast<int>(rows), cout, taps * cin, cin, static_cast<long long>(taps) * cin, ldc,
+                   0, nullptr, nullptr, bias, nullptr, nullptr, act, 0, workspace, workspace_bytes, status, stream,
+                   nullptr, nullptr, &cs);
 }
 
 // ------------------------------------------------------------------------------------------

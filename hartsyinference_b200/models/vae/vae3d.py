@@ -6,7 +6,8 @@ video [3, 4(T - 1) + 1, 8h, 8w].
 
 Reference: src/HartsyInference.Diffusion/Models/Vae/CausalConv3d.cs (fast path :146-174 = padded
 frames + kt 2-D convolutions + tap accumulation) and the Wan VAE decoder files beside it. The
-convolutions here go through PyTorch's conv3d (cuDNN implicit GEMM)."""
+convolutions run as one shifted-row tcgen05 GEMM per layer on CUDA (``ops.causal_conv3d``) and
+through PyTorch's conv3d on CPU."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -39,6 +40,7 @@ class Vae3dDecoder:
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self._get, self._g = get, torch.Generator().manual_seed(seed)
         self.w: dict[str, torch.Tensor] = {}
+        self._packed: dict[str, torch.Tensor] = {}      # conv weights in the GEMM layout, built on first use
         dims = [cfg.dim * m for m in [cfg.dim_mult[-1]] + list(reversed(cfg.dim_mult))]
         self._conv3("conv2", cfg.z_dim, cfg.z_dim, 1)
         self._conv3("decoder.conv1", dims[0], cfg.z_dim, 3)
@@ -110,6 +112,13 @@ class Vae3dDecoder:
         """x [B, C, T, H, W]; pads (kt - 1) frames on the past side, (k - 1) / 2 spatially."""
         w, b = self.w[name + ".weight"], self.w[name + ".bias"]
         kt, kh, kw = w.shape[2:]
+        if x.is_cuda and x.shape[0] == 1 and x.dtype == torch.bfloat16 and w.shape[1] >= 16:
+            # one tcgen05 GEMM over the padded channels-last volume (weights packed once)
+            from ... import ops
+            packed = self._packed.get(name)
+            if packed is None:
+                packed = self._packed[name] = ops.core.pack_conv3d_weight(w)
+            return ops.causal_conv3d(x, w, b, packed=packed)
         x = F.pad(x, (kw // 2, kw // 2, kh // 2, kh // 2, kt - 1, 0))
         return F.conv3d(x, w, b)
 

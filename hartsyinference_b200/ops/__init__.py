@@ -14,6 +14,7 @@ from .core import (  # noqa: F401
     attention,
     attn_decode,
     attn_prefill_paged,
+    causal_conv3d,
     cfg_euler_step,
     colbatched_linear,
     dit_qkv,

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "b200_mla_pick_splits": (i32, [i32, i32, i32]),
     "b200_mla_workspace_bytes": (i64, [i32, i32, i32]),
     "b200_mla_attn": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, f32, vp]),
+    "b200_conv_gemm": (i32, [vp, i64, i32, vp, i32, i32, vp, vp, i64, i64, vp, i32, vp, i64, vp, vp]),
     "b200_gguf_row_bytes": (i64, [i32, i32]),
     "b200_gguf_gemv_workspace_bytes": (i64, [i32, i32]),
     "b200_gguf_gemv": (i32, [vp, i64, vp, i32, vp, i64, vp, i32, i32, i32, vp, vp]),

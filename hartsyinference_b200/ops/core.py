@@ -795,3 +795,54 @@ def gguf_linear(x: torch.Tensor, w: GgufWeight, out: Optional[torch.Tensor] = No
                           N.ptr(w.bias), m, n, k, ws.data_ptr(), N.stream())
     N.check(rc, "b200_gguf_gemv")
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# convolution as one shifted-row GEMM (no im2col buffer)
+# ---------------------------------------------------------------------------------------------
+def pack_conv3d_weight(weight: torch.Tensor) -> torch.Tensor:
+    """[Cout, Cin, kt, kh, kw] -> bf16 [Cout, kt * kh * kw * Cin_p] with taps outermost and the
+    channel count padded to a multiple of 64 (done once per weight)."""
+    co, ci, kt, kh, kw = weight.shape
+    cp = (ci + 63) // 64 * 64
+    w = torch.zeros(co, kt, kh, kw, cp, dtype=torch.bfloat16, device=weight.device)
+    w[..., :ci] = weight.permute(0, 2, 3, 4, 1).to(torch.bfloat16)
+    return w.reshape(co, kt * kh * kw * cp).contiguous()
+
+
+def causal_conv3d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  packed: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Stride-1 3-D convolution, "same" padding in H and W, causal in T (kt - 1 zero frames in
+    front). x [C, T, H, W] or [1, C, T, H, W]; weight [Cout, Cin, kt, kh, kw]. On the device this
+    is one tcgen05 GEMM over the zero-padded channels-last volume: tap (dt, dy, dx) is the same
+    [positions, Cin] matrix shifted down by (dt * Hp + dy) * Wp + dx rows."""
+    batched = x.dim() == 5
+    if batched:
+        assert x.shape[0] == 1
+        x = x[0]
+    co, ci, kt, kh, kw = weight.shape
+    c, t, h, w_ = x.shape
+    assert c == ci
+    if not x.is_cuda:
+        xp = torch.nn.functional.pad(x[None].float(), (kw // 2, kw // 2, kh // 2, kh // 2, kt - 1, 0))
+        y = torch.nn.functional.conv3d(xp, weight.float(), None if bias is None else bias.float())[0].to(x.dtype)
+        return y[None] if batched else y
+    cp = (ci + 63) // 64 * 64
+    tp, hp, wp = t + kt - 1, h + kh - 1, w_ + kw - 1
+    xp = torch.zeros(tp, hp, wp, cp, dtype=torch.bfloat16, device=x.device)
+    xp[kt - 1:, kh // 2:kh // 2 + h, kw // 2:kw // 2 + w_, :ci] = x.permute(1, 2, 3, 0)
+    if packed is None:
+        packed = pack_conv3d_weight(weight)
+    shifts = torch.tensor([(dt * hp + dy) * wp + dx for dt in range(kt) for dy in range(kh) for dx in range(kw)],
+                          dtype=torch.int32)
+    rows = t * hp * wp
+    out = torch.empty(rows, co, dtype=torch.bfloat16, device=x.device)
+    st = N.state(x.device)
+    ws = st.gemm_workspace()
+    bias_b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+    rc = N.lib().b200_conv_gemm(xp.data_ptr(), tp * hp * wp, cp, packed.data_ptr(), co, kt * kh * kw,
+                                shifts.data_ptr(), out.data_ptr(), rows, co, N.ptr(bias_b), 0, ws.data_ptr(),
+                                ws.numel(), st.status.data_ptr(), N.stream())
+    N.check(rc, "b200_conv_gemm")
+    y = out.view(t, hp, wp, co)[:, :h, :w_, :].permute(3, 0, 1, 2).contiguous().to(x.dtype)
+    return y[None] if batched else y

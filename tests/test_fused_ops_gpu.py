@@ -128,3 +128,20 @@ def test_fill_random_statistics():
     ops.fill_random_(q, 8)
     f = q.view(torch.float8_e4m3fn).float()
     assert torch.isfinite(f).all() and abs(f.std().item() - 112) < 10
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ci,co,k,t,h,w", [(64, 96, (3, 3, 3), 3, 10, 12), (96, 192, (3, 3, 3), 2, 9, 7),
+                                            (192, 96, (1, 1, 1), 4, 8, 8), (128, 256, (3, 1, 1), 5, 6, 6),
+                                            (16, 64, (3, 3, 3), 2, 16, 16)])
+def test_causal_conv3d_as_gemm_matches_torch(ci, co, k, t, h, w):
+    torch.manual_seed(ci + co)
+    x = torch.randn(ci, t, h, w, device="cuda").to(torch.bfloat16)
+    wt = (torch.randn(co, ci, *k, device="cuda") * (1.0 / (ci * k[0] * k[1] * k[2]) ** 0.5)).to(torch.bfloat16)
+    b = torch.randn(co, device="cuda").to(torch.bfloat16)
+    y = ops.causal_conv3d(x, wt, b)
+    ref = ops.causal_conv3d(x.cpu(), wt.cpu(), b.cpu()).float()
+    assert y.shape == (co, t, h, w)
+    err = (y.float().cpu() - ref).abs().max() / ref.abs().max()
+    assert err < 2e-2, err
+    N.check_status()
