@@ -3,6 +3,7 @@ import pytest
 import torch
 
 from hartsyinference_b200 import ops
+from hartsyinference_b200.ops import _native as N
 from hartsyinference_b200.ops import reference as R
 
 pytestmark = pytest.mark.gpu
