@@ -63,6 +63,17 @@ class SingleComm(Comm):
     pass
 
 
+class ShardEmulationComm(Comm):
+    """Measurement aid: claims to be ``rank`` of ``world`` but has no peers. Models built on it
+    hold exactly one rank's weight shard and run that rank's kernels; every collective returns its
+    input, so the OUTPUTS ARE NOT MEANINGFUL. It exists to time one rank's compute of a TP / EP
+    layout on a single GPU (the collectives' cost has to be added from a multi-GPU run)."""
+    transport = "emulated-shard"
+
+    def __init__(self, world: int, rank: int = 0):
+        self.world, self.rank = world, rank
+
+
 class TorchDistComm(Comm):
     """A (sub)group of the default ``torch.distributed`` world."""
 

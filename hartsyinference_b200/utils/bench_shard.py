@@ -1,0 +1,72 @@
+"""Per-rank compute time of a tensor / expert parallel layout, measured on ONE GPU.
+
+    python -m hartsyinference_b200.utils.bench_shard --preset llama-3-70b --tp 8 --batch 64 --prompt-len 2048
+    python -m hartsyinference_b200.utils.bench_shard --preset deepseek-v3 --tp 8 --batch 256 --prompt-len 1024
+
+Builds rank 0's shard of the model on a communicator without peers (collectives are no-ops, so
+the generated tokens mean nothing), prefills the batch and times decode steps with CUDA events
+under CUDA graphs. The result is what one GPU of the group spends per step EXCLUDING the
+collectives: a lower bound for the group's step time and the place to look for kernel work. It is
+not a substitute for the multi-GPU benchmark (``bench.py --gpus N``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from dataclasses import replace
+
+import torch
+
+from ..engine import LLMEngine, SamplingParams
+from ..models.llm import config as C
+from ..models.llm.transformer import DecoderModel
+from ..ops import _native as N
+from ..parallel.comm import ShardEmulationComm
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--preset", default="llama-3-70b")
+    ap.add_argument("--tp", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--steps", type=int, default=24)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the preset's)")
+    ap.add_argument("--bf16", action="store_true")
+    args = ap.parse_args()
+    cfg = C.PRESETS[args.preset]
+    if args.layers:
+        cfg = replace(cfg, num_layers=args.layers)
+    comm = ShardEmulationComm(args.tp)
+    model = DecoderModel(cfg, "cuda", comm=comm, fp8=not args.bf16)
+    model.random_init(0)
+    dlen = args.steps + 16
+    page = 16
+    pps = (args.prompt_len + dlen + page - 1) // page + 1
+    eng = LLMEngine(model, num_pages=args.batch * pps + 8, page_size=page, max_batch=args.batch, prefill_chunk=8192,
+                    max_model_len=pps * page)
+    g = torch.Generator().manual_seed(1)
+    for p in torch.randint(0, cfg.vocab_size, (args.batch, args.prompt_len), generator=g).tolist():
+        eng.add_request(p, SamplingParams(greedy=True, ignore_eos=True, max_tokens=dlen))
+    while any(len(r.output) == 0 for r in eng.requests.values()):
+        eng.step()
+    for _ in range(4):
+        eng.step()
+    torch.cuda.synchronize()
+    eng.time_steps = True
+    ts = []
+    for _ in range(args.steps):
+        eng.step()
+        ts.append(eng.device_ms_last)
+    N.check_status()
+    ts.sort()
+    med = ts[len(ts) // 2]
+    print(json.dumps({"preset": args.preset, "emulated_rank_of": args.tp, "layers": cfg.num_layers, "batch": args.batch,
+                      "prompt_len": args.prompt_len, "ms_per_step_compute_only": med, "ms_min": ts[0],
+                      "us_per_layer": 1000 * med / cfg.num_layers, "launches_per_step": eng.kernel_launches_last,
+                      "weight_gib": model.weight_bytes() / 2 ** 30,
+                      "tokens_per_s_if_collectives_were_free": args.batch / med * 1e3}))
+
+
+if __name__ == "__main__":
+    main()
