@@ -76,6 +76,10 @@ struct GemmParams {
   // g * group_out_stride. 0 = stacked token blocks as described above.
   int group_b_koff;
   int group_out_stride;
+  // Stacked grouped mode with several token blocks per weight group (`group_chunks` > 1): B block
+  // e * chunks + c pairs with weight group e. Tiles are ordered (group, A tile, chunk) so that the
+  // chunks of one weight tile run next to each other and the second read of the weights hits L2.
+  int group_chunks;
   // MX mode (hardware block scaling): UE8M0 scale factors in the blocked layout
   // [row tile][k group of 512][128 x uint32], see quant_mx.cuh; sf_tile_b = B rows per SF block.
   const uint32_t* sf_a;
@@ -167,10 +171,20 @@ __device__ __forceinline__ WorkItem decode_item(const GemmParams& p, long long w
   it.ta = static_cast<int>(tile % tiles_a);
   it.bk = 0;
   if (p.group_n > 0) {
-    const int g = (it.ta * kTileA) / p.group_n;
-    if (p.group_b_koff > 0) { it.tb = 0; it.bk = g * p.group_b_koff; }
-    else it.tb = g;
-    it.skip = p.group_counts != nullptr && p.group_counts[g] == 0;
+    if (p.group_b_koff > 0) {
+      const int g = (it.ta * kTileA) / p.group_n;
+      it.tb = 0;
+      it.bk = g * p.group_b_koff;
+      it.skip = false;
+    } else {
+      const int chunks = p.group_chunks > 1 ? p.group_chunks : 1;
+      const int tpg = p.group_n / kTileA;                 // A tiles per weight group
+      const int t = static_cast<int>(tile);
+      const int chunk = t % chunks, within = (t / chunks) % tpg, e = t / (chunks * tpg);
+      it.ta = e * tpg + within;
+      it.tb = e * chunks + chunk;
+      it.skip = p.group_counts != nullptr && p.group_counts[it.tb] == 0;
+    }
   } else {
     it.tb = static_cast<int>(tile / tiles_a);
     it.skip = false;
@@ -910,9 +924,10 @@ constexpr long long kSplitCounterBytes = 16384;   // head of the scratch buffer:
 // Host description of a grouped launch (see GemmParams::group_n and ::group_b_koff).
 struct GroupSpec {
   int groups;
-  const int* counts;     // device, optional
+  const int* counts;     // device, optional: one per token block (groups * chunks)
   int b_koff;            // > 0: column-batched variant
   int out_stride;
+  int chunks = 1;        // token blocks per weight group (stacked mode)
 };
 
 // Host description of a shifted-row (convolution) launch: x is [x_rows][cin] (cin a multiple of
@@ -984,7 +999,8 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     p.group_b_koff = gs->b_koff;
     p.group_out_stride = gs->out_stride;
     p.rows_a = groups * n;
-    p.rows_b = gs->b_koff > 0 ? m : groups * m;
+    p.group_chunks = gs->chunks < 1 ? 1 : gs->chunks;
+    p.rows_b = gs->b_koff > 0 ? m : groups * p.group_chunks * m;
     a_ptr = w; lda = ldw; b_ptr = x; ldb = ldx;
     bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
     p.scale_a = w_scale; p.sa_gran = 128; p.sa_ld = k / 128;
@@ -1014,7 +1030,8 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     if (groups > 0 && gs->b_koff > 0) return -9;
   }
   const int total_kblocks = (k + kelems - 1) / kelems;
-  const int tiles = groups > 0 ? (p.rows_a + 127) / 128 : ((p.rows_a + 127) / 128) * ((p.rows_b + bn - 1) / bn);
+  const int tiles = groups > 0 ? ((p.rows_a + 127) / 128) * (gs->b_koff > 0 ? 1 : p.group_chunks)
+                               : ((p.rows_a + 127) / 128) * ((p.rows_b + bn - 1) / bn);
   const int sms = num_sms();
   p.num_tiles = tiles;
 
@@ -1241,15 +1258,17 @@ B200_API int b200_gemm_noalloc(const void* x, const void* w, void* out, int m, i
 
 // Grouped GEMM for expert layers: for every group g, out[g][m][n] = x[g][m][k] * w[g][n][k]^T with
 // all groups in ONE launch (weights stacked as [groups * n][k], token blocks as [groups * m][k],
-// m in {16, 32, 64, 128} slots per group, unused slots zero; groups whose entry of the optional
+// m in {16, 32, 64, 128} slots per token block, `chunks` token blocks per group (x and out are then
+// [groups * chunks * m] rows with block e * chunks + c belonging to group e); blocks whose entry of the optional
 // device array group_counts is zero are skipped and their output rows left untouched). Same kernel as b200_gemm: expert
 // weights fill the 128-row MMA dimension, each expert's token block is the N operand.
 B200_API int b200_gemm_grouped(const void* x, const void* w, void* out, int groups, int m, int n, int k,
                                int dtype, const float* x_scale, const float* w_scale, int act,
-                               const int* group_counts, void* workspace, long long workspace_bytes,
-                               void* status, cudaStream_t stream) {
+                               const int* group_counts, int chunks, void* workspace,
+                               long long workspace_bytes, void* status, cudaStream_t stream) {
   if (groups <= 0) return 0;
-  const GroupSpec gs{groups, group_counts, 0, 0};
+  GroupSpec gs{groups, group_counts, 0, 0};
+  gs.chunks = chunks < 1 ? 1 : chunks;
   return gemm_impl(x, w, out, m, n, k, k, k, n, dtype, x_scale, w_scale, nullptr, nullptr, nullptr, act, 0,
                    workspace, workspace_bytes, status, stream, nullptr, &gs);
 }
@@ -1264,7 +1283,7 @@ B200_API int b200_gemm_colbatched(const void* x, const void* w, void* out, int g
                                   long long workspace_bytes, void* status, cudaStream_t stream) {
   if (groups <= 0 || m <= 0) return 0;
   if (x_koff <= 0) return -9;
-  const GroupSpec gs{groups, nullptr, x_koff, out_stride};
+  GroupSpec gs{groups, nullptr, x_koff, out_stride};
   return gemm_impl(x, w, out, m, n, k, ldx, k, ldc, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0,
                    workspace, workspace_bytes, status, stream, nullptr, &gs);
 }

@@ -137,15 +137,19 @@ __global__ void moe_route_kernel(const RouteParams p) {
 
 // counts[e_local] must be zero on entry. slot_of[t][k] = e_local * capacity + position, or -1 when
 // the expert is not local or its block is full.
+// Tokens are taken in chunks of `chunk_tokens`: expert e keeps one block of `capacity` slots per
+// chunk (block index e * chunks + c), so a block can never overflow when capacity >= chunk_tokens.
 __global__ void moe_assign_kernel(const int* __restrict__ topk_ids, int* __restrict__ slot_of,
-                                  int* __restrict__ counts, int pairs, int e0, int e_local, int capacity) {
+                                  int* __restrict__ counts, int pairs, int top_k, int e0, int e_local,
+                                  int capacity, int chunks, int chunk_tokens) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= pairs) return;
   const int e = topk_ids[i] - e0;
   int slot = -1;
   if (e >= 0 && e < e_local) {
-    const int pos = atomicAdd(counts + e, 1);
-    if (pos < capacity) slot = e * capacity + pos;
+    const int blk = e * chunks + (i / top_k) / chunk_tokens;
+    const int pos = atomicAdd(counts + blk, 1);
+    if (pos < capacity) slot = blk * capacity + pos;
   }
   slot_of[i] = slot;
 }
@@ -212,12 +216,14 @@ B200_API int b200_moe_route(const void* logits, int logits_bf16, const float* bi
 }
 
 B200_API int b200_moe_dispatch(const void* x, void* xs, const int* topk_ids, int* slot_of, int* counts, int tokens,
-                               int top_k, int dim, int e0, int e_local, int capacity, cudaStream_t stream) {
+                               int top_k, int dim, int e0, int e_local, int capacity, int chunks, int chunk_tokens,
+                               cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (dim % 8) return -2;
+  if (dim % 8 || chunks < 1 || chunk_tokens < 1 || tokens > chunks * chunk_tokens) return -2;
   const int pairs = tokens * top_k;
-  if (cudaMemsetAsync(counts, 0, sizeof(int) * e_local, stream) != cudaSuccess) return -3;
-  moe_assign_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(topk_ids, slot_of, counts, pairs, e0, e_local, capacity);
+  if (cudaMemsetAsync(counts, 0, sizeof(int) * e_local * chunks, stream) != cudaSuccess) return -3;
+  moe_assign_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(topk_ids, slot_of, counts, pairs, top_k, e0, e_local,
+                                                             capacity, chunks, chunk_tokens);
   moe_scatter_kernel<<<pairs, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(xs),
                                                 slot_of, top_k, dim);
   return cudaGetLastError() == cudaSuccess ? 0 : -300;

@@ -7,9 +7,10 @@ expert is column/row-sharded like a dense FFN, and ONE all-reduce sums routed an
 outputs. Routing runs on the device on every rank (deterministic, identical results), so there is
 no host round trip per layer and the layer is CUDA-graph capturable.
 
-Per chunk of <= 128 tokens: router GEMM -> ``moe_route`` -> ``moe_dispatch`` into fixed-capacity
-expert blocks -> grouped gate_up GEMM (all local experts in one launch, idle experts skipped) ->
-GLU -> grouped down GEMM -> ``moe_combine`` (fixed order, deterministic).
+Per pass of <= 1024 tokens: router GEMM -> ``moe_route`` -> ``moe_dispatch`` into fixed-capacity
+blocks (one per expert and run of 128 tokens) -> grouped gate_up GEMM (all local experts and runs in
+one launch, idle blocks skipped) -> GLU -> grouped down GEMM -> ``moe_combine`` (fixed order,
+deterministic).
 
 Reference behaviour: src/HartsyInference.LLM/Transformer/MoeFeedForward.cs (Route:186-233,
 RouteGroupLimited:240-312, Forward:88-161 with one device-to-host copy of the router logits and
@@ -28,7 +29,7 @@ from ...ops import LinearWeight
 from ...ops import reference as R
 from .config import MoeConfig, TransformerConfig
 
-_CHUNK = 128
+_CHUNK = 1024        # tokens per pass: up to 8 runs of 128 tokens share one read of the expert weights
 
 
 @dataclass
@@ -56,7 +57,7 @@ class MoeFeedForward:
         self.all_reduce = all_reduce
         self.hidden = cfg.hidden_size
         self.ffn = moe.expert_ffn
-        self._xs: dict[int, torch.Tensor] = {}     # capacity -> dispatch buffer
+        self._xs: dict[tuple[int, int], torch.Tensor] = {}     # (capacity, runs) -> dispatch buffer
 
     def nbytes(self) -> int:
         n = 0
@@ -114,16 +115,20 @@ class MoeFeedForward:
     def _routed_gpu(self, h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, out: torch.Tensor,
                     accumulate: bool) -> None:
         t = h.shape[0]
-        cap = ops.moe_capacity(t)
-        xs = self._xs.get(cap)
+        # runs of 128 tokens: every expert keeps one block of `cap` slots per run, so no block can
+        # overflow, and one grouped launch covers all runs (the weights of an expert are fetched
+        # from HBM once; the other runs of the same weight tile hit L2)
+        chunks = (t + 127) // 128
+        cap = ops.moe_capacity(min(t, 128))
+        xs = self._xs.get((cap, chunks))
         if xs is None:
-            xs = torch.zeros(self.e_local * cap, self.hidden, dtype=torch.bfloat16, device=h.device)
-            self._xs[cap] = xs
-        slot_of, counts = ops.moe_dispatch(h, ids, self.e0, self.e_local, cap, xs)
-        gu = ops.grouped_linear(xs, self.w.gate_up, self.e_local, counts=counts)
+            xs = torch.zeros(self.e_local * chunks * cap, self.hidden, dtype=torch.bfloat16, device=h.device)
+            self._xs[(cap, chunks)] = xs
+        slot_of, counts = ops.moe_dispatch(h, ids, self.e0, self.e_local, cap, xs, chunks=chunks)
+        gu = ops.grouped_linear(xs, self.w.gate_up, self.e_local, counts=counts, chunks=chunks)
         fp8 = self.w.down.is_fp8
         a, a8 = ops.glu(gu, self.cfg.activation, emit_fp8=fp8, emit_bf16=not fp8, fp8_tile_rows=cap)
-        y = ops.grouped_linear(a8 if a8 is not None else a, self.w.down, self.e_local, counts=counts)
+        y = ops.grouped_linear(a8 if a8 is not None else a, self.w.down, self.e_local, counts=counts, chunks=chunks)
         ops.moe_combine(y, slot_of, wts, out, accumulate=accumulate)
 
     # ---------------------------------------------------------------------------------- forward

@@ -25,7 +25,7 @@ vp, i32, i64, f32, u64 = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulong
 _SIGNATURES = {
     "b200_gemm": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, vp, vp, i32, i32, vp, i64, vp, vp]),
     "b200_gemm_workspace_bytes": (i64, []),
-    "b200_gemm_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp, i64, vp, vp]),
+    "b200_gemm_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, i64, vp, vp]),
     "b200_gemm_colbatched": (i32, [vp, vp, vp, i32, i32, i32, i32, i64, i32, i64, i32, vp, i64, vp, vp]),
     "b200_mla_prep": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, f32, vp]),
     "b200_mla_pick_splits": (i32, [i32, i32, i32]),
@@ -37,7 +37,7 @@ _SIGNATURES = {
     "b200_gguf_gemv": (i32, [vp, i64, vp, i32, vp, i64, vp, i32, i32, i32, vp, vp]),
     "b200_gguf_dequant": (i32, [vp, i32, vp, i64, i32, vp]),
     "b200_moe_route": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp]),
-    "b200_moe_dispatch": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
+    "b200_moe_dispatch": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
     "b200_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "b200_norm": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, i32, i32, vp]),
     "b200_quant_fp8": (i32, [vp, vp, vp, i32, i32, i64, i32, vp]),

@@ -553,45 +553,53 @@ def moe_capacity(tokens: int) -> int:
 
 def moe_dispatch(x: torch.Tensor, topk_ids: torch.Tensor, e0: int, e_local: int, capacity: int,
                  xs: torch.Tensor, slot_of: Optional[torch.Tensor] = None,
-                 counts: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+                 counts: Optional[torch.Tensor] = None, chunks: int = 1) -> tuple[torch.Tensor, torch.Tensor]:
     """Copy each token row into a slot of every local expert that it selected.
 
-    ``xs`` [e_local * capacity, dim] is a caller-owned buffer (slots without a token keep stale,
-    finite values). Returns (slot_of int32 [T, k] with -1 for remote experts, counts int32 [e_local])."""
+    Tokens are taken in ``chunks`` runs of at most 128; expert e owns block ``e * chunks + c`` of
+    ``capacity`` slots for run c. ``xs`` [e_local * chunks * capacity, dim] is a caller-owned buffer
+    (slots without a token keep stale, finite values). Returns (slot_of int32 [T, k] with -1 for
+    remote experts, counts int32 [e_local * chunks])."""
     t, k = topk_ids.shape
     dim = x.shape[1]
-    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and xs.shape == (e_local * capacity, dim)
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+    assert xs.shape == (e_local * chunks * capacity, dim)
+    chunk_tokens = 128 if chunks > 1 else max(t, 1)
     if slot_of is None:
         slot_of = torch.empty(t, k, dtype=torch.int32, device=x.device)
     if counts is None:
-        counts = torch.empty(e_local, dtype=torch.int32, device=x.device)
+        counts = torch.empty(e_local * chunks, dtype=torch.int32, device=x.device)
     rc = N.lib().b200_moe_dispatch(x.data_ptr(), xs.data_ptr(), topk_ids.data_ptr(), slot_of.data_ptr(),
-                                   counts.data_ptr(), t, k, dim, e0, e_local, capacity, N.stream())
+                                   counts.data_ptr(), t, k, dim, e0, e_local, capacity, chunks, chunk_tokens,
+                                   N.stream())
     N.check(rc, "b200_moe_dispatch")
     return slot_of, counts
 
 
 def grouped_linear(x, w: LinearWeight, groups: int, act: Optional[str] = None,
-                   counts: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Per-group y[g] = x[g] @ w[g]^T in one launch. ``x`` [groups * m, K] (bf16 or Fp8Act, m in
-    {16, 32, 64, 128}), ``w`` stacked [groups * N, K]; groups with ``counts[g] == 0`` are skipped."""
+                   counts: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                   chunks: int = 1) -> torch.Tensor:
+    """Per-group y[b] = x[b] @ w[b // chunks]^T in one launch. ``x`` [groups * chunks * m, K] (bf16
+    or Fp8Act, m in {16, 32, 64, 128}), ``w`` stacked [groups * N, K]; token blocks with
+    ``counts[b] == 0`` are skipped."""
     xd = x.data if isinstance(x, Fp8Act) else x
-    m = xd.shape[0] // groups
+    m = xd.shape[0] // (groups * chunks)
     k = xd.shape[1]
     n = w.weight.shape[0] // groups
     if not xd.is_cuda:
         ys = []
-        for g in range(groups):
+        for b in range(groups * chunks):
+            g = b // chunks
             wg = w.weight[g * n:(g + 1) * n]
             if w.is_fp8:
                 sg = w.scale[g * (n // 128):(g + 1) * (n // 128)]
                 if isinstance(x, Fp8Act):
-                    q, s = x.data[g * m:(g + 1) * m], x.scale[g * m:(g + 1) * m]
+                    q, s = x.data[b * m:(b + 1) * m], x.scale[b * m:(b + 1) * m]
                 else:
-                    q, s = R.quant_fp8_act(xd[g * m:(g + 1) * m], pow2=fp8_mx())
+                    q, s = R.quant_fp8_act(xd[b * m:(b + 1) * m], pow2=fp8_mx())
                 ys.append(R.linear(q, wg, sg, s, None, act, None, None))
             else:
-                ys.append(R.linear(xd[g * m:(g + 1) * m], wg, None, None, None, act, None, None))
+                ys.append(R.linear(xd[b * m:(b + 1) * m], wg, None, None, None, act, None, None))
         return torch.cat(ys)
     if w.is_fp8 and not isinstance(x, Fp8Act):
         x = quant_fp8_act(x, tile_rows=m, mx=w.is_mx)
@@ -600,13 +608,13 @@ def grouped_linear(x, w: LinearWeight, groups: int, act: Optional[str] = None,
         raise ValueError("UE8M0 activations of a grouped GEMM need one scale-factor block per group")
     assert xd.is_contiguous() and w.weight.is_contiguous() and w.weight.shape[1] == k
     if out is None:
-        out = torch.empty(groups * m, n, dtype=torch.bfloat16, device=xd.device)
+        out = torch.empty(groups * chunks * m, n, dtype=torch.bfloat16, device=xd.device)
     fp8 = w.is_fp8
     st = N.state(xd.device)
     ws = st.gemm_workspace()
     xs_ptr, ws_ptr = _scale_ptrs(x, w)
     rc = N.lib().b200_gemm_grouped(xd.data_ptr(), w.weight.data_ptr(), out.data_ptr(), groups, m, n, k,
-                                   _gemm_dtype(w), xs_ptr, ws_ptr, _ACT[act], N.ptr(counts),
+                                   _gemm_dtype(w), xs_ptr, ws_ptr, _ACT[act], N.ptr(counts), chunks,
                                    ws.data_ptr(), ws.numel(), st.status.data_ptr(), N.stream())
     N.check(rc, "b200_gemm_grouped")
     return out

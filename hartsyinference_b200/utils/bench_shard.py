@@ -48,8 +48,13 @@ def main() -> None:
     g = torch.Generator().manual_seed(1)
     for p in torch.randint(0, cfg.vocab_size, (args.batch, args.prompt_len), generator=g).tolist():
         eng.add_request(p, SamplingParams(greedy=True, ignore_eos=True, max_tokens=dlen))
-    while any(len(r.output) == 0 for r in eng.requests.values()):
+    def failed():
+        return [r.error for r in eng.requests.values() if r.error]
+
+    while any(len(r.output) == 0 and not r.finished for r in eng.requests.values()):
         eng.step()
+        if failed():
+            raise SystemExit(f"a step failed: {failed()[0]}")
     for _ in range(4):
         eng.step()
     torch.cuda.synchronize()
@@ -58,6 +63,8 @@ def main() -> None:
     for _ in range(args.steps):
         eng.step()
         ts.append(eng.device_ms_last)
+        if failed():
+            raise SystemExit(f"a step failed: {failed()[0]}")
     N.check_status()
     ts.sort()
     med = ts[len(ts) // 2]

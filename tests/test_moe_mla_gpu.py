@@ -191,3 +191,35 @@ def test_toy_deepseek_gpu_matches_cpu_model():
         b = eng.generate(prompts, SamplingParams(greedy=True, max_tokens=8))
         assert a == b and all(len(x) == 8 for x in a)
         assert eng.model.kv_cache.shape[-1] == 576
+
+
+def test_dispatch_and_grouped_gemm_with_several_runs_per_expert():
+    torch.manual_seed(9)
+    t, k, dim, e_local, n = 300, 4, 256, 6, 256
+    chunks, cap = 3, 128
+    x = torch.randn(t, dim, device=DEV).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(e_local, device=DEV)[:k] for _ in range(t)]).to(torch.int32)
+    xs = torch.zeros(e_local * chunks * cap, dim, dtype=torch.bfloat16, device=DEV)
+    slot_of, counts = ops.moe_dispatch(x, ids, 0, e_local, cap, xs, chunks=chunks)
+    assert counts.numel() == e_local * chunks and int(counts.sum()) == t * k
+    blk = torch.div(slot_of.long(), cap, rounding_mode="floor")
+    tok_run = (torch.arange(t, device=DEV) // 128)[:, None].expand(t, k)
+    assert torch.equal(blk, ids.long() * chunks + tok_run)                 # block = expert * runs + run of the token
+    tok = torch.arange(t, device=DEV)[:, None].expand(t, k)
+    assert torch.equal(xs[slot_of.long().flatten()], x[tok.flatten()])
+    for fp8 in (False, True):
+        w = (torch.randn(e_local * n, dim, device=DEV) * 0.05).to(torch.bfloat16)
+        lw = LinearWeight.from_dense(w, fp8=fp8)
+        y = ops.grouped_linear(xs, lw, e_local, counts=counts, chunks=chunks)
+        wr = R.dequant_fp8_weight(lw.weight.cpu(), lw.scale.cpu()) if fp8 else w.float().cpu()
+        if fp8:
+            xq = ops.quant_fp8_act(xs, tile_rows=cap)
+            xr = R.dequant_fp8_act(xq.data.cpu(), xq.scales_fp32().cpu())
+        else:
+            xr = xs.float().cpu()
+        for b in range(e_local * chunks):
+            if int(counts[b]) == 0:
+                continue
+            e = b // chunks
+            ref = xr[b * cap:(b + 1) * cap] @ wr[e * n:(e + 1) * n].t()
+            assert _rel(y[b * cap:(b + 1) * cap].cpu(), ref) < 0.012, (fp8, b)
