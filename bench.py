@@ -195,16 +195,20 @@ def main() -> int:
     for _ in range(args.warmup):
         eng.step()
     torch.cuda.synchronize()
-    if fused:
-        # A bounded wait of the fused kernels that gave up on any rank means the peer protocol did
-        # not work on this machine: fall back to NCCL on every rank rather than time garbage.
+    peer_ar = getattr(model, "custom_ar", None) is not None
+    if fused or peer_ar:
+        # A bounded wait of the peer-memory kernels that gave up on any rank means the peer protocol
+        # did not work on this machine: fall back to NCCL on every rank rather than time garbage.
         bad = torch.tensor([int(N.state(device).status[0].item() != 0)], device=device)
         import torch.distributed as dist
         dist.all_reduce(bad, op=dist.ReduceOp.MAX)
         if int(bad.item()) != 0:
-            log.warn("[Collective] fused TP kernels reported a wait timeout; falling back to NCCL")
+            log.warn("[Collective] peer-memory TP kernels reported a wait timeout; falling back to NCCL")
             N.state(device).status.zero_()
             model.row_parallel_linear = None
+            model.custom_ar = None
+            model.all_reduce = comm.all_reduce
+            peer_ar = False
             eng._graphs.clear()
             fused = False
             for _ in range(2):
@@ -259,6 +263,7 @@ def main() -> int:
                        "decode_len": args.decode_len, "parallelism": f"tp{world}", "kv_page": page,
                        "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
                        "cuda_graphs": not args.no_graphs, "fused_comm": fused,
+                       "comm_path": "fused GEMM+all-reduce" if fused else "peer-memory all-reduce kernel" if peer_ar else ("nccl" if world > 1 else "none"),
                        "invalid_debug_overrides": invalid},
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "ms_per_step": wall_ms / steps,
                     "h2d_bytes_per_step": h2d // steps, "d2h_bytes_per_step": d2h // steps},

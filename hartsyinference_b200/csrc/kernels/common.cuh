@@ -150,6 +150,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute
+// may start before its predecessor in the stream has finished; pdl_wait() blocks until the
+// predecessor grid has completed and its writes are visible (a no-op for an ordinary launch).
+// pdl_trigger() in the predecessor lets such a dependent start early.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies, per-CTA form only)
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {

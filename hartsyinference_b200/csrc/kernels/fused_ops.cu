@@ -73,6 +73,7 @@ struct NormParams {
 // dim <= 8 * 1024 (blockDim 1024) .. generic fallback re-reads the row.
 template <int kMaxVec>
 __global__ void __launch_bounds__(1024) norm_kernel(const NormParams p) {
+  pdl_trigger();   // a GEMM launched behind this kernel may start fetching its weights now
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nvec = p.dim >> 3;
@@ -215,6 +216,7 @@ __global__ void __launch_bounds__(1024) norm_kernel(const NormParams p) {
 __global__ void quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out,
                                  float* __restrict__ scales, int rows, int dim, long long ld,
                                  int sf_tile_rows) {
+  pdl_trigger();
   const int groups = dim >> 7;
   const long long total = static_cast<long long>(rows) * groups * 16;   // one thread per 8 values
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -318,6 +320,7 @@ __global__ void quant_fp8_weight_kernel(const __nv_bfloat16* __restrict__ w,
 __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                            uint8_t* __restrict__ out_fp8, float* __restrict__ out_scale, int rows,
                            int f, int act, int sf_tile_rows) {
+  pdl_trigger();
   const int nvec = f >> 3;
   const long long total = static_cast<long long>(rows) * nvec;
   const long long padded = ((total + 31) / 32) * 32;

@@ -80,6 +80,11 @@ struct GemmParams {
   // e * chunks + c pairs with weight group e. Tiles are ordered (group, A tile, chunk) so that the
   // chunks of one weight tile run next to each other and the second read of the weights hits L2.
   int group_chunks;
+  // Stacked grouped mode with a DEVICE-SIDE block list (variable tokens per group): B block b
+  // belongs to weight group block_group[b] and *dyn_blocks blocks are in use; tile t is
+  // (block t / tpg, A tile t % tpg). Null = the static layouts above.
+  const int* block_group;
+  const int* dyn_blocks;
   // MX mode (hardware block scaling): UE8M0 scale factors in the blocked layout
   // [row tile][k group of 512][128 x uint32], see quant_mx.cuh; sf_tile_b = B rows per SF block.
   const uint32_t* sf_a;
@@ -147,6 +152,7 @@ struct WorkItem {
 };
 
 __device__ __forceinline__ long long num_work_items(const GemmParams& p) {
+  if (p.block_group != nullptr) return static_cast<long long>(*p.dyn_blocks) * (p.group_n / kTileA);
   return p.first_split_tile + static_cast<long long>(p.num_tiles - p.first_split_tile) * p.splits;
 }
 
@@ -175,6 +181,13 @@ __device__ __forceinline__ WorkItem decode_item(const GemmParams& p, long long w
       const int g = (it.ta * kTileA) / p.group_n;
       it.tb = 0;
       it.bk = g * p.group_b_koff;
+      it.skip = false;
+    } else if (p.block_group != nullptr) {
+      const int tpg = p.group_n / kTileA;
+      const int t = static_cast<int>(tile);
+      const int blk = t / tpg;
+      it.ta = p.block_group[blk] * tpg + (t - blk * tpg);
+      it.tb = blk;
       it.skip = false;
     } else {
       const int chunks = p.group_chunks > 1 ? p.group_chunks : 1;
@@ -530,32 +543,21 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       uint32_t ph = 0;
       long long issued = 0;
       bool ok = true;
-      for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
-        const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
-        if (it.skip) continue;
-        for (int kb = it.kb0; kb < it.kb1; kb += kAtoms) {
-          const int na = min(kAtoms, it.kb1 - kb);
-          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag)) {
-            report_status(p.status, kWaitTimeout, kKernelGemm, 1, blockIdx.x);
-            ok = false;
-            break;
-          }
-          uint8_t* sa = smem + s * kStageBytes;
-          uint8_t* sb = sa + kAtoms * kStageBytesA;
-          // MX: the stage that starts a group of four k-blocks also carries the group's scale factors
-          const bool with_sf = kMx && ((kb & 3) == 0 || kb == it.kb0);
-          constexpr int kSfBlocksB = BN > 128 ? 2 : 1;
-          mbar_arrive_expect_tx(&bars->full[s], na * (kStageBytesA + kAtomBytesB) +
-                                                    (with_sf ? 512 * (1 + kSfBlocksB) : 0));
+      // One stage of loads, in two parts: 1 = A operand (+ its scale factors) and the transaction
+      // count of the whole stage, 2 = B operand (+ its scale factors).
+      auto issue_stage = [&](const WorkItem& it, int kb, int st, int parts) {
+        const int na = min(kAtoms, it.kb1 - kb);
+        uint8_t* sa = smem + st * kStageBytes;
+        uint8_t* sb = sa + kAtoms * kStageBytesA;
+        // MX: the stage that starts a group of four k-blocks also carries the group's scale factors
+        const bool with_sf = kMx && ((kb & 3) == 0 || kb == it.kb0);
+        constexpr int kSfBlocksB = BN > 128 ? 2 : 1;
+        if (parts & 1) {
+          mbar_arrive_expect_tx(&bars->full[st], na * (kStageBytesA + kAtomBytesB) +
+                                                     (with_sf ? 512 * (1 + kSfBlocksB) : 0));
           if (with_sf) {
             const long long ga = (static_cast<long long>(it.ta) * p.sf_kgroups + (kb >> 2)) * 128;
-            bulk_load(sa + kSfOffset, p.sf_a + ga, 512, &bars->full[s]);
-            const long long tile_b = (static_cast<long long>(it.tb) * BN) / p.sf_tile_b;
-#pragma unroll
-            for (int j = 0; j < kSfBlocksB; ++j) {
-              const long long gb = ((tile_b + j) * p.sf_kgroups + (kb >> 2)) * 128;
-              bulk_load(sa + kSfOffset + 512 * (1 + j), p.sf_b + gb, 512, &bars->full[s]);
-            }
+            bulk_load(sa + kSfOffset, p.sf_a + ga, 512, &bars->full[st]);
           }
           for (int a = 0; a < na; ++a) {
             int ax = (kb + a) * kElemsPerAtom, ay = it.ta * kTileA;
@@ -564,10 +566,52 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
               ax = ((kb + a) - tap * p.tap_kblocks) * kElemsPerAtom;
               ay += p.tap_shift[tap];
             }
-            tma_load_2d(sa + a * kStageBytesA, &tm_a, &bars->full[s], ax, ay);
-            tma_load_2d(sb + a * kAtomBytesB, &tm_b, &bars->full[s], (kb + a) * kElemsPerAtom + it.bk,
-                        it.tb * BN);
+            tma_load_2d(sa + a * kStageBytesA, &tm_a, &bars->full[st], ax, ay);
           }
+        }
+        if (parts & 2) {
+          if (with_sf) {
+            const long long tile_b = (static_cast<long long>(it.tb) * BN) / p.sf_tile_b;
+#pragma unroll
+            for (int j = 0; j < kSfBlocksB; ++j) {
+              const long long gb = ((tile_b + j) * p.sf_kgroups + (kb >> 2)) * 128;
+              bulk_load(sa + kSfOffset + 512 * (1 + j), p.sf_b + gb, 512, &bars->full[st]);
+            }
+          }
+          for (int a = 0; a < na; ++a)
+            tma_load_2d(sb + a * kAtomBytesB, &tm_b, &bars->full[st], (kb + a) * kElemsPerAtom + it.bk,
+                        it.tb * BN);
+        }
+      };
+      // Programmatic dependent launch: this grid may start while the kernel before it is still
+      // running. In the small-token orientation the A operand is a weight matrix, which no earlier
+      // kernel of the step writes, so the first stages of weights are requested BEFORE waiting for
+      // the predecessor; the activation tiles follow after the wait.
+      int pre = 0;                 // stage iterations of the first item already half-issued
+      long long w_first = blockIdx.x;
+      if (p.swap_out && p.group_n == 0 && w_first < work_items) {
+        const WorkItem it = decode_item(p, w_first, tiles_a, total_kblocks);
+        for (int kb = it.kb0; kb < it.kb1 && pre < stages; kb += kAtoms, ++pre) issue_stage(it, kb, pre, 1);
+        pdl_wait();
+        for (int i = 0; i < pre; ++i) issue_stage(it, it.kb0 + i * kAtoms, i, 2);
+        issued = pre;
+        s = pre;
+        if (s == stages) { s = 0; ph ^= 1; }
+      } else {
+        pdl_wait();
+      }
+      for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
+        const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
+        if (it.skip) continue;
+        int kb = it.kb0;
+        if (w == w_first && pre > 0) kb += pre * kAtoms;      // already issued above
+        for (; kb < it.kb1; kb += kAtoms) {
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag)) {
+            report_status(p.status, kWaitTimeout, kKernelGemm, 1, blockIdx.x);
+            ok = false;
+            break;
+          }
+          issue_stage(it, kb, s, 3);
           ++issued;
           if (++s == stages) { s = 0; ph ^= 1; }
         }
@@ -586,6 +630,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      pdl_wait();
       int s = 0;
       uint32_t ph = 0;
       int abuf = 0;
@@ -674,6 +719,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
     // ------------------------------------------------------------------ epilogue warps 2..9
     // Two warps share each TMEM lane quarter; they split the accumulator columns in 32-column
     // chunks (even chunks -> first warp, odd chunks -> second warp).
+    pdl_wait();
     const int q = warp & 3;            // TMEM lane quarter this warp may read
     const int hsel = (warp - 2) >> 2;  // which half of the chunks
     constexpr int kChunks = (BN + 31) / 32;
@@ -891,6 +937,9 @@ int make_kmajor_map(CUtensorMap* out, const void* base, int elem_bytes, long lon
   return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 100;
 }
 
+// Programmatic dependent launch of the GEMM (see the producer warp); switchable for A/B timing.
+static bool g_pdl_enabled = true;
+
 template <int kMode, int BN, int kAtoms>
 int launch_gemm(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, int grid,
                 cudaStream_t stream) {
@@ -903,7 +952,17 @@ int launch_gemm(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& t
     if (e != cudaSuccess) return -static_cast<int>(e) - 200;
     configured = true;
   }
-  gemm_tcgen05_kernel<kMode, BN, kAtoms><<<grid, kGemmThreads, smem, stream>>>(p, ta, tb);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kMode, BN, kAtoms>, p, ta, tb) != cudaSuccess) return -300;
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 300;
 }
@@ -928,6 +987,8 @@ struct GroupSpec {
   int b_koff;            // > 0: column-batched variant
   int out_stride;
   int chunks = 1;        // token blocks per weight group (stacked mode)
+  const int* block_group = nullptr;   // device block list (see GemmParams::block_group) ...
+  const int* dyn_blocks = nullptr;    // ... and its length; `chunks` is then the CAPACITY of the list
 };
 
 // Host description of a shifted-row (convolution) launch: x is [x_rows][cin] (cin a multiple of
@@ -1000,7 +1061,10 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     p.group_out_stride = gs->out_stride;
     p.rows_a = groups * n;
     p.group_chunks = gs->chunks < 1 ? 1 : gs->chunks;
-    p.rows_b = gs->b_koff > 0 ? m : groups * p.group_chunks * m;
+    p.block_group = gs->block_group;
+    p.dyn_blocks = gs->dyn_blocks;
+    // with a device block list `chunks` is the total number of blocks the buffers can hold
+    p.rows_b = gs->b_koff > 0 ? m : (gs->block_group ? p.group_chunks * m : groups * p.group_chunks * m);
     a_ptr = w; lda = ldw; b_ptr = x; ldb = ldx;
     bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
     p.scale_a = w_scale; p.sa_gran = 128; p.sa_ld = k / 128;
@@ -1030,7 +1094,8 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     if (groups > 0 && gs->b_koff > 0) return -9;
   }
   const int total_kblocks = (k + kelems - 1) / kelems;
-  const int tiles = groups > 0 ? ((p.rows_a + 127) / 128) * (gs->b_koff > 0 ? 1 : p.group_chunks)
+  const int tiles = groups > 0 ? (gs->block_group ? p.group_chunks * (n / 128)
+                                                  : ((p.rows_a + 127) / 128) * (gs->b_koff > 0 ? 1 : p.group_chunks))
                                : ((p.rows_a + 127) / 128) * ((p.rows_b + bn - 1) / bn);
   const int sms = num_sms();
   p.num_tiles = tiles;
@@ -1041,7 +1106,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   if (splits > 1) {                                  // caller-forced uniform split
     first_split = 0;
     s_eff = splits;
-  } else if (splits <= 0) {                          // automatic
+  } else if (splits <= 0 && !(groups > 0 && gs->block_group)) {   // automatic (never with a device block list)
     const int q = tiles / sms, r = tiles % sms;
     // worthwhile when the partial wave is a visible share of the run: always for the
     // bandwidth-bound orientation, for the other only when there are few waves
@@ -1147,6 +1212,8 @@ using namespace b200;
 // Scratch that b200_gemm needs to be able to split tiles along K: a zero-initialised buffer of at
 // least this many bytes (tile counters followed by fp32 partials). The kernel leaves the counters
 // at zero again, so the buffer is zeroed once, at allocation.
+B200_API void b200_gemm_set_pdl(int enabled) { g_pdl_enabled = enabled != 0; }
+
 B200_API long long b200_gemm_workspace_bytes() {
   return 64ll << 20;   // the automatic policy needs at most 16 KB + 148 slots of 64 KB
 }
@@ -1278,6 +1345,23 @@ B200_API int b200_gemm_grouped(const void* x, const void* w, void* out, int grou
 // (multi-head latent attention: absorbing W_uk into the query and applying W_uv to the output)
 // without transposing activations to head-major order. x_koff * 2 bytes must be a multiple of 16
 // and k a multiple of 64.
+// Grouped GEMM over a device-side block list: token blocks of `m` slots each, block b uses the
+// weights of group block_group[b]; *dyn_blocks (<= max_blocks) blocks are computed. x / out are
+// [max_blocks * m] rows. Built by b200_moe_dispatch_dynamic.
+B200_API int b200_gemm_grouped_dynamic(const void* x, const void* w, void* out, int groups, int max_blocks, int m,
+                                       int n, int k, int dtype, const float* x_scale, const float* w_scale, int act,
+                                       const int* block_group, const int* dyn_blocks, void* status,
+                                       cudaStream_t stream) {
+  if (groups <= 0 || max_blocks <= 0) return 0;
+  if (block_group == nullptr || dyn_blocks == nullptr) return -9;
+  GroupSpec gs{groups, nullptr, 0, 0};
+  gs.chunks = max_blocks;
+  gs.block_group = block_group;
+  gs.dyn_blocks = dyn_blocks;
+  return gemm_impl(x, w, out, m, n, k, k, k, n, dtype, x_scale, w_scale, nullptr, nullptr, nullptr, act, 1,
+                   nullptr, 0, status, stream, nullptr, &gs);
+}
+
 B200_API int b200_gemm_colbatched(const void* x, const void* w, void* out, int groups, int m, int n, int k,
                                   long long ldx, int x_koff, long long ldc, int out_stride, void* workspace,
                                   long long workspace_bytes, void* status, cudaStream_t stream) {

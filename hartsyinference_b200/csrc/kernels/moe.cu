@@ -154,6 +154,56 @@ __global__ void moe_assign_kernel(const int* __restrict__ topk_ids, int* __restr
   slot_of[i] = slot;
 }
 
+// ---- variable-size dispatch: experts get as many blocks of `cap` slots as their token count needs
+// pass 1: position of every (token, k) pair inside its expert
+__global__ void moe_count_kernel(const int* __restrict__ topk_ids, int* __restrict__ pos_of, int* __restrict__ counts,
+                                 int pairs, int e0, int e_local) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= pairs) return;
+  const int e = topk_ids[i] - e0;
+  pos_of[i] = (e >= 0 && e < e_local) ? atomicAdd(counts + e, 1) : -1;
+}
+// pass 2 (one block): block_start[e] = sum of ceil(count / cap) over earlier experts; block list
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict__ block_start,
+                                int* __restrict__ block_group, int* __restrict__ dyn_blocks, int e_local, int cap,
+                                int max_blocks) {
+  __shared__ int s_start[1025];
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    int acc = 0;
+    for (int e = 0; e < e_local; ++e) {
+      s_start[e] = acc;
+      acc += (counts[e] + cap - 1) / cap;
+    }
+    s_start[e_local] = acc;
+    *dyn_blocks = acc < max_blocks ? acc : max_blocks;
+  }
+  __syncthreads();
+  for (int e = tid; e < e_local; e += blockDim.x) {
+    block_start[e] = s_start[e];
+    for (int b = s_start[e]; b < s_start[e + 1] && b < max_blocks; ++b) block_group[b] = e;
+  }
+}
+// pass 3: copy rows into their slots
+__global__ void moe_scatter_dynamic_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ xs,
+                                           const int* __restrict__ topk_ids, const int* __restrict__ pos_of,
+                                           const int* __restrict__ block_start, int* __restrict__ slot_of,
+                                           int top_k, int dim, int e0, int cap, int max_blocks) {
+  const int pair = blockIdx.x;
+  const int pos = pos_of[pair];
+  int slot = -1;
+  if (pos >= 0) {
+    const int blk = block_start[topk_ids[pair] - e0] + pos / cap;
+    if (blk < max_blocks) slot = blk * cap + pos % cap;
+  }
+  if (threadIdx.x == 0) slot_of[pair] = slot;
+  if (slot < 0) return;
+  const int t = pair / top_k;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(t) * dim);
+  uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<long long>(slot) * dim);
+  for (int i = threadIdx.x; i < (dim >> 3); i += blockDim.x) dst[i] = src[i];
+}
+
 // Copies token rows into their slots (bf16 rows of `dim`, 16-byte vectors). One block per pair.
 __global__ void moe_scatter_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ xs,
                                    const int* __restrict__ slot_of, int top_k, int dim) {
@@ -226,6 +276,29 @@ B200_API int b200_moe_dispatch(const void* x, void* xs, const int* topk_ids, int
                                                              capacity, chunks, chunk_tokens);
   moe_scatter_kernel<<<pairs, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(xs),
                                                 slot_of, top_k, dim);
+  return cudaGetLastError() == cudaSuccess ? 0 : -300;
+}
+
+// Variable-size dispatch. Every local expert receives ceil(tokens_for_it / cap) blocks of `cap`
+// slots, packed back to back: the grouped GEMM then runs only over blocks that hold tokens and the
+// MMA N dimension is `cap`, not a worst-case capacity. Worst case blocks: ceil(T k / cap) + e_local
+// (= max_blocks, the size of xs / block_group). scratch: int[2 * e_local + T * k] (counts,
+// block_start, positions). Outputs: slot_of [T][k], block_group [max_blocks], dyn_blocks [1].
+B200_API int b200_moe_dispatch_dynamic(const void* x, void* xs, const int* topk_ids, int* slot_of, int* scratch,
+                                       int* block_group, int* dyn_blocks, int tokens, int top_k, int dim, int e0,
+                                       int e_local, int cap, int max_blocks, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dim % 8 || e_local > 1024 || cap < 1) return -2;
+  const int pairs = tokens * top_k;
+  int* counts = scratch;
+  int* block_start = scratch + e_local;
+  int* pos_of = scratch + 2 * e_local;
+  if (cudaMemsetAsync(counts, 0, sizeof(int) * e_local, stream) != cudaSuccess) return -3;
+  moe_count_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(topk_ids, pos_of, counts, pairs, e0, e_local);
+  moe_plan_kernel<<<1, 256, 0, stream>>>(counts, block_start, block_group, dyn_blocks, e_local, cap, max_blocks);
+  moe_scatter_dynamic_kernel<<<pairs, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                        static_cast<__nv_bfloat16*>(xs), topk_ids, pos_of, block_start,
+                                                        slot_of, top_k, dim, e0, cap, max_blocks);
   return cudaGetLastError() == cudaSuccess ? 0 : -300;
 }
 

@@ -7,10 +7,10 @@ expert is column/row-sharded like a dense FFN, and ONE all-reduce sums routed an
 outputs. Routing runs on the device on every rank (deterministic, identical results), so there is
 no host round trip per layer and the layer is CUDA-graph capturable.
 
-Per pass of <= 1024 tokens: router GEMM -> ``moe_route`` -> ``moe_dispatch`` into fixed-capacity
-blocks (one per expert and run of 128 tokens) -> grouped gate_up GEMM (all local experts and runs in
-one launch, idle blocks skipped) -> GLU -> grouped down GEMM -> ``moe_combine`` (fixed order,
-deterministic).
+Per pass of <= 1024 tokens: router GEMM -> ``moe_route`` -> ``moe_dispatch_dynamic`` (device-side
+plan: every local expert gets as many blocks of ``cap`` slots as its tokens need) -> grouped
+gate_up GEMM over the blocks in use (one launch) -> GLU -> grouped down GEMM -> ``moe_combine``
+(fixed order, deterministic).
 
 Reference behaviour: src/HartsyInference.LLM/Transformer/MoeFeedForward.cs (Route:186-233,
 RouteGroupLimited:240-312, Forward:88-161 with one device-to-host copy of the router logits and
@@ -115,21 +115,21 @@ class MoeFeedForward:
     def _routed_gpu(self, h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, out: torch.Tensor,
                     accumulate: bool) -> None:
         t = h.shape[0]
-        # runs of 128 tokens: every expert keeps one block of `cap` slots per run, so no block can
-        # overflow, and one grouped launch covers all runs (the weights of an expert are fetched
-        # from HBM once; the other runs of the same weight tile hit L2)
-        chunks = (t + 127) // 128
-        cap = ops.moe_capacity(min(t, 128))
-        xs = self._xs.get((cap, chunks))
+        # variable-size dispatch: every expert gets as many blocks of `cap` slots as its tokens need
+        # (device-side plan, no host round trip), so the grouped GEMMs run only over blocks that hold
+        # tokens, read each active expert's weights once and use an MMA N of `cap`
+        cap = ops.moe_block_capacity(t, self.moe.top_k, self.moe.num_experts)
+        max_blocks = (t * self.moe.top_k + cap - 1) // cap + self.e_local
+        xs = self._xs.get((cap, max_blocks))
         if xs is None:
-            xs = torch.zeros(self.e_local * chunks * cap, self.hidden, dtype=torch.bfloat16, device=h.device)
-            self._xs[(cap, chunks)] = xs
-        slot_of, counts = ops.moe_dispatch(h, ids, self.e0, self.e_local, cap, xs, chunks=chunks)
-        gu = ops.grouped_linear(xs, self.w.gate_up, self.e_local, counts=counts, chunks=chunks)
+            xs = torch.zeros(max_blocks * cap, self.hidden, dtype=torch.bfloat16, device=h.device)
+            self._xs[(cap, max_blocks)] = xs
+        plan = ops.moe_dispatch_dynamic(h, ids, self.e0, self.e_local, cap, xs)
+        gu = ops.grouped_linear_dynamic(xs, self.w.gate_up, self.e_local, plan)
         fp8 = self.w.down.is_fp8
         a, a8 = ops.glu(gu, self.cfg.activation, emit_fp8=fp8, emit_bf16=not fp8, fp8_tile_rows=cap)
-        y = ops.grouped_linear(a8 if a8 is not None else a, self.w.down, self.e_local, counts=counts, chunks=chunks)
-        ops.moe_combine(y, slot_of, wts, out, accumulate=accumulate)
+        y = ops.grouped_linear_dynamic(a8 if a8 is not None else a, self.w.down, self.e_local, plan)
+        ops.moe_combine(y, plan.slot_of, wts, out, accumulate=accumulate)
 
     # ---------------------------------------------------------------------------------- forward
     def __call__(self, h: torch.Tensor, model=None) -> torch.Tensor:

@@ -119,6 +119,9 @@ class DecoderModel:
         self.all_reduce: Callable[[torch.Tensor], torch.Tensor] = self.comm.all_reduce
         # hook for the fused GEMM + all-reduce path: (x, weight, residual) -> reduced output
         self.row_parallel_linear: Optional[Callable] = None
+        # latency-oriented all-reduce over the symmetric heap (parallel/custom_ar.py): the row-parallel
+        # GEMM writes into its input buffer, tensors that do not fit go through ``all_reduce``
+        self.custom_ar = None
 
     # ------------------------------------------------------------------------------ weights
     def _lw(self, w: torch.Tensor, bias: Optional[torch.Tensor] = None, allow_fp8: bool = True) -> LinearWeight:
@@ -399,6 +402,12 @@ class DecoderModel:
         """Row-parallel linear: local partial product, then sum over the TP group."""
         if self.tp > 1 and self.row_parallel_linear is not None:
             return self.row_parallel_linear(x, w)
+        if self.tp > 1 and self.custom_ar is not None:
+            m = (x.data if isinstance(x, ops.Fp8Act) else x).shape[0]
+            n = w.out_features
+            if self.custom_ar.fits(m * n):
+                ops.linear(x, w, out=self.custom_ar.input(m, n))
+                return self.custom_ar.reduce(m, n)
         y = ops.linear(x, w)
         return self.all_reduce(y) if self.tp > 1 else y
 

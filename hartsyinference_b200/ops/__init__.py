@@ -24,6 +24,9 @@ from .core import (  # noqa: F401
     glu,
     gguf_linear,
     grouped_linear,
+    grouped_linear_dynamic,
+    moe_block_capacity,
+    moe_dispatch_dynamic,
     moe_capacity,
     moe_combine,
     moe_dispatch,

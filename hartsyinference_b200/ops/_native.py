@@ -25,17 +25,22 @@ vp, i32, i64, f32, u64 = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulong
 _SIGNATURES = {
     "b200_gemm": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, vp, vp, i32, i32, vp, i64, vp, vp]),
     "b200_gemm_workspace_bytes": (i64, []),
+    "b200_gemm_set_pdl": (None, [i32]),
     "b200_gemm_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, i64, vp, vp]),
     "b200_gemm_colbatched": (i32, [vp, vp, vp, i32, i32, i32, i32, i64, i32, i64, i32, vp, i64, vp, vp]),
     "b200_mla_prep": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, f32, vp]),
     "b200_mla_pick_splits": (i32, [i32, i32, i32]),
     "b200_mla_workspace_bytes": (i64, [i32, i32, i32]),
     "b200_mla_attn": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, f32, vp]),
+    "b200_attn_tc_workspace_bytes": (i64, [i32, i32, i32]),
+    "b200_attn_tc": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, f32, vp, vp, vp]),
     "b200_conv_gemm": (i32, [vp, i64, i32, vp, i32, i32, vp, vp, i64, i64, vp, i32, vp, i64, vp, vp]),
     "b200_gguf_row_bytes": (i64, [i32, i32]),
     "b200_gguf_gemv_workspace_bytes": (i64, [i32, i32]),
     "b200_gguf_gemv": (i32, [vp, i64, vp, i32, vp, i64, vp, i32, i32, i32, vp, vp]),
     "b200_gguf_dequant": (i32, [vp, i32, vp, i64, i32, vp]),
+    "b200_gemm_grouped_dynamic": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, vp]),
+    "b200_moe_dispatch_dynamic": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
     "b200_moe_route": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp]),
     "b200_moe_dispatch": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
     "b200_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
@@ -88,6 +93,11 @@ def lib() -> C.CDLL:
                     continue
                 fn.restype = res
                 fn.argtypes = args
+            from .. import config
+            try:
+                handle.b200_gemm_set_pdl(1 if config.get("pdl") else 0)
+            except AttributeError:
+                pass
             _lib = handle
     return _lib
 

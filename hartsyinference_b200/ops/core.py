@@ -20,6 +20,11 @@ def fp8_mx() -> bool:
     return config.get("fp8_scales") == "ue8m0"
 
 
+def _tc_attention() -> bool:
+    from .. import config
+    return bool(config.get("tc_attention"))
+
+
 def _alloc_sf(rows: int, k: int, tile_rows: int, device) -> torch.Tensor:
     """Blocked scale-factor array for ``rows`` x ``k`` e4m3 values (see reference.pack_sf). Bytes of
     K blocks past the end of K must be finite (they meet zero data), so a ragged last group is
@@ -388,6 +393,14 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
         return R.attention(q, k, v, causal, scale, softcap, window).to(q.dtype)
     assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
     out = torch.empty_like(q)
+    if d == 128 and hq == hkv and not causal and softcap == 0.0 and window <= 0 and tk >= 256 and _tc_attention():
+        # long bidirectional sequences (DiT blocks): tcgen05 kernel, V consumed transposed
+        L = N.lib()
+        vt = torch.empty(L.b200_attn_tc_workspace_bytes(1, hq, tk), dtype=torch.uint8, device=q.device)
+        rc = L.b200_attn_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 1, tq, tk, hq, float(scale),
+                            vt.data_ptr(), N.state(q.device).status.data_ptr(), N.stream())
+        N.check(rc, "b200_attn_tc")
+        return out
     rc = N.lib().b200_attn_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), None, None,
                                    None, None, 1, tq, tq, tk, hq, hkv, d, 16, 0, 0, int(causal), window,
                                    scale, softcap, N.stream())
@@ -617,6 +630,68 @@ def grouped_linear(x, w: LinearWeight, groups: int, act: Optional[str] = None,
                                    _gemm_dtype(w), xs_ptr, ws_ptr, _ACT[act], N.ptr(counts), chunks,
                                    ws.data_ptr(), ws.numel(), st.status.data_ptr(), N.stream())
     N.check(rc, "b200_gemm_grouped")
+    return out
+
+
+@dataclass
+class MoePlan:
+    """Device-side result of :func:`moe_dispatch_dynamic`."""
+    slot_of: torch.Tensor        # int32 [T, k], -1 for remote experts
+    block_group: torch.Tensor    # int32 [max_blocks]: local expert of every block
+    dyn_blocks: torch.Tensor     # int32 [1]: blocks in use
+    cap: int
+    max_blocks: int
+
+
+def moe_block_capacity(tokens: int, top_k: int, num_experts: int) -> int:
+    """Slots per block: about twice the expected tokens per expert, a power of two in [16, 128]."""
+    want = max(1, 2 * tokens * top_k // max(num_experts, 1))
+    for c in (16, 32, 64, 128):
+        if want <= c:
+            return c
+    return 128
+
+
+def moe_dispatch_dynamic(x: torch.Tensor, topk_ids: torch.Tensor, e0: int, e_local: int, cap: int,
+                         xs: torch.Tensor) -> MoePlan:
+    """Variable-size dispatch: every local expert gets as many ``cap``-slot blocks as its tokens
+    need, packed back to back in ``xs`` [max_blocks * cap, dim] (``max_blocks`` =
+    ceil(T k / cap) + e_local covers every routing). No host round trip."""
+    t, k = topk_ids.shape
+    dim = x.shape[1]
+    max_blocks = xs.shape[0] // cap
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+    assert max_blocks >= (t * k + cap - 1) // cap + e_local
+    dev = x.device
+    slot_of = torch.empty(t, k, dtype=torch.int32, device=dev)
+    scratch = torch.empty(2 * e_local + t * k, dtype=torch.int32, device=dev)
+    block_group = torch.zeros(max_blocks, dtype=torch.int32, device=dev)
+    dyn = torch.empty(1, dtype=torch.int32, device=dev)
+    rc = N.lib().b200_moe_dispatch_dynamic(x.data_ptr(), xs.data_ptr(), topk_ids.data_ptr(), slot_of.data_ptr(),
+                                           scratch.data_ptr(), block_group.data_ptr(), dyn.data_ptr(), t, k, dim, e0,
+                                           e_local, cap, max_blocks, N.stream())
+    N.check(rc, "b200_moe_dispatch_dynamic")
+    return MoePlan(slot_of, block_group, dyn, cap, max_blocks)
+
+
+def grouped_linear_dynamic(x, w: LinearWeight, groups: int, plan: MoePlan, act: Optional[str] = None) -> torch.Tensor:
+    """Grouped GEMM over the blocks of a :class:`MoePlan`: block b of ``x`` [max_blocks * cap, K]
+    times the weights of expert ``plan.block_group[b]``; only the blocks in use are computed."""
+    if w.is_fp8 and not isinstance(x, Fp8Act):
+        x = quant_fp8_act(x, tile_rows=plan.cap, mx=w.is_mx)
+    xd = x.data if isinstance(x, Fp8Act) else x
+    if w.is_mx and x.tile_rows != plan.cap:
+        raise ValueError("UE8M0 activations of a grouped GEMM need one scale-factor block per token block")
+    k = xd.shape[1]
+    n = w.weight.shape[0] // groups
+    assert xd.is_cuda and xd.is_contiguous() and xd.shape[0] == plan.max_blocks * plan.cap and w.weight.shape[1] == k
+    out = torch.empty(plan.max_blocks * plan.cap, n, dtype=torch.bfloat16, device=xd.device)
+    xs_ptr, ws_ptr = _scale_ptrs(x, w)
+    rc = N.lib().b200_gemm_grouped_dynamic(xd.data_ptr(), w.weight.data_ptr(), out.data_ptr(), groups, plan.max_blocks,
+                                           plan.cap, n, k, _gemm_dtype(w), xs_ptr, ws_ptr, _ACT[act],
+                                           plan.block_group.data_ptr(), plan.dyn_blocks.data_ptr(),
+                                           N.state(xd.device).status.data_ptr(), N.stream())
+    N.check(rc, "b200_gemm_grouped_dynamic")
     return out
 
 

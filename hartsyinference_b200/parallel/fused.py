@@ -111,25 +111,36 @@ def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_to
     model.row_parallel_linear = row_parallel
     model._fused_tp = fused
     if autotune_tokens > 0 and model.layers:
-        t_fused, t_nccl = _measure_row_parallel(model, comm, fused, autotune_tokens)
-        if t_fused > t_nccl:
-            model.row_parallel_linear = None
-            log.decision("TensorParallel", f"fused GEMM+all-reduce off: {t_fused * 1e3:.1f} us per layer against "
-                                           f"{t_nccl * 1e3:.1f} us for GEMM + NCCL at {autotune_tokens} tokens (tp={comm.world})")
-            return False
-        log.decision("TensorParallel", f"fused GEMM+all-reduce on for <= {MAX_TOKENS} tokens (tp={comm.world}): "
-                                       f"{t_fused * 1e3:.1f} us per layer against {t_nccl * 1e3:.1f} us for GEMM + NCCL")
-        return True
+        from .custom_ar import CustomAllReduce
+        car = CustomAllReduce(comm, MAX_TOKENS * hidden, model.device)
+        t_fused, t_car, t_nccl = _measure_row_parallel(model, comm, fused, car, autotune_tokens)
+        best = min(t_fused, t_car, t_nccl)
+        note = (f"per layer at {autotune_tokens} tokens (tp={comm.world}): fused GEMM+all-reduce {t_fused * 1e3:.1f} us, "
+                f"GEMM + peer-memory all-reduce {t_car * 1e3:.1f} us, GEMM + NCCL {t_nccl * 1e3:.1f} us")
+        if best == t_fused:
+            car.close()
+            log.decision("TensorParallel", "fused GEMM+all-reduce on; " + note)
+            return True
+        model.row_parallel_linear = None
+        if best == t_car:
+            model.custom_ar = car
+            model.all_reduce = lambda y: car(y)
+            log.decision("TensorParallel", "peer-memory all-reduce on; " + note)
+        else:
+            car.close()
+            log.decision("TensorParallel", "NCCL all-reduce kept; " + note)
+        return False
     log.decision("TensorParallel", f"fused GEMM+all-reduce on for <= {MAX_TOKENS} tokens (tp={comm.world})")
     return True
 
 
-def _measure_row_parallel(model, comm: Comm, fused: FusedRowParallel, tokens: int) -> tuple[float, float]:
+def _measure_row_parallel(model, comm: Comm, fused: FusedRowParallel, car, tokens: int) -> tuple[float, float, float]:
     """Device time (ms, summed over ranks so that every rank decides alike) of the two row-parallel
-    linears of one layer through the fused kernel and through GEMM + NCCL all-reduce."""
+    linears of one layer through the fused kernel, through GEMM + the peer-memory all-reduce, and
+    through GEMM + NCCL all-reduce."""
     lw = next((l for l in model.layers if l.o is not None and l.down is not None), None)
     if lw is None:
-        return 0.0, 1.0
+        return 0.0, 1.0, 1.0
     dev = model.device
     xs = [torch.randn(tokens, w.in_features, device=dev).to(torch.bfloat16) * 0.1 for w in (lw.o, lw.down)]
     ws = (lw.o, lw.down)
@@ -137,6 +148,11 @@ def _measure_row_parallel(model, comm: Comm, fused: FusedRowParallel, tokens: in
     def run_fused():
         for x, w in zip(xs, ws):
             fused(x, w)
+
+    def run_car():
+        for x, w in zip(xs, ws):
+            ops.linear(x, w, out=car.input(tokens, w.out_features))
+            car.reduce(tokens, w.out_features)
 
     def run_nccl():
         for x, w in zip(xs, ws):
@@ -146,7 +162,7 @@ def _measure_row_parallel(model, comm: Comm, fused: FusedRowParallel, tokens: in
     # host launch overhead (which differs: one launch against three) does not decide.
     times = []
     inner, reps = 8, 5
-    for fn in (run_fused, run_nccl):
+    for fn in (run_fused, run_car, run_nccl):
         for _ in range(3):
             fn()
         comm.barrier()
@@ -168,4 +184,4 @@ def _measure_row_parallel(model, comm: Comm, fused: FusedRowParallel, tokens: in
         del graph
     t = torch.tensor(times, device=dev, dtype=torch.float32)
     t = comm.all_reduce(t)
-    return float(t[0].item()), float(t[1].item())
+    return float(t[0].item()), float(t[1].item()), float(t[2].item())

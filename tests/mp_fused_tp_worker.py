@@ -43,6 +43,40 @@ def main():
             N.check_status(dev)
             e = rel(y, ref)
             assert e < 1.5e-2, (fp8, m, e)
+    # ---- peer-memory all-reduce kernel vs NCCL, eager and under a CUDA graph
+    from hartsyinference_b200.parallel.custom_ar import CustomAllReduce
+    car = CustomAllReduce(comm, 128 * 2048, dev)
+    for m, n in ((64, 2048), (1, 256), (128, 2048), (7, 512)):
+        for it in range(3):
+            x = torch.randn(m, n, device=dev).to(torch.bfloat16)
+            want = x.float().clone()
+            dist.all_reduce(want)
+            car.input(m, n).copy_(x)
+            got = car.reduce(m, n).float()
+            N.check_status(dev)
+            assert rel(got, want) < 8e-3, (m, n, it, rel(got, want))
+            res = torch.randn(m, n, device=dev).to(torch.bfloat16)
+            dist.broadcast(res, 0)             # the residual stream is replicated over the group
+            car.input(m, n).copy_(x)
+            got = car.reduce(m, n, residual=res).float()
+            assert rel(got, want + res.float()) < 8e-3
+    x = torch.randn(64, 2048, device=dev).to(torch.bfloat16)
+    car.input(64, 2048).copy_(x)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y1 = car.reduce(64, 2048)
+        car.input(64, 2048).copy_(y1)
+        y2 = car.reduce(64, 2048)
+    want = x.float().clone()
+    dist.all_reduce(want)
+    want = want.to(torch.bfloat16).float() * world
+    for _ in range(3):
+        car.input(64, 2048).copy_(x)
+        g.replay()
+        torch.cuda.synchronize()
+        assert rel(y2.float(), want) < 1e-2
+    N.check_status(dev)
+    car.close()
     # ---- TP model vs single-GPU model
     cfg = C.tiny("llama-3-70b", vocab_size=1024, hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=2,
                  head_dim=128, ffn_size=1024)

@@ -1,0 +1,48 @@
+"""Dense tcgen05 attention (head dim 128, bidirectional) against the fp32 statement."""
+import math
+
+import pytest
+import torch
+
+from hartsyinference_b200 import config, ops
+from hartsyinference_b200.ops import _native as N
+from hartsyinference_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture
+def tc_attention():
+    config.set_override("tc_attention", True)
+    yield
+    config.set_override("tc_attention", None)
+
+
+@pytest.mark.parametrize("tq,tk,heads", [(256, 256, 2), (128, 512, 1), (300, 1000, 3), (1024, 4608, 2), (77, 333, 4)])
+def test_tc_attention_matches_fp32(tq, tk, heads, tc_attention):
+    torch.manual_seed(tq + tk)
+    q = torch.randn(tq, heads, 128, device="cuda").to(torch.bfloat16)
+    k = torch.randn(tk, heads, 128, device="cuda").to(torch.bfloat16)
+    v = torch.randn(tk, heads, 128, device="cuda").to(torch.bfloat16)
+    out = ops.attention(q, k, v)
+    N.check_status()
+    ref = R.attention(q.cpu(), k.cpu(), v.cpu(), False, 1.0 / math.sqrt(128), 0.0, 0)
+    err = (out.float().cpu() - ref).abs().max().item()
+    assert err < 2e-2, err
+    # and against the mma.sync kernel
+    config.set_override("tc_attention", False)
+    base = ops.attention(q, k, v)
+    config.set_override("tc_attention", True)
+    assert (out.float() - base.float()).abs().max().item() < 2e-2
+
+
+def test_tc_attention_large_scores_and_determinism(tc_attention):
+    torch.manual_seed(0)
+    q = (torch.randn(384, 2, 128, device="cuda") * 3).to(torch.bfloat16)
+    k = (torch.randn(640, 2, 128, device="cuda") * 3).to(torch.bfloat16)
+    v = torch.randn(640, 2, 128, device="cuda").to(torch.bfloat16)
+    a = ops.attention(q, k, v)
+    b = ops.attention(q, k, v)
+    assert torch.equal(a, b) and torch.isfinite(a.float()).all()
+    ref = R.attention(q.cpu(), k.cpu(), v.cpu(), False, 1.0 / math.sqrt(128), 0.0, 0)
+    assert (a.float().cpu() - ref).abs().max().item() < 3e-2

@@ -6,6 +6,7 @@ import torch
 
 from hartsyinference_b200 import ops
 from hartsyinference_b200.ops import LinearWeight
+from hartsyinference_b200.ops import _native as N
 from hartsyinference_b200.ops import reference as R
 
 pytestmark = pytest.mark.gpu
@@ -223,3 +224,41 @@ def test_dispatch_and_grouped_gemm_with_several_runs_per_expert():
             e = b // chunks
             ref = xr[b * cap:(b + 1) * cap] @ wr[e * n:(e + 1) * n].t()
             assert _rel(y[b * cap:(b + 1) * cap].cpu(), ref) < 0.012, (fp8, b)
+
+
+@pytest.mark.parametrize("t,e_local,cap", [(40, 6, 16), (300, 8, 32), (256, 32, 16), (700, 4, 128)])
+def test_dynamic_dispatch_and_grouped_gemm(t, e_local, cap):
+    torch.manual_seed(t)
+    k, dim, n, e0 = 4, 256, 256, 2
+    e_total = e_local + 4
+    x = torch.randn(t, dim, device=DEV).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(e_total, device=DEV)[:k] for _ in range(t)]).to(torch.int32)
+    max_blocks = (t * k + cap - 1) // cap + e_local
+    xs = torch.zeros(max_blocks * cap, dim, dtype=torch.bfloat16, device=DEV)
+    plan = ops.moe_dispatch_dynamic(x, ids, e0, e_local, cap, xs)
+    local = (ids >= e0) & (ids < e0 + e_local)
+    assert torch.equal(plan.slot_of >= 0, local)
+    counts = torch.stack([(ids == e0 + j).sum() for j in range(e_local)])
+    assert int(plan.dyn_blocks) == int(((counts + cap - 1) // cap).sum())
+    s = plan.slot_of[local].long()
+    assert s.unique().numel() == s.numel()
+    blk = torch.div(s, cap, rounding_mode="floor")
+    assert torch.equal(plan.block_group[blk].long(), (ids[local] - e0).long())      # a slot's block belongs to its expert
+    tok = torch.arange(t, device=DEV)[:, None].expand(t, k)[local]
+    assert torch.equal(xs[s], x[tok])
+    for fp8 in (False, True):
+        w = (torch.randn(e_local * n, dim, device=DEV) * 0.05).to(torch.bfloat16)
+        lw = LinearWeight.from_dense(w, fp8=fp8)
+        y = ops.grouped_linear_dynamic(xs, lw, e_local, plan)
+        N.check_status()
+        wr = R.dequant_fp8_weight(lw.weight.cpu(), lw.scale.cpu()) if fp8 else w.float().cpu()
+        if fp8:
+            xq = ops.quant_fp8_act(xs, tile_rows=cap)
+            xr = R.dequant_fp8_act(xq.data.cpu(), xq.scales_fp32().cpu())
+        else:
+            xr = xs.float().cpu()
+        e_of = (ids[local] - e0).long().cpu()
+        sc = s.cpu()
+        for j in range(0, sc.numel(), max(1, sc.numel() // 50)):     # a sample of the assigned slots
+            ref = xr[sc[j]] @ wr[e_of[j] * n:(e_of[j] + 1) * n].t()
+            assert _rel(y[sc[j]].cpu(), ref) < 0.015, (fp8, j)
