@@ -150,6 +150,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Thread-block clusters: rank of this CTA, cluster-wide barrier, loads from a peer CTA's shared
+// memory (distributed shared memory).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_smem_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute
 // may start before its predecessor in the stream has finished; pdl_wait() blocks until the
 // predecessor grid has completed and its writes are visible (a no-op for an ordinary launch).

@@ -96,6 +96,10 @@ struct GemmParams {
   // [0, tap_kblocks * 64). 0 = ordinary GEMM.
   int tap_kblocks;
   int tap_shift[28];
+  // 1: every tile is split over the CTAs of a thread-block cluster (cluster size = splits, one work
+  // item per CTA); the partials stay in shared memory and are summed through distributed shared
+  // memory, each CTA reducing its share of the tile. No scratch traffic, no second kernel.
+  int cluster_reduce;
   // 1: every tile is split and a second kernel (splitk_reduce_kernel) sums the partials with the
   // whole machine; 0: the last CTA to arrive at a split tile sums them inside this kernel.
   int external_reduce;
@@ -373,7 +377,7 @@ __device__ __forceinline__ void finish_item(const GemmParams& p, const WorkItem&
     }
     return;
   }
-  if (it.slot < 0 || p.external_reduce) return;
+  if (it.slot < 0 || p.external_reduce || p.cluster_reduce) return;
   __threadfence();
   epilogue_barrier();
   if (et == 0) {
@@ -747,7 +751,16 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
               float v[32];
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-              emit_chunk<BN>(p, v, it, row_local, c);
+              if (p.cluster_reduce) {
+                // partial of this CTA's K range, kept in its own shared memory: [BN columns][128 rows]
+                // fp32 over the (now idle) pipeline stages
+                float* part = reinterpret_cast<float*>(smem);
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (c * 32 + j < BN) part[(c * 32 + j) * 128 + row_local] = v[j];
+              } else {
+                emit_chunk<BN>(p, v, it, row_local, c);
+              }
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -880,6 +893,43 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
 
   // the single-lane roles rejoin their warps before the CTA-wide barrier
   __syncwarp();
+  if (p.cluster_reduce) {
+    // every CTA of the cluster has its partial in shared memory -> each sums its share of the tile
+    // over all CTAs (fixed order: deterministic), applies the epilogue and stores C
+    cluster_sync_all();
+    if (warp >= 2) {
+      const WorkItem it = decode_item(p, blockIdx.x, tiles_a, total_kblocks);
+      const int et = threadIdx.x - 64;
+      const uint32_t rank = cluster_ctarank();
+      const int total4 = BN * 32;                                  // float4 groups of the tile
+      const int per = (total4 + p.splits - 1) / p.splits;
+      const int lo = static_cast<int>(rank) * per, hi = min(total4, lo + per);
+      const uint32_t part = smem_u32(smem);
+      for (int e4 = lo + et; e4 < hi; e4 += 256) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < p.splits; ++r) {
+          const float4 t = ld_dsmem_f4(part + e4 * 16, static_cast<uint32_t>(r));
+          acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+        }
+        const int e = e4 * 4;
+        const int a_row = it.ta * kTileA + (e & 127), b_row = it.tb * BN + (e >> 7);
+        if (a_row >= p.rows_a || b_row >= p.rows_b) continue;
+        const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (a_row + u >= p.rows_a) break;
+          if (p.swap_out) {
+            const long long col = swap_col(p, a_row + u);
+            p.out[static_cast<long long>(b_row) * p.ldc + col] = __float2bfloat16(apply_epilogue(p, v[u], b_row, col));
+          } else {
+            p.out[static_cast<long long>(a_row + u) * p.ldc + b_row] =
+                __float2bfloat16(apply_epilogue(p, v[u], a_row + u, b_row));
+          }
+        }
+      }
+    }
+    cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
+  }
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -939,6 +989,7 @@ int make_kmajor_map(CUtensorMap* out, const void* base, int elem_bytes, long lon
 
 // Programmatic dependent launch of the GEMM (see the producer warp); switchable for A/B timing.
 static bool g_pdl_enabled = true;
+static bool g_cluster_reduce = true;
 
 template <int kMode, int BN, int kAtoms>
 int launch_gemm(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, int grid,
@@ -957,11 +1008,18 @@ int launch_gemm(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& t
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (p.cluster_reduce) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = static_cast<unsigned>(p.splits);
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<kMode, BN, kAtoms>, p, ta, tb) != cudaSuccess) return -300;
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e) - 300;
@@ -1136,6 +1194,21 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   p.first_split_tile = first_split;
   p.splits = s_eff;
   p.external_reduce = (first_split == 0 && s_eff > 1 && ar == nullptr) ? 1 : 0;
+  int cluster = 1;
+  if (p.external_reduce && g_cluster_reduce && dtype != 1 && splits <= 0 && groups == 0 && cs == nullptr) {
+    // power-of-two cluster of at most 8 CTAs (portable size), every CTA exactly one K range
+    int c = 1;
+    while (c * 2 <= s_eff && c * 2 <= 8) c *= 2;
+    int kps = (total_kblocks + c - 1) / c;
+    if (mx) kps = (kps + 3) / 4 * 4;
+    if (c > 1 && (total_kblocks + kps - 1) / kps == c) {
+      cluster = c;
+      p.splits = s_eff = c;
+      p.kblocks_per_split = kps;
+      p.external_reduce = 0;
+      p.cluster_reduce = 1;
+    }
+  }
   p.split_counter = static_cast<uint32_t*>(workspace);
   p.split_ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kSplitCounterBytes);
 
@@ -1159,7 +1232,9 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   if (rc) return rc;
 
   const long long items = first_split + static_cast<long long>(tiles - first_split) * s_eff;
-  const int grid = static_cast<int>(items < sms ? items : sms);
+  // a cluster launch runs one work item per CTA: the grid is the item count, not the SM count
+  const int grid = p.cluster_reduce ? static_cast<int>(items) : static_cast<int>(items < sms ? items : sms);
+  (void)cluster;
 
   if (mx) {
     if (swap) {
@@ -1213,6 +1288,7 @@ using namespace b200;
 // least this many bytes (tile counters followed by fp32 partials). The kernel leaves the counters
 // at zero again, so the buffer is zeroed once, at allocation.
 B200_API void b200_gemm_set_pdl(int enabled) { g_pdl_enabled = enabled != 0; }
+B200_API void b200_gemm_set_cluster_reduce(int enabled) { g_cluster_reduce = enabled != 0; }
 
 B200_API long long b200_gemm_workspace_bytes() {
   return 64ll << 20;   // the automatic policy needs at most 16 KB + 148 slots of 64 KB
