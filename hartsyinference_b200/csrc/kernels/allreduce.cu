@@ -80,6 +80,8 @@ __device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& v) {
 }
 
 __global__ void __launch_bounds__(512) allreduce_kernel(const AllReduceArgs a) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ uint32_t s_ok;
   const int tid = threadIdx.x, b = blockIdx.x;
   const uint32_t e = *reinterpret_cast<volatile uint32_t*>(a.epoch) + 1u;
@@ -175,6 +177,6 @@ B200_API int b200_allreduce(void* const* in, void* const* out, void* const* flag
   int blocks = static_cast<int>((slice + 511) / 512);
   if (blocks < 1) blocks = 1;
   if (blocks > kArMaxBlocks) blocks = kArMaxBlocks;
-  allreduce_kernel<<<blocks, 512, 0, stream>>>(a);
+  launch_pdl(allreduce_kernel, dim3(blocks), dim3(512), 0, stream, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -300;
 }

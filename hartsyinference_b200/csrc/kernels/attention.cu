@@ -222,6 +222,8 @@ __device__ __forceinline__ void warp_tile(WarpState<D>& st, const uint32_t (&qf)
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_decode_kernel(const AttnParams p) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int kStages = 3;
   constexpr int kTileBytes = kTileTokens * D * 2;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -335,6 +337,8 @@ attn_decode_kernel(const AttnParams p) {
 
 template <int D>
 __global__ void attn_combine_kernel(const AttnParams p) {
+  pdl_wait();
+  pdl_trigger();
   const int seq = blockIdx.x, head = blockIdx.y;
   const long long base = (static_cast<long long>(seq) * p.hq + head) * p.splits;
   float mm = -INFINITY;
@@ -516,18 +520,18 @@ B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_
   if (d == 128) {
     static bool done = false;
     if (!done) { cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
-    attn_decode_kernel<128><<<grid, kAttnThreads, smem, stream>>>(p);
+    launch_pdl(attn_decode_kernel<128>, grid, dim3(kAttnThreads), smem, stream, p);
   } else {
     static bool done = false;
     if (!done) { cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
-    attn_decode_kernel<64><<<grid, kAttnThreads, smem, stream>>>(p);
+    launch_pdl(attn_decode_kernel<64>, grid, dim3(kAttnThreads), smem, stream, p);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return -static_cast<int>(e) - 300;
   if (p.splits > 1) {
     dim3 cg(seqs, hq);
-    if (d == 128) attn_combine_kernel<128><<<cg, 128, 0, stream>>>(p);
-    else attn_combine_kernel<64><<<cg, 64, 0, stream>>>(p);
+    if (d == 128) launch_pdl(attn_combine_kernel<128>, cg, dim3(128), 0, stream, p);
+    else launch_pdl(attn_combine_kernel<64>, cg, dim3(64), 0, stream, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return -static_cast<int>(e) - 400;
   }

@@ -73,6 +73,7 @@ struct NormParams {
 // dim <= 8 * 1024 (blockDim 1024) .. generic fallback re-reads the row.
 template <int kMaxVec>
 __global__ void __launch_bounds__(1024) norm_kernel(const NormParams p) {
+  pdl_wait();
   pdl_trigger();   // a GEMM launched behind this kernel may start fetching its weights now
   __shared__ float red[32];
   const int row = blockIdx.x;
@@ -216,6 +217,7 @@ __global__ void __launch_bounds__(1024) norm_kernel(const NormParams p) {
 __global__ void quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out,
                                  float* __restrict__ scales, int rows, int dim, long long ld,
                                  int sf_tile_rows) {
+  pdl_wait();
   pdl_trigger();
   const int groups = dim >> 7;
   const long long total = static_cast<long long>(rows) * groups * 16;   // one thread per 8 values
@@ -320,6 +322,7 @@ __global__ void quant_fp8_weight_kernel(const __nv_bfloat16* __restrict__ w,
 __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                            uint8_t* __restrict__ out_fp8, float* __restrict__ out_scale, int rows,
                            int f, int act, int sf_tile_rows) {
+  pdl_wait();
   pdl_trigger();
   const int nvec = f >> 3;
   const long long total = static_cast<long long>(rows) * nvec;
@@ -403,6 +406,8 @@ struct RopeParams {
 };
 
 __global__ void rope_kv_kernel(const RopeParams p) {
+  pdl_wait();
+  pdl_trigger();
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int heads = p.hq + 2 * p.hkv;
@@ -696,10 +701,10 @@ B200_API int b200_norm(const void* x, const void* residual, void* residual_out, 
   // threads: multiple of 32 covering the row with at most 2 vectors per thread
   int threads = ((nvec + 31) / 32) * 32;
   if (threads <= 1024) {
-    norm_kernel<1><<<rows, threads < 32 ? 32 : threads, 0, stream>>>(p);
+    launch_pdl(norm_kernel<1>, dim3(rows), dim3(threads < 32 ? 32 : threads), 0, stream, p);
   } else {
     threads = (((nvec + 1) / 2 + 31) / 32) * 32;
-    norm_kernel<2><<<rows, threads, 0, stream>>>(p);
+    launch_pdl(norm_kernel<2>, dim3(rows), dim3(threads), 0, stream, p);
   }
   CHECK_LAUNCH();
   return 0;
@@ -712,9 +717,8 @@ B200_API int b200_quant_fp8(const void* x, void* out, float* scales, int rows, i
   if (rows <= 0) return 0;
   if (dim % 128 != 0 || ld % 8 != 0) return -2;
   const long long n = static_cast<long long>(rows) * (dim / 8);
-  quant_fp8_kernel<<<grid_for(n, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
-                                                         static_cast<uint8_t*>(out), scales, rows,
-                                                         dim, ld, sf_tile_rows);
+  launch_pdl(quant_fp8_kernel, dim3(grid_for(n, 256)), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x),
+             static_cast<uint8_t*>(out), scales, rows, dim, ld, sf_tile_rows);
   CHECK_LAUNCH();
   return 0;
 }
@@ -734,10 +738,8 @@ B200_API int b200_glu(const void* in, void* out, void* out_fp8, float* out_scale
   if (rows <= 0) return 0;
   if (f % 8 != 0 || (out_fp8 && f % 128 != 0)) return -2;
   const long long n = static_cast<long long>(rows) * (f / 8);
-  glu_kernel<<<grid_for(n, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in),
-                                                   static_cast<__nv_bfloat16*>(out),
-                                                   static_cast<uint8_t*>(out_fp8), out_scale, rows,
-                                                   f, act, sf_tile_rows);
+  launch_pdl(glu_kernel, dim3(grid_for(n, 256)), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in),
+             static_cast<__nv_bfloat16*>(out), static_cast<uint8_t*>(out_fp8), out_scale, rows, f, act, sf_tile_rows);
   CHECK_LAUNCH();
   return 0;
 }
@@ -767,7 +769,7 @@ B200_API int b200_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_c
   const long long warps = static_cast<long long>(tokens) * (hq + 2 * hkv);
   const int block = 256;
   const long long blocks = (warps * 32 + block - 1) / block;
-  rope_kv_kernel<<<static_cast<int>(blocks), block, 0, stream>>>(p);
+  launch_pdl(rope_kv_kernel, dim3(static_cast<unsigned>(blocks)), dim3(block), 0, stream, p);
   CHECK_LAUNCH();
   return 0;
 }

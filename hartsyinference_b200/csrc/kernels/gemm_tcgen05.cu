@@ -459,6 +459,8 @@ __device__ __forceinline__ bool ar_reduce_tile(const GemmParams& p, int ta, uint
 // the machine is also reduced by the whole machine instead of by one CTA per tile.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p, int bn, int tiles_a,
                                                             int total_kblocks) {
+  pdl_wait();
+  pdl_trigger();
   const int e4 = blockIdx.x * blockDim.x + threadIdx.x;
   if (e4 >= bn * 32) return;
   const WorkItem it = decode_item(p, p.first_split_tile + static_cast<long long>(blockIdx.y) * p.splits,
@@ -539,6 +541,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
   volatile uint32_t* abort_flag = &bars->abort_flag;
+  pdl_trigger();   // the next kernel may be scheduled; it waits for this grid to finish before it reads
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -988,7 +991,9 @@ int make_kmajor_map(CUtensorMap* out, const void* base, int elem_bytes, long lon
 }
 
 // Programmatic dependent launch of the GEMM (see the producer warp); switchable for A/B timing.
-static bool g_pdl_enabled = true;
+}  // namespace b200
+bool b200::g_b200_pdl = true;
+namespace b200 {
 static bool g_cluster_reduce = true;
 
 template <int kMode, int BN, int kAtoms>
@@ -1010,7 +1015,7 @@ int launch_gemm(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& t
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = g_b200_pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (p.cluster_reduce) {
@@ -1274,8 +1279,8 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   }
   if (rc == 0 && p.external_reduce) {
     const dim3 rgrid((bn * 32 + 255) / 256, tiles);
-    splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(p, bn, (p.rows_a + kTileA - 1) / kTileA, total_kblocks);
-    if (cudaGetLastError() != cudaSuccess) rc = -300;
+    if (launch_pdl(splitk_reduce_kernel, rgrid, dim3(256), 0, stream, p, bn, (p.rows_a + kTileA - 1) / kTileA,
+                   total_kblocks) != cudaSuccess) rc = -300;
   }
   return rc;
 }
@@ -1287,7 +1292,7 @@ using namespace b200;
 // Scratch that b200_gemm needs to be able to split tiles along K: a zero-initialised buffer of at
 // least this many bytes (tile counters followed by fp32 partials). The kernel leaves the counters
 // at zero again, so the buffer is zeroed once, at allocation.
-B200_API void b200_gemm_set_pdl(int enabled) { g_pdl_enabled = enabled != 0; }
+B200_API void b200_gemm_set_pdl(int enabled) { g_b200_pdl = enabled != 0; }
 B200_API void b200_gemm_set_cluster_reduce(int enabled) { g_cluster_reduce = enabled != 0; }
 
 B200_API long long b200_gemm_workspace_bytes() {
