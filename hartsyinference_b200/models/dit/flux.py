@@ -191,6 +191,26 @@ class FluxTransformer:
         temb = temb + ops.linear(ops.linear(pooled.to(dt), self.p_in, act="silu"), self.p_out).float()
         return temb.to(dt)
 
+    def enable_block_streaming(self) -> None:
+        """Keep the transformer blocks in pinned host memory and stream them through two device
+        slots during the forward pass (low-VRAM mode; see engine/block_streaming.py)."""
+        from ...engine.block_streaming import BlockStreamer
+        self._streamers = {"double": BlockStreamer(self.double, self.device), "single": BlockStreamer(self.single, self.device)}
+        # the resident copies are dropped: the streamer owns the (host) weights now
+        self.double = [None] * len(self.double)
+        self.single = [None] * len(self.single)
+
+    def _blocks(self, blocks, kind: str):
+        st = getattr(self, "_streamers", None)
+        if not st:
+            yield from blocks
+            return
+        s = st[kind]
+        s.prime()
+        for i in range(len(s)):
+            yield s.block(i)
+        s.evict_all()
+
     def _attend(self, q, k, v, batch: int) -> torch.Tensor:
         """q, k, v [B * S, Hl, D] -> [B * S, Hl * D]; one attention call per sample."""
         s = q.shape[0] // batch
@@ -247,7 +267,7 @@ class FluxTransformer:
         use_cache = step_cache is not None and step_cache.enabled and whole and len(self.double) > 0
         first_x_i = None
         skip_rest = False
-        for bi, (wi, wt) in enumerate(self.double):
+        for bi, (wi, wt) in enumerate(self._blocks(self.double, "double")):
             if skip_rest:
                 break
             mod_i, mod_t = modulation(temb_act, wi.mod), modulation(temb_act, wt.mod)
@@ -282,7 +302,7 @@ class FluxTransformer:
                     joint = torch.cat([torch.cat([x_t[i * S_t:(i + 1) * S_t], x_i[i * S_i:(i + 1) * S_i]], 0) for i in range(B)], 0)
             cj, sj = (cos, sin) if B == 1 else (cos.repeat(B, 1), sin.repeat(B, 1))
             qkv_cols = 3 * self.hl * D
-            for w in self.single:
+            for w in self._blocks(self.single, "single"):
                 mod = modulation(temb_act, w.mod)
                 xn, _, xq = ops.norm(joint, None, shift=mod[:, 0:H], scale=mod[:, H:2 * H], rows_per_batch=S, layernorm=True,
                                      emit_fp8=self.fp8 and w.qkv_mlp.is_fp8, emit_bf16=not (self.fp8 and w.qkv_mlp.is_fp8))

@@ -39,5 +39,6 @@ from .core import (  # noqa: F401
     quant_fp8_weight,
     repetition_penalty_,
     rope_kv,
+    selective_scan,
 )
 from . import reference  # noqa: F401

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "b200_mla_attn": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, f32, vp]),
     "b200_attn_tc_workspace_bytes": (i64, [i32, i32, i32]),
     "b200_attn_tc": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, f32, vp, vp, vp]),
+    "b200_selective_scan": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "b200_conv_gemm": (i32, [vp, i64, i32, vp, i32, i32, vp, vp, i64, i64, vp, i32, vp, i64, vp, vp]),
     "b200_gguf_row_bytes": (i64, [i32, i32]),
     "b200_gguf_gemv_workspace_bytes": (i64, [i32, i32]),

@@ -929,3 +929,23 @@ def causal_conv3d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     N.check(rc, "b200_conv_gemm")
     y = out.view(t, hp, wp, co)[:, :h, :w_, :].permute(3, 0, 1, 2).contiguous().to(x.dtype)
     return y[None] if batched else y
+
+
+# ---------------------------------------------------------------------------------------------
+# state-space scan
+# ---------------------------------------------------------------------------------------------
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
+                   d: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+    """Mamba selective scan on the device: x [T, Di] bf16, dt [T, Di] fp32, a [Di, N] fp32 (negative),
+    b / c [T, N] bf16, d [Di] fp32, state [Di, N] fp32 (updated in place). Returns y [T, Di] bf16."""
+    t, di = x.shape
+    n = a.shape[1]
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and dt.dtype == torch.float32
+    assert dt.is_contiguous() and a.is_contiguous() and state.is_contiguous() and state.dtype == torch.float32
+    b = b.to(torch.bfloat16).contiguous()
+    c = c.to(torch.bfloat16).contiguous()
+    y = torch.empty(t, di, dtype=torch.bfloat16, device=x.device)
+    rc = N.lib().b200_selective_scan(x.data_ptr(), dt.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                     d.data_ptr(), state.data_ptr(), y.data_ptr(), t, di, n, N.stream())
+    N.check(rc, "b200_selective_scan")
+    return y

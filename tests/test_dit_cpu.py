@@ -91,3 +91,23 @@ def test_image_and_video_services_end_to_end_tiny():
     assert len(vid.frames) == 5 and vid.width == 32 and len(vid.frames[0]) == 32 * 32 * 3 and steps == [1, 2, 3]
     assert len(eng.loaded_pipeline_keys) == 2
     eng.free_memory()
+
+
+def test_flux_block_streaming_gives_the_same_output():
+    from hartsyinference_b200.models.dit import flux as F
+    cfg = F.tiny_flux(num_heads=4, head_dim=32)
+    g = torch.Generator().manual_seed(5)
+    img = torch.randn(1, 16, cfg.in_channels, generator=g)
+    txt = torch.randn(1, 6, cfg.context_dim, generator=g)
+    pooled = torch.randn(1, cfg.pooled_dim, generator=g)
+    ii, it = F.flux_ids(4, 4, 6)
+    args = (img, txt, torch.tensor([0.6]), pooled, ii, it, torch.tensor([3.5]))
+    a = F.FluxTransformer(cfg, "cpu", seed=9)
+    ref = a.forward(*args)
+    b = F.FluxTransformer(cfg, "cpu", seed=9)
+    b.enable_block_streaming()
+    out = b.forward(*args)
+    assert torch.equal(out, ref)
+    assert b._streamers["double"].uploads >= len(b._streamers["double"])
+    out2 = b.forward(*args)            # a second pass streams the blocks again
+    assert torch.equal(out2, ref)

@@ -146,3 +146,29 @@ def test_causal_conv3d_as_gemm_matches_torch(ci, co, k, t, h, w):
     err = (y.float().cpu() - ref).abs().max() / ref.abs().max()
     assert err < 2e-2, err
     N.check_status()
+
+
+@pytest.mark.gpu
+def test_mamba_gpu_matches_cpu_and_scan_kernel():
+    from hartsyinference_b200.models.ssm import MambaModel, tiny_mamba
+    from hartsyinference_b200.models.ssm.mamba import selective_scan
+    torch.manual_seed(3)
+    t, di, n = 37, 256, 16
+    x = torch.randn(t, di).to(torch.bfloat16)
+    dt = torch.rand(t, di) * 0.1
+    a = -torch.rand(di, n) * 2
+    b, c = torch.randn(t, n).to(torch.bfloat16), torch.randn(t, n).to(torch.bfloat16)
+    d = torch.randn(di)
+    st_c = torch.randn(di, n)
+    st_g = st_c.clone().cuda()
+    y_c = selective_scan(x, dt, a, b, c, d, st_c)
+    y_g = selective_scan(x.cuda(), dt.cuda(), a.cuda(), b.cuda(), c.cuda(), d.cuda(), st_g)
+    assert (y_g.float().cpu() - y_c.float()).abs().max() < 0.05 * y_c.float().abs().max()
+    assert torch.allclose(st_g.cpu(), st_c, atol=1e-3, rtol=1e-3)
+    cfg = tiny_mamba()
+    mc, mg = MambaModel(cfg, "cpu", seed=5), MambaModel(cfg, "cuda", seed=5)
+    ids = torch.randint(0, cfg.vocab_size, (23,))
+    lc = mc.logits(mc.forward(ids, mc.new_state()))
+    lg = mg.logits(mg.forward(ids, mg.new_state())).cpu()
+    cos = torch.nn.functional.cosine_similarity(lc, lg, dim=-1)
+    assert cos.min() > 0.99, cos.min()
