@@ -105,6 +105,13 @@ class MambaModel:
         self.norm_f = t("backbone.norm_f.weight", cfg.d_model, ones=True).to(dt16).to(dev)
         self.layers: list[_Layer] = []
         di, n, r = cfg.d_inner, cfg.d_state, cfg.rank
+        # the GEMM wants row pitches that are multiples of 16 bytes: pad the dt rank to a multiple
+        # of 8 with zero rows (x_proj) / zero columns (dt_proj); the result is unchanged
+        self.r_pad = rp = (r + 7) // 8 * 8
+
+        def pad_rows(w, rows):
+            return w if w.shape[0] == rows else torch.cat([w, torch.zeros(rows - w.shape[0], w.shape[1], dtype=w.dtype)])
+
         for i in range(cfg.n_layer):
             p = f"backbone.layers.{i}."
             a_log = t(p + "mixer.A_log", di, n)
@@ -116,9 +123,10 @@ class MambaModel:
                 in_proj=LinearWeight(t(p + "mixer.in_proj.weight", 2 * di, cfg.d_model).to(dt16).to(dev)),
                 conv_w=t(p + "mixer.conv1d.weight", di, 1, cfg.d_conv, std=0.2).reshape(di, cfg.d_conv).float().to(dev),
                 conv_b=t(p + "mixer.conv1d.bias", di).float().to(dev),
-                x_proj=LinearWeight(t(p + "mixer.x_proj.weight", r + 2 * n, di).to(dt16).to(dev)),
-                dt_proj=LinearWeight(t(p + "mixer.dt_proj.weight", di, r, std=r ** -0.5).to(dt16).to(dev), None,
-                                     dt_b.to(dt16).to(dev)),
+                x_proj=LinearWeight((lambda w: torch.cat([pad_rows(w[:r], rp), w[r:]]))(
+                    t(p + "mixer.x_proj.weight", r + 2 * n, di)).to(dt16).to(dev)),
+                dt_proj=LinearWeight(pad_rows(t(p + "mixer.dt_proj.weight", di, r, std=r ** -0.5).t().contiguous(), rp)
+                                     .t().contiguous().to(dt16).to(dev), None, dt_b.to(dt16).to(dev)),
                 a=(-torch.exp(a_log.float())).contiguous().to(dev),
                 d=t(p + "mixer.D", di, ones=True).float().to(dev),
                 out_proj=LinearWeight(t(p + "mixer.out_proj.weight", cfg.d_model, di).to(dt16).to(dev))))
@@ -130,7 +138,7 @@ class MambaModel:
 
     def _mixer(self, lw: _Layer, h: torch.Tensor, conv_state: torch.Tensor, ssm_state: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
-        di, n, r, k = cfg.d_inner, cfg.d_state, cfg.rank, cfg.d_conv
+        di, n, r, k = cfg.d_inner, cfg.d_state, self.r_pad, cfg.d_conv
         xz = ops.linear(h, lw.in_proj)                                  # [T, 2 Di]
         x, z = xz[:, :di], xz[:, di:]
         # causal depthwise conv over [previous k - 1 inputs | x]
