@@ -98,6 +98,7 @@ declare("tc_attention", bool, True, "dense non-causal attention with head dim 12
 declare("cluster_splitk", bool, False, "reduce the K splits of small GEMMs through distributed shared memory of a thread-block cluster instead of a second kernel")
 declare("pdl", bool, True, "launch GEMMs with programmatic dependent launch so that weight tiles are requested while the preceding kernel still runs")
 declare("fp8_scales", str, "ue8m0", "block-scale format of fp8 linears: ue8m0 (power-of-two scales applied by the tensor core) or fp32 (promoted per K block by the epilogue warps)")
+declare("gguf_resident", bool, False, "keep Q8_0 / Q4_K GGUF linears as quantised blocks on the device (integer-dot GEMV at decode) instead of dequantising at load")
 declare("low_vram", bool, False, "stream transformer blocks from pinned host memory instead of keeping weights resident")
 declare("model_cache_dir", str, "~/.hartsyinference/models", "where resolved checkpoints are cached")
 declare("same_gpu_concurrent", bool, False, "allow two requests to share one device slot")

@@ -142,8 +142,13 @@ def _load_gguf(p: Path, device, comm, fp8) -> LoadedLLM:
         g = hf_to_gguf.get(name)
         return None if g is None else f.get(g, torch.bfloat16)
 
-    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
+    from ... import config as _config
+    resident = bool(_config.get("gguf_resident")) and (comm is None or comm.world == 1)
+    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device) and not resident)
     model.load_state_dict(get)
+    if resident:
+        kept = _keep_gguf_blocks(model, f, hf_to_gguf)
+        log.decision("Load", f"{kept} linear(s) kept as GGUF blocks on {model.device}")
     tok = Tokenizer.from_gguf_metadata(f.metadata) if "tokenizer.ggml.tokens" in f.metadata else ByteTokenizer(vocab_size=cfg.vocab_size)
     src = f.metadata.get("tokenizer.chat_template")
     tokens = f.metadata.get("tokenizer.ggml.tokens") or []
@@ -153,6 +158,41 @@ def _load_gguf(p: Path, device, comm, fp8) -> LoadedLLM:
     tpl = ChatTemplate(src, bos, eos) if src else ChatTemplate.for_arch(cfg.arch)
     log.info(f"[Load] {p.name}: GGUF v{f.version} {cfg.arch} {cfg.num_layers}L hidden {cfg.hidden_size}")
     return LoadedLLM(model, tok, tpl, cfg, str(p))
+
+
+def _keep_gguf_blocks(model: DecoderModel, f: GgufFile, hf_to_gguf: dict[str, str]) -> int:
+    """Replace the dense linears of a single-rank model by :class:`ops.GgufWeight` views of the
+    file's own Q8_0 / Q4_K blocks (fused q/k/v and gate/up rows are concatenated block rows).
+    A linear whose tensors have mixed or unsupported types keeps its dequantised weight."""
+    from ... import ops
+
+    def blocks_of(hf_names: list[str]):
+        raws, typ, k = [], None, None
+        for hn in hf_names:
+            g = hf_to_gguf.get(hn)
+            if g is None:
+                return None
+            t, shape = f.info(g)
+            if len(shape) != 2 or not ops.GgufWeight.supported(t, shape[1]) or (typ is not None and (t, shape[1]) != (typ, k)):
+                return None
+            typ, k = t, shape[1]
+            raws.append(ops.GgufWeight.from_raw(f.raw(g).clone(), t, shape[0], shape[1]).blocks)
+        return ops.GgufWeight(torch.cat(raws).to(model.device).contiguous(), typ, k)
+
+    kept = 0
+    for i, lw in enumerate(model.layers):
+        p = f"model.layers.{model.layer0 + i}."
+        plan = {"qkv": [p + f"self_attn.{n}_proj.weight" for n in ("q", "k", "v")], "o": [p + "self_attn.o_proj.weight"],
+                "gate_up": [p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"], "down": [p + "mlp.down_proj.weight"]}
+        for attr, names in plan.items():
+            cur = getattr(lw, attr)
+            if cur is None or cur.bias is not None:
+                continue
+            gw = blocks_of(names)
+            if gw is not None and gw.out_features == cur.out_features and gw.k == cur.in_features:
+                setattr(lw, attr, gw)
+                kept += 1
+    return kept
 
 
 def save_hf_checkpoint(model_cfg: dict, tensors: dict[str, torch.Tensor], out_dir: str | Path) -> None:

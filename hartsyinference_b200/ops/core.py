@@ -166,6 +166,10 @@ def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.T
     ``x`` is a bf16 tensor [M, K] or an :class:`Fp8Act`. With an fp8 weight a bf16 ``x`` is
     quantised on the fly (1x128 groups). ``gate`` is a per-output-feature vector [N].
     """
+    if isinstance(w, GgufWeight):
+        if act is not None or gate is not None or residual is not None or isinstance(x, Fp8Act):
+            raise ValueError("GGUF block weights take bf16 activations and no fused epilogue")
+        return gguf_linear(x, w, out=out)
     xd = x.data if isinstance(x, Fp8Act) else x
     if not xd.is_cuda:
         if isinstance(x, Fp8Act):
@@ -823,6 +827,9 @@ class GgufWeight:
     ggml_type: int
     k: int
     bias: Optional[torch.Tensor] = None
+
+    is_fp8 = False        # so that model code can treat it like a LinearWeight
+    is_mx = False
 
     @property
     def out_features(self) -> int:

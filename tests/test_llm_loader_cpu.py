@@ -85,3 +85,24 @@ def test_quantised_gguf_stays_close(tmp_path):
     wa, wb = a.model.layers[0].qkv.weight.float(), b.model.layers[0].qkv.weight.float()
     assert ((wa - wb).norm() / wa.norm()).item() < 0.02
     assert not a.config.tie_embeddings
+
+
+def test_gguf_blocks_kept_resident_give_the_same_tokens(tmp_path):
+    from hartsyinference_b200 import config, ops
+    cfg, t = _synthetic(3, qkv_bias=False)
+    _to_gguf(cfg, t, tmp_path / "q.gguf", quant=G.GGML_TYPES["Q8_0"])
+    a = load_llm(tmp_path / "q.gguf", "cpu")
+    config.set_override("gguf_resident", True)
+    try:
+        b = load_llm(tmp_path / "q.gguf", "cpu")
+    finally:
+        config.set_override("gguf_resident", None)
+    lw = b.model.layers[0]
+    assert isinstance(lw.qkv, ops.GgufWeight) and isinstance(lw.down, ops.GgufWeight)
+    assert lw.qkv.out_features == a.model.layers[0].qkv.out_features
+    p = SamplingParams(greedy=True, max_tokens=8, ignore_eos=True)
+    ea = LLMEngine(a.model, num_pages=32, page_size=16, max_batch=2, prefill_chunk=64, max_model_len=128)
+    eb = LLMEngine(b.model, num_pages=32, page_size=16, max_batch=2, prefill_chunk=64, max_model_len=128)
+    prompt = [[3, 9, 27, 81, 5]]
+    assert ea.generate(prompt, p) == eb.generate(prompt, p)
+    assert b.model.weight_bytes() < a.model.weight_bytes()
