@@ -43,7 +43,7 @@ def test_resident_gguf_model_generates_like_the_dequantised_one(tmp_path):
     from hartsyinference_b200.engine import LLMEngine, SamplingParams
     from hartsyinference_b200.models.llm.loader import load_llm
     from tests.test_llm_loader_cpu import _synthetic, _to_gguf
-    cfg, t = _synthetic(5, qkv_bias=False)
+    cfg, t = _synthetic(5, qkv_bias=False, heads=4, kvh=2, d=64)      # head dim the device kernels support
     _to_gguf(cfg, t, tmp_path / "q.gguf", quant=G.GGML_TYPES["Q8_0"])
     dense = load_llm(tmp_path / "q.gguf", "cuda", fp8=False)
     config.set_override("gguf_resident", True)

@@ -8,9 +8,9 @@ from hartsyinference_b200.engine import LLMEngine, SamplingParams
 from hartsyinference_b200.models.llm.loader import load_llm, save_hf_checkpoint
 
 
-def _synthetic(seed=0, qkv_bias=True, tie=True):
+def _synthetic(seed=0, qkv_bias=True, tie=True, heads=4, kvh=2, d=32):
     g = torch.Generator().manual_seed(seed)
-    h, L, heads, kvh, d, ffn, vocab = 128, 2, 4, 2, 32, 256, 300
+    h, L, ffn, vocab = heads * d, 2, 256, 300
     cfg = {"model_type": "qwen2", "vocab_size": vocab, "hidden_size": h, "num_hidden_layers": L,
            "num_attention_heads": heads, "num_key_value_heads": kvh, "intermediate_size": ffn,
            "rms_norm_eps": 1e-6, "rope_theta": 1e6, "tie_word_embeddings": tie, "max_position_embeddings": 512,
