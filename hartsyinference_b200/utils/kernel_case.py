@@ -4,6 +4,7 @@
     python -m hartsyinference_b200.utils.kernel_case grouped fp8 32 16 4096 7168
     python -m hartsyinference_b200.utils.kernel_case attn_decode 64 8 1 128 2304
     python -m hartsyinference_b200.utils.kernel_case mla 64 16 2304
+    python -m hartsyinference_b200.utils.kernel_case attn_dense 4608 8
 
 Inputs are larger than the L2 cache where the op is bandwidth bound but stay far below a few GB,
 so a full-metric capture (dozens of replays per launch) ends in about a minute. The status word is
@@ -70,7 +71,16 @@ def _mla(argv):
         ops.mla_attn(q, cache, table, lens, 1.0 / math.sqrt(192), max_kv_len=ctx)
 
 
-CASES = {"gemm": _gemm, "grouped": _grouped, "attn_decode": _attn_decode, "mla": _mla}
+def _attn_dense(argv):
+    tokens, heads = (int(v) for v in argv[:2])
+    q = torch.randn(tokens, heads, 128, device="cuda").to(torch.bfloat16)
+    k = torch.randn(tokens, heads, 128, device="cuda").to(torch.bfloat16)
+    v = torch.randn(tokens, heads, 128, device="cuda").to(torch.bfloat16)
+    for _ in range(3):
+        ops.attention(q, k, v)
+
+
+CASES = {"attn_dense": _attn_dense, "gemm": _gemm, "grouped": _grouped, "attn_decode": _attn_decode, "mla": _mla}
 
 
 def main(argv=None) -> int:
