@@ -26,12 +26,27 @@
 // also covers every SM (a bandwidth-bound GEMM otherwise loses up to half its throughput to wave
 // quantisation). The CTAs of a split tile write fp32 partials to a scratch buffer and bump a
 // counter; whoever arrives last sums the partials in split order (deterministic) and runs the
-// epilogue. No second kernel is launched.
+// epilogue. A GEMM with fewer tiles than SMs is split completely; its partials are summed by a
+// second, machine-wide kernel (splitk_reduce_kernel) or, optionally, through the distributed
+// shared memory of a thread-block cluster (measured slower, off by default).
 //
-// fp8 block scaling (128 x 128 weight blocks, 1 x 128 activation groups, fp32 scales): every
-// 128-deep K block is accumulated into its own TMEM buffer (a ring of up to eight); the epilogue
-// warps pull the block out, multiply by scale_a(row, kb) * scale_b(col, kb) and add into fp32
-// registers while the tensor core already works on the next blocks.
+// fp8 (128 x 128 weight blocks, 1 x 128 activation groups), two scale modes:
+//   UE8M0  power-of-two scales in the blocked layout the tensor core reads: the producer brings the
+//          512-byte scale-factor blocks of four K blocks in with bulk copies, the MMA thread moves
+//          them to TMEM (tcgen05.cp) and issues tcgen05.mma.kind::mxf8f6f4.block_scale; the
+//          accumulator never leaves TMEM during the K loop (same flow as bf16).
+//   fp32   arbitrary scales: every 128-deep K block is accumulated into its own TMEM buffer (a ring
+//          of up to eight); the epilogue warps pull the block out, multiply by
+//          scale_a(row, kb) * scale_b(col, kb) and add into fp32 registers while the tensor core
+//          already works on the next blocks.
+//
+// Further modes of the same kernel: grouped (stacked expert weights; fixed blocks per expert or a
+// device-side block list for variable token counts), column-batched (per-head projections of one
+// token block), shifted-row accumulation (convolution taps as row offsets of one padded matrix).
+//
+// Programmatic dependent launch: the grid may start while its predecessor still runs. In the
+// small-token orientation the producer requests the first stages of WEIGHT tiles before
+// griddepcontrol.wait and the activation tiles after it; every other role waits first.
 #include "common.cuh"
 
 namespace b200 {
