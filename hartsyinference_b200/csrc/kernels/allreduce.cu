@@ -180,3 +180,115 @@ B200_API int b200_allreduce(void* const* in, void* const* out, void* const* flag
   launch_pdl(allreduce_kernel, dim3(blocks), dim3(512), 0, stream, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -300;
 }
+
+// ------------------------------------------------------------------------------------------
+// CFG-parallel combine fused with the scheduler step.
+//
+// Two ranks denoise the conditional (rank 0) and unconditional (rank 1) branch of the same latents.
+// Each writes its velocity prediction into its own slot of the symmetric heap; this kernel then
+//   1. tells the peer "my prediction of step e is written" and waits for the peer's flag,
+//   2. reads the PEER's prediction straight over NVLink (no gather into a local copy),
+//   3. applies v = u + g (c - u) and the Euler update z += v dt to the local fp32 latents.
+// Both ranks hold identical latents afterwards. One launch replaces all_gather + combine + step
+// (the reference copies the branch result peer to peer and runs a separate CFG/Euler kernel:
+// src/HartsyInference.Diffusion/Pipelines/FluxPipeline.cs PredictDrainFree:750-807, CopyFromPeer:780,
+// CfgEulerStep:821). A second flag pair keeps a fast rank from overwriting its slot for step e + 1
+// while the peer still reads step e.
+// ------------------------------------------------------------------------------------------
+namespace b200 {
+
+struct CfgCombineArgs {
+  const __nv_bfloat16* pred[2];   // [rank] prediction slots (peer-mapped)
+  uint32_t* ready[2];             // [rank] -> flag array of that rank: ready[q][r] = step written by r
+  uint32_t* consumed[2];          // [rank] -> consumed[q][r] = step that r has finished reading from q
+  float* z;                       // local latents
+  uint32_t* epoch;                // local call counter
+  uint32_t* fin;
+  long long n;
+  int rank;                       // 0 = conditional branch, 1 = unconditional
+  float guidance, dt;
+  long long wait_budget;
+  DeviceStatus* status;
+};
+
+__global__ void __launch_bounds__(256) cfg_combine_kernel(const CfgCombineArgs a) {
+  __shared__ uint32_t s_ok;
+  const uint32_t e = *reinterpret_cast<volatile uint32_t*>(a.epoch) + 1u;
+  const int peer = a.rank ^ 1;
+  if (threadIdx.x == 0) {
+    // my prediction (written by the kernels before this one) is complete: publish, then wait
+    __threadfence_system();
+    if (blockIdx.x == 0) st_release_sys(a.ready[peer] + a.rank, e);
+    s_ok = wait_geq(a.ready[a.rank] + peer, e, a.wait_budget) ? 1u : 0u;
+    if (!s_ok) report_status(a.status, kWaitTimeout, kKernelCfgStep, 1, blockIdx.x);
+  }
+  __syncthreads();
+  if (s_ok) {
+    const __nv_bfloat16* mine = a.pred[a.rank];
+    const __nv_bfloat16* theirs = a.pred[peer];
+    const long long nvec = a.n >> 3;
+    for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec;
+         v += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const uint4 m4 = *reinterpret_cast<const uint4*>(mine + v * 8);
+      const uint4 t4 = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(theirs + v * 8));
+      const __nv_bfloat162* mh = reinterpret_cast<const __nv_bfloat162*>(&m4);
+      const __nv_bfloat162* th = reinterpret_cast<const __nv_bfloat162*>(&t4);
+      float4 z0 = *reinterpret_cast<float4*>(a.z + v * 8), z1 = *reinterpret_cast<float4*>(a.z + v * 8 + 4);
+      float zz[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 fm = __bfloat1622float2(mh[i]), ft = __bfloat1622float2(th[i]);
+        const float2 c = a.rank == 0 ? fm : ft, u = a.rank == 0 ? ft : fm;
+        zz[2 * i] += (a.guidance * c.x + (1.f - a.guidance) * u.x) * a.dt;
+        zz[2 * i + 1] += (a.guidance * c.y + (1.f - a.guidance) * u.y) * a.dt;
+      }
+      *reinterpret_cast<float4*>(a.z + v * 8) = make_float4(zz[0], zz[1], zz[2], zz[3]);
+      *reinterpret_cast<float4*>(a.z + v * 8 + 4) = make_float4(zz[4], zz[5], zz[6], zz[7]);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.fin, 1u) == gridDim.x - 1) {
+      // every block of this rank is done with the peer's slot: let the peer reuse it, and do not
+      // return before the peer is done with ours (the next step overwrites it)
+      *a.fin = 0;
+      st_release_sys(a.consumed[peer] + a.rank, e);
+      if (!wait_geq(a.consumed[a.rank] + peer, e, a.wait_budget))
+        report_status(a.status, kWaitTimeout, kKernelCfgStep, 2, blockIdx.x);
+      *reinterpret_cast<volatile uint32_t*>(a.epoch) = e;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace b200
+
+// pred / flags: arrays of 2 device pointers (index = rank) into the symmetric heap; flags per rank:
+// 4 x u32 (ready[2], consumed[2]), zero-initialised; epoch / fin: local zero-initialised u32.
+// n bf16 values (a multiple of 8); z: local fp32 latents [n].
+B200_API int b200_cfg_combine(void* const* pred, void* const* flags, void* epoch, void* fin, float* z, long long n,
+                              int rank, float guidance, float dt, long long wait_budget_cycles, void* status,
+                              cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n % 8 != 0 || rank < 0 || rank > 1) return -2;
+  CfgCombineArgs a{};
+  for (int r = 0; r < 2; ++r) {
+    a.pred[r] = static_cast<const __nv_bfloat16*>(pred[r]);
+    a.ready[r] = static_cast<uint32_t*>(flags[r]);
+    a.consumed[r] = static_cast<uint32_t*>(flags[r]) + 2;
+  }
+  a.z = z;
+  a.epoch = static_cast<uint32_t*>(epoch);
+  a.fin = static_cast<uint32_t*>(fin);
+  a.n = n;
+  a.rank = rank;
+  a.guidance = guidance;
+  a.dt = dt;
+  a.wait_budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
+  a.status = static_cast<DeviceStatus*>(status);
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148) blocks = 148;
+  cfg_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -300;
+}

@@ -96,6 +96,14 @@ class FluxPipeline:
         branch = None
         if true_cfg and self.cfg_comm is not None and self.cfg_comm.world == 2:
             branch = self.cfg_comm.rank                                           # 0 = cond, 1 = uncond
+        # fused peer-memory combine + Euler step (one kernel, no all_gather) when the two branches sit
+        # on GPUs that can map each other's memory; the step cache needs the combined velocity, so it
+        # keeps the all_gather path
+        fused_cfg = None
+        if branch is not None and dev.type == "cuda" and step_cache_threshold <= 0 and S * x.shape[2] % 8 == 0:
+            from .. import config as _config
+            if _config.get("fused_comm") and not _config.get("p2p_disable"):
+                fused_cfg = self._fused_cfg(S * x.shape[2], dev)
         cache_prev_t: Optional[torch.Tensor] = None
         cache_v: Optional[torch.Tensor] = None
         # first-block cache: one per CFG branch, decided inside the transformer after block 0
@@ -125,14 +133,19 @@ class FluxPipeline:
                 else:
                     c_in, p_in = (ctx_d, pooled_d) if branch == 0 else (neg[0].to(dev)[None], neg[1].to(dev)[None])
                     mine = tr.forward(xin, c_in, sigma, p_in, img_ids, txt_ids, gvec, step_cache=fbc[0]).contiguous()
-                    both = self.cfg_comm.all_gather(mine[None], dim=0)             # [2, 1, S, C]
-                    v_cond, v_unc = both[0].contiguous(), both[1].contiguous()
+                    if fused_cfg is not None:
+                        fused_cfg.step(x, mine, cfg_scale, sched.dt(i))
+                        v_cond = None
+                    else:
+                        both = self.cfg_comm.all_gather(mine[None], dim=0)         # [2, 1, S, C]
+                        v_cond, v_unc = both[0].contiguous(), both[1].contiguous()
                 if step_cache_threshold > 0:
                     cache_prev_t = tr.time_embedding(sigma, gvec, pooled_d).float()
                     cache_v = v_cond if not true_cfg else (cfg_scale * v_cond.float() + (1 - cfg_scale) * v_unc.float()).to(torch.bfloat16)
                     if true_cfg:
                         v_cond, v_unc = cache_v, None
-            sched.step(x, v_cond.contiguous(), i, v_unc, cfg_scale)
+            if v_cond is not None:
+                sched.step(x, v_cond.contiguous(), i, v_unc, cfg_scale)
             if use_cuda:
                 e1.record()
                 e1.synchronize()
@@ -144,6 +157,21 @@ class FluxPipeline:
             if on_step is not None:
                 on_step(StepPreview(i + 1, steps))
         return unpack_latents(x, lh, lw)
+
+    def _fused_cfg(self, elems: int, dev):
+        """The fused CFG combine for latents of ``elems`` values (built once; None when the peer's
+        memory cannot be mapped)."""
+        cur = getattr(self, "_fused_cfg_obj", None)
+        if cur is not None and cur.max_elems >= elems:
+            return cur
+        try:
+            from ..parallel.cfg_combine import FusedCfgCombine
+            self._fused_cfg_obj = FusedCfgCombine(self.cfg_comm, elems, dev)
+        except Exception as e:      # no peer access: keep the all_gather path
+            from .. import log
+            log.decision("Collective", f"fused CFG combine unavailable ({type(e).__name__}: {e}); using all_gather")
+            self._fused_cfg_obj = None
+        return self._fused_cfg_obj
 
     def generate(self, req: ImageRequest, on_step: Optional[Callable[[StepPreview], None]] = None) -> ImageResult:
         seed = req.seed if req.seed is not None else int(time.time() * 1000) % (2 ** 31)

@@ -77,6 +77,21 @@ def main():
         assert rel(y2.float(), want) < 1e-2
     N.check_status(dev)
     car.close()
+    # ---- CFG-parallel combine fused with the Euler step (ranks 0 / 1 = conditional / unconditional)
+    if world == 2:
+        from hartsyinference_b200.parallel.cfg_combine import FusedCfgCombine
+        fc = FusedCfgCombine(comm, 4096 * 64, dev)
+        gen = torch.Generator(device="cpu").manual_seed(5)
+        z0 = torch.randn(4096 * 64, generator=gen)
+        for it in range(4):
+            preds = [(torch.randn(4096 * 64, generator=gen) * 0.5).to(torch.bfloat16) for _ in range(2)]   # same on both ranks
+            z = z0.clone().to(dev)
+            fc.step(z, preds[rank].to(dev), 3.5, -0.05)
+            want = z0 + (3.5 * preds[0].float() + (1 - 3.5) * preds[1].float()) * -0.05
+            N.check_status(dev)
+            assert (z.cpu() - want).abs().max() < 1e-5, (it, (z.cpu() - want).abs().max())
+            z0 = want
+        fc.close()
     # ---- TP model vs single-GPU model
     cfg = C.tiny("llama-3-70b", vocab_size=1024, hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=2,
                  head_dim=128, ffn_size=1024)
