@@ -43,6 +43,8 @@ class Request:
     t_done: float = 0.0
     error: Optional[str] = None
     generator: Optional[torch.Generator] = None
+    embeds: Optional[torch.Tensor] = None         # [len(prompt), hidden] replacement input embeddings
+    embeds_mask: Optional[torch.Tensor] = None    # [len(prompt)] bool: rows taken from ``embeds``
 
 
 def _bucket(n: int) -> int:
@@ -117,7 +119,10 @@ class LLMEngine:
 
     # ------------------------------------------------------------------------------- requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
-                    on_token: Optional[Callable[[int, int, bool], None]] = None) -> int:
+                    on_token: Optional[Callable[[int, int, bool], None]] = None,
+                    prompt_embeds: Optional[torch.Tensor] = None, embeds_mask: Optional[torch.Tensor] = None) -> int:
+        """``prompt_embeds`` [len(prompt), hidden] with ``embeds_mask`` [len(prompt)] (bool) replaces the
+        token embedding of the marked prompt positions (image patches of a vision-language model)."""
         params = params or SamplingParams()
         prompt = list(prompt)
         if len(prompt) == 0:
@@ -129,6 +134,12 @@ class LLMEngine:
         self._next_id += 1
         self.sched.submit(rid, len(prompt), max_new)
         req = Request(rid, prompt, params, on_token=on_token, t_submit=time.perf_counter())
+        if prompt_embeds is not None:
+            if prompt_embeds.shape[0] != len(prompt):
+                raise ValueError("prompt_embeds needs one row per prompt token")
+            req.embeds = prompt_embeds.to(self.device).to(torch.bfloat16)
+            req.embeds_mask = (embeds_mask if embeds_mask is not None else
+                               torch.ones(len(prompt), dtype=torch.bool)).to(self.device)
         if params.seed is not None and not params.is_greedy:
             req.generator = torch.Generator(device=self.device).manual_seed(params.seed)
         self.requests[rid] = req
@@ -186,10 +197,28 @@ class LLMEngine:
             t += count
         n = len(chunks)
         self.h_cu_q[n] = t
+        embeds = None
+        if any(self.requests[rid].embeds is not None for rid, _, _ in chunks):
+            # token embeddings first, then the rows that come from images are overwritten
+            from .. import ops as _ops
+            cfgm = self.model.cfg
+            embeds = _ops.embedding(self._to_device(self.h_tokens, t), self.model.embed,
+                                    cfgm.embed_scale * cfgm.embedding_multiplier)
+            t0 = 0
+            for rid, start, count in chunks:
+                req = self.requests[rid]
+                if req.embeds is not None:
+                    end = min(start + count, req.embeds.shape[0])
+                    if end > start:
+                        m = req.embeds_mask[start:end]
+                        rows = embeds[t0:t0 + (end - start)]
+                        rows[m] = req.embeds[start:end][m]
+                t0 += count
         batch = ForwardBatch(tokens=self._to_device(self.h_tokens, t), positions=self._to_device(self.h_positions, t),
                              slot_mapping=self._to_device(self.h_slots, t), block_table=self._to_device(self.h_table, n),
                              kv_lens=self._to_device(self.h_kv_lens, n), is_decode=False,
-                             cu_q=self._to_device(self.h_cu_q, n + 1), max_q_len=max_q, max_kv_len=max_kv)
+                             cu_q=self._to_device(self.h_cu_q, n + 1), max_q_len=max_q, max_kv_len=max_kv,
+                             embeds=embeds)
         hidden = self.model.forward_hidden(batch)
         done: list[tuple[Request, int]] = []
         fresh = [(row, req) for row, req in sample_rows if not req.output]

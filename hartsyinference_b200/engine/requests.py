@@ -90,6 +90,7 @@ class TextRequest:
     speculative_decode: bool = False
     stop: list[str] = field(default_factory=list)
     json_mode: bool = False
+    images: list = field(default_factory=list)   # one per "<image>" in the prompt (path, PIL image, array or tensor)
 
 
 @dataclass

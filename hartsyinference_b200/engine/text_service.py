@@ -125,10 +125,31 @@ class TextService:
 
     def _prompt_ids(self, llm: LoadedLLM, req: TextRequest) -> list[int]:
         if req.prompt is not None:
-            return llm.tokenizer.encode(req.prompt)
-        text = llm.chat_template.render(req.messages, add_generation_prompt=True, tools=req.tools,
-                                        enable_thinking=req.enable_thinking)
-        return llm.tokenizer.encode(text, add_special=not text.startswith(llm.chat_template.bos_token or "\0"))
+            text, special = req.prompt, True
+        else:
+            text = llm.chat_template.render(req.messages, add_generation_prompt=True, tools=req.tools,
+                                            enable_thinking=req.enable_thinking)
+            special = not text.startswith(llm.chat_template.bos_token or "\0")
+        if not req.images or llm.vlm is None:
+            return llm.tokenizer.encode(text, add_special=special)
+        # the text around each "<image>" is tokenised by itself, with the image token id between
+        ids: list[int] = []
+        for i, piece in enumerate(text.split("<image>")):
+            if i:
+                ids.append(llm.vlm.image_token_id)
+            if piece:
+                ids += llm.tokenizer.encode(piece, add_special=special and i == 0)
+        return ids
+
+    def _multimodal(self, llm: LoadedLLM, req: TextRequest, ids: list[int]):
+        """(ids, embeds, mask) with every image token expanded to its patch embeddings."""
+        from ..models.encoders.clip_vision import preprocess_image
+        if not req.images:
+            return ids, None, None
+        if llm.vlm is None:
+            raise ValueError("this model has no vision tower; images are not accepted")
+        size = llm.vlm.vision.cfg.image_size
+        return llm.vlm.expand_prompt(ids, [preprocess_image(im, size) for im in req.images])
 
     def stream(self, spec: ModelSpec, req: TextRequest, cancel: Optional[threading.Event] = None) -> Iterator[TextChunk]:
         h = self._host(spec)
@@ -137,7 +158,9 @@ class TextService:
         q: "queue.Queue[tuple[int, bool]]" = queue.Queue()
         t0 = time.perf_counter()
         with h.wake:
-            rid = h.engine.add_request(ids, self._params(req, llm), on_token=lambda r, tok, fin: q.put((tok, fin)))
+            ids, embeds, emask = self._multimodal(llm, req, ids)
+            rid = h.engine.add_request(ids, self._params(req, llm), on_token=lambda r, tok, fin: q.put((tok, fin)),
+                                       prompt_embeds=embeds, embeds_mask=emask)
             h.wake.notify_all()
         dec = llm.tokenizer.stream_decoder()
         text = ""

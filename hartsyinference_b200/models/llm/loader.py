@@ -61,6 +61,7 @@ class LoadedLLM:
     chat_template: ChatTemplate
     config: TransformerConfig
     source: str
+    vlm: Optional[object] = None      # LlavaModel when the checkpoint carries a vision tower
 
 
 def _gemma_sandwich_fix(cfg: TransformerConfig, get: Callable[[str], Optional[torch.Tensor]]):
@@ -97,11 +98,43 @@ def _want_fp8(fp8: Optional[bool], device) -> bool:
     return bool(config.get("fp8_linears")) and torch.device(device).type == "cuda"
 
 
+def _llava_names(ck) -> tuple[Callable, Callable]:
+    """Two checkpoint layouts exist for LLaVA: ``language_model.model.* / language_model.lm_head /
+    vision_tower.* / multi_modal_projector.*`` and the later ``model.language_model.* /
+    model.vision_tower.* / model.multi_modal_projector.* / lm_head``. Returns (decoder get, tower get)
+    that take the plain decoder names and the first layout's tower names."""
+    new = ck.get("model.language_model.embed_tokens.weight") is not None
+
+    def lm(name: str):
+        if new:
+            return ck.get("model.language_model." + name[len("model."):]) if name.startswith("model.") else ck.get(name)
+        return ck.get("language_model." + name)
+
+    def tower(name: str):
+        return ck.get(("model." if new else "") + name)
+
+    return lm, tower
+
+
 def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
-    cfg = from_hf_config(json.loads((p / "config.json").read_text()))
+    raw = json.loads((p / "config.json").read_text())
     ck = ShardedCheckpoint(p)
-    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
-    model.load_state_dict(ck.get)
+    vlm = None
+    if "vision_config" in raw and "text_config" in raw:
+        from ..encoders.clip_vision import clip_vision_from_hf
+        from ..vlm.llava import LlavaModel
+        text = dict(raw["text_config"])
+        text.setdefault("model_type", "llama")
+        cfg = from_hf_config(text)
+        lm_get, tower_get = _llava_names(ck)
+        model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
+        model.load_state_dict(lm_get)
+        vlm = LlavaModel(model, clip_vision_from_hf(raw["vision_config"]), int(raw.get("image_token_index", 32000)),
+                         get=tower_get, feature_layer=int(raw.get("vision_feature_layer", -2)))
+    else:
+        cfg = from_hf_config(raw)
+        model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
+        model.load_state_dict(ck.get)
     tok: Tokenizer
     if (p / "tokenizer.json").exists():
         tok = Tokenizer.from_hf_json(p / "tokenizer.json")
@@ -117,7 +150,7 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
     tpl = ChatTemplate(tpl_src, bos or "", eos or "") if tpl_src else ChatTemplate.for_arch(cfg.arch)
     log.info(f"[Load] {p.name}: {cfg.arch} {cfg.num_layers}L hidden {cfg.hidden_size} "
              f"({model.weight_bytes() / 2**30:.2f} GiB on {device})")
-    return LoadedLLM(model, tok, tpl, cfg, str(p))
+    return LoadedLLM(model, tok, tpl, cfg, str(p), vlm)
 
 
 def _load_gguf(p: Path, device, comm, fp8) -> LoadedLLM:

@@ -81,6 +81,33 @@ class UsageTracker:
                 self.by_key[key][k] += v
 
 
+def _flatten_parts(messages: list) -> tuple[list, list]:
+    """OpenAI content parts -> plain-text messages ("<image>" where a picture was) + decoded images.
+    Only ``data:`` URLs are accepted: the server fetches nothing from the network."""
+    import base64
+    import io
+    out, images = [], []
+    for m in messages:
+        c = m.get("content")
+        if not isinstance(c, list):
+            out.append(m)
+            continue
+        text = ""
+        for part in c:
+            kind = part.get("type")
+            if kind == "text":
+                text += part.get("text", "")
+            elif kind == "image_url":
+                url = (part.get("image_url") or {}).get("url", "")
+                if not url.startswith("data:") or "," not in url:
+                    raise ValueError("image_url must be a base64 data: URL")
+                from PIL import Image
+                images.append(Image.open(io.BytesIO(base64.b64decode(url.split(",", 1)[1]))).convert("RGB"))
+                text += "<image>\n"
+        out.append({**m, "content": text})
+    return out, images
+
+
 def create_app(options: Optional[ServerOptions] = None, engine: Optional[InferenceEngine] = None,
                engine_options: Optional[EngineOptions] = None) -> FastAPI:
     opts = options or ServerOptions()
@@ -176,6 +203,8 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
 
     # -------------------------------------------------------------------------- text
     def _text_request(body: dict) -> TextRequest:
+        messages, images = _flatten_parts(body.get("messages") or [])
+        body = {**body, "messages": messages}
         stop = body.get("stop") or []
         if isinstance(stop, str):
             stop = [stop]
@@ -187,7 +216,7 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
                            max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 4096),
                            seed=body.get("seed"), greedy=bool(body.get("greedy", False)) or float(body.get("temperature", 0.7)) == 0.0,
                            enable_thinking=body.get("enable_thinking"), tools=body.get("tools"), stop=list(stop),
-                           json_mode=rf.get("type") == "json_object")
+                           json_mode=rf.get("type") == "json_object", images=images)
 
     @app.post("/v1/chat/completions")
     async def chat_completions(request: Request):

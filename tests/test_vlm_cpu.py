@@ -1,0 +1,162 @@
+"""Vision tower parity against transformers' CLIPVisionModel, and LLaVA-style generation through
+the serving engine with image embeddings spliced into the prompt."""
+import pytest
+import torch
+
+from hartsyinference_b200.engine import LLMEngine, SamplingParams
+from hartsyinference_b200.models.encoders.clip_vision import ClipVisionEncoder, preprocess_image, tiny_clip_vision
+from hartsyinference_b200.models.llm import config as C
+from hartsyinference_b200.models.llm.transformer import DecoderModel
+from hartsyinference_b200.models.vlm import LlavaModel
+
+
+def test_clip_vision_matches_transformers():
+    tr = pytest.importorskip("transformers")
+    cfg = tiny_clip_vision()
+    hf_cfg = tr.CLIPVisionConfig(hidden_size=cfg.width, intermediate_size=cfg.width * cfg.mlp_ratio,
+                                 num_hidden_layers=cfg.layers, num_attention_heads=cfg.heads,
+                                 image_size=cfg.image_size, patch_size=cfg.patch, hidden_act="quick_gelu")
+    torch.manual_seed(0)
+    hf = tr.CLIPVisionModel(hf_cfg).eval()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    enc = ClipVisionEncoder(cfg, "cpu", get=lambda n: sd.get(n))
+    img = torch.randn(3, cfg.image_size, cfg.image_size)
+    with torch.no_grad():
+        out = hf(pixel_values=img[None], output_hidden_states=True)
+    mine = enc.hidden_states(img, -2).float()
+    ref = out.hidden_states[-2][0]
+    assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0) > 0.995
+    pooled = enc.embed(img).float()
+    assert torch.nn.functional.cosine_similarity(pooled, out.pooler_output[0], dim=0) > 0.995
+
+
+def _toy():
+    m = DecoderModel(C.tiny(), "cpu")
+    m.random_init(3, std=0.05)
+    return m
+
+
+def test_llava_generate_uses_image_embeddings():
+    model = _toy()
+    image_tok = model.cfg.vocab_size - 1
+    vcfg = tiny_clip_vision()
+    vlm = LlavaModel(model, vcfg, image_tok, seed=5)
+    img_a = torch.randn(3, 32, 32, generator=torch.Generator().manual_seed(1))
+    img_b = torch.randn(3, 32, 32, generator=torch.Generator().manual_seed(2)) * 3
+    prompt = [5, 9, image_tok, 11, 12]
+    ids, embeds, mask = vlm.expand_prompt(prompt, [img_a])
+    n = vcfg.num_patches
+    assert len(ids) == len(prompt) - 1 + n and int(mask.sum()) == n
+    assert mask.tolist() == [False, False] + [True] * n + [False, False]
+
+    # what reaches the decoder: token embeddings, with the image rows replaced by projected patches
+    seen = []
+    inner = model.forward_hidden
+
+    def spy(batch, *a, **k):
+        if batch.embeds is not None:
+            seen.append(batch.embeds.clone())
+        return inner(batch, *a, **k)
+
+    model.forward_hidden = spy
+    params = SamplingParams(greedy=True, max_tokens=4)
+    chunked = LLMEngine(model, num_pages=64, page_size=4, max_batch=2, prefill_chunk=8, max_model_len=64)
+    out_chunked = vlm.generate(chunked, prompt, [img_a], params)
+    got = torch.cat(seen, 0)
+    want = model.embed[torch.tensor(ids)].clone()
+    want[mask] = embeds[mask]
+    assert len(seen) > 1 and torch.equal(got, want)
+    model.forward_hidden = inner
+
+    # chunked prefill of the mixed embeddings gives the same tokens as one whole-prompt prefill
+    whole = LLMEngine(model, num_pages=64, page_size=4, max_batch=2, prefill_chunk=256, max_model_len=64)
+    out_whole = vlm.generate(whole, prompt, [img_a], params)
+    assert len(out_chunked) == 4 and out_chunked == out_whole
+
+    # a different image changes the patch embeddings
+    _, embeds_b, _ = vlm.expand_prompt(prompt, [img_b])
+    assert not torch.allclose(embeds_b[mask].float(), embeds[mask].float())
+    with pytest.raises(ValueError):
+        vlm.expand_prompt(prompt, [])
+    with pytest.raises(ValueError):
+        vlm.expand_prompt(prompt, [img_a, img_b])
+
+
+def _llava_checkpoint(tmp_path, layout: str):
+    """A tiny LLaVA checkpoint directory in one of the two tensor-name layouts."""
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    tr = pytest.importorskip("transformers")
+    vc = tiny_clip_vision()
+    torch.manual_seed(1)
+    hf_v = tr.CLIPVisionModel(tr.CLIPVisionConfig(hidden_size=vc.width, intermediate_size=vc.width * vc.mlp_ratio,
+                                                  num_hidden_layers=vc.layers, num_attention_heads=vc.heads,
+                                                  image_size=vc.image_size, patch_size=vc.patch))
+    lcfg = tr.LlamaConfig(vocab_size=300, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                          num_attention_heads=2, num_key_value_heads=2, max_position_embeddings=256,
+                          tie_word_embeddings=False)
+    hf_l = tr.LlamaForCausalLM(lcfg)
+    H = lcfg.hidden_size
+    proj = {"multi_modal_projector.linear_1.weight": torch.randn(H, vc.width) * 0.05,
+            "multi_modal_projector.linear_1.bias": torch.zeros(H),
+            "multi_modal_projector.linear_2.weight": torch.randn(H, H) * 0.05,
+            "multi_modal_projector.linear_2.bias": torch.zeros(H)}
+    tensors = {}
+    for k, v in hf_l.state_dict().items():
+        if layout == "old":
+            tensors["language_model." + k] = v
+        else:
+            tensors[("model.language_model." + k[len("model."):]) if k.startswith("model.") else k] = v
+    for k, v in list(hf_v.state_dict().items()) + list(proj.items()):
+        k = k if k.startswith("multi_modal") else "vision_tower." + k
+        tensors[k if layout == "old" else "model." + k] = v
+    tensors = {k: v.detach().to(torch.bfloat16).contiguous() for k, v in tensors.items()}
+    cfg = {"model_type": "llava", "image_token_index": 299, "vision_feature_layer": -2,
+           "text_config": {**lcfg.to_dict(), "model_type": "llama"},
+           "vision_config": {"hidden_size": vc.width, "intermediate_size": vc.width * vc.mlp_ratio,
+                             "num_hidden_layers": vc.layers, "num_attention_heads": vc.heads,
+                             "image_size": vc.image_size, "patch_size": vc.patch, "hidden_act": "quick_gelu"}}
+    d = tmp_path / f"llava-{layout}"
+    save_hf_checkpoint(cfg, tensors, d)
+    return d
+
+
+@pytest.mark.parametrize("layout", ["old", "new"])
+def test_llava_checkpoint_through_text_service(tmp_path, layout):
+    import numpy as np
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, TextRequest
+    d = _llava_checkpoint(tmp_path, layout)
+    eng = InferenceEngine("cpu")
+    try:
+        spec = ModelSpec(str(d))
+        img = (np.random.default_rng(0).random((40, 52, 3)) * 255).astype(np.uint8)
+        req = TextRequest(prompt="look: <image> what is it?", images=[img], max_tokens=3, greedy=True)
+        res = eng.text.generate(spec, req)
+        assert len(res.token_ids) == 3 and res.error is None
+        n = tiny_clip_vision().num_patches
+        plain = eng.text.generate(spec, TextRequest(prompt="look: <image> what is it?", max_tokens=3, greedy=True))
+        assert res.prompt_tokens > n                      # the image token expanded to its patches
+        assert plain.prompt_tokens < res.prompt_tokens    # without images "<image>" is ordinary text
+        other = (np.random.default_rng(1).random((40, 52, 3)) * 255).astype(np.uint8)
+        h = eng.text._host(spec)
+        a = h.llm.vlm.image_features(preprocess_image(img, 32))
+        b = h.llm.vlm.image_features(preprocess_image(other, 32))
+        assert a.shape == (n, 128) and not torch.allclose(a.float(), b.float())
+    finally:
+        eng.text.release()
+
+
+def test_server_flattens_openai_image_parts():
+    import base64
+    import io
+    from PIL import Image
+    buf = io.BytesIO()
+    Image.new("RGB", (8, 8), (255, 0, 0)).save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    from hartsyinference_b200.server.app import _flatten_parts
+    msgs, images = _flatten_parts([{"role": "user", "content": [{"type": "text", "text": "hi "},
+                                                                      {"type": "image_url", "image_url": {"url": url}}]},
+                                         {"role": "system", "content": "plain"}])
+    assert msgs[0]["content"] == "hi <image>\n" and msgs[1]["content"] == "plain"
+    assert len(images) == 1 and images[0].size == (8, 8)
+    with pytest.raises(ValueError):
+        _flatten_parts([{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "http://x/y.png"}}]}])
