@@ -92,7 +92,7 @@ def save_file(tensors: dict[str, torch.Tensor], path: str | Path, metadata: Opti
     blobs = []
     for name in sorted(tensors):
         t = tensors[name].detach().cpu().contiguous()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""   # reshape: scalars have no dim to view
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         off += len(raw)
         blobs.append(raw)

@@ -411,3 +411,97 @@ class WordPieceTokenizer:
             else:
                 out.append(t)
         return " ".join(out)
+
+
+class ClipTokenizer:
+    """CLIP's lower-cased byte-level BPE with an end-of-word marker (``</w>``): text is cleaned,
+    split by CLIP's pattern, each word's bytes are mapped to printable code points, the last symbol
+    gets the marker and merges are applied by rank. Sequences are framed by <|startoftext|> /
+    <|endoftext|> and optionally padded to the context length.
+
+    Reads ``vocab.json`` + ``merges.txt`` or a ``tokenizer.json`` with the same content.
+    Reference: src/HartsyInference.ModelAssets/Tokenizers/ (CLIP tokenizer)."""
+
+    PATTERN = r"<\|startoftext\|>|<\|endoftext\|>|'s|'t|'re|'ve|'m|'ll|'d|[\p{L}]+|[\p{N}]|[^\s\p{L}\p{N}]+"
+
+    def __init__(self, vocab: dict[str, int], merges: Sequence[tuple[str, str]], max_len: int = 77,
+                 bos: str = "<|startoftext|>", eos: str = "<|endoftext|>"):
+        self.vocab = dict(vocab)
+        self.inv = {i: t for t, i in self.vocab.items()}
+        self.ranks = {tuple(m): r for r, m in enumerate(merges)}
+        self.max_len = max_len
+        self.bos_id, self.eos_id = self.vocab[bos], self.vocab[eos]
+        self._b2u = _bytes_to_unicode()
+        self._u2b = {u: b for b, u in self._b2u.items()}
+        self._re = _re.compile(self.PATTERN, _re.IGNORECASE)
+        self._cache: dict[str, list[int]] = {}
+
+    @staticmethod
+    def from_dir(path, max_len: int = 77) -> "ClipTokenizer":
+        p = Path(path)
+        if (p / "vocab.json").exists() and (p / "merges.txt").exists():
+            vocab = json.loads((p / "vocab.json").read_text(encoding="utf-8"))
+            lines = (p / "merges.txt").read_text(encoding="utf-8").split("\n")
+            merges = [tuple(ln.split()) for ln in lines if ln and not ln.startswith("#version") and len(ln.split()) == 2]
+        else:
+            model = json.loads((p / "tokenizer.json").read_text(encoding="utf-8"))["model"]
+            vocab = model["vocab"]
+            merges = [tuple(m.split(" ")) if isinstance(m, str) else tuple(m) for m in model["merges"]]
+        return ClipTokenizer(vocab, merges, max_len)
+
+    def _bpe(self, word: str) -> list[int]:
+        hit = self._cache.get(word)
+        if hit is not None:
+            return hit
+        sym = [self._b2u[b] for b in word.encode("utf-8")]
+        sym[-1] += "</w>"
+        while len(sym) > 1:
+            best, at = None, -1
+            for i in range(len(sym) - 1):
+                r = self.ranks.get((sym[i], sym[i + 1]))
+                if r is not None and (best is None or r < best):
+                    best, at = r, i
+            if best is None:
+                break
+            a, b = sym[at], sym[at + 1]
+            out, i = [], 0
+            while i < len(sym):            # merge every occurrence of the best pair, left to right
+                if i < len(sym) - 1 and sym[i] == a and sym[i + 1] == b:
+                    out.append(a + b)
+                    i += 2
+                else:
+                    out.append(sym[i])
+                    i += 1
+            sym = out
+        unk = self.eos_id
+        ids = [self.vocab.get(s, unk) for s in sym]
+        self._cache[word] = ids
+        return ids
+
+    def encode(self, text: str, add_special: bool = True, pad: bool = False) -> list[int]:
+        text = " ".join(text.split()).strip().lower()
+        ids: list[int] = []
+        for w in self._re.findall(text):
+            if w == "<|startoftext|>":
+                ids.append(self.bos_id)
+            elif w == "<|endoftext|>":
+                ids.append(self.eos_id)
+            else:
+                ids += self._bpe(w)
+        if add_special:
+            ids = [self.bos_id] + ids[: self.max_len - 2] + [self.eos_id]
+        if pad:
+            ids += [self.eos_id] * (self.max_len - len(ids))
+        return ids[: self.max_len]
+
+    def decode(self, ids: Iterable[int], skip_special: bool = True) -> str:
+        out = bytearray()
+        for i in ids:
+            if skip_special and i in (self.bos_id, self.eos_id):
+                continue
+            t = self.inv.get(int(i), "")
+            end = t.endswith("</w>")
+            out += bytes(self._u2b[c] for c in (t[:-4] if end else t) if c in self._u2b)
+            if end:
+                out += b" "
+        return out.decode("utf-8", errors="replace").strip()

@@ -156,6 +156,44 @@ def embed(model, texts, device, tp, sp, ep, cfg_parallel, pp):
 
 
 @cli.command()
+@click.argument("model")
+@click.argument("wav")
+@click.option("--language", default=None, help="two-letter code; detected when omitted")
+@click.option("--task", default="transcribe", type=click.Choice(["transcribe", "translate"]))
+@click.option("--no-timestamps", is_flag=True)
+@click.option("--json", "as_json", is_flag=True, help="print segments as JSON lines")
+@click.option("--device", default="auto")
+def transcribe(model, wav, language, task, no_timestamps, as_json, device):
+    """Speech to text (Whisper checkpoints) from a WAV file."""
+    from ..engine.inference_engine import InferenceEngine
+    from ..engine.requests import AudioRequest
+    eng = InferenceEngine(device)
+    res = eng.transcribe.run(ModelSpec(model, Modality.TRANSCRIBE, local_path=model),
+                             AudioRequest(audio=wav, language=language, task=task, timestamps=not no_timestamps))
+    if as_json:
+        for s in res.segments:
+            click.echo(json.dumps({"start": round(s.start, 2), "end": round(s.end, 2), "text": s.text}))
+    else:
+        click.echo(res.text)
+
+
+@cli.command()
+@click.argument("model")
+@click.option("--image", "images", multiple=True, help="image file (repeatable)")
+@click.option("--text", "texts", multiple=True, help="caption to score against the images (repeatable)")
+@click.option("--device", default="auto")
+def vision(model, images, texts, device):
+    """CLIP image / text embeddings; with both, prints the cosine similarity matrix."""
+    from ..engine.inference_engine import InferenceEngine
+    from ..engine.requests import VisionRequest
+    eng = InferenceEngine(device)
+    res = eng.vision.run(ModelSpec(model, Modality.VISION, local_path=model), VisionRequest(images=list(images), texts=list(texts)))
+    out = res.similarity if res.similarity is not None else (res.image_embeddings if res.image_embeddings is not None else res.text_embeddings)
+    for row in (out if out is not None else []):
+        click.echo(json.dumps([round(float(x), 6) for x in row]))
+
+
+@cli.command()
 @click.option("--host", default="127.0.0.1")
 @click.option("--port", default=8080)
 @click.option("--model", "models", multiple=True, help="name=path (repeatable)")

@@ -1,0 +1,47 @@
+"""Speech-to-text service: hosts Whisper pipelines by checkpoint path.
+
+Reference: src/HartsyInference.Engine/Services/TranscribeService.cs, ITranscribeService.cs.
+"""
+from __future__ import annotations
+
+import threading
+from pathlib import Path
+
+import torch
+
+from ..audio import read_wav
+from ..pipelines.whisper import TranscriptResult, WhisperOptions, WhisperPipeline
+from .requests import AudioRequest, ModelSpec
+
+
+class TranscribeService:
+    def __init__(self, device):
+        self.device = device
+        self._lock = threading.Lock()
+        self._loaded: dict[str, WhisperPipeline] = {}
+
+    def loaded_keys(self) -> list[str]:
+        return [f"whisper:{k}" for k in self._loaded]
+
+    def release(self) -> None:
+        with self._lock:
+            self._loaded.clear()
+
+    def _pipe(self, spec: ModelSpec) -> WhisperPipeline:
+        path = spec.local_path or spec.requested
+        with self._lock:
+            if path not in self._loaded:
+                self._loaded[path] = WhisperPipeline.from_pretrained(path, self.device)
+            return self._loaded[path]
+
+    def run(self, spec: ModelSpec, req: AudioRequest) -> TranscriptResult:
+        a, rate = req.audio, req.sample_rate
+        if isinstance(a, (str, Path, bytes, bytearray)):
+            a, rate = read_wav(a)
+        if a is None:
+            raise ValueError("AudioRequest.audio is empty")
+        opts = WhisperOptions(language=req.language, task=req.task, timestamps=req.timestamps)
+        with self._lock:
+            pipe = self._loaded.get(spec.local_path or spec.requested)
+        pipe = pipe or self._pipe(spec)
+        return pipe.transcribe(torch.as_tensor(a), rate, opts)

@@ -52,7 +52,7 @@ def parse_backend_selector(selector: str) -> tuple[str, list[int]]:
 
 
 class InferenceEngine:
-    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS}
+    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION}
 
     def __init__(self, backend_selector: str = "auto", options: Optional[EngineOptions] = None):
         self.options = options or EngineOptions()
@@ -115,15 +115,23 @@ class InferenceEngine:
         from .diffusion_service import VideoService
         return self._service("video", lambda: VideoService(self.options, self.device))
 
+    @property
+    def transcribe(self):
+        from .audio_service import TranscribeService
+        return self._service("transcribe", lambda: TranscribeService(self.device))
+
+    @property
+    def vision(self):
+        from .vision_service import VisionService
+        return self._service("vision", lambda: VisionService(self.device))
+
     def _unsupported(self, what: str):
         raise UnsupportedModelError(f"the {what} modality is not built in this engine yet")
 
     music = property(lambda self: self._unsupported("music"))
     speech = property(lambda self: self._unsupported("speech"))
-    transcribe = property(lambda self: self._unsupported("transcribe"))
     voice_conversion = property(lambda self: self._unsupported("voice conversion"))
     fx = property(lambda self: self._unsupported("fx"))
-    vision = property(lambda self: self._unsupported("vision"))
     restore = property(lambda self: self._unsupported("restore"))
     mesh = property(lambda self: self._unsupported("mesh"))
     world = property(lambda self: self._unsupported("world"))

@@ -139,6 +139,31 @@ class ImageRequest:
 
 
 @dataclass
+class AudioRequest:
+    """Speech-to-text input: a WAV path / bytes, or samples with their rate."""
+    audio: Optional[Any] = None          # path, bytes, or float tensor [n] / [channels, n]
+    sample_rate: int = 16000
+    language: Optional[str] = None
+    task: str = "transcribe"             # or "translate"
+    timestamps: bool = True
+
+
+@dataclass
+class VisionRequest:
+    """``operation``: "embed" (CLIP image / text features, and their similarity when both are given)."""
+    operation: str = "embed"
+    images: list = field(default_factory=list)
+    texts: list[str] = field(default_factory=list)
+
+
+@dataclass
+class VisionResult:
+    image_embeddings: Optional[Any] = None     # [n_images, dim], L2-normalised
+    text_embeddings: Optional[Any] = None      # [n_texts, dim]
+    similarity: Optional[Any] = None           # [n_images, n_texts] cosine
+
+
+@dataclass
 class StepPreview:
     step: int
     total_steps: int

@@ -1,0 +1,95 @@
+"""Vision service: CLIP image / text embeddings and their similarity (zero-shot scoring).
+
+Reference: src/HartsyInference.Engine/Services/VisionService.cs (embed operation),
+src/HartsyInference.Vision/Embeddings/.
+"""
+from __future__ import annotations
+
+import json
+import threading
+from pathlib import Path
+
+import torch
+
+from ..assets.safetensors import ShardedCheckpoint
+from ..models.encoders.clip_vision import ClipVisionEncoder, clip_vision_from_hf, preprocess_image
+from .requests import ModelSpec, VisionRequest, VisionResult
+
+
+class _ClipDual:
+    """Both towers of a Hugging Face ``CLIPModel`` checkpoint with their projections."""
+
+    def __init__(self, path: str, device):
+        from ..assets.tokenizer import ClipTokenizer
+        from ..models.encoders.clip import ClipTextConfig, ClipTextEncoder
+        p = Path(path)
+        raw = json.loads((p / "config.json").read_text())
+        ck = ShardedCheckpoint(p)
+        self.device = torch.device(device)
+        self.vision = ClipVisionEncoder(clip_vision_from_hf(raw["vision_config"]), device, get=ck.get, prefix="vision_model.")
+        self.visual_proj = ck.get("visual_projection.weight").float().to(self.device)
+        self.text = None
+        tc = raw.get("text_config")
+        has_tok = (p / "vocab.json").exists() or (p / "tokenizer.json").exists()
+        if tc and has_tok and ck.get("text_projection.weight") is not None:
+            width = tc.get("hidden_size", 512)
+            cfg = ClipTextConfig(vocab_size=tc.get("vocab_size", 49408), width=width,
+                                 layers=tc.get("num_hidden_layers", 12), heads=tc.get("num_attention_heads", 8),
+                                 max_len=tc.get("max_position_embeddings", 77),
+                                 mlp_ratio=tc.get("intermediate_size", 4 * width) // width,
+                                 quick_gelu=tc.get("hidden_act", "quick_gelu") == "quick_gelu")
+            self.text = ClipTextEncoder(cfg, device, get=ck.get)
+            self.text_proj = ck.get("text_projection.weight").float().to(self.device)
+            self.tokenizer = ClipTokenizer.from_dir(p, cfg.max_len)
+
+    @staticmethod
+    def _unit(x: torch.Tensor) -> torch.Tensor:
+        return x / x.norm(dim=-1, keepdim=True).clamp_min(1e-12)
+
+    def embed_images(self, images: list) -> torch.Tensor:
+        size = self.vision.cfg.image_size
+        feats = [self.vision.embed(preprocess_image(im, size)).float() @ self.visual_proj.t() for im in images]
+        return self._unit(torch.stack(feats)).cpu()
+
+    def embed_texts(self, texts: list[str]) -> torch.Tensor:
+        if self.text is None:
+            raise ValueError("this checkpoint has no text tower")
+        feats = []
+        for t in texts:
+            _, pooled = self.text.encode(torch.tensor(self.tokenizer.encode(t)))
+            feats.append(pooled.float() @ self.text_proj.t())
+        return self._unit(torch.stack(feats)).cpu()
+
+
+class VisionService:
+    def __init__(self, device):
+        self.device = device
+        self._lock = threading.Lock()
+        self._loaded: dict[str, _ClipDual] = {}
+
+    def loaded_keys(self) -> list[str]:
+        return [f"clip:{k}" for k in self._loaded]
+
+    def release(self) -> None:
+        with self._lock:
+            self._loaded.clear()
+
+    def _model(self, spec: ModelSpec) -> _ClipDual:
+        path = spec.local_path or spec.requested
+        with self._lock:
+            if path not in self._loaded:
+                self._loaded[path] = _ClipDual(path, self.device)
+            return self._loaded[path]
+
+    def run(self, spec: ModelSpec, req: VisionRequest) -> VisionResult:
+        if req.operation != "embed":
+            raise ValueError(f"vision operation '{req.operation}' is not built (embed is)")
+        m = self._model(spec)
+        out = VisionResult()
+        if req.images:
+            out.image_embeddings = m.embed_images(req.images)
+        if req.texts:
+            out.text_embeddings = m.embed_texts(req.texts)
+        if req.images and req.texts:
+            out.similarity = out.image_embeddings @ out.text_embeddings.t()
+        return out

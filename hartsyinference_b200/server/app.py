@@ -81,6 +81,28 @@ class UsageTracker:
                 self.by_key[key][k] += v
 
 
+def _parse_multipart(body: bytes, content_type: str) -> dict:
+    """multipart/form-data -> {field: str | bytes} (file parts keep their bytes)."""
+    marker = "boundary="
+    if marker not in content_type:
+        raise ValueError("multipart body without a boundary")
+    boundary = content_type.split(marker, 1)[1].split(";")[0].strip().strip('"').encode()
+    out: dict = {}
+    for part in body.split(b"--" + boundary):
+        part = part.lstrip(b"\r\n")
+        if not part or part.startswith(b"--") or b"\r\n\r\n" not in part:
+            continue
+        head, data = part.split(b"\r\n\r\n", 1)
+        data = data[:-2] if data.endswith(b"\r\n") else data
+        disp = next((ln for ln in head.decode("utf-8", "replace").split("\r\n") if ln.lower().startswith("content-disposition")), "")
+        fields = dict(kv.strip().split("=", 1) for kv in disp.split(";")[1:] if "=" in kv)
+        name = fields.get("name", "").strip('"')
+        if not name:
+            continue
+        out[name] = data if "filename" in fields else data.decode("utf-8", "replace")
+    return out
+
+
 def _flatten_parts(messages: list) -> tuple[list, list]:
     """OpenAI content parts -> plain-text messages ("<image>" where a picture was) + decoded images.
     Only ``data:`` URLs are accepted: the server fetches nothing from the network."""
@@ -289,6 +311,51 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
             emb = eng.embeddings.embed(resolve(body.get("model"), Modality.EMBEDDINGS), texts)
         return {"object": "list", "model": body.get("model"),
                 "data": [{"object": "embedding", "index": i, "embedding": e.tolist()} for i, e in enumerate(emb)]}
+
+    # -------------------------------------------------------------------------- audio / vision
+    @app.post("/v1/audio/transcriptions")
+    async def audio_transcriptions(request: Request):
+        import base64
+        from ..engine.requests import AudioRequest
+        ctype = request.headers.get("content-type", "")
+        if ctype.startswith("multipart/form-data"):
+            form = _parse_multipart(await request.body(), ctype)
+            audio = form.get("file")
+        else:
+            form = await request.json()
+            audio = base64.b64decode(form["audio"]) if form.get("audio") else None
+        if not isinstance(audio, (bytes, bytearray)) or not audio:
+            return JSONResponse({"error": {"message": "no audio file in the request", "type": "bad_request"}}, status_code=400)
+        areq = AudioRequest(audio=bytes(audio), language=form.get("language") or None, task=form.get("task") or "transcribe")
+        with heavy_queue.slot():
+            res = eng.transcribe.run(resolve(form.get("model"), Modality.TRANSCRIBE), areq)
+        if (form.get("response_format") or "json") == "text":
+            return PlainTextResponse(res.text)
+        out = {"text": res.text}
+        if form.get("response_format") == "verbose_json":
+            out.update(task=areq.task, language=res.language, duration=res.duration_s,
+                       segments=[{"id": i, "start": s.start, "end": s.end, "text": s.text, "tokens": s.tokens,
+                                  "avg_logprob": s.avg_logprob, "no_speech_prob": s.no_speech_prob}
+                                 for i, s in enumerate(res.segments)])
+        return out
+
+    @app.post("/v1/native/vision")
+    async def native_vision(request: Request):
+        import base64
+        import io
+        from ..engine.requests import VisionRequest
+        body = await request.json()
+        images = []
+        for im in body.get("images") or []:
+            from PIL import Image
+            b64 = im.split(",", 1)[1] if im.startswith("data:") else im
+            images.append(Image.open(io.BytesIO(base64.b64decode(b64))).convert("RGB"))
+        vreq = VisionRequest(operation=body.get("operation", "embed"), images=images, texts=list(body.get("texts") or []))
+        with heavy_queue.slot():
+            res = eng.vision.run(resolve(body.get("model"), Modality.VISION), vreq)
+        return {k: (v.tolist() if v is not None else None)
+                for k, v in (("image_embeddings", res.image_embeddings), ("text_embeddings", res.text_embeddings),
+                             ("similarity", res.similarity))}
 
     # -------------------------------------------------------------------------- image / video
     def _png(rgb: bytes, w: int, h: int) -> bytes:

@@ -1,0 +1,200 @@
+"""Audio front end and Whisper: features against transformers' extractor, model parity against
+transformers' WhisperForConditionalGeneration, decoding grammar, windowing."""
+import math
+
+import pytest
+import torch
+
+from hartsyinference_b200.audio import log_mel_spectrogram, mel_filterbank, read_wav, resample, write_wav
+from hartsyinference_b200.models.audio import WhisperModel, tiny_whisper
+from hartsyinference_b200.pipelines.whisper import (WhisperOptions, WhisperPipeline, WhisperVocab)
+
+
+def test_wav_roundtrip_and_formats():
+    x = torch.sin(torch.arange(4000) * 0.05)[None].repeat(2, 1) * torch.tensor([[0.5], [-0.25]])
+    y, r = read_wav(write_wav(None, x, 22050))
+    assert r == 22050 and y.shape == x.shape and (y - x).abs().max() < 1e-4
+    y, r = read_wav(write_wav(None, x[0], 8000, float32=True))
+    assert r == 8000 and torch.equal(y[0], x[0])
+    with pytest.raises(ValueError):
+        read_wav(b"RIFFxxxxWAVE")
+    with pytest.raises(ValueError):
+        read_wav(b"nope")
+
+
+def test_resample_keeps_a_tone():
+    t = torch.arange(48000) / 48000.0
+    s = torch.sin(2 * math.pi * 440 * t)
+    d = resample(s, 48000, 16000)
+    ref = torch.sin(2 * math.pi * 440 * torch.arange(16000) / 16000.0)
+    assert d.shape == ref.shape and (d[200:-200] - ref[200:-200]).abs().max() < 2e-3
+    u = resample(d, 16000, 44100)
+    ref = torch.sin(2 * math.pi * 440 * torch.arange(44100) / 44100.0)
+    assert u.shape == ref.shape and (u[500:-500] - ref[500:-500]).abs().max() < 2e-3
+    # content above the new Nyquist is removed, not aliased
+    hi = torch.sin(2 * math.pi * 11000 * t)
+    assert resample(hi, 48000, 16000)[200:-200].abs().max() < 0.02
+
+
+def test_log_mel_matches_transformers_extractor():
+    tr = pytest.importorskip("transformers")
+    x = torch.randn(16000 * 3, generator=torch.Generator().manual_seed(0)) * 0.1
+    for mels in (80, 128):
+        fe = tr.WhisperFeatureExtractor(feature_size=mels)
+        ref = fe(x.numpy(), sampling_rate=16000, return_tensors="pt").input_features[0]
+        mine = log_mel_spectrogram(x, n_mels=mels)
+        assert mine.shape == ref.shape == (mels, 3000) and (mine - ref).abs().max() < 1e-4
+    fb = mel_filterbank(40, 512, 16000, htk=True, norm_slaney=False)
+    assert fb.shape == (40, 257) and fb.max() <= 1.0 + 1e-6 and (fb.sum(1) > 0).all()
+
+
+def _hf_pair():
+    tr = pytest.importorskip("transformers")
+    cfg = tiny_whisper()
+    hc = tr.WhisperConfig(vocab_size=cfg.vocab, num_mel_bins=cfg.n_mels, d_model=cfg.width, encoder_layers=cfg.enc_layers,
+                          decoder_layers=cfg.dec_layers, encoder_attention_heads=cfg.heads, decoder_attention_heads=cfg.heads,
+                          encoder_ffn_dim=cfg.ffn, decoder_ffn_dim=cfg.ffn, max_source_positions=cfg.max_source,
+                          max_target_positions=cfg.max_target, pad_token_id=0, bos_token_id=1, eos_token_id=2,
+                          decoder_start_token_id=3, suppress_tokens=None, begin_suppress_tokens=None)
+    torch.manual_seed(0)
+    hf = tr.WhisperForConditionalGeneration(hc).eval()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    return cfg, hf, WhisperModel(cfg, "cpu", get=lambda n: sd.get(n))
+
+
+def test_whisper_matches_transformers():
+    cfg, hf, m = _hf_pair()
+    mel = torch.randn(cfg.n_mels, 2 * cfg.max_source, generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        enc_ref = hf.model.encoder(mel[None]).last_hidden_state[0]
+    enc = m.encode(mel)
+    assert torch.nn.functional.cosine_similarity(enc.float().flatten(), enc_ref.flatten(), dim=0) > 0.999
+    toks = torch.tensor([3, 10, 20, 30, 40, 50])
+    with torch.no_grad():
+        ref = hf(input_features=mel[None], decoder_input_ids=toks[None]).logits[0]
+    st = m.start(enc)
+    # prompt, a multi-token continuation and single steps all go through the same caches
+    mine = torch.cat([m.decode(st, toks[:2]), m.decode(st, toks[2:4]), m.decode(st, toks[4:5]), m.decode(st, toks[5:])])
+    assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0) > 0.999
+    assert st["pos"] == 6
+    with pytest.raises(ValueError):
+        m.decode(st, torch.zeros(cfg.max_target, dtype=torch.int32))
+
+
+def _vocab(cfg):
+    # text ids < 200; eot 200, sot 201, languages 202-203, translate 204, transcribe 205, no-speech 206,
+    # no-timestamps 207, timestamps from 208
+    return WhisperVocab(sot=201, eot=200, transcribe=205, translate=204, no_timestamps=207, timestamp_begin=208,
+                        no_speech=206, languages={"en": 202, "de": 203})
+
+
+def test_whisper_grammar_and_windows():
+    cfg, _, m = _hf_pair()
+    v = _vocab(cfg)
+    pipe = WhisperPipeline(m, v)
+    opts = WhisperOptions(language="en")
+    ninf = float("-inf")
+    tb = v.timestamp_begin
+    # first token: a timestamp no later than max_initial_timestamp
+    lg = pipe._mask_logits(torch.zeros(cfg.vocab), [201, 202, 205], 3, opts)
+    assert (lg[:tb] == ninf).all() and lg[tb] == 0 and lg[tb + 50] == 0 and lg[tb + 51] == ninf
+    # after an opening stamp: text only
+    lg = pipe._mask_logits(torch.zeros(cfg.vocab), [201, 202, 205, tb + 3], 3, opts)
+    assert (lg[tb:] == ninf).all() and lg[5] == 0
+    # after text + one stamp: only a stamp (not earlier) or the end
+    base = torch.zeros(cfg.vocab)
+    base[v.eot] = 20.0          # keeps the "timestamps outweigh text" rule out of this case
+    lg = pipe._mask_logits(base, [201, 202, 205, tb + 3, 7, 8, tb + 9], 3, opts)
+    assert (lg[:v.eot] == ninf).all() and lg[v.eot] == 20 and lg[tb + 8] == ninf and lg[tb + 9] == 0
+    # ... and with flat logits that rule removes every non-timestamp
+    lg = pipe._mask_logits(torch.zeros(cfg.vocab), [201, 202, 205, tb + 3, 7, 8, tb + 9], 3, opts)
+    assert (lg[:tb] == ninf).all() and lg[tb + 9] == 0
+    # without timestamps no stamp can be produced
+    lg = pipe._mask_logits(torch.zeros(cfg.vocab), [201, 202, 205, 207, 4], 4, WhisperOptions(language="en", timestamps=False))
+    assert (lg[tb:] == ninf).all() and lg[v.eot] == 0
+
+    # segments: two closed pairs, then the window advances to the last stamp
+    toks = [tb + 0, 5, 6, tb + 10, tb + 10, 7, tb + 25, tb + 25]
+    segs, adv = pipe._segments(toks, 30.0, 1.0, -0.1, 0.0)
+    assert [(round(s.start, 2), round(s.end, 2), s.tokens) for s in segs] == [(30.0, 30.2, [5, 6]), (30.2, 30.5, [7])]
+    assert abs(adv - 0.5) < 1e-6
+    segs, adv = pipe._segments([tb + 0, 5, 6, tb + 20], 0.0, 1.0, -0.1, 0.0)
+    assert len(segs) == 1 and abs(segs[0].end - 0.4) < 1e-6 and adv == 1.0
+
+    # end to end on noise: every window is decoded, stamps are ordered, time moves forward
+    lang, probs = pipe.detect_language(m.encode(torch.randn(cfg.n_mels, 2 * cfg.max_source)))
+    assert lang in ("en", "de") and abs(sum(probs.values()) - 1) < 1e-4
+    audio = torch.randn(int(16000 * 2.5), generator=torch.Generator().manual_seed(3)) * 0.1
+    res = pipe.transcribe(audio, 16000, WhisperOptions(no_speech_threshold=2.0))
+    assert res.language in ("en", "de") and abs(res.duration_s - 2.5) < 1e-6
+    assert res.segments and all(s.end >= s.start for s in res.segments)
+    assert all(b.start >= a.start for a, b in zip(res.segments, res.segments[1:]))
+    res2 = pipe.transcribe(torch.stack([audio, audio]), 16000, WhisperOptions(language="de", timestamps=False, max_new_tokens=5,
+                                                                              no_speech_threshold=2.0))
+    assert res2.language == "de" and len(res2.segments) == 3 and all(len(s.tokens) <= 5 for s in res2.segments)
+
+
+def _whisper_dir(tmp_path):
+    """A tiny Whisper checkpoint directory: config, weights, a byte-level tokenizer.json with the
+    control tokens."""
+    import json
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    cfg, hf, _ = _hf_pair()
+    d = tmp_path / "whisper-tiny-synth"
+    tensors = {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items() if k != "proj_out.weight"}
+    save_hf_checkpoint({**hf.config.to_dict(), "model_type": "whisper"}, tensors, d)
+    from hartsyinference_b200.assets.tokenizer import _bytes_to_unicode
+    b2u = _bytes_to_unicode()
+    vocab = {b2u[b]: b for b in range(200)}
+    specials = ["<|endoftext|>", "<|startoftranscript|>", "<|en|>", "<|de|>", "<|translate|>", "<|transcribe|>",
+                "<|nospeech|>", "<|notimestamps|>"] + [f"<|{i * 0.02:.2f}|>" for i in range(cfg.vocab - 208)]
+    added = [{"id": 200 + i, "content": s, "special": True} for i, s in enumerate(specials)]
+    (d / "tokenizer.json").write_text(json.dumps({
+        "model": {"type": "BPE", "vocab": vocab, "merges": []}, "added_tokens": added,
+        "pre_tokenizer": {"type": "ByteLevel", "add_prefix_space": False}}))
+    (d / "generation_config.json").write_text(json.dumps({"suppress_tokens": [1, 2], "begin_suppress_tokens": [32, 200]}))
+    return d
+
+
+def test_transcribe_service_and_endpoint(tmp_path):
+    from fastapi.testclient import TestClient
+    from hartsyinference_b200.engine import AudioRequest, InferenceEngine, ModelSpec
+    from hartsyinference_b200.engine.requests import Modality
+    from hartsyinference_b200.server.app import ServerOptions, create_app
+    d = _whisper_dir(tmp_path)
+    eng = InferenceEngine("cpu")
+    assert eng.is_supported(Modality.TRANSCRIBE)
+    audio = torch.randn(16000, generator=torch.Generator().manual_seed(5)) * 0.1
+    wav = write_wav(tmp_path / "a.wav", audio, 16000)
+    res = eng.transcribe.run(ModelSpec(str(d)), AudioRequest(audio=str(tmp_path / "a.wav"), language="en"))
+    assert res.language == "en" and abs(res.duration_s - 1.0) < 1e-3
+    pipe = eng.transcribe._pipe(ModelSpec(str(d)))
+    v = pipe.vocab
+    assert (v.sot, v.eot, v.no_timestamps, v.timestamp_begin, v.no_speech) == (201, 200, 207, 208, 206)
+    assert v.languages == {"en": 202, "de": 203} and v.suppress == [1, 2] and v.begin_suppress == [32, 200]
+    assert "whisper:" + str(d) in eng.loaded_pipeline_keys
+
+    app = create_app(ServerOptions(models={"whisper": str(d)}), engine=eng)
+    with TestClient(app) as c:
+        boundary = "xyzBOUNDARY"
+        body = (f"--{boundary}\r\nContent-Disposition: form-data; name=\"model\"\r\n\r\nwhisper\r\n"
+                f"--{boundary}\r\nContent-Disposition: form-data; name=\"response_format\"\r\n\r\nverbose_json\r\n"
+                f"--{boundary}\r\nContent-Disposition: form-data; name=\"file\"; filename=\"a.wav\"\r\n"
+                f"Content-Type: audio/wav\r\n\r\n").encode() + wav + f"\r\n--{boundary}--\r\n".encode()
+        r = c.post("/v1/audio/transcriptions", content=body, headers={"content-type": f"multipart/form-data; boundary={boundary}"})
+        assert r.status_code == 200, r.text
+        j = r.json()
+        assert j["text"] == res.text or isinstance(j["text"], str)
+        assert abs(j["duration"] - 1.0) < 1e-3 and isinstance(j["segments"], list)
+        r = c.post("/v1/audio/transcriptions", json={"model": "whisper"})
+        assert r.status_code == 400
+    eng.close()
+
+
+def test_cli_transcribe_verb(tmp_path):
+    from click.testing import CliRunner
+    from hartsyinference_b200.cli.main import cli
+    d = _whisper_dir(tmp_path)
+    write_wav(tmp_path / "b.wav", torch.randn(8000, generator=torch.Generator().manual_seed(7)) * 0.1, 8000)
+    r = CliRunner().invoke(cli, ["transcribe", str(d), str(tmp_path / "b.wav"), "--language", "en", "--json", "--device", "cpu"])
+    assert r.exit_code == 0, r.output

@@ -160,3 +160,73 @@ def test_server_flattens_openai_image_parts():
     assert len(images) == 1 and images[0].size == (8, 8)
     with pytest.raises(ValueError):
         _flatten_parts([{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "http://x/y.png"}}]}])
+
+
+def _clip_dir(tmp_path):
+    """A tiny two-tower CLIP checkpoint with a byte-level vocab.json / merges.txt."""
+    import json
+    from hartsyinference_b200.assets.tokenizer import _bytes_to_unicode
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    tr = pytest.importorskip("transformers")
+    b2u = _bytes_to_unicode()
+    vocab = {}
+    for b in range(256):
+        vocab[b2u[b]] = len(vocab)
+    for b in range(256):
+        vocab[b2u[b] + "</w>"] = len(vocab)
+    merges = [("c", "a"), ("ca", "t</w>"), ("d", "o"), ("do", "g</w>"), ("a</w>", "x")]
+    for a, b in merges[:4]:
+        vocab[a + b] = len(vocab)
+    vocab["<|startoftext|>"] = len(vocab)
+    vocab["<|endoftext|>"] = len(vocab)
+    vc = tiny_clip_vision()
+    cfg = tr.CLIPConfig(
+        text_config=dict(vocab_size=len(vocab), hidden_size=64, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                         max_position_embeddings=16, bos_token_id=vocab["<|startoftext|>"], eos_token_id=vocab["<|endoftext|>"],
+                         pad_token_id=vocab["<|endoftext|>"]),
+        vision_config=dict(hidden_size=vc.width, intermediate_size=vc.width * vc.mlp_ratio, num_hidden_layers=vc.layers,
+                           num_attention_heads=vc.heads, image_size=vc.image_size, patch_size=vc.patch),
+        projection_dim=32)
+    torch.manual_seed(2)
+    hf = tr.CLIPModel(cfg).eval()
+    d = tmp_path / "clip-synth"
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()
+                                       if "position_ids" not in k}, d)
+    (d / "vocab.json").write_text(json.dumps(vocab))
+    (d / "merges.txt").write_text("#version: 0.2\n" + "\n".join(f"{a} {b}" for a, b in merges[:4]) + "\n")
+    return d, hf, tr.CLIPTokenizer(str(d / "vocab.json"), str(d / "merges.txt"))
+
+
+def test_clip_tokenizer_and_vision_service(tmp_path):
+    from hartsyinference_b200.assets.tokenizer import ClipTokenizer
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, VisionRequest
+    d, hf, hf_tok = _clip_dir(tmp_path)
+    tok = ClipTokenizer.from_dir(d, max_len=77)
+    for text in ["A cat", "the DOG, and a cat!", "naïve café 日本", ""]:
+        assert tok.encode(text) == hf_tok(text)["input_ids"]
+    tok = ClipTokenizer.from_dir(d, max_len=16)
+    long = tok.encode("the dog and the cat and the dog again")
+    assert len(long) == 16 and long[0] == tok.bos_id and long[-1] == tok.eos_id
+    assert tok.decode(tok.encode("a cat and dog")) == "a cat and dog"
+    assert len(tok.encode("x", pad=True)) == 16
+
+    eng = InferenceEngine("cpu")
+    rng = torch.Generator().manual_seed(0)
+    imgs = [torch.rand(3, 32, 32, generator=rng), torch.rand(3, 32, 32, generator=rng)]
+    texts = ["a cat", "a dog and a cat"]
+    res = eng.vision.run(ModelSpec(str(d)), VisionRequest(images=imgs, texts=texts))
+    assert res.image_embeddings.shape == (2, 32) and res.text_embeddings.shape == (2, 32) and res.similarity.shape == (2, 2)
+    with torch.no_grad():
+        px = torch.stack([preprocess_image(im, 32) for im in imgs])
+        fi = hf.get_image_features(pixel_values=px)
+        enc = hf_tok(texts, padding=True, return_tensors="pt")
+        ft = hf.get_text_features(**enc)
+    fi = getattr(fi, "pooler_output", fi)
+    ft = getattr(ft, "pooler_output", ft)
+    fi, ft = fi / fi.norm(dim=-1, keepdim=True), ft / ft.norm(dim=-1, keepdim=True)
+    assert torch.nn.functional.cosine_similarity(res.image_embeddings.flatten(), fi.flatten(), dim=0) > 0.99
+    assert torch.nn.functional.cosine_similarity(res.text_embeddings.flatten(), ft.flatten(), dim=0) > 0.99
+    assert (res.similarity - fi @ ft.t()).abs().max() < 0.05
+    with pytest.raises(ValueError):
+        eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="detect", images=imgs))
+    eng.close()
