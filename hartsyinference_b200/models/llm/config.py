@@ -85,6 +85,14 @@ class TransformerConfig:
     residual_multiplier: float = 1.0    # Granite
     embedding_multiplier: float = 1.0
     logits_scale: float = 1.0
+    pre_norm: bool = True               # False: norms only after the blocks (OLMo 2)
+    qk_norm_full: bool = False          # q/k RMSNorm over the whole projection instead of per head (OLMo 2, OLMoE)
+    rope_local_theta: float = 0.0       # rotary base of the sliding-window layers when it differs (Gemma 3)
+    layer_types: tuple = ()             # explicit per-layer "sliding_attention" / "full_attention"
+    norm_type: str = "rms"              # rms | layernorm
+    norm_bias: bool = False
+    parallel_residual: bool = False     # x + attn(n1(x)) + ffn(n2(x)) (GPT-NeoX, Cohere)
+    shared_parallel_norm: bool = False  # the parallel branches share one norm (Cohere)
     moe: Optional[MoeConfig] = None
     mla: Optional[MlaConfig] = None
     bos_token_id: int = 1
@@ -105,9 +113,18 @@ class TransformerConfig:
     def layer_is_moe(self, layer: int) -> bool:
         return self.moe is not None and self.moe.num_experts > 0 and layer >= self.moe.first_dense_layers
 
+    @property
+    def general_path(self) -> bool:
+        """Architectures whose block structure is outside the fused decode path: they run the same
+        kernels through an unfused layer loop."""
+        return (not self.pre_norm or self.qk_norm_full or self.norm_type != "rms" or self.parallel_residual
+                or self.o_bias or self.ffn_bias or not self.gated_ffn or self.activation not in ("silu", "gelu_tanh"))
+
     def layer_window(self, layer: int) -> int:
         if self.sliding_window <= 0:
             return 0
+        if self.layer_types:
+            return self.sliding_window if self.layer_types[layer] == "sliding_attention" else 0
         if self.sliding_window_pattern > 0 and (layer + 1) % self.sliding_window_pattern == 0:
             return 0
         return self.sliding_window
@@ -189,7 +206,11 @@ def from_hf_config(d: dict) -> TransformerConfig:
     heads = d["num_attention_heads"]
     hidden = d["hidden_size"]
     head_dim = d.get("head_dim") or hidden // heads
-    rs = d.get("rope_scaling") or {}
+    rs = d.get("rope_scaling") or d.get("rope_parameters") or {}
+    local_theta = float(d.get("rope_local_base_freq") or 0.0)
+    if "full_attention" in rs:            # per-layer-type rotary parameters (Gemma 3)
+        local_theta = float((rs.get("sliding_attention") or {}).get("rope_theta", local_theta) or 0.0)
+        rs = rs["full_attention"] or {}
     kind = rs.get("rope_type", rs.get("type", "none")) if rs else "none"
     scaling = RopeScaling(kind=kind if kind in ("linear", "llama3", "yarn") else "none",
                           factor=float(rs.get("factor", 1.0)),
@@ -204,21 +225,30 @@ def from_hf_config(d: dict) -> TransformerConfig:
         arch=mt, vocab_size=d["vocab_size"], hidden_size=hidden, num_layers=d["num_hidden_layers"],
         num_heads=heads, num_kv_heads=d.get("num_key_value_heads", heads), head_dim=head_dim,
         ffn_size=d.get("intermediate_size", 4 * hidden), rms_eps=d.get("rms_norm_eps", 1e-5),
-        rope_theta=float(d.get("rope_theta", 10000.0)), rope_scaling=scaling,
+        rope_theta=float(d.get("rope_theta") or rs.get("rope_theta") or 10000.0), rope_scaling=scaling,
         max_position=d.get("max_position_embeddings", 8192),
         tie_embeddings=bool(d.get("tie_word_embeddings", False)),
         qkv_bias=bool(d.get("attention_bias", mt in ("qwen2", "qwen2_moe"))),
         bos_token_id=d.get("bos_token_id", 1) or 0, eos_token_ids=eos)
-    if mt in ("qwen3", "qwen3_moe", "olmo2"):
+    prf = d.get("partial_rotary_factor", rs.get("partial_rotary_factor") if rs else None)
+    if prf and float(prf) < 1.0:
+        kw["rope_dim"] = int(head_dim * float(prf))
+    if mt in ("qwen3", "qwen3_moe", "olmo2", "olmoe"):
         kw["qk_norm"] = True
         kw["qkv_bias"] = bool(d.get("attention_bias", False))
+    if mt in ("olmo2", "olmoe"):
+        kw["qk_norm_full"] = True
+    if mt == "olmo2":
+        kw.update(pre_norm=False, post_norms=True)
     if mt.startswith("gemma"):
         kw.update(norm_plus_one=True, embed_scale=hidden ** 0.5, activation="gelu_tanh",
                   logit_softcap=float(d.get("final_logit_softcapping") or 0.0),
                   attn_softcap=float(d.get("attn_logit_softcapping") or 0.0),
                   post_norms=mt in ("gemma2", "gemma3", "gemma3_text"),
                   sliding_window=int(d.get("sliding_window") or 0),
-                  sliding_window_pattern=int(d.get("sliding_window_pattern", 2 if mt == "gemma2" else 6)),
+                  sliding_window_pattern=int(d.get("sliding_window_pattern") or (2 if mt == "gemma2" else 6)),
+                  layer_types=tuple(d.get("layer_types") or ()),
+                  rope_local_theta=local_theta if mt in ("gemma3", "gemma3_text") else 0.0,
                   qk_norm=mt in ("gemma3", "gemma3_text"))
         if d.get("query_pre_attn_scalar"):
             kw["attn_scale"] = float(d["query_pre_attn_scalar"]) ** -0.5

@@ -90,6 +90,8 @@ class LayerWeights:
     post_ffn_norm: Optional[torch.Tensor] = None
     ffn_module: Optional[object] = None               # MoE feed-forward (callable) instead of gate_up/down
     attn_module: Optional[object] = None              # MLA attention (callable) instead of qkv/o
+    in_norm_b: Optional[torch.Tensor] = None          # LayerNorm biases (StableLM, StarCoder 2, GPT-NeoX, Nemotron)
+    post_norm_b: Optional[torch.Tensor] = None
 
 
 class DecoderModel:
@@ -115,6 +117,10 @@ class DecoderModel:
         self.layers: list[LayerWeights] = []
         rot = cfg.mla.qk_rope_head_dim if cfg.mla is not None else cfg.rotary_dim
         self.inv_freq, self.rope_attn_factor = build_inv_freq(rot, cfg.rope_theta, cfg.rope_scaling, self.device)
+        # sliding-window layers of Gemma 3 rotate with their own base and no long-context scaling
+        self.inv_freq_local = (build_inv_freq(rot, cfg.rope_local_theta, RopeScaling(), self.device)[0]
+                               if cfg.rope_local_theta > 0 else None)
+        self.final_norm_b: Optional[torch.Tensor] = None
         self.kv_cache: Optional[torch.Tensor] = None
         self.all_reduce: Callable[[torch.Tensor], torch.Tensor] = self.comm.all_reduce
         # hook for the fused GEMM + all-reduce path: (x, weight, residual) -> reduced output
@@ -162,15 +168,32 @@ class DecoderModel:
             hw = torch.cat([hw, torch.zeros(self.vocab_local - hw.shape[0], hw.shape[1], dtype=hw.dtype)])
         self.lm_head = self._lw(hw.to(dt), allow_fp8=False)
         self.final_norm = need("model.norm.weight").to(dt).to(self.device)
+        dev = lambda t_: None if t_ is None else t_.to(dt).to(self.device)
+        self.final_norm_b = dev(get("model.norm.bias")) if cfg.norm_bias else None
+        if cfg.qk_norm_full and tp > 1:
+            raise ValueError("q/k normalisation over the whole projection is not sharded; load this model with tp=1")
         kvs = self.kv_head_slice()
         self.layers = []
+
+        def row_bias(name):            # the bias of a row-parallel linear is added once, by rank 0
+            b = get(name)
+            if b is None:
+                return None
+            return (b if r == 0 else torch.zeros_like(b)).to(dt)
+
         for i in range(self.layer0, self.layer1):
             p = f"model.layers.{i}."
             is_moe = cfg.moe is not None and cfg.moe.num_experts > 0 and i >= cfg.moe.first_dense_layers
+            post_name = "post_attention_layernorm"
+            if cfg.shared_parallel_norm:
+                post_name = "input_layernorm"
             lw = LayerWeights(
-                in_norm=need(p + "input_layernorm.weight").to(dt).to(self.device),
+                in_norm=dev(need(p + "input_layernorm.weight")) if cfg.pre_norm else None,
                 qkv=None, o=None,
-                post_norm=need(p + "post_attention_layernorm.weight").to(dt).to(self.device))
+                post_norm=dev(need(p + post_name + ".weight")))
+            if cfg.norm_bias:
+                lw.in_norm_b = dev(get(p + "input_layernorm.bias"))
+                lw.post_norm_b = dev(get(p + post_name + ".bias"))
             if cfg.mla is not None:
                 lw.attn_module = self._load_mla(need, get, p + "self_attn.")
             else:
@@ -184,22 +207,31 @@ class DecoderModel:
                                        need(p + "self_attn.v_proj.bias")[kvs.start * d:kvs.stop * d]])
                 o = need(p + "self_attn.o_proj.weight")[:, r * self.hq * d:(r + 1) * self.hq * d]
                 lw.qkv = self._lw(torch.cat([q, k, v]).to(dt), None if qkv_b is None else qkv_b.to(dt))
-                lw.o = self._lw(o.contiguous().to(dt))
+                lw.o = self._lw(o.contiguous().to(dt), row_bias(p + "self_attn.o_proj.bias") if cfg.o_bias else None)
             if is_moe:
                 lw.ffn_module = self._load_moe(need, get, p)
             else:
-                gate = need(p + "mlp.gate_proj.weight")[r * self.ffn:(r + 1) * self.ffn]
-                up = need(p + "mlp.up_proj.weight")[r * self.ffn:(r + 1) * self.ffn]
-                down = need(p + "mlp.down_proj.weight")[:, r * self.ffn:(r + 1) * self.ffn]
-                lw.gate_up = self._lw(torch.cat([gate, up]).to(dt))
-                lw.down = self._lw(down.contiguous().to(dt))
+                fs = slice(r * self.ffn, (r + 1) * self.ffn)
+                up = need(p + "mlp.up_proj.weight")[fs]
+                down = need(p + "mlp.down_proj.weight")[:, fs]
+                ub = get(p + "mlp.up_proj.bias") if cfg.ffn_bias else None
+                if cfg.gated_ffn:
+                    gate = need(p + "mlp.gate_proj.weight")[fs]
+                    gb = get(p + "mlp.gate_proj.bias") if cfg.ffn_bias else None
+                    gub = torch.cat([gb[fs], ub[fs]]).to(dt) if gb is not None and ub is not None else None
+                    lw.gate_up = self._lw(torch.cat([gate, up]).to(dt), gub)
+                else:
+                    lw.gate_up = self._lw(up.contiguous().to(dt), None if ub is None else ub[fs].to(dt))
+                lw.down = self._lw(down.contiguous().to(dt), row_bias(p + "mlp.down_proj.bias") if cfg.ffn_bias else None)
             if cfg.qk_norm:
-                lw.q_norm = need(p + "self_attn.q_norm.weight").to(dt).to(self.device)
-                lw.k_norm = need(p + "self_attn.k_norm.weight").to(dt).to(self.device)
+                qn, kn = need(p + "self_attn.q_norm.weight"), need(p + "self_attn.k_norm.weight")
+                if cfg.norm_plus_one:      # Gemma 3 stores w - 1 for these too; the rotary kernel multiplies by w
+                    qn, kn = qn.float() + 1.0, kn.float() + 1.0
+                lw.q_norm, lw.k_norm = qn.to(dt).to(self.device), kn.to(dt).to(self.device)
             if cfg.post_norms:
                 lw.post_attn_norm = lw.post_norm
-                lw.post_norm = need(p + "pre_feedforward_layernorm.weight").to(dt).to(self.device)
-                lw.post_ffn_norm = need(p + "post_feedforward_layernorm.weight").to(dt).to(self.device)
+                lw.post_norm = dev(need(p + "pre_feedforward_layernorm.weight")) if cfg.pre_norm else None
+                lw.post_ffn_norm = dev(need(p + "post_feedforward_layernorm.weight"))
             self.layers.append(lw)
 
     def _load_mla(self, need, get, p: str):
@@ -241,7 +273,12 @@ class DecoderModel:
         router = LinearWeight(need(base + "gate.weight").to(dt).to(self.device))
         bias = get(base + "gate.e_score_correction_bias")
         gus, dns = [], []
+        stacked_gu, stacked_dn = get(base + "experts.gate_up_proj"), get(base + "experts.down_proj")
         for e in range(r * e_local, (r + 1) * e_local):
+            if stacked_gu is not None:        # one [E, 2F, H] / [E, H, F] tensor per layer
+                gus.append(stacked_gu[e].to(dt))
+                dns.append(stacked_dn[e].to(dt))
+                continue
             ep = f"{base}experts.{e}."
             gus.append(torch.cat([need(ep + names[0] + ".weight"), need(ep + names[1] + ".weight")]).to(dt))
             dns.append(need(ep + names[2] + ".weight").to(dt))
@@ -411,6 +448,108 @@ class DecoderModel:
         y = ops.linear(x, w)
         return self.all_reduce(y) if self.tp > 1 else y
 
+    # ------------------------------------------------------------------------------ layer pieces
+    def _attention(self, lw: LayerWeights, li: int, h: torch.Tensor, hq8, batch: ForwardBatch, scale: float) -> torch.Tensor:
+        """qkv projection, (q/k norm,) rotary + KV-cache write, paged attention, output projection."""
+        cfg, d = self.cfg, self.cfg.head_dim
+        if lw.attn_module is not None:
+            return lw.attn_module(h, batch, li, self)
+        t = h.shape[0]
+        qkv = ops.linear(hq8 if hq8 is not None else h, lw.qkv)
+        q_norm_w, k_norm_w = lw.q_norm, lw.k_norm
+        if cfg.qk_norm_full and q_norm_w is not None:
+            # RMSNorm over all heads of q (and of k) at once, before the heads are split
+            nq, nk = self.hq * d, self.hkv * d
+            qn, _, _ = ops.norm(qkv[:, :nq].contiguous(), q_norm_w, eps=cfg.rms_eps)
+            kn, _, _ = ops.norm(qkv[:, nq:nq + nk].contiguous(), k_norm_w, eps=cfg.rms_eps)
+            qkv = torch.cat([qn, kn, qkv[:, nq + nk:]], 1)
+            q_norm_w = k_norm_w = None
+        kc, vc = (self.kv_cache[li, 0], self.kv_cache[li, 1]) if self.kv_cache is not None else (None, None)
+        window = cfg.layer_window(self.layer0 + li)
+        inv_freq = self.inv_freq_local if (window > 0 and self.inv_freq_local is not None) else self.inv_freq
+        q, _, _ = ops.rope_kv(qkv, batch.positions, self.hq, self.hkv, d, k_cache=kc, v_cache=vc,
+                              slot_mapping=batch.slot_mapping, rot=cfg.rotary_dim, theta=cfg.rope_theta,
+                              inv_freq=inv_freq, style=cfg.rope_style, q_norm_w=q_norm_w,
+                              k_norm_w=k_norm_w, eps=cfg.rms_eps)
+        if batch.is_decode:
+            att = ops.attn_decode(q, kc, vc, batch.block_table, batch.kv_lens, scale=scale,
+                                  softcap=cfg.attn_softcap, window=window,
+                                  max_kv_len=batch.max_kv_len or None)
+        else:
+            att = ops.attn_prefill_paged(q, kc, vc, batch.block_table, batch.kv_lens, batch.cu_q,
+                                         batch.max_q_len, causal=True, scale=scale,
+                                         softcap=cfg.attn_softcap, window=window)
+        return self._reduce_linear(att.reshape(t, self.hq * d), lw.o)
+
+    def _block_norm(self, x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor]) -> torch.Tensor:
+        cfg = self.cfg
+        return ops.norm(x, w, bias=b, eps=cfg.rms_eps, layernorm=cfg.norm_type == "layernorm",
+                        weight_plus_one=cfg.norm_plus_one)[0]
+
+    @staticmethod
+    def _activation(x: torch.Tensor, name: str) -> torch.Tensor:
+        xf = x.float()
+        if name == "silu":
+            y = torch.nn.functional.silu(xf)
+        elif name == "gelu":
+            y = torch.nn.functional.gelu(xf)
+        elif name == "gelu_tanh":
+            y = torch.nn.functional.gelu(xf, approximate="tanh")
+        elif name == "relu2":
+            y = torch.relu(xf) ** 2
+        elif name == "relu":
+            y = torch.relu(xf)
+        else:
+            raise ValueError(f"unknown activation '{name}'")
+        return y.to(x.dtype)
+
+    def _ffn(self, lw: LayerWeights, h: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        if lw.ffn_module is not None:
+            return lw.ffn_module(h, self)
+        gu = ops.linear(h, lw.gate_up)
+        if not cfg.gated_ffn:
+            return self._reduce_linear(self._activation(gu, cfg.activation), lw.down)
+        if cfg.activation in ("silu", "gelu_tanh"):
+            act, _ = ops.glu(gu, cfg.activation)
+        else:
+            f = gu.shape[1] // 2
+            act = (self._activation(gu[:, :f], cfg.activation).float() * gu[:, f:].float()).to(gu.dtype)
+        return self._reduce_linear(act.contiguous(), lw.down)
+
+    def _forward_general(self, batch: ForwardBatch, x: torch.Tensor, scale: float):
+        """Layer loop for block structures outside the fused path: norms after the blocks instead of
+        before (OLMo 2), LayerNorm with bias, parallel attention / feed-forward branches, linear
+        biases, non-gated or other activations. ``x`` is the residual stream itself; the kernels
+        underneath (GEMMs, rotary + cache write, paged attention) are the same."""
+        cfg = self.cfg
+        rm = cfg.residual_multiplier
+
+        def add(stream, *deltas):
+            y = stream.float()
+            for dlt in deltas:
+                y = y + (dlt.float() * rm if rm != 1.0 else dlt.float())
+            return y.to(stream.dtype)
+
+        for li, lw in enumerate(self.layers):
+            h = self._block_norm(x, lw.in_norm, lw.in_norm_b) if cfg.pre_norm else x
+            a = self._attention(lw, li, h, None, batch, scale)
+            if lw.post_attn_norm is not None:
+                a = self._block_norm(a, lw.post_attn_norm, None)
+            if cfg.parallel_residual:
+                h2 = h if cfg.shared_parallel_norm else self._block_norm(x, lw.post_norm, lw.post_norm_b)
+                x = add(x, a, self._ffn(lw, h2))
+                continue
+            x = add(x, a)
+            h2 = self._block_norm(x, lw.post_norm, lw.post_norm_b) if (cfg.pre_norm and lw.post_norm is not None) else x
+            f = self._ffn(lw, h2)
+            if lw.post_ffn_norm is not None:
+                f = self._block_norm(f, lw.post_ffn_norm, None)
+            x = add(x, f)
+        if not self.last_stage:
+            return x, None
+        return self._block_norm(x, self.final_norm, self.final_norm_b)
+
     def forward_hidden(self, batch: ForwardBatch, hidden_in: Optional[tuple] = None):
         """Runs this instance's layers. The last pipeline stage (the only one by default) returns the
         final-normed hidden states [T, H]; an earlier stage returns ``(x, residual)`` for the next
@@ -424,9 +563,10 @@ class DecoderModel:
             x = batch.embeds
         else:
             x = ops.embedding(batch.tokens, self.embed, cfg.embed_scale * cfg.embedding_multiplier)
-        t = x.shape[0]
         scale = self._attn_scale()
         fp8 = self.fp8 and x.is_cuda
+        if cfg.general_path:
+            return self._forward_general(batch, x if res is None else (x.float() + res.float()).to(x.dtype), scale)
         for li, lw in enumerate(self.layers):
             # ---- attention block
             if res is None:
@@ -437,25 +577,7 @@ class DecoderModel:
                 h, res, hq8 = ops.norm(x, lw.in_norm, residual=res, eps=cfg.rms_eps,
                                        weight_plus_one=cfg.norm_plus_one,
                                        emit_fp8=fp8 and lw.qkv is not None and lw.qkv.is_fp8, emit_bf16=True)
-            if lw.attn_module is not None:
-                a = lw.attn_module(h, batch, li, self)
-            else:
-                qkv = ops.linear(hq8 if hq8 is not None else h, lw.qkv)
-                kc, vc = (self.kv_cache[li, 0], self.kv_cache[li, 1]) if self.kv_cache is not None else (None, None)
-                q, _, _ = ops.rope_kv(qkv, batch.positions, self.hq, self.hkv, d, k_cache=kc, v_cache=vc,
-                                      slot_mapping=batch.slot_mapping, rot=cfg.rotary_dim, theta=cfg.rope_theta,
-                                      inv_freq=self.inv_freq, style=cfg.rope_style, q_norm_w=lw.q_norm,
-                                      k_norm_w=lw.k_norm, eps=cfg.rms_eps)
-                window = cfg.layer_window(self.layer0 + li)
-                if batch.is_decode:
-                    att = ops.attn_decode(q, kc, vc, batch.block_table, batch.kv_lens, scale=scale,
-                                          softcap=cfg.attn_softcap, window=window,
-                                          max_kv_len=batch.max_kv_len or None)
-                else:
-                    att = ops.attn_prefill_paged(q, kc, vc, batch.block_table, batch.kv_lens, batch.cu_q,
-                                                 batch.max_q_len, causal=True, scale=scale,
-                                                 softcap=cfg.attn_softcap, window=window)
-                a = self._reduce_linear(att.reshape(t, self.hq * d), lw.o)
+            a = self._attention(lw, li, h, hq8, batch, scale)
             if lw.post_attn_norm is not None:
                 a, _, _ = ops.norm(a, lw.post_attn_norm, eps=cfg.rms_eps, weight_plus_one=cfg.norm_plus_one)
             if cfg.residual_multiplier != 1.0:
