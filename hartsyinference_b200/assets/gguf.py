@@ -94,6 +94,8 @@ class GgufFile:
         self.metadata: dict = json.loads(L.b200_gguf_metadata(self._h).decode("utf-8", errors="replace"))
         self._index = {L.b200_gguf_name(self._h, i).decode(): i for i in range(L.b200_gguf_count(self._h))}
         self.metadata["__has_output_weight__"] = "output.weight" in self._index
+        self.metadata["__has_qkv_bias__"] = "blk.0.attn_q.bias" in self._index or "blk.0.attn_qkv.bias" in self._index
+        self.metadata["__has_expert_bias__"] = any(k.endswith("exp_probs_b.bias") for k in self._index)
 
     def keys(self) -> list[str]:
         return list(self._index)

@@ -221,7 +221,12 @@ def convert(src, dst, quant):
     import torch
     from ..assets import gguf as G
     from ..assets.safetensors import SafeTensorsFile, save_file
-    if src.endswith(".gguf") and dst.endswith(".safetensors"):
+    if Path(src).is_dir() and dst.endswith(".gguf"):
+        # a Hugging Face decoder directory: architecture-aware conversion (names, q/k permutation, experts, tokenizer)
+        from ..assets.converters import hf_to_gguf
+        md = hf_to_gguf(src, dst, quant)
+        click.echo(f"{md['general.architecture']}: {md.get(md['general.architecture'] + '.block_count')} blocks")
+    elif src.endswith(".gguf") and dst.endswith(".safetensors"):
         f = G.GgufFile(src)
         save_file({k: f.get(k) for k in f.keys()}, dst, {"format": "pt", "source": Path(src).name})
     elif dst.endswith(".gguf"):

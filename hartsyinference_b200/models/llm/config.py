@@ -200,8 +200,9 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 
 def from_hf_config(d: dict) -> TransformerConfig:
-    """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma / granite /
-    deepseek_v3 / olmoe / qwen2_moe families) onto :class:`TransformerConfig`."""
+    """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / nemotron / gpt_neox / deepseek_v2-v3 / mixtral /
+    olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     heads = d["num_attention_heads"]
     hidden = d["hidden_size"]
@@ -224,7 +225,9 @@ def from_hf_config(d: dict) -> TransformerConfig:
     kw: dict[str, Any] = dict(
         arch=mt, vocab_size=d["vocab_size"], hidden_size=hidden, num_layers=d["num_hidden_layers"],
         num_heads=heads, num_kv_heads=d.get("num_key_value_heads", heads), head_dim=head_dim,
-        ffn_size=d.get("intermediate_size", 4 * hidden), rms_eps=d.get("rms_norm_eps", 1e-5),
+        ffn_size=d.get("intermediate_size") or 4 * hidden,
+        rms_eps=float(next((d[k] for k in ("rms_norm_eps", "layer_norm_eps", "norm_epsilon", "norm_eps",
+                                           "layer_norm_epsilon") if d.get(k) is not None), 1e-5)),
         rope_theta=float(d.get("rope_theta") or rs.get("rope_theta") or 10000.0), rope_scaling=scaling,
         max_position=d.get("max_position_embeddings", 8192),
         tie_embeddings=bool(d.get("tie_word_embeddings", False)),
@@ -252,6 +255,34 @@ def from_hf_config(d: dict) -> TransformerConfig:
                   qk_norm=mt in ("gemma3", "gemma3_text"))
         if d.get("query_pre_attn_scalar"):
             kw["attn_scale"] = float(d["query_pre_attn_scalar"]) ** -0.5
+    act = {"silu": "silu", "swish": "silu", "gelu_pytorch_tanh": "gelu_tanh", "gelu_new": "gelu_tanh",
+           "gelu_fast": "gelu_tanh", "gelu": "gelu", "relu2": "relu2", "relu": "relu"}.get(
+               d.get("hidden_act") or d.get("hidden_activation") or "", None)
+    if act is not None and not mt.startswith("gemma"):
+        kw["activation"] = act
+    if mt in ("glm", "glm4"):
+        kw.update(rope_style=1, qkv_bias=bool(d.get("attention_bias", True)), post_norms=mt == "glm4")
+    if mt == "starcoder2":
+        ub = bool(d.get("use_bias", True))
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=ub, o_bias=ub, ffn_bias=ub,
+                  sliding_window=int(d.get("sliding_window") or 0))
+    if mt == "stablelm":
+        kw.update(norm_type="layernorm", norm_bias=True, qkv_bias=bool(d.get("use_qkv_bias", False)),
+                  parallel_residual=bool(d.get("use_parallel_residual", False)),
+                  shared_parallel_norm=bool(d.get("use_parallel_residual", False)))
+    if mt == "cohere":
+        kw.update(norm_type="layernorm", parallel_residual=True, shared_parallel_norm=True, rope_style=1,
+                  logits_scale=float(d.get("logit_scale", 1.0)), tie_embeddings=bool(d.get("tie_word_embeddings", True)))
+    if mt == "nemotron":
+        kw.update(norm_type="layernorm", norm_bias=True, norm_plus_one=True, gated_ffn=False,
+                  qkv_bias=bool(d.get("attention_bias", False)), o_bias=bool(d.get("attention_bias", False)),
+                  ffn_bias=bool(d.get("mlp_bias", False)))
+    if mt == "gpt_neox":
+        ab = bool(d.get("attention_bias", True))
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=ab, o_bias=ab, ffn_bias=True,
+                  parallel_residual=bool(d.get("use_parallel_residual", True)), num_kv_heads=heads)
+        if d.get("rotary_pct") and float(d["rotary_pct"]) < 1.0 and not kw.get("rope_dim"):
+            kw["rope_dim"] = int(head_dim * float(d["rotary_pct"]))
     if mt == "granite":
         kw.update(residual_multiplier=float(d.get("residual_multiplier", 1.0)),
                   embedding_multiplier=float(d.get("embedding_multiplier", 1.0)),
@@ -270,11 +301,11 @@ def from_hf_config(d: dict) -> TransformerConfig:
                               expert_ffn=d.get("moe_intermediate_size", 0),
                               num_shared_experts=d.get("n_shared_experts", 0) or 0,
                               shared_ffn=d.get("moe_intermediate_size", 0),
-                              scoring=d.get("scoring_func", "softmax"),
+                              scoring=d.get("scoring_func") or ("sigmoid" if mt == "deepseek_v3" else "softmax"),
                               norm_topk_prob=bool(d.get("norm_topk_prob", False)),
                               routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                               n_group=d.get("n_group", 1) or 1, topk_group=d.get("topk_group", 1) or 1,
-                              use_correction_bias=d.get("topk_method", "") == "noaux_tc",
+                              use_correction_bias=(d.get("topk_method") or ("noaux_tc" if mt == "deepseek_v3" else "")) == "noaux_tc",
                               first_dense_layers=d.get("first_k_dense_replace", 0))
     if mt in ("olmoe", "qwen2_moe", "qwen3_moe", "mixtral", "granitemoe"):
         kw["moe"] = MoeConfig(num_experts=d.get("num_experts", d.get("num_local_experts", 0)),
@@ -290,7 +321,8 @@ def from_hf_config(d: dict) -> TransformerConfig:
 _GGUF_ARCH_ALIASES = {"qwen2": "qwen2", "qwen3": "qwen3", "llama": "llama", "gemma": "gemma", "gemma2": "gemma2",
                       "gemma3": "gemma3", "phi3": "phi3", "granite": "granite", "deepseek2": "deepseek3",
                       "olmoe": "olmoe", "qwen2moe": "qwen2_moe", "mistral": "mistral", "glm4": "glm4",
-                      "stablelm": "stablelm", "olmo2": "olmo2", "internlm2": "internlm2", "minicpm": "minicpm"}
+                      "stablelm": "stablelm", "olmo2": "olmo2", "internlm2": "internlm2", "minicpm": "minicpm",
+                      "qwen3moe": "qwen3_moe", "starcoder2": "starcoder2", "gptneox": "gpt_neox", "nemotron": "nemotron"}
 
 
 def from_gguf_metadata(md: dict) -> TransformerConfig:
@@ -307,12 +339,13 @@ def from_gguf_metadata(md: dict) -> TransformerConfig:
         num_layers=int(g("block_count")), num_heads=heads,
         num_kv_heads=int(g("attention.head_count_kv", heads)), head_dim=head_dim,
         ffn_size=int(g("feed_forward_length", 4 * hidden)),
-        rms_eps=float(g("attention.layer_norm_rms_epsilon", 1e-5)),
+        rms_eps=float(g("attention.layer_norm_rms_epsilon", g("attention.layer_norm_epsilon", 1e-5))),
         rope_theta=float(g("rope.freq_base", 10000.0)), rope_dim=int(g("rope.dimension_count", 0) or 0),
         max_position=int(g("context_length", 8192)),
         # llama-family GGUF files store q/k permuted for interleaved-pair rotation
         rope_style=1 if arch in ("llama", "mistral", "granite", "deepseek2", "minicpm") else 0,
-        qkv_bias=arch in ("qwen2", "qwen2moe"), qk_norm=arch in ("qwen3", "qwen3moe", "olmo2", "gemma3"),
+        qkv_bias=bool(md.get("__has_qkv_bias__", arch in ("qwen2", "qwen2moe", "starcoder2", "gptneox"))),
+        qk_norm=arch in ("qwen3", "qwen3moe", "olmo2", "olmoe", "gemma3"),
         tie_embeddings=not bool(md.get("__has_output_weight__", False)),
         bos_token_id=int(md.get("tokenizer.ggml.bos_token_id", 1)),
         eos_token_ids=(int(md.get("tokenizer.ggml.eos_token_id", 2)),))
@@ -325,6 +358,29 @@ def from_gguf_metadata(md: dict) -> TransformerConfig:
                   logit_softcap=float(g("final_logit_softcapping", 0.0) or 0.0),
                   attn_softcap=float(g("attn_logit_softcapping", 0.0) or 0.0),
                   sliding_window=int(g("attention.sliding_window", 0) or 0), post_norms=arch != "gemma")
+    if arch in ("gemma2", "gemma3"):
+        kw["sliding_window_pattern"] = 2 if arch == "gemma2" else 6
+        if arch == "gemma3":
+            kw["rope_local_theta"] = float(g("rope.local_freq_base", 10000.0))
+    if g("attention.scale"):
+        kw["attn_scale"] = float(g("attention.scale"))
+    if arch == "granite":
+        kw.update(residual_multiplier=float(g("residual_scale", 1.0)), embedding_multiplier=float(g("embedding_scale", 1.0)),
+                  logits_scale=1.0 / float(g("logit_scale", 1.0) or 1.0))
+    if arch in ("olmo2", "olmoe"):
+        kw["qk_norm_full"] = True
+    if arch == "olmo2":
+        kw.update(pre_norm=False, post_norms=True)
+    if arch == "stablelm":
+        par = bool(g("use_parallel_residual", False))
+        kw.update(norm_type="layernorm", norm_bias=True, parallel_residual=par, shared_parallel_norm=par)
+    if arch == "starcoder2":
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, activation="gelu_tanh", o_bias=True, ffn_bias=True)
+    if arch == "gptneox":
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, activation="gelu", o_bias=True, ffn_bias=True,
+                  parallel_residual=bool(g("use_parallel_residual", True)))
+    if arch == "nemotron":
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, activation="relu2")
     if g("expert_count"):
         kw["moe"] = MoeConfig(num_experts=int(g("expert_count")), top_k=int(g("expert_used_count", 2)),
                               expert_ffn=int(g("expert_feed_forward_length", kw["ffn_size"])),
@@ -335,8 +391,11 @@ def from_gguf_metadata(md: dict) -> TransformerConfig:
                               routed_scaling_factor=float(g("expert_weights_scale", 1.0) or 1.0),
                               n_group=int(g("expert_group_count", 1) or 1),
                               topk_group=int(g("expert_group_used_count", 1) or 1),
+                              use_correction_bias=bool(md.get("__has_expert_bias__", False)),
+                              shared_gate=arch == "qwen2moe",
                               first_dense_layers=int(g("leading_dense_block_count", 0) or 0))
     if g("attention.kv_lora_rank"):
+        kw["head_dim"] = int(g("attention.key_length", 192))
         kw["mla"] = MlaConfig(q_lora_rank=int(g("attention.q_lora_rank", 0) or 0),
                               kv_lora_rank=int(g("attention.kv_lora_rank")),
                               qk_rope_head_dim=int(g("rope.dimension_count", 64)),

@@ -38,9 +38,24 @@ _GGUF_LAYER = {
     "ffn_down.weight": "mlp.down_proj.weight",
     "post_attention_norm.weight": "post_attention_layernorm.weight",
     "post_ffw_norm.weight": "post_feedforward_layernorm.weight",
+    # LayerNorm / linear biases (StableLM, StarCoder 2, GPT-NeoX)
+    "attn_norm.bias": "input_layernorm.bias", "ffn_norm.bias": "post_attention_layernorm.bias",
+    "attn_output.bias": "self_attn.o_proj.bias", "ffn_up.bias": "mlp.up_proj.bias", "ffn_down.bias": "mlp.down_proj.bias",
+    "ffn_gate.bias": "mlp.gate_proj.bias",
+    # fused projections (Phi-3, GPT-NeoX): sliced by ``standard_names``
+    "attn_qkv.weight": "self_attn.qkv_proj.weight", "attn_qkv.bias": "self_attn.qkv_proj.bias",
+    # mixture of experts: stacked [experts, out, in] tensors
+    "ffn_gate_inp.weight": "mlp.gate.weight", "exp_probs_b.bias": "mlp.gate.e_score_correction_bias",
+    "ffn_down_exps.weight": "mlp.experts.down_proj",
+    "ffn_gate_shexp.weight": "mlp.shared_experts.gate_proj.weight", "ffn_up_shexp.weight": "mlp.shared_experts.up_proj.weight",
+    "ffn_down_shexp.weight": "mlp.shared_experts.down_proj.weight", "ffn_gate_inp_shexp.weight": "mlp.shared_expert_gate.weight",
+    # multi-head latent attention
+    "attn_q_a.weight": "self_attn.q_a_proj.weight", "attn_q_a_norm.weight": "self_attn.q_a_layernorm.weight",
+    "attn_q_b.weight": "self_attn.q_b_proj.weight", "attn_kv_a_mqa.weight": "self_attn.kv_a_proj_with_mqa.weight",
+    "attn_kv_a_norm.weight": "self_attn.kv_a_layernorm.weight", "attn_kv_b.weight": "self_attn.kv_b_proj.weight",
 }
 _GGUF_TOP = {"token_embd.weight": "model.embed_tokens.weight", "output_norm.weight": "model.norm.weight",
-             "output.weight": "lm_head.weight"}
+             "output_norm.bias": "model.norm.bias", "output.weight": "lm_head.weight"}
 
 
 def gguf_name_to_hf(name: str) -> Optional[str]:
@@ -98,6 +113,71 @@ def _want_fp8(fp8: Optional[bool], device) -> bool:
     return bool(config.get("fp8_linears")) and torch.device(device).type == "cuda"
 
 
+def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> Callable[[str], Optional[torch.Tensor]]:
+    """Present an architecture's own tensor names and fused tensors under the llama-style names the
+    decoder loads (``model.layers.N.self_attn.q_proj.weight`` ...): Phi-3 / GLM fused projections are
+    sliced, GLM-4 / StarCoder 2 / GPT-NeoX names are translated, GPT-NeoX's per-head interleaved
+    query_key_value is regrouped."""
+    mt = raw.get("model_type", "llama")
+    heads = raw.get("num_attention_heads", 1)
+    hidden = raw.get("hidden_size", 0)
+    d = raw.get("head_dim") or (hidden // heads if heads else 0)
+    kvh = raw.get("num_key_value_heads") or heads
+
+    def fused_rows(name: str, fused: str, part: str, sizes: dict[str, tuple[int, int]]):
+        t = get(name.replace(part, fused))
+        if t is None:
+            return None
+        a, b = sizes[part]
+        return t[a:b]
+
+    if mt == "phi3" or mt in ("glm", "glm4"):
+        qs, ks = heads * d, kvh * d
+        qkv = {"q_proj": (0, qs), "k_proj": (qs, qs + ks), "v_proj": (qs + ks, qs + 2 * ks)}
+        ffn = raw.get("intermediate_size", 0)
+        gu = {"gate_proj": (0, ffn), "up_proj": (ffn, 2 * ffn)}
+        glm4 = {"post_attention_layernorm": "post_self_attn_layernorm", "pre_feedforward_layernorm": "post_attention_layernorm",
+                "post_feedforward_layernorm": "post_mlp_layernorm"}
+
+        def g(name: str):
+            if mt == "glm4":
+                for std, own in glm4.items():
+                    if "." + std + "." in name:
+                        return get(name.replace(std, own))
+            t = get(name)
+            if t is not None:
+                return t
+            for part in qkv:
+                if "self_attn." + part + "." in name:
+                    return fused_rows(name, "qkv_proj", part, qkv)
+            for part in gu:
+                if "mlp." + part + "." in name:
+                    return fused_rows(name, "gate_up_proj", part, gu)
+            return None
+        return g
+    if mt == "starcoder2":
+        return lambda name: get(name.replace("mlp.up_proj", "mlp.c_fc").replace("mlp.down_proj", "mlp.c_proj"))
+    if mt == "gpt_neox":
+        ren = (("model.embed_tokens", "gpt_neox.embed_in"), ("model.norm", "gpt_neox.final_layer_norm"),
+               ("lm_head", "embed_out"), ("model.layers", "gpt_neox.layers"), ("self_attn.o_proj", "attention.dense"),
+               ("mlp.up_proj", "mlp.dense_h_to_4h"), ("mlp.down_proj", "mlp.dense_4h_to_h"))
+
+        def g(name: str):
+            for i, part in enumerate(("q_proj", "k_proj", "v_proj")):
+                if "self_attn." + part + "." in name:
+                    own = name.replace("model.layers", "gpt_neox.layers").replace("self_attn." + part, "attention.query_key_value")
+                    t = get(own)
+                    if t is None:
+                        return None
+                    # rows are [head][q | k | v][d]
+                    return t.reshape(heads, 3, d, *t.shape[1:])[:, i].reshape(heads * d, *t.shape[1:])
+            for std, own in ren:
+                name = name.replace(std, own)
+            return get(name)
+        return g
+    return get
+
+
 def _llava_names(ck) -> tuple[Callable, Callable]:
     """Two checkpoint layouts exist for LLaVA: ``language_model.model.* / language_model.lm_head /
     vision_tower.* / multi_modal_projector.*`` and the later ``model.language_model.* /
@@ -134,7 +214,7 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
     else:
         cfg = from_hf_config(raw)
         model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
-        model.load_state_dict(ck.get)
+        model.load_state_dict(standard_names(ck.get, raw))
     tok: Tokenizer
     if (p / "tokenizer.json").exists():
         tok = Tokenizer.from_hf_json(p / "tokenizer.json")
@@ -161,7 +241,7 @@ def _load_gguf(p: Path, device, comm, fp8) -> LoadedLLM:
         hf = gguf_name_to_hf(name)
         if hf:
             hf_to_gguf[hf] = name
-    if cfg.post_norms:   # Gemma 2/3: ffn_norm is the pre-FFN norm
+    if cfg.post_norms:   # Gemma 2/3 (and OLMo 2, which has no ffn_norm): ffn_norm is the pre-FFN norm
         for i in range(cfg.num_layers):
             a = f"model.layers.{i}.post_attention_layernorm.weight"
             g = f"blk.{i}.ffn_norm.weight"
@@ -171,9 +251,29 @@ def _load_gguf(p: Path, device, comm, fp8) -> LoadedLLM:
             if g2 in f:
                 hf_to_gguf[a] = g2
 
-    def get(name: str) -> Optional[torch.Tensor]:
+    def get_plain(name: str) -> Optional[torch.Tensor]:
         g = hf_to_gguf.get(name)
-        return None if g is None else f.get(g, torch.bfloat16)
+        if g is not None:
+            return f.get(g, torch.bfloat16)
+        if name.endswith("mlp.experts.gate_up_proj"):          # gate and up expert stacks side by side
+            blk = "blk." + name.split(".")[2]
+            if blk + ".ffn_gate_exps.weight" in f:
+                return torch.cat([f.get(blk + ".ffn_gate_exps.weight", torch.bfloat16),
+                                  f.get(blk + ".ffn_up_exps.weight", torch.bfloat16)], 1)
+        return None
+
+    arch = f.metadata.get("general.architecture", "llama")
+    fused = {"phi3": "phi3", "gptneox": "phi3"}.get(arch)
+    if fused:
+        # both keep q|k|v (and Phi-3 gate|up in ffn_up) as one tensor: present them under the split names
+        raw = {"model_type": "phi3", "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_kv_heads,
+               "hidden_size": cfg.hidden_size, "head_dim": cfg.head_dim, "intermediate_size": cfg.ffn_size}
+        if arch == "phi3":
+            for i in range(cfg.num_layers):
+                hf_to_gguf[f"model.layers.{i}.mlp.gate_up_proj.weight"] = hf_to_gguf.pop(f"model.layers.{i}.mlp.up_proj.weight")
+        get = standard_names(get_plain, raw)
+    else:
+        get = get_plain
 
     from ... import config as _config
     resident = bool(_config.get("gguf_resident")) and (comm is None or comm.world == 1)

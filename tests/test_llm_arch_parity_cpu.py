@@ -31,6 +31,19 @@ ARCHS = {
     "qwen3_moe": ("Qwen3MoeConfig", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, head_dim=32,
                                          decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True)),
     "olmoe": ("OlmoeConfig", dict(num_experts=4, num_experts_per_tok=2)),
+    "phi3": ("Phi3Config", dict(pad_token_id=0)),
+    "glm": ("GlmConfig", dict(head_dim=32, pad_token_id=0)),
+    "glm4": ("Glm4Config", dict(head_dim=32, pad_token_id=0)),
+    "starcoder2": ("Starcoder2Config", dict()),
+    "stablelm": ("StableLmConfig", dict()),
+    "stablelm_parallel": ("StableLmConfig", dict(use_parallel_residual=True, use_qkv_bias=True)),
+    "cohere": ("CohereConfig", dict()),
+    "nemotron": ("NemotronConfig", dict()),
+    "gpt_neox": ("GPTNeoXConfig", dict()),
+    "deepseek_v3": ("DeepseekV3Config", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
+                                             q_lora_rank=64, kv_lora_rank=512, qk_nope_head_dim=32, qk_rope_head_dim=64,
+                                             v_head_dim=32, n_group=2, topk_group=1, first_k_dense_replace=1,
+                                             n_shared_experts=1, num_key_value_heads=4)),
 }
 
 
@@ -73,3 +86,65 @@ def test_arch_matches_transformers(name, tmp_path):
     assert cos > 0.995, f"{name}: cos {cos:.4f}"
     agree = (mine.argmax(-1) == ref.argmax(-1)).float().mean()
     assert agree >= 0.85, f"{name}: argmax agreement {agree:.2f}"
+
+
+GGUF_ARCHS = ["llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3_text", "granite", "olmo2", "phi3",
+              "stablelm", "stablelm_parallel", "starcoder2", "gpt_neox", "mixtral", "qwen2_moe", "qwen3_moe", "olmoe",
+              "deepseek_v3"]
+
+
+@pytest.mark.parametrize("name", GGUF_ARCHS)
+def test_converted_gguf_matches_the_hf_directory(name, tmp_path):
+    """HF directory -> GGUF (llama.cpp names, permuted q/k, stacked experts, baked Gemma norms) ->
+    loaded again: same logits as the directory it came from."""
+    from hartsyinference_b200.assets.converters import hf_to_gguf
+    cls, extra = ARCHS[name]
+    cfg = getattr(tr, cls)(**{**_BASE, **extra})
+    torch.manual_seed(0)
+    hf = tr.AutoModelForCausalLM.from_config(cfg)
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.mul_(3.0)
+            else:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = tmp_path / name
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()}, d)
+    md = hf_to_gguf(d, tmp_path / f"{name}.gguf")
+    assert md["general.architecture"]
+    a, b = load_llm(d, "cpu"), load_llm(tmp_path / f"{name}.gguf", "cpu")
+    ids = torch.randint(0, 320, (19,), generator=torch.Generator().manual_seed(2)).tolist()
+    la, lb = _logits(a, ids), _logits(b, ids)
+    cos = torch.nn.functional.cosine_similarity(la.flatten(), lb.flatten(), dim=0)
+    assert cos > 0.999, f"{name}: cos {cos:.4f}"
+    assert (la.argmax(-1) == lb.argmax(-1)).float().mean() >= 0.9
+
+
+def test_convert_verb_writes_a_quantised_gguf_with_its_tokenizer(tmp_path):
+    import json
+    from click.testing import CliRunner
+    from hartsyinference_b200.assets.gguf import GgufFile
+    from hartsyinference_b200.cli.main import cli
+    cfg = tr.Qwen2Config(**_BASE)
+    torch.manual_seed(0)
+    hf = tr.AutoModelForCausalLM.from_config(cfg)
+    d = tmp_path / "q"
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()}, d)
+    from hartsyinference_b200.assets.tokenizer import _bytes_to_unicode
+    b2u = _bytes_to_unicode()
+    vocab = {b2u[b]: b for b in range(256)}
+    vocab[b2u[ord("h")] + b2u[ord("i")]] = 256
+    (d / "tokenizer.json").write_text(json.dumps({
+        "model": {"type": "BPE", "vocab": vocab, "merges": [f"{b2u[ord('h')]} {b2u[ord('i')]}"]},
+        "added_tokens": [{"id": 300, "content": "<|end|>", "special": True}]}))
+    (d / "tokenizer_config.json").write_text(json.dumps({"chat_template": "{{ messages[0]['content'] }}"}))
+    r = CliRunner().invoke(cli, ["convert", str(d), str(tmp_path / "q.gguf"), "--quant", "Q8_0"])
+    assert r.exit_code == 0, r.output
+    f = GgufFile(tmp_path / "q.gguf")
+    assert f.info("blk.0.attn_q.weight")[0] == 8 and f.info("blk.0.attn_norm.weight")[0] == 0     # Q8_0 / F32
+    assert f.metadata["tokenizer.chat_template"].startswith("{{") and f.metadata["tokenizer.ggml.tokens"][300] == "<|end|>"
+    a, b = load_llm(d, "cpu"), load_llm(tmp_path / "q.gguf", "cpu")
+    assert b.tokenizer.encode("hi", add_special=False) == a.tokenizer.encode("hi", add_special=False) == [256]
+    ids = list(range(5, 20))
+    cos = torch.nn.functional.cosine_similarity(_logits(a, ids).flatten(), _logits(b, ids).flatten(), dim=0)
+    assert cos > 0.99
