@@ -476,9 +476,9 @@ __global__ void rope_kv_kernel(const RopeParams p) {
         pair_idx = c >> 1;
         partner = c ^ 1;
       }
-      // partner slot may differ from i (split-half with half % 32 != 0 is not supported when
-      // half < 32; d = 64/128/256 with rot = d or rot = d/2 all satisfy half % 32 == 0 or the
-      // interleaved style keeps the partner in the same slot)
+      // the partner may sit in another lane and another register slot (partial rotary with
+      // rot / 2 < 32 keeps it in slot 0 of lane c +- rot/2): fetch every slot from the partner's
+      // lane and keep the one that holds it
       float pv = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -751,7 +751,6 @@ B200_API int b200_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_c
                           float theta, float eps, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (d > 256 || rot > d || (rot & 1)) return -2;
-  if (style == 0 && rot > 0 && ((rot / 2) % 32) != 0) return -3;
   RopeParams p{};
   p.qkv = static_cast<const __nv_bfloat16*>(qkv);
   p.q_out = static_cast<__nv_bfloat16*>(q_out);

@@ -49,3 +49,54 @@ def test_llava_prefill_with_image_rows_on_device():
         outs[dev] = (embeds.float().cpu(), eng.requests[rid].output)
     assert torch.nn.functional.cosine_similarity(outs["cpu"][0].flatten(), outs["cuda"][0].flatten(), dim=0) > 0.99
     assert len(outs["cuda"][1]) == 1
+
+
+_GPU_BASE = dict(vocab_size=320, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                 num_key_value_heads=2, max_position_embeddings=256)
+_GPU_ARCHS = {
+    "olmo2": ("Olmo2Config", {}),
+    "gemma3_text": ("Gemma3TextConfig", dict(head_dim=64, sliding_window=8, query_pre_attn_scalar=64)),
+    "glm4": ("Glm4Config", dict(head_dim=64, pad_token_id=0)),
+    "starcoder2": ("Starcoder2Config", {}),
+    "stablelm": ("StableLmConfig", dict(use_parallel_residual=True, use_qkv_bias=True)),
+    "cohere": ("CohereConfig", {}),
+    "nemotron": ("NemotronConfig", {}),
+    "gpt_neox": ("GPTNeoXConfig", {}),
+    "phi3": ("Phi3Config", dict(pad_token_id=0)),
+    "olmoe": ("OlmoeConfig", dict(num_experts=4, num_experts_per_tok=2)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(_GPU_ARCHS))
+def test_architecture_on_device_matches_cpu(name, tmp_path):
+    """The block structures outside the fused decode path (LayerNorm with bias, parallel residual,
+    post-block norms, q/k norm over all heads, partial rotary, non-gated FFNs) on the device kernels."""
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.llm.loader import load_llm, save_hf_checkpoint
+    from hartsyinference_b200.models.llm.transformer import ForwardBatch
+    cls, extra = _GPU_ARCHS[name]
+    cfg = getattr(tr, cls)(**{**_GPU_BASE, **extra})
+    torch.manual_seed(0)
+    hf = tr.AutoModelForCausalLM.from_config(cfg)
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.mul_(3.0)
+            else:
+                p.add_(torch.randn_like(p) * 0.1)
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()}, tmp_path / name)
+    ids = torch.randint(0, 320, (37,), generator=torch.Generator().manual_seed(1)).tolist()
+    outs = []
+    for dev in ("cpu", "cuda"):
+        m = load_llm(tmp_path / name, dev, fp8=False).model
+        n = len(ids)
+        pages = (n + 15) // 16 + 1
+        m.alloc_kv(pages, 16)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        b = ForwardBatch(tokens=i32(ids), positions=i32(list(range(n))),
+                         slot_mapping=torch.arange(n, dtype=torch.int64 if dev == "cuda" else torch.int32, device=dev),
+                         block_table=i32(list(range(pages)))[None], kv_lens=i32([n]), is_decode=False,
+                         cu_q=i32([0, n]), max_q_len=n, max_kv_len=n)
+        outs.append(m.logits(m.forward_hidden(b)).float().cpu())
+    cos = torch.nn.functional.cosine_similarity(outs[0].flatten(), outs[1].flatten(), dim=0)
+    assert cos > 0.99, f"{name}: cos {cos:.4f}"
