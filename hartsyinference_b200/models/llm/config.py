@@ -93,6 +93,9 @@ class TransformerConfig:
     norm_bias: bool = False
     parallel_residual: bool = False     # x + attn(n1(x)) + ffn(n2(x)) (GPT-NeoX, Cohere)
     shared_parallel_norm: bool = False  # the parallel branches share one norm (Cohere)
+    use_rope: bool = True               # False: learned absolute positions instead (GPT-2)
+    learned_positions: bool = False
+    nope_global: bool = False           # full-attention layers carry no rotary embedding (Cohere 2)
     moe: Optional[MoeConfig] = None
     mla: Optional[MlaConfig] = None
     bos_token_id: int = 1
@@ -118,6 +121,7 @@ class TransformerConfig:
         """Architectures whose block structure is outside the fused decode path: they run the same
         kernels through an unfused layer loop."""
         return (not self.pre_norm or self.qk_norm_full or self.norm_type != "rms" or self.parallel_residual
+                or not self.use_rope or self.nope_global
                 or self.o_bias or self.ffn_bias or not self.gated_ffn or self.activation not in ("silu", "gelu_tanh"))
 
     def layer_window(self, layer: int) -> int:
@@ -201,9 +205,13 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / nemotron / gpt_neox / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
+    if mt == "gpt2":          # GPT-2 names its sizes differently
+        d = {**d, "hidden_size": d["n_embd"], "num_hidden_layers": d["n_layer"], "num_attention_heads": d["n_head"],
+             "max_position_embeddings": d.get("n_positions", 1024), "intermediate_size": d.get("n_inner") or 4 * d["n_embd"],
+             "hidden_act": d.get("activation_function", "gelu_new"), "tie_word_embeddings": d.get("tie_word_embeddings", True)}
     heads = d["num_attention_heads"]
     hidden = d["hidden_size"]
     head_dim = d.get("head_dim") or hidden // heads
@@ -270,7 +278,13 @@ def from_hf_config(d: dict) -> TransformerConfig:
         kw.update(norm_type="layernorm", norm_bias=True, qkv_bias=bool(d.get("use_qkv_bias", False)),
                   parallel_residual=bool(d.get("use_parallel_residual", False)),
                   shared_parallel_norm=bool(d.get("use_parallel_residual", False)))
-    if mt == "cohere":
+    if mt == "gpt2":
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=True, o_bias=True, ffn_bias=True,
+                  use_rope=False, learned_positions=True, num_kv_heads=heads)
+    if mt == "cohere2":
+        kw.update(sliding_window=int(d.get("sliding_window") or 0), layer_types=tuple(d.get("layer_types") or ()),
+                  sliding_window_pattern=int(d.get("sliding_window_pattern") or 4), nope_global=True)
+    if mt in ("cohere", "cohere2"):
         kw.update(norm_type="layernorm", parallel_residual=True, shared_parallel_norm=True, rope_style=1,
                   logits_scale=float(d.get("logit_scale", 1.0)), tie_embeddings=bool(d.get("tie_word_embeddings", True)))
     if mt == "nemotron":
@@ -283,6 +297,12 @@ def from_hf_config(d: dict) -> TransformerConfig:
                   parallel_residual=bool(d.get("use_parallel_residual", True)), num_kv_heads=heads)
         if d.get("rotary_pct") and float(d["rotary_pct"]) < 1.0 and not kw.get("rope_dim"):
             kw["rope_dim"] = int(head_dim * float(d["rotary_pct"]))
+    if mt == "minicpm":
+        # muP-style scaling: embeddings * scale_emb, each block's output * scale_depth / sqrt(layers),
+        # logits / (hidden / dim_model_base)
+        kw.update(embedding_multiplier=float(d.get("scale_emb", 1.0)),
+                  residual_multiplier=float(d.get("scale_depth", 1.0)) / (d["num_hidden_layers"] ** 0.5),
+                  logits_scale=float(d.get("dim_model_base", hidden)) / hidden)
     if mt == "granite":
         kw.update(residual_multiplier=float(d.get("residual_multiplier", 1.0)),
                   embedding_multiplier=float(d.get("embedding_multiplier", 1.0)),

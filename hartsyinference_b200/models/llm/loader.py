@@ -155,6 +155,49 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
                     return fused_rows(name, "gate_up_proj", part, gu)
             return None
         return g
+    if mt == "gpt2":
+        h = raw.get("n_embd", hidden)
+        ren = (("model.embed_tokens", "transformer.wte"), ("model.embed_positions", "transformer.wpe"),
+               ("model.norm", "transformer.ln_f"), ("model.layers", "transformer.h"), ("input_layernorm", "ln_1"),
+               ("post_attention_layernorm", "ln_2"), ("self_attn.o_proj", "attn.c_proj"), ("mlp.up_proj", "mlp.c_fc"),
+               ("mlp.down_proj", "mlp.c_proj"))
+
+        def g(name: str):
+            for i, part in enumerate(("q_proj", "k_proj", "v_proj")):
+                if "self_attn." + part + "." in name:
+                    t = get(name.replace("model.layers", "transformer.h").replace("self_attn." + part, "attn.c_attn"))
+                    if t is None:
+                        return None
+                    t = t.t() if t.dim() == 2 else t          # Conv1D keeps [in, out]
+                    return t[i * h:(i + 1) * h].contiguous()
+            own = name
+            for std, o in ren:
+                own = own.replace(std, o)
+            t = get(own)
+            if t is not None and t.dim() == 2 and (".attn.c_proj." in own or ".mlp.c_" in own):
+                t = t.t().contiguous()
+            return t
+        return g
+    if mt == "internlm2":
+        groups = heads // kvh
+        ren = (("model.embed_tokens", "model.tok_embeddings"), ("lm_head", "output"), ("input_layernorm", "attention_norm"),
+               ("post_attention_layernorm", "ffn_norm"), ("self_attn.o_proj", "attention.wo"),
+               ("mlp.gate_proj", "feed_forward.w1"), ("mlp.up_proj", "feed_forward.w3"), ("mlp.down_proj", "feed_forward.w2"))
+
+        def g(name: str):
+            for part in ("q_proj", "k_proj", "v_proj"):
+                if "self_attn." + part + "." in name:
+                    t = get(name.replace("self_attn." + part, "attention.wqkv"))
+                    if t is None:
+                        return None
+                    # rows are [kv head][its q heads..., k, v][d]
+                    t = t.reshape(kvh, groups + 2, d, *t.shape[1:])
+                    sel = t[:, :groups] if part == "q_proj" else t[:, groups + (0 if part == "k_proj" else 1)][:, None]
+                    return sel.reshape(-1, *t.shape[3:]).contiguous()
+            for std, own in ren:
+                name = name.replace(std, own)
+            return get(name)
+        return g
     if mt == "starcoder2":
         return lambda name: get(name.replace("mlp.up_proj", "mlp.c_fc").replace("mlp.down_proj", "mlp.c_proj"))
     if mt == "gpt_neox":

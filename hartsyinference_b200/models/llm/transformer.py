@@ -121,6 +121,7 @@ class DecoderModel:
         self.inv_freq_local = (build_inv_freq(rot, cfg.rope_local_theta, RopeScaling(), self.device)[0]
                                if cfg.rope_local_theta > 0 else None)
         self.final_norm_b: Optional[torch.Tensor] = None
+        self.pos_embed: Optional[torch.Tensor] = None      # learned absolute positions (GPT-2)
         self.kv_cache: Optional[torch.Tensor] = None
         self.all_reduce: Callable[[torch.Tensor], torch.Tensor] = self.comm.all_reduce
         # hook for the fused GEMM + all-reduce path: (x, weight, residual) -> reduced output
@@ -170,6 +171,8 @@ class DecoderModel:
         self.final_norm = need("model.norm.weight").to(dt).to(self.device)
         dev = lambda t_: None if t_ is None else t_.to(dt).to(self.device)
         self.final_norm_b = dev(get("model.norm.bias")) if cfg.norm_bias else None
+        if cfg.learned_positions:
+            self.pos_embed = dev(need("model.embed_positions.weight"))
         if cfg.qk_norm_full and tp > 1:
             raise ValueError("q/k normalisation over the whole projection is not sharded; load this model with tp=1")
         kvs = self.kv_head_slice()
@@ -467,8 +470,9 @@ class DecoderModel:
         kc, vc = (self.kv_cache[li, 0], self.kv_cache[li, 1]) if self.kv_cache is not None else (None, None)
         window = cfg.layer_window(self.layer0 + li)
         inv_freq = self.inv_freq_local if (window > 0 and self.inv_freq_local is not None) else self.inv_freq
+        rot = cfg.rotary_dim if cfg.use_rope and not (cfg.nope_global and window == 0) else 0
         q, _, _ = ops.rope_kv(qkv, batch.positions, self.hq, self.hkv, d, k_cache=kc, v_cache=vc,
-                              slot_mapping=batch.slot_mapping, rot=cfg.rotary_dim, theta=cfg.rope_theta,
+                              slot_mapping=batch.slot_mapping, rot=rot, theta=cfg.rope_theta,
                               inv_freq=inv_freq, style=cfg.rope_style, q_norm_w=q_norm_w,
                               k_norm_w=k_norm_w, eps=cfg.rms_eps)
         if batch.is_decode:
@@ -563,6 +567,8 @@ class DecoderModel:
             x = batch.embeds
         else:
             x = ops.embedding(batch.tokens, self.embed, cfg.embed_scale * cfg.embedding_multiplier)
+        if self.pos_embed is not None and hidden_in is None:
+            x = (x.float() + self.pos_embed[batch.positions.long()].float()).to(x.dtype)
         scale = self._attn_scale()
         fp8 = self.fp8 and x.is_cuda
         if cfg.general_path:

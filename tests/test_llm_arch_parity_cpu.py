@@ -38,6 +38,8 @@ ARCHS = {
     "stablelm": ("StableLmConfig", dict()),
     "stablelm_parallel": ("StableLmConfig", dict(use_parallel_residual=True, use_qkv_bias=True)),
     "cohere": ("CohereConfig", dict()),
+    "cohere2": ("Cohere2Config", dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
+    "gpt2": ("GPT2Config", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256)),
     "nemotron": ("NemotronConfig", dict()),
     "gpt_neox": ("GPTNeoXConfig", dict()),
     "deepseek_v3": ("DeepseekV3Config", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
@@ -148,3 +150,44 @@ def test_convert_verb_writes_a_quantised_gguf_with_its_tokenizer(tmp_path):
     ids = list(range(5, 20))
     cos = torch.nn.functional.cosine_similarity(_logits(a, ids).flatten(), _logits(b, ids).flatten(), dim=0)
     assert cos > 0.99
+
+
+def test_internlm2_and_minicpm_map_onto_the_llama_block(tmp_path):
+    """No transformers class exists for these two: InternLM 2 is checked by regrouping a llama
+    checkpoint into its fused per-kv-group layout, MiniCPM by its scaling rules against Granite's."""
+    from hartsyinference_b200.models.llm.config import from_hf_config
+    cfg = tr.LlamaConfig(**_BASE)
+    torch.manual_seed(0)
+    hf = tr.AutoModelForCausalLM.from_config(cfg)
+    sd = {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()}
+    save_hf_checkpoint(cfg.to_dict(), sd, tmp_path / "llama")
+    heads, kvh, d = 4, 2, 32
+    ren = {"model.embed_tokens.weight": "model.tok_embeddings.weight", "lm_head.weight": "output.weight",
+           "model.norm.weight": "model.norm.weight"}
+    out = {ren[k]: v for k, v in sd.items() if k in ren}
+    for i in range(2):
+        p = f"model.layers.{i}."
+        q = sd[p + "self_attn.q_proj.weight"].reshape(kvh, heads // kvh, d, -1)
+        k = sd[p + "self_attn.k_proj.weight"].reshape(kvh, 1, d, -1)
+        v = sd[p + "self_attn.v_proj.weight"].reshape(kvh, 1, d, -1)
+        out[p + "attention.wqkv.weight"] = torch.cat([q, k, v], 1).reshape(-1, q.shape[-1]).contiguous()
+        out[p + "attention.wo.weight"] = sd[p + "self_attn.o_proj.weight"]
+        out[p + "feed_forward.w1.weight"] = sd[p + "mlp.gate_proj.weight"]
+        out[p + "feed_forward.w3.weight"] = sd[p + "mlp.up_proj.weight"]
+        out[p + "feed_forward.w2.weight"] = sd[p + "mlp.down_proj.weight"]
+        out[p + "attention_norm.weight"] = sd[p + "input_layernorm.weight"]
+        out[p + "ffn_norm.weight"] = sd[p + "post_attention_layernorm.weight"]
+    save_hf_checkpoint({**cfg.to_dict(), "model_type": "internlm2"}, out, tmp_path / "internlm2")
+    ids = list(range(3, 24))
+    a, b = _logits(load_llm(tmp_path / "llama", "cpu"), ids), _logits(load_llm(tmp_path / "internlm2", "cpu"), ids)
+    assert torch.equal(a, b)
+
+    mc = from_hf_config({**cfg.to_dict(), "model_type": "minicpm", "scale_emb": 12.0, "scale_depth": 1.4, "dim_model_base": 32})
+    assert mc.embedding_multiplier == 12.0 and abs(mc.residual_multiplier - 1.4 / 2 ** 0.5) < 1e-9 and mc.logits_scale == 0.25
+    save_hf_checkpoint({**cfg.to_dict(), "model_type": "minicpm", "scale_emb": 12.0, "scale_depth": 1.4, "dim_model_base": 32},
+                       sd, tmp_path / "minicpm")
+    save_hf_checkpoint({**cfg.to_dict(), "model_type": "granite", "embedding_multiplier": 12.0,
+                        "residual_multiplier": 1.4 / 2 ** 0.5, "logits_scaling": 4.0, "attention_multiplier": d ** -0.5},
+                       sd, tmp_path / "granite")
+    c, e = _logits(load_llm(tmp_path / "minicpm", "cpu"), ids), _logits(load_llm(tmp_path / "granite", "cpu"), ids)
+    assert torch.allclose(c, e, atol=1e-3)
