@@ -240,9 +240,11 @@ def _llava_names(ck) -> tuple[Callable, Callable]:
 
 
 def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
+    from ...assets.lowbit import dequantizing_get
     raw = json.loads((p / "config.json").read_text())
     ck = ShardedCheckpoint(p)
     vlm = None
+    ck_get = dequantizing_get(ck.get)          # fp8 block-scaled / NVFP4 / MXFP4 / NF4 linears read as bf16
     if "vision_config" in raw and "text_config" in raw:
         from ..encoders.clip_vision import clip_vision_from_hf
         from ..vlm.llava import LlavaModel
@@ -257,7 +259,7 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
     else:
         cfg = from_hf_config(raw)
         model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
-        model.load_state_dict(standard_names(ck.get, raw))
+        model.load_state_dict(standard_names(ck_get, raw))
     tok: Tokenizer
     if (p / "tokenizer.json").exists():
         tok = Tokenizer.from_hf_json(p / "tokenizer.json")
