@@ -95,6 +95,7 @@ declare("wait_budget_ms", int, 2000, "budget of every bounded device-side wait")
 declare("p2p_disable", bool, False, "never map peer memory; collectives fall back to NCCL")
 declare("fp8_linears", bool, True, "quantise eligible linears to 128x128 block-scaled e4m3 at load")
 declare("tc_attention", bool, True, "dense non-causal attention with head dim 128 on the tcgen05 kernel instead of the mma.sync one")
+declare("decode_attn_stages", int, 2, "depth of the paged decode attention kernel's K/V staging ring: 3 (two CTAs per SM at head dim 128) or 2 (three CTAs per SM)")
 declare("cluster_splitk", bool, False, "reduce the K splits of small GEMMs through distributed shared memory of a thread-block cluster instead of a second kernel")
 declare("pdl", bool, True, "launch GEMMs with programmatic dependent launch so that weight tiles are requested while the preceding kernel still runs")
 declare("fp8_scales", str, "ue8m0", "block-scale format of fp8 linears: ue8m0 (power-of-two scales applied by the tensor core) or fp32 (promoted per K block by the epilogue warps)")

@@ -219,12 +219,11 @@ __device__ __forceinline__ void warp_tile(WarpState<D>& st, const uint32_t (&qf)
 // ------------------------------------------------------------------------------------------
 // decode
 // ------------------------------------------------------------------------------------------
-template <int D>
+template <int D, int kStages>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_decode_kernel(const AttnParams p) {
   pdl_wait();
   pdl_trigger();
-  constexpr int kStages = 3;
   constexpr int kTileBytes = kTileTokens * D * 2;
   extern __shared__ __align__(128) uint8_t smem[];
   const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -272,14 +271,14 @@ attn_decode_kernel(const AttnParams p) {
   stage_pages(pg_ring, table, tile_begin + 1, tile_end, p.page_shift, kv_len);
   stage_pages(pg_ring, table, tile_begin + 2, tile_end, p.page_shift, kv_len);
   __syncthreads();
-  issue(tile_begin, 0);
-  issue(tile_begin + 1, 1);
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) issue(tile_begin + i, i);
   int stage = 0;
   for (int tile = tile_begin; tile < tile_end; ++tile) {
-    // page ids of tile + 3 are read by issue() in the next iteration, after two barriers
+    // page ids of tile + 3 are read by issue() in a later iteration, after two barriers
     stage_pages(pg_ring, table, tile + 3, tile_end, p.page_shift, kv_len);
-    issue(tile + 2, (stage + 2) % kStages);
-    cp_async_wait<2>();
+    issue(tile + kStages - 1, (stage + kStages - 1) % kStages);
+    cp_async_wait<kStages - 1>();
     __syncthreads();
     const uint32_t kb = smem_base + stage * 2 * kTileBytes;
     warp_tile<D, 1>(st, qf, kb, kb + kTileBytes, warp * 16, tile * kTileTokens, lim, start, p);
@@ -475,18 +474,32 @@ B200_API long long b200_attn_decode_workspace_bytes(int seqs, int hq, int d, int
   return splits > 1 ? static_cast<long long>(seqs) * hq * splits * (d + 2) * 4 : 0;
 }
 
-// Number of KV splits that fills the GPU for a decode batch.
+static int g_decode_stages = 2;
+
+// Number of KV splits for a decode batch, from a wave model fitted to B200 timings: the grid runs
+// in waves of (148 SMs x resident CTAs) and a CTA costs its tiles plus about four tiles' worth of
+// prologue and merge, so the estimate is waves x (ceil(tiles / splits) + 4); ties go to fewer
+// splits (less partial traffic and a cheaper combine). Measured with the two-tile ring, 64-token
+// tiles, 2304-token contexts (CTAs before splitting: best splits, time): 16: 12, 13.5 us;
+// 64: 6, 24.9 us; 128: 3, 40.4 us; 256: 3 or 1, 76-78 us; 512: 2, 132 us (8192 tokens: 4, 388 us;
+// 512 tokens: 1, 41 us); 1024: 1, 238 us.
 B200_API int b200_attn_decode_pick_splits(int seqs, int hkv, int max_kv_len) {
-  const int ctas = seqs * hkv;
+  const int ctas = seqs * hkv > 0 ? seqs * hkv : 1;
   const int tiles = (max_kv_len + kTileTokens - 1) / kTileTokens;
-  // Measured on B200 (64 sequences of 2304 tokens): one wave of about 256 CTAs (two per SM, not all
-  // SMs doubled) is the optimum; more splits only add partial writes and the combine pass.
-  //   kv heads 1: s=4 26 us (s=16: 36 us)   2: s=2 45 us (s=8: 59 us)   4: s=1 79 us   8: s=1 152 us
-  int splits = (256 + ctas / 2) / (ctas > 0 ? ctas : 1);
-  if (splits > 32) splits = 32;
-  if (splits > tiles) splits = tiles;
-  return splits < 1 ? 1 : splits;
+  const int slots = 148 * (g_decode_stages == 2 ? 3 : 2);
+  int best = 1;
+  long long best_cost = -1;
+  for (int sp = 1; sp <= 16 && sp <= tiles; ++sp) {
+    const long long waves = (static_cast<long long>(ctas) * sp + slots - 1) / slots;
+    const long long cost = waves * ((tiles + sp - 1) / sp + 4);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = sp; }
+  }
+  return best;
 }
+
+
+// Depth of the decode kernel's K/V staging ring: 3 (two CTAs per SM at head dim 128) or 2 (three).
+B200_API void b200_attn_set_decode_stages(int stages) { g_decode_stages = stages == 2 ? 2 : 3; }
 
 B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
                               const int* block_table, const int* kv_lens, int seqs, int hq, int hkv,
@@ -516,15 +529,19 @@ B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_
     p.ws_ml = p.ws_o + static_cast<long long>(seqs) * hq * p.splits * d;
   }
   dim3 grid(seqs, hkv, p.splits);
-  const int smem = 3 * 2 * kTileTokens * d * 2;
+  // staging ring depth: 3 tiles (two CTAs per SM at d = 128) or 2 tiles (three CTAs per SM)
+  const int stages = g_decode_stages == 2 ? 2 : 3;
+  const int smem = stages * 2 * kTileTokens * d * 2;
+  static bool attr_set[2][2] = {{false, false}, {false, false}};
+  bool& done = attr_set[d == 128 ? 1 : 0][stages - 2];
+  auto launch = [&](auto kernel) {
+    if (!done) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
+    launch_pdl(kernel, grid, dim3(kAttnThreads), smem, stream, p);
+  };
   if (d == 128) {
-    static bool done = false;
-    if (!done) { cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
-    launch_pdl(attn_decode_kernel<128>, grid, dim3(kAttnThreads), smem, stream, p);
+    if (stages == 2) launch(attn_decode_kernel<128, 2>); else launch(attn_decode_kernel<128, 3>);
   } else {
-    static bool done = false;
-    if (!done) { cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
-    launch_pdl(attn_decode_kernel<64>, grid, dim3(kAttnThreads), smem, stream, p);
+    if (stages == 2) launch(attn_decode_kernel<64, 2>); else launch(attn_decode_kernel<64, 3>);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return -static_cast<int>(e) - 300;

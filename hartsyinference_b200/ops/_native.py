@@ -27,6 +27,7 @@ _SIGNATURES = {
     "b200_gemm_workspace_bytes": (i64, []),
     "b200_gemm_set_pdl": (None, [i32]),
     "b200_gemm_set_cluster_reduce": (None, [i32]),
+    "b200_attn_set_decode_stages": (None, [i32]),
     "b200_gemm_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, i64, vp, vp]),
     "b200_gemm_colbatched": (i32, [vp, vp, vp, i32, i32, i32, i32, i64, i32, i64, i32, vp, i64, vp, vp]),
     "b200_mla_prep": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, f32, vp]),
@@ -99,6 +100,7 @@ def lib() -> C.CDLL:
             try:
                 handle.b200_gemm_set_pdl(1 if config.get("pdl") else 0)
                 handle.b200_gemm_set_cluster_reduce(1 if config.get("cluster_splitk") else 0)
+                handle.b200_attn_set_decode_stages(int(config.get("decode_attn_stages")))
             except AttributeError:
                 pass
             _lib = handle
