@@ -231,3 +231,123 @@ def hf_to_gguf(src_dir, dst, quant: Optional[str] = None) -> dict:
              and k != "token_embd.weight" and "ffn_gate_inp" not in k}
     G.write_gguf(dst, md, {k: v.float() for k, v in out.items()}, quant=q)
     return md
+
+
+# ============================================================================================
+# Flux transformer: original (Black Forest Labs / ComfyUI) names <-> diffusers names
+# ============================================================================================
+_FLUX_TOP = {"time_in.in_layer": "time_text_embed.timestep_embedder.linear_1",
+             "time_in.out_layer": "time_text_embed.timestep_embedder.linear_2",
+             "vector_in.in_layer": "time_text_embed.text_embedder.linear_1",
+             "vector_in.out_layer": "time_text_embed.text_embedder.linear_2",
+             "guidance_in.in_layer": "time_text_embed.guidance_embedder.linear_1",
+             "guidance_in.out_layer": "time_text_embed.guidance_embedder.linear_2",
+             "txt_in": "context_embedder", "img_in": "x_embedder", "final_layer.linear": "proj_out"}
+_FLUX_DOUBLE = {"img_mod.lin": "norm1.linear", "txt_mod.lin": "norm1_context.linear",
+                "img_attn.proj": "attn.to_out.0", "txt_attn.proj": "attn.to_add_out",
+                "img_mlp.0": "ff.net.0.proj", "img_mlp.2": "ff.net.2",
+                "txt_mlp.0": "ff_context.net.0.proj", "txt_mlp.2": "ff_context.net.2"}
+_FLUX_DOUBLE_NORMS = {"img_attn.norm.query_norm.scale": "attn.norm_q.weight", "img_attn.norm.key_norm.scale": "attn.norm_k.weight",
+                      "txt_attn.norm.query_norm.scale": "attn.norm_added_q.weight",
+                      "txt_attn.norm.key_norm.scale": "attn.norm_added_k.weight"}
+_FLUX_SINGLE = {"modulation.lin": "norm.linear", "linear2": "proj_out"}
+_FLUX_SINGLE_NORMS = {"norm.query_norm.scale": "attn.norm_q.weight", "norm.key_norm.scale": "attn.norm_k.weight"}
+_FLUX_PREFIXES = ("model.diffusion_model.", "diffusion_model.", "transformer.")
+
+
+def is_flux_original(keys) -> bool:
+    return any(k.endswith("double_blocks.0.img_attn.qkv.weight") for k in keys)
+
+
+def _swap_halves(t: torch.Tensor) -> torch.Tensor:
+    """[shift; scale] rows <-> [scale; shift] rows (the two layouts order the AdaLN output differently)."""
+    a, b = t.chunk(2, 0)
+    return torch.cat([b, a], 0)
+
+
+def flux_original_to_diffusers(tensors: dict[str, torch.Tensor], hidden: Optional[int] = None) -> dict[str, torch.Tensor]:
+    """Rename (and split the fused projections of) an original-layout Flux transformer state dict.
+    ``hidden`` is inferred from ``img_in.weight`` when omitted."""
+    src = {}
+    for k, v in tensors.items():
+        for pre in _FLUX_PREFIXES:
+            if k.startswith(pre):
+                k = k[len(pre):]
+                break
+        src[k] = v
+    H = hidden or src["img_in.weight"].shape[0]
+    out: dict[str, torch.Tensor] = {}
+    for k, v in src.items():
+        stem, _, kind = k.rpartition(".")
+        if stem in _FLUX_TOP:
+            out[f"{_FLUX_TOP[stem]}.{kind}"] = v
+        elif stem == "final_layer.adaLN_modulation.1":
+            out[f"norm_out.linear.{kind}"] = _swap_halves(v)
+        elif k.startswith("double_blocks."):
+            _, i, rest = k.split(".", 2)
+            p = f"transformer_blocks.{i}."
+            rstem, _, rkind = rest.rpartition(".")
+            if rest in _FLUX_DOUBLE_NORMS:
+                out[p + _FLUX_DOUBLE_NORMS[rest]] = v
+            elif rstem in _FLUX_DOUBLE:
+                out[f"{p}{_FLUX_DOUBLE[rstem]}.{rkind}"] = v
+            elif rstem in ("img_attn.qkv", "txt_attn.qkv"):
+                names = ("attn.to_q", "attn.to_k", "attn.to_v") if rstem.startswith("img") else \
+                        ("attn.add_q_proj", "attn.add_k_proj", "attn.add_v_proj")
+                for n, part in zip(names, v.chunk(3, 0)):
+                    out[f"{p}{n}.{rkind}"] = part
+        elif k.startswith("single_blocks."):
+            _, i, rest = k.split(".", 2)
+            p = f"single_transformer_blocks.{i}."
+            rstem, _, rkind = rest.rpartition(".")
+            if rest in _FLUX_SINGLE_NORMS:
+                out[p + _FLUX_SINGLE_NORMS[rest]] = v
+            elif rstem in _FLUX_SINGLE:
+                out[f"{p}{_FLUX_SINGLE[rstem]}.{rkind}"] = v
+            elif rstem == "linear1":
+                q, kk, vv, mlp = v.split([H, H, H, v.shape[0] - 3 * H], 0)
+                for n, part in (("attn.to_q", q), ("attn.to_k", kk), ("attn.to_v", vv), ("proj_mlp", mlp)):
+                    out[f"{p}{n}.{rkind}"] = part
+    return out
+
+
+def flux_diffusers_to_original(tensors: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """The inverse: fuse q / k / v (and the single blocks' MLP input) and restore the original names."""
+    inv_top = {v: k for k, v in _FLUX_TOP.items()}
+    inv_double = {v: k for k, v in _FLUX_DOUBLE.items()}
+    inv_dn = {v: k for k, v in _FLUX_DOUBLE_NORMS.items()}
+    inv_single = {v: k for k, v in _FLUX_SINGLE.items()}
+    inv_sn = {v: k for k, v in _FLUX_SINGLE_NORMS.items()}
+    out: dict[str, torch.Tensor] = {}
+    fuse: dict[str, dict[str, torch.Tensor]] = {}
+    for k, v in tensors.items():
+        stem, _, kind = k.rpartition(".")
+        if stem in inv_top:
+            out[f"{inv_top[stem]}.{kind}"] = v
+        elif stem == "norm_out.linear":
+            out[f"final_layer.adaLN_modulation.1.{kind}"] = _swap_halves(v)
+        elif k.startswith("transformer_blocks."):
+            _, i, rest = k.split(".", 2)
+            p = f"double_blocks.{i}."
+            rstem, _, rkind = rest.rpartition(".")
+            if rest in inv_dn:
+                out[p + inv_dn[rest]] = v
+            elif rstem in inv_double:
+                out[f"{p}{inv_double[rstem]}.{rkind}"] = v
+            elif rstem in ("attn.to_q", "attn.to_k", "attn.to_v"):
+                fuse.setdefault(f"{p}img_attn.qkv.{rkind}", {})[rstem[-1]] = v
+            elif rstem in ("attn.add_q_proj", "attn.add_k_proj", "attn.add_v_proj"):
+                fuse.setdefault(f"{p}txt_attn.qkv.{rkind}", {})[rstem[9]] = v
+        elif k.startswith("single_transformer_blocks."):
+            _, i, rest = k.split(".", 2)
+            p = f"single_blocks.{i}."
+            rstem, _, rkind = rest.rpartition(".")
+            if rest in inv_sn:
+                out[p + inv_sn[rest]] = v
+            elif rstem in inv_single:
+                out[f"{p}{inv_single[rstem]}.{rkind}"] = v
+            elif rstem in ("attn.to_q", "attn.to_k", "attn.to_v", "proj_mlp"):
+                fuse.setdefault(f"{p}linear1.{rkind}", {})["m" if rstem == "proj_mlp" else rstem[-1]] = v
+    for name, parts in fuse.items():
+        out[name] = torch.cat([parts[c] for c in ("q", "k", "v", "m") if c in parts], 0)
+    return out

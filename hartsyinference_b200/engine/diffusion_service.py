@@ -41,7 +41,7 @@ class _PipelineCache:
 class ImagesService(_PipelineCache):
     def _build(self, spec: ModelSpec):
         from ..models.dit import flux as F
-        from ..models.vae.vae2d import FLUX_VAE, Vae2dDecoder, tiny_vae2d
+        from ..models.vae.vae2d import FLUX_VAE, Vae2dDecoder, Vae2dEncoder, tiny_vae2d
         from ..pipelines.flux import FluxComponents, FluxPipeline
         name = spec.requested
         fp8 = bool(config.get("fp8_linears")) and self.device.startswith("cuda")
@@ -53,17 +53,27 @@ class ImagesService(_PipelineCache):
                                torch.bfloat16 if self.device.startswith("cuda") else torch.float32)
             if tiny:   # the tiny DiT packs 4 latent channels
                 assert cfg.in_channels == 16
-            return FluxPipeline(FluxComponents(tr, vae))
+            enc = Vae2dEncoder(tiny_vae2d() if tiny else FLUX_VAE, self.device, vae.dtype)
+            return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc))
         path = Path(spec.local_path or name)
         if not path.exists():
             raise UnsupportedModelError(f"{name}: no such checkpoint")
         ck = ShardedCheckpoint(path / "transformer" if (path / "transformer").exists() else path)
-        tr = F.FluxTransformer(F.FLUX_DEV, self.device, fp8=fp8, get=ck.get)
-        vae = None
+        get = ck.get
+        from ..assets.converters import flux_original_to_diffusers, is_flux_original
+        if is_flux_original(ck.keys()):
+            # a Black Forest Labs / ComfyUI layout file: fused qkv and other names; rename lazily per tensor group
+            renamed = flux_original_to_diffusers({k: ck.get(k) for k in ck.keys()})
+            get = renamed.get
+            log.decision("Load", f"{path.name}: original Flux layout converted to diffusers names")
+        tr = F.FluxTransformer(F.FLUX_DEV, self.device, fp8=fp8, get=get)
+        vae = enc = None
         if "vae" in spec.aux or (path / "vae").exists():
             vck = ShardedCheckpoint(spec.aux.get("vae", path / "vae"))
             vae = Vae2dDecoder(FLUX_VAE, self.device, get=vck.get)
-        return FluxPipeline(FluxComponents(tr, vae))
+            if vck.get("encoder.conv_in.weight") is not None:
+                enc = Vae2dEncoder(FLUX_VAE, self.device, get=vck.get)
+        return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc))
 
     def pipeline(self, spec: ModelSpec):
         k = self.key(spec)

@@ -133,6 +133,7 @@ class ImageRequest:
     scheduler: str = "flow_match_euler"
     batch: int = 1
     init_image: Optional[Any] = None
+    mask_image: Optional[Any] = None     # white = repaint (inpainting; needs init_image)
     strength: float = 1.0
     loras: list[tuple[str, float]] = field(default_factory=list)
     step_cache_threshold: float = 0.0

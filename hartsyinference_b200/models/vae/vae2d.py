@@ -138,6 +138,66 @@ class Vae2dDecoder:
         return x.float().clamp(-1, 1)
 
 
+class Vae2dEncoder(Vae2dDecoder):
+    """The encoder half (image -> latent mean): conv_in, four down blocks of ResNets with a stride-2
+    convolution between them (asymmetric right / bottom padding), the same mid block, GroupNorm +
+    SiLU, conv_out to 2 x latent channels (mean | log-variance). Used by img2img and inpainting.
+    Reference: src/HartsyInference.Diffusion/Models/Vae/ (VaeEncoder)."""
+
+    def __init__(self, cfg: Vae2dConfig = FLUX_VAE, device="cpu", dtype=torch.bfloat16,
+                 get: Optional[Callable[[str], Optional[torch.Tensor]]] = None, seed: int = 1):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self._get = get
+        self._g = torch.Generator().manual_seed(seed)
+        self.w = {}
+        ch = list(cfg.block_out_channels)
+        self._conv("encoder.conv_in", ch[0], 3, 3)
+        prev = ch[0]
+        self.down: list[tuple[list[tuple[str, int, int]], Optional[str]]] = []
+        for i, c in enumerate(ch):
+            blocks = []
+            for j in range(cfg.layers_per_block):
+                name = f"encoder.down_blocks.{i}.resnets.{j}"
+                self._resnet(name, prev, c)
+                blocks.append((name, prev, c))
+                prev = c
+            dn = None
+            if i < len(ch) - 1:
+                dn = f"encoder.down_blocks.{i}.downsamplers.0.conv"
+                self._conv(dn, c, c, 3)
+            self.down.append((blocks, dn))
+        self._resnet("encoder.mid_block.resnets.0", prev, prev)
+        self._attn("encoder.mid_block.attentions.0", prev)
+        self._resnet("encoder.mid_block.resnets.1", prev, prev)
+        self._norm("encoder.conv_norm_out", prev)
+        self._conv("encoder.conv_out", 2 * cfg.latent_channels, prev, 3)
+
+    @torch.no_grad()
+    def encode(self, images: torch.Tensor, sample: bool = False, generator: Optional[torch.Generator] = None) -> torch.Tensor:
+        """images [B, 3, H, W] in [-1, 1] -> latents [B, C, H/8, W/8] in model space (fp32): the
+        posterior mean (or a sample), shifted and scaled."""
+        x = self._c(images.to(self.device).to(self.dtype), "encoder.conv_in")
+        for blocks, dn in self.down:
+            for name, ci, co in blocks:
+                x = self._res(x, name, ci, co)
+            if dn is not None:
+                x = F.conv2d(F.pad(x, (0, 1, 0, 1)), self.w[dn + ".weight"], self.w[dn + ".bias"], stride=2)
+        top = self.cfg.block_out_channels[-1]
+        x = self._res(x, "encoder.mid_block.resnets.0", top, top)
+        x = self._attention(x, "encoder.mid_block.attentions.0")
+        x = self._res(x, "encoder.mid_block.resnets.1", top, top)
+        moments = self._c(self._gn_silu(x, "encoder.conv_norm_out"), "encoder.conv_out").float()
+        mean, logvar = moments.chunk(2, 1)
+        z = mean
+        if sample:
+            std = torch.exp(0.5 * logvar.clamp(-30, 20))
+            z = mean + std * torch.randn(mean.shape, generator=generator).to(mean.device)
+        return (z - self.cfg.shift_factor) * self.cfg.scaling_factor
+
+    def decode(self, latents):  # pragma: no cover - this half has no decoder weights
+        raise NotImplementedError("Vae2dEncoder only encodes")
+
+
 def to_rgb24(images: torch.Tensor) -> list[bytes]:
     """[B, 3, H, W] in [-1, 1] -> RGB24 byte strings."""
     u8 = ((images.float().clamp(-1, 1) + 1) * 127.5).round().to(torch.uint8).permute(0, 2, 3, 1).contiguous().cpu()

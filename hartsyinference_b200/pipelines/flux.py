@@ -44,6 +44,7 @@ class FluxComponents:
     vae: Optional[Vae2dDecoder] = None
     t5: Optional[object] = None
     clip: Optional[object] = None
+    vae_encoder: Optional[object] = None      # Vae2dEncoder: img2img / inpainting start from an encoded image
     t5_tokenizer: Optional[object] = None
     clip_tokenizer: Optional[object] = None
 
@@ -78,8 +79,14 @@ class FluxPipeline:
     def denoise(self, ctx: torch.Tensor, pooled: torch.Tensor, height: int, width: int, steps: int, guidance: float,
                 seed: int, neg: Optional[tuple[torch.Tensor, torch.Tensor]] = None, cfg_scale: float = 1.0,
                 on_step: Optional[Callable[[StepPreview], None]] = None, step_cache_threshold: float = 0.0, first_block_cache: float = 0.0,
-                latents: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Returns the final latents [1, C, H/8, W/8] fp32 on the device."""
+                latents: Optional[torch.Tensor] = None, init_latents: Optional[torch.Tensor] = None, strength: float = 1.0,
+                mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Returns the final latents [1, C, H/8, W/8] fp32 on the device.
+
+        ``init_latents`` [1, C, H/8, W/8] with ``strength`` < 1 starts from the image noised to the
+        sigma of step ``steps * (1 - strength)`` and runs the remaining steps (img2img). ``mask``
+        [1, 1, H/8, W/8] (1 = repaint) additionally pins the unmasked region to the original image,
+        re-noised to each step's sigma (inpainting)."""
         tr = self.c.transformer
         dev = self.device
         C = tr.cfg.in_channels // 4
@@ -90,6 +97,16 @@ class FluxPipeline:
         S = x.shape[1]
         img_ids, txt_ids = flux_ids(lh // 2, lw // 2, ctx.shape[0], dev)
         sched = FlowMatchEulerScheduler(steps, mu=flux_mu(S))
+        first_step = 0
+        init_packed = noise_packed = mask_packed = None
+        if init_latents is not None:
+            first_step = min(steps - 1, max(0, int(round(steps * (1.0 - strength))))) if strength < 1.0 else 0
+            init_packed = pack_latents(init_latents.float()).to(dev).contiguous()
+            noise_packed = x.clone()
+            s0 = sched.sigma(first_step)
+            x = (s0 * noise_packed + (1.0 - s0) * init_packed).contiguous()      # flow matching: x_t = t noise + (1 - t) x_0
+            if mask is not None:
+                mask_packed = pack_latents(mask.float().expand(1, C, lh, lw)).to(dev).contiguous()
         ctx_d, pooled_d = ctx.to(dev)[None], pooled.to(dev)[None]
         gvec = torch.tensor([guidance], device=dev) if tr.cfg.guidance_embed else None
         true_cfg = cfg_scale > 1.0 and neg is not None
@@ -111,7 +128,7 @@ class FluxPipeline:
         fbc = [FirstBlockCache(first_block_cache), FirstBlockCache(first_block_cache)] if first_block_cache > 0 else [None, None]
         self.last_step_ms = []
         use_cuda = dev.type == "cuda"
-        for i in range(steps):
+        for i in range(first_step, steps):
             if use_cuda:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -146,6 +163,11 @@ class FluxPipeline:
                         v_cond, v_unc = cache_v, None
             if v_cond is not None:
                 sched.step(x, v_cond.contiguous(), i, v_unc, cfg_scale)
+            if mask_packed is not None:
+                # outside the mask the latent follows the original image at the next step's noise level
+                s_next = sched.sigma(i + 1) if i + 1 < steps else 0.0
+                known = s_next * noise_packed + (1.0 - s_next) * init_packed
+                x.copy_(mask_packed * x + (1.0 - mask_packed) * known)
             if use_cuda:
                 e1.record()
                 e1.synchronize()
@@ -173,13 +195,44 @@ class FluxPipeline:
             self._fused_cfg_obj = None
         return self._fused_cfg_obj
 
+    @staticmethod
+    def _image_tensor(image, width: int, height: int) -> torch.Tensor:
+        """Path, PIL image, uint8 HWC array / tensor or float CHW tensor in [0, 1] -> [1, 3, height, width] in [-1, 1]."""
+        if isinstance(image, (str, bytes)) or hasattr(image, "__fspath__"):
+            from PIL import Image
+            image = Image.open(image)
+        if hasattr(image, "convert"):
+            import numpy as np
+            image = torch.from_numpy(np.asarray(image.convert("RGB")).copy())
+        t = torch.as_tensor(image)
+        if t.dtype == torch.uint8:
+            t = t.float() / 255.0
+        if t.ndim == 2:
+            t = t[None].expand(3, -1, -1)
+        if t.ndim == 3 and t.shape[-1] in (1, 3) and t.shape[0] not in (1, 3):
+            t = t.permute(2, 0, 1)
+        if t.shape[0] == 1:
+            t = t.expand(3, -1, -1)
+        t = t.float()[None]
+        if t.shape[-2:] != (height, width):
+            t = torch.nn.functional.interpolate(t, size=(height, width), mode="bilinear", align_corners=False, antialias=True)
+        return t.clamp(0, 1) * 2.0 - 1.0
+
     def generate(self, req: ImageRequest, on_step: Optional[Callable[[StepPreview], None]] = None) -> ImageResult:
         seed = req.seed if req.seed is not None else int(time.time() * 1000) % (2 ** 31)
         ctx, pooled = self.encode_prompt(req.prompt)
         neg = self.encode_prompt(req.negative_prompt) if req.cfg_scale > 1.0 else None
         t0 = time.perf_counter()
+        init_latents = mask = None
+        if req.init_image is not None:
+            if self.c.vae_encoder is None:
+                raise ValueError("img2img / inpainting needs the VAE encoder (FluxComponents.vae_encoder)")
+            init_latents = self.c.vae_encoder.encode(self._image_tensor(req.init_image, req.width, req.height))
+            if getattr(req, "mask_image", None) is not None:
+                m = self._image_tensor(req.mask_image, req.width, req.height)[:, :1] * 0.5 + 0.5
+                mask = (torch.nn.functional.interpolate(m, size=(req.height // 8, req.width // 8), mode="area") > 0.5).float()
         z = self.denoise(ctx, pooled, req.height, req.width, req.steps, req.guidance, seed, neg, req.cfg_scale, on_step,
-                         req.step_cache_threshold)
+                         req.step_cache_threshold, init_latents=init_latents, strength=req.strength, mask=mask)
         t_denoise = time.perf_counter() - t0
         if self.c.vae is None:
             img = torch.zeros(1, 3, req.height, req.width)

@@ -378,6 +378,12 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
     async def native_image(request: Request):
         body = await request.json()
         fields = {k: v for k, v in body.items() if k in ImageRequest.__dataclass_fields__}
+        for key in ("init_image", "mask_image"):       # base64 (optionally a data: URL); never a server-side path
+            if isinstance(fields.get(key), str):
+                import io
+                from PIL import Image
+                b64 = fields[key].split(",", 1)[1] if fields[key].startswith("data:") else fields[key]
+                fields[key] = Image.open(io.BytesIO(base64.b64decode(b64))).convert("RGB")
         with heavy_queue.slot():
             res = eng.with_vram_cleanup(lambda: eng.images.generate(resolve(body.get("model"), Modality.IMAGE), ImageRequest(**fields)))
         return {"width": res.width, "height": res.height, "seed": res.seed, "meta": res.meta,

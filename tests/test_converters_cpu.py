@@ -1,0 +1,70 @@
+"""Flux checkpoint layouts: original <-> diffusers names, and loading an original-layout file."""
+import torch
+
+from hartsyinference_b200.assets.converters import (flux_diffusers_to_original, flux_original_to_diffusers,
+                                                    is_flux_original)
+from hartsyinference_b200.models.dit import flux as F
+
+
+def _diffusers_state(cfg, seed=0):
+    """Every tensor name the transformer asks for, with random values."""
+    g = torch.Generator().manual_seed(seed)
+    made = {}
+    H, D = cfg.hidden_size, cfg.head_dim
+    def lin(n, o, i):
+        made[n + ".weight"] = torch.randn(o, i, generator=g) * 0.05
+        made[n + ".bias"] = torch.randn(o, generator=g) * 0.05
+    lin("x_embedder", H, cfg.in_channels); lin("context_embedder", H, cfg.context_dim)
+    lin("time_text_embed.timestep_embedder.linear_1", H, 256); lin("time_text_embed.timestep_embedder.linear_2", H, H)
+    lin("time_text_embed.text_embedder.linear_1", H, cfg.pooled_dim); lin("time_text_embed.text_embedder.linear_2", H, H)
+    if cfg.guidance_embed:
+        lin("time_text_embed.guidance_embedder.linear_1", H, 256); lin("time_text_embed.guidance_embedder.linear_2", H, H)
+    for i in range(cfg.num_double_blocks):
+        p = f"transformer_blocks.{i}."
+        lin(p + "norm1.linear", 6 * H, H); lin(p + "norm1_context.linear", 6 * H, H)
+        for n in ("attn.to_q", "attn.to_k", "attn.to_v", "attn.add_q_proj", "attn.add_k_proj", "attn.add_v_proj",
+                  "attn.to_out.0", "attn.to_add_out"):
+            lin(p + n, H, H)
+        for n in ("attn.norm_q", "attn.norm_k", "attn.norm_added_q", "attn.norm_added_k"):
+            made[p + n + ".weight"] = 1 + torch.randn(D, generator=g) * 0.1
+        lin(p + "ff.net.0.proj", cfg.mlp_dim, H); lin(p + "ff.net.2", H, cfg.mlp_dim)
+        lin(p + "ff_context.net.0.proj", cfg.mlp_dim, H); lin(p + "ff_context.net.2", H, cfg.mlp_dim)
+    for i in range(cfg.num_single_blocks):
+        p = f"single_transformer_blocks.{i}."
+        lin(p + "norm.linear", 3 * H, H)
+        for n in ("attn.to_q", "attn.to_k", "attn.to_v"):
+            lin(p + n, H, H)
+        lin(p + "proj_mlp", cfg.mlp_dim, H); lin(p + "proj_out", H, H + cfg.mlp_dim)
+        made[p + "attn.norm_q.weight"] = 1 + torch.randn(D, generator=g) * 0.1
+        made[p + "attn.norm_k.weight"] = 1 + torch.randn(D, generator=g) * 0.1
+    lin("norm_out.linear", 2 * H, H); lin("proj_out", cfg.in_channels, H)
+    return made
+
+
+def test_flux_layout_roundtrip_and_load():
+    cfg = F.tiny_flux()
+    sd = _diffusers_state(cfg)
+    orig = flux_diffusers_to_original(sd)
+    assert is_flux_original(orig) and not is_flux_original(sd)
+    H = cfg.hidden_size
+    assert orig["double_blocks.0.img_attn.qkv.weight"].shape == (3 * H, H)
+    assert orig["single_blocks.0.linear1.weight"].shape == (3 * H + cfg.mlp_dim, H)
+    assert "final_layer.adaLN_modulation.1.weight" in orig and "double_blocks.0.txt_attn.norm.key_norm.scale" in orig
+    # the AdaLN output order differs between the layouts: [shift; scale] vs [scale; shift]
+    assert torch.equal(orig["final_layer.adaLN_modulation.1.weight"][:H], sd["norm_out.linear.weight"][H:])
+    back = flux_original_to_diffusers({"model.diffusion_model." + k: v for k, v in orig.items()})
+    assert set(back) == set(sd) and all(torch.equal(back[k], sd[k]) for k in sd)
+
+    a = F.FluxTransformer(cfg, "cpu", get=lambda n: sd.get(n))
+    b = F.FluxTransformer(cfg, "cpu", get=lambda n: back.get(n))
+    g = torch.Generator().manual_seed(1)
+    S_i, S_t = 16, 8
+    img = torch.randn(1, S_i, cfg.in_channels, generator=g)
+    txt = torch.randn(1, S_t, cfg.context_dim, generator=g)
+    pooled = torch.randn(1, cfg.pooled_dim, generator=g)
+    img_ids, txt_ids = F.flux_ids(4, 4, S_t)
+    t = torch.tensor([0.7])
+    gd = torch.tensor([3.5]) if cfg.guidance_embed else None
+    ya = a.forward(img, txt, t, pooled, img_ids, txt_ids, gd)
+    yb = b.forward(img, txt, t, pooled, img_ids, txt_ids, gd)
+    assert torch.equal(ya, yb) and ya.float().abs().max() > 0

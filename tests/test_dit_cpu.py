@@ -111,3 +111,43 @@ def test_flux_block_streaming_gives_the_same_output():
     assert b._streamers["double"].uploads >= len(b._streamers["double"])
     out2 = b.forward(*args)            # a second pass streams the blocks again
     assert torch.equal(out2, ref)
+
+
+def test_flux_img2img_and_inpaint():
+    """img2img starts from the encoded image at the sigma its strength selects; inpainting keeps the
+    unmasked latents equal to the original image's."""
+    import torch
+    from hartsyinference_b200.models.dit import flux as F
+    from hartsyinference_b200.models.vae.vae2d import Vae2dDecoder, Vae2dEncoder, tiny_vae2d
+    from hartsyinference_b200.pipelines.flux import FluxComponents, FluxPipeline
+    from hartsyinference_b200.engine.requests import ImageRequest
+    cfg = F.tiny_flux()
+    tr = F.FluxTransformer(cfg, "cpu", seed=0)
+    vcfg = tiny_vae2d()
+    pipe = FluxPipeline(FluxComponents(tr, Vae2dDecoder(vcfg, "cpu", torch.float32), vae_encoder=Vae2dEncoder(vcfg, "cpu", torch.float32)))
+    g = torch.Generator().manual_seed(0)
+    image = torch.rand(3, 64, 64, generator=g)
+    z0 = pipe.c.vae_encoder.encode(FluxPipeline._image_tensor(image, 64, 64))
+    assert z0.shape == (1, vcfg.latent_channels, 8, 8)
+    ctx, pooled = pipe.encode_prompt("a cat", max_len=8)
+    ran = []
+    low = pipe.denoise(ctx, pooled, 64, 64, 8, 3.5, 1, init_latents=z0, strength=0.1, on_step=lambda s: ran.append(s.step))
+    assert ran == [8]                                   # strength 0.1 of 8 steps: only the last one runs
+    ran.clear()
+    full = pipe.denoise(ctx, pooled, 64, 64, 8, 3.5, 1, init_latents=z0, strength=1.0, on_step=lambda s: ran.append(s.step))
+    assert len(ran) == 8
+    plain = pipe.denoise(ctx, pooled, 64, 64, 8, 3.5, 1)
+    assert torch.allclose(full, plain)                  # strength 1 ignores the image
+    assert (low - z0.to(low.device)).abs().mean() < (full - z0.to(full.device)).abs().mean()
+
+    mask = torch.zeros(1, 1, 8, 8)
+    mask[..., 2:6, 2:6] = 1
+    out = pipe.denoise(ctx, pooled, 64, 64, 4, 3.5, 2, init_latents=z0, strength=1.0, mask=mask)
+    keep = (mask == 0).expand_as(out)
+    assert torch.allclose(out[keep], z0.to(out.device)[keep], atol=1e-5)
+    assert not torch.allclose(out[~keep], z0.to(out.device)[~keep], atol=1e-3)
+
+    m_img = torch.zeros(64, 64)
+    m_img[16:48, 16:48] = 1.0
+    res = pipe.generate(ImageRequest(prompt="a cat", width=64, height=64, steps=3, seed=3, init_image=image, mask_image=m_img, strength=0.8))
+    assert res.width == 64 and len(res.rgb) == 64 * 64 * 3
