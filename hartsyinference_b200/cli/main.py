@@ -244,14 +244,38 @@ def convert(src, dst, quant):
 
 @cli.command("models")
 @click.option("--dir", "cache_dir", default=None)
-def list_models(cache_dir):
-    """List checkpoints in the model cache directory."""
-    d = Path(cache_dir or config.get("model_cache_dir")).expanduser()
-    if not d.exists():
-        click.echo(f"(no cache directory at {d})")
+@click.option("--catalog", "show_catalog", is_flag=True, help="list the built-in catalog instead of what is on disk")
+def list_models(cache_dir, show_catalog):
+    """List checkpoints in the model cache directory (or the catalog of known models)."""
+    from ..assets.catalog import ModelCacheStore, ModelCatalog
+    if show_catalog:
+        for e in ModelCatalog().entries():
+            click.echo(f"{e.id:32s} {e.modality.value:11s} {e.family:10s} {e.repo}")
         return
-    for p in sorted(d.iterdir()):
-        click.echo(p.name)
+    store = ModelCacheStore(cache_dir or config.get("model_cache_dir"))
+    rows = store.list()
+    if not rows:
+        click.echo(f"(nothing in {store.root})")
+    for r in rows:
+        click.echo(f"{r['id']:40s} {r['bytes'] / 2 ** 30:8.2f} GiB  {r.get('source', '')}")
+
+
+@cli.command()
+@click.argument("name")
+@click.option("--from", "src", default=None, help="register a checkpoint that is already on disk instead of downloading")
+@click.option("--copy", is_flag=True, help="copy instead of linking (with --from)")
+@click.option("--dir", "cache_dir", default=None)
+@click.option("--token", default=None, envvar="HF_TOKEN")
+def pull(name, src, copy, cache_dir, token):
+    """Fetch a catalog model or a Hugging Face repository into the model cache."""
+    from ..assets.catalog import ModelCacheStore, ModelResolver
+    store = ModelCacheStore(cache_dir or config.get("model_cache_dir"))
+    res = ModelResolver(store=store)
+    if src:
+        entry = res.catalog.find(name)
+        click.echo(str(store.add_local(entry.id if entry else name, src, link=not copy)))
+        return
+    click.echo(str(res.pull(name, token)))
 
 
 cli.add_command(list_models, "list")

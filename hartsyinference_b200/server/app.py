@@ -140,6 +140,8 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
     limiter = _RateLimiter(opts.rate_limit_per_minute)
     usage = UsageTracker()
     app.state.engine, app.state.usage, app.state.options = eng, usage, opts
+    from ..assets.catalog import ModelCacheStore, ModelResolver
+    resolver = ModelResolver(store=ModelCacheStore(eng.options.model_cache_directory))
 
     def resolve(name: Optional[str], modality: Modality) -> ModelSpec:
         default = {Modality.TEXT: opts.default_text_model, Modality.IMAGE: opts.default_image_model,
@@ -148,6 +150,13 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
         if not name:
             raise UnsupportedModelError("no model named in the request and no default configured")
         path = opts.models.get(name, name)
+        if name not in opts.models and not path.startswith("synthetic:"):
+            # not a configured name: a path, a catalog id / alias or a repository id that is on disk
+            import os
+            if not os.path.exists(os.path.expanduser(path)):
+                spec = resolver.resolve(path, modality)
+                return ModelSpec(requested=spec.local_path or path, modality=modality, catalog=spec.catalog,
+                                 local_path=spec.local_path, aux=spec.aux)
         return ModelSpec(requested=path, modality=modality, catalog=name if name in opts.models else None, local_path=path)
 
     @app.middleware("http")
