@@ -286,3 +286,146 @@ class LCMScheduler:
         a_p = float(self.ac[int(self.timesteps[i + 1])])
         noise = torch.randn(x.shape, generator=self.gen, dtype=torch.float32).to(x.device)
         return (a_p ** 0.5 * den + (1 - a_p) ** 0.5 * noise).to(x.dtype)
+
+
+class TCDScheduler(LCMScheduler):
+    """Trajectory-consistency sampling: like LCM, but each step first jumps to an intermediate
+    timestep ``s = (1 - gamma) t_next`` deterministically and only re-noises from there; ``gamma``
+    0 is deterministic multi-step consistency, 1 is LCM's full re-noising
+    (src/HartsyInference.Diffusion/Schedulers/TcdScheduler.cs)."""
+
+    def __init__(self, num_steps: int, gamma: float = 0.3, **kw):
+        super().__init__(num_steps, **kw)
+        self.gamma = gamma
+
+    def step(self, eps: torch.Tensor, i: int, x: torch.Tensor) -> torch.Tensor:
+        t = int(self.timesteps[i])
+        a_t = float(self.ac[t])
+        e = eps.float()
+        x0 = (x.float() - (1 - a_t) ** 0.5 * e) / a_t ** 0.5
+        if i == self.num_steps - 1:
+            return x0.to(x.dtype)
+        t_next = int(self.timesteps[i + 1])
+        s = int((1.0 - self.gamma) * t_next)
+        a_s, a_n = float(self.ac[s]), float(self.ac[t_next])
+        x_s = a_s ** 0.5 * x0 + (1 - a_s) ** 0.5 * e                      # deterministic jump to s
+        if self.gamma <= 0:
+            return x_s.to(x.dtype)
+        noise = torch.randn(x.shape, generator=self.gen, dtype=torch.float32).to(x.device)
+        ratio = a_n / a_s
+        return (ratio ** 0.5 * x_s + (1 - ratio) ** 0.5 * noise).to(x.dtype)   # forward diffusion s -> t_next
+
+
+class FlowDPMSolverMultistepScheduler:
+    """DPM-Solver++ (2M) on the flow-matching parameterisation ``x_t = (1 - sigma) x0 + sigma eps``
+    with a velocity model: ``x0 = x - sigma v``, half log-SNR ``lambda = log((1 - sigma) / sigma)``
+    (src/HartsyInference.Diffusion/Schedulers/FlowDpmPlusPlus2MScheduler.cs)."""
+
+    def __init__(self, num_steps: int, shift: float = 1.0, mu: Optional[float] = None):
+        base = FlowMatchEulerScheduler(num_steps, shift=shift, mu=mu)
+        self.sigmas = base.sigmas.double()
+        self.num_steps = num_steps
+        self._prev_x0: Optional[torch.Tensor] = None
+
+    def sigma(self, i: int) -> float:
+        return float(self.sigmas[i])
+
+    def timestep(self, i: int) -> float:
+        return float(self.sigmas[i]) * 1000.0
+
+    def _lam(self, i: int) -> float:
+        s = min(max(float(self.sigmas[i]), 1e-8), 1 - 1e-8)
+        return math.log((1 - s) / s)
+
+    def step(self, velocity: torch.Tensor, i: int, x: torch.Tensor) -> torch.Tensor:
+        s_c, s_n = float(self.sigmas[i]), float(self.sigmas[i + 1])
+        x0 = x.float() - s_c * velocity.float()
+        if i == self.num_steps - 1 or s_n <= 0:
+            self._prev_x0 = None
+            return x0.to(x.dtype)
+        h = self._lam(i + 1) - self._lam(i)
+        if self._prev_x0 is None or i == self.num_steps - 2:
+            d = x0
+        else:
+            r = (self._lam(i) - self._lam(i - 1)) / h
+            d = x0 + (x0 - self._prev_x0) / (2 * r)
+        self._prev_x0 = x0
+        return ((s_n / s_c) * x.float() - (1 - s_n) * math.expm1(-h) * d).to(x.dtype)
+
+
+class FlowMatchPingPongScheduler(FlowMatchEulerScheduler):
+    """Ping-pong sampling for flow models (the few-step Stable Audio / distilled samplers): denoise
+    fully to ``x0 = x - sigma v``, then re-noise to the next sigma with fresh noise
+    (src/HartsyInference.Diffusion/Schedulers/FlowMatchPingPongScheduler.cs, StableAudioPingPongScheduler.cs)."""
+
+    def __init__(self, num_steps: int, seed: int = 0, **kw):
+        super().__init__(num_steps, **kw)
+        self.gen = torch.Generator().manual_seed(seed)
+
+    def step(self, latents: torch.Tensor, cond: torch.Tensor, i: int, uncond: Optional[torch.Tensor] = None,
+             guidance: float = 1.0) -> torch.Tensor:
+        v = cond.float() if uncond is None else uncond.float() + guidance * (cond.float() - uncond.float())
+        s_c, s_n = self.sigma(i), float(self.sigmas[i + 1])
+        x0 = latents.float() - s_c * v.reshape(latents.shape)
+        if s_n <= 0:
+            latents.copy_(x0)
+            return latents
+        noise = torch.randn(latents.shape, generator=self.gen, dtype=torch.float32).to(latents.device)
+        latents.copy_((1 - s_n) * x0 + s_n * noise)
+        return latents
+
+
+class EulerAncestralScheduler(EulerDiscreteScheduler):
+    """Euler with ancestral noise: step down to ``sigma_down`` and add ``sigma_up`` of fresh noise,
+    ``sigma_up^2 = sigma_next^2 (sigma^2 - sigma_next^2) / sigma^2``
+    (the reference's samplers: euler_a)."""
+
+    def __init__(self, num_steps: int, seed: int = 0, eta: float = 1.0, **kw):
+        super().__init__(num_steps, **kw)
+        self.gen, self.eta = torch.Generator().manual_seed(seed), eta
+
+    def step(self, eps: torch.Tensor, i: int, x: torch.Tensor) -> torch.Tensor:
+        s, sn = float(self.sigmas[i]), float(self.sigmas[i + 1])
+        up = min(sn, self.eta * (sn ** 2 * (s ** 2 - sn ** 2) / s ** 2) ** 0.5) if s > 0 else 0.0
+        down = (sn ** 2 - up ** 2) ** 0.5
+        x = x + eps.float() * (down - s)
+        if up > 0:
+            x = x + torch.randn(x.shape, generator=self.gen, dtype=torch.float32).to(x.device) * up
+        return x
+
+
+class HeunScheduler(EulerDiscreteScheduler):
+    """Heun's second-order method on the sigma ODE ``dx / dsigma = eps``: an Euler predictor, a
+    second model call at the predicted point, and the trapezoidal corrector (first order on the
+    last step, where sigma_next = 0). ``step`` takes a callable for the second evaluation."""
+
+    def step(self, eps: torch.Tensor, i: int, x: torch.Tensor, model=None) -> torch.Tensor:
+        s, sn = float(self.sigmas[i]), float(self.sigmas[i + 1])
+        x_e = x + eps.float() * (sn - s)
+        if model is None or sn == 0:
+            return x_e
+        eps2 = model(x_e, i + 1).float()
+        return x + 0.5 * (eps.float() + eps2) * (sn - s)
+
+
+def logit_normal_sigmas(num_steps: int, mean: float = 0.0, std: float = 1.0, shift: float = 1.0) -> torch.Tensor:
+    """Inference sigmas placed at the quantiles of a logit-normal density (the density SD3-class
+    models are trained on), descending from 1 to 0, with the usual resolution shift
+    (src/HartsyInference.Diffusion/Schedulers/LogitNormalSchedule.cs)."""
+    q = torch.linspace(1.0, 0.0, num_steps + 1, dtype=torch.float64)[1:-1]
+    z = mean + std * math.sqrt(2.0) * torch.erfinv(2 * q - 1)
+    sig = torch.sigmoid(z)
+    sig = torch.cat([torch.ones(1, dtype=torch.float64), sig, torch.zeros(1, dtype=torch.float64)])
+    return (shift * sig / (1 + (shift - 1) * sig)).float()
+
+
+_MORE = {"tcd": TCDScheduler, "flow_dpm++2m": FlowDPMSolverMultistepScheduler, "flow_dpmpp_2m": FlowDPMSolverMultistepScheduler,
+         "pingpong": FlowMatchPingPongScheduler, "flow_match_pingpong": FlowMatchPingPongScheduler,
+         "euler_a": EulerAncestralScheduler, "euler_ancestral": EulerAncestralScheduler, "heun": HeunScheduler,
+         "ddim_v": lambda steps, **kw: DDIMScheduler(steps, v_prediction=True, **kw)}
+_make_base = make_scheduler
+
+
+def make_scheduler(name: str, steps: int, **kw):  # noqa: F811 - the factory, extended with the classes above
+    cls = _MORE.get(name.lower())
+    return cls(steps, **kw) if cls is not None else _make_base(name, steps, **kw)

@@ -151,3 +151,65 @@ def test_flux_img2img_and_inpaint():
     m_img[16:48, 16:48] = 1.0
     res = pipe.generate(ImageRequest(prompt="a cat", width=64, height=64, steps=3, seed=3, init_image=image, mask_image=m_img, strength=0.8))
     assert res.width == 64 and len(res.rgb) == 64 * 64 * 3
+
+
+def test_more_schedulers():
+    """Each sampler, driven by an exact model of a point-mass data distribution, lands on the data."""
+    import math
+    import torch
+    from hartsyinference_b200.models.diffusion import schedulers as S
+    g = torch.Generator().manual_seed(0)
+    x0 = torch.randn(4, 8, generator=g)
+
+    # flow parameterisation: x = (1 - s) x0 + s n, exact velocity v = n - x0 = (x - x0) / s
+    for name in ("flow_dpm++2m", "pingpong"):
+        sch = S.make_scheduler(name, 6)
+        x = torch.randn(4, 8, generator=g)
+        for i in range(6):
+            v = (x - x0) / sch.sigma(i)
+            x = sch.step(v, i, x) if name == "flow_dpm++2m" else sch.step(x, v, i)
+        assert torch.allclose(x, x0, atol=1e-4), name
+    # second order: on a curved velocity field the multistep solver beats Euler at equal step count
+    def field(x, s):
+        return (x - x0) / s + 0.5 * torch.sin(3 * x) * s
+    outs = {}
+    for name in ("flow_match_euler", "flow_dpm++2m"):
+        res = []
+        for n in (8, 256):
+            sch = S.make_scheduler(name, n)
+            x = torch.ones(4, 8)
+            for i in range(n):
+                v = field(x, sch.sigma(i))
+                x = sch.step(v, i, x) if name != "flow_match_euler" else x + v * sch.dt(i)
+            res.append(x)
+        outs[name] = (res[0] - res[1]).abs().mean().item()
+    assert outs["flow_dpm++2m"] < outs["flow_match_euler"]
+
+    # variance-preserving epsilon models: eps = (x - sqrt(a) x0) / sqrt(1 - a)
+    for name, kw in (("tcd", dict(gamma=0.0)), ("tcd", dict(gamma=0.3)), ("lcm", {})):
+        sch = S.make_scheduler(name, 4, **kw)
+        a0 = float(sch.ac[int(sch.timesteps[0])])
+        x = a0 ** 0.5 * x0 + (1 - a0) ** 0.5 * torch.randn(4, 8, generator=g)
+        for i in range(4):
+            a = float(sch.ac[int(sch.timesteps[i])])
+            eps = (x - a ** 0.5 * x0) / (1 - a) ** 0.5
+            x = sch.step(eps, i, x)
+        assert torch.allclose(x, x0, atol=1e-3), (name, kw)
+    # sigma-space epsilon models: x = x0 + sigma n
+    for name in ("euler_a", "heun", "euler"):
+        sch = S.make_scheduler(name, 10)
+        x = x0 + float(sch.sigmas[0]) * torch.randn(4, 8, generator=g)
+        model = lambda xx, j: (xx - x0) / float(sch.sigmas[j])
+        for i in range(10):
+            eps = model(x, i)
+            x = sch.step(eps, i, x, model) if name == "heun" else sch.step(eps, i, x)
+        assert torch.allclose(x, x0, atol=1e-3), name
+    ddv = S.make_scheduler("ddim_v", 5)
+    assert ddv.v_prediction
+    sig = S.logit_normal_sigmas(10, shift=3.0)
+    assert sig.shape == (11,) and sig[0] == 1 and sig[-1] == 0 and (sig[1:] < sig[:-1]).all()
+    mid = S.logit_normal_sigmas(10)
+    assert abs(float(mid[5]) - 0.5) < 1e-6 and (sig[1:-1] > mid[1:-1]).all()      # shift > 1 spends steps at high noise
+    import pytest
+    with pytest.raises(ValueError):
+        S.make_scheduler("nope", 4)
