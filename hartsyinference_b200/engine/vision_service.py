@@ -1,4 +1,5 @@
-"""Vision service: CLIP image / text embeddings and their similarity (zero-shot scoring).
+"""Vision service: CLIP image / text embeddings and their similarity (zero-shot scoring), SigLIP and
+DINOv2 image embeddings.
 
 Reference: src/HartsyInference.Engine/Services/VisionService.cs (embed operation),
 src/HartsyInference.Vision/Embeddings/.
@@ -61,6 +62,34 @@ class _ClipDual:
         return self._unit(torch.stack(feats)).cpu()
 
 
+class _VitEmbedder:
+    """A single-tower image embedder: SigLIP vision model or DINOv2."""
+    SIGLIP_MEAN_STD = ((0.5, 0.5, 0.5), (0.5, 0.5, 0.5))
+    IMAGENET_MEAN_STD = ((0.485, 0.456, 0.406), (0.229, 0.224, 0.225))
+
+    def __init__(self, path: str, raw: dict, device):
+        from ..models.encoders.vit import VitEncoder, vit_from_hf
+        vc = raw.get("vision_config", raw)
+        vc = {**vc, "model_type": "dinov2" if raw.get("model_type") == "dinov2" else "siglip"}
+        ck = ShardedCheckpoint(path)
+        self.enc = VitEncoder(vit_from_hf(vc), device, get=ck.get)
+        self.mean, self.std = self.IMAGENET_MEAN_STD if vc["model_type"] == "dinov2" else self.SIGLIP_MEAN_STD
+
+    def embed_images(self, images: list) -> torch.Tensor:
+        from ..models.encoders.clip_vision import CLIP_MEAN, CLIP_STD
+        size = self.enc.cfg.image_size
+        cm, cs = torch.tensor(CLIP_MEAN)[:, None, None], torch.tensor(CLIP_STD)[:, None, None]
+        m, sd = torch.tensor(self.mean)[:, None, None], torch.tensor(self.std)[:, None, None]
+        feats = []
+        for im in images:
+            x = preprocess_image(im, size) * cs + cm           # back to [0, 1], then this family's statistics
+            feats.append(self.enc.embed((x - m) / sd).float())
+        return _ClipDual._unit(torch.stack(feats)).cpu()
+
+    def embed_texts(self, texts):
+        raise ValueError("this checkpoint embeds images only")
+
+
 class VisionService:
     def __init__(self, device):
         self.device = device
@@ -78,7 +107,10 @@ class VisionService:
         path = spec.local_path or spec.requested
         with self._lock:
             if path not in self._loaded:
-                self._loaded[path] = _ClipDual(path, self.device)
+                raw = json.loads((Path(path) / "config.json").read_text())
+                mt = raw.get("model_type", "clip")
+                self._loaded[path] = (_VitEmbedder(path, raw, self.device) if mt in ("siglip", "siglip_vision_model", "dinov2")
+                                      else _ClipDual(path, self.device))
             return self._loaded[path]
 
     def run(self, spec: ModelSpec, req: VisionRequest) -> VisionResult:

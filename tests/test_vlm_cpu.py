@@ -230,3 +230,54 @@ def test_clip_tokenizer_and_vision_service(tmp_path):
     with pytest.raises(ValueError):
         eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="detect", images=imgs))
     eng.close()
+
+
+@pytest.mark.parametrize("kind", ["siglip", "dinov2"])
+def test_vit_embedders_match_transformers(kind):
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.encoders.vit import VitEncoder, tiny_vit, vit_from_hf
+    cfg = tiny_vit(kind)
+    torch.manual_seed(0)
+    if kind == "siglip":
+        hc = tr.SiglipVisionConfig(hidden_size=cfg.width, intermediate_size=cfg.ffn, num_hidden_layers=cfg.layers,
+                                   num_attention_heads=cfg.heads, image_size=cfg.image_size, patch_size=cfg.patch)
+        hf = tr.SiglipVisionModel(hc).eval()
+    else:
+        hc = tr.Dinov2Config(hidden_size=cfg.width, mlp_ratio=cfg.ffn // cfg.width, num_hidden_layers=cfg.layers,
+                             num_attention_heads=cfg.heads, image_size=cfg.image_size, patch_size=cfg.patch)
+        hf = tr.Dinov2Model(hc).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2 and "embeddings" not in n:
+                p.mul_(2.0)
+            if "lambda1" in n:
+                p.copy_(0.5 + torch.rand_like(p))
+    assert vit_from_hf(hc.to_dict()) == cfg
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    enc = VitEncoder(cfg, "cpu", get=lambda n: sd.get(n))
+    img = torch.randn(3, cfg.image_size, cfg.image_size, generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        out = hf(pixel_values=img[None])
+    cos = lambda a, b: torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0)
+    assert cos(enc.hidden_states(img), out.last_hidden_state[0]) > 0.995
+    assert cos(enc.embed(img), out.pooler_output[0]) > 0.995
+    if kind == "dinov2":
+        assert enc.embed(img, concat_patch_mean=True).shape == (2 * cfg.width,)
+
+
+def test_vision_service_loads_dinov2(tmp_path):
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, VisionRequest
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    hc = tr.Dinov2Config(hidden_size=128, mlp_ratio=2, num_hidden_layers=2, num_attention_heads=2, image_size=32, patch_size=8)
+    torch.manual_seed(0)
+    hf = tr.Dinov2Model(hc).eval()
+    save_hf_checkpoint(hc.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()}, tmp_path / "dino")
+    eng = InferenceEngine("cpu")
+    imgs = [torch.rand(3, 40, 40, generator=torch.Generator().manual_seed(i)) for i in range(2)]
+    res = eng.vision.run(ModelSpec(str(tmp_path / "dino")), VisionRequest(images=imgs))
+    assert res.image_embeddings.shape == (2, 128) and res.text_embeddings is None
+    assert torch.allclose(res.image_embeddings.norm(dim=-1), torch.ones(2), atol=1e-3)
+    with pytest.raises(ValueError):
+        eng.vision.run(ModelSpec(str(tmp_path / "dino")), VisionRequest(texts=["a"]))
+    eng.close()
