@@ -179,6 +179,23 @@ def transcribe(model, wav, language, task, no_timestamps, as_json, device):
 
 @cli.command()
 @click.argument("model")
+@click.argument("text")
+@click.option("--out", default="speech.wav")
+@click.option("--speed", default=None, type=float)
+@click.option("--device", default="auto")
+def speak(model, text, out, speed, device):
+    """Text to speech (VITS voices: MMS-TTS / Piper class) into a WAV file."""
+    from ..audio import write_wav
+    from ..engine.inference_engine import InferenceEngine
+    from ..engine.requests import SpeechRequest
+    eng = InferenceEngine(device)
+    res = eng.speech.run(ModelSpec(model, Modality.SPEECH, local_path=model), SpeechRequest(text=text, speed=speed))
+    write_wav(out, res.samples, res.sample_rate)
+    click.echo(f"{out}: {res.seconds:.2f} s at {res.sample_rate} Hz")
+
+
+@cli.command()
+@click.argument("model")
 @click.option("--image", "images", multiple=True, help="image file (repeatable)")
 @click.option("--text", "texts", multiple=True, help="caption to score against the images (repeatable)")
 @click.option("--device", default="auto")

@@ -14,6 +14,33 @@ from ..pipelines.whisper import TranscriptResult, WhisperOptions, WhisperPipelin
 from .requests import AudioRequest, ModelSpec
 
 
+class SpeechService:
+    """Text-to-speech: hosts VITS pipelines (MMS-TTS / Piper-class voices) by checkpoint path.
+    Reference: src/HartsyInference.Engine/Services/SpeechService.cs, ISpeechService.cs."""
+
+    def __init__(self, device):
+        self.device = device
+        self._lock = threading.Lock()
+        self._loaded: dict = {}
+
+    def loaded_keys(self) -> list[str]:
+        return [f"vits:{k}" for k in self._loaded]
+
+    def release(self) -> None:
+        with self._lock:
+            self._loaded.clear()
+
+    def run(self, spec: ModelSpec, req):
+        from ..pipelines.vits import VitsPipeline
+        path = spec.local_path or spec.requested
+        with self._lock:
+            if path not in self._loaded:
+                self._loaded[path] = VitsPipeline.from_pretrained(path, self.device)
+            pipe = self._loaded[path]
+        return pipe.speak(req.text, speaking_rate=req.speed, noise_scale=req.noise_scale,
+                          noise_scale_duration=req.noise_scale_duration)
+
+
 class TranscribeService:
     def __init__(self, device):
         self.device = device

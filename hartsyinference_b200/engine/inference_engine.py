@@ -52,7 +52,7 @@ def parse_backend_selector(selector: str) -> tuple[str, list[int]]:
 
 
 class InferenceEngine:
-    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION}
+    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH}
 
     def __init__(self, backend_selector: str = "auto", options: Optional[EngineOptions] = None):
         self.options = options or EngineOptions()
@@ -121,6 +121,11 @@ class InferenceEngine:
         return self._service("transcribe", lambda: TranscribeService(self.device))
 
     @property
+    def speech(self):
+        from .audio_service import SpeechService
+        return self._service("speech", lambda: SpeechService(self.device))
+
+    @property
     def vision(self):
         from .vision_service import VisionService
         return self._service("vision", lambda: VisionService(self.device))
@@ -129,7 +134,6 @@ class InferenceEngine:
         raise UnsupportedModelError(f"the {what} modality is not built in this engine yet")
 
     music = property(lambda self: self._unsupported("music"))
-    speech = property(lambda self: self._unsupported("speech"))
     voice_conversion = property(lambda self: self._unsupported("voice conversion"))
     fx = property(lambda self: self._unsupported("fx"))
     restore = property(lambda self: self._unsupported("restore"))

@@ -150,6 +150,16 @@ class AudioRequest:
 
 
 @dataclass
+class SpeechRequest:
+    """Text-to-speech input. ``speed`` > 1 talks faster; the noise scales default to the voice's own."""
+    text: str = ""
+    voice: Optional[str] = None
+    speed: Optional[float] = None
+    noise_scale: Optional[float] = None
+    noise_scale_duration: Optional[float] = None
+
+
+@dataclass
 class VisionRequest:
     """``operation``: "embed" (CLIP image / text features, and their similarity when both are given)."""
     operation: str = "embed"

@@ -24,6 +24,7 @@ from collections import defaultdict, deque
 from dataclasses import dataclass, field
 from typing import Optional
 
+import torch
 from fastapi import FastAPI, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
@@ -347,6 +348,27 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
                                   "avg_logprob": s.avg_logprob, "no_speech_prob": s.no_speech_prob}
                                  for i, s in enumerate(res.segments)])
         return out
+
+    @app.post("/v1/audio/speech")
+    async def audio_speech(request: Request):
+        from fastapi.responses import Response
+        from ..audio import write_wav
+        from ..engine.requests import SpeechRequest
+        body = await request.json()
+        text = body.get("input") or body.get("text") or ""
+        if not text.strip():
+            return JSONResponse({"error": {"message": "no input text", "type": "bad_request"}}, status_code=400)
+        fmt = body.get("response_format") or "wav"
+        if fmt not in ("wav", "pcm"):
+            return JSONResponse({"error": {"message": f"response_format '{fmt}' is not built (wav, pcm)", "type": "bad_request"}},
+                                status_code=400)
+        sreq = SpeechRequest(text=text, voice=body.get("voice"), speed=float(body["speed"]) if body.get("speed") else None)
+        with heavy_queue.slot():
+            res = eng.speech.run(resolve(body.get("model"), Modality.SPEECH), sreq)
+        if fmt == "pcm":
+            pcm = (res.samples.clamp(-1, 1) * 32767.0).round().to(torch.int16).numpy().tobytes()
+            return Response(pcm, media_type="audio/pcm", headers={"x-sample-rate": str(res.sample_rate)})
+        return Response(write_wav(None, res.samples, res.sample_rate), media_type="audio/wav")
 
     @app.post("/v1/native/vision")
     async def native_vision(request: Request):

@@ -198,3 +198,92 @@ def test_cli_transcribe_verb(tmp_path):
     write_wav(tmp_path / "b.wav", torch.randn(8000, generator=torch.Generator().manual_seed(7)) * 0.1, 8000)
     r = CliRunner().invoke(cli, ["transcribe", str(d), str(tmp_path / "b.wav"), "--language", "en", "--json", "--device", "cpu"])
     assert r.exit_code == 0, r.output
+
+
+def _vits_hf(stochastic=True):
+    tr = pytest.importorskip("transformers")
+    c = tr.VitsConfig(vocab_size=40, hidden_size=64, num_hidden_layers=2, num_attention_heads=2, ffn_dim=128, flow_size=64,
+                      spectrogram_bins=33, upsample_initial_channel=64, upsample_rates=[4, 4], upsample_kernel_sizes=[8, 8],
+                      resblock_kernel_sizes=[3, 5], resblock_dilation_sizes=[[1, 3], [1, 3]], prior_encoder_num_flows=2,
+                      prior_encoder_num_wavenet_layers=2, duration_predictor_num_flows=2, duration_predictor_filter_channels=32,
+                      depth_separable_num_layers=2, posterior_encoder_num_wavenet_layers=2, window_size=4,
+                      use_stochastic_duration_prediction=stochastic)
+    torch.manual_seed(0)
+    hf = tr.VitsModel(c).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2 and "emb_rel" not in n:
+                p.mul_(1.5)
+            if n.endswith("bias"):
+                p.add_(torch.randn_like(p) * 0.1)
+    return c, hf
+
+
+@pytest.mark.parametrize("stochastic", [True, False])
+def test_vits_matches_transformers(stochastic):
+    from hartsyinference_b200.models.audio.vits import VitsModel, tiny_vits, vits_from_hf
+    c, hf = _vits_hf(stochastic)
+    hf.noise_scale = hf.noise_scale_duration = 0.0        # both samplers off: the waveform is a function of the ids
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    cfg = vits_from_hf(c.to_dict())
+    assert cfg == tiny_vits(stochastic_duration=stochastic, sampling_rate=cfg.sampling_rate)
+    m = VitsModel(cfg, "cpu", get=lambda n: sd.get(n))
+    for seed, n in ((1, 13), (2, 3), (3, 30)):      # shorter and longer than the relative-attention window
+        ids = torch.randint(0, 40, (n,), generator=torch.Generator().manual_seed(seed))
+        with torch.no_grad():
+            ref = hf(input_ids=ids[None]).waveform[0]
+        mine = m.synthesize(ids, 0.0, 0.0)
+        assert mine.shape == ref.shape and mine.numel() % cfg.hop == 0
+        assert (mine - ref).abs().max() < 2e-3
+    slow = m.synthesize(ids, 0.0, 0.0, speaking_rate=0.5)
+    assert slow.numel() > mine.numel()
+    a, b = m.synthesize(ids), m.synthesize(ids)
+    assert a.abs().max() <= 1.0 and (a.shape != b.shape or not torch.equal(a, b))     # sampling is on by default
+
+
+def test_speech_service_endpoint_and_cli(tmp_path):
+    import json
+    from click.testing import CliRunner
+    from fastapi.testclient import TestClient
+    from hartsyinference_b200.cli.main import cli
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, SpeechRequest
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    from hartsyinference_b200.pipelines.vits import VitsCharTokenizer, VitsPipeline
+    from hartsyinference_b200.server.app import ServerOptions, create_app
+    c, hf = _vits_hf()
+    d = tmp_path / "voice"
+    save_hf_checkpoint(c.to_dict(), {k: v.detach().float().contiguous() for k, v in hf.state_dict().items()
+                                     if not k.startswith("posterior_encoder")}, d)
+    chars = "<pad> abcdefghijklmnopqrstuvwxyz.,!?'-"
+    vocab = {"<pad>": 0, **{ch: i + 1 for i, ch in enumerate(chars[5:])}}
+    (d / "vocab.json").write_text(json.dumps(vocab))
+    (d / "tokenizer_config.json").write_text(json.dumps({"add_blank": True, "normalize": True, "pad_token": "<pad>"}))
+    tok = VitsCharTokenizer.from_dir(d)
+    assert tok.encode("Ab") == [0, vocab["a"], 0, vocab["b"], 0] and tok.encode("#") == [0]
+
+    eng = InferenceEngine("cpu")
+    res = eng.speech.run(ModelSpec(str(d)), SpeechRequest(text="Hello there. How are you?", noise_scale=0.0, noise_scale_duration=0.0))
+    assert res.sample_rate == 16000 and res.samples.numel() > 0 and abs(res.seconds - res.samples.numel() / 16000) < 1e-6
+    pipe = eng.speech._loaded[str(d)]
+    assert isinstance(pipe, VitsPipeline) and "vits:" + str(d) in eng.loaded_pipeline_keys
+    pipe.max_chars = 12
+    assert pipe.split("Hello there. How are you? Fine.") == ["Hello there.", "How are you?", "Fine."]
+    assert all(len(x) <= 12 for x in pipe.split("a very long sentence without any punctuation at all"))
+    pipe.max_chars = 300
+    assert pipe.speak("###").samples.numel() == 0
+
+    app = create_app(ServerOptions(models={"voice": str(d)}), engine=eng)
+    with TestClient(app) as cl:
+        r = cl.post("/v1/audio/speech", json={"model": "voice", "input": "hi there", "voice": "default"})
+        assert r.status_code == 200 and r.headers["content-type"] == "audio/wav"
+        wav, rate = read_wav(r.content)
+        assert rate == 16000 and wav.shape[1] > 0
+        r = cl.post("/v1/audio/speech", json={"model": "voice", "input": "hi", "response_format": "pcm", "speed": 2.0})
+        assert r.status_code == 200 and len(r.content) % 2 == 0 and r.headers["x-sample-rate"] == "16000"
+        assert cl.post("/v1/audio/speech", json={"model": "voice", "input": " "}).status_code == 400
+        assert cl.post("/v1/audio/speech", json={"model": "voice", "input": "x", "response_format": "mp3"}).status_code == 400
+    eng.close()
+    out = tmp_path / "o.wav"
+    r = CliRunner().invoke(cli, ["speak", str(d), "hello", "--out", str(out), "--device", "cpu"])
+    assert r.exit_code == 0, r.output
+    assert read_wav(out)[1] == 16000
