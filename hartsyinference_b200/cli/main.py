@@ -179,6 +179,23 @@ def transcribe(model, wav, language, task, no_timestamps, as_json, device):
 
 @cli.command()
 @click.argument("model")
+@click.argument("image")
+@click.option("--out", default="upscaled.png")
+@click.option("--tile", default=128, help="input-space tile size (0 = whole image)")
+@click.option("--device", default="auto")
+def restore(model, image, out, tile, device):
+    """Upscale an image with a Real-ESRGAN checkpoint."""
+    from ..engine.inference_engine import InferenceEngine
+    from ..engine.requests import RestoreRequest
+    from ..utils.png import encode_png
+    eng = InferenceEngine(device)
+    res = eng.restore.run(ModelSpec(model, Modality.RESTORE, local_path=model), RestoreRequest(image=image, tile=tile))
+    Path(out).write_bytes(encode_png(res.rgb, res.width, res.height))
+    click.echo(f"{out}: {res.width}x{res.height}")
+
+
+@cli.command()
+@click.argument("model")
 @click.argument("text")
 @click.option("--out", default="speech.wav")
 @click.option("--speed", default=None, type=float)

@@ -52,7 +52,7 @@ def parse_backend_selector(selector: str) -> tuple[str, list[int]]:
 
 
 class InferenceEngine:
-    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH}
+    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH, Modality.RESTORE}
 
     def __init__(self, backend_selector: str = "auto", options: Optional[EngineOptions] = None):
         self.options = options or EngineOptions()
@@ -121,6 +121,11 @@ class InferenceEngine:
         return self._service("transcribe", lambda: TranscribeService(self.device))
 
     @property
+    def restore(self):
+        from .vision_service import RestoreService
+        return self._service("restore", lambda: RestoreService(self.device))
+
+    @property
     def speech(self):
         from .audio_service import SpeechService
         return self._service("speech", lambda: SpeechService(self.device))
@@ -136,7 +141,6 @@ class InferenceEngine:
     music = property(lambda self: self._unsupported("music"))
     voice_conversion = property(lambda self: self._unsupported("voice conversion"))
     fx = property(lambda self: self._unsupported("fx"))
-    restore = property(lambda self: self._unsupported("restore"))
     mesh = property(lambda self: self._unsupported("mesh"))
     world = property(lambda self: self._unsupported("world"))
 

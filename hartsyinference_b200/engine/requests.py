@@ -160,6 +160,15 @@ class SpeechRequest:
 
 
 @dataclass
+class RestoreRequest:
+    """``operation``: "upscale" (Real-ESRGAN). ``image``: path, PIL image, uint8 HWC array or float CHW tensor."""
+    operation: str = "upscale"
+    image: Optional[Any] = None
+    tile: int = 128                      # input-space tile size; 0 = whole image at once
+    tile_overlap: float = 0.25
+
+
+@dataclass
 class VisionRequest:
     """``operation``: "embed" (CLIP image / text features, and their similarity when both are given)."""
     operation: str = "embed"

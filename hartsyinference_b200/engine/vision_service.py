@@ -125,3 +125,68 @@ class VisionService:
         if req.images and req.texts:
             out.similarity = out.image_embeddings @ out.text_embeddings.t()
         return out
+
+
+class RestoreService:
+    """Image restoration: Real-ESRGAN upscaling from a ``.safetensors`` / ``.pth`` file or a directory
+    holding one. Reference: src/HartsyInference.Engine/Services/RestoreService.cs."""
+
+    def __init__(self, device):
+        self.device = device
+        self._lock = threading.Lock()
+        self._loaded: dict = {}
+
+    def loaded_keys(self) -> list[str]:
+        return [f"esrgan:{k}" for k in self._loaded]
+
+    def release(self) -> None:
+        with self._lock:
+            self._loaded.clear()
+
+    def _net(self, spec: ModelSpec):
+        from ..models.vision.rrdbnet import RrdbNet, detect_rrdb_config
+        path = spec.local_path or spec.requested
+        with self._lock:
+            if path not in self._loaded:
+                p = Path(path)
+                if p.is_dir():
+                    files = sorted(p.glob("*.safetensors")) + sorted(p.glob("*.pth"))
+                    if not files:
+                        raise ValueError(f"{path}: no .safetensors or .pth file")
+                    p = files[0]
+                if p.suffix == ".safetensors":
+                    from ..assets.safetensors import SafeTensorsFile
+                    f = SafeTensorsFile(p)
+                    tensors = {k: f.get(k) for k in f.keys()}
+                else:
+                    from ..assets.torch_checkpoint import load_torch_checkpoint
+                    tensors = load_torch_checkpoint(p)
+                dt = torch.bfloat16 if str(self.device).startswith("cuda") else torch.float32
+                self._loaded[path] = RrdbNet(detect_rrdb_config(tensors.keys()), self.device, dt, get=tensors.get)
+            return self._loaded[path]
+
+    def run(self, spec: ModelSpec, req):
+        from ..models.vision.rrdbnet import UpscalePipeline
+        if req.operation != "upscale":
+            raise ValueError(f"restore operation '{req.operation}' is not built (upscale is)")
+        if req.image is None:
+            raise ValueError("RestoreRequest.image is empty")
+        img = req.image
+        if not (isinstance(img, torch.Tensor) and img.is_floating_point()):
+            import numpy as np
+            if isinstance(img, (str, bytes)) or hasattr(img, "__fspath__"):
+                from PIL import Image
+                img = Image.open(img)
+            if hasattr(img, "convert"):
+                img = torch.from_numpy(np.asarray(img.convert("RGB")).copy())
+            img = torch.as_tensor(img)
+            if img.dtype == torch.uint8:
+                img = img.float() / 255.0
+            if img.ndim == 3 and img.shape[-1] == 3 and img.shape[0] != 3:
+                img = img.permute(2, 0, 1)
+        pipe = UpscalePipeline(self._net(spec), req.tile, req.tile_overlap)
+        up = pipe.upscale_tensor(img.float().clamp(0, 1))
+        from .requests import ImageResult
+        u8 = (up * 255.0).round().to(torch.uint8).permute(1, 2, 0).contiguous()
+        return ImageResult(rgb=u8.numpy().tobytes(), width=up.shape[2], height=up.shape[1], seed=0,
+                           meta={"operation": "upscale", "scale": pipe.net.scale})

@@ -370,6 +370,24 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
             return Response(pcm, media_type="audio/pcm", headers={"x-sample-rate": str(res.sample_rate)})
         return Response(write_wav(None, res.samples, res.sample_rate), media_type="audio/wav")
 
+    @app.post("/v1/native/restore")
+    async def native_restore(request: Request):
+        import io
+        from PIL import Image
+        from ..engine.requests import RestoreRequest
+        body = await request.json()
+        raw = body.get("image") or ""
+        if not raw:
+            return JSONResponse({"error": {"message": "no image", "type": "bad_request"}}, status_code=400)
+        b64 = raw.split(",", 1)[1] if raw.startswith("data:") else raw
+        img = Image.open(io.BytesIO(base64.b64decode(b64))).convert("RGB")
+        rreq = RestoreRequest(operation=body.get("operation", "upscale"), image=img, tile=int(body.get("tile", 128)),
+                              tile_overlap=float(body.get("tile_overlap", 0.25)))
+        with heavy_queue.slot():
+            res = eng.with_vram_cleanup(lambda: eng.restore.run(resolve(body.get("model"), Modality.RESTORE), rreq))
+        return {"width": res.width, "height": res.height, "meta": res.meta,
+                "png_base64": base64.b64encode(_png(res.rgb, res.width, res.height)).decode()}
+
     @app.post("/v1/native/vision")
     async def native_vision(request: Request):
         import base64
