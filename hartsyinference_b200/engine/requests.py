@@ -170,7 +170,8 @@ class RestoreRequest:
 
 @dataclass
 class VisionRequest:
-    """``operation``: "embed" (CLIP image / text features, and their similarity when both are given)."""
+    """``operation``: "embed" (CLIP / SigLIP / DINOv2 image features, CLIP text features and their
+    similarity when both are given) or "depth" (Depth Anything; one map per image)."""
     operation: str = "embed"
     images: list = field(default_factory=list)
     texts: list[str] = field(default_factory=list)
@@ -181,6 +182,7 @@ class VisionResult:
     image_embeddings: Optional[Any] = None     # [n_images, dim], L2-normalised
     text_embeddings: Optional[Any] = None      # [n_texts, dim]
     similarity: Optional[Any] = None           # [n_images, n_texts] cosine
+    depth: Optional[list] = None               # per image: float32 [H, W] at the image's own size
 
 
 @dataclass

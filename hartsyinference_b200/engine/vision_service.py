@@ -90,6 +90,37 @@ class _VitEmbedder:
         raise ValueError("this checkpoint embeds images only")
 
 
+class _DepthEstimator:
+    def __init__(self, path: str, raw: dict, device):
+        from ..models.vision.depth_anything import DepthAnything, depth_anything_from_hf
+        self.model = DepthAnything(depth_anything_from_hf(raw), device, get=ShardedCheckpoint(path).get)
+
+    def depth(self, images: list, short_side: int = 518) -> list:
+        import numpy as np
+        P = self.model.cfg.backbone.patch
+        mean = torch.tensor(_VitEmbedder.IMAGENET_MEAN_STD[0])[:, None, None]
+        std = torch.tensor(_VitEmbedder.IMAGENET_MEAN_STD[1])[:, None, None]
+        out = []
+        for im in images:
+            if isinstance(im, (str, bytes)) or hasattr(im, "__fspath__"):
+                from PIL import Image
+                im = Image.open(im)
+            if hasattr(im, "convert"):
+                im = torch.from_numpy(np.asarray(im.convert("RGB")).copy())
+            t = torch.as_tensor(im)
+            if t.dtype == torch.uint8:
+                t = t.float() / 255.0
+            if t.ndim == 3 and t.shape[-1] == 3 and t.shape[0] != 3:
+                t = t.permute(2, 0, 1)
+            _, h, w = t.shape
+            s = short_side / min(h, w)
+            nh, nw = max(P, round(h * s / P) * P), max(P, round(w * s / P) * P)      # both sides multiples of the patch
+            x = torch.nn.functional.interpolate(t.float()[None], size=(nh, nw), mode="bicubic", align_corners=False)[0].clamp(0, 1)
+            d = self.model.predict((x - mean) / std)
+            out.append(torch.nn.functional.interpolate(d[None, None].float().cpu(), size=(h, w), mode="bilinear", align_corners=False)[0, 0])
+        return out
+
+
 class VisionService:
     def __init__(self, device):
         self.device = device
@@ -109,15 +140,26 @@ class VisionService:
             if path not in self._loaded:
                 raw = json.loads((Path(path) / "config.json").read_text())
                 mt = raw.get("model_type", "clip")
-                self._loaded[path] = (_VitEmbedder(path, raw, self.device) if mt in ("siglip", "siglip_vision_model", "dinov2")
-                                      else _ClipDual(path, self.device))
+                if mt == "depth_anything":
+                    self._loaded[path] = _DepthEstimator(path, raw, self.device)
+                elif mt in ("siglip", "siglip_vision_model", "dinov2"):
+                    self._loaded[path] = _VitEmbedder(path, raw, self.device)
+                else:
+                    self._loaded[path] = _ClipDual(path, self.device)
             return self._loaded[path]
 
     def run(self, spec: ModelSpec, req: VisionRequest) -> VisionResult:
-        if req.operation != "embed":
-            raise ValueError(f"vision operation '{req.operation}' is not built (embed is)")
+        if req.operation not in ("embed", "depth"):
+            raise ValueError(f"vision operation '{req.operation}' is not built (embed and depth are)")
         m = self._model(spec)
         out = VisionResult()
+        if req.operation == "depth":
+            if not isinstance(m, _DepthEstimator):
+                raise ValueError("this checkpoint is not a depth estimator")
+            out.depth = m.depth(req.images, getattr(req, "short_side", 518))
+            return out
+        if isinstance(m, _DepthEstimator):
+            raise ValueError("this checkpoint estimates depth; use operation 'depth'")
         if req.images:
             out.image_embeddings = m.embed_images(req.images)
         if req.texts:

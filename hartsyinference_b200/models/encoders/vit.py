@@ -116,17 +116,35 @@ class VitEncoder:
         x = image.reshape(c, h // P, P, w // P, P).permute(1, 3, 0, 2, 4).reshape((h // P) * (w // P), c * P * P)
         return torch.nn.functional.pad(x, (0, self.k_pad - c * P * P))
 
+    def _positions(self, gh: int, gw: int) -> torch.Tensor:
+        """Position table for a gh x gw patch grid: the stored one, or (for another image size) its
+        patch part resampled bicubically, the class position kept."""
+        n0 = int(round(self.cfg.num_patches ** 0.5))
+        if (gh, gw) == (n0, n0):
+            return self.pos
+        extra = 0 if self.cls is None else 1
+        grid = self.pos[extra:].float().reshape(1, n0, n0, -1).permute(0, 3, 1, 2)
+        grid = torch.nn.functional.interpolate(grid, size=(gh, gw), mode="bicubic", align_corners=False)
+        grid = grid.permute(0, 2, 3, 1).reshape(gh * gw, -1).to(self.pos.dtype)
+        return torch.cat([self.pos[:extra], grid], 0)
+
     @torch.no_grad()
-    def hidden_states(self, image: torch.Tensor, layer: int = -1, final_norm: bool = True) -> torch.Tensor:
-        """image [3, H, W] normalised -> token states [(1 +) num_patches, W] after block ``layer``."""
+    def hidden_states(self, image: torch.Tensor, layer: int = -1, final_norm: bool = True, taps: Optional[list] = None):
+        """image [3, H, W] normalised -> token states [(1 +) num_patches, W] after block ``layer``.
+        With ``taps`` (1-based block counts) returns the final-normed states after each of those
+        blocks instead (what dense-prediction heads consume)."""
         cfg, dt = self.cfg, torch.bfloat16
         x = ops.linear(self._patchify(image.to(self.device).float()).to(dt).contiguous(), self.patch)
         if self.cls is not None:
             x = torch.cat([self.cls.to(dt)[None], x], 0)
-        x = (x.float() + self.pos[: x.shape[0]].float()).to(dt)
+        pos = self._positions(image.shape[-2] // cfg.patch, image.shape[-1] // cfg.patch)
+        x = (x.float() + pos[: x.shape[0]].float()).to(dt)
         L, d = x.shape[0], cfg.width // cfg.heads
         last = cfg.layers + layer + 1 if layer < 0 else layer
-        for b in self.blocks[:last]:
+        if taps:
+            last = max(taps)
+        tapped = []
+        for bi, b in enumerate(self.blocks[:last]):
             q, k, v = ops.dit_qkv(ops.linear(self._ln(x, b["n1"]), b["qkv"]), cfg.heads, cfg.heads, d)
             a = ops.linear(ops.attention(q, k, v, causal=False).reshape(L, -1), b["o"])
             if "ls1" in b:
@@ -136,6 +154,10 @@ class VitEncoder:
             if "ls2" in b:
                 m = (m.float() * b["ls2"].float()).to(dt)
             x = (x.float() + m.float()).to(dt)
+            if taps and bi + 1 in taps:
+                tapped.append(self._ln(x, self.final))
+        if taps:
+            return tapped
         return self._ln(x, self.final) if (final_norm and last == cfg.layers) else x
 
     @torch.no_grad()

@@ -402,6 +402,19 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
         vreq = VisionRequest(operation=body.get("operation", "embed"), images=images, texts=list(body.get("texts") or []))
         with heavy_queue.slot():
             res = eng.vision.run(resolve(body.get("model"), Modality.VISION), vreq)
+        if res.depth is not None:
+            # 16-bit grayscale PNGs, each map scaled to its own maximum
+            import io
+            import numpy as np
+            from PIL import Image
+            maps = []
+            for d in res.depth:
+                a = (d / d.max().clamp_min(1e-12) * 65535.0).round().numpy().astype(np.uint16)
+                buf = io.BytesIO()
+                Image.fromarray(a).save(buf, format="PNG")
+                maps.append({"width": int(d.shape[1]), "height": int(d.shape[0]), "max": float(d.max()),
+                             "png16_base64": base64.b64encode(buf.getvalue()).decode()})
+            return {"depth": maps}
         return {k: (v.tolist() if v is not None else None)
                 for k, v in (("image_embeddings", res.image_embeddings), ("text_embeddings", res.text_embeddings),
                              ("similarity", res.similarity))}

@@ -281,3 +281,52 @@ def test_vision_service_loads_dinov2(tmp_path):
     with pytest.raises(ValueError):
         eng.vision.run(ModelSpec(str(tmp_path / "dino")), VisionRequest(texts=["a"]))
     eng.close()
+
+
+def test_depth_anything_matches_transformers_and_serves(tmp_path):
+    tr = pytest.importorskip("transformers")
+    import base64
+    import io
+    from fastapi.testclient import TestClient
+    from PIL import Image
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, VisionRequest
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    from hartsyinference_b200.models.vision.depth_anything import DepthAnything, depth_anything_from_hf
+    from hartsyinference_b200.server.app import ServerOptions, create_app
+    bc = tr.Dinov2Config(hidden_size=128, num_hidden_layers=4, num_attention_heads=2, image_size=28, patch_size=14, mlp_ratio=2,
+                         out_indices=[1, 2, 3, 4], reshape_hidden_states=False, apply_layernorm=True)
+    c = tr.DepthAnythingConfig(backbone_config=bc, reassemble_hidden_size=128, neck_hidden_sizes=[16, 32, 64, 64],
+                               fusion_hidden_size=32, head_hidden_size=16, patch_size=14, reassemble_factors=[4, 2, 1, 0.5])
+    torch.manual_seed(0)
+    hf = tr.DepthAnythingForDepthEstimation(c).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2 and "embeddings" not in n:
+                p.mul_(2.0)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    m = DepthAnything(depth_anything_from_hf(c.to_dict()), "cpu", get=lambda n: sd.get(n))
+    for hw in ((28, 28), (42, 56)):          # the second size resamples the position table
+        img = torch.randn(3, *hw, generator=torch.Generator().manual_seed(1))
+        with torch.no_grad():
+            ref = hf(pixel_values=img[None]).predicted_depth[0]
+        mine = m.predict(img)
+        assert mine.shape == ref.shape
+        assert torch.nn.functional.cosine_similarity(ref.flatten(), mine.flatten(), dim=0) > 0.999
+
+    d = tmp_path / "depth"
+    save_hf_checkpoint(c.to_dict(), {k: v.to(torch.bfloat16).contiguous() for k, v in sd.items()}, d)
+    eng = InferenceEngine("cpu")
+    pic = (torch.rand(30, 45, 3, generator=torch.Generator().manual_seed(2)) * 255).to(torch.uint8)
+    res = eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="depth", images=[pic]))
+    assert len(res.depth) == 1 and res.depth[0].shape == (30, 45) and res.depth[0].min() >= 0
+    with pytest.raises(ValueError):
+        eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="embed", images=[pic]))
+    buf = io.BytesIO()
+    Image.fromarray(pic.numpy()).save(buf, format="PNG")
+    with TestClient(create_app(ServerOptions(models={"depth": str(d)}), engine=eng)) as cl:
+        r = cl.post("/v1/native/vision", json={"model": "depth", "operation": "depth", "images": [base64.b64encode(buf.getvalue()).decode()]})
+        assert r.status_code == 200, r.text
+        j = r.json()["depth"][0]
+        assert (j["width"], j["height"]) == (45, 30)
+        assert Image.open(io.BytesIO(base64.b64decode(j["png16_base64"]))).size == (45, 30)
+    eng.close()
