@@ -1,4 +1,5 @@
 """LoRA merge, family detection, extra schedulers and the first-block cache (CPU)."""
+import pytest
 import torch
 
 from hartsyinference_b200.assets import lora as L
@@ -279,3 +280,29 @@ def test_block_streamer_walks_blocks_with_two_slots():
     assert s.uploads >= 9            # every block fetched again on the second pass (two slots only)
     s.evict_all()
     assert not s._resident
+
+
+@pytest.mark.parametrize("groups", [1, 2])
+def test_mamba2_matches_transformers_and_state_carries_over(groups):
+    transformers = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.ssm import Mamba2Model, mamba2_from_hf
+    c = transformers.Mamba2Config(vocab_size=256, hidden_size=64, num_hidden_layers=2, state_size=16, num_heads=8, head_dim=16,
+                                  n_groups=groups, expand=2, conv_kernel=4, chunk_size=8, eos_token_id=0, bos_token_id=1, pad_token_id=0)
+    torch.manual_seed(0)
+    hf = transformers.Mamba2ForCausalLM(c).eval()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.ndim >= 2:
+                p.mul_(3.0)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    m = Mamba2Model(mamba2_from_hf(c.to_dict()), "cpu", get=lambda n: sd.get(n))
+    ids = torch.randint(0, 256, (21,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(ids[None]).logits[0]
+    st = m.new_state()
+    # a prompt, one decode step and a multi-token continuation all run on the carried state
+    mine = torch.cat([m.logits(m.forward(ids[:13], st)), m.logits(m.forward(ids[13:14], st)), m.logits(m.forward(ids[14:], st))])
+    assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0) > 0.999
+    assert (mine.argmax(-1) == ref.argmax(-1)).float().mean() > 0.9
+    out = m.generate(ids[:5].tolist(), max_tokens=4, stop_at_eos=False)
+    assert len(out) == 4

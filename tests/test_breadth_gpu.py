@@ -100,3 +100,14 @@ def test_architecture_on_device_matches_cpu(name, tmp_path):
         outs.append(m.logits(m.forward_hidden(b)).float().cpu())
     cos = torch.nn.functional.cosine_similarity(outs[0].flatten(), outs[1].flatten(), dim=0)
     assert cos > 0.99, f"{name}: cos {cos:.4f}"
+
+
+def test_mamba2_on_device_matches_cpu():
+    from hartsyinference_b200.models.ssm import Mamba2Model, tiny_mamba2
+    cfg = tiny_mamba2(n_groups=2)
+    cpu, gpu = Mamba2Model(cfg, "cpu", seed=3), Mamba2Model(cfg, "cuda", seed=3)
+    ids = torch.randint(0, 256, (19,), generator=torch.Generator().manual_seed(1))
+    sa, sb = cpu.new_state(), gpu.new_state()
+    la = torch.cat([cpu.logits(cpu.forward(ids[:12], sa)), cpu.logits(cpu.forward(ids[12:], sa))])
+    lb = torch.cat([gpu.logits(gpu.forward(ids[:12], sb)), gpu.logits(gpu.forward(ids[12:], sb))]).cpu()
+    assert torch.nn.functional.cosine_similarity(la.flatten(), lb.flatten(), dim=0) > 0.99
