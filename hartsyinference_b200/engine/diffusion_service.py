@@ -45,6 +45,14 @@ class ImagesService(_PipelineCache):
         from ..pipelines.flux import FluxComponents, FluxPipeline
         name = spec.requested
         fp8 = bool(config.get("fp8_linears")) and self.device.startswith("cuda")
+        if name.startswith("synthetic:sd3"):
+            from ..models.dit import sd3 as S3
+            from ..pipelines.sd3 import SD3_VAE, Sd3Components, Sd3Pipeline
+            tiny = name.endswith("-tiny")
+            cfg3 = S3.tiny_sd3() if tiny else S3.SD3_MEDIUM
+            dt = torch.bfloat16 if self.device.startswith("cuda") else torch.float32
+            vae = Vae2dDecoder(tiny_vae2d() if tiny else SD3_VAE, self.device, dt)
+            return Sd3Pipeline(Sd3Components(S3.Sd3Transformer(cfg3, self.device, fp8=fp8 and not tiny), vae))
         if name.startswith("synthetic:"):
             tiny = name.endswith("-tiny")
             cfg = F.tiny_flux() if tiny else F.FLUX_DEV
@@ -59,6 +67,17 @@ class ImagesService(_PipelineCache):
         if not path.exists():
             raise UnsupportedModelError(f"{name}: no such checkpoint")
         ck = ShardedCheckpoint(path / "transformer" if (path / "transformer").exists() else path)
+        if ck.get("pos_embed.pos_embed") is not None and ck.get("transformer_blocks.0.norm1_context.linear.weight") is not None:
+            # an SD3 / SD3.5 MMDiT (diffusers layout)
+            import json as _json
+            from ..models.dit import sd3 as S3
+            from ..pipelines.sd3 import SD3_VAE, Sd3Components, Sd3Pipeline
+            tdir = path / "transformer" if (path / "transformer").exists() else path
+            cfg3 = S3.sd3_from_hf(_json.loads((tdir / "config.json").read_text())) if (tdir / "config.json").exists() else S3.SD3_MEDIUM
+            vae = None
+            if "vae" in spec.aux or (path / "vae").exists():
+                vae = Vae2dDecoder(SD3_VAE, self.device, get=ShardedCheckpoint(spec.aux.get("vae", path / "vae")).get)
+            return Sd3Pipeline(Sd3Components(S3.Sd3Transformer(cfg3, self.device, fp8=fp8, get=ck.get), vae))
         get = ck.get
         from ..assets.converters import flux_original_to_diffusers, is_flux_original
         if is_flux_original(ck.keys()):

@@ -111,3 +111,17 @@ def test_mamba2_on_device_matches_cpu():
     la = torch.cat([cpu.logits(cpu.forward(ids[:12], sa)), cpu.logits(cpu.forward(ids[12:], sa))])
     lb = torch.cat([gpu.logits(gpu.forward(ids[:12], sb)), gpu.logits(gpu.forward(ids[12:], sb))]).cpu()
     assert torch.nn.functional.cosine_similarity(la.flatten(), lb.flatten(), dim=0) > 0.99
+
+
+def test_sd3_transformer_on_device_matches_cpu():
+    from hartsyinference_b200.models.dit.sd3 import Sd3Transformer, tiny_sd3
+    cfg = tiny_sd3(qk_norm=True)
+    cpu, gpu = Sd3Transformer(cfg, "cpu", seed=2), Sd3Transformer(cfg, "cuda", seed=2)
+    g = torch.Generator().manual_seed(1)
+    lat = torch.randn(1, cfg.in_channels, 16, 16, generator=g)
+    txt = torch.randn(1, 24, cfg.context_dim, generator=g)
+    pooled = torch.randn(1, cfg.pooled_dim, generator=g)
+    sigma = torch.tensor([0.4])
+    a = cpu.forward(lat, txt, sigma, pooled).float()
+    b = gpu.forward(lat, txt, sigma, pooled).float().cpu()
+    assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.99
