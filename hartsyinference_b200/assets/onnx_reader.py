@@ -7,7 +7,6 @@ detector checkpoints).
 """
 from __future__ import annotations
 
-import struct
 from pathlib import Path
 from typing import Iterator
 

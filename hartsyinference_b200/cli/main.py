@@ -8,7 +8,6 @@ under ``torchrun --nproc-per-node N``.
 from __future__ import annotations
 
 import json
-import sys
 from pathlib import Path
 
 import click

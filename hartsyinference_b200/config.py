@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass
-from typing import Any, Callable
+from typing import Any
 
 _FALSE = {"0", "false", "off", "no", ""}
 

@@ -108,7 +108,7 @@ class ImagesService(_PipelineCache):
 class VideoService(_PipelineCache):
     def _build(self, spec: ModelSpec):
         from ..models.dit import wan as W
-        from ..models.vae.vae3d import WAN_VAE, Vae3dDecoder, tiny_vae3d
+        from ..models.vae.vae3d import WAN_VAE, Vae3dDecoder
         from ..pipelines.wan import WanComponents, WanPipeline
         name = spec.requested
         fp8 = bool(config.get("fp8_linears")) and self.device.startswith("cuda")

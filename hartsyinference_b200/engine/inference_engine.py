@@ -19,7 +19,7 @@ import torch
 
 from .. import log
 from ..exceptions import OutOfVramError, UnsupportedBackendError, UnsupportedModelError
-from .gates import DeviceGate, InferenceQueue
+from .gates import DeviceGate
 from .requests import EngineOptions, Modality
 
 T = TypeVar("T")

@@ -22,7 +22,7 @@ from typing import Callable, Optional, Sequence
 import torch
 
 from .. import config, log, ops
-from ..exceptions import HartsyInferenceError, KvPoolExhaustedError
+from ..exceptions import HartsyInferenceError
 from ..models.llm.transformer import DecoderModel, ForwardBatch
 from ..ops import _native as N
 from ..runtime import KvAllocator, SchedulerCore
@@ -200,9 +200,8 @@ class LLMEngine:
         embeds = None
         if any(self.requests[rid].embeds is not None for rid, _, _ in chunks):
             # token embeddings first, then the rows that come from images are overwritten
-            from .. import ops as _ops
             cfgm = self.model.cfg
-            embeds = _ops.embedding(self._to_device(self.h_tokens, t), self.model.embed,
+            embeds = ops.embedding(self._to_device(self.h_tokens, t), self.model.embed,
                                     cfgm.embed_scale * cfgm.embedding_multiplier)
             t0 = 0
             for rid, start, count in chunks:

@@ -8,7 +8,7 @@ logits; only the chosen ids are read back.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Optional, Sequence
 
 import torch

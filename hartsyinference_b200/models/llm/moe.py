@@ -19,7 +19,7 @@ for the shared expert and the leading dense layers.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Optional
 
 import torch
@@ -27,7 +27,7 @@ import torch
 from ... import ops
 from ...ops import LinearWeight
 from ...ops import reference as R
-from .config import MoeConfig, TransformerConfig
+from .config import TransformerConfig
 
 _CHUNK = 1024        # tokens per pass: up to 8 runs of 128 tokens share one read of the expert weights
 

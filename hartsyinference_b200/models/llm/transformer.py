@@ -20,7 +20,7 @@ Layer dataflow (one launch per arrow, residual adds folded into the norm kernel)
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Optional
 
 import torch

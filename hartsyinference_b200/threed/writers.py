@@ -8,7 +8,6 @@ from __future__ import annotations
 import json
 import struct
 from pathlib import Path
-from typing import Optional
 
 import numpy as np
 import torch
