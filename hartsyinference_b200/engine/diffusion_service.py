@@ -62,7 +62,15 @@ class ImagesService(_PipelineCache):
             if tiny:   # the tiny DiT packs 4 latent channels
                 assert cfg.in_channels == 16
             enc = Vae2dEncoder(tiny_vae2d() if tiny else FLUX_VAE, self.device, vae.dtype)
-            return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc))
+            cnet = None
+        if "controlnet" in spec.aux:
+            import json as _json
+            from ..models.dit.flux_controlnet import FluxControlNet
+            cdir = Path(spec.aux["controlnet"])
+            cc = _json.loads((cdir / "config.json").read_text()) if (cdir / "config.json").exists() else {}
+            ccfg = F.FluxConfig(num_double_blocks=int(cc.get("num_layers", 5)), num_single_blocks=int(cc.get("num_single_layers", 10)))
+            cnet = FluxControlNet(ccfg, self.device, fp8=fp8, get=ShardedCheckpoint(cdir).get)
+        return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc, controlnet=cnet))
         path = Path(spec.local_path or name)
         if not path.exists():
             raise UnsupportedModelError(f"{name}: no such checkpoint")

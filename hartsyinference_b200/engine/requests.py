@@ -134,6 +134,8 @@ class ImageRequest:
     batch: int = 1
     init_image: Optional[Any] = None
     mask_image: Optional[Any] = None     # white = repaint (inpainting; needs init_image)
+    control_image: Optional[Any] = None  # ControlNet conditioning image (needs a ControlNet beside the model)
+    control_strength: float = 1.0
     strength: float = 1.0
     loras: list[tuple[str, float]] = field(default_factory=list)
     step_cache_threshold: float = 0.0

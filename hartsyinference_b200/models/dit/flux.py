@@ -79,8 +79,9 @@ class _SingleWeights:
 class FluxTransformer:
     def __init__(self, cfg: FluxConfig = FLUX_DEV, device="cpu", comm: Optional[Comm] = None, fp8: bool = False,
                  get: Optional[Callable[[str], Optional[torch.Tensor]]] = None, seed: int = 0,
-                 block_range: Optional[tuple[int, int]] = None):
+                 block_range: Optional[tuple[int, int]] = None, build_head: bool = True):
         self.cfg = cfg
+        self.has_head = build_head
         self.device = torch.device(device)
         self.comm = comm or SingleComm()
         self.tp, self.tp_rank = self.comm.world, self.comm.rank
@@ -130,7 +131,7 @@ class FluxTransformer:
                 continue
             p = f"single_transformer_blocks.{i}."
             self.single.append(self._single(f, p))
-        if last:
+        if last and build_head:
             self.norm_out = f.linear("norm_out.linear", 2 * H, H)
             self.proj_out = f.linear("proj_out", cfg.in_channels, H)
 
@@ -223,12 +224,17 @@ class FluxTransformer:
 
     def forward(self, img: torch.Tensor, txt: torch.Tensor, timestep: torch.Tensor, pooled: torch.Tensor,
                 img_ids: torch.Tensor, txt_ids: torch.Tensor, guidance: Optional[torch.Tensor] = None,
-                hidden_in: Optional[tuple] = None, step_cache=None):
+                hidden_in: Optional[tuple] = None, step_cache=None, control: Optional[tuple] = None,
+                collect: Optional[tuple] = None):
         """img [B, S_i, C_in] packed latents, txt [B, S_t, context_dim], timestep (sigma) [B],
         pooled [B, pooled_dim], ids [S, 3]. Returns the velocity prediction [B, S_i, C_in] (bf16), or
         the (img, txt | joint) hidden state when this instance holds only a block range.
         ``step_cache`` (a :class:`~.step_cache.FirstBlockCache`, whole-model instances only): after the
-        first block decide whether the rest of the stack can be replaced by last step's residual."""
+        first block decide whether the rest of the stack can be replaced by last step's residual.
+        ``control`` = (double residuals, single residuals): lists of [B * S_i, H] tensors from a
+        ControlNet, added to the image stream after the blocks they map to (one residual covers
+        ceil(blocks / residuals) consecutive blocks). ``collect`` = (list, list): filled with the image
+        stream after every double / single block (what a ControlNet branch projects)."""
         cfg = self.cfg
         B, S_i = img.shape[0], img.shape[1]
         S_t = txt.shape[1]
@@ -287,6 +293,11 @@ class FluxTransformer:
                 a_i = torch.cat([att[i * S + S_t:(i + 1) * S] for i in range(B)], 0)
             x_i = stream_post(x_i, a_i.contiguous(), wi, mod_i, S_i)
             x_t = stream_post(x_t, a_t.contiguous(), wt, mod_t, S_t)
+            if collect is not None:
+                collect[0].append(x_i)
+            if control is not None and control[0]:
+                every = -(-cfg.num_double_blocks // len(control[0]))
+                x_i = (x_i.float() + control[0][(self.block_range[0] + bi) // every].float()).to(dt)
             if use_cache and bi == 0:
                 first_x_i = x_i
                 if not step_cache.should_compute(x_i):
@@ -302,7 +313,7 @@ class FluxTransformer:
                     joint = torch.cat([torch.cat([x_t[i * S_t:(i + 1) * S_t], x_i[i * S_i:(i + 1) * S_i]], 0) for i in range(B)], 0)
             cj, sj = (cos, sin) if B == 1 else (cos.repeat(B, 1), sin.repeat(B, 1))
             qkv_cols = 3 * self.hl * D
-            for w in self._blocks(self.single, "single"):
+            for si, w in enumerate(self._blocks(self.single, "single")):
                 mod = modulation(temb_act, w.mod)
                 xn, _, xq = ops.norm(joint, None, shift=mod[:, 0:H], scale=mod[:, H:2 * H], rows_per_batch=S, layernorm=True,
                                      emit_fp8=self.fp8 and w.qkv_mlp.is_fp8, emit_bf16=not (self.fp8 and w.qkv_mlp.is_fp8))
@@ -313,12 +324,22 @@ class FluxTransformer:
                 mlp = torch.nn.functional.gelu(fused[:, qkv_cols:].float(), approximate="tanh").to(dt)
                 y = self._reduce(ops.linear(torch.cat([att, mlp], 1), w.out))
                 joint = self._gated_add(joint, y, mod[:, 2 * H:3 * H], S)
+                if collect is not None or (control is not None and control[1]):
+                    img_rows = slice(S_t, S) if B == 1 else None
+                    if img_rows is None:
+                        raise ValueError("ControlNet residuals on the single blocks need batch 1")
+                    if collect is not None:
+                        collect[1].append(joint[img_rows])
+                    if control is not None and control[1]:
+                        every = -(-cfg.num_single_blocks // len(control[1]))
+                        joint = joint.clone()
+                        joint[img_rows] = (joint[img_rows].float() + control[1][si // every].float()).to(dt)
             if self.block_range[1] == cfg.num_double_blocks + cfg.num_single_blocks:
                 if B == 1:
                     x_i = joint[S_t:]
                 else:
                     x_i = torch.cat([joint[i * S + S_t:(i + 1) * S] for i in range(B)], 0)
-        if self.block_range[1] != cfg.num_double_blocks + cfg.num_single_blocks:
+        if self.block_range[1] != cfg.num_double_blocks + cfg.num_single_blocks or not self.has_head:
             return x_i, x_t, joint
         if use_cache and not skip_rest:
             step_cache.store_residual(first_x_i, x_i)

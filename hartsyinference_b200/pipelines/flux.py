@@ -45,6 +45,7 @@ class FluxComponents:
     t5: Optional[object] = None
     clip: Optional[object] = None
     vae_encoder: Optional[object] = None      # Vae2dEncoder: img2img / inpainting start from an encoded image
+    controlnet: Optional[object] = None       # FluxControlNet: residuals from a control image's latents
     t5_tokenizer: Optional[object] = None
     clip_tokenizer: Optional[object] = None
 
@@ -80,7 +81,8 @@ class FluxPipeline:
                 seed: int, neg: Optional[tuple[torch.Tensor, torch.Tensor]] = None, cfg_scale: float = 1.0,
                 on_step: Optional[Callable[[StepPreview], None]] = None, step_cache_threshold: float = 0.0, first_block_cache: float = 0.0,
                 latents: Optional[torch.Tensor] = None, init_latents: Optional[torch.Tensor] = None, strength: float = 1.0,
-                mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+                mask: Optional[torch.Tensor] = None, control_latents: Optional[torch.Tensor] = None,
+                control_strength: float = 1.0) -> torch.Tensor:
         """Returns the final latents [1, C, H/8, W/8] fp32 on the device.
 
         ``init_latents`` [1, C, H/8, W/8] with ``strength`` < 1 starts from the image noised to the
@@ -97,6 +99,9 @@ class FluxPipeline:
         S = x.shape[1]
         img_ids, txt_ids = flux_ids(lh // 2, lw // 2, ctx.shape[0], dev)
         sched = FlowMatchEulerScheduler(steps, mu=flux_mu(S))
+        ctrl_packed = None
+        if control_latents is not None and self.c.controlnet is not None:
+            ctrl_packed = pack_latents(control_latents.float()).to(dev).to(torch.bfloat16).contiguous()
         first_step = 0
         init_packed = noise_packed = mask_packed = None
         if init_latents is not None:
@@ -143,13 +148,17 @@ class FluxPipeline:
                 v_cond, v_unc = cache_v, None
             else:
                 xin = x.to(torch.bfloat16)
+                ctl = None
+                if ctrl_packed is not None:      # the ControlNet branch sees the conditional prompt
+                    ctl = self.c.controlnet.residuals(xin, ctrl_packed, ctx_d, sigma, pooled_d, img_ids, txt_ids, gvec, control_strength)
                 if branch is None:
-                    v_cond = tr.forward(xin, ctx_d, sigma, pooled_d, img_ids, txt_ids, gvec, step_cache=fbc[0])
+                    v_cond = tr.forward(xin, ctx_d, sigma, pooled_d, img_ids, txt_ids, gvec, step_cache=fbc[0], control=ctl)
                     v_unc = tr.forward(xin, neg[0].to(dev)[None], sigma, neg[1].to(dev)[None], img_ids, txt_ids, gvec,
                                        step_cache=fbc[1]) if true_cfg else None
                 else:
                     c_in, p_in = (ctx_d, pooled_d) if branch == 0 else (neg[0].to(dev)[None], neg[1].to(dev)[None])
-                    mine = tr.forward(xin, c_in, sigma, p_in, img_ids, txt_ids, gvec, step_cache=fbc[0]).contiguous()
+                    mine = tr.forward(xin, c_in, sigma, p_in, img_ids, txt_ids, gvec, step_cache=fbc[0],
+                                      control=ctl if branch == 0 else None).contiguous()
                     if fused_cfg is not None:
                         fused_cfg.step(x, mine, cfg_scale, sched.dt(i))
                         v_cond = None
@@ -231,8 +240,14 @@ class FluxPipeline:
             if getattr(req, "mask_image", None) is not None:
                 m = self._image_tensor(req.mask_image, req.width, req.height)[:, :1] * 0.5 + 0.5
                 mask = (torch.nn.functional.interpolate(m, size=(req.height // 8, req.width // 8), mode="area") > 0.5).float()
+        control_latents = None
+        if getattr(req, "control_image", None) is not None:
+            if self.c.controlnet is None or self.c.vae_encoder is None:
+                raise ValueError("a control image needs a ControlNet and the VAE encoder (FluxComponents.controlnet / vae_encoder)")
+            control_latents = self.c.vae_encoder.encode(self._image_tensor(req.control_image, req.width, req.height))
         z = self.denoise(ctx, pooled, req.height, req.width, req.steps, req.guidance, seed, neg, req.cfg_scale, on_step,
-                         req.step_cache_threshold, init_latents=init_latents, strength=req.strength, mask=mask)
+                         req.step_cache_threshold, init_latents=init_latents, strength=req.strength, mask=mask,
+                         control_latents=control_latents, control_strength=getattr(req, "control_strength", 1.0))
         t_denoise = time.perf_counter() - t0
         if self.c.vae is None:
             img = torch.zeros(1, 3, req.height, req.width)

@@ -213,3 +213,63 @@ def test_more_schedulers():
     import pytest
     with pytest.raises(ValueError):
         S.make_scheduler("nope", 4)
+
+
+def test_flux_controlnet_residuals():
+    import torch
+    from hartsyinference_b200.models.dit import flux as F
+    from hartsyinference_b200.models.dit.flux_controlnet import FluxControlNet
+    cfg = F.tiny_flux(num_double_blocks=4, num_single_blocks=4)
+    base = F.FluxTransformer(cfg, "cpu", seed=0)
+    cn = FluxControlNet(F.tiny_flux(num_double_blocks=2, num_single_blocks=1), "cpu", seed=1)
+    assert not hasattr(cn, "proj_out")
+    g = torch.Generator().manual_seed(1)
+    S_i, S_t = 16, 8
+    img, ctrl = torch.randn(1, S_i, cfg.in_channels, generator=g), torch.randn(1, S_i, cfg.in_channels, generator=g)
+    txt, pooled = torch.randn(1, S_t, cfg.context_dim, generator=g), torch.randn(1, cfg.pooled_dim, generator=g)
+    img_ids, txt_ids = F.flux_ids(4, 4, S_t)
+    t, gd = torch.tensor([0.7]), torch.tensor([3.5])
+    args = (img, txt, t, pooled, img_ids, txt_ids, gd)
+    d, s = cn.residuals(img, ctrl, txt, t, pooled, img_ids, txt_ids, gd, scale=0.8)
+    assert len(d) == 2 and len(s) == 1 and d[0].shape == (S_i, cfg.hidden_size)
+    d2, _ = cn.residuals(img, ctrl, txt, t, pooled, img_ids, txt_ids, gd, scale=0.4)
+    assert torch.allclose(d2[0].float() * 2, d[0].float(), atol=2e-2)          # strength scales the residuals
+    other, _ = cn.residuals(img, ctrl * 0, txt, t, pooled, img_ids, txt_ids, gd, scale=0.8)
+    assert not torch.allclose(other[0].float(), d[0].float(), atol=1e-3)       # the control image matters
+    plain = base.forward(*args)
+    zeros = ([torch.zeros_like(x) for x in d], [torch.zeros_like(x) for x in s])
+    assert torch.equal(base.forward(*args, control=zeros), plain)
+    assert not torch.allclose(base.forward(*args, control=(d, s)).float(), plain.float(), atol=1e-3)
+    # two residuals over four double blocks: residual j covers blocks 2j and 2j + 1
+    only_second = ([torch.zeros_like(d[0]), d[1]], [])
+    seen_d, seen_s = [], []
+    base.forward(*args, control=only_second, collect=(seen_d, seen_s))
+    ref_d, ref_s = [], []
+    base.forward(*args, collect=(ref_d, ref_s))
+    assert len(seen_d) == 4 and len(seen_s) == 4
+    assert torch.equal(seen_d[0], ref_d[0]) and torch.equal(seen_d[1], ref_d[1]) and torch.equal(seen_d[2], ref_d[2])
+    assert not torch.equal(seen_d[3], ref_d[3])          # collected before the add: block 3 sees block 2's residual
+
+
+def test_flux_pipeline_with_controlnet():
+    import torch
+    from hartsyinference_b200.engine.requests import ImageRequest
+    from hartsyinference_b200.models.dit import flux as F
+    from hartsyinference_b200.models.dit.flux_controlnet import FluxControlNet
+    from hartsyinference_b200.models.vae.vae2d import Vae2dDecoder, Vae2dEncoder, tiny_vae2d
+    from hartsyinference_b200.pipelines.flux import FluxComponents, FluxPipeline
+    tr = F.FluxTransformer(F.tiny_flux(), "cpu", seed=0)
+    v = tiny_vae2d()
+    comp = FluxComponents(tr, Vae2dDecoder(v, "cpu", torch.float32), vae_encoder=Vae2dEncoder(v, "cpu", torch.float32),
+                          controlnet=FluxControlNet(F.tiny_flux(num_double_blocks=1, num_single_blocks=1), "cpu", seed=4))
+    pipe = FluxPipeline(comp)
+    edges = torch.zeros(3, 64, 64)
+    edges[:, 20:44, 30:34] = 1.0
+    base = pipe.generate(ImageRequest(prompt="a tower", width=64, height=64, steps=2, seed=7))
+    ctl = pipe.generate(ImageRequest(prompt="a tower", width=64, height=64, steps=2, seed=7, control_image=edges, control_strength=1.0))
+    off = pipe.generate(ImageRequest(prompt="a tower", width=64, height=64, steps=2, seed=7, control_image=edges, control_strength=0.0))
+    assert ctl.rgb != base.rgb and off.rgb == base.rgb
+    comp.controlnet = None
+    import pytest
+    with pytest.raises(ValueError):
+        pipe.generate(ImageRequest(prompt="a tower", width=64, height=64, steps=1, control_image=edges))
