@@ -38,6 +38,24 @@ class _PipelineCache:
             torch.cuda.empty_cache()
 
 
+def apply_recipe_defaults(spec: ModelSpec, req):
+    """A catalog model carries its family's request defaults (steps, guidance, size, frames): fields
+    the caller left at the request type's own default take the family's value. (The reference keeps
+    these in per-family recipe classes: src/HartsyInference.Engine/Recipes/.)"""
+    if not spec.catalog:
+        return req
+    import dataclasses
+    from ..assets.catalog import ModelCatalog
+    entry = ModelCatalog().find(spec.catalog)
+    if entry is None or not entry.defaults:
+        return req
+    changes = {}
+    for f in dataclasses.fields(req):
+        if f.name in entry.defaults and getattr(req, f.name) == f.default:
+            changes[f.name] = entry.defaults[f.name]
+    return dataclasses.replace(req, **changes) if changes else req
+
+
 class ImagesService(_PipelineCache):
     def _build(self, spec: ModelSpec):
         from ..models.dit import flux as F
@@ -110,7 +128,7 @@ class ImagesService(_PipelineCache):
         return self._pipes[k]
 
     def generate(self, spec: ModelSpec, req: ImageRequest, progress: Optional[Callable[[StepPreview], None]] = None) -> ImageResult:
-        return self.pipeline(spec).generate(req, progress)
+        return self.pipeline(spec).generate(apply_recipe_defaults(spec, req), progress)
 
 
 class VideoService(_PipelineCache):
@@ -145,7 +163,7 @@ class VideoService(_PipelineCache):
         return self._pipes[k]
 
     def generate(self, spec: ModelSpec, req: VideoRequest, progress: Optional[Callable[[StepPreview], None]] = None) -> VideoGenerationResult:
-        return self.pipeline(spec).generate(req, progress)
+        return self.pipeline(spec).generate(apply_recipe_defaults(spec, req), progress)
 
 
 def Vae3dDecoderCfg(tiny: bool, wan_cfg):

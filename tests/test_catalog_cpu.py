@@ -81,3 +81,15 @@ def test_cli_pull_from_disk_and_list(tmp_path):
     assert r.exit_code == 0 and "whisper-tiny" in r.output
     r = CliRunner().invoke(cli, ["models", "--catalog"])
     assert r.exit_code == 0 and "flux.1-dev" in r.output and "black-forest-labs/FLUX.1-dev" in r.output
+
+
+def test_recipe_defaults_fill_untouched_fields():
+    from hartsyinference_b200.engine.diffusion_service import apply_recipe_defaults
+    from hartsyinference_b200.engine.requests import ImageRequest, ModelSpec
+    spec = ModelSpec("flux-schnell", Modality.IMAGE, catalog="flux.1-schnell")
+    r = apply_recipe_defaults(spec, ImageRequest(prompt="x"))
+    assert (r.steps, r.guidance) == (4, 0.0) and r.prompt == "x"
+    r = apply_recipe_defaults(spec, ImageRequest(prompt="x", steps=9))
+    assert r.steps == 9 and r.guidance == 0.0                 # what the caller set stays
+    same = ImageRequest(prompt="y")
+    assert apply_recipe_defaults(ModelSpec("/some/path", Modality.IMAGE), same) is same
