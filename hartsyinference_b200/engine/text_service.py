@@ -148,8 +148,26 @@ class TextService:
             return ids, None, None
         if llm.vlm is None:
             raise ValueError("this model has no vision tower; images are not accepted")
+        if hasattr(llm.vlm, "image_features_anyres"):      # any-resolution models take the image at its own size
+            return llm.vlm.expand_prompt(ids, [self._unit_image(im) for im in req.images])
         size = llm.vlm.vision.cfg.image_size
         return llm.vlm.expand_prompt(ids, [preprocess_image(im, size) for im in req.images])
+
+    @staticmethod
+    def _unit_image(image) -> torch.Tensor:
+        """Path, PIL image, uint8 HWC array / tensor or float CHW tensor -> float [3, H, W] in [0, 1]."""
+        import numpy as np
+        if isinstance(image, (str, bytes)) or hasattr(image, "__fspath__"):
+            from PIL import Image
+            image = Image.open(image)
+        if hasattr(image, "convert"):
+            image = torch.from_numpy(np.asarray(image.convert("RGB")).copy())
+        t = torch.as_tensor(image)
+        if t.dtype == torch.uint8:
+            t = t.float() / 255.0
+        if t.ndim == 3 and t.shape[-1] == 3 and t.shape[0] != 3:
+            t = t.permute(2, 0, 1)
+        return t.float().clamp(0, 1)
 
     def stream(self, spec: ModelSpec, req: TextRequest, cancel: Optional[threading.Event] = None) -> Iterator[TextChunk]:
         h = self._host(spec)

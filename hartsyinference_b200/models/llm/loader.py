@@ -254,8 +254,14 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
         lm_get, tower_get = _llava_names(ck)
         model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
         model.load_state_dict(lm_get)
-        vlm = LlavaModel(model, clip_vision_from_hf(raw["vision_config"]), int(raw.get("image_token_index", 32000)),
-                         get=tower_get, feature_layer=int(raw.get("vision_feature_layer", -2)))
+        if raw.get("model_type") == "llava_next" or raw.get("image_grid_pinpoints"):
+            from ..vlm.llava_next import DEFAULT_PINPOINTS, LlavaNextModel
+            vlm = LlavaNextModel(model, clip_vision_from_hf(raw["vision_config"]), int(raw.get("image_token_index", 32000)),
+                                 get=tower_get, feature_layer=int(raw.get("vision_feature_layer", -2)),
+                                 pinpoints=[tuple(p) for p in raw.get("image_grid_pinpoints") or DEFAULT_PINPOINTS])
+        else:
+            vlm = LlavaModel(model, clip_vision_from_hf(raw["vision_config"]), int(raw.get("image_token_index", 32000)),
+                             get=tower_get, feature_layer=int(raw.get("vision_feature_layer", -2)))
     else:
         cfg = from_hf_config(raw)
         model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))

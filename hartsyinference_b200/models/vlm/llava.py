@@ -46,7 +46,9 @@ class LlavaModel:
     def expand_prompt(self, token_ids: Sequence[int], images: Sequence[torch.Tensor]):
         """Replace every image token by ``num_patches`` placeholders. Returns (ids, embeds [T, H],
         mask [T]) where ``mask`` marks the rows whose embedding comes from an image."""
-        feats = [self.image_features(im) for im in images]
+        return self._splice(token_ids, [self.image_features(im) for im in images])
+
+    def _splice(self, token_ids: Sequence[int], feats: list):
         ids: list[int] = []
         rows: list[torch.Tensor] = []
         mask: list[bool] = []

@@ -330,3 +330,72 @@ def test_depth_anything_matches_transformers_and_serves(tmp_path):
         assert (j["width"], j["height"]) == (45, 30)
         assert Image.open(io.BytesIO(base64.b64decode(j["png16_base64"]))).size == (45, 30)
     eng.close()
+
+
+def test_llava_next_anyres_matches_transformers():
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.vlm.llava_next import LlavaNextModel, select_best_resolution
+    vc = tiny_clip_vision()                       # 32 x 32 input, 8 x 8 patches -> 16 patch tokens per view
+    pins = [(32, 64), (64, 32), (64, 64), (96, 32), (32, 96)]
+    hv = tr.CLIPVisionConfig(hidden_size=vc.width, intermediate_size=vc.width * vc.mlp_ratio, num_hidden_layers=vc.layers,
+                             num_attention_heads=vc.heads, image_size=vc.image_size, patch_size=vc.patch)
+    ht = tr.LlamaConfig(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                        num_key_value_heads=2, max_position_embeddings=512)
+    cfg = tr.LlavaNextConfig(vision_config=hv, text_config=ht, image_grid_pinpoints=[list(p) for p in pins], image_token_index=319,
+                             vision_feature_layer=-2, vision_feature_select_strategy="default")
+    torch.manual_seed(0)
+    hf = tr.LlavaNextForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        hf.model.image_newline.copy_(torch.randn(128) * 0.1)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+
+    def get(name):      # this transformers version nests everything under "model."
+        for cand in (name, "model." + name):
+            if cand in sd:
+                return sd[cand]
+        return None
+    dec = DecoderModel(C.tiny(vocab_size=320, hidden_size=128, num_heads=2, num_kv_heads=2, head_dim=64), "cpu")
+    dec.random_init(1)
+    m = LlavaNextModel(dec, vc, 319, get=get, pinpoints=pins)
+    for (h, w) in ((40, 90), (70, 50), (33, 31)):
+        img = torch.rand(3, h, w, generator=torch.Generator().manual_seed(h))
+        views, grid = m.tiles(img)
+        best = select_best_resolution((h, w), pins)
+        assert grid == (best[0] // 32, best[1] // 32) and views.shape == (1 + grid[0] * grid[1], 3, 32, 32)
+        with torch.no_grad():
+            ref = hf.get_image_features(pixel_values=views[None], image_sizes=torch.tensor([[h, w]]),
+                                        vision_feature_layer=-2, vision_feature_select_strategy="default")
+        ref = ref.pooler_output if hasattr(ref, "pooler_output") else ref
+        ref = ref[0] if isinstance(ref, (list, tuple)) else ref
+        mine = m.image_features_anyres(img)
+        assert mine.shape == ref.shape, (mine.shape, ref.shape)
+        assert torch.nn.functional.cosine_similarity(mine.float().flatten(), ref.float().flatten(), dim=0) > 0.99
+    ids, embeds, mask = m.expand_prompt([5, 319, 7], [torch.rand(3, 40, 90)])
+    assert int(mask.sum()) == m.image_features_anyres(torch.rand(3, 40, 90)).shape[0] and len(ids) == int(mask.sum()) + 2
+
+
+def test_llava_next_checkpoint_through_text_service(tmp_path):
+    import numpy as np
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, TextRequest
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    import json
+    d = _llava_checkpoint(tmp_path, "new")
+    cfg = json.loads((d / "config.json").read_text())
+    cfg.update(model_type="llava_next", image_grid_pinpoints=[[32, 64], [64, 32], [64, 64]])
+    (d / "config.json").write_text(json.dumps(cfg))
+    from hartsyinference_b200.assets.safetensors import SafeTensorsFile, save_file
+    f = SafeTensorsFile(d / "model.safetensors")
+    tensors = {k: f.get(k) for k in f.keys()}
+    tensors["model.image_newline"] = torch.randn(128).to(torch.bfloat16)
+    save_file(tensors, d / "model.safetensors")
+    eng = InferenceEngine("cpu")
+    try:
+        wide = (np.random.default_rng(0).random((30, 80, 3)) * 255).astype(np.uint8)
+        tall = (np.random.default_rng(1).random((80, 30, 3)) * 255).astype(np.uint8)
+        a = eng.text.generate(ModelSpec(str(d)), TextRequest(prompt="<image> describe", images=[wide], max_tokens=2, greedy=True))
+        b = eng.text.generate(ModelSpec(str(d)), TextRequest(prompt="<image> describe", images=[tall], max_tokens=2, greedy=True))
+        assert len(a.token_ids) == 2 and a.error is None and b.error is None
+        assert a.prompt_tokens != b.prompt_tokens           # the token count follows the image's shape
+        assert type(eng.text._host(ModelSpec(str(d))).llm.vlm).__name__ == "LlavaNextModel"
+    finally:
+        eng.text.release()
