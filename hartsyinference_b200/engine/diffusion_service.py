@@ -23,8 +23,9 @@ class _PipelineCache:
         self.options, self.device = options, device
         self._pipes: dict[str, object] = {}
 
-    def key(self, spec: ModelSpec) -> str:
-        return f"{spec.local_path or spec.requested}|{self.options.placement.cache_key}|{self.device}"
+    def key(self, spec: ModelSpec, loras: tuple = ()) -> str:
+        tag = "|".join(f"{p}@{s:g}" for p, s in loras)
+        return f"{spec.local_path or spec.requested}|{self.options.placement.cache_key}|{self.device}" + (f"|lora:{tag}" if tag else "")
 
     def loaded_keys(self) -> list[str]:
         return list(self._pipes)
@@ -56,8 +57,24 @@ def apply_recipe_defaults(spec: ModelSpec, req):
     return dataclasses.replace(req, **changes) if changes else req
 
 
+def _with_loras(get, keys, loras: tuple):
+    """Merge LoRA adapters ((path, strength), ...) into the tensors ``get`` returns."""
+    if not loras:
+        return get
+    from ..assets.lora import LoraStack
+    from ..assets.safetensors import SafeTensorsFile
+    stack = LoraStack()
+    for path, strength in loras:
+        f = SafeTensorsFile(path)
+        stack.add({k: f.get(k) for k in f.keys()}, float(strength))
+    merged = stack.wrap(get, keys)
+    if stack.unmatched:
+        log.warn(f"[LoRA] {len(stack.unmatched)} adapter module(s) match no weight of the base model (first: {stack.unmatched[0]})")
+    return merged
+
+
 class ImagesService(_PipelineCache):
-    def _build(self, spec: ModelSpec):
+    def _build(self, spec: ModelSpec, loras: tuple = ()):
         from ..models.dit import flux as F
         from ..models.vae.vae2d import FLUX_VAE, Vae2dDecoder, Vae2dEncoder, tiny_vae2d
         from ..pipelines.flux import FluxComponents, FluxPipeline
@@ -80,15 +97,7 @@ class ImagesService(_PipelineCache):
             if tiny:   # the tiny DiT packs 4 latent channels
                 assert cfg.in_channels == 16
             enc = Vae2dEncoder(tiny_vae2d() if tiny else FLUX_VAE, self.device, vae.dtype)
-            cnet = None
-        if "controlnet" in spec.aux:
-            import json as _json
-            from ..models.dit.flux_controlnet import FluxControlNet
-            cdir = Path(spec.aux["controlnet"])
-            cc = _json.loads((cdir / "config.json").read_text()) if (cdir / "config.json").exists() else {}
-            ccfg = F.FluxConfig(num_double_blocks=int(cc.get("num_layers", 5)), num_single_blocks=int(cc.get("num_single_layers", 10)))
-            cnet = FluxControlNet(ccfg, self.device, fp8=fp8, get=ShardedCheckpoint(cdir).get)
-        return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc, controlnet=cnet))
+            return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc))
         path = Path(spec.local_path or name)
         if not path.exists():
             raise UnsupportedModelError(f"{name}: no such checkpoint")
@@ -104,11 +113,12 @@ class ImagesService(_PipelineCache):
             if "vae" in spec.aux or (path / "vae").exists():
                 vae = Vae2dDecoder(SD3_VAE, self.device, get=ShardedCheckpoint(spec.aux.get("vae", path / "vae")).get)
             return Sd3Pipeline(Sd3Components(S3.Sd3Transformer(cfg3, self.device, fp8=fp8, get=ck.get), vae))
-        get = ck.get
+        # adapters are merged in the checkpoint's own layout (their module names follow it)
+        get = _with_loras(ck.get, list(ck.keys()), loras)
         from ..assets.converters import flux_original_to_diffusers, is_flux_original
         if is_flux_original(ck.keys()):
-            # a Black Forest Labs / ComfyUI layout file: fused qkv and other names; rename lazily per tensor group
-            renamed = flux_original_to_diffusers({k: ck.get(k) for k in ck.keys()})
+            # a Black Forest Labs / ComfyUI layout file: fused qkv and other names
+            renamed = flux_original_to_diffusers({k: get(k) for k in ck.keys()})
             get = renamed.get
             log.decision("Load", f"{path.name}: original Flux layout converted to diffusers names")
         tr = F.FluxTransformer(F.FLUX_DEV, self.device, fp8=fp8, get=get)
@@ -118,17 +128,28 @@ class ImagesService(_PipelineCache):
             vae = Vae2dDecoder(FLUX_VAE, self.device, get=vck.get)
             if vck.get("encoder.conv_in.weight") is not None:
                 enc = Vae2dEncoder(FLUX_VAE, self.device, get=vck.get)
-        return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc))
+        cnet = None
+        if "controlnet" in spec.aux:
+            import json as _json
+            from ..models.dit.flux_controlnet import FluxControlNet
+            cdir = Path(spec.aux["controlnet"])
+            cc = _json.loads((cdir / "config.json").read_text()) if (cdir / "config.json").exists() else {}
+            ccfg = F.FluxConfig(num_double_blocks=int(cc.get("num_layers", 5)), num_single_blocks=int(cc.get("num_single_layers", 10)))
+            cnet = FluxControlNet(ccfg, self.device, fp8=fp8, get=ShardedCheckpoint(cdir).get)
+        return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc, controlnet=cnet))
 
-    def pipeline(self, spec: ModelSpec):
-        k = self.key(spec)
+    def pipeline(self, spec: ModelSpec, loras: tuple = ()):
+        k = self.key(spec, loras)
         if k not in self._pipes:
-            log.info(f"[Images] constructing pipeline for {spec.requested}")
-            self._pipes[k] = self._build(spec)
+            log.info(f"[Images] constructing pipeline for {spec.requested}" + (f" with {len(loras)} LoRA adapter(s)" if loras else ""))
+            self._pipes[k] = self._build(spec, loras)
         return self._pipes[k]
 
     def generate(self, spec: ModelSpec, req: ImageRequest, progress: Optional[Callable[[StepPreview], None]] = None) -> ImageResult:
-        return self.pipeline(spec).generate(apply_recipe_defaults(spec, req), progress)
+        loras = tuple((str(p), float(s)) for p, s in (req.loras or ()))
+        if loras and spec.requested.startswith("synthetic:"):
+            raise UnsupportedModelError("LoRA adapters need a checkpoint to merge into")
+        return self.pipeline(spec, loras).generate(apply_recipe_defaults(spec, req), progress)
 
 
 class VideoService(_PipelineCache):

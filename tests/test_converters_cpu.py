@@ -68,3 +68,41 @@ def test_flux_layout_roundtrip_and_load():
     ya = a.forward(img, txt, t, pooled, img_ids, txt_ids, gd)
     yb = b.forward(img, txt, t, pooled, img_ids, txt_ids, gd)
     assert torch.equal(ya, yb) and ya.float().abs().max() > 0
+
+
+def test_image_service_merges_loras_into_a_flux_checkpoint(tmp_path, monkeypatch):
+    """A PEFT-style adapter on a diffusers-layout transformer: the merged model differs from the base
+    by exactly strength * (alpha / rank) * B A on the adapted weight."""
+    from hartsyinference_b200.assets.safetensors import save_file
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec
+    from hartsyinference_b200.engine.requests import ImageRequest
+    cfg = F.tiny_flux()
+    monkeypatch.setattr(F, "FLUX_DEV", cfg)            # the service builds FLUX_DEV-shaped models from checkpoints
+    sd = _diffusers_state(cfg)
+    d = tmp_path / "flux"
+    (d / "transformer").mkdir(parents=True)
+    save_file({k: v.to(torch.bfloat16).contiguous() for k, v in sd.items()}, d / "transformer" / "model.safetensors")
+    H = cfg.hidden_size
+    g = torch.Generator().manual_seed(3)
+    A, B = torch.randn(4, H, generator=g) * 0.3, torch.randn(H, 4, generator=g) * 0.3
+    target = "transformer_blocks.0.attn.to_out.0"
+    save_file({f"transformer.{target}.lora_A.weight": A, f"transformer.{target}.lora_B.weight": B,
+               f"transformer.{target}.alpha": torch.tensor(8.0)}, tmp_path / "style.safetensors")
+    eng = InferenceEngine("cpu")
+    req = ImageRequest(prompt="x", width=32, height=32, steps=1, seed=1)
+    base = eng.images.pipeline(ModelSpec(str(d)))
+    tuned = eng.images.pipeline(ModelSpec(str(d)), ((str(tmp_path / "style.safetensors"), 0.5),))
+    assert base is not tuned and len(eng.images.loaded_keys()) == 2
+    wb = base.c.transformer.double[0][0].proj.weight.float()
+    wt = tuned.c.transformer.double[0][0].proj.weight.float()
+    want = 0.5 * (8.0 / 4) * (B @ A)
+    assert torch.allclose(wt - wb, want, atol=0.05) and (wt - wb).abs().max() > 0.05
+    assert torch.equal(base.c.transformer.double[1][0].proj.weight, tuned.c.transformer.double[1][0].proj.weight)
+    res = eng.images.generate(ModelSpec(str(d)), ImageRequest(prompt="x", width=32, height=32, steps=1, seed=1,
+                                                              loras=[(str(tmp_path / "style.safetensors"), 0.5)]))
+    assert res.width == 32 and len(eng.images.loaded_keys()) == 2       # the cached merged pipeline is reused
+    import pytest
+    from hartsyinference_b200.exceptions import UnsupportedModelError
+    with pytest.raises(UnsupportedModelError):
+        eng.images.generate(ModelSpec("synthetic:flux-tiny"), ImageRequest(prompt="x", loras=[("a.safetensors", 1.0)]))
+    eng.close()
