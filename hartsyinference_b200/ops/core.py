@@ -73,6 +73,15 @@ class LinearWeight:
     def is_mx(self) -> bool:
         return self.sf is not None
 
+    def host_f32(self) -> torch.Tensor:
+        """fp32 copy of a host-resident bf16 weight, made once: the CPU path multiplies in fp32 and
+        would otherwise widen the whole matrix on every call."""
+        c = self.__dict__.get("_host_f32")
+        if c is None or c.shape != self.weight.shape:
+            c = self.weight.float()
+            self.__dict__["_host_f32"] = c
+        return c
+
     @staticmethod
     def from_quantized(q: torch.Tensor, scale: torch.Tensor, bias: Optional[torch.Tensor] = None) -> "LinearWeight":
         """e4m3 bytes [N, K] + block scales [ceil(N/128), K/128]. In UE8M0 mode the scales must be
@@ -178,7 +187,7 @@ def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.T
             q, s = R.quant_fp8_act(x, pow2=fp8_mx())
             y = R.linear(q, w.weight, w.scale, s, w.bias, act, gate, residual)
         else:
-            y = R.linear(x, w.weight, None, None, w.bias, act, gate, residual)
+            y = R.linear(x, w.host_f32(), None, None, w.bias, act, gate, residual)
         if out is not None:
             out.copy_(y)
             return out
