@@ -20,6 +20,11 @@ public interface IInferenceEngine : IDisposable
     TextService Text { get; }
     ImagesService Images { get; }
     VideoService Video { get; }
+    TranscribeService Transcribe { get; }
+    SpeechService Speech { get; }
+    EmbeddingService Embeddings { get; }
+    VisionService Vision { get; }
+    RestoreService Restore { get; }
     void SetBackend(string selector);
     void FreeMemory();
     bool IsSupported(Modality modality);
@@ -32,6 +37,11 @@ public sealed class InferenceEngine : IInferenceEngine
     public TextService Text { get; }
     public ImagesService Images { get; }
     public VideoService Video { get; }
+    public TranscribeService Transcribe { get; }
+    public SpeechService Speech { get; }
+    public EmbeddingService Embeddings { get; }
+    public VisionService Vision { get; }
+    public RestoreService Restore { get; }
 
     public InferenceEngine(string backendSelector = "auto", EngineOptions? options = null)
     {
@@ -40,6 +50,11 @@ public sealed class InferenceEngine : IInferenceEngine
         Text = new TextService(this);
         Images = new ImagesService(this);
         Video = new VideoService(this);
+        Transcribe = new TranscribeService(this);
+        Speech = new SpeechService(this);
+        Embeddings = new EmbeddingService(this);
+        Vision = new VisionService(this);
+        Restore = new RestoreService(this);
     }
 
     public string BackendDescription
@@ -166,5 +181,86 @@ public sealed class VideoService
             return new VideoGenerationResult(frames, w, h, null, fps, seed);
         }
         finally { NativeMethods.b200_free(buf); GC.KeepAlive(cb); }
+    }, ct);
+}
+
+public sealed class TranscribeService
+{
+    private readonly InferenceEngine _e;
+    internal TranscribeService(InferenceEngine e) => _e = e;
+
+    /// <summary>Mono float samples in [-1, 1] at <paramref name="sampleRate"/> Hz -> transcript JSON mapped onto <see cref="TranscriptResult"/>.</summary>
+    public Task<TranscriptResult> RunAsync(ModelSpec spec, AudioRequest request, float[] pcm, int sampleRate, CancellationToken ct = default) => Task.Run(() =>
+    {
+        NativeMethods.Check(NativeMethods.b200_transcribe(_e.Handle, JsonSerializer.Serialize(spec with { Modality = Modality.Transcribe }),
+            JsonSerializer.Serialize(request), pcm, pcm.LongLength, sampleRate, out var p));
+        return JsonSerializer.Deserialize<TranscriptResult>(NativeMethods.TakeString(p), Records.SnakeCase)!;
+    }, ct);
+}
+
+public sealed class SpeechService
+{
+    private readonly InferenceEngine _e;
+    internal SpeechService(InferenceEngine e) => _e = e;
+
+    public Task<AudioResult> RunAsync(ModelSpec spec, SpeechRequest request, CancellationToken ct = default) => Task.Run(() =>
+    {
+        NativeMethods.Check(NativeMethods.b200_speak(_e.Handle, JsonSerializer.Serialize(spec with { Modality = Modality.Speech }),
+            JsonSerializer.Serialize(request), out var pcm, out long n, out int rate));
+        try
+        {
+            var samples = new float[n];
+            Marshal.Copy(pcm, samples, 0, (int)n);
+            return new AudioResult(samples, rate);
+        }
+        finally { NativeMethods.b200_free(pcm); }
+    }, ct);
+}
+
+public sealed class EmbeddingService
+{
+    private readonly InferenceEngine _e;
+    internal EmbeddingService(InferenceEngine e) => _e = e;
+
+    public Task<float[][]> EmbedAsync(ModelSpec spec, IReadOnlyList<string> texts, CancellationToken ct = default) => Task.Run(() =>
+    {
+        NativeMethods.Check(NativeMethods.b200_embed_text(_e.Handle, JsonSerializer.Serialize(spec with { Modality = Modality.Embeddings }),
+            JsonSerializer.Serialize(texts), out var buf, out int count, out int dim));
+        try
+        {
+            var rows = new float[count][];
+            for (int i = 0; i < count; i++) { rows[i] = new float[dim]; Marshal.Copy(buf + i * dim * sizeof(float), rows[i], 0, dim); }
+            return rows;
+        }
+        finally { NativeMethods.b200_free(buf); }
+    }, ct);
+}
+
+public sealed class VisionService
+{
+    private readonly InferenceEngine _e;
+    internal VisionService(InferenceEngine e) => _e = e;
+
+    /// <summary>L2-normalised embedding of one RGB24 image (CLIP / SigLIP / DINOv2 checkpoints).</summary>
+    public Task<float[]> EmbedImageAsync(ModelSpec spec, byte[] rgb, int width, int height, CancellationToken ct = default) => Task.Run(() =>
+    {
+        NativeMethods.Check(NativeMethods.b200_embed_image(_e.Handle, JsonSerializer.Serialize(spec with { Modality = Modality.Vision }),
+            rgb, width, height, out var buf, out int dim));
+        try { var v = new float[dim]; Marshal.Copy(buf, v, 0, dim); return v; }
+        finally { NativeMethods.b200_free(buf); }
+    }, ct);
+}
+
+public sealed class RestoreService
+{
+    private readonly InferenceEngine _e;
+    internal RestoreService(InferenceEngine e) => _e = e;
+
+    public Task<ImageResult> UpscaleAsync(ModelSpec spec, RestoreRequest request, byte[] rgb, int width, int height, CancellationToken ct = default) => Task.Run(() =>
+    {
+        NativeMethods.Check(NativeMethods.b200_upscale(_e.Handle, JsonSerializer.Serialize(spec with { Modality = Modality.Restore }),
+            JsonSerializer.Serialize(request), rgb, width, height, out var outBuf, out int w, out int h));
+        try { var bytes = new byte[w * h * 3]; Marshal.Copy(outBuf, bytes, 0, bytes.Length); return new ImageResult(bytes, w, h, 0); }
+        finally { NativeMethods.b200_free(outBuf); }
     }, ct);
 }

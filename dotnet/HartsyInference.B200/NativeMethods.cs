@@ -58,6 +58,27 @@ internal static unsafe class NativeMethods
         out IntPtr frames, out int frameCount, out int width, out int height, out int fps, out long seed);
 
     [DllImport(Lib, CallingConvention = CallingConvention.Cdecl)]
+    internal static extern int b200_transcribe(IntPtr engine, [MarshalAs(UnmanagedType.LPUTF8Str)] string spec,
+        [MarshalAs(UnmanagedType.LPUTF8Str)] string request, float[] pcm, long samples, int sampleRate, out IntPtr resultJson);
+
+    [DllImport(Lib, CallingConvention = CallingConvention.Cdecl)]
+    internal static extern int b200_speak(IntPtr engine, [MarshalAs(UnmanagedType.LPUTF8Str)] string spec,
+        [MarshalAs(UnmanagedType.LPUTF8Str)] string request, out IntPtr pcm, out long samples, out int sampleRate);
+
+    [DllImport(Lib, CallingConvention = CallingConvention.Cdecl)]
+    internal static extern int b200_embed_text(IntPtr engine, [MarshalAs(UnmanagedType.LPUTF8Str)] string spec,
+        [MarshalAs(UnmanagedType.LPUTF8Str)] string textsJson, out IntPtr values, out int count, out int dim);
+
+    [DllImport(Lib, CallingConvention = CallingConvention.Cdecl)]
+    internal static extern int b200_embed_image(IntPtr engine, [MarshalAs(UnmanagedType.LPUTF8Str)] string spec,
+        byte[] rgb, int width, int height, out IntPtr values, out int dim);
+
+    [DllImport(Lib, CallingConvention = CallingConvention.Cdecl)]
+    internal static extern int b200_upscale(IntPtr engine, [MarshalAs(UnmanagedType.LPUTF8Str)] string spec,
+        [MarshalAs(UnmanagedType.LPUTF8Str)] string request, byte[] rgb, int width, int height,
+        out IntPtr rgbOut, out int widthOut, out int heightOut);
+
+    [DllImport(Lib, CallingConvention = CallingConvention.Cdecl)]
     internal static extern IntPtr b200_last_error();
 
     [DllImport(Lib, CallingConvention = CallingConvention.Cdecl)]

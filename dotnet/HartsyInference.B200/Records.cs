@@ -83,3 +83,40 @@ public sealed record VideoRequest
 }
 
 public sealed record VideoGenerationResult(IReadOnlyList<byte[]> Frames, int Width, int Height, byte[]? Audio, int Fps, long Seed);
+
+public sealed record AudioRequest
+{
+    public string? Language { get; init; }
+    public string Task { get; init; } = "transcribe";
+    public bool Timestamps { get; init; } = true;
+}
+
+public sealed record TranscriptSegment(double Start, double End, string Text);
+
+public sealed record TranscriptResult(string Text, string? Language, double Duration, IReadOnlyList<TranscriptSegment> Segments);
+
+public sealed record SpeechRequest
+{
+    public string Text { get; init; } = "";
+    public string? Voice { get; init; }
+    public float? Speed { get; init; }
+}
+
+public sealed record AudioResult(float[] Samples, int SampleRate);
+
+public sealed record RestoreRequest
+{
+    public string Operation { get; init; } = "upscale";
+    public int Tile { get; init; } = 128;
+    public float TileOverlap { get; init; } = 0.25f;
+}
+
+public static class Records
+{
+    /// <summary>The native side answers in snake_case JSON.</summary>
+    public static readonly System.Text.Json.JsonSerializerOptions SnakeCase = new()
+    {
+        PropertyNamingPolicy = System.Text.Json.JsonNamingPolicy.SnakeCaseLower,
+        PropertyNameCaseInsensitive = true,
+    };
+}

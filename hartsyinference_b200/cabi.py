@@ -157,3 +157,59 @@ def video_generate(h: int, spec: str, req: str, cb_ptr: int, user: int):
     e = _engines[h]
     r = e.with_vram_cleanup(lambda: e.video.generate(_spec(spec), _fields(VideoRequest, req), _step_adapter(cb_ptr, user)))
     return (b"".join(r.frames), len(r.frames), r.width, r.height, r.fps, r.seed)
+
+
+@_guard
+def transcribe(h: int, spec: str, req: str, pcm: bytes, sample_rate: int):
+    import numpy as np
+    import torch
+    from .engine.requests import AudioRequest
+    e = _engines[h]
+    r = _fields(AudioRequest, req)
+    r.audio = torch.from_numpy(np.frombuffer(pcm, dtype="<f4").copy())
+    r.sample_rate = sample_rate
+    res = e.transcribe.run(_spec(spec), r)
+    return json.dumps({"text": res.text, "language": res.language, "duration": res.duration_s,
+                       "segments": [{"start": s.start, "end": s.end, "text": s.text} for s in res.segments]})
+
+
+@_guard
+def speak(h: int, spec: str, req: str):
+    from .engine.requests import SpeechRequest
+    e = _engines[h]
+    res = e.speech.run(_spec(spec), _fields(SpeechRequest, req))
+    return (res.samples.float().contiguous().numpy().astype("<f4").tobytes(), res.sample_rate)
+
+
+@_guard
+def embed_text(h: int, spec: str, texts: str):
+    e = _engines[h]
+    s = _spec(spec)
+    s.modality = Modality.EMBEDDINGS
+    emb = e.embeddings.embed(s, list(json.loads(texts)))
+    return (emb.float().contiguous().numpy().astype("<f4").tobytes(), int(emb.shape[0]), int(emb.shape[1]))
+
+
+def _rgb(buf: bytes, width: int, height: int):
+    import numpy as np
+    import torch
+    return torch.from_numpy(np.frombuffer(buf, dtype=np.uint8).reshape(height, width, 3).copy())
+
+
+@_guard
+def embed_image(h: int, spec: str, rgb: bytes, width: int, height: int):
+    from .engine.requests import VisionRequest
+    e = _engines[h]
+    res = e.vision.run(_spec(spec), VisionRequest(images=[_rgb(rgb, width, height)]))
+    v = res.image_embeddings[0].float().contiguous()
+    return (v.numpy().astype("<f4").tobytes(), int(v.numel()))
+
+
+@_guard
+def upscale(h: int, spec: str, req: str, rgb: bytes, width: int, height: int):
+    from .engine.requests import RestoreRequest
+    e = _engines[h]
+    r = _fields(RestoreRequest, req)
+    r.image = _rgb(rgb, width, height)
+    res = e.with_vram_cleanup(lambda: e.restore.run(_spec(spec), r))
+    return (res.rgb, res.width, res.height)

@@ -197,6 +197,75 @@ int b200_video_generate(b200_engine* e, const char* spec, const char* req, b200_
   LEAVE(rc);
 }
 
+int b200_transcribe(b200_engine* e, const char* spec, const char* req, const float* pcm, long long samples, int sample_rate,
+                    char** result_json_out) {
+  ENTER();
+  PyObject* p = NULL;
+  int rc = call("transcribe", Py_BuildValue("(Lssy#i)", e->handle, spec, req ? req : "{}", (const char*)pcm,
+                                            (Py_ssize_t)(samples * (long long)sizeof(float)), sample_rate), &p);
+  if (rc == 0 && result_json_out) *result_json_out = dup_str(p);
+  Py_XDECREF(p);
+  LEAVE(rc);
+}
+
+int b200_speak(b200_engine* e, const char* spec, const char* req, float** pcm_out, long long* samples_out, int* sample_rate_out) {
+  ENTER();
+  PyObject* p = NULL;
+  int rc = call("speak", Py_BuildValue("(Lss)", e->handle, spec, req), &p);
+  if (rc == 0) {   /* payload: (float32 bytes, sample rate) */
+    Py_ssize_t n = 0;
+    if (pcm_out) *pcm_out = (float*)dup_bytes(PyTuple_GetItem(p, 0), &n);
+    if (samples_out) *samples_out = (long long)(n / (Py_ssize_t)sizeof(float));
+    if (sample_rate_out) *sample_rate_out = (int)PyLong_AsLong(PyTuple_GetItem(p, 1));
+  }
+  Py_XDECREF(p);
+  LEAVE(rc);
+}
+
+int b200_embed_text(b200_engine* e, const char* spec, const char* texts_json, float** out, int* count, int* dim) {
+  ENTER();
+  PyObject* p = NULL;
+  int rc = call("embed_text", Py_BuildValue("(Lss)", e->handle, spec, texts_json), &p);
+  if (rc == 0) {   /* payload: (float32 bytes, count, dim) */
+    Py_ssize_t n = 0;
+    if (out) *out = (float*)dup_bytes(PyTuple_GetItem(p, 0), &n);
+    if (count) *count = (int)PyLong_AsLong(PyTuple_GetItem(p, 1));
+    if (dim) *dim = (int)PyLong_AsLong(PyTuple_GetItem(p, 2));
+  }
+  Py_XDECREF(p);
+  LEAVE(rc);
+}
+
+int b200_embed_image(b200_engine* e, const char* spec, const uint8_t* rgb, int width, int height, float** out, int* dim) {
+  ENTER();
+  PyObject* p = NULL;
+  int rc = call("embed_image", Py_BuildValue("(Lsy#ii)", e->handle, spec, (const char*)rgb, (Py_ssize_t)width * height * 3,
+                                             width, height), &p);
+  if (rc == 0) {   /* payload: (float32 bytes, dim) */
+    Py_ssize_t n = 0;
+    if (out) *out = (float*)dup_bytes(PyTuple_GetItem(p, 0), &n);
+    if (dim) *dim = (int)PyLong_AsLong(PyTuple_GetItem(p, 1));
+  }
+  Py_XDECREF(p);
+  LEAVE(rc);
+}
+
+int b200_upscale(b200_engine* e, const char* spec, const char* req, const uint8_t* rgb, int width, int height,
+                 uint8_t** rgb_out, int* width_out, int* height_out) {
+  ENTER();
+  PyObject* p = NULL;
+  int rc = call("upscale", Py_BuildValue("(Lssy#ii)", e->handle, spec, req ? req : "{}", (const char*)rgb,
+                                         (Py_ssize_t)width * height * 3, width, height), &p);
+  if (rc == 0) {   /* payload: (bytes, w, h) */
+    Py_ssize_t n = 0;
+    if (rgb_out) *rgb_out = dup_bytes(PyTuple_GetItem(p, 0), &n);
+    if (width_out) *width_out = (int)PyLong_AsLong(PyTuple_GetItem(p, 1));
+    if (height_out) *height_out = (int)PyLong_AsLong(PyTuple_GetItem(p, 2));
+  }
+  Py_XDECREF(p);
+  LEAVE(rc);
+}
+
 const char* b200_last_error(void) { return g_err; }
 void b200_free(void* p) { free(p); }
 const char* b200_version(void) { return "0.1.0"; }

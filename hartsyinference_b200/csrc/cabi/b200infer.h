@@ -48,6 +48,21 @@ int b200_image_generate(b200_engine* e, const char* spec_json, const char* reque
 int b200_video_generate(b200_engine* e, const char* spec_json, const char* request_json, b200_step_cb cb, void* user,
                         uint8_t** frames_out, int* frame_count, int* width, int* height, int* fps, long long* seed);
 
+/* Speech to text. pcm: mono float samples in [-1, 1] at sample_rate Hz. result_json_out: {"text", "language",
+   "duration", "segments": [{"start", "end", "text"}]}; released with b200_free(). */
+int b200_transcribe(b200_engine* e, const char* spec_json, const char* request_json, const float* pcm, long long samples,
+                    int sample_rate, char** result_json_out);
+/* Text to speech. pcm_out: mono float samples, released with b200_free(). */
+int b200_speak(b200_engine* e, const char* spec_json, const char* request_json, float** pcm_out, long long* samples_out,
+               int* sample_rate_out);
+/* Text embeddings. texts_json: a JSON array of strings. out: count * dim floats (row-major), released with b200_free(). */
+int b200_embed_text(b200_engine* e, const char* spec_json, const char* texts_json, float** out, int* count, int* dim);
+/* Image embedding of one RGB24 image. out: dim floats (L2-normalised), released with b200_free(). */
+int b200_embed_image(b200_engine* e, const char* spec_json, const uint8_t* rgb, int width, int height, float** out, int* dim);
+/* Upscale one RGB24 image. rgb_out: width_out * height_out * 3 bytes, released with b200_free(). */
+int b200_upscale(b200_engine* e, const char* spec_json, const char* request_json, const uint8_t* rgb, int width, int height,
+                 uint8_t** rgb_out, int* width_out, int* height_out);
+
 const char* b200_last_error(void);
 void b200_free(void* p);
 const char* b200_version(void);
