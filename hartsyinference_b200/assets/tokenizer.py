@@ -505,3 +505,85 @@ class ClipTokenizer:
             if end:
                 out += b" "
         return out.decode("utf-8", errors="replace").strip()
+
+
+class UnigramTokenizer:
+    """SentencePiece unigram model (T5 / umT5 / XLM-R style ``tokenizer.json`` with
+    ``model.type == "Unigram"``): the text is whitespace-normalised, spaces become U+2581 (with one
+    in front), and the most probable segmentation into vocabulary pieces is found by a Viterbi pass
+    over piece log-probabilities; characters no piece covers become the unknown id (merged when
+    adjacent). ``</s>`` is appended.
+
+    Reference: src/HartsyInference.ModelAssets/Tokenizers/ (SentencePiece unigram for T5)."""
+
+    SPACE = "▁"
+
+    def __init__(self, pieces: Sequence[tuple[str, float]], unk_id: int = 2, eos_id: Optional[int] = 1, add_prefix_space: bool = True,
+                 specials: Optional[dict[str, int]] = None):
+        self.pieces = [p for p, _ in pieces]
+        self.scores = [float(s) for _, s in pieces]
+        self.index = {p: i for i, p in enumerate(self.pieces)}
+        self.unk_id, self.eos_id, self.add_prefix_space = unk_id, eos_id, add_prefix_space
+        self.max_len = max((len(p) for p in self.pieces), default=1)
+        self.specials = dict(specials or {})
+        self.special_ids = set(self.specials.values())
+        # an unknown character costs more than any real piece, so known pieces always win
+        self.unk_score = min(self.scores, default=0.0) - 10.0
+
+    @staticmethod
+    def from_hf_json(path) -> "UnigramTokenizer":
+        data = json.loads(Path(path).read_text(encoding="utf-8"))
+        model = data["model"]
+        if model.get("type") != "Unigram":
+            raise ValueError("not a Unigram tokenizer.json")
+        specials = {a["content"]: a["id"] for a in data.get("added_tokens") or [] if a.get("special")}
+        eos = specials.get("</s>")
+        return UnigramTokenizer([(p, s) for p, s in model["vocab"]], unk_id=model.get("unk_id") or 0, eos_id=eos, specials=specials)
+
+    def _segment(self, text: str) -> list[int]:
+        n = len(text)
+        best = [float("-inf")] * (n + 1)
+        back: list[tuple[int, int]] = [(0, 0)] * (n + 1)
+        best[0] = 0.0
+        for i in range(n):
+            if best[i] == float("-inf"):
+                continue
+            for ln in range(1, min(self.max_len, n - i) + 1):
+                pid = self.index.get(text[i:i + ln])
+                if pid is None or pid in self.special_ids:
+                    continue
+                sc = best[i] + self.scores[pid]
+                if sc > best[i + ln]:
+                    best[i + ln], back[i + ln] = sc, (i, pid)
+            sc = best[i] + self.unk_score
+            if sc > best[i + 1]:
+                best[i + 1], back[i + 1] = sc, (i, self.unk_id)
+        ids: list[int] = []
+        pos = n
+        while pos > 0:
+            prev, pid = back[pos]
+            ids.append(pid)
+            pos = prev
+        ids.reverse()
+        out: list[int] = []
+        for t in ids:                              # runs of unknown characters collapse into one id
+            if t == self.unk_id and out and out[-1] == self.unk_id:
+                continue
+            out.append(t)
+        return out
+
+    def encode(self, text: str, add_special: bool = True) -> list[int]:
+        text = " ".join(text.split())
+        ids: list[int] = []
+        if text:
+            s = text.replace(" ", self.SPACE)
+            if self.add_prefix_space:
+                s = self.SPACE + s
+            ids = self._segment(s)
+        if add_special and self.eos_id is not None:
+            ids.append(self.eos_id)
+        return ids
+
+    def decode(self, ids: Iterable[int], skip_special: bool = True) -> str:
+        parts = [self.pieces[i] for i in ids if 0 <= i < len(self.pieces) and not (skip_special and i in self.special_ids)]
+        return "".join(parts).replace(self.SPACE, " ").strip()

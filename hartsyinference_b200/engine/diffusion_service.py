@@ -73,6 +73,31 @@ def _with_loras(get, keys, loras: tuple):
     return merged
 
 
+def _load_clip_text(d: Path, tok_dir: Path, device):
+    """(encoder, tokenizer) from a diffusers ``text_encoder*`` / ``tokenizer*`` pair, or (None, None)."""
+    import json as _json
+    from ..assets.tokenizer import ClipTokenizer
+    from ..models.encoders.clip import ClipTextEncoder, clip_text_from_hf
+    if not (d / "config.json").exists() or not ((tok_dir / "vocab.json").exists() or (tok_dir / "tokenizer.json").exists()):
+        return None, None
+    cfg = clip_text_from_hf(_json.loads((d / "config.json").read_text()))
+    return ClipTextEncoder(cfg, device, get=ShardedCheckpoint(d).get), ClipTokenizer.from_dir(tok_dir, cfg.max_len)
+
+
+def _load_t5(d: Path, tok_dir: Path, device, fp8: bool):
+    import json as _json
+    from ..assets.tokenizer import UnigramTokenizer
+    from ..models.encoders.t5 import T5Config, T5Encoder
+    if not (d / "config.json").exists() or not (tok_dir / "tokenizer.json").exists():
+        return None, None
+    c = _json.loads((d / "config.json").read_text())
+    cfg = T5Config(vocab_size=c["vocab_size"], d_model=c["d_model"], d_kv=c["d_kv"], d_ff=c["d_ff"], num_layers=c["num_layers"],
+                   num_heads=c["num_heads"], num_buckets=c.get("relative_attention_num_buckets", 32),
+                   max_distance=c.get("relative_attention_max_distance", 128), eps=c.get("layer_norm_epsilon", 1e-6),
+                   per_layer_bias=c.get("model_type") == "umt5")
+    return T5Encoder(cfg, device, fp8=fp8, get=ShardedCheckpoint(d).get), UnigramTokenizer.from_hf_json(tok_dir / "tokenizer.json")
+
+
 class ImagesService(_PipelineCache):
     def _build(self, spec: ModelSpec, loras: tuple = ()):
         from ..models.dit import flux as F
@@ -112,7 +137,15 @@ class ImagesService(_PipelineCache):
             vae = None
             if "vae" in spec.aux or (path / "vae").exists():
                 vae = Vae2dDecoder(SD3_VAE, self.device, get=ShardedCheckpoint(spec.aux.get("vae", path / "vae")).get)
-            return Sd3Pipeline(Sd3Components(S3.Sd3Transformer(cfg3, self.device, fp8=fp8, get=ck.get), vae))
+            comp = Sd3Components(S3.Sd3Transformer(cfg3, self.device, fp8=fp8, get=ck.get), vae)
+            cl, cl_tok = _load_clip_text(path / "text_encoder", path / "tokenizer", self.device)
+            cg, cg_tok = _load_clip_text(path / "text_encoder_2", path / "tokenizer_2", self.device)
+            t5, t5_tok = _load_t5(path / "text_encoder_3", path / "tokenizer_3", self.device, fp8)
+            if cl is not None and cg is not None and t5 is not None:
+                clip_fn = lambda enc, tok: (lambda prompt: enc.encode(torch.tensor(tok.encode(prompt, pad=True)), layer=-2, project=True))
+                comp.clip_l, comp.clip_g = clip_fn(cl, cl_tok), clip_fn(cg, cg_tok)
+                comp.t5 = lambda prompt: t5.encode(torch.tensor((t5_tok.encode(prompt)[:256] + [0] * 256)[:256]))
+            return Sd3Pipeline(comp)
         # adapters are merged in the checkpoint's own layout (their module names follow it)
         get = _with_loras(ck.get, list(ck.keys()), loras)
         from ..assets.converters import flux_original_to_diffusers, is_flux_original
@@ -136,7 +169,10 @@ class ImagesService(_PipelineCache):
             cc = _json.loads((cdir / "config.json").read_text()) if (cdir / "config.json").exists() else {}
             ccfg = F.FluxConfig(num_double_blocks=int(cc.get("num_layers", 5)), num_single_blocks=int(cc.get("num_single_layers", 10)))
             cnet = FluxControlNet(ccfg, self.device, fp8=fp8, get=ShardedCheckpoint(cdir).get)
-        return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc, controlnet=cnet))
+        comp = FluxComponents(tr, vae, vae_encoder=enc, controlnet=cnet)
+        comp.clip, comp.clip_tokenizer = _load_clip_text(path / "text_encoder", path / "tokenizer", self.device)
+        comp.t5, comp.t5_tokenizer = _load_t5(path / "text_encoder_2", path / "tokenizer_2", self.device, fp8)
+        return FluxPipeline(comp)
 
     def pipeline(self, spec: ModelSpec, loras: tuple = ()):
         k = self.key(spec, loras)

@@ -25,6 +25,16 @@ class ClipTextConfig:
 
 
 CLIP_L = ClipTextConfig()
+# OpenCLIP bigG text tower (SDXL / SD3 second encoder): GELU, projection to 1280
+CLIP_G = ClipTextConfig(width=1280, layers=32, heads=20, quick_gelu=False)
+
+
+def clip_text_from_hf(d: dict) -> ClipTextConfig:
+    width = d.get("hidden_size", 768)
+    return ClipTextConfig(vocab_size=d.get("vocab_size", 49408), width=width, layers=d.get("num_hidden_layers", 12),
+                          heads=d.get("num_attention_heads", 12), max_len=d.get("max_position_embeddings", 77),
+                          mlp_ratio=d.get("intermediate_size", 4 * width) // width, eps=d.get("layer_norm_eps", 1e-5),
+                          quick_gelu=d.get("hidden_act", "quick_gelu") == "quick_gelu")
 
 
 def tiny_clip() -> ClipTextConfig:
@@ -51,16 +61,26 @@ class ClipTextEncoder:
                 fc1=f.linear(p + "mlp.fc1", cfg.mlp_ratio * W, W), fc2=f.linear(p + "mlp.fc2", W, cfg.mlp_ratio * W)))
         self.lnfw = f.tensor(p0 + "final_layer_norm.weight", W, ones=True)
         self.lnfb = f.tensor(p0 + "final_layer_norm.bias", W, zeros=True)
+        # CLIPTextModelWithProjection checkpoints carry the projection of the pooled vector
+        proj = get("text_projection.weight") if get is not None else None
+        self.projection = None if proj is None else proj.float().to(self.device)
 
     @torch.no_grad()
-    def encode(self, ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-        """ids [L] -> (hidden [L, W], pooled [W]); pooled is taken at the highest token id (end of text)."""
+    def encode(self, ids: torch.Tensor, layer: int = -1, project: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+        """ids [L] -> (hidden [L, W], pooled [W]); pooled is taken at the highest token id (end of text)
+        after the final LayerNorm. ``layer`` = -2 returns the states after the second-to-last block
+        without the final norm (what SDXL / SD3 condition on); ``project`` applies the checkpoint's
+        text projection to the pooled vector."""
         cfg = self.cfg
         L = ids.shape[0]
         ids = ids.long().to(self.device)
         x = (self.tok[ids].float() + self.pos[:L].float()).to(torch.bfloat16)
         d = cfg.width // cfg.heads
-        for b in self.blocks:
+        tapped = None
+        stop = cfg.layers + layer + 1 if layer < 0 else layer
+        for bi, b in enumerate(self.blocks):
+            if bi == stop:
+                tapped = x
             h, _, _ = ops.norm(x, b["ln1w"], bias=b["ln1b"], layernorm=True, eps=cfg.eps)
             qkv = ops.linear(h, b["qkv"])
             q, k, v = ops.dit_qkv(qkv, cfg.heads, cfg.heads, d)
@@ -71,4 +91,7 @@ class ClipTextEncoder:
             m = (m * torch.sigmoid(1.702 * m)) if cfg.quick_gelu else torch.nn.functional.gelu(m)
             x = ops.linear(m.to(torch.bfloat16), b["fc2"], residual=x)
         out, _, _ = ops.norm(x, self.lnfw, bias=self.lnfb, layernorm=True, eps=cfg.eps)
-        return out, out[int(ids.argmax())]
+        pooled = out[int(ids.argmax())]
+        if project and self.projection is not None:
+            pooled = (pooled.float() @ self.projection.t()).to(out.dtype)
+        return (out if tapped is None else tapped), pooled

@@ -12,6 +12,7 @@ whose conditioning changed little.
 from __future__ import annotations
 
 import time
+import zlib
 from dataclasses import dataclass
 from typing import Callable, Optional
 
@@ -63,7 +64,7 @@ class FluxPipeline:
         tdim, pdim = c.transformer.cfg.context_dim, c.transformer.cfg.pooled_dim
         if c.t5 is None or c.t5_tokenizer is None:
             # synthetic conditioning (no text encoder loaded): deterministic N(0, 1) from the prompt text
-            g = torch.Generator().manual_seed(abs(hash(prompt)) % (2 ** 31))
+            g = torch.Generator().manual_seed(zlib.crc32(prompt.encode("utf-8")) % (2 ** 31))
             return torch.randn(max_len, tdim, generator=g), torch.randn(pdim, generator=g)
         ids = torch.tensor(c.t5_tokenizer.encode(prompt)[:max_len], dtype=torch.int64)
         ctx = c.t5.encode(ids)

@@ -12,6 +12,7 @@ Reference: src/HartsyInference.Diffusion/Pipelines/Sd3Pipeline.cs.
 from __future__ import annotations
 
 import time
+import zlib
 from dataclasses import dataclass
 from typing import Callable, Optional
 
@@ -54,7 +55,7 @@ class Sd3Pipeline:
         c = self.c
         cfg = c.transformer.cfg
         if c.clip_l is None or c.clip_g is None or c.t5 is None:
-            g = torch.Generator().manual_seed(abs(hash(("sd3", prompt))) % (2 ** 31))
+            g = torch.Generator().manual_seed(zlib.crc32(("sd3:" + prompt).encode("utf-8")) % (2 ** 31))
             return torch.randn(max_len, cfg.context_dim, generator=g), torch.randn(cfg.pooled_dim, generator=g)
         return join_conditioning(c.clip_l(prompt), c.clip_g(prompt), c.t5(prompt), cfg.context_dim)
 

@@ -10,6 +10,7 @@ groups apply the same update and stay in lock-step)."""
 from __future__ import annotations
 
 import time
+import zlib
 from dataclasses import dataclass
 from typing import Callable, Optional
 
@@ -43,7 +44,7 @@ class WanPipeline:
     def encode_prompt(self, prompt: str) -> torch.Tensor:
         cfg = self.c.transformer.cfg
         if self.c.text_encoder is None or self.c.tokenizer is None:
-            g = torch.Generator().manual_seed(abs(hash(prompt)) % (2 ** 31))
+            g = torch.Generator().manual_seed(zlib.crc32(prompt.encode("utf-8")) % (2 ** 31))
             return torch.randn(cfg.text_len, cfg.text_dim, generator=g)
         ids = torch.tensor(self.c.tokenizer.encode(prompt)[: cfg.text_len], dtype=torch.int64)
         ctx = self.c.text_encoder.encode(ids)

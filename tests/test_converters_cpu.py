@@ -106,3 +106,60 @@ def test_image_service_merges_loras_into_a_flux_checkpoint(tmp_path, monkeypatch
     with pytest.raises(UnsupportedModelError):
         eng.images.generate(ModelSpec("synthetic:flux-tiny"), ImageRequest(prompt="x", loras=[("a.safetensors", 1.0)]))
     eng.close()
+
+
+def test_flux_directory_with_text_encoders(tmp_path, monkeypatch):
+    """A diffusers-layout directory: transformer + CLIP text tower + T5 with their tokenizers. The
+    prompt then conditions the image through the real encoders."""
+    import json
+    import pytest
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.assets.safetensors import save_file
+    from hartsyinference_b200.assets.tokenizer import _bytes_to_unicode
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec
+    from hartsyinference_b200.engine.requests import ImageRequest
+    cfg = F.tiny_flux(context_dim=64, pooled_dim=64)
+    monkeypatch.setattr(F, "FLUX_DEV", cfg)
+    d = tmp_path / "flux"
+    (d / "transformer").mkdir(parents=True)
+    save_file({k: v.to(torch.bfloat16).contiguous() for k, v in _diffusers_state(cfg).items()}, d / "transformer" / "model.safetensors")
+    # CLIP text tower (pooled 64) with a byte-level vocabulary
+    b2u = _bytes_to_unicode()
+    vocab = {}
+    for b in range(256):
+        vocab[b2u[b]] = len(vocab)
+    for b in range(256):
+        vocab[b2u[b] + "</w>"] = len(vocab)
+    vocab["<|startoftext|>"], vocab["<|endoftext|>"] = len(vocab), len(vocab) + 1
+    hc = tr.CLIPTextConfig(vocab_size=len(vocab), hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+                           max_position_embeddings=24, eos_token_id=len(vocab) - 1, bos_token_id=len(vocab) - 2, pad_token_id=len(vocab) - 1)
+    torch.manual_seed(0)
+    (d / "text_encoder").mkdir()
+    (d / "tokenizer").mkdir()
+    save_file({k: v.detach().contiguous() for k, v in tr.CLIPTextModel(hc).state_dict().items() if "position_ids" not in k},
+              d / "text_encoder" / "model.safetensors")
+    (d / "text_encoder" / "config.json").write_text(json.dumps(hc.to_dict()))
+    (d / "tokenizer" / "vocab.json").write_text(json.dumps(vocab))
+    (d / "tokenizer" / "merges.txt").write_text("#version: 0.2\n")
+    # T5 encoder (d_model 64 = the transformer's context width) with a unigram vocabulary
+    tc = tr.T5Config(vocab_size=40, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_heads=4, feed_forward_proj="gated-gelu")
+    (d / "text_encoder_2").mkdir()
+    (d / "tokenizer_2").mkdir()
+    save_file({k: v.detach().contiguous() for k, v in tr.T5EncoderModel(tc).state_dict().items()}, d / "text_encoder_2" / "model.safetensors")
+    (d / "text_encoder_2" / "config.json").write_text(json.dumps(tc.to_dict()))
+    pieces = [["<pad>", 0.0], ["</s>", 0.0], ["<unk>", 0.0], ["▁", -2.0]] + [[ch, -3.0 - i * 0.01] for i, ch in enumerate("abcdefghijklmnopqrstuvwxyz")]
+    (d / "tokenizer_2" / "tokenizer.json").write_text(json.dumps({
+        "model": {"type": "Unigram", "unk_id": 2, "vocab": pieces},
+        "added_tokens": [{"id": 0, "content": "<pad>", "special": True}, {"id": 1, "content": "</s>", "special": True},
+                         {"id": 2, "content": "<unk>", "special": True}]}))
+    eng = InferenceEngine("cpu")
+    pipe = eng.images.pipeline(ModelSpec(str(d)))
+    assert pipe.c.t5 is not None and pipe.c.clip is not None
+    ctx_a, pooled_a = pipe.encode_prompt("a red fox", max_len=16)
+    ctx_b, pooled_b = pipe.encode_prompt("a blue whale", max_len=16)
+    assert ctx_a.shape == (16, 64) and pooled_a.shape == (64,)
+    assert not torch.allclose(ctx_a.float(), ctx_b.float()) and not torch.allclose(pooled_a.float(), pooled_b.float())
+    assert torch.equal(ctx_a, pipe.encode_prompt("a red fox", max_len=16)[0])
+    res = eng.images.generate(ModelSpec(str(d)), ImageRequest(prompt="a red fox", width=32, height=32, steps=1, seed=1))
+    assert (res.width, res.height) == (32, 32)
+    eng.close()

@@ -84,3 +84,25 @@ def test_byte_tokenizer_and_chat_template():
     assert l3.startswith("<|begin_of_text|><|start_header_id|>user<|end_header_id|>\n\nhi<|eot_id|>")
     with pytest.raises(Exception):
         ChatTemplate("{{ raise_exception('no') }}").render([])
+
+
+def test_unigram_tokenizer_matches_the_tokenizers_library(tmp_path):
+    import pytest
+    tk = pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer as HfTok, decoders, models, normalizers, pre_tokenizers, processors
+    from hartsyinference_b200.assets.tokenizer import UnigramTokenizer
+    sp = "▁"
+    vocab = [("<pad>", 0.0), ("</s>", 0.0), ("<unk>", 0.0), (sp, -2.0), (sp + "the", -3.0), (sp + "cat", -5.0), ("s", -3.5), (sp + "sat", -6.0),
+             (sp + "on", -4.5), ("a", -3.2), ("t", -3.3), ("c", -4.0), ("h", -4.1), ("e", -3.0), ("n", -3.6), ("o", -3.4), (sp + "mat", -7.0),
+             ("at", -4.2), (sp + "c", -5.5), ("the", -4.8), (sp + "t", -4.4), ("m", -4.6), (".", -3.9), ("on", -4.9), ("ca", -6.5), ("ts", -6.0)]
+    hf = HfTok(models.Unigram(vocab, unk_id=2))
+    hf.normalizer = normalizers.Sequence([normalizers.Replace(tk.Regex(" {2,}"), " ")])
+    hf.pre_tokenizer = pre_tokenizers.Metaspace(replacement=sp, prepend_scheme="always")
+    hf.post_processor = processors.TemplateProcessing(single="$A </s>", special_tokens=[("</s>", 1)])
+    hf.decoder = decoders.Metaspace(replacement=sp, prepend_scheme="always")
+    hf.add_special_tokens(["<pad>", "</s>", "<unk>"])
+    hf.save(str(tmp_path / "tokenizer.json"))
+    mine = UnigramTokenizer.from_hf_json(tmp_path / "tokenizer.json")
+    for text in ["the cat sat on the mat.", "cats", "the  cats   on a mat", "that", "the zebra", ""]:
+        assert mine.encode(text) == hf.encode(text).ids, text
+    assert mine.decode(mine.encode("the cat sat")) == "the cat sat"

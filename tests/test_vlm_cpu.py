@@ -399,3 +399,26 @@ def test_llava_next_checkpoint_through_text_service(tmp_path):
         assert type(eng.text._host(ModelSpec(str(d))).llm.vlm).__name__ == "LlavaNextModel"
     finally:
         eng.text.release()
+
+
+def test_clip_text_penultimate_states_and_projection():
+    """What SDXL / SD3 take from a CLIP text tower: hidden_states[-2] and the projected pooled vector."""
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.encoders.clip import ClipTextEncoder, clip_text_from_hf
+    hc = tr.CLIPTextConfig(vocab_size=128, hidden_size=64, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                           max_position_embeddings=16, hidden_act="gelu", projection_dim=32, eos_token_id=127, bos_token_id=126, pad_token_id=127)
+    torch.manual_seed(0)
+    hf = tr.CLIPTextModelWithProjection(hc).eval()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    cfg = clip_text_from_hf(hc.to_dict())
+    assert not cfg.quick_gelu and cfg.layers == 3
+    enc = ClipTextEncoder(cfg, "cpu", get=lambda n: sd.get(n))
+    ids = torch.tensor([126, 5, 9, 33, 127])
+    with torch.no_grad():
+        out = hf(input_ids=ids[None], output_hidden_states=True)
+    states, pooled = enc.encode(ids, layer=-2, project=True)
+    cos = lambda a, b: torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0)
+    assert cos(states, out.hidden_states[-2][0]) > 0.995
+    assert pooled.shape == (32,) and cos(pooled, out.text_embeds[0]) > 0.995
+    last, _ = enc.encode(ids)
+    assert cos(last, out.last_hidden_state[0]) > 0.995
