@@ -205,12 +205,18 @@ class VideoService(_PipelineCache):
         path = Path(spec.local_path or name)
         if not path.exists():
             raise UnsupportedModelError(f"{name}: no such checkpoint")
-        ck = ShardedCheckpoint(path)
+        # a diffusers-layout directory keeps the transformer, VAE, umT5 encoder and tokenizer in sub-folders
+        ck = ShardedCheckpoint(path / "transformer" if (path / "transformer").exists() else path)
         tr = W.WanTransformer(W.WAN_14B, self.device, fp8=fp8, get=ck.get)
         vae = None
-        if "vae" in spec.aux:
-            vae = Vae3dDecoder(WAN_VAE, self.device, dt, get=ShardedCheckpoint(spec.aux["vae"]).get)
-        return WanPipeline(WanComponents(tr, vae))
+        vae_dir = spec.aux.get("vae") or (str(path / "vae") if (path / "vae").exists() else None)
+        if vae_dir:
+            vae = Vae3dDecoder(WAN_VAE, self.device, dt, get=ShardedCheckpoint(vae_dir).get)
+        comp = WanComponents(tr, vae)
+        te_dir = Path(spec.aux["text_encoder"]) if "text_encoder" in spec.aux else path / "text_encoder"
+        tok_dir = te_dir if (te_dir / "tokenizer.json").exists() else path / "tokenizer"
+        comp.text_encoder, comp.tokenizer = _load_t5(te_dir, tok_dir, self.device, fp8)
+        return WanPipeline(comp)
 
     def pipeline(self, spec: ModelSpec):
         k = self.key(spec)
