@@ -66,8 +66,21 @@ class FluxPipeline:
             # synthetic conditioning (no text encoder loaded): deterministic N(0, 1) from the prompt text
             g = torch.Generator().manual_seed(zlib.crc32(prompt.encode("utf-8")) % (2 ** 31))
             return torch.randn(max_len, tdim, generator=g), torch.randn(pdim, generator=g)
-        ids = torch.tensor(c.t5_tokenizer.encode(prompt)[:max_len], dtype=torch.int64)
+        from ..models.diffusion.prompt_weighting import apply_token_weights, parse_prompt_weights, token_weights
+        runs = parse_prompt_weights(prompt)
+        prompt = "".join(t for t, _ in runs)            # the text without the weighting syntax
+        weights: list[float] = []
+        if len(runs) > 1 or runs[0][1] != 1.0:
+            # weighted prompt: tokenise run by run so every token knows its weight; the encoders see the plain text
+            tok = c.t5_tokenizer
+            piece_ids, weights = token_weights(runs, lambda t: tok.encode(t, add_special=False), max_len - 1)
+            eos = tok.encode("", add_special=True)
+            ids = torch.tensor(piece_ids + eos, dtype=torch.int64)
+        else:
+            ids = torch.tensor(c.t5_tokenizer.encode(prompt)[:max_len], dtype=torch.int64)
         ctx = c.t5.encode(ids)
+        if weights:
+            ctx = apply_token_weights(ctx, weights)
         if ctx.shape[0] < max_len:
             ctx = torch.cat([ctx, torch.zeros(max_len - ctx.shape[0], ctx.shape[1], dtype=ctx.dtype, device=ctx.device)])
         pooled = torch.zeros(pdim)

@@ -163,3 +163,24 @@ def test_flux_directory_with_text_encoders(tmp_path, monkeypatch):
     res = eng.images.generate(ModelSpec(str(d)), ImageRequest(prompt="a red fox", width=32, height=32, steps=1, seed=1))
     assert (res.width, res.height) == (32, 32)
     eng.close()
+
+
+def test_weighted_prompt_reaches_the_t5_states():
+    """With a T5 stack loaded, ``(word:w)`` scales that word's token states and leaves the plain text otherwise."""
+    import pytest
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.assets.tokenizer import UnigramTokenizer
+    from hartsyinference_b200.models.encoders.t5 import T5Config, T5Encoder
+    from hartsyinference_b200.pipelines.flux import FluxComponents, FluxPipeline
+    cfg = F.tiny_flux(context_dim=64, pooled_dim=32)
+    pieces = [("<pad>", 0.0), ("</s>", 0.0), ("<unk>", 0.0), ("▁", -2.0)] + [(ch, -3.0) for ch in "abcdefghijklmnopqrstuvwxyz"]
+    tok = UnigramTokenizer(pieces, unk_id=2, eos_id=1, specials={"<pad>": 0, "</s>": 1, "<unk>": 2})
+    t5 = T5Encoder(T5Config(vocab_size=40, d_model=64, d_kv=16, d_ff=128, num_layers=1, num_heads=4), "cpu", seed=1)
+    pipe = FluxPipeline(FluxComponents(F.FluxTransformer(cfg, "cpu", seed=0), t5=t5, t5_tokenizer=tok))
+    plain, _ = pipe.encode_prompt("a red fox", max_len=24)
+    same, _ = pipe.encode_prompt("a (red:1.0) fox", max_len=24)
+    heavy, _ = pipe.encode_prompt("a (red:2.0) fox", max_len=24)
+    assert plain.shape == heavy.shape == (24, 64)
+    assert not torch.allclose(plain.float(), heavy.float(), atol=1e-3)
+    # the weighted and the plain prompt tokenise to the same pieces here, so weight 1.0 changes nothing
+    assert torch.allclose(plain.float(), same.float(), atol=1e-2)

@@ -273,3 +273,25 @@ def test_flux_pipeline_with_controlnet():
     import pytest
     with pytest.raises(ValueError):
         pipe.generate(ImageRequest(prompt="a tower", width=64, height=64, steps=1, control_image=edges))
+
+
+def test_prompt_weighting():
+    import torch
+    from hartsyinference_b200.models.diffusion.prompt_weighting import apply_token_weights, parse_prompt_weights, token_weights
+    P = parse_prompt_weights
+    assert P("a red fox") == [("a red fox", 1.0)]
+    assert P("a (red:1.5) fox") == [("a ", 1.0), ("red", 1.5), (" fox", 1.0)]
+    r = P("((very)) [dull] sky")
+    assert r[0][0] == "very" and abs(r[0][1] - 1.21) < 1e-9 and r[2][0] == "dull" and abs(r[2][1] - 1 / 1.1) < 1e-9
+    assert P(r"literal \(paren\) here") == [("literal (paren) here", 1.0)]
+    nested = P("(a (b:2):1.5)")
+    assert nested == [("a ", 1.5), ("b", 3.0)]
+    assert P("(unclosed") == [("unclosed", 1.1)] and P("time: 12:30") == [("time: 12:30", 1.0)]
+    ids, ws = token_weights([("ab", 1.0), ("cd", 2.0)], lambda t: [ord(c) for c in t], 3)
+    assert ids == [97, 98, 99] and ws == [1.0, 1.0, 2.0]
+    x = torch.randn(6, 8, generator=torch.Generator().manual_seed(0)) + 0.5
+    y = apply_token_weights(x, [1.0, 2.0, 1.0])
+    assert abs(float(y.mean()) - float(x.mean())) < 1e-5
+    ratio = y[1].norm() / y[0].norm() / (x[1].norm() / x[0].norm())
+    assert abs(float(ratio) - 2.0) < 1e-4
+    assert apply_token_weights(x, [1.0, 1.0]) is x
