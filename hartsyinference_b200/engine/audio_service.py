@@ -58,7 +58,12 @@ class TranscribeService:
         path = spec.local_path or spec.requested
         with self._lock:
             if path not in self._loaded:
-                self._loaded[path] = WhisperPipeline.from_pretrained(path, self.device)
+                import json
+                from ..pipelines.whisper import MoonshinePipeline
+                cfg_file = Path(path) / "config.json"
+                kind = json.loads(cfg_file.read_text()).get("model_type", "whisper") if cfg_file.exists() else "whisper"
+                cls = MoonshinePipeline if kind == "moonshine" else WhisperPipeline
+                self._loaded[path] = cls.from_pretrained(path, self.device)
             return self._loaded[path]
 
     def run(self, spec: ModelSpec, req: AudioRequest) -> TranscriptResult:

@@ -261,3 +261,50 @@ class WhisperPipeline:
             seek += max(int(round(advance * SAMPLE_RATE)), HOP * 2)
         res.text = "".join(s.text for s in res.segments).strip() if self.tokenizer is not None else " ".join(s.text for s in res.segments)
         return res
+
+
+class MoonshinePipeline:
+    """Moonshine speech recognition over raw audio: resample to 16 kHz, cut long recordings into
+    windows at the quietest point near each boundary, greedy-decode each window.
+    Reference: src/HartsyInference.Audio/Pipelines/MoonshinePipeline.cs, MoonshineOptions.cs."""
+
+    def __init__(self, model, tokenizer=None, window_s: float = 30.0):
+        self.model, self.tokenizer, self.window_s = model, tokenizer, window_s
+
+    @staticmethod
+    def from_pretrained(path, device="cuda") -> "MoonshinePipeline":
+        from ..assets.safetensors import ShardedCheckpoint
+        from ..assets.tokenizer import Tokenizer
+        from ..models.audio.moonshine import MoonshineModel, moonshine_from_hf
+        p = Path(path)
+        raw = json.loads((p / "config.json").read_text())
+        tok = Tokenizer.from_hf_json(p / "tokenizer.json") if (p / "tokenizer.json").exists() else None
+        return MoonshinePipeline(MoonshineModel(moonshine_from_hf(raw), device, get=ShardedCheckpoint(p).get), tok)
+
+    def _windows(self, x: torch.Tensor) -> list[tuple[int, int]]:
+        n, w = x.numel(), int(self.window_s * SAMPLE_RATE)
+        out, start = [], 0
+        while n - start > w:
+            lo = start + int(0.8 * w)                      # look for a quiet 20 ms frame in the window's last fifth
+            frames = x[lo:start + w].abs().unfold(0, 320, 320).mean(-1)
+            cut = lo + int(frames.argmin()) * 320 + 160
+            out.append((start, cut))
+            start = cut
+        out.append((start, n))
+        return out
+
+    @torch.no_grad()
+    def transcribe(self, audio: torch.Tensor, rate: int = SAMPLE_RATE, options: Optional[WhisperOptions] = None) -> TranscriptResult:
+        x = audio.float()
+        if x.ndim == 2:
+            x = x.mean(0)
+        x = resample(x, rate, SAMPLE_RATE)
+        res = TranscriptResult(duration_s=x.numel() / SAMPLE_RATE, language="en")
+        for a, b in self._windows(x):
+            if b - a < 1024:                                # shorter than the first convolution's reach
+                continue
+            toks = self.model.transcribe_tokens(x[a:b], (options.max_new_tokens or None) if options else None)
+            text = self.tokenizer.decode(toks) if self.tokenizer is not None else " ".join(str(t) for t in toks)
+            res.segments.append(WhisperSegment(a / SAMPLE_RATE, b / SAMPLE_RATE, text, toks))
+        res.text = " ".join(s.text.strip() for s in res.segments).strip()
+        return res

@@ -287,3 +287,49 @@ def test_speech_service_endpoint_and_cli(tmp_path):
     r = CliRunner().invoke(cli, ["speak", str(d), "hello", "--out", str(out), "--device", "cpu"])
     assert r.exit_code == 0, r.output
     assert read_wav(out)[1] == 16000
+
+
+def test_moonshine_matches_transformers_and_serves(tmp_path):
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.engine import AudioRequest, InferenceEngine, ModelSpec
+    from hartsyinference_b200.models.audio.moonshine import MoonshineModel, moonshine_from_hf, tiny_moonshine
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    c = tr.MoonshineConfig(vocab_size=300, hidden_size=64, intermediate_size=128, encoder_num_hidden_layers=2, decoder_num_hidden_layers=2,
+                           encoder_num_attention_heads=2, decoder_num_attention_heads=2, max_position_embeddings=128)
+    torch.manual_seed(0)
+    hf = tr.MoonshineForConditionalGeneration(c).eval()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.ndim >= 2:
+                p.mul_(2.0)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    cfg = moonshine_from_hf(c.to_dict())
+    assert cfg == tiny_moonshine()
+    m = MoonshineModel(cfg, "cpu", get=lambda n: sd.get(n))
+    audio = torch.randn(16000, generator=torch.Generator().manual_seed(1)) * 0.1
+    toks = torch.tensor([1, 10, 20, 30, 40])
+    with torch.no_grad():
+        ref = hf(input_values=audio[None], decoder_input_ids=toks[None])
+    enc = m.encode(audio)
+    assert enc.shape == ref.encoder_last_hidden_state[0].shape == (40, 64)
+    assert torch.allclose(enc, ref.encoder_last_hidden_state[0], atol=1e-4)
+    st = m.start(enc)
+    mine = torch.cat([m.decode(st, toks[:3]), m.decode(st, toks[3:4]), m.decode(st, toks[4:])])
+    assert torch.allclose(mine, ref.logits[0], atol=1e-3) and st["pos"] == 5
+    with torch.no_grad():
+        gen = hf.generate(input_values=audio[None], max_new_tokens=6, do_sample=False)[0].tolist()
+    assert m.transcribe_tokens(audio, max_tokens=6) == [t for t in gen[1:] if t != cfg.eos_id][:6]
+
+    d = tmp_path / "moonshine"
+    save_hf_checkpoint({**c.to_dict(), "model_type": "moonshine"}, {k: v.contiguous() for k, v in sd.items() if k != "proj_out.weight"}, d)
+    eng = InferenceEngine("cpu")
+    long_audio = torch.randn(16000 * 3, generator=torch.Generator().manual_seed(2)) * 0.1
+    res = eng.transcribe.run(ModelSpec(str(d)), AudioRequest(audio=long_audio, sample_rate=16000))
+    assert abs(res.duration_s - 3.0) < 1e-6 and len(res.segments) == 1 and res.segments[0].tokens
+    pipe = eng.transcribe._pipe(ModelSpec(str(d)))
+    assert type(pipe).__name__ == "MoonshinePipeline"
+    pipe.window_s = 1.0
+    cuts = pipe._windows(long_audio)
+    assert len(cuts) >= 3 and cuts[0][0] == 0 and cuts[-1][1] == long_audio.numel() and all(a < b for a, b in cuts)
+    assert all(cuts[i][1] == cuts[i + 1][0] for i in range(len(cuts) - 1))
+    eng.close()
