@@ -306,3 +306,28 @@ def test_mamba2_matches_transformers_and_state_carries_over(groups):
     assert (mine.argmax(-1) == ref.argmax(-1)).float().mean() > 0.9
     out = m.generate(ids[:5].tolist(), max_tokens=4, stop_at_eos=False)
     assert len(out) == 4
+
+
+def test_rwkv_matches_transformers_and_state_carries_over():
+    transformers = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.ssm import RwkvModel, rwkv_from_hf
+    c = transformers.RwkvConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, attention_hidden_size=64, intermediate_size=128,
+                                context_length=64, rescale_every=0)
+    torch.manual_seed(0)
+    hf = transformers.RwkvForCausalLM(c).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim == 2:
+                p.mul_(3.0)
+            if "time_decay" in n or "time_first" in n:
+                p.copy_(torch.randn_like(p) * 0.5)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    m = RwkvModel(rwkv_from_hf(c.to_dict()), "cpu", get=lambda n: sd.get(n))
+    ids = torch.randint(0, 300, (17,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(ids[None]).logits[0]
+    st = m.new_state()
+    mine = torch.cat([m.logits(m.forward(ids[:9], st)), m.logits(m.forward(ids[9:10], st)), m.logits(m.forward(ids[10:], st))])
+    assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0) > 0.999
+    assert (mine.argmax(-1) == ref.argmax(-1)).float().mean() > 0.9
+    assert len(m.generate(ids[:4].tolist(), max_tokens=3, stop_at_eos=False)) == 3
