@@ -117,9 +117,8 @@ class GgufFile:
         n = C.c_uint64()
         ptr = self._L.b200_gguf_data(self._h, i, C.byref(n))
         buf = (C.c_uint8 * n.value).from_address(ptr)
-        t = torch.from_numpy(np.frombuffer(buf, dtype=np.uint8))
-        t._keepalive = self
-        return t
+        buf._mapping_owner = self        # storage -> numpy array -> buf -> file: every view keeps the mapping alive
+        return torch.from_numpy(np.frombuffer(buf, dtype=np.uint8))
 
     def get(self, name: str, dtype: torch.dtype = torch.float32) -> torch.Tensor:
         """Dequantised tensor in row-major shape."""

@@ -66,10 +66,11 @@ class SafeTensorsFile:
         if nbytes.value == 0:
             return torch.empty(shape, dtype=_DTYPES[dt])
         buf = (C.c_uint8 * nbytes.value).from_address(ptr)
+        # The mapping must outlive every view of these bytes, not just the tensor object returned
+        # here: the storage keeps the numpy array, the array keeps ``buf``, and ``buf`` keeps the file.
+        buf._mapping_owner = self
         arr = np.frombuffer(buf, dtype=np.uint8)
-        t = torch.from_numpy(arr).view(_DTYPES[dt]).reshape(shape)
-        t._keepalive = self                      # the mapping must outlive the view
-        return t
+        return torch.from_numpy(arr).view(_DTYPES[dt]).reshape(shape)
 
     def close(self) -> None:
         if self._h:

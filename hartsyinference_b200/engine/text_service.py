@@ -49,6 +49,7 @@ class TextService:
         self.device = device
         self.comm = comm
         self._models: dict[str, _Hosted] = {}
+        self._ssm: dict[str, tuple] = {}
         self._lock = threading.Lock()
 
     # ------------------------------------------------------------------------------ loading
@@ -71,13 +72,17 @@ class TextService:
             return h
 
     def loaded_keys(self) -> list[str]:
-        return list(self._models)
+        return list(self._models) + list(self._ssm)
 
     def unhealthy_models(self) -> list[str]:
         return [k for k, h in self._models.items() if not h.healthy or not (h.thread and h.thread.is_alive())]
 
     def release(self, key: Optional[str] = None) -> None:
         with self._lock:
+            if key is None:
+                self._ssm.clear()
+            else:
+                self._ssm.pop(key, None)
             keys = [key] if key else list(self._models)
             for k in keys:
                 h = self._models.pop(k, None)
@@ -169,7 +174,96 @@ class TextService:
             t = t.permute(2, 0, 1)
         return t.float().clamp(0, 1)
 
+    # ------------------------------------------------------------------------------ recurrent models
+    SSM_TYPES = ("mamba", "mamba2", "rwkv")
+
+    def _ssm_kind(self, spec: ModelSpec) -> Optional[str]:
+        import json
+        from pathlib import Path
+        cfg = Path(spec.local_path or spec.requested) / "config.json"
+        if not cfg.exists():
+            return None
+        try:
+            mt = json.loads(cfg.read_text()).get("model_type")
+        except Exception:
+            return None
+        return mt if mt in self.SSM_TYPES else None
+
+    def _ssm_host(self, spec: ModelSpec, kind: str):
+        """State-space / RWKV checkpoints: a model with constant-size recurrent state instead of a
+        paged KV cache (the reference's SsmGenerationPipeline). One request at a time per model."""
+        import json
+        from pathlib import Path
+        from ..assets.chat_template import ChatTemplate
+        from ..assets.safetensors import ShardedCheckpoint
+        from ..assets.tokenizer import ByteTokenizer, Tokenizer
+        from ..models import ssm as S
+        path = Path(spec.local_path or spec.requested)
+        key = f"ssm|{path}|{self.device}"
+        with self._lock:
+            if key not in self._ssm:
+                raw = json.loads((path / "config.json").read_text())
+                get = ShardedCheckpoint(path).get
+                if kind == "mamba":
+                    cfg = S.MambaConfig(vocab_size=raw["vocab_size"], d_model=raw["hidden_size"], n_layer=raw["num_hidden_layers"],
+                                        d_state=raw.get("state_size", 16), d_conv=raw.get("conv_kernel", 4), expand=raw.get("expand", 2),
+                                        dt_rank=raw["time_step_rank"] if isinstance(raw.get("time_step_rank"), int) else 0,
+                                        rms_eps=raw.get("layer_norm_epsilon", 1e-5), eos_token_id=raw.get("eos_token_id", 0) or 0)
+                    model = S.MambaModel(cfg, self.device, get=get)
+                elif kind == "mamba2":
+                    model = S.Mamba2Model(S.mamba2_from_hf(raw), self.device, get=get)
+                else:
+                    model = S.RwkvModel(S.rwkv_from_hf(raw), self.device, get=get)
+                tok = Tokenizer.from_hf_json(path / "tokenizer.json") if (path / "tokenizer.json").exists() else \
+                    ByteTokenizer(vocab_size=raw["vocab_size"])
+                self._ssm[key] = (model, tok, ChatTemplate.for_arch(kind), threading.Lock())
+            return self._ssm[key]
+
+    def _stream_ssm(self, spec: ModelSpec, req: TextRequest, kind: str, cancel: Optional[threading.Event]) -> Iterator[TextChunk]:
+        from .sampling import sample_row
+        model, tok, tpl, lock = self._ssm_host(spec, kind)
+        text = req.prompt if req.prompt is not None else tpl.render(req.messages, add_generation_prompt=True)
+        ids = tok.encode(text)
+        params = SamplingParams(temperature=req.temperature, top_p=req.top_p, top_k=req.top_k, min_p=req.min_p,
+                                repetition_penalty=req.repetition_penalty, max_tokens=req.max_tokens, seed=req.seed, greedy=req.greedy)
+        gen = torch.Generator(device="cpu").manual_seed(req.seed) if req.seed is not None else None
+        t0 = time.perf_counter()
+        out_ids: list[int] = []
+        out_text, ttft, reason = "", 0.0, StopReason.LENGTH
+        dec = tok.stream_decoder()
+        with lock:
+            state = model.new_state()
+            hidden = model.forward(torch.tensor(ids, dtype=torch.int32), state)[-1:]
+            for _ in range(req.max_tokens):
+                if cancel is not None and cancel.is_set():
+                    reason = StopReason.CANCELLED
+                    break
+                nxt = sample_row(model.logits(hidden)[0].float().cpu(), params, ids + out_ids, gen)
+                if not out_ids:
+                    ttft = time.perf_counter() - t0
+                if nxt == model.cfg.eos_token_id or nxt in getattr(tok, "special_ids", ()):
+                    reason = StopReason.STOP
+                    break
+                out_ids.append(nxt)
+                piece = dec.push(nxt)
+                if piece:
+                    out_text += piece
+                    if any(s and s in out_text for s in req.stop):
+                        out_text = out_text[: min(out_text.find(s) for s in req.stop if s and s in out_text)]
+                        reason = StopReason.STOP
+                        break
+                    yield TextChunk(ChunkKind.CHUNK, text=piece)
+                hidden = model.forward(torch.tensor([nxt], dtype=torch.int32), state)
+        res = TextResult(text=out_text, token_ids=out_ids, prompt_tokens=len(ids), completion_tokens=len(out_ids), stop_reason=reason,
+                         ttft_s=ttft, total_s=time.perf_counter() - t0)
+        yield TextChunk(ChunkKind.STOP_REASON, stop_reason=reason)
+        yield TextChunk(ChunkKind.RESULT, result=res)
+
     def stream(self, spec: ModelSpec, req: TextRequest, cancel: Optional[threading.Event] = None) -> Iterator[TextChunk]:
+        kind = self._ssm_kind(spec)
+        if kind is not None:
+            yield from self._stream_ssm(spec, req, kind, cancel)
+            return
         h = self._host(spec)
         llm = h.llm
         ids = self._prompt_ids(llm, req)

@@ -125,3 +125,21 @@ def test_gguf_write_read(tmp_path):
     from hartsyinference_b200.models.llm.config import from_gguf_metadata
     cfg = from_gguf_metadata(f.metadata)
     assert cfg.hidden_size == 256 and cfg.num_heads == 4 and cfg.vocab_size == 3
+
+
+def test_views_keep_the_file_mapping_alive(tmp_path):
+    """A view derived from a mapped tensor must stay readable after the reader object is gone."""
+    import gc
+    import torch
+    from hartsyinference_b200.assets import gguf as G
+    from hartsyinference_b200.assets.safetensors import SafeTensorsFile, save_file
+    save_file({"a": torch.arange(1000, dtype=torch.float32)}, tmp_path / "x.safetensors")
+    G.write_gguf(tmp_path / "x.gguf", {"general.architecture": "llama"}, {"a": torch.arange(1000, dtype=torch.float32).reshape(10, 100)})
+    f = SafeTensorsFile(tmp_path / "x.safetensors")
+    v = f.get("a").reshape(10, 100)[3:5]
+    g = G.GgufFile(tmp_path / "x.gguf")
+    w = g.get("a")[3:5]
+    r = g.raw("a")[:16].view(torch.float32)
+    del f, g
+    gc.collect()
+    assert v.sum().item() == w.sum().item() == float(torch.arange(300, 500).sum()) and r.tolist() == [0.0, 1.0, 2.0, 3.0]

@@ -331,3 +331,31 @@ def test_rwkv_matches_transformers_and_state_carries_over():
     assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0) > 0.999
     assert (mine.argmax(-1) == ref.argmax(-1)).float().mean() > 0.9
     assert len(m.generate(ids[:4].tolist(), max_tokens=3, stop_at_eos=False)) == 3
+
+
+@pytest.mark.parametrize("kind", ["mamba2", "rwkv"])
+def test_recurrent_models_through_the_text_service(kind, tmp_path):
+    transformers = pytest.importorskip("transformers")
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, TextRequest
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    torch.manual_seed(0)
+    if kind == "mamba2":
+        c = transformers.Mamba2Config(vocab_size=300, hidden_size=64, num_hidden_layers=2, state_size=16, num_heads=8, head_dim=16,
+                                      n_groups=1, expand=2, conv_kernel=4, chunk_size=8, eos_token_id=0, bos_token_id=1, pad_token_id=0)
+        hf = transformers.Mamba2ForCausalLM(c)
+    else:
+        c = transformers.RwkvConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, attention_hidden_size=64, intermediate_size=128,
+                                    context_length=64, rescale_every=0)
+        hf = transformers.RwkvForCausalLM(c)
+    d = tmp_path / kind
+    save_hf_checkpoint(c.to_dict(), {k: v.detach().contiguous() for k, v in hf.state_dict().items()}, d)
+    eng = InferenceEngine("cpu")
+    try:
+        r1 = eng.text.generate(ModelSpec(str(d)), TextRequest(prompt="hello", max_tokens=5, greedy=True))
+        r2 = eng.text.generate(ModelSpec(str(d)), TextRequest(prompt="hello", max_tokens=5, greedy=True))
+        assert r1.token_ids == r2.token_ids and 0 < r1.completion_tokens <= 5 and r1.prompt_tokens == 5
+        chunks = list(eng.text.stream(ModelSpec(str(d)), TextRequest(prompt="hello", max_tokens=3, temperature=0.8, seed=3)))
+        assert chunks[-1].result is not None and chunks[-1].result.completion_tokens <= 3
+        assert any(k.startswith("ssm|") for k in eng.loaded_pipeline_keys)
+    finally:
+        eng.text.release()
