@@ -103,6 +103,7 @@ class TextResult:
     ttft_s: float = 0.0
     total_s: float = 0.0
     error: Optional[str] = None
+    tool_calls: list = field(default_factory=list)     # assets.tool_calls.ToolCall, when tools were offered
 
     @property
     def tokens_per_second(self) -> float:

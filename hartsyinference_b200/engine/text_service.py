@@ -135,6 +135,9 @@ class TextService:
             text = llm.chat_template.render(req.messages, add_generation_prompt=True, tools=req.tools,
                                             enable_thinking=req.enable_thinking)
             special = not text.startswith(llm.chat_template.bos_token or "\0")
+            if req.force_tool_id:
+                from ..assets.tool_calls import forced_prefix
+                text += forced_prefix(req.force_tool_id)        # the reply is opened as a call of that tool
         if not req.images or llm.vlm is None:
             return llm.tokenizer.encode(text, add_special=special)
         # the text around each "<image>" is tokenised by itself, with the image token id between
@@ -314,9 +317,18 @@ class TextService:
         with h.wake:
             r = h.engine.release(rid)
         reason = StopReason.STOP if stop_hit else _REASON.get((r.finish_reason if r else None) or "stop", StopReason.STOP)
+        calls = []
+        if req.tools or req.force_tool_id:
+            from ..assets.tool_calls import forced_prefix, parse_tool_calls, tool_names
+            full = (forced_prefix(req.force_tool_id) + text) if req.force_tool_id else text
+            cleaned, calls = parse_tool_calls(full, tool_names(req.tools) or None)
+            if calls:
+                text, reason = cleaned, StopReason.TOOL_CALL
+                for c in calls:
+                    yield TextChunk(ChunkKind.NATIVE_TOOL_CALL, text=c.arguments, status=c.name)
         res = TextResult(text=text, token_ids=out_ids, prompt_tokens=len(ids), completion_tokens=len(out_ids),
                          stop_reason=reason, ttft_s=ttft, total_s=time.perf_counter() - t0,
-                         error=r.error if r else None)
+                         error=r.error if r else None, tool_calls=calls)
         REGISTRY.inc("hartsyinference_tokens_total", len(out_ids))
         REGISTRY.set("hartsyinference_ttft_seconds", ttft)
         REGISTRY.set("hartsyinference_decode_tok_s", res.tokens_per_second)

@@ -104,6 +104,24 @@ def _parse_multipart(body: bytes, content_type: str) -> dict:
     return out
 
 
+def _forced_tool(choice) -> Optional[str]:
+    """OpenAI ``tool_choice`` = {"type": "function", "function": {"name": ...}} names the tool to call."""
+    if isinstance(choice, dict):
+        return (choice.get("function") or {}).get("name")
+    return None
+
+
+def _finish(r) -> str:
+    return {"length": "length", "tool_call": "tool_calls"}.get(r.stop_reason.value, "stop")
+
+
+def _message(r) -> dict:
+    m = {"role": "assistant", "content": r.text or (None if r.tool_calls else "")}
+    if r.tool_calls:
+        m["tool_calls"] = [c.to_openai() for c in r.tool_calls]
+    return m
+
+
 def _flatten_parts(messages: list) -> tuple[list, list]:
     """OpenAI content parts -> plain-text messages ("<image>" where a picture was) + decoded images.
     Only ``data:`` URLs are accepted: the server fetches nothing from the network."""
@@ -248,6 +266,7 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
                            max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 4096),
                            seed=body.get("seed"), greedy=bool(body.get("greedy", False)) or float(body.get("temperature", 0.7)) == 0.0,
                            enable_thinking=body.get("enable_thinking"), tools=body.get("tools"), stop=list(stop),
+                           force_tool_id=_forced_tool(body.get("tool_choice")),
                            json_mode=rf.get("type") == "json_object", images=images)
 
     @app.post("/v1/chat/completions")
@@ -272,8 +291,11 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
                         elif ch.kind == ChunkKind.RESULT:
                             r = ch.result
                             usage.add(key, prompt_tokens=r.prompt_tokens, completion_tokens=r.completion_tokens)
+                            delta = {}
+                            if r.tool_calls:
+                                delta = {"tool_calls": [{"index": i, **c.to_openai()} for i, c in enumerate(r.tool_calls)]}
                             d = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": body.get("model"),
-                                 "choices": [{"index": 0, "delta": {}, "finish_reason": "length" if r.stop_reason.value == "length" else "stop"}],
+                                 "choices": [{"index": 0, "delta": delta, "finish_reason": _finish(r)}],
                                  "usage": {"prompt_tokens": r.prompt_tokens, "completion_tokens": r.completion_tokens,
                                            "total_tokens": r.prompt_tokens + r.completion_tokens}}
                             yield f"data: {json.dumps(d)}\n\n"
@@ -283,8 +305,7 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
             r = eng.text.generate(spec, treq)
         usage.add(key, prompt_tokens=r.prompt_tokens, completion_tokens=r.completion_tokens)
         return {"id": rid, "object": "chat.completion", "created": created, "model": body.get("model"),
-                "choices": [{"index": 0, "message": {"role": "assistant", "content": r.text},
-                             "finish_reason": "length" if r.stop_reason.value == "length" else "stop"}],
+                "choices": [{"index": 0, "message": _message(r), "finish_reason": _finish(r)}],
                 "usage": {"prompt_tokens": r.prompt_tokens, "completion_tokens": r.completion_tokens,
                           "total_tokens": r.prompt_tokens + r.completion_tokens}}
 

@@ -168,3 +168,29 @@ def test_prompt_lookup_speculative_matches_plain_greedy():
     assert spec == plain
     assert stats.drafted > 0 and stats.forward_passes <= 1 + 24
     assert eng.kv.num_free == free_before            # the sequence was released
+
+
+def test_forced_tool_call_through_the_text_service(tmp_path):
+    """``force_tool_id`` opens the reply as a call of that tool; whatever JSON the model completes is
+    returned as a tool call with stop reason TOOL_CALL when it parses."""
+    from hartsyinference_b200.assets.tool_calls import forced_prefix, parse_tool_calls
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, TextRequest
+    from hartsyinference_b200.engine.requests import ChunkKind, StopReason
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    from tests.test_llm_loader_cpu import _synthetic
+    cfg, t = _synthetic(seed=2)
+    save_hf_checkpoint(cfg, t, tmp_path / "toy")
+    eng = InferenceEngine("cpu")
+    try:
+        spec = ModelSpec(str(tmp_path / "toy"))
+        plain = eng.text.count_tokens(spec, TextRequest(messages=[{"role": "user", "content": "hi"}]))
+        forced = eng.text.count_tokens(spec, TextRequest(messages=[{"role": "user", "content": "hi"}], force_tool_id="lookup"))
+        assert forced == plain + len(forced_prefix("lookup").encode())          # the byte tokenizer: one id per byte
+        # a random toy model will not write valid JSON: the reply then stays text with an ordinary stop reason
+        chunks = list(eng.text.stream(spec, TextRequest(prompt="x", max_tokens=4, greedy=True, tools=[{"name": "lookup"}])))
+        res = chunks[-1].result
+        assert res.tool_calls == [] and res.stop_reason in (StopReason.LENGTH, StopReason.STOP)
+        assert not any(c.kind == ChunkKind.NATIVE_TOOL_CALL for c in chunks)
+    finally:
+        eng.text.release()
+    assert parse_tool_calls(forced_prefix("lookup") + '{"q": 1}}\n</tool_call>', {"lookup"})[1][0].name == "lookup"

@@ -79,3 +79,31 @@ def test_image_generation_and_unsupported_routes(server):
     assert png[:8] == b"\x89PNG\r\n\x1a\n" and r["data"][0]["seed"] == 3
     assert requests.post(server + "/v1/audio/speech", json={}, headers=H).status_code == 400
     assert requests.post(server + "/v1/chat/completions", json={"model": "/no/such/model", "messages": []}, headers=H).status_code in (400, 500)
+
+
+def test_tool_call_parsing_and_openai_shape():
+    from hartsyinference_b200.assets.tool_calls import ToolCall, forced_prefix, parse_tool_calls, tool_names
+    from hartsyinference_b200.engine.requests import StopReason, TextResult
+    from hartsyinference_b200.server.app import _finish, _forced_tool, _message
+    import json
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {}}}, {"name": "lookup"}]
+    known = tool_names(tools)
+    assert known == {"get_weather", "lookup"}
+    txt = 'Let me check.\n<tool_call>\n{"name": "get_weather", "arguments": {"city": "Oslo"}}\n</tool_call>'
+    rest, calls = parse_tool_calls(txt, known)
+    assert rest == "Let me check." and len(calls) == 1 and calls[0].name == "get_weather" and json.loads(calls[0].arguments) == {"city": "Oslo"}
+    two = '<tool_call>{"name": "lookup", "arguments": {"q": 1}}</tool_call><tool_call>{"name": "lookup", "arguments": {"q": 2}}</tool_call>'
+    assert [json.loads(c.arguments)["q"] for c in parse_tool_calls(two, known)[1]] == [1, 2]
+    rest, calls = parse_tool_calls('[TOOL_CALLS] [{"name": "lookup", "arguments": {"q": "x"}}]', known)
+    assert rest == "" and calls[0].name == "lookup"
+    rest, calls = parse_tool_calls('<|python_tag|>{"name": "get_weather", "parameters": {"city": "Rome"}}', known)
+    assert rest == "" and json.loads(calls[0].arguments) == {"city": "Rome"}
+    # not calls: unknown tool, ordinary JSON, broken JSON, unterminated tag with valid JSON is still a call
+    assert parse_tool_calls('<tool_call>{"name": "rm_rf", "arguments": {}}</tool_call>', known)[1] == []
+    assert parse_tool_calls('{"name": "Bob", "age": 3}', None)[1] == []
+    assert parse_tool_calls('<tool_call>{"name": </tool_call>', known) == ('<tool_call>{"name": </tool_call>', [])
+    assert len(parse_tool_calls(forced_prefix("lookup") + '{"q": 5}}', known)[1]) == 1
+    r = TextResult(text="", stop_reason=StopReason.TOOL_CALL, tool_calls=[ToolCall("call_1", "lookup", '{"q": 5}')])
+    m = _message(r)
+    assert _finish(r) == "tool_calls" and m["content"] is None and m["tool_calls"][0]["function"] == {"name": "lookup", "arguments": '{"q": 5}'}
+    assert _forced_tool({"type": "function", "function": {"name": "lookup"}}) == "lookup" and _forced_tool("auto") is None
