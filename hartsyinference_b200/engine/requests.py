@@ -174,7 +174,8 @@ class RestoreRequest:
 @dataclass
 class VisionRequest:
     """``operation``: "embed" (CLIP / SigLIP / DINOv2 image features, CLIP text features and their
-    similarity when both are given) or "depth" (Depth Anything; one map per image)."""
+    similarity when both are given), "depth" (Depth Anything; one map per image) or "segment" (CLIPSeg:
+    one probability map per (image, text) pair)."""
     operation: str = "embed"
     images: list = field(default_factory=list)
     texts: list[str] = field(default_factory=list)
@@ -186,6 +187,7 @@ class VisionResult:
     text_embeddings: Optional[Any] = None      # [n_texts, dim]
     similarity: Optional[Any] = None           # [n_images, n_texts] cosine
     depth: Optional[list] = None               # per image: float32 [H, W] at the image's own size
+    masks: Optional[list] = None               # per image: float32 [n_texts, H, W] probabilities in [0, 1]
 
 
 @dataclass

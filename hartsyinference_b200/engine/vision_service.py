@@ -121,6 +121,36 @@ class _DepthEstimator:
         return out
 
 
+class _Segmenter:
+    def __init__(self, path: str, raw: dict, device):
+        from ..assets.tokenizer import ClipTokenizer
+        from ..models.vision.clipseg import ClipSeg, clipseg_from_hf
+        cfg = clipseg_from_hf(raw)
+        self.model = ClipSeg(cfg, device, get=ShardedCheckpoint(path).get)
+        self.tokenizer = ClipTokenizer.from_dir(path, cfg.text.max_len)
+
+    def segment(self, images: list, texts: list[str]) -> list:
+        size = self.model.cfg.vision.image_size
+        conds = [self.model.text_embedding(torch.tensor(self.tokenizer.encode(t))) for t in texts]
+        out = []
+        for im in images:
+            x = preprocess_image(im, size)
+            h, w = _image_hw(im)
+            maps = torch.stack([torch.sigmoid(self.model.segment(x, c)).float().cpu() for c in conds])
+            out.append(torch.nn.functional.interpolate(maps[None], size=(h, w), mode="bilinear", align_corners=False)[0])
+        return out
+
+
+def _image_hw(image) -> tuple[int, int]:
+    if isinstance(image, (str, bytes)) or hasattr(image, "__fspath__"):
+        from PIL import Image
+        image = Image.open(image)
+    if hasattr(image, "size") and hasattr(image, "convert"):
+        return image.size[1], image.size[0]
+    t = torch.as_tensor(image)
+    return (t.shape[0], t.shape[1]) if (t.ndim == 3 and t.shape[-1] == 3 and t.shape[0] != 3) else (t.shape[-2], t.shape[-1])
+
+
 class VisionService:
     def __init__(self, device):
         self.device = device
@@ -142,6 +172,8 @@ class VisionService:
                 mt = raw.get("model_type", "clip")
                 if mt == "depth_anything":
                     self._loaded[path] = _DepthEstimator(path, raw, self.device)
+                elif mt == "clipseg":
+                    self._loaded[path] = _Segmenter(path, raw, self.device)
                 elif mt in ("siglip", "siglip_vision_model", "dinov2"):
                     self._loaded[path] = _VitEmbedder(path, raw, self.device)
                 else:
@@ -149,10 +181,19 @@ class VisionService:
             return self._loaded[path]
 
     def run(self, spec: ModelSpec, req: VisionRequest) -> VisionResult:
-        if req.operation not in ("embed", "depth"):
-            raise ValueError(f"vision operation '{req.operation}' is not built (embed and depth are)")
+        if req.operation not in ("embed", "depth", "segment"):
+            raise ValueError(f"vision operation '{req.operation}' is not built (embed, depth and segment are)")
         m = self._model(spec)
         out = VisionResult()
+        if req.operation == "segment":
+            if not isinstance(m, _Segmenter):
+                raise ValueError("this checkpoint is not a text-prompted segmenter")
+            if not req.texts:
+                raise ValueError("segment needs at least one text prompt")
+            out.masks = m.segment(req.images, req.texts)
+            return out
+        if isinstance(m, _Segmenter):
+            raise ValueError("this checkpoint segments; use operation 'segment'")
         if req.operation == "depth":
             if not isinstance(m, _DepthEstimator):
                 raise ValueError("this checkpoint is not a depth estimator")

@@ -423,6 +423,20 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
         vreq = VisionRequest(operation=body.get("operation", "embed"), images=images, texts=list(body.get("texts") or []))
         with heavy_queue.slot():
             res = eng.vision.run(resolve(body.get("model"), Modality.VISION), vreq)
+        if res.masks is not None:
+            import io
+            import numpy as np
+            from PIL import Image
+            out_masks = []
+            for per_image in res.masks:
+                row = []
+                for mk in per_image:
+                    buf = io.BytesIO()
+                    Image.fromarray((mk.clamp(0, 1) * 255).round().numpy().astype(np.uint8)).save(buf, format="PNG")
+                    row.append({"width": int(mk.shape[1]), "height": int(mk.shape[0]), "coverage": float((mk > 0.5).float().mean()),
+                                "png_base64": base64.b64encode(buf.getvalue()).decode()})
+                out_masks.append(row)
+            return {"masks": out_masks}
         if res.depth is not None:
             # 16-bit grayscale PNGs, each map scaled to its own maximum
             import io

@@ -422,3 +422,64 @@ def test_clip_text_penultimate_states_and_projection():
     assert pooled.shape == (32,) and cos(pooled, out.text_embeds[0]) > 0.995
     last, _ = enc.encode(ids)
     assert cos(last, out.last_hidden_state[0]) > 0.995
+
+
+def test_clipseg_matches_transformers_and_serves(tmp_path):
+    tr = pytest.importorskip("transformers")
+    import base64
+    import io
+    import json
+    from fastapi.testclient import TestClient
+    from PIL import Image
+    from hartsyinference_b200.assets.tokenizer import _bytes_to_unicode
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, VisionRequest
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    from hartsyinference_b200.models.vision.clipseg import ClipSeg, clipseg_from_hf
+    from hartsyinference_b200.server.app import ServerOptions, create_app
+    b2u = _bytes_to_unicode()
+    vocab = {}
+    for b in range(256):
+        vocab[b2u[b]] = len(vocab)
+    for b in range(256):
+        vocab[b2u[b] + "</w>"] = len(vocab)
+    vocab["<|startoftext|>"], vocab["<|endoftext|>"] = len(vocab), len(vocab) + 1
+    vc = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=2, image_size=32, patch_size=8)
+    tc = dict(vocab_size=len(vocab), hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+              max_position_embeddings=16, eos_token_id=len(vocab) - 1, bos_token_id=len(vocab) - 2, pad_token_id=len(vocab) - 1)
+    c = tr.CLIPSegConfig(text_config=tc, vision_config=vc, projection_dim=32, extract_layers=[1, 2, 3], reduce_dim=16,
+                         decoder_num_attention_heads=2, decoder_intermediate_size=32, conditional_layer=0)
+    torch.manual_seed(0)
+    hf = tr.CLIPSegForImageSegmentation(c).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2 and "embed" not in n:
+                p.mul_(2.0)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    m = ClipSeg(clipseg_from_hf(c.to_dict()), "cpu", get=lambda n: sd.get(n))
+    img = torch.randn(3, 32, 32, generator=torch.Generator().manual_seed(1))
+    ids = torch.tensor([len(vocab) - 2, 5, 7, len(vocab) - 1])
+    with torch.no_grad():
+        ref = hf(pixel_values=img[None], input_ids=ids[None]).logits[0]
+    mine = m.segment(img, m.text_embedding(ids))
+    assert mine.shape == ref.shape == (32, 32)
+    assert torch.nn.functional.cosine_similarity(ref.flatten(), mine.flatten(), dim=0) > 0.995
+
+    d = tmp_path / "clipseg"
+    save_hf_checkpoint(c.to_dict(), {k: v.contiguous() for k, v in sd.items() if "position_ids" not in k}, d)
+    (d / "vocab.json").write_text(json.dumps(vocab))
+    (d / "merges.txt").write_text("#version: 0.2\n")
+    eng = InferenceEngine("cpu")
+    pic = (torch.rand(40, 56, 3, generator=torch.Generator().manual_seed(2)) * 255).to(torch.uint8)
+    res = eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="segment", images=[pic], texts=["a cat", "the sky"]))
+    assert len(res.masks) == 1 and res.masks[0].shape == (2, 40, 56) and 0 <= float(res.masks[0].min()) and float(res.masks[0].max()) <= 1
+    with pytest.raises(ValueError):
+        eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="segment", images=[pic]))
+    buf = io.BytesIO()
+    Image.fromarray(pic.numpy()).save(buf, format="PNG")
+    with TestClient(create_app(ServerOptions(models={"seg": str(d)}), engine=eng)) as cl:
+        r = cl.post("/v1/native/vision", json={"model": "seg", "operation": "segment", "texts": ["a cat"],
+                                               "images": [base64.b64encode(buf.getvalue()).decode()]})
+        assert r.status_code == 200, r.text
+        mk = r.json()["masks"][0][0]
+        assert (mk["width"], mk["height"]) == (56, 40) and 0 <= mk["coverage"] <= 1
+    eng.close()
