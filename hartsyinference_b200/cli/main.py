@@ -213,14 +213,26 @@ def speak(model, text, out, speed, device):
 @cli.command()
 @click.argument("model")
 @click.option("--image", "images", multiple=True, help="image file (repeatable)")
-@click.option("--text", "texts", multiple=True, help="caption to score against the images (repeatable)")
+@click.option("--text", "texts", multiple=True, help="caption / query / prompt (repeatable)")
+@click.option("--op", "operation", default="embed", type=click.Choice(["embed", "depth", "segment", "detect"]))
+@click.option("--threshold", default=0.1, help="score threshold of detect")
 @click.option("--device", default="auto")
-def vision(model, images, texts, device):
-    """CLIP image / text embeddings; with both, prints the cosine similarity matrix."""
+def vision(model, images, texts, operation, threshold, device):
+    """Image embeddings / similarity (CLIP, SigLIP, DINOv2), depth, text-prompted segmentation, open-vocabulary detection."""
     from ..engine.inference_engine import InferenceEngine
     from ..engine.requests import VisionRequest
     eng = InferenceEngine(device)
-    res = eng.vision.run(ModelSpec(model, Modality.VISION, local_path=model), VisionRequest(images=list(images), texts=list(texts)))
+    res = eng.vision.run(ModelSpec(model, Modality.VISION, local_path=model),
+                         VisionRequest(operation=operation, images=list(images), texts=list(texts), score_threshold=threshold))
+    if res.detections is not None:
+        for img, dets in zip(images, res.detections):
+            for dt in dets:
+                click.echo(json.dumps({"image": img, **dt}))
+        return
+    if res.depth is not None or res.masks is not None:
+        for img, t in zip(images, res.depth if res.depth is not None else res.masks):
+            click.echo(json.dumps({"image": img, "shape": list(t.shape), "min": float(t.min()), "max": float(t.max())}))
+        return
     out = res.similarity if res.similarity is not None else (res.image_embeddings if res.image_embeddings is not None else res.text_embeddings)
     for row in (out if out is not None else []):
         click.echo(json.dumps([round(float(x), 6) for x in row]))

@@ -175,10 +175,13 @@ class RestoreRequest:
 class VisionRequest:
     """``operation``: "embed" (CLIP / SigLIP / DINOv2 image features, CLIP text features and their
     similarity when both are given), "depth" (Depth Anything; one map per image) or "segment" (CLIPSeg:
-    one probability map per (image, text) pair)."""
+    one probability map per (image, text) pair) or "detect" (OWL-ViT: boxes for each text query above
+    ``score_threshold``, after per-query non-maximum suppression)."""
     operation: str = "embed"
     images: list = field(default_factory=list)
     texts: list[str] = field(default_factory=list)
+    score_threshold: float = 0.1
+    nms_iou: float = 0.5
 
 
 @dataclass
@@ -188,6 +191,7 @@ class VisionResult:
     similarity: Optional[Any] = None           # [n_images, n_texts] cosine
     depth: Optional[list] = None               # per image: float32 [H, W] at the image's own size
     masks: Optional[list] = None               # per image: float32 [n_texts, H, W] probabilities in [0, 1]
+    detections: Optional[list] = None          # per image: [{"label", "score", "box": [x0, y0, x1, y1] in pixels}]
 
 
 @dataclass

@@ -141,6 +141,72 @@ class _Segmenter:
         return out
 
 
+def nms(boxes: torch.Tensor, scores: torch.Tensor, iou: float) -> list[int]:
+    """Greedy non-maximum suppression over [n, 4] corner boxes; returns kept indices, best first."""
+    order = scores.argsort(descending=True).tolist()
+    keep: list[int] = []
+    area = (boxes[:, 2] - boxes[:, 0]).clamp_min(0) * (boxes[:, 3] - boxes[:, 1]).clamp_min(0)
+    while order:
+        i = order.pop(0)
+        keep.append(i)
+        rest = []
+        for j in order:
+            w = (torch.minimum(boxes[i, 2], boxes[j, 2]) - torch.maximum(boxes[i, 0], boxes[j, 0])).clamp_min(0)
+            h = (torch.minimum(boxes[i, 3], boxes[j, 3]) - torch.maximum(boxes[i, 1], boxes[j, 1])).clamp_min(0)
+            inter = w * h
+            if float(inter / (area[i] + area[j] - inter).clamp_min(1e-12)) <= iou:
+                rest.append(j)
+        order = rest
+    return keep
+
+
+class _Detector:
+    def __init__(self, path: str, raw: dict, device):
+        from ..assets.tokenizer import ClipTokenizer
+        from ..models.vision.owlvit import OwlVit, owlvit_from_hf
+        cfg = owlvit_from_hf(raw)
+        self.model = OwlVit(cfg, device, get=ShardedCheckpoint(path).get)
+        self.tokenizer = ClipTokenizer.from_dir(path, cfg.text.max_len)
+
+    def detect(self, images: list, texts: list[str], threshold: float, iou: float) -> list:
+        size = self.model.cfg.vision.image_size
+        queries = torch.stack([self.model.text_embedding(torch.tensor(self.tokenizer.encode(t))) for t in texts])
+        out = []
+        for im in images:
+            h, w = _image_hw(im)
+            # the detector sees the whole picture squeezed to its input size; boxes scale back per axis
+            x = preprocess_image(self._squeeze(im, size), size)
+            logits, boxes = self.model.detect(x, queries)
+            scores = torch.sigmoid(logits).float().cpu()
+            b = boxes.float().cpu()
+            corners = torch.stack([(b[:, 0] - b[:, 2] / 2) * w, (b[:, 1] - b[:, 3] / 2) * h,
+                                   (b[:, 0] + b[:, 2] / 2) * w, (b[:, 1] + b[:, 3] / 2) * h], 1)
+            found = []
+            for qi, label in enumerate(texts):
+                sel = (scores[:, qi] >= threshold).nonzero().flatten()
+                for k in nms(corners[sel], scores[sel, qi], iou):
+                    i = int(sel[k])
+                    found.append({"label": label, "score": float(scores[i, qi]), "box": [float(v) for v in corners[i]]})
+            out.append(sorted(found, key=lambda d: -d["score"]))
+        return out
+
+    @staticmethod
+    def _squeeze(image, size: int) -> torch.Tensor:
+        import numpy as np
+        if isinstance(image, (str, bytes)) or hasattr(image, "__fspath__"):
+            from PIL import Image
+            image = Image.open(image)
+        if hasattr(image, "convert"):
+            image = torch.from_numpy(np.asarray(image.convert("RGB")).copy())
+        t = torch.as_tensor(image)
+        if t.dtype == torch.uint8:
+            t = t.float() / 255.0
+        if t.ndim == 3 and t.shape[-1] == 3 and t.shape[0] != 3:
+            t = t.permute(2, 0, 1)
+        return torch.nn.functional.interpolate(t.float()[None], size=(size, size), mode="bicubic", align_corners=False,
+                                               antialias=True)[0].clamp(0, 1)
+
+
 def _image_hw(image) -> tuple[int, int]:
     if isinstance(image, (str, bytes)) or hasattr(image, "__fspath__"):
         from PIL import Image
@@ -174,6 +240,8 @@ class VisionService:
                     self._loaded[path] = _DepthEstimator(path, raw, self.device)
                 elif mt == "clipseg":
                     self._loaded[path] = _Segmenter(path, raw, self.device)
+                elif mt in ("owlvit", "owlv2"):
+                    self._loaded[path] = _Detector(path, raw, self.device)
                 elif mt in ("siglip", "siglip_vision_model", "dinov2"):
                     self._loaded[path] = _VitEmbedder(path, raw, self.device)
                 else:
@@ -181,10 +249,19 @@ class VisionService:
             return self._loaded[path]
 
     def run(self, spec: ModelSpec, req: VisionRequest) -> VisionResult:
-        if req.operation not in ("embed", "depth", "segment"):
-            raise ValueError(f"vision operation '{req.operation}' is not built (embed, depth and segment are)")
+        if req.operation not in ("embed", "depth", "segment", "detect"):
+            raise ValueError(f"vision operation '{req.operation}' is not built (embed, depth, segment and detect are)")
         m = self._model(spec)
         out = VisionResult()
+        if req.operation == "detect":
+            if not isinstance(m, _Detector):
+                raise ValueError("this checkpoint is not an open-vocabulary detector")
+            if not req.texts:
+                raise ValueError("detect needs at least one text query")
+            out.detections = m.detect(req.images, req.texts, req.score_threshold, req.nms_iou)
+            return out
+        if isinstance(m, _Detector):
+            raise ValueError("this checkpoint detects; use operation 'detect'")
         if req.operation == "segment":
             if not isinstance(m, _Segmenter):
                 raise ValueError("this checkpoint is not a text-prompted segmenter")

@@ -80,7 +80,7 @@ def tiny_clip_vision() -> ClipVisionConfig:
 
 class ClipVisionEncoder:
     def __init__(self, cfg: ClipVisionConfig, device="cpu", get: Optional[Callable[[str], Optional[torch.Tensor]]] = None,
-                 seed: int = 0, prefix: str = "vision_model."):
+                 seed: int = 0, prefix: str = "vision_model.", pre_ln: str = "pre_layrnorm"):
         self.cfg, self.device = cfg, torch.device(device)
         f = WeightFactory(self.device, False, get=get, seed=seed)
         W, P = cfg.width, cfg.patch
@@ -93,9 +93,9 @@ class ClipVisionEncoder:
         w2[:, : 3 * P * P] = pw.reshape(W, 3 * P * P)
         self.patch = ops.LinearWeight(w2)
         self.pos = f.tensor(e + "position_embedding.weight", cfg.num_patches + 1, W)
-        # (sic) the checkpoint spells it "pre_layrnorm"
-        self.pre_w = f.tensor(prefix + "pre_layrnorm.weight", W, ones=True)
-        self.pre_b = f.tensor(prefix + "pre_layrnorm.bias", W, zeros=True)
+        # (sic) CLIP checkpoints spell it "pre_layrnorm"; OWL-ViT's spell it out
+        self.pre_w = f.tensor(prefix + pre_ln + ".weight", W, ones=True)
+        self.pre_b = f.tensor(prefix + pre_ln + ".bias", W, zeros=True)
         self.blocks = []
         for i in range(cfg.layers):
             p = f"{prefix}encoder.layers.{i}."

@@ -420,9 +420,12 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
             from PIL import Image
             b64 = im.split(",", 1)[1] if im.startswith("data:") else im
             images.append(Image.open(io.BytesIO(base64.b64decode(b64))).convert("RGB"))
-        vreq = VisionRequest(operation=body.get("operation", "embed"), images=images, texts=list(body.get("texts") or []))
+        vreq = VisionRequest(operation=body.get("operation", "embed"), images=images, texts=list(body.get("texts") or []),
+                             score_threshold=float(body.get("score_threshold", 0.1)), nms_iou=float(body.get("nms_iou", 0.5)))
         with heavy_queue.slot():
             res = eng.vision.run(resolve(body.get("model"), Modality.VISION), vreq)
+        if res.detections is not None:
+            return {"detections": res.detections}
         if res.masks is not None:
             import io
             import numpy as np

@@ -483,3 +483,72 @@ def test_clipseg_matches_transformers_and_serves(tmp_path):
         mk = r.json()["masks"][0][0]
         assert (mk["width"], mk["height"]) == (56, 40) and 0 <= mk["coverage"] <= 1
     eng.close()
+
+
+def _owlvit_pair():
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.vision.owlvit import OwlVit, owlvit_from_hf
+    vc = dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2, image_size=32, patch_size=8)
+    tc = dict(vocab_size=514, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+              max_position_embeddings=16, eos_token_id=513, bos_token_id=512, pad_token_id=0)
+    c = tr.OwlViTConfig(text_config=tc, vision_config=vc, projection_dim=64)
+    torch.manual_seed(0)
+    hf = tr.OwlViTForObjectDetection(c).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2 and "encoder.layers" in n:
+                p.mul_(2.0)
+            if n.startswith("box_head") and p.ndim == 2:
+                p.mul_(4.0)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    return c, hf, sd, OwlVit(owlvit_from_hf(c.to_dict()), "cpu", get=lambda n: sd.get(n))
+
+
+def test_owlvit_matches_transformers():
+    from hartsyinference_b200.models.vision.owlvit import OwlVit
+    c, hf, sd, m = _owlvit_pair()
+    img = torch.randn(3, 32, 32, generator=torch.Generator().manual_seed(1))
+    ids = torch.tensor([[512, 5, 7, 513], [512, 9, 513, 0]])
+    with torch.no_grad():
+        ref = hf(pixel_values=img[None], input_ids=ids, attention_mask=(ids != 0).long())
+    q = torch.stack([m.text_embedding(ids[0]), m.text_embedding(ids[1][:3])])
+    logits, boxes = m.detect(img, q)
+    cos = lambda a, b: torch.nn.functional.cosine_similarity(a.flatten().float(), b.flatten().float(), dim=0)
+    assert logits.shape == (16, 2) and cos(ref.logits[0], logits) > 0.995
+    assert boxes.shape == (16, 4) and (ref.pred_boxes[0] - boxes).abs().max() < 0.02
+    assert torch.equal(OwlVit.box_bias(4, 4), hf.compute_box_bias(4, 4))
+
+
+def test_detect_operation_and_nms(tmp_path):
+    import json
+    from hartsyinference_b200.assets.tokenizer import _bytes_to_unicode
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, VisionRequest
+    from hartsyinference_b200.engine.vision_service import nms
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    boxes = torch.tensor([[0, 0, 10, 10], [1, 1, 11, 11], [20, 20, 30, 30], [0, 0, 10, 9.0]])
+    assert nms(boxes, torch.tensor([0.9, 0.8, 0.7, 0.95]), 0.5) == [3, 2]
+    assert nms(boxes, torch.tensor([0.9, 0.8, 0.7, 0.95]), 0.95) == [3, 0, 1, 2]
+    c, hf, sd, _ = _owlvit_pair()
+    b2u = _bytes_to_unicode()
+    vocab = {}
+    for b in range(256):
+        vocab[b2u[b]] = len(vocab)
+    for b in range(256):
+        vocab[b2u[b] + "</w>"] = len(vocab)
+    vocab["<|startoftext|>"], vocab["<|endoftext|>"] = 512, 513
+    d = tmp_path / "owl"
+    save_hf_checkpoint(c.to_dict(), {k: v.contiguous() for k, v in sd.items() if "position_ids" not in k}, d)
+    (d / "vocab.json").write_text(json.dumps(vocab))
+    (d / "merges.txt").write_text("#version: 0.2\n")
+    eng = InferenceEngine("cpu")
+    pic = (torch.rand(48, 64, 3, generator=torch.Generator().manual_seed(2)) * 255).to(torch.uint8)
+    res = eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="detect", images=[pic], texts=["a cat", "a dog"], score_threshold=0.0))
+    dets = res.detections[0]
+    assert dets and {x["label"] for x in dets} <= {"a cat", "a dog"} and all(0 <= x["score"] <= 1 for x in dets)
+    assert dets == sorted(dets, key=lambda x: -x["score"])
+    assert all(-70 <= x["box"][0] <= 70 and x["box"][2] >= x["box"][0] and x["box"][3] >= x["box"][1] for x in dets)
+    none = eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="detect", images=[pic], texts=["a cat"], score_threshold=1.1))
+    assert none.detections == [[]]
+    with pytest.raises(ValueError):
+        eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="embed", images=[pic]))
+    eng.close()
