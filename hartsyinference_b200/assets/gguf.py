@@ -20,7 +20,8 @@ from .. import runtime
 from ..exceptions import HartsyInferenceError
 
 GGML_TYPES = {"F32": 0, "F16": 1, "Q4_0": 2, "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11,
-              "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "IQ4_NL": 20, "BF16": 30}
+              "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "IQ4_NL": 20, "BF16": 30, "MXFP4": 39}
+MXFP4 = 39            # 32 elements: one E8M0 scale byte + 16 bytes of E2M1 nibbles (element j low, j + 16 high)
 GGML_NAMES = {v: k for k, v in GGML_TYPES.items()}
 
 _bound = False
@@ -66,7 +67,14 @@ def dequantize(raw: torch.Tensor | np.ndarray | bytes, ggml_type: int, numel: in
 
 
 def quantize(x: torch.Tensor, ggml_type: int) -> torch.Tensor:
-    """fp32 tensor -> packed blocks (uint8 [nbytes]); supports Q8_0, Q4_0, Q4_K."""
+    """fp32 tensor -> packed blocks (uint8 [nbytes]); supports Q8_0, Q4_0, Q4_K, MXFP4."""
+    if ggml_type == MXFP4:
+        from .lowbit import E2M1_MAX, e2m1_encode, e8m0_decode, e8m0_from_amax
+        xb = x.detach().float().cpu().reshape(-1, 32)
+        sc = e8m0_from_amax(xb.abs().amax(-1), E2M1_MAX)
+        codes = e2m1_encode(xb / e8m0_decode(sc)[:, None])
+        packed = (codes[:, :16] | (codes[:, 16:] << 4)).to(torch.uint8)
+        return torch.cat([sc[:, None], packed], 1).reshape(-1)
     blk, nb = type_geometry(ggml_type)
     xf = np.ascontiguousarray(x.detach().float().cpu().numpy().reshape(-1))
     if xf.size % blk:

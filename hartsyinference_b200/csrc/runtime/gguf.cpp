@@ -3,7 +3,7 @@
 // The file is memory-mapped; metadata is handed to Python as one JSON document, tensor data as
 // pointers into the mapping. The codecs are the fp32 oracle of the device dequant-GEMM kernels and
 // the implementation of the CPU path: dequantise Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q2_K, Q4_K, Q5_K,
-// Q6_K, IQ4_NL, F16, BF16 to fp32 and quantise fp32 to Q8_0 / Q4_0 / Q4_K.
+// Q6_K, IQ4_NL, MXFP4, F16, BF16 to fp32 and quantise fp32 to Q8_0 / Q4_0 / Q4_K.
 //
 // Counterparts in the reference: GgufLoader (header / KV / tensor-info parser;
 // src/HartsyInference.ModelAssets/Gguf/GgufLoader.cs), the per-format codecs
@@ -70,7 +70,7 @@ const TypeInfo kTypes[] = {
     {10, "Q2_K", 256, 84}, {11, "Q3_K", 256, 110}, {12, "Q4_K", 256, 144}, {13, "Q5_K", 256, 176},
     {14, "Q6_K", 256, 210}, {15, "Q8_K", 256, 292}, {20, "IQ4_NL", 32, 18}, {24, "I8", 1, 1},
     {25, "I16", 1, 2},    {26, "I32", 1, 4},    {27, "I64", 1, 8},     {28, "F64", 1, 8},
-    {30, "BF16", 1, 2},
+    {30, "BF16", 1, 2},   {39, "MXFP4", 32, 17},
 };
 const TypeInfo* find_type(int id) {
   for (const auto& t : kTypes) if (t.id == id) return &t;
@@ -282,6 +282,15 @@ B200_API int32_t b200_ggml_dequant(int32_t type, const void* src, float* y, int6
     case 0: memcpy(y, p, static_cast<size_t>(n) * 4); return 0;
     case 1: for (int64_t i = 0; i < n; ++i) y[i] = f16_to_f32(rd16(p + 2 * i)); return 0;
     case 30: for (int64_t i = 0; i < n; ++i) { uint32_t b = static_cast<uint32_t>(rd16(p + 2 * i)) << 16; memcpy(&y[i], &b, 4); } return 0;
+    case 39: {   // one E8M0 scale byte, then E2M1 nibbles: element j low, element j + 16 high
+      static const float kE2m1[16] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+      for (int64_t b = 0; b < nb; ++b, p += 17, y += 32) {
+        const float d = std::ldexp(1.0f, static_cast<int>(p[0]) - 127);
+        const uint8_t* qs = p + 1;
+        for (int j = 0; j < 16; ++j) { y[j] = kE2m1[qs[j] & 0xF] * d; y[j + 16] = kE2m1[qs[j] >> 4] * d; }
+      }
+      return 0;
+    }
     case 2: case 20:
       for (int64_t b = 0; b < nb; ++b, p += 18, y += 32) {
         const float d = f16_to_f32(rd16(p));

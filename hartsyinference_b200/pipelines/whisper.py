@@ -308,3 +308,56 @@ class MoonshinePipeline:
             res.segments.append(WhisperSegment(a / SAMPLE_RATE, b / SAMPLE_RATE, text, toks))
         res.text = " ".join(s.text.strip() for s in res.segments).strip()
         return res
+
+
+class StreamingTranscriber:
+    """Incremental transcription of a live audio stream. Audio is pushed in pieces of any size; each
+    push transcribes the not-yet-committed audio and returns (committed segments that are new, the
+    current tentative text). A segment is committed once it ends at least ``hold_s`` before the end
+    of the audio received so far, so late context can still revise the tail; ``flush`` commits the rest.
+
+    Reference: src/HartsyInference.Audio/Pipelines/WhisperStreamingPipeline.cs, MoonshineStreamingPipeline.cs."""
+
+    def __init__(self, pipeline, rate: int = SAMPLE_RATE, hold_s: float = 2.0, options: Optional[WhisperOptions] = None):
+        self.pipe, self.rate, self.hold_s, self.options = pipeline, rate, hold_s, options
+        self.buffer = torch.zeros(0)
+        self.offset_s = 0.0                      # stream time of buffer[0]
+        self.committed: list[WhisperSegment] = []
+
+    def push(self, samples: torch.Tensor) -> tuple[list[WhisperSegment], str]:
+        x = samples.float()
+        if x.ndim == 2:
+            x = x.mean(0)
+        self.buffer = torch.cat([self.buffer, resample(x, self.rate, SAMPLE_RATE)])
+        return self._advance(final=False)
+
+    def flush(self) -> tuple[list[WhisperSegment], str]:
+        return self._advance(final=True)
+
+    def _advance(self, final: bool) -> tuple[list[WhisperSegment], str]:
+        have_s = self.buffer.numel() / SAMPLE_RATE
+        if have_s < 0.2:
+            return [], ""
+        res = self.pipe.transcribe(self.buffer, SAMPLE_RATE, self.options)
+        new: list[WhisperSegment] = []
+        tentative: list[str] = []
+        cut_s = 0.0
+        for seg in res.segments:
+            if final or seg.end <= have_s - self.hold_s:
+                new.append(WhisperSegment(seg.start + self.offset_s, seg.end + self.offset_s, seg.text, seg.tokens,
+                                          seg.avg_logprob, seg.no_speech_prob))
+                cut_s = max(cut_s, seg.end)
+            else:
+                tentative.append(seg.text)
+        if final:
+            cut_s = have_s
+        if cut_s > 0:
+            n = min(int(round(cut_s * SAMPLE_RATE)), self.buffer.numel())
+            self.buffer = self.buffer[n:]
+            self.offset_s += n / SAMPLE_RATE
+        self.committed += new
+        return new, "".join(tentative).strip()
+
+    @property
+    def text(self) -> str:
+        return "".join(s.text for s in self.committed).strip()

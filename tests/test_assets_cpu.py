@@ -143,3 +143,25 @@ def test_views_keep_the_file_mapping_alive(tmp_path):
     del f, g
     gc.collect()
     assert v.sum().item() == w.sum().item() == float(torch.arange(300, 500).sum()) and r.tolist() == [0.0, 1.0, 2.0, 3.0]
+
+
+def test_gguf_mxfp4_blocks(tmp_path):
+    import torch
+    from hartsyinference_b200.assets import gguf as G
+    from hartsyinference_b200.assets.lowbit import E2M1
+    assert G.type_geometry(G.MXFP4) == (32, 17)
+    # one hand-made block: scale 2^1, element j = code j % 16 in the low nibbles, the reverse in the high ones
+    lo = torch.arange(16, dtype=torch.uint8)
+    hi = (15 - torch.arange(16)).to(torch.uint8)
+    blk = torch.cat([torch.tensor([128], dtype=torch.uint8), lo | (hi << 4)])
+    v = G.dequantize(blk, G.MXFP4, 32)
+    table = torch.cat([E2M1, -E2M1]) * 2.0
+    assert torch.equal(v[:16], table[lo.long()]) and torch.equal(v[16:], table[hi.long()])
+    w = torch.randn(8, 64, generator=torch.Generator().manual_seed(0))
+    packed = G.quantize(w, G.MXFP4)
+    assert packed.numel() == 8 * 64 // 32 * 17
+    back = G.dequantize(packed, G.MXFP4, w.numel()).reshape(w.shape)
+    assert ((back - w).norm() / w.norm()) < 0.15
+    G.write_gguf(tmp_path / "m.gguf", {"general.architecture": "llama"}, {"w": w}, quant={"w": G.MXFP4})
+    f = G.GgufFile(tmp_path / "m.gguf")
+    assert f.info("w")[0] == G.MXFP4 and torch.equal(f.get("w"), back)

@@ -333,3 +333,29 @@ def test_moonshine_matches_transformers_and_serves(tmp_path):
     assert len(cuts) >= 3 and cuts[0][0] == 0 and cuts[-1][1] == long_audio.numel() and all(a < b for a, b in cuts)
     assert all(cuts[i][1] == cuts[i + 1][0] for i in range(len(cuts) - 1))
     eng.close()
+
+
+def test_streaming_transcriber_commits_behind_the_hold_window():
+    from hartsyinference_b200.pipelines.whisper import StreamingTranscriber, TranscriptResult, WhisperSegment
+
+    class Fake:
+        """Reports one segment per full second of the audio it is given."""
+        def __init__(self):
+            self.calls = []
+
+        def transcribe(self, audio, rate, options=None):
+            n = audio.numel() // rate
+            self.calls.append(audio.numel())
+            return TranscriptResult(segments=[WhisperSegment(float(i), float(i + 1), f" s{i}") for i in range(n)], duration_s=audio.numel() / rate)
+
+    st = StreamingTranscriber(Fake(), rate=16000, hold_s=2.0)
+    new, tail = st.push(torch.zeros(16000 * 3))
+    assert [s.text for s in new] == [" s0"] and tail == "s1 s2"          # only what ends 2 s before the live edge
+    new, tail = st.push(torch.zeros(8000))                                   # 2.5 s buffered, stream time 1.0 .. 3.5
+    assert new == [] and tail == "s0 s1"
+    new, tail = st.push(torch.zeros(2, 16000 * 2))                           # stereo input, 4.5 s buffered
+    assert [round(s.start, 2) for s in new] == [1.0, 2.0] and abs(st.offset_s - 3.0) < 1e-6
+    new, tail = st.flush()
+    assert tail == "" and [round(s.end, 2) for s in new] == [4.0, 5.0] and st.buffer.numel() == 0
+    assert len(st.committed) == 5 and st.text.startswith("s0")
+    assert StreamingTranscriber(Fake()).push(torch.zeros(100)) == ([], "")
