@@ -115,8 +115,13 @@ class ImagesService(_PipelineCache):
             return Sd3Pipeline(Sd3Components(S3.Sd3Transformer(cfg3, self.device, fp8=fp8 and not tiny), vae))
         if name.startswith("synthetic:"):
             tiny = name.endswith("-tiny")
-            cfg = F.tiny_flux() if tiny else F.FLUX_DEV
-            tr = F.FluxTransformer(cfg, self.device, fp8=fp8 and not tiny)
+            if "chroma" in name:
+                from ..models.dit import chroma as CH
+                cfg = CH.tiny_chroma() if tiny else CH.ChromaConfig()
+                tr = CH.ChromaTransformer(cfg, self.device, fp8=fp8 and not tiny)
+            else:
+                cfg = F.tiny_flux() if tiny else F.FLUX_DEV
+                tr = F.FluxTransformer(cfg, self.device, fp8=fp8 and not tiny)
             vae = Vae2dDecoder(tiny_vae2d() if tiny else FLUX_VAE, self.device,
                                torch.bfloat16 if self.device.startswith("cuda") else torch.float32)
             if tiny:   # the tiny DiT packs 4 latent channels
@@ -154,7 +159,19 @@ class ImagesService(_PipelineCache):
             renamed = flux_original_to_diffusers({k: get(k) for k in ck.keys()})
             get = renamed.get
             log.decision("Load", f"{path.name}: original Flux layout converted to diffusers names")
-        tr = F.FluxTransformer(F.FLUX_DEV, self.device, fp8=fp8, get=get)
+        if get("distilled_guidance_layer.in_proj.weight") is not None:
+            # Chroma: Flux blocks with the modulation table of an approximator network
+            import json as _json
+            from ..models.dit import chroma as CH
+            tdir = path / "transformer" if (path / "transformer").exists() else path
+            cc = _json.loads((tdir / "config.json").read_text()) if (tdir / "config.json").exists() else {}
+            ccfg = CH.ChromaConfig(num_double_blocks=int(cc.get("num_layers", 19)), num_single_blocks=int(cc.get("num_single_layers", 38)),
+                                   approximator_channels=int(cc.get("approximator_num_channels", 64)),
+                                   approximator_hidden=int(cc.get("approximator_hidden_dim", 5120)),
+                                   approximator_layers=int(cc.get("approximator_layers", 5)))
+            tr = CH.ChromaTransformer(ccfg, self.device, fp8=fp8, get=get)
+        else:
+            tr = F.FluxTransformer(F.FLUX_DEV, self.device, fp8=fp8, get=get)
         vae = enc = None
         if "vae" in spec.aux or (path / "vae").exists():
             vck = ShardedCheckpoint(spec.aux.get("vae", path / "vae"))

@@ -77,6 +77,10 @@ class _SingleWeights:
 
 
 class FluxTransformer:
+    # Variants whose AdaLN vectors do not come from per-block linears of the time / text embedding
+    # (Chroma) set this to False: those linears and the embedders are then not built.
+    HAS_MODULATION_LINEARS = True
+
     def __init__(self, cfg: FluxConfig = FLUX_DEV, device="cpu", comm: Optional[Comm] = None, fp8: bool = False,
                  get: Optional[Callable[[str], Optional[torch.Tensor]]] = None, seed: int = 0,
                  block_range: Optional[tuple[int, int]] = None, build_head: bool = True):
@@ -96,13 +100,17 @@ class FluxTransformer:
         first, last = self.block_range[0] == 0, self.block_range[1] == total_blocks
         self.x_embedder = f.linear("x_embedder", H, cfg.in_channels, allow_fp8=False) if first else None
         self.context_embedder = f.linear("context_embedder", H, cfg.context_dim) if first else None
-        self.t_in = f.linear("time_text_embed.timestep_embedder.linear_1", H, 256, allow_fp8=False)
-        self.t_out = f.linear("time_text_embed.timestep_embedder.linear_2", H, H)
-        if cfg.guidance_embed:
+        mods = self.HAS_MODULATION_LINEARS
+        lin_mod = (lambda name, n: f.linear(name, n * H, H)) if mods else (lambda name, n: None)
+        if mods:
+            self.t_in = f.linear("time_text_embed.timestep_embedder.linear_1", H, 256, allow_fp8=False)
+            self.t_out = f.linear("time_text_embed.timestep_embedder.linear_2", H, H)
+        if mods and cfg.guidance_embed:
             self.g_in = f.linear("time_text_embed.guidance_embedder.linear_1", H, 256, allow_fp8=False)
             self.g_out = f.linear("time_text_embed.guidance_embedder.linear_2", H, H)
-        self.p_in = f.linear("time_text_embed.text_embedder.linear_1", H, cfg.pooled_dim, allow_fp8=False)
-        self.p_out = f.linear("time_text_embed.text_embedder.linear_2", H, H)
+        if mods:
+            self.p_in = f.linear("time_text_embed.text_embedder.linear_1", H, cfg.pooled_dim, allow_fp8=False)
+            self.p_out = f.linear("time_text_embed.text_embedder.linear_2", H, H)
         self.double: list[tuple[_StreamWeights, _StreamWeights]] = []
         self.single: list[_SingleWeights] = []
         for i in range(cfg.num_double_blocks):
@@ -110,14 +118,14 @@ class FluxTransformer:
                 continue
             p = f"transformer_blocks.{i}."
             img = _StreamWeights(
-                mod=f.linear(p + "norm1.linear", 6 * H, H),
+                mod=lin_mod(p + "norm1.linear", 6),
                 qkv=self._qkv(f, [p + "attn.to_q", p + "attn.to_k", p + "attn.to_v"]),
                 q_norm=f.tensor(p + "attn.norm_q.weight", D, ones=True), k_norm=f.tensor(p + "attn.norm_k.weight", D, ones=True),
                 proj=f.linear(p + "attn.to_out.0", H, cfg.num_heads * D, shard="row"),
                 mlp_in=f.linear(p + "ff.net.0.proj", cfg.mlp_dim, H, shard="col"),
                 mlp_out=f.linear(p + "ff.net.2", H, cfg.mlp_dim, shard="row"))
             txt = _StreamWeights(
-                mod=f.linear(p + "norm1_context.linear", 6 * H, H),
+                mod=lin_mod(p + "norm1_context.linear", 6),
                 qkv=self._qkv(f, [p + "attn.add_q_proj", p + "attn.add_k_proj", p + "attn.add_v_proj"]),
                 q_norm=f.tensor(p + "attn.norm_added_q.weight", D, ones=True),
                 k_norm=f.tensor(p + "attn.norm_added_k.weight", D, ones=True),
@@ -132,7 +140,7 @@ class FluxTransformer:
             p = f"single_transformer_blocks.{i}."
             self.single.append(self._single(f, p))
         if last and build_head:
-            self.norm_out = f.linear("norm_out.linear", 2 * H, H)
+            self.norm_out = lin_mod("norm_out.linear", 2)
             self.proj_out = f.linear("proj_out", cfg.in_channels, H)
 
     # -- weight assembly ------------------------------------------------------------------
@@ -164,7 +172,7 @@ class FluxTransformer:
             bo = torch.zeros_like(bo)
         out = LinearWeight.from_dense(torch.cat([wo_a, wo_m], 1).contiguous().to(self.device), bo.to(self.device),
                                       fp8=f.fp8 and self.device.type == "cuda")
-        return _SingleWeights(mod=f.linear(p + "norm.linear", 3 * H, H),
+        return _SingleWeights(mod=f.linear(p + "norm.linear", 3 * H, H) if self.HAS_MODULATION_LINEARS else None,
                               qkv_mlp=LinearWeight.from_dense(w, b, fp8=f.fp8 and w.is_cuda),
                               q_norm=f.tensor(p + "attn.norm_q.weight", D, ones=True),
                               k_norm=f.tensor(p + "attn.norm_k.weight", D, ones=True), out=out)
@@ -211,6 +219,14 @@ class FluxTransformer:
         for i in range(len(s)):
             yield s.block(i)
         s.evict_all()
+
+    def _mod(self, temb_act: torch.Tensor, w, kind: str, index: int) -> torch.Tensor:
+        """AdaLN vectors of one block: ``kind`` is "img" / "txt" (double block ``index``) or "single".
+        Flux computes them from the time / text embedding; variants that look them up override this."""
+        return modulation(temb_act, w)
+
+    def _final_mod(self, temb_act: torch.Tensor) -> torch.Tensor:
+        return ops.linear(temb_act, self.norm_out)
 
     def _attend(self, q, k, v, batch: int) -> torch.Tensor:
         """q, k, v [B * S, Hl, D] -> [B * S, Hl * D]; one attention call per sample."""
@@ -276,7 +292,7 @@ class FluxTransformer:
         for bi, (wi, wt) in enumerate(self._blocks(self.double, "double")):
             if skip_rest:
                 break
-            mod_i, mod_t = modulation(temb_act, wi.mod), modulation(temb_act, wt.mod)
+            mod_i, mod_t = self._mod(temb_act, wi.mod, "img", self.block_range[0] + bi), self._mod(temb_act, wt.mod, "txt", self.block_range[0] + bi)
             qi, ki, vi = stream_pre(x_i, wi, mod_i, S_i, cos_i, sin_i)
             qt, kt, vt = stream_pre(x_t, wt, mod_t, S_t, cos_t, sin_t)
             # joint sequence per sample: [txt | img]
@@ -314,7 +330,7 @@ class FluxTransformer:
             cj, sj = (cos, sin) if B == 1 else (cos.repeat(B, 1), sin.repeat(B, 1))
             qkv_cols = 3 * self.hl * D
             for si, w in enumerate(self._blocks(self.single, "single")):
-                mod = modulation(temb_act, w.mod)
+                mod = self._mod(temb_act, w.mod, "single", si)
                 xn, _, xq = ops.norm(joint, None, shift=mod[:, 0:H], scale=mod[:, H:2 * H], rows_per_batch=S, layernorm=True,
                                      emit_fp8=self.fp8 and w.qkv_mlp.is_fp8, emit_bf16=not (self.fp8 and w.qkv_mlp.is_fp8))
                 fused = ops.linear(xq if xq is not None else xn, w.qkv_mlp)     # [T, 3 Hl D + mlp_l]
@@ -343,7 +359,7 @@ class FluxTransformer:
             return x_i, x_t, joint
         if use_cache and not skip_rest:
             step_cache.store_residual(first_x_i, x_i)
-        mo = ops.linear(temb_act, self.norm_out)                              # [B, 2H]: scale, shift
+        mo = self._final_mod(temb_act)                                        # [B, 2H]: scale, shift
         xn, _, _ = ops.norm(x_i.contiguous(), None, shift=mo[:, H:2 * H], scale=mo[:, 0:H], rows_per_batch=S_i, layernorm=True)
         out = ops.linear(xn, self.proj_out)
         return out.reshape(B, S_i, cfg.in_channels)

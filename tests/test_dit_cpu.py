@@ -295,3 +295,61 @@ def test_prompt_weighting():
     ratio = y[1].norm() / y[0].norm() / (x[1].norm() / x[0].norm())
     assert abs(float(ratio) - 2.0) < 1e-4
     assert apply_token_weights(x, [1.0, 1.0]) is x
+
+
+def test_chroma_slot_mapping_against_flux():
+    """A Flux model whose modulation linears ignore their input (zero weights) and whose biases hold
+    Chroma's table for one timestep computes the same function: this pins the slot order."""
+    import torch
+    from hartsyinference_b200.models.dit import flux as F
+    from hartsyinference_b200.models.dit.chroma import ChromaTransformer, tiny_chroma
+    ccfg = tiny_chroma()
+    chroma = ChromaTransformer(ccfg, "cpu", seed=3)
+    fcfg = F.tiny_flux(guidance_embed=False)
+    flux = F.FluxTransformer(fcfg, "cpu", seed=3)
+    H = ccfg.hidden_size
+    assert ccfg.mod_slots == 3 * 2 + 12 * 2 + 2
+    t = torch.tensor([0.35])
+    mods = chroma.modulations(t)
+    assert mods.shape == (1, ccfg.mod_slots, H)
+    assert not torch.allclose(mods, chroma.modulations(torch.tensor([0.9])), atol=1e-4)      # the table follows the timestep
+    assert not torch.allclose(mods[0, 0], mods[0, 1], atol=1e-4)                             # and the slot
+
+    def const(lw, vec):
+        lw.weight.zero_()
+        lw.bias.copy_(vec.reshape(-1).to(lw.bias.dtype))
+    for i in range(2):
+        const(flux.single[i].mod, mods[0, 3 * i:3 * i + 3])
+        const(flux.double[i][0].mod, mods[0, 6 + 6 * i:12 + 6 * i])
+        const(flux.double[i][1].mod, mods[0, 6 + 12 + 6 * i:6 + 12 + 6 * i + 6])
+    const(flux.norm_out, torch.stack([mods[0, -1], mods[0, -2]]))                            # Flux keeps (scale, shift)
+    # the same block weights on both sides
+    for (ci, ct), (fi, ft) in zip(chroma.double, flux.double):
+        for a, b in ((ci, fi), (ct, ft)):
+            for n in ("qkv", "q_norm", "k_norm", "proj", "mlp_in", "mlp_out"):
+                setattr(a, n, getattr(b, n))
+    for a, b in zip(chroma.single, flux.single):
+        for n in ("qkv_mlp", "q_norm", "k_norm", "out"):
+            setattr(a, n, getattr(b, n))
+    chroma.x_embedder, chroma.context_embedder, chroma.proj_out = flux.x_embedder, flux.context_embedder, flux.proj_out
+    g = torch.Generator().manual_seed(1)
+    S_i, S_t = 16, 6
+    img, txt = torch.randn(1, S_i, fcfg.in_channels, generator=g), torch.randn(1, S_t, fcfg.context_dim, generator=g)
+    pooled = torch.zeros(1, fcfg.pooled_dim)
+    img_ids, txt_ids = F.flux_ids(4, 4, S_t)
+    want = flux.forward(img, txt, t, pooled, img_ids, txt_ids)
+    got = chroma.forward(img, txt, t, pooled, img_ids, txt_ids)
+    assert torch.allclose(got.float(), want.float(), atol=2e-2) and want.float().abs().max() > 0.05
+    assert not hasattr(chroma, "t_in") and chroma.double[0][0].mod is None
+
+
+def test_chroma_through_the_image_service():
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec
+    from hartsyinference_b200.engine.requests import ImageRequest
+    eng = InferenceEngine("cpu")
+    req = ImageRequest(prompt="a harbour", negative_prompt="fog", width=64, height=64, steps=2, cfg_scale=3.0, seed=4)
+    a = eng.images.generate(ModelSpec("synthetic:chroma-tiny"), req)
+    b = eng.images.generate(ModelSpec("synthetic:chroma-tiny"), req)
+    assert (a.width, a.height) == (64, 64) and a.rgb == b.rgb
+    assert type(eng.images.pipeline(ModelSpec("synthetic:chroma-tiny")).c.transformer).__name__ == "ChromaTransformer"
+    eng.close()
