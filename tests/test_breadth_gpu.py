@@ -125,3 +125,20 @@ def test_sd3_transformer_on_device_matches_cpu():
     a = cpu.forward(lat, txt, sigma, pooled).float()
     b = gpu.forward(lat, txt, sigma, pooled).float().cpu()
     assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.99
+
+
+def test_chroma_on_device_matches_cpu():
+    from hartsyinference_b200.models.dit import flux as F
+    from hartsyinference_b200.models.dit.chroma import ChromaTransformer, tiny_chroma
+    cfg = tiny_chroma(head_dim=64, num_heads=2, axes_dim=(16, 24, 24))
+    cpu, gpu = ChromaTransformer(cfg, "cpu", seed=2), ChromaTransformer(cfg, "cuda", seed=2)
+    g = torch.Generator().manual_seed(1)
+    S_i, S_t = 64, 16
+    img, txt = torch.randn(1, S_i, cfg.in_channels, generator=g), torch.randn(1, S_t, cfg.context_dim, generator=g)
+    pooled = torch.zeros(1, cfg.pooled_dim)
+    t = torch.tensor([0.5])
+    outs = []
+    for m, dev in ((cpu, "cpu"), (gpu, "cuda")):
+        img_ids, txt_ids = F.flux_ids(8, 8, S_t, dev)
+        outs.append(m.forward(img.to(dev), txt.to(dev), t.to(dev), pooled.to(dev), img_ids, txt_ids).float().cpu())
+    assert torch.nn.functional.cosine_similarity(outs[0].flatten(), outs[1].flatten(), dim=0) > 0.99
