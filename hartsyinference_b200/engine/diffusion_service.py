@@ -171,7 +171,15 @@ class ImagesService(_PipelineCache):
                                    approximator_layers=int(cc.get("approximator_layers", 5)))
             tr = CH.ChromaTransformer(ccfg, self.device, fp8=fp8, get=get)
         else:
-            tr = F.FluxTransformer(F.FLUX_DEV, self.device, fp8=fp8, get=get)
+            import dataclasses
+            base = F.FLUX_DEV
+            xw = get("x_embedder.weight")
+            if xw is not None and xw.shape[1] != base.in_channels:
+                # a Fill / Canny / Depth variant: more input channels than predicted ones
+                base = dataclasses.replace(base, in_channels=int(xw.shape[1]), out_channels=base.in_channels)
+            if get("time_text_embed.guidance_embedder.linear_1.weight") is None:
+                base = dataclasses.replace(base, guidance_embed=False)          # schnell-class checkpoints
+            tr = F.FluxTransformer(base, self.device, fp8=fp8, get=get)
         vae = enc = None
         if "vae" in spec.aux or (path / "vae").exists():
             vck = ShardedCheckpoint(spec.aux.get("vae", path / "vae"))

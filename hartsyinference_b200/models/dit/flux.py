@@ -40,6 +40,11 @@ class FluxConfig:
     axes_dim: tuple = (16, 56, 56)
     theta: float = 10000.0
     guidance_embed: bool = True
+    out_channels: int = 0            # 0 = in_channels; the Fill / Canny / Depth variants read more channels than they predict
+
+    @property
+    def latent_channels(self) -> int:
+        return self.out_channels or self.in_channels
 
     @property
     def mlp_dim(self) -> int:
@@ -47,6 +52,10 @@ class FluxConfig:
 
 
 FLUX_DEV = FluxConfig()
+# Structural-conditioning variants (FLUX.1 Canny / Depth): the control image's latents ride along
+# the noisy latents channel-wise; FLUX.1 Fill adds the 8 x 8-folded mask (64 + 64 + 256 channels).
+FLUX_CONTROL = FluxConfig(in_channels=128, out_channels=64)
+FLUX_FILL = FluxConfig(in_channels=384, out_channels=64)
 
 
 def tiny_flux(**over) -> FluxConfig:
@@ -141,7 +150,7 @@ class FluxTransformer:
             self.single.append(self._single(f, p))
         if last and build_head:
             self.norm_out = lin_mod("norm_out.linear", 2)
-            self.proj_out = f.linear("proj_out", cfg.in_channels, H)
+            self.proj_out = f.linear("proj_out", cfg.latent_channels, H)
 
     # -- weight assembly ------------------------------------------------------------------
     def _qkv(self, f: WeightFactory, names) -> LinearWeight:
@@ -362,7 +371,7 @@ class FluxTransformer:
         mo = self._final_mod(temb_act)                                        # [B, 2H]: scale, shift
         xn, _, _ = ops.norm(x_i.contiguous(), None, shift=mo[:, H:2 * H], scale=mo[:, 0:H], rows_per_batch=S_i, layernorm=True)
         out = ops.linear(xn, self.proj_out)
-        return out.reshape(B, S_i, cfg.in_channels)
+        return out.reshape(B, S_i, cfg.latent_channels)
 
 
 def flux_ids(height_tokens: int, width_tokens: int, text_tokens: int, device="cpu") -> tuple[torch.Tensor, torch.Tensor]:

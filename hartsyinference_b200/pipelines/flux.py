@@ -96,7 +96,7 @@ class FluxPipeline:
                 on_step: Optional[Callable[[StepPreview], None]] = None, step_cache_threshold: float = 0.0, first_block_cache: float = 0.0,
                 latents: Optional[torch.Tensor] = None, init_latents: Optional[torch.Tensor] = None, strength: float = 1.0,
                 mask: Optional[torch.Tensor] = None, control_latents: Optional[torch.Tensor] = None,
-                control_strength: float = 1.0) -> torch.Tensor:
+                control_strength: float = 1.0, channel_cond: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Returns the final latents [1, C, H/8, W/8] fp32 on the device.
 
         ``init_latents`` [1, C, H/8, W/8] with ``strength`` < 1 starts from the image noised to the
@@ -105,7 +105,7 @@ class FluxPipeline:
         re-noised to each step's sigma (inpainting)."""
         tr = self.c.transformer
         dev = self.device
-        C = tr.cfg.in_channels // 4
+        C = tr.cfg.latent_channels // 4
         lh, lw = height // 8, width // 8
         g = torch.Generator().manual_seed(seed)
         z = latents if latents is not None else torch.randn(1, C, lh, lw, generator=g)
@@ -113,6 +113,12 @@ class FluxPipeline:
         S = x.shape[1]
         img_ids, txt_ids = flux_ids(lh // 2, lw // 2, ctx.shape[0], dev)
         sched = FlowMatchEulerScheduler(steps, mu=flux_mu(S))
+        extra_packed = None
+        if tr.cfg.in_channels != tr.cfg.latent_channels:
+            if channel_cond is None or channel_cond.shape[2] != tr.cfg.in_channels - tr.cfg.latent_channels:
+                raise ValueError(f"this transformer reads {tr.cfg.in_channels - tr.cfg.latent_channels} conditioning channels "
+                                 "per token beside the latents (a control image, or image + mask for the Fill variant)")
+            extra_packed = channel_cond.to(dev).to(torch.bfloat16).contiguous()
         ctrl_packed = None
         if control_latents is not None and self.c.controlnet is not None:
             ctrl_packed = pack_latents(control_latents.float()).to(dev).to(torch.bfloat16).contiguous()
@@ -162,6 +168,8 @@ class FluxPipeline:
                 v_cond, v_unc = cache_v, None
             else:
                 xin = x.to(torch.bfloat16)
+                if extra_packed is not None:      # Canny / Depth / Fill variants: conditioning rides along channel-wise
+                    xin = torch.cat([xin, extra_packed], 2)
                 ctl = None
                 if ctrl_packed is not None:      # the ControlNet branch sees the conditional prompt
                     ctl = self.c.controlnet.residuals(xin, ctrl_packed, ctx_d, sigma, pooled_d, img_ids, txt_ids, gvec, control_strength)
@@ -218,6 +226,27 @@ class FluxPipeline:
             self._fused_cfg_obj = None
         return self._fused_cfg_obj
 
+    def _channel_conditioning(self, req: ImageRequest) -> torch.Tensor:
+        """Packed per-token conditioning [1, S, extra] for the channel-concatenation variants:
+        Canny / Depth = the control image's latents; Fill = the masked image's latents and the mask
+        folded 8 x 8 into channels (then packed 2 x 2 like the latents)."""
+        tcfg = self.c.transformer.cfg
+        extra = tcfg.in_channels - tcfg.latent_channels
+        if self.c.vae_encoder is None:
+            raise ValueError("this variant needs the VAE encoder to embed its conditioning image")
+        h, w = req.height, req.width
+        if extra == tcfg.latent_channels:                    # control image only
+            if req.control_image is None:
+                raise ValueError("this model needs ImageRequest.control_image")
+            return pack_latents(self.c.vae_encoder.encode(self._image_tensor(req.control_image, w, h)).float())
+        if req.init_image is None or req.mask_image is None:
+            raise ValueError("the Fill variant needs ImageRequest.init_image and mask_image")
+        img = self._image_tensor(req.init_image, w, h)
+        m = (self._image_tensor(req.mask_image, w, h)[:, :1] * 0.5 + 0.5 > 0.5).float()
+        lat = pack_latents(self.c.vae_encoder.encode(img * (1 - m)).float())
+        folded = m.reshape(1, h // 8, 8, w // 8, 8).permute(0, 2, 4, 1, 3).reshape(1, 64, h // 8, w // 8)
+        return torch.cat([lat, pack_latents(folded).to(lat.device)], 2)
+
     @staticmethod
     def _image_tensor(image, width: int, height: int) -> torch.Tensor:
         """Path, PIL image, uint8 HWC array / tensor or float CHW tensor in [0, 1] -> [1, 3, height, width] in [-1, 1]."""
@@ -254,14 +283,18 @@ class FluxPipeline:
             if getattr(req, "mask_image", None) is not None:
                 m = self._image_tensor(req.mask_image, req.width, req.height)[:, :1] * 0.5 + 0.5
                 mask = (torch.nn.functional.interpolate(m, size=(req.height // 8, req.width // 8), mode="area") > 0.5).float()
-        control_latents = None
-        if getattr(req, "control_image", None) is not None:
+        control_latents = channel_cond = None
+        tcfg = self.c.transformer.cfg
+        if tcfg.in_channels != tcfg.latent_channels:
+            channel_cond = self._channel_conditioning(req)
+        elif getattr(req, "control_image", None) is not None:
             if self.c.controlnet is None or self.c.vae_encoder is None:
                 raise ValueError("a control image needs a ControlNet and the VAE encoder (FluxComponents.controlnet / vae_encoder)")
             control_latents = self.c.vae_encoder.encode(self._image_tensor(req.control_image, req.width, req.height))
         z = self.denoise(ctx, pooled, req.height, req.width, req.steps, req.guidance, seed, neg, req.cfg_scale, on_step,
                          req.step_cache_threshold, init_latents=init_latents, strength=req.strength, mask=mask,
-                         control_latents=control_latents, control_strength=getattr(req, "control_strength", 1.0))
+                         control_latents=control_latents, control_strength=getattr(req, "control_strength", 1.0),
+                         channel_cond=channel_cond)
         t_denoise = time.perf_counter() - t0
         if self.c.vae is None:
             img = torch.zeros(1, 3, req.height, req.width)

@@ -353,3 +353,35 @@ def test_chroma_through_the_image_service():
     assert (a.width, a.height) == (64, 64) and a.rgb == b.rgb
     assert type(eng.images.pipeline(ModelSpec("synthetic:chroma-tiny")).c.transformer).__name__ == "ChromaTransformer"
     eng.close()
+
+
+def test_flux_channel_conditioned_variants():
+    """Canny / Depth (latents + control latents) and Fill (latents + masked image + folded mask)."""
+    import pytest
+    import torch
+    from hartsyinference_b200.engine.requests import ImageRequest
+    from hartsyinference_b200.models.dit import flux as F
+    from hartsyinference_b200.models.vae.vae2d import Vae2dDecoder, Vae2dEncoder, tiny_vae2d
+    from hartsyinference_b200.pipelines.flux import FluxComponents, FluxPipeline
+    assert F.FLUX_CONTROL.latent_channels == 64 and F.FLUX_FILL.in_channels == 64 + 64 + 256
+    v = tiny_vae2d()
+    edges = torch.zeros(3, 64, 64)
+    edges[:, 30:34] = 1.0
+    for extra in (16, 16 + 256):            # tiny latents pack to 16 channels; the folded mask to 64 * 4
+        cfg = F.tiny_flux(in_channels=16 + extra, out_channels=16)
+        tr = F.FluxTransformer(cfg, "cpu", seed=0)
+        assert tr.proj_out.weight.shape[0] == 16 and tr.x_embedder.weight.shape[1] == 16 + extra
+        pipe = FluxPipeline(FluxComponents(tr, Vae2dDecoder(v, "cpu", torch.float32), vae_encoder=Vae2dEncoder(v, "cpu", torch.float32)))
+        if extra == 16:
+            a = pipe.generate(ImageRequest(prompt="x", width=64, height=64, steps=2, seed=3, control_image=edges))
+            b = pipe.generate(ImageRequest(prompt="x", width=64, height=64, steps=2, seed=3, control_image=edges * 0))
+            with pytest.raises(ValueError):
+                pipe.generate(ImageRequest(prompt="x", width=64, height=64, steps=1))
+        else:
+            mask = torch.zeros(64, 64)
+            mask[16:48, 16:48] = 1
+            a = pipe.generate(ImageRequest(prompt="x", width=64, height=64, steps=2, seed=3, init_image=torch.rand(3, 64, 64), mask_image=mask, strength=1.0))
+            b = pipe.generate(ImageRequest(prompt="x", width=64, height=64, steps=2, seed=3, init_image=torch.rand(3, 64, 64), mask_image=mask * 0, strength=1.0))
+            cond = pipe._channel_conditioning(ImageRequest(width=64, height=64, init_image=torch.rand(3, 64, 64), mask_image=mask))
+            assert cond.shape == (1, 16, 16 + 256) and set(cond[0, :, 16:].unique().tolist()) <= {0.0, 1.0}
+        assert (a.width, a.height) == (64, 64) and a.rgb != b.rgb
