@@ -359,3 +359,31 @@ def test_recurrent_models_through_the_text_service(kind, tmp_path):
         assert any(k.startswith("ssm|") for k in eng.loaded_pipeline_keys)
     finally:
         eng.text.release()
+
+
+def test_t5_seq2seq_matches_transformers():
+    transformers = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.encoders.t5 import T5Config, T5Seq2Seq
+    c = transformers.T5Config(vocab_size=128, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_decoder_layers=2, num_heads=4,
+                              feed_forward_proj="gated-gelu", tie_word_embeddings=False, decoder_start_token_id=0, eos_token_id=1, pad_token_id=0)
+    torch.manual_seed(0)
+    hf = transformers.T5ForConditionalGeneration(c).eval()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.ndim >= 2:
+                p.mul_(2.0)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    m = T5Seq2Seq(T5Config(vocab_size=128, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_heads=4), "cpu", get=lambda n: sd.get(n))
+    src = torch.tensor([5, 17, 33, 9, 1])
+    dec = torch.tensor([0, 11, 23, 47, 60, 3])
+    with torch.no_grad():
+        ref = hf(input_ids=src[None], decoder_input_ids=dec[None]).logits[0]
+    st = m.start(m.encoder.encode(src))
+    mine = torch.cat([m.decode(st, dec[:3]), m.decode(st, dec[3:4]), m.decode(st, dec[4:])])
+    assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0) > 0.999
+    assert (mine.argmax(-1) == ref.argmax(-1)).float().mean() >= 0.8
+    with torch.no_grad():
+        gen = hf.generate(input_ids=src[None], max_new_tokens=8, do_sample=False)[0].tolist()
+    want = [t for t in gen[1:] if t != 1]
+    got = m.generate(src, max_new=8)
+    assert got[: len(want)] == want[: len(got)] and len(got) > 0
