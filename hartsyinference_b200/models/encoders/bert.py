@@ -27,6 +27,7 @@ class BertConfig:
     type_vocab: int = 2
     eps: float = 1e-12
     pooling: str = "mean"          # mean | cls
+    position_offset: int = 0       # RoBERTa / XLM-R number positions from padding_idx + 1 (= 2)
 
 
 def tiny_bert() -> BertConfig:
@@ -40,6 +41,9 @@ class BertEncoder:
         if get is not None and prefix == "" and get("embeddings.word_embeddings.weight") is None \
                 and get("bert.embeddings.word_embeddings.weight") is not None:
             prefix = "bert."
+        if get is not None and prefix == "" and get("embeddings.word_embeddings.weight") is None \
+                and get("roberta.embeddings.word_embeddings.weight") is not None:
+            prefix = "roberta."
         f = WeightFactory(self.device, False, get=get, seed=seed)
         H = cfg.hidden
         e = prefix + "embeddings."
@@ -67,11 +71,12 @@ class BertEncoder:
         """ids [L] (one unpadded sequence) -> [L, H]."""
         cfg = self.cfg
         L = ids.shape[0]
-        if L > cfg.max_len:
-            raise ValueError(f"sequence of {L} tokens exceeds the model's {cfg.max_len} positions")
+        off = cfg.position_offset
+        if L + off > cfg.max_len:
+            raise ValueError(f"sequence of {L} tokens exceeds the model's {cfg.max_len - off} positions")
         ids = ids.long().to(self.device)
         tt = torch.zeros_like(ids) if type_ids is None else type_ids.long().to(self.device)
-        x = (self.tok[ids].float() + self.pos[:L].float() + self.typ[tt].float()).to(torch.bfloat16)
+        x = (self.tok[ids].float() + self.pos[off:off + L].float() + self.typ[tt].float()).to(torch.bfloat16)
         x, _, _ = ops.norm(x, self.ln_w, bias=self.ln_b, layernorm=True, eps=cfg.eps)
         d = cfg.hidden // cfg.heads
         for b in self.blocks:

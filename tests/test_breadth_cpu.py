@@ -387,3 +387,31 @@ def test_t5_seq2seq_matches_transformers():
     want = [t for t in gen[1:] if t != 1]
     got = m.generate(src, max_new=8)
     assert got[: len(want)] == want[: len(got)] and len(got) > 0
+
+
+def test_xlm_roberta_embeddings_match_transformers(tmp_path):
+    transformers = pytest.importorskip("transformers")
+    import json
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec
+    from hartsyinference_b200.models.encoders.bert import BertConfig, BertEncoder
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    c = transformers.XLMRobertaConfig(vocab_size=40, hidden_size=128, num_hidden_layers=2, num_attention_heads=2, intermediate_size=256,
+                                      max_position_embeddings=40, type_vocab_size=1, pad_token_id=1, bos_token_id=0, eos_token_id=2)
+    torch.manual_seed(0)
+    hf = transformers.XLMRobertaModel(c, add_pooling_layer=False).eval()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    cfg = BertConfig(vocab_size=40, hidden=128, layers=2, heads=2, intermediate=256, max_len=40, type_vocab=1, eps=c.layer_norm_eps, position_offset=2)
+    enc = BertEncoder(cfg, "cpu", get=lambda n: sd.get(n))
+    ids = torch.tensor([0, 7, 9, 30, 2])
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).last_hidden_state[0]
+    assert torch.nn.functional.cosine_similarity(enc.hidden_states(ids).float().flatten(), ref.flatten(), dim=0) > 0.995
+    d = tmp_path / "xlmr"
+    save_hf_checkpoint({**c.to_dict(), "model_type": "xlm-roberta"}, {k: v.contiguous() for k, v in sd.items()}, d)
+    pieces = [["<s>", 0.0], ["<pad>", 0.0], ["</s>", 0.0], ["<unk>", 0.0], ["▁", -2.0]] + [[ch, -3.0] for ch in "abcdefghijklmnopqrstuvwxyz"]
+    (d / "tokenizer.json").write_text(json.dumps({"model": {"type": "Unigram", "unk_id": 3, "vocab": pieces},
+                                                  "added_tokens": [{"id": i, "content": p[0], "special": True} for i, p in enumerate(pieces[:4])]}))
+    eng = InferenceEngine("cpu")
+    emb = eng.embeddings.embed(ModelSpec(str(d)), ["hello world", "goodbye"])
+    assert emb.shape == (2, 128) and torch.allclose(emb.norm(dim=-1), torch.ones(2), atol=1e-3)
+    eng.close()
