@@ -96,6 +96,7 @@ class TransformerConfig:
     use_rope: bool = True               # False: learned absolute positions instead (GPT-2)
     learned_positions: bool = False
     nope_global: bool = False           # full-attention layers carry no rotary embedding (Cohere 2)
+    lm_head_bias: bool = False          # the output projection has a bias (Phi-1 / Phi-2)
     moe: Optional[MoeConfig] = None
     mla: Optional[MlaConfig] = None
     bos_token_id: int = 1
@@ -205,7 +206,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / phi / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "gpt2":          # GPT-2 names its sizes differently
@@ -291,6 +292,10 @@ def from_hf_config(d: dict) -> TransformerConfig:
         kw.update(norm_type="layernorm", norm_bias=True, norm_plus_one=True, gated_ffn=False,
                   qkv_bias=bool(d.get("attention_bias", False)), o_bias=bool(d.get("attention_bias", False)),
                   ffn_bias=bool(d.get("mlp_bias", False)))
+    if mt == "phi":           # Phi-1 / Phi-2: one LayerNorm feeds the parallel attention and MLP branches
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=True, o_bias=True, ffn_bias=True,
+                  parallel_residual=True, shared_parallel_norm=True, lm_head_bias=True,
+                  num_kv_heads=d.get("num_key_value_heads") or heads)
     if mt == "gpt_neox":
         ab = bool(d.get("attention_bias", True))
         kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=ab, o_bias=ab, ffn_bias=True,

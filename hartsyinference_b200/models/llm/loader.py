@@ -198,6 +198,15 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
                 name = name.replace(std, own)
             return get(name)
         return g
+    if mt == "phi":
+        ren = (("model.norm", "model.final_layernorm"), ("self_attn.o_proj", "self_attn.dense"), ("mlp.up_proj", "mlp.fc1"),
+               ("mlp.down_proj", "mlp.fc2"))
+
+        def g(name: str):
+            for std, own in ren:
+                name = name.replace(std, own)
+            return get(name)
+        return g
     if mt == "starcoder2":
         return lambda name: get(name.replace("mlp.up_proj", "mlp.c_fc").replace("mlp.down_proj", "mlp.c_proj"))
     if mt == "gpt_neox":

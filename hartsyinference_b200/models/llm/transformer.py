@@ -167,7 +167,13 @@ class DecoderModel:
         hw = head[v0:v1]
         if hw.shape[0] < self.vocab_local:   # pad the last shard so every rank has the same shape
             hw = torch.cat([hw, torch.zeros(self.vocab_local - hw.shape[0], hw.shape[1], dtype=hw.dtype)])
-        self.lm_head = self._lw(hw.to(dt), allow_fp8=False)
+        hb = None
+        if cfg.lm_head_bias and get("lm_head.bias") is not None:
+            hb = get("lm_head.bias")[v0:v1]
+            if hb.shape[0] < self.vocab_local:
+                hb = torch.cat([hb, torch.zeros(self.vocab_local - hb.shape[0], dtype=hb.dtype)])
+            hb = hb.to(dt)
+        self.lm_head = self._lw(hw.to(dt), hb, allow_fp8=False)
         self.final_norm = need("model.norm.weight").to(dt).to(self.device)
         dev = lambda t_: None if t_ is None else t_.to(dt).to(self.device)
         self.final_norm_b = dev(get("model.norm.bias")) if cfg.norm_bias else None
