@@ -206,9 +206,13 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / phi / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / gptj / phi / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
+    if mt == "gptj":
+        d = {**d, "hidden_size": d["n_embd"], "num_hidden_layers": d["n_layer"], "num_attention_heads": d["n_head"],
+             "max_position_embeddings": d.get("n_positions", 2048), "intermediate_size": d.get("n_inner") or 4 * d["n_embd"],
+             "hidden_act": d.get("activation_function", "gelu_new"), "tie_word_embeddings": d.get("tie_word_embeddings", False)}
     if mt == "gpt2":          # GPT-2 names its sizes differently
         d = {**d, "hidden_size": d["n_embd"], "num_hidden_layers": d["n_layer"], "num_attention_heads": d["n_head"],
              "max_position_embeddings": d.get("n_positions", 1024), "intermediate_size": d.get("n_inner") or 4 * d["n_embd"],
@@ -292,6 +296,10 @@ def from_hf_config(d: dict) -> TransformerConfig:
         kw.update(norm_type="layernorm", norm_bias=True, norm_plus_one=True, gated_ffn=False,
                   qkv_bias=bool(d.get("attention_bias", False)), o_bias=bool(d.get("attention_bias", False)),
                   ffn_bias=bool(d.get("mlp_bias", False)))
+    if mt == "gptj":          # one LayerNorm, parallel branches, interleaved rotary on the first rotary_dim channels
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=False, o_bias=False, ffn_bias=True,
+                  parallel_residual=True, shared_parallel_norm=True, lm_head_bias=True, rope_style=1, num_kv_heads=heads,
+                  rope_dim=int(d.get("rotary_dim") or 0))
     if mt == "phi":           # Phi-1 / Phi-2: one LayerNorm feeds the parallel attention and MLP branches
         kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=True, o_bias=True, ffn_bias=True,
                   parallel_residual=True, shared_parallel_norm=True, lm_head_bias=True,

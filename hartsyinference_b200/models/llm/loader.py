@@ -198,6 +198,16 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
                 name = name.replace(std, own)
             return get(name)
         return g
+    if mt == "gptj":
+        ren = (("model.embed_tokens", "transformer.wte"), ("model.norm", "transformer.ln_f"), ("model.layers", "transformer.h"),
+               ("input_layernorm", "ln_1"), ("self_attn.o_proj", "attn.out_proj"), ("self_attn.", "attn."),
+               ("mlp.up_proj", "mlp.fc_in"), ("mlp.down_proj", "mlp.fc_out"))
+
+        def g(name: str):
+            for std, own in ren:
+                name = name.replace(std, own)
+            return get(name)
+        return g
     if mt == "phi":
         ren = (("model.norm", "model.final_layernorm"), ("self_attn.o_proj", "self_attn.dense"), ("mlp.up_proj", "mlp.fc1"),
                ("mlp.down_proj", "mlp.fc2"))
