@@ -97,6 +97,7 @@ class TransformerConfig:
     learned_positions: bool = False
     nope_global: bool = False           # full-attention layers carry no rotary embedding (Cohere 2)
     lm_head_bias: bool = False          # the output projection has a bias (Phi-1 / Phi-2)
+    learned_position_offset: int = 0    # rows skipped at the start of the learned position table (OPT: 2)
     moe: Optional[MoeConfig] = None
     mla: Optional[MlaConfig] = None
     bos_token_id: int = 1
@@ -206,9 +207,12 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / gptj / phi / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / gptj / opt / phi / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
+    if mt == "opt":
+        d = {**d, "intermediate_size": d.get("ffn_dim") or 4 * d["hidden_size"], "hidden_act": d.get("activation_function", "relu"),
+             "tie_word_embeddings": d.get("tie_word_embeddings", True)}
     if mt == "gptj":
         d = {**d, "hidden_size": d["n_embd"], "num_hidden_layers": d["n_layer"], "num_attention_heads": d["n_head"],
              "max_position_embeddings": d.get("n_positions", 2048), "intermediate_size": d.get("n_inner") or 4 * d["n_embd"],
@@ -296,6 +300,12 @@ def from_hf_config(d: dict) -> TransformerConfig:
         kw.update(norm_type="layernorm", norm_bias=True, norm_plus_one=True, gated_ffn=False,
                   qkv_bias=bool(d.get("attention_bias", False)), o_bias=bool(d.get("attention_bias", False)),
                   ffn_bias=bool(d.get("mlp_bias", False)))
+    if mt == "opt":
+        if not d.get("do_layer_norm_before", True) or d.get("word_embed_proj_dim", hidden) != hidden:
+            raise ValueError("OPT variants with post-LayerNorm blocks or projected embeddings (350m) are not mapped")
+        b = bool(d.get("enable_bias", True))
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=b, o_bias=b, ffn_bias=b, use_rope=False,
+                  learned_positions=True, learned_position_offset=2, num_kv_heads=heads)
     if mt == "gptj":          # one LayerNorm, parallel branches, interleaved rotary on the first rotary_dim channels
         kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=False, o_bias=False, ffn_bias=True,
                   parallel_residual=True, shared_parallel_norm=True, lm_head_bias=True, rope_style=1, num_kv_heads=heads,

@@ -198,6 +198,21 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
                 name = name.replace(std, own)
             return get(name)
         return g
+    if mt == "opt":
+        layer = (("input_layernorm", "self_attn_layer_norm"), ("post_attention_layernorm", "final_layer_norm"),
+                 ("self_attn.o_proj", "self_attn.out_proj"), ("mlp.up_proj", "fc1"), ("mlp.down_proj", "fc2"))
+
+        def g(name: str):
+            if name.startswith("model.layers."):
+                for std, own in layer:
+                    name = name.replace(std, own)
+                return get("model.decoder." + name[len("model."):])
+            if name.startswith("model.norm."):
+                return get("model.decoder.final_layer_norm." + name[len("model.norm."):])
+            if name.startswith("model.embed_"):
+                return get("model.decoder." + name[len("model."):])
+            return get(name)
+        return g
     if mt == "gptj":
         ren = (("model.embed_tokens", "transformer.wte"), ("model.norm", "transformer.ln_f"), ("model.layers", "transformer.h"),
                ("input_layernorm", "ln_1"), ("self_attn.o_proj", "attn.out_proj"), ("self_attn.", "attn."),

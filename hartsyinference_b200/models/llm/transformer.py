@@ -574,7 +574,7 @@ class DecoderModel:
         else:
             x = ops.embedding(batch.tokens, self.embed, cfg.embed_scale * cfg.embedding_multiplier)
         if self.pos_embed is not None and hidden_in is None:
-            x = (x.float() + self.pos_embed[batch.positions.long()].float()).to(x.dtype)
+            x = (x.float() + self.pos_embed[batch.positions.long() + cfg.learned_position_offset].float()).to(x.dtype)
         scale = self._attn_scale()
         fp8 = self.fp8 and x.is_cuda
         if cfg.general_path:

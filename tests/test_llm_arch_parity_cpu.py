@@ -43,6 +43,7 @@ ARCHS = {
     "nemotron": ("NemotronConfig", dict()),
     "gpt_neox": ("GPTNeoXConfig", dict()),
     "phi": ("PhiConfig", dict()),
+    "opt": ("OPTConfig", dict(ffn_dim=256, word_embed_proj_dim=128)),
     "gptj": ("GPTJConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, rotary_dim=16)),
     "deepseek_v3": ("DeepseekV3Config", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                                              q_lora_rank=64, kv_lora_rank=512, qk_nope_head_dim=32, qk_rope_head_dim=64,
