@@ -97,6 +97,7 @@ class TransformerConfig:
     learned_positions: bool = False
     nope_global: bool = False           # full-attention layers carry no rotary embedding (Cohere 2)
     lm_head_bias: bool = False          # the output projection has a bias (Phi-1 / Phi-2)
+    rope_layers: tuple = ()             # per layer: 1 = rotary embedding, 0 = none (SmolLM 3)
     learned_position_offset: int = 0    # rows skipped at the start of the learned position table (OPT: 2)
     moe: Optional[MoeConfig] = None
     mla: Optional[MlaConfig] = None
@@ -123,7 +124,7 @@ class TransformerConfig:
         """Architectures whose block structure is outside the fused decode path: they run the same
         kernels through an unfused layer loop."""
         return (not self.pre_norm or self.qk_norm_full or self.norm_type != "rms" or self.parallel_residual
-                or not self.use_rope or self.nope_global
+                or not self.use_rope or self.nope_global or bool(self.rope_layers)
                 or self.o_bias or self.ffn_bias or not self.gated_ffn or self.activation not in ("silu", "gelu_tanh"))
 
     def layer_window(self, layer: int) -> int:
@@ -207,7 +208,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / gptj / opt / phi / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -256,10 +257,25 @@ def from_hf_config(d: dict) -> TransformerConfig:
     if mt in ("qwen3", "qwen3_moe", "olmo2", "olmoe"):
         kw["qk_norm"] = True
         kw["qkv_bias"] = bool(d.get("attention_bias", False))
-    if mt in ("olmo2", "olmoe"):
+    if mt in ("olmo2", "olmo3", "olmoe"):
         kw["qk_norm_full"] = True
-    if mt == "olmo2":
+        kw["qk_norm"] = True
+    if mt in ("olmo2", "olmo3", "exaone4"):
         kw.update(pre_norm=False, post_norms=True)
+    if mt == "exaone4":
+        kw["qk_norm"] = True                      # per head, before the rotary embedding
+    if mt in ("olmo3", "exaone4", "ministral", "smollm3"):
+        kw.update(sliding_window=int(d.get("sliding_window") or 0), layer_types=tuple(d.get("layer_types") or ()))
+    if mt == "exaone4" and kw.get("sliding_window"):
+        kw["nope_global"] = True                  # hybrid models: full-attention layers carry no rotary embedding
+    if mt == "olmo":
+        kw.update(norm_type="layernorm", rms_eps=1e-5)        # parameter-free LayerNorm
+    if mt in ("helium", "ernie4_5"):
+        kw["rope_style"] = 1                      # interleaved rotary pairs
+    if mt == "arcee":
+        kw.update(gated_ffn=False)                # relu^2 MLP without a gate
+    if mt == "smollm3" and d.get("no_rope_layers"):
+        kw["rope_layers"] = tuple(int(v) for v in d["no_rope_layers"])       # 1 = rotary, 0 = none
     if mt.startswith("gemma"):
         kw.update(norm_plus_one=True, embed_scale=hidden ** 0.5, activation="gelu_tanh",
                   logit_softcap=float(d.get("final_logit_softcapping") or 0.0),

@@ -198,6 +198,14 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
                 name = name.replace(std, own)
             return get(name)
         return g
+    if mt == "olmo":
+        # OLMo 1 normalises with a LayerNorm that has no parameters: present a weight of ones
+        def g(name: str):
+            t = get(name)
+            if t is None and name.endswith(("layernorm.weight", "model.norm.weight")):
+                return torch.ones(hidden, dtype=torch.bfloat16)
+            return t
+        return g
     if mt == "opt":
         layer = (("input_layernorm", "self_attn_layer_norm"), ("post_attention_layernorm", "final_layer_norm"),
                  ("self_attn.o_proj", "self_attn.out_proj"), ("mlp.up_proj", "fc1"), ("mlp.down_proj", "fc2"))

@@ -477,6 +477,8 @@ class DecoderModel:
         window = cfg.layer_window(self.layer0 + li)
         inv_freq = self.inv_freq_local if (window > 0 and self.inv_freq_local is not None) else self.inv_freq
         rot = cfg.rotary_dim if cfg.use_rope and not (cfg.nope_global and window == 0) else 0
+        if cfg.rope_layers and not cfg.rope_layers[self.layer0 + li]:
+            rot = 0
         q, _, _ = ops.rope_kv(qkv, batch.positions, self.hq, self.hkv, d, k_cache=kc, v_cache=vc,
                               slot_mapping=batch.slot_mapping, rot=rot, theta=cfg.rope_theta,
                               inv_freq=inv_freq, style=cfg.rope_style, q_norm_w=q_norm_w,

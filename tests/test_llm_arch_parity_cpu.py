@@ -44,6 +44,16 @@ ARCHS = {
     "gpt_neox": ("GPTNeoXConfig", dict()),
     "phi": ("PhiConfig", dict()),
     "opt": ("OPTConfig", dict(ffn_dim=256, word_embed_proj_dim=128)),
+    "smollm3": ("SmolLM3Config", dict(pad_token_id=0, no_rope_layer_interval=2)),
+    "exaone4": ("Exaone4Config", dict(head_dim=32)),
+    "helium": ("HeliumConfig", dict(head_dim=32)),
+    "arcee": ("ArceeConfig", dict()),
+    "seed_oss": ("SeedOssConfig", dict(head_dim=32)),
+    "ministral": ("MinistralConfig", dict(head_dim=32, sliding_window=8,
+                                          layer_types=["sliding_attention", "full_attention"])),
+    "ernie4_5": ("Ernie4_5Config", dict(head_dim=32)),
+    "olmo": ("OlmoConfig", dict()),
+    "olmo3": ("Olmo3Config", dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
     "gptj": ("GPTJConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, rotary_dim=16)),
     "deepseek_v3": ("DeepseekV3Config", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                                              q_lora_rank=64, kv_lora_rank=512, qk_nope_head_dim=32, qk_rope_head_dim=64,
