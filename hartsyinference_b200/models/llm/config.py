@@ -97,6 +97,8 @@ class TransformerConfig:
     learned_positions: bool = False
     nope_global: bool = False           # full-attention layers carry no rotary embedding (Cohere 2)
     lm_head_bias: bool = False          # the output projection has a bias (Phi-1 / Phi-2)
+    alibi: bool = False                 # attention scores get slope[h] * key position; no rotary embedding (BLOOM)
+    embed_norm: bool = False            # LayerNorm directly after the token embedding (BLOOM)
     rope_layers: tuple = ()             # per layer: 1 = rotary embedding, 0 = none (SmolLM 3)
     learned_position_offset: int = 0    # rows skipped at the start of the learned position table (OPT: 2)
     moe: Optional[MoeConfig] = None
@@ -124,7 +126,7 @@ class TransformerConfig:
         """Architectures whose block structure is outside the fused decode path: they run the same
         kernels through an unfused layer loop."""
         return (not self.pre_norm or self.qk_norm_full or self.norm_type != "rms" or self.parallel_residual
-                or not self.use_rope or self.nope_global or bool(self.rope_layers)
+                or not self.use_rope or self.nope_global or bool(self.rope_layers) or self.alibi or self.embed_norm
                 or self.o_bias or self.ffn_bias or not self.gated_ffn or self.activation not in ("silu", "gelu_tanh"))
 
     def layer_window(self, layer: int) -> int:
@@ -208,7 +210,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / bloom / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -218,6 +220,10 @@ def from_hf_config(d: dict) -> TransformerConfig:
         d = {**d, "hidden_size": d["n_embd"], "num_hidden_layers": d["n_layer"], "num_attention_heads": d["n_head"],
              "max_position_embeddings": d.get("n_positions", 2048), "intermediate_size": d.get("n_inner") or 4 * d["n_embd"],
              "hidden_act": d.get("activation_function", "gelu_new"), "tie_word_embeddings": d.get("tie_word_embeddings", False)}
+    if mt == "bloom":
+        d = {**d, "num_hidden_layers": d["n_layer"], "num_attention_heads": d["n_head"], "intermediate_size": 4 * d["hidden_size"],
+             "max_position_embeddings": d.get("seq_length", 2048), "hidden_act": "gelu_new", "rms_norm_eps": d.get("layer_norm_epsilon", 1e-5),
+             "tie_word_embeddings": d.get("tie_word_embeddings", True)}
     if mt == "gpt2":          # GPT-2 names its sizes differently
         d = {**d, "hidden_size": d["n_embd"], "num_hidden_layers": d["n_layer"], "num_attention_heads": d["n_head"],
              "max_position_embeddings": d.get("n_positions", 1024), "intermediate_size": d.get("n_inner") or 4 * d["n_embd"],
@@ -330,6 +336,9 @@ def from_hf_config(d: dict) -> TransformerConfig:
         kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=True, o_bias=True, ffn_bias=True,
                   parallel_residual=True, shared_parallel_norm=True, lm_head_bias=True,
                   num_kv_heads=d.get("num_key_value_heads") or heads)
+    if mt == "bloom":         # LayerNorm blocks with biases everywhere, ALiBi instead of positions
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=True, o_bias=True, ffn_bias=True,
+                  num_kv_heads=heads, use_rope=False, alibi=True, embed_norm=True)
     if mt == "gpt_neox":
         ab = bool(d.get("attention_bias", True))
         kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=ab, o_bias=ab, ffn_bias=True,

@@ -119,7 +119,7 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
     sliced, GLM-4 / StarCoder 2 / GPT-NeoX names are translated, GPT-NeoX's per-head interleaved
     query_key_value is regrouped."""
     mt = raw.get("model_type", "llama")
-    heads = raw.get("num_attention_heads", 1)
+    heads = raw.get("num_attention_heads") or raw.get("n_head") or 1
     hidden = raw.get("hidden_size", 0)
     d = raw.get("head_dim") or (hidden // heads if heads else 0)
     kvh = raw.get("num_key_value_heads") or heads
@@ -242,6 +242,22 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
         return g
     if mt == "starcoder2":
         return lambda name: get(name.replace("mlp.up_proj", "mlp.c_fc").replace("mlp.down_proj", "mlp.c_proj"))
+    if mt == "bloom":
+        ren = (("model.embed_tokens", "transformer.word_embeddings"), ("model.embed_norm", "transformer.word_embeddings_layernorm"),
+               ("model.norm", "transformer.ln_f"), ("model.layers", "transformer.h"), ("self_attn.o_proj", "self_attention.dense"),
+               ("mlp.up_proj", "mlp.dense_h_to_4h"), ("mlp.down_proj", "mlp.dense_4h_to_h"))
+
+        def g(name: str):
+            for i, part in enumerate(("q_proj", "k_proj", "v_proj")):
+                if "self_attn." + part + "." in name:
+                    t = get(name.replace("model.layers", "transformer.h").replace("self_attn." + part, "self_attention.query_key_value"))
+                    if t is None:
+                        return None
+                    return t.reshape(heads, 3, d, *t.shape[1:])[:, i].reshape(heads * d, *t.shape[1:])   # rows are [head][q | k | v][d]
+            for std, own in ren:
+                name = name.replace(std, own)
+            return get(name)
+        return g
     if mt == "gpt_neox":
         ren = (("model.embed_tokens", "gpt_neox.embed_in"), ("model.norm", "gpt_neox.final_layer_norm"),
                ("lm_head", "embed_out"), ("model.layers", "gpt_neox.layers"), ("self_attn.o_proj", "attention.dense"),

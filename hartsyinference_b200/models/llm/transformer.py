@@ -76,6 +76,18 @@ def build_inv_freq(rot: int, theta: float, scaling: RopeScaling, device) -> tupl
     return inv.to(torch.float32).to(device), attn_factor
 
 
+def alibi_slopes(heads: int) -> torch.Tensor:
+    """ALiBi head slopes: a geometric sequence for the largest power of two <= heads, then every
+    other term of the sequence for twice that count to fill the remainder."""
+    n = 1 << (heads.bit_length() - 1)
+    base = 2.0 ** (-(2.0 ** -(math.log2(n) - 3)))
+    out = [base ** (i + 1) for i in range(n)]
+    if n < heads:
+        extra = 2.0 ** (-(2.0 ** -(math.log2(2 * n) - 3)))
+        out += [extra ** (2 * i + 1) for i in range(heads - n)]
+    return torch.tensor(out, dtype=torch.float32)
+
+
 @dataclass
 class LayerWeights:
     in_norm: torch.Tensor
@@ -92,6 +104,7 @@ class LayerWeights:
     attn_module: Optional[object] = None              # MLA attention (callable) instead of qkv/o
     in_norm_b: Optional[torch.Tensor] = None          # LayerNorm biases (StableLM, StarCoder 2, GPT-NeoX, Nemotron)
     post_norm_b: Optional[torch.Tensor] = None
+    sinks: Optional[torch.Tensor] = None              # per-head sink logit in the attention softmax (gpt-oss)
 
 
 class DecoderModel:
@@ -122,6 +135,9 @@ class DecoderModel:
                                if cfg.rope_local_theta > 0 else None)
         self.final_norm_b: Optional[torch.Tensor] = None
         self.pos_embed: Optional[torch.Tensor] = None      # learned absolute positions (GPT-2)
+        self.embed_norm_w: Optional[torch.Tensor] = None   # LayerNorm on the embedding output (BLOOM)
+        self.embed_norm_b: Optional[torch.Tensor] = None
+        self.alibi_slopes: Optional[torch.Tensor] = None   # [local heads]
         self.kv_cache: Optional[torch.Tensor] = None
         self.all_reduce: Callable[[torch.Tensor], torch.Tensor] = self.comm.all_reduce
         # hook for the fused GEMM + all-reduce path: (x, weight, residual) -> reduced output
@@ -177,6 +193,10 @@ class DecoderModel:
         self.final_norm = need("model.norm.weight").to(dt).to(self.device)
         dev = lambda t_: None if t_ is None else t_.to(dt).to(self.device)
         self.final_norm_b = dev(get("model.norm.bias")) if cfg.norm_bias else None
+        if cfg.embed_norm:
+            self.embed_norm_w, self.embed_norm_b = dev(need("model.embed_norm.weight")), dev(get("model.embed_norm.bias"))
+        if cfg.alibi:
+            self.alibi_slopes = alibi_slopes(cfg.num_heads)[self.tp_rank * self.hq:(self.tp_rank + 1) * self.hq].to(self.device)
         if cfg.learned_positions:
             self.pos_embed = dev(need("model.embed_positions.weight"))
         if cfg.qk_norm_full and tp > 1:
@@ -483,7 +503,12 @@ class DecoderModel:
                               slot_mapping=batch.slot_mapping, rot=rot, theta=cfg.rope_theta,
                               inv_freq=inv_freq, style=cfg.rope_style, q_norm_w=q_norm_w,
                               k_norm_w=k_norm_w, eps=cfg.rms_eps)
-        if batch.is_decode:
+        if self.alibi_slopes is not None or lw.sinks is not None:
+            att = ops.attn_paged_biased(q, kc, vc, batch.block_table, batch.kv_lens,
+                                        None if batch.is_decode else batch.cu_q, scale=scale,
+                                        softcap=cfg.attn_softcap, window=window, alibi=self.alibi_slopes,
+                                        sinks=lw.sinks)
+        elif batch.is_decode:
             att = ops.attn_decode(q, kc, vc, batch.block_table, batch.kv_lens, scale=scale,
                                   softcap=cfg.attn_softcap, window=window,
                                   max_kv_len=batch.max_kv_len or None)
@@ -575,6 +600,8 @@ class DecoderModel:
             x = batch.embeds
         else:
             x = ops.embedding(batch.tokens, self.embed, cfg.embed_scale * cfg.embedding_multiplier)
+        if self.embed_norm_w is not None and hidden_in is None:
+            x = self._block_norm(x, self.embed_norm_w, self.embed_norm_b)
         if self.pos_embed is not None and hidden_in is None:
             x = (x.float() + self.pos_embed[batch.positions.long() + cfg.learned_position_offset].float()).to(x.dtype)
         scale = self._attn_scale()

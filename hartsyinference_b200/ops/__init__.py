@@ -13,6 +13,7 @@ from .core import (  # noqa: F401
     argmax,
     attention,
     attn_decode,
+    attn_paged_biased,
     attn_prefill_paged,
     causal_conv3d,
     cfg_euler_step,

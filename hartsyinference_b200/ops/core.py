@@ -367,6 +367,26 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
     return out
 
 
+def attn_paged_biased(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                      kv_lens: torch.Tensor, cu_q: Optional[torch.Tensor], scale: Optional[float] = None,
+                      softcap: float = 0.0, window: int = 0, alibi: Optional[torch.Tensor] = None,
+                      sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Paged causal attention with ALiBi slopes and / or per-head sink logits, which the attention
+    kernels do not take: the sequences are gathered from the page pool and run through tensor ops
+    on whichever device holds them. ``cu_q`` None means one query token per sequence (decode)."""
+    nseq = kv_lens.numel()
+    bounds = list(range(nseq + 1)) if cu_q is None else cu_q.tolist()
+    lens = kv_lens.tolist()
+    out = torch.empty_like(q)
+    for i in range(nseq):
+        a, b = bounds[i], bounds[i + 1]
+        kk = R.gather_paged(k_cache, block_table[i], lens[i])
+        vv = R.gather_paged(v_cache, block_table[i], lens[i])
+        out[a:b] = R.attention(q[a:b], kk, vv, causal=True, scale=scale, softcap=softcap, window=window,
+                               alibi=alibi, sinks=sinks).to(q.dtype)
+    return out
+
+
 def attn_prefill_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                        block_table: torch.Tensor, kv_lens: torch.Tensor, cu_q: torch.Tensor,
                        max_q_len: int, causal: bool = True, scale: Optional[float] = None,

@@ -188,9 +188,12 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
 # attention
 # --------------------------------------------------------------------------------------------
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
-              scale: Optional[float] = None, softcap: float = 0.0, window: int = 0) -> torch.Tensor:
+              scale: Optional[float] = None, softcap: float = 0.0, window: int = 0,
+              alibi: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [Tq, Hq, D], k/v [Tk, Hkv, D] (one sequence). The last query row sits at key position
-    Tk - 1 (so a query chunk with a cached prefix is expressed by Tk > Tq). Returns fp32 [Tq, Hq, D]."""
+    Tk - 1 (so a query chunk with a cached prefix is expressed by Tk > Tq). ``alibi`` [Hq] adds
+    slope * key position to the scores; ``sinks`` [Hq] adds one extra logit per head to the softmax
+    denominator (it attends to nothing). Returns fp32 [Tq, Hq, D]."""
     tq, hq, d = q.shape
     tk, hkv, _ = k.shape
     g = hq // hkv
@@ -207,9 +210,15 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
         mask &= kpos <= qpos
     if window > 0:
         mask &= kpos > qpos - window
+    if alibi is not None:
+        s = s + alibi.float()[:, None, None] * kpos[None].float()
     s = s.masked_fill(~mask[None], float("-inf"))
+    if sinks is not None:
+        s = torch.cat([s, sinks.float()[:, None, None].expand(hq, tq, 1)], -1)
     p = torch.softmax(s, dim=-1)
     p = torch.nan_to_num(p)
+    if sinks is not None:
+        p = p[..., :tk]
     return torch.einsum("hqk,khd->qhd", p, vf)
 
 

@@ -52,6 +52,8 @@ ARCHS = {
     "ministral": ("MinistralConfig", dict(head_dim=32, sliding_window=8,
                                           layer_types=["sliding_attention", "full_attention"])),
     "ernie4_5": ("Ernie4_5Config", dict(head_dim=32)),
+    "bloom": ("BloomConfig", dict(n_layer=2, n_head=4)),
+    "bloom_6_heads": ("BloomConfig", dict(n_layer=2, n_head=6, hidden_size=192)),
     "olmo": ("OlmoConfig", dict()),
     "olmo3": ("Olmo3Config", dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
     "gptj": ("GPTJConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, rotary_dim=16)),
@@ -204,3 +206,26 @@ def test_internlm2_and_minicpm_map_onto_the_llama_block(tmp_path):
                        sd, tmp_path / "granite")
     c, e = _logits(load_llm(tmp_path / "minicpm", "cpu"), ids), _logits(load_llm(tmp_path / "granite", "cpu"), ids)
     assert torch.allclose(c, e, atol=1e-3)
+
+
+def test_alibi_decode_step_matches_prefill(tmp_path):
+    """BLOOM's attention runs through the gathered-page path: a decode step after a prefill gives
+    the logits the one-shot prefill gives for the same position."""
+    cfg = tr.BloomConfig(**{**_BASE, "n_layer": 2, "n_head": 4})
+    torch.manual_seed(0)
+    hf = tr.AutoModelForCausalLM.from_config(cfg).eval()
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()},
+                       tmp_path / "m")
+    llm = load_llm(tmp_path / "m", "cpu")
+    ids = torch.randint(0, 320, (19,), generator=torch.Generator().manual_seed(2)).tolist()
+    full = _logits(llm, ids)[-1]
+    m = llm.model
+    _logits(llm, ids[:-1])
+    n = len(ids)
+    b = ForwardBatch(tokens=torch.tensor(ids[-1:], dtype=torch.int32), positions=torch.tensor([n - 1], dtype=torch.int32),
+                     slot_mapping=torch.tensor([n - 1], dtype=torch.int32),
+                     block_table=torch.arange((n + 15) // 16 + 1, dtype=torch.int32)[None],
+                     kv_lens=torch.tensor([n], dtype=torch.int32), is_decode=True, max_kv_len=n)
+    step = m.logits(m.forward_hidden(b)).float()[0]
+    assert torch.nn.functional.cosine_similarity(step, full, dim=0) > 0.999
+    assert int(step.argmax()) == int(full.argmax())
