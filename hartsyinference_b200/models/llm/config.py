@@ -49,6 +49,7 @@ class RopeScaling:
     beta_fast: float = 32.0
     beta_slow: float = 1.0
     attn_factor: float = 1.0
+    truncate: bool = True               # YaRN: round the correction range to whole dimensions (gpt-oss does not)
 
 
 @dataclass(frozen=True)
@@ -97,6 +98,7 @@ class TransformerConfig:
     learned_positions: bool = False
     nope_global: bool = False           # full-attention layers carry no rotary embedding (Cohere 2)
     lm_head_bias: bool = False          # the output projection has a bias (Phi-1 / Phi-2)
+    attn_sinks: bool = False            # one learned sink logit per head in the attention softmax (gpt-oss)
     alibi: bool = False                 # attention scores get slope[h] * key position; no rotary embedding (BLOOM)
     embed_norm: bool = False            # LayerNorm directly after the token embedding (BLOOM)
     rope_layers: tuple = ()             # per layer: 1 = rotary embedding, 0 = none (SmolLM 3)
@@ -126,7 +128,7 @@ class TransformerConfig:
         """Architectures whose block structure is outside the fused decode path: they run the same
         kernels through an unfused layer loop."""
         return (not self.pre_norm or self.qk_norm_full or self.norm_type != "rms" or self.parallel_residual
-                or not self.use_rope or self.nope_global or bool(self.rope_layers) or self.alibi or self.embed_norm
+                or not self.use_rope or self.nope_global or bool(self.rope_layers) or self.alibi or self.embed_norm or self.attn_sinks
                 or self.o_bias or self.ffn_bias or not self.gated_ffn or self.activation not in ("silu", "gelu_tanh"))
 
     def layer_window(self, layer: int) -> int:
@@ -210,7 +212,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / bloom / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -243,7 +245,8 @@ def from_hf_config(d: dict) -> TransformerConfig:
                           high_freq_factor=float(rs.get("high_freq_factor", 4.0)),
                           original_max_position=int(rs.get("original_max_position_embeddings", 8192)),
                           beta_fast=float(rs.get("beta_fast", 32.0)), beta_slow=float(rs.get("beta_slow", 1.0)),
-                          attn_factor=float(rs.get("attn_factor", rs.get("mscale", 1.0)) or 1.0))
+                          attn_factor=float(rs.get("attn_factor", rs.get("mscale", 1.0)) or 1.0),
+                          truncate=bool(rs.get("truncate", True)))
     eos = d.get("eos_token_id", 2)
     eos = tuple(eos) if isinstance(eos, (list, tuple)) else (eos,)
     kw: dict[str, Any] = dict(
@@ -375,6 +378,12 @@ def from_hf_config(d: dict) -> TransformerConfig:
                               n_group=d.get("n_group", 1) or 1, topk_group=d.get("topk_group", 1) or 1,
                               use_correction_bias=(d.get("topk_method") or ("noaux_tc" if mt == "deepseek_v3" else "")) == "noaux_tc",
                               first_dense_layers=d.get("first_k_dense_replace", 0))
+    if mt == "gpt_oss":       # sink logits, biased projections, alternating windows, clamped-SwiGLU experts with biases
+        ab = bool(d.get("attention_bias", True))
+        kw.update(qkv_bias=ab, o_bias=ab, attn_sinks=True, sliding_window=int(d.get("sliding_window") or 0),
+                  layer_types=tuple(d.get("layer_types") or ()))
+        kw["moe"] = MoeConfig(num_experts=d.get("num_local_experts", 0), top_k=d.get("num_experts_per_tok", 4),
+                              expert_ffn=d.get("intermediate_size", 0), norm_topk_prob=True)
     if mt in ("olmoe", "qwen2_moe", "qwen3_moe", "mixtral", "granitemoe"):
         kw["moe"] = MoeConfig(num_experts=d.get("num_experts", d.get("num_local_experts", 0)),
                               top_k=d.get("num_experts_per_tok", 2),

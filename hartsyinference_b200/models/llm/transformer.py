@@ -67,8 +67,10 @@ def build_inv_freq(rot: int, theta: float, scaling: RopeScaling, device) -> tupl
     elif scaling.kind == "yarn":
         def corr_dim(n_rot):
             return (rot * math.log(scaling.original_max_position / (n_rot * 2 * math.pi))) / (2 * math.log(theta))
-        lo = max(math.floor(corr_dim(scaling.beta_fast)), 0)
-        hi = min(math.ceil(corr_dim(scaling.beta_slow)), rot // 2 - 1)
+        lo, hi = corr_dim(scaling.beta_fast), corr_dim(scaling.beta_slow)
+        if scaling.truncate:
+            lo, hi = math.floor(lo), math.ceil(hi)
+        lo, hi = max(lo, 0), min(hi, rot // 2 - 1)
         ramp = ((torch.arange(rot // 2, dtype=torch.float64) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
         mask = 1 - ramp
         inv = inv / scaling.factor * (1 - mask) + inv * mask
@@ -237,7 +239,15 @@ class DecoderModel:
                 o = need(p + "self_attn.o_proj.weight")[:, r * self.hq * d:(r + 1) * self.hq * d]
                 lw.qkv = self._lw(torch.cat([q, k, v]).to(dt), None if qkv_b is None else qkv_b.to(dt))
                 lw.o = self._lw(o.contiguous().to(dt), row_bias(p + "self_attn.o_proj.bias") if cfg.o_bias else None)
-            if is_moe:
+            if cfg.attn_sinks:
+                lw.sinks = dev(need(p + "self_attn.sinks"))[r * self.hq:(r + 1) * self.hq].float()
+            if is_moe and cfg.arch == "gpt_oss":
+                from .gpt_oss import GptOssMoe, expert_tensor
+                lw.ffn_module = GptOssMoe(dev(need(p + "mlp.router.weight").to(dt)), dev(need(p + "mlp.router.bias").to(dt)),
+                                          dev(expert_tensor(get, p + "mlp.experts.gate_up_proj").to(dt)), dev(need(p + "mlp.experts.gate_up_proj_bias").to(dt)),
+                                          dev(expert_tensor(get, p + "mlp.experts.down_proj").to(dt)), dev(need(p + "mlp.experts.down_proj_bias").to(dt)),
+                                          cfg.moe.top_k)
+            elif is_moe:
                 lw.ffn_module = self._load_moe(need, get, p)
             else:
                 fs = slice(r * self.ffn, (r + 1) * self.ffn)

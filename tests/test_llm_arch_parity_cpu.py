@@ -54,6 +54,8 @@ ARCHS = {
     "ernie4_5": ("Ernie4_5Config", dict(head_dim=32)),
     "bloom": ("BloomConfig", dict(n_layer=2, n_head=4)),
     "bloom_6_heads": ("BloomConfig", dict(n_layer=2, n_head=6, hidden_size=192)),
+    "gpt_oss": ("GptOssConfig", dict(num_local_experts=4, num_experts_per_tok=2, head_dim=32, sliding_window=8,
+                                     layer_types=["sliding_attention", "full_attention"])),
     "olmo": ("OlmoConfig", dict()),
     "olmo3": ("Olmo3Config", dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
     "gptj": ("GPTJConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, rotary_dim=16)),
@@ -229,3 +231,28 @@ def test_alibi_decode_step_matches_prefill(tmp_path):
     step = m.logits(m.forward_hidden(b)).float()[0]
     assert torch.nn.functional.cosine_similarity(step, full, dim=0) > 0.999
     assert int(step.argmax()) == int(full.argmax())
+
+
+def test_gpt_oss_mxfp4_expert_blocks_load(tmp_path):
+    """Released gpt-oss checkpoints keep the expert matrices as MXFP4 blocks + E8M0 scales, laid out
+    [E, out, in / 32, 16]: they load to the same logits as the dequantised matrices stored plainly."""
+    from hartsyinference_b200.assets.lowbit import mxfp4_dequantize, mxfp4_quantize
+    cfg = tr.GptOssConfig(**{**_BASE, **ARCHS["gpt_oss"][1]})
+    torch.manual_seed(0)
+    sd = {k: v.detach().to(torch.bfloat16).contiguous() for k, v in tr.AutoModelForCausalLM.from_config(cfg).state_dict().items()}
+    plain, packed = dict(sd), dict(sd)
+    for k in list(sd):
+        if k.endswith(("experts.gate_up_proj", "experts.down_proj")):
+            w = sd[k].float().transpose(1, 2).contiguous()                       # [E, out, in]
+            e, rows, cols = w.shape
+            q, sc = mxfp4_quantize(w.reshape(e * rows, cols))
+            plain[k] = mxfp4_dequantize(q, sc).reshape(e, rows, cols).transpose(1, 2).contiguous().to(torch.bfloat16)
+            del packed[k]
+            packed[k + "_blocks"] = q.reshape(e, rows, cols // 32, 16)
+            packed[k + "_scales"] = sc.reshape(e, rows, cols // 32)
+    save_hf_checkpoint(cfg.to_dict(), plain, tmp_path / "plain")
+    save_hf_checkpoint(cfg.to_dict(), packed, tmp_path / "packed")
+    ids = torch.randint(0, 320, (17,), generator=torch.Generator().manual_seed(3)).tolist()
+    a = _logits(load_llm(tmp_path / "plain", "cpu"), ids)
+    b = _logits(load_llm(tmp_path / "packed", "cpu"), ids)
+    assert torch.equal(a, b)
