@@ -25,7 +25,7 @@ ARCH = {"llama": "llama", "mistral": "llama", "mixtral": "llama", "qwen2": "qwen
         "gemma2": "gemma2", "gemma3_text": "gemma3", "gemma3": "gemma3", "phi3": "phi3", "olmo2": "olmo2",
         "granite": "granite", "stablelm": "stablelm", "starcoder2": "starcoder2", "gpt_neox": "gptneox",
         "qwen2_moe": "qwen2moe", "qwen3_moe": "qwen3moe", "olmoe": "olmoe", "deepseek_v3": "deepseek2",
-        "deepseek_v2": "deepseek2"}
+        "deepseek_v2": "deepseek2", "bloom": "bloom"}
 
 # architectures whose GGUF files rotate interleaved pairs: q / k rows are permuted on the way in
 _PERMUTE_QK = {"llama", "granite"}
@@ -37,7 +37,7 @@ _LAYER = {
     "pre_feedforward_layernorm": "ffn_norm", "post_feedforward_layernorm": "post_ffw_norm",
     "self_attn.qkv_proj": "attn_qkv", "mlp.gate_up_proj": "ffn_up", "mlp.c_fc": "ffn_up", "mlp.c_proj": "ffn_down",
     "attention.query_key_value": "attn_qkv", "attention.dense": "attn_output", "mlp.dense_h_to_4h": "ffn_up",
-    "mlp.dense_4h_to_h": "ffn_down",
+    "mlp.dense_4h_to_h": "ffn_down", "self_attention.query_key_value": "attn_qkv", "self_attention.dense": "attn_output",
     "mlp.gate": "ffn_gate_inp", "block_sparse_moe.gate": "ffn_gate_inp", "mlp.shared_expert_gate": "ffn_gate_inp_shexp",
     "mlp.shared_expert.gate_proj": "ffn_gate_shexp", "mlp.shared_expert.up_proj": "ffn_up_shexp",
     "mlp.shared_expert.down_proj": "ffn_down_shexp", "mlp.shared_experts.gate_proj": "ffn_gate_shexp",
@@ -47,7 +47,9 @@ _LAYER = {
     "self_attn.kv_b_proj": "attn_kv_b",
 }
 _TOP = {"model.embed_tokens": "token_embd", "model.norm": "output_norm", "lm_head": "output",
-        "gpt_neox.embed_in": "token_embd", "gpt_neox.final_layer_norm": "output_norm", "embed_out": "output"}
+        "gpt_neox.embed_in": "token_embd", "gpt_neox.final_layer_norm": "output_norm", "embed_out": "output",
+        "transformer.word_embeddings": "token_embd", "transformer.word_embeddings_layernorm": "token_embd_norm",
+        "transformer.ln_f": "output_norm"}
 
 
 def permute_qk(w: torch.Tensor, heads: int) -> torch.Tensor:
@@ -162,8 +164,12 @@ def hf_to_gguf(src_dir, dst, quant: Optional[str] = None) -> dict:
         raise ValueError(f"no GGUF mapping for model_type '{mt}'")
     arch = ARCH[mt]
     ck = ShardedCheckpoint(src)
+    if arch == "bloom":                                      # BLOOM names its sizes n_head / n_layer
+        raw = {**raw, "num_attention_heads": raw["n_head"], "num_hidden_layers": raw["n_layer"],
+               "rms_norm_eps": raw.get("layer_norm_epsilon", 1e-5), "max_position_embeddings": raw.get("seq_length", 2048),
+               "intermediate_size": 4 * raw["hidden_size"]}
     heads = raw["num_attention_heads"]
-    if arch == "gptneox":
+    if arch in ("gptneox", "bloom"):
         raw = {**raw, "num_key_value_heads": heads}          # always multi-head
     kvh = raw.get("num_key_value_heads") or heads
     hidden = raw["hidden_size"]
@@ -183,6 +189,8 @@ def hf_to_gguf(src_dir, dst, quant: Optional[str] = None) -> dict:
             out[f"{_TOP[stem]}.{kind}"] = t
             continue
         parts = stem.split(".")
+        if arch == "bloom" and "h" in parts:
+            parts[parts.index("h")] = "layers"
         if "layers" not in parts:
             continue
         li = parts.index("layers")
@@ -211,7 +219,7 @@ def hf_to_gguf(src_dir, dst, quant: Optional[str] = None) -> dict:
             t = t.float() + 1.0
         if arch in _PERMUTE_QK and rest in ("self_attn.q_proj", "self_attn.k_proj"):
             t = permute_qk(t, heads if rest.endswith("q_proj") else kvh)
-        if rest == "attention.query_key_value":           # [head][q | k | v][d] rows -> all q, all k, all v
+        if rest in ("attention.query_key_value", "self_attention.query_key_value"):           # [head][q | k | v][d] rows -> all q, all k, all v
             t = t.reshape(heads, 3, d, *t.shape[1:]).transpose(0, 1).reshape(t.shape)
         if arch in ("gemma2", "gemma3") and rest == "post_attention_layernorm":
             g = "post_attention_norm"

@@ -399,7 +399,8 @@ _GGUF_ARCH_ALIASES = {"qwen2": "qwen2", "qwen3": "qwen3", "llama": "llama", "gem
                       "gemma3": "gemma3", "phi3": "phi3", "granite": "granite", "deepseek2": "deepseek3",
                       "olmoe": "olmoe", "qwen2moe": "qwen2_moe", "mistral": "mistral", "glm4": "glm4",
                       "stablelm": "stablelm", "olmo2": "olmo2", "internlm2": "internlm2", "minicpm": "minicpm",
-                      "qwen3moe": "qwen3_moe", "starcoder2": "starcoder2", "gptneox": "gpt_neox", "nemotron": "nemotron"}
+                      "qwen3moe": "qwen3_moe", "starcoder2": "starcoder2", "gptneox": "gpt_neox", "nemotron": "nemotron",
+                      "bloom": "bloom"}
 
 
 def from_gguf_metadata(md: dict) -> TransformerConfig:
@@ -458,6 +459,9 @@ def from_gguf_metadata(md: dict) -> TransformerConfig:
                   parallel_residual=bool(g("use_parallel_residual", True)))
     if arch == "nemotron":
         kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, activation="relu2")
+    if arch == "bloom":
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, activation="gelu_tanh", o_bias=True, ffn_bias=True,
+                  use_rope=False, alibi=True, embed_norm=True, tie_embeddings=not md.get("__has_output_weight__", False))
     if g("expert_count"):
         kw["moe"] = MoeConfig(num_experts=int(g("expert_count")), top_k=int(g("expert_used_count", 2)),
                               expert_ffn=int(g("expert_feed_forward_length", kw["ffn_size"])),

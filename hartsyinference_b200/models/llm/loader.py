@@ -55,7 +55,8 @@ _GGUF_LAYER = {
     "attn_kv_a_norm.weight": "self_attn.kv_a_layernorm.weight", "attn_kv_b.weight": "self_attn.kv_b_proj.weight",
 }
 _GGUF_TOP = {"token_embd.weight": "model.embed_tokens.weight", "output_norm.weight": "model.norm.weight",
-             "output_norm.bias": "model.norm.bias", "output.weight": "lm_head.weight"}
+             "output_norm.bias": "model.norm.bias", "output.weight": "lm_head.weight",
+             "token_embd_norm.weight": "model.embed_norm.weight", "token_embd_norm.bias": "model.embed_norm.bias"}
 
 
 def gguf_name_to_hf(name: str) -> Optional[str]:
@@ -372,7 +373,7 @@ def _load_gguf(p: Path, device, comm, fp8) -> LoadedLLM:
         return None
 
     arch = f.metadata.get("general.architecture", "llama")
-    fused = {"phi3": "phi3", "gptneox": "phi3"}.get(arch)
+    fused = {"phi3": "phi3", "gptneox": "phi3", "bloom": "phi3"}.get(arch)
     if fused:
         # both keep q|k|v (and Phi-3 gate|up in ffn_up) as one tensor: present them under the split names
         raw = {"model_type": "phi3", "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_kv_heads,

@@ -107,7 +107,7 @@ def test_arch_matches_transformers(name, tmp_path):
     assert agree >= 0.85, f"{name}: argmax agreement {agree:.2f}"
 
 
-GGUF_ARCHS = ["llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3_text", "granite", "olmo2", "phi3",
+GGUF_ARCHS = ["bloom", "llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3_text", "granite", "olmo2", "phi3",
               "stablelm", "stablelm_parallel", "starcoder2", "gpt_neox", "mixtral", "qwen2_moe", "qwen3_moe", "olmoe",
               "deepseek_v3"]
 
