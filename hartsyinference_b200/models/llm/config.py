@@ -98,6 +98,7 @@ class TransformerConfig:
     learned_positions: bool = False
     nope_global: bool = False           # full-attention layers carry no rotary embedding (Cohere 2)
     lm_head_bias: bool = False          # the output projection has a bias (Phi-1 / Phi-2)
+    qk_norm_after_rope: bool = False    # per-head q/k RMSNorm applied after the rotary embedding (HunYuan)
     attn_sinks: bool = False            # one learned sink logit per head in the attention softmax (gpt-oss)
     alibi: bool = False                 # attention scores get slope[h] * key position; no rotary embedding (BLOOM)
     embed_norm: bool = False            # LayerNorm directly after the token embedding (BLOOM)
@@ -128,7 +129,7 @@ class TransformerConfig:
         """Architectures whose block structure is outside the fused decode path: they run the same
         kernels through an unfused layer loop."""
         return (not self.pre_norm or self.qk_norm_full or self.norm_type != "rms" or self.parallel_residual
-                or not self.use_rope or self.nope_global or bool(self.rope_layers) or self.alibi or self.embed_norm or self.attn_sinks
+                or not self.use_rope or self.nope_global or bool(self.rope_layers) or self.alibi or self.embed_norm or self.attn_sinks or self.qk_norm_after_rope
                 or self.o_bias or self.ffn_bias or not self.gated_ffn or self.activation not in ("silu", "gelu_tanh"))
 
     def layer_window(self, layer: int) -> int:
@@ -212,7 +213,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / hunyuan_v1_dense / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -271,6 +272,11 @@ def from_hf_config(d: dict) -> TransformerConfig:
         kw["qk_norm"] = True
     if mt in ("olmo2", "olmo3", "exaone4"):
         kw.update(pre_norm=False, post_norms=True)
+    if mt == "hunyuan_v1_dense":
+        kw.update(qk_norm=bool(d.get("use_qk_norm", True)), qk_norm_after_rope=True)
+        alpha = float(rs.get("alpha") or 0.0)
+        if alpha > 0:                             # NTK-alpha: a larger rotary base instead of scaled positions
+            kw["rope_theta"] = kw["rope_theta"] * alpha ** (head_dim / (head_dim - 2))
     if mt == "exaone4":
         kw["qk_norm"] = True                      # per head, before the rotary embedding
     if mt in ("olmo3", "exaone4", "ministral", "smollm3"):

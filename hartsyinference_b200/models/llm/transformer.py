@@ -509,6 +509,16 @@ class DecoderModel:
         rot = cfg.rotary_dim if cfg.use_rope and not (cfg.nope_global and window == 0) else 0
         if cfg.rope_layers and not cfg.rope_layers[self.layer0 + li]:
             rot = 0
+        if cfg.qk_norm_after_rope and q_norm_w is not None:
+            # rotate first (no cache write), normalise the rotated heads, then run the same kernel with
+            # no rotation for the cache write
+            qr, kr, vr = ops.rope_kv(qkv, batch.positions, self.hq, self.hkv, d, rot=rot, theta=cfg.rope_theta,
+                                     inv_freq=inv_freq, style=cfg.rope_style, want_kv=True)
+            qn, _, _ = ops.norm(qr.reshape(-1, d), q_norm_w, eps=cfg.rms_eps)
+            kn, _, _ = ops.norm(kr.reshape(-1, d), k_norm_w, eps=cfg.rms_eps)
+            qkv = torch.cat([qn.reshape(t, -1), kn.reshape(t, -1), vr.reshape(t, -1)], 1).contiguous()
+            q_norm_w = k_norm_w = None
+            rot = 0
         q, _, _ = ops.rope_kv(qkv, batch.positions, self.hq, self.hkv, d, k_cache=kc, v_cache=vc,
                               slot_mapping=batch.slot_mapping, rot=rot, theta=cfg.rope_theta,
                               inv_freq=inv_freq, style=cfg.rope_style, q_norm_w=q_norm_w,

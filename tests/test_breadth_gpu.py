@@ -64,6 +64,13 @@ _GPU_ARCHS = {
     "gpt_neox": ("GPTNeoXConfig", {}),
     "phi3": ("Phi3Config", dict(pad_token_id=0)),
     "olmoe": ("OlmoeConfig", dict(num_experts=4, num_experts_per_tok=2)),
+    "bloom": ("BloomConfig", dict(n_layer=2, n_head=4)),
+    "gpt_oss": ("GptOssConfig", dict(num_local_experts=4, num_experts_per_tok=2, head_dim=64, sliding_window=8,
+                                     layer_types=["sliding_attention", "full_attention"])),
+    "smollm3": ("SmolLM3Config", dict(pad_token_id=0, no_rope_layer_interval=2)),
+    "exaone4": ("Exaone4Config", dict(head_dim=64)),
+    "helium": ("HeliumConfig", dict(head_dim=64)),
+    "hunyuan_v1_dense": ("HunYuanDenseV1Config", dict(head_dim=64)),
 }
 
 

@@ -56,6 +56,8 @@ ARCHS = {
     "bloom_6_heads": ("BloomConfig", dict(n_layer=2, n_head=6, hidden_size=192)),
     "gpt_oss": ("GptOssConfig", dict(num_local_experts=4, num_experts_per_tok=2, head_dim=32, sliding_window=8,
                                      layer_types=["sliding_attention", "full_attention"])),
+    "hunyuan_v1_dense": ("HunYuanDenseV1Config", dict(head_dim=32)),
+    "hunyuan_ntk_alpha": ("HunYuanDenseV1Config", dict(head_dim=32, rope_parameters=dict(rope_type="dynamic", alpha=50.0, rope_theta=10000.0, factor=1.0))),
     "olmo": ("OlmoConfig", dict()),
     "olmo3": ("Olmo3Config", dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
     "gptj": ("GPTJConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, rotary_dim=16)),
