@@ -213,7 +213,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / hunyuan_v1_dense / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -277,6 +277,8 @@ def from_hf_config(d: dict) -> TransformerConfig:
         alpha = float(rs.get("alpha") or 0.0)
         if alpha > 0:                             # NTK-alpha: a larger rotary base instead of scaled positions
             kw["rope_theta"] = kw["rope_theta"] * alpha ** (head_dim / (head_dim - 2))
+    if mt == "apertus":       # non-gated xIELU MLP, per-head q/k norm
+        kw.update(gated_ffn=False, qk_norm=True)
     if mt == "exaone4":
         kw["qk_norm"] = True                      # per head, before the rotary embedding
     if mt in ("olmo3", "exaone4", "ministral", "smollm3"):
@@ -304,7 +306,7 @@ def from_hf_config(d: dict) -> TransformerConfig:
         if d.get("query_pre_attn_scalar"):
             kw["attn_scale"] = float(d["query_pre_attn_scalar"]) ** -0.5
     act = {"silu": "silu", "swish": "silu", "gelu_pytorch_tanh": "gelu_tanh", "gelu_new": "gelu_tanh",
-           "gelu_fast": "gelu_tanh", "gelu": "gelu", "relu2": "relu2", "relu": "relu"}.get(
+           "gelu_fast": "gelu_tanh", "gelu": "gelu", "relu2": "relu2", "relu": "relu", "xielu": "xielu"}.get(
                d.get("hidden_act") or d.get("hidden_activation") or "", None)
     if act is not None and not mt.startswith("gemma"):
         kw["activation"] = act

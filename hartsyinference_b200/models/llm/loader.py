@@ -211,6 +211,10 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
         def g(name: str):
             return get(name.replace("self_attn.q_norm", "self_attn.query_layernorm").replace("self_attn.k_norm", "self_attn.key_layernorm"))
         return g
+    if mt == "apertus":
+        def g(name: str):
+            return get(name.replace("input_layernorm", "attention_layernorm").replace("post_attention_layernorm", "feedforward_layernorm"))
+        return g
     if mt == "opt":
         layer = (("input_layernorm", "self_attn_layer_norm"), ("post_attention_layernorm", "final_layer_norm"),
                  ("self_attn.o_proj", "self_attn.out_proj"), ("mlp.up_proj", "fc1"), ("mlp.down_proj", "fc2"))

@@ -106,6 +106,7 @@ class LayerWeights:
     attn_module: Optional[object] = None              # MLA attention (callable) instead of qkv/o
     in_norm_b: Optional[torch.Tensor] = None          # LayerNorm biases (StableLM, StarCoder 2, GPT-NeoX, Nemotron)
     post_norm_b: Optional[torch.Tensor] = None
+    act_params: Optional[tuple] = None                # xIELU: (alpha_p, alpha_n, beta, eps) as floats (Apertus)
     sinks: Optional[torch.Tensor] = None              # per-head sink logit in the attention softmax (gpt-oss)
 
 
@@ -262,6 +263,12 @@ class DecoderModel:
                 else:
                     lw.gate_up = self._lw(up.contiguous().to(dt), None if ub is None else ub[fs].to(dt))
                 lw.down = self._lw(down.contiguous().to(dt), row_bias(p + "mlp.down_proj.bias") if cfg.ffn_bias else None)
+            if cfg.activation == "xielu":
+                sp = torch.nn.functional.softplus
+                beta = float(need(p + "mlp.act_fn.beta").float().reshape(-1)[0])
+                lw.act_params = (float(sp(need(p + "mlp.act_fn.alpha_p").float()).reshape(-1)[0]),
+                                 beta + float(sp(need(p + "mlp.act_fn.alpha_n").float()).reshape(-1)[0]),
+                                 beta, float(need(p + "mlp.act_fn.eps").float().reshape(-1)[0]))
             if cfg.qk_norm:
                 qn, kn = need(p + "self_attn.q_norm.weight"), need(p + "self_attn.k_norm.weight")
                 if cfg.norm_plus_one:      # Gemma 3 stores w - 1 for these too; the rotary kernel multiplies by w
@@ -544,9 +551,14 @@ class DecoderModel:
                         weight_plus_one=cfg.norm_plus_one)[0]
 
     @staticmethod
-    def _activation(x: torch.Tensor, name: str) -> torch.Tensor:
+    def _activation(x: torch.Tensor, name: str, params: Optional[tuple] = None) -> torch.Tensor:
         xf = x.float()
-        if name == "silu":
+        if name == "xielu":
+            # x > 0: alpha_p x^2 + beta x; otherwise alpha_n (expm1(min(x, eps)) - x) + beta x
+            ap, an, beta, eps = params
+            y = torch.where(xf > 0, ap * xf * xf + beta * xf,
+                            (torch.expm1(torch.clamp(xf, max=eps)) - xf) * an + beta * xf)
+        elif name == "silu":
             y = torch.nn.functional.silu(xf)
         elif name == "gelu":
             y = torch.nn.functional.gelu(xf)
@@ -566,12 +578,12 @@ class DecoderModel:
             return lw.ffn_module(h, self)
         gu = ops.linear(h, lw.gate_up)
         if not cfg.gated_ffn:
-            return self._reduce_linear(self._activation(gu, cfg.activation), lw.down)
+            return self._reduce_linear(self._activation(gu, cfg.activation, lw.act_params), lw.down)
         if cfg.activation in ("silu", "gelu_tanh"):
             act, _ = ops.glu(gu, cfg.activation)
         else:
             f = gu.shape[1] // 2
-            act = (self._activation(gu[:, :f], cfg.activation).float() * gu[:, f:].float()).to(gu.dtype)
+            act = (self._activation(gu[:, :f], cfg.activation, lw.act_params).float() * gu[:, f:].float()).to(gu.dtype)
         return self._reduce_linear(act.contiguous(), lw.down)
 
     def _forward_general(self, batch: ForwardBatch, x: torch.Tensor, scale: float):

@@ -58,6 +58,7 @@ ARCHS = {
                                      layer_types=["sliding_attention", "full_attention"])),
     "hunyuan_v1_dense": ("HunYuanDenseV1Config", dict(head_dim=32)),
     "hunyuan_ntk_alpha": ("HunYuanDenseV1Config", dict(head_dim=32, rope_parameters=dict(rope_type="dynamic", alpha=50.0, rope_theta=10000.0, factor=1.0))),
+    "apertus": ("ApertusConfig", dict()),
     "olmo": ("OlmoConfig", dict()),
     "olmo3": ("Olmo3Config", dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
     "gptj": ("GPTJConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, rotary_dim=16)),
