@@ -45,6 +45,8 @@ class ForwardBatch:
     max_kv_len: int = 0
     logit_rows: Optional[torch.Tensor] = None   # prefill: rows (into T) whose logits are needed
     embeds: Optional[torch.Tensor] = None       # optional precomputed input embeddings [T, H]
+    cross_states: Optional[torch.Tensor] = None     # Mllama: projected vision states [Tv, H] of the (single) sequence
+    cross_row_mask: Optional[torch.Tensor] = None   # Mllama: [T], 0 for text rows that precede every image
 
 
 def build_inv_freq(rot: int, theta: float, scaling: RopeScaling, device) -> tuple[torch.Tensor, float]:
@@ -106,6 +108,7 @@ class LayerWeights:
     attn_module: Optional[object] = None              # MLA attention (callable) instead of qkv/o
     in_norm_b: Optional[torch.Tensor] = None          # LayerNorm biases (StableLM, StarCoder 2, GPT-NeoX, Nemotron)
     post_norm_b: Optional[torch.Tensor] = None
+    cross: Optional[object] = None                    # cross-attention layer over vision states (Mllama) instead of a block
     act_params: Optional[tuple] = None                # xIELU: (alpha_p, alpha_n, beta, eps) as floats (Apertus)
     sinks: Optional[torch.Tensor] = None              # per-head sink logit in the attention softmax (gpt-oss)
 
@@ -215,6 +218,21 @@ class DecoderModel:
 
         for i in range(self.layer0, self.layer1):
             p = f"model.layers.{i}."
+            if i in cfg.cross_layers:
+                from .mllama import CrossLayer
+                full = lambda n: self._lw(need(p + n).contiguous().to(dt), None)      # replicated on every rank
+                gu = torch.cat([need(p + "mlp.gate_proj.weight"), need(p + "mlp.up_proj.weight")]).to(dt)
+                lw = LayerWeights(in_norm=None, qkv=None, o=None, post_norm=None)
+                lw.cross = CrossLayer(dev(need(p + "input_layernorm.weight")), dev(need(p + "post_attention_layernorm.weight")),
+                                      full("cross_attn.q_proj.weight"), full("cross_attn.k_proj.weight"),
+                                      full("cross_attn.v_proj.weight"), full("cross_attn.o_proj.weight"),
+                                      dev(need(p + "cross_attn.q_norm.weight")), dev(need(p + "cross_attn.k_norm.weight")),
+                                      self._lw(gu, None), full("mlp.down_proj.weight"),
+                                      float(torch.tanh(need(p + "cross_attn_attn_gate").float()).reshape(-1)[0]),
+                                      float(torch.tanh(need(p + "cross_attn_mlp_gate").float()).reshape(-1)[0]),
+                                      cfg.num_heads, cfg.num_kv_heads, d, cfg.rms_eps)
+                self.layers.append(lw)
+                continue
             is_moe = cfg.moe is not None and cfg.moe.num_experts > 0 and i >= cfg.moe.first_dense_layers
             post_name = "post_attention_layernorm"
             if cfg.shared_parallel_norm:
@@ -452,6 +470,8 @@ class DecoderModel:
             for w in (lw.qkv, lw.o, lw.gate_up, lw.down):
                 if w is not None:
                     n += w.nbytes()
+            if lw.cross is not None:
+                n += lw.cross.nbytes()
             if lw.ffn_module is not None and hasattr(lw.ffn_module, "nbytes"):
                 n += lw.ffn_module.nbytes()
             if lw.attn_module is not None and hasattr(lw.attn_module, "nbytes"):
@@ -601,6 +621,9 @@ class DecoderModel:
             return y.to(stream.dtype)
 
         for li, lw in enumerate(self.layers):
+            if lw.cross is not None:
+                x = lw.cross(x, batch.cross_states, batch.cross_row_mask)
+                continue
             h = self._block_norm(x, lw.in_norm, lw.in_norm_b) if cfg.pre_norm else x
             a = self._attention(lw, li, h, None, batch, scale)
             if lw.post_attn_norm is not None:

@@ -259,3 +259,52 @@ def test_gpt_oss_mxfp4_expert_blocks_load(tmp_path):
     a = _logits(load_llm(tmp_path / "plain", "cpu"), ids)
     b = _logits(load_llm(tmp_path / "packed", "cpu"), ids)
     assert torch.equal(a, b)
+
+
+def _mllama(tmp_path):
+    cfg = tr.models.mllama.configuration_mllama.MllamaTextConfig(**{**_BASE, "cross_attention_layers": [1], "num_hidden_layers": 3, "pad_token_id": 0,
+                                               "rope_parameters": {"rope_type": "default", "rope_theta": 10000.0}})
+    cfg._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = tr.MllamaForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2:
+                p.mul_(3.0)
+            if n.endswith(("cross_attn_attn_gate", "cross_attn_mlp_gate")):
+                p.fill_(0.7)                                     # the gates initialise to zero (identity layer)
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()},
+                       tmp_path / "m")
+    return hf.to(torch.bfloat16).float(), load_llm(tmp_path / "m", "cpu")
+
+
+def test_mllama_text_only_skips_cross_layers(tmp_path):
+    hf, llm = _mllama(tmp_path)
+    assert llm.config.cross_layers == (1,) and llm.model.layers[1].cross is not None
+    ids = torch.randint(0, 320, (21,), generator=torch.Generator().manual_seed(1)).tolist()
+    with torch.no_grad():
+        ref = hf(torch.tensor([ids])).logits[0].float()
+    mine = _logits(llm, ids)
+    assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0) > 0.995
+
+
+def test_mllama_cross_attention_over_vision_states(tmp_path):
+    hf, llm = _mllama(tmp_path)
+    ids = torch.randint(0, 320, (21,), generator=torch.Generator().manual_seed(1)).tolist()
+    states = torch.randn(1, 12, 128, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    rows = torch.ones(1, 1, 21, 1)
+    rows[:, :, :4] = 0                                           # the first text rows precede the image
+    with torch.no_grad():
+        ref = hf(torch.tensor([ids]), cross_attention_states=states.float(), full_text_row_masked_out_mask=rows).logits[0].float()
+        plain = hf(torch.tensor([ids])).logits[0].float()
+    m, n = llm.model, len(ids)
+    m.alloc_kv((n + 15) // 16 + 1, 16)
+    b = ForwardBatch(tokens=torch.tensor(ids, dtype=torch.int32), positions=torch.arange(n, dtype=torch.int32),
+                     slot_mapping=torch.arange(n, dtype=torch.int32),
+                     block_table=torch.arange((n + 15) // 16 + 1, dtype=torch.int32)[None],
+                     kv_lens=torch.tensor([n], dtype=torch.int32), is_decode=False,
+                     cu_q=torch.tensor([0, n], dtype=torch.int32), max_q_len=n, max_kv_len=n,
+                     cross_states=states[0], cross_row_mask=rows[0, 0, :, 0])
+    mine = m.logits(m.forward_hidden(b)).float()
+    assert torch.nn.functional.cosine_similarity(ref.flatten(), plain.flatten(), dim=0) < 0.98      # the image matters
+    assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0) > 0.995
