@@ -45,6 +45,7 @@ class Request:
     generator: Optional[torch.Generator] = None
     embeds: Optional[torch.Tensor] = None         # [len(prompt), hidden] replacement input embeddings
     embeds_mask: Optional[torch.Tensor] = None    # [len(prompt)] bool: rows taken from ``embeds``
+    cross_states: Optional[torch.Tensor] = None   # [Tv, hidden] vision states read by cross-attention layers
 
 
 def _bucket(n: int) -> int:
@@ -67,7 +68,8 @@ class LLMEngine:
         self.prefill_chunk = prefill_chunk or config.get("prefill_chunk")
         self.max_model_len = max_model_len
         self.max_pages_per_seq = (max_model_len + self.page - 1) // self.page
-        self.use_graphs = (config.get("cuda_graphs") if use_cuda_graphs is None else use_cuda_graphs) and self.cuda
+        self.use_graphs = ((config.get("cuda_graphs") if use_cuda_graphs is None else use_cuda_graphs) and self.cuda
+                           and getattr(model.cfg, "graph_safe", True))
         if num_pages is None:
             budget = kv_pool_bytes if kv_pool_bytes is not None else config.get("kv_pool_bytes")
             per_page = model.kv_bytes_per_page(self.page)
@@ -120,9 +122,12 @@ class LLMEngine:
     # ------------------------------------------------------------------------------- requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
                     on_token: Optional[Callable[[int, int, bool], None]] = None,
-                    prompt_embeds: Optional[torch.Tensor] = None, embeds_mask: Optional[torch.Tensor] = None) -> int:
+                    prompt_embeds: Optional[torch.Tensor] = None, embeds_mask: Optional[torch.Tensor] = None,
+                    cross_states: Optional[torch.Tensor] = None) -> int:
         """``prompt_embeds`` [len(prompt), hidden] with ``embeds_mask`` [len(prompt)] (bool) replaces the
-        token embedding of the marked prompt positions (image patches of a vision-language model)."""
+        token embedding of the marked prompt positions (image patches of a vision-language model).
+        ``cross_states`` [Tv, hidden] are the vision states this request's cross-attention layers read
+        (Llama 3.2 Vision), during the prefill and every decode step."""
         params = params or SamplingParams()
         prompt = list(prompt)
         if len(prompt) == 0:
@@ -140,6 +145,8 @@ class LLMEngine:
             req.embeds = prompt_embeds.to(self.device).to(torch.bfloat16)
             req.embeds_mask = (embeds_mask if embeds_mask is not None else
                                torch.ones(len(prompt), dtype=torch.bool)).to(self.device)
+        if cross_states is not None:
+            req.cross_states = cross_states.to(self.device).to(torch.bfloat16)
         if params.seed is not None and not params.is_greedy:
             req.generator = torch.Generator(device=self.device).manual_seed(params.seed)
         self.requests[rid] = req
@@ -217,7 +224,7 @@ class LLMEngine:
                              slot_mapping=self._to_device(self.h_slots, t), block_table=self._to_device(self.h_table, n),
                              kv_lens=self._to_device(self.h_kv_lens, n), is_decode=False,
                              cu_q=self._to_device(self.h_cu_q, n + 1), max_q_len=max_q, max_kv_len=max_kv,
-                             embeds=embeds)
+                             embeds=embeds, cross_states=self._cross_states([self.requests[rid] for rid, _, _ in chunks]))
         hidden = self.model.forward_hidden(batch)
         done: list[tuple[Request, int]] = []
         fresh = [(row, req) for row, req in sample_rows if not req.output]
@@ -287,9 +294,17 @@ class LLMEngine:
         max_kv = self._decode_batch_tensors(rids, n)
         batch = ForwardBatch(tokens=self._to_device(self.h_tokens, n), positions=self._to_device(self.h_positions, n),
                              slot_mapping=self._to_device(self.h_slots, n), block_table=self._to_device(self.h_table, n),
-                             kv_lens=self._to_device(self.h_kv_lens, n), is_decode=True, max_kv_len=self.max_model_len)
+                             kv_lens=self._to_device(self.h_kv_lens, n), is_decode=True, max_kv_len=self.max_model_len,
+                             cross_states=self._cross_states(reqs))
         hidden = self.model.forward_hidden(batch)
         return self._sample(hidden, reqs)
+
+    @staticmethod
+    def _cross_states(reqs: list) -> Optional[list]:
+        """One entry per sequence of the batch (None for a request without an image), or None."""
+        if not any(r.cross_states is not None for r in reqs):
+            return None
+        return [r.cross_states for r in reqs]
 
     def _run_decode_graph(self, rids: list[int]) -> list[int]:
         n = len(rids)

@@ -149,6 +149,17 @@ class TextService:
                 ids += llm.tokenizer.encode(piece, add_special=special and i == 0)
         return ids
 
+    def _cross_states(self, llm: LoadedLLM, req: TextRequest):
+        """Vision states for a model whose decoder reads images through cross-attention layers
+        (Llama 3.2 Vision): the tiles of every image, concatenated. None for other models."""
+        if not req.images or llm.vlm is None or not hasattr(llm.vlm, "encode_image"):
+            return None
+        states = []
+        for im in req.images:
+            tiles, th, tw = llm.vlm.split_image(self._unit_image(im))
+            states.append(llm.vlm.encode_image(tiles, th, tw))
+        return torch.cat(states, 0)
+
     def _multimodal(self, llm: LoadedLLM, req: TextRequest, ids: list[int]):
         """(ids, embeds, mask) with every image token expanded to its patch embeddings."""
         from ..models.encoders.clip_vision import preprocess_image
@@ -156,6 +167,8 @@ class TextService:
             return ids, None, None
         if llm.vlm is None:
             raise ValueError("this model has no vision tower; images are not accepted")
+        if hasattr(llm.vlm, "encode_image"):               # cross-attention models keep one image token per image
+            return ids, None, None
         if hasattr(llm.vlm, "image_features_anyres"):      # any-resolution models take the image at its own size
             return llm.vlm.expand_prompt(ids, [self._unit_image(im) for im in req.images])
         size = llm.vlm.vision.cfg.image_size
@@ -275,7 +288,7 @@ class TextService:
         with h.wake:
             ids, embeds, emask = self._multimodal(llm, req, ids)
             rid = h.engine.add_request(ids, self._params(req, llm), on_token=lambda r, tok, fin: q.put((tok, fin)),
-                                       prompt_embeds=embeds, embeds_mask=emask)
+                                       prompt_embeds=embeds, embeds_mask=emask, cross_states=self._cross_states(llm, req))
             h.wake.notify_all()
         dec = llm.tokenizer.stream_decoder()
         text = ""

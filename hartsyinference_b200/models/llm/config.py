@@ -133,6 +133,13 @@ class TransformerConfig:
                 or not self.use_rope or self.nope_global or bool(self.rope_layers) or self.alibi or self.embed_norm or self.attn_sinks or self.qk_norm_after_rope or bool(self.cross_layers)
                 or self.o_bias or self.ffn_bias or not self.gated_ffn or self.activation not in ("silu", "gelu_tanh"))
 
+    @property
+    def graph_safe(self) -> bool:
+        """False when a decode step reads sizes back to the host or branches on per-request state
+        (gathered-page attention, the gpt-oss expert loop, cross-attention states), which a CUDA
+        graph cannot capture."""
+        return not (self.alibi or self.attn_sinks or bool(self.cross_layers))
+
     def layer_window(self, layer: int) -> int:
         if self.sliding_window <= 0:
             return 0

@@ -321,7 +321,13 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
         lm_get, tower_get = _llava_names(ck)
         model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
         model.load_state_dict(lm_get)
-        if raw.get("model_type") == "llava_next" or raw.get("image_grid_pinpoints"):
+        if raw.get("model_type") == "mllama":
+            from ..vlm.mllama import MllamaModel, MllamaVisionConfig
+            new = ck.get("model.language_model.embed_tokens.weight") is not None
+            vlm = MllamaModel(model, MllamaVisionConfig.from_hf(raw["vision_config"]), ck.get, int(raw.get("image_token_index", 128256)),
+                              tower_prefix="model.vision_model." if new else "vision_model.",
+                              projector_prefix="model.multi_modal_projector." if new else "multi_modal_projector.")
+        elif raw.get("model_type") == "llava_next" or raw.get("image_grid_pinpoints"):
             from ..vlm.llava_next import DEFAULT_PINPOINTS, LlavaNextModel
             vlm = LlavaNextModel(model, clip_vision_from_hf(raw["vision_config"]), int(raw.get("image_token_index", 32000)),
                                  get=tower_get, feature_layer=int(raw.get("vision_feature_layer", -2)),

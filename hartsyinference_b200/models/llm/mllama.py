@@ -33,20 +33,25 @@ class CrossLayer:
         self.gate_up, self.down = gate_up, down
         self.attn_gate, self.mlp_gate = attn_gate, mlp_gate
         self.heads, self.kv_heads, self.d, self.eps = heads, kv_heads, head_dim, eps
-        self._states: Optional[torch.Tensor] = None                       # the tensor whose K / V are cached
-        self._kv_cache: Optional[tuple[torch.Tensor, torch.Tensor]] = None
+        # id(states) -> (states, K, V): K / V of the image sets in flight (the entry holds the states tensor,
+        # so its id stays unique while the entry lives)
+        self._kv_cache: dict[int, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+        self.max_cached = 16
 
     def nbytes(self) -> int:
         return sum(w.nbytes() for w in (self.q, self.k, self.v, self.o, self.gate_up, self.down))
 
     def _kv(self, states: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-        if self._states is not states:                                    # one image set at a time per layer
+        hit = self._kv_cache.get(id(states))
+        if hit is None:
             tv = states.shape[0]
             k = ops.linear(states, self.k).reshape(tv * self.kv_heads, self.d)
             k = ops.norm(k, self.k_norm, eps=self.eps)[0].reshape(tv, self.kv_heads, self.d)
             v = ops.linear(states, self.v).reshape(tv, self.kv_heads, self.d)
-            self._states, self._kv_cache = states, (k, v)
-        return self._kv_cache
+            if len(self._kv_cache) >= self.max_cached:                    # drop the oldest entry
+                self._kv_cache.pop(next(iter(self._kv_cache)))
+            hit = self._kv_cache[id(states)] = (states, k, v)
+        return hit[1], hit[2]
 
     def __call__(self, x: torch.Tensor, states: Optional[torch.Tensor], row_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x [T, hidden] (one sequence), states [Tv, hidden] or None, row_mask [T] (0 for text rows

@@ -45,7 +45,8 @@ class ForwardBatch:
     max_kv_len: int = 0
     logit_rows: Optional[torch.Tensor] = None   # prefill: rows (into T) whose logits are needed
     embeds: Optional[torch.Tensor] = None       # optional precomputed input embeddings [T, H]
-    cross_states: Optional[torch.Tensor] = None     # Mllama: projected vision states [Tv, H] of the (single) sequence
+    cross_states: Optional[object] = None           # Mllama: projected vision states [Tv, H] for every row, or a list
+                                                    # with one entry (tensor or None) per sequence
     cross_row_mask: Optional[torch.Tensor] = None   # Mllama: [T], 0 for text rows that precede every image
 
 
@@ -606,6 +607,24 @@ class DecoderModel:
             act = (self._activation(gu[:, :f], cfg.activation, lw.act_params).float() * gu[:, f:].float()).to(gu.dtype)
         return self._reduce_linear(act.contiguous(), lw.down)
 
+    @staticmethod
+    def _cross_layer(cross, x: torch.Tensor, batch: ForwardBatch) -> torch.Tensor:
+        """A cross-attention layer over each sequence's own vision states (sequences without an image
+        pass through unchanged)."""
+        cs, rm = batch.cross_states, batch.cross_row_mask
+        if cs is None or isinstance(cs, torch.Tensor):
+            return cross(x, cs, rm)
+        bounds = list(range(len(cs) + 1)) if batch.is_decode or batch.cu_q is None else batch.cu_q.tolist()
+        out = x
+        for i, st in enumerate(cs):
+            if st is None:
+                continue
+            if out is x:
+                out = x.clone()
+            a, b = bounds[i], bounds[i + 1]
+            out[a:b] = cross(x[a:b], st, None if rm is None else rm[a:b])
+        return out
+
     def _forward_general(self, batch: ForwardBatch, x: torch.Tensor, scale: float):
         """Layer loop for block structures outside the fused path: norms after the blocks instead of
         before (OLMo 2), LayerNorm with bias, parallel attention / feed-forward branches, linear
@@ -622,7 +641,7 @@ class DecoderModel:
 
         for li, lw in enumerate(self.layers):
             if lw.cross is not None:
-                x = lw.cross(x, batch.cross_states, batch.cross_row_mask)
+                x = self._cross_layer(lw.cross, x, batch)
                 continue
             h = self._block_norm(x, lw.in_norm, lw.in_norm_b) if cfg.pre_norm else x
             a = self._attention(lw, li, h, None, batch, scale)

@@ -308,3 +308,31 @@ def test_mllama_cross_attention_over_vision_states(tmp_path):
     mine = m.logits(m.forward_hidden(b)).float()
     assert torch.nn.functional.cosine_similarity(ref.flatten(), plain.flatten(), dim=0) < 0.98      # the image matters
     assert torch.nn.functional.cosine_similarity(mine.flatten(), ref.flatten(), dim=0) > 0.995
+
+
+def test_mllama_engine_batches_requests_with_and_without_images(tmp_path):
+    """Through the engine: a request with vision states and a text-only one decode in the same
+    batch, and each produces what it produces alone; the image request follows transformers' greedy
+    continuation."""
+    from hartsyinference_b200.engine.llm_engine import LLMEngine, SamplingParams
+    hf, llm = _mllama(tmp_path)
+    g = torch.Generator().manual_seed(5)
+    a = torch.randint(0, 320, (9,), generator=g).tolist()
+    b = torch.randint(0, 320, (13,), generator=g).tolist()
+    states = (torch.randn(10, 128, generator=g) * 2).to(torch.bfloat16)
+    sp = SamplingParams(greedy=True, max_tokens=5)
+
+    def run(jobs):
+        eng = LLMEngine(llm.model, num_pages=32, page_size=16, max_batch=4, prefill_chunk=64, max_model_len=64)
+        rids = [eng.add_request(ids, sp, cross_states=st) for ids, st in jobs]
+        eng.run_until_done()
+        return [eng.requests[r].output for r in rids]
+
+    both = run([(a, states), (b, None)])
+    assert both[0] == run([(a, states)])[0]
+    assert both[1] == run([(b, None)])[0]
+    assert both[0] != run([(a, None)])[0]
+    with torch.no_grad():
+        ref = hf.generate(torch.tensor([a]), cross_attention_states=states[None].float(), max_new_tokens=5, do_sample=False,
+                          pad_token_id=0)[0, len(a):].tolist()
+    assert both[0][:len(ref)] == ref

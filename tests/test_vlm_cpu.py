@@ -552,3 +552,75 @@ def test_detect_operation_and_nms(tmp_path):
     with pytest.raises(ValueError):
         eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="embed", images=[pic]))
     eng.close()
+
+
+def test_mllama_vision_tower_and_cross_attention_match_transformers(tmp_path):
+    """Llama 3.2 Vision end to end: tiled vision tower + projector + decoder with cross-attention
+    layers against ``MllamaForConditionalGeneration`` on a two-tile image."""
+    tr = pytest.importorskip("transformers")
+    from transformers.models.mllama.configuration_mllama import MllamaConfig, MllamaTextConfig, MllamaVisionConfig
+    from hartsyinference_b200.models.llm.loader import load_llm, save_hf_checkpoint
+    from hartsyinference_b200.models.llm.transformer import ForwardBatch
+    vc = MllamaVisionConfig(hidden_size=64, attention_heads=4, intermediate_size=128, num_hidden_layers=3, num_global_layers=2,
+                            image_size=28, patch_size=14, max_num_tiles=4, intermediate_layers_indices=[0, 2], vision_output_dim=192)
+    tc = MllamaTextConfig(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                          num_key_value_heads=2, max_position_embeddings=256, cross_attention_layers=[1], pad_token_id=0,
+                          rope_parameters={"rope_type": "default", "rope_theta": 10000.0})
+    cfg = MllamaConfig(vision_config=vc, text_config=tc, image_token_index=319)
+    cfg._attn_implementation = "eager"
+    cfg.text_config._attn_implementation = "eager"
+    cfg.vision_config._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = tr.MllamaForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2 and "embedding" not in n:
+                p.mul_(2.0)
+            if n.endswith("gate") or "cross_attn_attn_gate" in n or "cross_attn_mlp_gate" in n:
+                p.fill_(0.6)                                   # the gates start at zero
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()},
+                       tmp_path / "m")
+    hf = hf.to(torch.bfloat16).float()
+    llm = load_llm(tmp_path / "m", "cpu")
+    assert llm.vlm is not None and llm.config.cross_layers == (1,)
+    g = torch.Generator().manual_seed(3)
+    tiles = torch.zeros(4, 3, 28, 28)
+    tiles[:2] = torch.randn(2, 3, 28, 28, generator=g)
+    ids = [319] + torch.randint(0, 300, (14,), generator=g).tolist()          # the image token opens the prompt
+    n = len(ids)
+    ar_id = llm.vlm.tower.aspect_ratio_id(1, 2)
+    with torch.no_grad():
+        cam = torch.zeros(1, n, 1, 4)
+        cam[..., :2] = 1
+        ref = hf(input_ids=torch.tensor([ids]), pixel_values=tiles[None, None], aspect_ratio_ids=torch.tensor([[ar_id]]),
+                 aspect_ratio_mask=torch.tensor([[[1, 1, 0, 0]]]), cross_attention_mask=cam).logits[0].float()
+        plain = hf(input_ids=torch.tensor([ids])).logits[0].float()
+    states = llm.vlm.encode_image(tiles, 1, 2)
+    assert states.shape == (2 * 5, 128)
+    m = llm.model
+    m.alloc_kv(3, 16)
+    b = ForwardBatch(tokens=torch.tensor(ids, dtype=torch.int32), positions=torch.arange(n, dtype=torch.int32),
+                     slot_mapping=torch.arange(n, dtype=torch.int32), block_table=torch.arange(3, dtype=torch.int32)[None],
+                     kv_lens=torch.tensor([n], dtype=torch.int32), is_decode=False, cu_q=torch.tensor([0, n], dtype=torch.int32),
+                     max_q_len=n, max_kv_len=n, cross_states=states)
+    mine = m.logits(m.forward_hidden(b)).float()
+    cos = torch.nn.functional.cosine_similarity
+    assert cos(ref.flatten(), plain.flatten(), dim=0) < 0.99
+    assert cos(mine.flatten(), ref.flatten(), dim=0) > 0.99
+
+
+def test_mllama_split_image_picks_the_tile_grid_by_aspect_ratio():
+    from hartsyinference_b200.models.vlm.mllama import MllamaModel, MllamaVisionConfig, MllamaVisionTower
+    cfg = MllamaVisionConfig(image_size=28, patch=14, max_tiles=4)
+    glue = MllamaModel.__new__(MllamaModel)
+    glue.tower = MllamaVisionTower.__new__(MllamaVisionTower)
+    glue.tower.cfg = cfg
+    wide = torch.rand(3, 40, 120)
+    tiles, th, tw = glue.split_image(wide)
+    assert (th, tw) == (1, 3) and tiles.shape == (4, 3, 28, 28)
+    assert tiles[3].abs().sum() == 0 and tiles[2].abs().sum() > 0
+    tall = torch.rand(3, 100, 50)
+    assert glue.split_image(tall)[1:] == (2, 1)
+    square = torch.rand(3, 64, 64)
+    assert glue.split_image(square)[1:] == (2, 2)              # the largest grid of that shape
+    assert glue.tower.aspect_ratio_id(2, 2) == 6
