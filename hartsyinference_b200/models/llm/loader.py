@@ -294,8 +294,11 @@ def _llava_names(ck) -> tuple[Callable, Callable]:
     model.vision_tower.* / model.multi_modal_projector.* / lm_head``. Returns (decoder get, tower get)
     that take the plain decoder names and the first layout's tower names."""
     new = ck.get("model.language_model.embed_tokens.weight") is not None
+    flat = ck.get("model.embed_tokens.weight") is not None        # decoder names unprefixed (first Qwen-VL releases)
 
     def lm(name: str):
+        if flat:
+            return ck.get(name)
         if new:
             return ck.get("model.language_model." + name[len("model."):]) if name.startswith("model.") else ck.get(name)
         return ck.get("language_model." + name)
@@ -321,7 +324,11 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
         lm_get, tower_get = _llava_names(ck)
         model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
         model.load_state_dict(lm_get)
-        if raw.get("model_type") == "mllama":
+        if raw.get("model_type") in ("qwen2_5_vl",):
+            from ..vlm.qwen_vl import QwenVisionConfig, QwenVlModel
+            vlm = QwenVlModel(model, QwenVisionConfig.from_hf(raw["vision_config"]), ck.get, int(raw.get("image_token_id", 151655)),
+                              prefix="model.visual." if ck.get("model.visual.patch_embed.proj.weight") is not None else "visual.")
+        elif raw.get("model_type") == "mllama":
             from ..vlm.mllama import MllamaModel, MllamaVisionConfig
             new = ck.get("model.language_model.embed_tokens.weight") is not None
             vlm = MllamaModel(model, MllamaVisionConfig.from_hf(raw["vision_config"]), ck.get, int(raw.get("image_token_index", 128256)),

@@ -45,6 +45,7 @@ class ForwardBatch:
     max_kv_len: int = 0
     logit_rows: Optional[torch.Tensor] = None   # prefill: rows (into T) whose logits are needed
     embeds: Optional[torch.Tensor] = None       # optional precomputed input embeddings [T, H]
+    positions3: Optional[torch.Tensor] = None       # Qwen-VL: [3, T] int32 time / row / column positions (None: all = positions)
     cross_states: Optional[object] = None           # Mllama: projected vision states [Tv, H] for every row, or a list
                                                     # with one entry (tensor or None) per sequence
     cross_row_mask: Optional[torch.Tensor] = None   # Mllama: [T], 0 for text rows that precede every image
@@ -537,6 +538,9 @@ class DecoderModel:
         rot = cfg.rotary_dim if cfg.use_rope and not (cfg.nope_global and window == 0) else 0
         if cfg.rope_layers and not cfg.rope_layers[self.layer0 + li]:
             rot = 0
+        if cfg.mrope_section and batch.positions3 is not None and rot > 0:
+            qkv = self._mrope(qkv, batch.positions3, inv_freq)       # rotated here; the kernel below only writes the cache
+            rot = 0
         if cfg.qk_norm_after_rope and q_norm_w is not None:
             # rotate first (no cache write), normalise the rotated heads, then run the same kernel with
             # no rotation for the cache write
@@ -565,6 +569,23 @@ class DecoderModel:
                                          batch.max_q_len, causal=True, scale=scale,
                                          softcap=cfg.attn_softcap, window=window)
         return self._reduce_linear(att.reshape(t, self.hq * d), lw.o)
+
+    def _mrope(self, qkv: torch.Tensor, positions3: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+        """Rotary embedding whose frequency pairs are split into three sections, driven by the time,
+        row and column position of each token (split-half pairing). Rotates q and k inside the
+        packed [T, (hq + 2 hkv) d] activation."""
+        cfg, d = self.cfg, self.cfg.head_dim
+        t = qkv.shape[0]
+        axis = torch.repeat_interleave(torch.arange(3, device=qkv.device),
+                                       torch.tensor(cfg.mrope_section, device=qkv.device))          # [d / 2]
+        ang = positions3.to(qkv.device).float()[:, :, None] * inv_freq.float()[None, None, :]        # [3, T, d / 2]
+        ang = ang.gather(0, axis[None, None, :].expand(1, t, -1))[0]                                 # [T, d / 2]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        x = qkv.float().reshape(t, self.hq + 2 * self.hkv, d)
+        nr = self.hq + self.hkv
+        x1, x2 = x[:, :nr, : d // 2], x[:, :nr, d // 2:]
+        rotd = torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+        return torch.cat([rotd, x[:, nr:]], 1).reshape(t, -1).to(qkv.dtype).contiguous()
 
     def _block_norm(self, x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor]) -> torch.Tensor:
         cfg = self.cfg

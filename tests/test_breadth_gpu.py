@@ -149,3 +149,38 @@ def test_chroma_on_device_matches_cpu():
         img_ids, txt_ids = F.flux_ids(8, 8, S_t, dev)
         outs.append(m.forward(img.to(dev), txt.to(dev), t.to(dev), pooled.to(dev), img_ids, txt_ids).float().cpu())
     assert torch.nn.functional.cosine_similarity(outs[0].flatten(), outs[1].flatten(), dim=0) > 0.99
+
+
+def test_mllama_cross_attention_on_device_matches_cpu(tmp_path):
+    """Llama 3.2 Vision decoder with vision states on the device kernels against the CPU path."""
+    tr = pytest.importorskip("transformers")
+    from transformers.models.mllama.configuration_mllama import MllamaTextConfig
+    from hartsyinference_b200.models.llm.loader import load_llm, save_hf_checkpoint
+    from hartsyinference_b200.models.llm.transformer import ForwardBatch
+    cfg = MllamaTextConfig(**{**_GPU_BASE, "cross_attention_layers": [1], "num_hidden_layers": 3, "pad_token_id": 0,
+                              "rope_parameters": {"rope_type": "default", "rope_theta": 10000.0}})
+    torch.manual_seed(0)
+    hf = tr.MllamaForCausalLM(cfg)
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2:
+                p.mul_(3.0)
+            if n.endswith(("cross_attn_attn_gate", "cross_attn_mlp_gate")):
+                p.fill_(0.7)
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()}, tmp_path / "m")
+    ids = torch.randint(0, 320, (29,), generator=torch.Generator().manual_seed(1)).tolist()
+    states = torch.randn(24, 256, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    outs = []
+    for dev in ("cpu", "cuda"):
+        m = load_llm(tmp_path / "m", dev, fp8=False).model
+        n = len(ids)
+        pages = (n + 15) // 16 + 1
+        m.alloc_kv(pages, 16)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        b = ForwardBatch(tokens=i32(ids), positions=i32(list(range(n))),
+                         slot_mapping=torch.arange(n, dtype=torch.int64 if dev == "cuda" else torch.int32, device=dev),
+                         block_table=i32(list(range(pages)))[None], kv_lens=i32([n]), is_decode=False,
+                         cu_q=i32([0, n]), max_q_len=n, max_kv_len=n, cross_states=[states.to(dev)])
+        outs.append(m.logits(m.forward_hidden(b)).float().cpu())
+    cos = torch.nn.functional.cosine_similarity(outs[0].flatten(), outs[1].flatten(), dim=0)
+    assert cos > 0.99, f"cos {cos:.4f}"

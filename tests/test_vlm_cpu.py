@@ -624,3 +624,68 @@ def test_mllama_split_image_picks_the_tile_grid_by_aspect_ratio():
     square = torch.rand(3, 64, 64)
     assert glue.split_image(square)[1:] == (2, 2)              # the largest grid of that shape
     assert glue.tower.aspect_ratio_id(2, 2) == 6
+
+
+def _tiny_qwen_vl(tmp_path):
+    tr = pytest.importorskip("transformers")
+    from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLConfig
+    from hartsyinference_b200.models.llm.loader import load_llm, save_hf_checkpoint
+    cfg = Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "mrope_section": [4, 6, 6], "rope_theta": 10000.0}),
+        vision_config=dict(depth=3, hidden_size=64, intermediate_size=96, num_heads=4, out_hidden_size=128, patch_size=14,
+                           spatial_merge_size=2, temporal_patch_size=2, window_size=56, fullatt_block_indexes=[1]),
+        image_token_id=318, vision_start_token_id=317, vision_end_token_id=316, video_token_id=315)
+    for c in (cfg, cfg.text_config, cfg.vision_config):
+        c._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = tr.Qwen2_5_VLForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.mul_(2.0)
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()},
+                       tmp_path / "m")
+    return hf.to(torch.bfloat16).float(), load_llm(tmp_path / "m", "cpu")
+
+
+def test_qwen2_5_vl_matches_transformers(tmp_path):
+    """Windowed vision tower + merger + M-RoPE decoder against ``Qwen2_5_VLForConditionalGeneration``
+    on a 6 x 8 patch image (3 x 4 merged tokens, two attention windows)."""
+    from hartsyinference_b200.models.llm.transformer import ForwardBatch
+    from hartsyinference_b200.models.vlm.qwen_vl import mrope_positions
+    hf, llm = _tiny_qwen_vl(tmp_path)
+    assert llm.vlm is not None and llm.config.mrope_section == (4, 6, 6)
+    g = torch.Generator().manual_seed(4)
+    gh, gw = 6, 8
+    patches = torch.randn(gh * gw, 3 * 2 * 14 * 14, generator=g)
+    feats = llm.vlm.vision(patches, gh, gw)
+    with torch.no_grad():
+        ref_feats = hf.model.visual(patches, grid_thw=torch.tensor([[1, gh, gw]])).pooler_output
+    cos = torch.nn.functional.cosine_similarity
+    assert feats.shape == (12, 128)
+    assert cos(feats.float().flatten(), ref_feats.flatten(), dim=0) > 0.99
+    ids = [5, 9, 317] + [318] * 12 + [316] + torch.randint(0, 300, (9,), generator=g).tolist()
+    n = len(ids)
+    pos3, delta = mrope_positions(ids, 318, [(3, 4)])
+    assert pos3[:, 3:15].tolist() == [[3] * 12, [3, 3, 3, 3, 4, 4, 4, 4, 5, 5, 5, 5], [3, 4, 5, 6] * 3]
+    assert pos3[:, 15].tolist() == [7, 7, 7] and delta == int(pos3.max()) + 1 - n
+    with torch.no_grad():
+        ref = hf(input_ids=torch.tensor([ids]), pixel_values=patches, image_grid_thw=torch.tensor([[1, gh, gw]]),
+                 position_ids=pos3.long()[:, None, :]).logits[0].float()
+    m = llm.model
+    embeds = torch.zeros(n, 128, dtype=torch.bfloat16)
+    mask = torch.tensor([t == 318 for t in ids])
+    embeds[mask] = feats.to(torch.bfloat16)
+    full = m.embed[torch.tensor(ids)].clone()
+    full[mask] = embeds[mask]
+    pages = (n + 15) // 16 + 1
+    m.alloc_kv(pages, 16)
+    b = ForwardBatch(tokens=torch.tensor(ids, dtype=torch.int32), positions=torch.arange(n, dtype=torch.int32),
+                     slot_mapping=torch.arange(n, dtype=torch.int32), block_table=torch.arange(pages, dtype=torch.int32)[None],
+                     kv_lens=torch.tensor([n], dtype=torch.int32), is_decode=False, cu_q=torch.tensor([0, n], dtype=torch.int32),
+                     max_q_len=n, max_kv_len=n, embeds=full, positions3=pos3)
+    mine = m.logits(m.forward_hidden(b)).float()
+    assert cos(mine.flatten(), ref.flatten(), dim=0) > 0.99
+    assert (mine.argmax(-1) == ref.argmax(-1)).float().mean() > 0.9
