@@ -46,6 +46,8 @@ class Request:
     embeds: Optional[torch.Tensor] = None         # [len(prompt), hidden] replacement input embeddings
     embeds_mask: Optional[torch.Tensor] = None    # [len(prompt)] bool: rows taken from ``embeds``
     cross_states: Optional[torch.Tensor] = None   # [Tv, hidden] vision states read by cross-attention layers
+    positions3: Optional[torch.Tensor] = None     # [3, len(prompt)] int32 time / row / column rotary positions (Qwen-VL)
+    rope_delta: int = 0                           # rotary position of a generated token = its index + rope_delta
 
 
 def _bucket(n: int) -> int:
@@ -123,11 +125,14 @@ class LLMEngine:
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
                     on_token: Optional[Callable[[int, int, bool], None]] = None,
                     prompt_embeds: Optional[torch.Tensor] = None, embeds_mask: Optional[torch.Tensor] = None,
-                    cross_states: Optional[torch.Tensor] = None) -> int:
+                    cross_states: Optional[torch.Tensor] = None, positions3: Optional[torch.Tensor] = None,
+                    rope_delta: int = 0) -> int:
         """``prompt_embeds`` [len(prompt), hidden] with ``embeds_mask`` [len(prompt)] (bool) replaces the
         token embedding of the marked prompt positions (image patches of a vision-language model).
         ``cross_states`` [Tv, hidden] are the vision states this request's cross-attention layers read
-        (Llama 3.2 Vision), during the prefill and every decode step."""
+        (Llama 3.2 Vision), during the prefill and every decode step. ``positions3`` [3, len(prompt)]
+        gives the prompt's three-axis rotary positions and ``rope_delta`` the offset of every later
+        token's rotary position from its sequence index (Qwen-VL image prompts)."""
         params = params or SamplingParams()
         prompt = list(prompt)
         if len(prompt) == 0:
@@ -145,6 +150,10 @@ class LLMEngine:
             req.embeds = prompt_embeds.to(self.device).to(torch.bfloat16)
             req.embeds_mask = (embeds_mask if embeds_mask is not None else
                                torch.ones(len(prompt), dtype=torch.bool)).to(self.device)
+        if positions3 is not None:
+            if positions3.shape != (3, len(prompt)):
+                raise ValueError("positions3 needs shape [3, len(prompt)]")
+            req.positions3, req.rope_delta = positions3.to(torch.int32).cpu(), int(rope_delta)
         if cross_states is not None:
             req.cross_states = cross_states.to(self.device).to(torch.bfloat16)
         if params.seed is not None and not params.is_greedy:
@@ -191,7 +200,7 @@ class LLMEngine:
             toks = self._seq_tokens(req)
             target = len(req.prompt) + len(req.output) - (1 if req.output else 0)
             self.h_tokens[t:t + count] = torch.tensor(toks[start:start + count], dtype=torch.int32)
-            self.h_positions[t:t + count] = torch.arange(start, start + count, dtype=torch.int32)
+            self.h_positions[t:t + count] = self._rope_positions(req, start, count)
             self._fill_table(i, rid)
             pos = torch.arange(start, start + count, dtype=torch.int64)
             self.h_slots[t:t + count] = self.h_table[i][(pos // page)].to(torch.int64) * page + pos % page
@@ -224,7 +233,8 @@ class LLMEngine:
                              slot_mapping=self._to_device(self.h_slots, t), block_table=self._to_device(self.h_table, n),
                              kv_lens=self._to_device(self.h_kv_lens, n), is_decode=False,
                              cu_q=self._to_device(self.h_cu_q, n + 1), max_q_len=max_q, max_kv_len=max_kv,
-                             embeds=embeds, cross_states=self._cross_states([self.requests[rid] for rid, _, _ in chunks]))
+                             embeds=embeds, cross_states=self._cross_states([self.requests[rid] for rid, _, _ in chunks]),
+                             positions3=self._positions3(chunks))
         hidden = self.model.forward_hidden(batch)
         done: list[tuple[Request, int]] = []
         fresh = [(row, req) for row, req in sample_rows if not req.output]
@@ -266,7 +276,7 @@ class LLMEngine:
             req = self.requests[rid]
             pos = len(req.prompt) + len(req.output) - 1       # position of the token being fed
             self.h_tokens[i] = req.output[-1]
-            self.h_positions[i] = pos
+            self.h_positions[i] = pos + req.rope_delta
             self._fill_table(i, rid)
             self.h_slots[i] = int(self.h_table[i, pos // page]) * page + pos % page
             self.h_kv_lens[i] = pos + 1
@@ -298,6 +308,31 @@ class LLMEngine:
                              cross_states=self._cross_states(reqs))
         hidden = self.model.forward_hidden(batch)
         return self._sample(hidden, reqs)
+
+    @staticmethod
+    def _rope_positions(req: "Request", start: int, count: int) -> torch.Tensor:
+        """Rotary positions of sequence rows [start, start + count): the index, shifted by the
+        request's offset for rows after the prompt."""
+        pos = torch.arange(start, start + count, dtype=torch.int32)
+        if req.rope_delta:
+            pos = pos + (pos >= len(req.prompt)).to(torch.int32) * req.rope_delta
+        return pos
+
+    def _positions3(self, chunks: list) -> Optional[torch.Tensor]:
+        """[3, T] rotary positions of a prefill batch when any of its requests carries three-axis
+        prompt positions (rows of the other requests repeat their index on all axes)."""
+        if not any(self.requests[rid].positions3 is not None for rid, _, _ in chunks):
+            return None
+        cols = []
+        for rid, start, count in chunks:
+            req = self.requests[rid]
+            p3 = self._rope_positions(req, start, count)[None].expand(3, -1).clone()
+            if req.positions3 is not None:
+                end = min(start + count, req.positions3.shape[1])
+                if end > start:
+                    p3[:, :end - start] = req.positions3[:, start:end]
+            cols.append(p3)
+        return torch.cat(cols, 1).to(self.device)
 
     @staticmethod
     def _cross_states(reqs: list) -> Optional[list]:

@@ -168,6 +168,8 @@ class QwenVlModel:
     """Decoder + vision tower. ``expand_prompt`` turns a prompt with one image token per image into
     (ids, embeds, mask, positions3, rope_delta) for the engine."""
 
+    three_axis_positions = True
+
     def __init__(self, decoder, cfg: QwenVisionConfig, get: Callable[[str], Optional[torch.Tensor]], image_token_id: int,
                  prefix: str = "model.visual."):
         self.decoder, self.image_token_id = decoder, image_token_id

@@ -689,3 +689,36 @@ def test_qwen2_5_vl_matches_transformers(tmp_path):
     mine = m.logits(m.forward_hidden(b)).float()
     assert cos(mine.flatten(), ref.flatten(), dim=0) > 0.99
     assert (mine.argmax(-1) == ref.argmax(-1)).float().mean() > 0.9
+
+
+def test_qwen2_5_vl_engine_generation_follows_transformers(tmp_path):
+    """An image prompt through the engine (three-axis prompt positions, shifted positions for the
+    generated tokens, chunked prefill) continues like transformers' greedy generation; a text-only
+    request batched with it is unaffected."""
+    from hartsyinference_b200.engine.llm_engine import LLMEngine, SamplingParams
+    hf, llm = _tiny_qwen_vl(tmp_path)
+    g = torch.Generator().manual_seed(6)
+    image = torch.rand(3, 84, 112, generator=g)
+    prompt = [5, 9, 317, 318, 316] + torch.randint(0, 300, (6,), generator=g).tolist()
+    ids, embeds, mask, pos3, delta = llm.vlm.expand_prompt(prompt, [image])
+    assert len(ids) == len(prompt) - 1 + 12 and delta < 0
+    other = torch.randint(0, 300, (11,), generator=g).tolist()
+    sp = SamplingParams(greedy=True, max_tokens=6)
+
+    def run(with_other, chunk):
+        eng = LLMEngine(llm.model, num_pages=32, page_size=16, max_batch=4, prefill_chunk=chunk, max_model_len=96)
+        rid = eng.add_request(ids, sp, prompt_embeds=embeds, embeds_mask=mask, positions3=pos3, rope_delta=delta)
+        rid2 = eng.add_request(other, sp) if with_other else None
+        eng.run_until_done()
+        return eng.requests[rid].output, (eng.requests[rid2].output if with_other else None)
+
+    out, out_other = run(True, 64)
+    assert run(False, 8)[0] == out                              # chunked prefill slices the positions correctly
+    eng = LLMEngine(llm.model, num_pages=32, page_size=16, max_batch=4, prefill_chunk=64, max_model_len=96)
+    assert eng.generate([other], sp)[0] == out_other
+    from hartsyinference_b200.models.vlm.qwen_vl import patchify
+    patches, gh, gw = patchify(image, llm.vlm.vision.cfg)
+    with torch.no_grad():
+        ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values=patches, image_grid_thw=torch.tensor([[1, gh, gw]]),
+                          max_new_tokens=6, do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
+    assert out[:len(ref)] == ref
