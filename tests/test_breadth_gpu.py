@@ -184,3 +184,39 @@ def test_mllama_cross_attention_on_device_matches_cpu(tmp_path):
         outs.append(m.logits(m.forward_hidden(b)).float().cpu())
     cos = torch.nn.functional.cosine_similarity(outs[0].flatten(), outs[1].flatten(), dim=0)
     assert cos > 0.99, f"cos {cos:.4f}"
+
+
+def test_qwen_vl_three_axis_rotary_on_device_matches_cpu(tmp_path):
+    """Qwen2.5-VL: vision tower, merged-token embeddings and the three-section rotary embedding on
+    the device against the CPU path, through the engine."""
+    tr = pytest.importorskip("transformers")
+    from transformers.models.qwen2_5_vl.configuration_qwen2_5_vl import Qwen2_5_VLConfig
+    from hartsyinference_b200.engine.llm_engine import LLMEngine, SamplingParams
+    from hartsyinference_b200.models.llm.loader import load_llm, save_hf_checkpoint
+    cfg = Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=320, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "mrope_section": [8, 12, 12], "rope_theta": 10000.0}),
+        vision_config=dict(depth=3, hidden_size=64, intermediate_size=96, num_heads=4, out_hidden_size=256, patch_size=14,
+                           spatial_merge_size=2, temporal_patch_size=2, window_size=56, fullatt_block_indexes=[1]),
+        image_token_id=318, vision_start_token_id=317, vision_end_token_id=316, video_token_id=315)
+    torch.manual_seed(0)
+    hf = tr.Qwen2_5_VLForConditionalGeneration(cfg)
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.mul_(2.0)
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()}, tmp_path / "m")
+    image = torch.rand(3, 84, 112, generator=torch.Generator().manual_seed(6))
+    prompt = [5, 9, 317, 318, 316, 40, 41, 42, 43]
+    outs = {}
+    for dev in ("cpu", "cuda"):
+        llm = load_llm(tmp_path / "m", dev, fp8=False)
+        ids, embeds, mask, pos3, delta = llm.vlm.expand_prompt(prompt, [image])
+        eng = LLMEngine(llm.model, num_pages=32, page_size=16, max_batch=2, prefill_chunk=64, max_model_len=96)
+        rid = eng.add_request(ids, SamplingParams(greedy=True, max_tokens=4), prompt_embeds=embeds, embeds_mask=mask,
+                              positions3=pos3, rope_delta=delta)
+        eng.run_until_done()
+        outs[dev] = (embeds.float().cpu(), eng.requests[rid].output)
+    assert torch.nn.functional.cosine_similarity(outs["cpu"][0].flatten(), outs["cuda"][0].flatten(), dim=0) > 0.99
+    assert len(outs["cuda"][1]) == 4 and outs["cuda"][1][0] == outs["cpu"][1][0]
