@@ -324,7 +324,7 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
         lm_get, tower_get = _llava_names(ck)
         model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
         model.load_state_dict(lm_get)
-        if raw.get("model_type") in ("qwen2_5_vl",):
+        if raw.get("model_type") in ("qwen2_5_vl", "qwen2_vl"):
             from ..vlm.qwen_vl import QwenVisionConfig, QwenVlModel
             vlm = QwenVlModel(model, QwenVisionConfig.from_hf(raw["vision_config"]), ck.get, int(raw.get("image_token_id", 151655)),
                               prefix="model.visual." if ck.get("model.visual.patch_embed.proj.weight") is not None else "visual.")

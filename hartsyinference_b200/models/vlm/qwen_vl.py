@@ -1,4 +1,4 @@
-"""Qwen2.5-VL: the windowed vision transformer, its 2x2 patch merger, and the three-axis rotary
+"""Qwen2-VL / Qwen2.5-VL: the (windowed) vision transformer, its 2x2 patch merger, and the three-axis rotary
 positions (M-RoPE) its decoder uses.
 
 Vision tower, for one image of ``gh x gw`` patches (both even):
@@ -8,6 +8,9 @@ Vision tower, for one image of ``gh x gw`` patches (both even):
     RMSNorm, SwiGLU MLP. Blocks listed in ``full_blocks`` attend over the whole image; the others
     only within windows of ``window / patch / merge`` merged cells per side. The merger normalises,
     concatenates each 2x2 block and maps it through a two-layer MLP to the decoder width.
+
+Qwen2-VL's tower is the same skeleton with LayerNorm, a plain quick-GELU MLP and full attention in
+every block (``QwenVisionConfig.legacy``).
 
 Attention inside a window is expressed with a block mask on the natural token order, so no
 reordering (and no inverse reordering after the merger) is needed.
@@ -35,9 +38,16 @@ class QwenVisionConfig:
     window: int = 112
     full_blocks: tuple = (7, 15, 23, 31)
     eps: float = 1e-6
+    legacy: bool = False                # Qwen2-VL: LayerNorm, plain quick-GELU MLP, full attention in every block
 
     @staticmethod
     def from_hf(d: dict) -> "QwenVisionConfig":
+        if d.get("model_type") == "qwen2_vl" or "embed_dim" in d:
+            hidden = d.get("embed_dim", 1280)
+            return QwenVisionConfig(hidden=hidden, heads=d.get("num_heads", 16), ffn=int(hidden * d.get("mlp_ratio", 4)),
+                                    depth=d.get("depth", 32), out_hidden=d.get("hidden_size", 3584), patch=d.get("patch_size", 14),
+                                    temporal_patch=d.get("temporal_patch_size", 2), merge=d.get("spatial_merge_size", 2),
+                                    window=0, full_blocks=(), legacy=True)
         return QwenVisionConfig(hidden=d.get("hidden_size", 1280), heads=d.get("num_heads", 16), ffn=d.get("intermediate_size", 3420),
                                 depth=d.get("depth", 32), out_hidden=d.get("out_hidden_size", 3584), patch=d.get("patch_size", 14),
                                 temporal_patch=d.get("temporal_patch_size", 2), merge=d.get("spatial_merge_size", 2),
@@ -73,11 +83,23 @@ def patchify(image: torch.Tensor, cfg: QwenVisionConfig, max_pixels: int = 1280 
     return x.reshape(gh * gw, 3 * tp * p * p).contiguous(), gh, gw
 
 
+def _norm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    if b is None:
+        return _rms(x, w, eps)
+    return F.layer_norm(x.float(), (x.shape[-1],), w.float(), b.float(), eps).to(x.dtype)
+
+
 class _Block:
-    def __init__(self, t: Callable, p: str):
+    def __init__(self, t: Callable, p: str, legacy: bool = False):
         self.n1, self.n2 = t(p + "norm1.weight"), t(p + "norm2.weight")
+        self.n1_b = self.n2_b = None
         self.qkv_w, self.qkv_b = t(p + "attn.qkv.weight"), t(p + "attn.qkv.bias")
         self.proj_w, self.proj_b = t(p + "attn.proj.weight"), t(p + "attn.proj.bias")
+        self.legacy = legacy
+        if legacy:
+            self.n1_b, self.n2_b = t(p + "norm1.bias"), t(p + "norm2.bias")
+            self.fc1_w, self.fc1_b, self.fc2_w, self.fc2_b = t(p + "mlp.fc1.weight"), t(p + "mlp.fc1.bias"), t(p + "mlp.fc2.weight"), t(p + "mlp.fc2.bias")
+            return
         self.gate_w, self.gate_b = t(p + "mlp.gate_proj.weight"), t(p + "mlp.gate_proj.bias")
         self.up_w, self.up_b = t(p + "mlp.up_proj.weight"), t(p + "mlp.up_proj.bias")
         self.down_w, self.down_b = t(p + "mlp.down_proj.weight"), t(p + "mlp.down_proj.bias")
@@ -85,7 +107,7 @@ class _Block:
     def __call__(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, mask: Optional[torch.Tensor], heads: int, eps: float):
         n, c = x.shape
         d = c // heads
-        q, k, v = F.linear(_rms(x, self.n1, eps), self.qkv_w, self.qkv_b).reshape(n, 3, heads, d).unbind(1)
+        q, k, v = F.linear(_norm(x, self.n1, self.n1_b, eps), self.qkv_w, self.qkv_b).reshape(n, 3, heads, d).unbind(1)
 
         def rot(u):
             uf = u.float()
@@ -95,7 +117,10 @@ class _Block:
         a = F.scaled_dot_product_attention(rot(q).transpose(0, 1)[None], rot(k).transpose(0, 1)[None], v.transpose(0, 1)[None],
                                            attn_mask=mask)[0]
         x = x + F.linear(a.transpose(0, 1).reshape(n, c), self.proj_w, self.proj_b)
-        h = _rms(x, self.n2, eps)
+        h = _norm(x, self.n2, self.n2_b, eps)
+        if self.legacy:
+            u = F.linear(h, self.fc1_w, self.fc1_b)
+            return x + F.linear(u * torch.sigmoid(1.702 * u.float()).to(u.dtype), self.fc2_w, self.fc2_b)
         return x + F.linear(F.silu(F.linear(h, self.gate_w, self.gate_b)) * F.linear(h, self.up_w, self.up_b), self.down_w, self.down_b)
 
 
@@ -111,8 +136,9 @@ class QwenVisionTower:
             return w.to(dtype).to(self.device)
 
         self.patch_w = t("patch_embed.proj.weight").reshape(cfg.hidden, -1)
-        self.blocks = [_Block(t, f"blocks.{i}.") for i in range(cfg.depth)]
+        self.blocks = [_Block(t, f"blocks.{i}.", cfg.legacy) for i in range(cfg.depth)]
         self.ln_q = t("merger.ln_q.weight")
+        self.ln_q_b = t("merger.ln_q.bias") if cfg.legacy else None
         self.m0_w, self.m0_b, self.m2_w, self.m2_b = t("merger.mlp.0.weight"), t("merger.mlp.0.bias"), t("merger.mlp.2.weight"), t("merger.mlp.2.bias")
         d = cfg.hidden // cfg.heads
         self.inv_freq = 1.0 / (10000.0 ** (torch.arange(0, d // 2, 2, dtype=torch.float32) / (d // 2)))
@@ -126,13 +152,15 @@ class QwenVisionTower:
         fr = torch.cat([rows[:, None].float() * self.inv_freq[None], cols[:, None].float() * self.inv_freq[None]], -1)
         emb = torch.cat([fr, fr], -1).to(self.device)
         cos, sin = emb.cos(), emb.sin()
-        cells = cfg.window // cfg.merge // cfg.patch                         # window side in merged cells
-        win = ((rows // cfg.merge) // cells) * (gw // cfg.merge // cells + 1) + (cols // cfg.merge) // cells
-        wmask = (win[:, None] == win[None, :]).to(self.device)
+        wmask = None
+        if cfg.window > 0:
+            cells = cfg.window // cfg.merge // cfg.patch                     # window side in merged cells
+            win = ((rows // cfg.merge) // cells) * (gw // cfg.merge // cells + 1) + (cols // cfg.merge) // cells
+            wmask = (win[:, None] == win[None, :]).to(self.device)
         for i, blk in enumerate(self.blocks):
-            x = blk(x, cos, sin, None if i in cfg.full_blocks else wmask, cfg.heads, cfg.eps)
+            x = blk(x, cos, sin, None if (i in cfg.full_blocks or wmask is None) else wmask, cfg.heads, cfg.eps)
         g = cfg.merge * cfg.merge
-        y = _rms(x, self.ln_q, cfg.eps).reshape(-1, g * cfg.hidden)
+        y = _norm(x, self.ln_q, self.ln_q_b, cfg.eps).reshape(-1, g * cfg.hidden)
         return F.linear(F.gelu(F.linear(y, self.m0_w, self.m0_b)), self.m2_w, self.m2_b)
 
 

@@ -650,6 +650,50 @@ def _tiny_qwen_vl(tmp_path):
     return hf.to(torch.bfloat16).float(), load_llm(tmp_path / "m", "cpu")
 
 
+def test_qwen2_vl_matches_transformers(tmp_path):
+    """The first Qwen-VL generation (LayerNorm tower, quick-GELU MLP, no windows) against
+    ``Qwen2VLForConditionalGeneration``: vision features and an image prompt's greedy continuation."""
+    tr = pytest.importorskip("transformers")
+    from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLConfig
+    from hartsyinference_b200.engine.llm_engine import LLMEngine, SamplingParams
+    from hartsyinference_b200.models.llm.loader import load_llm, save_hf_checkpoint
+    from hartsyinference_b200.models.vlm.qwen_vl import patchify
+    cfg = Qwen2VLConfig(
+        text_config=dict(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "mrope_section": [4, 6, 6], "rope_theta": 10000.0}),
+        vision_config=dict(depth=2, embed_dim=64, hidden_size=128, num_heads=4, mlp_ratio=2, patch_size=14),
+        image_token_id=318, vision_start_token_id=317, vision_end_token_id=316, video_token_id=315)
+    for c in (cfg, cfg.text_config, cfg.vision_config):
+        c._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = tr.Qwen2VLForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.mul_(2.0)
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()},
+                       tmp_path / "m")
+    hf = hf.to(torch.bfloat16).float()
+    llm = load_llm(tmp_path / "m", "cpu")
+    assert llm.vlm.vision.cfg.legacy
+    image = torch.rand(3, 56, 84, generator=torch.Generator().manual_seed(7))
+    patches, gh, gw = patchify(image, llm.vlm.vision.cfg)
+    with torch.no_grad():
+        ref_feats = hf.model.visual(patches, grid_thw=torch.tensor([[1, gh, gw]])).pooler_output
+    feats = llm.vlm.vision(patches, gh, gw)
+    assert torch.nn.functional.cosine_similarity(feats.float().flatten(), ref_feats.flatten(), dim=0) > 0.99
+    ids, embeds, mask, pos3, delta = llm.vlm.expand_prompt([5, 317, 318, 316, 20, 21, 22], [image])
+    eng = LLMEngine(llm.model, num_pages=32, page_size=16, max_batch=2, prefill_chunk=64, max_model_len=96)
+    rid = eng.add_request(ids, SamplingParams(greedy=True, max_tokens=5), prompt_embeds=embeds, embeds_mask=mask,
+                          positions3=pos3, rope_delta=delta)
+    eng.run_until_done()
+    with torch.no_grad():
+        ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values=patches, image_grid_thw=torch.tensor([[1, gh, gw]]),
+                          max_new_tokens=5, do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
+    assert eng.requests[rid].output[:len(ref)] == ref
+
+
 def test_qwen2_5_vl_matches_transformers(tmp_path):
     """Windowed vision tower + merger + M-RoPE decoder against ``Qwen2_5_VLForConditionalGeneration``
     on a 6 x 8 patch image (3 x 4 merged tokens, two attention windows)."""
