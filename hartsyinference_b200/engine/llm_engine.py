@@ -47,6 +47,7 @@ class Request:
     embeds_mask: Optional[torch.Tensor] = None    # [len(prompt)] bool: rows taken from ``embeds``
     cross_states: Optional[torch.Tensor] = None   # [Tv, hidden] vision states read by cross-attention layers
     positions3: Optional[torch.Tensor] = None     # [3, len(prompt)] int32 time / row / column rotary positions (Qwen-VL)
+    deepstack: Optional[torch.Tensor] = None      # [taps, len(prompt), hidden] added after the first decoder layers (Qwen3-VL)
     rope_delta: int = 0                           # rotary position of a generated token = its index + rope_delta
 
 
@@ -126,7 +127,7 @@ class LLMEngine:
                     on_token: Optional[Callable[[int, int, bool], None]] = None,
                     prompt_embeds: Optional[torch.Tensor] = None, embeds_mask: Optional[torch.Tensor] = None,
                     cross_states: Optional[torch.Tensor] = None, positions3: Optional[torch.Tensor] = None,
-                    rope_delta: int = 0) -> int:
+                    rope_delta: int = 0, deepstack: Optional[torch.Tensor] = None) -> int:
         """``prompt_embeds`` [len(prompt), hidden] with ``embeds_mask`` [len(prompt)] (bool) replaces the
         token embedding of the marked prompt positions (image patches of a vision-language model).
         ``cross_states`` [Tv, hidden] are the vision states this request's cross-attention layers read
@@ -154,6 +155,10 @@ class LLMEngine:
             if positions3.shape != (3, len(prompt)):
                 raise ValueError("positions3 needs shape [3, len(prompt)]")
             req.positions3, req.rope_delta = positions3.to(torch.int32).cpu(), int(rope_delta)
+        if deepstack is not None:
+            if deepstack.shape[1] != len(prompt):
+                raise ValueError("deepstack needs one row per prompt token")
+            req.deepstack = deepstack.to(self.device).to(torch.bfloat16)
         if cross_states is not None:
             req.cross_states = cross_states.to(self.device).to(torch.bfloat16)
         if params.seed is not None and not params.is_greedy:
@@ -234,7 +239,7 @@ class LLMEngine:
                              kv_lens=self._to_device(self.h_kv_lens, n), is_decode=False,
                              cu_q=self._to_device(self.h_cu_q, n + 1), max_q_len=max_q, max_kv_len=max_kv,
                              embeds=embeds, cross_states=self._cross_states([self.requests[rid] for rid, _, _ in chunks]),
-                             positions3=self._positions3(chunks))
+                             positions3=self._positions3(chunks), deepstack=self._deepstack(chunks, t))
         hidden = self.model.forward_hidden(batch)
         done: list[tuple[Request, int]] = []
         fresh = [(row, req) for row, req in sample_rows if not req.output]
@@ -333,6 +338,23 @@ class LLMEngine:
                     p3[:, :end - start] = req.positions3[:, start:end]
             cols.append(p3)
         return torch.cat(cols, 1).to(self.device)
+
+    def _deepstack(self, chunks: list, total: int) -> Optional[torch.Tensor]:
+        """[taps, T, hidden] rows to add after the first decoder layers, for a prefill batch in which
+        some request carries them (zero rows elsewhere)."""
+        have = [self.requests[rid].deepstack for rid, _, _ in chunks if self.requests[rid].deepstack is not None]
+        if not have:
+            return None
+        out = torch.zeros(max(d.shape[0] for d in have), total, have[0].shape[2], dtype=torch.bfloat16, device=self.device)
+        t0 = 0
+        for rid, start, count in chunks:
+            ds = self.requests[rid].deepstack
+            if ds is not None:
+                end = min(start + count, ds.shape[1])
+                if end > start:
+                    out[:ds.shape[0], t0:t0 + end - start] = ds[:, start:end]
+            t0 += count
+        return out
 
     @staticmethod
     def _cross_states(reqs: list) -> Optional[list]:

@@ -171,7 +171,7 @@ class TextService:
             return ids, None, None
         if getattr(llm.vlm, "three_axis_positions", False):   # Qwen-VL: native-resolution patches + three-axis positions
             ids, embeds, mask, pos3, delta = llm.vlm.expand_prompt(ids, [self._unit_image(im) for im in req.images])
-            self._mrope = (pos3, delta)
+            self._mrope = (pos3, delta, llm.vlm.deepstack)
             return ids, embeds, mask
         if hasattr(llm.vlm, "image_features_anyres"):      # any-resolution models take the image at its own size
             return llm.vlm.expand_prompt(ids, [self._unit_image(im) for im in req.images])
@@ -290,12 +290,12 @@ class TextService:
         q: "queue.Queue[tuple[int, bool]]" = queue.Queue()
         t0 = time.perf_counter()
         with h.wake:
-            self._mrope = (None, 0)
+            self._mrope = (None, 0, None)
             ids, embeds, emask = self._multimodal(llm, req, ids)
-            pos3, delta = self._mrope
+            pos3, delta, deepstack = self._mrope
             rid = h.engine.add_request(ids, self._params(req, llm), on_token=lambda r, tok, fin: q.put((tok, fin)),
                                        prompt_embeds=embeds, embeds_mask=emask, cross_states=self._cross_states(llm, req),
-                                       positions3=pos3, rope_delta=delta)
+                                       positions3=pos3, rope_delta=delta, deepstack=deepstack)
             h.wake.notify_all()
         dec = llm.tokenizer.stream_decoder()
         text = ""

@@ -99,6 +99,7 @@ class TransformerConfig:
     nope_global: bool = False           # full-attention layers carry no rotary embedding (Cohere 2)
     lm_head_bias: bool = False          # the output projection has a bias (Phi-1 / Phi-2)
     mrope_section: tuple = ()           # rotary frequency pairs driven by the time / row / column position (Qwen-VL)
+    mrope_interleaved: bool = False     # sections interleaved over the frequency pairs (t h w t h w ...) instead of chunked (Qwen3-VL)
     cross_layers: tuple = ()            # indices of cross-attention layers reading vision states (Mllama)
     qk_norm_after_rope: bool = False    # per-head q/k RMSNorm applied after the rotary embedding (HunYuan)
     attn_sinks: bool = False            # one learned sink logit per head in the attention softmax (gpt-oss)
@@ -222,7 +223,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / mllama (text) / qwen2_vl - qwen2_5_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -288,6 +289,10 @@ def from_hf_config(d: dict) -> TransformerConfig:
             kw["rope_theta"] = kw["rope_theta"] * alpha ** (head_dim / (head_dim - 2))
     if mt in ("qwen2_vl", "qwen2_vl_text", "qwen2_5_vl", "qwen2_5_vl_text"):
         kw.update(qkv_bias=True, mrope_section=tuple(int(v) for v in rs.get("mrope_section") or ()))
+    if mt in ("qwen3_vl", "qwen3_vl_text"):
+        kw.update(qk_norm=True, qkv_bias=bool(d.get("attention_bias", False)),
+                  mrope_section=tuple(int(v) for v in rs.get("mrope_section") or (24, 20, 20)),
+                  mrope_interleaved=bool(rs.get("mrope_interleaved", True)))
     if mt in ("mllama", "mllama_text_model"):
         kw["cross_layers"] = tuple(int(v) for v in d.get("cross_attention_layers") or ())
     if mt == "apertus":       # non-gated xIELU MLP, per-head q/k norm

@@ -324,9 +324,10 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
         lm_get, tower_get = _llava_names(ck)
         model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
         model.load_state_dict(lm_get)
-        if raw.get("model_type") in ("qwen2_5_vl", "qwen2_vl"):
-            from ..vlm.qwen_vl import QwenVisionConfig, QwenVlModel
-            vlm = QwenVlModel(model, QwenVisionConfig.from_hf(raw["vision_config"]), ck.get, int(raw.get("image_token_id", 151655)),
+        if raw.get("model_type") in ("qwen2_5_vl", "qwen2_vl", "qwen3_vl"):
+            from ..vlm.qwen_vl import Qwen3VisionConfig, QwenVisionConfig, QwenVlModel
+            vcfg = (Qwen3VisionConfig if raw["model_type"] == "qwen3_vl" else QwenVisionConfig).from_hf(raw["vision_config"])
+            vlm = QwenVlModel(model, vcfg, ck.get, int(raw.get("image_token_id", 151655)),
                               prefix="model.visual." if ck.get("model.visual.patch_embed.proj.weight") is not None else "visual.")
         elif raw.get("model_type") == "mllama":
             from ..vlm.mllama import MllamaModel, MllamaVisionConfig

@@ -46,6 +46,7 @@ class ForwardBatch:
     logit_rows: Optional[torch.Tensor] = None   # prefill: rows (into T) whose logits are needed
     embeds: Optional[torch.Tensor] = None       # optional precomputed input embeddings [T, H]
     positions3: Optional[torch.Tensor] = None       # Qwen-VL: [3, T] int32 time / row / column positions (None: all = positions)
+    deepstack: Optional[torch.Tensor] = None        # Qwen3-VL: [taps, T, H] added to the hidden states after the first layers
     cross_states: Optional[object] = None           # Mllama: projected vision states [Tv, H] for every row, or a list
                                                     # with one entry (tensor or None) per sequence
     cross_row_mask: Optional[torch.Tensor] = None   # Mllama: [T], 0 for text rows that precede every image
@@ -576,8 +577,13 @@ class DecoderModel:
         packed [T, (hq + 2 hkv) d] activation."""
         cfg, d = self.cfg, self.cfg.head_dim
         t = qkv.shape[0]
-        axis = torch.repeat_interleave(torch.arange(3, device=qkv.device),
-                                       torch.tensor(cfg.mrope_section, device=qkv.device))          # [d / 2]
+        if cfg.mrope_interleaved:         # pair j follows axis j % 3 while that axis has pairs left, else time
+            j = torch.arange(d // 2, device=qkv.device)
+            lim = torch.tensor([0, cfg.mrope_section[1] * 3, cfg.mrope_section[2] * 3], device=qkv.device)
+            axis = torch.where(j < lim[j % 3], j % 3, torch.zeros_like(j))
+        else:
+            axis = torch.repeat_interleave(torch.arange(3, device=qkv.device),
+                                           torch.tensor(cfg.mrope_section, device=qkv.device))      # [d / 2]
         ang = positions3.to(qkv.device).float()[:, :, None] * inv_freq.float()[None, None, :]        # [3, T, d / 2]
         ang = ang.gather(0, axis[None, None, :].expand(1, t, -1))[0]                                 # [T, d / 2]
         cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
@@ -678,6 +684,8 @@ class DecoderModel:
             if lw.post_ffn_norm is not None:
                 f = self._block_norm(f, lw.post_ffn_norm, None)
             x = add(x, f)
+            if batch.deepstack is not None and self.layer0 + li < batch.deepstack.shape[0]:
+                x = (x.float() + batch.deepstack[self.layer0 + li].float()).to(x.dtype)
         if not self.last_stage:
             return x, None
         return self._block_norm(x, self.final_norm, self.final_norm_b)

@@ -66,7 +66,7 @@ def merge_block_coords(gh: int, gw: int, merge: int) -> tuple[torch.Tensor, torc
     return rows, cols
 
 
-def patchify(image: torch.Tensor, cfg: QwenVisionConfig, max_pixels: int = 1280 * 28 * 28) -> tuple[torch.Tensor, int, int]:
+def patchify(image: torch.Tensor, cfg, max_pixels: int = 1280 * 28 * 28) -> tuple[torch.Tensor, int, int]:
     """image [3, H, W] in [0, 1] -> (patches [gh * gw, 3 * temporal * p * p] in merge-block order, gh, gw).
     The image is resized to multiples of ``patch * merge``, CLIP-normalised and repeated along time."""
     from ..encoders.clip_vision import CLIP_MEAN, CLIP_STD
@@ -76,7 +76,10 @@ def patchify(image: torch.Tensor, cfg: QwenVisionConfig, max_pixels: int = 1280 
     scale = min(1.0, (max_pixels / (h * w)) ** 0.5)
     hh, ww = max(unit, round(h * scale / unit) * unit), max(unit, round(w * scale / unit) * unit)
     x = F.interpolate(image[None].float(), size=(hh, ww), mode="bicubic", align_corners=False, antialias=True)[0].clamp(0, 1)
-    x = (x - torch.tensor(CLIP_MEAN).view(3, 1, 1)) / torch.tensor(CLIP_STD).view(3, 1, 1)
+    if isinstance(cfg, Qwen3VisionConfig):                    # Qwen3-VL normalises to [-1, 1]
+        x = (x - 0.5) / 0.5
+    else:
+        x = (x - torch.tensor(CLIP_MEAN).view(3, 1, 1)) / torch.tensor(CLIP_STD).view(3, 1, 1)
     gh, gw = hh // p, ww // p
     x = x[None].expand(tp, 3, hh, ww).reshape(tp, 3, gh // m, m, p, gw // m, m, p)
     x = x.permute(2, 5, 3, 6, 1, 0, 4, 7)                     # block row, block col, in-block row, in-block col, C, T, p, p
@@ -164,6 +167,118 @@ class QwenVisionTower:
         return F.linear(F.gelu(F.linear(y, self.m0_w, self.m0_b)), self.m2_w, self.m2_b)
 
 
+@dataclass(frozen=True)
+class Qwen3VisionConfig:
+    hidden: int = 1152
+    heads: int = 16
+    ffn: int = 4304
+    depth: int = 27
+    out_hidden: int = 3584
+    patch: int = 16
+    temporal_patch: int = 2
+    merge: int = 2
+    num_positions: int = 2304
+    deepstack: tuple = (8, 16, 24)
+    eps: float = 1e-6
+    window: int = 0
+
+    @staticmethod
+    def from_hf(d: dict) -> "Qwen3VisionConfig":
+        return Qwen3VisionConfig(hidden=d.get("hidden_size", 1152), heads=d.get("num_heads", 16), ffn=d.get("intermediate_size", 4304),
+                                 depth=d.get("depth", 27), out_hidden=d.get("out_hidden_size", 3584), patch=d.get("patch_size", 16),
+                                 temporal_patch=d.get("temporal_patch_size", 2), merge=d.get("spatial_merge_size", 2),
+                                 num_positions=d.get("num_position_embeddings", 2304),
+                                 deepstack=tuple(d.get("deepstack_visual_indexes") or ()))
+
+
+class _Merger3:
+    """LayerNorm (before or after the 2x2 blocks are concatenated) -> Linear -> GELU -> Linear."""
+
+    def __init__(self, t: Callable, p: str, post_shuffle: bool):
+        self.nw, self.nb = t(p + "norm.weight"), t(p + "norm.bias")
+        self.w1, self.b1, self.w2, self.b2 = t(p + "linear_fc1.weight"), t(p + "linear_fc1.bias"), t(p + "linear_fc2.weight"), t(p + "linear_fc2.bias")
+        self.post_shuffle = post_shuffle
+
+    def __call__(self, x: torch.Tensor, group: int, eps: float) -> torch.Tensor:
+        wide = x.shape[-1] * group
+        y = _norm(x.reshape(-1, wide), self.nw, self.nb, eps) if self.post_shuffle else _norm(x, self.nw, self.nb, eps).reshape(-1, wide)
+        return F.linear(F.gelu(F.linear(y, self.w1, self.b1)), self.w2, self.b2)
+
+
+class Qwen3VisionTower:
+    """Qwen3-VL tower: patch embedding with bias + a learned position table interpolated bilinearly to
+    the image's grid, LayerNorm / tanh-GELU blocks with the 2-D rotary embedding and full attention,
+    the merger, and "deepstack" mergers that tap the blocks in ``cfg.deepstack``; their outputs are
+    added to the decoder's hidden states at the image rows after its first layers."""
+
+    def __init__(self, cfg: Qwen3VisionConfig, get: Callable[[str], Optional[torch.Tensor]], device="cpu",
+                 dtype: torch.dtype = torch.bfloat16, prefix: str = "model.visual."):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+
+        def t(n):
+            w = get(prefix + n)
+            if w is None:
+                raise KeyError(f"missing tensor {prefix + n}")
+            return w.to(dtype).to(self.device)
+
+        self.patch_w, self.patch_b = t("patch_embed.proj.weight").reshape(cfg.hidden, -1), t("patch_embed.proj.bias")
+        self.pos = t("pos_embed.weight")
+        self.blocks = []
+        for i in range(cfg.depth):
+            p = f"blocks.{i}."
+            self.blocks.append(dict(n1=t(p + "norm1.weight"), n1b=t(p + "norm1.bias"), n2=t(p + "norm2.weight"), n2b=t(p + "norm2.bias"),
+                                    qkv=t(p + "attn.qkv.weight"), qkvb=t(p + "attn.qkv.bias"), proj=t(p + "attn.proj.weight"),
+                                    projb=t(p + "attn.proj.bias"), f1=t(p + "mlp.linear_fc1.weight"), f1b=t(p + "mlp.linear_fc1.bias"),
+                                    f2=t(p + "mlp.linear_fc2.weight"), f2b=t(p + "mlp.linear_fc2.bias")))
+        self.merger = _Merger3(t, "merger.", False)
+        self.deep = [_Merger3(t, f"deepstack_merger_list.{i}.", True) for i in range(len(cfg.deepstack))]
+        d = cfg.hidden // cfg.heads
+        self.inv_freq = 1.0 / (10000.0 ** (torch.arange(0, d // 2, 2, dtype=torch.float32) / (d // 2)))
+
+    def _positions(self, gh: int, gw: int) -> torch.Tensor:
+        """The side x side position table sampled bilinearly on a gh x gw grid, in merge-block order."""
+        side = int(self.cfg.num_positions ** 0.5)
+        hi, wi = torch.linspace(0, side - 1, gh), torch.linspace(0, side - 1, gw)
+        h0, w0 = hi.int(), wi.int()
+        h1, w1 = (h0 + 1).clamp(max=side - 1), (w0 + 1).clamp(max=side - 1)
+        dh, dw = (hi - h0)[:, None], (wi - w0)[None, :]
+        tab = self.pos.float().cpu()
+        at = lambda a, b: tab[(a[:, None] * side + b[None, :]).long().flatten()].reshape(gh, gw, -1)
+        out = (at(h0, w0) * ((1 - dh) * (1 - dw))[..., None] + at(h0, w1) * ((1 - dh) * dw)[..., None]
+               + at(h1, w0) * (dh * (1 - dw))[..., None] + at(h1, w1) * (dh * dw)[..., None])
+        m = self.cfg.merge
+        out = out.reshape(gh // m, m, gw // m, m, -1).permute(0, 2, 1, 3, 4).reshape(gh * gw, -1)
+        return out.to(self.dtype).to(self.device)
+
+    @torch.no_grad()
+    def __call__(self, patches: torch.Tensor, gh: int, gw: int) -> tuple[torch.Tensor, list[torch.Tensor]]:
+        """-> (merged tokens [gh * gw / merge^2, out_hidden], one tensor of the same shape per deepstack tap)."""
+        cfg = self.cfg
+        x = F.linear(patches.to(self.device, self.dtype), self.patch_w, self.patch_b) + self._positions(gh, gw)
+        rows, cols = merge_block_coords(gh, gw, cfg.merge)
+        fr = torch.cat([rows[:, None].float() * self.inv_freq[None], cols[:, None].float() * self.inv_freq[None]], -1)
+        emb = torch.cat([fr, fr], -1).to(self.device)
+        cos, sin = emb.cos()[:, None], emb.sin()[:, None]
+        n, c = x.shape
+        d = c // cfg.heads
+        g = cfg.merge * cfg.merge
+
+        def rot(u):
+            uf = u.float()
+            return (uf * cos + torch.cat([-uf[..., d // 2:], uf[..., : d // 2]], -1) * sin).to(u.dtype)
+
+        taps = []
+        for i, b in enumerate(self.blocks):
+            q, k, v = F.linear(_norm(x, b["n1"], b["n1b"], cfg.eps), b["qkv"], b["qkvb"]).reshape(n, 3, cfg.heads, d).unbind(1)
+            a = F.scaled_dot_product_attention(rot(q).transpose(0, 1)[None], rot(k).transpose(0, 1)[None], v.transpose(0, 1)[None])[0]
+            x = x + F.linear(a.transpose(0, 1).reshape(n, c), b["proj"], b["projb"])
+            h = _norm(x, b["n2"], b["n2b"], cfg.eps)
+            x = x + F.linear(F.gelu(F.linear(h, b["f1"], b["f1b"]), approximate="tanh"), b["f2"], b["f2b"])
+            if i in cfg.deepstack:
+                taps.append(self.deep[cfg.deepstack.index(i)](x, g, cfg.eps))
+        return self.merger(x, g, cfg.eps), taps
+
+
 def mrope_positions(ids: Sequence[int], image_token_id: int, grids: Sequence[tuple[int, int]]) -> tuple[torch.Tensor, int]:
     """Three-axis positions [3, len(ids)] (time, row, column) and the offset to add to the sequence
     index for every token generated afterwards. Text advances all three axes together; the tokens
@@ -194,19 +309,25 @@ def mrope_positions(ids: Sequence[int], image_token_id: int, grids: Sequence[tup
 
 class QwenVlModel:
     """Decoder + vision tower. ``expand_prompt`` turns a prompt with one image token per image into
-    (ids, embeds, mask, positions3, rope_delta) for the engine."""
+    (ids, embeds, mask, positions3, rope_delta) for the engine; a Qwen3-VL tower also leaves the
+    deepstack rows of that prompt in ``self.deepstack`` ([taps, len(ids), hidden], else None)."""
 
     three_axis_positions = True
+    deepstack: Optional[torch.Tensor] = None
 
-    def __init__(self, decoder, cfg: QwenVisionConfig, get: Callable[[str], Optional[torch.Tensor]], image_token_id: int,
+    def __init__(self, decoder, cfg, get: Callable[[str], Optional[torch.Tensor]], image_token_id: int,
                  prefix: str = "model.visual."):
         self.decoder, self.image_token_id = decoder, image_token_id
-        self.vision = QwenVisionTower(cfg, get, decoder.device, torch.bfloat16, prefix)
+        tower = Qwen3VisionTower if isinstance(cfg, Qwen3VisionConfig) else QwenVisionTower
+        self.vision = tower(cfg, get, decoder.device, torch.bfloat16, prefix)
 
-    def image_features(self, image: torch.Tensor) -> tuple[torch.Tensor, int, int]:
+    def image_features(self, image: torch.Tensor) -> tuple[torch.Tensor, int, int, list]:
+        """(merged tokens, merged rows, merged columns, deepstack taps)."""
         patches, gh, gw = patchify(image, self.vision.cfg)
         m = self.vision.cfg.merge
-        return self.vision(patches, gh, gw), gh // m, gw // m
+        out = self.vision(patches, gh, gw)
+        feats, taps = out if isinstance(out, tuple) else (out, [])
+        return feats, gh // m, gw // m, taps
 
     def expand_prompt(self, ids: Sequence[int], images: Sequence[torch.Tensor]):
         feats = [self.image_features(im) for im in images]
@@ -227,5 +348,11 @@ class QwenVlModel:
         embeds = torch.zeros(len(out), hidden, dtype=torch.bfloat16, device=self.decoder.device)
         if rows:
             embeds[mask.to(embeds.device)] = torch.cat(rows, 0).to(embeds.dtype)
-        pos3, delta = mrope_positions(out, self.image_token_id, [(r, c) for _, r, c in feats])
+        pos3, delta = mrope_positions(out, self.image_token_id, [(r, c) for _, r, c, _ in feats])
+        self.deepstack = None
+        if feats and feats[0][3]:
+            # [taps, len(ids), hidden]: every tap's tokens at the image rows, zero at the text rows
+            self.deepstack = torch.zeros(len(feats[0][3]), len(out), hidden, dtype=torch.bfloat16, device=self.decoder.device)
+            for li in range(self.deepstack.shape[0]):
+                self.deepstack[li][mask.to(embeds.device)] = torch.cat([f[3][li] for f in feats], 0).to(torch.bfloat16)
         return out, embeds, mask, pos3, delta

@@ -766,3 +766,63 @@ def test_qwen2_5_vl_engine_generation_follows_transformers(tmp_path):
         ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values=patches, image_grid_thw=torch.tensor([[1, gh, gw]]),
                           max_new_tokens=6, do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
     assert out[:len(ref)] == ref
+
+
+def test_qwen3_vl_matches_transformers(tmp_path):
+    """Qwen3-VL: interpolated position table, deepstack taps added after the first decoder layers,
+    interleaved three-axis rotary sections, against ``Qwen3VLForConditionalGeneration`` (vision
+    features, deepstack features and the greedy continuation of an image prompt through the engine)."""
+    tr = pytest.importorskip("transformers")
+    if not hasattr(tr, "Qwen3VLForConditionalGeneration"):
+        pytest.skip("transformers has no Qwen3-VL")
+    from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLConfig
+    from hartsyinference_b200.engine.llm_engine import LLMEngine, SamplingParams
+    from hartsyinference_b200.models.llm.loader import load_llm, save_hf_checkpoint
+    from hartsyinference_b200.models.vlm.qwen_vl import patchify
+    cfg = Qwen3VLConfig(
+        text_config=dict(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "mrope_section": [6, 5, 5], "mrope_interleaved": True,
+                                          "rope_theta": 10000.0}),
+        vision_config=dict(depth=3, hidden_size=64, intermediate_size=96, num_heads=4, out_hidden_size=128, patch_size=16,
+                           spatial_merge_size=2, temporal_patch_size=2, num_position_embeddings=16, deepstack_visual_indexes=[0, 2]),
+        image_token_id=318, vision_start_token_id=317, vision_end_token_id=316, video_token_id=315)
+    for c in (cfg, cfg.text_config, cfg.vision_config):
+        c._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = tr.Qwen3VLForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.mul_(2.0)
+    save_hf_checkpoint(cfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()},
+                       tmp_path / "m")
+    hf = hf.to(torch.bfloat16).float()
+    llm = load_llm(tmp_path / "m", "cpu")
+    assert llm.config.mrope_interleaved and llm.config.qk_norm
+    image = torch.rand(3, 64, 96, generator=torch.Generator().manual_seed(8))
+    patches, gh, gw = patchify(image, llm.vlm.vision.cfg)
+    assert (gh, gw) == (4, 6)
+    with torch.no_grad():
+        ref_out = hf.model.visual(patches, grid_thw=torch.tensor([[1, gh, gw]]))
+    feats, taps = llm.vlm.vision(patches, gh, gw)
+    cos = torch.nn.functional.cosine_similarity
+    assert cos(feats.float().flatten(), ref_out.pooler_output.flatten(), dim=0) > 0.99
+    assert len(taps) == 2
+    for mine, ref in zip(taps, ref_out.deepstack_features):
+        assert cos(mine.float().flatten(), ref.flatten(), dim=0) > 0.99
+    ids, embeds, mask, pos3, delta = llm.vlm.expand_prompt([5, 317, 318, 316, 20, 21, 22], [image])
+    assert llm.vlm.deepstack.shape == (2, len(ids), 128)
+    outs = []
+    for chunk in (64, 4):                                        # one-shot and chunked prefill
+        eng = LLMEngine(llm.model, num_pages=32, page_size=16, max_batch=2, prefill_chunk=chunk, max_model_len=96)
+        rid = eng.add_request(ids, SamplingParams(greedy=True, max_tokens=5), prompt_embeds=embeds, embeds_mask=mask,
+                              positions3=pos3, rope_delta=delta, deepstack=llm.vlm.deepstack)
+        eng.run_until_done()
+        outs.append(eng.requests[rid].output)
+    assert outs[0] == outs[1]
+    with torch.no_grad():
+        ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values=patches, image_grid_thw=torch.tensor([[1, gh, gw]]),
+                          mm_token_type_ids=torch.tensor([[1 if t == 318 else 0 for t in ids]]),
+                          max_new_tokens=5, do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
+    assert outs[0][:len(ref)] == ref
