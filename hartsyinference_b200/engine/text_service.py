@@ -195,7 +195,7 @@ class TextService:
         return t.float().clamp(0, 1)
 
     # ------------------------------------------------------------------------------ recurrent models
-    SSM_TYPES = ("mamba", "mamba2", "rwkv")
+    SSM_TYPES = ("mamba", "falcon_mamba", "mamba2", "rwkv")
 
     def _ssm_kind(self, spec: ModelSpec) -> Optional[str]:
         import json
@@ -224,8 +224,9 @@ class TextService:
             if key not in self._ssm:
                 raw = json.loads((path / "config.json").read_text())
                 get = ShardedCheckpoint(path).get
-                if kind == "mamba":
-                    cfg = S.MambaConfig(vocab_size=raw["vocab_size"], d_model=raw["hidden_size"], n_layer=raw["num_hidden_layers"],
+                if kind in ("mamba", "falcon_mamba"):
+                    cfg = S.MambaConfig(bcdt_rms_eps=float(raw.get("mixer_rms_eps", 1e-6)) if kind == "falcon_mamba" else 0.0,
+                                        vocab_size=raw["vocab_size"], d_model=raw["hidden_size"], n_layer=raw["num_hidden_layers"],
                                         d_state=raw.get("state_size", 16), d_conv=raw.get("conv_kernel", 4), expand=raw.get("expand", 2),
                                         dt_rank=raw["time_step_rank"] if isinstance(raw.get("time_step_rank"), int) else 0,
                                         rms_eps=raw.get("layer_norm_epsilon", 1e-5), eos_token_id=raw.get("eos_token_id", 0) or 0)

@@ -34,6 +34,7 @@ class MambaConfig:
     dt_rank: int = 0                 # 0 = ceil(d_model / 16)
     rms_eps: float = 1e-5
     eos_token_id: int = 0
+    bcdt_rms_eps: float = 0.0        # > 0: weight-free RMS normalisation of dt, B and C after x_proj (FalconMamba)
 
     @property
     def d_inner(self) -> int:
@@ -147,9 +148,14 @@ class MambaModel:
         win = seq.unfold(0, k, 1)                                        # [T, Di, k]
         xc = F.silu((win * lw.conv_w[None]).sum(-1) + lw.conv_b).to(h.dtype)
         dbc = ops.linear(xc.contiguous(), lw.x_proj)                     # [T, r + 2 N]
-        dt = F.softplus(ops.linear(dbc[:, :r].contiguous(), lw.dt_proj).float())
-        y = selective_scan(xc.contiguous(), dt.contiguous(), lw.a, dbc[:, r:r + n].contiguous(),
-                           dbc[:, r + n:].contiguous(), lw.d, ssm_state)
+        dt_in, b_in, c_in = dbc[:, :r], dbc[:, r:r + n], dbc[:, r + n:]
+        if cfg.bcdt_rms_eps > 0:
+            def rms(u, count):           # the padded dt columns are zero: divide by the real width
+                uf = u.float()
+                return (uf * torch.rsqrt(uf.pow(2).sum(-1, keepdim=True) / count + cfg.bcdt_rms_eps)).to(u.dtype)
+            dt_in, b_in, c_in = rms(dt_in, cfg.rank), rms(b_in, n), rms(c_in, n)
+        dt = F.softplus(ops.linear(dt_in.contiguous(), lw.dt_proj).float())
+        y = selective_scan(xc.contiguous(), dt.contiguous(), lw.a, b_in.contiguous(), c_in.contiguous(), lw.d, ssm_state)
         y = (y.float() * F.silu(z.float())).to(h.dtype)
         return ops.linear(y.contiguous(), lw.out_proj)
 

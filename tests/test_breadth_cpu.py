@@ -259,6 +259,30 @@ def test_mamba_matches_transformers_and_state_carries_over():
     assert len(out) == 6
 
 
+def test_falcon_mamba_matches_transformers():
+    """FalconMamba = Mamba with a weight-free RMS normalisation of dt, B and C."""
+    import transformers
+    from dataclasses import replace
+    from hartsyinference_b200.models.ssm import MambaModel, tiny_mamba
+    cfg = replace(tiny_mamba(), bcdt_rms_eps=1e-6)
+    hf_cfg = transformers.FalconMambaConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.d_model, state_size=cfg.d_state,
+                                            num_hidden_layers=cfg.n_layer, conv_kernel=cfg.d_conv, expand=cfg.expand,
+                                            time_step_rank=cfg.rank, layer_norm_epsilon=cfg.rms_eps, mixer_rms_eps=1e-6,
+                                            use_falcon_mambapy=False)
+    torch.manual_seed(0)
+    hf = transformers.FalconMambaForCausalLM(hf_cfg).eval()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    m = MambaModel(cfg, "cpu", get=lambda n: sd.get(n))
+    ids = torch.randint(0, cfg.vocab_size, (19,))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    ours = m.logits(m.forward(ids, m.new_state()))
+    assert torch.nn.functional.cosine_similarity(ours, ref, dim=-1).min() > 0.99
+    plain = MambaModel(tiny_mamba(), "cpu", get=lambda n: sd.get(n))
+    off = plain.logits(plain.forward(ids, plain.new_state()))
+    assert torch.nn.functional.cosine_similarity(off, ref, dim=-1).min() < 0.99      # the normalisation matters
+
+
 def test_block_streamer_walks_blocks_with_two_slots():
     from dataclasses import dataclass
     from hartsyinference_b200.engine.block_streaming import BlockStreamer, tree_bytes
