@@ -439,3 +439,44 @@ def test_xlm_roberta_embeddings_match_transformers(tmp_path):
     emb = eng.embeddings.embed(ModelSpec(str(d)), ["hello world", "goodbye"])
     assert emb.shape == (2, 128) and torch.allclose(emb.norm(dim=-1), torch.ones(2), atol=1e-3)
     eng.close()
+
+
+def test_qwen35_hybrid_matches_transformers_and_state_carries_over():
+    """Gated-DeltaNet + gated-attention hybrid against ``Qwen3_5ForCausalLM``: logits of a prompt,
+    the same prompt fed in two pieces through the carried state, and the greedy continuation."""
+    import transformers
+    if not hasattr(transformers, "Qwen3_5ForCausalLM"):
+        pytest.skip("transformers has no Qwen3.5")
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig
+    from hartsyinference_b200.models.ssm import Qwen35Model, qwen35_from_hf
+    hf_cfg = Qwen3_5TextConfig(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4,
+                               num_key_value_heads=2, head_dim=32, linear_conv_kernel_dim=4, linear_key_head_dim=16,
+                               linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4,
+                               max_position_embeddings=256, pad_token_id=0)
+    hf_cfg._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = transformers.Qwen3_5ForCausalLM(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2:
+                p.mul_(2.0)
+            elif "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    cfg = qwen35_from_hf(hf_cfg.to_dict())
+    assert cfg.layer_types == ("linear_attention",) * 3 + ("full_attention",) and cfg.rot == 8
+    m = Qwen35Model(cfg, "cpu", get=lambda n: sd.get(n), dtype=torch.float32)
+    ids = torch.randint(0, 320, (21,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    st = m.new_state()
+    ours = m.logits(m.forward(ids, st))
+    cos = torch.nn.functional.cosine_similarity(ours, ref, dim=-1)
+    assert cos.min() > 0.999, cos.min()
+    st2 = m.new_state()
+    m.forward(ids[:9], st2)
+    tail = m.logits(m.forward(ids[9:], st2))
+    assert torch.allclose(tail[-1], ours[-1], atol=1e-3, rtol=1e-3)
+    with torch.no_grad():
+        gen = hf.generate(ids[None, :7], max_new_tokens=6, do_sample=False, pad_token_id=0)[0, 7:].tolist()
+    assert m.generate(ids[:7].tolist(), max_tokens=6, stop_at_eos=False) == gen
