@@ -220,3 +220,33 @@ def test_qwen_vl_three_axis_rotary_on_device_matches_cpu(tmp_path):
         outs[dev] = (embeds.float().cpu(), eng.requests[rid].output)
     assert torch.nn.functional.cosine_similarity(outs["cpu"][0].flatten(), outs["cuda"][0].flatten(), dim=0) > 0.99
     assert len(outs["cuda"][1]) == 4 and outs["cuda"][1][0] == outs["cpu"][1][0]
+
+
+def test_qwen35_hybrid_on_device_matches_cpu():
+    """Qwen3.5 hybrid (gated DeltaNet + gated attention) on the device GEMM / GLU kernels against the CPU path."""
+    tr = pytest.importorskip("transformers")
+    if not hasattr(tr, "Qwen3_5ForCausalLM"):
+        pytest.skip("transformers has no Qwen3.5")
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig
+    from hartsyinference_b200.models.ssm import Qwen35Model, qwen35_from_hf
+    hf_cfg = Qwen3_5TextConfig(vocab_size=320, hidden_size=256, intermediate_size=512, num_hidden_layers=4, num_attention_heads=4,
+                               num_key_value_heads=2, head_dim=64, linear_conv_kernel_dim=4, linear_key_head_dim=32,
+                               linear_value_head_dim=32, linear_num_key_heads=4, linear_num_value_heads=8,
+                               max_position_embeddings=256, pad_token_id=0)
+    torch.manual_seed(0)
+    hf = tr.Qwen3_5ForCausalLM(hf_cfg)
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.mul_(2.0)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    cfg = qwen35_from_hf(hf_cfg.to_dict())
+    ids = torch.randint(0, 320, (24,), generator=torch.Generator().manual_seed(1))
+    outs = []
+    for dev in ("cpu", "cuda"):
+        m = Qwen35Model(cfg, dev, get=lambda n: sd.get(n))
+        st = m.new_state()
+        m.forward(ids[:16], st)
+        outs.append(m.logits(m.forward(ids[16:], st)).float().cpu())
+    cos = torch.nn.functional.cosine_similarity(outs[0].flatten(), outs[1].flatten(), dim=0)
+    assert cos > 0.99, f"cos {cos:.4f}"
