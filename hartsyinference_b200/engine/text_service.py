@@ -195,7 +195,7 @@ class TextService:
         return t.float().clamp(0, 1)
 
     # ------------------------------------------------------------------------------ recurrent models
-    SSM_TYPES = ("mamba", "falcon_mamba", "mamba2", "rwkv", "qwen3_5", "qwen3_5_text")
+    SSM_TYPES = ("mamba", "falcon_mamba", "mamba2", "rwkv", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text")
 
     def _ssm_kind(self, spec: ModelSpec) -> Optional[str]:
         import json
@@ -233,7 +233,7 @@ class TextService:
                     model = S.MambaModel(cfg, self.device, get=get)
                 elif kind == "mamba2":
                     model = S.Mamba2Model(S.mamba2_from_hf(raw), self.device, get=get)
-                elif kind in ("qwen3_5", "qwen3_5_text"):
+                elif kind.startswith("qwen3_5"):
                     ck = ShardedCheckpoint(path)
                     nested = ck.get("model.language_model.embed_tokens.weight") is not None     # image-text checkpoints nest the decoder
                     get35 = (lambda n: ck.get(n.replace("model.", "model.language_model.", 1))) if nested else ck.get

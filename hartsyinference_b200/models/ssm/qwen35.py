@@ -8,7 +8,8 @@ Gated DeltaNet layer, per value head with state S [dk, dv]:
     y   = out_proj(rmsnorm(o) * w * silu(in_proj_z(x)))
 Full-attention layer: q_proj gives a query and an output gate per head; per-head RMSNorm (1 + w) on
 q / k, rotary embedding on the first quarter of the head, causal attention, output * sigmoid(gate).
-Every norm multiplies by (1 + w).
+Every norm multiplies by (1 + w). The MoE variant replaces every feed-forward by top-k routed
+experts (softmax scores renormalised over the chosen k) plus a shared expert scaled by sigmoid(x . w).
 
 State per sequence: conv tail [conv_dim, k - 1] and S per linear layer, K / V grown per attention
 layer. The recurrence runs token by token in tensor ops (the recurrent form; no chunked kernel), so
@@ -49,6 +50,10 @@ class Qwen35Config:
     rotary_factor: float = 0.25
     tie_embeddings: bool = False
     eos_token_id: int = 0
+    experts: int = 0                 # > 0: every feed-forward is top-k routed experts + a sigmoid-gated shared expert
+    top_k: int = 0
+    expert_ffn: int = 0
+    shared_ffn: int = 0
 
     @property
     def rot(self) -> int:
@@ -61,7 +66,7 @@ def qwen35_from_hf(d: dict) -> Qwen35Config:
     n = d["num_hidden_layers"]
     types = tuple(d.get("layer_types") or ["full_attention" if (i + 1) % 4 == 0 else "linear_attention" for i in range(n)])
     eos = d.get("eos_token_id", 0)
-    return Qwen35Config(vocab_size=d["vocab_size"], hidden=d["hidden_size"], ffn=d["intermediate_size"], layers=n,
+    return Qwen35Config(vocab_size=d["vocab_size"], hidden=d["hidden_size"], ffn=int(d.get("intermediate_size") or 0), layers=n,
                         heads=d["num_attention_heads"], kv_heads=d.get("num_key_value_heads") or d["num_attention_heads"],
                         head_dim=d.get("head_dim") or d["hidden_size"] // d["num_attention_heads"],
                         lin_k_heads=d.get("linear_num_key_heads", 16), lin_v_heads=d.get("linear_num_value_heads", 32),
@@ -70,6 +75,9 @@ def qwen35_from_hf(d: dict) -> Qwen35Config:
                         rope_theta=float(rp.get("rope_theta") or d.get("rope_theta") or 1e7),
                         rotary_factor=float(rp.get("partial_rotary_factor") or d.get("partial_rotary_factor") or 0.25),
                         tie_embeddings=bool(d.get("tie_word_embeddings", False)),
+                        experts=int(d.get("num_experts") or 0), top_k=int(d.get("num_experts_per_tok") or 0),
+                        expert_ffn=int(d.get("moe_intermediate_size") or 0),
+                        shared_ffn=int(d.get("shared_expert_intermediate_size") or 0),
                         eos_token_id=(eos[0] if isinstance(eos, (list, tuple)) else eos) or 0)
 
 
@@ -108,9 +116,15 @@ class Qwen35Model:
         self.layers = []
         for i in range(cfg.layers):
             p = f"model.layers.{i}."
-            lw = dict(kind=cfg.layer_types[i], n1=t(p + "input_layernorm.weight"), n2=t(p + "post_attention_layernorm.weight"),
-                      gate_up=LinearWeight(torch.cat([t(p + "mlp.gate_proj.weight"), t(p + "mlp.up_proj.weight")]).contiguous()),
-                      down=lin(p + "mlp.down_proj.weight"))
+            lw = dict(kind=cfg.layer_types[i], n1=t(p + "input_layernorm.weight"), n2=t(p + "post_attention_layernorm.weight"))
+            if cfg.experts > 0:
+                m = p + "mlp."
+                lw.update(router=t(m + "gate.weight", torch.float32), e_gate_up=t(m + "experts.gate_up_proj"), e_down=t(m + "experts.down_proj"),
+                          gate_up=LinearWeight(torch.cat([t(m + "shared_expert.gate_proj.weight"), t(m + "shared_expert.up_proj.weight")]).contiguous()),
+                          down=lin(m + "shared_expert.down_proj.weight"), shared_gate=t(m + "shared_expert_gate.weight", torch.float32))
+            else:
+                lw.update(gate_up=LinearWeight(torch.cat([t(p + "mlp.gate_proj.weight"), t(p + "mlp.up_proj.weight")]).contiguous()),
+                          down=lin(p + "mlp.down_proj.weight"))
             if lw["kind"] == "linear_attention":
                 a = p + "linear_attn."
                 lw.update(qkv=lin(a + "in_proj_qkv.weight"), z=lin(a + "in_proj_z.weight"),
@@ -184,6 +198,25 @@ class Qwen35Model:
         a = (a.float() * torch.sigmoid(gate.float())).to(h.dtype)
         return ops.linear(a.contiguous(), lw["o"])
 
+    def _ffn(self, lw: dict, h: torch.Tensor) -> torch.Tensor:
+        act, _ = ops.glu(ops.linear(h, lw["gate_up"]), "silu")
+        y = ops.linear(act, lw["down"])
+        if self.cfg.experts <= 0:
+            return y
+        # shared expert scaled by sigmoid(x . w), plus the top-k experts weighted by their renormalised softmax scores
+        out = y.float() * torch.sigmoid(h.float() @ lw["shared_gate"].t())
+        probs = torch.softmax(h.float() @ lw["router"].t(), -1)
+        top, idx = torch.topk(probs, self.cfg.top_k, -1)
+        top = top / top.sum(-1, keepdim=True)
+        for e in idx.unique().tolist():
+            rows, slot = (idx == e).nonzero(as_tuple=True)
+            xe = h[rows]
+            gu = xe @ lw["e_gate_up"][e].t()
+            f = gu.shape[1] // 2
+            ye = (F.silu(gu[:, :f].float()) * gu[:, f:].float()).to(h.dtype) @ lw["e_down"][e].t()
+            out.index_add_(0, rows, ye.float() * top[rows, slot][:, None])
+        return out.to(h.dtype)
+
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, state: Qwen35State) -> torch.Tensor:
         """tokens [T] appended to the sequence held in ``state`` -> final-normed hidden states [T, H]."""
@@ -196,8 +229,7 @@ class Qwen35Model:
             a = self._delta(lw, li, h, state) if lw["kind"] == "linear_attention" else self._attn(lw, li, h, state, pos)
             x = (x.float() + a.float()).to(x.dtype)
             h = _rms1(x, lw["n2"], cfg.rms_eps)
-            act, _ = ops.glu(ops.linear(h, lw["gate_up"]), "silu")
-            x = (x.float() + ops.linear(act, lw["down"]).float()).to(x.dtype)
+            x = (x.float() + self._ffn(lw, h).float()).to(x.dtype)
         state.length += tokens.numel()
         return _rms1(x, self.final_norm, cfg.rms_eps)
 

@@ -480,3 +480,31 @@ def test_qwen35_hybrid_matches_transformers_and_state_carries_over():
     with torch.no_grad():
         gen = hf.generate(ids[None, :7], max_new_tokens=6, do_sample=False, pad_token_id=0)[0, 7:].tolist()
     assert m.generate(ids[:7].tolist(), max_tokens=6, stop_at_eos=False) == gen
+
+
+def test_qwen35_moe_matches_transformers():
+    import transformers
+    if not hasattr(transformers, "Qwen3_5MoeForCausalLM"):
+        pytest.skip("transformers has no Qwen3.5-MoE")
+    from transformers.models.qwen3_5_moe.configuration_qwen3_5_moe import Qwen3_5MoeTextConfig
+    from hartsyinference_b200.models.ssm import Qwen35Model, qwen35_from_hf
+    hf_cfg = Qwen3_5MoeTextConfig(vocab_size=320, hidden_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                                  head_dim=32, linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=2,
+                                  linear_num_value_heads=4, moe_intermediate_size=64, shared_expert_intermediate_size=96,
+                                  num_experts=4, num_experts_per_tok=2, max_position_embeddings=256, pad_token_id=0)
+    hf_cfg._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = transformers.Qwen3_5MoeForCausalLM(hf_cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.mul_(2.0)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    cfg = qwen35_from_hf(hf_cfg.to_dict())
+    assert cfg.experts == 4 and cfg.top_k == 2
+    m = Qwen35Model(cfg, "cpu", get=lambda n: sd.get(n), dtype=torch.float32)
+    ids = torch.randint(0, 320, (17,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(input_ids=ids[None]).logits[0]
+    ours = m.logits(m.forward(ids, m.new_state()))
+    assert torch.nn.functional.cosine_similarity(ours, ref, dim=-1).min() > 0.999
