@@ -141,10 +141,15 @@ class TextService:
         if not req.images or llm.vlm is None:
             return llm.tokenizer.encode(text, add_special=special)
         # the text around each "<image>" is tokenised by itself, with the image token id between
+        # (Qwen-VL brackets it with its vision-start / vision-end tokens); a prompt with images but no
+        # placeholder gets them in front
+        marker = [*getattr(llm.vlm, "image_prefix_ids", ()), llm.vlm.image_token_id, *getattr(llm.vlm, "image_suffix_ids", ())]
+        if "<image>" not in text:
+            text = "<image>" * len(req.images) + text
         ids: list[int] = []
         for i, piece in enumerate(text.split("<image>")):
             if i:
-                ids.append(llm.vlm.image_token_id)
+                ids += marker
             if piece:
                 ids += llm.tokenizer.encode(piece, add_special=special and i == 0)
         return ids

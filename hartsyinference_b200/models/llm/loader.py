@@ -328,7 +328,8 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
             from ..vlm.qwen_vl import Qwen3VisionConfig, QwenVisionConfig, QwenVlModel
             vcfg = (Qwen3VisionConfig if raw["model_type"] == "qwen3_vl" else QwenVisionConfig).from_hf(raw["vision_config"])
             vlm = QwenVlModel(model, vcfg, ck.get, int(raw.get("image_token_id", 151655)),
-                              prefix="model.visual." if ck.get("model.visual.patch_embed.proj.weight") is not None else "visual.")
+                              prefix="model.visual." if ck.get("model.visual.patch_embed.proj.weight") is not None else "visual.",
+                              vision_start_id=raw.get("vision_start_token_id"), vision_end_id=raw.get("vision_end_token_id"))
         elif raw.get("model_type") == "mllama":
             from ..vlm.mllama import MllamaModel, MllamaVisionConfig
             new = ck.get("model.language_model.embed_tokens.weight") is not None

@@ -316,8 +316,10 @@ class QwenVlModel:
     deepstack: Optional[torch.Tensor] = None
 
     def __init__(self, decoder, cfg, get: Callable[[str], Optional[torch.Tensor]], image_token_id: int,
-                 prefix: str = "model.visual."):
+                 prefix: str = "model.visual.", vision_start_id: Optional[int] = None, vision_end_id: Optional[int] = None):
         self.decoder, self.image_token_id = decoder, image_token_id
+        self.image_prefix_ids = () if vision_start_id is None else (int(vision_start_id),)
+        self.image_suffix_ids = () if vision_end_id is None else (int(vision_end_id),)
         tower = Qwen3VisionTower if isinstance(cfg, Qwen3VisionConfig) else QwenVisionTower
         self.vision = tower(cfg, get, decoder.device, torch.bfloat16, prefix)
 

@@ -826,3 +826,47 @@ def test_qwen3_vl_matches_transformers(tmp_path):
                           mm_token_type_ids=torch.tensor([[1 if t == 318 else 0 for t in ids]]),
                           max_new_tokens=5, do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
     assert outs[0][:len(ref)] == ref
+
+
+def test_qwen_vl_and_mllama_checkpoints_through_text_service(tmp_path):
+    """Image requests served end to end (prompt markers, vision tower, engine extras) for the two
+    families that need more than replaced embeddings: Qwen2.5-VL and Llama 3.2 Vision."""
+    import numpy as np
+    tr = pytest.importorskip("transformers")
+    from transformers.models.mllama.configuration_mllama import MllamaConfig, MllamaTextConfig, MllamaVisionConfig
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, TextRequest
+    from hartsyinference_b200.models.llm.loader import save_hf_checkpoint
+    _tiny_qwen_vl(tmp_path / "q")
+    vc = MllamaVisionConfig(hidden_size=64, attention_heads=4, intermediate_size=128, num_hidden_layers=2, num_global_layers=1,
+                            image_size=28, patch_size=14, max_num_tiles=4, intermediate_layers_indices=[0], vision_output_dim=128)
+    tc = MllamaTextConfig(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                          num_key_value_heads=2, max_position_embeddings=256, cross_attention_layers=[1], pad_token_id=0,
+                          rope_parameters={"rope_type": "default", "rope_theta": 10000.0})
+    mcfg = MllamaConfig(vision_config=vc, text_config=tc, image_token_index=319)
+    torch.manual_seed(0)
+    hf = tr.MllamaForConditionalGeneration(mcfg)
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("gate") or "cross_attn_attn_gate" in n or "cross_attn_mlp_gate" in n:
+                p.fill_(0.8)
+            elif p.ndim >= 2:
+                p.mul_(3.0)
+    save_hf_checkpoint(mcfg.to_dict(), {k: v.detach().to(torch.bfloat16).contiguous() for k, v in hf.state_dict().items()},
+                       tmp_path / "mllama")
+    img = (np.random.default_rng(0).random((56, 84, 3)) * 255).astype(np.uint8)
+    other = (np.random.default_rng(1).random((56, 84, 3)) * 255).astype(np.uint8)
+    eng = InferenceEngine("cpu")
+    try:
+        for d in (tmp_path / "q" / "m", tmp_path / "mllama"):
+            spec = ModelSpec(str(d))
+            text = eng.text.generate(spec, TextRequest(prompt="what is this?", max_tokens=4, greedy=True))
+            a = eng.text.generate(spec, TextRequest(prompt="<image>what is this?", images=[img], max_tokens=4, greedy=True))
+            again = eng.text.generate(spec, TextRequest(prompt="what is this?", images=[img], max_tokens=4, greedy=True))
+            b = eng.text.generate(spec, TextRequest(prompt="<image>what is this?", images=[other], max_tokens=4, greedy=True))
+            assert a.error is None and len(a.token_ids) == 4, a.error
+            assert again.token_ids == a.token_ids                 # no placeholder: the image goes in front
+            assert a.prompt_tokens > text.prompt_tokens
+            logits_differ = a.token_ids != text.token_ids or a.token_ids != b.token_ids
+            assert logits_differ, d
+    finally:
+        eng.text.release()
