@@ -359,3 +359,40 @@ def test_streaming_transcriber_commits_behind_the_hold_window():
     assert tail == "" and [round(s.end, 2) for s in new] == [4.0, 5.0] and st.buffer.numel() == 0
     assert len(st.committed) == 5 and st.text.startswith("s0")
     assert StreamingTranscriber(Fake()).push(torch.zeros(100)) == ([], "")
+
+
+def test_dac_codec_matches_transformers():
+    """DAC encode (codes) and decode (waveform) against ``DacModel``, with plain and weight-normalised convolutions."""
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.audio.dac import DacCodec, DacConfig
+    hf_cfg = tr.DacConfig(encoder_hidden_size=8, downsampling_ratios=[2, 4], upsampling_ratios=[4, 2], decoder_hidden_size=32,
+                          n_codebooks=3, codebook_size=16, codebook_dim=4, hidden_size=32)
+    torch.manual_seed(0)
+    hf = tr.DacModel(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("alpha"):
+                p.uniform_(0.5, 1.5)
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    cfg = DacConfig.from_hf(hf_cfg.to_dict())
+    assert cfg.hop == 8 and cfg.up == (4, 2)
+    codec = DacCodec(cfg, lambda n: sd.get(n))
+    wave = torch.randn(2, 160, generator=torch.Generator().manual_seed(1)) * 0.3
+    with torch.no_grad():
+        enc = hf.encode(wave[:, None])
+        ref_wave = hf.decode(audio_codes=enc.audio_codes).audio_values
+    codes = codec.encode(wave)
+    assert codes.shape == (2, 3, 20)
+    assert (codes == enc.audio_codes).float().mean() > 0.97          # ties between near-equal codes may flip
+    out = codec.decode(enc.audio_codes)
+    assert out.shape == (2, 160)
+    assert torch.allclose(out, ref_wave.reshape(2, -1), atol=1e-4)
+    # weight-normalised storage (g, v) folds to the same convolution
+    wn = dict(sd)
+    for k in [k for k in sd if k.endswith("conv1.weight") and k.startswith("decoder.block")]:
+        v = sd[k]
+        wn.pop(k)
+        wn[k[:-len("weight")] + "weight_v"] = v * 3.0
+        wn[k[:-len("weight")] + "weight_g"] = v.flatten(1).norm(dim=1).reshape(-1, 1, 1)
+    out2 = DacCodec(cfg, lambda n: wn.get(n)).decode(enc.audio_codes)
+    assert torch.allclose(out2, out, atol=1e-5)
