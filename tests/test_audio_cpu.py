@@ -396,3 +396,26 @@ def test_dac_codec_matches_transformers():
         wn[k[:-len("weight")] + "weight_g"] = v.flatten(1).norm(dim=1).reshape(-1, 1, 1)
     out2 = DacCodec(cfg, lambda n: wn.get(n)).decode(enc.audio_codes)
     assert torch.allclose(out2, out, atol=1e-5)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_encodec_decoder_matches_transformers(causal):
+    """EnCodec codes -> waveform against ``EncodecModel.decode`` (causal and centred padding)."""
+    tr = pytest.importorskip("transformers")
+    from hartsyinference_b200.models.audio.encodec import EncodecConfig, EncodecDecoder
+    hf_cfg = tr.EncodecConfig(num_filters=4, upsampling_ratios=[4, 2], hidden_size=16, codebook_size=16, num_lstm_layers=2,
+                              target_bandwidths=[1.5, 3.0], sampling_rate=800, num_residual_layers=2, use_causal_conv=causal,
+                              use_conv_shortcut=causal)
+    torch.manual_seed(0)
+    hf = tr.EncodecModel(hf_cfg).eval()
+    with torch.no_grad():
+        for layer in hf.quantizer.layers:
+            layer.codebook.embed.normal_()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    dec = EncodecDecoder(EncodecConfig.from_hf(hf_cfg.to_dict()), lambda n: sd.get(n))
+    codes = torch.randint(0, 16, (2, 3, 11), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf.decode(codes[None], [None])[0]
+    out = dec.decode(codes)
+    assert out.shape == ref.shape == (2, 1, 88)
+    assert torch.allclose(out, ref, atol=1e-5), (out - ref).abs().max()
