@@ -212,6 +212,27 @@ def speak(model, text, out, speed, device):
 
 @cli.command()
 @click.argument("model")
+@click.argument("prompt")
+@click.option("--out", default="music.wav")
+@click.option("--seconds", default=5.0)
+@click.option("--guidance", default=3.0)
+@click.option("--greedy", is_flag=True)
+@click.option("--seed", default=0)
+@click.option("--device", default="auto")
+def music(model, prompt, out, seconds, guidance, greedy, seed, device):
+    """Text to music (MusicGen) into a WAV file."""
+    from ..audio import write_wav
+    from ..engine.inference_engine import InferenceEngine
+    from ..engine.requests import MusicRequest
+    eng = InferenceEngine(device)
+    res = eng.music.run(ModelSpec(model, Modality.MUSIC, local_path=model),
+                        MusicRequest(prompt=prompt, seconds=seconds, guidance=guidance, greedy=greedy, seed=seed))
+    write_wav(out, res.samples, res.sample_rate)
+    click.echo(f"{out}: {res.seconds:.2f} s at {res.sample_rate} Hz")
+
+
+@cli.command()
+@click.argument("model")
 @click.option("--image", "images", multiple=True, help="image file (repeatable)")
 @click.option("--text", "texts", multiple=True, help="caption / query / prompt (repeatable)")
 @click.option("--op", "operation", default="embed", type=click.Choice(["embed", "depth", "segment", "detect"]))

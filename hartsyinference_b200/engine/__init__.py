@@ -2,7 +2,7 @@
 from .llm_engine import LLMEngine, Request  # noqa: F401
 from .sampling import SamplingParams  # noqa: F401
 from .requests import (  # noqa: F401
-    AudioRequest, EngineOptions, RestoreRequest, ImageRequest, ModelSpec, SpeechRequest, TextRequest, TextResult, VideoRequest, VisionRequest,
+    AudioRequest, MusicRequest, EngineOptions, RestoreRequest, ImageRequest, ModelSpec, SpeechRequest, TextRequest, TextResult, VideoRequest, VisionRequest,
 )
 
 

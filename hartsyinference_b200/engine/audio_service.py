@@ -4,6 +4,7 @@ Reference: src/HartsyInference.Engine/Services/TranscribeService.cs, ITranscribe
 """
 from __future__ import annotations
 
+import math
 import threading
 from pathlib import Path
 
@@ -39,6 +40,47 @@ class SpeechService:
             pipe = self._loaded[path]
         return pipe.speak(req.text, speaking_rate=req.speed, noise_scale=req.noise_scale,
                           noise_scale_duration=req.noise_scale_duration)
+
+
+class MusicService:
+    """Text-to-music: hosts MusicGen checkpoints (T5 text encoder, codebook language model, EnCodec
+    decoder in one directory) by path. Reference: src/HartsyInference.Engine/Services (music)."""
+
+    def __init__(self, device):
+        self.device = device
+        self._lock = threading.Lock()
+        self._loaded: dict = {}
+
+    def loaded_keys(self) -> list[str]:
+        return [f"musicgen:{k}" for k in self._loaded]
+
+    def release(self) -> None:
+        with self._lock:
+            self._loaded.clear()
+
+    def run(self, spec: ModelSpec, req):
+        import json
+        from pathlib import Path
+        from ..assets.safetensors import ShardedCheckpoint
+        from ..assets.tokenizer import ByteTokenizer, UnigramTokenizer
+        from ..models.audio.musicgen import Musicgen
+        from ..pipelines.vits import SpeechResult
+        path = Path(spec.local_path or spec.requested)
+        with self._lock:
+            if str(path) not in self._loaded:
+                raw = json.loads((path / "config.json").read_text())
+                model = Musicgen(raw, ShardedCheckpoint(path).get, self.device)
+                tok = (UnigramTokenizer.from_hf_json(path / "tokenizer.json") if (path / "tokenizer.json").exists()
+                       else ByteTokenizer(vocab_size=raw["text_encoder"]["vocab_size"]))
+                self._loaded[str(path)] = (model, tok, raw)
+            model, tok, raw = self._loaded[str(path)]
+        ids = tok.encode(req.prompt)
+        ids = [i for i in ids if i < raw["text_encoder"]["vocab_size"]] or [0]
+        frame_rate = model.sampling_rate / math.prod(model.codec.cfg.ratios)
+        frames = max(1, int(round(req.seconds * frame_rate)))
+        wave = model.generate(torch.tensor(ids), frames, guidance=req.guidance, sample=not req.greedy, seed=req.seed)
+        samples = wave.mean(0).float().cpu().clamp(-1, 1)
+        return SpeechResult(samples, model.sampling_rate, samples.numel() / model.sampling_rate)
 
 
 class TranscribeService:

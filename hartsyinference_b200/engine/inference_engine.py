@@ -52,7 +52,7 @@ def parse_backend_selector(selector: str) -> tuple[str, list[int]]:
 
 
 class InferenceEngine:
-    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH, Modality.RESTORE}
+    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH, Modality.RESTORE, Modality.MUSIC}
 
     def __init__(self, backend_selector: str = "auto", options: Optional[EngineOptions] = None):
         self.options = options or EngineOptions()
@@ -126,6 +126,11 @@ class InferenceEngine:
         return self._service("restore", lambda: RestoreService(self.device))
 
     @property
+    def music(self):
+        from .audio_service import MusicService
+        return self._service("music", lambda: MusicService(self.device))
+
+    @property
     def speech(self):
         from .audio_service import SpeechService
         return self._service("speech", lambda: SpeechService(self.device))
@@ -138,7 +143,6 @@ class InferenceEngine:
     def _unsupported(self, what: str):
         raise UnsupportedModelError(f"the {what} modality is not built in this engine yet")
 
-    music = property(lambda self: self._unsupported("music"))
     voice_conversion = property(lambda self: self._unsupported("voice conversion"))
     fx = property(lambda self: self._unsupported("fx"))
     mesh = property(lambda self: self._unsupported("mesh"))

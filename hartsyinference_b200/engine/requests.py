@@ -163,6 +163,17 @@ class SpeechRequest:
 
 
 @dataclass
+class MusicRequest:
+    """Text-to-music input (MusicGen). ``guidance`` is the classifier-free guidance scale; sampling
+    draws from the top-k tokens, greedy decoding is deterministic."""
+    prompt: str = ""
+    seconds: float = 5.0
+    guidance: float = 3.0
+    greedy: bool = False
+    seed: int = 0
+
+
+@dataclass
 class RestoreRequest:
     """``operation``: "upscale" (Real-ESRGAN). ``image``: path, PIL image, uint8 HWC array or float CHW tensor."""
     operation: str = "upscale"

@@ -28,6 +28,7 @@ class T5Config:
     max_distance: int = 128
     per_layer_bias: bool = False      # umT5
     eps: float = 1e-6
+    gated: bool = True                # False: the original T5 feed-forward, wo(relu(wi(x)))
 
 
 T5_XXL = T5Config()
@@ -70,9 +71,10 @@ class T5Encoder:
                                                            for n in ("q", "k", "v")], 0), fp8=f.fp8 and self.device.type == "cuda"),
                 o=f.linear(p + "0.SelfAttention.o", cfg.d_model, inner, bias=False),
                 ln2=f.tensor(p + "1.layer_norm.weight", cfg.d_model, ones=True),
-                wi=ops.LinearWeight.from_dense(torch.cat([f.linear(p + "1.DenseReluDense.wi_0", cfg.d_ff, cfg.d_model, bias=False, allow_fp8=False).weight,
-                                                          f.linear(p + "1.DenseReluDense.wi_1", cfg.d_ff, cfg.d_model, bias=False, allow_fp8=False).weight], 0),
-                                               fp8=f.fp8 and self.device.type == "cuda"),
+                wi=(ops.LinearWeight.from_dense(torch.cat([f.linear(p + "1.DenseReluDense.wi_0", cfg.d_ff, cfg.d_model, bias=False, allow_fp8=False).weight,
+                                                           f.linear(p + "1.DenseReluDense.wi_1", cfg.d_ff, cfg.d_model, bias=False, allow_fp8=False).weight], 0),
+                                                fp8=f.fp8 and self.device.type == "cuda") if cfg.gated else
+                    f.linear(p + "1.DenseReluDense.wi", cfg.d_ff, cfg.d_model, bias=False)),
                 wo=f.linear(p + "1.DenseReluDense.wo", cfg.d_model, cfg.d_ff, bias=False))
             if i == 0 or cfg.per_layer_bias:
                 lw["rel"] = f.tensor(p + "0.SelfAttention.relative_attention_bias.weight", cfg.num_buckets, cfg.num_heads)
@@ -99,7 +101,10 @@ class T5Encoder:
             att = att.transpose(0, 1).reshape(L, -1).to(torch.bfloat16)
             x = ops.linear(att, lw["o"], residual=x)
             h, _, _ = ops.norm(x, lw["ln2"], eps=cfg.eps)
-            g, _ = ops.glu(ops.linear(h, lw["wi"]), "gelu_tanh")
+            if cfg.gated:
+                g, _ = ops.glu(ops.linear(h, lw["wi"]), "gelu_tanh")
+            else:
+                g = torch.relu(ops.linear(h, lw["wi"]))
             x = ops.linear(g, lw["wo"], residual=x)
         out, _, _ = ops.norm(x, self.final_ln, eps=cfg.eps)
         return out

@@ -391,6 +391,21 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
             return Response(pcm, media_type="audio/pcm", headers={"x-sample-rate": str(res.sample_rate)})
         return Response(write_wav(None, res.samples, res.sample_rate), media_type="audio/wav")
 
+    @app.post("/v1/native/music")
+    async def native_music(request: Request):
+        from fastapi.responses import Response
+        from ..audio import write_wav
+        from ..engine.requests import MusicRequest
+        body = await request.json()
+        prompt = body.get("prompt") or body.get("input") or ""
+        if not prompt.strip():
+            return JSONResponse({"error": {"message": "no prompt", "type": "bad_request"}}, status_code=400)
+        mreq = MusicRequest(prompt=prompt, seconds=float(body.get("seconds", 5.0)), guidance=float(body.get("guidance", 3.0)),
+                            greedy=bool(body.get("greedy", False)), seed=int(body.get("seed", 0)))
+        with heavy_queue.slot():
+            res = eng.music.run(resolve(body.get("model"), Modality.MUSIC), mreq)
+        return Response(write_wav(None, res.samples, res.sample_rate), media_type="audio/wav")
+
     @app.post("/v1/native/restore")
     async def native_restore(request: Request):
         import io
@@ -500,7 +515,7 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
                 "first_frame_png_base64": base64.b64encode(_png(res.frames[0], res.width, res.height)).decode() if res.frames else None}
 
     for route in ("/v1/audio/speech", "/v1/audio/transcriptions", "/v1/native/mesh", "/v1/native/vision",
-                  "/v1/native/restore", "/v1/native/world", "/v1/native/music"):
+                  "/v1/native/restore", "/v1/native/world"):
         def _make(r):
             async def _nyi():
                 raise UnsupportedModelError(f"{r}: this modality is not built in this engine yet")

@@ -419,3 +419,90 @@ def test_encodec_decoder_matches_transformers(causal):
     out = dec.decode(codes)
     assert out.shape == ref.shape == (2, 1, 88)
     assert torch.allclose(out, ref, atol=1e-5), (out - ref).abs().max()
+
+
+def test_musicgen_matches_transformers():
+    """MusicGen decoder logits (teacher forced) and the whole text -> codes -> audio path with greedy
+    decoding, the codebook delay pattern and classifier-free guidance, against transformers."""
+    tr = pytest.importorskip("transformers")
+    from transformers.models.musicgen.configuration_musicgen import MusicgenDecoderConfig
+    from hartsyinference_b200.models.audio.musicgen import Musicgen, delay_mask
+    t5 = tr.T5Config(vocab_size=64, d_model=32, d_kv=8, d_ff=64, num_layers=2, num_heads=4, feed_forward_proj="relu")
+    enc = tr.EncodecConfig(num_filters=4, upsampling_ratios=[4, 2], hidden_size=16, codebook_size=16, num_lstm_layers=1,
+                           target_bandwidths=[1.5, 3.0], sampling_rate=800, num_residual_layers=1)
+    dec = MusicgenDecoderConfig(vocab_size=16, hidden_size=48, num_hidden_layers=2, num_attention_heads=4, ffn_dim=64, num_codebooks=4,
+                                max_position_embeddings=64, pad_token_id=16, bos_token_id=16)
+    cfg = tr.MusicgenConfig(text_encoder=t5.to_dict(), audio_encoder=enc.to_dict(), decoder=dec.to_dict())
+    torch.manual_seed(0)
+    hf = tr.MusicgenForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim >= 2:
+                p.mul_(3.0)
+        for layer in hf.audio_encoder.quantizer.layers:
+            layer.codebook.embed.normal_()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    m = Musicgen(cfg.to_dict(), lambda n: sd.get(n))
+    assert not m.text.cfg.gated and m.proj_w is not None
+    ids = torch.randint(2, 64, (7,), generator=torch.Generator().manual_seed(1))
+    states = m.text_states(ids)
+    with torch.no_grad():
+        ref_states = hf.enc_to_dec_proj(hf.text_encoder(input_ids=ids[None]).last_hidden_state)[0]
+    assert torch.nn.functional.cosine_similarity(states.flatten(), ref_states.flatten(), dim=0) > 0.99
+    codes_in = torch.randint(0, 17, (4, 9), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        ref = hf.decoder(input_ids=codes_in, encoder_hidden_states=ref_states[None]).logits            # [1, K, T, V]
+    mine = m.decoder.forward(codes_in, ref_states, m.decoder.new_cache())
+    assert torch.allclose(mine, ref.reshape(4, 9, 16), atol=2e-3), (mine - ref.reshape(4, 9, 16)).abs().max()
+    assert delay_mask(4, 8).int().tolist() == [[0, 1, 1, 1, 1, 0, 0, 0], [0, 0, 1, 1, 1, 1, 0, 0],
+                                               [0, 0, 0, 1, 1, 1, 1, 0], [0, 0, 0, 0, 1, 1, 1, 1]]
+    hf.generation_config.update(do_sample=False, guidance_scale=3.0, max_length=12, pad_token_id=16, bos_token_id=16,
+                                decoder_start_token_id=16)
+    with torch.no_grad():
+        ref_audio = hf.generate(input_ids=ids[None], attention_mask=torch.ones(1, 7, dtype=torch.long))
+    frames = ref_audio.shape[-1] // 8
+    assert frames in (12 - 4, 12 - 4 + 1)                      # the generation-length bookkeeping differs between releases
+    codes = m.decoder.generate(ref_states, frames, guidance=3.0)
+    audio = m.codec.decode(codes[None])[0]
+    assert audio.shape == ref_audio[0].shape == (1, frames * 8)
+    assert torch.allclose(audio, ref_audio[0], atol=1e-3), (audio - ref_audio[0]).abs().max()
+
+
+def test_music_service_generates_audio_from_a_checkpoint_directory(tmp_path):
+    """A MusicGen directory (config.json + safetensors) through the engine's music service: the
+    requested duration, determinism of greedy decoding, and the prompt actually steering the result."""
+    tr = pytest.importorskip("transformers")
+    import json
+    from transformers.models.musicgen.configuration_musicgen import MusicgenDecoderConfig
+    from hartsyinference_b200.assets.safetensors import save_file
+    from hartsyinference_b200.engine import InferenceEngine, ModelSpec, MusicRequest
+    t5 = tr.T5Config(vocab_size=300, d_model=32, d_kv=8, d_ff=64, num_layers=1, num_heads=4, feed_forward_proj="relu")
+    enc = tr.EncodecConfig(num_filters=4, upsampling_ratios=[4, 2], hidden_size=16, codebook_size=16, num_lstm_layers=1,
+                           target_bandwidths=[1.5, 3.0], sampling_rate=800, num_residual_layers=1)
+    dec = MusicgenDecoderConfig(vocab_size=16, hidden_size=48, num_hidden_layers=1, num_attention_heads=4, ffn_dim=64, num_codebooks=4,
+                                max_position_embeddings=256, pad_token_id=16, bos_token_id=16)
+    cfg = tr.MusicgenConfig(text_encoder=t5.to_dict(), audio_encoder=enc.to_dict(), decoder=dec.to_dict())
+    torch.manual_seed(0)
+    hf = tr.MusicgenForConditionalGeneration(cfg)
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.ndim >= 2 and not n.startswith("audio_encoder."):
+                p.mul_(4.0)                                      # make the text matter; the codec stays unsaturated
+        for layer in hf.audio_encoder.quantizer.layers:
+            layer.codebook.embed.normal_(std=0.3)
+    d = tmp_path / "musicgen"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg.to_dict()))
+    save_file({k: v.detach().contiguous() for k, v in hf.state_dict().items()}, d / "model.safetensors")
+    eng = InferenceEngine("cpu")
+    spec = ModelSpec(str(d))
+    a = eng.music.run(spec, MusicRequest(prompt="slow piano", seconds=0.2, greedy=True))
+    assert a.sample_rate == 800 and a.samples.shape == (160,) and abs(a.seconds - 0.2) < 1e-6
+    again = eng.music.run(spec, MusicRequest(prompt="slow piano", seconds=0.2, greedy=True))
+    assert torch.equal(a.samples, again.samples)
+    b = eng.music.run(spec, MusicRequest(prompt="fast drums and bass", seconds=0.2, greedy=True, guidance=8.0))
+    assert not torch.allclose(a.samples, b.samples)
+    s1 = eng.music.run(spec, MusicRequest(prompt="slow piano", seconds=0.2, seed=1))
+    s2 = eng.music.run(spec, MusicRequest(prompt="slow piano", seconds=0.2, seed=1))
+    assert torch.equal(s1.samples, s2.samples)
+    assert "musicgen:" + str(d) in eng.music.loaded_keys()

@@ -78,6 +78,7 @@ def test_image_generation_and_unsupported_routes(server):
     png = base64.b64decode(r["data"][0]["b64_json"])
     assert png[:8] == b"\x89PNG\r\n\x1a\n" and r["data"][0]["seed"] == 3
     assert requests.post(server + "/v1/audio/speech", json={}, headers=H).status_code == 400
+    assert requests.post(server + "/v1/native/music", json={}, headers=H).status_code == 400
     assert requests.post(server + "/v1/chat/completions", json={"model": "/no/such/model", "messages": []}, headers=H).status_code in (400, 500)
 
 
