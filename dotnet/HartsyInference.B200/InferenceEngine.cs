@@ -22,6 +22,7 @@ public interface IInferenceEngine : IDisposable
     VideoService Video { get; }
     TranscribeService Transcribe { get; }
     SpeechService Speech { get; }
+    MusicService Music { get; }
     EmbeddingService Embeddings { get; }
     VisionService Vision { get; }
     RestoreService Restore { get; }
@@ -39,6 +40,7 @@ public sealed class InferenceEngine : IInferenceEngine
     public VideoService Video { get; }
     public TranscribeService Transcribe { get; }
     public SpeechService Speech { get; }
+    public MusicService Music { get; }
     public EmbeddingService Embeddings { get; }
     public VisionService Vision { get; }
     public RestoreService Restore { get; }
@@ -52,6 +54,7 @@ public sealed class InferenceEngine : IInferenceEngine
         Video = new VideoService(this);
         Transcribe = new TranscribeService(this);
         Speech = new SpeechService(this);
+        Music = new MusicService(this);
         Embeddings = new EmbeddingService(this);
         Vision = new VisionService(this);
         Restore = new RestoreService(this);
@@ -195,6 +198,25 @@ public sealed class TranscribeService
         NativeMethods.Check(NativeMethods.b200_transcribe(_e.Handle, JsonSerializer.Serialize(spec with { Modality = Modality.Transcribe }),
             JsonSerializer.Serialize(request), pcm, pcm.LongLength, sampleRate, out var p));
         return JsonSerializer.Deserialize<TranscriptResult>(NativeMethods.TakeString(p), Records.SnakeCase)!;
+    }, ct);
+}
+
+public sealed class MusicService
+{
+    private readonly InferenceEngine _e;
+    internal MusicService(InferenceEngine e) => _e = e;
+
+    public Task<AudioResult> RunAsync(ModelSpec spec, MusicRequest request, CancellationToken ct = default) => Task.Run(() =>
+    {
+        NativeMethods.Check(NativeMethods.b200_music(_e.Handle, JsonSerializer.Serialize(spec with { Modality = Modality.Music }),
+            JsonSerializer.Serialize(request), out var pcm, out long n, out int rate));
+        try
+        {
+            var samples = new float[n];
+            Marshal.Copy(pcm, samples, 0, (int)n);
+            return new AudioResult(samples, rate);
+        }
+        finally { NativeMethods.b200_free(pcm); }
     }, ct);
 }
 

@@ -66,6 +66,10 @@ internal static unsafe class NativeMethods
         [MarshalAs(UnmanagedType.LPUTF8Str)] string request, out IntPtr pcm, out long samples, out int sampleRate);
 
     [DllImport(Lib, CallingConvention = CallingConvention.Cdecl)]
+    internal static extern int b200_music(IntPtr engine, [MarshalAs(UnmanagedType.LPUTF8Str)] string spec,
+        [MarshalAs(UnmanagedType.LPUTF8Str)] string request, out IntPtr pcm, out long samples, out int sampleRate);
+
+    [DllImport(Lib, CallingConvention = CallingConvention.Cdecl)]
     internal static extern int b200_embed_text(IntPtr engine, [MarshalAs(UnmanagedType.LPUTF8Str)] string spec,
         [MarshalAs(UnmanagedType.LPUTF8Str)] string textsJson, out IntPtr values, out int count, out int dim);
 

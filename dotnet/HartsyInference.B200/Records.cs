@@ -95,6 +95,15 @@ public sealed record TranscriptSegment(double Start, double End, string Text);
 
 public sealed record TranscriptResult(string Text, string? Language, double Duration, IReadOnlyList<TranscriptSegment> Segments);
 
+public sealed record MusicRequest
+{
+    public string Prompt { get; init; } = "";
+    public float Seconds { get; init; } = 5f;
+    public float Guidance { get; init; } = 3f;
+    public bool Greedy { get; init; }
+    public int Seed { get; init; }
+}
+
 public sealed record SpeechRequest
 {
     public string Text { get; init; } = "";

@@ -182,6 +182,14 @@ def speak(h: int, spec: str, req: str):
 
 
 @_guard
+def music(h: int, spec: str, req: str):
+    from .engine.requests import MusicRequest
+    e = _engines[h]
+    res = e.music.run(_spec(spec), _fields(MusicRequest, req))
+    return (res.samples.float().contiguous().numpy().astype("<f4").tobytes(), res.sample_rate)
+
+
+@_guard
 def embed_text(h: int, spec: str, texts: str):
     e = _engines[h]
     s = _spec(spec)

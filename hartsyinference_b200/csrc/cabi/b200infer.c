@@ -222,6 +222,20 @@ int b200_speak(b200_engine* e, const char* spec, const char* req, float** pcm_ou
   LEAVE(rc);
 }
 
+int b200_music(b200_engine* e, const char* spec, const char* req, float** pcm_out, long long* samples_out, int* sample_rate_out) {
+  ENTER();
+  PyObject* p = NULL;
+  int rc = call("music", Py_BuildValue("(Lss)", e->handle, spec, req), &p);
+  if (rc == 0) {   /* payload: (float32 bytes, sample rate) */
+    Py_ssize_t n = 0;
+    if (pcm_out) *pcm_out = (float*)dup_bytes(PyTuple_GetItem(p, 0), &n);
+    if (samples_out) *samples_out = (long long)(n / (Py_ssize_t)sizeof(float));
+    if (sample_rate_out) *sample_rate_out = (int)PyLong_AsLong(PyTuple_GetItem(p, 1));
+  }
+  Py_XDECREF(p);
+  LEAVE(rc);
+}
+
 int b200_embed_text(b200_engine* e, const char* spec, const char* texts_json, float** out, int* count, int* dim) {
   ENTER();
   PyObject* p = NULL;

@@ -55,6 +55,9 @@ int b200_transcribe(b200_engine* e, const char* spec_json, const char* request_j
 /* Text to speech. pcm_out: mono float samples, released with b200_free(). */
 int b200_speak(b200_engine* e, const char* spec_json, const char* request_json, float** pcm_out, long long* samples_out,
                int* sample_rate_out);
+/* Text to music. request_json: {"prompt", "seconds", "guidance", "greedy", "seed"}. pcm_out: mono float samples, released with b200_free(). */
+int b200_music(b200_engine* e, const char* spec_json, const char* request_json, float** pcm_out, long long* samples_out,
+               int* sample_rate_out);
 /* Text embeddings. texts_json: a JSON array of strings. out: count * dim floats (row-major), released with b200_free(). */
 int b200_embed_text(b200_engine* e, const char* spec_json, const char* texts_json, float** out, int* count, int* dim);
 /* Image embedding of one RGB24 image. out: dim floats (L2-normalised), released with b200_free(). */

@@ -93,4 +93,6 @@ def test_new_modalities_via_ctypes(ckpt, tmp_path):
     lib.b200_free(pcm)
     assert rate.value == 16000 and n.value > 0 and np.abs(wave).max() <= 1.0
     assert lib.b200_speak(eng, b'{"requested": "/no/such/voice"}', b'{"text": "x"}', C.byref(pcm), C.byref(n), C.byref(rate)) != 0
+    assert lib.b200_music(eng, b'{"requested": "/no/such/model"}', b'{"prompt": "x", "seconds": 0.1}', C.byref(pcm), C.byref(n), C.byref(rate)) != 0
+    assert b"No such file" in lib.b200_last_error() or len(lib.b200_last_error()) > 0
     lib.b200_engine_destroy(eng)
