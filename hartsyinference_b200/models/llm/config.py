@@ -223,7 +223,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / granitemoe / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -380,7 +380,7 @@ def from_hf_config(d: dict) -> TransformerConfig:
         kw.update(embedding_multiplier=float(d.get("scale_emb", 1.0)),
                   residual_multiplier=float(d.get("scale_depth", 1.0)) / (d["num_hidden_layers"] ** 0.5),
                   logits_scale=float(d.get("dim_model_base", hidden)) / hidden)
-    if mt == "granite":
+    if mt in ("granite", "granitemoe"):
         kw.update(residual_multiplier=float(d.get("residual_multiplier", 1.0)),
                   embedding_multiplier=float(d.get("embedding_multiplier", 1.0)),
                   logits_scale=1.0 / float(d.get("logits_scaling", 1.0)),
@@ -417,7 +417,7 @@ def from_hf_config(d: dict) -> TransformerConfig:
                               num_shared_experts=1 if d.get("shared_expert_intermediate_size") else 0,
                               shared_ffn=d.get("shared_expert_intermediate_size", 0) or 0,
                               shared_gate=mt == "qwen2_moe",
-                              norm_topk_prob=bool(d.get("norm_topk_prob", mt == "mixtral")))
+                              norm_topk_prob=bool(d.get("norm_topk_prob", mt in ("mixtral", "granitemoe"))))
     return TransformerConfig(**kw)
 
 

@@ -211,6 +211,16 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
         def g(name: str):
             return get(name.replace("self_attn.q_norm", "self_attn.query_layernorm").replace("self_attn.k_norm", "self_attn.key_layernorm"))
         return g
+    if mt == "granitemoe":
+        ren = (("mlp.gate.weight", "block_sparse_moe.router.layer.weight"), ("mlp.experts.gate_up_proj", "block_sparse_moe.input_linear.weight"),
+               ("mlp.experts.down_proj", "block_sparse_moe.output_linear.weight"))
+
+        def g(name: str):
+            for std, own in ren:
+                if name.endswith(std):
+                    return get(name[: -len(std)] + own)
+            return get(name)
+        return g
     if mt == "apertus":
         def g(name: str):
             return get(name.replace("input_layernorm", "attention_layernorm").replace("post_attention_layernorm", "feedforward_layernorm"))
