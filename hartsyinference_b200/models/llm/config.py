@@ -380,7 +380,7 @@ def from_hf_config(d: dict) -> TransformerConfig:
         kw.update(embedding_multiplier=float(d.get("scale_emb", 1.0)),
                   residual_multiplier=float(d.get("scale_depth", 1.0)) / (d["num_hidden_layers"] ** 0.5),
                   logits_scale=float(d.get("dim_model_base", hidden)) / hidden)
-    if mt in ("granite", "granitemoe"):
+    if mt in ("granite", "granitemoe", "granitemoeshared"):
         kw.update(residual_multiplier=float(d.get("residual_multiplier", 1.0)),
                   embedding_multiplier=float(d.get("embedding_multiplier", 1.0)),
                   logits_scale=1.0 / float(d.get("logits_scaling", 1.0)),
@@ -410,14 +410,14 @@ def from_hf_config(d: dict) -> TransformerConfig:
                   layer_types=tuple(d.get("layer_types") or ()))
         kw["moe"] = MoeConfig(num_experts=d.get("num_local_experts", 0), top_k=d.get("num_experts_per_tok", 4),
                               expert_ffn=d.get("intermediate_size", 0), norm_topk_prob=True)
-    if mt in ("olmoe", "qwen2_moe", "qwen3_moe", "mixtral", "granitemoe"):
+    if mt in ("olmoe", "qwen2_moe", "qwen3_moe", "mixtral", "granitemoe", "granitemoeshared"):
         kw["moe"] = MoeConfig(num_experts=d.get("num_experts", d.get("num_local_experts", 0)),
                               top_k=d.get("num_experts_per_tok", 2),
                               expert_ffn=d.get("moe_intermediate_size", d.get("intermediate_size", 0)),
-                              num_shared_experts=1 if d.get("shared_expert_intermediate_size") else 0,
-                              shared_ffn=d.get("shared_expert_intermediate_size", 0) or 0,
+                              num_shared_experts=1 if (d.get("shared_expert_intermediate_size") or d.get("shared_intermediate_size")) else 0,
+                              shared_ffn=d.get("shared_expert_intermediate_size") or d.get("shared_intermediate_size") or 0,
                               shared_gate=mt == "qwen2_moe",
-                              norm_topk_prob=bool(d.get("norm_topk_prob", mt in ("mixtral", "granitemoe"))))
+                              norm_topk_prob=bool(d.get("norm_topk_prob", mt in ("mixtral", "granitemoe", "granitemoeshared"))))
     return TransformerConfig(**kw)
 
 

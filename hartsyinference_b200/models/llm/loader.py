@@ -211,11 +211,21 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
         def g(name: str):
             return get(name.replace("self_attn.q_norm", "self_attn.query_layernorm").replace("self_attn.k_norm", "self_attn.key_layernorm"))
         return g
-    if mt == "granitemoe":
+    if mt in ("granitemoe", "granitemoeshared"):
+        sf = int(raw.get("shared_intermediate_size") or 0)
+
+        def shared(name: str):          # shared_mlp keeps gate | up in one input_linear
+            base = name[: name.index("mlp.shared_experts.")] + "shared_mlp."
+            if name.endswith("down_proj.weight"):
+                return get(base + "output_linear.weight")
+            t = get(base + "input_linear.weight")
+            return None if t is None else (t[:sf] if name.endswith("gate_proj.weight") else t[sf:])
         ren = (("mlp.gate.weight", "block_sparse_moe.router.layer.weight"), ("mlp.experts.gate_up_proj", "block_sparse_moe.input_linear.weight"),
                ("mlp.experts.down_proj", "block_sparse_moe.output_linear.weight"))
 
         def g(name: str):
+            if "mlp.shared_experts." in name:
+                return shared(name) if sf else None
             for std, own in ren:
                 if name.endswith(std):
                     return get(name[: -len(std)] + own)

@@ -61,6 +61,8 @@ ARCHS = {
     "apertus": ("ApertusConfig", dict()),
     "granitemoe": ("GraniteMoeConfig", dict(num_local_experts=4, num_experts_per_tok=2, intermediate_size=64, residual_multiplier=0.5,
                                             embedding_multiplier=3.0, logits_scaling=2.0, attention_multiplier=0.2)),
+    "granitemoeshared": ("GraniteMoeSharedConfig", dict(num_local_experts=4, num_experts_per_tok=2, intermediate_size=64,
+                                                        shared_intermediate_size=96, residual_multiplier=0.5, logits_scaling=2.0)),
     "olmo": ("OlmoConfig", dict()),
     "olmo3": ("Olmo3Config", dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
     "gptj": ("GPTJConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, rotary_dim=16)),
