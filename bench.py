@@ -116,9 +116,6 @@ def main() -> int:
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
-    if os.environ.get("B200_BENCH_TRACE_AFTER"):
-        import faulthandler
-        faulthandler.dump_traceback_later(float(os.environ["B200_BENCH_TRACE_AFTER"]), repeat=False, exit=True)
 
     import torch
     from hartsyinference_b200 import log
@@ -196,6 +193,7 @@ def main() -> int:
         eng.step()
     torch.cuda.synchronize()
     peer_ar = getattr(model, "custom_ar", None) is not None
+    multimem = bool(getattr(getattr(model, "fused_rp", None) or getattr(model, "custom_ar", None), "use_mc", False))
     if fused or peer_ar:
         # A bounded wait of the peer-memory kernels that gave up on any rank means the peer protocol
         # did not work on this machine: fall back to NCCL on every rank rather than time garbage.
@@ -204,10 +202,9 @@ def main() -> int:
         dist.all_reduce(bad, op=dist.ReduceOp.MAX)
         if int(bad.item()) != 0:
             log.warn("[Collective] peer-memory TP kernels reported a wait timeout; falling back to NCCL")
-            N.state(device).status.zero_()
-            model.row_parallel_linear = None
-            model.custom_ar = None
-            model.all_reduce = comm.all_reduce
+            N.state(device).reset_after_fault()
+            from hartsyinference_b200.parallel.fused import disable_fused_tp
+            disable_fused_tp(model, comm)
             peer_ar = False
             eng._graphs.clear()
             fused = False
@@ -262,7 +259,7 @@ def main() -> int:
             "config": {"model": args.preset, "global_batch": args.batch, "seq_len": args.prompt_len,
                        "decode_len": args.decode_len, "parallelism": f"tp{world}", "kv_page": page,
                        "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
-                       "cuda_graphs": not args.no_graphs, "fused_comm": fused,
+                       "cuda_graphs": not args.no_graphs, "fused_comm": fused, "multimem": multimem,
                        "comm_path": "fused GEMM+all-reduce" if fused else "peer-memory all-reduce kernel" if peer_ar else ("nccl" if world > 1 else "none"),
                        "invalid_debug_overrides": invalid},
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "ms_per_step": wall_ms / steps,
@@ -275,8 +272,14 @@ def main() -> int:
         }
         print(json.dumps(out))
     if world > 1:
-        # NCCL communicators that were captured into CUDA graphs can block in their teardown; the
-        # result is already printed, so leave without running it.
+        # Every rank takes its memory out of the multicast object and unmaps its peers before any
+        # rank leaves. NCCL communicators that were captured into CUDA graphs can block in their
+        # teardown; the result is already printed, so leave without running it.
+        comm.barrier()
+        torch.cuda.synchronize()
+        eng._graphs.clear()
+        from hartsyinference_b200.parallel.fused import disable_fused_tp
+        disable_fused_tp(model, comm)
         comm.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()

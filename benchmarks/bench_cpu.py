@@ -3,7 +3,7 @@ of 128 uniformly drawn token ids and 128 greedy decode steps through the serving
 (PyTorch CPU path of every op), plus a logits check of the paged / chunked engine path against one
 dense fp32 pass over the same tokens.
 
-    python -m hartsyinference_b200.utils.bench_cpu [--prompt 128] [--decode 128] [--threads N]
+    python benchmarks/bench_cpu.py [--prompt 128] [--decode 128] [--threads N]
 
 Prints one JSON line: decode tokens/s, prefill tokens/s, bytes of weights read per token, the
 implied host bandwidth, and the parity figures.
@@ -13,6 +13,11 @@ from __future__ import annotations
 import argparse
 import json
 import time
+
+import os as _os
+import sys as _sys
+
+_sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
 
 import torch
 

@@ -1,8 +1,8 @@
 """Measure DiT denoise-step time (Flux or Wan) on random-init weights of the named architecture.
 
-    python -m hartsyinference_b200.utils.bench_dit --model flux --steps 4 [--gpus-env torchrun]
-    torchrun --nproc-per-node N -m hartsyinference_b200.utils.bench_dit --model flux --tp N
-    torchrun --nproc-per-node N -m hartsyinference_b200.utils.bench_dit --model wan --sp N [--frames 81 --height 720 --width 1280]
+    python benchmarks/bench_dit.py --model flux --steps 4 [--gpus-env torchrun]
+    torchrun --nproc-per-node N -m benchmarks/bench_dit --model flux --tp N
+    torchrun --nproc-per-node N -m benchmarks/bench_dit --model wan --sp N [--frames 81 --height 720 --width 1280]
 
 Prints one JSON line: s/step (device-timed, max over ranks), the FLOP estimate and the fraction of
 the measured bf16 peak."""
@@ -13,10 +13,15 @@ import json
 import os
 from dataclasses import replace
 
+import os as _os
+import sys as _sys
+
+_sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+
 import torch
 
-from ..parallel import init_comm
-from . import profiling
+from hartsyinference_b200.parallel import init_comm
+from hartsyinference_b200.utils import profiling
 
 
 def main() -> None:

@@ -1,7 +1,7 @@
 """Per-rank compute time of a tensor / expert parallel layout, measured on ONE GPU.
 
-    python -m hartsyinference_b200.utils.bench_shard --preset llama-3-70b --tp 8 --batch 64 --prompt-len 2048
-    python -m hartsyinference_b200.utils.bench_shard --preset deepseek-v3 --tp 8 --batch 256 --prompt-len 1024
+    python benchmarks/bench_shard.py --preset llama-3-70b --tp 8 --batch 64 --prompt-len 2048
+    python benchmarks/bench_shard.py --preset deepseek-v3 --tp 8 --batch 256 --prompt-len 1024
 
 Builds rank 0's shard of the model on a communicator without peers (collectives are no-ops, so
 the generated tokens mean nothing), prefills the batch and times decode steps with CUDA events
@@ -15,13 +15,18 @@ import argparse
 import json
 from dataclasses import replace
 
+import os as _os
+import sys as _sys
+
+_sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+
 import torch
 
-from ..engine import LLMEngine, SamplingParams
-from ..models.llm import config as C
-from ..models.llm.transformer import DecoderModel
-from ..ops import _native as N
-from ..parallel.comm import ShardEmulationComm
+from hartsyinference_b200.engine import LLMEngine, SamplingParams
+from hartsyinference_b200.models.llm import config as C
+from hartsyinference_b200.models.llm.transformer import DecoderModel
+from hartsyinference_b200.ops import _native as N
+from hartsyinference_b200.parallel.comm import ShardEmulationComm
 
 
 def main() -> None:
@@ -33,6 +38,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=24)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the preset's)")
     ap.add_argument("--bf16", action="store_true")
+    ap.add_argument("--fused", action="store_true",
+                    help="run the fused GEMM + all-reduce + norm kernel with this GPU standing in for its peers "
+                         "(the rank's full protocol and row share; no NVLink latency)")
     args = ap.parse_args()
     cfg = C.PRESETS[args.preset]
     if args.layers:
@@ -40,6 +48,9 @@ def main() -> None:
     comm = ShardEmulationComm(args.tp)
     model = DecoderModel(cfg, "cuda", comm=comm, fp8=not args.bf16)
     model.random_init(0)
+    if args.fused:
+        from hartsyinference_b200.parallel.fused import FusedRowParallel
+        model.fused_rp = FusedRowParallel(comm, cfg.hidden_size, model.device, emulate_peers=True)
     dlen = args.steps + 16
     page = 16
     pps = (args.prompt_len + dlen + page - 1) // page + 1
@@ -68,7 +79,7 @@ def main() -> None:
     N.check_status()
     ts.sort()
     med = ts[len(ts) // 2]
-    print(json.dumps({"preset": args.preset, "emulated_rank_of": args.tp, "layers": cfg.num_layers, "batch": args.batch,
+    print(json.dumps({"preset": args.preset, "emulated_rank_of": args.tp, "fused_row_parallel": bool(args.fused), "layers": cfg.num_layers, "batch": args.batch,
                       "prompt_len": args.prompt_len, "ms_per_step_compute_only": med, "ms_min": ts[0],
                       "us_per_layer": 1000 * med / cfg.num_layers, "launches_per_step": eng.kernel_launches_last,
                       "weight_gib": model.weight_bytes() / 2 ** 30,

@@ -1,10 +1,10 @@
 """Runs ONE kernel on a small, fixed case a few times: the program that profiler captures wrap.
 
-    python -m hartsyinference_b200.utils.kernel_case gemm fp8 64 28672 4096
-    python -m hartsyinference_b200.utils.kernel_case grouped fp8 32 16 4096 7168
-    python -m hartsyinference_b200.utils.kernel_case attn_decode 64 8 1 128 2304
-    python -m hartsyinference_b200.utils.kernel_case mla 64 16 2304
-    python -m hartsyinference_b200.utils.kernel_case attn_dense 4608 8
+    python benchmarks/kernel_case.py gemm fp8 64 28672 4096
+    python benchmarks/kernel_case.py grouped fp8 32 16 4096 7168
+    python benchmarks/kernel_case.py attn_decode 64 8 1 128 2304
+    python benchmarks/kernel_case.py mla 64 16 2304
+    python benchmarks/kernel_case.py attn_dense 4608 8
 
 Inputs are larger than the L2 cache where the op is bandwidth bound but stay far below a few GB,
 so a full-metric capture (dozens of replays per launch) ends in about a minute. The status word is
@@ -15,10 +15,15 @@ from __future__ import annotations
 import math
 import sys
 
+import os as _os
+import sys as _sys
+
+_sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+
 import torch
 
-from .. import ops
-from ..ops import _native as N
+from hartsyinference_b200 import ops
+from hartsyinference_b200.ops import _native as N
 
 
 def _gemm(argv):

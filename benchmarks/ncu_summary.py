@@ -1,6 +1,6 @@
 """Condenses an Nsight Compute report into the handful of figures used for roofline notes.
 
-    python -m hartsyinference_b200.utils.ncu_summary report.ncu-rep [more.ncu-rep ...]
+    python benchmarks/ncu_summary.py report.ncu-rep [more.ncu-rep ...]
 
 Reads the report with ``ncu -i <file> --page raw --csv`` (works on a machine without a GPU) and
 prints, per captured launch: kernel name, grid / block, registers, duration, DRAM bytes and

@@ -1,6 +1,6 @@
 """Profile one decode step of the serving engine.
 
-    python -m hartsyinference_b200.utils.profile_decode --preset llama-3-8b --batch 64 --prompt-len 2048
+    python benchmarks/profile_decode.py --preset llama-3-8b --batch 64 --prompt-len 2048
 
 Builds a random-init model, prefills ``batch`` prompts, runs a few decode steps, then runs ONE
 eager (graph-free) decode step inside a cudaProfilerStart/Stop window so that
@@ -12,13 +12,18 @@ from __future__ import annotations
 import argparse
 from dataclasses import replace
 
+import os as _os
+import sys as _sys
+
+_sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+
 import torch
 
-from .. import config
-from ..engine import LLMEngine, SamplingParams
-from ..models.llm import config as C
-from ..models.llm.transformer import DecoderModel
-from . import profiling
+from hartsyinference_b200 import config
+from hartsyinference_b200.engine import LLMEngine, SamplingParams
+from hartsyinference_b200.models.llm import config as C
+from hartsyinference_b200.models.llm.transformer import DecoderModel
+from hartsyinference_b200.utils import profiling
 
 
 def main() -> None:

@@ -91,12 +91,15 @@ declare("max_batch", int, 256, "largest decode batch the scheduler forms")
 declare("prefill_chunk", int, 8192, "tokens per prefill chunk")
 declare("fused_comm", bool, True, "use the fused compute+collective kernels; off = NCCL baseline")
 declare("nvls", bool, True, "allow multimem (in-switch) reductions when the symmetric heap has a multicast mapping")
+declare("symm_ipc", bool, False, "map the symmetric heap through CUDA IPC handles even where virtual-memory handles work (no multicast mapping then)")
 declare("wait_budget_ms", int, 2000, "budget of every bounded device-side wait")
 declare("p2p_disable", bool, False, "never map peer memory; collectives fall back to NCCL")
 declare("fp8_linears", bool, True, "quantise eligible linears to 128x128 block-scaled e4m3 at load")
 declare("tc_attention", bool, True, "dense non-causal attention with head dim 128 on the tcgen05 kernel instead of the mma.sync one")
 declare("decode_attn_stages", int, 2, "depth of the paged decode attention kernel's K/V staging ring: 3 (two CTAs per SM at head dim 128) or 2 (three CTAs per SM)")
 declare("cluster_splitk", bool, False, "reduce the K splits of small GEMMs through distributed shared memory of a thread-block cluster instead of a second kernel")
+declare("splitk_second_kernel", bool, True, "sum the K splits of a fully split small GEMM with a second, machine-wide kernel (on) or inside the GEMM by the last CTA to arrive at each tile (off)")
+declare("kernels_lib", str, "", "path of another build of libb200_kernels.so to load instead of the in-tree one")
 declare("pdl", bool, True, "launch GEMMs with programmatic dependent launch so that weight tiles are requested while the preceding kernel still runs")
 declare("fp8_scales", str, "ue8m0", "block-scale format of fp8 linears: ue8m0 (power-of-two scales applied by the tensor core) or fp32 (promoted per K block by the epilogue warps)")
 declare("gguf_resident", bool, False, "keep Q8_0 / Q4_K GGUF linears as quantised blocks on the device (integer-dot GEMV at decode) instead of dequantising at load")

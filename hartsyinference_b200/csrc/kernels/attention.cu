@@ -43,6 +43,11 @@ struct AttnParams {
   float scale_log2;             // softmax scale * log2(e)
   float softcap;                // 0 = off; scores = cap * tanh(scores / cap) (pre-scale units)
   float scale;                  // plain softmax scale (needed with softcap)
+  // decode, head dim 128, split path: the combine kernel also emits the output as e4m3 with one
+  // scale per head (= one 1x128 group of the following linear's input), saving a quantise kernel
+  uint8_t* out_q;               // [seqs][hq * d] or null
+  void* out_scale;              // fp32 [seqs][hq], or blocked UE8M0 bytes when sf_tile_rows > 0
+  int sf_tile_rows;
 };
 
 // Shared-memory tile: [64 tokens][D] bf16, row pitch D * 2 bytes, 16-byte chunks XOR-swizzled with
@@ -350,8 +355,42 @@ __global__ void attn_combine_kernel(const AttnParams p) {
       acc += p.ws_o[(base + s) * D + c] * f;
       ll += p.ws_ml[(base + s) * 2 + 1] * f;
     }
-    p.out[(static_cast<long long>(seq) * p.hq + head) * D + c] =
-        __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+    const __nv_bfloat16 o = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+    if (p.out) p.out[(static_cast<long long>(seq) * p.hq + head) * D + c] = o;
+    if (D == 128 && p.out_q) {
+      // blockDim == D: every thread holds one value of the head; the head is one quantisation group
+      __shared__ float wmax[4];
+      const float v = __bfloat162float(o);
+      float amax = warp_max(fabsf(v));
+      if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = amax;
+      __syncthreads();
+      amax = fmaxf(fmaxf(wmax[0], wmax[1]), fmaxf(wmax[2], wmax[3]));
+      float sc = fmaxf(amax, 1e-12f) / 448.f, inv = 1.f / sc;
+      uint32_t eb = 127;
+      if (p.sf_tile_rows > 0) {
+        // UE8M0: the smallest power of two >= amax / 448
+        const uint32_t bits = __float_as_uint(amax / 448.f);
+        int e = static_cast<int>(bits >> 23) - 127 + ((bits & 0x7fffffu) != 0 ? 1 : 0);
+        e = max(-126, min(126, e));
+        eb = static_cast<uint32_t>(e + 127);
+        inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+      }
+      p.out_q[(static_cast<long long>(seq) * p.hq + head) * D + c] =
+          static_cast<uint8_t>(__nv_cvt_float_to_fp8(v * inv, __NV_SATFINITE, __NV_E4M3));
+      if (c == 0) {
+        if (p.sf_tile_rows > 0) {
+          // blocked layout: row tiles of sf_tile_rows, K groups of four 128-wide blocks, row r of a
+          // tile at word (r % 32) * 4 + r / 32, K block kb at byte kb % 4
+          const int kgroups = (p.hq * D + 511) >> 9;
+          const int tile = seq / p.sf_tile_rows, r = seq - tile * p.sf_tile_rows;
+          const long long blk = static_cast<long long>(tile) * kgroups + (head >> 2);
+          static_cast<uint8_t*>(p.out_scale)[(blk * 128 + (r & 31) * 4 + (r >> 5)) * 4 + (head & 3)] =
+              static_cast<uint8_t>(eb);
+        } else {
+          static_cast<float*>(p.out_scale)[static_cast<long long>(seq) * p.hq + head] = sc;
+        }
+      }
+    }
   }
 }
 
@@ -504,8 +543,10 @@ B200_API void b200_attn_set_decode_stages(int stages) { g_decode_stages = stages
 B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
                               const int* block_table, const int* kv_lens, int seqs, int hq, int hkv,
                               int d, int page, int max_pages, int splits, void* workspace,
-                              float scale, float softcap, int window, cudaStream_t stream) {
+                              float scale, float softcap, int window, void* out_q, void* out_scale,
+                              int sf_tile_rows, cudaStream_t stream) {
   if (seqs <= 0) return 0;
+  if (out_q != nullptr && (d != 128 || splits <= 1 || out_scale == nullptr)) return -6;   // combine kernel only
   if (d != 64 && d != 128) return -2;
   if (hq % hkv != 0 || hq / hkv > 16) return -3;
   if (splits > 1 && !workspace) return -5;
@@ -524,6 +565,9 @@ B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.softcap = softcap;
+  p.out_q = static_cast<uint8_t*>(out_q);
+  p.out_scale = out_scale;
+  p.sf_tile_rows = sf_tile_rows;
   if (p.splits > 1) {
     p.ws_o = static_cast<float*>(workspace);
     p.ws_ml = p.ws_o + static_cast<long long>(seqs) * hq * p.splits * d;
@@ -532,10 +576,10 @@ B200_API int b200_attn_decode(const void* q, const void* k_cache, const void* v_
   // staging ring depth: 3 tiles (two CTAs per SM at d = 128) or 2 tiles (three CTAs per SM)
   const int stages = g_decode_stages == 2 ? 2 : 3;
   const int smem = stages * 2 * kTileTokens * d * 2;
-  static bool attr_set[2][2] = {{false, false}, {false, false}};
-  bool& done = attr_set[d == 128 ? 1 : 0][stages - 2];
+  static PerDeviceOnce attr_set[2][2];
+  PerDeviceOnce& once = attr_set[d == 128 ? 1 : 0][stages - 2];
   auto launch = [&](auto kernel) {
-    if (!done) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); done = true; }
+    if (once.first_time()) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     launch_pdl(kernel, grid, dim3(kAttnThreads), smem, stream, p);
   };
   if (d == 128) {
@@ -587,12 +631,10 @@ B200_API int b200_attn_prefill(const void* q, const void* k, const void* v, void
   const int smem = 2 * 2 * kTileTokens * d * 2;
 #define LAUNCH_PREFILL(DD, PG)                                                                   \
   do {                                                                                           \
-    static bool done = false;                                                                    \
-    if (!done) {                                                                                 \
+    static PerDeviceOnce once;                                                                   \
+    if (once.first_time())                                                                       \
       cudaFuncSetAttribute(attn_prefill_kernel<DD, PG>,                                          \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                   \
-      done = true;                                                                               \
-    }                                                                                            \
     attn_prefill_kernel<DD, PG><<<grid, kAttnThreads, smem, stream>>>(p);                        \
   } while (0)
   if (d == 128) {

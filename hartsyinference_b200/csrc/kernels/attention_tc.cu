@@ -335,10 +335,9 @@ B200_API int b200_attn_tc(const void* q, const void* k, const void* v, void* out
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = static_cast<DeviceStatus*>(status);
   const int smem = 6 * kAtTileBytes + static_cast<int>(sizeof(AttnTcBarriers)) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first_time()) {
     if (cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
-    configured = true;
   }
   dim3 grid((sq + kAtTile - 1) / kAtTile, heads, batch);
   attn_tc_kernel<<<grid, kAtThreads, smem, stream>>>(p, tq, tk, tv);

@@ -174,6 +174,23 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_smem_addr, uint32_t
 }
 
 // ---------------------------------------------------------------------------------------------
+// Per-device one-time set-up. Function attributes (dynamic shared memory limit) and device
+// properties belong to a device, not to the process: one process may drive several GPUs, so the
+// "done once" marks are kept per device ordinal.
+// ---------------------------------------------------------------------------------------------
+struct PerDeviceOnce {
+  bool done[64] = {};
+  // True exactly once per device (always true for ordinals past the table, which only repeats work).
+  bool first_time() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
 // Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute
 // may start before its predecessor in the stream has finished; pdl_wait() blocks until the
 // predecessor grid has completed and its writes are visible (a no-op for an ordinary launch).

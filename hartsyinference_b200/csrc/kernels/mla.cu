@@ -386,12 +386,11 @@ B200_API int b200_mla_attn(const void* q, const void* cache, void* out, const in
   p.rows = rows; p.heads = heads; p.page = page; p.page_shift = shift; p.table_stride = table_stride;
   p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
-  static bool configured = false;
+  static PerDeviceOnce configured;
   const int smem = static_cast<int>(sizeof(MlaSmem));
-  if (!configured) {
+  if (configured.first_time()) {
     if (cudaFuncSetAttribute(mla_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return -4;
-    configured = true;
   }
   const dim3 grid((heads + 15) / 16, rows, splits);
   mla_attn_kernel<<<grid, kMlaThreads, smem, stream>>>(p);

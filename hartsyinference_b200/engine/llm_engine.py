@@ -22,7 +22,7 @@ from typing import Callable, Optional, Sequence
 import torch
 
 from .. import config, log, ops
-from ..exceptions import HartsyInferenceError
+from ..exceptions import DeviceWaitTimeout, HartsyInferenceError
 from ..models.llm.transformer import DecoderModel, ForwardBatch
 from ..ops import _native as N
 from ..runtime import KvAllocator, SchedulerCore
@@ -115,6 +115,10 @@ class LLMEngine:
         self.h_cu_q = torch.zeros(cap_seqs + 1, dtype=torch.int32, pin_memory=pin)
         self.h_rows = torch.zeros(cap_seqs, dtype=torch.int64, pin_memory=pin)
         self.h_out = torch.zeros(cap_seqs, dtype=torch.int32, pin_memory=pin)
+        self.h_status = torch.zeros(4, dtype=torch.int32, pin_memory=pin)
+        # called with [code, kernel, site, detail] when a kernel's bounded wait ran out, before the
+        # step's requests are failed; a service hangs its fallback (e.g. back to NCCL) here
+        self.on_device_fault: Optional[Callable[[list], None]] = None
         if self.cuda:
             N.reserve_workspace(self.device, 256 << 20)
             N.state(self.device).gemm_workspace()
@@ -255,16 +259,31 @@ class LLMEngine:
                 done.append((req, -1))
         return done
 
+    def _read_tokens(self, dev_tokens: torch.Tensor, n: int) -> list[int]:
+        """Sampled ids and the kernels' status word come back in the same synchronising read. A
+        recorded wait timeout (a peer that stopped signalling) fails this step's requests instead
+        of letting them continue on garbage."""
+        self.h_out[:n].copy_(dev_tokens[:n], non_blocking=True)
+        self.h_status.copy_(N.state(self.device).status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes_last += n * 4 + 16
+        if int(self.h_status[0]) != 0:
+            vals = self.h_status.tolist()
+            N.state(self.device).reset_after_fault()
+            self._graphs.clear()
+            if self.on_device_fault is not None:
+                self.on_device_fault(vals)
+            raise DeviceWaitTimeout(f"device wait failed: code={vals[0]} kernel={vals[1]} site={vals[2]} "
+                                    f"detail={vals[3]}", kernel=vals[1], site=vals[2], detail=vals[3])
+        return self.h_out[:n].tolist()
+
     def _sample(self, hidden: torch.Tensor, reqs: list[Request]) -> list[int]:
         """hidden [n, H] for n requests -> one sampled token each."""
         n = len(reqs)
         if all(not r.params.needs_logits for r in reqs):
             tok = self.model.greedy_tokens(hidden)
             if self.cuda:
-                self.h_out[:n].copy_(tok, non_blocking=True)
-                torch.cuda.current_stream().synchronize()
-                self.d2h_bytes_last += n * 4
-                return self.h_out[:n].tolist()
+                return self._read_tokens(tok, n)
             return tok.tolist()
         logits = self.model.full_logits(hidden).float()
         out = []
@@ -381,10 +400,7 @@ class LLMEngine:
         st["kv_lens"].copy_(self.h_kv_lens[:bucket], non_blocking=True)
         self.h2d_bytes_last += bucket * (4 + 4 + 8 + 4 + 4 * mp)
         graph.replay()
-        self.h_out[:bucket].copy_(st["out"], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        self.d2h_bytes_last += bucket * 4
-        return self.h_out[:n].tolist()
+        return self._read_tokens(st["out"], bucket)[:n]
 
     def _capture(self, bucket: int):
         dev, mp = self.device, self.max_pages_per_seq

@@ -154,6 +154,9 @@ class DecoderModel:
         # latency-oriented all-reduce over the symmetric heap (parallel/custom_ar.py): the row-parallel
         # GEMM writes into its input buffer, tensors that do not fit go through ``all_reduce``
         self.custom_ar = None
+        # fused row-parallel linear + all-reduce + residual + RMSNorm (+ fp8 emit) kernel
+        # (parallel/fused.py::FusedRowParallel); drives the whole layer loop of small batches
+        self.fused_rp = None
 
     # ------------------------------------------------------------------------------ weights
     def _lw(self, w: torch.Tensor, bias: Optional[torch.Tensor] = None, allow_fp8: bool = True) -> LinearWeight:
@@ -520,10 +523,16 @@ class DecoderModel:
     # ------------------------------------------------------------------------------ layer pieces
     def _attention(self, lw: LayerWeights, li: int, h: torch.Tensor, hq8, batch: ForwardBatch, scale: float) -> torch.Tensor:
         """qkv projection, (q/k norm,) rotary + KV-cache write, paged attention, output projection."""
-        cfg, d = self.cfg, self.cfg.head_dim
         if lw.attn_module is not None:
             return lw.attn_module(h, batch, li, self)
-        t = h.shape[0]
+        return self._reduce_linear(self._attention_core(lw, li, h, hq8, batch, scale), lw.o)
+
+    def _attention_core(self, lw: LayerWeights, li: int, h: Optional[torch.Tensor], hq8, batch: ForwardBatch,
+                        scale: float) -> torch.Tensor:
+        """Everything of the attention block before the output projection: [T, local heads * d]
+        (bf16, or already quantised for an fp8 output projection at decode)."""
+        cfg, d = self.cfg, self.cfg.head_dim
+        t = (h if h is not None else hq8.data).shape[0]
         qkv = ops.linear(hq8 if hq8 is not None else h, lw.qkv)
         q_norm_w, k_norm_w = lw.q_norm, lw.k_norm
         if cfg.qk_norm_full and q_norm_w is not None:
@@ -562,6 +571,12 @@ class DecoderModel:
                                         softcap=cfg.attn_softcap, window=window, alibi=self.alibi_slopes,
                                         sinks=lw.sinks)
         elif batch.is_decode:
+            if self.fp8 and q.is_cuda and lw.o is not None and lw.o.is_fp8 and d == 128:
+                # the split-combine kernel emits the o-projection's fp8 input itself
+                _, att8 = ops.attn_decode(q, kc, vc, batch.block_table, batch.kv_lens, scale=scale,
+                                          softcap=cfg.attn_softcap, window=window,
+                                          max_kv_len=batch.max_kv_len or None, emit_fp8=True, emit_bf16=False)
+                return att8
             att = ops.attn_decode(q, kc, vc, batch.block_table, batch.kv_lens, scale=scale,
                                   softcap=cfg.attn_softcap, window=window,
                                   max_kv_len=batch.max_kv_len or None)
@@ -569,7 +584,7 @@ class DecoderModel:
             att = ops.attn_prefill_paged(q, kc, vc, batch.block_table, batch.kv_lens, batch.cu_q,
                                          batch.max_q_len, causal=True, scale=scale,
                                          softcap=cfg.attn_softcap, window=window)
-        return self._reduce_linear(att.reshape(t, self.hq * d), lw.o)
+        return att.reshape(t, self.hq * d)
 
     def _mrope(self, qkv: torch.Tensor, positions3: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
         """Rotary embedding whose frequency pairs are split into three sections, driven by the time,
@@ -690,6 +705,54 @@ class DecoderModel:
             return x, None
         return self._block_norm(x, self.final_norm, self.final_norm_b)
 
+    def _fused_tp_ok(self, tokens: int) -> bool:
+        """True when the layer loop can run on the fused row-parallel kernel: a plain pre-norm
+        RMSNorm decoder with dense gated feed-forward blocks, held completely by this instance."""
+        cfg, frp = self.cfg, self.fused_rp
+        if frp is None or self.tp <= 1 or not (self.first_stage and self.last_stage):
+            return False
+        if not frp.supports(tokens, cfg.hidden_size) or cfg.general_path or not cfg.gated_ffn:
+            return False
+        if cfg.residual_multiplier != 1.0 or cfg.post_norms or cfg.activation not in ("silu", "gelu_tanh"):
+            return False
+        return all(lw.qkv is not None and lw.o is not None and lw.gate_up is not None and lw.down is not None
+                   and lw.o.bias is None and lw.down.bias is None and lw.post_attn_norm is None
+                   and lw.post_ffn_norm is None and lw.cross is None for lw in self.layers)
+
+    def _forward_fused_tp(self, batch: ForwardBatch, x: torch.Tensor) -> torch.Tensor:
+        """Layer loop of a tensor-parallel rank for at most 128 tokens. Per layer:
+
+            qkv GEMM -> rope + KV write -> attention -> o GEMM    [all-reduce + residual + norm + fp8 emit]
+            gate|up GEMM -> GLU (fp8 emit) -> down GEMM           [all-reduce + residual + norm + fp8 emit]
+
+        where each bracket is the epilogue of the GEMM before it (one kernel), and the second
+        bracket already applies the NEXT layer's input norm (the final norm after the last layer).
+        The residual stream ``res`` is sharded by token row: each rank keeps only the rows it owns
+        up to date, the kernel updates them in place."""
+        cfg, frp = self.cfg, self.fused_rp
+        fp8 = self.fp8
+        scale = self._attn_scale()
+        kw = dict(eps=cfg.rms_eps, weight_plus_one=cfg.norm_plus_one)
+        lw0 = self.layers[0]
+        q8 = fp8 and lw0.qkv.is_fp8
+        h, _, hq8 = ops.norm(x, lw0.in_norm, emit_fp8=q8, emit_bf16=not q8, **kw)
+        res = x.clone() if batch.embeds is not None else x
+        last = len(self.layers) - 1
+        for li, lw in enumerate(self.layers):
+            att = self._attention_core(lw, li, h, hq8, batch, scale)
+            g8 = fp8 and lw.gate_up.is_fp8
+            h2, h2q8 = frp(att, lw.o, res=res, norm_w=lw.post_norm, emit_fp8=g8, emit_bf16=not g8, **kw)
+            gu = ops.linear(h2q8 if h2q8 is not None else h2, lw.gate_up)
+            d8 = fp8 and lw.down.is_fp8
+            act, act8 = ops.glu(gu, cfg.activation, emit_fp8=d8, emit_bf16=not d8)
+            if li == last:
+                h, hq8 = frp(act8 if act8 is not None else act, lw.down, res=res, norm_w=self.final_norm, **kw)
+            else:
+                n8 = fp8 and self.layers[li + 1].qkv.is_fp8
+                h, hq8 = frp(act8 if act8 is not None else act, lw.down, res=res,
+                             norm_w=self.layers[li + 1].in_norm, emit_fp8=n8, emit_bf16=not n8, **kw)
+        return h
+
     def forward_hidden(self, batch: ForwardBatch, hidden_in: Optional[tuple] = None):
         """Runs this instance's layers. The last pipeline stage (the only one by default) returns the
         final-normed hidden states [T, H]; an earlier stage returns ``(x, residual)`` for the next
@@ -711,6 +774,8 @@ class DecoderModel:
         fp8 = self.fp8 and x.is_cuda
         if cfg.general_path:
             return self._forward_general(batch, x if res is None else (x.float() + res.float()).to(x.dtype), scale)
+        if hidden_in is None and x.is_cuda and self._fused_tp_ok(x.shape[0]):
+            return self._forward_fused_tp(batch, x)
         for li, lw in enumerate(self.layers):
             # ---- attention block
             if res is None:

@@ -27,6 +27,7 @@ _SIGNATURES = {
     "b200_gemm_workspace_bytes": (i64, []),
     "b200_gemm_set_pdl": (None, [i32]),
     "b200_gemm_set_cluster_reduce": (None, [i32]),
+    "b200_gemm_set_external_reduce": (None, [i32]),
     "b200_attn_set_decode_stages": (None, [i32]),
     "b200_gemm_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, i64, vp, vp]),
     "b200_gemm_colbatched": (i32, [vp, vp, vp, i32, i32, i32, i32, i64, i32, i64, i32, vp, i64, vp, vp]),
@@ -59,7 +60,7 @@ _SIGNATURES = {
     "b200_gated_residual": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "b200_dit_qkv": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i64, f32, vp]),
     "b200_fill_random": (i32, [vp, i64, u64, f32, i32, vp]),
-    "b200_attn_decode": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, f32, f32, i32, vp]),
+    "b200_attn_decode": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, f32, f32, i32, vp, vp, i32, vp]),
     "b200_attn_decode_pick_splits": (i32, [i32, i32, i32]),
     "b200_attn_decode_workspace_bytes": (i64, [i32, i32, i32, i32]),
     "b200_attn_prefill": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, vp]),
@@ -67,9 +68,9 @@ _SIGNATURES = {
 
 
 def lib_path() -> Path:
-    """The kernels library; ``B200_KERNELS_LIB`` points at another build of it (kernel experiments)."""
-    import os
-    override = os.environ.get("B200_KERNELS_LIB")
+    """The kernels library (flag ``kernels_lib`` points at another build of it)."""
+    from .. import config
+    override = config.get("kernels_lib")
     return Path(override) if override else _LIB_DIR / "libb200_kernels.so"
 
 
@@ -100,6 +101,7 @@ def lib() -> C.CDLL:
             try:
                 handle.b200_gemm_set_pdl(1 if config.get("pdl") else 0)
                 handle.b200_gemm_set_cluster_reduce(1 if config.get("cluster_splitk") else 0)
+                handle.b200_gemm_set_external_reduce(1 if config.get("splitk_second_kernel") else 0)
                 handle.b200_attn_set_decode_stages(int(config.get("decode_attn_stages")))
             except AttributeError:
                 pass
@@ -145,10 +147,20 @@ class _DeviceState:
 
     def gemm_workspace(self) -> torch.Tensor:
         """Zero-initialised scratch of the GEMM's K-split path (tile counters + fp32 partials). The
-        kernel leaves the counters at zero, so it is cleared only here, once."""
+        kernel leaves the counters at zero, so it is cleared here, once, and again only after a
+        reported wait timeout (:meth:`reset_after_fault`)."""
         if self._gemm_ws is None:
             self._gemm_ws = torch.zeros(lib().b200_gemm_workspace_bytes(), dtype=torch.uint8, device=self.device)
         return self._gemm_ws
+
+    def reset_after_fault(self) -> None:
+        """Clear the status word and the split-K arrival counters (the first 16 KB of the GEMM
+        scratch). A GEMM whose wait ran out skips its arrival, so the counters of its tiles are
+        left non-zero and every later GEMM that reuses those slots would mis-detect its last
+        arrival; after a reported timeout they have to be zeroed again."""
+        self.status.zero_()
+        if self._gemm_ws is not None:
+            self._gemm_ws[:16384].zero_()
 
     def scratch(self, nbytes: int) -> torch.Tensor:
         if self.workspace.numel() < nbytes:
@@ -182,7 +194,7 @@ def check_status(device: Optional[torch.device] = None, reset: bool = True) -> N
     vals = st.status.cpu().tolist()
     if vals[0] != 0:
         if reset:
-            st.status.zero_()
+            st.reset_after_fault()
         raise DeviceWaitTimeout(
             f"device wait failed: code={vals[0]} kernel={vals[1]} site={vals[2]} detail={vals[3]}",
             kernel=vals[1], site=vals[2], detail=vals[3])

@@ -337,8 +337,12 @@ def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, hq: int, hkv: int, d: in
 
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                 kv_lens: torch.Tensor, scale: Optional[float] = None, softcap: float = 0.0,
-                window: int = 0, splits: Optional[int] = None, max_kv_len: Optional[int] = None) -> torch.Tensor:
-    """One query token per sequence against a paged KV pool. q [B, hq, d] -> [B, hq, d]."""
+                window: int = 0, splits: Optional[int] = None, max_kv_len: Optional[int] = None,
+                emit_fp8: bool = False, emit_bf16: bool = True):
+    """One query token per sequence against a paged KV pool. q [B, hq, d] -> [B, hq, d].
+    With ``emit_fp8`` the result is ``(out, Fp8Act of out.reshape(B, hq * d))``: quantised by the
+    split-combine kernel itself when it runs (head dim 128, more than one KV split; ``out`` is then
+    None unless ``emit_bf16``), by a separate kernel otherwise."""
     b, hq, d = q.shape
     hkv, page = k_cache.shape[1], k_cache.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
@@ -350,9 +354,9 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
             vv = R.gather_paged(v_cache, block_table[i], ln)
             outs.append(R.attention(q[i:i + 1], kk, vv, causal=False, scale=scale, softcap=softcap,
                                     window=window))
-        return torch.cat(outs, 0).to(q.dtype)
+        o = torch.cat(outs, 0).to(q.dtype)
+        return (o, quant_fp8_act(o.reshape(b, hq * d))) if emit_fp8 else o
     assert block_table.dtype == torch.int32 and kv_lens.dtype == torch.int32
-    out = torch.empty_like(q)
     L = N.lib()
     if splits is None:
         mk = max_kv_len if max_kv_len is not None else block_table.shape[1] * page
@@ -360,11 +364,23 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, b
     ws = None
     if splits > 1:
         ws = N.state(q.device).scratch(L.b200_attn_decode_workspace_bytes(b, hq, d, splits)).data_ptr()
-    rc = L.b200_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+    fused_q = emit_fp8 and d == 128 and splits > 1
+    out = torch.empty_like(q) if (emit_bf16 or not fused_q) else None
+    oq = osc = None
+    mx = fp8_mx()
+    if fused_q:
+        oq = torch.empty(b, hq * d, dtype=torch.uint8, device=q.device)
+        osc = _alloc_sf(b, hq * d, 128, q.device) if mx else torch.empty(b, hq, dtype=torch.float32, device=q.device)
+    rc = L.b200_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), N.ptr(out),
                             block_table.data_ptr(), kv_lens.data_ptr(), b, hq, hkv, d, page,
-                            block_table.shape[1], splits, ws, scale, softcap, window, N.stream())
+                            block_table.shape[1], splits, ws, scale, softcap, window, N.ptr(oq), N.ptr(osc),
+                            128 if (fused_q and mx) else 0, N.stream())
     N.check(rc, "b200_attn_decode", 2 if splits > 1 else 1)
-    return out
+    if not emit_fp8:
+        return out
+    if fused_q:
+        return out, (Fp8Act(oq, None, osc, 128) if mx else Fp8Act(oq, osc))
+    return out, quant_fp8_act(out.reshape(b, hq * d))
 
 
 def attn_paged_biased(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,

@@ -1,6 +1,7 @@
 """Latency-oriented all-reduce for decode-sized tensors (``b200_allreduce``,
-csrc/kernels/allreduce.cu): one kernel, two-shot over NVLink peer loads / stores in the CUDA-IPC
-symmetric heap, device-resident call counter (CUDA-graph capturable), bounded waits.
+csrc/kernels/allreduce.cu): one kernel over the symmetric heap, in-switch reduction and multicast
+stores (``multimem``) when the heap has a multicast mapping, peer loads / stores otherwise;
+device-resident call counters (CUDA-graph capturable), bounded waits.
 
 The producer GEMM writes its partial result straight into the heap's input buffer
 (:meth:`CustomAllReduce.input`), so the collective adds no copy. Larger tensors and groups without
@@ -25,21 +26,21 @@ class CustomAllReduce:
         self.rank, self.world = comm.rank, comm.world
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.max_elems = max_elems
-        L = N.lib()
         vp, i32, i64 = C.c_void_p, C.c_int, C.c_longlong
-        self._flag_bytes = N.bind("b200_allreduce_flag_bytes", i64, [])()
-        self._fn = N.bind("b200_allreduce", i32, [vp, vp, vp, vp, vp, vp, i64, i32, i32, i64, vp, vp])
+        self._fn = N.bind("b200_allreduce", i32, [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, vp, vp])
         buf = max_elems * 2
-        self.heap = SymmetricHeap(comm, buf * (1 + num_out_buffers) + self._flag_bytes + 8192, self.device)
+        self.heap = SymmetricHeap(comm, buf * (1 + num_out_buffers) + 8192, self.device)
+        self.use_mc = self.heap.has_multicast
         self.off_in = self.heap.alloc(buf)
         self.off_out = [self.heap.alloc(buf) for _ in range(num_out_buffers)]
-        self.off_flags = self.heap.alloc(self._flag_bytes)
+        self.off_flags = self.heap.alloc(256)
         self.off_ctr = self.heap.alloc(256)
-        self._in = self.heap.ptr_array(self.off_in)
-        self._outs = [self.heap.ptr_array(o) for o in self.off_out]
-        self._flags = self.heap.ptr_array(self.off_flags)
-        self._epoch = self.heap.ptr(self.rank, self.off_ctr)
-        self._fin = self.heap.ptr(self.rank, self.off_ctr + 64)
+        arr = self.heap.mc_array if self.use_mc else self.heap.ptr_array
+        self._in = arr(self.off_in)
+        self._outs = [arr(o) for o in self.off_out]
+        self._flags = arr(self.off_flags)
+        self._flags_local = self.heap.ptr(self.rank, self.off_flags)
+        self._ctr = self.heap.ptr(self.rank, self.off_ctr)
         self._next = 0
         self.budget_cycles = int(config.get("wait_budget_ms")) * 2_000_000
 
@@ -57,8 +58,9 @@ class CustomAllReduce:
         slot = self._next
         self._next = (self._next + 1) % len(self.off_out)
         st = N.state(self.device)
-        rc = self._fn(self._in, self._outs[slot], self._flags, self._epoch, self._fin, N.ptr(residual), m * n,
-                      self.rank, self.world, self.budget_cycles, st.status.data_ptr(), N.stream())
+        rc = self._fn(self._in, self._outs[slot], self._flags, self._flags_local, self._ctr, N.ptr(residual), m * n,
+                      self.rank, self.world, 1 if self.use_mc else 0, self.budget_cycles, st.status.data_ptr(),
+                      N.stream())
         N.check(rc, "b200_allreduce")
         return self.heap.tensor(self.off_out[slot], (m, n), torch.bfloat16)
 

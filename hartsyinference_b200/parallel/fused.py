@@ -1,16 +1,21 @@
 """Fused compute + collective paths for tensor parallelism.
 
 ``FusedRowParallel`` runs the row-parallel linears of a TP group (attention output projection,
-FFN down projection) as ONE kernel per linear: tcgen05 GEMM tiles whose epilogue pushes the bf16
-partial tile over NVLink into the rank that owns those output columns, the owner reduces in fp32
-(+ bias / residual) and pushes the result into every rank's output buffer
-(``b200_gemm_allreduce``, csrc/kernels/gemm_tcgen05.cu). It covers token counts up to 128 (the
-decode regime, where the all-reduce is latency-bound); larger batches use the plain GEMM and an
-NCCL all-reduce, which is also the measured baseline of the fused path.
+FFN down projection) as ONE kernel per linear (``b200_gemm_allreduce``,
+csrc/kernels/gemm_tcgen05.cu): tcgen05 GEMM tiles of the rank's partial product are stored into
+the rank's own part of the symmetric heap; each rank then pulls the token rows it owns summed over
+all ranks (``multimem.ld_reduce``: the NVSwitch adds the copies; peer loads when the heap has no
+multicast mapping), adds the residual row, applies the RMSNorm that follows the linear, optionally
+quantises to e4m3 for the next linear, and stores the result into every rank (``multimem.st``).
+So the all-reduce, the residual add, the norm and the activation quantisation of the next GEMM
+are the epilogue of the GEMM. It covers token counts up to 128 (the decode regime, where the
+all-reduce is latency-bound); larger batches use the plain GEMM and an NCCL all-reduce, which is
+also the measured baseline of the fused path.
 
 The reference performs the same two reductions per layer with ``AllReduceSum`` after the o-proj and
 the down-proj (src/HartsyInference.LLM/Transformer/TensorParallelTransformer.cs:298,307) through
-NCCL calls issued by one thread for all ranks (src/HartsyInference.Cuda/NcclComm.cs:53-85).
+NCCL calls issued by one thread for all ranks (src/HartsyInference.Cuda/NcclComm.cs:53-85), and
+runs the residual add + norm as separate kernels afterwards.
 """
 from __future__ import annotations
 
@@ -26,63 +31,115 @@ from .comm import Comm
 from .symm import SymmetricHeap
 
 MAX_TOKENS = 128
-STAGE_SPLITS = 4      # K splits per rank that the staging buffer has slots for
+PART_SPLITS = 4       # K splits per rank that the partial buffer has room for
 
 
 class FusedRowParallel:
     def __init__(self, comm: Comm, max_features: int, device: Optional[torch.device] = None,
-                 num_out_buffers: int = 2):
+                 num_out_buffers: int = 2, emulate_peers: bool = False):
+        """``emulate_peers`` (measurement aid for one GPU): ``comm`` claims a rank of a larger world
+        but has no peers; every "peer" address is this GPU's own buffer, so the kernel runs the full
+        protocol of that rank (its row share, one signal per pretended peer) with meaningless sums."""
         self.comm = comm
         self.rank, self.world = comm.rank, comm.world
         self.device = device or torch.device("cuda", torch.cuda.current_device())
+        heap_comm = comm
+        if emulate_peers:
+            from .comm import SingleComm
+            heap_comm = SingleComm()
         self.max_features = max_features
-        tiles = (max_features + 127) // 128
-        stage_bytes = STAGE_SPLITS * tiles * 128 * 128 * 2   # [world * splits][tiles/world][128][128] bf16
-        out_bytes = MAX_TOKENS * max_features * 2
-        flags_bytes = 4096
-        self.heap = SymmetricHeap(comm, stage_bytes + num_out_buffers * out_bytes + flags_bytes + 4096, self.device)
-        self.off_stage = self.heap.alloc(stage_bytes)
-        self.off_out = [self.heap.alloc(out_bytes) for _ in range(num_out_buffers)]
-        self.off_flags = self.heap.alloc(flags_bytes)
-        # flags region: [0, 2048) tile flags (u32 each), 2048: done, 2304: epoch, 2560: fin
-        self._stage = self.heap.ptr_array(self.off_stage)
-        self._outs = [self.heap.ptr_array(o) for o in self.off_out]
-        self._tile_flag = self.heap.ptr_array(self.off_flags)
-        self._done = self.heap.ptr_array(self.off_flags + 2048)
-        self._epoch = self.heap.ptr(self.rank, self.off_flags + 2304)
-        self._fin = self.heap.ptr(self.rank, self.off_flags + 2560)
+        f = max_features
+        part_bytes = PART_SPLITS * MAX_TOKENS * f * 2
+        bf16_bytes = MAX_TOKENS * f * 2
+        q_bytes = MAX_TOKENS * f
+        sf_bytes = max(MAX_TOKENS * ((f + 127) // 128) * 4, ((f + 511) // 512) * 512)
+        per_slot = bf16_bytes + q_bytes + sf_bytes + 3 * 256
+        self.heap = SymmetricHeap(heap_comm, part_bytes + num_out_buffers * per_slot + 4096, self.device)
+        self.use_mc = self.heap.has_multicast
+        self.off_part = self.heap.alloc(part_bytes)
+        self.off_bf16 = [self.heap.alloc(bf16_bytes) for _ in range(num_out_buffers)]
+        self.off_q = [self.heap.alloc(q_bytes) for _ in range(num_out_buffers)]
+        self.off_sf = [self.heap.alloc(sf_bytes) for _ in range(num_out_buffers)]
+        self.off_flags = self.heap.alloc(256)
+        self.off_ctr = self.heap.alloc(256)
+        arr = self.heap.mc_array if self.use_mc else self.heap.ptr_array
+        own = 0 if emulate_peers else self.rank
+        if emulate_peers:
+            def arr(off, _w=self.world, _h=self.heap):
+                a = (C.c_void_p * _w)()
+                for r in range(_w):
+                    a[r] = _h.ptr(0, off)
+                return a
+        self._part = self.heap.ptr(own, self.off_part)
+        self._part_src = arr(self.off_part)
+        self._bf16 = [arr(o) for o in self.off_bf16]
+        self._q = [arr(o) for o in self.off_q]
+        self._sf = [arr(o) for o in self.off_sf]
+        self._flags = arr(self.off_flags)
+        self._flags_local = self.heap.ptr(own, self.off_flags)
+        self._ctr = self.heap.ptr(own, self.off_ctr)
         self._next = 0
         vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
         self._fn = N.bind("b200_gemm_allreduce", i32,
-                          [vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, vp, vp, i32,
-                           vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, vp, vp])
+                          [vp, vp, i32, i32, i32, i64, i64, i32, vp, vp, vp, vp, vp, f32, i32, vp, vp, vp, vp, vp,
+                           i32, vp, vp, vp, i32, i32, i32, i32, i64, i32, vp, vp])
         self.budget_cycles = int(config.get("wait_budget_ms")) * 2_000_000
+        self.debug_skip_ready = False    # tests: withhold this rank's "ready" signal once per call
+
+    def reset(self) -> None:
+        """Clear the counters on every rank (all ranks call this together, with no call in
+        flight). Needed after a wait that ran out: the cumulative counters no longer agree."""
+        torch.cuda.synchronize(self.device)
+        self.comm.barrier()
+        self.heap.tensor(self.off_flags, (64,), torch.int32).zero_()
+        self.heap.tensor(self.off_ctr, (64,), torch.int32).zero_()
+        torch.cuda.synchronize(self.device)
+        self.comm.barrier()
 
     def supports(self, m: int, n: int) -> bool:
-        return m <= MAX_TOKENS and n <= self.max_features and n % (128 * self.world) == 0
+        return 0 < m <= MAX_TOKENS and n <= self.max_features and n % 128 == 0
 
-    def __call__(self, x, w: LinearWeight, residual: Optional[torch.Tensor] = None, act: Optional[str] = None,
-                 gate: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """All ranks call this together. Returns the reduced [m, n] bf16 result, a view of one of
-        the heap's output buffers (valid until the buffer comes round again)."""
+    def __call__(self, x, w: LinearWeight, *, res: Optional[torch.Tensor] = None,
+                 norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6, weight_plus_one: bool = False,
+                 emit_bf16: bool = True, emit_fp8: bool = False):
+        """All ranks call this together. ``res`` ([m, n] bf16, contiguous) is this rank's residual
+        stream: the rows the rank owns (a contiguous block of ceil(m / world)) are read and updated
+        in place, the other rows are left alone. Returns ``(h, h_fp8)``: the all-reduced (+ residual,
+        + RMSNorm) activations as a bf16 tensor and / or an :class:`Fp8Act`, both views of the
+        heap's output buffers (valid until the buffer comes round again, ``num_out_buffers`` calls
+        later)."""
         if w.is_fp8 and not isinstance(x, Fp8Act):
             x = ops.quant_fp8_act(x, mx=w.is_mx)
         xd = x.data if isinstance(x, Fp8Act) else x
         m, k = xd.shape
         n = w.weight.shape[0]
+        assert self.supports(m, n), (m, n)
+        assert res is None or (res.is_contiguous() and res.shape == (m, n) and res.dtype == torch.bfloat16)
         slot = self._next
-        self._next = (self._next + 1) % len(self.off_out)
+        self._next = (self._next + 1) % len(self.off_bf16)
         fp8 = w.is_fp8
+        mx_out = emit_fp8 and ops.fp8_mx()
         st = N.state(self.device)
-        rc = self._fn(xd.data_ptr(), w.weight.data_ptr(), m, n, k, xd.stride(0), w.weight.stride(0), n,
+        rc = self._fn(xd.data_ptr(), w.weight.data_ptr(), m, n, k, xd.stride(0), w.weight.stride(0),
                       2 if w.is_mx else 1 if fp8 else 0,
                       None if not fp8 else x.sf.data_ptr() if w.is_mx else x.scale.data_ptr(),
                       None if not fp8 else w.sf.data_ptr() if w.is_mx else w.scale.data_ptr(),
-                      N.ptr(w.bias), N.ptr(gate), N.ptr(residual), {None: 0, "gelu_tanh": 1, "silu": 2}[act],
-                      self._stage, self._outs[slot], self._tile_flag, self._done, self._epoch, self._fin,
-                      self.rank, self.world, STAGE_SPLITS, self.budget_cycles, st.status.data_ptr(), N.stream())
+                      N.ptr(w.bias), N.ptr(res), N.ptr(norm_w), float(eps), int(weight_plus_one),
+                      self._part, self._part_src, self._bf16[slot] if emit_bf16 else None,
+                      self._q[slot] if emit_fp8 else None, self._sf[slot] if emit_fp8 else None,
+                      128 if mx_out else 0, self._flags, self._flags_local, self._ctr,
+                      self.rank, self.world, 1 if self.use_mc else 0, PART_SPLITS, self.budget_cycles,
+                      1 if self.debug_skip_ready else 0, st.status.data_ptr(), N.stream())
         N.check(rc, "b200_gemm_allreduce")
-        return self.heap.tensor(self.off_out[slot], (m, n), torch.bfloat16)
+        h = self.heap.tensor(self.off_bf16[slot], (m, n), torch.bfloat16) if emit_bf16 else None
+        h8 = None
+        if emit_fp8:
+            q = self.heap.tensor(self.off_q[slot], (m, n), torch.uint8)
+            if mx_out:
+                h8 = Fp8Act(q, None, self.heap.tensor(self.off_sf[slot], (1, (n + 511) // 512, 128), torch.int32), 128)
+            else:
+                h8 = Fp8Act(q, self.heap.tensor(self.off_sf[slot], (m, n // 128), torch.float32))
+        return h, h8
 
     def close(self) -> None:
         self.heap.close()
@@ -90,38 +147,43 @@ class FusedRowParallel:
 
 def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_tokens: int = 0) -> bool:
     """Route the model's row-parallel linears through the fused kernel when the shapes allow it.
-    With ``autotune_tokens`` > 0 the fused kernel and GEMM + NCCL all-reduce are both timed on this
-    model's o / down projections at that token count and the faster one is kept.
-    Returns True when the fused path is active."""
+    With ``autotune_tokens`` > 0 three ways of running "row-parallel linear, all-reduce, residual
+    add, RMSNorm, fp8 quantisation" are timed on this model's o / down projections at that token
+    count (the fused kernel; GEMM + peer-memory all-reduce kernel + norm kernel; GEMM + NCCL + norm
+    kernel) and the fastest is kept. Returns True when the fused path is active."""
     if comm.world <= 1 or not config.get("fused_comm") or config.get("p2p_disable"):
         return False
     hidden = model.cfg.hidden_size
-    if hidden % (128 * comm.world) != 0:
-        log.decision("TensorParallel", f"fused all-reduce off: hidden {hidden} not a multiple of {128 * comm.world}")
+    if hidden % 128 != 0:
+        log.decision("TensorParallel", f"fused all-reduce off: hidden {hidden} is not a multiple of 128")
         return False
     fused = FusedRowParallel(comm, hidden, model.device)
 
     def row_parallel(x, w: LinearWeight) -> torch.Tensor:
         m = (x.data if isinstance(x, Fp8Act) else x).shape[0]
         if fused.supports(m, w.weight.shape[0]):
-            return fused(x, w)
+            return fused(x, w)[0]
         y = ops.linear(x, w)
         return comm.all_reduce(y)
 
     model.row_parallel_linear = row_parallel
-    model._fused_tp = fused
+    model.fused_rp = fused
     if autotune_tokens > 0 and model.layers:
         from .custom_ar import CustomAllReduce
         car = CustomAllReduce(comm, MAX_TOKENS * hidden, model.device)
         t_fused, t_car, t_nccl = _measure_row_parallel(model, comm, fused, car, autotune_tokens)
         best = min(t_fused, t_car, t_nccl)
-        note = (f"per layer at {autotune_tokens} tokens (tp={comm.world}): fused GEMM+all-reduce {t_fused * 1e3:.1f} us, "
-                f"GEMM + peer-memory all-reduce {t_car * 1e3:.1f} us, GEMM + NCCL {t_nccl * 1e3:.1f} us")
+        how = "multimem" if fused.use_mc else "peer loads"
+        note = (f"per layer at {autotune_tokens} tokens (tp={comm.world}, {how}): fused GEMM+all-reduce+norm "
+                f"{t_fused * 1e3:.1f} us, GEMM + peer-memory all-reduce + norm {t_car * 1e3:.1f} us, "
+                f"GEMM + NCCL + norm {t_nccl * 1e3:.1f} us")
         if best == t_fused:
             car.close()
             log.decision("TensorParallel", "fused GEMM+all-reduce on; " + note)
             return True
         model.row_parallel_linear = None
+        model.fused_rp = None
+        fused.close()
         if best == t_car:
             model.custom_ar = car
             model.all_reduce = lambda y: car(y)
@@ -134,32 +196,49 @@ def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_to
     return True
 
 
+def disable_fused_tp(model, comm: Comm) -> None:
+    """Back to GEMM + NCCL on every rank (used after a reported wait timeout)."""
+    for name in ("fused_rp", "custom_ar"):
+        obj = getattr(model, name, None)
+        if obj is not None:
+            obj.close()
+            setattr(model, name, None)
+    model.row_parallel_linear = None
+    model.all_reduce = comm.all_reduce
+
+
 def _measure_row_parallel(model, comm: Comm, fused: FusedRowParallel, car, tokens: int) -> tuple[float, float, float]:
-    """Device time (ms, summed over ranks so that every rank decides alike) of the two row-parallel
-    linears of one layer through the fused kernel, through GEMM + the peer-memory all-reduce, and
-    through GEMM + NCCL all-reduce."""
+    """Device time (ms, summed over ranks so that every rank decides alike) of one layer's two
+    row-parallel linears, each followed by all-reduce + residual add + RMSNorm (+ fp8 quantisation
+    when the model's linears are fp8), through the three paths."""
     lw = next((l for l in model.layers if l.o is not None and l.down is not None), None)
     if lw is None:
         return 0.0, 1.0, 1.0
     dev = model.device
+    cfg = model.cfg
     xs = [torch.randn(tokens, w.in_features, device=dev).to(torch.bfloat16) * 0.1 for w in (lw.o, lw.down)]
     ws = (lw.o, lw.down)
+    res = torch.zeros(tokens, cfg.hidden_size, dtype=torch.bfloat16, device=dev)
+    norm_w = lw.post_norm if lw.post_norm is not None else torch.ones(cfg.hidden_size, dtype=torch.bfloat16, device=dev)
+    fp8 = bool(lw.o.is_fp8)
 
     def run_fused():
         for x, w in zip(xs, ws):
-            fused(x, w)
+            fused(x, w, res=res, norm_w=norm_w, eps=cfg.rms_eps, emit_bf16=not fp8, emit_fp8=fp8)
 
     def run_car():
         for x, w in zip(xs, ws):
             ops.linear(x, w, out=car.input(tokens, w.out_features))
-            car.reduce(tokens, w.out_features)
+            y = car.reduce(tokens, w.out_features)
+            ops.norm(y, norm_w, residual=res, eps=cfg.rms_eps, emit_fp8=fp8, emit_bf16=not fp8)
 
     def run_nccl():
         for x, w in zip(xs, ws):
-            comm.all_reduce(ops.linear(x, w))
+            y = comm.all_reduce(ops.linear(x, w))
+            ops.norm(y, norm_w, residual=res, eps=cfg.rms_eps, emit_fp8=fp8, emit_bf16=not fp8)
 
-    # Both candidates are timed as CUDA-graph replays, the way the decode step runs them, so that
-    # host launch overhead (which differs: one launch against three) does not decide.
+    # All candidates are timed as CUDA-graph replays, the way the decode step runs them, so that
+    # host launch overhead (which differs: one launch against three or four) does not decide.
     times = []
     inner, reps = 8, 5
     for fn in (run_fused, run_car, run_nccl):

@@ -1,8 +1,9 @@
 """Worker of the multi-GPU fused tensor-parallel test (one process per GPU under torchrun).
 
-Checks (1) the fused GEMM+all-reduce kernel against a NCCL all-reduce of the plain GEMM and
-(2) that a tensor-parallel toy decoder produces the same logits as the single-GPU model built from
-the same full weights, through both the NCCL path and the fused path."""
+Checks (1) the fused GEMM + all-reduce + residual + RMSNorm + fp8-emit kernel against a NCCL
+all-reduce of the plain GEMM followed by the same math in fp32, (2) the stand-alone all-reduce and
+CFG-combine kernels, and (3) that a tensor-parallel toy decoder produces the same logits as the
+single-GPU model built from the same full weights, through both the NCCL path and the fused path."""
 import os
 import sys
 
@@ -15,6 +16,7 @@ from hartsyinference_b200 import ops
 from hartsyinference_b200.models.llm import config as C
 from hartsyinference_b200.models.llm.transformer import DecoderModel, ForwardBatch
 from hartsyinference_b200.ops import _native as N
+from hartsyinference_b200.ops import reference as R
 from hartsyinference_b200.parallel import init_comm
 from hartsyinference_b200.parallel.fused import FusedRowParallel, enable_fused_tp
 
@@ -29,20 +31,38 @@ def main():
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.manual_seed(100 + rank)
     fused = FusedRowParallel(comm, 2048, dev)
+    if rank == 0:
+        print("heap transport", fused.heap.transport, "multicast", fused.use_mc, flush=True)
     for fp8 in (False, True):
-        for m in (64, 5, 128):
-            n, k = 2048, 512
+        for m in (64, 5, 128, 1):
+            n, k = 2048, 1024
             x = (torch.randn(m, k, device=dev) * 0.5).to(torch.bfloat16)
             w = ops.LinearWeight.from_dense((torch.randn(n, k, device=dev) * 0.2).to(torch.bfloat16), fp8=fp8)
-            res = torch.randn(m, n, device=dev).to(torch.bfloat16)
-            dist.broadcast(res, 0)
-            y = fused(x, w, residual=res).clone()
+            res0 = torch.randn(m, n, device=dev).to(torch.bfloat16)
+            nw = (1 + 0.1 * torch.randn(n, device=dev)).to(torch.bfloat16)
+            dist.broadcast(res0, 0)
+            dist.broadcast(nw, 0)
+            res = res0.clone()
+            h, h8 = fused(x, w, res=res, norm_w=nw, eps=1e-5, emit_bf16=True, emit_fp8=True)
+            h = h.clone()
+            deq = R.dequant_fp8_act(h8.data.clone(), h8.scales_fp32())
             part = ops.linear(x, w, splits=1).float()
             dist.all_reduce(part)
-            ref = part + res.float()
+            rr = (part.to(torch.bfloat16).float() + res0.float()).to(torch.bfloat16).float()
+            want = rr * torch.rsqrt((rr * rr).mean(-1, keepdim=True) + 1e-5) * nw.float()
             N.check_status(dev)
-            e = rel(y, ref)
-            assert e < 1.5e-2, (fp8, m, e)
+            per = (m + world - 1) // world
+            own = slice(min(m, rank * per), min(m, (rank + 1) * per))
+            assert rel(h, want) < 1.5e-2, (fp8, m, "norm", rel(h, want))
+            assert rel(deq, want) < 6e-2, (fp8, m, "fp8", rel(deq, want))
+            if own.stop > own.start:
+                assert rel(res[own], rr[own]) < 1.5e-2, (fp8, m, "residual", rel(res[own], rr[own]))
+            # rows of other ranks are left alone
+            other = torch.ones(m, dtype=torch.bool, device=dev)
+            other[own] = False
+            assert torch.equal(res[other], res0[other])
+            y, _ = fused(x, w)                                   # plain all-reduced linear
+            assert rel(y, part) < 1.5e-2, (fp8, m, "plain", rel(y, part))
     # ---- peer-memory all-reduce kernel vs NCCL, eager and under a CUDA graph
     from hartsyinference_b200.parallel.custom_ar import CustomAllReduce
     car = CustomAllReduce(comm, 128 * 2048, dev)
@@ -136,13 +156,17 @@ def main():
     cos = torch.nn.functional.cosine_similarity(got, ref, dim=-1).min().item()
     assert cos > 0.999, ("nccl", cos)
     assert enable_fused_tp(tp, comm)
+    assert tp._fused_tp_ok(t)
     got2 = run(tp)
     N.check_status(dev)
     cos2 = torch.nn.functional.cosine_similarity(got2, ref, dim=-1).min().item()
     assert cos2 > 0.999, ("fused", cos2)
     tok_a = tp.greedy_tokens(tp.forward_hidden.__self__.final_norm[None].expand(1, -1).contiguous() * 0 + 1)
     comm.barrier()
+    torch.cuda.synchronize()
     fused.close()
+    tp.fused_rp.close()
+    comm.barrier()
     if rank == 0:
         print("FUSED_TP_OK", cos, cos2)
     dist.destroy_process_group()

@@ -27,6 +27,32 @@ def test_decode_paged(d, hq, hkv, splits):
     assert torch.allclose(out.float().cpu(), ref.float(), rtol=2e-2, atol=2e-2), (out.float().cpu() - ref.float()).abs().max()
 
 
+@pytest.mark.parametrize("mx", [True, False])
+@pytest.mark.parametrize("hq,hkv,splits", [(8, 1, 4), (12, 4, 2), (8, 2, 1)])
+def test_decode_emits_fp8_for_the_output_projection(hq, hkv, splits, mx):
+    """The split-combine kernel quantises its output (one 1x128 group per head); with a single
+    split a separate kernel does. Either way the dequantised values match the bf16 output."""
+    from hartsyinference_b200 import config
+    config.set_override("fp8_scales", "ue8m0" if mx else "fp32")
+    try:
+        torch.manual_seed(4)
+        page, b, max_pages = 16, 6, 40
+        kc, vc = _pool(256, hkv, page, 128)
+        lens = torch.tensor([1, 17, 300, 640, 63, 129], dtype=torch.int32, device="cuda")
+        table = torch.stack([torch.randperm(256, device="cuda")[:max_pages] for _ in range(b)]).to(torch.int32)
+        q = torch.randn(b, hq, 128, device="cuda").to(torch.bfloat16)
+        out, o8 = ops.attn_decode(q, kc, vc, table, lens, splits=splits, emit_fp8=True)
+        ref = ops.attn_decode(q.cpu(), kc.cpu(), vc.cpu(), table.cpu(), lens.cpu()).float().reshape(b, -1)
+        assert torch.allclose(out.float().cpu().reshape(b, -1), ref, rtol=2e-2, atol=2e-2)
+        deq = R.dequant_fp8_act(o8.data, o8.scales_fp32()).cpu()
+        err = (deq - ref).norm() / ref.norm()
+        assert err < 5e-2, err
+        only8 = ops.attn_decode(q, kc, vc, table, lens, splits=splits, emit_fp8=True, emit_bf16=False)[1]
+        assert torch.equal(only8.data, o8.data)
+    finally:
+        config.set_override("fp8_scales", None)
+
+
 def test_decode_window_softcap():
     torch.manual_seed(1)
     page, b = 16, 3
