@@ -5,6 +5,13 @@ with 2048-token prompts and paged KV (16-token pages).
 
     python bench.py --gpus N --steps K --warmup W          (N > 1: launched through torchrun)
 
+The other headline workloads run through ``--preset``: ``deepseek-v3`` (DeepSeek-V3 architecture,
+fp8, 256 x (1024 + 128), experts sharded over N = 8 GPUs; decode tok/s), ``flux-dev`` (Flux-Dev
+1024 x 1024, TP = N; s/step) and ``wan-14b`` (Wan2.1-14B, 81 frames x 720 x 1280, sequence parallel
++ CFG-parallel over N GPUs; s/step), see ``benchmarks/headline_dit.py``. On more than one GPU every
+preset first checks a two-layer slice of its model in the parallel layout against one rank alone
+and reports it as ``parity``.
+
 A "step" is one engine decode iteration for the whole batch (64 new tokens). The weights are
 random-init tensors of the named architecture and the prompts are uniform-random token ids
 (there is no network for checkpoints or datasets). The prompts are really prefilled, so the KV
@@ -40,10 +47,13 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--preset", default="llama-3-70b", help="architecture preset (the headline is llama-3-70b)")
-    ap.add_argument("--batch", type=int, default=64)
-    ap.add_argument("--prompt-len", type=int, default=2048)
-    ap.add_argument("--decode-len", type=int, default=256)
+    ap.add_argument("--preset", default="llama-3-70b",
+                    choices=["llama-3-70b", "deepseek-v3", "flux-dev", "wan-14b", "llama-3-8b", "qwen2.5-0.5b"],
+                    help="workload (the headline is llama-3-70b)")
+    ap.add_argument("--batch", type=int, default=0, help="requests (default: 64; deepseek-v3: 256)")
+    ap.add_argument("--prompt-len", type=int, default=0, help="prompt tokens (default: 2048; deepseek-v3: 1024)")
+    ap.add_argument("--decode-len", type=int, default=0, help="decode tokens (default: 256; deepseek-v3: 128)")
+    ap.add_argument("--no-parity", action="store_true", help="skip the multi-GPU parity block")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--bf16", action="store_true", help="debug only: bf16 weights instead of fp8")
     ap.add_argument("--no-fused-comm", action="store_true", help="NCCL all-reduce instead of the fused kernels")
@@ -141,6 +151,18 @@ def main() -> int:
     if rank != 0:
         import logging
         log.logger.setLevel(logging.WARNING)
+    sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+    if args.preset in ("flux-dev", "wan-14b"):
+        import headline_dit
+        fn = headline_dit.run_flux if args.preset == "flux-dev" else headline_dit.run_wan
+        out = fn(args, comm, device, ClockSampler(local_rank))
+        if rank == 0:
+            print(json.dumps(out))
+        return _leave(comm, world)
+    dsv3 = args.preset == "deepseek-v3"
+    args.batch = args.batch or (256 if dsv3 else 64)
+    args.prompt_len = args.prompt_len or (1024 if dsv3 else 2048)
+    args.decode_len = args.decode_len or (128 if dsv3 else 256)
 
     cfg = C.PRESETS[args.preset]
     invalid = []
@@ -150,6 +172,26 @@ def main() -> int:
         invalid.append(f"layers={args.layers}")
     if args.bf16:
         invalid.append("bf16 weights")
+    need = _weight_bytes_estimate(cfg, world, fp8=not args.bf16)
+    total_mem = torch.cuda.get_device_properties(device).total_memory
+    if need > 0.8 * total_mem:
+        if rank == 0:
+            print(json.dumps({"metric": _metric_name(args), "n_gpus": world, "value": None,
+                              "unavailable": f"{need / 2**30:.0f} GiB of weights per GPU at {world} GPU(s) do not fit "
+                                             f"{total_mem / 2**30:.0f} GiB of device memory",
+                              "config": {"model": args.preset, "parallelism": f"tp{world}"}}))
+        return _leave(comm, world)
+    parity = None
+    if world > 1 and not args.no_parity:
+        import llm_parity
+        def _enable(m):
+            if args.no_fused_comm:
+                return False
+            from hartsyinference_b200.parallel.fused import enable_fused_tp
+            return enable_fused_tp(m, comm)
+        parity = llm_parity.run(cfg, comm, device, not args.bf16, _enable)
+        if rank == 0:
+            log.info(f"[Bench] parity {parity}")
     t0 = time.perf_counter()
     model = DecoderModel(cfg, device, comm=comm, fp8=not args.bf16)
     model.random_init(seed=0)
@@ -244,7 +286,7 @@ def main() -> int:
     tokens = steps * args.batch
     if rank == 0:
         out = {
-            "metric": "decode tok/s (Llama-3-70B-architecture, fp8 128x128 block-scaled weights, TP=N, 64 x (2048 prompt + 256 decode), paged KV)",
+            "metric": _metric_name(args),
             "value": tokens / (dev_ms / 1e3),
             "unit": "tokens/s",
             "n_gpus": world,
@@ -266,26 +308,64 @@ def main() -> int:
                     "h2d_bytes_per_step": h2d // steps, "d2h_bytes_per_step": d2h // steps},
             "gpu_launches": launches,
             "clocks": clocks,
+            "parity": parity,
             "ttft_s": {"batch_prefill_wall": t_prefill, "median": ttft[len(ttft) // 2], "max": ttft[-1]},
             "load_s": t_load,
             "weight_bytes_per_gpu": model.weight_bytes(),
         }
         print(json.dumps(out))
     if world > 1:
-        # Every rank takes its memory out of the multicast object and unmaps its peers before any
-        # rank leaves. NCCL communicators that were captured into CUDA graphs can block in their
-        # teardown; the result is already printed, so leave without running it.
-        comm.barrier()
-        torch.cuda.synchronize()
         eng._graphs.clear()
         from hartsyinference_b200.parallel.fused import disable_fused_tp
         disable_fused_tp(model, comm)
+    return _leave(comm, world)
+
+
+def _leave(comm, world: int) -> int:
+    """Every rank has taken its memory out of the multicast object and unmapped its peers before
+    any rank leaves. NCCL communicators that were captured into CUDA graphs can block in their
+    teardown; the result is already printed, so leave without running it."""
+    if world > 1:
+        import torch
         comm.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
     return 0
+
+
+def _metric_name(args) -> str:
+    if args.preset == "deepseek-v3":
+        return (f"decode tok/s (DeepSeek-V3-architecture MoE, fp8 128x128 block-scaled weights, experts sharded over N GPUs, "
+                f"{args.batch} x ({args.prompt_len} prompt + {args.decode_len} decode), MLA latent KV)")
+    name = {"llama-3-70b": "Llama-3-70B"}.get(args.preset, args.preset)
+    return (f"decode tok/s ({name}-architecture, fp8 128x128 block-scaled weights, TP=N, "
+            f"{args.batch} x ({args.prompt_len} prompt + {args.decode_len} decode), paged KV)")
+
+
+def _weight_bytes_estimate(cfg, world: int, fp8: bool) -> int:
+    """Bytes of weights one rank will hold (linears fp8 or bf16, embeddings bf16)."""
+    H, L = cfg.hidden_size, cfg.num_layers
+    per = 1 if fp8 else 2
+    if cfg.mla is not None:
+        m = cfg.mla
+        attn = H * (m.q_lora_rank or 0) + (m.q_lora_rank or H) * cfg.num_heads * (m.qk_nope_head_dim + m.qk_rope_head_dim) // world \
+            + H * (m.kv_lora_rank + m.qk_rope_head_dim) * 2 // per + cfg.num_heads * m.kv_lora_rank * (m.qk_nope_head_dim + m.v_head_dim) * 2 // per // world \
+            + H * cfg.num_heads * m.v_head_dim // world
+    else:
+        attn = H * (cfg.q_size + 2 * cfg.kv_size) // world + H * cfg.q_size // world
+    dense = 3 * H * cfg.ffn_size // world
+    total = 0
+    for li in range(L):
+        moe = cfg.moe is not None and cfg.moe.num_experts > 0 and li >= cfg.moe.first_dense_layers
+        if moe:
+            total += attn + 3 * H * cfg.moe.expert_ffn * cfg.moe.num_experts // world \
+                + 3 * H * cfg.moe.shared_ffn * cfg.moe.num_shared_experts // world
+        else:
+            total += attn + dense
+    emb = cfg.vocab_size * H * 2 * (1 if cfg.tie_embeddings else 1 + 1 / world)
+    return int(total * per + emb)
 
 
 if __name__ == "__main__":

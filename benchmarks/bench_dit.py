@@ -43,8 +43,8 @@ def main() -> None:
     fp8 = not args.bf16
     peaks = profiling.measured_peaks()
     if args.model == "flux":
-        from ..models.dit import flux as F
-        from ..pipelines.flux import FluxComponents, FluxPipeline
+        from hartsyinference_b200.models.dit import flux as F
+        from hartsyinference_b200.pipelines.flux import FluxComponents, FluxPipeline
         cfg = F.FLUX_DEV
         if args.layers:
             cfg = replace(cfg, num_double_blocks=args.layers, num_single_blocks=2 * args.layers)
@@ -63,8 +63,8 @@ def main() -> None:
         flops = (lin + att) * (2 if args.cfg else 1)
         name, par = "flux-dev 1024x1024" if (h, w) == (1024, 1024) else f"flux-dev {w}x{h}", f"tp{comm.world}"
     else:
-        from ..models.dit import wan as W
-        from ..pipelines.wan import WanComponents, WanPipeline
+        from hartsyinference_b200.models.dit import wan as W
+        from hartsyinference_b200.pipelines.wan import WanComponents, WanPipeline
         cfg = W.WAN_14B if args.model == "wan" else W.WAN_1_3B
         if args.layers:
             cfg = replace(cfg, num_layers=args.layers)

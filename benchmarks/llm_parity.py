@@ -1,0 +1,124 @@
+"""Multi-GPU correctness check that ``bench.py`` runs before its timed region: a two-layer slice of
+the benchmarked LLM architecture (same hidden size, heads, feed-forward / expert shapes; smaller
+vocabulary) is built once from full weights, sharded over the N ranks exactly as the benchmark
+model is, and run on a short prompt; rank 0 also builds the unsharded model from the same weights.
+The cosine between the two sets of logits (minimum over rows) and the share of identical greedy
+tokens are reported. With fused tensor-parallel kernels enabled, the sharded run goes through them
+(the prompt is shorter than their 128-token limit)."""
+from __future__ import annotations
+
+import zlib
+from dataclasses import replace
+
+import torch
+
+from hartsyinference_b200 import ops
+from hartsyinference_b200.models.llm.transformer import DecoderModel, ForwardBatch
+from hartsyinference_b200.parallel.comm import SingleComm
+
+PARITY_VOCAB = 16384
+
+
+def _shape(name: str, cfg) -> tuple:
+    H = cfg.hidden_size
+    mla, moe = cfg.mla, cfg.moe
+    leaf = name.rsplit(".", 2)[-2] if name.endswith(".weight") else name.rsplit(".", 1)[-1]
+    if leaf in ("embed_tokens", "lm_head"):
+        return (cfg.vocab_size, H)
+    if leaf == "q_a_layernorm":
+        return (mla.q_lora_rank,)
+    if leaf == "kv_a_layernorm":
+        return (mla.kv_lora_rank,)
+    if "layernorm" in leaf or leaf == "norm":
+        return (H,)
+    if leaf == "e_score_correction_bias":
+        return (moe.num_experts,)
+    if leaf == "gate" and ".mlp.gate." in name:
+        return (moe.num_experts, H)
+    if mla is not None and ".self_attn." in name:
+        dq = mla.qk_nope_head_dim + mla.qk_rope_head_dim
+        return {"q_a_proj": (mla.q_lora_rank, H), "q_b_proj": (cfg.num_heads * dq, mla.q_lora_rank),
+                "q_proj": (cfg.num_heads * dq, H),
+                "kv_a_proj_with_mqa": (mla.kv_lora_rank + mla.qk_rope_head_dim, H),
+                "kv_b_proj": (cfg.num_heads * (mla.qk_nope_head_dim + mla.v_head_dim), mla.kv_lora_rank),
+                "o_proj": (H, cfg.num_heads * mla.v_head_dim)}[leaf]
+    if ".self_attn." in name:
+        return {"q_proj": (cfg.q_size, H), "k_proj": (cfg.kv_size, H), "v_proj": (cfg.kv_size, H),
+                "o_proj": (H, cfg.q_size)}[leaf]
+    if ".shared_expert." in name:
+        raise KeyError(name)
+    if ".experts." in name:
+        f = moe.expert_ffn
+    elif ".shared_experts." in name:
+        f = moe.shared_ffn * moe.num_shared_experts
+    else:
+        f = cfg.ffn_size
+    return {"gate_proj": (f, H), "up_proj": (f, H), "down_proj": (H, f)}[leaf]
+
+
+def _weights(cfg, dev):
+    """``get(name)`` producing each full tensor on the device from a seed derived from its name:
+    identical on every rank, never all resident at once."""
+    def get(name: str):
+        if name.endswith(".bias") and "e_score_correction_bias" not in name:
+            return None
+        try:
+            shape = _shape(name, cfg)
+        except KeyError:
+            return None
+        if len(shape) == 1 and "e_score_correction_bias" not in name:
+            return torch.ones(shape, dtype=torch.bfloat16, device=dev)
+        t = torch.empty(shape if len(shape) == 2 else (1, shape[0]), dtype=torch.bfloat16, device=dev)
+        ops.fill_random_(t, zlib.crc32(name.encode()) + 1, 0.05 if ".mlp.gate." in name else 0.02)
+        return t if len(shape) == 2 else t.reshape(-1).float()
+    return get
+
+
+def run(cfg, comm, dev, fp8: bool, enable_fused=None) -> dict:
+    """All ranks call this. ``enable_fused(model)`` (optional) switches the sharded model to the
+    fused kernels the benchmark will use."""
+    moe = cfg.moe
+    if moe is not None and moe.num_experts > 0:
+        moe = replace(moe, first_dense_layers=min(1, moe.first_dense_layers))
+    cfg2 = replace(cfg, num_layers=2, vocab_size=PARITY_VOCAB, moe=moe)
+    get = _weights(cfg2, dev)
+    t = 48
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, cfg2.vocab_size, (t,), generator=g).to(torch.int32).to(dev)
+
+    def forward(model):
+        model.alloc_kv(8, 16)
+        b = ForwardBatch(tokens=toks, positions=torch.arange(t, dtype=torch.int32, device=dev),
+                         slot_mapping=torch.arange(t, dtype=torch.int64, device=dev),
+                         block_table=torch.arange(8, dtype=torch.int32, device=dev)[None],
+                         kv_lens=torch.tensor([t], dtype=torch.int32, device=dev), is_decode=False,
+                         cu_q=torch.tensor([0, t], dtype=torch.int32, device=dev), max_q_len=t, max_kv_len=t)
+        return model.full_logits(model.forward_hidden(b)).float()
+
+    sharded = DecoderModel(cfg2, dev, comm=comm, fp8=fp8)
+    sharded.load_state_dict(get)
+    path = "nccl"
+    if enable_fused is not None and enable_fused(sharded):
+        path = "fused"
+    got = forward(sharded)
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    for name in ("fused_rp", "custom_ar"):
+        obj = getattr(sharded, name, None)
+        if obj is not None:
+            obj.close()
+    del sharded
+    res = torch.zeros(2, device=dev)
+    if comm.rank == 0:
+        one = DecoderModel(cfg2, dev, comm=SingleComm(), fp8=fp8)
+        one.load_state_dict(get)
+        ref = forward(one)
+        del one
+        res[0] = torch.nn.functional.cosine_similarity(got, ref, dim=-1).min()
+        res[1] = (got.argmax(-1) == ref.argmax(-1)).float().mean()
+    comm.broadcast(res, 0)
+    if dev.type == "cuda":
+        torch.cuda.empty_cache()
+    cos, agree = float(res[0].item()), float(res[1].item())
+    return {"ok": cos > 0.99, "cos": cos, "greedy_agreement": agree, "path": path,
+            "what": f"2-layer slice (vocab {PARITY_VOCAB}), {t}-token prompt, {comm.world} ranks vs 1"}

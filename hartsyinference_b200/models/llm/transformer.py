@@ -116,6 +116,10 @@ class LayerWeights:
     sinks: Optional[torch.Tensor] = None              # per-head sink logit in the attention softmax (gpt-oss)
 
 
+def x_is_cuda(x) -> bool:
+    return (x.data if isinstance(x, ops.Fp8Act) else x).is_cuda
+
+
 class DecoderModel:
     def __init__(self, cfg: TransformerConfig, device: torch.device | str = "cpu", comm: Optional[Comm] = None,
                  fp8: bool = False, layer_range: Optional[tuple[int, int]] = None):
@@ -508,13 +512,17 @@ class DecoderModel:
         return s * self.rope_attn_factor * self.rope_attn_factor if self.rope_attn_factor != 1.0 else s
 
     def _reduce_linear(self, x, w: LinearWeight) -> torch.Tensor:
-        """Row-parallel linear: local partial product, then sum over the TP group."""
-        if self.tp > 1 and self.row_parallel_linear is not None:
-            return self.row_parallel_linear(x, w)
-        if self.tp > 1 and self.custom_ar is not None:
+        """Row-parallel linear: local partial product, then sum over the TP group. In order of
+        preference: the fused GEMM + all-reduce kernel (up to 128 tokens), GEMM written straight
+        into the peer-memory all-reduce kernel's input buffer, GEMM + NCCL."""
+        if self.tp > 1:
             m = (x.data if isinstance(x, ops.Fp8Act) else x).shape[0]
             n = w.out_features
-            if self.custom_ar.fits(m * n):
+            if self.fused_rp is not None and self.fused_rp.supports(m, n) and x_is_cuda(x):
+                return self.fused_rp(x, w)[0]
+            if self.row_parallel_linear is not None and self.fused_rp is None:
+                return self.row_parallel_linear(x, w)
+            if self.custom_ar is not None and self.custom_ar.fits(m * n):
                 ops.linear(x, w, out=self.custom_ar.input(m, n))
                 return self.custom_ar.reduce(m, n)
         y = ops.linear(x, w)

@@ -157,6 +157,25 @@ def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_to
     if hidden % 128 != 0:
         log.decision("TensorParallel", f"fused all-reduce off: hidden {hidden} is not a multiple of 128")
         return False
+    dense = next((l for l in model.layers if l.o is not None and l.down is not None), None)
+    if dense is None:
+        # no plain attention / feed-forward pair (latent attention, expert layers): the row-parallel
+        # outputs go through the stand-alone all-reduce; pick the kernel or NCCL by measurement
+        if autotune_tokens <= 0:
+            return False
+        from .custom_ar import CustomAllReduce
+        car = CustomAllReduce(comm, max(max_tokens, autotune_tokens, MAX_TOKENS) * hidden, model.device)
+        t_car, t_nccl = _measure_allreduce(comm, car, autotune_tokens, hidden, model.device)
+        note = (f"all-reduce of {autotune_tokens} x {hidden} bf16 (tp={comm.world}, "
+                f"{'multimem' if car.use_mc else 'peer loads'}): kernel {t_car * 1e3:.1f} us, NCCL {t_nccl * 1e3:.1f} us")
+        if t_car < t_nccl:
+            model.custom_ar = car
+            model.all_reduce = lambda y: car(y)
+            log.decision("TensorParallel", "peer-memory all-reduce on; " + note)
+        else:
+            car.close()
+            log.decision("TensorParallel", "NCCL all-reduce kept; " + note)
+        return False
     fused = FusedRowParallel(comm, hidden, model.device)
 
     def row_parallel(x, w: LinearWeight) -> torch.Tensor:
@@ -170,15 +189,19 @@ def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_to
     model.fused_rp = fused
     if autotune_tokens > 0 and model.layers:
         from .custom_ar import CustomAllReduce
-        car = CustomAllReduce(comm, MAX_TOKENS * hidden, model.device)
-        t_fused, t_car, t_nccl = _measure_row_parallel(model, comm, fused, car, autotune_tokens)
+        tokens = min(autotune_tokens, MAX_TOKENS)
+        car = CustomAllReduce(comm, max(max_tokens, MAX_TOKENS) * hidden, model.device)
+        t_fused, t_car, t_nccl = _measure_row_parallel(model, comm, fused, car, tokens)
         best = min(t_fused, t_car, t_nccl)
         how = "multimem" if fused.use_mc else "peer loads"
-        note = (f"per layer at {autotune_tokens} tokens (tp={comm.world}, {how}): fused GEMM+all-reduce+norm "
+        note = (f"per layer at {tokens} tokens (tp={comm.world}, {how}): fused GEMM+all-reduce+norm "
                 f"{t_fused * 1e3:.1f} us, GEMM + peer-memory all-reduce + norm {t_car * 1e3:.1f} us, "
                 f"GEMM + NCCL + norm {t_nccl * 1e3:.1f} us")
         if best == t_fused:
-            car.close()
+            if t_car < t_nccl:      # batches beyond the fused kernel's token limit still avoid NCCL
+                model.custom_ar = car
+            else:
+                car.close()
             log.decision("TensorParallel", "fused GEMM+all-reduce on; " + note)
             return True
         model.row_parallel_linear = None
@@ -194,6 +217,38 @@ def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_to
         return False
     log.decision("TensorParallel", f"fused GEMM+all-reduce on for <= {MAX_TOKENS} tokens (tp={comm.world})")
     return True
+
+
+def _time_graph(fn, comm: Comm, dev, inner: int = 8, reps: int = 5) -> float:
+    """Device ms per call of ``fn`` replayed from a CUDA graph (the way the decode step runs it)."""
+    for _ in range(3):
+        fn()
+    comm.barrier()
+    torch.cuda.synchronize(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(inner):
+            fn()
+    graph.replay()
+    comm.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / (inner * reps)
+    del graph
+    return ms
+
+
+def _measure_allreduce(comm: Comm, car, tokens: int, hidden: int, dev) -> tuple[float, float]:
+    """Device time (ms, summed over ranks) of one [tokens, hidden] bf16 all-reduce: kernel, NCCL."""
+    x = torch.randn(tokens, hidden, device=dev).to(torch.bfloat16)
+    times = [_time_graph(lambda: car(x), comm, dev), _time_graph(lambda: comm.all_reduce(x), comm, dev)]
+    t = comm.all_reduce(torch.tensor(times, device=dev, dtype=torch.float32))
+    return float(t[0].item()), float(t[1].item())
 
 
 def disable_fused_tp(model, comm: Comm) -> None:
@@ -239,28 +294,7 @@ def _measure_row_parallel(model, comm: Comm, fused: FusedRowParallel, car, token
 
     # All candidates are timed as CUDA-graph replays, the way the decode step runs them, so that
     # host launch overhead (which differs: one launch against three or four) does not decide.
-    times = []
-    inner, reps = 8, 5
-    for fn in (run_fused, run_car, run_nccl):
-        for _ in range(3):
-            fn()
-        comm.barrier()
-        torch.cuda.synchronize(dev)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for _ in range(inner):
-                fn()
-        graph.replay()
-        comm.barrier()
-        torch.cuda.synchronize(dev)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            graph.replay()
-        e1.record()
-        torch.cuda.synchronize(dev)
-        times.append(e0.elapsed_time(e1) / (inner * reps))
-        del graph
+    times = [_time_graph(fn, comm, dev) for fn in (run_fused, run_car, run_nccl)]
     t = torch.tensor(times, device=dev, dtype=torch.float32)
     t = comm.all_reduce(t)
     return float(t[0].item()), float(t[1].item()), float(t[2].item())

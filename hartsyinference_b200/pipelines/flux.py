@@ -153,12 +153,17 @@ class FluxPipeline:
         fbc = [FirstBlockCache(first_block_cache), FirstBlockCache(first_block_cache)] if first_block_cache > 0 else [None, None]
         self.last_step_ms = []
         use_cuda = dev.type == "cuda"
+        # the per-step scalars are staged in pinned host memory and copied as each step starts
+        h_sigmas = torch.tensor([sched.sigma(i) for i in range(steps)], dtype=torch.float32)
+        if use_cuda:
+            h_sigmas = h_sigmas.pin_memory()
+        self.h2d_bytes_per_step = 4
         for i in range(first_step, steps):
             if use_cuda:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
             t0 = time.perf_counter()
-            sigma = torch.tensor([sched.sigma(i)], device=dev)
+            sigma = h_sigmas[i:i + 1].to(dev, non_blocking=True)
             skip = False
             if step_cache_threshold > 0 and cache_v is not None:
                 temb = tr.time_embedding(sigma, gvec, pooled_d).float()
@@ -208,7 +213,7 @@ class FluxPipeline:
             self.last_step_ms.append(ms)
             REGISTRY.set("hartsyinference_step_seconds", ms / 1e3, model="flux")
             if on_step is not None:
-                on_step(StepPreview(i + 1, steps))
+                on_step(StepPreview(i + 1, steps, latents=x))      # packed fp32 latents [1, S, 4C] on the device
         return unpack_latents(x, lh, lw)
 
     def _fused_cfg(self, elems: int, dev):

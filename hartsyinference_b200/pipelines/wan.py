@@ -68,12 +68,17 @@ class WanPipeline:
         branch = self.cfg_comm.rank if (self.cfg_comm is not None and self.cfg_comm.world == 2 and c_neg is not None) else None
         self.last_step_ms = []
         use_cuda = dev.type == "cuda"
+        # the per-step scalars are staged in pinned host memory and copied as each step starts
+        h_t = torch.tensor([float((uni or eul).timestep(i)) for i in range(steps)], dtype=torch.float32)
+        if use_cuda:
+            h_t = h_t.pin_memory()
+        self.h2d_bytes_per_step = 4
         for i in range(steps):
             if use_cuda:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
             t0 = time.perf_counter()
-            t = torch.tensor((uni or eul).timestep(i), device=dev)
+            t = h_t[i].to(dev, non_blocking=True)
             xin = x.to(torch.bfloat16)
             if branch is None:
                 v = tr.forward(xin, t, c_pos)
@@ -97,7 +102,7 @@ class WanPipeline:
             self.last_step_ms.append(ms)
             REGISTRY.set("hartsyinference_step_seconds", ms / 1e3, model="wan")
             if on_step is not None:
-                on_step(StepPreview(i + 1, steps))
+                on_step(StepPreview(i + 1, steps, latents=x))      # fp32 latents [C, T, H / 8, W / 8] on the device
         return x
 
     def generate(self, req: VideoRequest, on_step: Optional[Callable[[StepPreview], None]] = None) -> VideoGenerationResult:
