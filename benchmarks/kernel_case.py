@@ -76,16 +76,59 @@ def _mla(argv):
         ops.mla_attn(q, cache, table, lens, 1.0 / math.sqrt(192), max_kv_len=ctx)
 
 
+def _time(fn, reps=5):
+    """Median device time (ms) of ``fn`` over ``reps`` runs after three warm-up runs (CUDA events)."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return sorted(ts)[len(ts) // 2]
+
+
 def _attn_dense(argv):
+    """attn_dense TOKENS HEADS [fa|fa8|tc|mma]: dense bidirectional attention, head dim 128; prints
+    the device time and TFLOP/s (4 * T^2 * 128 * heads) of the chosen kernel."""
+    from hartsyinference_b200 import config
     tokens, heads = (int(v) for v in argv[:2])
+    mode = argv[2] if len(argv) > 2 else "fa"
+    config.set_override("fa_attention", mode in ("fa", "fa8"))
+    config.set_override("tc_attention", mode != "mma")
     q = torch.randn(tokens, heads, 128, device="cuda").to(torch.bfloat16)
     k = torch.randn(tokens, heads, 128, device="cuda").to(torch.bfloat16)
     v = torch.randn(tokens, heads, 128, device="cuda").to(torch.bfloat16)
-    for _ in range(3):
-        ops.attention(q, k, v)
+    ms = _time(lambda: ops.attention(q, k, v, int8=mode == "fa8"))
+    print(f"attention {mode}: {tokens} tokens x {heads} heads: {ms:.3f} ms, "
+          f"{4.0 * tokens * tokens * 128 * heads / ms / 1e9:.0f} TFLOP/s")
 
 
-CASES = {"attn_dense": _attn_dense, "gemm": _gemm, "grouped": _grouped, "attn_decode": _attn_decode, "mla": _mla}
+def _gemm_ar(argv):
+    """gemm_ar M N K WORLD: the fused GEMM + all-reduce + residual + RMSNorm + fp8-emit kernel for
+    rank 0 of WORLD with this GPU standing in for its peers (protocol and row share of that rank, no
+    NVLink latency), against GEMM + norm kernels on the same operands."""
+    from hartsyinference_b200.parallel.comm import ShardEmulationComm
+    from hartsyinference_b200.parallel.fused import FusedRowParallel
+    m, n, k, world = (int(v) for v in argv[:4])
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    lw = ops.LinearWeight.from_dense((torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16), fp8=True)
+    xq = ops.quant_fp8_act(x)
+    res = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    nw = torch.ones(n, device="cuda", dtype=torch.bfloat16)
+    f = FusedRowParallel(ShardEmulationComm(world), n, torch.device("cuda", 0), emulate_peers=True)
+    t_fused = _time(lambda: f(xq, lw, res=res, norm_w=nw, emit_bf16=False, emit_fp8=True), reps=9)
+    t_plain = _time(lambda: ops.norm(ops.linear(xq, lw), nw, residual=res, emit_fp8=True, emit_bf16=False), reps=9)
+    t_gemm = _time(lambda: ops.linear(xq, lw), reps=9)
+    print(f"gemm_ar {m}x{n}x{k} world {world}: fused {t_fused * 1e3:.1f} us, GEMM + norm {t_plain * 1e3:.1f} us, GEMM {t_gemm * 1e3:.1f} us")
+    f.close()
+
+
+CASES = {"gemm_ar": _gemm_ar, "attn_dense": _attn_dense, "gemm": _gemm, "grouped": _grouped, "attn_decode": _attn_decode, "mla": _mla}
 
 
 def main(argv=None) -> int:

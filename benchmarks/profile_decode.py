@@ -33,21 +33,24 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--bf16", action="store_true")
-    ap.add_argument("--tp-shard", type=int, default=1, help="build the 1/N tensor-parallel shard shapes on one GPU")
+    ap.add_argument("--tp-shard", type=int, default=1,
+                    help="build rank 0's shard of an N-way tensor-parallel group on one GPU (no peers)")
+    ap.add_argument("--fused", action="store_true",
+                    help="with --tp-shard: run the fused GEMM + all-reduce + norm kernel with this GPU standing in for its peers")
     args = ap.parse_args()
     cfg = C.PRESETS[args.preset]
     if args.layers:
         cfg = replace(cfg, num_layers=args.layers)
-    if args.tp_shard > 1:   # same per-GPU GEMM / attention shapes as rank 0 of a TP group (no collectives)
-        n = args.tp_shard
-        cfg = replace(cfg, num_heads=cfg.num_heads // n, num_kv_heads=max(1, cfg.num_kv_heads // n),
-                      ffn_size=cfg.ffn_size // n)
     dev = torch.device("cuda", 0)
-    model = DecoderModel(cfg, dev, fp8=not args.bf16)
-    if args.tp_shard > 1:
-        # keep the hidden size of the full model: q/o projections use num_heads * head_dim columns
-        pass
+    comm = None
+    if args.tp_shard > 1:   # same per-GPU GEMM / attention shapes as rank 0 of a TP group
+        from hartsyinference_b200.parallel.comm import ShardEmulationComm
+        comm = ShardEmulationComm(args.tp_shard)
+    model = DecoderModel(cfg, dev, comm=comm, fp8=not args.bf16)
     model.random_init(0)
+    if args.fused and comm is not None:
+        from hartsyinference_b200.parallel.fused import FusedRowParallel
+        model.fused_rp = FusedRowParallel(comm, cfg.hidden_size, dev, emulate_peers=True)
     total = args.prompt_len + 64
     pages = (total + 15) // 16 + 1
     eng = LLMEngine(model, num_pages=args.batch * pages + 8, page_size=16, max_batch=args.batch, prefill_chunk=8192,

@@ -2,8 +2,10 @@
 ``embed``, ``serve``, ``convert``, ``models`` / ``list``, ``flags``, ``plan`` (plus an interactive
 ``chat`` REPL). Placement flags follow src/HartsyInference.Cli/Infra/PlacementCli.cs
 (``--gpu``, ``--device "cuda:0+cuda:1"``, ``--parallel auto``) and add the NVSwitch degrees
-``--tp / --sp / --ep / --cfg-parallel / --pp``. Multi-GPU runs are SPMD: launch the same command
-under ``torchrun --nproc-per-node N``.
+``--tp / --sp / --ep / --cfg-parallel / --pp``. Multi-GPU runs are SPMD, one process per GPU: a
+command whose placement needs N > 1 devices re-launches itself under ``torch.distributed.run`` with
+N processes (or is started that way by the user); rank 0 runs the verb, the other ranks follow it.
+``--parallel auto`` asks the planner for the placement.
 """
 from __future__ import annotations
 
@@ -17,10 +19,36 @@ from ..engine.requests import EngineOptions, ImageRequest, Modality, ModelSpec, 
 from ..parallel.config import ParallelConfig
 
 
-def _engine(device: str, tp: int, sp: int, ep: int, cfg_parallel: bool, pp: int, max_len: int = 8192):
+def _engine(device: str, tp: int, sp: int, ep: int, cfg_parallel: bool, pp: int, max_len: int = 8192,
+            parallel: str = "", model: str = ""):
+    """Build the engine for a verb. Needs-more-than-one-process placements re-launch the command
+    under ``torch.distributed.run``; follower ranks serve rank 0 and exit with it."""
+    import atexit
+    import os
+    import subprocess
+    import sys
+    import torch
     from ..engine.inference_engine import InferenceEngine
-    placement = ParallelConfig(tp=tp, sp=sp, ep=ep, cfg=2 if cfg_parallel else 1, pp=pp)
-    return InferenceEngine(device, EngineOptions(placement=placement, max_model_len=max_len))
+    placement = ParallelConfig(tp=tp, sp=sp, ep=max(ep, 1), cfg=2 if cfg_parallel else 1, pp=pp)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if parallel == "auto":
+        from ..engine.planner import shape_of_checkpoint, suggest
+        gpus = world if world > 1 else (torch.cuda.device_count() if device != "cpu" and torch.cuda.is_available() else 1)
+        shape = shape_of_checkpoint(model) if model else None
+        if shape is not None and gpus > 1:
+            placement = suggest(shape, gpus)
+    need = placement.tp * placement.sp * placement.cfg * placement.dp
+    if need > 1 and world == 1:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={need}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29533"),
+               "-m", "hartsyinference_b200.cli"] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    eng = InferenceEngine(device, EngineOptions(placement=placement, max_model_len=max_len))
+    if not eng.is_front:
+        eng.follow()
+        sys.exit(0)
+    atexit.register(eng.close)          # releases the follower ranks
+    return eng
 
 
 def placement_options(f):
@@ -29,7 +57,8 @@ def placement_options(f):
                 click.option("--sp", default=1, help="Ulysses sequence-parallel degree (DiT)"),
                 click.option("--ep", default=1, help="expert-parallel degree (MoE)"),
                 click.option("--cfg-parallel", is_flag=True, help="run the two guidance branches on two device groups"),
-                click.option("--pp", default=1, help="pipeline stages (layer / block split)")):
+                click.option("--pp", default=1, help="pipeline stages (layer / block split)"),
+                click.option("--parallel", default="", help="'auto': let the planner choose the placement for the visible GPUs")):
         f = opt(f)
     return f
 
@@ -51,9 +80,9 @@ def cli():
 @click.option("--raw", is_flag=True, help="do not apply the chat template")
 @click.option("--json-mode", is_flag=True)
 @placement_options
-def text(model, prompt, max_tokens, temperature, top_p, top_k, seed, greedy, raw, json_mode, device, tp, sp, ep, cfg_parallel, pp):
+def text(model, prompt, max_tokens, temperature, top_p, top_k, seed, greedy, raw, json_mode, device, tp, sp, ep, cfg_parallel, pp, parallel):
     """Generate text (streams to stdout)."""
-    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp, parallel=parallel, model=model)
     req = TextRequest(messages=[] if raw else [{"role": "user", "content": prompt}], prompt=prompt if raw else None,
                       max_tokens=max_tokens, temperature=temperature, top_p=top_p, top_k=top_k, seed=seed, greedy=greedy,
                       json_mode=json_mode)
@@ -71,9 +100,9 @@ def text(model, prompt, max_tokens, temperature, top_p, top_k, seed, greedy, raw
 @cli.command()
 @click.argument("model")
 @placement_options
-def chat(model, device, tp, sp, ep, cfg_parallel, pp):
+def chat(model, device, tp, sp, ep, cfg_parallel, pp, parallel):
     """Interactive chat REPL (empty line or Ctrl-D quits)."""
-    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp, parallel=parallel, model=model)
     spec = ModelSpec(model, Modality.TEXT, local_path=model)
     history: list[dict] = []
     while True:
@@ -105,10 +134,10 @@ def chat(model, device, tp, sp, ep, cfg_parallel, pp):
 @click.option("--negative", default="")
 @click.option("--seed", default=None, type=int)
 @placement_options
-def image(model, prompt, out, width, height, steps, guidance, cfg_scale, negative, seed, device, tp, sp, ep, cfg_parallel, pp):
+def image(model, prompt, out, width, height, steps, guidance, cfg_scale, negative, seed, device, tp, sp, ep, cfg_parallel, pp, parallel):
     """Generate an image (PNG)."""
     from ..utils.png import encode_png
-    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp, parallel=parallel, model=model)
     res = eng.images.generate(ModelSpec(model, Modality.IMAGE, local_path=model if Path(model).exists() else None),
                               ImageRequest(prompt=prompt, negative_prompt=negative, width=width, height=height, steps=steps,
                                            guidance=guidance, cfg_scale=cfg_scale, seed=seed),
@@ -128,10 +157,10 @@ def image(model, prompt, out, width, height, steps, guidance, cfg_scale, negativ
 @click.option("--cfg-scale", default=5.0)
 @click.option("--seed", default=None, type=int)
 @placement_options
-def video(model, prompt, out_dir, width, height, frames, steps, cfg_scale, seed, device, tp, sp, ep, cfg_parallel, pp):
+def video(model, prompt, out_dir, width, height, frames, steps, cfg_scale, seed, device, tp, sp, ep, cfg_parallel, pp, parallel):
     """Generate a video (PNG frame sequence; pipe to ffmpeg to mux)."""
     from ..utils.png import encode_png
-    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp, parallel=parallel, model=model)
     res = eng.video.generate(ModelSpec(model, Modality.VIDEO, local_path=model if Path(model).exists() else None),
                              VideoRequest(prompt=prompt, width=width, height=height, frames=frames, steps=steps,
                                           cfg_scale=cfg_scale, seed=seed),
@@ -147,9 +176,9 @@ def video(model, prompt, out_dir, width, height, frames, steps, cfg_scale, seed,
 @click.argument("model")
 @click.argument("texts", nargs=-1)
 @placement_options
-def embed(model, texts, device, tp, sp, ep, cfg_parallel, pp):
+def embed(model, texts, device, tp, sp, ep, cfg_parallel, pp, parallel):
     """Embed texts; prints one JSON array per line."""
-    eng = _engine(device, tp, sp, ep, cfg_parallel, pp)
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp, parallel=parallel, model=model)
     for e in eng.embeddings.embed(ModelSpec(model, Modality.EMBEDDINGS, local_path=model), list(texts)):
         click.echo(json.dumps([round(float(x), 6) for x in e]))
 
@@ -266,15 +295,19 @@ def vision(model, images, texts, operation, threshold, device):
 @click.option("--api-key", "api_keys", multiple=True)
 @click.option("--max-concurrency", default=1)
 @click.option("--max-queue-depth", default=16)
-@click.option("--device", default="auto")
-def serve(host, port, models, api_keys, max_concurrency, max_queue_depth, device):
-    """Run the HTTP server."""
+@click.option("--allow-model-paths", is_flag=True, help="let API callers name arbitrary local paths as models")
+@placement_options
+def serve(host, port, models, api_keys, max_concurrency, max_queue_depth, allow_model_paths, device, tp, sp, ep, cfg_parallel,
+          pp, parallel):
+    """Run the HTTP server (rank 0 of a multi-GPU placement hosts it; the other ranks follow)."""
     import uvicorn
     from ..server import ServerOptions, create_app
     table = dict(m.split("=", 1) for m in models)
     first = next(iter(table), None)
+    eng = _engine(device, tp, sp, ep, cfg_parallel, pp, parallel=parallel, model=table.get(first, "") if first else "")
     app = create_app(ServerOptions(backend=device, models=table, api_keys=list(api_keys), max_concurrency=max_concurrency,
-                                   max_queue_depth=max_queue_depth, default_text_model=first))
+                                   max_queue_depth=max_queue_depth, default_text_model=first,
+                                   allow_model_paths=allow_model_paths), engine=eng)
     uvicorn.run(app, host=host, port=port)
 
 

@@ -1,0 +1,584 @@
+// Dense (non-causal) flash attention on the 5th-generation tensor cores, head dim 128, for the
+// long joint sequences of the DiT families (thousands to tens of thousands of tokens), in two
+// operand modes of one kernel:
+//   bf16   S = Q K^T with tcgen05.mma.kind::f16
+//   int8   "SageAttention": Q quantised to int8 with one scale per row, K with one scale per tile of
+//          128 keys after its per-head mean over the sequence has been removed (softmax cannot see
+//          a vector added to every key), S = Q8 K8^T with tcgen05.mma.kind::i8 (s32 accumulators);
+//          the dequantisation is one fused multiply-add inside the exponent; P V stays bf16.
+//          Replaces the reference's five-launch host sequence around sage_attn_int8_v1
+//          (src/HartsyInference.Cuda/Kernels/attention/sage_attn_int8_v1.cu:394-480, sage_attn_int8.cu
+//          sage_k_mean_f32 / sage_quant_q_int8_f32 / sage_quant_k_int8_f32; CudaBackend.cs:7623-7695)
+//          and its cuDNN SDPA path (CudnnSdpa.cs).
+//
+// One CTA owns TWO tiles of 128 query rows of one head and walks the keys in tiles of 128:
+//   warp 0       TMA producer: both Q tiles once, then K tile [128 keys x 128] and V^T tile [128
+//                dims x 128 keys] per step into separate rings
+//   warp 1       one thread issues every tcgen05.mma. TMEM holds S0 | S1 | O0 | O1 (4 x 128 columns).
+//                Per key tile j and query tile t: O_t += P_t(j) V_j with P_t read from TMEM (it lives in
+//                the first 64 columns of S_t, written there by the softmax warps), directly
+//                followed by S_t(j+1) = Q_t K_{j+1}^T, so the two query tiles alternate on the tensor
+//                core and each one's softmax overlaps the other one's matrix products
+//   warps 2..5   softmax of query tile 0; warps 6..9 softmax of query tile 1. Thread r owns query
+//                row r (TMEM lane r): reads its S row (tcgen05.ld), applies scale (and the int8
+//                dequantisation), keeps running maximum / sum in the exp2 domain, writes P as bf16
+//                pairs back into TMEM (tcgen05.st). O is never read back during the loop: the
+//                running maximum is only raised (and O rescaled in TMEM) when it would grow by
+//                more than 2^8, otherwise the stale maximum keeps being used, which is exact
+//                because the final division by the row sum uses the same maximum.
+//
+// V is consumed transposed ([head dim][keys], keys contiguous) so that both MMAs use K-major
+// operands; the transpose (and the int8 quantisation) is a small kernel of its own in front.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kFaD = 128;
+constexpr int kFaTile = 128;              // rows of one query tile and keys per step
+constexpr int kFaThreads = 320;           // producer, MMA, 2 x 4 softmax warps
+constexpr float kFaRescaleGap = 8.f;      // raise the running maximum only beyond this many powers of two
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct FaBarriers {
+  uint64_t q_full;
+  uint64_t k_full[3], k_empty[3];
+  uint64_t v_full[3], v_empty[3];
+  uint64_t s_full[2];        // S_t(j) is in TMEM
+  uint64_t p_ready[2];       // P_t(j) is in TMEM (and O_t rescaled if needed): 4 warp arrivals
+  uint64_t o_done[2];        // O_t += P_t(j) V_j has completed
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+struct FaParams {
+  __nv_bfloat16* out;        // [batch * sq][ld_out]
+  long long ld_out;
+  int sq, sk, heads, batch;
+  float scale_log2;          // softmax scale * log2(e)
+  // int8 mode: q_scale [batch * heads][sq_pad] (one per query row), k_scale [batch * heads][key tiles]
+  const float* q_scale;
+  const float* k_scale;
+  int sq_pad;
+  DeviceStatus* status;
+};
+
+template <bool kI8>
+__global__ void __maxnreg__(192)
+attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
+               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_vt) {
+  constexpr int kQkTileBytes = kI8 ? 128 * 128 : 128 * 128 * 2;   // one Q or K tile
+  constexpr int kQkAtoms = kI8 ? 1 : 2;                           // 128-byte-wide swizzle atoms per tile
+  constexpr int kVTileBytes = 128 * 128 * 2;
+  constexpr int kStages = kI8 ? 3 : 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* sq = smem;                                           // two Q tiles
+  uint8_t* sk = sq + 2 * kQkTileBytes;                          // K ring
+  uint8_t* sv = sk + kStages * kQkTileBytes;                    // V^T ring
+  FaBarriers* bars = reinterpret_cast<FaBarriers*>(sv + kStages * kVTileBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt2 = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  const int n_tiles = (p.sk + kFaTile - 1) / kFaTile;
+  const int q_row0 = b * p.sq + qt2 * 2 * kFaTile;     // row of the CTA's first query in [batch * sq]
+  const int k_row0 = b * p.sk;
+  const int vt_row0 = (b * p.heads + head) * kFaD;     // row in the [batch * heads * 128][sk_pad] matrix
+  const int col0 = head * kFaD;                        // element (= byte for int8) column of the head
+  // the second query tile may lie completely past the end of the sequence
+  const bool tile1 = qt2 * 2 * kFaTile + kFaTile < p.sq;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_ready[t], 4);
+      mbar_init(&bars->o_done[t], 1);
+    }
+    bars->abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_vt);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+  constexpr uint32_t kIdescS = kI8 ? make_idesc(128, 128, kFmtS8, kFmtS8, 2) : make_idesc(128, 128, kFmtBf16, kFmtBf16);
+  constexpr uint32_t kIdescPV = make_idesc(128, 128, kFmtBf16, kFmtBf16);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      const int nq = tile1 ? 2 : 1;
+      mbar_arrive_expect_tx(&bars->q_full, nq * kQkTileBytes);
+      for (int t = 0; t < nq; ++t)
+        for (int a = 0; a < kQkAtoms; ++a)
+          tma_load_2d(sq + t * kQkTileBytes + a * (kQkTileBytes / kQkAtoms), &tm_q, &bars->q_full,
+                      col0 + a * 64, q_row0 + t * kFaTile);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
+        if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(&bars->k_full[s], kQkTileBytes);
+        for (int a = 0; a < kQkAtoms; ++a)
+          tma_load_2d(sk + s * kQkTileBytes + a * (kQkTileBytes / kQkAtoms), &tm_k, &bars->k_full[s],
+                      col0 + a * 64, k_row0 + j * kFaTile);
+        if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(&bars->v_full[s], kVTileBytes);
+        tma_load_2d(sv + s * kVTileBytes, &tm_vt, &bars->v_full[s], j * kFaTile, vt_row0);
+        tma_load_2d(sv + s * kVTileBytes + kVTileBytes / 2, &tm_vt, &bars->v_full[s], j * kFaTile + 64, vt_row0);
+      }
+      if (!ok) report_status(p.status, kWaitTimeout, kKernelAttnPrefill, 21, blockIdx.x);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const int nq = tile1 ? 2 : 1;
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      // S_t(j) = Q_t K_j^T into TMEM columns [t * 128, t * 128 + 128)
+      auto issue_s = [&](int t, int j) {
+        const int s = j % kStages;
+        const uint32_t d_tmem = tmem_base + t * 128;
+#pragma unroll
+        for (int a = 0; a < kQkAtoms; ++a) {
+          const uint64_t ad = make_desc_sw128(smem_u32(sq + t * kQkTileBytes + a * (kQkTileBytes / kQkAtoms)));
+          const uint64_t bd = make_desc_sw128(smem_u32(sk + s * kQkTileBytes + a * (kQkTileBytes / kQkAtoms)));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (kI8) mma_i8_ss(d_tmem, ad + 2 * k, bd + 2 * k, kIdescS, (a | k) != 0);
+            else mma_bf16_ss(d_tmem, ad + 2 * k, bd + 2 * k, kIdescS, (a | k) != 0);
+          }
+        }
+        tc_commit(&bars->s_full[t]);
+      };
+      if (ok) ok = mbar_wait(&bars->k_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        for (int t = 0; t < nq; ++t) issue_s(t, 0);
+        tc_commit(&bars->k_empty[0]);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
+        for (int t = 0; t < nq && ok; ++t) {
+          if (!mbar_wait(&bars->p_ready[t], j & 1, abort_flag)) { ok = false; break; }
+          if (t == 0 && !mbar_wait(&bars->v_full[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          // O_t += P_t V_j: A = P_t in TMEM (64 columns of bf16 pairs), B = V^T tile (two atoms of 64 keys)
+          const uint32_t d_tmem = tmem_base + 256 + t * 128;
+          const uint32_t a_tmem = tmem_base + t * 128;
+#pragma unroll
+          for (int a = 0; a < 2; ++a) {
+            const uint64_t bd = make_desc_sw128(smem_u32(sv + s * kVTileBytes + a * (kVTileBytes / 2)));
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mma_bf16_ts(d_tmem, a_tmem + (a * 4 + k) * 8, bd + 2 * k, kIdescPV, (j | a | k) != 0);
+          }
+          tc_commit(&bars->o_done[t]);
+          if (t == nq - 1) tc_commit(&bars->v_empty[s]);
+          if (j + 1 < n_tiles) {
+            const int s1 = (j + 1) % kStages;
+            if (t == 0 && !mbar_wait(&bars->k_full[s1], static_cast<uint32_t>(((j + 1) / kStages) & 1), abort_flag)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue_s(t, j + 1);       // executes after the P_t V_j above: it overwrites the columns P_t lives in
+            if (t == nq - 1) tc_commit(&bars->k_empty[s1]);
+          }
+        }
+      }
+      if (!ok) report_status(p.status, kWaitTimeout, kKernelAttnPrefill, 22, blockIdx.x);
+    }
+  } else {
+    // ------------------------------------------------------------------------- softmax warps
+    const int t = (warp - 2) >> 2;                        // query tile of this warp group
+    const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;                  // query row inside the tile = TMEM lane
+    const int q_idx = qt2 * 2 * kFaTile + t * kFaTile + row;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_col = lane_base + t * 128, o_col = lane_base + 256 + t * 128;
+    if (t == 0 || tile1) {
+      float m_run = -INFINITY, l_run = 0.f;
+      float qs = p.scale_log2;
+      if (kI8)
+        qs *= q_idx < p.sq ? p.q_scale[static_cast<long long>(b * p.heads + head) * p.sq_pad + q_idx] : 0.f;
+      bool ok = true;
+      const float* ksc = kI8 ? p.k_scale + static_cast<long long>(b * p.heads + head) * n_tiles : nullptr;
+      float ks_next = kI8 ? ksc[0] : 1.f;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        // scores -> exp2 domain: x = raw * c (bf16: c = scale; int8: c = q row scale * K tile scale * scale)
+        const float c = qs * ks_next;
+        if (kI8 && j + 1 < n_tiles) ks_next = ksc[j + 1];
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full[t], j & 1, abort_flag))) { ok = false; break; }
+        tc_fence_after_sync();
+        const int key0 = j * kFaTile;
+        const bool tail = key0 + kFaTile > p.sk;
+        // the whole raw S row of this thread: four loads in flight, one wait
+        uint32_t r[128];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) tmem_ld_32x32(s_col + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[cc * 32]));
+        tmem_ld_wait();
+        if (tail) {
+          // keys past the end: the most negative value the exponent path below maps far below any maximum
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (key0 + i >= p.sk) r[i] = kI8 ? static_cast<uint32_t>(-(1 << 22)) : 0xff800000u;
+        }
+        float mx;
+        if (kI8) {
+          int mi = static_cast<int>(r[0]);
+#pragma unroll
+          for (int i = 1; i < 128; ++i) mi = max(mi, static_cast<int>(r[i]));
+          mx = static_cast<float>(mi) * c;
+        } else {
+          float mf = __uint_as_float(r[0]);
+#pragma unroll
+          for (int i = 1; i < 128; ++i) mf = fmaxf(mf, __uint_as_float(r[i]));
+          mx = mf * c;
+        }
+        // raise the running maximum only when it would grow by more than the gap (or on the first
+        // tile); a warp decides together because the O rescale below is a warp-wide TMEM access
+        const bool grow = mx > m_run + kFaRescaleGap;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m_run, mx);
+          const float alpha = m_run == -INFINITY ? 0.f : fast_exp2(m_run - m_new);
+          if (j > 0) {
+            // O_t must be complete up to tile j - 1 before it is rescaled
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->o_done[t], (j - 1) & 1, abort_flag))) { ok = false; break; }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+              uint32_t o[32];
+              tmem_ld_32x32(o_col + cc * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st_32x32(o_col + cc * 32, o);
+            }
+            tmem_st_wait();
+          }
+          l_run *= alpha;
+          m_run = m_new;
+        }
+        const float m_safe = m_run == -INFINITY ? 0.f : m_run;
+        // p = 2^(raw * c - m): one fused multiply-add and one ex2 per score. int8: the s32 score is
+        // turned into 12582912 + s by an integer add on its bits (exact for |s| < 2^22) and the
+        // constant is folded into the subtrahend, so no conversion instruction is spent
+        const float sub = kI8 ? fmaf(12582912.f, c, m_safe) : m_safe;
+        float sum = 0.f;
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t packed[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t r0 = r[cc * 64 + 2 * i], r1 = r[cc * 64 + 2 * i + 1];
+            const float f0 = kI8 ? __uint_as_float(r0 + 0x4B400000u) : __uint_as_float(r0);
+            const float f1 = kI8 ? __uint_as_float(r1 + 0x4B400000u) : __uint_as_float(r1);
+            const float a = fast_exp2(fmaf(f0, c, -sub));
+            const float bq = fast_exp2(fmaf(f1, c, -sub));
+            sum += a + bq;
+            packed[i] = pack_bf16x2(a, bq);
+          }
+          tmem_st_32x32(s_col + cc * 32, packed);      // P_t: columns [0, 64) of S_t
+        }
+        tmem_st_wait();
+        l_run += sum;
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_ready[t]);
+      }
+      if (ok && n_tiles > 0)
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_done[t], (n_tiles - 1) & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) report_status(p.status, kWaitTimeout, kKernelAttnPrefill, 23, blockIdx.x);
+      } else {
+        tc_fence_after_sync();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* dst = p.out + static_cast<long long>(q_row0 + t * kFaTile + row) * p.ld_out + col0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(o_col + c * 32, r);
+          tmem_ld_wait();
+          if (q_idx < p.sq) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                w[u] = pack_bf16x2(__uint_as_float(r[i + 2 * u]) * inv, __uint_as_float(r[i + 2 * u + 1]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// v [batch * sk][ld] (head h at columns h * 128 ...) -> vt [batch * heads * 128][sk_pad], zero padded
+__global__ void fa_transpose_v_kernel(const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ vt, long long ld,
+                                      int sk, int sk_pad, int heads) {
+  __shared__ __nv_bfloat16 tile[64][66];
+  const int bh = blockIdx.z, b = bh / heads, h = bh % heads;
+  const int key0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  for (int i = threadIdx.y; i < 64; i += blockDim.y) {
+    const int key = key0 + i;
+    for (int j = threadIdx.x; j < 64; j += blockDim.x)
+      tile[i][j] = key < sk ? v[(static_cast<long long>(b) * sk + key) * ld + h * kFaD + d0 + j] : __float2bfloat16(0.f);
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 64; i += blockDim.y) {
+    const long long row = (static_cast<long long>(bh) * kFaD + d0 + i) * sk_pad;
+    for (int j = threadIdx.x; j < 64; j += blockDim.x)
+      if (key0 + j < sk_pad) vt[row + key0 + j] = tile[j][i];
+  }
+}
+
+// ---- SageAttention preparation --------------------------------------------------------------
+// Column sums of K per (batch, head): ksum [batch * heads][128] fp32 (zeroed by the caller), so that
+// mean = ksum / sk. grid (chunks of 256 keys, batch * heads), 128 threads (one per dim).
+__global__ void sage_k_sum_kernel(const __nv_bfloat16* __restrict__ k, float* __restrict__ ksum, long long ld, int sk,
+                                  int heads) {
+  const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
+  const int key0 = blockIdx.x * 256, key1 = min(sk, key0 + 256);
+  float acc = 0.f;
+  for (int key = key0; key < key1; ++key)
+    acc += __bfloat162float(k[(static_cast<long long>(b) * sk + key) * ld + h * kFaD + threadIdx.x]);
+  atomicAdd(ksum + static_cast<long long>(bh) * kFaD + threadIdx.x, acc);
+}
+
+// Row quantisation to int8: one warp per (row, head). x [batch * s][ld] bf16 -> out [batch * s][ld]
+// int8 (same column layout), scale [batch * heads][s_pad] fp32 = max|row| / 127. `center` (optional,
+// [batch * heads][128], with `center_div`) is subtracted first: the K mean.
+__global__ void sage_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ out,
+                                       float* __restrict__ scale, const float* __restrict__ center, float center_div,
+                                       long long ld, int s, int s_pad, int heads, int batch) {
+  const int lane = threadIdx.x & 31;
+  const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = static_cast<long long>(batch) * s * heads;
+  if (w >= total) return;
+  const int h = static_cast<int>(w % heads);
+  const long long row = w / heads;                 // row in [batch * s]
+  const int b = static_cast<int>(row / s), tok = static_cast<int>(row % s);
+  const __nv_bfloat16* src = x + row * ld + h * kFaD + lane * 4;
+  const uint2 raw = *reinterpret_cast<const uint2*>(src);
+  const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float v[4];
+  v[0] = __bfloat162float(hp[0].x); v[1] = __bfloat162float(hp[0].y);
+  v[2] = __bfloat162float(hp[1].x); v[3] = __bfloat162float(hp[1].y);
+  if (center) {
+    const float* c = center + static_cast<long long>(b * heads + h) * kFaD + lane * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] -= c[i] / center_div;
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  amax = warp_max(amax);
+  const float sc = fmaxf(amax, 1e-12f) / 127.f;
+  const float inv = 1.f / sc;
+  uint32_t q = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int iv = max(-127, min(127, __float2int_rn(v[i] * inv)));
+    q |= static_cast<uint32_t>(static_cast<uint8_t>(static_cast<int8_t>(iv))) << (8 * i);
+  }
+  *reinterpret_cast<uint32_t*>(out + row * ld + h * kFaD + lane * 4) = q;
+  if (lane == 0) scale[static_cast<long long>(b * heads + h) * s_pad + tok] = sc;
+}
+
+// K quantisation with one scale per tile of 128 keys: grid (key tiles, batch * heads), 256 threads;
+// thread (row, half) handles 64 dims of one key. k [batch * sk][ld] bf16 -> out int8 (same layout),
+// scale [batch * heads][key tiles] = max|tile - mean| / 127. `center` [batch * heads][128] holds the
+// column sums of K (mean = center / sk).
+__global__ void __launch_bounds__(256) sage_quant_k_tiles_kernel(const __nv_bfloat16* __restrict__ k,
+                                                                 int8_t* __restrict__ out, float* __restrict__ scale,
+                                                                 const float* __restrict__ center, long long ld, int sk,
+                                                                 int heads) {
+  __shared__ float wmax[8];
+  const int tile = blockIdx.x, bh = blockIdx.y, b = bh / heads, h = bh % heads;
+  const int n_tiles = gridDim.x;
+  const int key = tile * kFaTile + (threadIdx.x >> 1), d0 = (threadIdx.x & 1) * 64;
+  const bool valid = key < sk;
+  float v[64];
+  float amax = 0.f;
+  const float inv_sk = 1.f / static_cast<float>(sk);
+  if (valid) {
+    const __nv_bfloat16* src = k + (static_cast<long long>(b) * sk + key) * ld + h * kFaD + d0;
+    const float* c = center + static_cast<long long>(bh) * kFaD + d0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + i * 8);
+      const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 f = __bfloat1622float2(hp[u]);
+        v[i * 8 + 2 * u] = f.x - c[i * 8 + 2 * u] * inv_sk;
+        v[i * 8 + 2 * u + 1] = f.y - c[i * 8 + 2 * u + 1] * inv_sk;
+        amax = fmaxf(amax, fmaxf(fabsf(v[i * 8 + 2 * u]), fabsf(v[i * 8 + 2 * u + 1])));
+      }
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = wmax[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, wmax[i]);
+  const float sc = fmaxf(amax, 1e-12f) / 127.f;
+  if (threadIdx.x == 0) scale[static_cast<long long>(bh) * n_tiles + tile] = sc;
+  if (!valid) return;
+  const float inv = 1.f / sc;
+  int8_t* dst = out + (static_cast<long long>(b) * sk + key) * ld + h * kFaD + d0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 q;
+    uint32_t* qw = reinterpret_cast<uint32_t*>(&q);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int iv = max(-127, min(127, __float2int_rn(v[i * 16 + w * 4 + e] * inv)));
+        word |= static_cast<uint32_t>(static_cast<uint8_t>(static_cast<int8_t>(iv))) << (8 * e);
+      }
+      qw[w] = word;
+    }
+    *reinterpret_cast<uint4*>(dst + i * 16) = q;
+  }
+}
+
+}  // namespace b200
+
+namespace b200 {
+// defined in gemm_tcgen05.cu
+int make_kmajor_map(CUtensorMap* out, const void* base, int elem_bytes, long long rows, long long k,
+                    long long ld, int box_rows);
+}  // namespace b200
+
+using namespace b200;
+
+static inline int fa_pad(int s, int to) { return (s + to - 1) / to * to; }
+
+// Scratch layout of one call: V^T [batch * heads * 128][sk_pad64] bf16, then (int8 mode) Q8
+// [batch * sq][heads * 128], K8 [batch * sk][heads * 128], q scales [batch * heads][sq_pad128],
+// K tile scales [batch * heads][key tiles] fp32, K sums [batch * heads][128] fp32.
+struct FaScratch {
+  long long vt, q8, k8, qs, ks, ksum, total;
+};
+static FaScratch fa_scratch(int batch, int heads, int sq, int sk, int int8) {
+  FaScratch s{};
+  auto up = [](long long v) { return (v + 255) / 256 * 256; };
+  long long off = 0;
+  s.vt = off; off = up(off + static_cast<long long>(batch) * heads * kFaD * fa_pad(sk, 64) * 2);
+  if (int8) {
+    s.q8 = off; off = up(off + static_cast<long long>(batch) * sq * heads * kFaD);
+    s.k8 = off; off = up(off + static_cast<long long>(batch) * sk * heads * kFaD);
+    s.qs = off; off = up(off + static_cast<long long>(batch) * heads * fa_pad(sq, 128) * 4);
+    s.ks = off; off = up(off + static_cast<long long>(batch) * heads * (fa_pad(sk, 128) / 128) * 4);
+    s.ksum = off; off = up(off + static_cast<long long>(batch) * heads * kFaD * 4);
+  }
+  s.total = off;
+  return s;
+}
+
+B200_API long long b200_attn_fa_workspace_bytes(int batch, int heads, int sq, int sk, int int8) {
+  return fa_scratch(batch, heads, sq, sk, int8).total;
+}
+
+// Dense attention, head dim 128: q [batch * sq][heads * 128], k / v [batch * sk][heads * 128] bf16
+// (contiguous), out like q: softmax(q k^T * scale) v per (batch, head). int8 != 0: SageAttention
+// (K mean removal, int8 Q K^T). `scratch`: b200_attn_fa_workspace_bytes bytes.
+B200_API int b200_attn_fa(const void* q, const void* k, const void* v, void* out, int batch, int sq, int sk,
+                          int heads, float scale, int int8, void* scratch, void* status, cudaStream_t stream) {
+  if (batch <= 0 || sq <= 0 || sk <= 0) return 0;
+  if (scratch == nullptr) return -2;
+  const long long ld = static_cast<long long>(heads) * kFaD;
+  const FaScratch sc = fa_scratch(batch, heads, sq, sk, int8);
+  uint8_t* base = static_cast<uint8_t*>(scratch);
+  const int sk_pad64 = fa_pad(sk, 64);
+  dim3 tgrid((sk_pad64 + 63) / 64, kFaD / 64, batch * heads);
+  fa_transpose_v_kernel<<<tgrid, dim3(32, 8), 0, stream>>>(static_cast<const __nv_bfloat16*>(v),
+                                                           reinterpret_cast<__nv_bfloat16*>(base + sc.vt), ld, sk,
+                                                           sk_pad64, heads);
+  FaParams p{};
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ld_out = ld;
+  p.sq = sq; p.sk = sk; p.heads = heads; p.batch = batch;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = static_cast<DeviceStatus*>(status);
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if (int8) {
+    const int sq_pad = fa_pad(sq, 128), n_tiles = fa_pad(sk, 128) / 128;
+    float* ksum = reinterpret_cast<float*>(base + sc.ksum);
+    float* qs = reinterpret_cast<float*>(base + sc.qs);
+    float* ks = reinterpret_cast<float*>(base + sc.ks);
+    if (cudaMemsetAsync(ksum, 0, static_cast<size_t>(batch) * heads * kFaD * 4, stream) != cudaSuccess) return -3;
+    sage_k_sum_kernel<<<dim3((sk + 255) / 256, batch * heads), 128, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(k), ksum, ld, sk, heads);
+    const long long wq = static_cast<long long>(batch) * sq * heads;
+    sage_quant_rows_kernel<<<static_cast<unsigned>((wq + 7) / 8), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(q), reinterpret_cast<int8_t*>(base + sc.q8), qs, nullptr, 1.f, ld, sq, sq_pad,
+        heads, batch);
+    sage_quant_k_tiles_kernel<<<dim3(n_tiles, batch * heads), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(k), reinterpret_cast<int8_t*>(base + sc.k8), ks, ksum, ld, sk, heads);
+    p.q_scale = qs;
+    p.k_scale = ks;
+    p.sq_pad = sq_pad;
+    rc = make_kmajor_map(&tq, base + sc.q8, 1, static_cast<long long>(batch) * sq, ld, ld, 128);
+    if (rc) return rc;
+    rc = make_kmajor_map(&tk, base + sc.k8, 1, static_cast<long long>(batch) * sk, ld, ld, 128);
+    if (rc) return rc;
+  } else {
+    rc = make_kmajor_map(&tq, q, 2, static_cast<long long>(batch) * sq, ld, ld, 128);
+    if (rc) return rc;
+    rc = make_kmajor_map(&tk, k, 2, static_cast<long long>(batch) * sk, ld, ld, 128);
+    if (rc) return rc;
+  }
+  rc = make_kmajor_map(&tv, base + sc.vt, 2, static_cast<long long>(batch) * heads * kFaD, sk_pad64, sk_pad64, 128);
+  if (rc) return rc;
+  const int qk_tile = int8 ? 128 * 128 : 128 * 128 * 2;
+  const int stages = int8 ? 3 : 2;
+  const int smem = 2 * qk_tile + stages * (qk_tile + 128 * 128 * 2) + static_cast<int>(sizeof(FaBarriers)) + 1024;
+  static PerDeviceOnce configured[2];
+  dim3 grid((sq + 2 * kFaTile - 1) / (2 * kFaTile), heads, batch);
+  if (int8) {
+    if (configured[1].first_time() &&
+        cudaFuncSetAttribute(attn_fa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return -4;
+    attn_fa_kernel<true><<<grid, kFaThreads, smem, stream>>>(p, tq, tk, tv);
+  } else {
+    if (configured[0].first_time() &&
+        cudaFuncSetAttribute(attn_fa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return -4;
+    attn_fa_kernel<false><<<grid, kFaThreads, smem, stream>>>(p, tq, tk, tv);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -300;
+}

@@ -18,6 +18,9 @@ __device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
 __device__ __forceinline__ void red_release_sys_add(uint32_t* addr, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_relaxed_sys_add(uint32_t* addr, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");

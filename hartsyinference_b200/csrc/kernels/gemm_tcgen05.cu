@@ -433,56 +433,89 @@ __device__ __forceinline__ void ar_signal(const AllReduceParams& a, int which) {
   if (a.use_mc) {
     multimem_red_release_add(a.flags[0] + which, 1u);
   } else {
-    for (int r = 0; r < a.world; ++r) red_release_sys_add(a.flags[(a.rank + r) % a.world] + which, 1u);
+    // one release fence at system scope, then a relaxed add per peer (a release on every add
+    // would pay the fence once per peer)
+    fence_acq_rel_sys();
+    for (int r = 0; r < a.world; ++r) red_relaxed_sys_add(a.flags[(a.rank + r) % a.world] + which, 1u);
   }
 }
 
+// Layout of the rank-local counter block `ctr` (u32 words, zero-initialised once):
+//   [0] calls completed   [1] CTAs past the GEMM   [2] CTAs done with their reduce units   [3] CTAs finished
+//   [64, 192)    per owned row: segments of the row whose sum of squares has been posted
+//   [256, 2304)  per owned row 16 floats: the segments' sums of squares
+constexpr int kArRowCounters = 64, kArRowPartials = 256, kArCtrWords = 2304, kArMaxSegs = 16;
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
 // Called by the 256 epilogue threads of every CTA once all its work items are stored.
-__device__ __forceinline__ void ar_finish(const GemmParams& p, uint8_t* smem, GemmBarriers* bars) {
+__device__ __forceinline__ void ar_finish(const GemmParams& p, GemmBarriers* bars) {
   const AllReduceParams& a = p.ar;
   const int et = threadIdx.x - 64;
   const int m = p.rows_b, n = p.rows_a;          // tokens, features
   const uint32_t call = *reinterpret_cast<volatile uint32_t*>(a.ctr) + 1u;   // 1-based index of this call
-  // ---- 2. this CTA's partial tiles are written; the rank's last CTA tells every rank
+  // ---- 2. this CTA's partial tiles are written; the rank's last CTA tells every rank. Peers read
+  // the tiles through this GPU's L2, so a device-scope fence per CTA orders them; the one release
+  // at system scope by the last CTA then covers all of them (fences are cumulative).
   epilogue_barrier();
   if (et == 0) {
-    __threadfence_system();
+    __threadfence();
     if (atomicAdd(a.ctr + 1, 1u) == gridDim.x - 1 && !a.debug_skip_ready) {
-      __threadfence_system();
+      __threadfence();
       ar_signal(a, 0);
     }
   }
-  // ---- 3. rows owned by this rank: contiguous block of ceil(m / world)
+  // ---- 3. rows owned by this rank: a contiguous block of ceil(m / world). A row is cut into
+  // segments of 256 vectors of eight features (one vector per thread) and the (row, segment) units
+  // are dealt to the CTAs, so that even a few rows keep many SMs' worth of loads in flight; the
+  // segments of a row meet through a sum-of-squares slot per segment and a counter per row.
   const int per = (m + a.world - 1) / a.world;
   const int row0 = a.rank * per;
   const int owned = max(0, min(per, m - row0));
-  const int row_ctas = min(owned, static_cast<int>(gridDim.x));
-  if (static_cast<int>(blockIdx.x) < row_ctas) {
+  const int nvec = n >> 3;
+  const int nseg = (nvec + 255) >> 8;
+  const int units = owned * nseg;
+  const int unit_ctas = min(units, static_cast<int>(gridDim.x));
+  if (static_cast<int>(blockIdx.x) < unit_ctas) {
     if (et == 0) {
       const bool ok = wait_flag_geq(a.flags_local, call * static_cast<uint32_t>(a.world), a.wait_budget);
       if (!ok) report_status(p.status, kWaitTimeout, kKernelGemmAllReduce, 1, blockIdx.x);
       bars->flag = ok ? 1u : 0u;
     }
     epilogue_barrier();
-    const bool ok = bars->flag != 0;
+    bool ok = bars->flag != 0;
     epilogue_barrier();
-    const int nvec = n >> 3;
-    uint4* rowbuf = reinterpret_cast<uint4*>(smem);            // the pipeline stages are idle by now
-    uint8_t* sfb = smem + static_cast<size_t>(n) * 2;            // one exponent byte per 128 features
     float* red = &bars->cs_bcast[0][0][0];
+    uint8_t* sfb = reinterpret_cast<uint8_t*>(&bars->cs_bcast[1][0][0]);   // exponent bytes of this unit
+    uint32_t* rowcnt = a.ctr + kArRowCounters;
+    float* rowpart = reinterpret_cast<float*>(a.ctr + kArRowPartials);
     const int kb_n = n >> 7, kgroups = (n + 511) >> 9;
-    for (int ri = blockIdx.x; ri < owned && ok; ri += gridDim.x) {
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      const int ri = u / nseg, seg = u - ri * nseg;
       const int row = row0 + ri;
-      float sumsq = 0.f;
-      for (int v = et; v < nvec; v += 256) {
-        float acc[8];
+      const int v = seg * 256 + et;
+      const bool active = v < nvec;
+      // -- sum over ranks (and K splits) of this thread's eight features, + bias, + residual
+      float acc[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        for (int sp = 0; sp < p.splits; ++sp) {
-          const long long off = (static_cast<long long>(sp) * m + row) * n + v * 8;
-          if (a.use_mc) {
-            add_bf16x8(acc, multimem_ld_reduce_bf16x8(a.part_src[0] + off));
-          } else {
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      if (active) {
+        if (a.use_mc) {
+          uint4 x[4];
+#pragma unroll
+          for (int sp = 0; sp < 4; ++sp)
+            if (sp < p.splits)
+              x[sp] = multimem_ld_reduce_bf16x8(a.part_src[0] + (static_cast<long long>(sp) * m + row) * n + v * 8);
+#pragma unroll
+          for (int sp = 0; sp < 4; ++sp)
+            if (sp < p.splits) add_bf16x8(acc, x[sp]);
+        } else {
+          for (int sp = 0; sp < p.splits; ++sp) {
+            const long long off = (static_cast<long long>(sp) * m + row) * n + v * 8;
             uint4 x[8];
 #pragma unroll
             for (int r = 0; r < 8; ++r)
@@ -493,124 +526,152 @@ __device__ __forceinline__ void ar_finish(const GemmParams& p, uint8_t* smem, Ge
           }
         }
         if (a.bias) add_bf16x8(acc, *reinterpret_cast<const uint4*>(a.bias + v * 8));
-        // what the unfused path would have stored as the all-reduce result is bf16: round here too
-        uint4 packed;
-        uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
+      }
+      // what the unfused path would have stored as the all-reduce result is bf16: round here too
+      uint4 packed;
+      uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) pw[i] = pack_bf16x2(acc[2 * i], acc[2 * i + 1]);
-        if (a.res) {
-          __nv_bfloat16* rr = a.res + static_cast<long long>(row) * n + v * 8;
-          float t[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) t[i] = 0.f;
-          add_bf16x8(t, packed);
-          add_bf16x8(t, *reinterpret_cast<const uint4*>(rr));
-#pragma unroll
-          for (int i = 0; i < 4; ++i) pw[i] = pack_bf16x2(t[2 * i], t[2 * i + 1]);
-          *reinterpret_cast<uint4*>(rr) = packed;          // new residual row (this rank only)
-        }
-        rowbuf[v] = packed;
+      for (int i = 0; i < 4; ++i) pw[i] = pack_bf16x2(acc[2 * i], acc[2 * i + 1]);
+      if (active && a.res) {
+        __nv_bfloat16* rr = a.res + static_cast<long long>(row) * n + v * 8;
         float t[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) t[i] = 0.f;
         add_bf16x8(t, packed);
+        add_bf16x8(t, *reinterpret_cast<const uint4*>(rr));
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sumsq += t[i] * t[i];
+        for (int i = 0; i < 4; ++i) pw[i] = pack_bf16x2(t[2 * i], t[2 * i + 1]);
+        *reinterpret_cast<uint4*>(rr) = packed;          // new residual row (this rank only)
       }
+      float y[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = 0.f;
+      add_bf16x8(y, packed);
       float rstd = 1.f;
-      if (a.norm_w) rstd = rsqrtf(epilogue_block_sum(sumsq, red) / n + a.eps);
+      if (a.norm_w) {
+        float sumsq = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sumsq += y[i] * y[i];
+        const float part = epilogue_block_sum(sumsq, red);
+        if (et == 0) {
+          float total = part;
+          if (nseg > 1) {
+            // post this segment's share, then wait for the row's other segments (all resident: every
+            // CTA of the grid is; units are taken in ascending order, so the lowest unfinished row
+            // never waits on a CTA that is itself blocked)
+            rowpart[ri * kArMaxSegs + seg] = part;
+            __threadfence();
+            atomicAdd(rowcnt + ri, 1u);
+            long long t0 = 0;
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(rowcnt + ri) < static_cast<uint32_t>(nseg)) {
+              if ((++spins & 0x3f) == 0) {
+                const long long now = clock64();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > a.wait_budget) { ok = false; break; }
+              }
+            }
+            total = 0.f;
+            for (int sg = 0; sg < nseg; ++sg) total += __ldcg(rowpart + ri * kArMaxSegs + sg);   // fixed order
+            if (!ok) report_status(p.status, kWaitTimeout, kKernelGemmAllReduce, 3, blockIdx.x);
+          }
+          red[8] = rsqrtf(total / n + a.eps);
+          bars->flag = ok ? 1u : 0u;
+        }
+        epilogue_barrier();
+        rstd = red[8];
+        ok = bars->flag != 0;
+        epilogue_barrier();
+        if (!ok) break;
+      }
       const long long rbase = static_cast<long long>(row) * n;
-      for (int v = et; v < ((nvec + 31) & ~31); v += 256) {
-        const bool active = v < nvec;
-        float y[8];
+      if (active) {
+        if (a.norm_w) {
+          float w[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w[i] = 0.f;
+          add_bf16x8(w, *reinterpret_cast<const uint4*>(a.norm_w + v * 8));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) y[i] = y[i] * rstd * (a.weight_plus_one ? 1.f + w[i] : w[i]);
+        }
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ow[i] = pack_bf16x2(y[2 * i], y[2 * i + 1]);
+        if (a.out_bf16[0]) ar_store_all(a, a.out_bf16, rbase + v * 8, o, 16);
+        // fp8 consumers see the bf16-rounded activations, like the unfused path
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] = 0.f;
-        if (active) {
-          add_bf16x8(y, rowbuf[v]);
-          if (a.norm_w) {
-            float w[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) w[i] = 0.f;
-            add_bf16x8(w, *reinterpret_cast<const uint4*>(a.norm_w + v * 8));
-#pragma unroll
-            for (int i = 0; i < 8; ++i) y[i] = y[i] * rstd * (a.weight_plus_one ? 1.f + w[i] : w[i]);
-          }
-          uint4 o;
-          uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) ow[i] = pack_bf16x2(y[2 * i], y[2 * i + 1]);
-          if (a.out_bf16[0]) ar_store_all(a, a.out_bf16, rbase + v * 8, o, 16);
-          // fp8 consumers see the bf16-rounded activations, like the unfused path
-#pragma unroll
-          for (int i = 0; i < 8; ++i) y[i] = 0.f;
-          add_bf16x8(y, o);
-        }
-        if (a.out_q[0]) {
-          // n % 128 == 0: a 16-lane group is all-active or all-inactive
-          float amax = 0.f;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(y[i]));
-#pragma unroll
-          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-          if (active) {
-            float sc = fmaxf(amax, 1e-12f) / kArFp8Max;
-            float inv = 1.f / sc;
-            uint32_t eb = 127;
-            if (a.sf_tile_rows > 0) {
-              // UE8M0: the smallest power of two >= amax / 448
-              const uint32_t bits = __float_as_uint(amax / kArFp8Max);
-              int e = static_cast<int>(bits >> 23) - 127 + ((bits & 0x7fffffu) != 0 ? 1 : 0);
-              e = max(-126, min(126, e));
-              eb = static_cast<uint32_t>(e + 127);
-              inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-            }
-            uint4 q = make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              q.x |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(y[i] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              q.y |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(y[4 + i] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
-            ar_store_all(a, a.out_q, rbase + v * 8, q, 8);
-            if ((v & 15) == 0) {
-              if (a.sf_tile_rows > 0) sfb[v >> 4] = static_cast<uint8_t>(eb);
-              else ar_store_all(a, a.out_sf, static_cast<long long>(row) * kb_n + (v >> 4),
-                                make_uint4(__float_as_uint(sc), 0, 0, 0), 4);
-            }
-          }
-        }
+        add_bf16x8(y, o);
       }
-      if (a.out_q[0] && a.sf_tile_rows > 0) {
-        // blocked UE8M0 layout: one 32-bit word per (row, group of four 128-wide K blocks)
-        epilogue_barrier();
-        if (et < kgroups) {
-          uint32_t word = 0;
+      if (a.out_q[0]) {
+        // n % 128 == 0: a 16-lane group is all-active or all-inactive
+        float amax = 0.f;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int kb = et * 4 + i;
-            word |= static_cast<uint32_t>(kb < kb_n ? sfb[kb] : 127) << (8 * i);
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(y[i]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (active) {
+          float sc = fmaxf(amax, 1e-12f) / kArFp8Max;
+          float inv = 1.f / sc;
+          uint32_t eb = 127;
+          if (a.sf_tile_rows > 0) {
+            // UE8M0: the smallest power of two >= amax / 448
+            const uint32_t bits = __float_as_uint(amax / kArFp8Max);
+            int e = static_cast<int>(bits >> 23) - 127 + ((bits & 0x7fffffu) != 0 ? 1 : 0);
+            e = max(-126, min(126, e));
+            eb = static_cast<uint32_t>(e + 127);
+            inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
           }
-          const int tile = row / a.sf_tile_rows, r = row - tile * a.sf_tile_rows;
-          const long long widx = (static_cast<long long>(tile) * kgroups + et) * 128 + (r & 31) * 4 + (r >> 5);
-          ar_store_all(a, a.out_sf, widx, make_uint4(word, 0, 0, 0), 4);
+          uint4 q = make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            q.x |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(y[i] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            q.y |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(y[4 + i] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+          ar_store_all(a, a.out_q, rbase + v * 8, q, 8);
+          if ((et & 15) == 0) {
+            if (a.sf_tile_rows > 0) sfb[et >> 4] = static_cast<uint8_t>(eb);
+            else ar_store_all(a, a.out_sf, static_cast<long long>(row) * kb_n + (v >> 4),
+                              make_uint4(__float_as_uint(sc), 0, 0, 0), 4);
+          }
         }
-        epilogue_barrier();
+        if (a.sf_tile_rows > 0) {
+          // blocked UE8M0 layout: one 32-bit word per (row, group of four 128-wide K blocks); a
+          // segment of 2048 features owns four whole words
+          epilogue_barrier();
+          const int kg = seg * 4 + et;
+          if (et < 4 && kg < kgroups) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              word |= static_cast<uint32_t>(kg * 4 + i < kb_n ? sfb[et * 4 + i] : 127) << (8 * i);
+            const int tile = row / a.sf_tile_rows, r = row - tile * a.sf_tile_rows;
+            const long long widx = (static_cast<long long>(tile) * kgroups + kg) * 128 + (r & 31) * 4 + (r >> 5);
+            ar_store_all(a, a.out_sf, widx, make_uint4(word, 0, 0, 0), 4);
+          }
+          epilogue_barrier();
+        }
       }
     }
   }
-  // ---- 4. this rank's rows are out: its last row CTA raises `done` everywhere (a rank without
-  // rows does so right away), and CTA 0 holds the kernel until every rank's rows have landed here
+  // ---- 4. this rank's rows are out: the last CTA with units raises `done` everywhere (a rank
+  // without rows does so right away), and CTA 0 holds the kernel until every rank's rows have
+  // landed here
   epilogue_barrier();
   if (et == 0) {
     bool signal = false;
-    if (row_ctas == 0) {
+    if (unit_ctas == 0) {
       signal = blockIdx.x == 0;
-    } else if (static_cast<int>(blockIdx.x) < row_ctas) {
+    } else if (static_cast<int>(blockIdx.x) < unit_ctas) {
+      // this CTA's stores went to other GPUs: they must have been performed system-wide before the
+      // count below lets another CTA announce them
       __threadfence_system();
-      signal = atomicAdd(a.ctr + 2, 1u) == static_cast<uint32_t>(row_ctas) - 1;
+      signal = atomicAdd(a.ctr + 2, 1u) == static_cast<uint32_t>(unit_ctas) - 1;
     }
     if (signal) {
-      __threadfence_system();
+      __threadfence();
       ar_signal(a, 1);
     }
     if (blockIdx.x == 0 &&
@@ -1042,7 +1103,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       }
       finish_item<BN>(p, it, ok, &bars->flag);
     }
-    if (p.ar.world > 0) ar_finish(p, smem, bars);
+    if (p.ar.world > 0) ar_finish(p, bars);
   }
 
   // the single-lane roles rejoin their warps before the CTA-wide barrier
@@ -1098,6 +1159,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       p.ar.ctr[1] = 0;
       p.ar.ctr[2] = 0;
       p.ar.ctr[3] = 0;
+      for (int i = 0; i < 128; ++i) p.ar.ctr[kArRowCounters + i] = 0;
       *reinterpret_cast<volatile uint32_t*>(p.ar.ctr) = e + 1u;
       __threadfence();
     }
@@ -1254,7 +1316,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   p.status = static_cast<DeviceStatus*>(status);
   p.swap_out = swap ? 1 : 0;
   if (ar != nullptr) {
-    if (m > 128 || n % 128 != 0 || groups > 0 || cs != nullptr) return -6;   // one token tile, whole feature tiles
+    if (m > 128 || n % 128 != 0 || groups > 0 || cs != nullptr || ar->part_splits > 4) return -6;   // one token tile, whole feature tiles
     if (bias != nullptr || gate != nullptr || residual != nullptr || act != 0) return -6;   // see AllReduceParams
     p.ar = *ar;
     // K splits fill the machine when there are fewer tiles than SMs; every split is one more
@@ -1478,11 +1540,13 @@ B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, in
 // for m <= 128 tokens and n a multiple of 128 (and of 128 when out_q is asked for). See
 // AllReduceParams for the protocol. `part_src`, `out_*`, `flags` are arrays of `world` peer
 // pointers into the symmetric heap (index = rank), or, with use_mc = 1, arrays whose entry 0 is
-// the multicast alias of the buffer. `part` (partials), `flags_local` (two u32) and `ctr` (four
-// u32) are this rank's own, zero-initialised once. Every wait on a peer is bounded by
+// the multicast alias of the buffer. `part` (partials), `flags_local` (two u32) and `ctr`
+// (b200_gemm_allreduce_ctr_bytes() bytes) are this rank's own, zero-initialised once. Every wait on a peer is bounded by
 // `wait_budget_cycles` and reports through `status`. `debug_skip_ready` = 1 (tests of the timeout
 // path) makes this rank withhold its `ready` signal: the waits then give up, report and return, and
 // the counters must be cleared on every rank before the next call.
+B200_API long long b200_gemm_allreduce_ctr_bytes() { return kArCtrWords * 4; }
+
 B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int k, long long ldx,
                                  long long ldw, int dtype, const float* x_scale, const float* w_scale,
                                  const void* bias, void* res, const void* norm_w, float eps,
@@ -1495,6 +1559,7 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return -7;
   if (part == nullptr || part_src == nullptr || flags == nullptr || flags_local == nullptr || ctr == nullptr) return -7;
   if (out_q != nullptr && (out_sf == nullptr || n % 128 != 0)) return -7;
+  if (n / 8 > 256 * kArMaxSegs) return -7;   // row segments of the reduce phase
   AllReduceParams ar{};
   const int np = use_mc ? 1 : world;
   for (int r = 0; r < np; ++r) {

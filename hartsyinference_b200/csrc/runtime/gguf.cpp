@@ -214,18 +214,30 @@ B200_API void* b200_gguf_open(const char* path) {
     const uint32_t nd = r.get<uint32_t>();
     if (!r.ok || nd > 8) { f->error = "corrupt tensor table"; f->tensors.clear(); return f; }
     uint64_t elems = 1;
-    for (uint32_t d = 0; d < nd; ++d) { const int64_t v = static_cast<int64_t>(r.get<uint64_t>()); t.dims.push_back(v); elems *= static_cast<uint64_t>(v); }
+    bool bad_dims = false;
+    for (uint32_t d = 0; d < nd; ++d) {
+      const int64_t v = static_cast<int64_t>(r.get<uint64_t>());
+      t.dims.push_back(v);
+      // a crafted file must not wrap the element count (and with it the bounds check below)
+      if (v <= 0 || __builtin_mul_overflow(elems, static_cast<uint64_t>(v), &elems)) bad_dims = true;
+    }
+    if (bad_dims) { f->error = "bad dimensions in " + t.name; f->tensors.clear(); return f; }
     t.type = static_cast<int>(r.get<uint32_t>());
     t.offset = r.get<uint64_t>();
     const TypeInfo* ti = find_type(t.type);
     if (!r.ok || !ti) { f->error = "unknown tensor type in " + t.name; f->tensors.clear(); return f; }
-    t.nbytes = elems / static_cast<uint64_t>(ti->block) * static_cast<uint64_t>(ti->bytes);
+    if (__builtin_mul_overflow(elems / static_cast<uint64_t>(ti->block), static_cast<uint64_t>(ti->bytes), &t.nbytes)) {
+      f->error = "tensor size overflow in " + t.name; f->tensors.clear(); return f;
+    }
     f->tensors.push_back(std::move(t));
   }
   const uint64_t pos = static_cast<uint64_t>(r.p - f->map);
   f->data_start = (pos + alignment - 1) / alignment * alignment;
+  if (f->data_start > f->size) { f->error = "tensor data starts past the end of the file"; f->tensors.clear(); return f; }
+  const uint64_t room = f->size - f->data_start;
   for (const auto& t : f->tensors)
-    if (f->data_start + t.offset + t.nbytes > f->size) { f->error = "tensor " + t.name + " out of bounds"; f->tensors.clear(); break; }
+    // written so that no sum can wrap: offset and size are each checked against what is left
+    if (t.offset > room || t.nbytes > room - t.offset) { f->error = "tensor " + t.name + " out of bounds"; f->tensors.clear(); break; }
   return f;
 }
 B200_API const char* b200_gguf_error(void* h) { auto* f = static_cast<GFile*>(h); return f->error.empty() ? nullptr : f->error.c_str(); }

@@ -19,9 +19,48 @@ from .requests import EngineOptions, ImageRequest, ImageResult, ModelSpec, StepP
 
 
 class _PipelineCache:
-    def __init__(self, options: EngineOptions, device: str):
+    """Pipelines cached per (model, placement, device). ``ranks`` (see :mod:`.distributed`) makes the
+    service SPMD: rank 0's ``generate`` is first broadcast as a command so that every rank runs the
+    same denoise loop and the collectives inside the transformer / the CFG exchange line up; the
+    placement's tensor- or sequence-parallel group goes to the transformer, its CFG pair to the
+    pipeline. Without ``ranks`` the placement's ``text_encoder_device`` / ``vae_device`` ordinals put
+    those components on other GPUs of the same process (the reference's component placement,
+    src/HartsyInference.Core/Backends/PlacementConfig.cs:23,26)."""
+    COMMAND = ""
+
+    def __init__(self, options: EngineOptions, device: str, ranks=None):
         self.options, self.device = options, device
+        self.ranks = ranks
         self._pipes: dict[str, object] = {}
+        self._progress = None
+        if ranks is not None and self.COMMAND:
+            ranks.register(self.COMMAND, self._generate_local)
+
+    def _comms(self):
+        """(inner group, CFG pair) of this rank for the engine's placement; (None, None) single process."""
+        if self.ranks is None:
+            return None, None
+        g = self.ranks.groups(self.options.placement)
+        return (g.inner if g.inner.world > 1 else None), g.cfg
+
+    def _component_device(self, ordinal: int) -> str:
+        """Device of a text encoder / VAE: the placement's ordinal when one is given (single process,
+        CUDA), else the denoiser's device."""
+        if ordinal is None or ordinal < 0 or self.ranks is not None or not self.device.startswith("cuda"):
+            return self.device
+        if ordinal >= torch.cuda.device_count():
+            raise UnsupportedModelError(f"placement names cuda:{ordinal}, {torch.cuda.device_count()} device(s) are visible")
+        log.decision("Placement", f"component on cuda:{ordinal} (denoiser on {self.device})")
+        return f"cuda:{ordinal}"
+
+    def generate(self, spec: ModelSpec, req, progress=None):
+        if self.ranks is None:
+            return self._generate_local(spec, req, progress)
+        self._progress = progress            # callbacks stay on rank 0
+        try:
+            return self.ranks.command(self.COMMAND, spec, req)
+        finally:
+            self._progress = None
 
     def key(self, spec: ModelSpec, loras: tuple = ()) -> str:
         tag = "|".join(f"{p}@{s:g}" for p, s in loras)
@@ -31,6 +70,9 @@ class _PipelineCache:
         return list(self._pipes)
 
     def release(self, key: Optional[str] = None) -> None:
+        self._release_local(key)
+
+    def _release_local(self, key: Optional[str] = None) -> None:
         if key is None:
             self._pipes.clear()
         else:
@@ -99,12 +141,17 @@ def _load_t5(d: Path, tok_dir: Path, device, fp8: bool):
 
 
 class ImagesService(_PipelineCache):
+    COMMAND = "images.generate"
+
     def _build(self, spec: ModelSpec, loras: tuple = ()):
         from ..models.dit import flux as F
         from ..models.vae.vae2d import FLUX_VAE, Vae2dDecoder, Vae2dEncoder, tiny_vae2d
         from ..pipelines.flux import FluxComponents, FluxPipeline
         name = spec.requested
         fp8 = bool(config.get("fp8_linears")) and self.device.startswith("cuda")
+        tp_comm, cfg_comm = self._comms()
+        pl = self.options.placement
+        te_dev, vae_dev = self._component_device(pl.text_encoder_device), self._component_device(pl.vae_device)
         if name.startswith("synthetic:sd3"):
             from ..models.dit import sd3 as S3
             from ..pipelines.sd3 import SD3_VAE, Sd3Components, Sd3Pipeline
@@ -118,16 +165,16 @@ class ImagesService(_PipelineCache):
             if "chroma" in name:
                 from ..models.dit import chroma as CH
                 cfg = CH.tiny_chroma() if tiny else CH.ChromaConfig()
-                tr = CH.ChromaTransformer(cfg, self.device, fp8=fp8 and not tiny)
+                tr = CH.ChromaTransformer(cfg, self.device, comm=tp_comm, fp8=fp8 and not tiny)
             else:
                 cfg = F.tiny_flux() if tiny else F.FLUX_DEV
-                tr = F.FluxTransformer(cfg, self.device, fp8=fp8 and not tiny)
-            vae = Vae2dDecoder(tiny_vae2d() if tiny else FLUX_VAE, self.device,
+                tr = F.FluxTransformer(cfg, self.device, comm=tp_comm, fp8=fp8 and not tiny)
+            vae = Vae2dDecoder(tiny_vae2d() if tiny else FLUX_VAE, vae_dev,
                                torch.bfloat16 if self.device.startswith("cuda") else torch.float32)
             if tiny:   # the tiny DiT packs 4 latent channels
                 assert cfg.in_channels == 16
-            enc = Vae2dEncoder(tiny_vae2d() if tiny else FLUX_VAE, self.device, vae.dtype)
-            return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc))
+            enc = Vae2dEncoder(tiny_vae2d() if tiny else FLUX_VAE, vae_dev, vae.dtype)
+            return FluxPipeline(FluxComponents(tr, vae, vae_encoder=enc), cfg_comm=cfg_comm)
         path = Path(spec.local_path or name)
         if not path.exists():
             raise UnsupportedModelError(f"{name}: no such checkpoint")
@@ -169,7 +216,7 @@ class ImagesService(_PipelineCache):
                                    approximator_channels=int(cc.get("approximator_num_channels", 64)),
                                    approximator_hidden=int(cc.get("approximator_hidden_dim", 5120)),
                                    approximator_layers=int(cc.get("approximator_layers", 5)))
-            tr = CH.ChromaTransformer(ccfg, self.device, fp8=fp8, get=get)
+            tr = CH.ChromaTransformer(ccfg, self.device, comm=tp_comm, fp8=fp8, get=get)
         else:
             import dataclasses
             base = F.FLUX_DEV
@@ -179,13 +226,13 @@ class ImagesService(_PipelineCache):
                 base = dataclasses.replace(base, in_channels=int(xw.shape[1]), out_channels=base.in_channels)
             if get("time_text_embed.guidance_embedder.linear_1.weight") is None:
                 base = dataclasses.replace(base, guidance_embed=False)          # schnell-class checkpoints
-            tr = F.FluxTransformer(base, self.device, fp8=fp8, get=get)
+            tr = F.FluxTransformer(base, self.device, comm=tp_comm, fp8=fp8, get=get)
         vae = enc = None
         if "vae" in spec.aux or (path / "vae").exists():
             vck = ShardedCheckpoint(spec.aux.get("vae", path / "vae"))
-            vae = Vae2dDecoder(FLUX_VAE, self.device, get=vck.get)
+            vae = Vae2dDecoder(FLUX_VAE, vae_dev, get=vck.get)
             if vck.get("encoder.conv_in.weight") is not None:
-                enc = Vae2dEncoder(FLUX_VAE, self.device, get=vck.get)
+                enc = Vae2dEncoder(FLUX_VAE, vae_dev, get=vck.get)
         cnet = None
         if "controlnet" in spec.aux:
             import json as _json
@@ -195,9 +242,9 @@ class ImagesService(_PipelineCache):
             ccfg = F.FluxConfig(num_double_blocks=int(cc.get("num_layers", 5)), num_single_blocks=int(cc.get("num_single_layers", 10)))
             cnet = FluxControlNet(ccfg, self.device, fp8=fp8, get=ShardedCheckpoint(cdir).get)
         comp = FluxComponents(tr, vae, vae_encoder=enc, controlnet=cnet)
-        comp.clip, comp.clip_tokenizer = _load_clip_text(path / "text_encoder", path / "tokenizer", self.device)
-        comp.t5, comp.t5_tokenizer = _load_t5(path / "text_encoder_2", path / "tokenizer_2", self.device, fp8)
-        return FluxPipeline(comp)
+        comp.clip, comp.clip_tokenizer = _load_clip_text(path / "text_encoder", path / "tokenizer", te_dev)
+        comp.t5, comp.t5_tokenizer = _load_t5(path / "text_encoder_2", path / "tokenizer_2", te_dev, fp8)
+        return FluxPipeline(comp, cfg_comm=cfg_comm)
 
     def pipeline(self, spec: ModelSpec, loras: tuple = ()):
         k = self.key(spec, loras)
@@ -206,14 +253,18 @@ class ImagesService(_PipelineCache):
             self._pipes[k] = self._build(spec, loras)
         return self._pipes[k]
 
-    def generate(self, spec: ModelSpec, req: ImageRequest, progress: Optional[Callable[[StepPreview], None]] = None) -> ImageResult:
+    def _generate_local(self, spec: ModelSpec, req: ImageRequest, progress: Optional[Callable[[StepPreview], None]] = None) -> ImageResult:
         loras = tuple((str(p), float(s)) for p, s in (req.loras or ()))
         if loras and spec.requested.startswith("synthetic:"):
             raise UnsupportedModelError("LoRA adapters need a checkpoint to merge into")
-        return self.pipeline(spec, loras).generate(apply_recipe_defaults(spec, req), progress)
+        if req.seed is None and self.ranks is not None:
+            raise ValueError("a multi-process engine needs ImageRequest.seed (every rank must draw the same noise)")
+        return self.pipeline(spec, loras).generate(apply_recipe_defaults(spec, req), progress or self._progress)
 
 
 class VideoService(_PipelineCache):
+    COMMAND = "video.generate"
+
     def _build(self, spec: ModelSpec):
         from ..models.dit import wan as W
         from ..models.vae.vae3d import WAN_VAE, Vae3dDecoder
@@ -221,27 +272,30 @@ class VideoService(_PipelineCache):
         name = spec.requested
         fp8 = bool(config.get("fp8_linears")) and self.device.startswith("cuda")
         dt = torch.bfloat16 if self.device.startswith("cuda") else torch.float32
+        sp_comm, cfg_comm = self._comms()
+        pl = self.options.placement
+        te_dev, vae_dev = self._component_device(pl.text_encoder_device), self._component_device(pl.vae_device)
         if name.startswith("synthetic:"):
             tiny = name.endswith("-tiny")
             cfg = W.tiny_wan() if tiny else (W.WAN_1_3B if "1.3b" in name else W.WAN_14B)
-            tr = W.WanTransformer(cfg, self.device, fp8=fp8 and not tiny)
-            vae = Vae3dDecoder(Vae3dDecoderCfg(tiny, cfg), self.device, dt)
-            return WanPipeline(WanComponents(tr, vae))
+            tr = W.WanTransformer(cfg, self.device, sp_comm=sp_comm, fp8=fp8 and not tiny)
+            vae = Vae3dDecoder(Vae3dDecoderCfg(tiny, cfg), vae_dev, dt)
+            return WanPipeline(WanComponents(tr, vae), cfg_comm=cfg_comm)
         path = Path(spec.local_path or name)
         if not path.exists():
             raise UnsupportedModelError(f"{name}: no such checkpoint")
         # a diffusers-layout directory keeps the transformer, VAE, umT5 encoder and tokenizer in sub-folders
         ck = ShardedCheckpoint(path / "transformer" if (path / "transformer").exists() else path)
-        tr = W.WanTransformer(W.WAN_14B, self.device, fp8=fp8, get=ck.get)
+        tr = W.WanTransformer(W.WAN_14B, self.device, sp_comm=sp_comm, fp8=fp8, get=ck.get)
         vae = None
         vae_dir = spec.aux.get("vae") or (str(path / "vae") if (path / "vae").exists() else None)
         if vae_dir:
-            vae = Vae3dDecoder(WAN_VAE, self.device, dt, get=ShardedCheckpoint(vae_dir).get)
+            vae = Vae3dDecoder(WAN_VAE, vae_dev, dt, get=ShardedCheckpoint(vae_dir).get)
         comp = WanComponents(tr, vae)
         te_dir = Path(spec.aux["text_encoder"]) if "text_encoder" in spec.aux else path / "text_encoder"
         tok_dir = te_dir if (te_dir / "tokenizer.json").exists() else path / "tokenizer"
-        comp.text_encoder, comp.tokenizer = _load_t5(te_dir, tok_dir, self.device, fp8)
-        return WanPipeline(comp)
+        comp.text_encoder, comp.tokenizer = _load_t5(te_dir, tok_dir, te_dev, fp8)
+        return WanPipeline(comp, cfg_comm=cfg_comm)
 
     def pipeline(self, spec: ModelSpec):
         k = self.key(spec)
@@ -250,8 +304,10 @@ class VideoService(_PipelineCache):
             self._pipes[k] = self._build(spec)
         return self._pipes[k]
 
-    def generate(self, spec: ModelSpec, req: VideoRequest, progress: Optional[Callable[[StepPreview], None]] = None) -> VideoGenerationResult:
-        return self.pipeline(spec).generate(apply_recipe_defaults(spec, req), progress)
+    def _generate_local(self, spec: ModelSpec, req: VideoRequest, progress: Optional[Callable[[StepPreview], None]] = None) -> VideoGenerationResult:
+        if req.seed is None and self.ranks is not None:
+            raise ValueError("a multi-process engine needs VideoRequest.seed (every rank must draw the same noise)")
+        return self.pipeline(spec).generate(apply_recipe_defaults(spec, req), progress or self._progress)
 
 
 def Vae3dDecoderCfg(tiny: bool, wan_cfg):

@@ -6,6 +6,11 @@ Mirrors the reference's ``IInferenceEngine`` (src/HartsyInference.Engine/Service
 ``UnsupportedModelError``), ``set_backend``, ``free_memory``, ``is_supported``,
 ``loaded_pipeline_keys``, and the load / generate wrappers that free cached device memory and retry
 once after an out-of-memory error (GenerateWithVramCleanup:224, ConstructWithVramCleanup:270).
+Multi-GPU: under ``torch.distributed.run`` every process builds the same engine; rank 0 is the
+front, the others call :meth:`InferenceEngine.follow` (the CLI and the server do this), and
+``EngineOptions.placement`` decides the process groups (see :mod:`.distributed`; the reference's
+EnsureBackend / EnsureCfgParallelBackend / EnsureDitShardBackends / EnsureCpBackends,
+InferenceEngine.cs:198-208).
 Backend selectors: ``auto | cpu | cuda | cuda:N | cuda:0+cuda:1`` (device lists select multi-GPU
 placement); ``vulkan`` is rejected with ``UnsupportedBackendError``
 (src/HartsyInference.Engine/BackendFactory.cs).
@@ -54,12 +59,38 @@ def parse_backend_selector(selector: str) -> tuple[str, list[int]]:
 class InferenceEngine:
     SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH, Modality.RESTORE, Modality.MUSIC}
 
-    def __init__(self, backend_selector: str = "auto", options: Optional[EngineOptions] = None):
+    def __init__(self, backend_selector: str = "auto", options: Optional[EngineOptions] = None, ranks="auto"):
         self.options = options or EngineOptions()
         self.gate = DeviceGate()
         self._services: dict[str, object] = {}
-        self._lock = threading.Lock()
+        self._lock = threading.RLock()
+        if ranks == "auto":
+            from .distributed import RankContext
+            ranks = RankContext.from_env()
+        self.ranks = ranks
         self.set_backend(backend_selector)
+        if self.ranks is not None:
+            # every rank owns the services that take part in collective work, so that rank 0's
+            # commands find their handlers; followers then wait in follow()
+            self.ranks.register("ready", lambda: self.ranks.ready_report(not self.unhealthy()))
+            self.ranks.register("release", self._release_local)
+            _ = self.text, self.images, self.video
+
+    def follow(self) -> None:
+        """Ranks other than 0 of a multi-process engine: execute rank 0's commands until it closes."""
+        if self.ranks is not None:
+            self.ranks.follow()
+
+    @property
+    def is_front(self) -> bool:
+        return self.ranks is None or self.ranks.is_front
+
+    def ready(self) -> dict:
+        """Health of every rank (``{"ranks": N, "healthy": [...]}``), collected through the command stream."""
+        if self.ranks is None:
+            return {"ranks": 1, "healthy": [not self.unhealthy()]}
+        flags = self.ranks.command("ready")
+        return {"ranks": self.ranks.size, "healthy": flags}
 
     # ------------------------------------------------------------------------------ backend
     def set_backend(self, selector: str) -> None:
@@ -75,6 +106,12 @@ class InferenceEngine:
         self.backend_selector = selector
         self.kind, self.ordinals = kind, ordinals
         self.device = f"cuda:{ordinals[0]}" if kind == "cuda" else "cpu"
+        if self.ranks is not None and kind == "cuda":
+            # one process per GPU: this process drives the device torchrun gave it
+            import os
+            local = int(os.environ.get("LOCAL_RANK", "0"))
+            self.ordinals = [local]
+            self.device = f"cuda:{local}"
         log.decision("Placement", f"backend={self.backend_description}")
 
     @property
@@ -97,7 +134,7 @@ class InferenceEngine:
     @property
     def text(self):
         from .text_service import TextService
-        return self._service("text", lambda: TextService(self.options, self.device))
+        return self._service("text", lambda: TextService(self.options, self.device, ranks=self.ranks))
 
     @property
     def embeddings(self):
@@ -108,12 +145,12 @@ class InferenceEngine:
     @property
     def images(self):
         from .diffusion_service import ImagesService
-        return self._service("images", lambda: ImagesService(self.options, self.device))
+        return self._service("images", lambda: ImagesService(self.options, self.device, ranks=self.ranks))
 
     @property
     def video(self):
         from .diffusion_service import VideoService
-        return self._service("video", lambda: VideoService(self.options, self.device))
+        return self._service("video", lambda: VideoService(self.options, self.device, ranks=self.ranks))
 
     @property
     def transcribe(self):
@@ -157,8 +194,14 @@ class InferenceEngine:
         return keys
 
     def release_loaded(self) -> None:
+        if getattr(self, "ranks", None) is not None and self.ranks.is_front and self._services:
+            self.ranks.command("release")
+        else:
+            self._release_local()
+
+    def _release_local(self) -> None:
         for s in list(self._services.values()):
-            rel = getattr(s, "release", None)
+            rel = getattr(s, "_release_local", None) or getattr(s, "release", None)
             if rel:
                 rel()
 
@@ -192,6 +235,8 @@ class InferenceEngine:
     def close(self) -> None:
         self.release_loaded()
         self._services.clear()
+        if self.ranks is not None:
+            self.ranks.shutdown()
 
 
 class _EmbeddingsRouter:

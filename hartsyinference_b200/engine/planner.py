@@ -117,8 +117,12 @@ def suggest(shape: ModelShape, gpus: int, latency_bound: bool = True) -> Paralle
             tp = largest_divisor(shape.num_heads or rest, rest)
             plan = ParallelConfig(tp=tp, cfg=cfg, dp=max(1, rest // tp))
     elif shape.kind == "moe_llm":
-        ep = largest_divisor(shape.num_experts or gpus, gpus)
-        plan = ParallelConfig(ep=ep, dp=ep)          # data-parallel attention + expert-parallel FFN
+        # experts are sharded over the tensor-parallel group (activations replicated, one all-reduce
+        # for routed + shared outputs), so ep rides on tp
+        g = largest_divisor(shape.num_experts or gpus, gpus)
+        if shape.num_heads:
+            g = largest_divisor(shape.num_heads, g)
+        plan = ParallelConfig(tp=g, ep=g, dp=max(1, gpus // g))
     else:
         fits_one = shape.weight_bytes * FIT_OVERHEAD <= GPU_BYTES
         tp = largest_divisor(shape.num_heads or gpus, gpus)
@@ -132,3 +136,36 @@ def suggest(shape: ModelShape, gpus: int, latency_bound: bool = True) -> Paralle
         plan = ParallelConfig()
     log.decision("ParallelPlan", f"{shape.kind} {shape.weight_bytes / 1e9:.1f} GB on {gpus} GPU(s) -> {plan.describe()}")
     return plan
+
+
+def shape_of_checkpoint(path) -> Optional[ModelShape]:
+    """Model shape for :func:`suggest` from a Hugging Face-style directory (``config.json`` + weight
+    files) or a single weight file; None when nothing can be read."""
+    import json
+    from pathlib import Path
+    p = Path(path)
+    if not p.exists():
+        return None
+    files = [p] if p.is_file() else [f for f in p.rglob("*") if f.suffix in (".safetensors", ".gguf", ".bin", ".pt")]
+    nbytes = sum(f.stat().st_size for f in files)
+    cfg = {}
+    for cand in ((p / "config.json"), (p / "transformer" / "config.json")) if p.is_dir() else ():
+        if cand.exists():
+            try:
+                cfg = json.loads(cand.read_text())
+                break
+            except Exception:
+                pass
+    heads = int(cfg.get("num_attention_heads") or cfg.get("n_head") or 0)
+    experts = int(cfg.get("n_routed_experts") or cfg.get("num_local_experts") or cfg.get("num_experts") or 0)
+    cls = str(cfg.get("_class_name", "")).lower()
+    if "transformer3d" in cls or "wan" in cls:
+        kind = "video_dit"
+    elif "transformer2d" in cls or "flux" in cls or "sd3" in cls:
+        kind = "image_dit"
+    else:
+        kind = "moe_llm" if experts else "llm"
+    return ModelShape(kind=kind, weight_bytes=nbytes, num_heads=heads,
+                      num_kv_heads=int(cfg.get("num_key_value_heads") or heads),
+                      ffn_size=int(cfg.get("intermediate_size") or 0), hidden_size=int(cfg.get("hidden_size") or 0),
+                      num_experts=experts)

@@ -41,35 +41,162 @@ class _Hosted:
     thread: Optional[threading.Thread] = None
     running: bool = True
     healthy: bool = True
+    key: str = ""
+    # SPMD: requests of every replica as seen by rank 0: (replica, request id) -> token callback
+    remote_callbacks: Optional[dict] = None
+    next_replica: int = 0
 
 
 class TextService:
-    def __init__(self, options: EngineOptions, device: str = "cuda", comm: Optional[Comm] = None):
+    """``ranks`` (an :class:`~hartsyinference_b200.engine.distributed.RankContext`) switches the
+    service to SPMD operation: the model is sharded over the placement's tensor-parallel group,
+    rank 0 owns the serving loop and broadcasts every scheduler tick (new requests, cancellations,
+    "run one step") so that all ranks of a replica step the same batch together; with more replicas
+    than one (``dp``), requests are dealt round-robin and each tick gathers the replicas' new tokens
+    on rank 0."""
+
+    def __init__(self, options: EngineOptions, device: str = "cuda", comm: Optional[Comm] = None, ranks=None):
         self.options = options
         self.device = device
         self.comm = comm
+        self.ranks = ranks
+        self.groups = None
         self._models: dict[str, _Hosted] = {}
         self._ssm: dict[str, tuple] = {}
-        self._lock = threading.Lock()
+        self._lock = threading.RLock()
+        self._tickets: dict[int, object] = {}
+        self._next_ticket = 1
+        if ranks is not None:
+            ranks.register("text.load", self._host_local)
+            ranks.register("text.tick", self._tick)
+            ranks.register("text.release", self._release_local)
 
     # ------------------------------------------------------------------------------ loading
+    def _key(self, spec: ModelSpec) -> str:
+        return f"{spec.local_path or spec.requested}|{self.options.placement.cache_key}|{self.device}"
+
     def _host(self, spec: ModelSpec) -> _Hosted:
+        key = self._key(spec)
+        h = self._models.get(key)
+        if h is not None:
+            return h
+        if self.ranks is not None:
+            return self.ranks.command("text.load", spec)      # every rank loads its shard
+        return self._host_local(spec)
+
+    def _host_local(self, spec: ModelSpec) -> _Hosted:
         path = spec.local_path or spec.requested
-        key = f"{path}|{self.options.placement.cache_key}|{self.device}"
+        key = self._key(spec)
         with self._lock:
             h = self._models.get(key)
             if h is not None:
                 return h
-            llm = load_llm(path, self.device, self.comm)
+            comm = self.comm
+            if self.ranks is not None:
+                self.groups = self.ranks.groups(self.options.placement)
+                comm = self.groups.inner
+            llm = load_llm(path, self.device, comm)
+            if comm is not None and comm.world > 1 and llm.model.device.type == "cuda":
+                # row-parallel linears through the fused GEMM + all-reduce kernels where they measure faster
+                from ..parallel.fused import enable_fused_tp
+                try:
+                    enable_fused_tp(llm.model, comm, autotune_tokens=min(self.options.max_batch, 64))
+                except Exception as e:
+                    log.warn(f"[Collective] fused TP kernels unavailable ({type(e).__name__}: {e}); using NCCL")
             eng = LLMEngine(llm.model, page_size=self.options.kv_page_size, max_batch=self.options.max_batch,
                             max_model_len=min(self.options.max_model_len, llm.config.max_position),
                             kv_pool_bytes=self.options.kv_pool_bytes_budget or None)
-            lk = threading.Lock()
-            h = _Hosted(llm, eng, lk, threading.Condition(lk))
-            h.thread = threading.Thread(target=self._loop, args=(h,), daemon=True, name=f"llm-loop-{len(self._models)}")
-            h.thread.start()
+            eng.on_device_fault = lambda vals, m=llm.model, c=comm: self._on_device_fault(m, c, vals)
+            lk = threading.RLock()
+            h = _Hosted(llm, eng, lk, threading.Condition(lk), key=key, remote_callbacks={})
+            if self.ranks is None or self.ranks.is_front:
+                h.thread = threading.Thread(target=self._loop, args=(h,), daemon=True, name=f"llm-loop-{len(self._models)}")
+                h.thread.start()
             self._models[key] = h
             return h
+
+    @staticmethod
+    def _on_device_fault(model, comm, vals) -> None:
+        """A kernel's bounded wait on a peer ran out: leave the peer-memory kernels for NCCL."""
+        if comm is not None and comm.world > 1:
+            from ..parallel.fused import disable_fused_tp
+            log.warn(f"[Collective] device wait timeout {vals}; row-parallel linears fall back to NCCL")
+            disable_fused_tp(model, comm)
+
+    # ------------------------------------------------------------------------------ SPMD ticks
+    def _tick(self, key: str, adds: list, cancels: list, step: bool):
+        """One scheduler tick, run by every rank with the same arguments. ``adds``: (ticket,
+        replica, prompt ids, request, seed, extras); ``cancels``: (replica, request id). Returns, on
+        rank 0, ``({ticket: request id}, [(replica, request id, token, finished)])`` for all replicas."""
+        h = self._models[key]
+        g = self.groups
+        mine = g.dp_index if g is not None else 0
+        new_ids: dict[int, int] = {}
+        for ticket, replica, ids, req, seed, extras in adds:
+            if replica != mine:
+                continue
+            params = self._params(req, h.llm)
+            if params.seed is None and not params.is_greedy:
+                params.seed = seed               # every rank of the replica must draw the same tokens
+            cb = self._tickets.pop(ticket, None) if (self.ranks is None or self.ranks.is_front) else None
+            new_ids[ticket] = h.engine.add_request(ids, params, on_token=cb, **(extras or {}))
+        for replica, rid in cancels:
+            if replica == mine:
+                h.engine.cancel(rid)
+        events = h.engine.step() if step and h.engine.has_work() else []
+        if self.ranks is not None and not self.ranks.is_front:
+            for r, _, fin in events:             # nobody collects results on a follower
+                if fin:
+                    h.engine.release(r)
+        if g is None or g.dp <= 1:
+            return new_ids, [(mine, r, t, f) for r, t, f in events]
+        # replicas other than rank 0's: their leaders report, rank 0 delivers to the callers
+        lead = g.inner_rank == 0 and g.cfg_index == 0
+        got = self.ranks.gather((mine, new_ids, events) if lead else None)
+        if got is None:
+            return new_ids, []
+        all_ids: dict[int, int] = {}
+        all_events = []
+        for item in got:
+            if item is None:
+                continue
+            rep, ids_r, ev_r = item
+            all_ids.update(ids_r)
+            all_events += [(rep, r, t, f) for r, t, f in ev_r]
+            if rep != 0:
+                for r, t, f in ev_r:
+                    cb = h.remote_callbacks.get((rep, r))
+                    if cb is not None:
+                        cb(r, t, f)
+        for ticket, rid in all_ids.items():
+            cb = self._tickets.pop(ticket, None)     # tickets of other replicas: remember the caller
+            rep = next((a[1] for a in adds if a[0] == ticket), 0)
+            if cb is not None and rep != 0:
+                h.remote_callbacks[(rep, rid)] = cb
+        return all_ids, all_events
+
+    def _submit(self, h: _Hosted, ids: list, req: TextRequest, on_token, extras: dict) -> tuple[int, int]:
+        """Queue one request on the engine(s); returns (replica, request id)."""
+        if self.ranks is None:
+            rid = h.engine.add_request(ids, self._params(req, h.llm), on_token=on_token, **extras)
+            return 0, rid
+        import random
+        with self._lock:
+            ticket = self._next_ticket
+            self._next_ticket += 1
+            self._tickets[ticket] = on_token
+        dp = self.groups.dp if self.groups is not None else 1
+        replica = h.next_replica % dp
+        h.next_replica += 1
+        new_ids, _ = self.ranks.command("text.tick", h.key, [(ticket, replica, ids, req, random.getrandbits(31), extras)],
+                                        [], False)
+        return replica, new_ids[ticket]
+
+    def _cancel(self, h: _Hosted, replica: int, rid: int) -> None:
+        if self.ranks is None:
+            h.engine.cancel(rid)
+        else:
+            self.ranks.command("text.tick", h.key, [], [(replica, rid)], False)
 
     def loaded_keys(self) -> list[str]:
         return list(self._models) + list(self._ssm)
@@ -78,6 +205,12 @@ class TextService:
         return [k for k, h in self._models.items() if not h.healthy or not (h.thread and h.thread.is_alive())]
 
     def release(self, key: Optional[str] = None) -> None:
+        if self.ranks is not None and self.ranks.is_front and self._models:
+            self.ranks.command("text.release", key)
+        else:
+            self._release_local(key)
+
+    def _release_local(self, key: Optional[str] = None) -> None:
         with self._lock:
             if key is None:
                 self._ssm.clear()
@@ -101,12 +234,15 @@ class TextService:
             torch.cuda.set_device(h.engine.device)
         while True:
             with h.wake:
-                while h.running and not h.engine.has_work():
+                while h.running and not (h.engine.has_work() or h.remote_callbacks):
                     h.wake.wait(timeout=0.5)
                 if not h.running:
                     return
                 try:
-                    h.engine.step()
+                    if self.ranks is not None:
+                        self.ranks.command("text.tick", h.key, [], [], True)
+                    else:
+                        h.engine.step()
                     st = h.engine.stats()
                     REGISTRY.set("hartsyinference_kv_pages_used", st["pages_used"])
                     REGISTRY.set("hartsyinference_batch_size", st["running"])
@@ -304,9 +440,9 @@ class TextService:
             self._mrope = (None, 0, None)
             ids, embeds, emask = self._multimodal(llm, req, ids)
             pos3, delta, deepstack = self._mrope
-            rid = h.engine.add_request(ids, self._params(req, llm), on_token=lambda r, tok, fin: q.put((tok, fin)),
-                                       prompt_embeds=embeds, embeds_mask=emask, cross_states=self._cross_states(llm, req),
-                                       positions3=pos3, rope_delta=delta, deepstack=deepstack)
+            replica, rid = self._submit(h, ids, req, lambda r, tok, fin: q.put((tok, fin)),
+                                        dict(prompt_embeds=embeds, embeds_mask=emask, cross_states=self._cross_states(llm, req),
+                                             positions3=pos3, rope_delta=delta, deepstack=deepstack))
             h.wake.notify_all()
         dec = llm.tokenizer.stream_decoder()
         text = ""
@@ -316,7 +452,7 @@ class TextService:
         while True:
             if cancel is not None and cancel.is_set():
                 with h.wake:
-                    h.engine.cancel(rid)
+                    self._cancel(h, replica, rid)
                 break
             try:
                 tok, fin = q.get(timeout=0.1)
@@ -336,7 +472,7 @@ class TextService:
                         text = text[:cut]
                         stop_hit = True
                         with h.wake:
-                            h.engine.cancel(rid)
+                            self._cancel(h, replica, rid)
                         break
                     yield TextChunk(ChunkKind.CHUNK, text=piece)
             if fin:
@@ -346,7 +482,9 @@ class TextService:
             text += tail
             yield TextChunk(ChunkKind.CHUNK, text=tail)
         with h.wake:
-            r = h.engine.release(rid)
+            r = h.engine.release(rid) if replica == (self.groups.dp_index if self.groups is not None else 0) else None
+            if h.remote_callbacks is not None:
+                h.remote_callbacks.pop((replica, rid), None)
         reason = StopReason.STOP if stop_hit else _REASON.get((r.finish_reason if r else None) or "stop", StopReason.STOP)
         calls = []
         if req.tools or req.force_tool_id:

@@ -21,6 +21,7 @@ from .core import (  # noqa: F401
     dit_qkv,
     embedding,
     fill_random_,
+    fp8_mx,
     gated_residual,
     glu,
     gguf_linear,

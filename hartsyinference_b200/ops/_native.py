@@ -35,6 +35,8 @@ _SIGNATURES = {
     "b200_mla_pick_splits": (i32, [i32, i32, i32]),
     "b200_mla_workspace_bytes": (i64, [i32, i32, i32]),
     "b200_mla_attn": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, f32, vp]),
+    "b200_attn_fa_workspace_bytes": (i64, [i32, i32, i32, i32, i32]),
+    "b200_attn_fa": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, vp, vp, vp]),
     "b200_attn_tc_workspace_bytes": (i64, [i32, i32, i32]),
     "b200_attn_tc": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, f32, vp, vp, vp]),
     "b200_selective_scan": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),

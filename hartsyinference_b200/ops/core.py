@@ -433,8 +433,10 @@ def attn_prefill_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
-              scale: Optional[float] = None, softcap: float = 0.0, window: int = 0) -> torch.Tensor:
-    """Dense attention for one sequence: q [Tq, hq, d], k/v [Tk, hkv, d] -> [Tq, hq, d]."""
+              scale: Optional[float] = None, softcap: float = 0.0, window: int = 0,
+              int8: Optional[bool] = None) -> torch.Tensor:
+    """Dense attention for one sequence: q [Tq, hq, d], k/v [Tk, hkv, d] -> [Tq, hq, d].
+    ``int8`` (default: flag ``sage_attention``) selects the int8 Q K^T mode of the tcgen05 kernel."""
     tq, hq, d = q.shape
     tk, hkv, _ = k.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
@@ -442,7 +444,18 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
         return R.attention(q, k, v, causal, scale, softcap, window).to(q.dtype)
     assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
     out = torch.empty_like(q)
-    if d == 128 and hq == hkv and not causal and softcap == 0.0 and window <= 0 and tk >= 256 and _tc_attention():
+    dense_tc = d == 128 and hq == hkv and not causal and softcap == 0.0 and window <= 0 and tk >= 256 and _tc_attention()
+    from .. import config
+    if dense_tc and config.get("fa_attention"):
+        # long bidirectional sequences (DiT blocks): two query tiles per CTA, S / P / O in TMEM
+        L = N.lib()
+        i8 = int(config.get("sage_attention") if int8 is None else int8)
+        ws = N.state(q.device).scratch(L.b200_attn_fa_workspace_bytes(1, hq, tq, tk, i8))
+        rc = L.b200_attn_fa(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 1, tq, tk, hq, float(scale), i8,
+                            ws.data_ptr(), N.state(q.device).status.data_ptr(), N.stream())
+        N.check(rc, "b200_attn_fa", 5 if i8 else 2)
+        return out
+    if dense_tc:
         # long bidirectional sequences (DiT blocks): tcgen05 kernel, V consumed transposed
         L = N.lib()
         vt = torch.empty(L.b200_attn_tc_workspace_bytes(1, hq, tk), dtype=torch.uint8, device=q.device)

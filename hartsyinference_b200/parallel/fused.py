@@ -54,14 +54,16 @@ class FusedRowParallel:
         q_bytes = MAX_TOKENS * f
         sf_bytes = max(MAX_TOKENS * ((f + 127) // 128) * 4, ((f + 511) // 512) * 512)
         per_slot = bf16_bytes + q_bytes + sf_bytes + 3 * 256
-        self.heap = SymmetricHeap(heap_comm, part_bytes + num_out_buffers * per_slot + 4096, self.device)
+        self.heap = SymmetricHeap(heap_comm, part_bytes + num_out_buffers * per_slot + 16384, self.device)
         self.use_mc = self.heap.has_multicast
         self.off_part = self.heap.alloc(part_bytes)
         self.off_bf16 = [self.heap.alloc(bf16_bytes) for _ in range(num_out_buffers)]
         self.off_q = [self.heap.alloc(q_bytes) for _ in range(num_out_buffers)]
         self.off_sf = [self.heap.alloc(sf_bytes) for _ in range(num_out_buffers)]
         self.off_flags = self.heap.alloc(256)
-        self.off_ctr = self.heap.alloc(256)
+        ctr_bytes = int(N.bind("b200_gemm_allreduce_ctr_bytes", C.c_longlong, [])())
+        self.off_ctr = self.heap.alloc(ctr_bytes)
+        self._ctr_words = ctr_bytes // 4
         arr = self.heap.mc_array if self.use_mc else self.heap.ptr_array
         own = 0 if emulate_peers else self.rank
         if emulate_peers:
@@ -92,7 +94,7 @@ class FusedRowParallel:
         torch.cuda.synchronize(self.device)
         self.comm.barrier()
         self.heap.tensor(self.off_flags, (64,), torch.int32).zero_()
-        self.heap.tensor(self.off_ctr, (64,), torch.int32).zero_()
+        self.heap.tensor(self.off_ctr, (self._ctr_words,), torch.int32).zero_()
         torch.cuda.synchronize(self.device)
         self.comm.barrier()
 

@@ -45,6 +45,7 @@ class ServerOptions:
     api_keys: list[str] = field(default_factory=list)       # empty = auth off
     rate_limit_per_minute: int = 0                          # 0 = unlimited
     models: dict[str, str] = field(default_factory=dict)    # public name -> path / synthetic spec
+    allow_model_paths: bool = False                         # let callers name arbitrary local paths as models
     default_text_model: Optional[str] = None
     default_image_model: Optional[str] = None
     default_video_model: Optional[str] = None
@@ -170,26 +171,56 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
             raise UnsupportedModelError("no model named in the request and no default configured")
         path = opts.models.get(name, name)
         if name not in opts.models and not path.startswith("synthetic:"):
-            # not a configured name: a path, a catalog id / alias or a repository id that is on disk
+            # not a configured name: a catalog id / alias or a repository id that is on disk. A bare
+            # filesystem path is honoured only below the model cache directory, or anywhere when the
+            # operator opted in (an API caller must not be able to make the server open arbitrary files)
             import os
-            if not os.path.exists(os.path.expanduser(path)):
+            real = os.path.realpath(os.path.expanduser(path))
+            if os.path.exists(real):
+                cache_root = os.path.realpath(os.path.expanduser(eng.options.model_cache_directory))
+                inside = real == cache_root or real.startswith(cache_root + os.sep)
+                if not (opts.allow_model_paths or inside):
+                    raise UnsupportedModelError(f"'{name}' is not a configured model name or catalog id")
+                path = real
+            else:
                 spec = resolver.resolve(path, modality)
                 return ModelSpec(requested=spec.local_path or path, modality=modality, catalog=spec.catalog,
                                  local_path=spec.local_path, aux=spec.aux)
         return ModelSpec(requested=path, modality=modality, catalog=name if name in opts.models else None, local_path=path)
 
+    import hmac
+
+    def key_ok(key: str) -> bool:
+        # constant-time comparison against every configured key (no early exit on the first match)
+        ok = False
+        for k in opts.api_keys:
+            ok |= hmac.compare_digest(key.encode(), k.encode())
+        return ok
+
+    def route_label(request: Request) -> str:
+        """The matched route template (bounded label cardinality), not the raw path."""
+        for r in app.router.routes:
+            try:
+                match, _ = r.matches(request.scope)
+            except Exception:
+                continue
+            if match.value == 2:            # starlette.routing.Match.FULL
+                return getattr(r, "path", "other")
+        return "unmatched"
+
     @app.middleware("http")
     async def auth_and_metrics(request: Request, call_next):
-        route = request.url.path
+        path_ = request.url.path
+        route = route_label(request)
         key = request.headers.get("x-api-key") or ""
         auth = request.headers.get("authorization", "")
         if not key and auth.lower().startswith("bearer "):
             key = auth[7:].strip()
         open_routes = ("/health", "/ready", "/version", "/metrics", "/openapi.json", "/docs")
-        if opts.api_keys and route not in open_routes and key not in opts.api_keys:
+        if opts.api_keys and path_ not in open_routes and not key_ok(key):
             REGISTRY.inc("hartsyinference_requests_total", route=route, outcome="unauthorized")
             return JSONResponse({"error": {"message": "invalid or missing API key", "type": "unauthorized"}}, status_code=401)
-        if route not in open_routes and not limiter.allow(key or request.client.host if request.client else "anon"):
+        if path_ not in open_routes and not limiter.allow(key or request.client.host if request.client else "anon"):
             REGISTRY.inc("hartsyinference_requests_total", route=route, outcome="rate_limited")
             return JSONResponse({"error": {"message": "rate limit exceeded", "type": "rate_limited"}}, status_code=429)
         request.state.api_key = key or "anonymous"
@@ -224,9 +255,10 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
     @app.get("/ready")
     def ready():
         bad = eng.unhealthy()
-        if bad:
-            return JSONResponse({"status": "unhealthy", "models": bad}, status_code=503)
-        return {"status": "ready", "backend": eng.backend_description, "loaded": eng.loaded_pipeline_keys}
+        ranks = eng.ready()          # every rank of a multi-process engine answers through the command stream
+        if bad or not all(ranks["healthy"]):
+            return JSONResponse({"status": "unhealthy", "models": bad, "ranks": ranks}, status_code=503)
+        return {"status": "ready", "backend": eng.backend_description, "loaded": eng.loaded_pipeline_keys, "ranks": ranks}
 
     @app.get("/version")
     def version():

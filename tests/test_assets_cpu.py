@@ -165,3 +165,41 @@ def test_gguf_mxfp4_blocks(tmp_path):
     G.write_gguf(tmp_path / "m.gguf", {"general.architecture": "llama"}, {"w": w}, quant={"w": G.MXFP4})
     f = G.GgufFile(tmp_path / "m.gguf")
     assert f.info("w")[0] == G.MXFP4 and torch.equal(f.get("w"), back)
+
+
+def test_gguf_rejects_crafted_tensor_tables(tmp_path):
+    """Offsets, dimensions and sizes that would wrap 64-bit arithmetic (and with it a naive bounds
+    check), a negative dimension and data that starts past the end of the file are all refused at
+    open instead of yielding a pointer outside the mapping."""
+    import struct
+    import pytest
+    from hartsyinference_b200.assets import gguf as G
+    from hartsyinference_b200.exceptions import HartsyInferenceError
+
+    def s(text):
+        b = text.encode()
+        return struct.pack("<Q", len(b)) + b
+
+    def build(dims, offset, ggml_type=0, pad=64):
+        out = b"GGUF" + struct.pack("<IQQ", 3, 1, 0)            # version, tensors, metadata entries
+        out += s("w") + struct.pack("<I", len(dims)) + b"".join(struct.pack("<q", d) for d in dims)
+        out += struct.pack("<IQ", ggml_type, offset)
+        out += b"\0" * ((-len(out)) % 32) + b"\0" * pad
+        return out
+
+    ok = tmp_path / "ok.gguf"
+    ok.write_bytes(build([4, 4], 0))
+    assert G.GgufFile(ok).get("w").shape == (4, 4)
+    cases = {
+        "wrapped_offset": build([4, 4], (1 << 64) - 32),
+        "huge_offset": build([4, 4], 1 << 40),
+        "negative_dim": build([-4, 4], 0),
+        "zero_dim": build([0, 4], 0),
+        "wrapping_dims": build([1 << 33, 1 << 33], 0),
+        "too_big": build([1 << 20, 1 << 20], 0),
+    }
+    for name, blob in cases.items():
+        p = tmp_path / f"{name}.gguf"
+        p.write_bytes(blob)
+        with pytest.raises(HartsyInferenceError):
+            G.GgufFile(p)
