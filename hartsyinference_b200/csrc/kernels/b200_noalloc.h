@@ -25,8 +25,16 @@ extern "C" {
 #define B200_NOALLOC_SCRATCH_BYTES (10 * 1024 * 1024)
 
 /* out[m][n] (bf16, leading dimension ldc) = x[m][k] * w[n][k]^T (+ bias[n]) (+ residual[m][n])
- *   dtype 0: x, w are bf16.  dtype 1: x, w are e4m3 bytes with fp32 scales x_scale [m][k/128] and
- *   w_scale [ceil(n/128)][k/128]; k must then be a multiple of 128.
+ *   dtype 0: x, w are bf16.
+ *   dtype 1: x, w are e4m3 bytes with fp32 scales x_scale [m][k/128] and w_scale [ceil(n/128)][k/128];
+ *            k must then be a multiple of 128.
+ *   dtype 2: x, w are e4m3 bytes with power-of-two (UE8M0) scales applied by the tensor core. The two
+ *            scale arguments then point (through the same `const float*` parameters) at blocked
+ *            scale-factor arrays of 32-bit words: [row tiles of 128][ceil(k/512)][128 words]; row r of
+ *            a tile sits at word (r % 32) * 4 + r / 32, and byte (kb % 4) of the word is the biased
+ *            exponent of 128-wide K block kb. Weight rows of one 128-row block share their scale, so
+ *            its tile repeats one byte per K block. k must be a multiple of 16; bytes of K blocks
+ *            past the end of k must hold a finite exponent (127).
  * Same arithmetic and the same kernel as b200_gemm; only the scratch memory differs.
  *
  * The caller passes inputs and outputs (device pointers, 16-byte aligned rows); nothing is
@@ -42,6 +50,12 @@ extern "C" {
  *     `stream` at the start of every call. Two calls that can overlap on the GPU (different
  *     streams without an ordering between them) race on the array and give wrong results:
  *     serialise them.
+ *   - Fully split small GEMMs are reduced by a second kernel launched by the same call (the
+ *     library default; b200_gemm_set_cluster_reduce / b200_gemm_set_external_reduce change it
+ *     for every entry point of the process, this one included).
+ *   - The kernel's internal waits are bounded, but this entry point takes no status word: a wait
+ *     that ran out cannot be reported here. Callers that need that report use b200_gemm, which
+ *     accepts a 16-byte status record.
  * Returns 0 on success, a negative code otherwise (argument / launch errors as b200_gemm). */
 #define B200_NOALLOC_ERR_TOO_LARGE (-8)
 #define B200_NOALLOC_ERR_SETUP (-9)

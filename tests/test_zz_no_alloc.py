@@ -60,6 +60,32 @@ def test_noalloc_gemm_matches_regular_entry_twice(fp8):
             assert _rel(out, ref) < 1e-2, (m, n, k, call, _rel(out, ref))
 
 
+def test_noalloc_gemm_with_cluster_reduction_of_the_k_splits():
+    """The library-wide switch that sums K splits through distributed shared memory of a
+    thread-block cluster applies to this entry point too; one small shape is checked with it on,
+    then the switch goes back to what the loader had set."""
+    from hartsyinference_b200 import config, ops
+    from hartsyinference_b200.ops import _native as N
+    fn = _entry()
+    L = N.lib()
+    torch.manual_seed(12)
+    m, n, k = 32, 1024, 2048
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16)
+    ref = ops.linear(x, ops.LinearWeight(w), splits=1)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    L.b200_gemm_set_cluster_reduce(1)
+    try:
+        for _ in range(2):
+            rc = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, k, k, n, 0, None, None, None, None,
+                    torch.cuda.current_stream().cuda_stream)
+            assert rc == 0, rc
+            torch.cuda.synchronize()
+            assert _rel(out, ref) < 1e-2
+    finally:
+        L.b200_gemm_set_cluster_reduce(1 if config.get("cluster_splitk") else 0)
+
+
 def test_noalloc_gemm_rejects_oversize():
     fn = _entry()
     x = torch.zeros(256, 256, device="cuda", dtype=torch.bfloat16)
