@@ -2,8 +2,8 @@
 //
 // The file is memory-mapped; metadata is handed to Python as one JSON document, tensor data as
 // pointers into the mapping. The codecs are the fp32 oracle of the device dequant-GEMM kernels and
-// the implementation of the CPU path: dequantise Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q2_K, Q4_K, Q5_K,
-// Q6_K, IQ4_NL, MXFP4, F16, BF16 to fp32 and quantise fp32 to Q8_0 / Q4_0 / Q4_K.
+// the implementation of the CPU path: dequantise Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1, Q2_K, Q3_K, Q4_K,
+// Q5_K, Q6_K, Q8_K, IQ4_NL, MXFP4, F16, BF16 to fp32 and quantise fp32 to Q8_0 / Q4_0 / Q4_K.
 //
 // Counterparts in the reference: GgufLoader (header / KV / tensor-info parser;
 // src/HartsyInference.ModelAssets/Gguf/GgufLoader.cs), the per-format codecs
@@ -358,6 +358,48 @@ B200_API int32_t b200_ggml_dequant(int32_t type, const void* src, float* y, int6
             shift += 2;
           }
           q += 32;
+        }
+      }
+      return 0;
+    case 9:    // Q8_1: scale, precomputed sum (unused when dequantising), 32 int8
+      for (int64_t b = 0; b < nb; ++b, p += 36, y += 32) {
+        const float d = f16_to_f32(rd16(p));
+        const int8_t* q = reinterpret_cast<const int8_t*>(p + 4);
+        for (int j = 0; j < 32; ++j) y[j] = q[j] * d;
+      }
+      return 0;
+    case 15:   // Q8_K: fp32 scale, 256 int8, 16 block sums (unused when dequantising)
+      for (int64_t b = 0; b < nb; ++b, p += 292, y += 256) {
+        float d; memcpy(&d, p, 4);
+        const int8_t* q = reinterpret_cast<const int8_t*>(p + 4);
+        for (int j = 0; j < 256; ++j) y[j] = q[j] * d;
+      }
+      return 0;
+    case 11:   // Q3_K: high-bit mask [32], 2-bit quants [64], sixteen 6-bit scales in 12 bytes, f16 scale
+      for (int64_t b = 0; b < nb; ++b, p += 110) {
+        const uint8_t* hm = p; const uint8_t* q = p + 32; const uint8_t* packed = p + 96;
+        const float d = f16_to_f32(rd16(p + 108));
+        // scale i: low 4 bits from bytes 0..7 (low nibble for i < 8, high nibble for i >= 8), top 2
+        // bits from bytes 8..11 (byte 8 + i % 4, bit pair i / 4); stored with a bias of 32
+        int sc[16];
+        for (int i = 0; i < 16; ++i) {
+          const int lo = i < 8 ? (packed[i] & 0xF) : (packed[i - 8] >> 4);
+          const int hi = (packed[8 + (i & 3)] >> (2 * (i >> 2))) & 3;
+          sc[i] = (lo | (hi << 4)) - 32;
+        }
+        int is = 0;
+        uint8_t bit = 1;
+        for (int half = 0; half < 2; ++half, q += 32) {
+          for (int shift = 0; shift < 8; shift += 2, bit = static_cast<uint8_t>(bit << 1)) {
+            for (int part = 0; part < 2; ++part) {
+              const float dl = d * sc[is++];
+              for (int l = 0; l < 16; ++l) {
+                const int idx = part * 16 + l;
+                const int v = ((q[idx] >> shift) & 3) - ((hm[idx] & bit) ? 0 : 4);
+                *y++ = dl * v;
+              }
+            }
+          }
         }
       }
       return 0;

@@ -203,3 +203,70 @@ def test_gguf_rejects_crafted_tensor_tables(tmp_path):
         p.write_bytes(blob)
         with pytest.raises(HartsyInferenceError):
             G.GgufFile(p)
+
+
+def test_gguf_q3k_q8_1_q8_k_decoders():
+    """Q3_K blocks against an independent statement of the format (the 6-bit scales recovered with
+    the 32-bit mask arithmetic of the format's description), Q8_1 and Q8_K against their definition."""
+    import ctypes as C
+    import struct
+    import numpy as np
+    from hartsyinference_b200 import runtime
+    fn = runtime.lib().b200_ggml_dequant
+    fn.restype = C.c_int32
+    rng = np.random.default_rng(0)
+
+    def dequant(type_id, blocks, n):
+        out = np.zeros(n, dtype=np.float32)
+        rc = fn(type_id, blocks.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.POINTER(C.c_float)), C.c_int64(n))
+        assert rc == 0
+        return out
+
+    nb = 5
+    blk = rng.integers(0, 256, size=(nb, 110), dtype=np.uint8)
+    for b in range(nb):
+        blk[b, 108:110] = np.frombuffer(np.float16(rng.uniform(0.01, 0.1)).tobytes(), dtype=np.uint8)
+
+    def ref_q3k(p):
+        hm, qs, sc12 = p[:32], p[32:96], p[96:108]
+        d = np.frombuffer(p[108:110].tobytes(), dtype=np.float16)[0].astype(np.float32)
+        aux = list(struct.unpack("<3I", sc12.tobytes())) + [0]
+        k1, k2 = 0x03030303, 0x0F0F0F0F
+        tmp = aux[2]
+        aux[2] = ((aux[0] >> 4) & k2) | (((tmp >> 4) & k1) << 4)
+        aux[3] = ((aux[1] >> 4) & k2) | (((tmp >> 6) & k1) << 4)
+        aux[0] = (aux[0] & k2) | (((tmp >> 0) & k1) << 4)
+        aux[1] = (aux[1] & k2) | (((tmp >> 2) & k1) << 4)
+        scales = np.frombuffer(struct.pack("<4I", *aux), dtype=np.int8).astype(np.int32) - 32
+        y, i_s, m, q = [], 0, 1, 0
+        for _ in range(2):
+            shift = 0
+            for _ in range(4):
+                for part in (0, 16):
+                    dl = d * scales[i_s]
+                    i_s += 1
+                    for l in range(16):
+                        y.append(dl * (((int(qs[q + l + part]) >> shift) & 3) - (0 if hm[l + part] & m else 4)))
+                shift += 2
+                m <<= 1
+            q += 32
+        return np.array(y, dtype=np.float32)
+
+    want = np.concatenate([ref_q3k(blk[b]) for b in range(nb)])
+    assert np.array_equal(dequant(11, blk, nb * 256), want)
+    # Q8_1: f16 scale, f16 sum, 32 int8
+    b81 = np.zeros((3, 36), dtype=np.uint8)
+    q81 = rng.integers(-127, 128, size=(3, 32)).astype(np.int8)
+    for i in range(3):
+        b81[i, 0:2] = np.frombuffer(np.float16(0.03 * (i + 1)).tobytes(), dtype=np.uint8)
+        b81[i, 4:] = q81[i].view(np.uint8)
+    got = dequant(9, b81, 96).reshape(3, 32)
+    assert np.allclose(got, q81.astype(np.float32) * np.array([np.float16(0.03 * (i + 1)) for i in range(3)], dtype=np.float32)[:, None])
+    # Q8_K: fp32 scale, 256 int8, 16 int16 block sums
+    b8k = np.zeros((2, 292), dtype=np.uint8)
+    q8k = rng.integers(-127, 128, size=(2, 256)).astype(np.int8)
+    for i in range(2):
+        b8k[i, 0:4] = np.frombuffer(np.float32(0.011 * (i + 1)).tobytes(), dtype=np.uint8)
+        b8k[i, 4:260] = q8k[i].view(np.uint8)
+    got = dequant(15, b8k, 512).reshape(2, 256)
+    assert np.allclose(got, q8k.astype(np.float32) * np.array([0.011, 0.022], dtype=np.float32)[:, None])
