@@ -428,6 +428,38 @@ __device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
 }
 
 // ---------------------------------------------------------------------------------------------
+// Deferred split-K sums. A small-token GEMM whose tiles were all cut along K leaves fp32 partials
+// in scratch: per 128-feature tile `ta` and K range `s` one slot [bn tokens][128 features]. Instead
+// of a reduce kernel of its own, the kernel that consumes the GEMM's output can add the ranges
+// while it reads: value(token, feature) = sum over s of ws[((ta * splits + s) * bn + token) * 128 +
+// feature % 128], ta = feature / 128, rounded to bf16 as the stored output would have been.
+// ---------------------------------------------------------------------------------------------
+struct SplitPartials {
+  const float* ws;     // nullptr: the consumer reads its ordinary bf16 input
+  int splits, bn;
+};
+__device__ __forceinline__ float split_sum(const SplitPartials& sp, int token, int feature) {
+  const float* base = sp.ws + (static_cast<long long>(feature >> 7) * sp.splits * sp.bn + token) * 128 + (feature & 127);
+  float acc = 0.f;
+  for (int s = 0; s < sp.splits; ++s) acc += __ldcg(base + static_cast<long long>(s) * sp.bn * 128);
+  return __bfloat162float(__float2bfloat16(acc));
+}
+// eight consecutive features (feature0 a multiple of 8)
+__device__ __forceinline__ void split_sum8(const SplitPartials& sp, int token, int feature0, float (&out)[8]) {
+  const float* base = sp.ws + (static_cast<long long>(feature0 >> 7) * sp.splits * sp.bn + token) * 128 + (feature0 & 127);
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+  for (int s = 0; s < sp.splits; ++s) {
+    const float4 x = __ldcg(reinterpret_cast<const float4*>(base + static_cast<long long>(s) * sp.bn * 128));
+    const float4 y = __ldcg(reinterpret_cast<const float4*>(base + static_cast<long long>(s) * sp.bn * 128 + 4));
+    a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+    b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+  }
+  const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out[i] = __bfloat162float(__float2bfloat16(v[i]));
+}
+
+// ---------------------------------------------------------------------------------------------
 // small numeric helpers
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {

@@ -321,7 +321,7 @@ __global__ void quant_fp8_weight_kernel(const __nv_bfloat16* __restrict__ w,
 // up), act: 0 = SiLU, 1 = GELU-tanh. Optional fp8 1x128 output (F % 128 == 0).
 __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                            uint8_t* __restrict__ out_fp8, float* __restrict__ out_scale, int rows,
-                           int f, int act, int sf_tile_rows) {
+                           int f, int act, int sf_tile_rows, const SplitPartials part) {
   pdl_wait();
   pdl_trigger();
   const int nvec = f >> 3;
@@ -332,18 +332,27 @@ __global__ void glu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* 
     const bool active = i < total;
     const long long ii = active ? i : total - 1;
     const int row = static_cast<int>(ii / nvec), vi = static_cast<int>(ii % nvec);
-    const __nv_bfloat16* g = in + static_cast<long long>(row) * 2 * f + vi * 8;
-    uint4 graw = *reinterpret_cast<const uint4*>(g);
-    uint4 uraw = *reinterpret_cast<const uint4*>(g + f);
-    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&graw);
-    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    float gv[8], uv[8];
+    if (part.ws) {
+      // the producing GEMM left its K ranges unsummed: add them here (no reduce kernel in between)
+      split_sum8(part, row, vi * 8, gv);
+      split_sum8(part, row, f + vi * 8, uv);
+    } else {
+      const __nv_bfloat16* g = in + static_cast<long long>(row) * 2 * f + vi * 8;
+      uint4 graw = *reinterpret_cast<const uint4*>(g);
+      uint4 uraw = *reinterpret_cast<const uint4*>(g + f);
+      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&graw);
+      const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = __bfloat1622float2(gh[k]), b = __bfloat1622float2(uh[k]);
+        gv[2 * k] = a.x; gv[2 * k + 1] = a.y;
+        uv[2 * k] = b.x; uv[2 * k + 1] = b.y;
+      }
+    }
     float y[8];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float2 a = __bfloat1622float2(gh[k]), b = __bfloat1622float2(uh[k]);
-      y[2 * k] = (act == 0 ? silu(a.x) : gelu_tanh(a.x)) * b.x;
-      y[2 * k + 1] = (act == 0 ? silu(a.y) : gelu_tanh(a.y)) * b.y;
-    }
+    for (int k = 0; k < 8; ++k) y[k] = (act == 0 ? silu(gv[k]) : gelu_tanh(gv[k])) * uv[k];
     if (out && active) {
       uint4 o;
       uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
@@ -403,6 +412,7 @@ struct RopeParams {
   const float* inv_freq;          // optional [rot/2] precomputed (scaled) inverse frequencies
   int tokens, hq, hkv, d, rot, style, page;
   float theta, eps;
+  SplitPartials part;             // ws != null: qkv comes as unsummed K ranges of the producing GEMM
 };
 
 __global__ void rope_kv_kernel(const RopeParams p) {
@@ -421,7 +431,9 @@ __global__ void rope_kv_kernel(const RopeParams p) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int c = lane + 32 * i;
-    v[i] = (i < per && c < p.d) ? __bfloat162float(src[c]) : 0.f;
+    if (!(i < per && c < p.d)) v[i] = 0.f;
+    else if (p.part.ws) v[i] = split_sum(p.part, t, h * p.d + c);
+    else v[i] = __bfloat162float(src[c]);
   }
   const __nv_bfloat16* nw = kind == 0 ? p.q_norm_w : (kind == 1 ? p.k_norm_w : nullptr);
   if (nw) {
@@ -733,13 +745,18 @@ B200_API int b200_quant_fp8_weight(const void* w, void* out, float* scales, int 
   return 0;
 }
 
+// part_ws != null: `in` is ignored and the [rows][2f] input is read as the unsummed K ranges a
+// deferred small-token GEMM left in its scratch (see SplitPartials; b200_gemm_deferred).
 B200_API int b200_glu(const void* in, void* out, void* out_fp8, float* out_scale, int rows, int f,
-                      int act, int sf_tile_rows, cudaStream_t stream) {
+                      int act, int sf_tile_rows, const float* part_ws, int part_splits, int part_bn,
+                      cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (f % 8 != 0 || (out_fp8 && f % 128 != 0)) return -2;
   const long long n = static_cast<long long>(rows) * (f / 8);
+  const SplitPartials part{part_ws, part_splits, part_bn};
   launch_pdl(glu_kernel, dim3(grid_for(n, 256)), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in),
-             static_cast<__nv_bfloat16*>(out), static_cast<uint8_t*>(out_fp8), out_scale, rows, f, act, sf_tile_rows);
+             static_cast<__nv_bfloat16*>(out), static_cast<uint8_t*>(out_fp8), out_scale, rows, f, act, sf_tile_rows,
+             part);
   CHECK_LAUNCH();
   return 0;
 }
@@ -748,10 +765,12 @@ B200_API int b200_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_c
                           void* v_out, const int* positions, const long long* slot_mapping,
                           const void* q_norm_w, const void* k_norm_w, const float* inv_freq,
                           int tokens, int hq, int hkv, int d, int rot, int style, int page,
-                          float theta, float eps, cudaStream_t stream) {
+                          float theta, float eps, const float* part_ws, int part_splits, int part_bn,
+                          cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (d > 256 || rot > d || (rot & 1)) return -2;
   RopeParams p{};
+  p.part = SplitPartials{part_ws, part_splits, part_bn};
   p.qkv = static_cast<const __nv_bfloat16*>(qkv);
   p.q_out = static_cast<__nv_bfloat16*>(q_out);
   p.k_cache = static_cast<__nv_bfloat16*>(k_cache);

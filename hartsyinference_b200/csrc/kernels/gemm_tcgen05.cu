@@ -1283,7 +1283,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
                      const float* w_scale, const void* bias, const void* gate, const void* residual,
                      int act, int splits, void* workspace, long long workspace_bytes, void* status,
                      cudaStream_t stream, const AllReduceParams* ar, const GroupSpec* gs = nullptr,
-                     const ConvSpec* cs = nullptr) {
+                     const ConvSpec* cs = nullptr, int* defer_info = nullptr) {
   const int groups = gs ? gs->groups : 0;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   // grouped: x is [groups * m][k], w is [groups * n][k], out is [groups * m][n]; m = tokens per group
@@ -1492,6 +1492,15 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
       rc = launch_gemm<0, 256, 1>(p, ta, tb, grid, stream);
     }
   }
+  if (defer_info != nullptr) {
+    // the caller's consumer kernel sums the K ranges itself: report their layout, launch no reduce
+    const bool deferred = rc == 0 && p.external_reduce && swap && groups == 0 && bias == nullptr &&
+                          gate == nullptr && residual == nullptr && act == 0 && m <= bn;
+    defer_info[0] = deferred ? 1 : 0;
+    defer_info[1] = p.splits;
+    defer_info[2] = bn;
+    if (deferred) return rc;
+  }
   if (rc == 0 && p.external_reduce) {
     const dim3 rgrid((bn * 32 + 255) / 256, tiles);
     if (launch_pdl(splitk_reduce_kernel, rgrid, dim3(256), 0, stream, p, bn, (p.rows_a + kTileA - 1) / kTileA,
@@ -1529,6 +1538,19 @@ B200_API int b200_gemm(const void* x, const void* w, void* out, int m, int n, in
                        long long workspace_bytes, void* status, cudaStream_t stream) {
   return gemm_impl(x, w, out, m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, bias, gate, residual,
                    act, splits, workspace, workspace_bytes, status, stream, nullptr);
+}
+
+// b200_gemm for a consumer that can add split-K ranges itself (b200_glu, b200_rope_kv): when the
+// policy cuts every tile along K (small-token GEMMs with fewer tiles than SMs) and no epilogue term
+// is asked for, the reduce kernel is NOT launched and `out` is left untouched; info[0] = 1 then and
+// the partials sit at workspace + 16384 bytes as [feature tile][info[1] K ranges][info[2] tokens][128]
+// fp32. Otherwise info[0] = 0 and `out` holds the result as usual.
+B200_API int b200_gemm_deferred(const void* x, const void* w, void* out, int m, int n, int k, long long ldx,
+                                long long ldw, long long ldc, int dtype, const float* x_scale,
+                                const float* w_scale, void* workspace, long long workspace_bytes, int* info,
+                                void* status, cudaStream_t stream) {
+  return gemm_impl(x, w, out, m, n, k, ldx, ldw, ldc, dtype, x_scale, w_scale, nullptr, nullptr, nullptr, 0, 0,
+                   workspace, workspace_bytes, status, stream, nullptr, nullptr, nullptr, info);
 }
 
 // Row-parallel linear of a tensor-parallel group fused with the all-reduce of its output, the

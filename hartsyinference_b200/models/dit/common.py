@@ -48,8 +48,20 @@ class WeightFactory:
         self.get = get
         self.std = std
         self._g = torch.Generator().manual_seed(seed)
+        self._seed = seed
+        self._big = 0
 
     def _rand(self, *shape, std=None) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= d
+        if self.device.type == "cuda" and n >= (1 << 22) and len(shape) == 2:
+            # full-size synthetic models: draw the (unsharded) tensor on the device from a counter-based
+            # generator: the same values on every rank, without seconds of host random numbers per tensor
+            self._big += 1
+            t = torch.empty(*shape, dtype=torch.bfloat16, device=self.device)
+            ops.fill_random_(t, self._seed * 1000003 + 7919 * self._big + 1, self.std if std is None else std)
+            return t
         return (torch.randn(*shape, generator=self._g) * (self.std if std is None else std)).to(torch.bfloat16)
 
     def tensor(self, name: str, *shape, ones: bool = False, zeros: bool = False) -> torch.Tensor:
@@ -93,7 +105,7 @@ class WeightFactory:
             ws.append(w)
             if b is not None:
                 bs.append(b)
-        w = torch.cat(ws, 0).contiguous().to(torch.bfloat16).to(self.device)
+        w = torch.cat([x.to(self.device) for x in ws], 0).contiguous().to(torch.bfloat16)
         b = torch.cat(bs, 0).to(torch.bfloat16).to(self.device) if bs else None
         return LinearWeight.from_dense(w, b, fp8=self.fp8 and allow_fp8 and w.is_cuda and w.shape[1] % 128 == 0)
 

@@ -541,7 +541,10 @@ class DecoderModel:
         (bf16, or already quantised for an fp8 output projection at decode)."""
         cfg, d = self.cfg, self.cfg.head_dim
         t = (h if h is not None else hq8.data).shape[0]
-        qkv = ops.linear(hq8 if hq8 is not None else h, lw.qkv)
+        # decode-size batches: a fully K-split qkv GEMM leaves its ranges to the rotary kernel
+        simple = (not cfg.qk_norm_full and not cfg.qk_norm_after_rope and not (cfg.mrope_section and batch.positions3 is not None)
+                  and self.kv_cache is not None)
+        qkv = ops.linear(hq8 if hq8 is not None else h, lw.qkv, defer=simple and t <= 128 and x_is_cuda(hq8 if hq8 is not None else h))
         q_norm_w, k_norm_w = lw.q_norm, lw.k_norm
         if cfg.qk_norm_full and q_norm_w is not None:
             # RMSNorm over all heads of q (and of k) at once, before the heads are split
@@ -750,7 +753,7 @@ class DecoderModel:
             att = self._attention_core(lw, li, h, hq8, batch, scale)
             g8 = fp8 and lw.gate_up.is_fp8
             h2, h2q8 = frp(att, lw.o, res=res, norm_w=lw.post_norm, emit_fp8=g8, emit_bf16=not g8, **kw)
-            gu = ops.linear(h2q8 if h2q8 is not None else h2, lw.gate_up)
+            gu = ops.linear(h2q8 if h2q8 is not None else h2, lw.gate_up, defer=True)
             d8 = fp8 and lw.down.is_fp8
             act, act8 = ops.glu(gu, cfg.activation, emit_fp8=d8, emit_bf16=not d8)
             if li == last:
@@ -806,7 +809,9 @@ class DecoderModel:
             if lw.ffn_module is not None:
                 f = lw.ffn_module(h2, self)
             else:
-                gu = ops.linear(h2q8 if h2q8 is not None else h2, lw.gate_up)
+                gated_fast = cfg.gated_ffn and cfg.activation in ("silu", "gelu_tanh")
+                gu = ops.linear(h2q8 if h2q8 is not None else h2, lw.gate_up,
+                                defer=gated_fast and x.is_cuda and x.shape[0] <= 128)
                 if cfg.gated_ffn:
                     act, act8 = ops.glu(gu, cfg.activation, emit_fp8=fp8 and lw.down.is_fp8,
                                         emit_bf16=not (fp8 and lw.down.is_fp8))

@@ -53,8 +53,9 @@ _SIGNATURES = {
     "b200_norm": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, i32, i32, vp]),
     "b200_quant_fp8": (i32, [vp, vp, vp, i32, i32, i64, i32, vp]),
     "b200_quant_fp8_weight": (i32, [vp, vp, vp, i32, i32, vp]),
-    "b200_glu": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
-    "b200_rope_kv": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, f32, vp]),
+    "b200_glu": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp]),
+    "b200_gemm_deferred": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, i64, vp, vp, vp]),
+    "b200_rope_kv": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, f32, vp, i32, i32, vp]),
     "b200_embedding": (i32, [vp, vp, vp, i32, i32, i32, f32, vp]),
     "b200_argmax": (i32, [vp, vp, i32, i32, i64, i32, vp]),
     "b200_repetition_penalty": (i32, [vp, vp, vp, i32, i32, i32, vp, vp]),

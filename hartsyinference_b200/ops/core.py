@@ -155,6 +155,24 @@ def quant_fp8_weight(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return q, s
 
 
+@dataclass
+class SplitSum:
+    """Result of a small-token GEMM whose K ranges were left unsummed in the GEMM scratch
+    (``linear(..., defer=True)``): the consumer kernel (``glu``, ``rope_kv``) adds them while it
+    reads, so no reduce kernel runs in between. Valid until the next GEMM on the device."""
+    ws: torch.Tensor          # the device's GEMM scratch
+    splits: int
+    bn: int
+    shape: tuple              # (tokens, features) of the product
+
+    def part_args(self):
+        return self.ws.data_ptr() + 16384, self.splits, self.bn
+
+
+def _part_args(x):
+    return x.part_args() if isinstance(x, SplitSum) else (None, 0, 0)
+
+
 def _gemm_dtype(w: LinearWeight) -> int:
     return 2 if w.is_mx else 1 if w.is_fp8 else 0
 
@@ -169,11 +187,13 @@ def _scale_ptrs(x, w: LinearWeight):
 
 def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.Tensor] = None,
            residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-           splits: Optional[int] = None) -> torch.Tensor:
+           splits: Optional[int] = None, defer: bool = False):
     """y = residual + gate * act(x @ W^T + bias), bf16 output [M, N].
 
     ``x`` is a bf16 tensor [M, K] or an :class:`Fp8Act`. With an fp8 weight a bf16 ``x`` is
     quantised on the fly (1x128 groups). ``gate`` is a per-output-feature vector [N].
+    ``defer=True`` (device, plain product only): when the GEMM cuts all its tiles along K, return a
+    :class:`SplitSum` for a consumer that adds the ranges itself instead of running the reduce kernel.
     """
     if isinstance(w, GgufWeight):
         if act is not None or gate is not None or residual is not None or isinstance(x, Fp8Act):
@@ -210,6 +230,14 @@ def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.T
     st = N.state(xd.device)
     ws = st.gemm_workspace()
     xs_ptr, ws_ptr = _scale_ptrs(x, w)
+    if defer and m <= 128 and w.bias is None and act is None and gate is None and residual is None and splits is None:
+        import ctypes as C
+        info = (C.c_int * 4)()
+        rc = L.b200_gemm_deferred(xd.data_ptr(), w.weight.data_ptr(), out.data_ptr(), m, n, k, xd.stride(0),
+                                  w.weight.stride(0), out.stride(0), _gemm_dtype(w), xs_ptr, ws_ptr, ws.data_ptr(),
+                                  ws.numel(), info, st.status.data_ptr(), N.stream())
+        N.check(rc, "b200_gemm_deferred")
+        return SplitSum(ws, int(info[1]), int(info[2]), (m, n)) if info[0] else out
     rc = L.b200_gemm(xd.data_ptr(), w.weight.data_ptr(), out.data_ptr(), m, n, k,
                      xd.stride(0), w.weight.stride(0), out.stride(0), _gemm_dtype(w),
                      xs_ptr, ws_ptr,
@@ -267,6 +295,20 @@ def glu(x: torch.Tensor, act: str = "silu", emit_fp8: bool = False, emit_bf16: b
     """act(x[:, :F]) * x[:, F:] for x [rows, 2F]. Returns (y bf16 or None, y_fp8 or None)."""
     rows, f2 = x.shape
     f = f2 // 2
+    if isinstance(x, SplitSum):
+        dev = x.ws.device
+        y = torch.empty(rows, f, dtype=torch.bfloat16, device=dev) if emit_bf16 else None
+        q = s = None
+        mx = emit_fp8 and fp8_mx()
+        if emit_fp8:
+            q = torch.empty(rows, f, dtype=torch.uint8, device=dev)
+            s = _alloc_sf(rows, f, fp8_tile_rows, dev) if mx else torch.empty(rows, f // 128, dtype=torch.float32, device=dev)
+        rc = N.lib().b200_glu(None, N.ptr(y), N.ptr(q), N.ptr(s), rows, f, 0 if act == "silu" else 1,
+                              fp8_tile_rows if mx else 0, *x.part_args(), N.stream())
+        N.check(rc, "b200_glu")
+        if not emit_fp8:
+            return y, None
+        return y, (Fp8Act(q, None, s, fp8_tile_rows) if mx else Fp8Act(q, s))
     if not x.is_cuda:
         y = R.glu(x, act).to(x.dtype)
         fq = None
@@ -283,7 +325,7 @@ def glu(x: torch.Tensor, act: str = "silu", emit_fp8: bool = False, emit_bf16: b
         s = _alloc_sf(rows, f, fp8_tile_rows, x.device) if mx else \
             torch.empty(rows, f // 128, dtype=torch.float32, device=x.device)
     rc = N.lib().b200_glu(x.data_ptr(), N.ptr(y), N.ptr(q), N.ptr(s), rows, f, 0 if act == "silu" else 1,
-                          fp8_tile_rows if mx else 0, N.stream())
+                          fp8_tile_rows if mx else 0, None, 0, 0, N.stream())
     N.check(rc, "b200_glu")
     if not emit_fp8:
         return y, None
@@ -298,10 +340,11 @@ def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, hq: int, hkv: int, d: in
             eps: float = 1e-6, want_kv: bool = False):
     """Optional QK RMSNorm + rotary embedding on a packed qkv activation [T, (hq + 2 hkv) d], and
     the K/V write into the page pool ([pages, hkv, page, d], slot = page_index * page + offset).
-    Returns (q [T, hq, d], k [T, hkv, d] or None, v or None)."""
+    Returns (q [T, hq, d], k [T, hkv, d] or None, v or None). ``qkv`` may be a :class:`SplitSum`."""
+    part = qkv if isinstance(qkv, SplitSum) else None
     t = qkv.shape[0]
     rot = d if rot is None else rot
-    if not qkv.is_cuda:
+    if part is None and not qkv.is_cuda:
         x = qkv.float().reshape(t, hq + 2 * hkv, d)
         q, k, v = x[:, :hq], x[:, hq:hq + hkv], x[:, hq + hkv:]
         if q_norm_w is not None:
@@ -320,17 +363,19 @@ def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, hq: int, hkv: int, d: in
             k_cache[pg, :, off] = k[ok]
             v_cache[pg, :, off] = v[ok]
         return q.contiguous(), (k.contiguous() if want_kv else None), (v.contiguous() if want_kv else None)
-    assert qkv.is_contiguous() and qkv.dtype == torch.bfloat16
-    q = torch.empty(t, hq, d, dtype=torch.bfloat16, device=qkv.device)
-    k = torch.empty(t, hkv, d, dtype=torch.bfloat16, device=qkv.device) if want_kv else None
-    v = torch.empty(t, hkv, d, dtype=torch.bfloat16, device=qkv.device) if want_kv else None
+    dev = part.ws.device if part is not None else qkv.device
+    assert part is not None or (qkv.is_contiguous() and qkv.dtype == torch.bfloat16)
+    q = torch.empty(t, hq, d, dtype=torch.bfloat16, device=dev)
+    k = torch.empty(t, hkv, d, dtype=torch.bfloat16, device=dev) if want_kv else None
+    v = torch.empty(t, hkv, d, dtype=torch.bfloat16, device=dev) if want_kv else None
     page = k_cache.shape[2] if k_cache is not None else 16
     if slot_mapping is not None:
         assert slot_mapping.dtype == torch.int64
     assert positions.dtype == torch.int32
-    rc = N.lib().b200_rope_kv(qkv.data_ptr(), q.data_ptr(), N.ptr(k_cache), N.ptr(v_cache), N.ptr(k), N.ptr(v),
-                              positions.data_ptr(), N.ptr(slot_mapping), N.ptr(q_norm_w), N.ptr(k_norm_w),
-                              N.ptr(inv_freq), t, hq, hkv, d, rot, style, page, theta, eps, N.stream())
+    rc = N.lib().b200_rope_kv(None if part is not None else qkv.data_ptr(), q.data_ptr(), N.ptr(k_cache), N.ptr(v_cache),
+                              N.ptr(k), N.ptr(v), positions.data_ptr(), N.ptr(slot_mapping), N.ptr(q_norm_w),
+                              N.ptr(k_norm_w), N.ptr(inv_freq), t, hq, hkv, d, rot, style, page, theta, eps,
+                              *_part_args(qkv), N.stream())
     N.check(rc, "b200_rope_kv")
     return q, k, v
 

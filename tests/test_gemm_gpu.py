@@ -115,3 +115,40 @@ def test_gemm_deterministic():
     a = ops.linear(x, lw, splits=4)
     b = ops.linear(x, lw, splits=4)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_deferred_split_sums_match_the_reduce_kernel(fp8):
+    """A small-token GEMM whose tiles are all cut along K can leave the ranges to its consumer:
+    GLU and the rotary / KV-write kernel then give the results of the unfused sequence."""
+    from hartsyinference_b200.ops.core import SplitSum
+    torch.manual_seed(5)
+    m, k = 48, 2048
+    # gate|up projection -> GLU (fp8 emit)
+    f = 1024
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    w = ops.LinearWeight.from_dense((torch.randn(2 * f, k, device="cuda") * 0.05).to(torch.bfloat16), fp8=fp8)
+    xin = ops.quant_fp8_act(x) if fp8 else x
+    d = ops.linear(xin, w, defer=True)
+    assert isinstance(d, SplitSum), "this shape has fewer tiles than SMs: the GEMM must have deferred its reduction"
+    y1, q1 = ops.glu(d, "silu", emit_fp8=True)
+    y0, q0 = ops.glu(ops.linear(xin, w), "silu", emit_fp8=True)
+    assert torch.equal(y1, y0) and torch.equal(q1.data, q0.data)
+    # qkv projection -> rotary + paged KV write
+    hq, hkv, dd = 4, 2, 128
+    wq = ops.LinearWeight.from_dense((torch.randn((hq + 2 * hkv) * dd, k, device="cuda") * 0.05).to(torch.bfloat16), fp8=fp8)
+    pos = torch.arange(m, dtype=torch.int32, device="cuda")
+    slots = torch.arange(m, dtype=torch.int64, device="cuda")
+    outs = []
+    for defer in (True, False):
+        kc = torch.zeros(4, hkv, 16, dd, device="cuda", dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        qkv = ops.linear(xin, wq, defer=defer)
+        assert isinstance(qkv, SplitSum) == defer
+        q, _, _ = ops.rope_kv(qkv, pos, hq, hkv, dd, k_cache=kc, v_cache=vc, slot_mapping=slots, theta=5e5)
+        outs.append((q, kc, vc))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    # a large GEMM is never deferred
+    big = ops.LinearWeight.from_dense((torch.randn(148 * 128, 256, device="cuda") * 0.05).to(torch.bfloat16))
+    assert isinstance(ops.linear(x[:, :256].contiguous(), big, defer=True), torch.Tensor)
