@@ -106,7 +106,10 @@ class WanTransformer:
         self.device = torch.device(device)
         self.comm = sp_comm or SingleComm()
         self.sp, self.sp_rank = self.comm.world, self.comm.rank
-        assert cfg.num_heads % self.sp == 0, "Ulysses needs whole heads per rank"
+        # Ulysses (head exchange) needs whole heads per rank; otherwise the tokens stay where they
+        # are and every rank gathers all keys / values (the reference's context-parallel exchange,
+        # src/HartsyInference.Diffusion/Utilities/CpKvExchange.cs:48, CpSequencePlan.cs:38)
+        self.ulysses = cfg.num_heads % self.sp == 0
         H = cfg.hidden_size
         f = WeightFactory(self.device, fp8, 0, 1, get, seed)
         self.fp8 = fp8 and self.device.type == "cuda"
@@ -158,6 +161,11 @@ class WanTransformer:
         """q, k, v [S_local, heads, D] -> [S_local, heads * D]."""
         if self.sp == 1:
             o = ops.attention(q, k, v)
+            return o.reshape(o.shape[0], -1)
+        if not self.ulysses:
+            kf = self.comm.all_gather(k.contiguous(), dim=0)                      # [S, heads, D]
+            vf = self.comm.all_gather(v.contiguous(), dim=0)
+            o = ops.attention(q.contiguous(), kf, vf)
             return o.reshape(o.shape[0], -1)
         a2a = self.comm.all_to_all
         qf, kf, vf = (a2a(t, split_dim=1, concat_dim=0) for t in (q, k, v))      # [S, heads / sp, D]

@@ -44,3 +44,28 @@ from .core import (  # noqa: F401
     selective_scan,
 )
 from . import reference  # noqa: F401
+
+
+# Every op entry point runs inside a named range when ``B200_PROFILE`` / ``B200_NVTX`` is set
+# (per-op device-time table, NVTX ranges for a timeline tool); with both off the wrapper is one
+# flag lookup. (The reference wraps its backend calls the same way: NvtxRange + HARTSY_PROFILE,
+# src/HartsyInference.Cuda/Profiling/NvtxRange.cs:33-67.)
+def _install_ranges() -> None:
+    import sys
+    from ..utils.profiling import traced
+    from . import core
+    mod = sys.modules[__name__]
+    for name in ("linear", "norm", "glu", "rope_kv", "attn_decode", "attn_prefill_paged", "attn_paged_biased", "attention",
+                 "embedding", "argmax", "quant_fp8_act", "grouped_linear", "grouped_linear_dynamic", "moe_route",
+                 "moe_dispatch", "moe_dispatch_dynamic", "moe_combine", "mla_prep", "mla_attn", "colbatched_linear",
+                 "dit_qkv", "gated_residual", "cfg_euler_step", "causal_conv3d", "gguf_linear", "selective_scan"):
+        fn = getattr(core, name, None)
+        if fn is None:
+            continue
+        wrapped = traced(name)(fn)
+        setattr(core, name, wrapped)          # internal calls (core.linear -> core.gguf_linear) are traced too
+        if hasattr(mod, name):
+            setattr(mod, name, wrapped)
+
+
+_install_ranges()

@@ -28,6 +28,8 @@ def op_range(label: str):
     """NVTX range (``B200_NVTX=1``) and/or device-time accounting (``B200_PROFILE=1``)."""
     use_nvtx = config.get("nvtx") and torch.cuda.is_available()
     prof = config.get("profile") and torch.cuda.is_available()
+    if prof and torch.cuda.is_current_stream_capturing():
+        prof = False          # timing events recorded into a CUDA graph cannot be read back
     if use_nvtx:
         torch.cuda.nvtx.range_push(label)
     if prof:
@@ -47,6 +49,26 @@ def op_range(label: str):
                 _pending.append((label, a, b))
         if use_nvtx:
             torch.cuda.nvtx.range_pop()
+
+
+def active() -> bool:
+    """True when either flag asks for ranges (checked by the op wrappers before they pay for one)."""
+    return bool(config.get("profile") or config.get("nvtx"))
+
+
+def traced(label: str):
+    """Decorator: run the function inside ``op_range(label)`` when profiling or NVTX is on."""
+    def wrap(fn):
+        import functools
+
+        @functools.wraps(fn)
+        def inner(*a, **kw):
+            if not active():
+                return fn(*a, **kw)
+            with op_range(label):
+                return fn(*a, **kw)
+        return inner
+    return wrap
 
 
 def _drain() -> None:

@@ -88,6 +88,16 @@ def main():
     o1 = w1.forward(lat, torch.tensor(300.0), w1.encode_text(ctxr))
     o2 = w2.forward(lat, torch.tensor(300.0), w2.encode_text(ctxr))
     assert cos(o1, o2) > 0.999, cos(o1, o2)
+    # ---- head count that does not divide by the group: keys / values are gathered instead (context parallel)
+    if world == 2:
+        odd = W.tiny_wan(hidden_size=96, num_heads=3, head_dim=32)
+        a1 = W.WanTransformer(odd, "cpu", seed=13)
+        a2 = W.WanTransformer(odd, "cpu", sp_comm=comm, seed=13)
+        assert not a2.ulysses
+        ctxo = torch.randn(odd.text_len, odd.text_dim, generator=gi)
+        r1 = a1.forward(lat, torch.tensor(300.0), a1.encode_text(ctxo))
+        r2 = a2.forward(lat, torch.tensor(300.0), a2.encode_text(ctxo))
+        assert cos(r1, r2) > 0.999, cos(r1, r2)
     # ---- CFG-parallel pipelines vs sequential CFG
     from hartsyinference_b200.pipelines.flux import FluxComponents, FluxPipeline
     from hartsyinference_b200.pipelines.wan import WanComponents, WanPipeline

@@ -194,3 +194,36 @@ def test_forced_tool_call_through_the_text_service(tmp_path):
     finally:
         eng.text.release()
     assert parse_tool_calls(forced_prefix("lookup") + '{"q": 1}}\n</tool_call>', {"lookup"})[1][0].name == "lookup"
+
+
+def test_native_host_decoder_matches_the_op_by_op_path():
+    """The native batch-1 host decoder (AVX-512 row kernels + thread team) gives the same logits and
+    greedy tokens as the general path on a llama-family toy model, and refuses models it cannot run."""
+    import torch
+    from hartsyinference_b200.models.llm.config import tiny
+    from hartsyinference_b200.models.llm.cpu_decoder import CpuDecoder, eligible
+    from hartsyinference_b200.models.llm.transformer import DecoderModel, ForwardBatch
+    cfg = tiny("qwen2.5-0.5b", vocab_size=512, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32, ffn_size=256)
+    m = DecoderModel(cfg, "cpu")
+    m.random_init(0, std=0.05)
+    assert eligible(m)
+    dec = CpuDecoder(m, 64, threads=3)
+    seq = [5, 17, 300, 44, 9, 2, 88, 123, 7, 7, 400]
+    got = [dec.step(t, want_logits=True) for t in seq]
+    n = len(seq)
+    m.alloc_kv(2, 16)
+    b = ForwardBatch(tokens=torch.tensor(seq, dtype=torch.int32), positions=torch.arange(n, dtype=torch.int32),
+                     slot_mapping=torch.arange(n, dtype=torch.int64), block_table=torch.arange(2, dtype=torch.int32)[None],
+                     kv_lens=torch.tensor([n], dtype=torch.int32), is_decode=False, cu_q=torch.tensor([0, n], dtype=torch.int32),
+                     max_q_len=n, max_kv_len=n)
+    ref = m.logits(m.forward_hidden(b)).float()[:, : cfg.vocab_size]
+    for i, (tok, lg) in enumerate(got):
+        assert torch.nn.functional.cosine_similarity(lg, ref[i], dim=0) > 0.999
+        top2 = ref[i].topk(2).values
+        if top2[0] - top2[1] > 0.05:
+            assert tok == int(ref[i].argmax())
+    assert dec.generate(seq[:4], 3) == dec.generate(seq[:4], 3)
+    gem = DecoderModel(tiny("qwen2.5-0.5b", vocab_size=64, hidden_size=64, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=32,
+                            ffn_size=64, activation="gelu_tanh"), "cpu")
+    gem.random_init(0)
+    assert not eligible(gem)
