@@ -59,6 +59,9 @@ def parse_args():
     ap.add_argument("--no-fused-comm", action="store_true", help="NCCL all-reduce instead of the fused kernels")
     ap.add_argument("--force-fused", action="store_true", help="keep the fused kernels even where GEMM + NCCL measures faster")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--via", default="steps", choices=["steps", "engine"],
+                    help="steps: drive LLMEngine.step directly (the headline); engine: client threads streaming through "
+                         "InferenceEngine.text, followers under engine.follow() (benchmarks/via_engine.py)")
     return ap.parse_args()
 
 
@@ -145,6 +148,25 @@ def main() -> int:
                    "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29517"),
                    os.path.abspath(__file__)] + sys.argv[1:]
             return subprocess.call(cmd)
+    if args.via == "engine":
+        if args.preset in ("flux-dev", "wan-14b"):
+            print(json.dumps({"unavailable": "--via engine covers the text presets"}))
+            return 0
+        dsv3 = args.preset == "deepseek-v3"
+        args.batch = args.batch or (256 if dsv3 else 64)
+        args.prompt_len = args.prompt_len or (1024 if dsv3 else 2048)
+        args.decode_len = args.decode_len or (128 if dsv3 else 256)
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local_rank)
+        sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+        import via_engine
+        out = via_engine.run(args, world, rank, local_rank, ClockSampler(local_rank), _metric_name(args))
+        if out is not None:
+            print(json.dumps(out))
+        sys.stdout.flush()
+        if world > 1:
+            os._exit(0)
+        return 0
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     comm = init_comm()

@@ -159,6 +159,8 @@ def wan_parity(comm, dev, fp8: bool) -> dict:
     t = torch.tensor(500.0, device=dev)
     sp = W.WanTransformer(cfg, dev, sp_comm=comm, fp8=fp8, seed=7)
     got = sp.forward(lat, t, sp.encode_text(text)).float()
+    path = sp.exchange_path
+    sp.close()
     del sp
     cos = 1.0
     if comm.rank == 0:
@@ -168,7 +170,8 @@ def wan_parity(comm, dev, fp8: bool) -> dict:
     c = torch.tensor([cos], device=dev)
     comm.broadcast(c, 0)
     torch.cuda.empty_cache()
-    return {"ok": bool(c.item() > 0.99), "cos": float(c.item()), "what": f"2 blocks, 128 tokens, sp{comm.world} vs sp1"}
+    return {"ok": bool(c.item() > 0.99), "cos": float(c.item()), "what": f"2 blocks, 128 tokens, sp{comm.world} vs sp1",
+            "path": path}
 
 
 def run_wan(args, comm, dev, sampler) -> dict:
@@ -204,6 +207,8 @@ def run_wan(args, comm, dev, sampler) -> dict:
     ms_step, e2e = _finish(pipe, io, warmup, steps, comm, dev, 2 * ctx.numel() * 4)
     from hartsyinference_b200.ops import _native as N
     N.check_status(dev)
+    exchange = tr.exchange_path
+    tr.close()
     S, H = 21 * 45 * 80, cfg.hidden_size
     lin = cfg.num_layers * (2 * S * H * (4 * H + 2 * H + 2 * cfg.ffn_size))
     att = cfg.num_layers * (4 * S * S * H + 4 * S * cfg.text_len * H)
@@ -221,7 +226,7 @@ def run_wan(args, comm, dev, sampler) -> dict:
                    "attention": "bf16 tcgen05 flash attention",
                    "l2": "inputs larger than L2 (activations of 75600 tokens x 5120 alone are 774 MB)",
                    "invalid_debug_overrides": invalid,
-                   "comm_path": "nccl all-to-all / all-gather" if comm.world > 1 else "none"},
+                   "comm_path": exchange + ("; CFG pair: all-gather of the two velocity fields (NCCL)" if cfg_comm is not None else "")},
         "e2e": e2e, "gpu_launches": N.launch_count, "clocks": clocks, "parity": parity, "load_s": t_load,
         "flops_per_step": flops, "tflops_per_gpu": flops / (ms_step / 1e3) / 1e12 / comm.world,
         "weight_bytes_per_gpu": tr.weight_bytes(),

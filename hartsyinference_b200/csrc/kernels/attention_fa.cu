@@ -29,7 +29,7 @@
 //
 // V is consumed transposed ([head dim][keys], keys contiguous) so that both MMAs use K-major
 // operands; the transpose (and the int8 quantisation) is a small kernel of its own in front.
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace b200 {
 
@@ -65,10 +65,35 @@ struct FaParams {
   const float* k_scale;
   int sq_pad;
   DeviceStatus* status;
+  // Segmented operands (the sequence-parallel exchange below): the key buffers hold `nseg`
+  // segments of `seg_pad` rows (a multiple of 128) of which the first `seg_len` are real; segment
+  // s was written by rank s and is complete once seg_flags[s] has reached seg_target. The walk
+  // over the keys starts with segment `seg_first` (this rank's own, which arrives first). Query
+  // rows use the same layout; the output rows of query segment s go to out_seg[s] (rank s's
+  // buffer, row = index inside the segment, column offset out_col0). A plain call has one segment
+  // and no flags.
+  int n_tiles, tiles_per_seg, nseg, seg_len, seg_first, seg_pad;
+  int seg_mode;
+  const uint32_t* seg_flags;
+  uint32_t seg_target;
+  long long wait_budget;
+  __nv_bfloat16* out_seg[8];
+  long long out_col0;
+  uint32_t* done_flags[8];   // rank s's "outputs have arrived" counter
+  uint32_t* done_ctr;        // CTAs of this launch that have finished
 };
 
+// Buffer tile (index into the segmented key buffers) and number of real keys of walk step j.
+__device__ __forceinline__ void fa_key_tile(const FaParams& p, int j, int& buf_tile, int& valid, int& seg) {
+  const int sg = j / p.tiles_per_seg, lt = j - sg * p.tiles_per_seg;
+  seg = p.seg_first + sg;
+  if (seg >= p.nseg) seg -= p.nseg;
+  buf_tile = seg * p.tiles_per_seg + lt;
+  valid = min(kFaTile, p.seg_len - lt * kFaTile);
+}
+
 template <bool kI8>
-__global__ void __maxnreg__(192)
+__global__ void __launch_bounds__(kFaThreads, 1)
 attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_vt) {
   constexpr int kQkTileBytes = kI8 ? 128 * 128 : 128 * 128 * 2;   // one Q or K tile
@@ -84,7 +109,7 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt2 = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
-  const int n_tiles = (p.sk + kFaTile - 1) / kFaTile;
+  const int n_tiles = p.n_tiles;
   const int q_row0 = b * p.sq + qt2 * 2 * kFaTile;     // row of the CTA's first query in [batch * sq]
   const int k_row0 = b * p.sk;
   const int vt_row0 = (b * p.heads + head) * kFaD;     // row in the [batch * heads * 128][sk_pad] matrix
@@ -127,24 +152,44 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
     // ------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
       const int nq = tile1 ? 2 : 1;
-      mbar_arrive_expect_tx(&bars->q_full, nq * kQkTileBytes);
-      for (int t = 0; t < nq; ++t)
-        for (int a = 0; a < kQkAtoms; ++a)
-          tma_load_2d(sq + t * kQkTileBytes + a * (kQkTileBytes / kQkAtoms), &tm_q, &bars->q_full,
-                      col0 + a * 64, q_row0 + t * kFaTile);
       bool ok = true;
+      // a segment written by a peer: its flag first, then a proxy fence, because the loads below
+      // are issued by the TMA unit and the peer's data arrived as ordinary stores
+      auto wait_segment = [&](int seg) {
+        if (p.seg_flags == nullptr) return true;
+        if (!wait_flag_geq(p.seg_flags + seg, p.seg_target, p.wait_budget)) {
+          *abort_flag = 1;
+          return false;
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        return true;
+      };
+      if (p.seg_mode) {
+        const int first = qt2 * 2 * kFaTile, last = first + nq * kFaTile - 1;
+        for (int seg = first / p.seg_pad; seg <= last / p.seg_pad && ok; ++seg) ok = wait_segment(seg);
+      }
+      if (ok) {
+        mbar_arrive_expect_tx(&bars->q_full, nq * kQkTileBytes);
+        for (int t = 0; t < nq; ++t)
+          for (int a = 0; a < kQkAtoms; ++a)
+            tma_load_2d(sq + t * kQkTileBytes + a * (kQkTileBytes / kQkAtoms), &tm_q, &bars->q_full,
+                        col0 + a * 64, q_row0 + t * kFaTile);
+      }
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kStages;
         const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
+        int bt, valid, seg;
+        fa_key_tile(p, j, bt, valid, seg);
+        if (p.seg_mode && j % p.tiles_per_seg == 0 && !wait_segment(seg)) { ok = false; break; }
         if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&bars->k_full[s], kQkTileBytes);
         for (int a = 0; a < kQkAtoms; ++a)
           tma_load_2d(sk + s * kQkTileBytes + a * (kQkTileBytes / kQkAtoms), &tm_k, &bars->k_full[s],
-                      col0 + a * 64, k_row0 + j * kFaTile);
+                      col0 + a * 64, k_row0 + bt * kFaTile);
         if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&bars->v_full[s], kVTileBytes);
-        tma_load_2d(sv + s * kVTileBytes, &tm_vt, &bars->v_full[s], j * kFaTile, vt_row0);
-        tma_load_2d(sv + s * kVTileBytes + kVTileBytes / 2, &tm_vt, &bars->v_full[s], j * kFaTile + 64, vt_row0);
+        tma_load_2d(sv + s * kVTileBytes, &tm_vt, &bars->v_full[s], bt * kFaTile, vt_row0);
+        tma_load_2d(sv + s * kVTileBytes + kVTileBytes / 2, &tm_vt, &bars->v_full[s], bt * kFaTile + 64, vt_row0);
       }
       if (!ok) report_status(p.status, kWaitTimeout, kKernelAttnPrefill, 21, blockIdx.x);
     }
@@ -216,22 +261,27 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
     const int q_idx = qt2 * 2 * kFaTile + t * kFaTile + row;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t s_col = lane_base + t * 128, o_col = lane_base + 256 + t * 128;
+    // position of the row inside its query segment (a plain call has one segment of sq rows)
+    const int q_seg = p.seg_mode ? q_idx / p.seg_pad : 0;
+    const int q_local = q_idx - q_seg * p.seg_pad;
+    const bool q_valid = p.seg_mode ? q_local < p.seg_len : q_idx < p.sq;
     if (t == 0 || tile1) {
       float m_run = -INFINITY, l_run = 0.f;
       float qs = p.scale_log2;
-      if (kI8)
-        qs *= q_idx < p.sq ? p.q_scale[static_cast<long long>(b * p.heads + head) * p.sq_pad + q_idx] : 0.f;
       bool ok = true;
       const float* ksc = kI8 ? p.k_scale + static_cast<long long>(b * p.heads + head) * n_tiles : nullptr;
-      float ks_next = kI8 ? ksc[0] : 1.f;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        // scores -> exp2 domain: x = raw * c (bf16: c = scale; int8: c = q row scale * K tile scale * scale)
-        const float c = qs * ks_next;
-        if (kI8 && j + 1 < n_tiles) ks_next = ksc[j + 1];
+        int bt, valid, seg;
+        fa_key_tile(p, j, bt, valid, seg);
         if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full[t], j & 1, abort_flag))) { ok = false; break; }
         tc_fence_after_sync();
-        const int key0 = j * kFaTile;
-        const bool tail = key0 + kFaTile > p.sk;
+        // scores -> exp2 domain: x = raw * c (bf16: c = scale; int8: c = q row scale * K tile scale * scale).
+        // Both scales are read past the wait and around L1: in a segmented call a peer wrote them, and
+        // they arrive with the segment.
+        if (kI8 && j == 0)
+          qs *= q_valid ? __ldcg(p.q_scale + static_cast<long long>(b * p.heads + head) * p.sq_pad + q_idx) : 0.f;
+        const float c = kI8 ? qs * __ldcg(ksc + bt) : qs;
+        const bool tail = valid < kFaTile;
         // the whole raw S row of this thread: four loads in flight, one wait
         uint32_t r[128];
 #pragma unroll
@@ -241,7 +291,7 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
           // keys past the end: the most negative value the exponent path below maps far below any maximum
 #pragma unroll
           for (int i = 0; i < 128; ++i)
-            if (key0 + i >= p.sk) r[i] = kI8 ? static_cast<uint32_t>(-(1 << 22)) : 0xff800000u;
+            if (i >= valid) r[i] = kI8 ? static_cast<uint32_t>(-(1 << 22)) : 0xff800000u;
         }
         float mx;
         if (kI8) {
@@ -313,13 +363,15 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
       } else {
         tc_fence_after_sync();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* dst = p.out + static_cast<long long>(q_row0 + t * kFaTile + row) * p.ld_out + col0;
+        __nv_bfloat16* dst = p.seg_mode
+            ? p.out_seg[q_valid ? q_seg : 0] + static_cast<long long>(q_local) * p.ld_out + p.out_col0 + col0
+            : p.out + static_cast<long long>(q_row0 + t * kFaTile + row) * p.ld_out + col0;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(o_col + c * 32, r);
           tmem_ld_wait();
-          if (q_idx < p.sq) {
+          if (q_valid) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 v;
@@ -331,6 +383,7 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
             }
           }
         }
+        if (p.seg_mode) __threadfence_system();    // the rows went to peers: order them before the count below
       }
     }
   }
@@ -340,6 +393,16 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
+  }
+  if (p.done_ctr != nullptr && threadIdx.x == 0) {
+    // the last CTA of the launch tells every rank that this rank's share of its output is there
+    __threadfence();
+    const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+    if (atomicAdd(p.done_ctr, 1u) == total - 1) {
+      atomicExch(p.done_ctr, 0u);
+      fence_acq_rel_sys();
+      for (int s = 0; s < p.nseg; ++s) red_relaxed_sys_add(p.done_flags[s], 1u);
+    }
   }
 }
 
@@ -474,6 +537,225 @@ __global__ void __launch_bounds__(256) sage_quant_k_tiles_kernel(const __nv_bflo
   }
 }
 
+
+// ---- Ulysses exchange fused around the attention kernel ------------------------------------------
+// Sequence parallelism: every rank holds `s_l` tokens of all heads and needs all tokens of its
+// heads / world heads. Instead of three all-to-all collectives in front of the attention and one
+// behind it, the quantisation kernel below stores its results straight into the destination rank's
+// operand buffers (ordinary 16-byte peer stores into the symmetric heap) and raises one arrival
+// counter per (destination, source); the attention kernel starts with its own segment, waits per
+// segment for the others, and stores its output rows into the owning rank's output buffer. One
+// tiny kernel in front of the consumer waits for the `world` output shares.
+// Replaces the reference's exchange of K / V through a host-side rendezvous
+// (src/HartsyInference.Diffusion/Utilities/CpKvExchange.cs:48-135, called from
+// Models/Denoisers/DiTBlocks/WanVideoBlock.cs:193-195).
+//
+// Flag words of one rank (cumulative counters, one exchange adds one): [0, 8) operand segment of
+// source s has arrived; [8, 16) K column sums of source s have arrived; [16] output shares.
+constexpr int kUlyFlagArrive = 0, kUlyFlagKsum = 8, kUlyFlagDone = 16, kUlyFlagWords = 32;
+
+struct UlyPush {
+  const __nv_bfloat16* q;      // local [s_l][heads * 128]
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  int s_l, s_pad, heads, hl, rank, world;
+  void* qbuf[8];               // rank d's Q operand [world * s_pad][hl * 128] (int8 or bf16)
+  void* kbuf[8];
+  __nv_bfloat16* vtbuf[8];     // rank d's V^T [hl * 128][world * s_pad]
+  float* qscale[8];            // rank d's [hl][world * s_pad]
+  float* kscale[8];            // rank d's [hl][world * tiles]
+  const float* ksum_in;        // local [world][heads][128]: every rank's K column sums
+  const uint32_t* flags_local;
+  uint32_t* flags[8];          // rank d's flag words
+  uint32_t* ctr;               // CTAs of this launch that have finished
+  uint32_t target;
+  float inv_total;             // 1 / (tokens of the whole sequence)
+  long long wait_budget;
+  DeviceStatus* status;
+};
+
+// Local column sums [heads][128] -> every rank's ksum_in[rank], then one arrival per destination.
+struct UlyTabs {
+  float* ksum_in[8];
+  uint32_t* flags[8];
+};
+__global__ void __launch_bounds__(1024) uly_ksum_push_kernel(const float* __restrict__ ksum_local, const UlyTabs tabs, int n,
+                                                             int rank, int world) {
+  for (int d = 0; d < world; ++d) {
+    float* dst = tabs.ksum_in[d] + static_cast<long long>(rank) * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = ksum_local[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fence_acq_rel_sys();
+    for (int d = 0; d < world; ++d) red_relaxed_sys_add(tabs.flags[d] + kUlyFlagKsum + rank, 1u);
+  }
+}
+
+// grid (token tiles of 128, heads), 256 threads: thread (row, half) owns 64 dims of one token.
+template <bool kI8>
+__global__ void __launch_bounds__(256) uly_push_kernel(const UlyPush p) {
+  __shared__ float mean[kFaD];
+  __shared__ float wmax[8];
+  __shared__ int wait_ok;
+  __shared__ __align__(16) __nv_bfloat16 vtile[kFaTile][kFaD + 8];
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int dst = head / p.hl, hi = head - dst * p.hl;
+  const int row = threadIdx.x >> 1, d0 = (threadIdx.x & 1) * 64;
+  const int tok = tile * kFaTile + row;
+  const bool valid = tok < p.s_l;
+  const long long ld_in = static_cast<long long>(p.heads) * kFaD;
+  const long long ld_out = static_cast<long long>(p.hl) * kFaD;
+  const long long seg_row = static_cast<long long>(p.rank) * p.s_pad + tok;     // row in the destination buffers
+  const int tiles = p.s_pad / kFaTile;
+
+  if (kI8) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      for (int s = 0; s < p.world && ok; ++s)
+        ok = wait_flag_geq(p.flags_local + kUlyFlagKsum + s, p.target, p.wait_budget) ? 1 : 0;
+      wait_ok = ok;
+      if (!ok) report_status(p.status, kWaitTimeout, kKernelAllToAll, 1, blockIdx.x);
+    }
+    __syncthreads();
+    if (threadIdx.x < kFaD) {
+      float acc = 0.f;
+      if (wait_ok)
+        for (int s = 0; s < p.world; ++s)
+          acc += __ldcg(p.ksum_in + (static_cast<long long>(s) * p.heads + head) * kFaD + threadIdx.x);
+      mean[threadIdx.x] = acc * p.inv_total;
+    }
+    __syncthreads();
+  }
+
+  auto load64 = [&](const __nv_bfloat16* src, float (&out)[64]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + i * 8);
+      const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 f = __bfloat1622float2(hp[u]);
+        out[i * 8 + 2 * u] = f.x;
+        out[i * 8 + 2 * u + 1] = f.y;
+      }
+    }
+  };
+  auto store_q8 = [&](int8_t* dstp, const float (&v)[64], float inv) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 q;
+      uint32_t* qw = reinterpret_cast<uint32_t*>(&q);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int iv = max(-127, min(127, __float2int_rn(v[i * 16 + w * 4 + e] * inv)));
+          word |= static_cast<uint32_t>(static_cast<uint8_t>(static_cast<int8_t>(iv))) << (8 * e);
+        }
+        qw[w] = word;
+      }
+      *reinterpret_cast<uint4*>(dstp + i * 16) = q;
+    }
+  };
+
+  // ---- Q: one scale per row
+  if (kI8) {
+    float v[64];
+    float amax = 0.f;
+    if (valid) {
+      load64(p.q + static_cast<long long>(tok) * ld_in + head * kFaD + d0, v);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const float sc = fmaxf(amax, 1e-12f) / 127.f;
+    if (valid) {
+      store_q8(static_cast<int8_t*>(p.qbuf[dst]) + seg_row * ld_out + hi * kFaD + d0, v, 1.f / sc);
+      if (d0 == 0) p.qscale[dst][static_cast<long long>(hi) * p.world * p.s_pad + seg_row] = sc;
+    }
+  } else if (valid) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.q + static_cast<long long>(tok) * ld_in + head * kFaD + d0);
+    uint4* out = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.qbuf[dst]) + seg_row * ld_out + hi * kFaD + d0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = src[i];
+  }
+
+  // ---- K: mean removed, one scale per tile of 128 keys
+  if (kI8) {
+    float v[64];
+    float amax = 0.f;
+    if (valid) {
+      load64(p.k + static_cast<long long>(tok) * ld_in + head * kFaD + d0, v);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        v[i] -= mean[d0 + i];
+        amax = fmaxf(amax, fabsf(v[i]));
+      }
+    }
+    amax = warp_max(amax);
+    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = wmax[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, wmax[i]);
+    const float sc = fmaxf(amax, 1e-12f) / 127.f;
+    if (threadIdx.x == 0) p.kscale[dst][static_cast<long long>(hi) * p.world * tiles + p.rank * tiles + tile] = sc;
+    if (valid) store_q8(static_cast<int8_t*>(p.kbuf[dst]) + seg_row * ld_out + hi * kFaD + d0, v, 1.f / sc);
+  } else if (valid) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.k + static_cast<long long>(tok) * ld_in + head * kFaD + d0);
+    uint4* out = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.kbuf[dst]) + seg_row * ld_out + hi * kFaD + d0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = src[i];
+  }
+
+  // ---- V: transposed through shared memory; rows past the end become zeros
+  {
+    uint4* srow = reinterpret_cast<uint4*>(&vtile[row][d0]);
+    if (valid) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.v + static_cast<long long>(tok) * ld_in + head * kFaD + d0);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) srow[i] = src[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) srow[i] = make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+    // thread (dim, half) writes 64 consecutive tokens of one dim
+    const int dim = threadIdx.x >> 1, t0 = (threadIdx.x & 1) * 64;
+    __nv_bfloat16* out = p.vtbuf[dst] + (static_cast<long long>(hi) * kFaD + dim) * p.world * p.s_pad +
+                         static_cast<long long>(p.rank) * p.s_pad + tile * kFaTile + t0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint4 o;
+      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) e[u] = vtile[t0 + i * 8 + u][dim];
+      *reinterpret_cast<uint4*>(out + i * 8) = o;
+    }
+  }
+
+  // ---- arrival: the last CTA of the launch adds one to this rank's slot on every destination
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned total = gridDim.x * gridDim.y;
+    if (atomicAdd(p.ctr, 1u) == total - 1) {
+      atomicExch(p.ctr, 0u);
+      fence_acq_rel_sys();
+      for (int d = 0; d < p.world; ++d) red_relaxed_sys_add(p.flags[d] + kUlyFlagArrive + p.rank, 1u);
+    }
+  }
+}
+
+// One thread waits until *flag >= target, or reports that the wait ran out.
+__global__ void flag_wait_kernel(const uint32_t* flag, uint32_t target, long long budget, DeviceStatus* status,
+                                 uint32_t kernel_id, uint32_t site) {
+  if (threadIdx.x == 0 && !wait_flag_geq(flag, target, budget)) report_status(status, kWaitTimeout, kernel_id, site, 0);
+}
 }  // namespace b200
 
 namespace b200 {
@@ -485,6 +767,8 @@ int make_kmajor_map(CUtensorMap* out, const void* base, int elem_bytes, long lon
 using namespace b200;
 
 static inline int fa_pad(int s, int to) { return (s + to - 1) / to * to; }
+static int fa_launch(const FaParams& p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, dim3 grid,
+                     int int8, cudaStream_t stream);
 
 // Scratch layout of one call: V^T [batch * heads * 128][sk_pad64] bf16, then (int8 mode) Q8
 // [batch * sq][heads * 128], K8 [batch * sk][heads * 128], q scales [batch * heads][sq_pad128],
@@ -533,6 +817,11 @@ B200_API int b200_attn_fa(const void* q, const void* k, const void* v, void* out
   p.sq = sq; p.sk = sk; p.heads = heads; p.batch = batch;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = static_cast<DeviceStatus*>(status);
+  p.n_tiles = fa_pad(sk, 128) / 128;
+  p.tiles_per_seg = p.n_tiles;
+  p.nseg = 1;
+  p.seg_len = sk;
+  p.seg_pad = p.n_tiles * 128;
   CUtensorMap tq, tk, tv;
   int rc;
   if (int8) {
@@ -564,11 +853,15 @@ B200_API int b200_attn_fa(const void* q, const void* k, const void* v, void* out
   }
   rc = make_kmajor_map(&tv, base + sc.vt, 2, static_cast<long long>(batch) * heads * kFaD, sk_pad64, sk_pad64, 128);
   if (rc) return rc;
+  return fa_launch(p, tq, tk, tv, dim3((sq + 2 * kFaTile - 1) / (2 * kFaTile), heads, batch), int8, stream);
+}
+
+static int fa_launch(const FaParams& p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, dim3 grid,
+                     int int8, cudaStream_t stream) {
   const int qk_tile = int8 ? 128 * 128 : 128 * 128 * 2;
   const int stages = int8 ? 3 : 2;
   const int smem = 2 * qk_tile + stages * (qk_tile + 128 * 128 * 2) + static_cast<int>(sizeof(FaBarriers)) + 1024;
   static PerDeviceOnce configured[2];
-  dim3 grid((sq + 2 * kFaTile - 1) / (2 * kFaTile), heads, batch);
   if (int8) {
     if (configured[1].first_time() &&
         cudaFuncSetAttribute(attn_fa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -580,5 +873,145 @@ B200_API int b200_attn_fa(const void* q, const void* k, const void* v, void* out
       return -4;
     attn_fa_kernel<false><<<grid, kFaThreads, smem, stream>>>(p, tq, tk, tv);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -300;
+  const cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? 0 : -(1000 + static_cast<int>(err));   // the CUDA error number stays readable
+}
+
+// ---- host side of the fused exchange --------------------------------------------------------------
+// Bytes of one rank's exchange region, and where its parts sit (the same on every rank).
+struct UlyLayout {
+  long long flags, ctr, ksum_in, ksum_local, qbuf, kbuf, vtbuf, qscale, kscale, out, total;
+};
+static UlyLayout uly_layout(int s_l, int heads, int world, int int8) {
+  UlyLayout l{};
+  auto up = [](long long v) { return (v + 1023) / 1024 * 1024; };
+  const int s_pad = fa_pad(s_l, 128), hl = heads / world;
+  const long long rows = static_cast<long long>(world) * s_pad;
+  long long off = 0;
+  l.flags = off; off = up(off + kUlyFlagWords * 4);
+  l.ctr = off; off = up(off + 64);
+  l.ksum_in = off; off = up(off + static_cast<long long>(world) * heads * kFaD * 4);
+  l.ksum_local = off; off = up(off + static_cast<long long>(heads) * kFaD * 4);
+  l.qbuf = off; off = up(off + rows * hl * kFaD * (int8 ? 1 : 2));
+  l.kbuf = off; off = up(off + rows * hl * kFaD * (int8 ? 1 : 2));
+  l.vtbuf = off; off = up(off + rows * hl * kFaD * 2);
+  l.qscale = off; off = up(off + static_cast<long long>(hl) * rows * 4);
+  l.kscale = off; off = up(off + static_cast<long long>(hl) * (rows / 128) * 4);
+  l.out = off; off = up(off + static_cast<long long>(s_pad) * heads * kFaD * 2);
+  l.total = off;
+  return l;
+}
+
+B200_API long long b200_ulysses_region_bytes(int s_l, int heads, int world, int int8) {
+  if (world <= 0 || world > 8 || heads % world != 0) return -1;
+  return uly_layout(s_l, heads, world, int8).total;
+}
+// Offset of the output [s_l][heads * 128] bf16 inside the region (the caller reads it after
+// b200_ulysses_wait_outputs).
+B200_API long long b200_ulysses_out_offset(int s_l, int heads, int world, int int8) {
+  return uly_layout(s_l, heads, world, int8).out;
+}
+
+// One exchange + attention on this rank. q, k, v: local [s_l][heads * 128] bf16. `regions`: the base
+// address of every rank's region in this process's address space (entry `rank` is local); regions
+// must have been zeroed once. `epoch`: 1 for the first call on these regions, then 2, 3 ... (the
+// same on every rank). The output lands in every rank's region at b200_ulysses_out_offset.
+// `phases` selects the steps (bits: 1 K column sums, 2 operand push, 4 attention, 8 wait for the
+// outputs); a rank passes 15. Tests that play every rank on one GPU run each phase for all ranks
+// before the next one, so that no kernel ever waits for a later launch.
+B200_API int b200_ulysses_attention(const void* q, const void* k, const void* v, void* const* regions, int s_l, int heads,
+                                    int rank, int world, float scale, int int8, unsigned epoch, int phases,
+                                    long long wait_budget_cycles, void* status, cudaStream_t stream) {
+  if (world <= 0 || world > 8 || heads % world != 0 || s_l <= 0) return -2;
+  const UlyLayout l = uly_layout(s_l, heads, world, int8);
+  const int s_pad = fa_pad(s_l, 128), hl = heads / world, tiles = s_pad / 128;
+  const long long rows = static_cast<long long>(world) * s_pad;
+  uint8_t* mine = static_cast<uint8_t*>(regions[rank]);
+  const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
+
+  UlyPush u{};
+  u.q = static_cast<const __nv_bfloat16*>(q);
+  u.k = static_cast<const __nv_bfloat16*>(k);
+  u.v = static_cast<const __nv_bfloat16*>(v);
+  u.s_l = s_l; u.s_pad = s_pad; u.heads = heads; u.hl = hl; u.rank = rank; u.world = world;
+  for (int d = 0; d < world; ++d) {
+    uint8_t* r = static_cast<uint8_t*>(regions[d]);
+    u.qbuf[d] = r + l.qbuf;
+    u.kbuf[d] = r + l.kbuf;
+    u.vtbuf[d] = reinterpret_cast<__nv_bfloat16*>(r + l.vtbuf);
+    u.qscale[d] = reinterpret_cast<float*>(r + l.qscale);
+    u.kscale[d] = reinterpret_cast<float*>(r + l.kscale);
+    u.flags[d] = reinterpret_cast<uint32_t*>(r + l.flags);
+  }
+  u.ksum_in = reinterpret_cast<const float*>(mine + l.ksum_in);
+  u.flags_local = reinterpret_cast<const uint32_t*>(mine + l.flags);
+  u.ctr = reinterpret_cast<uint32_t*>(mine + l.ctr);
+  u.target = epoch;
+  u.inv_total = 1.f / (static_cast<float>(s_l) * world);
+  u.wait_budget = budget;
+  u.status = static_cast<DeviceStatus*>(status);
+
+  if (int8 && (phases & 1)) {
+    float* ksum_local = reinterpret_cast<float*>(mine + l.ksum_local);
+    const int n = heads * kFaD;
+    if (cudaMemsetAsync(ksum_local, 0, static_cast<size_t>(n) * 4, stream) != cudaSuccess) return -3;
+    sage_k_sum_kernel<<<dim3((s_l + 255) / 256, heads), 128, 0, stream>>>(u.k, ksum_local, static_cast<long long>(heads) * kFaD,
+                                                                         s_l, heads);
+    UlyTabs tabs{};
+    for (int d = 0; d < world; ++d) {
+      tabs.ksum_in[d] = reinterpret_cast<float*>(static_cast<uint8_t*>(regions[d]) + l.ksum_in);
+      tabs.flags[d] = u.flags[d];
+    }
+    uly_ksum_push_kernel<<<1, 1024, 0, stream>>>(ksum_local, tabs, n, rank, world);
+  }
+  if (phases & 2) {
+    if (int8) uly_push_kernel<true><<<dim3(tiles, heads), 256, 0, stream>>>(u);
+    else uly_push_kernel<false><<<dim3(tiles, heads), 256, 0, stream>>>(u);
+  }
+  if (cudaGetLastError() != cudaSuccess) return -5;
+  if ((phases & 12) == 0) return 0;
+
+  FaParams p{};
+  p.ld_out = static_cast<long long>(heads) * kFaD;
+  p.sq = static_cast<int>(rows); p.sk = static_cast<int>(rows); p.heads = hl; p.batch = 1;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = static_cast<DeviceStatus*>(status);
+  p.q_scale = reinterpret_cast<const float*>(mine + l.qscale);
+  p.k_scale = reinterpret_cast<const float*>(mine + l.kscale);
+  p.sq_pad = static_cast<int>(rows);
+  p.n_tiles = world * tiles;
+  p.tiles_per_seg = tiles;
+  p.nseg = world;
+  p.seg_len = s_l;
+  p.seg_first = rank;
+  p.seg_pad = s_pad;
+  p.seg_mode = 1;
+  p.seg_flags = reinterpret_cast<const uint32_t*>(mine + l.flags) + kUlyFlagArrive;
+  p.seg_target = epoch;
+  p.wait_budget = budget;
+  p.out_col0 = static_cast<long long>(rank) * hl * kFaD;
+  for (int d = 0; d < world; ++d) {
+    uint8_t* r = static_cast<uint8_t*>(regions[d]);
+    p.out_seg[d] = reinterpret_cast<__nv_bfloat16*>(r + l.out);
+    p.done_flags[d] = reinterpret_cast<uint32_t*>(r + l.flags) + kUlyFlagDone;
+  }
+  p.done_ctr = reinterpret_cast<uint32_t*>(mine + l.ctr) + 4;
+  CUtensorMap tq, tk, tv;
+  const int eb = int8 ? 1 : 2;
+  int rc = make_kmajor_map(&tq, mine + l.qbuf, eb, rows, static_cast<long long>(hl) * kFaD, static_cast<long long>(hl) * kFaD, 128);
+  if (rc) return rc;
+  rc = make_kmajor_map(&tk, mine + l.kbuf, eb, rows, static_cast<long long>(hl) * kFaD, static_cast<long long>(hl) * kFaD, 128);
+  if (rc) return rc;
+  rc = make_kmajor_map(&tv, mine + l.vtbuf, 2, static_cast<long long>(hl) * kFaD, rows, rows, 128);
+  if (rc) return rc;
+  if (phases & 4) {
+    rc = fa_launch(p, tq, tk, tv, dim3(static_cast<unsigned>((rows + 2 * kFaTile - 1) / (2 * kFaTile)), hl, 1), int8, stream);
+    if (rc) return rc;
+  }
+  if (phases & 8)
+    flag_wait_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint32_t*>(mine + l.flags) + kUlyFlagDone,
+                                         epoch * static_cast<unsigned>(world), budget, static_cast<DeviceStatus*>(status),
+                                         kKernelAllToAll, 2);
+  const cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? 0 : -(1000 + static_cast<int>(err));
 }

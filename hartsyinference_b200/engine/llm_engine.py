@@ -101,6 +101,7 @@ class LLMEngine:
         self.kernel_launches_last = 0
         self.time_steps = False          # record device time of every step with CUDA events
         self.device_ms_last = 0.0
+        self.step_log = None             # a list: every step appends (wall clock at its end, device ms, kernel launches, H2D bytes, D2H bytes, events)
         self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) if self.cuda else None
         pin = self.cuda
         mp = self.max_pages_per_seq
@@ -507,6 +508,9 @@ class LLMEngine:
             self._ev[1].record()
             self._ev[1].synchronize()
             self.device_ms_last = self._ev[0].elapsed_time(self._ev[1])
+        if self.step_log is not None:
+            self.step_log.append((time.perf_counter(), self.device_ms_last, self.kernel_launches_last, self.h2d_bytes_last,
+                                  self.d2h_bytes_last, len(events)))
         return events
 
     def run_until_done(self, max_steps: int = 1 << 30) -> None:

@@ -74,6 +74,8 @@ class EngineOptions:
 class TextRequest:
     messages: list[dict] = field(default_factory=list)
     prompt: Optional[str] = None         # raw prompt (bypasses the chat template)
+    prompt_token_ids: Optional[list[int]] = None   # already tokenised prompt (bypasses template and tokenizer)
+    ignore_eos: bool = False             # keep generating up to max_tokens (throughput measurements)
     temperature: float = 0.7
     top_p: float = 0.95
     top_k: int = 0

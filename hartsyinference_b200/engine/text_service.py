@@ -258,13 +258,15 @@ class TextService:
             mask = grammar.allowed_mask
         return SamplingParams(temperature=req.temperature, top_p=req.top_p, top_k=req.top_k, min_p=req.min_p,
                               repetition_penalty=req.repetition_penalty, max_tokens=req.max_tokens, seed=req.seed,
-                              greedy=req.greedy, logits_mask=mask)
+                              greedy=req.greedy, logits_mask=mask, ignore_eos=req.ignore_eos)
 
     def count_tokens(self, spec: ModelSpec, req: TextRequest) -> int:
         h = self._host(spec)
         return len(self._prompt_ids(h.llm, req))
 
     def _prompt_ids(self, llm: LoadedLLM, req: TextRequest) -> list[int]:
+        if req.prompt_token_ids is not None:
+            return [int(t) for t in req.prompt_token_ids]
         if req.prompt is not None:
             text, special = req.prompt, True
         else:

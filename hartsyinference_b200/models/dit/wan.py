@@ -22,7 +22,7 @@ from typing import Callable, Optional
 
 import torch
 
-from ... import ops
+from ... import config, log, ops
 from ...ops import LinearWeight
 from ...parallel.comm import Comm, SingleComm
 from .common import WeightFactory, rope_tables, silu, timestep_embedding
@@ -110,6 +110,8 @@ class WanTransformer:
         # are and every rank gathers all keys / values (the reference's context-parallel exchange,
         # src/HartsyInference.Diffusion/Utilities/CpKvExchange.cs:48, CpSequencePlan.cs:38)
         self.ulysses = cfg.num_heads % self.sp == 0
+        self._fused_exchange = {}        # local token count -> FusedUlyssesAttention
+        self.exchange_path = "none" if self.sp == 1 else "nccl all-to-all" if self.ulysses else "nccl all-gather of K / V"
         H = cfg.hidden_size
         f = WeightFactory(self.device, fp8, 0, 1, get, seed)
         self.fp8 = fp8 and self.device.type == "cuda"
@@ -157,6 +159,27 @@ class WanTransformer:
         a = min(total_tokens, self.sp_rank * per)
         return a, min(total_tokens, a + per)
 
+    def _fused(self, s_l: int, heads: int, d: int):
+        """The exchange fused into the attention kernels (parallel/ulysses.py) for this shape, or
+        None when it does not apply (CPU ranks, head dim other than 128, flag off, no peer access)."""
+        if self.device.type != "cuda" or d != 128 or not config.get("fused_ulysses"):
+            return None
+        if s_l not in self._fused_exchange:
+            from ...parallel.ulysses import FusedUlyssesAttention
+            try:
+                self._fused_exchange[s_l] = FusedUlyssesAttention(self.comm, s_l, heads, self.device)
+                self.exchange_path = "peer stores from the quantisation kernel into the attention kernel's operand buffers"
+            except Exception as e:      # no peer mapping between these GPUs: keep the collective form
+                log.warn(f"[SequenceParallel] fused exchange unavailable ({type(e).__name__}: {e}); using NCCL all-to-all")
+                self._fused_exchange[s_l] = None
+        return self._fused_exchange[s_l]
+
+    def close(self) -> None:
+        for f in self._fused_exchange.values():
+            if f is not None:
+                f.close()
+        self._fused_exchange.clear()
+
     def _self_attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
         """q, k, v [S_local, heads, D] -> [S_local, heads * D]."""
         if self.sp == 1:
@@ -167,6 +190,9 @@ class WanTransformer:
             vf = self.comm.all_gather(v.contiguous(), dim=0)
             o = ops.attention(q.contiguous(), kf, vf)
             return o.reshape(o.shape[0], -1)
+        fused = self._fused(q.shape[0], q.shape[1], q.shape[2])
+        if fused is not None:
+            return fused(q.contiguous(), k.contiguous(), v.contiguous())
         a2a = self.comm.all_to_all
         qf, kf, vf = (a2a(t, split_dim=1, concat_dim=0) for t in (q, k, v))      # [S, heads / sp, D]
         o = ops.attention(qf.contiguous(), kf.contiguous(), vf.contiguous())

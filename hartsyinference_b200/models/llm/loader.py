@@ -95,6 +95,8 @@ def _gemma_sandwich_fix(cfg: TransformerConfig, get: Callable[[str], Optional[to
 
 def load_llm(path: str | Path, device: str | torch.device = "cuda", comm: Optional[Comm] = None,
              fp8: Optional[bool] = None) -> LoadedLLM:
+    if str(path).startswith("synthetic:"):
+        return _load_synthetic(str(path)[len("synthetic:"):], device, comm, fp8)
     p = Path(path)
     if p.is_file() and p.suffix == ".gguf":
         return _load_gguf(p, device, comm, fp8)
@@ -105,6 +107,28 @@ def load_llm(path: str | Path, device: str | torch.device = "cuda", comm: Option
         if ggufs:
             return _load_gguf(ggufs[0], device, comm, fp8)
     raise UnsupportedModelError(f"{path}: neither a .gguf file nor a directory with config.json")
+
+
+def _load_synthetic(spec: str, device, comm: Optional[Comm], fp8: Optional[bool]) -> LoadedLLM:
+    """``synthetic:<preset>[:layers=N]``: the named architecture with random-init weights (seed 0)
+    and a byte tokenizer padded to the vocabulary size. For benchmarks and smoke tests of the
+    serving stack where no checkpoint is at hand; prompts are best passed as token ids."""
+    from ...assets.tokenizer import ByteTokenizer
+    from .config import PRESETS
+    name, *mods = spec.split(":")
+    if name not in PRESETS:
+        raise UnsupportedModelError(f"synthetic:{name}: unknown preset (known: {sorted(PRESETS)})")
+    cfg = PRESETS[name]
+    for m in mods:
+        k, _, v = m.partition("=")
+        if k == "layers":
+            from dataclasses import replace
+            cfg = replace(cfg, num_layers=int(v))
+        else:
+            raise UnsupportedModelError(f"synthetic:{spec}: unknown modifier {k!r}")
+    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
+    model.random_init(seed=0)
+    return LoadedLLM(model, ByteTokenizer(vocab_size=cfg.vocab_size), ChatTemplate.for_arch(cfg.arch), cfg, f"synthetic:{spec}")
 
 
 def _want_fp8(fp8: Optional[bool], device) -> bool:

@@ -112,6 +112,25 @@ def main():
             assert (z.cpu() - want).abs().max() < 1e-5, (it, (z.cpu() - want).abs().max())
             z0 = want
         fc.close()
+    # ---- sequence-parallel attention with the exchange fused into the kernels, vs fp32 over the full sequence
+    from hartsyinference_b200.parallel.ulysses import FusedUlyssesAttention
+    heads = 2 * world
+    for int8 in (False, True):
+        for s_l in (192, 100):
+            gen = torch.Generator(device="cpu").manual_seed(11 + s_l)
+            q, k, v = (torch.randn(world * s_l, heads, 128, generator=gen).to(torch.bfloat16).to(dev) for _ in range(3))   # same on all ranks
+            sc = torch.einsum("qhd,khd->hqk", q.float(), k.float()) * 128 ** -0.5
+            want = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v.float()).reshape(world * s_l, -1)
+            fu = FusedUlyssesAttention(comm, s_l, heads, dev, int8=int8)
+            mine = slice(rank * s_l, (rank + 1) * s_l)
+            for it in range(3):
+                got = fu(q[mine].contiguous(), k[mine].contiguous(), v[mine].contiguous()).clone()
+                N.check_status(dev)
+                assert rel(got, want[mine]) < (0.06 if int8 else 0.02), ("ulysses", int8, s_l, it, rel(got, want[mine]))
+            comm.barrier()
+            fu.close()
+    if rank == 0:
+        print("ULYSSES_OK", flush=True)
     # ---- TP model vs single-GPU model
     cfg = C.tiny("llama-3-70b", vocab_size=1024, hidden_size=512, num_layers=2, num_heads=8, num_kv_heads=2,
                  head_dim=128, ffn_size=1024)

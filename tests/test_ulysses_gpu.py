@@ -1,0 +1,117 @@
+"""Sequence-parallel attention with the exchange fused into the kernels (parallel/ulysses.py,
+csrc/kernels/attention_fa.cu). Oracle: fp32 softmax attention over the whole sequence.
+
+On one GPU several ranks are played in turn, phase by phase (all K sums, then all operand pushes,
+then all attentions, then all output waits), so every flag a kernel waits for has been raised by a
+kernel that already finished; the real multi-GPU run is in mp_fused_tp_worker.py.
+"""
+import ctypes as C
+import math
+
+import pytest
+import torch
+
+from hartsyinference_b200.exceptions import DeviceWaitTimeout
+from hartsyinference_b200.ops import _native as N
+from hartsyinference_b200.parallel.comm import SingleComm
+from hartsyinference_b200.parallel.ulysses import FusedUlyssesAttention
+
+
+def _oracle(q, k, v):
+    """q, k, v [S, heads, 128] -> [S, heads * 128] fp32."""
+    s = torch.einsum("qhd,khd->hqk", q.float(), k.float()) / math.sqrt(q.shape[-1])
+    o = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v.float())
+    return o.reshape(o.shape[0], -1)
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm())
+
+
+def _inputs(s, heads, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(s, heads, 128, device="cuda", generator=g).to(torch.bfloat16)
+    # keys with a common offset, the case the mean removal of the int8 mode is for
+    k = (torch.randn(s, heads, 128, device="cuda", generator=g) + 0.7 * torch.randn(1, heads, 128, device="cuda", generator=g)).to(torch.bfloat16)
+    v = torch.randn(s, heads, 128, device="cuda", generator=g).to(torch.bfloat16)
+    return q, k, v
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("tokens", [128, 300])
+def test_one_rank_matches_fp32(int8, tokens):
+    q, k, v = _inputs(tokens, 2, 1)
+    f = FusedUlyssesAttention(SingleComm(), tokens, 2, int8=int8)
+    try:
+        want = _oracle(q, k, v)
+        for _ in range(2):                      # the second call reuses the buffers one epoch later
+            got = f(q, k, v).clone()
+            N.check_status()
+            assert _rel(got, want) < (0.06 if int8 else 0.02)
+    finally:
+        f.close()
+
+
+def _bind():
+    i32, i64, vp = C.c_int, C.c_longlong, C.c_void_p
+    size = N.bind("b200_ulysses_region_bytes", i64, [i32, i32, i32, i32])
+    out_off = N.bind("b200_ulysses_out_offset", i64, [i32, i32, i32, i32])
+    fn = N.bind("b200_ulysses_attention", i32, [vp, vp, vp, vp, i32, i32, i32, i32, C.c_float, i32, C.c_uint, i32, i64, vp, vp])
+    return size, out_off, fn
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("world,s_l,heads", [(2, 192, 4), (4, 100, 4), (2, 128, 2)])
+def test_ranks_played_in_turn_match_fp32(world, s_l, heads, int8):
+    size, out_off, fn = _bind()
+    nbytes = int(size(s_l, heads, world, int(int8)))
+    off = int(out_off(s_l, heads, world, int(int8)))
+    regions = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    table = (C.c_void_p * 8)()
+    for r in range(world):
+        table[r] = regions[r].data_ptr()
+    q, k, v = _inputs(world * s_l, heads, 3)
+    want = _oracle(q, k, v)
+    st = N.state(torch.device("cuda", torch.cuda.current_device()))
+    parts = [tuple(t[r * s_l:(r + 1) * s_l].contiguous() for t in (q, k, v)) for r in range(world)]
+    for epoch in (1, 2):
+        for phase in (1, 2, 4, 8):
+            for r in range(world):
+                qr, kr, vr = parts[r]
+                rc = fn(qr.data_ptr(), kr.data_ptr(), vr.data_ptr(), table, s_l, heads, r, world, 128 ** -0.5, int(int8), epoch,
+                        phase, 100_000_000, st.status.data_ptr(), N.stream())
+                assert rc == 0
+        N.check_status()
+        for r in range(world):
+            got = regions[r][off:off + s_l * heads * 128 * 2].view(torch.bfloat16).reshape(s_l, heads * 128)
+            assert _rel(got, want[r * s_l:(r + 1) * s_l]) < (0.06 if int8 else 0.02), (epoch, r)
+
+
+@pytest.mark.gpu
+def test_missing_peer_runs_out_and_reports():
+    """Rank 0 of two runs alone: its waits for rank 1's segment and for rank 1's output share give
+    up after about a millisecond each, the kernels return, and the status word says which wait."""
+    size, _, fn = _bind()
+    world, s_l, heads = 2, 128, 2
+    regions = [torch.zeros(int(size(s_l, heads, world, 0)), dtype=torch.uint8, device="cuda") for _ in range(world)]
+    table = (C.c_void_p * 8)()
+    for r in range(world):
+        table[r] = regions[r].data_ptr()
+    q, k, v = _inputs(s_l, heads, 5)
+    st = N.state(torch.device("cuda", torch.cuda.current_device()))
+    rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), table, s_l, heads, 0, world, 128 ** -0.5, 0, 1, 15, 2_000_000,
+            st.status.data_ptr(), N.stream())
+    assert rc == 0
+    with pytest.raises(DeviceWaitTimeout) as ei:
+        N.check_status()
+    assert ei.value.kernel in (4, 10)        # the attention kernel's segment wait, or the output wait
+    # the context is intact: a complete one-rank exchange works right afterwards
+    f = FusedUlyssesAttention(SingleComm(), s_l, heads, int8=False)
+    try:
+        got = f(q, k, v)
+        N.check_status()
+        assert _rel(got, _oracle(q, k, v)) < 0.02
+    finally:
+        f.close()
