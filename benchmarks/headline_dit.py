@@ -65,13 +65,15 @@ def flux_parity(comm, dev, fp8: bool) -> dict:
     g = torch.Generator().manual_seed(11)
     S = 256
     x = (torch.randn(1, S, cfg.in_channels, generator=g) * 0.5).to(torch.bfloat16).to(dev)
-    ctx = torch.randn(1, 64, cfg.context_dim, generator=g).to(torch.bfloat16).to(dev)
+    ctx = torch.randn(1, 192, cfg.context_dim, generator=g).to(torch.bfloat16).to(dev)
     pooled = torch.randn(1, cfg.pooled_dim, generator=g).to(torch.bfloat16).to(dev)
     from hartsyinference_b200.pipelines.flux import flux_ids
-    img_ids, txt_ids = flux_ids(16, 16, 64, dev)
+    img_ids, txt_ids = flux_ids(16, 16, 192, dev)
     sigma, gvec = torch.tensor([0.7], device=dev), torch.tensor([3.5], device=dev)
     tp = F.FluxTransformer(cfg, dev, comm=comm, fp8=fp8, seed=5)
     got = tp.forward(x, ctx, sigma, pooled, img_ids, txt_ids, gvec).float()
+    path = getattr(tp, "comm_path", "nccl")
+    tp.close()
     del tp
     cos = 1.0
     if comm.rank == 0:
@@ -82,7 +84,8 @@ def flux_parity(comm, dev, fp8: bool) -> dict:
     if comm.world > 1:
         comm.broadcast(c, 0)
     torch.cuda.empty_cache()
-    return {"ok": bool(c.item() > 0.99), "cos": float(c.item()), "what": f"1 double + 1 single block, tp{comm.world} vs tp1"}
+    return {"ok": bool(c.item() > 0.99), "cos": float(c.item()), "what": f"1 double + 1 single block, 256 image + 192 text tokens, tp{comm.world} vs tp1",
+            "path": path}
 
 
 def run_flux(args, comm, dev, sampler) -> dict:
@@ -116,6 +119,8 @@ def run_flux(args, comm, dev, sampler) -> dict:
     ms_step, e2e = _finish(pipe, io, warmup, steps, comm, dev, ctx.numel() * 4 + pooled.numel() * 4)
     from hartsyinference_b200.ops import _native as N
     N.check_status(dev)
+    comm_path = getattr(tr, "comm_path", "nccl") if comm.world > 1 else "none"
+    tr.close()
     S, H = 4096 + 512, cfg.hidden_size
     lin = cfg.num_double_blocks * (2 * S * H * (3 * H + H + 2 * cfg.mlp_dim)) + \
         cfg.num_single_blocks * (2 * S * H * (3 * H + cfg.mlp_dim) + 2 * S * (H + cfg.mlp_dim) * H)
@@ -129,7 +134,7 @@ def run_flux(args, comm, dev, sampler) -> dict:
         "config": {"model": "flux-dev", "global_batch": 1, "seq_len": S, "parallelism": f"tp{comm.world}",
                    "denoise_steps_of_the_workload": 20,
                    "l2": "inputs larger than L2 (12 GB of weights read per step)", "invalid_debug_overrides": invalid,
-                   "comm_path": "nccl" if comm.world > 1 else "none"},
+                   "comm_path": comm_path},
         "e2e": e2e, "gpu_launches": N.launch_count, "clocks": clocks, "parity": parity, "load_s": t_load,
         "flops_per_step": lin + att, "tflops_per_gpu": (lin + att) / (ms_step / 1e3) / 1e12 / comm.world,
         "weight_bytes_per_gpu": tr.weight_bytes(),
@@ -226,7 +231,7 @@ def run_wan(args, comm, dev, sampler) -> dict:
                    "attention": "bf16 tcgen05 flash attention",
                    "l2": "inputs larger than L2 (activations of 75600 tokens x 5120 alone are 774 MB)",
                    "invalid_debug_overrides": invalid,
-                   "comm_path": exchange + ("; CFG pair: all-gather of the two velocity fields (NCCL)" if cfg_comm is not None else "")},
+                   "comm_path": exchange + (f"; CFG pair: {getattr(pipe, 'cfg_path', 'all-gather of the two velocity fields (NCCL)')}" if cfg_comm is not None else "")},
         "e2e": e2e, "gpu_launches": N.launch_count, "clocks": clocks, "parity": parity, "load_s": t_load,
         "flops_per_step": flops, "tflops_per_gpu": flops / (ms_step / 1e3) / 1e12 / comm.world,
         "weight_bytes_per_gpu": tr.weight_bytes(),

@@ -184,6 +184,8 @@ struct CfgCombineArgs {
   long long n;
   int rank;                       // 0 = conditional branch, 1 = unconditional
   float guidance, dt;
+  int mode;                       // 0: z += v dt (Euler step); 1: z = v (the combined prediction, for any other scheduler)
+  int pred_f32;                   // the prediction slots hold fp32 instead of bf16
   long long wait_budget;
   DeviceStatus* status;
 };
@@ -206,18 +208,42 @@ __global__ void __launch_bounds__(256) cfg_combine_kernel(const CfgCombineArgs a
     const long long nvec = a.n >> 3;
     for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec;
          v += static_cast<long long>(gridDim.x) * blockDim.x) {
-      const uint4 m4 = *reinterpret_cast<const uint4*>(mine + v * 8);
-      const uint4 t4 = ld_relaxed_sys_v4(theirs + v * 8);
-      const __nv_bfloat162* mh = reinterpret_cast<const __nv_bfloat162*>(&m4);
-      const __nv_bfloat162* th = reinterpret_cast<const __nv_bfloat162*>(&t4);
-      float4 z0 = *reinterpret_cast<float4*>(a.z + v * 8), z1 = *reinterpret_cast<float4*>(a.z + v * 8 + 4);
-      float zz[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+      float fm[8], ft[8];
+      if (a.pred_f32) {
+        const float* mf = reinterpret_cast<const float*>(mine) + v * 8;
+        const float* tf = reinterpret_cast<const float*>(theirs) + v * 8;
+        const uint4 m0 = *reinterpret_cast<const uint4*>(mf), m1 = *reinterpret_cast<const uint4*>(mf + 4);
+        const uint4 t0 = ld_relaxed_sys_v4(tf), t1 = ld_relaxed_sys_v4(tf + 4);
+        const uint32_t mw[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        const uint32_t tw[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 fm = __bfloat1622float2(mh[i]), ft = __bfloat1622float2(th[i]);
-        const float2 c = a.rank == 0 ? fm : ft, u = a.rank == 0 ? ft : fm;
-        zz[2 * i] += (a.guidance * c.x + (1.f - a.guidance) * u.x) * a.dt;
-        zz[2 * i + 1] += (a.guidance * c.y + (1.f - a.guidance) * u.y) * a.dt;
+        for (int i = 0; i < 8; ++i) {
+          fm[i] = __uint_as_float(mw[i]);
+          ft[i] = __uint_as_float(tw[i]);
+        }
+      } else {
+        const uint4 m4 = *reinterpret_cast<const uint4*>(mine + v * 8);
+        const uint4 t4 = ld_relaxed_sys_v4(theirs + v * 8);
+        const __nv_bfloat162* mh = reinterpret_cast<const __nv_bfloat162*>(&m4);
+        const __nv_bfloat162* th = reinterpret_cast<const __nv_bfloat162*>(&t4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 a2 = __bfloat1622float2(mh[i]), b2 = __bfloat1622float2(th[i]);
+          fm[2 * i] = a2.x; fm[2 * i + 1] = a2.y;
+          ft[2 * i] = b2.x; ft[2 * i + 1] = b2.y;
+        }
+      }
+      float zz[8];
+      if (a.mode == 0) {
+        const float4 z0 = *reinterpret_cast<float4*>(a.z + v * 8), z1 = *reinterpret_cast<float4*>(a.z + v * 8 + 4);
+        zz[0] = z0.x; zz[1] = z0.y; zz[2] = z0.z; zz[3] = z0.w;
+        zz[4] = z1.x; zz[5] = z1.y; zz[6] = z1.z; zz[7] = z1.w;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float c = a.rank == 0 ? fm[i] : ft[i], u = a.rank == 0 ? ft[i] : fm[i];
+        const float comb = a.guidance * c + (1.f - a.guidance) * u;
+        zz[i] = a.mode == 0 ? zz[i] + comb * a.dt : comb;
       }
       *reinterpret_cast<float4*>(a.z + v * 8) = make_float4(zz[0], zz[1], zz[2], zz[3]);
       *reinterpret_cast<float4*>(a.z + v * 8 + 4) = make_float4(zz[4], zz[5], zz[6], zz[7]);
@@ -244,9 +270,10 @@ __global__ void __launch_bounds__(256) cfg_combine_kernel(const CfgCombineArgs a
 // pred / flags: arrays of 2 device pointers (index = rank) into the symmetric heap; flags per rank:
 // 4 x u32 (ready[2], consumed[2]), zero-initialised; epoch / fin: local zero-initialised u32.
 // n bf16 values (a multiple of 8); z: local fp32 latents [n].
+// mode 0: z += (u + g (c - u)) dt; mode 1: z = u + g (c - u). pred_f32: the slots hold fp32.
 B200_API int b200_cfg_combine(void* const* pred, void* const* flags, void* epoch, void* fin, float* z, long long n,
-                              int rank, float guidance, float dt, long long wait_budget_cycles, void* status,
-                              cudaStream_t stream) {
+                              int rank, float guidance, float dt, int mode, int pred_f32, long long wait_budget_cycles,
+                              void* status, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (n % 8 != 0 || rank < 0 || rank > 1) return -2;
   CfgCombineArgs a{};
@@ -262,6 +289,8 @@ B200_API int b200_cfg_combine(void* const* pred, void* const* flags, void* epoch
   a.rank = rank;
   a.guidance = guidance;
   a.dt = dt;
+  a.mode = mode;
+  a.pred_f32 = pred_f32;
   a.wait_budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
   a.status = static_cast<DeviceStatus*>(status);
   long long blocks = (n / 8 + 255) / 256;

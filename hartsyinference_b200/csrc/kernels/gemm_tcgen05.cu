@@ -89,6 +89,12 @@ struct AllReduceParams {
   uint32_t* ctr;                     // local: [0] calls completed, [1] CTAs past the GEMM, [2] row CTAs done, [3] CTAs finished
   long long wait_budget;             // cycles
   int debug_skip_ready;              // test aid: this rank never raises `ready`, so the waits on it run out
+  // More than 128 tokens (prefill, DiT sequences): the GEMM runs in its large-token orientation
+  // without K splits, `part` is [tokens][features], and the reduce phase is elementwise:
+  //   out = res + gate * (sum over ranks + bias)      (res, gate optional; no norm, no fp8 emit)
+  // `res` is then the replicated residual stream and is only read (the new stream is `out`).
+  int large;
+  const __nv_bfloat16* gate;         // [features], may be null
 };
 
 struct GemmParams {
@@ -274,6 +280,18 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
   if (p.ar.world > 0) {
     // fused all-reduce: raw bf16 partial of this K split into the rank's own [split][token][feature]
     // buffer (always the small-token orientation: a_row is the feature, the chunk walks tokens)
+    if (!p.swap_out) {
+      // large-token orientation: a_row is the token, the chunk walks 32 features (whole chunks:
+      // the feature count is a multiple of 128)
+      if (b0 >= b_end) return;
+      __nv_bfloat16* dst = p.ar.part + static_cast<long long>(a_row) * p.rows_b + b0;
+#pragma unroll
+      for (int j = 0; j < 32; j += 8)
+        *reinterpret_cast<uint4*>(dst + j) =
+            make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]), pack_bf16x2(v[j + 4], v[j + 5]),
+                       pack_bf16x2(v[j + 6], v[j + 7]));
+      return;
+    }
     __nv_bfloat16* dst = p.ar.part + (static_cast<long long>(split) * p.rows_b + b0) * p.rows_a + a_row;
 #pragma unroll
     for (int j = 0; j < 32; ++j)
@@ -456,7 +474,7 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* addr) {
 __device__ __forceinline__ void ar_finish(const GemmParams& p, GemmBarriers* bars) {
   const AllReduceParams& a = p.ar;
   const int et = threadIdx.x - 64;
-  const int m = p.rows_b, n = p.rows_a;          // tokens, features
+  const int m = p.swap_out ? p.rows_b : p.rows_a, n = p.swap_out ? p.rows_a : p.rows_b;          // tokens, features
   const uint32_t call = *reinterpret_cast<volatile uint32_t*>(a.ctr) + 1u;   // 1-based index of this call
   // ---- 2. this CTA's partial tiles are written; the rank's last CTA tells every rank. Peers read
   // the tiles through this GPU's L2, so a device-scope fence per CTA orders them; the one release
@@ -526,6 +544,14 @@ __device__ __forceinline__ void ar_finish(const GemmParams& p, GemmBarriers* bar
           }
         }
         if (a.bias) add_bf16x8(acc, *reinterpret_cast<const uint4*>(a.bias + v * 8));
+        if (a.gate) {
+          float g[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) g[i] = 0.f;
+          add_bf16x8(g, *reinterpret_cast<const uint4*>(a.gate + v * 8));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] *= g[i];
+        }
       }
       // what the unfused path would have stored as the all-reduce result is bf16: round here too
       uint4 packed;
@@ -541,7 +567,7 @@ __device__ __forceinline__ void ar_finish(const GemmParams& p, GemmBarriers* bar
         add_bf16x8(t, *reinterpret_cast<const uint4*>(rr));
 #pragma unroll
         for (int i = 0; i < 4; ++i) pw[i] = pack_bf16x2(t[2 * i], t[2 * i + 1]);
-        *reinterpret_cast<uint4*>(rr) = packed;          // new residual row (this rank only)
+        if (!a.large) *reinterpret_cast<uint4*>(rr) = packed;          // new residual row (this rank only)
       }
       float y[8];
 #pragma unroll
@@ -1316,7 +1342,8 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   p.status = static_cast<DeviceStatus*>(status);
   p.swap_out = swap ? 1 : 0;
   if (ar != nullptr) {
-    if (m > 128 || n % 128 != 0 || groups > 0 || cs != nullptr || ar->part_splits > 4) return -6;   // one token tile, whole feature tiles
+    if ((m > 128) != (ar->large != 0)) return -6;
+    if (n % 128 != 0 || groups > 0 || cs != nullptr || ar->part_splits > 4) return -6;   // whole feature tiles
     if (bias != nullptr || gate != nullptr || residual != nullptr || act != 0) return -6;   // see AllReduceParams
     p.ar = *ar;
     // K splits fill the machine when there are fewer tiles than SMs; every split is one more
@@ -1326,7 +1353,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     if (s_ar > 4) s_ar = 4;
     const int kb_all = (k + kelems - 1) / kelems;
     if (s_ar > kb_all / 4) s_ar = kb_all / 4;
-    splits = s_ar < 1 ? 1 : s_ar;
+    splits = s_ar < 1 || ar->large ? 1 : s_ar;
   }
 
   int bn;
@@ -1559,7 +1586,10 @@ B200_API int b200_gemm_deferred(const void* x, const void* w, void* out, int m, 
 //   res    = res + s            (rank-local residual stream; rows this rank owns only, in place)
 //   h      = norm_w == null ? res : rmsnorm(res, eps) * norm_w                (res = s when res is null)
 //   out_bf16 / out_q + out_sf = h as bf16 / as e4m3 with 1x128 scales, on every rank
-// for m <= 128 tokens and n a multiple of 128 (and of 128 when out_q is asked for). See
+// for m <= 128 tokens and n a multiple of 128. For m > 128 (prefill, DiT sequences; norm_w and out_q
+// must be null) the reduce phase is  out_bf16 = res + gate * (s + bias)  with `res` the replicated
+// residual stream (read only) and `gate` an optional per-feature factor; `part` then holds
+// [m][n] bf16. See
 // AllReduceParams for the protocol. `part_src`, `out_*`, `flags` are arrays of `world` peer
 // pointers into the symmetric heap (index = rank), or, with use_mc = 1, arrays whose entry 0 is
 // the multicast alias of the buffer. `part` (partials), `flags_local` (two u32) and `ctr`
@@ -1576,9 +1606,12 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
                                  void* const* out_bf16, void* const* out_q, void* const* out_sf,
                                  int sf_tile_rows, void* const* flags, void* flags_local, void* ctr,
                                  int rank, int world, int use_mc, int part_splits,
-                                 long long wait_budget_cycles, int debug_skip_ready, void* status,
-                                 cudaStream_t stream) {
+                                 long long wait_budget_cycles, int debug_skip_ready, const void* gate,
+                                 void* status, cudaStream_t stream) {
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return -7;
+  const bool large = m > 128;
+  if (large && (norm_w != nullptr || out_q != nullptr)) return -7;   // the large-token form is elementwise
+  if (!large && gate != nullptr) return -7;
   if (part == nullptr || part_src == nullptr || flags == nullptr || flags_local == nullptr || ctr == nullptr) return -7;
   if (out_q != nullptr && (out_sf == nullptr || n % 128 != 0)) return -7;
   if (n / 8 > 256 * kArMaxSegs) return -7;   // row segments of the reduce phase
@@ -1606,6 +1639,8 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
   ar.part_splits = part_splits < 1 ? 1 : part_splits;
   ar.wait_budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
   ar.debug_skip_ready = debug_skip_ready;
+  ar.large = large ? 1 : 0;
+  ar.gate = static_cast<const __nv_bfloat16*>(gate);
   return gemm_impl(x, w, nullptr, m, n, k, ldx, ldw, n, dtype, x_scale, w_scale, nullptr, nullptr,
                    nullptr, 0, 1, nullptr, 0, status, stream, &ar);
 }

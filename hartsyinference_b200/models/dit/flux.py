@@ -20,7 +20,7 @@ from typing import Callable, Optional
 
 import torch
 
-from ... import ops
+from ... import config, log, ops
 from ...ops import LinearWeight
 from ...parallel.comm import Comm, SingleComm
 from .common import WeightFactory, modulation, rope_tables, silu, timestep_embedding
@@ -247,6 +247,37 @@ class FluxTransformer:
     def _gated_add(self, x, y, gate, rows_per_batch):
         return ops.gated_residual(x, y, gate, rows_per_batch)
 
+    def _fused_rows(self, tokens: int):
+        """The fused GEMM + all-reduce + gated residual kernel (parallel/fused.py, large-token form)
+        sized for ``tokens`` rows, or None (one rank, CPU, flag off, no peer mapping)."""
+        if self.tp == 1 or self.device.type != "cuda" or not config.get("fused_dit_tp"):
+            return None
+        cur = getattr(self, "_fused_rp", None)
+        if cur is None or (cur is not False and cur.max_large_tokens < tokens):
+            from ...parallel.fused import FusedRowParallel
+            try:
+                if cur:
+                    cur.close()
+                self._fused_rp = FusedRowParallel(self.comm, self.cfg.hidden_size, self.device, max_large_tokens=tokens)
+                self.comm_path = "fused GEMM + all-reduce + gated residual (multimem)" if self._fused_rp.use_mc else \
+                    "fused GEMM + all-reduce + gated residual (peer loads)"
+            except Exception as e:
+                log.warn(f"[TensorParallel] fused row-parallel kernel unavailable ({type(e).__name__}: {e}); using NCCL")
+                self._fused_rp = False
+        return self._fused_rp or None
+
+    def close(self) -> None:
+        cur = getattr(self, "_fused_rp", None)
+        if cur:
+            cur.close()
+        self._fused_rp = None
+
+    def _row_parallel(self, a, w, x, gate, rows_per_batch, fused, slot):
+        """x + gate * all_reduce(a w^T + bias): one fused kernel where it applies."""
+        if fused is not None and gate.shape[0] == 1 and fused.supports_large(a.shape[0], w.weight.shape[0]):
+            return fused.large(a, w, res=x.contiguous(), gate=gate.reshape(-1).contiguous(), slot=slot)
+        return self._gated_add(x, self._reduce(ops.linear(a, w)), gate, rows_per_batch)
+
     def forward(self, img: torch.Tensor, txt: torch.Tensor, timestep: torch.Tensor, pooled: torch.Tensor,
                 img_ids: torch.Tensor, txt_ids: torch.Tensor, guidance: Optional[torch.Tensor] = None,
                 hidden_in: Optional[tuple] = None, step_cache=None, control: Optional[tuple] = None,
@@ -284,15 +315,17 @@ class FluxTransformer:
             qkv = ops.linear(xq if xq is not None else xn, w.qkv)
             return ops.dit_qkv(qkv, self.hl, self.hl, D, q_norm_w=w.q_norm, k_norm_w=w.k_norm, cos=c, sin=s)
 
-        def stream_post(x, a, w: _StreamWeights, mod, S):
-            y = self._reduce(ops.linear(a, w.proj))
-            x = self._gated_add(x, y, mod[:, 2 * H:3 * H], S)
+        # the fused row-parallel kernel hands out views of its own buffers: not while something
+        # (ControlNet residual collection, the step cache) keeps the streams beyond the next block
+        fused = self._fused_rows(B * (S_i + S_t)) if (control is None and collect is None and step_cache is None) else None
+
+        def stream_post(x, a, w: _StreamWeights, mod, S, slot):
+            x = self._row_parallel(a, w.proj, x, mod[:, 2 * H:3 * H], S, fused, slot)
             xn, _, xq = ops.norm(x, None, shift=mod[:, 3 * H:4 * H], scale=mod[:, 4 * H:5 * H], rows_per_batch=S,
                                  layernorm=True, emit_fp8=self.fp8 and w.mlp_in.is_fp8,
                                  emit_bf16=not (self.fp8 and w.mlp_in.is_fp8))
             h = ops.linear(xq if xq is not None else xn, w.mlp_in, act="gelu_tanh")
-            y = self._reduce(ops.linear(h, w.mlp_out))
-            return self._gated_add(x, y, mod[:, 5 * H:6 * H], S)
+            return self._row_parallel(h, w.mlp_out, x, mod[:, 5 * H:6 * H], S, fused, slot + 1)
 
         whole = self.block_range == (0, cfg.num_double_blocks + cfg.num_single_blocks)
         use_cache = step_cache is not None and step_cache.enabled and whole and len(self.double) > 0
@@ -316,8 +349,8 @@ class FluxTransformer:
             else:
                 a_t = torch.cat([att[i * S:i * S + S_t] for i in range(B)], 0)
                 a_i = torch.cat([att[i * S + S_t:(i + 1) * S] for i in range(B)], 0)
-            x_i = stream_post(x_i, a_i.contiguous(), wi, mod_i, S_i)
-            x_t = stream_post(x_t, a_t.contiguous(), wt, mod_t, S_t)
+            x_i = stream_post(x_i, a_i.contiguous(), wi, mod_i, S_i, 0)
+            x_t = stream_post(x_t, a_t.contiguous(), wt, mod_t, S_t, 2)
             if collect is not None:
                 collect[0].append(x_i)
             if control is not None and control[0]:
@@ -347,8 +380,7 @@ class FluxTransformer:
                                       cos=cj, sin=sj)
                 att = self._attend(q, k, v, B)
                 mlp = torch.nn.functional.gelu(fused[:, qkv_cols:].float(), approximate="tanh").to(dt)
-                y = self._reduce(ops.linear(torch.cat([att, mlp], 1), w.out))
-                joint = self._gated_add(joint, y, mod[:, 2 * H:3 * H], S)
+                joint = self._row_parallel(torch.cat([att, mlp], 1), w.out, joint, mod[:, 2 * H:3 * H], S, fused, si & 1)
                 if collect is not None or (control is not None and control[1]):
                     img_rows = slice(S_t, S) if B == 1 else None
                     if img_rows is None:

@@ -32,11 +32,12 @@ from .symm import SymmetricHeap
 
 MAX_TOKENS = 128
 PART_SPLITS = 4       # K splits per rank that the partial buffer has room for
+LARGE_SLOTS = 4       # output buffers of the > 128-token form (the caller names the one to write)
 
 
 class FusedRowParallel:
     def __init__(self, comm: Comm, max_features: int, device: Optional[torch.device] = None,
-                 num_out_buffers: int = 2, emulate_peers: bool = False):
+                 num_out_buffers: int = 2, emulate_peers: bool = False, max_large_tokens: int = 0):
         """``emulate_peers`` (measurement aid for one GPU): ``comm`` claims a rank of a larger world
         but has no peers; every "peer" address is this GPU's own buffer, so the kernel runs the full
         protocol of that rank (its row share, one signal per pretended peer) with meaningless sums."""
@@ -54,12 +55,18 @@ class FusedRowParallel:
         q_bytes = MAX_TOKENS * f
         sf_bytes = max(MAX_TOKENS * ((f + 127) // 128) * 4, ((f + 511) // 512) * 512)
         per_slot = bf16_bytes + q_bytes + sf_bytes + 3 * 256
-        self.heap = SymmetricHeap(heap_comm, part_bytes + num_out_buffers * per_slot + 16384, self.device)
+        # sequences of more than MAX_TOKENS rows (prefill, DiT): one [tokens][features] partial buffer
+        # and two output buffers
+        self.max_large_tokens = int(max_large_tokens)
+        large_bytes = self.max_large_tokens * f * 2
+        self.heap = SymmetricHeap(heap_comm, part_bytes + num_out_buffers * per_slot + (LARGE_SLOTS + 1) * (large_bytes + 256) + 16384, self.device)
         self.use_mc = self.heap.has_multicast
         self.off_part = self.heap.alloc(part_bytes)
         self.off_bf16 = [self.heap.alloc(bf16_bytes) for _ in range(num_out_buffers)]
         self.off_q = [self.heap.alloc(q_bytes) for _ in range(num_out_buffers)]
         self.off_sf = [self.heap.alloc(sf_bytes) for _ in range(num_out_buffers)]
+        self.off_part_large = self.heap.alloc(large_bytes) if large_bytes else 0
+        self.off_out_large = [self.heap.alloc(large_bytes) for _ in range(LARGE_SLOTS)] if large_bytes else []
         self.off_flags = self.heap.alloc(256)
         ctr_bytes = int(N.bind("b200_gemm_allreduce_ctr_bytes", C.c_longlong, [])())
         self.off_ctr = self.heap.alloc(ctr_bytes)
@@ -77,6 +84,10 @@ class FusedRowParallel:
         self._bf16 = [arr(o) for o in self.off_bf16]
         self._q = [arr(o) for o in self.off_q]
         self._sf = [arr(o) for o in self.off_sf]
+        self._part_large = self.heap.ptr(own, self.off_part_large) if large_bytes else None
+        self._part_large_src = arr(self.off_part_large) if large_bytes else None
+        self._out_large = [arr(o) for o in self.off_out_large]
+        self._next_large = 0
         self._flags = arr(self.off_flags)
         self._flags_local = self.heap.ptr(own, self.off_flags)
         self._ctr = self.heap.ptr(own, self.off_ctr)
@@ -84,9 +95,44 @@ class FusedRowParallel:
         vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
         self._fn = N.bind("b200_gemm_allreduce", i32,
                           [vp, vp, i32, i32, i32, i64, i64, i32, vp, vp, vp, vp, vp, f32, i32, vp, vp, vp, vp, vp,
-                           i32, vp, vp, vp, i32, i32, i32, i32, i64, i32, vp, vp])
+                           i32, vp, vp, vp, i32, i32, i32, i32, i64, i32, vp, vp, vp])
         self.budget_cycles = int(config.get("wait_budget_ms")) * 2_000_000
         self.debug_skip_ready = False    # tests: withhold this rank's "ready" signal once per call
+
+    def supports_large(self, m: int, n: int) -> bool:
+        return MAX_TOKENS < m <= self.max_large_tokens and n <= self.max_features and n % 128 == 0
+
+    def large(self, x, w: LinearWeight, *, res: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+              slot: Optional[int] = None) -> torch.Tensor:
+        """Row-parallel linear over more than 128 tokens fused with its all-reduce and the gated
+        residual add: returns ``res + gate * (sum over ranks of x_r w_r^T + bias)`` ([m, n] bf16) on
+        every rank, a view of output buffer ``slot`` (one of LARGE_SLOTS; default: they take turns).
+        The view is valid until a later call names the same slot; ``res`` may be the view returned by
+        an earlier call with a different slot. ``res`` ([m, n] bf16, the replicated residual stream)
+        and ``gate`` ([n] bf16) are optional."""
+        if w.is_fp8 and not isinstance(x, Fp8Act):
+            x = ops.quant_fp8_act(x, mx=w.is_mx)
+        xd = x.data if isinstance(x, Fp8Act) else x
+        m, k = xd.shape
+        n = w.weight.shape[0]
+        assert self.supports_large(m, n), (m, n, self.max_large_tokens)
+        assert res is None or (res.is_contiguous() and res.shape == (m, n) and res.dtype == torch.bfloat16)
+        assert gate is None or (gate.is_contiguous() and gate.numel() == n and gate.dtype == torch.bfloat16)
+        if slot is None:
+            slot = self._next_large
+            self._next_large = (self._next_large + 1) % LARGE_SLOTS
+        fp8 = w.is_fp8
+        st = N.state(self.device)
+        rc = self._fn(xd.data_ptr(), w.weight.data_ptr(), m, n, k, xd.stride(0), w.weight.stride(0),
+                      2 if w.is_mx else 1 if fp8 else 0,
+                      None if not fp8 else x.sf.data_ptr() if w.is_mx else x.scale.data_ptr(),
+                      None if not fp8 else w.sf.data_ptr() if w.is_mx else w.scale.data_ptr(),
+                      N.ptr(w.bias), N.ptr(res), None, 0.0, 0,
+                      self._part_large, self._part_large_src, self._out_large[slot], None, None, 0,
+                      self._flags, self._flags_local, self._ctr, self.rank, self.world, 1 if self.use_mc else 0, 1,
+                      self.budget_cycles, 0, N.ptr(gate), st.status.data_ptr(), N.stream())
+        N.check(rc, "b200_gemm_allreduce")
+        return self.heap.tensor(self.off_out_large[slot], (m, n), torch.bfloat16)
 
     def reset(self) -> None:
         """Clear the counters on every rank (all ranks call this together, with no call in
@@ -131,7 +177,7 @@ class FusedRowParallel:
                       self._q[slot] if emit_fp8 else None, self._sf[slot] if emit_fp8 else None,
                       128 if mx_out else 0, self._flags, self._flags_local, self._ctr,
                       self.rank, self.world, 1 if self.use_mc else 0, PART_SPLITS, self.budget_cycles,
-                      1 if self.debug_skip_ready else 0, st.status.data_ptr(), N.stream())
+                      1 if self.debug_skip_ready else 0, None, st.status.data_ptr(), N.stream())
         N.check(rc, "b200_gemm_allreduce")
         h = self.heap.tensor(self.off_bf16[slot], (m, n), torch.bfloat16) if emit_bf16 else None
         h8 = None

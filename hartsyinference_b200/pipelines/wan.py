@@ -16,7 +16,7 @@ from typing import Callable, Optional
 
 import torch
 
-from .. import log
+from .. import config, log
 from ..engine.metrics import REGISTRY
 from ..engine.requests import StepPreview, VideoGenerationResult, VideoRequest
 from ..models.diffusion.schedulers import FlowMatchEulerScheduler, FlowUniPCScheduler
@@ -87,8 +87,12 @@ class WanPipeline:
                     v = vu + cfg_scale * (v - vu)
             else:
                 mine = tr.forward(xin, t, c_pos if branch == 0 else c_neg).contiguous()
-                both = self.cfg_comm.all_gather(mine[None], dim=0)
-                v = both[1] + cfg_scale * (both[0] - both[1])
+                fused = self._cfg_kernel(mine.numel())
+                if fused is not None:
+                    v = fused.combine(mine.float(), cfg_scale)       # peer loads inside the combine kernel
+                else:
+                    both = self.cfg_comm.all_gather(mine[None], dim=0)
+                    v = both[1] + cfg_scale * (both[0] - both[1])
             if uni is not None:
                 x = uni.step(v, x)
             else:
@@ -104,6 +108,30 @@ class WanPipeline:
             if on_step is not None:
                 on_step(StepPreview(i + 1, steps, latents=x))      # fp32 latents [C, T, H / 8, W / 8] on the device
         return x
+
+    def _cfg_kernel(self, n: int):
+        """The two-rank combine kernel over peer memory (parallel/cfg_combine.py), or None on CPU
+        ranks, for sizes the kernel does not take, or when the peer mapping cannot be made."""
+        if self.device.type != "cuda" or n % 8 != 0 or not config.get("fused_cfg_combine"):
+            return None
+        cur = getattr(self, "_cfg_fused", None)
+        if cur is None or cur[0] < n:
+            from ..parallel.cfg_combine import FusedCfgCombine
+            try:
+                if cur is not None and cur[1] is not None:
+                    cur[1].close()
+                self._cfg_fused = (n, FusedCfgCombine(self.cfg_comm, n, self.device))
+                self.cfg_path = "peer loads inside the CFG combine kernel"
+            except Exception as e:
+                log.warn(f"[Collective] CFG combine kernel unavailable ({type(e).__name__}: {e}); using all_gather")
+                self._cfg_fused = (1 << 62, None)
+        return self._cfg_fused[1]
+
+    def close(self) -> None:
+        cur = getattr(self, "_cfg_fused", None)
+        if cur is not None and cur[1] is not None:
+            cur[1].close()
+        self._cfg_fused = None
 
     def generate(self, req: VideoRequest, on_step: Optional[Callable[[StepPreview], None]] = None) -> VideoGenerationResult:
         seed = req.seed if req.seed is not None else int(time.time() * 1000) % (2 ** 31)

@@ -63,6 +63,38 @@ def main():
             assert torch.equal(res[other], res0[other])
             y, _ = fused(x, w)                                   # plain all-reduced linear
             assert rel(y, part) < 1.5e-2, (fp8, m, "plain", rel(y, part))
+    # ---- more than 128 tokens: GEMM + all-reduce + gated residual in one kernel
+    big = FusedRowParallel(comm, 1024, dev, max_large_tokens=1200)
+    for fp8 in (False, True):
+        for m in (1100, 300):
+            n, k = 1024, 512
+            x = (torch.randn(m, k, device=dev) * 0.5).to(torch.bfloat16)
+            w = ops.LinearWeight.from_dense((torch.randn(n, k, device=dev) * 0.2).to(torch.bfloat16),
+                                            torch.randn(n, device=dev).to(torch.bfloat16), fp8=fp8)
+            res = torch.randn(m, n, device=dev).to(torch.bfloat16)
+            gate = torch.randn(n, device=dev).to(torch.bfloat16)
+            dist.broadcast(res, 0)
+            dist.broadcast(gate, 0)
+            part = ops.linear(x, w).float()                      # includes this rank's bias
+            dist.all_reduce(part)
+            # every rank added its own bias in `part`; the fused kernel adds the bias once (rank-local bias tensor of the owner)
+            want = None
+            for it in range(3):
+                y = big.large(x, w, res=res, gate=gate, slot=it % 2).clone()
+                N.check_status(dev)
+                bias_all = w.bias.float().clone()
+                dist.all_reduce(bias_all)
+                # owner-row bias: rows owned by rank r carry rank r's bias
+                per = (m + world - 1) // world
+                wb = torch.zeros(m, n, device=dev)
+                biases = [torch.zeros_like(w.bias) for _ in range(world)]
+                dist.all_gather(biases, w.bias)
+                for r in range(world):
+                    wb[r * per:(r + 1) * per] = biases[r].float()
+                want = res.float() + gate.float() * (part - bias_all + wb)
+                assert rel(y, want) < 1.5e-2, ("large", fp8, m, it, rel(y, want))
+    comm.barrier()
+    big.close()
     # ---- peer-memory all-reduce kernel vs NCCL, eager and under a CUDA graph
     from hartsyinference_b200.parallel.custom_ar import CustomAllReduce
     car = CustomAllReduce(comm, 128 * 2048, dev)
@@ -111,6 +143,11 @@ def main():
             N.check_status(dev)
             assert (z.cpu() - want).abs().max() < 1e-5, (it, (z.cpu() - want).abs().max())
             z0 = want
+        # the guided prediction by itself (fp32 slots), for schedulers that are not an Euler step
+        pf = [torch.randn(4096 * 64, generator=gen) for _ in range(2)]
+        v = fc.combine(pf[rank].to(dev), 5.0)
+        N.check_status(dev)
+        assert (v.cpu() - (5.0 * pf[0] + (1 - 5.0) * pf[1])).abs().max() < 1e-5
         fc.close()
     # ---- sequence-parallel attention with the exchange fused into the kernels, vs fp32 over the full sequence
     from hartsyinference_b200.parallel.ulysses import FusedUlyssesAttention

@@ -116,6 +116,43 @@ def test_single_rank_cuda_graph_replay():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("fp8", [False, True])
+def test_large_token_form_matches_fp32(fp8):
+    """More than 128 tokens: GEMM in the large-token orientation, elementwise reduce phase with bias,
+    gate and the (read-only) residual stream; slots chained like the DiT blocks chain them."""
+    torch.manual_seed(4)
+    f = FusedRowParallel(SingleComm(), 768, max_large_tokens=700)
+    try:
+        for m in (300, 640, 129):
+            n, k = 768, 512
+            x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+            w = (torch.randn(n, k, device="cuda") * 0.2).to(torch.bfloat16)
+            b = torch.randn(n, device="cuda").to(torch.bfloat16)
+            lw = ops.LinearWeight.from_dense(w, b, fp8=fp8)
+            res = torch.randn(m, n, device="cuda").to(torch.bfloat16)
+            gate = torch.randn(n, device="cuda").to(torch.bfloat16)
+            plain = ops.linear(x, lw).float()             # same operands, bias included
+            y1 = f.large(x, lw, res=res, gate=gate, slot=0)
+            want1 = res.float() + gate.float() * plain
+            N.check_status()
+            assert _rel(y1, want1) < 1e-2, (m, "gated", _rel(y1, want1))
+            y2 = f.large(x, lw, res=y1, slot=1)           # the previous output as the residual stream
+            N.check_status()
+            assert _rel(y2, y1.float() + plain) < 1e-2, (m, "chained", _rel(y2, y1.float() + plain))
+            assert _rel(y1, want1) < 1e-2                 # slot 0 is untouched by the call into slot 1
+            y3 = f.large(x, lw)                           # plain all-reduced linear
+            assert _rel(y3, plain) < 1e-2
+        # the small-token form still works on the same instance afterwards
+        x = (torch.randn(64, 512, device="cuda") * 0.5).to(torch.bfloat16)
+        lw = ops.LinearWeight.from_dense((torch.randn(768, 512, device="cuda") * 0.2).to(torch.bfloat16), fp8=fp8)
+        y, _ = f(x, lw)
+        N.check_status()
+        assert _rel(y, ops.linear(x, lw, splits=1)) < 1e-2
+    finally:
+        f.close()
+
+
+@pytest.mark.gpu
 def test_wait_runs_out_reports_and_recovers():
     """A rank that never raises `ready`: the bounded wait gives up after about a millisecond, the
     kernel returns, the status word names kernel and site, and after the counters are cleared the
