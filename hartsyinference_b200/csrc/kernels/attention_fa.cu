@@ -19,7 +19,9 @@
 //                the first 64 columns of S_t, written there by the softmax warps), directly
 //                followed by S_t(j+1) = Q_t K_{j+1}^T, so the two query tiles alternate on the tensor
 //                core and each one's softmax overlaps the other one's matrix products
-//   warps 2..5   softmax of query tile 0; warps 6..9 softmax of query tile 1. Thread r owns query
+//   warps 4..7   softmax of query tile 0; warps 8..11 softmax of query tile 1 (warps 2, 3 idle, so
+//                that each role is a whole warp group and registers can be moved between the
+//                groups with setmaxnreg). Thread r owns query
 //                row r (TMEM lane r): reads its S row (tcgen05.ld), applies scale (and the int8
 //                dequantisation), keeps running maximum / sum in the exp2 domain, writes P as bf16
 //                pairs back into TMEM (tcgen05.st). O is never read back during the loop: the
@@ -35,7 +37,7 @@ namespace b200 {
 
 constexpr int kFaD = 128;
 constexpr int kFaTile = 128;              // rows of one query tile and keys per step
-constexpr int kFaThreads = 320;           // producer, MMA, 2 x 4 softmax warps
+constexpr int kFaThreads = 384;           // warp group 0: producer, MMA (+ 2 idle warps); groups 1, 2: softmax of tile 0, 1
 constexpr float kFaRescaleGap = 8.f;      // raise the running maximum only beyond this many powers of two
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -148,6 +150,10 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
   constexpr uint32_t kIdescS = kI8 ? make_idesc(128, 128, kFmtS8, kFmtS8, 2) : make_idesc(128, 128, kFmtBf16, kFmtBf16);
   constexpr uint32_t kIdescPV = make_idesc(128, 128, kFmtBf16, kFmtBf16);
 
+  // The softmax threads keep a whole score row in registers; the producer and MMA warps need few.
+  // Registers move between the warp groups accordingly (launch: 168 per thread).
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     // ------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -253,9 +259,11 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
       }
       if (!ok) report_status(p.status, kWaitTimeout, kKernelAttnPrefill, 22, blockIdx.x);
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     // ------------------------------------------------------------------------- softmax warps
-    const int t = (warp - 2) >> 2;                        // query tile of this warp group
+    const int t = (warp >> 2) - 1;                        // query tile of this warp group
     const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;                  // query row inside the tile = TMEM lane
     const int q_idx = qt2 * 2 * kFaTile + t * kFaTile + row;
@@ -282,28 +290,42 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
           qs *= q_valid ? __ldcg(p.q_scale + static_cast<long long>(b * p.heads + head) * p.sq_pad + q_idx) : 0.f;
         const float c = kI8 ? qs * __ldcg(ksc + bt) : qs;
         const bool tail = valid < kFaTile;
-        // the whole raw S row of this thread: four loads in flight, one wait
+        // the raw S row of this thread in two halves: the second half is in flight while the maximum
+        // of the first is taken; eight independent running maxima keep the compare pipe busy instead
+        // of one chain of 128 dependent compares
         uint32_t r[128];
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) tmem_ld_32x32(s_col + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[cc * 32]));
+        for (int cc = 0; cc < 2; ++cc) tmem_ld_32x32(s_col + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[cc * 32]));
         tmem_ld_wait();
+#pragma unroll
+        for (int cc = 2; cc < 4; ++cc) tmem_ld_32x32(s_col + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[cc * 32]));
+        float mx;
+        if (kI8) {
+          int mi[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) mi[u] = tail && u >= valid ? -(1 << 22) : static_cast<int>(r[u]);
+#pragma unroll
+          for (int i = 8; i < 64; ++i) mi[i & 7] = max(mi[i & 7], tail && i >= valid ? -(1 << 22) : static_cast<int>(r[i]));
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 64; i < 128; ++i) mi[i & 7] = max(mi[i & 7], tail && i >= valid ? -(1 << 22) : static_cast<int>(r[i]));
+          mx = static_cast<float>(max(max(max(mi[0], mi[1]), max(mi[2], mi[3])), max(max(mi[4], mi[5]), max(mi[6], mi[7])))) * c;
+        } else {
+          float mf[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) mf[u] = tail && u >= valid ? -INFINITY : __uint_as_float(r[u]);
+#pragma unroll
+          for (int i = 8; i < 64; ++i) mf[i & 7] = fmaxf(mf[i & 7], tail && i >= valid ? -INFINITY : __uint_as_float(r[i]));
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 64; i < 128; ++i) mf[i & 7] = fmaxf(mf[i & 7], tail && i >= valid ? -INFINITY : __uint_as_float(r[i]));
+          mx = fmaxf(fmaxf(fmaxf(mf[0], mf[1]), fmaxf(mf[2], mf[3])), fmaxf(fmaxf(mf[4], mf[5]), fmaxf(mf[6], mf[7]))) * c;
+        }
         if (tail) {
           // keys past the end: the most negative value the exponent path below maps far below any maximum
 #pragma unroll
           for (int i = 0; i < 128; ++i)
             if (i >= valid) r[i] = kI8 ? static_cast<uint32_t>(-(1 << 22)) : 0xff800000u;
-        }
-        float mx;
-        if (kI8) {
-          int mi = static_cast<int>(r[0]);
-#pragma unroll
-          for (int i = 1; i < 128; ++i) mi = max(mi, static_cast<int>(r[i]));
-          mx = static_cast<float>(mi) * c;
-        } else {
-          float mf = __uint_as_float(r[0]);
-#pragma unroll
-          for (int i = 1; i < 128; ++i) mf = fmaxf(mf, __uint_as_float(r[i]));
-          mx = mf * c;
         }
         // raise the running maximum only when it would grow by more than the gap (or on the first
         // tile); a warp decides together because the O rescale below is a warp-wide TMEM access
@@ -334,7 +356,7 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
         // turned into 12582912 + s by an integer add on its bits (exact for |s| < 2^22) and the
         // constant is folded into the subtrahend, so no conversion instruction is spent
         const float sub = kI8 ? fmaf(12582912.f, c, m_safe) : m_safe;
-        float sum = 0.f;
+        float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           uint32_t packed[32];
@@ -345,13 +367,13 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
             const float f1 = kI8 ? __uint_as_float(r1 + 0x4B400000u) : __uint_as_float(r1);
             const float a = fast_exp2(fmaf(f0, c, -sub));
             const float bq = fast_exp2(fmaf(f1, c, -sub));
-            sum += a + bq;
+            sums[i & 3] += a + bq;
             packed[i] = pack_bf16x2(a, bq);
           }
           tmem_st_32x32(s_col + cc * 32, packed);      // P_t: columns [0, 64) of S_t
         }
         tmem_st_wait();
-        l_run += sum;
+        l_run += (sums[0] + sums[1]) + (sums[2] + sums[3]);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_ready[t]);

@@ -43,6 +43,7 @@ class Request:
     t_done: float = 0.0
     error: Optional[str] = None
     generator: Optional[torch.Generator] = None
+    rng_seed: int = 0                    # stream id of the device sampler (the request's seed, or drawn at submission)
     embeds: Optional[torch.Tensor] = None         # [len(prompt), hidden] replacement input embeddings
     embeds_mask: Optional[torch.Tensor] = None    # [len(prompt)] bool: rows taken from ``embeds``
     cross_states: Optional[torch.Tensor] = None   # [Tv, hidden] vision states read by cross-attention layers
@@ -168,6 +169,11 @@ class LLMEngine:
             req.cross_states = cross_states.to(self.device).to(torch.bfloat16)
         if params.seed is not None and not params.is_greedy:
             req.generator = torch.Generator(device=self.device).manual_seed(params.seed)
+        if params.seed is not None:
+            req.rng_seed = int(params.seed) & 0x7fffffff
+        else:
+            import random
+            req.rng_seed = random.getrandbits(31)
         self.requests[rid] = req
         return rid
 
@@ -287,11 +293,48 @@ class LLMEngine:
                 return self._read_tokens(tok, n)
             return tok.tolist()
         logits = self.model.full_logits(hidden).float()
+        if self.cuda and all(r.params.logits_mask is None for r in reqs):
+            return self._sample_on_device(logits, reqs)
         out = []
         for i, r in enumerate(reqs):
             out.append(sample_row(logits[i], r.params, r.prompt + r.output, r.generator))
         self.d2h_bytes_last += n * 4
         return out
+
+    def _sample_on_device(self, logits: torch.Tensor, reqs: list[Request]) -> list[int]:
+        """The whole batch in one kernel (temperature -> top-k -> top-p -> min-p -> seeded draw;
+        greedy rows are an argmax); repetition penalties are applied to the logits first, also on the
+        device. Only the chosen ids come back."""
+        n = len(reqs)
+        pen = [r for r in reqs if r.params.repetition_penalty != 1.0 and (len(r.prompt) + len(r.output)) > 0]
+        if pen:
+            width = min(4096, max(len(r.prompt) + len(r.output) for r in pen))
+            hist = torch.zeros(n, width, dtype=torch.int32)
+            hlen = torch.zeros(n, dtype=torch.int32)
+            pv = torch.ones(n, dtype=torch.float32)
+            for i, r in enumerate(reqs):
+                if r.params.repetition_penalty != 1.0:
+                    h = (r.prompt + r.output)[-width:]
+                    hist[i, :len(h)] = torch.tensor(h, dtype=torch.int32)
+                    hlen[i] = len(h)
+                    pv[i] = r.params.repetition_penalty
+            ops.repetition_penalty_(logits, hist.to(self.device), hlen.to(self.device), pv.to(self.device))
+            self.h2d_bytes_last += hist.numel() * 4 + n * 8
+        host = torch.empty(n, 6, dtype=torch.float64)
+        for i, r in enumerate(reqs):
+            p = r.params
+            host[i, 0] = 0.0 if p.is_greedy else max(p.temperature, 1e-6)
+            host[i, 1] = p.top_k or 0
+            host[i, 2] = p.top_p
+            host[i, 3] = p.min_p
+            host[i, 4] = r.rng_seed
+            host[i, 5] = len(r.output)
+        dev = host.to(self.device)
+        self.h2d_bytes_last += host.numel() * 8
+        tok = ops.sample_tokens(logits, dev[:, 0].float().contiguous(), dev[:, 1].to(torch.int32).contiguous(),
+                                dev[:, 2].float().contiguous(), dev[:, 3].float().contiguous(),
+                                dev[:, 4].to(torch.int64).contiguous(), dev[:, 5].to(torch.int64).contiguous())
+        return self._read_tokens(tok, n)
 
     def _decode_batch_tensors(self, rids: list[int], bucket: int):
         page = self.page

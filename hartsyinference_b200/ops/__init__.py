@@ -41,6 +41,7 @@ from .core import (  # noqa: F401
     quant_fp8_weight,
     repetition_penalty_,
     rope_kv,
+    sample_tokens,
     selective_scan,
 )
 from . import reference  # noqa: F401
@@ -58,7 +59,7 @@ def _install_ranges() -> None:
     for name in ("linear", "norm", "glu", "rope_kv", "attn_decode", "attn_prefill_paged", "attn_paged_biased", "attention",
                  "embedding", "argmax", "quant_fp8_act", "grouped_linear", "grouped_linear_dynamic", "moe_route",
                  "moe_dispatch", "moe_dispatch_dynamic", "moe_combine", "mla_prep", "mla_attn", "colbatched_linear",
-                 "dit_qkv", "gated_residual", "cfg_euler_step", "causal_conv3d", "gguf_linear", "selective_scan"):
+                 "dit_qkv", "gated_residual", "cfg_euler_step", "causal_conv3d", "gguf_linear", "selective_scan", "sample_tokens"):
         fn = getattr(core, name, None)
         if fn is None:
             continue

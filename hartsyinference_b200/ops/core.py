@@ -543,6 +543,33 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     return out
 
 
+def sample_tokens(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                  min_p: torch.Tensor, seed: torch.Tensor, counter: torch.Tensor) -> torch.Tensor:
+    """One token per row of ``logits`` [rows, vocab] (fp32 or bf16): temperature -> top-k -> top-p ->
+    min-p -> draw, all on the device. Per-row parameters: ``temperature`` fp32 (<= 0: argmax),
+    ``top_k`` int32 (<= 0: off), ``top_p`` / ``min_p`` fp32 (<= 0: off), ``seed`` / ``counter`` int64
+    (the draw is a pure function of the two, so a request's stream is reproducible). int32 [rows]."""
+    rows, vocab = logits.shape
+    if not logits.is_cuda:
+        out = torch.empty(rows, dtype=torch.int32)
+        for r in range(rows):
+            t = float(temperature[r])
+            if t <= 0:
+                out[r] = int(logits[r].float().argmax())
+                continue
+            keep = R.sampling_keep_mask(logits[r], t, int(top_k[r]), float(top_p[r]), float(min_p[r]))
+            lg = (logits[r].float() / max(t, 1e-6)).masked_fill(~keep, float("-inf"))
+            g = torch.Generator().manual_seed((int(seed[r]) * 1000003 + int(counter[r])) % (2 ** 63))
+            out[r] = int(torch.multinomial(torch.softmax(lg, -1), 1, generator=g)[0])
+        return out
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    assert logits.stride(1) == 1 and logits.dtype in (torch.float32, torch.bfloat16)
+    N.check(N.lib().b200_sample(logits.data_ptr(), 1 if logits.dtype == torch.float32 else 0, logits.stride(0), rows, vocab,
+                                temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(),
+                                seed.data_ptr(), counter.data_ptr(), out.data_ptr(), N.stream()), "b200_sample")
+    return out
+
+
 def repetition_penalty_(logits: torch.Tensor, history: torch.Tensor, hist_len: torch.Tensor,
                         penalty: torch.Tensor) -> torch.Tensor:
     """In place: logits[b, t] /= p if > 0 else *= p for every token id t in history[b, :hist_len[b]]."""

@@ -274,3 +274,24 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, n_
     if norm_topk:
         w = w / (w.sum(-1, keepdim=True) + 1e-20)
     return ids.to(torch.int32), w * scale
+
+
+def sampling_keep_mask(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float) -> torch.Tensor:
+    """Tokens that survive temperature -> top-k -> top-p -> min-p for one row of fp32 logits, with
+    ties at a cut kept (the statement the device sampler is checked against). Returns a bool mask."""
+    lg = logits.float() / max(temperature, 1e-6)
+    w = torch.exp(lg - lg.max())
+    keep = torch.ones_like(w, dtype=torch.bool)
+    if 0 < top_k < w.numel():
+        kth = torch.topk(w, top_k).values[-1]
+        keep &= w >= kth
+    if 0.0 < top_p < 1.0:
+        ws = torch.where(keep, w, torch.zeros_like(w))
+        sp, _ = torch.sort(ws, descending=True)
+        cum = torch.cumsum(sp.double(), 0)
+        limit = top_p * float(ws.double().sum())
+        first_over = int((cum > limit).nonzero()[0]) if bool((cum > limit).any()) else w.numel() - 1
+        keep &= w >= sp[first_over]
+    if min_p > 0.0:
+        keep &= w >= min(min_p, 1.0)
+    return keep
