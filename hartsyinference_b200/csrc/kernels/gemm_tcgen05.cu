@@ -95,7 +95,43 @@ struct AllReduceParams {
   // `res` is then the replicated residual stream and is only read (the new stream is `out`).
   int large;
   const __nv_bfloat16* gate;         // [features], may be null
+  // Reduce-scatter form of the large-token case (sequence-parallel regions): the result rows this
+  // rank owns go to `out_local` ([owned rows][features], local memory) and nowhere else; `res` is
+  // then the rank's block of the residual stream, indexed from the first owned row.
+  __nv_bfloat16* out_local;
 };
+
+// All-gather -> GEMM for the column-parallel linears of a sequence-parallel region (more than 128
+// tokens): every rank holds a contiguous block of ceil(m / world) token rows (activations, and for
+// fp8 their scales). One kernel per linear:
+//   1. the epilogue warps of all CTAs copy the rank's block into the same rows of EVERY rank's
+//      gather buffer (multimem.st through the NVSwitch, or one store per peer), then the rank's last
+//      CTA raises the rank's arrival counter on every rank;
+//   2. the TMA producer waits for the arrival counters of the ranks whose rows a token tile covers
+//      before it loads that tile from the LOCAL gather buffer; tiles are walked starting with the
+//      rank's own rows, so the tensor core works on local data while the peers' rows arrive;
+//   3. when the rank's last CTA is through, it raises `done` on every rank; the copy phase of the
+//      next call waits for the `done` of all ranks before it overwrites the gather buffers.
+// Counters are cumulative (capturable in CUDA graphs); every wait is bounded.
+struct GatherParams {
+  int rank, world;
+  int use_mc;                         // 1: entries [0] of the destination arrays are multicast aliases
+  int rows_total, rows_per_rank;      // rank r owns rows [r * rows_per_rank, ...) of rows_total
+  const uint8_t* src;                 // local block [rows][row_bytes]
+  long long row_bytes;                // bytes of one activation row (a multiple of 16)
+  uint8_t* dst[8];                    // every rank's gather buffer [rows_total][row_bytes]
+  // scales of an fp8 operand: fp32 [rows][k / 128] (sf_words = 0) or the blocked UE8M0 layout, one
+  // 32-bit word per (row, group of four 128-wide K blocks) (sf_words = words per row = k groups)
+  const uint32_t* src_scale;
+  uint32_t* dst_scale[8];
+  int scale_words;                    // fp32 scales per row (fp32 mode)
+  int sf_words;                       // > 0: blocked UE8M0 layout
+  uint32_t* flags[8];                 // per rank: [0, 8) arrival of source rank s, [8] done
+  uint32_t* flags_local;
+  uint32_t* ctr;                      // local: [0] calls completed, [1] CTAs past the copy, [2] CTAs finished
+  long long wait_budget;
+};
+constexpr int kAgFlagDone = 8;
 
 struct GemmParams {
   int rows_a;          // rows of the A operand (tiled by 128)
@@ -163,6 +199,8 @@ struct GemmParams {
   int sa_gran, sa_ld, sb_gran, sb_ld;
   DeviceStatus* status;
   AllReduceParams ar;   // ar.world == 0: plain GEMM
+  GatherParams ag;      // ag.world == 0: the A operand is complete when the kernel starts
+  int ta_rotate;        // plain GEMM: A tiles are walked starting with this one
 };
 
 constexpr int kTileA = 128;
@@ -244,6 +282,10 @@ __device__ __forceinline__ WorkItem decode_item(const GemmParams& p, long long w
   } else {
     it.tb = static_cast<int>(tile / tiles_a);
     it.skip = false;
+    if (p.ta_rotate > 0) {
+      it.ta += p.ta_rotate;
+      if (it.ta >= tiles_a) it.ta -= tiles_a;
+    }
   }
   return it;
 }
@@ -559,7 +601,7 @@ __device__ __forceinline__ void ar_finish(const GemmParams& p, GemmBarriers* bar
 #pragma unroll
       for (int i = 0; i < 4; ++i) pw[i] = pack_bf16x2(acc[2 * i], acc[2 * i + 1]);
       if (active && a.res) {
-        __nv_bfloat16* rr = a.res + static_cast<long long>(row) * n + v * 8;
+        __nv_bfloat16* rr = a.res + static_cast<long long>(a.out_local ? ri : row) * n + v * 8;
         float t[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) t[i] = 0.f;
@@ -624,7 +666,8 @@ __device__ __forceinline__ void ar_finish(const GemmParams& p, GemmBarriers* bar
         uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
         for (int i = 0; i < 4; ++i) ow[i] = pack_bf16x2(y[2 * i], y[2 * i + 1]);
-        if (a.out_bf16[0]) ar_store_all(a, a.out_bf16, rbase + v * 8, o, 16);
+        if (a.out_local) *reinterpret_cast<uint4*>(a.out_local + static_cast<long long>(ri) * n + v * 8) = o;
+        else if (a.out_bf16[0]) ar_store_all(a, a.out_bf16, rbase + v * 8, o, 16);
         // fp8 consumers see the bf16-rounded activations, like the unfused path
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] = 0.f;
@@ -704,6 +747,95 @@ __device__ __forceinline__ void ar_finish(const GemmParams& p, GemmBarriers* bar
         !wait_flag_geq(a.flags_local + 1, call * static_cast<uint32_t>(a.world), a.wait_budget))
       report_status(p.status, kWaitTimeout, kKernelGemmAllReduce, 2, blockIdx.x);
   }
+}
+
+// ---- all-gather -> GEMM (see GatherParams) --------------------------------------------------------
+// Copy phase, run by the 256 epilogue threads of every CTA before their first tile.
+__device__ __forceinline__ void ag_copy(const GemmParams& p, GemmBarriers* bars) {
+  const GatherParams& g = p.ag;
+  const int et = threadIdx.x - 64;
+  const uint32_t call = *reinterpret_cast<volatile uint32_t*>(g.ctr) + 1u;
+  // the gather buffers still hold the previous call's rows until every rank is done with them
+  if (et == 0) {
+    bool ok = true;
+    if (call > 1) ok = wait_flag_geq(g.flags_local + kAgFlagDone, (call - 1u) * static_cast<uint32_t>(g.world), g.wait_budget);
+    if (!ok) report_status(p.status, kWaitTimeout, kKernelAllToAll, 11, blockIdx.x);
+    bars->flag = ok ? 1u : 0u;
+  }
+  epilogue_barrier();
+  const bool ok = bars->flag != 0;
+  epilogue_barrier();
+  const int row0 = g.rank * g.rows_per_rank;
+  const int rows = max(0, min(g.rows_per_rank, g.rows_total - row0));
+  if (ok) {
+    const long long vec_per_row = g.row_bytes >> 4;
+    const long long nvec = static_cast<long long>(rows) * vec_per_row;
+    const long long base = static_cast<long long>(row0) * g.row_bytes;
+    for (long long v = static_cast<long long>(blockIdx.x) * 256 + et; v < nvec; v += static_cast<long long>(gridDim.x) * 256) {
+      const uint4 x = *reinterpret_cast<const uint4*>(g.src + v * 16);
+      if (g.use_mc) {
+        multimem_st_v4(g.dst[0] + base + v * 16, x);
+      } else {
+        for (int r = 0; r < g.world; ++r) *reinterpret_cast<uint4*>(g.dst[(g.rank + r) % g.world] + base + v * 16) = x;
+      }
+    }
+    if (g.src_scale != nullptr) {
+      const int wpr = g.sf_words > 0 ? g.sf_words : g.scale_words;
+      const long long nw = static_cast<long long>(rows) * wpr;
+      for (long long i = static_cast<long long>(blockIdx.x) * 256 + et; i < nw; i += static_cast<long long>(gridDim.x) * 256) {
+        const int r = static_cast<int>(i / wpr), c = static_cast<int>(i - static_cast<long long>(r) * wpr);
+        long long si, di;
+        if (g.sf_words > 0) {
+          // blocked layout: [row tile of 128][k group][(row % 32) * 4 + (row % 128) / 32]
+          const int gr = row0 + r;
+          si = (static_cast<long long>(r >> 7) * wpr + c) * 128 + (r & 31) * 4 + ((r & 127) >> 5);
+          di = (static_cast<long long>(gr >> 7) * wpr + c) * 128 + (gr & 31) * 4 + ((gr & 127) >> 5);
+        } else {
+          si = i;
+          di = static_cast<long long>(row0) * wpr + i;
+        }
+        const uint32_t w = g.src_scale[si];
+        if (g.use_mc) {
+          multimem_st_b32(g.dst_scale[0] + di, w);
+        } else {
+          for (int q = 0; q < g.world; ++q) g.dst_scale[(g.rank + q) % g.world][di] = w;
+        }
+      }
+    }
+  }
+  // the stores went to other GPUs: system-wide before the count lets another CTA announce them
+  __threadfence_system();
+  epilogue_barrier();
+  if (et == 0) {
+    __threadfence();
+    if (atomicAdd(g.ctr + 1, 1u) == gridDim.x - 1) {
+      __threadfence();
+      if (g.use_mc) {
+        multimem_red_release_add(g.flags[0] + g.rank, 1u);
+      } else {
+        fence_acq_rel_sys();
+        for (int r = 0; r < g.world; ++r) red_relaxed_sys_add(g.flags[(g.rank + r) % g.world] + g.rank, 1u);
+      }
+    }
+  }
+}
+
+// Producer side: the rows of A tile `ta` have arrived from the ranks that own them. `seen` caches the
+// sources already found complete in this call.
+__device__ __forceinline__ bool ag_wait_tile(const GemmParams& p, int ta, uint32_t call, uint32_t& seen) {
+  const GatherParams& g = p.ag;
+  const int first = (ta * kTileA) / g.rows_per_rank;
+  const int last = min(g.world - 1, (min(g.rows_total, (ta + 1) * kTileA) - 1) / g.rows_per_rank);
+  bool waited = false;
+  for (int s = first; s <= last; ++s) {
+    if (seen & (1u << s)) continue;
+    if (!wait_flag_geq(g.flags_local + s, call, g.wait_budget)) return false;
+    seen |= 1u << s;
+    waited = true;
+  }
+  // the rows arrived as ordinary (or multimem) stores; the loads that follow are issued by the TMA unit
+  if (waited) asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
 }
 
 // Second kernel of a fully split GEMM: one thread per four output values, grid.y = tile. Sums the
@@ -859,9 +991,17 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
       } else {
         pdl_wait();
       }
+      const uint32_t ag_call = p.ag.world > 0 ? *reinterpret_cast<volatile uint32_t*>(p.ag.ctr) + 1u : 0u;
+      uint32_t ag_seen = 0;
       for (long long w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
         const WorkItem it = decode_item(p, w, tiles_a, total_kblocks);
         if (it.skip) continue;
+        if (p.ag.world > 0 && !ag_wait_tile(p, it.ta, ag_call, ag_seen)) {
+          report_status(p.status, kWaitTimeout, kKernelAllToAll, 12, blockIdx.x);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
         int kb = it.kb0;
         if (w == w_first && pre > 0) kb += pre * kAtoms;      // already issued above
         for (; kb < it.kb1; kb += kAtoms) {
@@ -979,6 +1119,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
     // Two warps share each TMEM lane quarter; they split the accumulator columns in 32-column
     // chunks (even chunks -> first warp, odd chunks -> second warp).
     pdl_wait();
+    if (p.ag.world > 0) ag_copy(p, bars);
     const int q = warp & 3;            // TMEM lane quarter this warp may read
     const int hsel = (warp - 2) >> 2;  // which half of the chunks
     constexpr int kChunks = (BN + 31) / 32;
@@ -1177,6 +1318,24 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (p.ag.world > 0 && threadIdx.x == 0) {
+    // the last CTA to finish tells every rank that this rank no longer reads its gather buffer and
+    // closes the call (every CTA has read the call counter by now)
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.ag.ctr);
+    __threadfence();
+    if (atomicAdd(p.ag.ctr + 2, 1u) == gridDim.x - 1) {
+      p.ag.ctr[1] = 0;
+      p.ag.ctr[2] = 0;
+      *reinterpret_cast<volatile uint32_t*>(p.ag.ctr) = e + 1u;
+      __threadfence();
+      if (p.ag.use_mc) {
+        multimem_red_release_add(p.ag.flags[0] + kAgFlagDone, 1u);
+      } else {
+        fence_acq_rel_sys();
+        for (int r = 0; r < p.ag.world; ++r) red_relaxed_sys_add(p.ag.flags[(p.ag.rank + r) % p.ag.world] + kAgFlagDone, 1u);
+      }
+    }
+  }
   if (p.ar.world > 0 && threadIdx.x == 0) {
     // the last CTA to finish closes the call: every CTA has read the call counter by now
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.ar.ctr);
@@ -1309,7 +1468,7 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
                      const float* w_scale, const void* bias, const void* gate, const void* residual,
                      int act, int splits, void* workspace, long long workspace_bytes, void* status,
                      cudaStream_t stream, const AllReduceParams* ar, const GroupSpec* gs = nullptr,
-                     const ConvSpec* cs = nullptr, int* defer_info = nullptr) {
+                     const ConvSpec* cs = nullptr, int* defer_info = nullptr, const GatherParams* ag = nullptr) {
   const int groups = gs ? gs->groups : 0;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   // grouped: x is [groups * m][k], w is [groups * n][k], out is [groups * m][n]; m = tokens per group
@@ -1356,6 +1515,14 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
     splits = s_ar < 1 || ar->large ? 1 : s_ar;
   }
 
+  if (ag != nullptr) {
+    // the gathered operand is the 128-row MMA operand: the large-token orientation only
+    if (swap || groups > 0 || cs != nullptr || ar != nullptr) return -11;
+    p.ag = *ag;
+    // start with the tiles of this rank's own rows
+    p.ta_rotate = (ag->rank * ag->rows_per_rank) / kTileA;
+    splits = 1;
+  }
   int bn;
   const void *a_ptr, *b_ptr;
   long long lda, ldb;
@@ -1589,7 +1756,9 @@ B200_API int b200_gemm_deferred(const void* x, const void* w, void* out, int m, 
 // for m <= 128 tokens and n a multiple of 128. For m > 128 (prefill, DiT sequences; norm_w and out_q
 // must be null) the reduce phase is  out_bf16 = res + gate * (s + bias)  with `res` the replicated
 // residual stream (read only) and `gate` an optional per-feature factor; `part` then holds
-// [m][n] bf16. See
+// [m][n] bf16. With `out_local` (reduce-scatter form) only the rows this rank owns (a contiguous
+// block of ceil(m / world)) are produced, into out_local [owned][n], and `res` is the rank's block
+// of the residual stream. See
 // AllReduceParams for the protocol. `part_src`, `out_*`, `flags` are arrays of `world` peer
 // pointers into the symmetric heap (index = rank), or, with use_mc = 1, arrays whose entry 0 is
 // the multicast alias of the buffer. `part` (partials), `flags_local` (two u32) and `ctr`
@@ -1607,11 +1776,11 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
                                  int sf_tile_rows, void* const* flags, void* flags_local, void* ctr,
                                  int rank, int world, int use_mc, int part_splits,
                                  long long wait_budget_cycles, int debug_skip_ready, const void* gate,
-                                 void* status, cudaStream_t stream) {
+                                 void* out_local, void* status, cudaStream_t stream) {
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return -7;
   const bool large = m > 128;
   if (large && (norm_w != nullptr || out_q != nullptr)) return -7;   // the large-token form is elementwise
-  if (!large && gate != nullptr) return -7;
+  if (!large && (gate != nullptr || out_local != nullptr)) return -7;
   if (part == nullptr || part_src == nullptr || flags == nullptr || flags_local == nullptr || ctr == nullptr) return -7;
   if (out_q != nullptr && (out_sf == nullptr || n % 128 != 0)) return -7;
   if (n / 8 > 256 * kArMaxSegs) return -7;   // row segments of the reduce phase
@@ -1641,8 +1810,51 @@ B200_API int b200_gemm_allreduce(const void* x, const void* w, int m, int n, int
   ar.debug_skip_ready = debug_skip_ready;
   ar.large = large ? 1 : 0;
   ar.gate = static_cast<const __nv_bfloat16*>(gate);
+  ar.out_local = static_cast<__nv_bfloat16*>(out_local);
   return gemm_impl(x, w, nullptr, m, n, k, ldx, ldw, n, dtype, x_scale, w_scale, nullptr, nullptr,
                    nullptr, 0, 1, nullptr, 0, status, stream, &ar);
+}
+
+// Column-parallel linear of a sequence-parallel region fused with the all-gather of its input (see
+// GatherParams): every rank passes its block of token rows (rank r owns rows [r * per, (r + 1) * per)
+// of m, per = ceil(m / world)) and gets out[m][n] = X[m][k] * w[n][k]^T (+ bias, activation) for all m
+// tokens and its own n output features. x_local: [rows][k] bf16 (dtype 0) or e4m3 (1, 2) with
+// x_scale_local fp32 [rows][k / 128] (dtype 1) or blocked UE8M0 words for the local rows (dtype 2).
+// gather / gather_scale / flags: arrays of `world` peer pointers into the symmetric heap (index =
+// rank), or with use_mc = 1 arrays whose entry 0 is the multicast alias; gather_local,
+// gather_scale_local, flags_local (16 u32) and ctr (16 u32) are this rank's own, zeroed once.
+B200_API int b200_allgather_gemm(const void* x_local, const void* x_scale_local, const void* w, void* out, int m, int n,
+                                 int k, long long ldw, long long ldc, int dtype, const float* w_scale, const void* bias,
+                                 int act, void* const* gather, void* gather_local, void* const* gather_scale,
+                                 void* gather_scale_local, void* const* flags, void* flags_local, void* ctr, int rank,
+                                 int world, int use_mc, long long wait_budget_cycles, void* status, cudaStream_t stream) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || m <= 128) return -7;
+  if (gather == nullptr || gather_local == nullptr || flags == nullptr || flags_local == nullptr || ctr == nullptr) return -7;
+  const int esz = dtype != 0 ? 1 : 2;
+  if ((static_cast<long long>(k) * esz) % 16 != 0) return -2;
+  if (dtype != 0 && (gather_scale == nullptr || gather_scale_local == nullptr || x_scale_local == nullptr)) return -7;
+  GatherParams g{};
+  g.rank = rank;
+  g.world = world;
+  g.use_mc = use_mc ? 1 : 0;
+  g.rows_total = m;
+  g.rows_per_rank = (m + world - 1) / world;
+  g.src = static_cast<const uint8_t*>(x_local);
+  g.row_bytes = static_cast<long long>(k) * esz;
+  g.src_scale = static_cast<const uint32_t*>(x_scale_local);
+  g.scale_words = dtype == 1 ? k / 128 : 0;
+  g.sf_words = dtype == 2 ? (k + 511) / 512 : 0;
+  const int np = use_mc ? 1 : world;
+  for (int r = 0; r < np; ++r) {
+    g.dst[r] = static_cast<uint8_t*>(gather[r]);
+    g.dst_scale[r] = gather_scale ? static_cast<uint32_t*>(gather_scale[r]) : nullptr;
+    g.flags[r] = static_cast<uint32_t*>(flags[r]);
+  }
+  g.flags_local = static_cast<uint32_t*>(flags_local);
+  g.ctr = static_cast<uint32_t*>(ctr);
+  g.wait_budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
+  return gemm_impl(gather_local, w, out, m, n, k, k, ldw, ldc, dtype, static_cast<const float*>(gather_scale_local), w_scale,
+                   bias, nullptr, nullptr, act, 1, nullptr, 0, status, stream, nullptr, nullptr, nullptr, nullptr, &g);
 }
 
 // Convolution as ONE tcgen05 GEMM without an im2col buffer. The input is a zero-padded,

@@ -95,28 +95,43 @@ class FusedRowParallel:
         vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
         self._fn = N.bind("b200_gemm_allreduce", i32,
                           [vp, vp, i32, i32, i32, i64, i64, i32, vp, vp, vp, vp, vp, f32, i32, vp, vp, vp, vp, vp,
-                           i32, vp, vp, vp, i32, i32, i32, i32, i64, i32, vp, vp, vp])
+                           i32, vp, vp, vp, i32, i32, i32, i32, i64, i32, vp, vp, vp, vp])
         self.budget_cycles = int(config.get("wait_budget_ms")) * 2_000_000
         self.debug_skip_ready = False    # tests: withhold this rank's "ready" signal once per call
 
     def supports_large(self, m: int, n: int) -> bool:
         return MAX_TOKENS < m <= self.max_large_tokens and n <= self.max_features and n % 128 == 0
 
+    def owned_rows(self, m: int) -> tuple[int, int]:
+        """The block of ``m`` token rows this rank owns in the reduce-scatter / all-gather forms."""
+        per = (m + self.world - 1) // self.world
+        a = min(m, self.rank * per)
+        return a, min(m, a + per)
+
     def large(self, x, w: LinearWeight, *, res: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-              slot: Optional[int] = None) -> torch.Tensor:
+              slot: Optional[int] = None, scatter_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Row-parallel linear over more than 128 tokens fused with its all-reduce and the gated
         residual add: returns ``res + gate * (sum over ranks of x_r w_r^T + bias)`` ([m, n] bf16) on
         every rank, a view of output buffer ``slot`` (one of LARGE_SLOTS; default: they take turns).
         The view is valid until a later call names the same slot; ``res`` may be the view returned by
         an earlier call with a different slot. ``res`` ([m, n] bf16, the replicated residual stream)
-        and ``gate`` ([n] bf16) are optional."""
+        and ``gate`` ([n] bf16) are optional.
+
+        Reduce-scatter form (``scatter_out`` given: a local [owned rows, n] bf16 tensor, see
+        :meth:`owned_rows`): only this rank's block of the result is produced, into ``scatter_out``
+        (which is returned), and ``res`` is the rank's block of the residual stream."""
         if w.is_fp8 and not isinstance(x, Fp8Act):
             x = ops.quant_fp8_act(x, mx=w.is_mx)
         xd = x.data if isinstance(x, Fp8Act) else x
         m, k = xd.shape
         n = w.weight.shape[0]
         assert self.supports_large(m, n), (m, n, self.max_large_tokens)
-        assert res is None or (res.is_contiguous() and res.shape == (m, n) and res.dtype == torch.bfloat16)
+        rows = m
+        if scatter_out is not None:
+            a, b = self.owned_rows(m)
+            rows = b - a
+            assert scatter_out.is_contiguous() and scatter_out.shape == (rows, n) and scatter_out.dtype == torch.bfloat16
+        assert res is None or (res.is_contiguous() and res.shape == (rows, n) and res.dtype == torch.bfloat16)
         assert gate is None or (gate.is_contiguous() and gate.numel() == n and gate.dtype == torch.bfloat16)
         if slot is None:
             slot = self._next_large
@@ -130,8 +145,10 @@ class FusedRowParallel:
                       N.ptr(w.bias), N.ptr(res), None, 0.0, 0,
                       self._part_large, self._part_large_src, self._out_large[slot], None, None, 0,
                       self._flags, self._flags_local, self._ctr, self.rank, self.world, 1 if self.use_mc else 0, 1,
-                      self.budget_cycles, 0, N.ptr(gate), st.status.data_ptr(), N.stream())
+                      self.budget_cycles, 0, N.ptr(gate), N.ptr(scatter_out), st.status.data_ptr(), N.stream())
         N.check(rc, "b200_gemm_allreduce")
+        if scatter_out is not None:
+            return scatter_out
         return self.heap.tensor(self.off_out_large[slot], (m, n), torch.bfloat16)
 
     def reset(self) -> None:
@@ -177,7 +194,7 @@ class FusedRowParallel:
                       self._q[slot] if emit_fp8 else None, self._sf[slot] if emit_fp8 else None,
                       128 if mx_out else 0, self._flags, self._flags_local, self._ctr,
                       self.rank, self.world, 1 if self.use_mc else 0, PART_SPLITS, self.budget_cycles,
-                      1 if self.debug_skip_ready else 0, None, st.status.data_ptr(), N.stream())
+                      1 if self.debug_skip_ready else 0, None, None, st.status.data_ptr(), N.stream())
         N.check(rc, "b200_gemm_allreduce")
         h = self.heap.tensor(self.off_bf16[slot], (m, n), torch.bfloat16) if emit_bf16 else None
         h8 = None
@@ -188,6 +205,90 @@ class FusedRowParallel:
             else:
                 h8 = Fp8Act(q, self.heap.tensor(self.off_sf[slot], (m, n // 128), torch.float32))
         return h, h8
+
+    def close(self) -> None:
+        self.heap.close()
+
+
+class FusedColumnParallel:
+    """All-gather -> GEMM in one kernel (``b200_allgather_gemm``, csrc/kernels/gemm_tcgen05.cu) for the
+    column-parallel linears of a sequence-parallel region: every rank passes its block of token rows
+    (:meth:`owned_rows`), the kernel copies it into every rank's gather buffer (``multimem.st``) while
+    the tensor core starts on the rank's own rows, and the TMA producer waits per token tile for the
+    ranks that own its rows. Returns the rank's output features for ALL tokens. More than 128 tokens.
+
+    The reference has no sequence-parallel linears; its tensor-parallel DiT path replicates the
+    activations and all-reduces after every row-parallel linear
+    (src/HartsyInference.Diffusion/Models/Denoisers/TensorParallelDiT.cs)."""
+
+    def __init__(self, comm: Comm, max_tokens: int, max_k: int, device: Optional[torch.device] = None):
+        self.comm, self.rank, self.world = comm, comm.rank, comm.world
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.max_tokens, self.max_k = int(max_tokens), int(max_k)
+        tiles = (self.max_tokens + 127) // 128
+        act_bytes = tiles * 128 * self.max_k * 2
+        sf_bytes = max(tiles * 128 * ((self.max_k + 127) // 128) * 4, tiles * ((self.max_k + 511) // 512) * 512)
+        self.heap = SymmetricHeap(comm, act_bytes + sf_bytes + 8192, self.device)
+        self.use_mc = self.heap.has_multicast
+        self.off_act = self.heap.alloc(act_bytes, align=1024)
+        self.off_sf = self.heap.alloc(sf_bytes, align=1024)
+        self.off_flags = self.heap.alloc(256)
+        self.off_ctr = self.heap.alloc(256)
+        self._sf_bytes = sf_bytes
+        # exponent bytes of rows that no rank writes (the tail of the last 128-row tile) must be finite
+        self.heap.tensor(self.off_sf, (sf_bytes,), torch.uint8).fill_(127)
+        torch.cuda.synchronize(self.device)
+        comm.barrier()
+        arr = self.heap.mc_array if self.use_mc else self.heap.ptr_array
+        self._act, self._sf, self._flags = arr(self.off_act), arr(self.off_sf), arr(self.off_flags)
+        self._act_local = self.heap.ptr(self.rank, self.off_act)
+        self._sf_local = self.heap.ptr(self.rank, self.off_sf)
+        self._flags_local = self.heap.ptr(self.rank, self.off_flags)
+        self._ctr = self.heap.ptr(self.rank, self.off_ctr)
+        vp, i32, i64 = C.c_void_p, C.c_int, C.c_longlong
+        self._fn = N.bind("b200_allgather_gemm", i32,
+                          [vp, vp, vp, vp, i32, i32, i32, i64, i64, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32,
+                           i32, i64, vp, vp])
+        self.budget_cycles = int(config.get("wait_budget_ms")) * 2_000_000
+
+    def owned_rows(self, m: int) -> tuple[int, int]:
+        per = (m + self.world - 1) // self.world
+        a = min(m, self.rank * per)
+        return a, min(m, a + per)
+
+    def supports(self, m: int, k: int) -> bool:
+        return MAX_TOKENS < m <= self.max_tokens and k <= self.max_k
+
+    def __call__(self, x_local, w: LinearWeight, m: int, act: Optional[str] = None) -> torch.Tensor:
+        """``x_local``: this rank's block of the ``m`` token rows ([rows, k] bf16, or an :class:`Fp8Act`
+        when ``w`` is fp8). Returns [m, n_local] bf16."""
+        if w.is_fp8 and not isinstance(x_local, Fp8Act):
+            x_local = ops.quant_fp8_act(x_local, mx=w.is_mx)
+        xd = x_local.data if isinstance(x_local, Fp8Act) else x_local
+        a, b = self.owned_rows(m)
+        k = xd.shape[1]
+        assert xd.shape[0] == b - a and xd.is_contiguous() and self.supports(m, k), (xd.shape, m, a, b)
+        n = w.weight.shape[0]
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
+        fp8 = w.is_fp8
+        sc = None if not fp8 else x_local.sf if w.is_mx else x_local.scale
+        st = N.state(self.device)
+        rc = self._fn(xd.data_ptr(), N.ptr(sc), w.weight.data_ptr(), out.data_ptr(), m, n, k, w.weight.stride(0), n,
+                      2 if w.is_mx else 1 if fp8 else 0,
+                      None if not fp8 else w.sf.data_ptr() if w.is_mx else w.scale.data_ptr(), N.ptr(w.bias),
+                      {None: 0, "none": 0, "gelu_tanh": 1, "silu": 2}[act], self._act, self._act_local, self._sf,
+                      self._sf_local, self._flags, self._flags_local, self._ctr, self.rank, self.world,
+                      1 if self.use_mc else 0, self.budget_cycles, st.status.data_ptr(), N.stream())
+        N.check(rc, "b200_allgather_gemm")
+        return out
+
+    def reset(self) -> None:
+        torch.cuda.synchronize(self.device)
+        self.comm.barrier()
+        self.heap.tensor(self.off_flags, (64,), torch.int32).zero_()
+        self.heap.tensor(self.off_ctr, (64,), torch.int32).zero_()
+        torch.cuda.synchronize(self.device)
+        self.comm.barrier()
 
     def close(self) -> None:
         self.heap.close()

@@ -18,7 +18,7 @@ from hartsyinference_b200.models.llm.transformer import DecoderModel, ForwardBat
 from hartsyinference_b200.ops import _native as N
 from hartsyinference_b200.ops import reference as R
 from hartsyinference_b200.parallel import init_comm
-from hartsyinference_b200.parallel.fused import FusedRowParallel, enable_fused_tp
+from hartsyinference_b200.parallel.fused import FusedColumnParallel, FusedRowParallel, enable_fused_tp
 
 
 def rel(a, b):
@@ -93,6 +93,32 @@ def main():
                     wb[r * per:(r + 1) * per] = biases[r].float()
                 want = res.float() + gate.float() * (part - bias_all + wb)
                 assert rel(y, want) < 1.5e-2, ("large", fp8, m, it, rel(y, want))
+    # ---- a sequence-parallel MLP: all-gather -> GEMM (column-parallel, gelu), GEMM -> reduce-scatter
+    # (row-parallel, gated residual on the rank's rows), against the same MLP on one GPU
+    colp = FusedColumnParallel(comm, 1200, 1024, dev)
+    gen = torch.Generator(device="cpu").manual_seed(21)
+    for fp8 in (False, True):
+        for m in (1100, 300):
+            hdim, fdim = 1024, 2048
+            x_full = (torch.randn(m, hdim, generator=gen) * 0.5).to(torch.bfloat16).to(dev)       # same on all ranks
+            w1 = (torch.randn(fdim, hdim, generator=gen) * 0.05).to(torch.bfloat16).to(dev)
+            w2 = (torch.randn(hdim, fdim, generator=gen) * 0.05).to(torch.bfloat16).to(dev)
+            b1 = torch.randn(fdim, generator=gen).to(torch.bfloat16).to(dev)
+            gate = torch.randn(hdim, generator=gen).to(torch.bfloat16).to(dev)
+            fl = fdim // world
+            lw1 = ops.LinearWeight.from_dense(w1[rank * fl:(rank + 1) * fl].contiguous(), b1[rank * fl:(rank + 1) * fl].contiguous(), fp8=fp8)
+            lw2 = ops.LinearWeight.from_dense(w2[:, rank * fl:(rank + 1) * fl].contiguous(), fp8=fp8)
+            a, b = colp.owned_rows(m)
+            for it in range(2):
+                h = colp(x_full[a:b].contiguous(), lw1, m, act="gelu_tanh")                         # [m, fl]
+                out = torch.empty(b - a, hdim, dtype=torch.bfloat16, device=dev)
+                big.large(h, lw2, res=x_full[a:b].contiguous(), gate=gate, scatter_out=out)
+                N.check_status(dev)
+                hh = torch.nn.functional.gelu(x_full.float() @ w1.float().t() + b1.float(), approximate="tanh").to(torch.bfloat16).float()
+                want = x_full.float() + gate.float() * (hh @ w2.float().t())
+                assert rel(out, want[a:b]) < (6e-2 if fp8 else 2e-2), ("sp-mlp", fp8, m, it, rel(out, want[a:b]))
+    comm.barrier()
+    colp.close()
     comm.barrier()
     big.close()
     # ---- peer-memory all-reduce kernel vs NCCL, eager and under a CUDA graph

@@ -14,7 +14,7 @@ from hartsyinference_b200.exceptions import DeviceWaitTimeout
 from hartsyinference_b200.ops import _native as N
 from hartsyinference_b200.ops import reference as R
 from hartsyinference_b200.parallel.comm import SingleComm
-from hartsyinference_b200.parallel.fused import FusedRowParallel
+from hartsyinference_b200.parallel.fused import FusedColumnParallel, FusedRowParallel
 
 
 def _rel(a, b):
@@ -150,6 +150,35 @@ def test_large_token_form_matches_fp32(fp8):
         assert _rel(y, ops.linear(x, lw, splits=1)) < 1e-2
     finally:
         f.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fp8", [False, True])
+def test_allgather_gemm_and_reduce_scatter_single_rank(fp8):
+    """One rank owns all rows: the copy into the gather buffer, the per-tile arrival waits, the tile
+    rotation and the reduce-scatter store path all run; results match the plain linear."""
+    torch.manual_seed(6)
+    col = FusedColumnParallel(SingleComm(), 700, 1024)
+    row = FusedRowParallel(SingleComm(), 768, max_large_tokens=700)
+    try:
+        for m, k in ((300, 512), (640, 1024), (129, 256), (300, 512)):
+            n = 768
+            x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+            lw = ops.LinearWeight.from_dense((torch.randn(n, k, device="cuda") * 0.2).to(torch.bfloat16),
+                                             torch.randn(n, device="cuda").to(torch.bfloat16), fp8=fp8)
+            want = ops.linear(x, lw, act="gelu_tanh")
+            got = col(x, lw, m, act="gelu_tanh")
+            N.check_status()
+            assert _rel(got, want) < 1e-2, (m, k, _rel(got, want))
+            res = torch.randn(m, n, device="cuda").to(torch.bfloat16)
+            gate = torch.randn(n, device="cuda").to(torch.bfloat16)
+            out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            row.large(x, lw, res=res, gate=gate, scatter_out=out)
+            N.check_status()
+            assert _rel(out, res.float() + gate.float() * ops.linear(x, lw).float()) < 1e-2
+    finally:
+        col.close()
+        row.close()
 
 
 @pytest.mark.gpu
