@@ -98,6 +98,7 @@ declare("fp8_linears", bool, True, "quantise eligible linears to 128x128 block-s
 declare("tc_attention", bool, True, "dense non-causal attention with head dim 128 on the tcgen05 kernel instead of the mma.sync one")
 declare("fa_attention", bool, True, "dense non-causal head-dim-128 attention on the two-query-tile tcgen05 kernel (S / P / O resident in TMEM); off = the older one-tile tcgen05 kernel")
 declare("fused_dit_tp", bool, True, "tensor-parallel DiT: row-parallel linears run as one GEMM + all-reduce + gated-residual kernel; off = GEMM, NCCL all-reduce, gated residual")
+declare("fused_dit_sp", bool, True, "tensor-parallel DiT blocks keep activations sharded by token rows between the linears (all-gather -> GEMM, GEMM -> reduce-scatter kernels); off = replicated activations")
 declare("fused_cfg_combine", bool, True, "CFG-parallel video pipelines combine the two branches with the peer-memory kernel; off = NCCL all_gather")
 declare("fused_ulysses", bool, True, "sequence-parallel attention exchanges heads inside the quantisation / attention kernels (peer stores into the symmetric heap); off = NCCL all-to-all")
 declare("sage_attention", bool, False, "int8 Q K^T (SageAttention: K mean removal, per-row int8 scales, tcgen05 kind::i8) in the dense attention kernel")

@@ -860,9 +860,12 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
   // A stage holds kAtoms swizzle atoms (128 bytes of K each) per operand: [A atoms][B atoms].
   // kMode: 0 = bf16, 1 = e4m3 with fp32 block scales promoted by the epilogue warps per k-block,
   // 2 = e4m3 with UE8M0 block scales applied by the tensor core (kind::mxf8f6f4.block_scale).
-  constexpr bool kFp8Data = kMode != 0;
+  // 3 = int8 operands (W8A8): s32 accumulation over the whole K in TMEM, one scale per token row and
+  // one per output channel applied by the epilogue.
+  constexpr bool kFp8Data = kMode != 0;            // one-byte operands
   constexpr bool kFp8 = kMode == 1;                // software promotion
   constexpr bool kMx = kMode == 2;
+  constexpr bool kI8 = kMode == 3;
   constexpr int kAtomBytesB = BN * 128;
   constexpr int kSfBytes = kMx ? 1536 : 0;         // per stage: SF block of A + up to two of B
   constexpr int kStageBytes = kAtoms * (kStageBytesA + kAtomBytesB) + (kMx ? 2048 : 0);
@@ -880,6 +883,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
   constexpr uint32_t kTmemCols = kTmemNeed <= 32 ? 32 : kTmemNeed <= 64 ? 64 : kTmemNeed <= 128 ? 128
                                : kTmemNeed <= 256 ? 256 : 512;
   constexpr uint32_t kIdesc = kMx ? make_idesc_mx(128, BN)
+                            : kI8 ? make_idesc(128, BN, kFmtS8, kFmtS8, 2)
                             : kFp8Data ? make_idesc(128, BN, kFmtE4m3, kFmtE4m3)
                                        : make_idesc(128, BN, kFmtBf16, kFmtBf16);
   static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256,
@@ -1087,6 +1091,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
                 const uint32_t slot = tmem_base + kSfCol + (((kb + a) >> 2) & 1) * 16;
                 mma_mxf8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc | (sf_id << 29) | (sf_id << 4), acc,
                             slot, slot + 4);
+              } else if (kI8) {
+                mma_i8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
               } else if (kFp8Data) {
                 mma_fp8_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
               } else {
@@ -1145,8 +1151,18 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_a
               tmem_ld_32x32(lane_base + abuf * kBufStride + c * 32, r);
               tmem_ld_wait();
               float v[32];
+              if constexpr (kI8) {
+                // s32 accumulators -> fp32 with the row scale of the A operand and the row scales of
+                // the 32 B rows of this chunk (whichever of the two is the token side)
+                const float sa = p.scale_a[min(it.ta * kTileA + row_local, p.rows_a - 1)];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                for (int j = 0; j < 32; ++j)
+                  v[j] = static_cast<float>(static_cast<int>(r[j])) * sa *
+                         __ldg(p.scale_b + min(it.tb * BN + c * 32 + j, p.rows_b - 1));
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              }
               if (p.cluster_reduce) {
                 // partial of this CTA's K range, kept in its own shared memory: [BN columns][128 rows]
                 // fp32 over the (now idle) pipeline stages
@@ -1472,13 +1488,15 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   const int groups = gs ? gs->groups : 0;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   // grouped: x is [groups * m][k], w is [groups * n][k], out is [groups * m][n]; m = tokens per group
-  const bool fp8 = dtype != 0;          // 1: fp32 block scales, 2: UE8M0 scale factors (blocked layout)
+  const bool i8 = dtype == 3;           // int8 operands, one fp32 scale per x row and per w row
+  const bool fp8 = dtype != 0;          // one-byte operands. 1: fp32 block scales, 2: UE8M0 scale factors (blocked layout)
   const bool mx = dtype == 2;
   const int esz = fp8 ? 1 : 2;
   const int kelems = fp8 ? 128 : 64;
   if ((ldx * esz) % 16 != 0 || (ldw * esz) % 16 != 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -3;
-  if (fp8 && ((!mx && k % 128 != 0) || k % 16 != 0 || !x_scale || !w_scale)) return -4;
+  if (fp8 && ((!mx && !i8 && k % 128 != 0) || k % 16 != 0 || !x_scale || !w_scale)) return -4;
+  if (i8 && (groups > 0 || cs != nullptr || ar != nullptr)) return -4;
   if (groups > 0) {
     if (m < 1 || m > 128 || n % 128 != 0) return -9;
     if (gs->b_koff > 0) {
@@ -1550,8 +1568,8 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   } else {
     p.rows_a = m; p.rows_b = n;
     a_ptr = x; lda = ldx; b_ptr = w; ldb = ldw;
-    bn = fp8 ? 128 : 256;
-    if (!fp8 && n <= 128) bn = 128;
+    bn = fp8 && !i8 ? 128 : 256;
+    if ((!fp8 || i8) && n <= 128) bn = 128;
     p.scale_a = x_scale; p.sa_gran = 1;   p.sa_ld = k / 128;
     p.scale_b = w_scale; p.sb_gran = 128; p.sb_ld = k / 128;
   }
@@ -1650,7 +1668,23 @@ int gemm_impl(const void* x, const void* w, void* out, int m, int n, int k, long
   const int grid = p.cluster_reduce ? static_cast<int>(items) : static_cast<int>(items < sms ? items : sms);
   (void)cluster;
 
-  if (mx) {
+  if (i8) {
+    // scales: one per row of either operand
+    p.sa_gran = p.sb_gran = 1;
+    p.sa_ld = p.sb_ld = 1;
+    if (swap) {
+      switch (bn) {
+        case 16: rc = launch_gemm<3, 16, 2>(p, ta, tb, grid, stream); break;
+        case 32: rc = launch_gemm<3, 32, 2>(p, ta, tb, grid, stream); break;
+        case 64: rc = launch_gemm<3, 64, 2>(p, ta, tb, grid, stream); break;
+        default: rc = launch_gemm<3, 128, 2>(p, ta, tb, grid, stream); break;
+      }
+    } else if (bn == 128) {
+      rc = launch_gemm<3, 128, 1>(p, ta, tb, grid, stream);
+    } else {
+      rc = launch_gemm<3, 256, 1>(p, ta, tb, grid, stream);
+    }
+  } else if (mx) {
     if (swap) {
       switch (bn) {
         case 16: rc = launch_gemm<2, 16, 2>(p, ta, tb, grid, stream); break;

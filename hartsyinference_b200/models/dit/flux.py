@@ -266,11 +266,99 @@ class FluxTransformer:
                 self._fused_rp = False
         return self._fused_rp or None
 
+    def _fused_cols(self, tokens: int):
+        """The all-gather -> GEMM kernel (parallel/fused.py) for ``tokens`` rows of width H, or None."""
+        cur = getattr(self, "_fused_cp", None)
+        if cur is None or (cur is not False and cur.max_tokens < tokens):
+            from ...parallel.fused import FusedColumnParallel
+            try:
+                if cur:
+                    cur.close()
+                self._fused_cp = FusedColumnParallel(self.comm, tokens, self.cfg.hidden_size, self.device)
+            except Exception as e:
+                log.warn(f"[TensorParallel] all-gather GEMM kernel unavailable ({type(e).__name__}: {e})")
+                self._fused_cp = False
+        return self._fused_cp or None
+
     def close(self) -> None:
-        cur = getattr(self, "_fused_rp", None)
-        if cur:
-            cur.close()
-        self._fused_rp = None
+        for name in ("_fused_rp", "_fused_cp"):
+            cur = getattr(self, name, None)
+            if cur:
+                cur.close()
+            setattr(self, name, None)
+
+    def _forward_sp(self, img, txt, timestep, pooled, img_ids, txt_ids, guidance, rp, cp):
+        """Sequence-parallel form of :meth:`forward` for one sample on a tensor-parallel group: between
+        the row-parallel and the column-parallel linears every rank keeps only its block of token
+        rows, so norms, modulations, gated residuals and activation quantisation run on 1 / tp of the
+        rows. Row-parallel linears end in a reduce-scatter inside the GEMM kernel (``rp.large`` with
+        ``scatter_out``), column-parallel linears start with an all-gather inside the GEMM kernel
+        (``cp``). Attention sees all tokens of the rank's heads, as before."""
+        cfg = self.cfg
+        S_i, S_t = img.shape[1], txt.shape[1]
+        S = S_t + S_i
+        H, D = cfg.hidden_size, cfg.head_dim
+        dt = torch.bfloat16
+        temb = self.time_embedding(timestep, guidance, pooled)
+        temb_act = silu(temb)
+        cos, sin = rope_tables(torch.cat([txt_ids, img_ids], 0).to(self.device), cfg.axes_dim, cfg.theta)
+        cos_t, sin_t, cos_i, sin_i = cos[:S_t].contiguous(), sin[:S_t].contiguous(), cos[S_t:].contiguous(), sin[S_t:].contiguous()
+        (ai, bi_), (at, bt_) = rp.owned_rows(S_i), rp.owned_rows(S_t)
+        x_i = ops.linear(img.reshape(S_i, -1)[ai:bi_].to(dt).contiguous(), self.x_embedder)        # the rank's image rows
+        x_t = ops.linear(txt.reshape(S_t, -1)[at:bt_].to(dt).contiguous(), self.context_embedder)  # the rank's text rows
+
+        def pre(x, w, mod, rows_total, c, s_):
+            xn, _, xq = ops.norm(x, None, shift=mod[:, 0:H], scale=mod[:, H:2 * H], rows_per_batch=x.shape[0], layernorm=True,
+                                 emit_fp8=self.fp8 and w.qkv.is_fp8, emit_bf16=not (self.fp8 and w.qkv.is_fp8))
+            qkv = cp(xq if xq is not None else xn, w.qkv, rows_total)
+            return ops.dit_qkv(qkv, self.hl, self.hl, D, q_norm_w=w.q_norm, k_norm_w=w.k_norm, cos=c, sin=s_)
+
+        def post(x, a, w, mod, rows_total):
+            x = rp.large(a, w.proj, res=x, gate=mod[0, 2 * H:3 * H].contiguous(), scatter_out=torch.empty_like(x))
+            xn, _, xq = ops.norm(x, None, shift=mod[:, 3 * H:4 * H], scale=mod[:, 4 * H:5 * H], rows_per_batch=x.shape[0],
+                                 layernorm=True, emit_fp8=self.fp8 and w.mlp_in.is_fp8,
+                                 emit_bf16=not (self.fp8 and w.mlp_in.is_fp8))
+            h = cp(xq if xq is not None else xn, w.mlp_in, rows_total, act="gelu_tanh")
+            return rp.large(h, w.mlp_out, res=x, gate=mod[0, 5 * H:6 * H].contiguous(), scatter_out=torch.empty_like(x))
+
+        for bi, (wi, wt) in enumerate(self._blocks(self.double, "double")):
+            mod_i, mod_t = self._mod(temb_act, wi.mod, "img", bi), self._mod(temb_act, wt.mod, "txt", bi)
+            qi, ki, vi = pre(x_i, wi, mod_i, S_i, cos_i, sin_i)
+            qt, kt, vt = pre(x_t, wt, mod_t, S_t, cos_t, sin_t)
+            att = self._attend(torch.cat([qt, qi], 0), torch.cat([kt, ki], 0), torch.cat([vt, vi], 0), 1)
+            x_i = post(x_i, att[S_t:].contiguous(), wi, mod_i, S_i)
+            x_t = post(x_t, att[:S_t].contiguous(), wt, mod_t, S_t)
+
+        # the single blocks work on the joint sequence [txt | img], cut into blocks of rows again
+        def gather_rows(x, rows_total):
+            per = (rows_total + self.tp - 1) // self.tp
+            pad = torch.zeros(per, H, dtype=dt, device=self.device)
+            pad[:x.shape[0]] = x
+            return self.comm.all_gather(pad, dim=0)[:rows_total]
+
+        aj, bj = rp.owned_rows(S)
+        if self.single:
+            joint = torch.cat([gather_rows(x_t, S_t), gather_rows(x_i, S_i)], 0)[aj:bj].contiguous()
+            qkv_cols = 3 * self.hl * D
+            for si, w in enumerate(self._blocks(self.single, "single")):
+                mod = self._mod(temb_act, w.mod, "single", si)
+                xn, _, xq = ops.norm(joint, None, shift=mod[:, 0:H], scale=mod[:, H:2 * H], rows_per_batch=joint.shape[0],
+                                     layernorm=True, emit_fp8=self.fp8 and w.qkv_mlp.is_fp8,
+                                     emit_bf16=not (self.fp8 and w.qkv_mlp.is_fp8))
+                fused = cp(xq if xq is not None else xn, w.qkv_mlp, S)                       # [S, 3 Hl D + mlp_l]
+                q, k, v = ops.dit_qkv(fused[:, :qkv_cols], self.hl, self.hl, D, q_norm_w=w.q_norm, k_norm_w=w.k_norm,
+                                      cos=cos, sin=sin)
+                att = self._attend(q, k, v, 1)
+                mlp = torch.nn.functional.gelu(fused[:, qkv_cols:].float(), approximate="tanh").to(dt)
+                joint = rp.large(torch.cat([att, mlp], 1), w.out, res=joint, gate=mod[0, 2 * H:3 * H].contiguous(),
+                                 scatter_out=torch.empty_like(joint))
+            x_img = gather_rows(joint, S)[S_t:]
+        else:
+            x_img = gather_rows(x_i, S_i)
+        mo = self._final_mod(temb_act)
+        xn, _, _ = ops.norm(x_img.contiguous(), None, shift=mo[:, H:2 * H], scale=mo[:, 0:H], rows_per_batch=S_i, layernorm=True)
+        out = ops.linear(xn, self.proj_out)
+        return out.reshape(1, S_i, cfg.latent_channels)
 
     def _row_parallel(self, a, w, x, gate, rows_per_batch, fused, slot):
         """x + gate * all_reduce(a w^T + bias): one fused kernel where it applies."""
@@ -296,6 +384,15 @@ class FluxTransformer:
         S_t = txt.shape[1]
         H, D = cfg.hidden_size, cfg.head_dim
         dt = torch.bfloat16
+        if (self.tp > 1 and B == 1 and hidden_in is None and step_cache is None and control is None and collect is None
+                and self.has_head and self.block_range == (0, cfg.num_double_blocks + cfg.num_single_blocks)
+                and min(S_i, S_t) > 128 and not getattr(self, "_streamers", None) and config.get("fused_dit_sp")):
+            rp = self._fused_rows(S_i + S_t)
+            cp = self._fused_cols(S_i + S_t) if rp is not None else None
+            if rp is not None and cp is not None:
+                self.comm_path = ("sequence-parallel blocks: all-gather -> GEMM and GEMM -> reduce-scatter kernels ("
+                                  + ("multimem" if rp.use_mc else "peer loads") + ")")
+                return self._forward_sp(img, txt, timestep, pooled, img_ids, txt_ids, guidance, rp, cp)
         temb = self.time_embedding(timestep, guidance, pooled)
         temb_act = silu(temb)
         cos, sin = rope_tables(torch.cat([txt_ids, img_ids], 0).to(self.device), cfg.axes_dim, cfg.theta)

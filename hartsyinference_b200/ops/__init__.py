@@ -9,6 +9,7 @@ default bodies) collapses into this module plus ``torch.Tensor``.
 from .core import (  # noqa: F401
     Fp8Act,
     GgufWeight,
+    Int8Weight,
     LinearWeight,
     argmax,
     attention,
@@ -25,6 +26,7 @@ from .core import (  # noqa: F401
     gated_residual,
     glu,
     gguf_linear,
+    int8_linear,
     grouped_linear,
     grouped_linear_dynamic,
     moe_block_capacity,
@@ -38,6 +40,7 @@ from .core import (  # noqa: F401
     mla_prep,
     norm,
     quant_fp8_act,
+    quant_int8_act,
     quant_fp8_weight,
     repetition_penalty_,
     rope_kv,

@@ -119,6 +119,88 @@ class LinearWeight:
         return LinearWeight(w, None, None if bias is None else bias.to(torch.bfloat16))
 
 
+@dataclass
+class Int8Weight:
+    """W8A8 linear weight: int8 [N, K] with one fp32 scale per output row, optionally stored rotated
+    (ConvRot: ``W H^T`` per group of ``convrot_group`` input features, see assets/int8_convrot.py) and
+    with per-input-channel SmoothQuant factors ``inv_smooth`` [K] applied to the activations."""
+    weight: torch.Tensor
+    row_scale: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+    convrot_group: int = 0
+    inv_smooth: Optional[torch.Tensor] = None
+
+    @staticmethod
+    def from_dense(w: torch.Tensor, bias: Optional[torch.Tensor] = None, convrot_group: int = 0) -> "Int8Weight":
+        from ..assets.int8_convrot import quantize_weight
+        q, s = quantize_weight(w.float().cpu(), convrot_group)
+        return Int8Weight(q.to(w.device).contiguous(), s.to(w.device), None if bias is None else bias.to(torch.bfloat16),
+                          convrot_group)
+
+    def nbytes(self) -> int:
+        return self.weight.numel() + self.row_scale.numel() * 4 + (0 if self.bias is None else self.bias.numel() * 2)
+
+    @property
+    def out_features(self) -> int:
+        return self.weight.shape[0]
+
+    @property
+    def in_features(self) -> int:
+        return self.weight.shape[1]
+
+
+def quant_int8_act(x: torch.Tensor, convrot_group: int = 0, inv_smooth: Optional[torch.Tensor] = None):
+    """bf16 [M, K] -> (int8 [M, K], fp32 row scales [M]) after the optional SmoothQuant factors and the
+    ConvRot rotation; one kernel on the device."""
+    if not x.is_cuda:
+        from ..assets.int8_convrot import quantize_activation
+        return quantize_activation(x, convrot_group, inv_smooth)
+    m, k = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    q = torch.empty(m, k, dtype=torch.int8, device=x.device)
+    sc = torch.empty(m, dtype=torch.float32, device=x.device)
+    N.check(N.lib().b200_quant_int8_rows(x.data_ptr(), q.data_ptr(), sc.data_ptr(), N.ptr(inv_smooth), m, k, x.stride(0), k,
+                                         int(convrot_group), N.stream()), "b200_quant_int8_rows")
+    return q, sc
+
+
+def int8_linear(x: torch.Tensor, w: Int8Weight, act: Optional[str] = None, gate: Optional[torch.Tensor] = None,
+                residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = residual + gate * act((x H) (W H^T)^T + bias) with int8 operands and s32 accumulation on the
+    tensor core (tcgen05 kind::i8); the two scale vectors are applied by the GEMM epilogue. Replaces the
+    reference's cublasLt int8 GEMM + dequant pass (src/HartsyInference.Cuda/Kernels/dequant/w8a8.cu,
+    int8_mma_gemm.cu:221)."""
+    q, sc = quant_int8_act(x, w.convrot_group, w.inv_smooth)
+    m, k = q.shape
+    n = w.weight.shape[0]
+    if not x.is_cuda:
+        y = (q.float() @ w.weight.float().t()) * sc[:, None] * w.row_scale.float()[None, :]
+        if w.bias is not None:
+            y = y + w.bias.float()
+        if act == "gelu_tanh":
+            y = R.gelu_tanh(y)
+        elif act == "silu":
+            y = torch.nn.functional.silu(y)
+        if gate is not None:
+            y = y * gate.float()
+        if residual is not None:
+            y = y + residual.float()
+        y = y.to(torch.bfloat16)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    st = N.state(x.device)
+    ws = st.gemm_workspace()
+    rc = N.lib().b200_gemm(q.data_ptr(), w.weight.data_ptr(), out.data_ptr(), m, n, k, q.stride(0), w.weight.stride(0),
+                           out.stride(0), 3, sc.data_ptr(), w.row_scale.data_ptr(), N.ptr(w.bias), N.ptr(gate), N.ptr(residual),
+                           _ACT[act], 0, ws.data_ptr(), ws.numel(), st.status.data_ptr(), N.stream())
+    N.check(rc, "b200_gemm")
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 def quant_fp8_act(x: torch.Tensor, tile_rows: int = 128, mx: Optional[bool] = None) -> Fp8Act:
     """bf16 [M, K] -> e4m3 with one scale per 128 consecutive K values (fp32, or UE8M0 in the
@@ -199,6 +281,10 @@ def linear(x, w: LinearWeight, act: Optional[str] = None, gate: Optional[torch.T
         if act is not None or gate is not None or residual is not None or isinstance(x, Fp8Act):
             raise ValueError("GGUF block weights take bf16 activations and no fused epilogue")
         return gguf_linear(x, w, out=out)
+    if isinstance(w, Int8Weight):
+        if isinstance(x, Fp8Act):
+            raise ValueError("int8 weights take bf16 activations")
+        return int8_linear(x, w, act, gate, residual, out)
     xd = x.data if isinstance(x, Fp8Act) else x
     if not xd.is_cuda:
         if isinstance(x, Fp8Act):
