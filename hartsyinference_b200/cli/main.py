@@ -222,6 +222,24 @@ def restore(model, image, out, tile, device):
     click.echo(f"{out}: {res.width}x{res.height}")
 
 
+@cli.command(name="3d")
+@click.argument("model")
+@click.argument("image")
+@click.option("--out", default="mesh.glb", help=".obj, .ply or .glb")
+@click.option("--resolution", default=256, help="lattice points per axis of the density field")
+@click.option("--threshold", default=None, type=float, help="density iso level (model default when omitted)")
+@click.option("--device", default="auto")
+def mesh3d(model, image, out, resolution, threshold, device):
+    """Reconstruct a textured mesh from one image (TripoSR checkpoints)."""
+    from ..engine.inference_engine import InferenceEngine
+    from ..engine.requests import MeshRequest
+    eng = InferenceEngine(device)
+    res = eng.mesh.run(ModelSpec(model, Modality.MESH, local_path=model),
+                       MeshRequest(image=image, resolution=resolution, threshold=threshold, output_path=out))
+    click.echo(f"{out}: {len(res.vertices)} vertices, {len(res.faces)} faces "
+               f"(triplane {res.meta['triplane_s']:.2f} s, field + surface {res.meta['mesh_s']:.2f} s)")
+
+
 @cli.command()
 @click.argument("model")
 @click.argument("text")

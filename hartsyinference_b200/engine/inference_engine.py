@@ -57,7 +57,7 @@ def parse_backend_selector(selector: str) -> tuple[str, list[int]]:
 
 
 class InferenceEngine:
-    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH, Modality.RESTORE, Modality.MUSIC}
+    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH, Modality.RESTORE, Modality.MUSIC, Modality.MESH}
 
     def __init__(self, backend_selector: str = "auto", options: Optional[EngineOptions] = None, ranks="auto"):
         self.options = options or EngineOptions()
@@ -182,7 +182,11 @@ class InferenceEngine:
 
     voice_conversion = property(lambda self: self._unsupported("voice conversion"))
     fx = property(lambda self: self._unsupported("fx"))
-    mesh = property(lambda self: self._unsupported("mesh"))
+    @property
+    def mesh(self):
+        from .mesh_service import MeshService
+        return self._service("mesh", lambda: MeshService(self.device))
+
     world = property(lambda self: self._unsupported("world"))
 
     # ------------------------------------------------------------------------------ memory

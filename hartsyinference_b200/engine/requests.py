@@ -185,6 +185,38 @@ class RestoreRequest:
 
 
 @dataclass
+class MeshRequest:
+    """Single image -> mesh. ``image``: path, PIL image, uint8 HWC array or float CHW tensor (RGBA inputs
+    are composited on mid-grey). ``resolution``: lattice points per axis (0 = the model's default);
+    ``threshold``: density iso level (None = the model's default)."""
+    image: Optional[Any] = None
+    resolution: int = 0
+    threshold: Optional[float] = None
+    foreground_ratio: float = 0.85
+    output_path: Optional[str] = None    # .obj / .ply / .glb
+
+
+@dataclass
+class MeshResult:
+    vertices: Any = None                 # float32 [V, 3]
+    faces: Any = None                    # int64 [F, 3]
+    colors: Any = None                   # float32 [V, 3] in [0, 1]
+    meta: dict = field(default_factory=dict)
+
+    def save(self, path: str) -> None:
+        from ..threed import writers
+        ext = str(path).lower().rsplit(".", 1)[-1]
+        if ext == "obj":
+            writers.write_obj(path, self.vertices, self.faces)
+        elif ext == "ply":
+            writers.write_ply(path, self.vertices, self.faces, self.colors)
+        elif ext == "glb":
+            writers.write_glb(path, self.vertices, self.faces, colors=self.colors)
+        else:
+            raise ValueError(f"unknown mesh format '.{ext}' (obj, ply, glb)")
+
+
+@dataclass
 class VisionRequest:
     """``operation``: "embed" (CLIP / SigLIP / DINOv2 image features, CLIP text features and their
     similarity when both are given), "depth" (Depth Anything; one map per image) or "segment" (CLIPSeg:

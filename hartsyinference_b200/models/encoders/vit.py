@@ -22,7 +22,7 @@ from ..dit.common import WeightFactory
 
 @dataclass(frozen=True)
 class VitConfig:
-    kind: str = "siglip"          # siglip | dinov2
+    kind: str = "siglip"          # siglip | dinov2 | vit (Hugging Face ViTModel names: DINO v1, the image tokenizer of TripoSR)
     image_size: int = 224
     patch: int = 16
     width: int = 768
@@ -83,6 +83,10 @@ class VitEncoder:
             if sig:
                 qkv = [p + f"self_attn.{n}_proj" for n in ("q", "k", "v")]
                 o, n1, n2, fc1, fc2 = p + "self_attn.out_proj", p + "layer_norm1", p + "layer_norm2", p + "mlp.fc1", p + "mlp.fc2"
+            elif cfg.kind == "vit":
+                qkv = [p + f"attention.attention.{n}" for n in ("query", "key", "value")]
+                o, n1, n2 = p + "attention.output.dense", p + "layernorm_before", p + "layernorm_after"
+                fc1, fc2 = p + "intermediate.dense", p + "output.dense"
             else:
                 qkv = [p + f"attention.attention.{n}" for n in ("query", "key", "value")]
                 o, n1, n2, fc1, fc2 = p + "attention.output.dense", p + "norm1", p + "norm2", p + "mlp.fc1", p + "mlp.fc2"
@@ -90,7 +94,7 @@ class VitEncoder:
                      n1=(f.tensor(n1 + ".weight", W, ones=True), f.tensor(n1 + ".bias", W, zeros=True)),
                      n2=(f.tensor(n2 + ".weight", W, ones=True), f.tensor(n2 + ".bias", W, zeros=True)),
                      fc1=f.linear(fc1, cfg.ffn, W), fc2=f.linear(fc2, W, cfg.ffn))
-            if not sig:
+            if cfg.kind == "dinov2":
                 b["ls1"] = f.tensor(p + "layer_scale1.lambda1", W, ones=True)
                 b["ls2"] = f.tensor(p + "layer_scale2.lambda1", W, ones=True)
             self.blocks.append(b)

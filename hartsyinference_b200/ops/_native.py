@@ -59,6 +59,7 @@ _SIGNATURES = {
     "b200_embedding": (i32, [vp, vp, vp, i32, i32, i32, f32, vp]),
     "b200_argmax": (i32, [vp, vp, i32, i32, i64, i32, vp]),
     "b200_quant_int8_rows": (i32, [vp, vp, vp, vp, i64, i32, i64, i64, i32, vp]),
+    "b200_triplane_nerf": (i32, [vp, i32, i32, i32, vp, i64, i32, C.c_float, i64, vp, vp, vp, vp, i32, vp, vp, vp, vp]),
     "b200_sample": (i32, [vp, i32, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]),
     "b200_repetition_penalty": (i32, [vp, vp, vp, i32, i32, i32, vp, vp]),
     "b200_cfg_euler": (i32, [vp, vp, vp, i64, f32, f32, vp]),

@@ -16,6 +16,7 @@ UsageTracker, HartsyInferenceServerOptions (MaxConcurrency 1, MaxQueueDepth 16).
 from __future__ import annotations
 
 import base64
+import os
 import json
 import threading
 import time
@@ -456,6 +457,31 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
         return {"width": res.width, "height": res.height, "meta": res.meta,
                 "png_base64": base64.b64encode(_png(res.rgb, res.width, res.height)).decode()}
 
+    @app.post("/v1/native/mesh")
+    async def native_mesh(request: Request):
+        import io
+        import tempfile
+        from PIL import Image
+        from ..engine.requests import MeshRequest
+        body = await request.json()
+        raw = body.get("image") or ""
+        if not raw:
+            return JSONResponse({"error": {"message": "no image", "type": "bad_request"}}, status_code=400)
+        b64 = raw.split(",", 1)[1] if raw.startswith("data:") else raw
+        img = Image.open(io.BytesIO(base64.b64decode(b64)))
+        fmt = str(body.get("format", "glb")).lower()
+        if fmt not in ("glb", "obj", "ply"):
+            return JSONResponse({"error": {"message": "format must be glb, obj or ply", "type": "bad_request"}}, status_code=400)
+        mreq = MeshRequest(image=img, resolution=int(body.get("resolution", 0)), threshold=body.get("threshold"))
+        with heavy_queue.slot():
+            res = eng.with_vram_cleanup(lambda: eng.mesh.run(resolve(body.get("model"), Modality.MESH), mreq))
+        with tempfile.TemporaryDirectory() as td:
+            path = os.path.join(td, "mesh." + fmt)
+            res.save(path)
+            data = open(path, "rb").read()
+        return {"format": fmt, "vertices": len(res.vertices), "faces": len(res.faces), "meta": res.meta,
+                "mesh_base64": base64.b64encode(data).decode()}
+
     @app.post("/v1/native/vision")
     async def native_vision(request: Request):
         import base64
@@ -548,6 +574,8 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
 
     for route in ("/v1/audio/speech", "/v1/audio/transcriptions", "/v1/native/mesh", "/v1/native/vision",
                   "/v1/native/restore", "/v1/native/world"):
+        if any(getattr(r, "path", None) == route for r in app.routes):
+            continue
         def _make(r):
             async def _nyi():
                 raise UnsupportedModelError(f"{r}: this modality is not built in this engine yet")
