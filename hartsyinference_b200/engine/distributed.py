@@ -58,6 +58,12 @@ class RankContext:
         self._groups: dict[str, ParallelGroups] = {}
         self._handlers: dict[str, Callable[..., Any]] = {}
         self._following = False
+        # a follower whose handler raised says so here; rank 0 looks before every command, so that a
+        # rank that fell out of step ends the next call with an error instead of a hung collective
+        try:
+            self._store = dist.distributed_c10d._get_default_store()
+        except Exception:
+            self._store = None
 
     @staticmethod
     def from_env() -> Optional["RankContext"]:
@@ -141,8 +147,22 @@ class RankContext:
         if self.rank != 0:
             raise CommError("commands are issued by rank 0 only")
         with self.lock:
+            failed = self.follower_failure()
+            if failed:
+                raise CommError(f"a follower rank fell out of step: {failed}")
             self.broadcast((name, args))
             return self._handlers[name](*args)
+
+    def follower_failure(self) -> Optional[str]:
+        """What a follower reported when one of its command handlers raised (None: all in step)."""
+        if self._store is None:
+            return None
+        try:
+            if self._store.check(["spmd/failed"]):
+                return self._store.get("spmd/failed").decode()
+        except Exception:
+            return None
+        return None
 
     def follow(self) -> None:
         """Followers: run rank 0's commands until it sends ``shutdown``."""
@@ -157,6 +177,11 @@ class RankContext:
                 self._handlers[name](*args)
             except Exception as e:      # keep following: rank 0 sees its own copy of the failure
                 log.warn(f"[Placement] follower rank {self.rank}: command {name} failed: {type(e).__name__}: {e}")
+                if self._store is not None:
+                    try:
+                        self._store.set("spmd/failed", f"rank {self.rank}, command {name}: {type(e).__name__}: {e}")
+                    except Exception:
+                        pass
         self._following = False
 
     def shutdown(self) -> None:

@@ -73,7 +73,9 @@ class TextService:
 
     # ------------------------------------------------------------------------------ loading
     def _key(self, spec: ModelSpec) -> str:
-        return f"{spec.local_path or spec.requested}|{self.options.placement.cache_key}|{self.device}"
+        # the same string on every rank of an SPMD engine (rank 0 names models by it in its commands):
+        # the device kind, not the ordinal
+        return f"{spec.local_path or spec.requested}|{self.options.placement.cache_key}|{str(self.device).split(':')[0]}"
 
     def _host(self, spec: ModelSpec) -> _Hosted:
         key = self._key(spec)

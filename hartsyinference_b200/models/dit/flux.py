@@ -414,15 +414,15 @@ class FluxTransformer:
 
         # the fused row-parallel kernel hands out views of its own buffers: not while something
         # (ControlNet residual collection, the step cache) keeps the streams beyond the next block
-        fused = self._fused_rows(B * (S_i + S_t)) if (control is None and collect is None and step_cache is None) else None
+        rp_fused = self._fused_rows(B * (S_i + S_t)) if (control is None and collect is None and step_cache is None) else None
 
         def stream_post(x, a, w: _StreamWeights, mod, S, slot):
-            x = self._row_parallel(a, w.proj, x, mod[:, 2 * H:3 * H], S, fused, slot)
+            x = self._row_parallel(a, w.proj, x, mod[:, 2 * H:3 * H], S, rp_fused, slot)
             xn, _, xq = ops.norm(x, None, shift=mod[:, 3 * H:4 * H], scale=mod[:, 4 * H:5 * H], rows_per_batch=S,
                                  layernorm=True, emit_fp8=self.fp8 and w.mlp_in.is_fp8,
                                  emit_bf16=not (self.fp8 and w.mlp_in.is_fp8))
             h = ops.linear(xq if xq is not None else xn, w.mlp_in, act="gelu_tanh")
-            return self._row_parallel(h, w.mlp_out, x, mod[:, 5 * H:6 * H], S, fused, slot + 1)
+            return self._row_parallel(h, w.mlp_out, x, mod[:, 5 * H:6 * H], S, rp_fused, slot + 1)
 
         whole = self.block_range == (0, cfg.num_double_blocks + cfg.num_single_blocks)
         use_cache = step_cache is not None and step_cache.enabled and whole and len(self.double) > 0
@@ -477,7 +477,7 @@ class FluxTransformer:
                                       cos=cj, sin=sj)
                 att = self._attend(q, k, v, B)
                 mlp = torch.nn.functional.gelu(fused[:, qkv_cols:].float(), approximate="tanh").to(dt)
-                joint = self._row_parallel(torch.cat([att, mlp], 1), w.out, joint, mod[:, 2 * H:3 * H], S, fused, si & 1)
+                joint = self._row_parallel(torch.cat([att, mlp], 1), w.out, joint, mod[:, 2 * H:3 * H], S, rp_fused, si & 1)
                 if collect is not None or (control is not None and control[1]):
                     img_rows = slice(S_t, S) if B == 1 else None
                     if img_rows is None:
