@@ -67,10 +67,12 @@ def run(args, world: int, rank: int, local_rank: int, sampler, metric: str) -> d
         arm()
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, cfg.vocab_size, (args.batch, args.prompt_len), generator=g).tolist()
-    need = args.warmup + args.steps + 4
 
     def client(i: int) -> None:
-        req = TextRequest(prompt_token_ids=prompts[i], greedy=True, ignore_eos=True, max_tokens=min(args.decode_len, need))
+        # the full decode length of the workload: requests that finish their prefill early keep
+        # decoding while the others are still prefilling, so the steady state (every request
+        # decoding) is only reached when each request has tokens left by then
+        req = TextRequest(prompt_token_ids=prompts[i], greedy=True, ignore_eos=True, max_tokens=args.decode_len)
         for _ in eng.text.stream(spec, req):
             pass
 
@@ -93,7 +95,8 @@ def run(args, world: int, rank: int, local_rank: int, sampler, metric: str) -> d
     first = next(i for i, e in enumerate(log0) if e[5] == args.batch)      # the step that finished the last prefill
     a, b = first + 1 + args.warmup, first + 1 + args.warmup + args.steps
     window = log0[a:b]
-    assert all(e[5] == args.batch for e in window)
+    if len(window) < args.steps or not all(e[5] == args.batch for e in window):
+        raise RuntimeError("the steady state (every request decoding) lasted fewer steps than asked for; lower --steps or raise --decode-len")
     wall_ms = (window[-1][0] - log0[a - 1][0]) * 1e3
     dev_ms = max(sum(e[1] for e in lg[a:b]) for lg in logs if lg)
     tokens = args.steps * args.batch
