@@ -149,6 +149,7 @@ def _wan_groups(comm):
     if n == 1:
         return None, None
     half = n // 2
+    # every rank takes part in the creation of every group and keeps the two it belongs to
     groups = [comm.subgroup(list(range(0, half))), comm.subgroup(list(range(half, n)))] if half > 1 else [None, None]
     pairs = [comm.subgroup([i, i + half]) for i in range(half)]
     sp = groups[0 if r < half else 1]

@@ -128,7 +128,110 @@ def _gemm_ar(argv):
     f.close()
 
 
-CASES = {"gemm_ar": _gemm_ar, "attn_dense": _attn_dense, "gemm": _gemm, "grouped": _grouped, "attn_decode": _attn_decode, "mla": _mla}
+def _gemm_ar_large(argv):
+    """gemm_ar_large M N K WORLD: the > 128-token form (GEMM + all-reduce + gated residual in one kernel)
+    for rank 0 of WORLD with this GPU standing in for its peers, against GEMM + gated-residual kernels."""
+    from hartsyinference_b200.parallel.comm import ShardEmulationComm
+    from hartsyinference_b200.parallel.fused import FusedRowParallel
+    m, n, k, world = (int(v) for v in argv[:4])
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    lw = ops.LinearWeight.from_dense((torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16), fp8=True)
+    xq = ops.quant_fp8_act(x)
+    res = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    gate = torch.ones(n, device="cuda", dtype=torch.bfloat16)
+    f = FusedRowParallel(ShardEmulationComm(world), n, torch.device("cuda", 0), emulate_peers=True, max_large_tokens=m)
+    t_fused = _time(lambda: f.large(xq, lw, res=res, gate=gate, slot=0), reps=9)
+    t_plain = _time(lambda: ops.gated_residual(res, ops.linear(xq, lw), gate[None], m), reps=9)
+    print(f"gemm_ar_large {m}x{n}x{k} world {world}: fused {t_fused * 1e3:.1f} us, GEMM + gated residual {t_plain * 1e3:.1f} us "
+          f"({2.0 * m * n * k / t_fused / 1e9:.0f} TFLOP/s fused)")
+    f.close()
+
+
+def _ag_gemm(argv):
+    """ag_gemm M N K: all-gather -> GEMM kernel with one rank (copy into the gather buffer, per-tile
+    arrival waits, tile rotation), against the plain GEMM on the same operands."""
+    from hartsyinference_b200.parallel.comm import SingleComm
+    from hartsyinference_b200.parallel.fused import FusedColumnParallel
+    m, n, k = (int(v) for v in argv[:3])
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    lw = ops.LinearWeight.from_dense((torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16), fp8=True)
+    xq = ops.quant_fp8_act(x)
+    f = FusedColumnParallel(SingleComm(), m, k)
+    t_fused = _time(lambda: f(xq, lw, m), reps=9)
+    t_plain = _time(lambda: ops.linear(xq, lw), reps=9)
+    print(f"ag_gemm {m}x{n}x{k}: fused {t_fused * 1e3:.1f} us, GEMM {t_plain * 1e3:.1f} us")
+    f.close()
+
+
+def _ulysses(argv):
+    """ulysses TOKENS HEADS [int8]: the exchange-fused attention with one rank (operand push into the
+    heap, segment flags, output store, output wait), against the plain attention call."""
+    from hartsyinference_b200.parallel.comm import SingleComm
+    from hartsyinference_b200.parallel.ulysses import FusedUlyssesAttention
+    tokens, heads = (int(v) for v in argv[:2])
+    int8 = len(argv) > 2 and argv[2] == "int8"
+    q, k, v = (torch.randn(tokens, heads, 128, device="cuda").to(torch.bfloat16) for _ in range(3))
+    f = FusedUlyssesAttention(SingleComm(), tokens, heads, int8=int8)
+    t_fused = _time(lambda: f(q, k, v))
+    t_plain = _time(lambda: ops.attention(q, k, v, int8=int8))
+    print(f"ulysses {tokens} x {heads} {'int8' if int8 else 'bf16'}: exchange + attention {t_fused:.3f} ms, attention alone {t_plain:.3f} ms")
+    f.close()
+
+
+def _allreduce(argv):
+    """allreduce M N: the peer-memory all-reduce kernel with one rank (protocol only)."""
+    from hartsyinference_b200.parallel.comm import SingleComm
+    from hartsyinference_b200.parallel.custom_ar import CustomAllReduce
+    m, n = (int(v) for v in argv[:2])
+    car = CustomAllReduce(SingleComm(), m * n)
+    car.input(m, n).normal_()
+    t = _time(lambda: car.reduce(m, n), reps=9)
+    print(f"allreduce {m}x{n} one rank: {t * 1e3:.1f} us")
+    car.close()
+
+
+def _sample(argv):
+    """sample ROWS VOCAB: the device sampler (temperature 0.8, top-k 50, top-p 0.9)."""
+    rows, vocab = (int(v) for v in argv[:2])
+    logits = torch.randn(rows, vocab, device="cuda") * 3
+    f32 = lambda v: torch.full((rows,), v, dtype=torch.float32, device="cuda")
+    args = (f32(0.8), torch.full((rows,), 50, dtype=torch.int32, device="cuda"), f32(0.9), f32(0.0),
+            torch.arange(rows, dtype=torch.int64, device="cuda"), torch.zeros(rows, dtype=torch.int64, device="cuda"))
+    t = _time(lambda: ops.sample_tokens(logits, *args), reps=9)
+    print(f"sample {rows} x {vocab}: {t * 1e3:.1f} us")
+
+
+def _int8(argv):
+    """int8 M N K [GROUP]: W8A8 linear (activation rotation + quantisation kernel, int8 GEMM) against the fp8 linear."""
+    m, n, k = (int(v) for v in argv[:3])
+    group = int(argv[3]) if len(argv) > 3 else 0
+    x = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    w = torch.randn(n, k, device="cuda") * 0.05
+    lw8 = ops.Int8Weight.from_dense(w, None, group)
+    lwf = ops.LinearWeight.from_dense(w.to(torch.bfloat16), fp8=True)
+    t8 = _time(lambda: ops.linear(x, lw8), reps=9)
+    tf = _time(lambda: ops.linear(x, lwf), reps=9)
+    print(f"int8 {m}x{n}x{k} group {group}: W8A8 {t8 * 1e3:.1f} us ({2.0 * m * n * k / t8 / 1e9:.0f} TFLOP/s incl. quantisation), "
+          f"fp8 {tf * 1e3:.1f} us ({2.0 * m * n * k / tf / 1e9:.0f})")
+
+
+def _triplane(argv):
+    """triplane RES: density / colour field of a TripoSR-sized decoder over a RES^3 lattice in one kernel."""
+    from hartsyinference_b200.models.threed.triposr import TRIPOSR, TripoSr
+    from dataclasses import replace
+    res = int(argv[0])
+    cfg = replace(TRIPOSR, depth=0)
+    m = TripoSr(cfg, "cuda")
+    planes = torch.randn(3, 40, 64, 64, device="cuda")
+    t = _time(lambda: m.field(planes, resolution=res))
+    pts = res ** 3
+    flop = pts * 2.0 * (120 * 64 + 8 * 64 * 64 + 64 * 4)
+    print(f"triplane {res}^3 = {pts} points: {t:.2f} ms, {flop / t / 1e9:.1f} TFLOP/s fp32, {pts / t / 1e6:.2f} G points/s")
+
+
+CASES = {"gemm_ar_large": _gemm_ar_large, "ag_gemm": _ag_gemm, "ulysses": _ulysses, "allreduce": _allreduce, "sample": _sample,
+         "int8": _int8, "triplane": _triplane,
+         "gemm_ar": _gemm_ar, "attn_dense": _attn_dense, "gemm": _gemm, "grouped": _grouped, "attn_decode": _attn_decode, "mla": _mla}
 
 
 def main(argv=None) -> int:

@@ -142,9 +142,13 @@ class TorchDistComm(Comm):
         return out
 
     def subgroup(self, ranks: Sequence[int]) -> "TorchDistComm":
-        """Every rank of the parent must call this with the same ``ranks`` lists, in the same order."""
-        g = self._dist.new_group([self.ranks[r] for r in ranks])
-        return TorchDistComm(g, [self.ranks[r] for r in ranks])
+        """Every rank of the parent must call this with the same ``ranks`` lists, in the same order.
+        Returns the communicator on the member ranks and None on the others."""
+        members = [self.ranks[r] for r in ranks]
+        g = self._dist.new_group(members)
+        if self.global_rank not in members:
+            return None
+        return TorchDistComm(g, members)
 
 
 def init_comm(backend: Optional[str] = None, timeout_s: float = 600.0) -> Comm:
