@@ -222,7 +222,7 @@ def main() -> int:
         try:
             from hartsyinference_b200.parallel.fused import enable_fused_tp
             fused = enable_fused_tp(model, comm, max_tokens=max(args.batch, 128),
-                                    autotune_tokens=0 if args.force_fused else args.batch)
+                                    autotune_tokens=0 if args.force_fused else args.batch, large_tokens=8192)
         except Exception as e:  # keep the run alive on NCCL, but say so
             log.warn(f"[Collective] fused TP kernels unavailable ({type(e).__name__}: {e}); using NCCL")
     torch.cuda.synchronize()

@@ -11,15 +11,16 @@ drafts are verified by the engine.
 """
 from __future__ import annotations
 
+import contextlib
 import queue
 import threading
 import time
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Iterator, Optional
 
 import torch
 
-from .. import log
+from .. import config, log
 from ..assets.grammar import JsonGrammar
 from ..models.llm.loader import LoadedLLM, load_llm
 from ..parallel.comm import Comm
@@ -45,6 +46,25 @@ class _Hosted:
     # SPMD: requests of every replica as seen by rank 0: (replica, request id) -> token callback
     remote_callbacks: Optional[dict] = None
     next_replica: int = 0
+    # callers waiting to submit or cancel: the serving loop lets them in between two steps (a Python
+    # lock is not fair: a loop that re-acquires it at once would admit waiting callers one at a time)
+    waiting_callers: int = 0
+    callers_lock: threading.Lock = field(default_factory=threading.Lock)
+
+    @contextlib.contextmanager
+    def admitted(self):
+        """``with h.admitted():`` = ``with h.wake:`` for callers of the serving loop."""
+        with self.callers_lock:
+            self.waiting_callers += 1
+        try:
+            self.wake.acquire()
+        finally:
+            with self.callers_lock:
+                self.waiting_callers -= 1
+        try:
+            yield
+        finally:
+            self.wake.release()
 
 
 class TextService:
@@ -102,7 +122,8 @@ class TextService:
                 # row-parallel linears through the fused GEMM + all-reduce kernels where they measure faster
                 from ..parallel.fused import enable_fused_tp
                 try:
-                    enable_fused_tp(llm.model, comm, autotune_tokens=min(self.options.max_batch, 64))
+                    enable_fused_tp(llm.model, comm, autotune_tokens=min(self.options.max_batch, 64),
+                                    large_tokens=int(config.get("prefill_chunk")))
                 except Exception as e:
                     log.warn(f"[Collective] fused TP kernels unavailable ({type(e).__name__}: {e}); using NCCL")
             eng = LLMEngine(llm.model, page_size=self.options.kv_page_size, max_batch=self.options.max_batch,
@@ -235,6 +256,11 @@ class TextService:
         if h.engine.cuda:
             torch.cuda.set_device(h.engine.device)
         while True:
+            # callers that want the lock get it before the next step (bounded, so that a stuck caller
+            # cannot stop the loop)
+            t_yield = time.perf_counter()
+            while h.waiting_callers > 0 and h.running and time.perf_counter() - t_yield < 0.05:
+                time.sleep(0.0002)
             with h.wake:
                 while h.running and not (h.engine.has_work() or h.remote_callbacks):
                     h.wake.wait(timeout=0.5)
@@ -440,7 +466,7 @@ class TextService:
         ids = self._prompt_ids(llm, req)
         q: "queue.Queue[tuple[int, bool]]" = queue.Queue()
         t0 = time.perf_counter()
-        with h.wake:
+        with h.admitted():
             self._mrope = (None, 0, None)
             ids, embeds, emask = self._multimodal(llm, req, ids)
             pos3, delta, deepstack = self._mrope
@@ -455,7 +481,7 @@ class TextService:
         stop_hit = False
         while True:
             if cancel is not None and cancel.is_set():
-                with h.wake:
+                with h.admitted():
                     self._cancel(h, replica, rid)
                 break
             try:
@@ -475,7 +501,7 @@ class TextService:
                     if cut >= 0:
                         text = text[:cut]
                         stop_hit = True
-                        with h.wake:
+                        with h.admitted():
                             self._cancel(h, replica, rid)
                         break
                     yield TextChunk(ChunkKind.CHUNK, text=piece)
@@ -485,7 +511,7 @@ class TextService:
         if tail and not stop_hit:
             text += tail
             yield TextChunk(ChunkKind.CHUNK, text=tail)
-        with h.wake:
+        with h.admitted():
             r = h.engine.release(rid) if replica == (self.groups.dp_index if self.groups is not None else 0) else None
             if h.remote_callbacks is not None:
                 h.remote_callbacks.pop((replica, rid), None)

@@ -520,6 +520,10 @@ class DecoderModel:
             n = w.out_features
             if self.fused_rp is not None and self.fused_rp.supports(m, n) and x_is_cuda(x):
                 return self.fused_rp(x, w)[0]
+            if self.fused_rp is not None and self.fused_rp.supports_large(m, n) and x_is_cuda(x):
+                # prefill chunks: the same kernel in its large-token form (the view is consumed by the
+                # residual add that follows, long before its output slot comes round again)
+                return self.fused_rp.large(x, w)
             if self.row_parallel_linear is not None and self.fused_rp is None:
                 return self.row_parallel_linear(x, w)
             if self.custom_ar is not None and self.custom_ar.fits(m * n):

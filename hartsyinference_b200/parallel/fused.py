@@ -294,12 +294,15 @@ class FusedColumnParallel:
         self.heap.close()
 
 
-def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_tokens: int = 0) -> bool:
+def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_tokens: int = 0,
+                    large_tokens: int = 0) -> bool:
     """Route the model's row-parallel linears through the fused kernel when the shapes allow it.
     With ``autotune_tokens`` > 0 three ways of running "row-parallel linear, all-reduce, residual
     add, RMSNorm, fp8 quantisation" are timed on this model's o / down projections at that token
     count (the fused kernel; GEMM + peer-memory all-reduce kernel + norm kernel; GEMM + NCCL + norm
-    kernel) and the fastest is kept. Returns True when the fused path is active."""
+    kernel) and the fastest is kept. ``large_tokens`` > 0 also sizes the kernel's form for more than
+    128 tokens (prefill chunks), so that their row-parallel linears end in the in-kernel all-reduce
+    as well. Returns True when the fused path is active."""
     if comm.world <= 1 or not config.get("fused_comm") or config.get("p2p_disable"):
         return False
     hidden = model.cfg.hidden_size
@@ -325,12 +328,14 @@ def enable_fused_tp(model, comm: Comm, max_tokens: int = MAX_TOKENS, autotune_to
             car.close()
             log.decision("TensorParallel", "NCCL all-reduce kept; " + note)
         return False
-    fused = FusedRowParallel(comm, hidden, model.device)
+    fused = FusedRowParallel(comm, hidden, model.device, max_large_tokens=max(0, int(large_tokens)))
 
     def row_parallel(x, w: LinearWeight) -> torch.Tensor:
         m = (x.data if isinstance(x, Fp8Act) else x).shape[0]
         if fused.supports(m, w.weight.shape[0]):
             return fused(x, w)[0]
+        if fused.supports_large(m, w.weight.shape[0]):
+            return fused.large(x, w)
         y = ops.linear(x, w)
         return comm.all_reduce(y)
 
