@@ -405,7 +405,6 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
             }
           }
         }
-        if (p.seg_mode) __threadfence_system();    // the rows went to peers: order them before the count below
       }
     }
   }
@@ -417,8 +416,11 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
     tmem_dealloc(tmem_base, 512);
   }
   if (p.done_ctr != nullptr && threadIdx.x == 0) {
-    // the last CTA of the launch tells every rank that this rank's share of its output is there
-    __threadfence();
+    // the last CTA of the launch tells every rank that this rank's share of its output is there.
+    // The softmax threads' stores to the peers are ordered before this thread by the barrier above;
+    // one system-scope fence here then covers all of them (fences are cumulative), instead of one
+    // fence per storing thread
+    __threadfence_system();
     const unsigned total = gridDim.x * gridDim.y * gridDim.z;
     if (atomicAdd(p.done_ctr, 1u) == total - 1) {
       atomicExch(p.done_ctr, 0u);
@@ -759,11 +761,12 @@ __global__ void __launch_bounds__(256) uly_push_kernel(const UlyPush p) {
     }
   }
 
-  // ---- arrival: the last CTA of the launch adds one to this rank's slot on every destination
-  __threadfence_system();
+  // ---- arrival: the last CTA of the launch adds one to this rank's slot on every destination. The
+  // barrier orders every thread's peer stores before thread 0, whose single system-scope fence then
+  // covers them all (a fence per thread made the kernel wait on `membar` most of the time)
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
+    __threadfence_system();
     const unsigned total = gridDim.x * gridDim.y;
     if (atomicAdd(p.ctr, 1u) == total - 1) {
       atomicExch(p.ctr, 0u);

@@ -8,7 +8,7 @@
 //   min-p   tau = min_p * max w = min_p.
 // The two order statistics are found by a radix search on the bit pattern of w (positive floats
 // order like their bits): three passes of 11 + 11 + 10 bits, each one histogram of counts and of
-// masses in shared memory. The draw walks the vocabulary in index order with a block-wide prefix
+// (fixed-point) masses in shared memory. The draw walks the vocabulary in index order with a block-wide prefix
 // sum of the kept masses. Eight passes over a row that stays in L2.
 //
 // The reference applies the same chain on the host, one request at a time, after copying the logits
@@ -78,13 +78,19 @@ struct RadixState {
   float mass_before;
 };
 
+// Masses are accumulated in 2^-40 fixed point: integer shared-memory atomics are native (float ones are
+// compare-and-swap loops that crawl when most of the vocabulary lands in a few bins) and the sums do
+// not depend on the order of arrival, so a (seed, counter) pair always draws the same token.
+constexpr float kMassScale = 1099511627776.f;        // 2^40
+constexpr float kMassInv = 1.f / 1099511627776.f;
+
 __device__ void radix_level(const SampleParams& p, long long row_off, float mx, float inv_t, float floor_w, int shift, int bits,
-                            unsigned hi_mask, RadixState& st, bool by_count, float target, float* hist_cnt, float* hist_mass,
-                            int* bin_out) {
+                            unsigned hi_mask, RadixState& st, bool by_count, float target, unsigned* hist_cnt,
+                            unsigned long long* hist_mass, int* bin_out) {
   const int nb = 1 << bits;
   for (int b = threadIdx.x; b < nb; b += blockDim.x) {
-    hist_cnt[b] = 0.f;
-    hist_mass[b] = 0.f;
+    hist_cnt[b] = 0u;
+    hist_mass[b] = 0ull;
   }
   __syncthreads();
   for (int i = threadIdx.x; i < p.vocab; i += blockDim.x) {
@@ -93,16 +99,16 @@ __device__ void radix_level(const SampleParams& p, long long row_off, float mx, 
     const unsigned u = __float_as_uint(w);
     if ((u & hi_mask) != st.prefix) continue;
     const int b = (u >> shift) & (nb - 1);
-    atomicAdd(hist_cnt + b, 1.f);
-    atomicAdd(hist_mass + b, w);
+    atomicAdd(hist_cnt + b, 1u);
+    atomicAdd(hist_mass + b, static_cast<unsigned long long>(w * kMassScale));
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     float c = st.count_before, m = st.mass_before;
     int chosen = -1;
     for (int b = nb - 1; b >= 0; --b) {
-      const float bc = hist_cnt[b], bm = hist_mass[b];
-      if (bc == 0.f) continue;
+      if (hist_cnt[b] == 0u) continue;
+      const float bc = static_cast<float>(hist_cnt[b]), bm = static_cast<float>(hist_mass[b]) * kMassInv;
       // by count: the k-th element lies in this bin when the count reaches k here. By mass: the bin
       // holds an element with more than `target` in front of it when the mass in front of the
       // bin's LAST element can exceed the target, which is certain once the whole bin passes it.
@@ -120,8 +126,8 @@ __device__ void radix_level(const SampleParams& p, long long row_off, float mx, 
 
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SampleParams p) {
   __shared__ float red[32];
-  __shared__ float hist_cnt[kSampleBins];
-  __shared__ float hist_mass[kSampleBins];
+  __shared__ unsigned hist_cnt[kSampleBins];
+  __shared__ unsigned long long hist_mass[kSampleBins];
   __shared__ int s_bin;
   __shared__ float s_scan[kSampleThreads / 32];
   __shared__ int s_pick;

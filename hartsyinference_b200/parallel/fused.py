@@ -401,7 +401,7 @@ def _measure_allreduce(comm: Comm, car, tokens: int, hidden: int, dev) -> tuple[
     """Device time (ms, summed over ranks) of one [tokens, hidden] bf16 all-reduce: kernel, NCCL."""
     x = torch.randn(tokens, hidden, device=dev).to(torch.bfloat16)
     times = [_time_graph(lambda: car(x), comm, dev), _time_graph(lambda: comm.all_reduce(x), comm, dev)]
-    t = comm.all_reduce(torch.tensor(times, device=dev, dtype=torch.float32))
+    t = comm.all_reduce(torch.tensor(times, device=dev, dtype=torch.float32)) / comm.world      # mean over ranks: the same decision everywhere
     return float(t[0].item()), float(t[1].item())
 
 
@@ -450,5 +450,5 @@ def _measure_row_parallel(model, comm: Comm, fused: FusedRowParallel, car, token
     # host launch overhead (which differs: one launch against three or four) does not decide.
     times = [_time_graph(fn, comm, dev) for fn in (run_fused, run_car, run_nccl)]
     t = torch.tensor(times, device=dev, dtype=torch.float32)
-    t = comm.all_reduce(t)
+    t = comm.all_reduce(t) / comm.world          # mean over ranks: the same decision everywhere
     return float(t[0].item()), float(t[1].item()), float(t[2].item())
