@@ -70,28 +70,35 @@ __device__ __forceinline__ float block_reduce_max(float v, float* red) {
 // the bins from the top, with `count_before` / `mass_before` already in front:
 //   by_count: stop in the bin where the count reaches `k`
 //   else:     stop in the bin that holds the first element whose mass in front exceeds `limit`
-// Returns the chosen bin through *bin_out (or -1: the walk ran off the end, everything is kept) and
-// updates the running totals to what lies in front of that bin.
-struct RadixState {
-  unsigned prefix;       // bits above the current level
-  float count_before;    // elements in front of the current prefix
-  float mass_before;
-};
-
-// Masses are accumulated in 2^-40 fixed point: integer shared-memory atomics are native (float ones are
-// compare-and-swap loops that crawl when most of the vocabulary lands in a few bins) and the sums do
+// Leaves the chosen bin in sh->bin (-1: the walk ran off the end, everything is kept) and adds what lies
+// in front of that bin to the running totals in `sh`.
+// Masses are accumulated in 2^-40 fixed point: integer shared-memory atomics are native and the sums do
 // not depend on the order of arrival, so a (seed, counter) pair always draws the same token.
 constexpr float kMassScale = 1099511627776.f;        // 2^40
-constexpr float kMassInv = 1.f / 1099511627776.f;
+
+struct RadixState {
+  unsigned prefix;                      // bits above the current level (every thread keeps a copy)
+};
+
+// Block-wide state of the search (shared memory): what lies in front of the current prefix, the
+// chosen bin, and the scratch of the scans.
+struct RadixShared {
+  unsigned count_before;
+  unsigned long long mass_before;       // 2^-40 fixed point
+  int bin;
+  unsigned warp_cnt[kSampleThreads / 32];
+  unsigned long long warp_mass[kSampleThreads / 32];
+};
 
 __device__ void radix_level(const SampleParams& p, long long row_off, float mx, float inv_t, float floor_w, int shift, int bits,
-                            unsigned hi_mask, RadixState& st, bool by_count, float target, unsigned* hist_cnt,
-                            unsigned long long* hist_mass, int* bin_out) {
+                            unsigned hi_mask, const RadixState& st, bool by_count, unsigned long long target, unsigned* hist_cnt,
+                            unsigned long long* hist_mass, RadixShared* sh) {
   const int nb = 1 << bits;
   for (int b = threadIdx.x; b < nb; b += blockDim.x) {
     hist_cnt[b] = 0u;
     hist_mass[b] = 0ull;
   }
+  if (threadIdx.x == 0) sh->bin = -1;
   __syncthreads();
   for (int i = threadIdx.x; i < p.vocab; i += blockDim.x) {
     const float w = __expf((sample_logit(p, row_off, i) - mx) * inv_t);
@@ -103,23 +110,57 @@ __device__ void radix_level(const SampleParams& p, long long row_off, float mx, 
     atomicAdd(hist_mass + b, static_cast<unsigned long long>(w * kMassScale));
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float c = st.count_before, m = st.mass_before;
-    int chosen = -1;
-    for (int b = nb - 1; b >= 0; --b) {
-      if (hist_cnt[b] == 0u) continue;
-      const float bc = static_cast<float>(hist_cnt[b]), bm = static_cast<float>(hist_mass[b]) * kMassInv;
-      // by count: the k-th element lies in this bin when the count reaches k here. By mass: the bin
-      // holds an element with more than `target` in front of it when the mass in front of the
-      // bin's LAST element can exceed the target, which is certain once the whole bin passes it.
-      const bool stop = by_count ? (c + bc >= target) : (m + bm > target);
-      if (stop) { chosen = b; break; }
-      c += bc;
-      m += bm;
-    }
-    st.count_before = c;
-    st.mass_before = m;
-    *bin_out = chosen;
+  // Walk from the top bin down, all bins at once: thread t owns bins 2t and 2t + 1; an inclusive scan
+  // over the threads gives every bin what lies at and above it. By count the wanted bin is the
+  // highest non-empty one at which the count from the top reaches the target; by mass the highest
+  // non-empty one at which the mass from the top exceeds it.
+  const int t = threadIdx.x, lane = t & 31, wid = t >> 5;
+  const unsigned c0 = 2 * t < nb ? hist_cnt[2 * t] : 0u, c1 = 2 * t + 1 < nb ? hist_cnt[2 * t + 1] : 0u;
+  const unsigned long long m0 = 2 * t < nb ? hist_mass[2 * t] : 0ull, m1 = 2 * t + 1 < nb ? hist_mass[2 * t + 1] : 0ull;
+  unsigned pc = c0 + c1;
+  unsigned long long pm = m0 + m1;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned vc = __shfl_up_sync(0xffffffffu, pc, o);
+    const unsigned long long vm = __shfl_up_sync(0xffffffffu, pm, o);
+    if (lane >= o) { pc += vc; pm += vm; }
+  }
+  if (lane == 31) { sh->warp_cnt[wid] = pc; sh->warp_mass[wid] = pm; }
+  __syncthreads();
+  unsigned base_c = 0, total_c = 0;
+  unsigned long long base_m = 0, total_m = 0;
+#pragma unroll 4
+  for (int w = 0; w < kSampleThreads / 32; ++w) {
+    const unsigned wc = sh->warp_cnt[w];
+    const unsigned long long wm = sh->warp_mass[w];
+    if (w < wid) { base_c += wc; base_m += wm; }
+    total_c += wc;
+    total_m += wm;
+  }
+  // inclusive prefix (ascending bins) up to and including this thread's pair -> what lies at and above
+  const unsigned incl_c = base_c + pc;
+  const unsigned long long incl_m = base_m + pm;
+  const unsigned above_c = total_c - incl_c;                  // bins above 2t + 1
+  const unsigned long long above_m = total_m - incl_m;
+  const unsigned before_c = sh->count_before;
+  const unsigned long long before_m = sh->mass_before;
+  // bin 2t + 1, then bin 2t
+  auto hit = [&](unsigned cnt, unsigned front_c, unsigned long long mass, unsigned long long front_m) {
+    if (cnt == 0u) return false;
+    return by_count ? (static_cast<unsigned long long>(before_c) + front_c + cnt >= target) : (before_m + front_m + mass > target);
+  };
+  int mine = -1;
+  if (hit(c1, above_c, m1, above_m)) mine = 2 * t + 1;
+  else if (hit(c0, above_c + c1, m0, above_m + m1)) mine = 2 * t;
+  if (mine >= 0) atomicMax(&sh->bin, mine);
+  __syncthreads();
+  const int chosen = sh->bin;
+  __syncthreads();
+  if (chosen >= 0 && (chosen >> 1) == t) {
+    // what lies in front of the chosen bin joins the running totals
+    const bool upper = (chosen & 1) != 0;
+    sh->count_before = before_c + above_c + (upper ? 0u : c1);
+    sh->mass_before = before_m + above_m + (upper ? 0ull : m1);
   }
   __syncthreads();
 }
@@ -128,7 +169,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SamplePara
   __shared__ float red[32];
   __shared__ unsigned hist_cnt[kSampleBins];
   __shared__ unsigned long long hist_mass[kSampleBins];
-  __shared__ int s_bin;
+  __shared__ RadixShared rsh;
   __shared__ float s_scan[kSampleThreads / 32];
   __shared__ int s_pick;
   const int row = blockIdx.x;
@@ -165,16 +206,18 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SamplePara
   const int k = p.top_k[row];
   float kept_mass = -1.f;
   if (k > 0 && k < p.vocab) {
-    RadixState st{0u, 0.f, 0.f};
+    RadixState st{0u};
+    if (threadIdx.x == 0) { rsh.count_before = 0u; rsh.mass_before = 0ull; }
+    __syncthreads();
     unsigned hi_mask = 0u;
     int shift = 21;
     const int level_bits[3] = {11, 11, 10};
     bool open_end = false;
     for (int lv = 0; lv < 3; ++lv) {
       shift = lv == 0 ? 21 : lv == 1 ? 10 : 0;
-      radix_level(p, row_off, bmx, inv_t, 0.f, shift, level_bits[lv], hi_mask, st, true, static_cast<float>(k), hist_cnt,
-                  hist_mass, &s_bin);
-      const int b = s_bin;
+      radix_level(p, row_off, bmx, inv_t, 0.f, shift, level_bits[lv], hi_mask, st, true, static_cast<unsigned long long>(k),
+                  hist_cnt, hist_mass, &rsh);
+      const int b = rsh.bin;
       if (b < 0) { open_end = true; break; }
       st.prefix |= static_cast<unsigned>(b) << shift;
       hi_mask |= static_cast<unsigned>((1 << level_bits[lv]) - 1) << shift;
@@ -205,15 +248,19 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SamplePara
   // ---- top-p over the survivors: the smallest w whose mass in front is <= p * kept_mass
   const float tp = p.top_p[row];
   if (tp > 0.f && tp < 1.f) {
-    const float limit = tp * kept_mass;
-    RadixState st{0u, 0.f, 0.f};
+    const unsigned long long limit = static_cast<unsigned long long>(static_cast<double>(tp) * static_cast<double>(kept_mass) *
+                                                                   static_cast<double>(kMassScale));
+    RadixState st{0u};
+    __syncthreads();
+    if (threadIdx.x == 0) { rsh.count_before = 0u; rsh.mass_before = 0ull; }
+    __syncthreads();
     unsigned hi_mask = 0u;
     const int level_bits[3] = {11, 11, 10};
     bool open_end = false;
     for (int lv = 0; lv < 3; ++lv) {
       const int shift = lv == 0 ? 21 : lv == 1 ? 10 : 0;
-      radix_level(p, row_off, bmx, inv_t, tau, shift, level_bits[lv], hi_mask, st, false, limit, hist_cnt, hist_mass, &s_bin);
-      const int b = s_bin;
+      radix_level(p, row_off, bmx, inv_t, tau, shift, level_bits[lv], hi_mask, st, false, limit, hist_cnt, hist_mass, &rsh);
+      const int b = rsh.bin;
       if (b < 0) { open_end = true; break; }
       st.prefix |= static_cast<unsigned>(b) << shift;
       hi_mask |= static_cast<unsigned>((1 << level_bits[lv]) - 1) << shift;

@@ -52,6 +52,12 @@ class Comm:
     def recv(self, t: torch.Tensor, src: int) -> torch.Tensor:
         raise RuntimeError("recv on a single-rank communicator")
 
+    def isend(self, t: torch.Tensor, dst: int):
+        raise RuntimeError("isend on a single-rank communicator")
+
+    def irecv(self, t: torch.Tensor, src: int):
+        raise RuntimeError("irecv on a single-rank communicator")
+
     def barrier(self) -> None:
         return None
 
@@ -132,6 +138,16 @@ class TorchDistComm(Comm):
     def recv(self, t, src):
         self._dist.recv(t, src=self.ranks[src], group=self.group)
         return t
+
+    def isend(self, t, dst):
+        """Non-blocking send; returns a handle with ``wait()``. ``t`` must stay alive until then. With
+        NCCL the transfer runs on the communicator's own stream behind the work that produced ``t``, so
+        kernels launched afterwards on the current stream overlap it."""
+        return self._dist.isend(t, dst=self.ranks[dst], group=self.group)
+
+    def irecv(self, t, src):
+        """Non-blocking receive into ``t``; ``wait()`` on the handle before reading it."""
+        return self._dist.irecv(t, src=self.ranks[src], group=self.group)
 
     def barrier(self):
         self._dist.barrier(group=self.group)

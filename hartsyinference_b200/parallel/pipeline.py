@@ -6,6 +6,12 @@ gloo on CPU), runs its layers and passes the pair on; the last stage applies the
 the LM head and broadcasts the sampled tokens, so that every stage's scheduler sees the same
 sequence state. Only activations of the current step cross the link (2 x T x H bf16).
 
+A step's batch is cut into micro-batches along its sequences (``micro_batches``): stage s works on
+micro-batch i while stage s + 1 works on micro-batch i - 1. Transfers are non-blocking (the receive
+of micro-batch i + 1 is posted before the layers of micro-batch i run; sends are only waited for at
+the end of the step), which on GPUs puts them on the communicator's stream beside the compute
+stream. With one micro-batch the stages take turns, as a plain relay would.
+
 ``PipelinedModel`` has the surface the serving engine uses (``forward_hidden``, ``greedy_tokens``,
 ``full_logits``, ``alloc_kv`` ...), so an engine per stage runs unchanged.
 
@@ -53,8 +59,10 @@ class PipelinedModel:
     """One pipeline stage with the model surface of :class:`DecoderModel`."""
 
     def __init__(self, cfg: TransformerConfig, comm: Comm, device="cpu", fp8: bool = False,
-                 ratios: Optional[Sequence[float]] = None):
+                 ratios: Optional[Sequence[float]] = None, micro_batches: int = 0):
         self.comm = comm
+        # 0 = as many as there are stages (the smallest count that can keep every stage busy)
+        self.micro_batches = int(micro_batches) if micro_batches else comm.world
         self.stage, self.stages = comm.rank, comm.world
         self.ranges = split_layers(cfg.num_layers, self.stages, ratios)
         self.model = DecoderModel(cfg, device, fp8=fp8, layer_range=self.ranges[self.stage])
@@ -82,25 +90,86 @@ class PipelinedModel:
     def kv_cache(self):
         return self.model.kv_cache
 
+    # -- micro-batches
+    def split_batch(self, batch: ForwardBatch) -> list[ForwardBatch]:
+        """Cut ``batch`` into up to ``micro_batches`` pieces along its sequences (a decode row or a
+        prefill sequence is never divided). Batches that carry per-row extras the stages would have to
+        re-slice (embeddings, multimodal positions, cross-attention states) stay whole."""
+        n_seq = int(batch.kv_lens.shape[0])
+        want = min(self.micro_batches, n_seq)
+        if want <= 1 or batch.embeds is not None or batch.positions3 is not None or batch.deepstack is not None \
+                or batch.cross_states is not None or batch.cross_row_mask is not None:
+            return [batch]
+        if batch.is_decode:
+            bounds = [(n_seq * i) // want for i in range(want + 1)]
+            rows = bounds
+        else:
+            cu = batch.cu_q.tolist()
+            total = cu[-1]
+            # sequence boundaries closest to equal token shares
+            bounds = [0]
+            for i in range(1, want):
+                target = total * i / want
+                j = min(range(bounds[-1] + 1, n_seq), key=lambda k: abs(cu[k] - target), default=None)
+                if j is None:
+                    break
+                bounds.append(j)
+            bounds.append(n_seq)
+            rows = [cu[b] for b in bounds]
+        parts = []
+        for i in range(len(bounds) - 1):
+            s0, s1, r0, r1 = bounds[i], bounds[i + 1], rows[i], rows[i + 1]
+            if s1 <= s0:
+                continue
+            lr = None
+            if batch.logit_rows is not None:
+                sel = (batch.logit_rows >= r0) & (batch.logit_rows < r1)
+                lr = (batch.logit_rows[sel] - r0).contiguous()
+            cu_q = None if batch.cu_q is None else (batch.cu_q[s0:s1 + 1] - batch.cu_q[s0]).contiguous()
+            parts.append(ForwardBatch(tokens=batch.tokens[r0:r1].contiguous(), positions=batch.positions[r0:r1].contiguous(),
+                                      slot_mapping=batch.slot_mapping[r0:r1].contiguous(),
+                                      block_table=batch.block_table[s0:s1].contiguous(), kv_lens=batch.kv_lens[s0:s1].contiguous(),
+                                      is_decode=batch.is_decode, cu_q=cu_q,
+                                      max_q_len=batch.max_q_len, max_kv_len=batch.max_kv_len, logit_rows=lr))
+        return parts or [batch]
+
     # -- forward
     def forward_hidden(self, batch: ForwardBatch) -> torch.Tensor:
         m = self.model
-        hidden_in = None
-        t = batch.tokens.shape[0] if batch.tokens is not None else batch.embeds.shape[0]
         h = self.cfg.hidden_size
-        if not m.first_stage:
-            buf = torch.empty(2, t, h, dtype=torch.bfloat16, device=self.device)
-            self.comm.recv(buf, self.stage - 1)
-            hidden_in = (buf[0], buf[1])
-        out = m.forward_hidden(batch, hidden_in=hidden_in)
+        parts = self.split_batch(batch)
+        sizes = [p.tokens.shape[0] for p in parts]
+        recv_bufs = [None] * len(parts)
+        recv_work = [None] * len(parts)
+
+        def post_recv(i: int) -> None:
+            if not m.first_stage and i < len(parts):
+                recv_bufs[i] = torch.empty(2, sizes[i], h, dtype=torch.bfloat16, device=self.device)
+                recv_work[i] = self.comm.irecv(recv_bufs[i], self.stage - 1)
+
+        post_recv(0)
+        sends, outs = [], []
+        for i, mb in enumerate(parts):
+            hidden_in = None
+            if not m.first_stage:
+                recv_work[i].wait()
+                hidden_in = (recv_bufs[i][0], recv_bufs[i][1])
+            post_recv(i + 1)                      # the next micro-batch arrives while this one is computed
+            out = m.forward_hidden(mb, hidden_in=hidden_in)
+            if m.last_stage:
+                outs.append(out)
+            else:
+                x, res = out
+                if res is None:
+                    res = torch.zeros_like(x)
+                payload = torch.stack([x, res]).contiguous()
+                sends.append((self.comm.isend(payload, self.stage + 1), payload))
+        for work, _ in sends:
+            work.wait()
         if m.last_stage:
-            return out
-        x, res = out
-        if res is None:
-            res = torch.zeros_like(x)
-        self.comm.send(torch.stack([x, res]).contiguous(), self.stage + 1)
+            return outs[0] if len(outs) == 1 else torch.cat(outs, 0)
         # earlier stages have no logits; callers get a placeholder of the right shape
-        return torch.zeros(t, h, dtype=torch.bfloat16, device=self.device)
+        return torch.zeros(sum(sizes), h, dtype=torch.bfloat16, device=self.device)
 
     def greedy_tokens(self, hidden: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = hidden.shape[0]

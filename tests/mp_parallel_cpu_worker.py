@@ -69,6 +69,19 @@ def main():
     ref_out = LLMEngine(single, num_pages=16, page_size=16, max_batch=4, prefill_chunk=64, max_model_len=64).generate(prompts, sp)
     pp_out = LLMEngine(pp, num_pages=16, page_size=16, max_batch=4, prefill_chunk=64, max_model_len=64).generate(prompts, sp)
     assert pp_out == ref_out, (pp_out, ref_out)
+    # micro-batches: a batch of four sequences is cut in two, stage 1 works on the first half while
+    # stage 0 computes the second; prefill (cut at a sequence boundary) and decode steps both split
+    pp2 = PipelinedModel(cfg, comm, "cpu", micro_batches=2)
+    pp2.load_state_dict(full.get)
+    prompts4 = [toks.tolist(), toks[:7].tolist(), toks[3:12].tolist(), toks[:5].tolist()]
+    ref4 = LLMEngine(single, num_pages=32, page_size=16, max_batch=4, prefill_chunk=64, max_model_len=64).generate(prompts4, sp)
+    eng2 = LLMEngine(pp2, num_pages=32, page_size=16, max_batch=4, prefill_chunk=64, max_model_len=64)
+    seen = []
+    orig_split = pp2.split_batch
+    pp2.split_batch = lambda b: (lambda parts: (seen.append((b.is_decode, len(parts))), parts)[1])(orig_split(b))
+    out4 = eng2.generate(prompts4, sp)
+    assert out4 == ref4, (out4, ref4)
+    assert (True, 2) in seen and (False, 2) in seen, seen
     # ---- TP Flux vs single (same seed => same full weights, sharded per rank)
     fcfg = F.tiny_flux(num_heads=4, head_dim=32)
     gi = torch.Generator().manual_seed(5)
