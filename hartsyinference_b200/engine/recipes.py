@@ -108,7 +108,7 @@ class Recipe:
             need |= Features.CONTROLNET
         if getattr(req, "init_image", None) is not None:
             need |= Features.IMG2IMG
-        if getattr(req, "mask", None) is not None:
+        if getattr(req, "mask_image", None) is not None:
             need |= Features.INPAINT
         missing = need & ~self.supports
         if missing:

@@ -142,6 +142,9 @@ class ImageRequest:
     strength: float = 1.0
     loras: list[tuple[str, float]] = field(default_factory=list)
     step_cache_threshold: float = 0.0
+    guidance_interval: Optional[tuple] = None   # (start, end) in [0, 1]: true CFG only on those steps (None: all)
+    preview_every: int = 0               # > 0: every n-th step callback carries a small RGB preview of the latents
+    vae_tile: int = 0                    # > 0: decode in latent tiles of this size (bounded activation memory)
 
 
 @dataclass
@@ -244,7 +247,9 @@ class StepPreview:
     step: int
     total_steps: int
     latents: Optional[Any] = None
-    preview_rgb: Optional[bytes] = None
+    preview_rgb: Optional[bytes] = None  # RGB24 at latent resolution (preview_width x preview_height)
+    preview_width: int = 0
+    preview_height: int = 0
 
 
 @dataclass

@@ -121,6 +121,45 @@ class Vae2dDecoder:
         return x + o.transpose(1, 2).reshape(b, c, hh, ww)
 
     @torch.no_grad()
+    def decode_tiled(self, latents: torch.Tensor, tile: int = 64, overlap: int = 16) -> torch.Tensor:
+        """Decode in overlapping latent tiles of ``tile`` x ``tile`` and cross-fade the overlaps (linear
+        ramps of ``overlap`` latent pixels), so that activation memory is bounded by the tile and not by
+        the image. Tiles see only their own GroupNorm / attention context, so the result differs from
+        :meth:`decode` by the usual tiling tolerance; images no larger than one tile take the plain path.
+        (Reference: src/HartsyInference.Diffusion/Models/Vae/ tiled decode of its low-VRAM mode.)"""
+        b, c, h, w = latents.shape
+        if h <= tile and w <= tile:
+            return self.decode(latents)
+        f = 2 ** (len(self.cfg.block_out_channels) - 1)
+        overlap = max(0, min(overlap, tile // 2))
+        step = tile - overlap
+        ys = list(range(0, max(h - overlap, 1), step))
+        xs = list(range(0, max(w - overlap, 1), step))
+        out = torch.zeros(b, 3, h * f, w * f)
+        weight = torch.zeros(1, 1, h * f, w * f)
+        for y0 in ys:
+            for x0 in xs:
+                y1, x1 = min(h, y0 + tile), min(w, x0 + tile)
+                ya, xa = max(0, y1 - tile), max(0, x1 - tile)          # edge tiles keep the full tile size
+                img = self.decode(latents[:, :, ya:y1, xa:x1]).cpu()
+                th, tw = img.shape[-2], img.shape[-1]
+                ramp = max(1, overlap * f)
+                wy = torch.ones(th)
+                wx = torch.ones(tw)
+                if ya > 0:
+                    wy[:ramp] = torch.linspace(0, 1, ramp + 2)[1:-1]
+                if y1 < h:
+                    wy[-ramp:] = torch.linspace(1, 0, ramp + 2)[1:-1]
+                if xa > 0:
+                    wx[:ramp] = torch.linspace(0, 1, ramp + 2)[1:-1]
+                if x1 < w:
+                    wx[-ramp:] = torch.linspace(1, 0, ramp + 2)[1:-1]
+                m = (wy[:, None] * wx[None, :])[None, None]
+                out[:, :, ya * f:y1 * f, xa * f:x1 * f] += img * m
+                weight[:, :, ya * f:y1 * f, xa * f:x1 * f] += m
+        return (out / weight.clamp_min(1e-6)).clamp(-1, 1)
+
+    @torch.no_grad()
     def decode(self, latents: torch.Tensor) -> torch.Tensor:
         """latents [B, C, h, w] (model space) -> images [B, 3, 8h, 8w] in [-1, 1] (float32)."""
         z = latents.to(self.device).float() / self.cfg.scaling_factor + self.cfg.shift_factor

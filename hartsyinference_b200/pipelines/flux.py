@@ -21,6 +21,7 @@ import torch
 from .. import log
 from ..engine.metrics import REGISTRY
 from ..engine.requests import ImageRequest, ImageResult, StepPreview
+from ..models.diffusion.preview import in_guidance_interval
 from ..models.diffusion.schedulers import FlowMatchEulerScheduler, flux_mu
 from ..models.dit.flux import FluxTransformer, flux_ids
 from ..models.vae.vae2d import Vae2dDecoder, to_rgb24
@@ -96,8 +97,12 @@ class FluxPipeline:
                 on_step: Optional[Callable[[StepPreview], None]] = None, step_cache_threshold: float = 0.0, first_block_cache: float = 0.0,
                 latents: Optional[torch.Tensor] = None, init_latents: Optional[torch.Tensor] = None, strength: float = 1.0,
                 mask: Optional[torch.Tensor] = None, control_latents: Optional[torch.Tensor] = None,
-                control_strength: float = 1.0, channel_cond: Optional[torch.Tensor] = None) -> torch.Tensor:
+                control_strength: float = 1.0, channel_cond: Optional[torch.Tensor] = None,
+                guidance_interval: Optional[tuple] = None) -> torch.Tensor:
         """Returns the final latents [1, C, H/8, W/8] fp32 on the device.
+
+        ``guidance_interval`` (start, end) limits true classifier-free guidance to the steps inside it
+        (single-process runs; with the two branches on two ranks both always run).
 
         ``init_latents`` [1, C, H/8, W/8] with ``strength`` < 1 starts from the image noised to the
         sigma of step ``steps * (1 - strength)`` and runs the remaining steps (img2img). ``mask``
@@ -181,7 +186,7 @@ class FluxPipeline:
                 if branch is None:
                     v_cond = tr.forward(xin, ctx_d, sigma, pooled_d, img_ids, txt_ids, gvec, step_cache=fbc[0], control=ctl)
                     v_unc = tr.forward(xin, neg[0].to(dev)[None], sigma, neg[1].to(dev)[None], img_ids, txt_ids, gvec,
-                                       step_cache=fbc[1]) if true_cfg else None
+                                       step_cache=fbc[1]) if (true_cfg and in_guidance_interval(i, steps, guidance_interval)) else None
                 else:
                     c_in, p_in = (ctx_d, pooled_d) if branch == 0 else (neg[0].to(dev)[None], neg[1].to(dev)[None])
                     mine = tr.forward(xin, c_in, sigma, p_in, img_ids, txt_ids, gvec, step_cache=fbc[0],
@@ -194,7 +199,7 @@ class FluxPipeline:
                         v_cond, v_unc = both[0].contiguous(), both[1].contiguous()
                 if step_cache_threshold > 0:
                     cache_prev_t = tr.time_embedding(sigma, gvec, pooled_d).float()
-                    cache_v = v_cond if not true_cfg else (cfg_scale * v_cond.float() + (1 - cfg_scale) * v_unc.float()).to(torch.bfloat16)
+                    cache_v = v_cond if (not true_cfg or v_unc is None) else (cfg_scale * v_cond.float() + (1 - cfg_scale) * v_unc.float()).to(torch.bfloat16)
                     if true_cfg:
                         v_cond, v_unc = cache_v, None
             if v_cond is not None:
@@ -275,6 +280,23 @@ class FluxPipeline:
             t = torch.nn.functional.interpolate(t, size=(height, width), mode="bilinear", align_corners=False, antialias=True)
         return t.clamp(0, 1) * 2.0 - 1.0
 
+    def _with_previews(self, on_step, req):
+        """Wrap the step callback so that every ``req.preview_every``-th step carries an RGB preview of the
+        latents (a linear map fitted once against this pipeline's VAE)."""
+        every = int(getattr(req, "preview_every", 0) or 0)
+        if on_step is None or every <= 0 or self.c.vae is None:
+            return on_step
+        if getattr(self, "_previewer", None) is None:
+            from ..models.diffusion.preview import LatentPreviewer
+            self._previewer = LatentPreviewer.fit(self.c.vae, self.c.transformer.cfg.latent_channels // 4)
+        lh, lw = req.height // 8, req.width // 8
+
+        def wrapped(p: StepPreview):
+            if p.step % every == 0 and p.latents is not None:
+                p.preview_rgb, p.preview_width, p.preview_height = self._previewer.rgb(unpack_latents(p.latents, lh, lw))
+            on_step(p)
+        return wrapped
+
     def generate(self, req: ImageRequest, on_step: Optional[Callable[[StepPreview], None]] = None) -> ImageResult:
         seed = req.seed if req.seed is not None else int(time.time() * 1000) % (2 ** 31)
         ctx, pooled = self.encode_prompt(req.prompt)
@@ -296,13 +318,16 @@ class FluxPipeline:
             if self.c.controlnet is None or self.c.vae_encoder is None:
                 raise ValueError("a control image needs a ControlNet and the VAE encoder (FluxComponents.controlnet / vae_encoder)")
             control_latents = self.c.vae_encoder.encode(self._image_tensor(req.control_image, req.width, req.height))
+        on_step = self._with_previews(on_step, req)
         z = self.denoise(ctx, pooled, req.height, req.width, req.steps, req.guidance, seed, neg, req.cfg_scale, on_step,
                          req.step_cache_threshold, init_latents=init_latents, strength=req.strength, mask=mask,
                          control_latents=control_latents, control_strength=getattr(req, "control_strength", 1.0),
-                         channel_cond=channel_cond)
+                         channel_cond=channel_cond, guidance_interval=getattr(req, "guidance_interval", None))
         t_denoise = time.perf_counter() - t0
         if self.c.vae is None:
             img = torch.zeros(1, 3, req.height, req.width)
+        elif getattr(req, "vae_tile", 0) > 0:
+            img = self.c.vae.decode_tiled(z, req.vae_tile, req.vae_tile // 4)
         else:
             img = self.c.vae.decode(z)
         rgb = to_rgb24(img)[0]
