@@ -109,7 +109,7 @@ declare("kernels_lib", str, "", "path of another build of libb200_kernels.so to 
 declare("pdl", bool, True, "launch GEMMs with programmatic dependent launch so that weight tiles are requested while the preceding kernel still runs")
 declare("fp8_scales", str, "ue8m0", "block-scale format of fp8 linears: ue8m0 (power-of-two scales applied by the tensor core) or fp32 (promoted per K block by the epilogue warps)")
 declare("gguf_resident", bool, False, "keep Q8_0 / Q4_K GGUF linears as quantised blocks on the device (integer-dot GEMV at decode) instead of dequantising at load")
-declare("low_vram", bool, False, "stream transformer blocks from pinned host memory instead of keeping weights resident")
+declare("low_vram", str, "auto", "auto: stream transformer blocks from pinned host memory only when the weights do not fit; on: always stream what can be streamed; off: never")
 declare("model_cache_dir", str, "~/.hartsyinference/models", "where resolved checkpoints are cached")
 declare("same_gpu_concurrent", bool, False, "allow two requests to share one device slot")
 declare("assert_ambient", bool, False, "debug: verify every op runs on the device its tensors live on")

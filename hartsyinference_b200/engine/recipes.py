@@ -219,8 +219,17 @@ class FluxRecipe(Recipe):
         return (ck.get("x_embedder.weight") is not None and ck.get("single_transformer_blocks.0.attn.to_q.weight") is not None) or \
             ck.get("double_blocks.0.img_attn.qkv.weight") is not None
 
+    def _stream(self, ctx, weight_bytes: int) -> bool:
+        """Ask the VRAM planner where the denoiser's weights go (tensor-parallel shards stay resident)."""
+        from .vram_planner import Placement, VramPlanner, resolve_mode
+        planner = VramPlanner(ctx.device, ctx.spec.requested, resolve_mode(ctx.options.low_vram))
+        # activations of a 1024 x 1024 step: a few dozen [tokens, 4 x hidden] bf16 buffers
+        reserve = 3 << 30
+        return planner.plan_phase("denoise", weight_bytes, reserve, can_stream=ctx.inner_comm is None) == Placement.STREAMED
+
     def _transformer(self, ctx, get):
         from ..models.dit import flux as F
+        from .vram_planner import checkpoint_bytes
         base = F.FLUX_DEV
         xw = get("x_embedder.weight")
         if xw is not None and xw.shape[1] != base.in_channels:
@@ -228,7 +237,8 @@ class FluxRecipe(Recipe):
             base = dataclasses.replace(base, in_channels=int(xw.shape[1]), out_channels=base.in_channels)
         if get("time_text_embed.guidance_embedder.linear_1.weight") is None:
             base = dataclasses.replace(base, guidance_embed=False)          # schnell-class checkpoints
-        return F.FluxTransformer(base, ctx.device, comm=ctx.inner_comm, fp8=ctx.fp8, get=get)
+        stream = self._stream(ctx, checkpoint_bytes(ctx.checkpoint, ctx.fp8, ctx.inner_comm.world if ctx.inner_comm else 1))
+        return F.FluxTransformer(base, ctx.device, comm=ctx.inner_comm, fp8=ctx.fp8, get=get, stream_blocks=stream)
 
     def construct(self, ctx: RecipeContext):
         from ..assets.converters import flux_original_to_diffusers, is_flux_original
@@ -269,7 +279,10 @@ class FluxRecipe(Recipe):
 
     def _synthetic_transformer(self, ctx, tiny):
         from ..models.dit import flux as F
-        return F.FluxTransformer(F.tiny_flux() if tiny else F.FLUX_DEV, ctx.device, comm=ctx.inner_comm, fp8=ctx.fp8 and not tiny)
+        from .vram_planner import LowVramMode, resolve_mode
+        stream = resolve_mode(ctx.options.low_vram) == LowVramMode.ON and ctx.inner_comm is None and ctx.device.startswith("cuda")
+        return F.FluxTransformer(F.tiny_flux() if tiny else F.FLUX_DEV, ctx.device, comm=ctx.inner_comm, fp8=ctx.fp8 and not tiny,
+                                 stream_blocks=stream)
 
 
 class ChromaRecipe(FluxRecipe):

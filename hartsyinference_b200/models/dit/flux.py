@@ -92,7 +92,10 @@ class FluxTransformer:
 
     def __init__(self, cfg: FluxConfig = FLUX_DEV, device="cpu", comm: Optional[Comm] = None, fp8: bool = False,
                  get: Optional[Callable[[str], Optional[torch.Tensor]]] = None, seed: int = 0,
-                 block_range: Optional[tuple[int, int]] = None, build_head: bool = True):
+                 block_range: Optional[tuple[int, int]] = None, build_head: bool = True, stream_blocks: bool = False):
+        """``stream_blocks``: every transformer block moves to pinned host memory as soon as it is built
+        (device peak: embedders + one block) and the forward pass streams them through two device slots
+        (engine/block_streaming.py); chosen by the engine's VRAM planner when the weights do not fit."""
         self.cfg = cfg
         self.has_head = build_head
         self.device = torch.device(device)
@@ -141,16 +144,24 @@ class FluxTransformer:
                 proj=f.linear(p + "attn.to_add_out", H, cfg.num_heads * D, shard="row"),
                 mlp_in=f.linear(p + "ff_context.net.0.proj", cfg.mlp_dim, H, shard="col"),
                 mlp_out=f.linear(p + "ff_context.net.2", H, cfg.mlp_dim, shard="row"))
-            self.double.append((img, txt))
+            self.double.append(self._parked((img, txt), stream_blocks))
         for i in range(cfg.num_single_blocks):
             gi = cfg.num_double_blocks + i
             if not (self.block_range[0] <= gi < self.block_range[1]):
                 continue
             p = f"single_transformer_blocks.{i}."
-            self.single.append(self._single(f, p))
+            self.single.append(self._parked(self._single(f, p), stream_blocks))
         if last and build_head:
             self.norm_out = lin_mod("norm_out.linear", 2)
             self.proj_out = f.linear("proj_out", cfg.latent_channels, H)
+        if stream_blocks:
+            self.enable_block_streaming()
+
+    def _parked(self, block, stream_blocks: bool):
+        if not stream_blocks or self.device.type != "cuda":
+            return block
+        from ...engine.block_streaming import map_tensors
+        return map_tensors(block, lambda t: t.detach().cpu().pin_memory())
 
     # -- weight assembly ------------------------------------------------------------------
     def _qkv(self, f: WeightFactory, names) -> LinearWeight:

@@ -55,6 +55,25 @@ def test_flux_gpu_matches_cpu(fp8):
 
 
 @pytest.mark.parametrize("fp8", [False, True])
+def test_flux_streamed_construction_matches_resident(fp8):
+    """Blocks parked in pinned host memory as they are built and streamed through two device slots give
+    the resident model's output, and hold (almost) no block weights on the device."""
+    cfg = F.tiny_flux(hidden_size=256, num_heads=2, head_dim=128, context_dim=128, pooled_dim=64, axes_dim=(16, 56, 56), in_channels=64)
+    resident = F.FluxTransformer(cfg, "cuda", fp8=fp8, seed=4)
+    streamed = F.FluxTransformer(cfg, "cuda", fp8=fp8, seed=4, stream_blocks=True)
+    assert all(b is None for b in streamed.double) and all(b is None for b in streamed.single)
+    gen = torch.Generator().manual_seed(0)
+    img = torch.randn(1, 64, 64, generator=gen).cuda(); txt = torch.randn(1, 40, 128, generator=gen).cuda()
+    pooled = torch.randn(1, 64, generator=gen).cuda()
+    ii, it = F.flux_ids(8, 8, 40)
+    args = (img, txt, torch.tensor([0.6]).cuda(), pooled, ii.cuda(), it.cuda(), torch.tensor([3.5]).cuda())
+    a, b = resident.forward(*args), streamed.forward(*args)
+    N.check_status()
+    assert torch.equal(a, b)
+    assert torch.equal(streamed.forward(*args), b)          # a second pass re-streams the same blocks
+
+
+@pytest.mark.parametrize("fp8", [False, True])
 def test_wan_gpu_matches_cpu(fp8):
     cfg = W.tiny_wan(hidden_size=256, num_heads=2, head_dim=128, ffn_size=512, text_dim=128, text_len=32, freq_dim=64)
     g = W.WanTransformer(cfg, "cuda", fp8=fp8, seed=5)
