@@ -76,6 +76,7 @@ struct FaParams {
   // and no flags.
   int n_tiles, tiles_per_seg, nseg, seg_len, seg_first, seg_pad;
   int seg_mode;
+  int q_seg_base;            // segment index of query row 0 (context-parallel form: the queries are this rank's only)
   const uint32_t* seg_flags;
   uint32_t seg_target;
   long long wait_budget;
@@ -172,7 +173,7 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
       };
       if (p.seg_mode) {
         const int first = qt2 * 2 * kFaTile, last = first + nq * kFaTile - 1;
-        for (int seg = first / p.seg_pad; seg <= last / p.seg_pad && ok; ++seg) ok = wait_segment(seg);
+        for (int seg = first / p.seg_pad; seg <= last / p.seg_pad && ok; ++seg) ok = wait_segment(seg + p.q_seg_base);
       }
       if (ok) {
         mbar_arrive_expect_tx(&bars->q_full, nq * kQkTileBytes);
@@ -386,7 +387,7 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
         tc_fence_after_sync();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         __nv_bfloat16* dst = p.seg_mode
-            ? p.out_seg[q_valid ? q_seg : 0] + static_cast<long long>(q_local) * p.ld_out + p.out_col0 + col0
+            ? p.out_seg[q_valid ? q_seg + p.q_seg_base : 0] + static_cast<long long>(q_local) * p.ld_out + p.out_col0 + col0
             : p.out + static_cast<long long>(q_row0 + t * kFaTile + row) * p.ld_out + col0;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -579,6 +580,7 @@ __global__ void __launch_bounds__(256) sage_quant_k_tiles_kernel(const __nv_bflo
 constexpr int kUlyFlagArrive = 0, kUlyFlagKsum = 8, kUlyFlagDone = 16, kUlyFlagWords = 32;
 
 struct UlyPush {
+  int cp;                      // 1: context-parallel form (K / V of all heads to every rank, Q stays here)
   const __nv_bfloat16* q;      // local [s_l][heads * 128]
   const __nv_bfloat16* k;
   const __nv_bfloat16* v;
@@ -625,13 +627,18 @@ __global__ void __launch_bounds__(256) uly_push_kernel(const UlyPush p) {
   __shared__ int wait_ok;
   __shared__ __align__(16) __nv_bfloat16 vtile[kFaTile][kFaD + 8];
   const int tile = blockIdx.x, head = blockIdx.y;
-  const int dst = head / p.hl, hi = head - dst * p.hl;
+  // Ulysses: the head belongs to one destination rank. Context parallel: every rank gets K / V of every
+  // head (p.hl == p.heads), the queries stay local (row = token, no segment offset).
+  const int dst = p.cp ? p.rank : head / p.hl, hi = p.cp ? head : head - dst * p.hl;
+  const int first_dst = p.cp ? 0 : dst, last_dst = p.cp ? p.world - 1 : dst;
   const int row = threadIdx.x >> 1, d0 = (threadIdx.x & 1) * 64;
   const int tok = tile * kFaTile + row;
   const bool valid = tok < p.s_l;
   const long long ld_in = static_cast<long long>(p.heads) * kFaD;
   const long long ld_out = static_cast<long long>(p.hl) * kFaD;
-  const long long seg_row = static_cast<long long>(p.rank) * p.s_pad + tok;     // row in the destination buffers
+  const long long seg_row = static_cast<long long>(p.rank) * p.s_pad + tok;     // row in the destination K / V buffers
+  const long long q_row = p.cp ? tok : seg_row;
+  const long long q_rows = p.cp ? p.s_pad : static_cast<long long>(p.world) * p.s_pad;
   const int tiles = p.s_pad / kFaTile;
 
   if (kI8) {
@@ -697,12 +704,12 @@ __global__ void __launch_bounds__(256) uly_push_kernel(const UlyPush p) {
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     const float sc = fmaxf(amax, 1e-12f) / 127.f;
     if (valid) {
-      store_q8(static_cast<int8_t*>(p.qbuf[dst]) + seg_row * ld_out + hi * kFaD + d0, v, 1.f / sc);
-      if (d0 == 0) p.qscale[dst][static_cast<long long>(hi) * p.world * p.s_pad + seg_row] = sc;
+      store_q8(static_cast<int8_t*>(p.qbuf[dst]) + q_row * ld_out + hi * kFaD + d0, v, 1.f / sc);
+      if (d0 == 0) p.qscale[dst][static_cast<long long>(hi) * q_rows + q_row] = sc;
     }
   } else if (valid) {
     const uint4* src = reinterpret_cast<const uint4*>(p.q + static_cast<long long>(tok) * ld_in + head * kFaD + d0);
-    uint4* out = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.qbuf[dst]) + seg_row * ld_out + hi * kFaD + d0);
+    uint4* out = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.qbuf[dst]) + q_row * ld_out + hi * kFaD + d0);
 #pragma unroll
     for (int i = 0; i < 8; ++i) out[i] = src[i];
   }
@@ -726,13 +733,20 @@ __global__ void __launch_bounds__(256) uly_push_kernel(const UlyPush p) {
 #pragma unroll
     for (int i = 1; i < 8; ++i) amax = fmaxf(amax, wmax[i]);
     const float sc = fmaxf(amax, 1e-12f) / 127.f;
-    if (threadIdx.x == 0) p.kscale[dst][static_cast<long long>(hi) * p.world * tiles + p.rank * tiles + tile] = sc;
-    if (valid) store_q8(static_cast<int8_t*>(p.kbuf[dst]) + seg_row * ld_out + hi * kFaD + d0, v, 1.f / sc);
+    for (int d = first_dst; d <= last_dst; ++d) {
+      if (threadIdx.x == 0) p.kscale[d][static_cast<long long>(hi) * p.world * tiles + p.rank * tiles + tile] = sc;
+      if (valid) store_q8(static_cast<int8_t*>(p.kbuf[d]) + seg_row * ld_out + hi * kFaD + d0, v, 1.f / sc);
+    }
   } else if (valid) {
     const uint4* src = reinterpret_cast<const uint4*>(p.k + static_cast<long long>(tok) * ld_in + head * kFaD + d0);
-    uint4* out = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.kbuf[dst]) + seg_row * ld_out + hi * kFaD + d0);
+    uint4 kv[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) out[i] = src[i];
+    for (int i = 0; i < 8; ++i) kv[i] = src[i];
+    for (int d = first_dst; d <= last_dst; ++d) {
+      uint4* out = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.kbuf[d]) + seg_row * ld_out + hi * kFaD + d0);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) out[i] = kv[i];
+    }
   }
 
   // ---- V: transposed through shared memory; rows past the end become zeros
@@ -749,15 +763,15 @@ __global__ void __launch_bounds__(256) uly_push_kernel(const UlyPush p) {
     __syncthreads();
     // thread (dim, half) writes 64 consecutive tokens of one dim
     const int dim = threadIdx.x >> 1, t0 = (threadIdx.x & 1) * 64;
-    __nv_bfloat16* out = p.vtbuf[dst] + (static_cast<long long>(hi) * kFaD + dim) * p.world * p.s_pad +
-                         static_cast<long long>(p.rank) * p.s_pad + tile * kFaTile + t0;
+    const long long off = (static_cast<long long>(hi) * kFaD + dim) * p.world * p.s_pad +
+                          static_cast<long long>(p.rank) * p.s_pad + tile * kFaTile + t0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       uint4 o;
       __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&o);
 #pragma unroll
       for (int u = 0; u < 8; ++u) e[u] = vtile[t0 + i * 8 + u][dim];
-      *reinterpret_cast<uint4*>(out + i * 8) = o;
+      for (int d = first_dst; d <= last_dst; ++d) *reinterpret_cast<uint4*>(p.vtbuf[d] + off + i * 8) = o;
     }
   }
 
@@ -907,20 +921,21 @@ static int fa_launch(const FaParams& p, const CUtensorMap& tq, const CUtensorMap
 struct UlyLayout {
   long long flags, ctr, ksum_in, ksum_local, qbuf, kbuf, vtbuf, qscale, kscale, out, total;
 };
-static UlyLayout uly_layout(int s_l, int heads, int world, int int8) {
+static UlyLayout uly_layout(int s_l, int heads, int world, int int8, int cp = 0) {
   UlyLayout l{};
   auto up = [](long long v) { return (v + 1023) / 1024 * 1024; };
-  const int s_pad = fa_pad(s_l, 128), hl = heads / world;
+  const int s_pad = fa_pad(s_l, 128), hl = cp ? heads : heads / world;
   const long long rows = static_cast<long long>(world) * s_pad;
+  const long long q_rows = cp ? s_pad : rows;
   long long off = 0;
   l.flags = off; off = up(off + kUlyFlagWords * 4);
   l.ctr = off; off = up(off + 64);
   l.ksum_in = off; off = up(off + static_cast<long long>(world) * heads * kFaD * 4);
   l.ksum_local = off; off = up(off + static_cast<long long>(heads) * kFaD * 4);
-  l.qbuf = off; off = up(off + rows * hl * kFaD * (int8 ? 1 : 2));
+  l.qbuf = off; off = up(off + q_rows * hl * kFaD * (int8 ? 1 : 2));
   l.kbuf = off; off = up(off + rows * hl * kFaD * (int8 ? 1 : 2));
   l.vtbuf = off; off = up(off + rows * hl * kFaD * 2);
-  l.qscale = off; off = up(off + static_cast<long long>(hl) * rows * 4);
+  l.qscale = off; off = up(off + static_cast<long long>(hl) * q_rows * 4);
   l.kscale = off; off = up(off + static_cast<long long>(hl) * (rows / 128) * 4);
   l.out = off; off = up(off + static_cast<long long>(s_pad) * heads * kFaD * 2);
   l.total = off;
@@ -930,6 +945,14 @@ static UlyLayout uly_layout(int s_l, int heads, int world, int int8) {
 B200_API long long b200_ulysses_region_bytes(int s_l, int heads, int world, int int8) {
   if (world <= 0 || world > 8 || heads % world != 0) return -1;
   return uly_layout(s_l, heads, world, int8).total;
+}
+// Context-parallel form (any head count): every rank keeps its own queries and receives K / V of all heads.
+B200_API long long b200_context_parallel_region_bytes(int s_l, int heads, int world, int int8) {
+  if (world <= 0 || world > 8) return -1;
+  return uly_layout(s_l, heads, world, int8, 1).total;
+}
+B200_API long long b200_context_parallel_out_offset(int s_l, int heads, int world, int int8) {
+  return uly_layout(s_l, heads, world, int8, 1).out;
 }
 // Offset of the output [s_l][heads * 128] bf16 inside the region (the caller reads it after
 // b200_ulysses_wait_outputs).
@@ -944,13 +967,20 @@ B200_API long long b200_ulysses_out_offset(int s_l, int heads, int world, int in
 // `phases` selects the steps (bits: 1 K column sums, 2 operand push, 4 attention, 8 wait for the
 // outputs); a rank passes 15. Tests that play every rank on one GPU run each phase for all ranks
 // before the next one, so that no kernel ever waits for a later launch.
+// Bit 16 selects the context-parallel form, for head counts the group size does not divide: every rank
+// keeps its queries (and its output rows, [s_l][heads * 128] at b200_context_parallel_out_offset of its
+// own region) and receives the K / V operands of all heads from every rank. world x the K / V bytes
+// cross the links instead of (world - 1) / world of Q, K, V and the output, so the head-split form
+// is the one to use whenever it applies.
 B200_API int b200_ulysses_attention(const void* q, const void* k, const void* v, void* const* regions, int s_l, int heads,
                                     int rank, int world, float scale, int int8, unsigned epoch, int phases,
                                     long long wait_budget_cycles, void* status, cudaStream_t stream) {
-  if (world <= 0 || world > 8 || heads % world != 0 || s_l <= 0) return -2;
-  const UlyLayout l = uly_layout(s_l, heads, world, int8);
-  const int s_pad = fa_pad(s_l, 128), hl = heads / world, tiles = s_pad / 128;
+  const int cp = (phases & 16) ? 1 : 0;
+  if (world <= 0 || world > 8 || (!cp && heads % world != 0) || s_l <= 0) return -2;
+  const UlyLayout l = uly_layout(s_l, heads, world, int8, cp);
+  const int s_pad = fa_pad(s_l, 128), hl = cp ? heads : heads / world, tiles = s_pad / 128;
   const long long rows = static_cast<long long>(world) * s_pad;
+  const long long q_rows = cp ? s_pad : rows;
   uint8_t* mine = static_cast<uint8_t*>(regions[rank]);
   const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
 
@@ -958,6 +988,7 @@ B200_API int b200_ulysses_attention(const void* q, const void* k, const void* v,
   u.q = static_cast<const __nv_bfloat16*>(q);
   u.k = static_cast<const __nv_bfloat16*>(k);
   u.v = static_cast<const __nv_bfloat16*>(v);
+  u.cp = cp;
   u.s_l = s_l; u.s_pad = s_pad; u.heads = heads; u.hl = hl; u.rank = rank; u.world = world;
   for (int d = 0; d < world; ++d) {
     uint8_t* r = static_cast<uint8_t*>(regions[d]);
@@ -998,12 +1029,13 @@ B200_API int b200_ulysses_attention(const void* q, const void* k, const void* v,
 
   FaParams p{};
   p.ld_out = static_cast<long long>(heads) * kFaD;
-  p.sq = static_cast<int>(rows); p.sk = static_cast<int>(rows); p.heads = hl; p.batch = 1;
+  p.sq = static_cast<int>(q_rows); p.sk = static_cast<int>(rows); p.heads = hl; p.batch = 1;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = static_cast<DeviceStatus*>(status);
   p.q_scale = reinterpret_cast<const float*>(mine + l.qscale);
   p.k_scale = reinterpret_cast<const float*>(mine + l.kscale);
-  p.sq_pad = static_cast<int>(rows);
+  p.sq_pad = static_cast<int>(q_rows);
+  p.q_seg_base = cp ? rank : 0;
   p.n_tiles = world * tiles;
   p.tiles_per_seg = tiles;
   p.nseg = world;
@@ -1014,7 +1046,7 @@ B200_API int b200_ulysses_attention(const void* q, const void* k, const void* v,
   p.seg_flags = reinterpret_cast<const uint32_t*>(mine + l.flags) + kUlyFlagArrive;
   p.seg_target = epoch;
   p.wait_budget = budget;
-  p.out_col0 = static_cast<long long>(rank) * hl * kFaD;
+  p.out_col0 = cp ? 0 : static_cast<long long>(rank) * hl * kFaD;
   for (int d = 0; d < world; ++d) {
     uint8_t* r = static_cast<uint8_t*>(regions[d]);
     p.out_seg[d] = reinterpret_cast<__nv_bfloat16*>(r + l.out);
@@ -1023,14 +1055,14 @@ B200_API int b200_ulysses_attention(const void* q, const void* k, const void* v,
   p.done_ctr = reinterpret_cast<uint32_t*>(mine + l.ctr) + 4;
   CUtensorMap tq, tk, tv;
   const int eb = int8 ? 1 : 2;
-  int rc = make_kmajor_map(&tq, mine + l.qbuf, eb, rows, static_cast<long long>(hl) * kFaD, static_cast<long long>(hl) * kFaD, 128);
+  int rc = make_kmajor_map(&tq, mine + l.qbuf, eb, q_rows, static_cast<long long>(hl) * kFaD, static_cast<long long>(hl) * kFaD, 128);
   if (rc) return rc;
   rc = make_kmajor_map(&tk, mine + l.kbuf, eb, rows, static_cast<long long>(hl) * kFaD, static_cast<long long>(hl) * kFaD, 128);
   if (rc) return rc;
   rc = make_kmajor_map(&tv, mine + l.vtbuf, 2, static_cast<long long>(hl) * kFaD, rows, rows, 128);
   if (rc) return rc;
   if (phases & 4) {
-    rc = fa_launch(p, tq, tk, tv, dim3(static_cast<unsigned>((rows + 2 * kFaTile - 1) / (2 * kFaTile)), hl, 1), int8, stream);
+    rc = fa_launch(p, tq, tk, tv, dim3(static_cast<unsigned>((q_rows + 2 * kFaTile - 1) / (2 * kFaTile)), hl, 1), int8, stream);
     if (rc) return rc;
   }
   if (phases & 8)

@@ -170,7 +170,7 @@ class WanTransformer:
                 self._fused_exchange[s_l] = FusedUlyssesAttention(self.comm, s_l, heads, self.device)
                 self.exchange_path = "peer stores from the quantisation kernel into the attention kernel's operand buffers"
             except Exception as e:      # no peer mapping between these GPUs: keep the collective form
-                log.warn(f"[SequenceParallel] fused exchange unavailable ({type(e).__name__}: {e}); using NCCL all-to-all")
+                log.warn(f"[SequenceParallel] fused exchange unavailable ({type(e).__name__}: {e}); using the NCCL collectives")
                 self._fused_exchange[s_l] = None
         return self._fused_exchange[s_l]
 
@@ -186,6 +186,9 @@ class WanTransformer:
             o = ops.attention(q, k, v)
             return o.reshape(o.shape[0], -1)
         if not self.ulysses:
+            fused = self._fused(q.shape[0], q.shape[1], q.shape[2])
+            if fused is not None:                                                 # K / V stored into every rank's buffers
+                return fused(q.contiguous(), k.contiguous(), v.contiguous())
             kf = self.comm.all_gather(k.contiguous(), dim=0)                      # [S, heads, D]
             vf = self.comm.all_gather(v.contiguous(), dim=0)
             o = ops.attention(q.contiguous(), kf, vf)

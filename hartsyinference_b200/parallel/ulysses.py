@@ -14,6 +14,11 @@ exchange inside the kernels around the dense attention (csrc/kernels/attention_f
 * a one-thread kernel waits for the ``world`` output shares before the consumer (the output
   projection) runs.
 
+When the head count does not divide by the group size the same kernels run in their
+context-parallel form (``context_parallel=True``): the queries and the output rows stay on their
+rank and the K / V operands of all heads are stored into every rank's buffers, which is the
+exchange the reference performs (its ranks publish K / V and read everyone else's).
+
 There is no all-to-all collective and no NCCL call on this path; the NCCL all-to-all form
 (models/dit/wan.py) is the fallback and the measured baseline. The reference exchanges K and V
 between its device threads through a host rendezvous around every attention call
@@ -36,24 +41,28 @@ from .symm import SymmetricHeap
 class FusedUlyssesAttention:
     """One instance per (sequence-parallel group, shape). All ranks construct and call it together.
 
-    ``local_tokens`` must be the same on every rank and ``heads`` divisible by the group size;
-    head dim is 128.
+    ``local_tokens`` must be the same on every rank; head dim is 128. ``context_parallel`` defaults to
+    whether ``heads`` fails to divide by the group size (the head-split form moves fewer bytes and is
+    used whenever it applies).
     """
 
     def __init__(self, comm: Comm, local_tokens: int, heads: int, device: Optional[torch.device] = None,
-                 int8: Optional[bool] = None):
+                 int8: Optional[bool] = None, context_parallel: Optional[bool] = None):
         self.comm = comm
         self.rank, self.world = comm.rank, comm.world
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.s_l, self.heads = int(local_tokens), int(heads)
         self.int8 = bool(config.get("sage_attention")) if int8 is None else bool(int8)
-        if heads % self.world != 0 or self.world > 8:
+        self.context_parallel = heads % self.world != 0 if context_parallel is None else bool(context_parallel)
+        if self.world > 8 or (heads % self.world != 0 and not self.context_parallel):
             raise ValueError(f"{heads} heads cannot be split over {self.world} ranks")
         i32, i64, vp = C.c_int, C.c_longlong, C.c_void_p
-        nbytes = int(N.bind("b200_ulysses_region_bytes", i64, [i32, i32, i32, i32])(self.s_l, heads, self.world, int(self.int8)))
+        form = "b200_context_parallel" if self.context_parallel else "b200_ulysses"
+        nbytes = int(N.bind(f"{form}_region_bytes", i64, [i32, i32, i32, i32])(self.s_l, heads, self.world, int(self.int8)))
         if nbytes <= 0:
             raise ValueError("unsupported exchange shape")
-        self._out_off = int(N.bind("b200_ulysses_out_offset", i64, [i32, i32, i32, i32])(self.s_l, heads, self.world, int(self.int8)))
+        self._out_off = int(N.bind(f"{form}_out_offset", i64, [i32, i32, i32, i32])(self.s_l, heads, self.world, int(self.int8)))
+        self._phases = 15 | (16 if self.context_parallel else 0)
         # plain peer stores and loads only: no multicast mapping is needed (or wanted) for this heap
         self.heap = SymmetricHeap(comm, nbytes + 4096, self.device, multicast=False)
         self.base = self.heap.alloc(nbytes, align=1024)
@@ -69,7 +78,8 @@ class FusedUlyssesAttention:
         self.budget_cycles = int(config.get("wait_budget_ms")) * 2_000_000
         self.nbytes = nbytes
         log.decision("SequenceParallel", f"attention exchange fused into the kernels: {self.world} ranks x {self.s_l} tokens, "
-                                         f"{heads} heads, {'int8 Q K^T' if self.int8 else 'bf16'}, {nbytes / 2**20:.0f} MiB of "
+                                         f"{heads} heads ({'K / V to every rank' if self.context_parallel else 'head split'}), "
+                                         f"{'int8 Q K^T' if self.int8 else 'bf16'}, {nbytes / 2**20:.0f} MiB of "
                                          f"operand buffers per rank ({self.heap.transport})")
 
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
@@ -80,7 +90,7 @@ class FusedUlyssesAttention:
         self.epoch += 1
         st = N.state(self.device)
         rc = self._fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), self._regions, self.s_l, self.heads, self.rank, self.world,
-                      float(scale if scale is not None else 128 ** -0.5), int(self.int8), self.epoch, 15,
+                      float(scale if scale is not None else 128 ** -0.5), int(self.int8), self.epoch, self._phases,
                       self.budget_cycles, st.status.data_ptr(), N.stream())
         N.check(rc, "b200_ulysses_attention")
         return self.heap.tensor(self.base + self._out_off, (self.s_l, self.heads * 128), torch.bfloat16)

@@ -177,19 +177,21 @@ def main():
         fc.close()
     # ---- sequence-parallel attention with the exchange fused into the kernels, vs fp32 over the full sequence
     from hartsyinference_b200.parallel.ulysses import FusedUlyssesAttention
-    heads = 2 * world
-    for int8 in (False, True):
-        for s_l in (192, 100):
+    # head counts: one the group divides (head split), and one it does not (K / V to every rank)
+    for heads, int8, s_l in [(2 * world, False, 192), (2 * world, False, 100), (2 * world, True, 192), (2 * world, True, 100),
+                             (world + 1, False, 192), (world + 1, True, 100)]:
+        if True:
             gen = torch.Generator(device="cpu").manual_seed(11 + s_l)
             q, k, v = (torch.randn(world * s_l, heads, 128, generator=gen).to(torch.bfloat16).to(dev) for _ in range(3))   # same on all ranks
             sc = torch.einsum("qhd,khd->hqk", q.float(), k.float()) * 128 ** -0.5
             want = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v.float()).reshape(world * s_l, -1)
             fu = FusedUlyssesAttention(comm, s_l, heads, dev, int8=int8)
+            assert fu.context_parallel == (heads % world != 0)
             mine = slice(rank * s_l, (rank + 1) * s_l)
             for it in range(3):
                 got = fu(q[mine].contiguous(), k[mine].contiguous(), v[mine].contiguous()).clone()
                 N.check_status(dev)
-                assert rel(got, want[mine]) < (0.06 if int8 else 0.02), ("ulysses", int8, s_l, it, rel(got, want[mine]))
+                assert rel(got, want[mine]) < (0.06 if int8 else 0.02), ("ulysses", heads, int8, s_l, it, rel(got, want[mine]))
             comm.barrier()
             fu.close()
     if rank == 0:

@@ -90,6 +90,39 @@ def test_ranks_played_in_turn_match_fp32(world, s_l, heads, int8):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("world,s_l,heads", [(2, 192, 3), (4, 100, 2), (3, 300, 1)])
+def test_context_parallel_ranks_played_in_turn_match_fp32(world, s_l, heads, int8):
+    """Head counts the group size does not divide: queries and outputs stay on their rank, K / V of
+    all heads go to every rank (phase bit 16)."""
+    i32, i64 = C.c_int, C.c_longlong
+    size = N.bind("b200_context_parallel_region_bytes", i64, [i32, i32, i32, i32])
+    out_off = N.bind("b200_context_parallel_out_offset", i64, [i32, i32, i32, i32])
+    _, _, fn = _bind()
+    nbytes = int(size(s_l, heads, world, int(int8)))
+    off = int(out_off(s_l, heads, world, int(int8)))
+    regions = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    table = (C.c_void_p * 8)()
+    for r in range(world):
+        table[r] = regions[r].data_ptr()
+    q, k, v = _inputs(world * s_l, heads, 7)
+    want = _oracle(q, k, v)
+    st = N.state(torch.device("cuda", torch.cuda.current_device()))
+    parts = [tuple(t[r * s_l:(r + 1) * s_l].contiguous() for t in (q, k, v)) for r in range(world)]
+    for epoch in (1, 2):
+        for phase in (1, 2, 4, 8):
+            for r in range(world):
+                qr, kr, vr = parts[r]
+                rc = fn(qr.data_ptr(), kr.data_ptr(), vr.data_ptr(), table, s_l, heads, r, world, 128 ** -0.5, int(int8), epoch,
+                        phase | 16, 100_000_000, st.status.data_ptr(), N.stream())
+                assert rc == 0
+        N.check_status()
+        for r in range(world):
+            got = regions[r][off:off + s_l * heads * 128 * 2].view(torch.bfloat16).reshape(s_l, heads * 128)
+            assert _rel(got, want[r * s_l:(r + 1) * s_l]) < (0.06 if int8 else 0.02), (epoch, r)
+
+
+@pytest.mark.gpu
 def test_missing_peer_runs_out_and_reports():
     """Rank 0 of two runs alone: its waits for rank 1's segment and for rank 1's output share give
     up after about a millisecond each, the kernels return, and the status word says which wait."""
