@@ -131,6 +131,7 @@ def main() -> int:
         return run_reference(args)
 
     import torch
+    from hartsyinference_b200 import config as hconfig
     from hartsyinference_b200 import log
     from hartsyinference_b200.engine import LLMEngine, SamplingParams
     from hartsyinference_b200.models.llm import config as C
@@ -211,12 +212,20 @@ def main() -> int:
                 return False
             from hartsyinference_b200.parallel.fused import enable_fused_tp
             return enable_fused_tp(m, comm)
-        parity = llm_parity.run(cfg, comm, device, not args.bf16, _enable)
+        parity = llm_parity.run(cfg, comm, device, not args.bf16, _enable,
+                                dp_attention=cfg.mla is not None and bool(hconfig.get("dp_attention")),
+                                dp_fused=False if args.no_fused_comm else None)
         if rank == 0:
             log.info(f"[Bench] parity {parity}")
     t0 = time.perf_counter()
-    model = DecoderModel(cfg, device, comm=comm, fp8=not args.bf16)
+    # latent-attention MoE models: decode steps deal the requests over the ranks for the attention block
+    dp_attn = world > 1 and cfg.mla is not None and bool(hconfig.get("dp_attention")) and args.batch % world == 0
+    model = DecoderModel(cfg, device, comm=comm, fp8=not args.bf16, dp_attention=dp_attn)
     model.random_init(seed=0)
+    dp_fused = False
+    if dp_attn:
+        from hartsyinference_b200.parallel.dp_attention import enable_dp_attention
+        dp_fused = enable_dp_attention(model, comm, max_rows=args.batch, fused=False if args.no_fused_comm else None)
     fused = False
     if world > 1 and not args.no_fused_comm:
         try:
@@ -325,6 +334,9 @@ def main() -> int:
                        "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
                        "cuda_graphs": not args.no_graphs, "fused_comm": fused, "multimem": multimem,
                        "comm_path": "fused GEMM+all-reduce" if fused else "peer-memory all-reduce kernel" if peer_ar else ("nccl" if world > 1 else "none"),
+                       "attention_layout": (f"data parallel at decode: {args.batch // world} requests x all heads per rank, tokens exchanged around "
+                                            f"the expert layer {'inside the norm / combine kernels (peer stores)' if dp_fused else 'with all_gather / reduce_scatter'}; "
+                                            "prefill tensor parallel") if model.dp_exchange is not None else "tensor parallel",
                        "invalid_debug_overrides": invalid},
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "ms_per_step": wall_ms / steps,
                     "h2d_bytes_per_step": h2d // steps, "d2h_bytes_per_step": d2h // steps},
@@ -340,6 +352,10 @@ def main() -> int:
         eng._graphs.clear()
         from hartsyinference_b200.parallel.fused import disable_fused_tp
         disable_fused_tp(model, comm)
+        if model.dp_exchange is not None:
+            torch.cuda.synchronize()
+            comm.barrier()
+            model.dp_exchange.close()
     return _leave(comm, world)
 
 
@@ -387,6 +403,13 @@ def _weight_bytes_estimate(cfg, world: int, fp8: bool) -> int:
         else:
             total += attn + dense
     emb = cfg.vocab_size * H * 2 * (1 if cfg.tie_embeddings else 1 + 1 / world)
+    if cfg.mla is not None and world > 1:
+        # the data-parallel attention layout also keeps the attention weights of all heads on every rank
+        m = cfg.mla
+        dq = m.qk_nope_head_dim + m.qk_rope_head_dim
+        full = (m.q_lora_rank or H) * cfg.num_heads * dq + H * cfg.num_heads * m.v_head_dim \
+            + cfg.num_heads * m.kv_lora_rank * (m.qk_nope_head_dim + m.v_head_dim) * 2 // per
+        total += L * full
     return int(total * per + emb)
 
 

@@ -74,9 +74,11 @@ def _weights(cfg, dev):
     return get
 
 
-def run(cfg, comm, dev, fp8: bool, enable_fused=None) -> dict:
+def run(cfg, comm, dev, fp8: bool, enable_fused=None, dp_attention: bool = False, dp_fused=None) -> dict:
     """All ranks call this. ``enable_fused(model)`` (optional) switches the sharded model to the
-    fused kernels the benchmark will use."""
+    fused kernels the benchmark will use. ``dp_attention``: the sharded model also runs one decode step
+    of ``2 x ranks`` requests in the data-parallel attention layout (after prefilling them in the
+    tensor-parallel layout) and its logits are compared too (``decode_*`` fields)."""
     moe = cfg.moe
     if moe is not None and moe.num_experts > 0:
         moe = replace(moe, first_dense_layers=min(1, moe.first_dense_layers))
@@ -95,34 +97,67 @@ def run(cfg, comm, dev, fp8: bool, enable_fused=None) -> dict:
                          cu_q=torch.tensor([0, t], dtype=torch.int32, device=dev), max_q_len=t, max_kv_len=t)
         return model.full_logits(model.forward_hidden(b)).float()
 
-    sharded = DecoderModel(cfg2, dev, comm=comm, fp8=fp8)
+    seqs, plen, page = 2 * comm.world, 24, 32
+
+    def decode_step(model):
+        """Prefill ``seqs`` requests of ``plen`` tokens (one page each), then one decode step of all of
+        them with fixed input tokens: [seqs, vocab] logits."""
+        model.alloc_kv(seqs + 1, page)
+        gd = torch.Generator().manual_seed(11)
+        tok = torch.randint(0, cfg2.vocab_size, (seqs * plen,), generator=gd).to(torch.int32).to(dev)
+        nxt = torch.randint(0, cfg2.vocab_size, (seqs,), generator=gd).to(torch.int32).to(dev)
+        ar = torch.arange(seqs, device=dev)
+        table = ar.to(torch.int32)[:, None].contiguous()
+        b = ForwardBatch(tokens=tok, positions=torch.arange(plen, dtype=torch.int32, device=dev).repeat(seqs),
+                         slot_mapping=(ar[:, None] * page + torch.arange(plen, device=dev)[None]).reshape(-1).to(torch.int64),
+                         block_table=table, kv_lens=torch.full((seqs,), plen, dtype=torch.int32, device=dev), is_decode=False,
+                         cu_q=(torch.arange(seqs + 1, dtype=torch.int32, device=dev) * plen), max_q_len=plen, max_kv_len=plen)
+        model.forward_hidden(b)
+        b = ForwardBatch(tokens=nxt, positions=torch.full((seqs,), plen, dtype=torch.int32, device=dev),
+                         slot_mapping=(ar * page + plen).to(torch.int64), block_table=table,
+                         kv_lens=torch.full((seqs,), plen + 1, dtype=torch.int32, device=dev), is_decode=True,
+                         max_q_len=1, max_kv_len=plen + 1)
+        return model.full_logits(model.forward_hidden(b)).float()
+
+    dp_attention = dp_attention and cfg2.mla is not None and comm.world > 1
+    sharded = DecoderModel(cfg2, dev, comm=comm, fp8=fp8, dp_attention=dp_attention)
     sharded.load_state_dict(get)
     path = "nccl"
     if enable_fused is not None and enable_fused(sharded):
         path = "fused"
     got = forward(sharded)
+    got_dec, dp_path = None, None
+    if dp_attention:
+        from hartsyinference_b200.parallel.dp_attention import enable_dp_attention
+        dp_path = "fused" if enable_dp_attention(sharded, comm, max_rows=seqs, fused=dp_fused) else "collectives"
+        got_dec = decode_step(sharded)
     if dev.type == "cuda":
         torch.cuda.synchronize()
-    for name in ("fused_rp", "custom_ar"):
+    for name in ("fused_rp", "custom_ar", "dp_exchange"):
         obj = getattr(sharded, name, None)
         if obj is not None:
             obj.close()
     del sharded
-    res = torch.zeros(4, device=dev)
+    res = torch.zeros(7, device=dev)
     if comm.rank == 0:
         one = DecoderModel(cfg2, dev, comm=SingleComm(), fp8=fp8)
         one.load_state_dict(get)
         ref = forward(one)
-        del one
         rows = torch.nn.functional.cosine_similarity(got, ref, dim=-1)
         res[0] = rows.min()
         res[1] = (got.argmax(-1) == ref.argmax(-1)).float().mean()
         res[2] = rows.median()
         res[3] = (rows < 0.99).float().sum()
+        if got_dec is not None:
+            ref_dec = decode_step(one)
+            rows = torch.nn.functional.cosine_similarity(got_dec, ref_dec, dim=-1)
+            res[4], res[5] = rows.min(), rows.median()
+            res[6] = (got_dec.argmax(-1) == ref_dec.argmax(-1)).float().mean()
+        del one
     comm.broadcast(res, 0)
     if dev.type == "cuda":
         torch.cuda.empty_cache()
-    cos, agree, med, low = (float(v) for v in res.tolist())
+    cos, agree, med, low, dcos, dmed, dagree = (float(v) for v in res.tolist())
     out = {"ok": cos > 0.99, "cos": cos, "cos_median": med, "rows_below_0.99": int(low), "greedy_agreement": agree, "path": path,
            "what": f"2-layer slice (vocab {PARITY_VOCAB}), {t}-token prompt, {comm.world} ranks vs 1; cos = minimum over rows"}
     if cfg.moe is not None and cfg.moe.num_experts > 0:
@@ -130,4 +165,8 @@ def run(cfg, comm, dev, fp8: bool, enable_fused=None) -> dict:
         # order, so a few rows pick a different expert set and differ as a whole, the others agree closely
         out["ok"] = med > 0.99 and cos > 0.9
         out["what"] += "; MoE: rows whose near-tied routing flips differ, judged by the median row (and minimum > 0.9)"
+    if dp_path is not None:
+        out.update(decode_cos=dcos, decode_cos_median=dmed, decode_greedy_agreement=dagree, decode_path=dp_path,
+                   decode_what=f"one decode step of {seqs} requests after a {plen}-token prefill, attention data parallel")
+        out["ok"] = bool(out["ok"] and dmed > 0.99 and dcos > 0.9)
     return out

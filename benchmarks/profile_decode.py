@@ -37,6 +37,9 @@ def main() -> None:
                     help="build rank 0's shard of an N-way tensor-parallel group on one GPU (no peers)")
     ap.add_argument("--fused", action="store_true",
                     help="with --tp-shard: run the fused GEMM + all-reduce + norm kernel with this GPU standing in for its peers")
+    ap.add_argument("--dp-attention", action="store_true",
+                    help="with --tp-shard on a latent-attention MoE preset: rank 0's work of the data-parallel attention "
+                         "layout (batch / N requests x all heads, experts over all rows); the exchange is emulated")
     args = ap.parse_args()
     cfg = C.PRESETS[args.preset]
     if args.layers:
@@ -46,8 +49,25 @@ def main() -> None:
     if args.tp_shard > 1:   # same per-GPU GEMM / attention shapes as rank 0 of a TP group
         from hartsyinference_b200.parallel.comm import ShardEmulationComm
         comm = ShardEmulationComm(args.tp_shard)
-    model = DecoderModel(cfg, dev, comm=comm, fp8=not args.bf16)
+    model = DecoderModel(cfg, dev, comm=comm, fp8=not args.bf16, dp_attention=args.dp_attention)
     model.random_init(0)
+    if args.dp_attention and comm is not None:
+        from hartsyinference_b200.parallel.dp_attention import CollectiveDpExchange
+
+        class _Peerless:
+            """Stands in for the group: a gather repeats this rank's rows, a reduce-scatter keeps its share."""
+            rank, world = comm.rank, comm.world
+
+            @staticmethod
+            def all_gather(t, dim=0):
+                return t.repeat_interleave(comm.world, dim=dim) if dim else t.repeat(comm.world, *([1] * (t.dim() - 1)))
+
+            @staticmethod
+            def reduce_scatter(t, dim=0):
+                return t.chunk(comm.world, dim=dim)[comm.rank].contiguous()
+
+        model.dp_exchange = CollectiveDpExchange(_Peerless, args.batch, cfg.hidden_size, dev)
+        model.comm.all_gather = _Peerless.all_gather        # the final gather of the hidden states
     if args.fused and comm is not None:
         from hartsyinference_b200.parallel.fused import FusedRowParallel
         model.fused_rp = FusedRowParallel(comm, cfg.hidden_size, dev, emulate_peers=True)

@@ -44,6 +44,7 @@ enum KernelId : uint32_t {
   kKernelCfgStep = 9,
   kKernelAllToAll = 10,
   kKernelWaitProbe = 11,
+  kKernelDpExchange = 12,
 };
 
 struct DeviceStatus {

@@ -63,6 +63,9 @@ class MlaAttention:
         self.cfg, self.m, self.w = cfg, m, weights
         self.heads = heads_local
         self.dq = m.qk_nope_head_dim + m.qk_rope_head_dim
+        # False: the output projection covers all heads on this rank (data-parallel attention), so there
+        # is nothing to sum over the ranks
+        self.reduce_output = True
 
     def nbytes(self) -> int:
         n = sum(w.nbytes() for w in self.w.all())
@@ -106,7 +109,7 @@ class MlaAttention:
                            max_kv_len=batch.max_kv_len or None)
         v = torch.empty(t, self.heads * m.v_head_dim, dtype=h.dtype, device=h.device)
         ops.colbatched_linear(lat.view(t, self.heads * LATENT), w.w_uv.weight, self.heads, LATENT, v, m.v_head_dim)
-        return model._reduce_linear(v, w.o)
+        return model._reduce_linear(v, w.o) if self.reduce_output else ops.linear(v, w.o)
 
 
 def mla_reference(h: torch.Tensor, positions: torch.Tensor, cfg: TransformerConfig, full: dict,

@@ -114,6 +114,11 @@ class MoeFeedForward:
 
     def _routed_gpu(self, h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, out: torch.Tensor,
                     accumulate: bool) -> None:
+        y, plan = self._experts_gpu(h, ids)
+        ops.moe_combine(y, plan.slot_of, wts, out, accumulate=accumulate)
+
+    def _experts_gpu(self, h: torch.Tensor, ids: torch.Tensor):
+        """Dispatch + the two grouped GEMMs of this rank's experts: (outputs by slot, dispatch plan)."""
         t = h.shape[0]
         # variable-size dispatch: every expert gets as many blocks of `cap` slots as its tokens need
         # (device-side plan, no host round trip), so the grouped GEMMs run only over blocks that hold
@@ -129,7 +134,22 @@ class MoeFeedForward:
         fp8 = self.w.down.is_fp8
         a, a8 = ops.glu(gu, self.cfg.activation, emit_fp8=fp8, emit_bf16=not fp8, fp8_tile_rows=cap)
         y = ops.grouped_linear_dynamic(a8 if a8 is not None else a, self.w.down, self.e_local, plan)
-        ops.moe_combine(y, plan.slot_of, wts, out, accumulate=accumulate)
+        return y, plan
+
+    def forward_partial(self, h: torch.Tensor, exchange) -> None:
+        """This rank's contribution (its experts + its shard of the shared expert) to every row of ``h``
+        [T, H], handed to ``exchange.scatter`` uncombined so that the combine kernel can store each
+        row at the rank that owns it (parallel/dp_attention.py). T <= 1024."""
+        assert h.shape[0] <= _CHUNK
+        ids, wts = self.route(h)
+        shared = self._shared(h)
+        if h.is_cuda:
+            y, plan = self._experts_gpu(h.contiguous(), ids)
+            exchange.scatter(y, plan.slot_of, wts, shared, self.moe.top_k)
+        else:
+            out = shared if shared is not None else torch.zeros_like(h)
+            self._routed_cpu(h, ids, wts, out)
+            exchange.scatter(None, None, None, out, 0)
 
     # ---------------------------------------------------------------------------------- forward
     def __call__(self, h: torch.Tensor, model=None) -> torch.Tensor:

@@ -109,6 +109,8 @@ class LayerWeights:
     post_ffn_norm: Optional[torch.Tensor] = None
     ffn_module: Optional[object] = None               # MoE feed-forward (callable) instead of gate_up/down
     attn_module: Optional[object] = None              # MLA attention (callable) instead of qkv/o
+    attn_dp: Optional[object] = None                  # the same attention over ALL heads with replicated weights
+                                                      # (data-parallel attention at decode, parallel/dp_attention.py)
     in_norm_b: Optional[torch.Tensor] = None          # LayerNorm biases (StableLM, StarCoder 2, GPT-NeoX, Nemotron)
     post_norm_b: Optional[torch.Tensor] = None
     cross: Optional[object] = None                    # cross-attention layer over vision states (Mllama) instead of a block
@@ -122,7 +124,7 @@ def x_is_cuda(x) -> bool:
 
 class DecoderModel:
     def __init__(self, cfg: TransformerConfig, device: torch.device | str = "cpu", comm: Optional[Comm] = None,
-                 fp8: bool = False, layer_range: Optional[tuple[int, int]] = None):
+                 fp8: bool = False, layer_range: Optional[tuple[int, int]] = None, dp_attention: bool = False):
         self.cfg = cfg
         # pipeline stage: this instance holds layers [layer0, layer1) only (all of them by default)
         self.layer0, self.layer1 = layer_range if layer_range is not None else (0, cfg.num_layers)
@@ -161,6 +163,10 @@ class DecoderModel:
         # fused row-parallel linear + all-reduce + residual + RMSNorm (+ fp8 emit) kernel
         # (parallel/fused.py::FusedRowParallel); drives the whole layer loop of small batches
         self.fused_rp = None
+        # data-parallel attention at decode (latent-attention MoE models, tp > 1): every layer also holds
+        # the attention weights of all heads; ``dp_exchange`` (parallel/dp_attention.py) moves the tokens
+        self.dp_attention = bool(dp_attention) and cfg.mla is not None and self.tp > 1 and layer_range is None
+        self.dp_exchange = None
 
     # ------------------------------------------------------------------------------ weights
     def _lw(self, w: torch.Tensor, bias: Optional[torch.Tensor] = None, allow_fp8: bool = True) -> LinearWeight:
@@ -256,6 +262,7 @@ class DecoderModel:
                 lw.post_norm_b = dev(get(p + post_name + ".bias"))
             if cfg.mla is not None:
                 lw.attn_module = self._load_mla(need, get, p + "self_attn.")
+                lw.attn_dp, self._attn_dp_pending = getattr(self, "_attn_dp_pending", None), None
             else:
                 q = need(p + "self_attn.q_proj.weight")[r * self.hq * d:(r + 1) * self.hq * d]
                 k = need(p + "self_attn.k_proj.weight")[kvs.start * d:kvs.stop * d]
@@ -332,6 +339,15 @@ class DecoderModel:
             w_uk=self._lw(w_uk, allow_fp8=False), w_uv=self._lw(w_uv, allow_fp8=False),
             o=self._lw(need(p + "o_proj.weight")[:, r * hl * m.v_head_dim:(r + 1) * hl * m.v_head_dim]
                        .contiguous().to(dt)))
+        if self.dp_attention:
+            heads = cfg.num_heads
+            uk, uv = split_kv_b(need(p + "kv_b_proj.weight").to(dt), heads, m.qk_nope_head_dim, m.v_head_dim)
+            full = MlaWeights(q_a=w.q_a, q_a_norm=w.q_a_norm,
+                              q_b=self._lw(need(p + ("q_b_proj.weight" if m.q_lora_rank else "q_proj.weight")).to(dt)),
+                              kv_a=w.kv_a, kv_a_norm=w.kv_a_norm, w_uk=self._lw(uk, allow_fp8=False),
+                              w_uv=self._lw(uv, allow_fp8=False), o=self._lw(need(p + "o_proj.weight").to(dt)))
+            self._attn_dp_pending = MlaAttention(cfg, full, heads)
+            self._attn_dp_pending.reduce_output = False
         return MlaAttention(cfg, w, hl)
 
     def _load_moe(self, need, get, p: str):
@@ -385,8 +401,14 @@ class DecoderModel:
             ops.fill_random_(t, counter[0], s)
             return t
 
-        def lin(n, k, bias=False, allow_fp8=True):
+        def lin(n, k, bias=False, allow_fp8=True, seed=None):
             counter[0] += 1
+            if seed is not None:          # a tensor that is the same on every rank
+                keep, counter[0] = counter[0], seed
+                try:
+                    return lin(n, k, bias, allow_fp8)
+                finally:
+                    counter[0] = keep
             if self.fp8 and allow_fp8 and k % 128 == 0:
                 w = torch.empty(n, k, dtype=torch.uint8, device=dev)
                 ops.fill_random_(w, counter[0])
@@ -428,6 +450,7 @@ class DecoderModel:
                 lw.ffn_module = self._random_moe(lin, dense)
             if cfg.mla is not None:
                 lw.attn_module = self._random_mla(lin, ones)
+                lw.attn_dp, self._attn_dp_pending = getattr(self, "_attn_dp_pending", None), None
             if cfg.qk_norm:
                 lw.q_norm, lw.k_norm = ones(d), ones(d)
             if cfg.post_norms:
@@ -461,6 +484,8 @@ class DecoderModel:
         cfg, m = self.cfg, self.cfg.mla
         hl = self.hq
         dq = m.qk_nope_head_dim + m.qk_rope_head_dim
+        if self.dp_attention:
+            return self._random_mla_dp(lin, ones)
         w = MlaWeights(
             q_a=lin(m.q_lora_rank, cfg.hidden_size) if m.q_lora_rank else None,
             q_a_norm=ones(m.q_lora_rank) if m.q_lora_rank else None,
@@ -471,6 +496,51 @@ class DecoderModel:
             w_uv=lin(hl * m.v_head_dim, m.kv_lora_rank, allow_fp8=False),
             o=lin(cfg.hidden_size, hl * m.v_head_dim))
         return MlaAttention(cfg, w, hl)
+
+    def _random_mla_dp(self, lin, ones):
+        """Attention weights of all heads, the same on every rank (seeded independently of the rank), and
+        this rank's head shard for the tensor-parallel prefill path as slices of them, so that prefill
+        and decode are the same model."""
+        from .mla import MlaAttention, MlaWeights
+        cfg, m, r = self.cfg, self.cfg.mla, self.tp_rank
+        heads, hl = cfg.num_heads, self.hq
+        dq = m.qk_nope_head_dim + m.qk_rope_head_dim
+
+        def shared(n, k, allow_fp8=True):      # the factory's own counter depends on the rank
+            self._replicated_seed = getattr(self, "_replicated_seed", 9_000_001) + 2
+            return lin(n, k, allow_fp8=allow_fp8, seed=self._replicated_seed)
+
+        q_in = m.q_lora_rank if m.q_lora_rank else cfg.hidden_size
+        full = MlaWeights(
+            q_a=shared(m.q_lora_rank, cfg.hidden_size) if m.q_lora_rank else None,
+            q_a_norm=ones(m.q_lora_rank) if m.q_lora_rank else None,
+            q_b=shared(heads * dq, q_in),
+            kv_a=shared(m.kv_lora_rank + m.qk_rope_head_dim, cfg.hidden_size, allow_fp8=False),
+            kv_a_norm=ones(m.kv_lora_rank),
+            w_uk=shared(heads * m.kv_lora_rank, m.qk_nope_head_dim, allow_fp8=False),
+            w_uv=shared(heads * m.v_head_dim, m.kv_lora_rank, allow_fp8=False),
+            o=shared(cfg.hidden_size, heads * m.v_head_dim))
+
+        def rows(w: LinearWeight, per: int) -> LinearWeight:
+            a, b = r * hl * per, (r + 1) * hl * per
+            if w.scale is None:
+                return LinearWeight(w.weight[a:b])
+            assert a % 128 == 0 and b % 128 == 0, "head shard not aligned to the 128-row scale blocks"
+            return LinearWeight.from_quantized(w.weight[a:b], w.scale[a // 128:b // 128].contiguous())
+
+        def cols(w: LinearWeight, per: int) -> LinearWeight:
+            a, b = r * hl * per, (r + 1) * hl * per
+            if w.scale is None:
+                return LinearWeight(w.weight[:, a:b].contiguous())
+            assert a % 128 == 0 and b % 128 == 0, "head shard not aligned to the 128-column scale blocks"
+            return LinearWeight.from_quantized(w.weight[:, a:b].contiguous(), w.scale[:, a // 128:b // 128].contiguous())
+
+        shard = MlaWeights(q_a=full.q_a, q_a_norm=full.q_a_norm, q_b=rows(full.q_b, dq), kv_a=full.kv_a,
+                           kv_a_norm=full.kv_a_norm, w_uk=rows(full.w_uk, m.kv_lora_rank),
+                           w_uv=rows(full.w_uv, m.v_head_dim), o=cols(full.o, m.v_head_dim))
+        self._attn_dp_pending = MlaAttention(cfg, full, heads)
+        self._attn_dp_pending.reduce_output = False
+        return MlaAttention(cfg, shard, hl)
 
     def weight_bytes(self) -> int:
         n = self.embed.numel() * 2 + self.final_norm.numel() * 2
@@ -486,6 +556,8 @@ class DecoderModel:
                 n += lw.ffn_module.nbytes()
             if lw.attn_module is not None and hasattr(lw.attn_module, "nbytes"):
                 n += lw.attn_module.nbytes()
+            if lw.attn_dp is not None:      # the all-head copy (its head shard above may share storage with it)
+                n += lw.attn_dp.nbytes()
         return n
 
     # ------------------------------------------------------------------------------ KV cache
@@ -768,6 +840,55 @@ class DecoderModel:
                              norm_w=self.layers[li + 1].in_norm, emit_fp8=n8, emit_bf16=not n8, **kw)
         return h
 
+    def _dp_attention_ok(self, batch: ForwardBatch) -> bool:
+        """True when this decode step can run in the data-parallel attention layout: a plain pre-norm
+        RMSNorm stack whose every layer has the all-head attention weights, and a row count the ranks
+        divide."""
+        ex, cfg = self.dp_exchange, self.cfg
+        if ex is None or not batch.is_decode or batch.embeds is not None or not (self.first_stage and self.last_stage):
+            return False
+        if cfg.general_path or cfg.post_norms or cfg.residual_multiplier != 1.0 or cfg.norm_plus_one:
+            return False
+        if self.embed_norm_w is not None or self.pos_embed is not None or batch.deepstack is not None:
+            return False
+        if not ex.supports(batch.tokens.shape[0]):
+            return False
+        return all(lw.attn_dp is not None and lw.cross is None for lw in self.layers)
+
+    def _forward_dp_attention(self, batch: ForwardBatch) -> torch.Tensor:
+        """Decode step with the requests dealt over the ranks for the attention block and the expert /
+        feed-forward block run over all rows with this rank's weight shards. Per layer:
+
+            attention of the L local rows (all heads)     [residual + RMSNorm -> every rank's buffer]
+            router, experts, shared expert over T rows    [combine -> owning rank; sum + residual + RMSNorm]
+
+        where each bracket is one exchange step (parallel/dp_attention.py). Returns the final-normed
+        hidden states of all T rows (one all-gather at the end), like the tensor-parallel path."""
+        cfg, ex = self.cfg, self.dp_exchange
+        t = batch.tokens.shape[0]
+        l = t // self.tp
+        sl = slice(self.tp_rank * l, (self.tp_rank + 1) * l)
+        lb = ForwardBatch(tokens=batch.tokens[sl], positions=batch.positions[sl], slot_mapping=batch.slot_mapping[sl],
+                          block_table=batch.block_table[sl], kv_lens=batch.kv_lens[sl], is_decode=True, max_q_len=1,
+                          max_kv_len=batch.max_kv_len)
+        res = ops.embedding(lb.tokens, self.embed, cfg.embed_scale * cfg.embedding_multiplier).contiguous()
+        h, _, _ = ops.norm(res, self.layers[0].in_norm, eps=cfg.rms_eps)
+        fp8 = self.fp8 and res.is_cuda
+        last = len(self.layers) - 1
+        for li, lw in enumerate(self.layers):
+            a = lw.attn_dp(h, lb, li, self)
+            cache = self.kv_cache[li] if self.kv_cache is not None else None
+            g = ex.gather(a.contiguous(), res, lw.post_norm, cfg.rms_eps, cache, lb.slot_mapping, batch.slot_mapping)
+            if lw.ffn_module is not None:
+                lw.ffn_module.forward_partial(g, ex)
+            else:
+                gu = ops.linear(g, lw.gate_up)
+                d8 = fp8 and lw.down.is_fp8
+                act, act8 = ops.glu(gu, cfg.activation, emit_fp8=d8, emit_bf16=not d8)
+                ex.scatter(None, None, None, ops.linear(act8 if act8 is not None else act, lw.down), 0)
+            h = ex.reduce(res, self.final_norm if li == last else self.layers[li + 1].in_norm, cfg.rms_eps)
+        return self.comm.all_gather(h.contiguous(), dim=0)
+
     def forward_hidden(self, batch: ForwardBatch, hidden_in: Optional[tuple] = None):
         """Runs this instance's layers. The last pipeline stage (the only one by default) returns the
         final-normed hidden states [T, H]; an earlier stage returns ``(x, residual)`` for the next
@@ -775,6 +896,8 @@ class DecoderModel:
         cfg = self.cfg
         d = cfg.head_dim
         res: Optional[torch.Tensor] = None
+        if hidden_in is None and self._dp_attention_ok(batch):
+            return self._forward_dp_attention(batch)
         if hidden_in is not None:
             x, res = hidden_in
         elif batch.embeds is not None:
@@ -791,6 +914,7 @@ class DecoderModel:
             return self._forward_general(batch, x if res is None else (x.float() + res.float()).to(x.dtype), scale)
         if hidden_in is None and x.is_cuda and self._fused_tp_ok(x.shape[0]):
             return self._forward_fused_tp(batch, x)
+
         for li, lw in enumerate(self.layers):
             # ---- attention block
             if res is None:
