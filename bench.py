@@ -267,17 +267,21 @@ def main() -> int:
     torch.cuda.synchronize()
     peer_ar = getattr(model, "custom_ar", None) is not None
     multimem = bool(getattr(getattr(model, "fused_rp", None) or getattr(model, "custom_ar", None), "use_mc", False))
-    if fused or peer_ar:
+    if fused or peer_ar or dp_fused:
         # A bounded wait of the peer-memory kernels that gave up on any rank means the peer protocol
         # did not work on this machine: fall back to NCCL on every rank rather than time garbage.
         bad = torch.tensor([int(N.state(device).status[0].item() != 0)], device=device)
         import torch.distributed as dist
         dist.all_reduce(bad, op=dist.ReduceOp.MAX)
         if int(bad.item()) != 0:
-            log.warn("[Collective] peer-memory TP kernels reported a wait timeout; falling back to NCCL")
+            log.warn("[Collective] peer-memory kernels reported a wait timeout; falling back to NCCL")
             N.state(device).reset_after_fault()
             from hartsyinference_b200.parallel.fused import disable_fused_tp
             disable_fused_tp(model, comm)
+            if dp_fused:
+                from hartsyinference_b200.parallel.dp_attention import enable_dp_attention
+                model.dp_exchange.close()
+                dp_fused = enable_dp_attention(model, comm, max_rows=args.batch, fused=False)
             peer_ar = False
             eng._graphs.clear()
             fused = False

@@ -74,6 +74,9 @@ def _mla(argv):
     q = (torch.randn(rows, heads, 576, device="cuda") * 0.3).to(torch.bfloat16)
     for _ in range(3):
         ops.mla_attn(q, cache, table, lens, 1.0 / math.sqrt(192), max_kv_len=ctx)
+    ms = _time_cold(lambda: ops.mla_attn(q, cache, table, lens, 1.0 / math.sqrt(192), max_kv_len=ctx))
+    print(f"mla {rows} x {heads} x {ctx}: {ms * 1e3:.1f} us ({rows * ctx * 576 * 2 / ms / 1e9:.2f} TB/s of distinct cache bytes, "
+          f"{rows * heads * ctx * (576 + 512) * 2 / ms / 1e9:.0f} TFLOP/s)")
 
 
 def _time(fn, reps=5):
@@ -90,6 +93,59 @@ def _time(fn, reps=5):
         e1.synchronize()
         ts.append(e0.elapsed_time(e1))
     return sorted(ts)[len(ts) // 2]
+
+
+def _time_cold(fn, reps=7):
+    """Median device time (ms) of ``fn`` with the L2 cache flushed before every run (a 256 MB buffer is
+    rewritten), as weights arrive inside a decode step."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    ts = []
+    for i in range(reps + 2):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        if i >= 2:
+            ts.append(e0.elapsed_time(e1))
+    return sorted(ts)[len(ts) // 2]
+
+
+def _mla_proj(argv):
+    """mla_proj TOKENS HEADS: the projections around the latent attention of DeepSeek-V3 (hidden 7168,
+    q rank 1536, 128 + 64 query dims, 512 latent, 128 value dims) for TOKENS rows and HEADS heads, each
+    timed by itself with a cold L2: q_b (fp8), rotary / cache-write prep, W_uk absorb, W_uv, o (fp8)."""
+    t, heads = (int(v) for v in argv[:2])
+    dev = "cuda"
+    bf = lambda *s_: (torch.randn(*s_, device=dev) * 0.05).to(torch.bfloat16)
+    q_b = ops.LinearWeight.from_dense(bf(heads * 192, 1536), fp8=True)
+    o_w = ops.LinearWeight.from_dense(bf(7168, heads * 128), fp8=True)
+    w_uk, w_uv = bf(heads * 512, 128), bf(heads * 128, 512)
+    qa8 = ops.quant_fp8_act(bf(t, 1536))
+    q = bf(t, heads * 192)
+    q_abs = torch.empty(t, heads, 576, dtype=torch.bfloat16, device=dev)
+    lat = bf(t, heads * 512)
+    v = torch.empty(t, heads * 128, dtype=torch.bfloat16, device=dev)
+    v8 = ops.quant_fp8_act(bf(t, heads * 128))
+    kv = bf(t, 576)
+    cache = torch.zeros(t + 16, 576, dtype=torch.bfloat16, device=dev)
+    pos = torch.arange(t, dtype=torch.int32, device=dev)
+    slots = torch.arange(t, dtype=torch.int64, device=dev)
+    inv_freq = torch.rand(32, device=dev)
+    ones = torch.ones(512, dtype=torch.bfloat16, device=dev)
+    q_fold = ops.LinearWeight.from_dense(bf(heads * 576, 1536), fp8=True)
+    cases = [
+        ("q_b fp8", lambda: ops.linear(qa8, q_b), heads * 192 * 1536),
+        ("q_b with W_uk folded in, fp8", lambda: ops.linear(qa8, q_fold), heads * 576 * 1536),
+        ("mla_prep", lambda: ops.mla_prep(kv, ones, q, q_abs, cache, pos, slots, inv_freq, heads, 192, 128), t * heads * 192 * 2),
+        ("W_uk absorb", lambda: ops.colbatched_linear(q, w_uk, heads, 192, q_abs.view(t, heads * 576), 576), heads * 512 * 128 * 2),
+        ("W_uv", lambda: ops.colbatched_linear(lat, w_uv, heads, 512, v, 128), heads * 128 * 512 * 2),
+        ("o fp8", lambda: ops.linear(v8, o_w), heads * 128 * 7168),
+    ]
+    for name, fn, nbytes in cases:
+        ms = _time_cold(fn)
+        print(f"mla_proj {t} x {heads} {name}: {ms * 1e3:.1f} us ({nbytes / ms / 1e9:.2f} TB/s of weight bytes)")
 
 
 def _attn_dense(argv):
@@ -229,7 +285,7 @@ def _triplane(argv):
     print(f"triplane {res}^3 = {pts} points: {t:.2f} ms, {flop / t / 1e9:.1f} TFLOP/s fp32, {pts / t / 1e6:.2f} G points/s")
 
 
-CASES = {"gemm_ar_large": _gemm_ar_large, "ag_gemm": _ag_gemm, "ulysses": _ulysses, "allreduce": _allreduce, "sample": _sample,
+CASES = {"mla_proj": _mla_proj, "gemm_ar_large": _gemm_ar_large, "ag_gemm": _ag_gemm, "ulysses": _ulysses, "allreduce": _allreduce, "sample": _sample,
          "int8": _int8, "triplane": _triplane,
          "gemm_ar": _gemm_ar, "attn_dense": _attn_dense, "gemm": _gemm, "grouped": _grouped, "attn_decode": _attn_decode, "mla": _mla}
 

@@ -101,6 +101,7 @@ declare("fused_dit_tp", bool, True, "tensor-parallel DiT: row-parallel linears r
 declare("fused_dit_sp", bool, True, "tensor-parallel DiT blocks keep activations sharded by token rows between the linears (all-gather -> GEMM, GEMM -> reduce-scatter kernels); off = replicated activations")
 declare("fused_cfg_combine", bool, True, "CFG-parallel video pipelines combine the two branches with the peer-memory kernel; off = NCCL all_gather")
 declare("fused_ulysses", bool, True, "sequence-parallel attention exchanges heads inside the quantisation / attention kernels (peer stores into the symmetric heap); off = NCCL all-to-all")
+declare("mla_fold_q", bool, True, "latent attention on a CUDA device: keep a second query projection with W_uk folded in ([heads * 576, q rank]) and use it for batches of up to 256 rows (one GEMM instead of q_b + per-head absorb); off = always q_b + absorb")
 declare("dp_attention", bool, True, "latent-attention MoE models on more than one GPU: decode steps deal the requests over the ranks for the attention block (all heads, replicated attention weights) and exchange tokens around the expert layer; off = tensor-parallel attention over all requests")
 declare("fused_dp_exchange", bool, True, "the token exchange of the data-parallel attention layout runs inside the norm / expert-combine kernels over peer memory; off = all_gather / reduce_scatter collectives")
 declare("sage_attention", bool, False, "int8 Q K^T (SageAttention: K mean removal, per-row int8 scales, tcgen05 kind::i8) in the dense attention kernel")

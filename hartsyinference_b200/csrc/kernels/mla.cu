@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(128) mla_prep_kernel(const MlaPrepParams p) {
     cs[tid] = c * p.rope_mscale;
     sn[tid] = s * p.rope_mscale;
   }
+  // grid.y deals the heads' q_pe rotation in chunks of 16; the latent row is the first chunk's work
+  if (blockIdx.y == 0) {
   // latent RMSNorm: 4 values per thread
   const __nv_bfloat16* row = p.kv + static_cast<long long>(t) * kRow;
   float v[4];
@@ -88,8 +90,12 @@ __global__ void __launch_bounds__(128) mla_prep_kernel(const MlaPrepParams p) {
           pack_bf16x2(x.x * cs[tid] - x.y * sn[tid], x.x * sn[tid] + x.y * cs[tid]);
     }
   }
-  // q_pe of every head
-  for (int i = tid; i < p.heads * 32; i += blockDim.x) {
+  } else {
+    __syncthreads();     // the rotation table
+  }
+  // q_pe of this block's heads
+  const int h0 = blockIdx.y * 16, h1 = min(p.heads, h0 + 16);
+  for (int i = h0 * 32 + tid; i < h1 * 32; i += blockDim.x) {
     const int h = i >> 5, j = i & 31;
     const __nv_bfloat16* src = p.q + (static_cast<long long>(t) * p.heads + h) * p.q_stride + p.q_rope_off + 2 * j;
     const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src));
@@ -111,19 +117,23 @@ struct MlaAttnParams {
   float scale_log2;
 };
 
+// kSets groups of four warps share one CTA and one staged KV tile; each group owns 16 heads of the
+// same query row (with many heads per row, as in the data-parallel attention layout, every tile that
+// is read from memory then serves 32 heads instead of 16, and eight warps hide each other's latencies).
+template <int kSets>
 struct MlaSmem {
   uint8_t kv[2][kMlaTile * kPitch];
-  uint8_t q[16 * kPitch];
-  uint8_t pmat[16 * kPPitch];
-  float red_max[4][16];
-  float red_sum[4][16];
+  uint8_t q[kSets][16 * kPitch];
+  uint8_t pmat[kSets][16 * kPPitch];
+  float red_max[kSets][4][16];
+  float red_sum[kSets][4][16];
   int pages[2][kMaxPagesPerTile];
 };
 
 __device__ __forceinline__ void mla_load_tile(uint32_t dst, const MlaAttnParams& p, const int* pages,
                                               int tok0, int kv_len) {
   // 64 tokens x 72 chunks of 16 bytes
-  for (int i = threadIdx.x; i < kMlaTile * (kRow / 8); i += kMlaThreads) {
+  for (int i = threadIdx.x; i < kMlaTile * (kRow / 8); i += blockDim.x) {
     const int token = i / (kRow / 8), chunk = i - token * (kRow / 8);
     const int pos = tok0 + token;
     const bool valid = pos < kv_len;
@@ -133,29 +143,37 @@ __device__ __forceinline__ void mla_load_tile(uint32_t dst, const MlaAttnParams&
   }
 }
 
-__global__ void __launch_bounds__(kMlaThreads) mla_attn_kernel(const MlaAttnParams p) {
+template <int kSets>
+__global__ void __launch_bounds__(kMlaThreads * kSets) mla_attn_kernel(const MlaAttnParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  MlaSmem& sm = *reinterpret_cast<MlaSmem*>(smem_raw);
-  const int hg = blockIdx.x, row_q = blockIdx.y, split = blockIdx.z;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  MlaSmem<kSets>& sm = *reinterpret_cast<MlaSmem<kSets>*>(smem_raw);
+  const int row_q = blockIdx.y, split = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int set = kSets > 1 ? tid >> 7 : 0;      // which group of four warps
+  const int warp = (tid >> 5) & 3;               // warp inside its group
+  const int hg = blockIdx.x * kSets + set;
   const int kv_len = p.kv_lens[row_q];
   const int seq = p.row_seq ? p.row_seq[row_q] : row_q;
   const int* table = p.block_table + static_cast<long long>(seq) * p.table_stride;
   const int n_tiles = (kv_len + kMlaTile - 1) / kMlaTile;
   const int per = (n_tiles + p.splits - 1) / p.splits;
   const int t0 = split * per, t1 = min(n_tiles, t0 + per);
-  const int heads_here = min(16, p.heads - hg * 16);
+  const int heads_here = max(0, min(16, p.heads - hg * 16));
   const int pages_per_tile = kMlaTile >> p.page_shift;
 
   const uint32_t kv_s[2] = {smem_u32(sm.kv[0]), smem_u32(sm.kv[1])};
-  const uint32_t q_s = smem_u32(sm.q), p_s = smem_u32(sm.pmat);
+  const uint32_t q_s = smem_u32(sm.q[set]), p_s = smem_u32(sm.pmat[set]);
+  uint8_t* pmat = sm.pmat[set];
+  float (*red_max)[16] = sm.red_max[set];
+  float (*red_sum)[16] = sm.red_sum[set];
 
-  // Q rows of this head group (zero rows for heads past the end)
-  for (int i = tid; i < 16 * (kRow / 8); i += kMlaThreads) {
-    const int h = i / (kRow / 8), chunk = i - h * (kRow / 8);
-    const bool valid = h < heads_here;
-    const __nv_bfloat16* src = p.q + (static_cast<long long>(row_q) * p.heads + hg * 16 + (valid ? h : 0)) * kRow + chunk * 8;
-    cp_async_16(q_s + h * kPitch + chunk * 16, src, valid);
+  // Q rows of the CTA's head groups (zero rows for heads past the end)
+  for (int i = tid; i < kSets * 16 * (kRow / 8); i += kMlaThreads * kSets) {
+    const int hh = i / (kRow / 8), chunk = i - hh * (kRow / 8);
+    const int head = blockIdx.x * kSets * 16 + hh;
+    const bool valid = head < p.heads;
+    const __nv_bfloat16* src = p.q + (static_cast<long long>(row_q) * p.heads + (valid ? head : 0)) * kRow + chunk * 8;
+    cp_async_16(smem_u32(sm.q[0]) + hh * kPitch + chunk * 16, src, valid);
   }
   auto stage_pages = [&](int tile, int buf) {
     if (tid < pages_per_tile) {
@@ -191,22 +209,34 @@ __global__ void __launch_bounds__(kMlaThreads) mla_attn_kernel(const MlaAttnPara
     }
     __syncthreads();
     // ---- scores of this warp's 16 tokens
-    float s[2][4];
+    // two accumulator sets over alternate k steps: four independent chains of 18 tensor-core
+    // instructions instead of two of 36 (the chain latency is what a warp waits on here)
+    float s[2][4], s_odd[2][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
-#pragma unroll 4
-    for (int kk = 0; kk < kRow / 16; ++kk) {
-      uint32_t a[4];
-      ldmatrix_x4(q_s + (lane & 15) * kPitch + (kk * 2 + (lane >> 4)) * 16, a[0], a[1], a[2], a[3]);
+      for (int j = 0; j < 4; ++j) s[i][j] = s_odd[i][j] = 0.f;
+    {
       const int mi = lane >> 3;
-      const int token = warp * 16 + (lane & 7) + 8 * (mi >> 1);
-      uint32_t b0, b1, b2, b3;
-      ldmatrix_x4(kv_s[buf] + token * kPitch + (kk * 2 + (mi & 1)) * 16, b0, b1, b2, b3);
-      mma_bf16_16816(s[0], a, b0, b1);
-      mma_bf16_16816(s[1], a, b2, b3);
+      const uint32_t q_lane = q_s + (lane & 15) * kPitch + (lane >> 4) * 16;
+      const uint32_t k_lane = kv_s[buf] + (warp * 16 + (lane & 7) + 8 * (mi >> 1)) * kPitch + (mi & 1) * 16;
+#pragma unroll 6
+      for (int kk = 0; kk < kRow / 16; kk += 2) {
+        uint32_t a[4], a2[4], b0, b1, b2, b3, c0, c1, c2, c3;
+        ldmatrix_x4(q_lane + kk * 32, a[0], a[1], a[2], a[3]);
+        ldmatrix_x4(k_lane + kk * 32, b0, b1, b2, b3);
+        ldmatrix_x4(q_lane + kk * 32 + 32, a2[0], a2[1], a2[2], a2[3]);
+        ldmatrix_x4(k_lane + kk * 32 + 32, c0, c1, c2, c3);
+        mma_bf16_16816(s[0], a, b0, b1);
+        mma_bf16_16816(s[1], a, b2, b3);
+        mma_bf16_16816(s_odd[0], a2, c0, c1);
+        mma_bf16_16816(s_odd[1], a2, c2, c3);
+      }
     }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] += s_odd[i][j];
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
@@ -222,13 +252,13 @@ __global__ void __launch_bounds__(kMlaThreads) mla_attn_kernel(const MlaAttnPara
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     }
-    if (tq == 0) { sm.red_max[warp][r0] = mx[0]; sm.red_max[warp][r0 + 8] = mx[1]; }
+    if (tq == 0) { red_max[warp][r0] = mx[0]; red_max[warp][r0 + 8] = mx[1]; }
     __syncthreads();
     float alpha[2], msafe[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int rr = r0 + 8 * r;
-      const float tm = fmaxf(fmaxf(sm.red_max[0][rr], sm.red_max[1][rr]), fmaxf(sm.red_max[2][rr], sm.red_max[3][rr]));
+      const float tm = fmaxf(fmaxf(red_max[0][rr], red_max[1][rr]), fmaxf(red_max[2][rr], red_max[3][rr]));
       const float mnew = fmaxf(m_run[r], tm);
       msafe[r] = mnew == -INFINITY ? 0.f : mnew;
       alpha[r] = m_run[r] == -INFINITY ? 0.f : exp2f(m_run[r] - msafe[r]);
@@ -244,15 +274,15 @@ __global__ void __launch_bounds__(kMlaThreads) mla_attn_kernel(const MlaAttnPara
         rs[j >> 1] += e[j];
       }
       const int col = warp * 16 + nt * 8 + tq * 2;
-      *reinterpret_cast<uint32_t*>(sm.pmat + r0 * kPPitch + col * 2) = pack_bf16x2(e[0], e[1]);
-      *reinterpret_cast<uint32_t*>(sm.pmat + (r0 + 8) * kPPitch + col * 2) = pack_bf16x2(e[2], e[3]);
+      *reinterpret_cast<uint32_t*>(pmat + r0 * kPPitch + col * 2) = pack_bf16x2(e[0], e[1]);
+      *reinterpret_cast<uint32_t*>(pmat + (r0 + 8) * kPPitch + col * 2) = pack_bf16x2(e[2], e[3]);
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
       rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
     }
-    if (tq == 0) { sm.red_sum[warp][r0] = rs[0]; sm.red_sum[warp][r0 + 8] = rs[1]; }
+    if (tq == 0) { red_sum[warp][r0] = rs[0]; red_sum[warp][r0 + 8] = rs[1]; }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
@@ -262,7 +292,7 @@ __global__ void __launch_bounds__(kMlaThreads) mla_attn_kernel(const MlaAttnPara
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int rr = r0 + 8 * r;
-      l_run[r] = l_run[r] * alpha[r] + sm.red_sum[0][rr] + sm.red_sum[1][rr] + sm.red_sum[2][rr] + sm.red_sum[3][rr];
+      l_run[r] = l_run[r] * alpha[r] + red_sum[0][rr] + red_sum[1][rr] + red_sum[2][rr] + red_sum[3][rr];
     }
     // ---- O[:, warp * 128 ...] += P V
 #pragma unroll
@@ -347,12 +377,16 @@ B200_API int b200_mla_prep(const void* kv, const void* kv_norm_w, const void* q,
                   static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(q_abs),
                   static_cast<__nv_bfloat16*>(cache), positions, slot_mapping, inv_freq, tokens, heads, q_stride,
                   q_rope_off, eps, rope_mscale};
-  mla_prep_kernel<<<tokens, 128, 0, stream>>>(p);
+  mla_prep_kernel<<<dim3(tokens, heads > 16 ? (heads + 15) / 16 : 1), 128, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -300;
 }
 
+// Head groups of 16 that one CTA serves: two once a row has more than one group.
+static int mla_sets(int heads) { return heads > 16 ? 2 : 1; }
+
 B200_API int b200_mla_pick_splits(int rows, int heads, int max_kv_len) {
-  const int ctas = rows * ((heads + 15) / 16);
+  const int per_cta = 16 * mla_sets(heads);
+  const int ctas = rows * ((heads + per_cta - 1) / per_cta);
   const int tiles = (max_kv_len + kMlaTile - 1) / kMlaTile;
   int s = (2 * 148 + ctas - 1) / ctas;
   if (s > tiles) s = tiles;
@@ -387,13 +421,17 @@ B200_API int b200_mla_attn(const void* q, const void* cache, void* out, const in
   p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   static PerDeviceOnce configured;
-  const int smem = static_cast<int>(sizeof(MlaSmem));
+  const int smem1 = static_cast<int>(sizeof(MlaSmem<1>)), smem2 = static_cast<int>(sizeof(MlaSmem<2>));
   if (configured.first_time()) {
-    if (cudaFuncSetAttribute(mla_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(mla_attn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1) != cudaSuccess ||
+        cudaFuncSetAttribute(mla_attn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess)
       return -4;
   }
-  const dim3 grid((heads + 15) / 16, rows, splits);
-  mla_attn_kernel<<<grid, kMlaThreads, smem, stream>>>(p);
+  if (mla_sets(heads) == 2) {
+    mla_attn_kernel<2><<<dim3((heads + 31) / 32, rows, splits), kMlaThreads * 2, smem2, stream>>>(p);
+  } else {
+    mla_attn_kernel<1><<<dim3((heads + 15) / 16, rows, splits), kMlaThreads, smem1, stream>>>(p);
+  }
   if (splits > 1) mla_combine_kernel<<<rows * heads, 128, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -300;
 }

@@ -38,9 +38,26 @@ class MlaWeights:
     w_uk: LinearWeight                   # stacked [heads_local * 512, nope]: W_uk[h]^T
     w_uv: LinearWeight                   # stacked [heads_local * v_dim, 512]
     o: LinearWeight                      # [H, heads_local * v_dim]
+    # optional: q_b with W_uk folded in, [heads_local * 576, q_lora or H]; per head 512 rows
+    # W_uk[h]^T W_qb_nope[h] followed by the 64 rotary rows of q_b. Small batches then get the absorbed
+    # query from ONE weight-streaming GEMM instead of q_b plus a per-head projection with K = 128.
+    q_fold: Optional[LinearWeight] = None
 
     def all(self):
-        return [w for w in (self.q_a, self.q_b, self.kv_a, self.w_uk, self.w_uv, self.o) if w is not None]
+        return [w for w in (self.q_a, self.q_b, self.kv_a, self.w_uk, self.w_uv, self.o, self.q_fold) if w is not None]
+
+
+FOLD_MAX_TOKENS = 256      # above this the extra rows of the folded projection cost more than they save
+
+
+def fold_q(q_b: torch.Tensor, w_uk: torch.Tensor, heads: int, nope: int, rope: int) -> torch.Tensor:
+    """``q_b`` [heads * (nope + rope), K] and the stacked ``w_uk`` [heads * 512, nope] -> the folded
+    projection [heads * 576, K] (fp32 product, returned in q_b's dtype)."""
+    k = q_b.shape[1]
+    qb = q_b.float().reshape(heads, nope + rope, k)
+    uk = w_uk.float().reshape(heads, -1, nope)
+    top = torch.bmm(uk, qb[:, :nope])                              # [heads, 512, K]
+    return torch.cat([top, qb[:, nope:]], dim=1).reshape(heads * (uk.shape[1] + rope), k).to(q_b.dtype)
 
 
 def split_kv_b(kv_b: torch.Tensor, heads: int, nope: int, v_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -92,18 +109,23 @@ class MlaAttention:
     def __call__(self, h: torch.Tensor, batch, li: int, model) -> torch.Tensor:
         cfg, m, w = self.cfg, self.m, self.w
         t = h.shape[0]
+        qin = h
         if w.q_a is not None:
             qa = ops.linear(h, w.q_a)
-            qa, _, _ = ops.norm(qa, w.q_a_norm, eps=cfg.rms_eps)
-            q = ops.linear(qa, w.q_b)
-        else:
-            q = ops.linear(h, w.q_b)
+            qin, _, _ = ops.norm(qa, w.q_a_norm, eps=cfg.rms_eps)
         kv = ops.linear(h, w.kv_a)
         cache = model.kv_cache[li] if model.kv_cache is not None else None      # [pages, page, 576]
-        q_abs = torch.empty(t, self.heads, ROW, dtype=h.dtype, device=h.device)
-        ops.mla_prep(kv, w.kv_a_norm, q, q_abs, cache, batch.positions, batch.slot_mapping, model.inv_freq,
-                     self.heads, self.dq, m.qk_nope_head_dim, eps=cfg.rms_eps)
-        ops.colbatched_linear(q, w.w_uk.weight, self.heads, self.dq, q_abs.view(t, self.heads * ROW), ROW)
+        if w.q_fold is not None and t <= FOLD_MAX_TOKENS:
+            # absorbed queries straight from the folded projection; the rotary part is rotated in place
+            q_abs = ops.linear(qin, w.q_fold).view(t, self.heads, ROW)
+            ops.mla_prep(kv, w.kv_a_norm, q_abs.view(t, self.heads * ROW), q_abs, cache, batch.positions,
+                         batch.slot_mapping, model.inv_freq, self.heads, ROW, LATENT, eps=cfg.rms_eps)
+        else:
+            q = ops.linear(qin, w.q_b)
+            q_abs = torch.empty(t, self.heads, ROW, dtype=h.dtype, device=h.device)
+            ops.mla_prep(kv, w.kv_a_norm, q, q_abs, cache, batch.positions, batch.slot_mapping, model.inv_freq,
+                         self.heads, self.dq, m.qk_nope_head_dim, eps=cfg.rms_eps)
+            ops.colbatched_linear(q, w.w_uk.weight, self.heads, self.dq, q_abs.view(t, self.heads * ROW), ROW)
         row_seq, row_len = self.row_lengths(batch, t, h.device)
         lat = ops.mla_attn(q_abs, cache, batch.block_table, row_len, self.scale(model), row_seq=row_seq,
                            max_kv_len=batch.max_kv_len or None)

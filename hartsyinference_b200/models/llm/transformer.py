@@ -25,7 +25,7 @@ from typing import Callable, Optional
 
 import torch
 
-from ... import ops
+from ... import config, ops
 from ...ops import LinearWeight
 from ...parallel.comm import Comm, SingleComm
 from .config import RopeScaling, TransformerConfig
@@ -317,35 +317,42 @@ class DecoderModel:
 
     def _load_mla(self, need, get, p: str):
         """Hugging Face DeepSeek attention tensors -> absorbed, head-sharded MLA weights."""
-        from .mla import MlaAttention, MlaWeights, split_kv_b
+        from .mla import MlaAttention, MlaWeights, fold_q, split_kv_b
         cfg, m, dt = self.cfg, self.cfg.mla, torch.bfloat16
         r, hl = self.tp_rank, self.hq
         dq = m.qk_nope_head_dim + m.qk_rope_head_dim
         dev = lambda t_: t_.to(dt).to(self.device)
+        fold = self.device.type == "cuda" and bool(config.get("mla_fold_q"))
+        q_name = p + ("q_b_proj.weight" if m.q_lora_rank else "q_proj.weight")
         if m.q_lora_rank:
             q_a = self._lw(need(p + "q_a_proj.weight").to(dt))
             q_a_norm = dev(need(p + "q_a_layernorm.weight"))
-            q_b = self._lw(need(p + "q_b_proj.weight")[r * hl * dq:(r + 1) * hl * dq].to(dt))
         else:
             q_a, q_a_norm = None, None
-            q_b = self._lw(need(p + "q_proj.weight")[r * hl * dq:(r + 1) * hl * dq].to(dt))
+        q_b_dense = need(q_name)[r * hl * dq:(r + 1) * hl * dq].to(dt)
+        q_b = self._lw(q_b_dense)
         per = m.qk_nope_head_dim + m.v_head_dim
         kv_b = need(p + "kv_b_proj.weight")[r * hl * per:(r + 1) * hl * per].to(dt)
         w_uk, w_uv = split_kv_b(kv_b, hl, m.qk_nope_head_dim, m.v_head_dim)
+
+        def folded(qb, uk, heads):
+            return self._lw(fold_q(qb.to(self.device), uk.to(self.device), heads, m.qk_nope_head_dim, m.qk_rope_head_dim)) if fold else None
+
         w = MlaWeights(
             q_a=q_a, q_a_norm=q_a_norm, q_b=q_b,
             kv_a=self._lw(need(p + "kv_a_proj_with_mqa.weight").to(dt), allow_fp8=False),
             kv_a_norm=dev(need(p + "kv_a_layernorm.weight")),
             w_uk=self._lw(w_uk, allow_fp8=False), w_uv=self._lw(w_uv, allow_fp8=False),
             o=self._lw(need(p + "o_proj.weight")[:, r * hl * m.v_head_dim:(r + 1) * hl * m.v_head_dim]
-                       .contiguous().to(dt)))
+                       .contiguous().to(dt)),
+            q_fold=folded(q_b_dense, w_uk, hl))
         if self.dp_attention:
             heads = cfg.num_heads
             uk, uv = split_kv_b(need(p + "kv_b_proj.weight").to(dt), heads, m.qk_nope_head_dim, m.v_head_dim)
-            full = MlaWeights(q_a=w.q_a, q_a_norm=w.q_a_norm,
-                              q_b=self._lw(need(p + ("q_b_proj.weight" if m.q_lora_rank else "q_proj.weight")).to(dt)),
+            full = MlaWeights(q_a=w.q_a, q_a_norm=w.q_a_norm, q_b=self._lw(need(q_name).to(dt)),
                               kv_a=w.kv_a, kv_a_norm=w.kv_a_norm, w_uk=self._lw(uk, allow_fp8=False),
-                              w_uv=self._lw(uv, allow_fp8=False), o=self._lw(need(p + "o_proj.weight").to(dt)))
+                              w_uv=self._lw(uv, allow_fp8=False), o=self._lw(need(p + "o_proj.weight").to(dt)),
+                              q_fold=folded(need(q_name).to(dt), uk, heads))
             self._attn_dp_pending = MlaAttention(cfg, full, heads)
             self._attn_dp_pending.reduce_output = False
         return MlaAttention(cfg, w, hl)
@@ -495,6 +502,10 @@ class DecoderModel:
             w_uk=lin(hl * m.kv_lora_rank, m.qk_nope_head_dim, allow_fp8=False),
             w_uv=lin(hl * m.v_head_dim, m.kv_lora_rank, allow_fp8=False),
             o=lin(cfg.hidden_size, hl * m.v_head_dim))
+        if self.device.type == "cuda" and config.get("mla_fold_q"):
+            # synthetic weights: the folded projection is drawn by itself (prefill chunks above 256 rows use
+            # q_b + W_uk, a different random function of the input; timing is what such a model is for)
+            w.q_fold = lin(hl * (m.kv_lora_rank + m.qk_rope_head_dim), m.q_lora_rank if m.q_lora_rank else cfg.hidden_size)
         return MlaAttention(cfg, w, hl)
 
     def _random_mla_dp(self, lin, ones):
@@ -520,6 +531,8 @@ class DecoderModel:
             w_uk=shared(heads * m.kv_lora_rank, m.qk_nope_head_dim, allow_fp8=False),
             w_uv=shared(heads * m.v_head_dim, m.kv_lora_rank, allow_fp8=False),
             o=shared(cfg.hidden_size, heads * m.v_head_dim))
+        if self.device.type == "cuda" and config.get("mla_fold_q"):
+            full.q_fold = shared(heads * (m.kv_lora_rank + m.qk_rope_head_dim), q_in)
 
         def rows(w: LinearWeight, per: int) -> LinearWeight:
             a, b = r * hl * per, (r + 1) * hl * per
@@ -537,7 +550,8 @@ class DecoderModel:
 
         shard = MlaWeights(q_a=full.q_a, q_a_norm=full.q_a_norm, q_b=rows(full.q_b, dq), kv_a=full.kv_a,
                            kv_a_norm=full.kv_a_norm, w_uk=rows(full.w_uk, m.kv_lora_rank),
-                           w_uv=rows(full.w_uv, m.v_head_dim), o=cols(full.o, m.v_head_dim))
+                           w_uv=rows(full.w_uv, m.v_head_dim), o=cols(full.o, m.v_head_dim),
+                           q_fold=None if full.q_fold is None else rows(full.q_fold, m.kv_lora_rank + m.qk_rope_head_dim))
         self._attn_dp_pending = MlaAttention(cfg, full, heads)
         self._attn_dp_pending.reduce_output = False
         return MlaAttention(cfg, shard, hl)

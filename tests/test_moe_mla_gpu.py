@@ -262,3 +262,52 @@ def test_dynamic_dispatch_and_grouped_gemm(t, e_local, cap):
         for j in range(0, sc.numel(), max(1, sc.numel() // 50)):     # a sample of the assigned slots
             ref = xr[sc[j]] @ wr[e_of[j] * n:(e_of[j] + 1) * n].t()
             assert _rel(y[sc[j]].cpu(), ref) < 0.015, (fp8, j)
+
+
+def test_folded_query_projection_matches_q_b_plus_absorb():
+    """The second query projection with W_uk folded in (used for up to 256 rows) against q_b followed by
+    the per-head absorb, on the same checkpoint tensors, bf16 and fp8."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks"))
+    import llm_parity
+    from hartsyinference_b200 import config
+    from hartsyinference_b200.models.llm import config as C
+    from hartsyinference_b200.models.llm.mla import fold_q
+    from hartsyinference_b200.models.llm.transformer import DecoderModel, ForwardBatch
+    # the fold itself against its definition
+    heads, nope, rope, k = 3, 128, 64, 96
+    qb = torch.randn(heads * (nope + rope), k, device=DEV)
+    uk = torch.randn(heads * 512, nope, device=DEV)
+    x = torch.randn(5, k, device=DEV)
+    f = (x @ fold_q(qb, uk, heads, nope, rope).t()).reshape(5, heads, 576)
+    q = (x @ qb.t()).reshape(5, heads, nope + rope)
+    want = torch.cat([torch.einsum("thn,hln->thl", q[..., :nope], uk.reshape(heads, 512, nope)), q[..., nope:]], dim=-1)
+    assert _rel(f, want) < 1e-4
+    mla = C.MlaConfig(q_lora_rank=128, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128)
+    cfg = C.tiny("deepseek-v3", vocab_size=512, hidden_size=256, num_heads=16, num_kv_heads=16, head_dim=192, mla=mla,
+                 num_layers=2, ffn_size=256, moe=None)
+    get = llm_parity._weights(cfg, torch.device(DEV))
+    t = 40
+    toks = torch.randint(0, cfg.vocab_size, (t,), device=DEV).to(torch.int32)
+
+    def logits(fold, fp8):
+        config.set_override("mla_fold_q", fold)
+        try:
+            m = DecoderModel(cfg, DEV, fp8=fp8)
+            m.load_state_dict(get)
+        finally:
+            config.set_override("mla_fold_q", None)
+        assert (m.layers[0].attn_module.w.q_fold is not None) == fold
+        m.alloc_kv(4, 16)
+        b = ForwardBatch(tokens=toks, positions=torch.arange(t, dtype=torch.int32, device=DEV),
+                         slot_mapping=torch.arange(t, dtype=torch.int64, device=DEV),
+                         block_table=torch.arange(4, dtype=torch.int32, device=DEV)[None],
+                         kv_lens=torch.tensor([t], dtype=torch.int32, device=DEV), is_decode=False,
+                         cu_q=torch.tensor([0, t], dtype=torch.int32, device=DEV), max_q_len=t, max_kv_len=t)
+        return m.full_logits(m.forward_hidden(b)).float()
+
+    for fp8 in (False, True):
+        a, b_ = logits(True, fp8), logits(False, fp8)
+        cos = torch.nn.functional.cosine_similarity(a, b_, dim=-1)
+        assert float(cos.min()) > (0.99 if fp8 else 0.999), (fp8, cos.min())
