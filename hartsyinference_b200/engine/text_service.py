@@ -126,6 +126,10 @@ class TextService:
                                     large_tokens=int(config.get("prefill_chunk")))
                 except Exception as e:
                     log.warn(f"[Collective] fused TP kernels unavailable ({type(e).__name__}: {e}); using NCCL")
+            if comm is not None and comm.world > 1 and getattr(llm.model, "dp_attention", False):
+                # latent-attention MoE models: decode steps deal the requests over the ranks for attention
+                from ..parallel.dp_attention import enable_dp_attention
+                enable_dp_attention(llm.model, comm, max_rows=self.options.max_batch)
             eng = LLMEngine(llm.model, page_size=self.options.kv_page_size, max_batch=self.options.max_batch,
                             max_model_len=min(self.options.max_model_len, llm.config.max_position),
                             kv_pool_bytes=self.options.kv_pool_bytes_budget or None)
@@ -145,6 +149,11 @@ class TextService:
             from ..parallel.fused import disable_fused_tp
             log.warn(f"[Collective] device wait timeout {vals}; row-parallel linears fall back to NCCL")
             disable_fused_tp(model, comm)
+            ex = getattr(model, "dp_exchange", None)
+            if ex is not None and ex.fused:
+                from ..parallel.dp_attention import enable_dp_attention
+                ex.close()
+                enable_dp_attention(model, comm, max_rows=ex.max_rows, fused=False)
 
     # ------------------------------------------------------------------------------ SPMD ticks
     def _tick(self, key: str, adds: list, cancels: list, step: bool):

@@ -126,9 +126,16 @@ def _load_synthetic(spec: str, device, comm: Optional[Comm], fp8: Optional[bool]
             cfg = replace(cfg, num_layers=int(v))
         else:
             raise UnsupportedModelError(f"synthetic:{spec}: unknown modifier {k!r}")
-    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
+    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device), dp_attention=_want_dp_attention(cfg, comm))
     model.random_init(seed=0)
     return LoadedLLM(model, ByteTokenizer(vocab_size=cfg.vocab_size), ChatTemplate.for_arch(cfg.arch), cfg, f"synthetic:{spec}")
+
+
+def _want_dp_attention(cfg, comm) -> bool:
+    """Latent-attention models on more than one rank also keep the attention weights of all heads, for
+    the data-parallel attention layout of decode steps (parallel/dp_attention.py)."""
+    from ... import config
+    return cfg.mla is not None and comm is not None and comm.world > 1 and bool(config.get("dp_attention"))
 
 
 def _want_fp8(fp8: Optional[bool], device) -> bool:
@@ -366,7 +373,7 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
         text.setdefault("model_type", "llama")
         cfg = from_hf_config(text)
         lm_get, tower_get = _llava_names(ck)
-        model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
+        model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device), dp_attention=_want_dp_attention(cfg, comm))
         model.load_state_dict(lm_get)
         if raw.get("model_type") in ("qwen2_5_vl", "qwen2_vl", "qwen3_vl"):
             from ..vlm.qwen_vl import Qwen3VisionConfig, QwenVisionConfig, QwenVlModel
@@ -390,7 +397,7 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
                              get=tower_get, feature_layer=int(raw.get("vision_feature_layer", -2)))
     else:
         cfg = from_hf_config(raw)
-        model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device))
+        model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device), dp_attention=_want_dp_attention(cfg, comm))
         model.load_state_dict(standard_names(ck_get, raw))
     tok: Tokenizer
     if (p / "tokenizer.json").exists():
@@ -454,7 +461,8 @@ def _load_gguf(p: Path, device, comm, fp8) -> LoadedLLM:
 
     from ... import config as _config
     resident = bool(_config.get("gguf_resident")) and (comm is None or comm.world == 1)
-    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device) and not resident)
+    model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device) and not resident,
+                         dp_attention=_want_dp_attention(cfg, comm))
     model.load_state_dict(get)
     if resident:
         kept = _keep_gguf_blocks(model, f, hf_to_gguf)
