@@ -207,6 +207,33 @@ class _Detector:
                                                antialias=True)[0].clamp(0, 1)
 
 
+class _ClosedSetDetector:
+    """RT-DETR: fixed label set from the checkpoint's ``id2label``; ``texts`` (optional) keep only the
+    named labels."""
+
+    def __init__(self, path: str, raw: dict, device):
+        from ..models.vision.rtdetr import RtDetr, rtdetr_from_hf
+        self.cfg = rtdetr_from_hf(raw)
+        self.model = RtDetr(self.cfg, device, get=ShardedCheckpoint(path).get)
+
+    def detect(self, images: list, texts: list, threshold: float, iou: float) -> list:
+        size = self.cfg.image_size
+        keep = {t.strip().lower() for t in (texts or [])}
+        out = []
+        for im in images:
+            h, w = _image_hw(im)
+            x = _Detector._squeeze(im, size)[None]                 # the whole picture squeezed to the input size, values in [0, 1]
+            found = []
+            for label, score, (cx, cy, bw, bh) in self.model.detect(x, threshold)[0]:
+                name = self.cfg.id2label.get(label, str(label))
+                if keep and name.lower() not in keep:
+                    continue
+                found.append({"label": name, "score": float(score),
+                              "box": [(cx - bw / 2) * w, (cy - bh / 2) * h, (cx + bw / 2) * w, (cy + bh / 2) * h]})
+            out.append(found)
+        return out
+
+
 def _image_hw(image) -> tuple[int, int]:
     if isinstance(image, (str, bytes)) or hasattr(image, "__fspath__"):
         from PIL import Image
@@ -242,6 +269,8 @@ class VisionService:
                     self._loaded[path] = _Segmenter(path, raw, self.device)
                 elif mt in ("owlvit", "owlv2"):
                     self._loaded[path] = _Detector(path, raw, self.device)
+                elif mt == "rt_detr":
+                    self._loaded[path] = _ClosedSetDetector(path, raw, self.device)
                 elif mt in ("siglip", "siglip_vision_model", "dinov2"):
                     self._loaded[path] = _VitEmbedder(path, raw, self.device)
                 else:
@@ -254,13 +283,16 @@ class VisionService:
         m = self._model(spec)
         out = VisionResult()
         if req.operation == "detect":
+            if isinstance(m, _ClosedSetDetector):
+                out.detections = m.detect(req.images, req.texts, req.score_threshold, req.nms_iou)
+                return out
             if not isinstance(m, _Detector):
-                raise ValueError("this checkpoint is not an open-vocabulary detector")
+                raise ValueError("this checkpoint is not a detector")
             if not req.texts:
                 raise ValueError("detect needs at least one text query")
             out.detections = m.detect(req.images, req.texts, req.score_threshold, req.nms_iou)
             return out
-        if isinstance(m, _Detector):
+        if isinstance(m, (_Detector, _ClosedSetDetector)):
             raise ValueError("this checkpoint detects; use operation 'detect'")
         if req.operation == "segment":
             if not isinstance(m, _Segmenter):

@@ -38,6 +38,7 @@ from .core import (  # noqa: F401
     linear,
     mla_attn,
     mla_prep,
+    msda,
     norm,
     quant_fp8_act,
     quant_int8_act,

@@ -1,6 +1,7 @@
 """Python entry points of the fused ops (see the package docstring for the dispatch rule)."""
 from __future__ import annotations
 
+import ctypes as C
 import math
 from dataclasses import dataclass
 from typing import Optional
@@ -957,6 +958,31 @@ def colbatched_linear(x: torch.Tensor, w: torch.Tensor, groups: int, x_koff: int
                                           x_koff, out.stride(0), out_stride, ws.data_ptr(), ws.numel(),
                                           st.status.data_ptr(), N.stream())
         N.check(rc, "b200_gemm_colbatched")
+    return out
+
+
+def msda(value: torch.Tensor, shapes: list, offsets: torch.Tensor, logits: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
+    """Multi-scale deformable attention between its linear layers: softmax over the sampling points,
+    sampling locations from the reference boxes / points, bilinear gathers and the weighted sum, one
+    kernel on the device (csrc/kernels/msda.cu); see :func:`reference.msda` for the shapes. Returns
+    [B, Q, heads * D] in the dtype of ``value``."""
+    if not value.is_cuda:
+        return R.msda(value, shapes, offsets, logits, ref).to(value.dtype)
+    b, rows, heads, d = value.shape
+    _, q, _, lv, pts, _ = offsets.shape
+    assert value.dtype in (torch.bfloat16, torch.float32) and sum(h * w for h, w in shapes) == rows and len(shapes) == lv
+    value = value.contiguous()
+    offsets, logits, ref = offsets.float().contiguous(), logits.float().contiguous(), ref.float().contiguous()
+    sh = torch.tensor([[h, w] for h, w in shapes], dtype=torch.int32)
+    st = torch.cumsum(torch.tensor([0] + [h * w for h, w in shapes[:-1]], dtype=torch.int32), 0).to(torch.int32)
+    meta = torch.cat([sh.reshape(-1), st]).to(value.device)
+    out = torch.empty(b, q, heads * d, dtype=value.dtype, device=value.device)
+    fn = N.bind("b200_msda", C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p,
+                                       C.c_void_p, C.c_void_p] + [C.c_int] * 7 + [C.c_void_p])
+    rc = fn(value.data_ptr(), int(value.dtype == torch.bfloat16), offsets.data_ptr(), logits.data_ptr(), ref.data_ptr(),
+            ref.shape[-1], int(ref.dim() == 4), meta.data_ptr(), meta.data_ptr() + 8 * lv, out.data_ptr(), b, rows, q, heads, d, lv,
+            pts, N.stream())
+    N.check(rc, "b200_msda")
     return out
 
 

@@ -295,3 +295,46 @@ def sampling_keep_mask(logits: torch.Tensor, temperature: float, top_k: int, top
     if min_p > 0.0:
         keep &= w >= min(min_p, 1.0)
     return keep
+
+
+def msda(value: torch.Tensor, shapes: list, offsets: torch.Tensor, logits: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
+    """Multi-scale deformable attention between its linear layers, fp32.
+
+    value [B, S, heads, D] (levels concatenated along S in the order of ``shapes`` = [(h, w), ...]),
+    offsets [B, Q, heads, L, P, 2], logits [B, Q, heads, L, P], ref [B, Q, 4] (cx, cy, w, h), [B, Q, 2]
+    or per level [B, Q, L, 2 | 4]. Softmax over the L * P points, locations as in Deformable DETR
+    (4-d: centre + offset / P * size / 2; 2-d: point + offset / (w, h) of the level), bilinear
+    samples with zero padding and pixel centres at half-integers. Returns [B, Q, heads * D]."""
+    b, s_, heads, d = value.shape
+    _, q, _, lv, pts, _ = offsets.shape
+    v = value.float()
+    w = torch.softmax(logits.float().reshape(b, q, heads, lv * pts), -1).reshape(b, q, heads, lv, pts)
+    r = ref.float()
+    if r.dim() == 3:
+        r = r[:, :, None, :].expand(b, q, lv, r.shape[-1])
+    out = torch.zeros(b, q, heads, d)
+    out = out.to(v.device)
+    start = 0
+    for li, (h, wd) in enumerate(shapes):
+        vl = v[:, start:start + h * wd].reshape(b, h, wd, heads, d)
+        start += h * wd
+        off = offsets[:, :, :, li].float()                               # [B, Q, heads, P, 2]
+        rl = r[:, :, li]                                                 # [B, Q, 2 | 4]
+        if rl.shape[-1] == 4:
+            loc = rl[:, :, None, None, :2] + off / pts * rl[:, :, None, None, 2:] * 0.5
+        else:
+            loc = rl[:, :, None, None, :] + off / torch.tensor([wd, h], dtype=torch.float32, device=v.device)
+        x = loc[..., 0] * wd - 0.5
+        y = loc[..., 1] * h - 0.5
+        x0, y0 = torch.floor(x), torch.floor(y)
+        ax, ay = x - x0, y - y0
+        bi = torch.arange(b, device=v.device)[:, None, None, None]
+        hi = torch.arange(heads, device=v.device)[None, None, :, None]
+        for dy in (0, 1):
+            for dx in (0, 1):
+                xx, yy = (x0 + dx).long(), (y0 + dy).long()
+                ok = (xx >= 0) & (xx < wd) & (yy >= 0) & (yy < h)
+                cw = (ax if dx else 1 - ax) * (ay if dy else 1 - ay) * w[:, :, :, li] * ok
+                g = vl[bi, yy.clamp(0, h - 1), xx.clamp(0, wd - 1), hi]  # [B, Q, heads, P, D]
+                out += (cw[..., None] * g).sum(3)
+    return out.reshape(b, q, heads * d)
