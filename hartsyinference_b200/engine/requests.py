@@ -143,6 +143,8 @@ class ImageRequest:
     loras: list[tuple[str, float]] = field(default_factory=list)
     step_cache_threshold: float = 0.0
     guidance_interval: Optional[tuple] = None   # (start, end) in [0, 1]: true CFG only on those steps (None: all)
+    cfg_renorm_min: Optional[float] = None      # true CFG: rescale the guided prediction by clamp(|cond| / |guided|, this, 1)
+    cfg_row_norm: bool = False                  # true CFG: rescale every guided row to the norm of its conditional row
     preview_every: int = 0               # > 0: every n-th step callback carries a small RGB preview of the latents
     vae_tile: int = 0                    # > 0: decode in latent tiles of this size (bounded activation memory)
 

@@ -47,8 +47,15 @@ class FlowMatchEulerScheduler:
         return float(self.sigmas[i + 1] - self.sigmas[i])
 
     def step(self, latents: torch.Tensor, cond: torch.Tensor, i: int, uncond: Optional[torch.Tensor] = None,
-             guidance: float = 1.0) -> torch.Tensor:
-        """In-place CFG combine + Euler step on fp32 latents (one fused kernel)."""
+             guidance: float = 1.0, renorm_min: Optional[float] = None, row_norm: bool = False) -> torch.Tensor:
+        """In-place CFG combine + Euler step on fp32 latents (one fused kernel). With true guidance,
+        ``renorm_min`` rescales the guided prediction by clamp(||cond|| / ||guided||, renorm_min, 1) over the
+        whole tensor and ``row_norm`` rescales every row of the last dimension to the norm of its
+        conditional row (the two guidance normalisations of the reference's CfgHelper)."""
+        if uncond is not None and row_norm:
+            return ops.cfg_rownorm_euler_step(latents, cond.contiguous(), uncond.contiguous(), guidance, self.dt(i))
+        if uncond is not None and renorm_min is not None:
+            return ops.cfg_renorm_euler_step(latents, cond.contiguous(), uncond.contiguous(), guidance, self.dt(i), renorm_min)
         return ops.cfg_euler_step(latents, cond, uncond, guidance, self.dt(i))
 
     def add_noise(self, x0: torch.Tensor, noise: torch.Tensor, i: int) -> torch.Tensor:
@@ -108,23 +115,29 @@ class FlowUniPCScheduler:
         m0 = self.model_outputs[-1]
         i = self.step_index
         h_phi_1, B_h, rks, R, b, alpha_t, ratio = self._coeffs(order, i, i + 1, 0)
-        x = ratio * sample - alpha_t * h_phi_1 * m0
+        # x = ratio sample - alpha h_phi_1 m0 - alpha B_h / 2 (m1 - m0) / r, gathered per tensor so that the
+        # update is one pass over the latents (ops.lincomb: one kernel on the device)
+        c0 = -alpha_t * h_phi_1
+        terms = [(ratio, sample)]
         if order >= 2:
-            d1 = (self.model_outputs[-2] - m0) / rks[0]
-            x = x - alpha_t * B_h * 0.5 * d1
-        return x
+            k = -alpha_t * B_h * 0.5 / rks[0]
+            terms += [(c0 - k, m0), (k, self.model_outputs[-2])]
+        else:
+            terms += [(c0, m0)]
+        return _combine(terms)
 
     def _correct(self, this_x0: torch.Tensor, last_sample: torch.Tensor, order: int) -> torch.Tensor:
         m0 = self.model_outputs[-1]
         i = self.step_index
         h_phi_1, B_h, rks, R, b, alpha_t, ratio = self._coeffs(order, i - 1, i, 0)
-        x = ratio * last_sample - alpha_t * h_phi_1 * m0
-        d1_t = this_x0 - m0
+        c0 = -alpha_t * h_phi_1
         if order == 1:
-            return x - alpha_t * B_h * 0.5 * d1_t
+            k_t = -alpha_t * B_h * 0.5
+            return _combine([(ratio, last_sample), (c0 - k_t, m0), (k_t, this_x0)])
         rhos = torch.linalg.solve(torch.tensor(R, dtype=torch.float64), torch.tensor(b, dtype=torch.float64)).tolist()
-        d1 = (self.model_outputs[-2] - m0) / rks[0]
-        return x - alpha_t * B_h * (rhos[0] * d1 + rhos[-1] * d1_t)
+        k1 = -alpha_t * B_h * rhos[0] / rks[0]          # weight of (m1 - m0)
+        k_t = -alpha_t * B_h * rhos[-1]                 # weight of (this_x0 - m0)
+        return _combine([(ratio, last_sample), (c0 - k1 - k_t, m0), (k1, self.model_outputs[-2]), (k_t, this_x0)])
 
     def step(self, velocity: torch.Tensor, sample: torch.Tensor) -> torch.Tensor:
         """velocity: model output at the current step (fp32 or bf16), sample fp32 -> next sample."""
@@ -142,6 +155,18 @@ class FlowUniPCScheduler:
             self.lower_order_nums += 1
         self.step_index += 1
         return nxt
+
+
+def _combine(terms: list) -> torch.Tensor:
+    """sum of coef * tensor; fp32 device tensors go through the one-pass kernel."""
+    from ... import ops
+    xs = [t for _, t in terms]
+    if xs[0].is_cuda and all(t.dtype == torch.float32 and t.is_contiguous() for t in xs):
+        return ops.lincomb(terms)
+    acc = terms[0][0] * terms[0][1]
+    for c, t in terms[1:]:
+        acc = acc + c * t
+    return acc
 
 
 class EulerDiscreteScheduler:

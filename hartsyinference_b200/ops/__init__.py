@@ -38,6 +38,9 @@ from .core import (  # noqa: F401
     linear,
     mla_attn,
     mla_prep,
+    cfg_renorm_euler_step,
+    cfg_rownorm_euler_step,
+    lincomb,
     msda,
     norm,
     quant_fp8_act,

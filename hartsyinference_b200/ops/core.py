@@ -690,6 +690,66 @@ def cfg_euler_step(z: torch.Tensor, cond: torch.Tensor, uncond: Optional[torch.T
     return z
 
 
+_RENORM_SCRATCH: dict = {}
+
+
+def cfg_renorm_euler_step(z: torch.Tensor, cond: torch.Tensor, uncond: torch.Tensor, guidance: float, dt: float,
+                          renorm_min: float = 0.0) -> torch.Tensor:
+    """In place on fp32 latents: guided = uncond + g (cond - uncond), rescaled by ONE factor
+    clamp(||cond|| / ||guided||, renorm_min, 1) for the whole tensor, then z += guided dt. cond / uncond
+    bf16 or fp32. Two launches on the device (norms + scale, then the update)."""
+    if not z.is_cuda:
+        z.copy_(R.cfg_renorm_euler(z, cond, uncond, guidance, dt, renorm_min))
+        return z
+    assert z.dtype == torch.float32 and z.is_contiguous() and cond.dtype == uncond.dtype and cond.dtype in (torch.bfloat16, torch.float32)
+    assert cond.is_contiguous() and uncond.is_contiguous() and cond.numel() == z.numel() == uncond.numel()
+    key = (z.device.index, N.stream())
+    scratch = _RENORM_SCRATCH.get(key)
+    if scratch is None:
+        nbytes = int(N.bind("b200_cfg_renorm_scratch_bytes", C.c_longlong, [])())
+        scratch = torch.zeros((nbytes + 7) // 8, dtype=torch.int64, device=z.device)
+        _RENORM_SCRATCH[key] = scratch
+    fn = N.bind("b200_cfg_renorm_euler", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_float,
+                                                   C.c_float, C.c_void_p, C.c_void_p])
+    N.check(fn(z.data_ptr(), cond.data_ptr(), uncond.data_ptr(), int(cond.dtype == torch.bfloat16), z.numel(), guidance, dt,
+               renorm_min, scratch.data_ptr(), N.stream()), "b200_cfg_renorm_euler")
+    return z
+
+
+def cfg_rownorm_euler_step(z: torch.Tensor, cond: torch.Tensor, uncond: torch.Tensor, guidance: float, dt: float,
+                           eps: float = 1e-12) -> torch.Tensor:
+    """In place on fp32 latents [..., D]: guided rows rescaled to the norm of the conditional rows
+    (ratio per row of the last dimension), then z += guided dt. One launch on the device."""
+    if not z.is_cuda:
+        z.copy_(R.cfg_rownorm_euler(z, cond, uncond, guidance, dt, eps))
+        return z
+    assert z.dtype == torch.float32 and z.is_contiguous() and cond.dtype == uncond.dtype and cond.dtype in (torch.bfloat16, torch.float32)
+    assert cond.is_contiguous() and uncond.is_contiguous() and cond.shape == z.shape == uncond.shape
+    d = z.shape[-1]
+    fn = N.bind("b200_cfg_rownorm_euler", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_float,
+                                                    C.c_float, C.c_float, C.c_void_p])
+    N.check(fn(z.data_ptr(), cond.data_ptr(), uncond.data_ptr(), int(cond.dtype == torch.bfloat16), z.numel() // d, d, guidance, dt,
+               eps, N.stream()), "b200_cfg_rownorm_euler")
+    return z
+
+
+def lincomb(terms: list, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sum_i coef_i * x_i for ``terms`` = [(coef, fp32 tensor), ...] (at most eight, same shape): the update
+    of a multistep solver in one pass over the latents. ``out`` may be one of the operands."""
+    xs = [t for _, t in terms]
+    if out is None:
+        out = torch.empty_like(xs[0])
+    if not xs[0].is_cuda or len(xs) > 8 or any(t.dtype != torch.float32 or not t.is_contiguous() or t.data_ptr() % 16 for t in xs + [out]):
+        acc = sum(float(c) * t.float() for c, t in terms)
+        out.copy_(acc.to(out.dtype))
+        return out
+    ptrs = (C.c_void_p * 8)(*[t.data_ptr() for t in xs])
+    coefs = (C.c_float * 8)(*[float(c) for c, _ in terms])
+    fn = N.bind("b200_lincomb", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p])
+    N.check(fn(out.data_ptr(), ptrs, coefs, len(xs), out.numel(), N.stream()), "b200_lincomb")
+    return out
+
+
 def gated_residual(x: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, rows_per_batch: int = 0) -> torch.Tensor:
     """x + gate[batch] * y for [rows, dim] bf16 with gate [batch, >= dim]."""
     rows, dim = x.shape

@@ -338,3 +338,23 @@ def msda(value: torch.Tensor, shapes: list, offsets: torch.Tensor, logits: torch
                 g = vl[bi, yy.clamp(0, h - 1), xx.clamp(0, wd - 1), hi]  # [B, Q, heads, P, D]
                 out += (cw[..., None] * g).sum(3)
     return out.reshape(b, q, heads * d)
+
+
+def cfg_renorm_euler(z: torch.Tensor, cond: torch.Tensor, uncond: torch.Tensor, guidance: float, dt: float,
+                     renorm_min: float = 0.0) -> torch.Tensor:
+    """z + s * guided * dt with guided = uncond + g (cond - uncond) and one scale for the whole tensor,
+    s = clamp(||cond|| / (||guided|| + 1e-8), renorm_min, 1) (norms in double precision)."""
+    c, u = cond.double(), uncond.double()
+    guided = (uncond.float() + guidance * (cond.float() - uncond.float()))
+    ratio = float(c.pow(2).sum().sqrt() / (guided.double().pow(2).sum().sqrt() + 1e-8))
+    ratio = renorm_min if ratio < renorm_min else 1.0 if ratio > 1.0 else ratio
+    return z.float() + guided * (ratio * dt)
+
+
+def cfg_rownorm_euler(z: torch.Tensor, cond: torch.Tensor, uncond: torch.Tensor, guidance: float, dt: float,
+                      eps: float = 1e-12) -> torch.Tensor:
+    """The same with one ratio per row of the last dimension and no clamp; a zero denominator gives 0."""
+    guided = uncond.float() + guidance * (cond.float() - uncond.float())
+    den = guided.double().pow(2).sum(-1, keepdim=True).sqrt() + eps
+    ratio = torch.where(den > 0, cond.double().pow(2).sum(-1, keepdim=True).sqrt() / den, torch.zeros_like(den)).float()
+    return z.float() + guided * ratio * dt

@@ -98,7 +98,8 @@ class FluxPipeline:
                 latents: Optional[torch.Tensor] = None, init_latents: Optional[torch.Tensor] = None, strength: float = 1.0,
                 mask: Optional[torch.Tensor] = None, control_latents: Optional[torch.Tensor] = None,
                 control_strength: float = 1.0, channel_cond: Optional[torch.Tensor] = None,
-                guidance_interval: Optional[tuple] = None) -> torch.Tensor:
+                guidance_interval: Optional[tuple] = None, cfg_renorm_min: Optional[float] = None,
+                cfg_row_norm: bool = False) -> torch.Tensor:
         """Returns the final latents [1, C, H/8, W/8] fp32 on the device.
 
         ``guidance_interval`` (start, end) limits true classifier-free guidance to the steps inside it
@@ -203,7 +204,7 @@ class FluxPipeline:
                     if true_cfg:
                         v_cond, v_unc = cache_v, None
             if v_cond is not None:
-                sched.step(x, v_cond.contiguous(), i, v_unc, cfg_scale)
+                sched.step(x, v_cond.contiguous(), i, v_unc, cfg_scale, renorm_min=cfg_renorm_min, row_norm=cfg_row_norm)
             if mask_packed is not None:
                 # outside the mask the latent follows the original image at the next step's noise level
                 s_next = sched.sigma(i + 1) if i + 1 < steps else 0.0
@@ -322,7 +323,8 @@ class FluxPipeline:
         z = self.denoise(ctx, pooled, req.height, req.width, req.steps, req.guidance, seed, neg, req.cfg_scale, on_step,
                          req.step_cache_threshold, init_latents=init_latents, strength=req.strength, mask=mask,
                          control_latents=control_latents, control_strength=getattr(req, "control_strength", 1.0),
-                         channel_cond=channel_cond, guidance_interval=getattr(req, "guidance_interval", None))
+                         channel_cond=channel_cond, guidance_interval=getattr(req, "guidance_interval", None),
+                         cfg_renorm_min=getattr(req, "cfg_renorm_min", None), cfg_row_norm=bool(getattr(req, "cfg_row_norm", False)))
         t_denoise = time.perf_counter() - t0
         if self.c.vae is None:
             img = torch.zeros(1, 3, req.height, req.width)
