@@ -242,6 +242,33 @@ def mesh3d(model, image, out, resolution, threshold, device):
 
 @cli.command()
 @click.argument("model")
+@click.argument("image")
+@click.option("--actions", default=None, help="JSON file: a list of action rows (25 floats each); default: --frames rows of zeros")
+@click.option("--frames", default=8, help="frames to generate when no action file is given")
+@click.option("--out", default="world_frames", help="directory for frame_NNNN.png")
+@click.option("--seed", default=0)
+@click.option("--device", default="auto")
+def world(model, image, actions, frames, out, seed, device):
+    """Play an action-conditioned world model (Oasis checkpoints) from a first picture."""
+    import json
+    import os
+    import torch
+    from ..engine.inference_engine import InferenceEngine
+    from ..engine.requests import WorldRequest
+    from ..utils.png import encode_png
+    rows = json.load(open(actions)) if actions else [[0.0] * 25 for _ in range(frames)]
+    eng = InferenceEngine(device)
+    res = eng.world.run(ModelSpec(model, Modality.WORLD, local_path=model), WorldRequest(image=image, actions=rows, seed=seed))
+    os.makedirs(out, exist_ok=True)
+    for i, f in enumerate(res.frames):
+        rgb = (f.clamp(0, 1) * 255).round().to(torch.uint8).permute(1, 2, 0).contiguous()
+        with open(os.path.join(out, f"frame_{i:04d}.png"), "wb") as fh:
+            fh.write(encode_png(rgb.numpy().tobytes(), rgb.shape[1], rgb.shape[0]))
+    click.echo(f"{out}: {len(res.frames)} frames, {res.meta['seconds_per_frame']:.3f} s per generated frame")
+
+
+@cli.command()
+@click.argument("model")
 @click.argument("text")
 @click.option("--out", default="speech.wav")
 @click.option("--speed", default=None, type=float)

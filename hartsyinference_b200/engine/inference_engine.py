@@ -57,7 +57,7 @@ def parse_backend_selector(selector: str) -> tuple[str, list[int]]:
 
 
 class InferenceEngine:
-    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH, Modality.RESTORE, Modality.MUSIC, Modality.MESH}
+    SUPPORTED = {Modality.TEXT, Modality.IMAGE, Modality.VIDEO, Modality.EMBEDDINGS, Modality.TRANSCRIBE, Modality.VISION, Modality.SPEECH, Modality.RESTORE, Modality.MUSIC, Modality.MESH, Modality.WORLD}
 
     def __init__(self, backend_selector: str = "auto", options: Optional[EngineOptions] = None, ranks="auto"):
         self.options = options or EngineOptions()
@@ -187,7 +187,10 @@ class InferenceEngine:
         from .mesh_service import MeshService
         return self._service("mesh", lambda: MeshService(self.device))
 
-    world = property(lambda self: self._unsupported("world"))
+    @property
+    def world(self):
+        from .world_service import WorldService
+        return self._service("world", lambda: WorldService(self.device))
 
     # ------------------------------------------------------------------------------ memory
     @property

@@ -222,6 +222,22 @@ class MeshResult:
 
 
 @dataclass
+class WorldRequest:
+    """First picture + one action row per frame to generate. ``image``: path, PIL image, uint8 HWC array
+    or float CHW tensor; ``actions``: rows of 25 floats (Oasis: 23 keys / buttons, then the two camera
+    deltas)."""
+    image: Optional[Any] = None
+    actions: list = field(default_factory=list)
+    seed: Optional[int] = None
+
+
+@dataclass
+class WorldResult:
+    frames: Any = None                   # float32 [N, 3, H, W] in [0, 1], the first picture's reconstruction included
+    meta: dict = field(default_factory=dict)
+
+
+@dataclass
 class VisionRequest:
     """``operation``: "embed" (CLIP / SigLIP / DINOv2 image features, CLIP text features and their
     similarity when both are given), "depth" (Depth Anything; one map per image) or "segment" (CLIPSeg:

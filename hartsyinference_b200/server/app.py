@@ -482,6 +482,46 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
         return {"format": fmt, "vertices": len(res.vertices), "faces": len(res.faces), "meta": res.meta,
                 "mesh_base64": base64.b64encode(data).decode()}
 
+    def _frame_png(frame) -> str:
+        """[3, H, W] float in [0, 1] -> base64 PNG."""
+        rgb = (frame.clamp(0, 1) * 255).round().to(torch.uint8).permute(1, 2, 0).contiguous()
+        return base64.b64encode(_png(rgb.numpy().tobytes(), rgb.shape[1], rgb.shape[0])).decode()
+
+    def _b64_image(raw: str):
+        import io
+        from PIL import Image
+        b64 = raw.split(",", 1)[1] if raw.startswith("data:") else raw
+        return Image.open(io.BytesIO(base64.b64decode(b64)))
+
+    @app.post("/v1/native/world")
+    async def native_world(request: Request):
+        """Interactive world model. ``{"model", "image"}`` opens a session and returns its id with the
+        first frame; ``{"session", "action": [25 floats]}`` advances it by one frame; ``{"session",
+        "close": true}`` ends it; ``{"model", "image", "actions": [[...], ...]}`` plays a whole plan."""
+        from ..engine.requests import WorldRequest
+        body = await request.json()
+        world = eng.world
+        try:
+            if body.get("session") and body.get("close"):
+                return {"closed": world.close(body["session"])}
+            if body.get("session"):
+                with heavy_queue.slot():
+                    frame = world.step(body["session"], body.get("action") or [0.0] * 25)
+                return {"session": body["session"], "frame_png_base64": _frame_png(frame), "stats": world.stats(body["session"])}
+            if not body.get("image"):
+                return JSONResponse({"error": {"message": "no image", "type": "bad_request"}}, status_code=400)
+            spec = resolve(body.get("model"), Modality.WORLD)
+            img = _b64_image(body["image"])
+            if body.get("actions") is not None:
+                with heavy_queue.slot():
+                    res = eng.with_vram_cleanup(lambda: world.run(spec, WorldRequest(image=img, actions=body["actions"], seed=body.get("seed"))))
+                return {"frames": len(res.frames), "meta": res.meta, "frames_png_base64": [_frame_png(f) for f in res.frames]}
+            with heavy_queue.slot():
+                sid, first = world.open(spec, img, int(body.get("seed") or 0))
+            return {"session": sid, "frame_png_base64": _frame_png(first)}
+        except KeyError as e:
+            return JSONResponse({"error": {"message": str(e), "type": "not_found"}}, status_code=404)
+
     @app.post("/v1/native/vision")
     async def native_vision(request: Request):
         import base64

@@ -30,9 +30,9 @@ def test_backend_selectors():
     with pytest.raises(UnsupportedBackendError):
         parse_backend_selector("cuda:0+cuda:0")
     e = InferenceEngine("cpu")
-    assert e.is_supported(Modality.TEXT) and e.is_supported(Modality.MESH) and not e.is_supported(Modality.WORLD)
+    assert e.is_supported(Modality.TEXT) and e.is_supported(Modality.MESH) and e.is_supported(Modality.WORLD)
     with pytest.raises(UnsupportedModelError):
-        _ = e.world
+        _ = e.fx
 
 
 def test_text_generate_stream_and_concurrency(ckpt):
