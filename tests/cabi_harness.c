@@ -23,7 +23,7 @@ int main(int argc, char** argv) {
     fprintf(stderr, "create: %s\n", b200_last_error());
     return 1;
   }
-  if (!b200_engine_is_supported(e, "text") || !b200_engine_is_supported(e, "mesh") || b200_engine_is_supported(e, "world")) return 3;
+  if (!b200_engine_is_supported(e, "text") || !b200_engine_is_supported(e, "mesh") || !b200_engine_is_supported(e, "world") || b200_engine_is_supported(e, "fx")) return 3;
   char spec[1024];
   snprintf(spec, sizeof spec, "{\"Requested\": \"%s\", \"Modality\": \"text\", \"LocalPath\": \"%s\"}", argv[1], argv[1]);
   char* result = NULL;
