@@ -33,6 +33,7 @@ def main() -> None:
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--int8", type=int, default=1)
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--pull", type=int, default=0, help="1: also time the form that reads K / V from their owners (bf16)")
     args = ap.parse_args()
 
     from hartsyinference_b200 import ops
@@ -91,11 +92,18 @@ def main() -> None:
         err[name] = float((got - want).norm() / want.norm())
     t_fused = timed(run_fused)
     t_nccl = timed(run_nccl)
+    t_pull = None
+    if args.pull and not int8:
+        puller = FusedUlyssesAttention(comm, s_l, heads, dev, pull=True)
+        err["pull"] = float((puller(q, k, v)[:256].float() - want).norm() / want.norm())
+        t_pull = timed(lambda: puller(q, k, v))
+        comm.barrier()
+        puller.close()
     flops = 4.0 * args.tokens * args.tokens * heads * 128 / world        # per rank, either form
     if rank == 0:
         print(json.dumps({"case": "sp_attention", "n_gpus": world, "tokens": args.tokens, "heads": heads,
                           "form": "head split" if split else "K / V to every rank", "int8_qk": int8,
-                          "fused_ms": t_fused, "nccl_ms": t_nccl, "fused_tflops_per_gpu": flops / t_fused / 1e9,
+                          "fused_ms": t_fused, "nccl_ms": t_nccl, "pull_ms": t_pull, "fused_tflops_per_gpu": flops / t_fused / 1e9,
                           "rel_err_vs_fp32": err, "transport": fused.heap.transport}))
     comm.barrier()
     fused.close()

@@ -77,6 +77,8 @@ struct FaParams {
   int n_tiles, tiles_per_seg, nseg, seg_len, seg_first, seg_pad;
   int seg_mode;
   int q_seg_base;            // segment index of query row 0 (context-parallel form: the queries are this rank's only)
+  int pull;                  // 1: segment s of K / V^T stays in rank s's memory and is read from there, tile by tile,
+                             // through the tensor maps of FaPeerMaps (rows / columns counted inside the segment)
   const uint32_t* seg_flags;
   uint32_t seg_target;
   long long wait_budget;
@@ -84,6 +86,14 @@ struct FaParams {
   long long out_col0;
   uint32_t* done_flags[8];   // rank s's "outputs have arrived" counter
   uint32_t* done_ctr;        // CTAs of this launch that have finished
+};
+
+// K and V^T tensor maps per source rank for the pull form (ring-style context parallelism without
+// copies: the TMA unit loads each key / value tile straight from the owner's memory over NVLink; plain
+// tiled loads, no cluster multicast).
+struct FaPeerMaps {
+  CUtensorMap k[8];
+  CUtensorMap vt[8];
 };
 
 // Buffer tile (index into the segmented key buffers) and number of real keys of walk step j.
@@ -98,7 +108,8 @@ __device__ __forceinline__ void fa_key_tile(const FaParams& p, int j, int& buf_t
 template <bool kI8>
 __global__ void __launch_bounds__(kFaThreads, 1)
 attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
-               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_vt) {
+               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_vt,
+               const __grid_constant__ FaPeerMaps peers) {
   constexpr int kQkTileBytes = kI8 ? 128 * 128 : 128 * 128 * 2;   // one Q or K tile
   constexpr int kQkAtoms = kI8 ? 1 : 2;                           // 128-byte-wide swizzle atoms per tile
   constexpr int kVTileBytes = 128 * 128 * 2;
@@ -189,14 +200,18 @@ attn_fa_kernel(const FaParams p, const __grid_constant__ CUtensorMap tm_q,
         fa_key_tile(p, j, bt, valid, seg);
         if (p.seg_mode && j % p.tiles_per_seg == 0 && !wait_segment(seg)) { ok = false; break; }
         if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+        // pull form: the tile is read from its owner's buffers (tile index inside the segment)
+        const CUtensorMap* mk = p.pull ? &peers.k[seg] : &tm_k;
+        const CUtensorMap* mv = p.pull ? &peers.vt[seg] : &tm_vt;
+        const int tile_at = p.pull ? bt - seg * p.tiles_per_seg : bt;
         mbar_arrive_expect_tx(&bars->k_full[s], kQkTileBytes);
         for (int a = 0; a < kQkAtoms; ++a)
-          tma_load_2d(sk + s * kQkTileBytes + a * (kQkTileBytes / kQkAtoms), &tm_k, &bars->k_full[s],
-                      col0 + a * 64, k_row0 + bt * kFaTile);
+          tma_load_2d(sk + s * kQkTileBytes + a * (kQkTileBytes / kQkAtoms), mk, &bars->k_full[s],
+                      col0 + a * 64, k_row0 + tile_at * kFaTile);
         if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&bars->v_full[s], kVTileBytes);
-        tma_load_2d(sv + s * kVTileBytes, &tm_vt, &bars->v_full[s], bt * kFaTile, vt_row0);
-        tma_load_2d(sv + s * kVTileBytes + kVTileBytes / 2, &tm_vt, &bars->v_full[s], bt * kFaTile + 64, vt_row0);
+        tma_load_2d(sv + s * kVTileBytes, mv, &bars->v_full[s], tile_at * kFaTile, vt_row0);
+        tma_load_2d(sv + s * kVTileBytes + kVTileBytes / 2, mv, &bars->v_full[s], tile_at * kFaTile + 64, vt_row0);
       }
       if (!ok) report_status(p.status, kWaitTimeout, kKernelAttnPrefill, 21, blockIdx.x);
     }
@@ -630,13 +645,14 @@ __global__ void __launch_bounds__(256) uly_push_kernel(const UlyPush p) {
   // Ulysses: the head belongs to one destination rank. Context parallel: every rank gets K / V of every
   // head (p.hl == p.heads), the queries stay local (row = token, no segment offset).
   const int dst = p.cp ? p.rank : head / p.hl, hi = p.cp ? head : head - dst * p.hl;
-  const int first_dst = p.cp ? 0 : dst, last_dst = p.cp ? p.world - 1 : dst;
+  const bool pull = p.cp == 2;          // K / V^T stay in this rank's own region (peers read them from here)
+  const int first_dst = pull ? p.rank : p.cp ? 0 : dst, last_dst = pull ? p.rank : p.cp ? p.world - 1 : dst;
   const int row = threadIdx.x >> 1, d0 = (threadIdx.x & 1) * 64;
   const int tok = tile * kFaTile + row;
   const bool valid = tok < p.s_l;
   const long long ld_in = static_cast<long long>(p.heads) * kFaD;
   const long long ld_out = static_cast<long long>(p.hl) * kFaD;
-  const long long seg_row = static_cast<long long>(p.rank) * p.s_pad + tok;     // row in the destination K / V buffers
+  const long long seg_row = (pull ? 0 : static_cast<long long>(p.rank) * p.s_pad) + tok;     // row in the destination K / V buffers
   const long long q_row = p.cp ? tok : seg_row;
   const long long q_rows = p.cp ? p.s_pad : static_cast<long long>(p.world) * p.s_pad;
   const int tiles = p.s_pad / kFaTile;
@@ -763,8 +779,9 @@ __global__ void __launch_bounds__(256) uly_push_kernel(const UlyPush p) {
     __syncthreads();
     // thread (dim, half) writes 64 consecutive tokens of one dim
     const int dim = threadIdx.x >> 1, t0 = (threadIdx.x & 1) * 64;
-    const long long off = (static_cast<long long>(hi) * kFaD + dim) * p.world * p.s_pad +
-                          static_cast<long long>(p.rank) * p.s_pad + tile * kFaTile + t0;
+    const long long off = pull ? (static_cast<long long>(hi) * kFaD + dim) * p.s_pad + tile * kFaTile + t0
+                               : (static_cast<long long>(hi) * kFaD + dim) * p.world * p.s_pad +
+                                     static_cast<long long>(p.rank) * p.s_pad + tile * kFaTile + t0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       uint4 o;
@@ -807,7 +824,7 @@ using namespace b200;
 
 static inline int fa_pad(int s, int to) { return (s + to - 1) / to * to; }
 static int fa_launch(const FaParams& p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, dim3 grid,
-                     int int8, cudaStream_t stream);
+                     int int8, cudaStream_t stream, const FaPeerMaps* peers = nullptr);
 
 // Scratch layout of one call: V^T [batch * heads * 128][sk_pad64] bf16, then (int8 mode) Q8
 // [batch * sq][heads * 128], K8 [batch * sk][heads * 128], q scales [batch * heads][sq_pad128],
@@ -896,7 +913,9 @@ B200_API int b200_attn_fa(const void* q, const void* k, const void* v, void* out
 }
 
 static int fa_launch(const FaParams& p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, dim3 grid,
-                     int int8, cudaStream_t stream) {
+                     int int8, cudaStream_t stream, const FaPeerMaps* peers) {
+  static const FaPeerMaps no_peers{};
+  const FaPeerMaps& pm = peers ? *peers : no_peers;
   const int qk_tile = int8 ? 128 * 128 : 128 * 128 * 2;
   const int stages = int8 ? 3 : 2;
   const int smem = 2 * qk_tile + stages * (qk_tile + 128 * 128 * 2) + static_cast<int>(sizeof(FaBarriers)) + 1024;
@@ -905,12 +924,12 @@ static int fa_launch(const FaParams& p, const CUtensorMap& tq, const CUtensorMap
     if (configured[1].first_time() &&
         cudaFuncSetAttribute(attn_fa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return -4;
-    attn_fa_kernel<true><<<grid, kFaThreads, smem, stream>>>(p, tq, tk, tv);
+    attn_fa_kernel<true><<<grid, kFaThreads, smem, stream>>>(p, tq, tk, tv, pm);
   } else {
     if (configured[0].first_time() &&
         cudaFuncSetAttribute(attn_fa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return -4;
-    attn_fa_kernel<false><<<grid, kFaThreads, smem, stream>>>(p, tq, tk, tv);
+    attn_fa_kernel<false><<<grid, kFaThreads, smem, stream>>>(p, tq, tk, tv, pm);
   }
   const cudaError_t err = cudaGetLastError();
   return err == cudaSuccess ? 0 : -(1000 + static_cast<int>(err));   // the CUDA error number stays readable
@@ -925,7 +944,7 @@ static UlyLayout uly_layout(int s_l, int heads, int world, int int8, int cp = 0)
   UlyLayout l{};
   auto up = [](long long v) { return (v + 1023) / 1024 * 1024; };
   const int s_pad = fa_pad(s_l, 128), hl = cp ? heads : heads / world;
-  const long long rows = static_cast<long long>(world) * s_pad;
+  const long long rows = cp == 2 ? s_pad : static_cast<long long>(world) * s_pad;     // K / V^T rows held per rank
   const long long q_rows = cp ? s_pad : rows;
   long long off = 0;
   l.flags = off; off = up(off + kUlyFlagWords * 4);
@@ -954,6 +973,12 @@ B200_API long long b200_context_parallel_region_bytes(int s_l, int heads, int wo
 B200_API long long b200_context_parallel_out_offset(int s_l, int heads, int world, int int8) {
   return uly_layout(s_l, heads, world, int8, 1).out;
 }
+// Pull form (bf16 only): a rank's region holds its own K / V^T segment only; peers read it in place.
+B200_API long long b200_ring_region_bytes(int s_l, int heads, int world) {
+  if (world <= 0 || world > 8) return -1;
+  return uly_layout(s_l, heads, world, 0, 2).total;
+}
+B200_API long long b200_ring_out_offset(int s_l, int heads, int world) { return uly_layout(s_l, heads, world, 0, 2).out; }
 // Offset of the output [s_l][heads * 128] bf16 inside the region (the caller reads it after
 // b200_ulysses_wait_outputs).
 B200_API long long b200_ulysses_out_offset(int s_l, int heads, int world, int int8) {
@@ -975,11 +1000,13 @@ B200_API long long b200_ulysses_out_offset(int s_l, int heads, int world, int in
 B200_API int b200_ulysses_attention(const void* q, const void* k, const void* v, void* const* regions, int s_l, int heads,
                                     int rank, int world, float scale, int int8, unsigned epoch, int phases,
                                     long long wait_budget_cycles, void* status, cudaStream_t stream) {
-  const int cp = (phases & 16) ? 1 : 0;
+  const int cp = (phases & 32) ? 2 : (phases & 16) ? 1 : 0;
   if (world <= 0 || world > 8 || (!cp && heads % world != 0) || s_l <= 0) return -2;
+  if (cp == 2 && int8) return -6;      // the pull form reads bf16 operands (no per-tile scale tables on the peers)
   const UlyLayout l = uly_layout(s_l, heads, world, int8, cp);
   const int s_pad = fa_pad(s_l, 128), hl = cp ? heads : heads / world, tiles = s_pad / 128;
-  const long long rows = static_cast<long long>(world) * s_pad;
+  const long long rows = static_cast<long long>(world) * s_pad;        // keys of the whole sequence
+  const long long kv_rows = cp == 2 ? s_pad : rows;                    // rows of one rank's K / V^T buffers
   const long long q_rows = cp ? s_pad : rows;
   uint8_t* mine = static_cast<uint8_t*>(regions[rank]);
   const long long budget = wait_budget_cycles > 0 ? wait_budget_cycles : kWaitBudgetCycles;
@@ -1036,6 +1063,7 @@ B200_API int b200_ulysses_attention(const void* q, const void* k, const void* v,
   p.k_scale = reinterpret_cast<const float*>(mine + l.kscale);
   p.sq_pad = static_cast<int>(q_rows);
   p.q_seg_base = cp ? rank : 0;
+  p.pull = cp == 2 ? 1 : 0;
   p.n_tiles = world * tiles;
   p.tiles_per_seg = tiles;
   p.nseg = world;
@@ -1057,12 +1085,23 @@ B200_API int b200_ulysses_attention(const void* q, const void* k, const void* v,
   const int eb = int8 ? 1 : 2;
   int rc = make_kmajor_map(&tq, mine + l.qbuf, eb, q_rows, static_cast<long long>(hl) * kFaD, static_cast<long long>(hl) * kFaD, 128);
   if (rc) return rc;
-  rc = make_kmajor_map(&tk, mine + l.kbuf, eb, rows, static_cast<long long>(hl) * kFaD, static_cast<long long>(hl) * kFaD, 128);
+  rc = make_kmajor_map(&tk, mine + l.kbuf, eb, kv_rows, static_cast<long long>(hl) * kFaD, static_cast<long long>(hl) * kFaD, 128);
   if (rc) return rc;
-  rc = make_kmajor_map(&tv, mine + l.vtbuf, 2, static_cast<long long>(hl) * kFaD, rows, rows, 128);
+  rc = make_kmajor_map(&tv, mine + l.vtbuf, 2, static_cast<long long>(hl) * kFaD, kv_rows, kv_rows, 128);
   if (rc) return rc;
+  FaPeerMaps pm{};
+  if (cp == 2 && (phases & 4)) {
+    for (int d = 0; d < world; ++d) {
+      uint8_t* r = static_cast<uint8_t*>(regions[d]);
+      rc = make_kmajor_map(&pm.k[d], r + l.kbuf, eb, kv_rows, static_cast<long long>(hl) * kFaD, static_cast<long long>(hl) * kFaD, 128);
+      if (rc) return rc;
+      rc = make_kmajor_map(&pm.vt[d], r + l.vtbuf, 2, static_cast<long long>(hl) * kFaD, kv_rows, kv_rows, 128);
+      if (rc) return rc;
+    }
+  }
   if (phases & 4) {
-    rc = fa_launch(p, tq, tk, tv, dim3(static_cast<unsigned>((q_rows + 2 * kFaTile - 1) / (2 * kFaTile)), hl, 1), int8, stream);
+    rc = fa_launch(p, tq, tk, tv, dim3(static_cast<unsigned>((q_rows + 2 * kFaTile - 1) / (2 * kFaTile)), hl, 1), int8, stream,
+                   cp == 2 ? &pm : nullptr);
     if (rc) return rc;
   }
   if (phases & 8)

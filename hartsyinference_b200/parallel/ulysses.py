@@ -19,6 +19,14 @@ context-parallel form (``context_parallel=True``): the queries and the output ro
 rank and the K / V operands of all heads are stored into every rank's buffers, which is the
 exchange the reference performs (its ranks publish K / V and read everyone else's).
 
+A third form, ``pull=True`` (bf16 only), keeps every rank's K / V segment in its own region and lets
+the attention kernel's TMA producer read each key / value tile from the owner's memory as it walks the
+segments: no copies of K / V at all and ``4 x tokens / world`` rows of buffers per rank, the memory
+profile of ring attention without its hop-by-hop latency (every peer is one NVSwitch hop away). The
+price: a tile crosses NVLink once per query-tile pair that needs it, so this form pays off only
+while a rank has few query tiles per head (short local sequences); with long local sequences the
+store-once forms above move far fewer bytes and are the default.
+
 There is no all-to-all collective and no NCCL call on this path; the NCCL all-to-all form
 (models/dit/wan.py) is the fallback and the measured baseline. The reference exchanges K and V
 between its device threads through a host rendezvous around every attention call
@@ -47,22 +55,29 @@ class FusedUlyssesAttention:
     """
 
     def __init__(self, comm: Comm, local_tokens: int, heads: int, device: Optional[torch.device] = None,
-                 int8: Optional[bool] = None, context_parallel: Optional[bool] = None):
+                 int8: Optional[bool] = None, context_parallel: Optional[bool] = None, pull: bool = False):
         self.comm = comm
         self.rank, self.world = comm.rank, comm.world
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.s_l, self.heads = int(local_tokens), int(heads)
         self.int8 = bool(config.get("sage_attention")) if int8 is None else bool(int8)
-        self.context_parallel = heads % self.world != 0 if context_parallel is None else bool(context_parallel)
+        self.pull = bool(pull)
+        if self.pull:
+            self.int8 = False                   # peers hold bf16 operands only
+        self.context_parallel = self.pull or (heads % self.world != 0 if context_parallel is None else bool(context_parallel))
         if self.world > 8 or (heads % self.world != 0 and not self.context_parallel):
             raise ValueError(f"{heads} heads cannot be split over {self.world} ranks")
         i32, i64, vp = C.c_int, C.c_longlong, C.c_void_p
-        form = "b200_context_parallel" if self.context_parallel else "b200_ulysses"
-        nbytes = int(N.bind(f"{form}_region_bytes", i64, [i32, i32, i32, i32])(self.s_l, heads, self.world, int(self.int8)))
+        if self.pull:
+            nbytes = int(N.bind("b200_ring_region_bytes", i64, [i32, i32, i32])(self.s_l, heads, self.world))
+            self._out_off = int(N.bind("b200_ring_out_offset", i64, [i32, i32, i32])(self.s_l, heads, self.world))
+        else:
+            form = "b200_context_parallel" if self.context_parallel else "b200_ulysses"
+            nbytes = int(N.bind(f"{form}_region_bytes", i64, [i32, i32, i32, i32])(self.s_l, heads, self.world, int(self.int8)))
+            self._out_off = int(N.bind(f"{form}_out_offset", i64, [i32, i32, i32, i32])(self.s_l, heads, self.world, int(self.int8)))
         if nbytes <= 0:
             raise ValueError("unsupported exchange shape")
-        self._out_off = int(N.bind(f"{form}_out_offset", i64, [i32, i32, i32, i32])(self.s_l, heads, self.world, int(self.int8)))
-        self._phases = 15 | (16 if self.context_parallel else 0)
+        self._phases = 15 | (32 if self.pull else 16 if self.context_parallel else 0)
         # plain peer stores and loads only: no multicast mapping is needed (or wanted) for this heap
         self.heap = SymmetricHeap(comm, nbytes + 4096, self.device, multicast=False)
         self.base = self.heap.alloc(nbytes, align=1024)
@@ -78,7 +93,7 @@ class FusedUlyssesAttention:
         self.budget_cycles = int(config.get("wait_budget_ms")) * 2_000_000
         self.nbytes = nbytes
         log.decision("SequenceParallel", f"attention exchange fused into the kernels: {self.world} ranks x {self.s_l} tokens, "
-                                         f"{heads} heads ({'K / V to every rank' if self.context_parallel else 'head split'}), "
+                                         f"{heads} heads ({'K / V read from their owners' if self.pull else 'K / V to every rank' if self.context_parallel else 'head split'}), "
                                          f"{'int8 Q K^T' if self.int8 else 'bf16'}, {nbytes / 2**20:.0f} MiB of "
                                          f"operand buffers per rank ({self.heap.transport})")
 

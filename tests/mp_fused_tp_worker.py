@@ -187,6 +187,16 @@ def main():
             want = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v.float()).reshape(world * s_l, -1)
             fu = FusedUlyssesAttention(comm, s_l, heads, dev, int8=int8)
             assert fu.context_parallel == (heads % world != 0)
+            if not int8 and heads % world != 0:
+                # the same case with K / V read from their owners by the attention kernel (over NVLink here)
+                fp = FusedUlyssesAttention(comm, s_l, heads, dev, pull=True)
+                mine_p = slice(rank * s_l, (rank + 1) * s_l)
+                for it in range(2):
+                    got_p = fp(q[mine_p].contiguous(), k[mine_p].contiguous(), v[mine_p].contiguous()).clone()
+                    N.check_status(dev)
+                    assert rel(got_p, want[mine_p]) < 0.02, ("pull", heads, s_l, it, rel(got_p, want[mine_p]))
+                comm.barrier()
+                fp.close()
             mine = slice(rank * s_l, (rank + 1) * s_l)
             for it in range(3):
                 got = fu(q[mine].contiguous(), k[mine].contiguous(), v[mine].contiguous()).clone()

@@ -123,6 +123,40 @@ def test_context_parallel_ranks_played_in_turn_match_fp32(world, s_l, heads, int
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("world,s_l,heads", [(2, 192, 3), (4, 100, 2), (3, 300, 1)])
+def test_pull_form_ranks_played_in_turn_match_fp32(world, s_l, heads):
+    """K / V^T stay in their owner's region; the attention kernel reads every segment's tiles through the
+    owner's tensor maps (phase bit 32). All "ranks" live on this GPU, so the reads are local."""
+    i32, i64 = C.c_int, C.c_longlong
+    size = N.bind("b200_ring_region_bytes", i64, [i32, i32, i32])
+    out_off = N.bind("b200_ring_out_offset", i64, [i32, i32, i32])
+    _, _, fn = _bind()
+    nbytes, off = int(size(s_l, heads, world)), int(out_off(s_l, heads, world))
+    assert nbytes < int(N.bind("b200_context_parallel_region_bytes", i64, [i32, i32, i32, i32])(s_l, heads, world, 0))
+    regions = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    table = (C.c_void_p * 8)()
+    for r in range(world):
+        table[r] = regions[r].data_ptr()
+    q, k, v = _inputs(world * s_l, heads, 9)
+    want = _oracle(q, k, v)
+    st = N.state(torch.device("cuda", torch.cuda.current_device()))
+    parts = [tuple(t[r * s_l:(r + 1) * s_l].contiguous() for t in (q, k, v)) for r in range(world)]
+    for epoch in (1, 2):
+        for phase in (2, 4, 8):
+            for r in range(world):
+                qr, kr, vr = parts[r]
+                rc = fn(qr.data_ptr(), kr.data_ptr(), vr.data_ptr(), table, s_l, heads, r, world, 128 ** -0.5, 0, epoch,
+                        phase | 32, 100_000_000, st.status.data_ptr(), N.stream())
+                assert rc == 0
+        N.check_status()
+        for r in range(world):
+            got = regions[r][off:off + s_l * heads * 128 * 2].view(torch.bfloat16).reshape(s_l, heads * 128)
+            assert _rel(got, want[r * s_l:(r + 1) * s_l]) < 0.02, (epoch, r)
+    assert fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), table, s_l, heads, 0, world, 0.1, 1, 3, 15 | 32, 0, st.status.data_ptr(),
+              N.stream()) == -6          # int8 operands are not offered in this form
+
+
+@pytest.mark.gpu
 def test_missing_peer_runs_out_and_reports():
     """Rank 0 of two runs alone: its waits for rank 1's segment and for rank 1's output share give
     up after about a millisecond each, the kernels return, and the status word says which wait."""
