@@ -373,9 +373,20 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
         text.setdefault("model_type", "llama")
         cfg = from_hf_config(text)
         lm_get, tower_get = _llava_names(ck)
+        if raw.get("model_type") in ("idefics3", "smolvlm"):
+            # decoder tensors sit under model.text_model.*
+            lm_get = lambda name: ck.get("model.text_model." + name[len("model."):]) if name.startswith("model.") else ck.get(name)
         model = DecoderModel(cfg, device, comm=comm, fp8=_want_fp8(fp8, device), dp_attention=_want_dp_attention(cfg, comm))
         model.load_state_dict(lm_get)
-        if raw.get("model_type") in ("qwen2_5_vl", "qwen2_vl", "qwen3_vl"):
+        if raw.get("model_type") in ("idefics3", "smolvlm"):
+            from ..vlm.idefics3 import Idefics3Model, idefics3_vision_from_hf
+            edge = None
+            pp = p / "preprocessor_config.json"
+            if pp.exists():
+                edge = (json.loads(pp.read_text()).get("size") or {}).get("longest_edge")
+            vlm = Idefics3Model(model, idefics3_vision_from_hf(raw["vision_config"]), int(raw.get("image_token_id", 128257)),
+                                int(raw.get("scale_factor", 2)), get=ck.get, longest_edge=edge)
+        elif raw.get("model_type") in ("qwen2_5_vl", "qwen2_vl", "qwen3_vl"):
             from ..vlm.qwen_vl import Qwen3VisionConfig, QwenVisionConfig, QwenVlModel
             vcfg = (Qwen3VisionConfig if raw["model_type"] == "qwen3_vl" else QwenVisionConfig).from_hf(raw["vision_config"])
             vlm = QwenVlModel(model, vcfg, ck.get, int(raw.get("image_token_id", 151655)),
@@ -412,6 +423,9 @@ def _load_hf(p: Path, device, comm, fp8) -> LoadedLLM:
         bos = d.get("bos_token") if isinstance(d.get("bos_token"), str) else ""
         eos = d.get("eos_token") if isinstance(d.get("eos_token"), str) else ""
     tpl = ChatTemplate(tpl_src, bos or "", eos or "") if tpl_src else ChatTemplate.for_arch(cfg.arch)
+    if vlm is not None and hasattr(vlm, "bind_tokenizer"):
+        specials = getattr(tok, "special_tokens", None) or {}
+        vlm.bind_tokenizer(specials.get, tok.encode("\n", add_special=False))
     log.info(f"[Load] {p.name}: {cfg.arch} {cfg.num_layers}L hidden {cfg.hidden_size} "
              f"({model.weight_bytes() / 2**30:.2f} GiB on {device})")
     return LoadedLLM(model, tok, tpl, cfg, str(p), vlm)
