@@ -248,6 +248,11 @@ class VisionRequest:
     texts: list[str] = field(default_factory=list)
     score_threshold: float = 0.1
     nms_iou: float = 0.5
+    # promptable segmentation (SAM 2): one mask per prompt; a prompt is a list of [x, y] points with their
+    # labels (1 foreground, 0 background), a box [x0, y0, x1, y1], or both, in pixels of the image
+    points: list = field(default_factory=list)        # per prompt: [[x, y], ...]
+    point_labels: list = field(default_factory=list)  # per prompt: [1, 0, ...] (default: all foreground)
+    boxes: list = field(default_factory=list)         # per prompt: [x0, y0, x1, y1]
 
 
 @dataclass
@@ -258,6 +263,7 @@ class VisionResult:
     depth: Optional[list] = None               # per image: float32 [H, W] at the image's own size
     masks: Optional[list] = None               # per image: float32 [n_texts, H, W] probabilities in [0, 1]
     detections: Optional[list] = None          # per image: [{"label", "score", "box": [x0, y0, x1, y1] in pixels}]
+    mask_scores: Optional[list] = None         # promptable segmentation, per image: predicted IoU of every returned mask
 
 
 @dataclass

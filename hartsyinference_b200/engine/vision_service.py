@@ -141,6 +141,49 @@ class _Segmenter:
         return out
 
 
+class _PromptSegmenter:
+    """SAM 2: one mask per prompt (points and / or a box); of the three candidate masks the one with the
+    highest predicted IoU is returned, as probabilities at the image's own size."""
+    MEAN, STD = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
+
+    def __init__(self, path: str, raw: dict, device):
+        from ..models.vision.sam2 import Sam2, sam2_from_hf
+        self.cfg = sam2_from_hf(raw)
+        self.model = Sam2(self.cfg, device, get=ShardedCheckpoint(path).get)
+
+    def segment(self, images: list, points: list, labels: list, boxes: list) -> tuple[list, list]:
+        size = self.cfg.image_size
+        n = max(len(points), len(boxes))
+        if n == 0:
+            raise ValueError("promptable segmentation needs points or boxes")
+        if points and boxes and len(points) != len(boxes):
+            raise ValueError("give as many boxes as point prompts (or only one of the two)")
+        masks, scores = [], []
+        for im in images:
+            h, w = _image_hw(im)
+            x = _Detector._squeeze(im, size)
+            x = (x - torch.tensor(self.MEAN)[:, None, None]) / torch.tensor(self.STD)[:, None, None]
+            sx, sy = size / w, size / h
+            pts = lab = bxs = None
+            if points:
+                m = max(len(p) for p in points)
+                pts = torch.zeros(1, n, m, 2)
+                lab = torch.full((1, n, m), -10, dtype=torch.int64)           # padding points are ignored
+                for i, p in enumerate(points):
+                    for j, (px, py) in enumerate(p):
+                        pts[0, i, j] = torch.tensor([px * sx, py * sy])
+                        lab[0, i, j] = int(labels[i][j]) if (i < len(labels) and j < len(labels[i])) else 1
+            if boxes:
+                bxs = torch.tensor([[b[0] * sx, b[1] * sy, b[2] * sx, b[3] * sy] for b in boxes])[None]
+            logits, iou, _ = self.model.segment(x[None], pts, lab, bxs, multimask=True)
+            best = iou[0].argmax(-1)                                           # [n]
+            pick = logits[0][torch.arange(n), best]                            # [n, h', w']
+            up = torch.nn.functional.interpolate(pick[None].float().cpu(), size=(h, w), mode="bilinear", align_corners=False)[0]
+            masks.append(torch.sigmoid(up))
+            scores.append(iou[0][torch.arange(n), best].float().cpu())
+        return masks, scores
+
+
 def nms(boxes: torch.Tensor, scores: torch.Tensor, iou: float) -> list[int]:
     """Greedy non-maximum suppression over [n, 4] corner boxes; returns kept indices, best first."""
     order = scores.argsort(descending=True).tolist()
@@ -269,6 +312,8 @@ class VisionService:
                     self._loaded[path] = _Segmenter(path, raw, self.device)
                 elif mt in ("owlvit", "owlv2"):
                     self._loaded[path] = _Detector(path, raw, self.device)
+                elif mt in ("sam2", "sam2_video"):
+                    self._loaded[path] = _PromptSegmenter(path, raw, self.device)
                 elif mt == "rt_detr":
                     self._loaded[path] = _ClosedSetDetector(path, raw, self.device)
                 elif mt in ("siglip", "siglip_vision_model", "dinov2"):
@@ -294,6 +339,11 @@ class VisionService:
             return out
         if isinstance(m, (_Detector, _ClosedSetDetector)):
             raise ValueError("this checkpoint detects; use operation 'detect'")
+        if req.operation == "segment" and isinstance(m, _PromptSegmenter):
+            out.masks, out.mask_scores = m.segment(req.images, req.points, req.point_labels, req.boxes)
+            return out
+        if isinstance(m, _PromptSegmenter):
+            raise ValueError("this checkpoint segments from point / box prompts; use operation 'segment'")
         if req.operation == "segment":
             if not isinstance(m, _Segmenter):
                 raise ValueError("this checkpoint is not a text-prompted segmenter")
