@@ -534,7 +534,9 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
             b64 = im.split(",", 1)[1] if im.startswith("data:") else im
             images.append(Image.open(io.BytesIO(base64.b64decode(b64))).convert("RGB"))
         vreq = VisionRequest(operation=body.get("operation", "embed"), images=images, texts=list(body.get("texts") or []),
-                             score_threshold=float(body.get("score_threshold", 0.1)), nms_iou=float(body.get("nms_iou", 0.5)))
+                             score_threshold=float(body.get("score_threshold", 0.1)), nms_iou=float(body.get("nms_iou", 0.5)),
+                             points=list(body.get("points") or []), point_labels=list(body.get("point_labels") or []),
+                             boxes=list(body.get("boxes") or []))
         with heavy_queue.slot():
             res = eng.vision.run(resolve(body.get("model"), Modality.VISION), vreq)
         if res.detections is not None:
@@ -552,7 +554,10 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
                     row.append({"width": int(mk.shape[1]), "height": int(mk.shape[0]), "coverage": float((mk > 0.5).float().mean()),
                                 "png_base64": base64.b64encode(buf.getvalue()).decode()})
                 out_masks.append(row)
-            return {"masks": out_masks}
+            out = {"masks": out_masks}
+            if res.mask_scores is not None:
+                out["mask_scores"] = [[float(v) for v in sc] for sc in res.mask_scores]
+            return out
         if res.depth is not None:
             # 16-bit grayscale PNGs, each map scaled to its own maximum
             import io
