@@ -92,3 +92,19 @@ def test_loader_builds_the_model_from_a_checkpoint_directory(tmp_path):
     assert llm.vlm is not None and llm.vlm.longest_edge == 64 and llm.vlm.rows_per_tile == 4
     ids, emb, mask = llm.vlm.expand_prompt([3, IMG, 4], [torch.rand(3, 20, 40)])
     assert int(mask.sum()) == 12 and emb.shape[0] == len(ids)
+
+
+import pytest
+
+
+@pytest.mark.gpu
+def test_gpu_image_rows_agree_with_cpu():
+    c, hf, _, mine = _pair()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    text = dict(c.text_config.to_dict(), model_type="llama")
+    dec = DecoderModel(from_hf_config(text), "cuda")
+    dec.load_state_dict(lambda n: sd.get("model.text_model." + n[len("model."):]) if n.startswith("model.") else sd.get(n))
+    gpu = Idefics3Model(dec, idefics3_vision_from_hf(c.vision_config.to_dict()), IMG, 2, get=sd.get)
+    views = torch.randn(2, 3, 32, 32)
+    a, b = mine.view_features(views).float(), gpu.view_features(views.cuda()).float().cpu()
+    assert torch.nn.functional.cosine_similarity(a, b, dim=-1).min() > 0.99

@@ -90,3 +90,16 @@ def test_vision_service_segments_from_points_and_boxes(tmp_path):
         eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="segment", images=[pic]))
     with pytest.raises(ValueError):
         eng.vision.run(ModelSpec(str(d)), VisionRequest(operation="embed", images=[pic]))
+
+
+@pytest.mark.gpu
+def test_gpu_bf16_agrees_with_cpu():
+    c, hf = _hf(2)
+    sd = hf.state_dict()
+    cfg = sam2_from_hf(c.to_dict())
+    x = torch.randn(1, 3, 64, 64)
+    pts, lab = torch.tensor([[[[20.0, 30.0]]]]), torch.tensor([[[1]]])
+    m0, i0, _ = Sam2(cfg, "cpu", get=sd.get).segment(x, pts, lab)
+    m1, i1, _ = Sam2(cfg, "cuda", get=sd.get).segment(x, pts, lab)          # bf16 on the device
+    cos = torch.nn.functional.cosine_similarity(m1.cpu().flatten(), m0.flatten(), dim=0)
+    assert cos > 0.98 and (i1.cpu() - i0).abs().max() < 0.05

@@ -131,3 +131,17 @@ def test_world_service_sessions_and_http(tmp_path):
     assert client.post("/v1/native/world", json={"session": sid, "action": [0.0] * 25}).status_code == 404
     r3 = client.post("/v1/native/world", json={"model": "synthetic:oasis:tiny", "image": img, "actions": [[0.0] * 25]})
     assert r3.status_code == 200 and r3.json()["frames"] == 2
+
+
+@pytest.mark.gpu
+def test_gpu_world_steps_and_agrees_with_cpu_on_the_first_frame():
+    cfg = O.tiny_oasis(hidden=128, heads=2, vae_width=128)
+    pic = torch.rand(3, 16, 24, generator=torch.Generator().manual_seed(0))
+    frames = {}
+    for dev in ("cpu", "cuda"):
+        w = O.OasisWorld(cfg, O.OasisDit(cfg, dev, seed=1), O.OasisVae(cfg, dev, seed=2), seed=3)
+        w.reset(pic)
+        frames[dev] = torch.stack([w.step(torch.zeros(25)).float().cpu() for _ in range(2)])
+    assert torch.isfinite(frames["cuda"]).all()
+    # same random weights and noise; the device runs bf16 GEMMs
+    assert (frames["cuda"][0] - frames["cpu"][0]).abs().mean() < 0.05
