@@ -144,7 +144,7 @@ class _Weights:
 
 def _linear(x: torch.Tensor, lw: LinearWeight) -> torch.Tensor:
     shape = x.shape
-    if x.is_cuda and x.dtype == torch.bfloat16 and shape[-1] % 8 == 0 and lw.out_features % 8 == 0:
+    if x.is_cuda and x.dtype == torch.bfloat16 and shape[-1] % 64 == 0 and lw.out_features % 16 == 0:
         return ops.linear(x.reshape(-1, shape[-1]).contiguous(), lw).reshape(*shape[:-1], lw.out_features)
     return F.linear(x, lw.weight, lw.bias)
 
