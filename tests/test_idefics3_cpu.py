@@ -12,11 +12,11 @@ from hartsyinference_b200.models.vlm.idefics3 import Idefics3Model, idefics3_vis
 IMG = 290
 
 
-def _pair():
+def _pair(vision_width: int = 32):
     from transformers import Idefics3Config, Idefics3ForConditionalGeneration
     torch.manual_seed(0)
-    c = Idefics3Config(vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2,
-                                          image_size=32, patch_size=8),
+    c = Idefics3Config(vision_config=dict(hidden_size=vision_width, intermediate_size=2 * vision_width, num_hidden_layers=2,
+                                          num_attention_heads=2, image_size=32, patch_size=8),
                        text_config=dict(model_type="llama", hidden_size=64, intermediate_size=128, num_hidden_layers=2,
                                         num_attention_heads=4, num_key_value_heads=2, vocab_size=300, head_dim=16,
                                         tie_word_embeddings=False),
@@ -99,7 +99,7 @@ import pytest
 
 @pytest.mark.gpu
 def test_gpu_image_rows_agree_with_cpu():
-    c, hf, _, mine = _pair()
+    c, hf, _, mine = _pair(vision_width=128)            # head dim 64: the device attention kernel's smallest
     sd = {k: v.detach() for k, v in hf.state_dict().items()}
     text = dict(c.text_config.to_dict(), model_type="llama")
     dec = DecoderModel(from_hf_config(text), "cuda")
