@@ -67,7 +67,8 @@ class _PipelineCache:
                 raise UnsupportedModelError(f"{spec.requested}: no such checkpoint")
             ctx.root = path
             # a diffusers-layout directory keeps the transformer, VAE, encoders and tokenizers in sub-folders
-            ctx.checkpoint = ShardedCheckpoint(path / "transformer" if (path / "transformer").exists() else path)
+            sub = next((path / n for n in ("transformer", "unet") if (path / n).exists()), path)
+            ctx.checkpoint = ShardedCheckpoint(sub)
         return ctx
 
     def generate(self, spec: ModelSpec, req, progress=None):

@@ -348,6 +348,49 @@ class Sd3Recipe(Recipe):
         return Sd3Pipeline(comp)
 
 
+class StableDiffusionRecipe(Recipe):
+    """Stable Diffusion 1.5 and SDXL (diffusers layout: ``unet/``, ``vae/``, ``text_encoder[_2]/``,
+    ``tokenizer[_2]/``): convolutional U-Net, CLIP conditioning, epsilon prediction, true CFG."""
+    name = "stable-diffusion"
+    families = ("sdxl", "sd15", "sd1.5", "sd-1.5", "stable-diffusion-xl", "stable-diffusion-v1", "stable-diffusion-1")
+    supports = Features.TRUE_CFG
+    defaults = Defaults({"steps": 30, "cfg_scale": 7.0, "width": 1024, "height": 1024})
+
+    def detect(self, ck):
+        return ck.get("down_blocks.0.resnets.0.conv1.weight") is not None and ck.get("time_embedding.linear_1.weight") is not None
+
+    def construct(self, ctx: RecipeContext):
+        from ..models.unet import unet2d as U
+        from ..models.vae.vae2d import Vae2dDecoder, tiny_vae2d
+        from ..pipelines.sdxl import SD15_VAE, SDXL_VAE, SdComponents, StableDiffusionPipeline
+        spec = ctx.spec
+        if ctx.checkpoint is None:
+            fam = spec.requested[len("synthetic:"):]
+            tiny, xl = fam.endswith("-tiny"), fam.startswith("sdxl") or "xl" in fam.split("-")[0]
+            cfg = U.tiny_unet(xl) if tiny else (U.SDXL_BASE if xl else U.SD15)
+            vae = Vae2dDecoder(tiny_vae2d() if tiny else (SDXL_VAE if xl else SD15_VAE), ctx.device, ctx.dtype)
+            return StableDiffusionPipeline(SdComponents(U.UNet2D(cfg, ctx.device), vae))
+        path = ctx.root
+        udir = path / "unet" if (path / "unet").exists() else path
+        ucfg_path = udir / "config.json"
+        cfg = U.unet_from_hf(json.loads(ucfg_path.read_text())) if ucfg_path.exists() else U.SD15
+        ck = ctx.checkpoint                      # the service opens ``unet/`` when the directory has one
+        xl = cfg.addition_embed_dim > 0
+        vae = None
+        if "vae" in spec.aux or (path / "vae").exists():
+            vae = Vae2dDecoder(SDXL_VAE if xl else SD15_VAE, ctx.vae_device, get=ShardedCheckpoint(spec.aux.get("vae", path / "vae")).get)
+        comp = SdComponents(U.UNet2D(cfg, ctx.device, get=ck.get), vae)
+        cl, cl_tok = load_clip_text(path / "text_encoder", path / "tokenizer", ctx.text_encoder_device)
+        if cl is not None:
+            layer = -2 if xl else -1
+            comp.clip_l = lambda prompt: cl.encode(torch.tensor(cl_tok.encode(prompt, pad=True)), layer=layer)
+        if xl:
+            cg, cg_tok = load_clip_text(path / "text_encoder_2", path / "tokenizer_2", ctx.text_encoder_device)
+            if cg is not None:
+                comp.clip_g = lambda prompt: cg.encode(torch.tensor(cg_tok.encode(prompt, pad=True)), layer=-2, project=True)
+        return StableDiffusionPipeline(comp)
+
+
 # ------------------------------------------------------------------------------------ video families
 def wan_tiny_vae_config(wan_cfg):
     from ..models.vae.vae3d import Vae3dConfig
@@ -393,4 +436,5 @@ class WanRecipe(Recipe):
 IMAGE_RECIPES.register(ChromaRecipe())
 IMAGE_RECIPES.register(Sd3Recipe())
 IMAGE_RECIPES.register(FluxRecipe())
+IMAGE_RECIPES.register(StableDiffusionRecipe())
 VIDEO_RECIPES.register(WanRecipe())
