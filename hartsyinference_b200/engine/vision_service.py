@@ -277,6 +277,109 @@ class _ClosedSetDetector:
         return out
 
 
+COCO80 = ("person,bicycle,car,motorcycle,airplane,bus,train,truck,boat,traffic light,fire hydrant,stop sign,"
+          "parking meter,bench,bird,cat,dog,horse,sheep,cow,elephant,bear,zebra,giraffe,backpack,umbrella,handbag,tie,"
+          "suitcase,frisbee,skis,snowboard,sports ball,kite,baseball bat,baseball glove,skateboard,surfboard,"
+          "tennis racket,bottle,wine glass,cup,fork,knife,spoon,bowl,banana,apple,sandwich,orange,broccoli,carrot,"
+          "hot dog,pizza,donut,cake,chair,couch,potted plant,bed,dining table,toilet,tv,laptop,mouse,remote,keyboard,"
+          "cell phone,microwave,oven,toaster,sink,refrigerator,book,clock,vase,scissors,teddy bear,hair drier,"
+          "toothbrush")
+
+
+def coco_names() -> list[str]:
+    return COCO80.split(",")
+
+
+class _YoloDetector:
+    """YOLOv8 / YOLO11 (detect, segment, pose and face-landmark heads): a state dict (``.safetensors`` or ``.pt``) with the trainer's ``model.N.*`` names, BatchNorm folded
+    or not. Labels come from ``names`` / ``id2label`` of a ``config.json`` beside it, else COCO's 80 when the head
+    has 80 classes, else the class index."""
+
+    def __init__(self, path: str, raw: dict, device):
+        from ..models.vision.yolo import YoloV8, detect_size
+        p = Path(path)
+        if p.is_dir():
+            files = sorted(p.glob("*.safetensors")) + sorted(p.glob("*.pt")) + sorted(p.glob("*.pth"))
+            if not files:
+                raise ValueError(f"{path}: no .safetensors or .pt file")
+            p = files[0]
+        if p.suffix == ".safetensors":
+            from ..assets.safetensors import SafeTensorsFile
+            f = SafeTensorsFile(p)
+            tensors = {k: f.get(k) for k in f.keys()}
+        else:
+            from ..assets.torch_checkpoint import load_torch_checkpoint
+            tensors = load_torch_checkpoint(p)
+        self.cfg = detect_size(tensors.get)
+        self.model = YoloV8(self.cfg, device, get=tensors.get)
+        names = raw.get("names") or raw.get("id2label") or {}
+        if isinstance(names, list):
+            names = dict(enumerate(names))
+        self.names = {int(k): str(v) for k, v in names.items()}
+        if not self.names and self.cfg.num_classes == 80:
+            self.names = dict(enumerate(coco_names()))
+        elif not self.names and self.cfg.num_classes == 1 and self.cfg.task == "pose":
+            self.names = {0: "person" if self.cfg.keypoints == 17 else "face"}
+        self.size = int(raw.get("image_size", 640))
+
+    def detect(self, images: list, texts: list, threshold: float, iou: float) -> list:
+        """Boxes in the pixels of each picture. Pose / face checkpoints add ``keypoints`` ([K][x, y(, visibility)]),
+        segmentation checkpoints ``mask`` (bool tensor [H, W] of the picture)."""
+        keep = {t.strip().lower() for t in (texts or [])}
+        out = []
+        for im in images:
+            x, scale, (px, py) = letterbox(_as_chw(im), self.size)
+            h, w = _image_hw(im)
+            found = []
+            for d in self.model.detect(x[None], threshold, iou, full=True)[0]:
+                name = self.names.get(d["label"], str(d["label"]))
+                if keep and name.lower() not in keep:
+                    continue
+                x0, y0, x1, y1 = d["box"]
+                box = [(x0 - px) / scale, (y0 - py) / scale, (x1 - px) / scale, (y1 - py) / scale]
+                item = {"label": name, "score": d["score"],
+                        "box": [min(max(box[0], 0.0), w), min(max(box[1], 0.0), h), min(max(box[2], 0.0), w), min(max(box[3], 0.0), h)]}
+                if "keypoints" in d:
+                    k = d["keypoints"].clone()
+                    k[:, 0], k[:, 1] = (k[:, 0] - px) / scale, (k[:, 1] - py) / scale
+                    item["keypoints"] = k.tolist()
+                if "mask" in d:
+                    nh, nw = max(int(round(h * scale)), 1), max(int(round(w * scale)), 1)
+                    m = d["mask"][py:py + nh, px:px + nw].float()[None, None]
+                    item["mask"] = torch.nn.functional.interpolate(m, size=(h, w), mode="bilinear", align_corners=False)[0, 0] > 0.5
+                found.append(item)
+            out.append(found)
+        return out
+
+
+def _as_chw(image) -> torch.Tensor:
+    import numpy as np
+    if isinstance(image, (str, bytes)) or hasattr(image, "__fspath__"):
+        from PIL import Image
+        image = Image.open(image)
+    if hasattr(image, "convert"):
+        image = torch.from_numpy(np.asarray(image.convert("RGB")).copy())
+    t = torch.as_tensor(image)
+    if t.dtype == torch.uint8:
+        t = t.float() / 255.0
+    if t.ndim == 3 and t.shape[-1] == 3 and t.shape[0] != 3:
+        t = t.permute(2, 0, 1)
+    return t.float()
+
+
+def letterbox(chw: torch.Tensor, size: int, fill: float = 114 / 255):
+    """Aspect-preserving resize of [3, H, W] into a ``size`` x ``size`` square, centred on grey. Returns the square,
+    the scale applied and the (x, y) padding, so a box maps back as ``(v - pad) / scale``."""
+    _, h, w = chw.shape
+    scale = min(size / h, size / w)
+    nh, nw = max(int(round(h * scale)), 1), max(int(round(w * scale)), 1)
+    r = torch.nn.functional.interpolate(chw[None], size=(nh, nw), mode="bilinear", align_corners=False, antialias=scale < 1)[0]
+    out = torch.full((3, size, size), fill)
+    py, px = (size - nh) // 2, (size - nw) // 2
+    out[:, py:py + nh, px:px + nw] = r.clamp(0, 1)
+    return out, scale, (px, py)
+
+
 def _image_hw(image) -> tuple[int, int]:
     if isinstance(image, (str, bytes)) or hasattr(image, "__fspath__"):
         from PIL import Image
@@ -304,9 +407,12 @@ class VisionService:
         path = spec.local_path or spec.requested
         with self._lock:
             if path not in self._loaded:
-                raw = json.loads((Path(path) / "config.json").read_text())
-                mt = raw.get("model_type", "clip")
-                if mt == "depth_anything":
+                cfg_file = Path(path) / "config.json"
+                raw = json.loads(cfg_file.read_text()) if cfg_file.is_file() else {}
+                mt = raw.get("model_type", "clip" if raw else "yolov8")
+                if str(mt).startswith("yolo"):
+                    self._loaded[path] = _YoloDetector(path, raw, self.device)
+                elif mt == "depth_anything":
                     self._loaded[path] = _DepthEstimator(path, raw, self.device)
                 elif mt == "clipseg":
                     self._loaded[path] = _Segmenter(path, raw, self.device)
@@ -328,7 +434,7 @@ class VisionService:
         m = self._model(spec)
         out = VisionResult()
         if req.operation == "detect":
-            if isinstance(m, _ClosedSetDetector):
+            if isinstance(m, (_ClosedSetDetector, _YoloDetector)):
                 out.detections = m.detect(req.images, req.texts, req.score_threshold, req.nms_iou)
                 return out
             if not isinstance(m, _Detector):
@@ -337,7 +443,7 @@ class VisionService:
                 raise ValueError("detect needs at least one text query")
             out.detections = m.detect(req.images, req.texts, req.score_threshold, req.nms_iou)
             return out
-        if isinstance(m, (_Detector, _ClosedSetDetector)):
+        if isinstance(m, (_Detector, _ClosedSetDetector, _YoloDetector)):
             raise ValueError("this checkpoint detects; use operation 'detect'")
         if req.operation == "segment" and isinstance(m, _PromptSegmenter):
             out.masks, out.mask_scores = m.segment(req.images, req.points, req.point_labels, req.boxes)
