@@ -15,8 +15,44 @@ from ..pipelines.whisper import TranscriptResult, WhisperOptions, WhisperPipelin
 from .requests import AudioRequest, ModelSpec
 
 
+class _BarkVoice:
+    """Bark checkpoint directory: weights, WordPiece tokenizer, ``generation_config.json`` (token bookkeeping of
+    the three stages) and optional voice presets (``speaker_embeddings/<voice>_{semantic,coarse,fine}_prompt.npy``)."""
+
+    def __init__(self, path: Path, raw: dict, device):
+        import json
+        from ..assets.safetensors import ShardedCheckpoint
+        from ..assets.tokenizer import WordPieceTokenizer
+        from ..models.audio.bark import Bark
+        gen_file = path / "generation_config.json"
+        generation = json.loads(gen_file.read_text()) if gen_file.exists() else {}
+        dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+        self.path, self.model = path, Bark(raw, ShardedCheckpoint(path).get, device, dtype, generation)
+        self.tokenizer = WordPieceTokenizer.from_dir(path)
+
+    def _history(self, voice):
+        if not voice:
+            return None
+        import numpy as np
+        out = {}
+        for part in ("semantic", "coarse", "fine"):
+            hits = [self.path / "speaker_embeddings" / f"{voice}_{part}_prompt.npy", self.path / f"{voice}_{part}_prompt.npy"]
+            f = next((h for h in hits if h.exists()), None)
+            if f is None:
+                raise ValueError(f"voice '{voice}': no {part} prompt beside the checkpoint")
+            out[f"{part}_prompt"] = torch.from_numpy(np.load(f)).long()
+        return out
+
+    def speak(self, req):
+        from ..pipelines.vits import SpeechResult
+        ids = torch.tensor(self.tokenizer.encode(req.text, add_special=False) or [0])
+        wave = self.model.generate(ids, self._history(req.voice), sample=not getattr(req, "greedy", False),
+                                   seed=int(getattr(req, "seed", 0) or 0)).float().cpu().clamp(-1, 1)
+        return SpeechResult(wave, self.model.sampling_rate, wave.numel() / self.model.sampling_rate)
+
+
 class SpeechService:
-    """Text-to-speech: hosts VITS pipelines (MMS-TTS / Piper-class voices) by checkpoint path.
+    """Text-to-speech: hosts VITS pipelines (MMS-TTS / Piper-class voices) and Bark checkpoints by path.
     Reference: src/HartsyInference.Engine/Services/SpeechService.cs, ISpeechService.cs."""
 
     def __init__(self, device):
@@ -25,7 +61,7 @@ class SpeechService:
         self._loaded: dict = {}
 
     def loaded_keys(self) -> list[str]:
-        return [f"vits:{k}" for k in self._loaded]
+        return [f"{'bark' if isinstance(v, _BarkVoice) else 'vits'}:{k}" for k, v in self._loaded.items()]
 
     def release(self) -> None:
         with self._lock:
@@ -36,8 +72,16 @@ class SpeechService:
         path = spec.local_path or spec.requested
         with self._lock:
             if path not in self._loaded:
-                self._loaded[path] = VitsPipeline.from_pretrained(path, self.device)
+                import json
+                cfg_file = Path(path) / "config.json"
+                raw = json.loads(cfg_file.read_text()) if cfg_file.exists() else {}
+                if raw.get("model_type") == "bark":
+                    self._loaded[path] = _BarkVoice(Path(path), raw, self.device)
+                else:
+                    self._loaded[path] = VitsPipeline.from_pretrained(path, self.device)
             pipe = self._loaded[path]
+        if isinstance(pipe, _BarkVoice):
+            return pipe.speak(req)
         return pipe.speak(req.text, speaking_rate=req.speed, noise_scale=req.noise_scale,
                           noise_scale_duration=req.noise_scale_duration)
 

@@ -167,6 +167,8 @@ class SpeechRequest:
     speed: Optional[float] = None
     noise_scale: Optional[float] = None
     noise_scale_duration: Optional[float] = None
+    seed: int = 0                      # sampling models (Bark)
+    greedy: bool = False
 
 
 @dataclass
