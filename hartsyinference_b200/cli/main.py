@@ -13,6 +13,7 @@ import json
 from pathlib import Path
 
 import click
+import torch
 
 from .. import config
 from ..engine.requests import EngineOptions, ImageRequest, Modality, ModelSpec, TextRequest, VideoRequest
@@ -282,6 +283,81 @@ def speak(model, text, out, speed, device):
     res = eng.speech.run(ModelSpec(model, Modality.SPEECH, local_path=model), SpeechRequest(text=text, speed=speed))
     write_wav(out, res.samples, res.sample_rate)
     click.echo(f"{out}: {res.seconds:.2f} s at {res.sample_rate} Hz")
+
+
+@cli.command(name="wake-listen")
+@click.argument("models_dir")
+@click.option("--host", default="127.0.0.1")
+@click.option("--port", "-p", default=10400, type=int)
+@click.option("--threshold", default=0.5, type=float)
+@click.option("--device", default="cpu")
+def wake_listen(models_dir, host, port, threshold, device):
+    """Serve wake-word detection to voice satellites (Wyoming protocol). MODELS_DIR holds melspectrogram and
+    embedding_model files plus one head per wake word."""
+    from ..audio.wake import WakeModelSet, WakeWordSettings
+    from ..server.wyoming import WyomingWakeServer
+    models = WakeModelSet(models_dir, device)
+    click.echo(f"wake words: {', '.join(models.heads) or '(none)'}; listening on {host}:{port}")
+    WyomingWakeServer(models, host, port, {n: WakeWordSettings(threshold=threshold) for n in models.heads}).serve_forever()
+
+
+@cli.command(name="wake-client")
+@click.argument("wav")
+@click.option("--host", default="127.0.0.1")
+@click.option("--port", "-p", default=10400, type=int)
+@click.option("--word", "words", multiple=True, help="only these wake words")
+@click.option("--realtime", is_flag=True, help="pace the stream like a microphone")
+def wake_client(wav, host, port, words, realtime):
+    """Stream a WAV file to a wake-word listener as a voice satellite would."""
+    import asyncio
+    from ..audio import read_wav
+    from ..server.wyoming import stream_wav
+    samples, rate = read_wav(wav)
+    if samples.dim() > 1:
+        samples = samples.mean(0)
+    hits = asyncio.run(stream_wav(host, port, samples, rate, words or None, realtime=realtime))
+    for h in hits:
+        click.echo(f"{h['name']} at {h['timestamp'] / 1000:.2f} s (score {h.get('score', 0):.2f})")
+    if not hits:
+        click.echo("no wake word detected")
+
+
+@cli.command(name="wake-train")
+@click.argument("phrase")
+@click.option("--models-dir", required=True, help="directory with melspectrogram / embedding_model; the head is written here")
+@click.option("--voice", "voices", multiple=True, required=True, help="text-to-speech checkpoint(s) that say the phrase")
+@click.option("--negative-audio", "negative_dirs", multiple=True, help="directories of WAV files that do not hold the phrase")
+@click.option("--negative-phrase", "negative_phrases", multiple=True, help="other sentences spoken by the same voices")
+@click.option("--epochs", default=40, type=int)
+@click.option("--device", default="cpu")
+def wake_train(phrase, models_dir, voices, negative_dirs, negative_phrases, epochs, device):
+    """Train a new wake word from its text with the engine's own text-to-speech voices."""
+    from pathlib import Path
+    from ..audio import read_wav
+    from ..audio.wake import RATE, WakeModelSet, train_wake_word
+    from ..audio.wav import resample
+    from ..engine.inference_engine import InferenceEngine
+    from ..engine.requests import SpeechRequest
+    eng = InferenceEngine(device)
+    models = WakeModelSet(models_dir, device)
+
+    def say(voice, text, speed):
+        res = eng.speech.run(ModelSpec(voice, Modality.SPEECH, local_path=voice), SpeechRequest(text=text, speed=speed))
+        x = res.samples.float().cpu()
+        return (resample(x, res.sample_rate, RATE) if res.sample_rate != RATE else x) * 32767.0
+
+    positives = [say(v, phrase, s) for v in voices for s in (0.85, 1.0, 1.15)]
+    others = list(negative_phrases) or ["what time is it", "turn on the kitchen lights please", "the weather looks fine today",
+                                        "play some music in the living room", "set a timer for ten minutes"]
+    negatives = [torch.cat([say(v, t, 1.0) for t in others]) for v in voices]
+    for d in negative_dirs:
+        for f in sorted(Path(d).expanduser().glob("**/*.wav")):
+            x, rate = read_wav(f)
+            x = x.mean(0) if x.dim() > 1 else x
+            negatives.append((resample(x, rate, RATE) if rate != RATE else x) * 32767.0)
+    name = "_".join(phrase.lower().split())
+    report = train_wake_word(models, name, positives, negatives, epochs=epochs, log=click.echo)
+    click.echo(f"wrote {report['path']}: recall {report['recall']:.2f}, false accepts {report['false_accepts']:.3f} on the training windows")
 
 
 @cli.command()
