@@ -51,8 +51,32 @@ class _BarkVoice:
         return SpeechResult(wave, self.model.sampling_rate, wave.numel() / self.model.sampling_rate)
 
 
+class _CsmVoice:
+    """CSM checkpoint directory (weights incl. the Mimi codec, ``tokenizer.json``). A turn is written
+    ``<|begin_of_text|>[speaker]text<|end_of_text|>``; ``voice`` is the speaker number."""
+
+    def __init__(self, path: Path, raw: dict, device):
+        from ..assets.safetensors import ShardedCheckpoint
+        from ..assets.tokenizer import Tokenizer
+        from ..models.audio.csm import Csm
+        dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+        self.model = Csm(raw, ShardedCheckpoint(path).get, device, dtype)
+        self.tokenizer = Tokenizer.from_hf_json(path / "tokenizer.json")
+        self.bos = raw.get("bos_token_id", 128000)
+        self.eot = self.tokenizer.special_tokens.get("<|end_of_text|>")
+
+    def speak(self, req):
+        from ..pipelines.vits import SpeechResult
+        body = self.tokenizer.encode(f"[{req.voice or 0}]{req.text}", add_special=False)
+        ids = [self.bos] + body + ([self.eot] if self.eot is not None else [])
+        limit = max(1, int(round(float(getattr(req, "max_seconds", 0) or 30.0) * self.model.codec.cfg.frame_rate)))
+        wave = self.model.generate(torch.tensor(ids), max_frames=limit, sample=not getattr(req, "greedy", False),
+                                   seed=int(getattr(req, "seed", 0) or 0)).float().cpu().clamp(-1, 1)
+        return SpeechResult(wave, self.model.sampling_rate, wave.numel() / self.model.sampling_rate)
+
+
 class SpeechService:
-    """Text-to-speech: hosts VITS pipelines (MMS-TTS / Piper-class voices) and Bark checkpoints by path.
+    """Text-to-speech: hosts VITS pipelines (MMS-TTS / Piper-class voices), Bark and CSM checkpoints by path.
     Reference: src/HartsyInference.Engine/Services/SpeechService.cs, ISpeechService.cs."""
 
     def __init__(self, device):
@@ -61,7 +85,8 @@ class SpeechService:
         self._loaded: dict = {}
 
     def loaded_keys(self) -> list[str]:
-        return [f"{'bark' if isinstance(v, _BarkVoice) else 'vits'}:{k}" for k, v in self._loaded.items()]
+        kind = lambda v: "bark" if isinstance(v, _BarkVoice) else "csm" if isinstance(v, _CsmVoice) else "vits"
+        return [f"{kind(v)}:{k}" for k, v in self._loaded.items()]
 
     def release(self) -> None:
         with self._lock:
@@ -77,10 +102,12 @@ class SpeechService:
                 raw = json.loads(cfg_file.read_text()) if cfg_file.exists() else {}
                 if raw.get("model_type") == "bark":
                     self._loaded[path] = _BarkVoice(Path(path), raw, self.device)
+                elif raw.get("model_type") == "csm":
+                    self._loaded[path] = _CsmVoice(Path(path), raw, self.device)
                 else:
                     self._loaded[path] = VitsPipeline.from_pretrained(path, self.device)
             pipe = self._loaded[path]
-        if isinstance(pipe, _BarkVoice):
+        if isinstance(pipe, (_BarkVoice, _CsmVoice)):
             return pipe.speak(req)
         return pipe.speak(req.text, speaking_rate=req.speed, noise_scale=req.noise_scale,
                           noise_scale_duration=req.noise_scale_duration)

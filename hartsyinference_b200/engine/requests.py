@@ -167,8 +167,9 @@ class SpeechRequest:
     speed: Optional[float] = None
     noise_scale: Optional[float] = None
     noise_scale_duration: Optional[float] = None
-    seed: int = 0                      # sampling models (Bark)
+    seed: int = 0                      # sampling models (Bark, CSM)
     greedy: bool = False
+    max_seconds: float = 30.0          # autoregressive models stop here if no end frame came
 
 
 @dataclass

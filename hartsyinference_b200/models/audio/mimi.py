@@ -183,7 +183,8 @@ class Mimi:
     @torch.no_grad()
     def dequantize(self, codes: torch.Tensor) -> torch.Tensor:
         """codes [B, n, frames] -> latents [B, hidden, frames]."""
-        codes = codes.to(self.device).long()
+        # ids outside the tables (a language model's control ids) are clamped, never used as gather indices
+        codes = codes.to(self.device).long().clamp(0, self.cfg.codebook_size - 1)
         s = self.cfg.semantic_quantizers
         total = None
         for group, lo, hi in (("semantic", 0, min(s, codes.shape[1])), ("acoustic", s, codes.shape[1])):
