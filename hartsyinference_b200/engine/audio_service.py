@@ -154,6 +154,51 @@ class MusicService:
         return SpeechResult(samples, model.sampling_rate, samples.numel() / model.sampling_rate)
 
 
+class _KyutaiTranscriber:
+    """Kyutai speech-to-text checkpoint directory (language model + Mimi codec, ``tokenizer.json`` or
+    ``tokenizer.model``-derived json). Words come out ``audio_delay_seconds`` after they were spoken; a segment is
+    written per word run with the time of the frame that produced its first piece, shifted back by the delay."""
+
+    def __init__(self, path: Path, raw: dict, device):
+        import json
+        from ..assets.safetensors import ShardedCheckpoint
+        from ..assets.tokenizer import Tokenizer
+        from ..models.audio.kyutai_stt import KyutaiStt
+        dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+        self.model = KyutaiStt(raw, ShardedCheckpoint(path).get, device, dtype)
+        self.tokenizer = Tokenizer.from_hf_json(path / "tokenizer.json")
+        pre = path / "preprocessor_config.json"
+        extra = json.loads(pre.read_text()) if pre.exists() else {}
+        self.delay = float(extra.get("audio_delay_seconds", 2.5))
+        self.prefix = float(extra.get("audio_silence_prefix_seconds", 1.0))
+
+    def transcribe(self, audio: torch.Tensor, rate: int, opts) -> TranscriptResult:
+        from ..audio.wav import resample
+        from ..pipelines.whisper import WhisperSegment
+        x = audio.float()
+        x = x.mean(0) if x.dim() > 1 else x
+        want = self.model.codec.cfg.sampling_rate
+        if rate != want:
+            x = resample(x, rate, want)
+        tokens = self.model.transcribe_tokens(x, self.delay, self.prefix)
+        frame = self.model.cfg.frame_size / want
+        skip = {self.model.cfg.pad, self.model.cfg.bos}
+        segments, run, start = [], [], 0.0
+        for i, t in enumerate(tokens.tolist() + [self.model.cfg.pad]):
+            if t in skip:
+                if run:
+                    text = self.tokenizer.decode(run)
+                    end = max(i * frame - self.delay - self.prefix, start)
+                    segments.append(WhisperSegment(start=start, end=end, text=text, tokens=list(run)))
+                    run = []
+                continue
+            if not run:
+                start = max(i * frame - self.delay - self.prefix, 0.0)
+            run.append(t)
+        text = " ".join(s.text.strip() for s in segments if s.text.strip())
+        return TranscriptResult(text=text, language=None, segments=segments, duration_s=x.numel() / want)
+
+
 class TranscribeService:
     def __init__(self, device):
         self.device = device
@@ -161,7 +206,7 @@ class TranscribeService:
         self._loaded: dict[str, WhisperPipeline] = {}
 
     def loaded_keys(self) -> list[str]:
-        return [f"whisper:{k}" for k in self._loaded]
+        return [f"{'kyutai' if isinstance(v, _KyutaiTranscriber) else 'whisper'}:{k}" for k, v in self._loaded.items()]
 
     def release(self) -> None:
         with self._lock:
@@ -175,8 +220,11 @@ class TranscribeService:
                 from ..pipelines.whisper import MoonshinePipeline
                 cfg_file = Path(path) / "config.json"
                 kind = json.loads(cfg_file.read_text()).get("model_type", "whisper") if cfg_file.exists() else "whisper"
-                cls = MoonshinePipeline if kind == "moonshine" else WhisperPipeline
-                self._loaded[path] = cls.from_pretrained(path, self.device)
+                if kind == "kyutai_speech_to_text":
+                    self._loaded[path] = _KyutaiTranscriber(Path(path), json.loads(cfg_file.read_text()), self.device)
+                else:
+                    cls = MoonshinePipeline if kind == "moonshine" else WhisperPipeline
+                    self._loaded[path] = cls.from_pretrained(path, self.device)
             return self._loaded[path]
 
     def run(self, spec: ModelSpec, req: AudioRequest) -> TranscriptResult:
