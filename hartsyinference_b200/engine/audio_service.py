@@ -75,8 +75,41 @@ class _CsmVoice:
         return SpeechResult(wave, self.model.sampling_rate, wave.numel() / self.model.sampling_rate)
 
 
+class _DiaVoice:
+    """Dia checkpoint directory; the DAC codec it writes for sits in a ``dac`` (or ``audio_tokenizer``) subdirectory
+    with its own ``config.json``. Text is read as bytes, the speaker tags ``[S1]`` / ``[S2]`` as bytes 1 / 2."""
+
+    def __init__(self, path: Path, raw: dict, device):
+        import json
+        from ..assets.safetensors import ShardedCheckpoint
+        from ..models.audio.dac import DacCodec, DacConfig
+        from ..models.audio.dia import Dia
+        dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+        sub = next((path / n for n in ("dac", "audio_tokenizer", "codec") if (path / n / "config.json").exists()), None)
+        if sub is None:
+            raise FileNotFoundError(f"{path}: no dac / audio_tokenizer subdirectory with the codec")
+        codec_raw = json.loads((sub / "config.json").read_text())
+        self.codec = DacCodec(DacConfig.from_hf(codec_raw), ShardedCheckpoint(sub).get, device)
+        self.model = Dia(raw, ShardedCheckpoint(path).get, device, dtype, codec=self.codec)
+        self.sampling_rate = codec_raw.get("sampling_rate", 44100)
+        self.frame_rate = self.sampling_rate / self.codec.cfg.hop
+
+    @staticmethod
+    def text_bytes(text: str) -> list[int]:
+        return list(text.replace("[S1]", "\x01").replace("[S2]", "\x02").encode("utf-8"))
+
+    def speak(self, req):
+        from ..pipelines.vits import SpeechResult
+        text = req.text if req.text.lstrip().startswith("[S") else "[S1] " + req.text
+        limit = max(2, int(round(float(getattr(req, "max_seconds", 0) or 30.0) * self.frame_rate))) + max(self.model.delays) + 2
+        wave = self.model.generate(torch.tensor(self.text_bytes(text)), max_steps=limit, sample=not getattr(req, "greedy", False),
+                                   temperature=1.3 if not getattr(req, "greedy", False) else 1.0,
+                                   seed=int(getattr(req, "seed", 0) or 0)).float().cpu().clamp(-1, 1)
+        return SpeechResult(wave, self.sampling_rate, wave.numel() / self.sampling_rate)
+
+
 class SpeechService:
-    """Text-to-speech: hosts VITS pipelines (MMS-TTS / Piper-class voices), Bark and CSM checkpoints by path.
+    """Text-to-speech: hosts VITS pipelines (MMS-TTS / Piper-class voices), Bark, CSM and Dia checkpoints by path.
     Reference: src/HartsyInference.Engine/Services/SpeechService.cs, ISpeechService.cs."""
 
     def __init__(self, device):
@@ -85,7 +118,8 @@ class SpeechService:
         self._loaded: dict = {}
 
     def loaded_keys(self) -> list[str]:
-        kind = lambda v: "bark" if isinstance(v, _BarkVoice) else "csm" if isinstance(v, _CsmVoice) else "vits"
+        kind = lambda v: ("bark" if isinstance(v, _BarkVoice) else "csm" if isinstance(v, _CsmVoice) else
+                          "dia" if isinstance(v, _DiaVoice) else "vits")
         return [f"{kind(v)}:{k}" for k, v in self._loaded.items()]
 
     def release(self) -> None:
@@ -104,10 +138,12 @@ class SpeechService:
                     self._loaded[path] = _BarkVoice(Path(path), raw, self.device)
                 elif raw.get("model_type") == "csm":
                     self._loaded[path] = _CsmVoice(Path(path), raw, self.device)
+                elif raw.get("model_type") == "dia":
+                    self._loaded[path] = _DiaVoice(Path(path), raw, self.device)
                 else:
                     self._loaded[path] = VitsPipeline.from_pretrained(path, self.device)
             pipe = self._loaded[path]
-        if isinstance(pipe, (_BarkVoice, _CsmVoice)):
+        if isinstance(pipe, (_BarkVoice, _CsmVoice, _DiaVoice)):
             return pipe.speak(req)
         return pipe.speak(req.text, speaking_rate=req.speed, noise_scale=req.noise_scale,
                           noise_scale_duration=req.noise_scale_duration)
