@@ -275,7 +275,32 @@ class FluxRecipe(Recipe):
         comp = FluxComponents(tr, vae, vae_encoder=enc, controlnet=cnet)
         comp.clip, comp.clip_tokenizer = load_clip_text(path / "text_encoder", path / "tokenizer", ctx.text_encoder_device)
         comp.t5, comp.t5_tokenizer = load_t5(path / "text_encoder_2", path / "tokenizer_2", ctx.text_encoder_device, ctx.fp8)
+        self._redux(comp, path, spec, ctx)
         return FluxPipeline(comp, cfg_comm=ctx.cfg_comm)
+
+    @staticmethod
+    def _redux(comp, path: Path, spec, ctx) -> None:
+        """Optional picture prompts: ``redux/`` (the projector file) with ``image_encoder/`` (SigLIP vision tower);
+        ``spec.aux`` may name them elsewhere (``redux``, ``image_encoder``)."""
+        rdir = Path(spec.aux.get("redux", path / "redux"))
+        edir = Path(spec.aux.get("image_encoder", path / "image_encoder"))
+        if not rdir.exists() or not (edir / "config.json").exists():
+            return
+        from ..models.dit.redux import ReduxImageEncoder
+        from ..models.encoders.clip_vision import CLIP_MEAN, CLIP_STD, preprocess_image
+        from ..models.encoders.vit import VitEncoder, vit_from_hf
+        rck = ShardedCheckpoint(rdir)
+        comp.redux = ReduxImageEncoder(rck.get, ctx.device, ctx.dtype)
+        raw = json.loads((edir / "config.json").read_text())
+        vit = VitEncoder(vit_from_hf({**raw.get("vision_config", raw), "model_type": "siglip"}), ctx.text_encoder_device,
+                         get=ShardedCheckpoint(edir).get)
+        cm, cs = torch.tensor(CLIP_MEAN)[:, None, None], torch.tensor(CLIP_STD)[:, None, None]
+
+        def states(picture):
+            x = preprocess_image(picture, vit.cfg.image_size) * cs + cm          # back to [0, 1], then SigLIP's 0.5 / 0.5
+            return vit.hidden_states((x - 0.5) / 0.5)
+
+        comp.image_states = states
 
     def _synthetic_transformer(self, ctx, tiny):
         from ..models.dit import flux as F
@@ -353,7 +378,7 @@ class StableDiffusionRecipe(Recipe):
     ``tokenizer[_2]/``): convolutional U-Net, CLIP conditioning, epsilon prediction, true CFG."""
     name = "stable-diffusion"
     families = ("sdxl", "sd15", "sd1.5", "sd-1.5", "stable-diffusion-xl", "stable-diffusion-v1", "stable-diffusion-1")
-    supports = Features.TRUE_CFG
+    supports = Features.TRUE_CFG | Features.CONTROLNET
     defaults = Defaults({"steps": 30, "cfg_scale": 7.0, "width": 1024, "height": 1024})
 
     def detect(self, ck):
@@ -388,7 +413,36 @@ class StableDiffusionRecipe(Recipe):
             cg, cg_tok = load_clip_text(path / "text_encoder_2", path / "tokenizer_2", ctx.text_encoder_device)
             if cg is not None:
                 comp.clip_g = lambda prompt: cg.encode(torch.tensor(cg_tok.encode(prompt, pad=True)), layer=-2, project=True)
+        self._adapters(comp, cfg, path, spec, ctx)
         return StableDiffusionPipeline(comp)
+
+    @staticmethod
+    def _adapters(comp, cfg, path: Path, spec, ctx) -> None:
+        """Optional adapters beside the model: ``controlnet/`` (diffusers ControlNet of the same family),
+        ``ip_adapter/`` (one adapter file) with ``image_encoder/`` (CLIP vision tower with projection). ``spec.aux``
+        may name them elsewhere (``controlnet``, ``ip_adapter``, ``image_encoder``)."""
+        from ..models.unet import unet2d as U
+        cdir = Path(spec.aux.get("controlnet", path / "controlnet"))
+        if cdir.is_dir() and ((cdir / "config.json").exists() or any(cdir.glob("*.safetensors"))):
+            ccfg = U.unet_from_hf(json.loads((cdir / "config.json").read_text())) if (cdir / "config.json").exists() else cfg
+            comp.controlnet = U.ControlNet(ccfg, ctx.device, get=ShardedCheckpoint(cdir).get)
+        adir = Path(spec.aux.get("ip_adapter", path / "ip_adapter"))
+        if adir.exists():
+            from ..assets.safetensors import SafeTensorsFile
+            files = [adir] if adir.is_file() else sorted(adir.glob("*.safetensors"))
+            if files:
+                f = SafeTensorsFile(files[0])
+                names = set(f.keys())
+                comp.image_projector = U.install_ip_adapter(comp.unet, lambda n: f.get(n) if n in names else None)
+        edir = Path(spec.aux.get("image_encoder", path / "image_encoder"))
+        if comp.image_projector is not None and (edir / "config.json").exists():
+            from ..models.encoders.clip_vision import ClipVisionEncoder, clip_vision_from_hf, preprocess_image
+            raw = json.loads((edir / "config.json").read_text())
+            eck = ShardedCheckpoint(edir)
+            vision = ClipVisionEncoder(clip_vision_from_hf(raw.get("vision_config", raw)), ctx.text_encoder_device, get=eck.get,
+                                       prefix="vision_model.")
+            proj = eck.get("visual_projection.weight").float().to(vision.device)
+            comp.image_encoder = lambda picture: (vision.embed(preprocess_image(picture, vision.cfg.image_size)).float() @ proj.t())[None]
 
 
 # ------------------------------------------------------------------------------------ video families

@@ -138,6 +138,8 @@ class ImageRequest:
     init_image: Optional[Any] = None
     mask_image: Optional[Any] = None     # white = repaint (inpainting; needs init_image)
     control_image: Optional[Any] = None  # ControlNet conditioning image (needs a ControlNet beside the model)
+    image_prompt: Optional[Any] = None   # picture prompt (IP-Adapter on U-Net models, Redux on Flux)
+    image_prompt_scale: float = 1.0
     control_strength: float = 1.0
     strength: float = 1.0
     loras: list[tuple[str, float]] = field(default_factory=list)

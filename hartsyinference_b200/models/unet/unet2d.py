@@ -113,6 +113,23 @@ class UNet2D:
         self._get, self._g = get, torch.Generator().manual_seed(seed)
         self._w: dict = {}
         self._lin: dict = {}
+        self._ip: Optional[dict] = None
+
+    def cross_attention_paths(self) -> list[str]:
+        """Every cross-attention layer in the order adapters index them: down blocks, up blocks, middle block."""
+        cfg = self.cfg
+        out = []
+        for i in range(len(cfg.block_out_channels)):
+            if cfg.down_attention[i]:
+                out += [f"down_blocks.{i}.attentions.{j}.transformer_blocks.{k}.attn2" for j in range(cfg.layers_per_block)
+                        for k in range(cfg.transformer_layers[i])]
+        depth = list(reversed(cfg.transformer_layers))
+        for i in range(len(cfg.block_out_channels)):
+            if cfg.up_attention[i]:
+                out += [f"up_blocks.{i}.attentions.{j}.transformer_blocks.{k}.attn2" for j in range(cfg.layers_per_block + 1)
+                        for k in range(depth[i])]
+        out += [f"mid_block.attentions.0.transformer_blocks.{k}.attn2" for k in range(cfg.transformer_layers[-1])]
+        return out
 
     # ------------------------------------------------------------------------------ weights
     def _tensor(self, name: str, shape: tuple, kind: str = "weight"):
@@ -172,8 +189,16 @@ class UNet2D:
         q = self._linear(x, p + ".to_q", c, c, bias=False).view(b, t, heads, d).transpose(1, 2)
         k = self._linear(ctx, p + ".to_k", c, kdim, bias=False).view(b, ctx.shape[1], heads, d).transpose(1, 2)
         v = self._linear(ctx, p + ".to_v", c, kdim, bias=False).view(b, ctx.shape[1], heads, d).transpose(1, 2)
-        o = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, t, c)
-        return self._linear(o, p + ".to_out.0", c, c)
+        o = F.scaled_dot_product_attention(q, k, v)
+        ip = self._ip
+        if ip is not None and p in ip["layers"]:
+            # decoupled cross-attention: the same queries over keys / values projected from the image tokens
+            wk, wv = ip["layers"][p]
+            tok = ip["tokens"]
+            ik = F.linear(tok, wk).view(b, tok.shape[1], heads, d).transpose(1, 2)
+            iv = F.linear(tok, wv).view(b, tok.shape[1], heads, d).transpose(1, 2)
+            o = o + ip["scale"] * F.scaled_dot_product_attention(q, ik, iv)
+        return self._linear(o.transpose(1, 2).reshape(b, t, c), p + ".to_out.0", c, c)
 
     def _transformer(self, x, context, p: str, c: int, heads: int, depth: int):
         cfg = self.cfg
@@ -199,17 +224,9 @@ class UNet2D:
         return y + res
 
     # ------------------------------------------------------------------------------ forward
-    @torch.no_grad()
-    def forward(self, latents: torch.Tensor, timestep: torch.Tensor, context: torch.Tensor,
-                pooled: Optional[torch.Tensor] = None, time_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """latents [B, C, h, w], timestep [B] (or scalar), context [B, L, cross_attention_dim]; SDXL also takes
-        ``pooled`` [B, P] and ``time_ids`` [B, 6] (original size, crop offset, target size). Returns the
-        prediction [B, C, h, w] in fp32."""
+    def _embedding(self, b: int, timestep, pooled, time_ids) -> torch.Tensor:
         cfg = self.cfg
         ch = cfg.block_out_channels
-        x = latents.to(self.device).to(self.dtype)
-        b = x.shape[0]
-        context = context.to(self.device).to(self.dtype)
         t = torch.as_tensor(timestep, dtype=torch.float32, device=self.device).reshape(-1).expand(b)
         te = cfg.time_embed_dim
         emb = self._linear(sinusoid(t, ch[0]).to(self.dtype), "time_embedding.linear_1", te, ch[0])
@@ -222,9 +239,15 @@ class UNet2D:
             assert add.shape[-1] == cfg.addition_embed_dim, (add.shape, cfg.addition_embed_dim)
             a = self._linear(add, "add_embedding.linear_1", te, cfg.addition_embed_dim)
             emb = emb + self._linear(F.silu(a), "add_embedding.linear_2", te, te)
-        emb_act = F.silu(emb)
+        return F.silu(emb)
 
+    def _down_and_mid(self, x, emb_act, context, after_conv_in: Optional[torch.Tensor] = None):
+        """conv_in, the down blocks and the middle block: (skips as (tensor, channels), middle output)."""
+        cfg = self.cfg
+        ch = cfg.block_out_channels
         x = self._conv(x, "conv_in", ch[0], cfg.in_channels, 3)
+        if after_conv_in is not None:
+            x = x + after_conv_in
         skips = [(x, ch[0])]
         prev = ch[0]
         for i, c in enumerate(ch):
@@ -241,17 +264,109 @@ class UNet2D:
         x = self._resnet(x, emb_act, "mid_block.resnets.0", top, top)
         x = self._transformer(x, context, "mid_block.attentions.0", top, cfg.num_heads[-1], cfg.transformer_layers[-1])
         x = self._resnet(x, emb_act, "mid_block.resnets.1", top, top)
-        rev = list(reversed(ch))
-        heads, depth = list(reversed(cfg.num_heads)), list(reversed(cfg.transformer_layers))
-        prev = top
-        for i, c in enumerate(rev):
-            for j in range(cfg.layers_per_block + 1):
-                skip, sc = skips.pop()
-                x = self._resnet(torch.cat([x, skip], 1), emb_act, f"up_blocks.{i}.resnets.{j}", prev + sc, c)
-                prev = c
-                if cfg.up_attention[i]:
-                    x = self._transformer(x, context, f"up_blocks.{i}.attentions.{j}", c, heads[i], depth[i])
-            if i < len(rev) - 1:
-                x = self._conv(F.interpolate(x, scale_factor=2.0, mode="nearest"), f"up_blocks.{i}.upsamplers.0.conv", c, c, 3)
+        return skips, x
+
+    @torch.no_grad()
+    def forward(self, latents: torch.Tensor, timestep: torch.Tensor, context: torch.Tensor,
+                pooled: Optional[torch.Tensor] = None, time_ids: Optional[torch.Tensor] = None,
+                down_residuals: Optional[list] = None, mid_residual: Optional[torch.Tensor] = None,
+                image_tokens: Optional[torch.Tensor] = None, image_scale: float = 1.0) -> torch.Tensor:
+        """latents [B, C, h, w], timestep [B] (or scalar), context [B, L, cross_attention_dim]; SDXL also takes
+        ``pooled`` [B, P] and ``time_ids`` [B, 6] (original size, crop offset, target size). ``down_residuals`` /
+        ``mid_residual`` (a ControlNet's outputs) are added to the skip connections and the middle block's
+        output; ``image_tokens`` [B, n, cross_attention_dim] go through the image adapter installed with
+        :func:`install_ip_adapter`. Returns the prediction [B, C, h, w] in fp32."""
+        cfg = self.cfg
+        ch = cfg.block_out_channels
+        x = latents.to(self.device).to(self.dtype)
+        b = x.shape[0]
+        context = context.to(self.device).to(self.dtype)
+        emb_act = self._embedding(b, timestep, pooled, time_ids)
+        if self._ip is not None:
+            self._ip["tokens"] = None if image_tokens is None else image_tokens.to(self.device).to(self.dtype)
+            self._ip["scale"] = float(image_scale)
+        ip_saved = self._ip
+        if image_tokens is None:
+            self._ip = None
+        try:
+            skips, x = self._down_and_mid(x, emb_act, context)
+            if down_residuals is not None:
+                if len(down_residuals) != len(skips):
+                    raise ValueError(f"{len(down_residuals)} residuals for {len(skips)} skip connections")
+                skips = [(s + r.to(s.dtype), c) for (s, c), r in zip(skips, down_residuals)]
+            if mid_residual is not None:
+                x = x + mid_residual.to(x.dtype)
+            top = ch[-1]
+            rev = list(reversed(ch))
+            heads, depth = list(reversed(cfg.num_heads)), list(reversed(cfg.transformer_layers))
+            prev = top
+            for i, c in enumerate(rev):
+                for j in range(cfg.layers_per_block + 1):
+                    skip, sc = skips.pop()
+                    x = self._resnet(torch.cat([x, skip], 1), emb_act, f"up_blocks.{i}.resnets.{j}", prev + sc, c)
+                    prev = c
+                    if cfg.up_attention[i]:
+                        x = self._transformer(x, context, f"up_blocks.{i}.attentions.{j}", c, heads[i], depth[i])
+                if i < len(rev) - 1:
+                    x = self._conv(F.interpolate(x, scale_factor=2.0, mode="nearest"), f"up_blocks.{i}.upsamplers.0.conv", c, c, 3)
+        finally:
+            self._ip = ip_saved
         x = F.silu(self._gn(x, "conv_norm_out", ch[0]))
         return self._conv(x, "conv_out", cfg.out_channels, ch[0], 3).float()
+
+
+class ControlNet(UNet2D):
+    """The U-Net's encoder half run on the same latents plus a conditioning picture: the picture [B, 3, 8h, 8w]
+    goes through a small strided convolution stack (16, 32, 96, 256 channels, three stride-2 steps) and is added
+    after ``conv_in``; every skip connection and the middle output pass through a zero-initialised 1 x 1
+    convolution and are returned, scaled, for :meth:`UNet2D.forward` to add. Weights by the diffusers names
+    (``controlnet_cond_embedding.*``, ``controlnet_down_blocks.N``, ``controlnet_mid_block``). Reference:
+    src/HartsyInference.Diffusion/Adapters/ (ControlNet for U-Net models)."""
+
+    HINT_CHANNELS = (16, 32, 96, 256)
+
+    def _hint(self, cond: torch.Tensor) -> torch.Tensor:
+        hc = self.HINT_CHANNELS
+        p = "controlnet_cond_embedding"
+        x = F.silu(self._conv(cond, p + ".conv_in", hc[0], cond.shape[1], 3))
+        k = 0
+        for i in range(len(hc) - 1):
+            x = F.silu(self._conv(x, f"{p}.blocks.{k}", hc[i], hc[i], 3))
+            x = F.silu(self._conv(x, f"{p}.blocks.{k + 1}", hc[i + 1], hc[i], 3, stride=2))
+            k += 2
+        return self._conv(x, p + ".conv_out", self.cfg.block_out_channels[0], hc[-1], 3)
+
+    @torch.no_grad()
+    def forward(self, latents, timestep, context, cond: torch.Tensor, pooled=None, time_ids=None, scale: float = 1.0):
+        """-> (down residuals, one per skip connection; middle residual), each already multiplied by ``scale``."""
+        x = latents.to(self.device).to(self.dtype)
+        emb_act = self._embedding(x.shape[0], timestep, pooled, time_ids)
+        hint = self._hint(cond.to(self.device).to(self.dtype))
+        skips, mid = self._down_and_mid(x, emb_act, context.to(self.device).to(self.dtype), after_conv_in=hint)
+        down = [self._conv(s, f"controlnet_down_blocks.{i}", c, c, 1) * scale for i, (s, c) in enumerate(skips)]
+        top = self.cfg.block_out_channels[-1]
+        return down, self._conv(mid, "controlnet_mid_block", top, top, 1) * scale
+
+
+def install_ip_adapter(unet: UNet2D, get: Callable[[str], Optional[torch.Tensor]]) -> Callable[[torch.Tensor], torch.Tensor]:
+    """Attaches an image-prompt adapter (``ip_adapter.N.to_k_ip / to_v_ip`` per cross-attention layer, N = 2 i + 1 in
+    the adapters' layer order; ``image_proj.proj`` + ``image_proj.norm``) to ``unet``. Returns the projector:
+    CLIP image embedding [B, E] -> image tokens [B, n, cross_attention_dim] for ``forward(image_tokens=...)``.
+    Reference: src/HartsyInference.Diffusion/Adapters/ (IP-Adapter)."""
+    layers = {}
+    for i, path in enumerate(unet.cross_attention_paths()):
+        wk, wv = get(f"ip_adapter.{2 * i + 1}.to_k_ip.weight"), get(f"ip_adapter.{2 * i + 1}.to_v_ip.weight")
+        if wk is None or wv is None:
+            raise KeyError(f"ip_adapter.{2 * i + 1}.to_k_ip.weight")
+        layers[path] = (wk.to(unet.device).to(unet.dtype), wv.to(unet.device).to(unet.dtype))
+    unet._ip = {"layers": layers, "tokens": None, "scale": 1.0}
+    pw, pb = get("image_proj.proj.weight").to(unet.device).float(), get("image_proj.proj.bias").to(unet.device).float()
+    nw, nb = get("image_proj.norm.weight").to(unet.device).float(), get("image_proj.norm.bias").to(unet.device).float()
+    dim = unet.cfg.cross_attention_dim
+
+    def project(image_embeds: torch.Tensor) -> torch.Tensor:
+        e = image_embeds.to(unet.device).float()
+        tok = F.linear(e, pw, pb).view(e.shape[0], -1, dim)
+        return F.layer_norm(tok, (dim,), nw, nb).to(unet.dtype)
+
+    return project

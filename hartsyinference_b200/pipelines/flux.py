@@ -50,6 +50,8 @@ class FluxComponents:
     controlnet: Optional[object] = None       # FluxControlNet: residuals from a control image's latents
     t5_tokenizer: Optional[object] = None
     clip_tokenizer: Optional[object] = None
+    redux: Optional[object] = None            # models.dit.redux.ReduxImageEncoder
+    image_states: Optional[Callable] = None   # picture -> SigLIP patch states [n, 1152]
 
 
 class FluxPipeline:
@@ -302,6 +304,13 @@ class FluxPipeline:
         seed = req.seed if req.seed is not None else int(time.time() * 1000) % (2 ** 31)
         ctx, pooled = self.encode_prompt(req.prompt)
         neg = self.encode_prompt(req.negative_prompt) if req.cfg_scale > 1.0 else None
+        if getattr(req, "image_prompt", None) is not None:
+            if self.c.redux is None or self.c.image_states is None:
+                raise ValueError("a picture prompt needs the Redux projector and its image encoder beside the model")
+            tokens = self.c.redux(self.c.image_states(req.image_prompt), float(getattr(req, "image_prompt_scale", 1.0)))
+            ctx = torch.cat([ctx.to(tokens.device), tokens.to(ctx.dtype)], 0)
+            if neg is not None:                   # the unconditional branch sees as many (empty) picture tokens
+                neg = (torch.cat([neg[0].to(tokens.device), torch.zeros_like(tokens).to(neg[0].dtype)], 0), neg[1])
         t0 = time.perf_counter()
         init_latents = mask = None
         if req.init_image is not None:
