@@ -250,6 +250,55 @@ class _Detector:
                                                antialias=True)[0].clamp(0, 1)
 
 
+class _GroundedDetector:
+    """Grounding DINO: the queries are joined into one caption ("a cat . a remote control .") and every detection is
+    labelled with the phrase whose tokens it matched best."""
+
+    MEAN, STD = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
+
+    def __init__(self, path: str, raw: dict, device):
+        from ..assets.tokenizer import WordPieceTokenizer
+        from ..models.vision.grounding_dino import GroundingDino, GroundingDinoConfig
+        self.model = GroundingDino(GroundingDinoConfig.from_hf(raw), ShardedCheckpoint(path).get, device,
+                                   torch.bfloat16 if str(device).startswith("cuda") else torch.float32)
+        self.tokenizer = WordPieceTokenizer.from_dir(path)
+        self.short_side = int(raw.get("short_side", 800))
+
+    def detect(self, images: list, texts: list[str], threshold: float, iou: float) -> list:
+        tok = self.tokenizer
+        ids, spans = [tok.cls_id], []
+        dot = tok.encode(".", add_special=False)
+        for t in texts:
+            piece = tok.encode(t.strip().lower().rstrip("."), add_special=False)
+            spans.append((len(ids), len(ids) + len(piece)))
+            ids += piece + dot
+        ids.append(tok.sep_id)
+        ids_t = torch.tensor(ids)
+        mean, std = torch.tensor(self.MEAN)[:, None, None], torch.tensor(self.STD)[:, None, None]
+        out = []
+        for im in images:
+            x = _as_chw(im)
+            h, w = x.shape[-2:]
+            scale = min(self.short_side / min(h, w), 1333 / max(h, w))
+            nh, nw = max(32, int(round(h * scale))), max(32, int(round(w * scale)))
+            x = torch.nn.functional.interpolate(x[None], size=(nh, nw), mode="bilinear", align_corners=False, antialias=scale < 1)[0]
+            logits, boxes = self.model.forward(((x - mean) / std)[None], ids_t)
+            probs = logits.sigmoid().cpu()
+            boxes = boxes.cpu()
+            per_phrase = torch.stack([probs[:, a:b].max(-1)[0] if b > a else torch.zeros(probs.shape[0]) for a, b in spans], 1)
+            score, which = per_phrase.max(-1)
+            corners = torch.stack([(boxes[:, 0] - boxes[:, 2] / 2) * w, (boxes[:, 1] - boxes[:, 3] / 2) * h,
+                                   (boxes[:, 0] + boxes[:, 2] / 2) * w, (boxes[:, 1] + boxes[:, 3] / 2) * h], 1)
+            found = []
+            for qi, label in enumerate(texts):
+                sel = ((which == qi) & (score >= threshold)).nonzero().flatten()
+                for k in nms(corners[sel], score[sel], iou):
+                    i = int(sel[k])
+                    found.append({"label": label, "score": float(score[i]), "box": [float(v) for v in corners[i]]})
+            out.append(sorted(found, key=lambda d_: -d_["score"]))
+        return out
+
+
 class _ClosedSetDetector:
     """RT-DETR: fixed label set from the checkpoint's ``id2label``; ``texts`` (optional) keep only the
     named labels."""
@@ -418,6 +467,8 @@ class VisionService:
                     self._loaded[path] = _Segmenter(path, raw, self.device)
                 elif mt in ("owlvit", "owlv2"):
                     self._loaded[path] = _Detector(path, raw, self.device)
+                elif mt in ("grounding-dino", "grounding_dino", "mm-grounding-dino"):
+                    self._loaded[path] = _GroundedDetector(path, raw, self.device)
                 elif mt in ("sam2", "sam2_video"):
                     self._loaded[path] = _PromptSegmenter(path, raw, self.device)
                 elif mt == "rt_detr":
@@ -437,13 +488,13 @@ class VisionService:
             if isinstance(m, (_ClosedSetDetector, _YoloDetector)):
                 out.detections = m.detect(req.images, req.texts, req.score_threshold, req.nms_iou)
                 return out
-            if not isinstance(m, _Detector):
+            if not isinstance(m, (_Detector, _GroundedDetector)):
                 raise ValueError("this checkpoint is not a detector")
             if not req.texts:
                 raise ValueError("detect needs at least one text query")
             out.detections = m.detect(req.images, req.texts, req.score_threshold, req.nms_iou)
             return out
-        if isinstance(m, (_Detector, _ClosedSetDetector, _YoloDetector)):
+        if isinstance(m, (_Detector, _GroundedDetector, _ClosedSetDetector, _YoloDetector)):
             raise ValueError("this checkpoint detects; use operation 'detect'")
         if req.operation == "segment" and isinstance(m, _PromptSegmenter):
             out.masks, out.mask_scores = m.segment(req.images, req.points, req.point_labels, req.boxes)
