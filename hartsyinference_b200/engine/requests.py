@@ -269,6 +269,7 @@ class VisionResult:
     masks: Optional[list] = None               # per image: float32 [n_texts, H, W] probabilities in [0, 1]
     detections: Optional[list] = None          # per image: [{"label", "score", "box": [x0, y0, x1, y1] in pixels}]
     mask_scores: Optional[list] = None         # promptable segmentation, per image: predicted IoU of every returned mask
+    labels: Optional[list] = None              # scene parsing, per image: names of the classes present (masks hold int64 label maps)
 
 
 @dataclass

@@ -250,6 +250,34 @@ class _Detector:
                                                antialias=True)[0].clamp(0, 1)
 
 
+class _SceneParser:
+    """UperNet: a class per pixel (ADE20K-style label sets from the checkpoint's ``id2label``)."""
+
+    MEAN, STD = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
+
+    def __init__(self, path: str, raw: dict, device):
+        from ..models.vision.upernet import UperNet, UperNetConfig
+        self.model = UperNet(UperNetConfig.from_hf(raw), ShardedCheckpoint(path).get, device,
+                             torch.bfloat16 if str(device).startswith("cuda") else torch.float32)
+        self.names = {int(k): str(v) for k, v in (raw.get("id2label") or {}).items()}
+        self.short_side = int(raw.get("short_side", 512))
+
+    def parse(self, images: list):
+        mean, std = torch.tensor(self.MEAN)[:, None, None], torch.tensor(self.STD)[:, None, None]
+        maps, names = [], []
+        for im in images:
+            x = _as_chw(im)
+            h, w = x.shape[-2:]
+            scale = self.short_side / min(h, w)
+            nh, nw = max(32, int(round(h * scale / 32)) * 32), max(32, int(round(w * scale / 32)) * 32)
+            y = torch.nn.functional.interpolate(x[None], size=(nh, nw), mode="bilinear", align_corners=False, antialias=scale < 1)[0]
+            logits = self.model.logits(((y - mean) / std)[None])
+            labels = torch.nn.functional.interpolate(logits, size=(h, w), mode="bilinear", align_corners=False)[0].argmax(0).cpu()
+            maps.append(labels)
+            names.append([self.names.get(int(i), str(int(i))) for i in labels.unique()])
+        return maps, names
+
+
 class _GroundedDetector:
     """Grounding DINO: the queries are joined into one caption ("a cat . a remote control .") and every detection is
     labelled with the phrase whose tokens it matched best."""
@@ -467,6 +495,8 @@ class VisionService:
                     self._loaded[path] = _Segmenter(path, raw, self.device)
                 elif mt in ("owlvit", "owlv2"):
                     self._loaded[path] = _Detector(path, raw, self.device)
+                elif mt == "upernet":
+                    self._loaded[path] = _SceneParser(path, raw, self.device)
                 elif mt in ("grounding-dino", "grounding_dino", "mm-grounding-dino"):
                     self._loaded[path] = _GroundedDetector(path, raw, self.device)
                 elif mt in ("sam2", "sam2_video"):
@@ -496,6 +526,11 @@ class VisionService:
             return out
         if isinstance(m, (_Detector, _GroundedDetector, _ClosedSetDetector, _YoloDetector)):
             raise ValueError("this checkpoint detects; use operation 'detect'")
+        if req.operation == "segment" and isinstance(m, _SceneParser):
+            out.masks, out.labels = m.parse(req.images)
+            return out
+        if isinstance(m, _SceneParser):
+            raise ValueError("this checkpoint labels every pixel; use operation 'segment'")
         if req.operation == "segment" and isinstance(m, _PromptSegmenter):
             out.masks, out.mask_scores = m.segment(req.images, req.points, req.point_labels, req.boxes)
             return out
