@@ -258,6 +258,11 @@ class VisionRequest:
     points: list = field(default_factory=list)        # per prompt: [[x, y], ...]
     point_labels: list = field(default_factory=list)  # per prompt: [1, 0, ...] (default: all foreground)
     boxes: list = field(default_factory=list)         # per prompt: [x0, y0, x1, y1]
+    # "annotate": control pictures for ControlNets. ``annotator``: "canny" / "tile" / "blur" (no model needed),
+    # "pose" (a pose checkpoint), "depth" (a depth checkpoint), "segmentation" (a scene-parsing checkpoint)
+    annotator: str = "canny"
+    canny_low: float = 100.0
+    canny_high: float = 200.0
 
 
 @dataclass
@@ -270,6 +275,7 @@ class VisionResult:
     detections: Optional[list] = None          # per image: [{"label", "score", "box": [x0, y0, x1, y1] in pixels}]
     mask_scores: Optional[list] = None         # promptable segmentation, per image: predicted IoU of every returned mask
     labels: Optional[list] = None              # scene parsing, per image: names of the classes present (masks hold int64 label maps)
+    control_images: Optional[list] = None      # annotate, per image: uint8 [H, W, 3]
 
 
 @dataclass

@@ -509,9 +509,45 @@ class VisionService:
                     self._loaded[path] = _ClipDual(path, self.device)
             return self._loaded[path]
 
+    def _annotate(self, spec: ModelSpec, req: VisionRequest) -> VisionResult:
+        from ..models.vision import annotators as A
+        out = VisionResult(control_images=[])
+        kind = req.annotator
+        if kind in ("canny", "tile", "blur"):
+            for im in req.images:
+                x = _as_chw(im)
+                if kind == "canny":
+                    e = A.canny(x, req.canny_low, req.canny_high)
+                    out.control_images.append((e[..., None].expand(-1, -1, 3) * 255).to(torch.uint8).contiguous())
+                else:
+                    y = A.pixelate(x) if kind == "tile" else A.tile_blur(x)
+                    out.control_images.append((y.clamp(0, 1) * 255).round().to(torch.uint8).permute(1, 2, 0).contiguous())
+            return out
+        if kind not in ("pose", "depth", "segmentation"):
+            raise ValueError(f"annotator '{kind}' is not built (canny, tile, blur, pose, depth and segmentation are)")
+        m = self._model(spec)
+        if kind == "pose":
+            if not isinstance(m, _YoloDetector) or m.cfg.task != "pose":
+                raise ValueError("the pose annotator needs a pose checkpoint")
+            found = m.detect(req.images, [], req.score_threshold, req.nms_iou)
+            for im, people in zip(req.images, found):
+                h, w = _image_hw(im)
+                out.control_images.append(A.render_pose([torch.tensor(p["keypoints"]) for p in people], h, w))
+        elif kind == "depth":
+            if not isinstance(m, _DepthEstimator):
+                raise ValueError("the depth annotator needs a depth checkpoint")
+            out.control_images = [A.depth_control(torch.as_tensor(d)) for d in m.depth(req.images, getattr(req, "short_side", 518))]
+        elif kind == "segmentation":
+            if not isinstance(m, _SceneParser):
+                raise ValueError("the segmentation annotator needs a scene-parsing checkpoint")
+            out.control_images = [A.label_palette(l) for l in m.parse(req.images)[0]]
+        return out
+
     def run(self, spec: ModelSpec, req: VisionRequest) -> VisionResult:
+        if req.operation == "annotate":
+            return self._annotate(spec, req)
         if req.operation not in ("embed", "depth", "segment", "detect"):
-            raise ValueError(f"vision operation '{req.operation}' is not built (embed, depth, segment and detect are)")
+            raise ValueError(f"vision operation '{req.operation}' is not built (embed, depth, segment, detect and annotate are)")
         m = self._model(spec)
         out = VisionResult()
         if req.operation == "detect":

@@ -536,10 +536,33 @@ def create_app(options: Optional[ServerOptions] = None, engine: Optional[Inferen
         vreq = VisionRequest(operation=body.get("operation", "embed"), images=images, texts=list(body.get("texts") or []),
                              score_threshold=float(body.get("score_threshold", 0.1)), nms_iou=float(body.get("nms_iou", 0.5)),
                              points=list(body.get("points") or []), point_labels=list(body.get("point_labels") or []),
-                             boxes=list(body.get("boxes") or []))
+                             boxes=list(body.get("boxes") or []), annotator=str(body.get("annotator", "canny")),
+                             canny_low=float(body.get("canny_low", 100.0)), canny_high=float(body.get("canny_high", 200.0)))
         with heavy_queue.slot():
             res = eng.vision.run(resolve(body.get("model"), Modality.VISION), vreq)
+
+        def png(array) -> str:
+            import io
+            from PIL import Image
+            buf = io.BytesIO()
+            Image.fromarray(array).save(buf, format="PNG")
+            return base64.b64encode(buf.getvalue()).decode()
+
+        if res.control_images is not None:
+            return {"control_images": [{"width": int(c.shape[1]), "height": int(c.shape[0]), "png_base64": png(c.numpy())}
+                                       for c in res.control_images]}
+        if res.labels is not None:
+            import numpy as np
+            return {"label_maps": [{"width": int(m.shape[1]), "height": int(m.shape[0]), "labels": names,
+                                    "png_base64": png(m.numpy().astype(np.uint8 if int(m.max()) < 256 else np.uint16))}
+                                   for m, names in zip(res.masks, res.labels)]}
         if res.detections is not None:
+            import numpy as np
+            for per_image in res.detections:
+                for det in per_image:
+                    if "mask" in det:                # instance masks travel as 1-bit PNGs
+                        mk = det.pop("mask")
+                        det["mask_png_base64"] = png((mk.numpy().astype(np.uint8) * 255))
             return {"detections": res.detections}
         if res.masks is not None:
             import io
