@@ -285,6 +285,48 @@ def speak(model, text, out, speed, device):
     click.echo(f"{out}: {res.seconds:.2f} s at {res.sample_rate} Hz")
 
 
+@cli.command()
+@click.argument("wav")
+@click.option("--out", default="fx.wav")
+@click.option("--op", "ops_", multiple=True, type=click.Choice(["normalize-peak", "normalize-rms", "trim", "resample", "pitch"]),
+              help="applied in the order given")
+@click.option("--peak", default=0.95, type=float)
+@click.option("--rms", default=0.1, type=float)
+@click.option("--rate", default=0, type=int, help="target rate of 'resample'")
+@click.option("--silence-db", default=-45.0, type=float, help="'trim': level under which the edges are cut")
+def fx(wav, out, ops_, peak, rms, rate, silence_db):
+    """Signal-processing effects on a WAV file: level normalisation, silence trimming, resampling, pitch contour
+    (the learned effects of the reference, stem separation and speech enhancement, are not built)."""
+    from ..audio import read_wav, write_wav
+    from ..audio import dsp
+    from ..audio.wav import resample
+    x, sr = read_wav(wav)
+    x = x.mean(0) if x.dim() > 1 else x
+    for op in ops_ or ("normalize-peak",):
+        if op == "normalize-peak":
+            x = dsp.normalize_peak(x, peak)
+        elif op == "normalize-rms":
+            x = dsp.normalize_rms(x, rms, peak)
+        elif op == "resample":
+            if rate <= 0:
+                raise click.UsageError("'resample' needs --rate")
+            x, sr = resample(x, sr, rate), rate
+        elif op == "trim":
+            frame = max(1, sr // 100)
+            level = x[:x.numel() // frame * frame].view(-1, frame).pow(2).mean(1).clamp_min(1e-12).log10() * 10
+            loud = (level > silence_db).nonzero().flatten()
+            if loud.numel():
+                x = x[max(0, (int(loud[0]) - 5) * frame):min(x.numel(), (int(loud[-1]) + 6) * frame)]
+        elif op == "pitch":
+            x16 = resample(x, sr, 16000) if sr != 16000 else x
+            f0 = dsp.estimate_f0(x16, 16000, 320)
+            voiced = f0[f0 > 0]
+            click.echo(f"pitch: {voiced.numel()}/{f0.numel()} voiced frames" +
+                       (f", median {float(voiced.median()):.1f} Hz, range {float(voiced.min()):.1f}-{float(voiced.max()):.1f} Hz" if voiced.numel() else ""))
+    write_wav(out, x.clamp(-1, 1), sr)
+    click.echo(f"{out}: {x.numel() / sr:.2f} s at {sr} Hz")
+
+
 @cli.command(name="wake-listen")
 @click.argument("models_dir")
 @click.option("--host", default="127.0.0.1")
