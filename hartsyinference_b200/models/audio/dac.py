@@ -53,9 +53,13 @@ def snake(x: torch.Tensor, alpha: torch.Tensor) -> torch.Tensor:
 
 
 class DacCodec:
-    def __init__(self, cfg: DacConfig, get: Callable[[str], Optional[torch.Tensor]], device="cpu"):
+    def __init__(self, cfg: DacConfig, get: Callable[[str], Optional[torch.Tensor]], device="cpu", final_tanh: bool = True,
+                 odd_stride_padding: bool = False):
+        """``final_tanh`` False and ``odd_stride_padding`` True give the decoder variant X-Codec uses (no output
+        squashing; transposed convolutions of odd stride emit one more sample so that lengths stay multiples of the hop)."""
         self.cfg, self.device = cfg, torch.device(device)
         self._get, self._cache = get, {}
+        self.final_tanh, self.odd_stride_padding = final_tanh, odd_stride_padding
 
     def _w(self, name: str) -> torch.Tensor:
         """fp32 tensor ``name``; a weight-normalised convolution (g * v / |v| per output channel) is folded."""
@@ -87,10 +91,10 @@ class DacCodec:
 
     # ------------------------------------------------------------------------------------ parts
     @torch.no_grad()
-    def encode_latents(self, wave: torch.Tensor) -> torch.Tensor:
+    def encode_latents(self, wave: torch.Tensor, pad_to_hop: bool = True) -> torch.Tensor:
         """wave [B, samples] -> continuous latents [B, hidden, frames] (the input is zero-padded to a whole hop)."""
         x = wave.to(self.device).float()
-        x = F.pad(x, (0, (-x.shape[-1]) % self.cfg.hop))[:, None]
+        x = (F.pad(x, (0, (-x.shape[-1]) % self.cfg.hop)) if pad_to_hop else x)[:, None]
         x = self._conv(x, "encoder.conv1", padding=3)
         for i, s in enumerate(self.cfg.down):
             p = f"encoder.block.{i}"
@@ -132,11 +136,11 @@ class DacCodec:
         for i, s in enumerate(self.cfg.up):
             p = f"decoder.block.{i}"
             x = F.conv_transpose1d(snake(x, self._w(p + ".snake1.alpha")), self._w(p + ".conv_t1.weight"), self._w(p + ".conv_t1.bias"),
-                                   stride=s, padding=math.ceil(s / 2))
+                                   stride=s, padding=math.ceil(s / 2), output_padding=s % 2 if self.odd_stride_padding else 0)
             for j, dil in enumerate((1, 3, 9)):
                 x = self._res(x, f"{p}.res_unit{j + 1}", dil)
         x = self._conv(snake(x, self._w("decoder.snake1.alpha")), "decoder.conv2", padding=3)
-        return torch.tanh(x)[:, 0]
+        return (torch.tanh(x) if self.final_tanh else x)[:, 0]
 
     # ------------------------------------------------------------------------------------ public
     def encode(self, wave: torch.Tensor, n_codebooks: Optional[int] = None) -> torch.Tensor:

@@ -127,6 +127,12 @@ class Hubert:
         return x.transpose(1, 2)
 
     @torch.no_grad()
+    def all_hidden_states(self, wave: torch.Tensor) -> list:
+        """The input of the first block and the output of every block (the last one with the closing norm where the
+        model has one): ``layers + 1`` tensors [B, frames, hidden]. Codecs average these into a semantic feature."""
+        return [self.hidden_states(wave, layer=i) for i in range(self.cfg.layers)] + [self.hidden_states(wave)]
+
+    @torch.no_grad()
     def hidden_states(self, wave: torch.Tensor, layer: Optional[int] = None) -> torch.Tensor:
         """-> [B, frames, hidden] after ``layer`` transformer blocks (all of them, with the closing norm, when None)."""
         cfg = self.cfg
