@@ -223,7 +223,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / granitemoe / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / granitemoe / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / glm4_moe / dots1 / cwm / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -403,6 +403,18 @@ def from_hf_config(d: dict) -> TransformerConfig:
                               routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                               n_group=d.get("n_group", 1) or 1, topk_group=d.get("topk_group", 1) or 1,
                               use_correction_bias=(d.get("topk_method") or ("noaux_tc" if mt == "deepseek_v3" else "")) == "noaux_tc",
+                              first_dense_layers=d.get("first_k_dense_replace", 0))
+    if mt in ("glm4_moe", "dots1"):
+        # routed experts of the DeepSeek-V3 kind (sigmoid scores, selection bias, grouped top-k, shared experts, leading
+        # dense layers) on ordinary grouped-query attention with per-head q / k norms
+        kw["qk_norm"] = bool(d.get("use_qk_norm", mt == "dots1"))
+        kw["qkv_bias"] = bool(d.get("attention_bias", False))
+        kw["moe"] = MoeConfig(num_experts=d.get("n_routed_experts", 0), top_k=d.get("num_experts_per_tok", 0),
+                              expert_ffn=d.get("moe_intermediate_size", 0), num_shared_experts=d.get("n_shared_experts", 0) or 0,
+                              shared_ffn=d.get("moe_intermediate_size", 0), scoring="sigmoid",
+                              norm_topk_prob=bool(d.get("norm_topk_prob", True)),
+                              routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
+                              n_group=d.get("n_group", 1) or 1, topk_group=d.get("topk_group", 1) or 1, use_correction_bias=True,
                               first_dense_layers=d.get("first_k_dense_replace", 0))
     if mt == "gpt_oss":       # sink logits, biased projections, alternating windows, clamped-SwiGLU experts with biases
         ab = bool(d.get("attention_bias", True))

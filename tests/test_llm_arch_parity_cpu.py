@@ -66,6 +66,14 @@ ARCHS = {
     "olmo": ("OlmoConfig", dict()),
     "olmo3": ("Olmo3Config", dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
     "gptj": ("GPTJConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, rotary_dim=16)),
+    "deepseek_v2": ("DeepseekV2Config", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, q_lora_rank=64,
+                                             kv_lora_rank=512, qk_nope_head_dim=32, qk_rope_head_dim=64, v_head_dim=32, n_group=1,
+                                             topk_group=1, first_k_dense_replace=1, n_shared_experts=1, num_key_value_heads=4)),
+    "glm4_moe": ("Glm4MoeConfig", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, n_group=1, topk_group=1,
+                                       first_k_dense_replace=1, n_shared_experts=1, head_dim=32)),
+    "dots1": ("Dots1Config", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, n_group=1, topk_group=1,
+                                  first_k_dense_replace=1, n_shared_experts=1, head_dim=32)),
+    "cwm": ("CwmConfig", dict()),
     "deepseek_v3": ("DeepseekV3Config", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                                              q_lora_rank=64, kv_lora_rank=512, qk_nope_head_dim=32, qk_rope_head_dim=64,
                                              v_head_dim=32, n_group=2, topk_group=1, first_k_dense_replace=1,
