@@ -223,7 +223,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / granitemoe / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / glm4_moe / dots1 / cwm / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / granitemoe / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / glm4_moe / dots1 / ernie4_5_moe / hunyuan_v1_moe / cwm / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -416,6 +416,21 @@ def from_hf_config(d: dict) -> TransformerConfig:
                               routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)),
                               n_group=d.get("n_group", 1) or 1, topk_group=d.get("topk_group", 1) or 1, use_correction_bias=True,
                               first_dense_layers=d.get("first_k_dense_replace", 0))
+    if mt == "ernie4_5_moe":
+        # softmax scores, selection bias, renormalised top-k, shared experts; dense layers before ``moe_layer_start_index``
+        kw["rope_style"] = 1
+        shared = int(d.get("moe_num_shared_experts", 0) or 0)
+        kw["moe"] = MoeConfig(num_experts=d.get("moe_num_experts", 0), top_k=d.get("moe_k", 2), expert_ffn=d.get("moe_intermediate_size", 0),
+                              num_shared_experts=shared, shared_ffn=d.get("moe_intermediate_size", 0), scoring="softmax",
+                              norm_topk_prob=True, use_correction_bias=True, first_dense_layers=int(d.get("moe_layer_start_index", 0) or 0))
+    if mt == "hunyuan_v1_moe":
+        topk = d.get("moe_topk", 1)
+        shared = d.get("num_shared_expert", 1)
+        kw.update(qk_norm=bool(d.get("use_qk_norm", True)), qk_norm_after_rope=True)
+        kw["moe"] = MoeConfig(num_experts=d.get("num_experts", 0) if not isinstance(d.get("num_experts"), list) else d["num_experts"][0],
+                              top_k=topk[0] if isinstance(topk, list) else topk, expert_ffn=d.get("moe_intermediate_size") or d.get("intermediate_size", 0),
+                              num_shared_experts=shared[0] if isinstance(shared, list) else shared, shared_ffn=d.get("intermediate_size", 0),
+                              scoring="softmax", norm_topk_prob=True)
     if mt == "gpt_oss":       # sink logits, biased projections, alternating windows, clamped-SwiGLU experts with biases
         ab = bool(d.get("attention_bias", True))
         kw.update(qkv_bias=ab, o_bias=ab, attn_sinks=True, sliding_window=int(d.get("sliding_window") or 0),

@@ -238,7 +238,7 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
                 return torch.ones(hidden, dtype=torch.bfloat16)
             return t
         return g
-    if mt == "hunyuan_v1_dense":
+    if mt in ("hunyuan_v1_dense", "hunyuan_v1_moe"):
         def g(name: str):
             return get(name.replace("self_attn.q_norm", "self_attn.query_layernorm").replace("self_attn.k_norm", "self_attn.key_layernorm"))
         return g

@@ -367,8 +367,12 @@ class DecoderModel:
         mixtral = get(p + "block_sparse_moe.gate.weight") is not None
         base = p + ("block_sparse_moe." if mixtral else "mlp.")
         names = ("w1", "w3", "w2") if mixtral else ("gate_proj", "up_proj", "down_proj")
-        router = LinearWeight(need(base + "gate.weight").to(dt).to(self.device))
+        router_w = next((t for t in (get(base + n) for n in ("gate.weight", "gate.wg.weight", "router.weight")) if t is not None), None)
+        router = LinearWeight((router_w if router_w is not None else need(base + "gate.weight")).to(dt).to(self.device))
         bias = get(base + "gate.e_score_correction_bias")
+        if bias is None:
+            bias = get(base + "gate.moe_statics.e_score_correction_bias")
+            bias = None if bias is None else bias.reshape(-1)
         gus, dns = [], []
         stacked_gu, stacked_dn = get(base + "experts.gate_up_proj"), get(base + "experts.down_proj")
         for e in range(r * e_local, (r + 1) * e_local):
@@ -382,7 +386,7 @@ class DecoderModel:
         w = MoeWeights(router=router,
                        router_bias=None if bias is None else bias.float().contiguous().to(self.device),
                        gate_up=self._lw(torch.cat(gus)), down=self._lw(torch.cat(dns)))
-        for sp in ("shared_experts.", "shared_expert."):
+        for sp in ("shared_experts.", "shared_expert.", "shared_mlp."):
             sg = get(base + sp + "gate_proj.weight")
             if sg is None:
                 continue

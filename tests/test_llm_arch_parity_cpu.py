@@ -74,6 +74,9 @@ ARCHS = {
     "dots1": ("Dots1Config", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, n_group=1, topk_group=1,
                                   first_k_dense_replace=1, n_shared_experts=1, head_dim=32)),
     "cwm": ("CwmConfig", dict()),
+    "ernie4_5_moe": ("Ernie4_5_MoeConfig", dict(moe_num_experts=4, moe_k=2, moe_intermediate_size=64, head_dim=32, moe_layer_start_index=1,
+                                                moe_num_shared_experts=1)),
+    "hunyuan_v1_moe": ("HunYuanMoEV1Config", dict(num_experts=4, moe_topk=2, head_dim=32)),
     "deepseek_v3": ("DeepseekV3Config", dict(n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                                              q_lora_rank=64, kv_lora_rank=512, qk_nope_head_dim=32, qk_rope_head_dim=64,
                                              v_head_dim=32, n_group=2, topk_group=1, first_k_dense_replace=1,
@@ -105,6 +108,8 @@ def test_arch_matches_transformers(name, tmp_path):
     with torch.no_grad():
         for p in hf.parameters():            # default init is tiny; widen so that every branch matters
             if p.ndim >= 2:
+                if not bool(p.any()):         # a router the library leaves at zero: every expert would tie
+                    p.normal_(0, 0.02)
                 p.mul_(3.0)
             elif "norm" in "".join(n for n, q in hf.named_parameters() if q is p):
                 p.add_(torch.randn_like(p) * 0.1)
