@@ -223,7 +223,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / granitemoe / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / glm4_moe / dots1 / ernie4_5_moe / hunyuan_v1_moe / cwm / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / granitemoe / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / glm4_moe / dots1 / ernie4_5_moe / hunyuan_v1_moe / cwm / gpt_bigcode / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -237,7 +237,7 @@ def from_hf_config(d: dict) -> TransformerConfig:
         d = {**d, "num_hidden_layers": d["n_layer"], "num_attention_heads": d["n_head"], "intermediate_size": 4 * d["hidden_size"],
              "max_position_embeddings": d.get("seq_length", 2048), "hidden_act": "gelu_new", "rms_norm_eps": d.get("layer_norm_epsilon", 1e-5),
              "tie_word_embeddings": d.get("tie_word_embeddings", True)}
-    if mt == "gpt2":          # GPT-2 names its sizes differently
+    if mt in ("gpt2", "gpt_bigcode"):          # GPT-2 names its sizes differently
         d = {**d, "hidden_size": d["n_embd"], "num_hidden_layers": d["n_layer"], "num_attention_heads": d["n_head"],
              "max_position_embeddings": d.get("n_positions", 1024), "intermediate_size": d.get("n_inner") or 4 * d["n_embd"],
              "hidden_act": d.get("activation_function", "gelu_new"), "tie_word_embeddings": d.get("tie_word_embeddings", True)}
@@ -338,9 +338,10 @@ def from_hf_config(d: dict) -> TransformerConfig:
         kw.update(norm_type="layernorm", norm_bias=True, qkv_bias=bool(d.get("use_qkv_bias", False)),
                   parallel_residual=bool(d.get("use_parallel_residual", False)),
                   shared_parallel_norm=bool(d.get("use_parallel_residual", False)))
-    if mt == "gpt2":
+    if mt in ("gpt2", "gpt_bigcode"):
         kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=True, o_bias=True, ffn_bias=True,
-                  use_rope=False, learned_positions=True, num_kv_heads=heads)
+                  use_rope=False, learned_positions=True,
+                  num_kv_heads=1 if (mt == "gpt_bigcode" and d.get("multi_query", True)) else heads)
     if mt == "cohere2":
         kw.update(sliding_window=int(d.get("sliding_window") or 0), layer_types=tuple(d.get("layer_types") or ()),
                   sliding_window_pattern=int(d.get("sliding_window_pattern") or 4), nope_global=True)

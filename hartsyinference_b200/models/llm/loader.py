@@ -187,6 +187,31 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
                     return fused_rows(name, "gate_up_proj", part, gu)
             return None
         return g
+    if mt == "gpt_bigcode":
+        # GPT-2 names with ordinary [out, in] Linear weights; the fused projection is [hidden | k | v] with one shared
+        # key / value head when multi_query, else per head [q | k | v]
+        h = raw.get("n_embd", hidden)
+        ren = (("model.embed_tokens", "transformer.wte"), ("model.embed_positions", "transformer.wpe"),
+               ("model.norm", "transformer.ln_f"), ("model.layers", "transformer.h"), ("input_layernorm", "ln_1"),
+               ("post_attention_layernorm", "ln_2"), ("self_attn.o_proj", "attn.c_proj"), ("mlp.up_proj", "mlp.c_fc"),
+               ("mlp.down_proj", "mlp.c_proj"))
+        mq = bool(raw.get("multi_query", True))
+        hd = h // heads
+
+        def g(name: str):
+            for i, part in enumerate(("q_proj", "k_proj", "v_proj")):
+                if "self_attn." + part + "." in name:
+                    t = get(name.replace("model.layers", "transformer.h").replace("self_attn." + part, "attn.c_attn"))
+                    if t is None:
+                        return None
+                    if mq:
+                        return (t[:h] if i == 0 else t[h + (i - 1) * hd:h + i * hd]).contiguous()
+                    return t.reshape(heads, 3, hd, *t.shape[1:])[:, i].reshape(h, *t.shape[1:]).contiguous()
+            own = name
+            for std, o in ren:
+                own = own.replace(std, o)
+            return get(own)
+        return g
     if mt == "gpt2":
         h = raw.get("n_embd", hidden)
         ren = (("model.embed_tokens", "transformer.wte"), ("model.embed_positions", "transformer.wpe"),

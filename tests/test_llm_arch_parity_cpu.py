@@ -40,6 +40,8 @@ ARCHS = {
     "cohere": ("CohereConfig", dict()),
     "cohere2": ("Cohere2Config", dict(sliding_window=8, layer_types=["sliding_attention", "full_attention"])),
     "gpt2": ("GPT2Config", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256)),
+    "gpt_bigcode": ("GPTBigCodeConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256)),
+    "gpt_bigcode_mha": ("GPTBigCodeConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, multi_query=False)),
     "nemotron": ("NemotronConfig", dict()),
     "gpt_neox": ("GPTNeoXConfig", dict()),
     "phi": ("PhiConfig", dict()),
