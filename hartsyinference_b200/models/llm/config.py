@@ -223,7 +223,7 @@ def tiny(base: str = "qwen2.5-0.5b", **over: Any) -> TransformerConfig:
 
 def from_hf_config(d: dict) -> TransformerConfig:
     """Map a Hugging Face ``config.json`` (llama / mistral / qwen2 / qwen3 / gemma 1-3 / granite / olmo2 /
-    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / granitemoe / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / glm4_moe / dots1 / ernie4_5_moe / hunyuan_v1_moe / cwm / gpt_bigcode / mixtral /
+    phi3 / glm / glm4 / starcoder2 / stablelm / cohere / cohere2 / nemotron / gpt_neox / gpt2 / granitemoe / mllama (text) / qwen2_vl - qwen2_5_vl - qwen3_vl (text) / hunyuan_v1_dense / apertus / bloom / gpt_oss / gptj / opt / phi / olmo3 / exaone4 / helium / ernie4_5 / arcee / smollm3 / ministral / seed_oss / minicpm / internlm2 / deepseek_v2-v3 / glm4_moe / dots1 / ernie4_5_moe / hunyuan_v1_moe / cwm / gpt_bigcode / falcon / mixtral /
     olmoe / qwen2_moe / qwen3_moe families) onto :class:`TransformerConfig`."""
     mt = d.get("model_type", "llama")
     if mt == "opt":
@@ -369,6 +369,18 @@ def from_hf_config(d: dict) -> TransformerConfig:
     if mt == "bloom":         # LayerNorm blocks with biases everywhere, ALiBi instead of positions
         kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=True, o_bias=True, ffn_bias=True,
                   num_kv_heads=heads, use_rope=False, alibi=True, embed_norm=True)
+    if mt == "falcon":
+        # attention and MLP read the same residual stream in parallel (one shared LayerNorm, or ln_attn / ln_mlp in the
+        # 40B-class layout); multi-query or grouped keys / values; rotary (or ALiBi) positions; plain GELU MLP
+        new = bool(d.get("new_decoder_architecture", False))
+        bias = bool(d.get("bias", False))
+        kvh = (d.get("num_kv_heads") or heads) if new else (1 if d.get("multi_query", True) else heads)
+        parallel = bool(d.get("parallel_attn", True)) or new
+        kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=bias, o_bias=bias, ffn_bias=bias, num_kv_heads=kvh,
+                  parallel_residual=parallel, shared_parallel_norm=parallel and not (new and (d.get("num_ln_in_parallel_attn") or 2) == 2),
+                  activation="gelu", ffn_size=d.get("ffn_hidden_size") or 4 * hidden)
+        if d.get("alibi", False):
+            kw.update(use_rope=False, alibi=True)
     if mt == "gpt_neox":
         ab = bool(d.get("attention_bias", True))
         kw.update(norm_type="layernorm", norm_bias=True, gated_ffn=False, qkv_bias=ab, o_bias=ab, ffn_bias=True,

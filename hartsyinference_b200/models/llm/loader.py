@@ -343,6 +343,32 @@ def standard_names(get: Callable[[str], Optional[torch.Tensor]], raw: dict) -> C
                 name = name.replace(std, own)
             return get(name)
         return g
+    if mt == "falcon":
+        new = bool(raw.get("new_decoder_architecture", False))
+        two_norms = new and (raw.get("num_ln_in_parallel_attn") or 2) == 2
+        ren = (("model.embed_tokens", "transformer.word_embeddings"), ("model.norm", "transformer.ln_f"), ("model.layers", "transformer.h"),
+               ("self_attn.o_proj", "self_attention.dense"), ("mlp.up_proj", "mlp.dense_h_to_4h"), ("mlp.down_proj", "mlp.dense_4h_to_h")) + \
+              ((("input_layernorm", "ln_attn"), ("post_attention_layernorm", "ln_mlp")) if two_norms else ())
+        kvf = (raw.get("num_kv_heads") or heads) if new else (1 if raw.get("multi_query", True) else heads)
+        groups = heads // kvf
+
+        def g(name: str):
+            for i, part in enumerate(("q_proj", "k_proj", "v_proj")):
+                if "self_attn." + part + "." in name:
+                    t = get(name.replace("model.layers", "transformer.h").replace("self_attn." + part, "self_attention.query_key_value"))
+                    if t is None:
+                        return None
+                    if new:                                  # rows are [kv head][its q heads..., k, v][d]
+                        t = t.reshape(kvf, groups + 2, d, *t.shape[1:])
+                        sel = t[:, :groups] if i == 0 else t[:, groups + i - 1][:, None]
+                        return sel.reshape(-1, *t.shape[3:]).contiguous()
+                    if kvf == 1:                             # multi-query: [all q heads | k | v]
+                        return (t[:heads * d] if i == 0 else t[heads * d + (i - 1) * d:heads * d + i * d]).contiguous()
+                    return t.reshape(heads, 3, d, *t.shape[1:])[:, i].reshape(heads * d, *t.shape[1:]).contiguous()
+            for std, own in ren:
+                name = name.replace(std, own)
+            return get(name)
+        return g
     if mt == "gpt_neox":
         ren = (("model.embed_tokens", "gpt_neox.embed_in"), ("model.norm", "gpt_neox.final_layer_norm"),
                ("lm_head", "embed_out"), ("model.layers", "gpt_neox.layers"), ("self_attn.o_proj", "attention.dense"),

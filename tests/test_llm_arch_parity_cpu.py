@@ -42,6 +42,9 @@ ARCHS = {
     "gpt2": ("GPT2Config", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256)),
     "gpt_bigcode": ("GPTBigCodeConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256)),
     "gpt_bigcode_mha": ("GPTBigCodeConfig", dict(n_embd=128, n_layer=2, n_head=4, n_positions=256, multi_query=False)),
+    "falcon": ("FalconConfig", dict(new_decoder_architecture=False, multi_query=True, parallel_attn=True, bias=False, alibi=False)),
+    "falcon_grouped": ("FalconConfig", dict(new_decoder_architecture=True, num_kv_heads=2, parallel_attn=True, bias=False, alibi=False)),
+    "falcon_mha_bias": ("FalconConfig", dict(new_decoder_architecture=False, multi_query=False, parallel_attn=True, bias=True, alibi=False)),
     "nemotron": ("NemotronConfig", dict()),
     "gpt_neox": ("GPTNeoXConfig", dict()),
     "phi": ("PhiConfig", dict()),
